@@ -1,0 +1,100 @@
+"""Build the native libraries in-tree.
+
+Two shared objects are produced under ``fastllm_b200/lib``:
+
+* ``libfb_kernels.so`` -- every CUDA kernel, compiled for sm_100a only (``nvcc -gencode
+  arch=compute_100a,code=sm_100a``).  Plain ``extern "C"`` launchers, no libtorch dependency; Python
+  calls them through ctypes with raw device pointers and the current CUDA stream.
+* ``libfb_runtime.so`` -- the host runtime in C++ (paged-KV page manager with prefix trie, tokenizer,
+  chat-template engine, quantiser, CPU operator backend).
+
+Run ``python -m fastllm_b200.build`` (add ``--force`` to rebuild everything).  Objects are rebuilt only
+when a source or header is newer than the object.
+"""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+CSRC = ROOT / "csrc"
+LIB = ROOT / "lib"
+OBJ = ROOT / "_build"
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
+    "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v",
+]
+CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-fopenmp", "-march=x86-64-v3", "-Wall", "-Wno-unused-function"]
+
+
+def _newer(src: Path, deps: list[Path], out: Path) -> bool:
+    if not out.exists():
+        return True
+    t = out.stat().st_mtime
+    return any(d.stat().st_mtime > t for d in [src, *deps])
+
+
+def _run(cmd: list[str], log: Path | None = None) -> None:
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if log is not None:
+        log.write_text(r.stdout + r.stderr)
+    if r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError("build step failed: " + " ".join(cmd))
+
+
+def build_kernels(force: bool = False) -> Path:
+    OBJ.mkdir(exist_ok=True)
+    LIB.mkdir(exist_ok=True)
+    headers = sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
+    sources = sorted(CSRC.glob("*.cu"))
+    out = LIB / "libfb_kernels.so"
+    jobs = []
+    for src in sources:
+        obj = OBJ / (src.stem + ".o")
+        if force or _newer(src, headers, obj):
+            jobs.append((["nvcc", *NVCC_FLAGS, "-I", str(CSRC), "-c", str(src), "-o", str(obj)], OBJ / (src.stem + ".ptxas.log")))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
+            list(ex.map(lambda j: _run(*j), jobs))
+    objs = [OBJ / (s.stem + ".o") for s in sources]
+    if force or jobs or not out.exists():
+        _run(["nvcc", "-shared", "-o", str(out), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"])
+    return out
+
+
+def build_runtime(force: bool = False) -> Path:
+    OBJ.mkdir(exist_ok=True)
+    LIB.mkdir(exist_ok=True)
+    rt = CSRC / "runtime"
+    sources = sorted(rt.glob("*.cpp"))
+    headers = sorted(rt.glob("*.h"))
+    out = LIB / "libfb_runtime.so"
+    if not sources:
+        return out
+    jobs = []
+    for src in sources:
+        obj = OBJ / ("rt_" + src.stem + ".o")
+        if force or _newer(src, headers, obj):
+            jobs.append((["g++", *CXX_FLAGS, "-I", str(rt), "-c", str(src), "-o", str(obj)], None))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(len(jobs), os.cpu_count() or 4)) as ex:
+            list(ex.map(lambda j: _run(*j), jobs))
+    objs = [OBJ / ("rt_" + s.stem + ".o") for s in sources]
+    if force or jobs or not out.exists():
+        _run(["g++", "-shared", "-fopenmp", "-o", str(out), *map(str, objs), "-lpthread"])
+    return out
+
+
+def build_all(force: bool = False) -> None:
+    build_kernels(force)
+    build_runtime(force)
+
+
+if __name__ == "__main__":
+    build_all("--force" in sys.argv)
+    print("built:", *(p.name for p in sorted(LIB.glob("*.so"))))

@@ -1,0 +1,315 @@
+// Paged GQA decode attention for sm_100a (head_dim 128, page length 128, up to 16 query heads per KV head).
+//
+// One KV page (128 tokens of one KV head) is exactly one UMMA tile:
+//     S^T[128 tokens x G] = K_page[128 x 128] * Q^T        (A = K page, K-major, straight from the page pool by TMA)
+//     O^T[128 dims   x G] = V_page^T[128 x 128] * P^T      (A = V page read MN-major, B = P^T written by the softmax warps)
+// so the tensor core runs full 128-row MMAs although only G (<= 16) query rows exist.  Work items are
+// (request, page) pairs listed by a tiny plan kernel; CTAs stride over items x KV heads with a 3-stage
+// TMA ring, write un-normalised partial outputs + (max, sum) per item to scratch, and a combine kernel
+// merges the partials.  This is the split-KV structure of the reference's native paged fallback
+// (src/devices/cuda/attention/paged/fastllm-paged-attention-native.cu:1050-1562) mapped onto tcgen05;
+// the reference's main path is FlashInfer's mma.sync prefill kernel (fastllm-attention.cu:3032-3600).
+//
+// Page pools must be zero-initialised: the unused tail of a request's last page is multiplied by P = 0.
+#include "ptx.cuh"
+#include "tmap.h"
+
+FB_DEFINE_ERROR_API(attn_decode)
+
+namespace fb {
+
+constexpr int KID_ATTN_DECODE = 10;
+constexpr int AD_STAGES = 3;
+constexpr int AD_D = 128;
+constexpr int AD_PAGE = 128;
+constexpr int AD_NPAD = 16;
+constexpr int AD_K_BYTES = AD_PAGE * AD_D * 2;     // 32 KB
+constexpr int AD_Q_BYTES = AD_NPAD * AD_D * 2;     // 4 KB
+constexpr int AD_STAGE_BYTES = 2 * AD_K_BYTES + AD_Q_BYTES;   // K, V, Q
+constexpr int AD_P_BYTES = AD_NPAD * AD_PAGE * 2;  // 4 KB
+constexpr int AD_SMEM_BYTES = AD_STAGES * AD_STAGE_BYTES + AD_P_BYTES + 1024 /*barriers+red*/ + 1024 /*align*/;
+
+struct AttnDecodeParams {
+  const int* work;        // [n_work][2] = (request, page index within the request)
+  const int* n_work;      // device scalar
+  const int* page_table;  // [B, max_pages]
+  const int* seq_lens;    // [B]
+  float* part_o;          // [B, Hkv, max_splits, G, D]
+  float* part_ml;         // [B, Hkv, max_splits, G, 2]
+  int max_pages, max_splits, Hq, Hkv, G;
+  float scale_log2;       // softmax scale * log2(e)
+  uint32_t idesc_s, idesc_o;
+};
+
+// ---- plan: flatten (request, page) pairs ---------------------------------------------------------
+__global__ void attn_decode_plan_kernel(const int* __restrict__ seq_lens, int B, int* __restrict__ work, int* __restrict__ n_work,
+                                        int max_items) {
+  __shared__ int offs[1025];
+  // single CTA; B <= 1024
+  const int t = threadIdx.x;
+  int np = 0;
+  if (t < B) np = (seq_lens[t] + AD_PAGE - 1) / AD_PAGE;
+  offs[t + 1] = np;
+  if (t == 0) offs[0] = 0;
+  __syncthreads();
+  // inclusive scan (Hillis-Steele) over blockDim entries
+  for (int d = 1; d < blockDim.x; d <<= 1) {
+    int v = 0;
+    if (t >= d) v = offs[t + 1 - d];
+    __syncthreads();
+    if (t >= d) offs[t + 1] += v;
+    __syncthreads();
+  }
+  if (t < B) {
+    const int base = offs[t];
+    for (int i = 0; i < np; ++i)
+      if (base + i < max_items) { work[2 * (base + i)] = t; work[2 * (base + i) + 1] = i; }
+  }
+  if (t == 0) { const int total = offs[B]; *n_work = total < max_items ? total : max_items; }
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(192, 1)
+attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
+                   const __grid_constant__ CUtensorMap tmQ, const AttnDecodeParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* p_smem = smem + AD_STAGES * AD_STAGE_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + AD_P_BYTES);
+  uint64_t* full_k = bars;                  // [STAGES]  K + Q landed
+  uint64_t* full_v = bars + AD_STAGES;      // [STAGES]
+  uint64_t* empty = bars + 2 * AD_STAGES;   // [STAGES]
+  uint64_t* s_full = bars + 3 * AD_STAGES;
+  uint64_t* p_ready = s_full + 1;
+  uint64_t* o_full = s_full + 2;
+  uint64_t* o_empty = s_full + 3;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 4);
+  float* red_max = reinterpret_cast<float*>(tmem_slot + 4);      // [4 warps][16]
+  float* red_sum = red_max + 64;                                  // [2 parity][4 warps][16]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total = (*p.n_work) * p.Hkv;
+  bool dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < AD_STAGES; ++s) { mbar_init(&full_k[s], 1); mbar_init(&full_v[s], 1); mbar_init(&empty[s], 1); }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_full, 1);
+    mbar_init(o_empty, 128);
+    mbar_init_fence();
+    tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmQ);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 32); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_s = *tmem_slot;        // columns [0,16): S^T, [16,32): O^T
+  const uint32_t tmem_o = tmem_s + 16;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int it = 0;
+      for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
+        const int item = w / p.Hkv, kvh = w - item * p.Hkv;
+        const int b = p.work[2 * item], pg = p.work[2 * item + 1];
+        const int page = p.page_table[(size_t)b * p.max_pages + pg];
+        const int s = it % AD_STAGES;
+        const uint32_t ph = (uint32_t)(it / AD_STAGES) & 1u;
+        if (!mbar_wait(&empty[s], ph ^ 1u, dead, KID_ATTN_DECODE, 1)) break;
+        uint8_t* kb = smem + s * AD_STAGE_BYTES;
+        uint8_t* vb = kb + AD_K_BYTES;
+        uint8_t* qb = vb + AD_K_BYTES;
+        mbar_expect_tx(&full_k[s], AD_K_BYTES + AD_Q_BYTES);
+        tma_load_2d(kb, &tmK, &full_k[s], kvh * AD_D, page * AD_PAGE);
+        tma_load_2d(kb + AD_K_BYTES / 2, &tmK, &full_k[s], kvh * AD_D + 64, page * AD_PAGE);
+        tma_load_2d(qb, &tmQ, &full_k[s], 0, b * p.Hq + kvh * p.G);
+        tma_load_2d(qb + AD_Q_BYTES / 2, &tmQ, &full_k[s], 64, b * p.Hq + kvh * p.G);
+        mbar_expect_tx(&full_v[s], AD_K_BYTES);
+        tma_load_2d(vb, &tmV, &full_v[s], kvh * AD_D, page * AD_PAGE);
+        tma_load_2d(vb + AD_K_BYTES / 2, &tmV, &full_v[s], kvh * AD_D + 64, page * AD_PAGE);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      int it = 0;
+      for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
+        const int s = it % AD_STAGES;
+        const uint32_t ph = (uint32_t)(it / AD_STAGES) & 1u;
+        const uint32_t iph = (uint32_t)it & 1u;
+        const uint32_t kb = smem_u32(smem + s * AD_STAGE_BYTES);
+        const uint32_t vb = kb + AD_K_BYTES, qb = vb + AD_K_BYTES;
+        if (!mbar_wait(&full_k[s], ph, dead, KID_ATTN_DECODE, 2)) break;
+        tc_fence_after_sync();
+        // S^T = K * Q^T : K-major operands, 128-byte swizzle; d 0..63 in the first half tile, 64..127 in the second
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t da = make_smem_desc(kb + (k >> 2) * (AD_K_BYTES / 2) + (k & 3) * 32, 16, 1024, SWZ_128B);
+          const uint64_t db = make_smem_desc(qb + (k >> 2) * (AD_Q_BYTES / 2) + (k & 3) * 32, 16, 1024, SWZ_128B);
+          umma_f16(tmem_s, da, db, p.idesc_s, k != 0 ? 1u : 0u);
+        }
+        umma_commit(s_full);
+        if (!mbar_wait(p_ready, iph, dead, KID_ATTN_DECODE, 3)) break;
+        if (!mbar_wait(&full_v[s], ph, dead, KID_ATTN_DECODE, 4)) break;
+        if (it > 0 && !mbar_wait(o_empty, iph ^ 1u, dead, KID_ATTN_DECODE, 5)) break;
+        tc_fence_after_sync();
+        // O^T = V^T * P^T : A = V page read MN-major (dims contiguous), 16 tokens per MMA;
+        // B = P^T [16 x 128 tokens] in the un-swizzled core-matrix layout written by the softmax warps.
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint64_t da = make_smem_desc(vb + k * 2048, AD_K_BYTES / 2, 1024, SWZ_128B);
+          const uint64_t db = make_smem_desc(smem_u32(p_smem) + k * 512, 256, 128, SWZ_NONE);
+          umma_f16(tmem_o, da, db, p.idesc_o, k != 0 ? 1u : 0u);
+        }
+        umma_commit(o_full);
+        umma_commit(&empty[s]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;                // TMEM lane quarter
+    const int t = q * 32 + lane;           // token within page (softmax) / head dim (epilogue)
+    const int G = p.G;
+    int it = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
+      const int item = w / p.Hkv, kvh = w - item * p.Hkv;
+      const int b = p.work[2 * item], pg = p.work[2 * item + 1];
+      const int seq = p.seq_lens[b];
+      const uint32_t iph = (uint32_t)it & 1u;
+      const bool valid = pg * AD_PAGE + t < seq;
+      mbar_wait(s_full, iph, dead, KID_ATTN_DECODE, 6);
+      tc_fence_after_sync();
+      uint32_t r[16];
+      tmem_ld_32x32b_x16(tmem_s + ((uint32_t)(q * 32) << 16), r);
+      tmem_ld_wait();
+      float sv[16];
+#pragma unroll
+      for (int h = 0; h < 16; ++h) sv[h] = (valid && h < G) ? __uint_as_float(r[h]) * p.scale_log2 : -INFINITY;
+#pragma unroll
+      for (int h = 0; h < 16; ++h) {
+        float m = sv[h];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) red_max[q * 16 + h] = m;
+      }
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");
+      float mx[16];
+#pragma unroll
+      for (int h = 0; h < 16; ++h)
+        mx[h] = fmaxf(fmaxf(red_max[h], red_max[16 + h]), fmaxf(red_max[32 + h], red_max[48 + h]));
+      // P^T[n][t] in the K-major core-matrix layout: ((t/8)*2 + n/8)*128 + (n%8)*16 + (t%8)*2 bytes
+      uint8_t* pb = p_smem + (t >> 3) * 256 + (t & 7) * 2;
+      float* rs = red_sum + iph * 64;
+#pragma unroll
+      for (int h = 0; h < 16; ++h) {
+        float pv = 0.f;
+        if (h < G && valid) pv = exp2f(sv[h] - mx[h]);
+        const uint16_t bits = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(pv)) : __half_as_ushort(__float2half_rn(pv));
+        *reinterpret_cast<uint16_t*>(pb + (h >> 3) * 128 + (h & 7) * 16) = bits;
+        // sum what the tensor core will actually see
+        float pr = BF16 ? __bfloat162float(__ushort_as_bfloat16(bits)) : __half2float(__ushort_as_half(bits));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
+        if (lane == 0) rs[q * 16 + h] = pr;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before_sync();
+      mbar_arrive(p_ready);
+      // ---- epilogue: O^T lanes = head dims ----
+      mbar_wait(o_full, iph, dead, KID_ATTN_DECODE, 7);
+      tc_fence_after_sync();
+      tmem_ld_32x32b_x16(tmem_o + ((uint32_t)(q * 32) << 16), r);
+      tmem_ld_wait();
+      tc_fence_before_sync();
+      mbar_arrive(o_empty);
+      const size_t slot = ((size_t)(b * p.Hkv + kvh) * p.max_splits + pg) * G;
+      float* po = p.part_o + slot * AD_D + t;
+#pragma unroll
+      for (int h = 0; h < 16; ++h)
+        if (h < G) po[(size_t)h * AD_D] = __uint_as_float(r[h]);
+      if (t < G) {
+        const float l = rs[t] + rs[16 + t] + rs[32 + t] + rs[48 + t];
+        p.part_ml[(slot + t) * 2] = mx[t];
+        p.part_ml[(slot + t) * 2 + 1] = l;
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_s, 32);
+}
+
+// ---- combine: one CTA per (request, query head), 128 threads = head dims --------------------------
+template <bool BF16>
+__global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                           const int* __restrict__ seq_lens, uint16_t* __restrict__ out, int ld_out, int Hq,
+                                           int Hkv, int G, int max_splits) {
+  const int b = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
+  const int kvh = hq / G, g = hq - kvh * G;
+  const int seq = seq_lens[b];
+  const int ns = (seq + AD_PAGE - 1) / AD_PAGE;
+  const size_t base = (size_t)(b * Hkv + kvh) * max_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[((base + s) * G + g) * 2]);
+  float acc = 0.f, L = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    const size_t sl = (base + s) * G + g;
+    const float wgt = exp2f(part_ml[sl * 2] - M);
+    L += part_ml[sl * 2 + 1] * wgt;
+    acc += part_o[sl * AD_D + d] * wgt;
+  }
+  const float o = ns > 0 ? acc / L : 0.f;
+  uint16_t bits = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
+  out[(size_t)b * ld_out + (size_t)hq * AD_D + d] = bits;
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n_work, int max_items, void* stream) {
+  if (B <= 0 || B > 1024) return -1;
+  int threads = 32;
+  while (threads < B) threads <<= 1;
+  attn_decode_plan_kernel<<<1, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(seq_lens, B, work, n_work, max_items);
+  return (int)cudaGetLastError();
+}
+
+// Scratch sizes (floats): part_o = B*Hkv*max_splits*G*128, part_ml = B*Hkv*max_splits*G*2.
+// q: [B, Hq, 128] with row stride ld_q elements between requests' heads packed (ld_q == Hq*128 required).
+// k_pool/v_pool: [num_slots, Hkv, 128].  dtype: 0 = fp16, 1 = bf16.
+extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
+                              const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
+                              int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, float scale,
+                              int dtype, int grid_ctas, void* stream_) {
+  if (B <= 0) return 0;
+  if (D != AD_D || Hq % Hkv != 0) return -1;
+  const int G = Hq / Hkv;
+  if (G > AD_NPAD) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  CUtensorMap tmK, tmV, tmQ;
+  if (!make_tmap_2d(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 64, 2, 3)) return -2;
+  AttnDecodeParams p;
+  p.work = work; p.n_work = n_work; p.page_table = page_table; p.seq_lens = seq_lens; p.part_o = part_o; p.part_ml = part_ml;
+  p.max_pages = max_pages; p.max_splits = max_splits; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const uint32_t f = dtype == 1 ? 1u : 0u;
+  p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);
+  p.idesc_o = make_idesc(f, f, 1, 0, 128, AD_NPAD);
+  if (grid_ctas <= 0) grid_ctas = 148;
+  if (dtype == 1) {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM_BYTES); cfg = true; }
+    attn_decode_kernel<true><<<grid_ctas, 192, AD_SMEM_BYTES, stream>>>(tmK, tmV, tmQ, p);
+    attn_decode_combine_kernel<true><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM_BYTES); cfg = true; }
+    attn_decode_kernel<false><<<grid_ctas, 192, AD_SMEM_BYTES, stream>>>(tmK, tmV, tmQ, p);
+    attn_decode_combine_kernel<false><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits);
+  }
+  return (int)cudaGetLastError();
+}

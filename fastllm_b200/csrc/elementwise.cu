@@ -1,0 +1,460 @@
+// Bandwidth-bound row kernels for sm_100a: RMSNorm (+ residual), fused QKV post-processing
+// (per-head RMSNorm + RoPE + paged-KV append), SiLU-mul, embedding gather, greedy arg-max, top-k router.
+// All use 128-bit global accesses and fp32 math.
+//
+// Reference behaviour reproduced here:
+//   RMSNorm                              src/devices/cuda/fastllm-cuda.cu:2733-3085
+//   QKVRMSNormRopeSplitAppendPagedCache  src/devices/cuda/fastllm-cuda.cu:12190
+//   Swiglu                               src/devices/cuda/fastllm-cuda.cu:1704-1727
+//   greedy sampling                      src/devices/cuda/fastllm-cuda.cu:13579-13784
+//   SelectExpert                         src/devices/cpu/cpudevice.cpp:8885-8955
+#include "ptx.cuh"
+
+FB_DEFINE_ERROR_API(elementwise)
+
+namespace fb {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float block_sum(float v, float* sh) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  if (l == 0) sh[w] = v;
+  __syncthreads();
+  float t = l < nw ? sh[l] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+// ------------------------------------------------------------------------------------------------
+// RMSNorm:  if residual != nullptr:  residual = residual + x (written back), y = norm(residual) * w
+//           else                      y = norm(x) * w.        One CTA per row, H % 8 == 0.
+// `unit_offset` adds 1 to the weight (Gemma convention).
+// ------------------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
+                               uint16_t* residual, int H, int ldx, int ldy, float eps, float unit_offset) {
+  __shared__ float sh[32];
+  extern __shared__ float rowbuf[];   // H floats
+  const int row = blockIdx.x;
+  const uint4* xp = reinterpret_cast<const uint4*>(x + (size_t)row * ldx);
+  uint4* rp = residual ? reinterpret_cast<uint4*>(residual + (size_t)row * H) : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    uint4 v = xp[i];
+    float2 a = unpack_16<BF16>(v.x), b = unpack_16<BF16>(v.y), c = unpack_16<BF16>(v.z), d = unpack_16<BF16>(v.w);
+    if (rp) {
+      uint4 r = rp[i];
+      float2 ra = unpack_16<BF16>(r.x), rb = unpack_16<BF16>(r.y), rc = unpack_16<BF16>(r.z), rd = unpack_16<BF16>(r.w);
+      a.x += ra.x; a.y += ra.y; b.x += rb.x; b.y += rb.y; c.x += rc.x; c.y += rc.y; d.x += rd.x; d.y += rd.y;
+      uint4 o;
+      o.x = pack_16<BF16>(a.x, a.y); o.y = pack_16<BF16>(b.x, b.y); o.z = pack_16<BF16>(c.x, c.y); o.w = pack_16<BF16>(d.x, d.y);
+      rp[i] = o;
+      // keep the rounded value so that the norm sees exactly what later layers will read
+      a = unpack_16<BF16>(o.x); b = unpack_16<BF16>(o.y); c = unpack_16<BF16>(o.z); d = unpack_16<BF16>(o.w);
+    }
+    float* rb_ = rowbuf + i * 8;
+    rb_[0] = a.x; rb_[1] = a.y; rb_[2] = b.x; rb_[3] = b.y; rb_[4] = c.x; rb_[5] = c.y; rb_[6] = d.x; rb_[7] = d.y;
+    ss += a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y + c.x * c.x + c.y * c.y + d.x * d.x + d.y * d.y;
+  }
+  ss = block_sum(ss, sh);
+  const float inv = rsqrtf(ss / (float)H + eps);
+  const uint4* wp = reinterpret_cast<const uint4*>(w);
+  uint4* yp = reinterpret_cast<uint4*>(y + (size_t)row * ldy);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    uint4 wv = wp[i];
+    float2 wa = unpack_16<BF16>(wv.x), wb = unpack_16<BF16>(wv.y), wc = unpack_16<BF16>(wv.z), wd = unpack_16<BF16>(wv.w);
+    const float* r = rowbuf + i * 8;
+    uint4 o;
+    o.x = pack_16<BF16>(r[0] * inv * (wa.x + unit_offset), r[1] * inv * (wa.y + unit_offset));
+    o.y = pack_16<BF16>(r[2] * inv * (wb.x + unit_offset), r[3] * inv * (wb.y + unit_offset));
+    o.z = pack_16<BF16>(r[4] * inv * (wc.x + unit_offset), r[5] * inv * (wc.y + unit_offset));
+    o.w = pack_16<BF16>(r[6] * inv * (wd.x + unit_offset), r[7] * inv * (wd.y + unit_offset));
+    yp[i] = o;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// QKV post-processing, one warp per (token, head):
+//   q heads : optional per-head RMSNorm, RoPE, write to q_out [M, Hq*D]
+//   k heads : optional per-head RMSNorm, RoPE, write to the K page pool at slot[token]
+//   v heads : copy to the V page pool at slot[token]
+// cos/sin tables are fp32 [max_pos, rot/2].  rope_mode: 0 none, 1 neox (rotate-half), 2 interleaved pairs.
+// Page pools are [num_slots, Hkv, D] (slot = page * page_len + offset).  slot < 0 skips the cache write.
+// ------------------------------------------------------------------------------------------------
+struct QkvPostParams {
+  const uint16_t* qkv; int ld_qkv;
+  uint16_t* q_out; int ld_q;
+  uint16_t* k_pool; uint16_t* v_pool;
+  const int* positions; const int* slots;
+  const uint16_t* q_norm_w; const uint16_t* k_norm_w;
+  const float* cos_tab; const float* sin_tab;
+  int M, Hq, Hkv, D, rot, rope_mode;
+  float eps; float norm_unit_offset;
+};
+
+template <bool BF16>
+__global__ void qkv_post_kernel(const QkvPostParams p) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = p.Hq + 2 * p.Hkv;
+  if (gw >= p.M * heads) return;
+  const int tok = gw / heads, head = gw - tok * heads;
+  const uint16_t* src = p.qkv + (size_t)tok * p.ld_qkv + (size_t)head * p.D;
+  const int D = p.D, half = p.rot >> 1;
+  // each lane owns element pairs (2i, 2i+1) for i = lane, lane+32, ... (D <= 512)
+  float v[16];
+  const int npairs = D >> 1;
+  int cnt = 0;
+  float ss = 0.f;
+  for (int i = lane; i < npairs; i += 32, ++cnt) {
+    float2 f = unpack_16<BF16>(*reinterpret_cast<const uint32_t*>(src + 2 * i));
+    v[2 * cnt] = f.x; v[2 * cnt + 1] = f.y;
+    ss += f.x * f.x + f.y * f.y;
+  }
+  const bool is_q = head < p.Hq, is_k = !is_q && head < p.Hq + p.Hkv;
+  const uint16_t* nw = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+  if (nw) {
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / (float)D + p.eps);
+    cnt = 0;
+    for (int i = lane; i < npairs; i += 32, ++cnt) {
+      float2 w = unpack_16<BF16>(*reinterpret_cast<const uint32_t*>(nw + 2 * i));
+      // round to the storage dtype after the norm, as a separate norm op would
+      float2 r = unpack_16<BF16>(pack_16<BF16>(v[2 * cnt] * inv * (w.x + p.norm_unit_offset),
+                                               v[2 * cnt + 1] * inv * (w.y + p.norm_unit_offset)));
+      v[2 * cnt] = r.x; v[2 * cnt + 1] = r.y;
+    }
+  }
+  uint16_t* dst;
+  if (is_q) {
+    dst = p.q_out + (size_t)tok * p.ld_q + (size_t)head * D;
+  } else {
+    const int slot = p.slots[tok];
+    if (slot < 0) return;
+    const int kvh = is_k ? head - p.Hq : head - p.Hq - p.Hkv;
+    dst = (is_k ? p.k_pool : p.v_pool) + ((size_t)slot * p.Hkv + kvh) * D;
+  }
+  if ((is_q || is_k) && p.rope_mode != 0) {
+    const int pos = p.positions[tok];
+    const float* ct = p.cos_tab + (size_t)pos * half;
+    const float* st = p.sin_tab + (size_t)pos * half;
+    if (p.rope_mode == 2) {
+      // interleaved: pair (2i, 2i+1) rotates with frequency i
+      cnt = 0;
+      for (int i = lane; i < npairs; i += 32, ++cnt) {
+        if (i < half) {
+          const float c = ct[i], s = st[i];
+          const float a = v[2 * cnt], b = v[2 * cnt + 1];
+          v[2 * cnt] = a * c - b * s;
+          v[2 * cnt + 1] = a * s + b * c;
+        }
+      }
+    } else {
+      // neox: element j < half pairs with j + half.  Lane's pair index i covers elements 2i, 2i+1; the partner
+      // elements 2i + half, 2i + 1 + half belong to pair index i + half/2, owned by lane (i + half/2) % 32.
+      // half/2 is a multiple of 32 for D = 128 / rot = 128 (half = 64, half/2 = 32) -> same lane, next slot.
+      // General case goes through shared-free shuffles: handled by staging via registers only when half/2 % 32 == 0,
+      // otherwise fall back to a shuffle exchange.
+      const int hp = half >> 1;  // number of pairs in the first half
+      if ((hp & 31) == 0) {
+        const int step = hp >> 5;  // register slots between an element and its partner
+        cnt = 0;
+        for (int i = lane; i < hp; i += 32, ++cnt) {
+          const float c0 = ct[2 * i], s0 = st[2 * i], c1 = ct[2 * i + 1], s1 = st[2 * i + 1];
+          const float a0 = v[2 * cnt], a1 = v[2 * cnt + 1];
+          const float b0 = v[2 * (cnt + step)], b1 = v[2 * (cnt + step) + 1];
+          v[2 * cnt] = a0 * c0 - b0 * s0;
+          v[2 * cnt + 1] = a1 * c1 - b1 * s1;
+          v[2 * (cnt + step)] = b0 * c0 + a0 * s0;
+          v[2 * (cnt + step) + 1] = b1 * c1 + a1 * s1;
+        }
+      } else {
+        // partner pair index = i + hp (first half) or i - hp (second half); owner lane = partner % 32, slot = partner / 32
+        const int total_slots = (npairs + 31) >> 5;
+        float nv[16];
+        for (int s = 0; s < total_slots; ++s) { nv[2 * s] = v[2 * s]; nv[2 * s + 1] = v[2 * s + 1]; }
+        for (int s = 0; s < total_slots; ++s) {
+          const int i = lane + 32 * s;
+          const bool in_rot = i < 2 * hp;
+          const int partner = i < hp ? i + hp : i - hp;
+          for (int ps = 0; ps < total_slots; ++ps) {
+            // every lane publishes slot ps; readers pick the lane they need
+            const float px = __shfl_sync(0xffffffffu, v[2 * ps], partner & 31);
+            const float py = __shfl_sync(0xffffffffu, v[2 * ps + 1], partner & 31);
+            if (in_rot && i < npairs && (partner >> 5) == ps) {
+              const int f = 2 * (i < hp ? i : i - hp);
+              const float c0 = ct[f], s0 = st[f], c1 = ct[f + 1], s1 = st[f + 1];
+              if (i < hp) { nv[2 * s] = v[2 * s] * c0 - px * s0; nv[2 * s + 1] = v[2 * s + 1] * c1 - py * s1; }
+              else        { nv[2 * s] = v[2 * s] * c0 + px * s0; nv[2 * s + 1] = v[2 * s + 1] * c1 + py * s1; }
+            }
+          }
+        }
+        for (int s = 0; s < total_slots; ++s) { v[2 * s] = nv[2 * s]; v[2 * s + 1] = nv[2 * s + 1]; }
+      }
+    }
+  }
+  cnt = 0;
+  for (int i = lane; i < npairs; i += 32, ++cnt)
+    *reinterpret_cast<uint32_t*>(dst + 2 * i) = pack_16<BF16>(v[2 * cnt], v[2 * cnt + 1]);
+}
+
+// ------------------------------------------------------------------------------------------------
+// SiLU(gate) * up :  x [M, 2I] (gate | up) -> y [M, I]
+// ------------------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void silu_mul_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int I, int ldx, int ldy) {
+  const size_t total = (size_t)M * (I / 8);
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / (I / 8)), c = (int)(idx % (I / 8)) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + c);
+    const uint4 u = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + I + c);
+    const uint32_t gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = unpack_16<BF16>(gs[k]), b = unpack_16<BF16>(us[k]);
+      o[k] = pack_16<BF16>(a.x / (1.f + __expf(-a.x)) * b.x, a.y / (1.f + __expf(-a.y)) * b.y);
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)m * ldy + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Embedding gather: out[m, :] = table[ids[m], :]
+// ------------------------------------------------------------------------------------------------
+__global__ void embedding_kernel(const int* __restrict__ ids, const uint16_t* __restrict__ table, uint16_t* __restrict__ out,
+                                 int H, int vocab) {
+  const int m = blockIdx.x;
+  int id = ids[m];
+  if (id < 0 || id >= vocab) id = 0;
+  const uint4* src = reinterpret_cast<const uint4*>(table + (size_t)id * H);
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)m * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// ------------------------------------------------------------------------------------------------
+// Greedy arg-max over logits rows (fp32 or 16-bit); ties resolve to the lowest index.
+// Writes ids[m] and, if vals != nullptr, the max logit (used when merging vocab shards across ranks).
+// ------------------------------------------------------------------------------------------------
+template <int KIND>  // 0 = f32, 1 = bf16, 2 = f16
+__global__ void argmax_kernel(const void* __restrict__ logits, int* __restrict__ ids, float* __restrict__ vals, int V, int ld,
+                              int id_offset) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int m = blockIdx.x;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float x;
+    if (KIND == 0) x = reinterpret_cast<const float*>(logits)[(size_t)m * ld + i];
+    else if (KIND == 1) x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[(size_t)m * ld + i]);
+    else x = __half2float(reinterpret_cast<const __half*>(logits)[(size_t)m * ld + i]);
+    if (x > best || (x == best && i < bi)) { best = x; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  if (l == 0) { sv[w] = best; si[w] = bi; }
+  __syncthreads();
+  if (w == 0) {
+    const int nw = blockDim.x >> 5;
+    best = l < nw ? sv[l] : -INFINITY;
+    bi = l < nw ? si[l] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (l == 0) { ids[m] = bi + id_offset; if (vals) vals[m] = best; }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Router: scores = softmax / sigmoid / identity of logits [M, E] (fp32), optional bias added for selection
+// only, optional group-limited selection (n_group groups, keep topk_group groups ranked by the sum of their
+// two best biased scores), top-k, optional renormalisation, times route_scale.  One warp per token, E <= 512.
+// ------------------------------------------------------------------------------------------------
+struct RouteParams {
+  const float* logits; const float* bias; int* out_idx; float* out_w;
+  int M, E, topk, score_mode /*0 softmax 1 sigmoid 2 none*/, renorm, n_group, topk_group;
+  float route_scale;
+};
+__global__ void route_topk_kernel(const RouteParams p) {
+  const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (gw >= p.M) return;
+  const float* lg = p.logits + (size_t)gw * p.E;
+  float sc[16], sel[16];
+  const int per = (p.E + 31) >> 5;
+  float mx = -INFINITY;
+  for (int s = 0; s < per; ++s) { const int e = lane + 32 * s; sc[s] = e < p.E ? lg[e] : -INFINITY; mx = fmaxf(mx, sc[s]); }
+  if (p.score_mode == 0) {
+    mx = warp_max(mx);
+    float sum = 0.f;
+    for (int s = 0; s < per; ++s) { const int e = lane + 32 * s; sc[s] = e < p.E ? __expf(sc[s] - mx) : 0.f; sum += sc[s]; }
+    sum = warp_sum(sum);
+    for (int s = 0; s < per; ++s) sc[s] /= sum;
+  } else if (p.score_mode == 1) {
+    for (int s = 0; s < per; ++s) sc[s] = 1.f / (1.f + __expf(-sc[s]));
+  }
+  for (int s = 0; s < per; ++s) {
+    const int e = lane + 32 * s;
+    sel[s] = e < p.E ? sc[s] + (p.bias ? p.bias[e] : 0.f) : -INFINITY;
+  }
+  if (p.n_group > 1 && p.topk_group < p.n_group) {
+    // group g = e / (E / n_group); score(g) = sum of top-2 biased scores in the group
+    const int gs = p.E / p.n_group;
+    float gscore[32];
+    for (int g = 0; g < p.n_group; ++g) {
+      float m1 = -INFINITY, m2 = -INFINITY;
+      for (int s = 0; s < per; ++s) {
+        const int e = lane + 32 * s;
+        if (e < p.E && e / gs == g) { const float x = sel[s]; if (x > m1) { m2 = m1; m1 = x; } else if (x > m2) m2 = x; }
+      }
+      // merge (m1, m2) across lanes
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float o1 = __shfl_xor_sync(0xffffffffu, m1, o), o2 = __shfl_xor_sync(0xffffffffu, m2, o);
+        const float n1 = fmaxf(m1, o1);
+        const float n2 = fmaxf(fminf(m1, o1), fmaxf(m2, o2));
+        m1 = n1; m2 = n2;
+      }
+      gscore[g] = m1 + m2;
+    }
+    // keep the topk_group best groups (ties to the lower index)
+    unsigned keep = 0;
+    for (int r = 0; r < p.topk_group; ++r) {
+      int bg = -1; float bv = -INFINITY;
+      for (int g = 0; g < p.n_group; ++g)
+        if (!((keep >> g) & 1u) && (bg < 0 || gscore[g] > bv)) { bg = g; bv = gscore[g]; }
+      keep |= 1u << bg;
+    }
+    for (int s = 0; s < per; ++s) {
+      const int e = lane + 32 * s;
+      if (e < p.E && !((keep >> (e / gs)) & 1u)) sel[s] = -INFINITY;
+    }
+  }
+  float wsum = 0.f;
+  float my_w = 0.f; int my_i = 0;
+  for (int k = 0; k < p.topk; ++k) {
+    float bv = -INFINITY; int bi = 0x7fffffff; float bs = 0.f;
+    for (int s = 0; s < per; ++s) {
+      const int e = lane + 32 * s;
+      if (e < p.E && (sel[s] > bv || (sel[s] == bv && e < bi))) { bv = sel[s]; bi = e; bs = sc[s]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      const float os = __shfl_xor_sync(0xffffffffu, bs, o);
+      if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; bs = os; }
+    }
+    if ((bi & 31) == lane) sel[bi >> 5] = -INFINITY;   // remove from further rounds
+    wsum += bs;
+    if (lane == k) { my_w = bs; my_i = bi; }
+  }
+  if (lane < p.topk) {
+    float w = my_w;
+    if (p.renorm) w = w / (wsum + 1e-20f);
+    p.out_idx[(size_t)gw * p.topk + lane] = my_i;
+    p.out_w[(size_t)gw * p.topk + lane] = w * p.route_scale;
+  }
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_rmsnorm(const void* x, const void* w, void* y, void* residual, int M, int H, int ldx, int ldy, float eps,
+                          float unit_offset, int dtype, void* stream) {
+  if (M <= 0) return 0;
+  if (H % 8 != 0 || H > 32768) return -1;
+  int threads = H / 8;
+  threads = threads > 1024 ? 1024 : ((threads + 31) / 32) * 32;
+  const size_t smem = (size_t)H * sizeof(float);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); cfg = true; }
+    rmsnorm_kernel<true><<<M, threads, smem, s>>>((const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); cfg = true; }
+    rmsnorm_kernel<false><<<M, threads, smem, s>>>((const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
+  }
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_qkv_post(const void* qkv, int ld_qkv, void* q_out, int ld_q, void* k_pool, void* v_pool, const int* positions,
+                           const int* slots, const void* q_norm_w, const void* k_norm_w, const float* cos_tab,
+                           const float* sin_tab, int M, int Hq, int Hkv, int D, int rot, int rope_mode, float eps,
+                           float norm_unit_offset, int dtype, void* stream) {
+  if (M <= 0) return 0;
+  if (D % 2 != 0 || D > 512 || rot > D || (rot & 3) != 0) return -1;
+  QkvPostParams p;
+  p.qkv = (const uint16_t*)qkv; p.ld_qkv = ld_qkv; p.q_out = (uint16_t*)q_out; p.ld_q = ld_q;
+  p.k_pool = (uint16_t*)k_pool; p.v_pool = (uint16_t*)v_pool; p.positions = positions; p.slots = slots;
+  p.q_norm_w = (const uint16_t*)q_norm_w; p.k_norm_w = (const uint16_t*)k_norm_w; p.cos_tab = cos_tab; p.sin_tab = sin_tab;
+  p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rot = rot; p.rope_mode = rope_mode; p.eps = eps; p.norm_unit_offset = norm_unit_offset;
+  const long long warps = (long long)M * (Hq + 2 * Hkv);
+  const int wpb = 8;
+  const int blocks = (int)((warps + wpb - 1) / wpb);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) qkv_post_kernel<true><<<blocks, wpb * 32, 0, s>>>(p);
+  else qkv_post_kernel<false><<<blocks, wpb * 32, 0, s>>>(p);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_silu_mul(const void* x, void* y, int M, int I, int ldx, int ldy, int dtype, void* stream) {
+  if (M <= 0) return 0;
+  if (I % 8 != 0) return -1;
+  const size_t total = (size_t)M * (I / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) silu_mul_kernel<true><<<blocks, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
+  else silu_mul_kernel<false><<<blocks, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_embedding(const int* ids, const void* table, void* out, int M, int H, int vocab, void* stream) {
+  if (M <= 0) return 0;
+  if (H % 8 != 0) return -1;
+  embedding_kernel<<<M, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ids, (const uint16_t*)table, (uint16_t*)out, H, vocab);
+  return (int)cudaGetLastError();
+}
+
+// kind: 0 = f32, 1 = bf16, 2 = f16
+extern "C" int fb_argmax(const void* logits, int* ids, float* vals, int M, int V, int ld, int id_offset, int kind, void* stream) {
+  if (M <= 0) return 0;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (kind == 0) argmax_kernel<0><<<M, 1024, 0, s>>>(logits, ids, vals, V, ld, id_offset);
+  else if (kind == 1) argmax_kernel<1><<<M, 1024, 0, s>>>(logits, ids, vals, V, ld, id_offset);
+  else argmax_kernel<2><<<M, 1024, 0, s>>>(logits, ids, vals, V, ld, id_offset);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_route_topk(const float* logits, const float* bias, int* out_idx, float* out_w, int M, int E, int topk,
+                             int score_mode, int renorm, int n_group, int topk_group, float route_scale, void* stream) {
+  if (M <= 0) return 0;
+  if (E > 512 || topk > 32 || n_group > 32 || (n_group > 1 && E % n_group != 0)) return -1;
+  RouteParams p{logits, bias, out_idx, out_w, M, E, topk, score_mode, renorm, n_group, topk_group, route_scale};
+  const int wpb = 4;
+  route_topk_kernel<<<(M + wpb - 1) / wpb, wpb * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,499 @@
+// Dense 16-bit GEMM family for sm_100a:  Y[M,N] = X[M,K] * W[N,K]^T  (+ bias, + residual, SwiGLU)
+//
+// Role in the framework: every Linear / LinearAdd / LinearSwiglu with fp16 or bf16 weights.  The reference
+// runs these as one-CTA-per-output-row GEMV for < 8 tokens and convert + cublasGemmEx otherwise
+// (reference: src/devices/cuda/linear/fastllm-linear-fp16.cu:561-650, fastllm-linear-bf16.cu:332-648).
+//
+// Two kernels, both tcgen05 (UMMA) with fp32 accumulators in TMEM, operands staged by TMA into
+// 128-byte-swizzled shared memory through an mbarrier ring:
+//
+//  * small-M ("decode") kernel: swap-AB.  The weight tile [128 out-features x 64 k] is the UMMA A operand,
+//    the token tile [MPAD tokens x 64 k] the B operand, so the 128-row MMA is always full no matter how
+//    few tokens there are.  K is split across a thread-block cluster (1/2/4/8 CTAs); the partial tiles
+//    are reduced through distributed shared memory in a fixed order (deterministic), each CTA reducing
+//    and writing a slice of the tile with the epilogue applied.  No global scratch.
+//  * large-M ("prefill") kernel: 128 tokens x 256 out-features tile per CTA, K pipelined, epilogue straight
+//    from TMEM to global.
+//
+// SwiGLU epilogue expects the gate/up weight rows interleaved per 128-row tile: rows [0,64) of tile t are
+// gate rows 64t..64t+63 and rows [64,128) are the matching up rows; output column = 64t + i.
+#include "ptx.cuh"
+#include "tmap.h"
+
+FB_DEFINE_ERROR_API(gemm)
+
+namespace fb {
+
+constexpr int KID_GEMM_SMALLM = 1;
+constexpr int KID_GEMM_LARGEM = 2;
+
+enum GemmFlags : int {
+  GEMM_BIAS = 1,       // += bias[n]
+  GEMM_RESIDUAL = 2,   // += residual[m, n]
+  GEMM_SWIGLU = 4,     // out[m, i] = silu(gate) * up   (N_out = N / 2)
+  GEMM_OUT_F32 = 8,    // write fp32 instead of the 16-bit input dtype
+};
+
+struct GemmParams {
+  void* out;
+  const void* bias;
+  const void* residual;
+  int M, N, K;
+  int ld_out, ld_res;
+  int kb_per_split;   // 64-wide k blocks per cluster rank
+  int kb_total;
+  uint32_t idesc;
+  int flags;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int MPAD>
+struct SmallMCfg {
+  static constexpr int A_BYTES = 128 * 128;            // 128 rows x 64 bf16
+  static constexpr int B_BYTES = MPAD * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int MAX_STAGES = (200 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 10 ? 10 : MAX_STAGES;
+  static constexpr int RED_BYTES = MPAD * 128 * 4;     // fp32 partial tile [MPAD][128]
+  static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
+  static constexpr int SMEM_BYTES = BODY_BYTES + 256 + 1024;   // + barriers + alignment slack
+  static constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
+};
+
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(192, 1)
+gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
+  using Cfg = SmallMCfg<MPAD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* accum_bar = empty_bar + Cfg::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = (int)cluster_ctarank();
+  const int nsplit = (int)cluster_nctarank();
+  const int n_tile = blockIdx.y;
+  const int kb0 = split * p.kb_per_split;
+  int kb_cnt = p.kb_total - kb0;
+  if (kb_cnt > p.kb_per_split) kb_cnt = p.kb_per_split;
+  if (kb_cnt < 0) kb_cnt = 0;
+  bool dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(accum_bar, 1);
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_SMALLM, 1)) break;
+        uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 64, n_tile * 128, pol_w);
+        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], (kb0 + i) * 64, 0, pol_x);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_SMALLM, 2)) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+        const uint64_t db = make_smem_desc(a_addr + Cfg::A_BYTES, 16, 1024, SWZ_128B);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, p.idesc, (i | k) != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(accum_bar);
+    }
+    __syncwarp();
+  } else {
+    // epilogue warps 2..5: TMEM lanes [32q, 32q+32) -> fp32 partial tile P[token][n] in shared memory
+    const int q = warp & 3;
+    float* P = reinterpret_cast<float*>(smem);
+    const int n_local = q * 32 + lane;
+    if (kb_cnt > 0) {
+      mbar_wait(accum_bar, 0, dead, KID_GEMM_SMALLM, 3);
+      tc_fence_after_sync();
+      constexpr int CH = MPAD < 32 ? MPAD : 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < MPAD; c0 += CH) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if (CH == 32) tmem_ld_32x32b_x32(taddr, r); else tmem_ld_32x32b_x16(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; ++j) P[(c0 + j) * 128 + n_local] = __uint_as_float(r[j]);
+      }
+    } else {
+      for (int j = 0; j < MPAD; ++j) P[j * 128 + n_local] = 0.f;
+    }
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+
+  // ---- cross-CTA reduction over the k splits + epilogue; this CTA owns a column slice of the tile ----
+  {
+    const bool swiglu = (p.flags & GEMM_SWIGLU) != 0;
+    const int outw = swiglu ? 64 : 128;
+    const int per = outw / nsplit;           // columns owned by this CTA (>= 8)
+    const int vec_per_row = per >> 2;
+    const int items = p.M * vec_per_row;
+    const uint32_t P_addr = smem_u32(smem);
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+      const int j = it / vec_per_row;
+      const int c = split * per + (it - j * vec_per_row) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), acc2 = acc;
+      for (int s = 0; s < nsplit; ++s) {
+        const uint32_t ra = mapa_u32(P_addr + (uint32_t)(j * 128 + c) * 4u, (uint32_t)s);
+        float4 v = ld_dsmem_f4(ra);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        if (swiglu) {
+          float4 u = ld_dsmem_f4(ra + 64 * 4);
+          acc2.x += u.x; acc2.y += u.y; acc2.z += u.z; acc2.w += u.w;
+        }
+      }
+      int n_out;
+      if (swiglu) {
+        n_out = n_tile * 64 + c;
+        if (p.flags & GEMM_BIAS) {
+          const uint32_t* bg = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_tile * 128 + c);
+          float2 b0 = unpack_16<BF16>(bg[0]), b1 = unpack_16<BF16>(bg[1]);
+          float2 u0 = unpack_16<BF16>(bg[32]), u1 = unpack_16<BF16>(bg[33]);
+          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+          acc2.x += u0.x; acc2.y += u0.y; acc2.z += u1.x; acc2.w += u1.y;
+        }
+        acc.x = silu_f(acc.x) * acc2.x; acc.y = silu_f(acc.y) * acc2.y;
+        acc.z = silu_f(acc.z) * acc2.z; acc.w = silu_f(acc.w) * acc2.w;
+        if (n_out >= (p.N >> 1)) continue;
+      } else {
+        n_out = n_tile * 128 + c;
+        if (n_out >= p.N) continue;
+        if (p.flags & GEMM_BIAS) {
+          const uint32_t* bp = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_out);
+          float2 b0 = unpack_16<BF16>(bp[0]), b1 = unpack_16<BF16>(bp[1]);
+          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+        }
+      }
+      if (p.flags & GEMM_RESIDUAL) {
+        const uint2 rv = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)j * p.ld_res + n_out);
+        float2 r0 = unpack_16<BF16>(rv.x), r1 = unpack_16<BF16>(rv.y);
+        acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
+      }
+      if (p.flags & GEMM_OUT_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)j * p.ld_out + n_out) = acc;
+      } else {
+        uint2 o;
+        o.x = pack_16<BF16>(acc.x, acc.y);
+        o.y = pack_16<BF16>(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)j * p.ld_out + n_out) = o;
+      }
+    }
+  }
+  cluster_sync_all();   // peers may still be reading this CTA's partial tile
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// large-M kernel: tile 128 tokens x BN out-features, BK = 64
+// ---------------------------------------------------------------------------------------------------
+template <int BN>
+struct LargeMCfg {
+  static constexpr int A_BYTES = 128 * 128;
+  static constexpr int B_BYTES = BN * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (196 * 1024) / STAGE_BYTES > 8 ? 8 : (196 * 1024) / STAGE_BYTES;
+  static constexpr int BODY_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int SMEM_BYTES = BODY_BYTES + 256 + 1024;
+  static constexpr int TMEM_COLS = BN;
+};
+
+template <int BN, bool BF16>
+__global__ void __launch_bounds__(192, 1)
+gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
+  using Cfg = LargeMCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* accum_bar = empty_bar + Cfg::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_tile = blockIdx.x, m_tile = blockIdx.y;
+  const int kb_cnt = p.kb_total;
+  bool dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(accum_bar, 1);
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_LARGEM, 1)) break;
+        uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d(a, &tmX, &full_bar[s], i * 64, m_tile * 128);
+        tma_load_2d(a + Cfg::A_BYTES, &tmW, &full_bar[s], i * 64, n_tile * BN);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_LARGEM, 2)) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+        const uint64_t db = make_smem_desc(a_addr + Cfg::A_BYTES, 16, 1024, SWZ_128B);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, p.idesc, (i | k) != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(accum_bar);
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    const int m = m_tile * 128 + q * 32 + lane;
+    mbar_wait(accum_bar, 0, dead, KID_GEMM_LARGEM, 3);
+    tc_fence_after_sync();
+    const bool swiglu = (p.flags & GEMM_SWIGLU) != 0;
+    const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(p.bias);
+    if (!swiglu) {
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_wait();
+        const int n0 = n_tile * BN + c0;
+        if (m >= p.M || n0 >= p.N) continue;
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (p.flags & GEMM_BIAS) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            float2 b = unpack_16<BF16>(*reinterpret_cast<const uint32_t*>(bias16 + n0 + j));
+            v[j] += b.x; v[j + 1] += b.y;
+          }
+        }
+        if (p.flags & GEMM_RESIDUAL) {
+          const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)m * p.ld_res + n0);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 rv = rp[g];
+            float2 a0 = unpack_16<BF16>(rv.x), a1 = unpack_16<BF16>(rv.y), a2 = unpack_16<BF16>(rv.z), a3 = unpack_16<BF16>(rv.w);
+            v[g * 8 + 0] += a0.x; v[g * 8 + 1] += a0.y; v[g * 8 + 2] += a1.x; v[g * 8 + 3] += a1.y;
+            v[g * 8 + 4] += a2.x; v[g * 8 + 5] += a2.y; v[g * 8 + 6] += a3.x; v[g * 8 + 7] += a3.y;
+          }
+        }
+        if (p.flags & GEMM_OUT_F32) {
+          float4* op = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)m * p.ld_out + n0);
+#pragma unroll
+          for (int g = 0; g < 8; ++g) op[g] = make_float4(v[g * 4], v[g * 4 + 1], v[g * 4 + 2], v[g * 4 + 3]);
+        } else {
+          uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)m * p.ld_out + n0);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 o;
+            o.x = pack_16<BF16>(v[g * 8 + 0], v[g * 8 + 1]); o.y = pack_16<BF16>(v[g * 8 + 2], v[g * 8 + 3]);
+            o.z = pack_16<BF16>(v[g * 8 + 4], v[g * 8 + 5]); o.w = pack_16<BF16>(v[g * 8 + 6], v[g * 8 + 7]);
+            op[g] = o;
+          }
+        }
+      }
+    } else {
+      // gate columns [128b, 128b+64), up columns [128b+64, 128b+128) of this tile -> out columns 64*(tile) + ...
+#pragma unroll 1
+      for (int blk = 0; blk < BN / 128; ++blk) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < 64; c0 += 32) {
+          uint32_t g[32], u[32];
+          __syncwarp();
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(blk * 128 + c0), g);
+          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(blk * 128 + 64 + c0), u);
+          tmem_ld_wait();
+          const int nin = n_tile * BN + blk * 128 + c0;            // gate row index in W
+          const int nout = (n_tile * BN + blk * 128) / 2 + c0;
+          if (m >= p.M || nout >= (p.N >> 1)) continue;
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float gv = __uint_as_float(g[j]), uv = __uint_as_float(u[j]);
+            if (p.flags & GEMM_BIAS) {
+              gv += BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias16)[nin + j])
+                         : __half2float(reinterpret_cast<const __half*>(bias16)[nin + j]);
+              uv += BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias16)[nin + 64 + j])
+                         : __half2float(reinterpret_cast<const __half*>(bias16)[nin + 64 + j]);
+            }
+            v[j] = silu_f(gv) * uv;
+          }
+          uint4* op = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)m * p.ld_out + nout);
+#pragma unroll
+          for (int gq = 0; gq < 4; ++gq) {
+            uint4 o;
+            o.x = pack_16<BF16>(v[gq * 8 + 0], v[gq * 8 + 1]); o.y = pack_16<BF16>(v[gq * 8 + 2], v[gq * 8 + 3]);
+            o.z = pack_16<BF16>(v[gq * 8 + 4], v[gq * 8 + 5]); o.w = pack_16<BF16>(v[gq * 8 + 6], v[gq * 8 + 7]);
+            op[gq] = o;
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------------
+// host launchers
+// ---------------------------------------------------------------------------------------------------
+template <int MPAD, bool BF16>
+static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int nsplit, int n_tiles,
+                                 cudaStream_t stream) {
+  using Cfg = SmallMCfg<MPAD>;
+  auto kern = gemm_smallm_kernel<MPAD, BF16>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
+}
+
+template <int BN, bool BF16>
+static cudaError_t launch_largem(const CUtensorMap& tmX, const CUtensorMap& tmW, const GemmParams& p, cudaStream_t stream) {
+  using Cfg = LargeMCfg<BN>;
+  auto kern = gemm_largem_kernel<BN, BF16>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  dim3 grid((p.N + BN - 1) / BN, (p.M + 127) / 128, 1);
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmX, tmW, p);
+  return cudaGetLastError();
+}
+
+}  // namespace fb
+
+// Heuristic used by the launcher: how many cluster ranks split K so that about one CTA lands on each SM.
+extern "C" int fb_gemm_pick_split(int M, int N, int K, int sm_count) {
+  const int n_tiles = (N + 127) / 128;
+  const int kb = K / 64;
+  int best = 1;
+  for (int s = 1; s <= 8; s *= 2) {
+    if (kb / s < 4) break;                      // keep at least 4 k-blocks per rank
+    const int per = (kb + s - 1) / s;
+    if ((s - 1) * per >= kb) break;             // every rank must own at least one block
+    best = s;
+    if (n_tiles * s >= sm_count - sm_count / 8) break;
+  }
+  return best;
+}
+
+// Y = X W^T.  dtype: 0 = fp16, 1 = bf16.  X: [M, K] row stride ldx; W: [N, K] row stride ldw (elements).
+// nsplit <= 0 picks automatically.  Returns 0 on success, a cudaError_t, or -1 for unsupported shapes.
+extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void* bias, const void* residual, int M, int N,
+                             int K, int ldx, int ldw, int ld_out, int ld_res, int dtype, int flags, int nsplit, void* stream_) {
+  using namespace fb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (K % 64 != 0 || N % 8 != 0 || (dtype != 0 && dtype != 1)) return -1;
+  if ((flags & GEMM_SWIGLU) && (N % 128 != 0)) return -1;
+  GemmParams p;
+  p.out = out; p.bias = bias; p.residual = residual;
+  p.M = M; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res;
+  p.kb_total = K / 64;
+  p.flags = flags;
+  const bool bf16 = dtype == 1;
+  if (M <= 256) {
+    const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+    static int sm_count = 0;
+    if (sm_count == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    }
+    if (nsplit <= 0) nsplit = fb_gemm_pick_split(M, N, K, sm_count);
+    if (nsplit != 1 && nsplit != 2 && nsplit != 4 && nsplit != 8) return -1;
+    p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
+    p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
+    CUtensorMap tmW, tmX;
+    if (!make_tmap_2d(&tmW, W, N, K, ldw, 128, 64, 2, 3)) return -2;
+    if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
+    const int n_tiles = (N + 127) / 128;
+#define FB_SM(MP)                                                                                        \
+  return (int)(bf16 ? launch_smallm<MP, true>(tmW, tmX, p, nsplit, n_tiles, stream)                      \
+                    : launch_smallm<MP, false>(tmW, tmX, p, nsplit, n_tiles, stream));
+    switch (mpad) {
+      case 16: FB_SM(16)
+      case 32: FB_SM(32)
+      case 64: FB_SM(64)
+      case 128: FB_SM(128)
+      default: FB_SM(256)
+    }
+#undef FB_SM
+  }
+  if (N % 32 != 0) return -1;
+  p.kb_per_split = p.kb_total;
+  const int bn = (N >= 256 && N % 256 == 0) || N > 2048 ? 256 : 128;
+  p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, bn);
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmX, X, M, K, ldx, 128, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmW, W, N, K, ldw, bn, 64, 2, 3)) return -2;
+  if (bn == 256)
+    return (int)(bf16 ? launch_largem<256, true>(tmX, tmW, p, stream) : launch_largem<256, false>(tmX, tmW, p, stream));
+  return (int)(bf16 ? launch_largem<128, true>(tmX, tmW, p, stream) : launch_largem<128, false>(tmX, tmW, p, stream));
+}

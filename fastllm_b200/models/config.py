@@ -1,0 +1,244 @@
+"""Typed model configuration parsed from a Hugging Face ``config.json``.
+
+The reference flattens ``config.json`` into a string dictionary and queries it by key at use sites
+(src/model.cpp:2450+, e.g. ``rope_scaling.type`` in src/models/llama.cpp:82); here every field the
+decoder needs is resolved once into a dataclass, per model family.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "llama"
+    architectures: list = field(default_factory=list)
+    vocab_size: int = 32000
+    hidden_size: int = 4096
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 32
+    head_dim: int = 128
+    intermediate_size: int = 11008
+    rms_eps: float = 1e-6
+    norm_unit_offset: float = 0.0          # Gemma-style (1 + w)
+    rope_theta: float = 10000.0
+    rope_scaling: dict | None = None
+    rope_mode: str = "neox"                # neox | interleaved | none
+    rotary_dim: int | None = None          # partial rotary
+    max_position: int = 8192
+    tie_embeddings: bool = False
+    attention_bias: bool = False
+    mlp_bias: bool = False
+    qk_norm: bool = False
+    hidden_act: str = "silu"
+    embed_scale: float = 1.0
+    logit_scale: float = 1.0
+    sliding_window: int | None = None
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    num_shared_experts: int = 0
+    shared_expert_intermediate_size: int = 0
+    shared_expert_gate: bool = False       # qwen2_moe gates the shared expert with a sigmoid
+    first_k_dense: int = 0
+    moe_layer_freq: int = 1
+    scoring_func: str = "softmax"          # softmax | sigmoid
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    router_bias: bool = False              # e_score_correction_bias
+    # MLA
+    use_mla: bool = False
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    # bookkeeping
+    eos_token_ids: list = field(default_factory=list)
+    bos_token_id: int | None = None
+    quantization_config: dict | None = None
+    torch_dtype: str = "bfloat16"
+    raw: dict = field(default_factory=dict)
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_is_moe(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_k_dense and (i % self.moe_layer_freq == 0 or self.moe_layer_freq == 1)
+
+    @property
+    def q_head_dim(self) -> int:
+        return self.qk_nope_head_dim + self.qk_rope_head_dim if self.use_mla else self.head_dim
+
+
+LLAMA_LIKE = {"llama", "mistral", "internlm", "internlm3", "baichuan", "yi", "deepseek", "qwen2", "qwen3", "minicpm",
+              "phi3", "glm4", "glm", "gemma", "gemma2", "ernie4_5", "hunyuan", "telechat", "internlm2", "qwen"}
+MOE_LIKE = {"qwen3_moe", "qwen2_moe", "moe", "mixtral", "deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32",
+            "glm4_moe", "ernie4_5_moe", "minimax_m2", "hunyuan_moe", "gpt_oss", "PanguProMoE"}
+
+
+def _eos_list(v) -> list:
+    if v is None:
+        return []
+    return list(v) if isinstance(v, (list, tuple)) else [v]
+
+
+def from_hf_dict(d: dict) -> ModelConfig:
+    """Build a ModelConfig from the ``config.json`` dictionary of any supported family."""
+    if "text_config" in d and isinstance(d["text_config"], dict):   # multimodal wrappers keep the LLM config nested
+        inner = dict(d["text_config"])
+        inner.setdefault("model_type", d.get("model_type", "llama"))
+        for k in ("eos_token_id", "bos_token_id", "tie_word_embeddings", "quantization_config"):
+            if k in d and k not in inner:
+                inner[k] = d[k]
+        d = inner
+    mt = d.get("model_type", "llama")
+    c = ModelConfig(model_type=mt, raw=d, architectures=d.get("architectures", []))
+    g = d.get
+    c.vocab_size = g("vocab_size", c.vocab_size)
+    c.hidden_size = g("hidden_size", g("n_embd", c.hidden_size))
+    c.num_layers = g("num_hidden_layers", g("n_layer", g("num_layers", c.num_layers)))
+    c.num_heads = g("num_attention_heads", g("n_head", c.num_heads))
+    c.num_kv_heads = g("num_key_value_heads", g("multi_query_group_num", c.num_heads)) or c.num_heads
+    c.head_dim = g("head_dim") or g("kv_channels") or c.hidden_size // c.num_heads
+    c.intermediate_size = g("intermediate_size", g("ffn_hidden_size", c.intermediate_size))
+    c.rms_eps = g("rms_norm_eps", g("layernorm_epsilon", g("layer_norm_eps", c.rms_eps)))
+    c.rope_theta = float(g("rope_theta", g("rotary_emb_base", 10000.0)))
+    rs = g("rope_scaling") or g("rope_parameters")
+    if isinstance(rs, dict):
+        if "rope_theta" in rs:
+            c.rope_theta = float(rs["rope_theta"])
+        kind = rs.get("rope_type", rs.get("type", "default"))
+        c.rope_scaling = rs if kind not in ("default", None) else None
+    c.max_position = g("max_position_embeddings", g("seq_length", c.max_position))
+    c.tie_embeddings = bool(g("tie_word_embeddings", False))
+    c.attention_bias = bool(g("attention_bias", g("qkv_bias", g("add_qkv_bias", mt in ("qwen2", "qwen2_moe", "qwen")))))
+    c.mlp_bias = bool(g("mlp_bias", False))
+    c.hidden_act = g("hidden_act", g("hidden_activation", "silu"))
+    c.sliding_window = g("sliding_window") if g("use_sliding_window", True) else None
+    c.eos_token_ids = _eos_list(g("eos_token_id"))
+    c.bos_token_id = g("bos_token_id")
+    c.quantization_config = g("quantization_config")
+    c.torch_dtype = str(g("torch_dtype", g("dtype", "bfloat16"))).replace("torch.", "")
+    prf = g("partial_rotary_factor")
+    if prf:
+        c.rotary_dim = int(c.head_dim * float(prf))
+    if mt in ("qwen3", "qwen3_moe"):
+        c.qk_norm = True
+    if mt in ("gemma", "gemma2", "gemma3_text"):
+        c.norm_unit_offset = 1.0
+        c.embed_scale = float(c.hidden_size) ** 0.5
+    if mt in ("chatglm", "glm"):
+        c.rope_mode = "interleaved" if mt == "chatglm" else "neox"
+    # --- MoE families ---
+    if mt in ("qwen3_moe", "qwen2_moe", "moe"):
+        c.num_experts = g("num_experts", 0)
+        c.num_experts_per_tok = g("num_experts_per_tok", 0)
+        c.moe_intermediate_size = g("moe_intermediate_size", 0)
+        c.norm_topk_prob = bool(g("norm_topk_prob", mt == "qwen3_moe"))
+        c.moe_layer_freq = g("decoder_sparse_step", 1) or 1
+        sis = g("shared_expert_intermediate_size", 0) or 0
+        if sis:
+            c.num_shared_experts = 1
+            c.shared_expert_intermediate_size = sis
+            c.shared_expert_gate = True
+    elif mt == "mixtral":
+        c.num_experts = g("num_local_experts", 8)
+        c.num_experts_per_tok = g("num_experts_per_tok", 2)
+        c.moe_intermediate_size = c.intermediate_size
+        c.norm_topk_prob = True
+    elif mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe", "minimax_m2", "ernie4_5_moe"):
+        c.num_experts = g("n_routed_experts", g("num_experts", g("moe_num_experts", 0))) or 0
+        c.num_experts_per_tok = g("num_experts_per_tok", g("moe_k", 0))
+        c.moe_intermediate_size = g("moe_intermediate_size", 0)
+        c.norm_topk_prob = bool(g("norm_topk_prob", True))
+        c.num_shared_experts = g("n_shared_experts", g("moe_num_shared_experts", 0)) or 0
+        c.shared_expert_intermediate_size = c.moe_intermediate_size * c.num_shared_experts
+        c.first_k_dense = g("first_k_dense_replace", 0) or 0
+        c.moe_layer_freq = g("moe_layer_freq", 1) or 1
+        c.scoring_func = g("scoring_func", "sigmoid" if mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe") else "softmax")
+        c.n_group = g("n_group", 1) or 1
+        c.topk_group = g("topk_group", 1) or 1
+        c.routed_scaling_factor = float(g("routed_scaling_factor", 1.0))
+        c.router_bias = g("topk_method", "") == "noaux_tc" or mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe")
+        if mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32"):
+            c.use_mla = True
+            c.q_lora_rank = g("q_lora_rank") or 0
+            c.kv_lora_rank = g("kv_lora_rank", 512)
+            c.qk_nope_head_dim = g("qk_nope_head_dim", 128)
+            c.qk_rope_head_dim = g("qk_rope_head_dim", 64)
+            c.v_head_dim = g("v_head_dim", 128)
+            c.rope_mode = "interleaved"
+            c.head_dim = c.qk_nope_head_dim + c.qk_rope_head_dim
+        if mt == "glm4_moe":
+            c.qk_norm = bool(g("use_qk_norm", False))
+    return c
+
+
+def load_config(path: str | Path) -> ModelConfig:
+    p = Path(path)
+    if p.is_dir():
+        p = p / "config.json"
+    with open(p, "r", encoding="utf-8") as f:
+        return from_hf_dict(json.load(f))
+
+
+# ---------------------------------------------------------------------------------------------------
+# Named architectures used by the benchmarks and tests (random-init, no checkpoint needed)
+# ---------------------------------------------------------------------------------------------------
+def preset(name: str) -> ModelConfig:
+    name = name.lower()
+    if name in ("qwen3-0.6b", "qwen3_0.6b"):
+        return from_hf_dict(dict(model_type="qwen3", vocab_size=151936, hidden_size=1024, num_hidden_layers=28,
+                                 num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072,
+                                 rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True, max_position_embeddings=40960))
+    if name in ("llama-3-8b", "llama3-8b"):
+        return from_hf_dict(dict(model_type="llama", vocab_size=128256, hidden_size=4096, num_hidden_layers=32,
+                                 num_attention_heads=32, num_key_value_heads=8, intermediate_size=14336, rms_norm_eps=1e-5,
+                                 rope_theta=5e5, max_position_embeddings=8192))
+    if name in ("llama-3-70b", "llama3-70b"):
+        return from_hf_dict(dict(model_type="llama", vocab_size=128256, hidden_size=8192, num_hidden_layers=80,
+                                 num_attention_heads=64, num_key_value_heads=8, intermediate_size=28672, rms_norm_eps=1e-5,
+                                 rope_theta=5e5, max_position_embeddings=8192))
+    if name in ("qwen3-30b-a3b",):
+        return from_hf_dict(dict(model_type="qwen3_moe", vocab_size=151936, hidden_size=2048, num_hidden_layers=48,
+                                 num_attention_heads=32, num_key_value_heads=4, head_dim=128, intermediate_size=6144,
+                                 moe_intermediate_size=768, num_experts=128, num_experts_per_tok=8, norm_topk_prob=True,
+                                 rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=40960))
+    if name in ("deepseek-v3", "deepseek_v3"):
+        return from_hf_dict(dict(model_type="deepseek_v3", vocab_size=129280, hidden_size=7168, num_hidden_layers=61,
+                                 num_attention_heads=128, num_key_value_heads=128, intermediate_size=18432,
+                                 moe_intermediate_size=2048, n_routed_experts=256, num_experts_per_tok=8, n_shared_experts=1,
+                                 first_k_dense_replace=3, n_group=8, topk_group=4, routed_scaling_factor=2.5,
+                                 scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=1536,
+                                 kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=163840))
+    if name == "tiny-llama":
+        return from_hf_dict(dict(model_type="llama", vocab_size=512, hidden_size=256, num_hidden_layers=2,
+                                 num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
+                                 rms_norm_eps=1e-5, rope_theta=10000.0, max_position_embeddings=2048))
+    if name == "tiny-qwen3":
+        return from_hf_dict(dict(model_type="qwen3", vocab_size=512, hidden_size=256, num_hidden_layers=2,
+                                 num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
+                                 rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True, max_position_embeddings=2048))
+    if name == "tiny-qwen3-moe":
+        return from_hf_dict(dict(model_type="qwen3_moe", vocab_size=512, hidden_size=256, num_hidden_layers=2,
+                                 num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
+                                 moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True,
+                                 rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=2048))
+    if name == "tiny-deepseek-v3":
+        return from_hf_dict(dict(model_type="deepseek_v3", vocab_size=512, hidden_size=256, num_hidden_layers=3,
+                                 num_attention_heads=4, num_key_value_heads=4, intermediate_size=512,
+                                 moe_intermediate_size=128, n_routed_experts=16, num_experts_per_tok=4, n_shared_experts=1,
+                                 first_k_dense_replace=1, n_group=4, topk_group=2, routed_scaling_factor=2.5,
+                                 scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=96,
+                                 kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=2048))
+    raise KeyError(f"unknown preset '{name}'")

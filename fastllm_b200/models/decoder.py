@@ -1,0 +1,359 @@
+"""Generic paged-KV decoder used by every causal-LM family (dense GQA, MoE, MLA).
+
+Model families differ only in configuration (``ModelConfig``) and weight naming (``loader/hf.py``); the
+layer stack below covers what the reference implements per family in src/models/{llama,qwen2,qwen3,
+qwen3_moe,deepseekv2,glm4_moe,...}.cpp.  The per-layer sequence on CUDA is
+
+    RMSNorm -> QKV GEMM -> fused (QK-norm + RoPE + paged-KV append) -> paged attention ->
+    O-proj GEMM (+residual in the epilogue) -> RMSNorm -> gate/up GEMM (+SwiGLU in the epilogue) ->
+    down GEMM (+residual in the epilogue)
+
+With tensor parallelism the two row-parallel GEMMs (O-proj, down) hand their partial sums to
+``parallel.tp`` for the all-reduce (+residual).  All tensors are plain ``torch.Tensor`` attributes:
+there is no autograd and no nn.Module overhead on the decode path.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import torch
+
+from ..ops import attention as A
+from ..ops import basic as B
+from ..ops import moe as MOE
+from ..ops.quant import LinearWeight
+from .config import ModelConfig
+
+
+@dataclass
+class ForwardBatch:
+    """One scheduler step: packed new tokens of all scheduled requests (prefill chunks and/or decodes)."""
+    ids: torch.Tensor            # int32 [T]
+    positions: torch.Tensor      # int32 [T]
+    slots: torch.Tensor          # int32 [T]   cache slot of each new token (-1 = do not store)
+    page_table: torch.Tensor     # int32 [B, P]
+    kv_lens: torch.Tensor        # int32 [B]   cached tokens per request after this step's append
+    cu_q: torch.Tensor           # int32 [B+1]
+    logit_rows: torch.Tensor | None = None   # int64 [R] rows of the packed batch that need logits
+    is_decode: bool = False      # every request contributes exactly one token
+    cu_q_host: list | None = None
+    decode_ws: A.DecodeWorkspace | None = None
+    decode_planned: bool = False
+
+
+@dataclass
+class TPInfo:
+    rank: int = 0
+    size: int = 1
+    comm: object | None = None   # parallel.tp.TPComm
+
+    def all_reduce(self, t, residual=None):
+        if self.size == 1:
+            return t if residual is None else t + residual
+        return self.comm.all_reduce(t, residual)
+
+
+class AttentionWeights:
+    def __init__(self):
+        self.ln = None
+        self.qkv: LinearWeight | None = None
+        self.o: LinearWeight | None = None
+        self.q_norm = None
+        self.k_norm = None
+        # MLA
+        self.q_a: LinearWeight | None = None
+        self.q_a_norm = None
+        self.q_b: LinearWeight | None = None
+        self.kv_a: LinearWeight | None = None      # -> [kv_lora + rope]
+        self.kv_a_norm = None
+        self.w_uk = None       # [H, nope, kv_lora]   absorbed K up-projection
+        self.w_uv = None       # [H, v_dim, kv_lora]  absorbed V up-projection
+
+
+class MLPWeights:
+    def __init__(self):
+        self.ln = None
+        self.gate_up: LinearWeight | None = None
+        self.down: LinearWeight | None = None
+        # MoE
+        self.router = None          # fp32 [E, H]
+        self.router_bias = None     # fp32 [E]
+        self.experts: MOE.ExpertWeights | None = None
+        self.shared_gate_up: LinearWeight | None = None
+        self.shared_down: LinearWeight | None = None
+        self.shared_gate = None     # [1, H] sigmoid gate (qwen2_moe)
+
+
+class LayerWeights:
+    def __init__(self):
+        self.attn = AttentionWeights()
+        self.mlp = MLPWeights()
+
+
+class DecoderModel:
+    """Weights + forward pass of one tensor-parallel rank."""
+
+    def __init__(self, cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | None = None, ep=None):
+        self.cfg = cfg
+        self.device = torch.device(device)
+        self.dtype = dtype
+        self.tp = tp or TPInfo()
+        self.ep = ep                       # parallel.ep.EPInfo or None
+        self.embed = None                  # [vocab(/tp), H]
+        self.layers: list[LayerWeights] = []
+        self.final_norm = None
+        self.lm_head: LinearWeight | None = None
+        self.vocab_shard = (0, cfg.vocab_size)
+        self.on_cuda = self.device.type == "cuda"
+        self.num_heads_local = cfg.num_heads // self.tp.size
+        self.num_kv_heads_local = max(1, cfg.num_kv_heads // self.tp.size)
+        self.kv_replicas = max(1, self.tp.size // cfg.num_kv_heads)
+        self._rope = None
+        self.rope_mode = {"neox": A.ROPE_NEOX, "interleaved": A.ROPE_INTERLEAVED, "none": A.ROPE_NONE}[cfg.rope_mode]
+        self.rot_dim = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
+        self.attn_scale = 1.0 / math.sqrt(cfg.q_head_dim)
+        if cfg.use_mla and cfg.rope_scaling and cfg.rope_scaling.get("mscale_all_dim"):
+            ms = 0.1 * float(cfg.rope_scaling["mscale_all_dim"]) * math.log(float(cfg.rope_scaling.get("factor", 1.0))) + 1.0
+            self.attn_scale *= ms * ms
+
+    # -----------------------------------------------------------------------------------------------
+    def rope_tables(self, max_pos: int | None = None):
+        if self._rope is None:
+            mp = max_pos or min(self.cfg.max_position, 1 << 17)
+            scaling = self.cfg.rope_scaling
+            if self.cfg.use_mla and scaling:
+                # DeepSeek applies the yarn magnitude to the softmax scale (above), not to cos/sin
+                scaling = dict(scaling)
+                scaling["attention_factor"] = 1.0
+            self._rope = A.build_rope_tables(self.rot_dim, mp, self.cfg.rope_theta, scaling, self.device)
+        return self._rope
+
+    def kv_cache_shape(self, num_pages: int):
+        """Per-layer page-pool shapes of this rank: (K shape, V shape or None for MLA)."""
+        c = self.cfg
+        if c.use_mla:
+            return (num_pages, A.PAGE_LEN, 1, c.kv_lora_rank + c.qk_rope_head_dim), None
+        s = (num_pages, A.PAGE_LEN, self.num_kv_heads_local, c.head_dim)
+        return s, s
+
+    def kv_bytes_per_page(self) -> int:
+        ks, vs = self.kv_cache_shape(1)
+        n = math.prod(ks) + (math.prod(vs) if vs else 0)
+        return n * self.cfg.num_layers * torch.finfo(self.dtype).bits // 8
+
+    # -----------------------------------------------------------------------------------------------
+    def _attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual):
+        c = self.cfg
+        if c.use_mla:
+            return self._mla_attention(lw, x, fb, kv, residual)
+        Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
+        cos, sin = self.rope_tables()
+        qkv = lw.qkv(x)
+        k_pool, v_pool = kv
+        q = A.qkv_post(qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
+                       lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
+        if fb.is_decode:
+            a = A.attn_decode(q, k_pool, v_pool, fb.page_table, fb.kv_lens, self.attn_scale, Hq, Hkv, D, ws=fb.decode_ws,
+                              planned=fb.decode_planned)
+        else:
+            a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
+                               cu_q_host=fb.cu_q_host)
+        return self._row_parallel(lw.o, a, residual)
+
+    def _row_parallel(self, w: LinearWeight, x, residual):
+        """Row-parallel linear (input dim sharded): partial GEMM, then sum over ranks, plus the residual."""
+        if self.tp.size == 1:
+            return w(x, residual=residual)
+        return self.tp.comm.row_linear(w, x, residual)
+
+    def _mla_attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual):
+        """Absorbed multi-head latent attention over a paged latent cache (kv_lora + rope dims per token).
+
+        Reference: src/models/deepseekv2.cpp:283-697 (q_nope x W_UK -> MergeMLAPaged -> x W_UV -> o_proj).
+        """
+        c = self.cfg
+        H = self.num_heads_local
+        nope, rope, lora, vd = c.qk_nope_head_dim, c.qk_rope_head_dim, c.kv_lora_rank, c.v_head_dim
+        T = x.shape[0]
+        if lw.q_a is not None:
+            q = lw.q_b(B.rmsnorm(lw.q_a(x), lw.q_a_norm, c.rms_eps))
+        else:
+            q = lw.q_b(x)
+        q = q.view(T, H, nope + rope)
+        ckv = lw.kv_a(x)                                   # [T, lora + rope]
+        c_lat = B.rmsnorm(ckv[:, :lora].contiguous(), lw.kv_a_norm, c.rms_eps)
+        cos, sin = self.rope_tables()
+        k_pe = A.apply_rope_ref(ckv[:, lora:].reshape(T, 1, rope), fb.positions, cos, sin, self.rope_mode, rope)
+        q_pe = A.apply_rope_ref(q[..., nope:], fb.positions, cos, sin, self.rope_mode, rope)
+        lat_pool = kv[0]
+        flat = lat_pool.view(-1, lora + rope)
+        valid = fb.slots >= 0
+        entry = torch.cat([c_lat, k_pe.reshape(T, rope)], dim=-1).to(flat.dtype)
+        if bool(valid.all()):
+            flat[fb.slots.long()] = entry
+        else:
+            flat[fb.slots[valid].long()] = entry[valid]
+        # absorb: q_lat[h] = q_nope[h] @ W_UK[h]  -> attention in latent space with a single shared "KV head"
+        q_lat = torch.einsum("thn,hnl->thl", q[..., :nope].float(), lw.w_uk.float()).to(x.dtype)
+        q_full = torch.cat([q_lat, q_pe.to(x.dtype)], dim=-1)              # [T, H, lora + rope]
+        o_lat = MOE.mla_paged_attention(q_full, lat_pool, fb, self.attn_scale, lora)   # [T, H, lora]
+        o = torch.einsum("thl,hvl->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype).reshape(T, H * vd)
+        return self._row_parallel(lw.o, o, residual)
+
+    # -----------------------------------------------------------------------------------------------
+    def _mlp(self, lw: MLPWeights, x, residual, layer_idx):
+        c = self.cfg
+        if lw.experts is None:
+            act = lw.gate_up(x, swiglu=True)
+            return self._row_parallel(lw.down, act, residual)
+        # ---- mixture of experts ----
+        logits = torch.matmul(x.float(), lw.router.t())
+        idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
+                                  0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
+                                  c.routed_scaling_factor)
+        y = MOE.moe_forward(x, idx, wts, lw.experts, self.ep)
+        if lw.shared_gate_up is not None:
+            s = lw.shared_down(lw.shared_gate_up(x, swiglu=True))
+            if lw.shared_gate is not None:
+                s = s * torch.sigmoid(torch.matmul(x.float(), lw.shared_gate.float().t())).to(s.dtype)
+            y = y + s
+        if self.tp.size > 1 and (self.ep is None or lw.shared_gate_up is not None) and not MOE.output_is_complete(self.ep):
+            return self.tp.all_reduce(y, residual)
+        return y + residual
+
+    # -----------------------------------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, fb: ForwardBatch, kv_caches) -> torch.Tensor:
+        """Returns fp32 logits ``[R, vocab_local]`` for ``fb.logit_rows`` (all rows if None)."""
+        c = self.cfg
+        h = self.embed_tokens(fb.ids)
+        for i, lw in enumerate(self.layers):
+            x = B.rmsnorm(h, lw.attn.ln, c.rms_eps, unit_offset=c.norm_unit_offset)
+            h = self._attention(lw.attn, x, fb, kv_caches[i], h)
+            x = B.rmsnorm(h, lw.mlp.ln, c.rms_eps, unit_offset=c.norm_unit_offset)
+            h = self._mlp(lw.mlp, x, h, i)
+        if fb.logit_rows is not None:
+            h = h.index_select(0, fb.logit_rows)
+        x = B.rmsnorm(h, self.final_norm, c.rms_eps, unit_offset=c.norm_unit_offset)
+        logits = self.lm_head(x, out_f32=True)
+        if c.logit_scale != 1.0:
+            logits = logits * c.logit_scale
+        return logits
+
+    def embed_tokens(self, ids):
+        c = self.cfg
+        if self.tp.size > 1 and self.embed.shape[0] != c.vocab_size:
+            lo, hi = self.vocab_shard
+            local = ids - lo
+            mask = (local >= 0) & (local < hi - lo)
+            h = B.embedding(torch.where(mask, local, torch.zeros_like(local)), self.embed)
+            h = h * mask[:, None].to(h.dtype)
+            h = self.tp.all_reduce(h)
+        else:
+            h = B.embedding(ids, self.embed)
+        if c.embed_scale != 1.0:
+            h = h * c.embed_scale
+        return h
+
+
+# ---------------------------------------------------------------------------------------------------
+# random initialisation of a full model of the given architecture (benchmarks and tests)
+# ---------------------------------------------------------------------------------------------------
+def _randn(shape, std, device, dtype, gen):
+    # generate in fp32 chunks on the target device to bound peak memory
+    return (torch.randn(shape, device=device, dtype=torch.float32, generator=gen) * std).to(dtype)
+
+
+def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | None = None, ep=None, seed: int = 0,
+                std: float = 0.02, wdtype: str = "auto", moe_wdtype: str | None = None) -> DecoderModel:
+    """Build a model with N(0, std) weights and unit norm weights, sharded for this TP/EP rank.
+
+    Every rank draws the full tensor from the same seed and keeps its shard, so a TP group is numerically
+    a sharding of one model.  ``wdtype`` / ``moe_wdtype`` select weight quantisation (see ops.quant).
+    """
+    from ..loader.shard import finalize_model   # local import: loader depends on this module
+
+    tp = tp or TPInfo()
+    m = DecoderModel(cfg, device, dtype, tp, ep)
+    dev = m.device
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    H = cfg.hidden_size
+    raw: dict[str, torch.Tensor] = {}
+
+    def mk(name, shape, s=std):
+        raw[name] = _randn(shape, s, dev, dtype, gen)
+
+    def ones(name, n):
+        raw[name] = torch.ones(n, device=dev, dtype=dtype)
+
+    # The state dict is produced layer by layer and consumed immediately to bound memory.
+    def layer_tensors(i):
+        raw.clear()
+        p = f"model.layers.{i}."
+        ones(p + "input_layernorm.weight", H)
+        ones(p + "post_attention_layernorm.weight", H)
+        if cfg.use_mla:
+            qd = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
+            if cfg.q_lora_rank:
+                mk(p + "self_attn.q_a_proj.weight", (cfg.q_lora_rank, H))
+                ones(p + "self_attn.q_a_layernorm.weight", cfg.q_lora_rank)
+                mk(p + "self_attn.q_b_proj.weight", (cfg.num_heads * qd, cfg.q_lora_rank))
+            else:
+                mk(p + "self_attn.q_proj.weight", (cfg.num_heads * qd, H))
+            mk(p + "self_attn.kv_a_proj_with_mqa.weight", (cfg.kv_lora_rank + cfg.qk_rope_head_dim, H))
+            ones(p + "self_attn.kv_a_layernorm.weight", cfg.kv_lora_rank)
+            mk(p + "self_attn.kv_b_proj.weight", (cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank))
+            mk(p + "self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim))
+        else:
+            D = cfg.head_dim
+            mk(p + "self_attn.q_proj.weight", (cfg.num_heads * D, H))
+            mk(p + "self_attn.k_proj.weight", (cfg.num_kv_heads * D, H))
+            mk(p + "self_attn.v_proj.weight", (cfg.num_kv_heads * D, H))
+            mk(p + "self_attn.o_proj.weight", (H, cfg.num_heads * D))
+            if cfg.attention_bias:
+                mk(p + "self_attn.q_proj.bias", (cfg.num_heads * D,))
+                mk(p + "self_attn.k_proj.bias", (cfg.num_kv_heads * D,))
+                mk(p + "self_attn.v_proj.bias", (cfg.num_kv_heads * D,))
+            if cfg.qk_norm:
+                ones(p + "self_attn.q_norm.weight", D)
+                ones(p + "self_attn.k_norm.weight", D)
+        if cfg.layer_is_moe(i):
+            mk(p + "mlp.gate.weight", (cfg.num_experts, H))
+            if cfg.router_bias:
+                raw[p + "mlp.gate.e_score_correction_bias"] = torch.zeros(cfg.num_experts, device=dev, dtype=torch.float32)
+            lo, hi = MOE.local_expert_range(cfg.num_experts, ep)
+            I = cfg.moe_intermediate_size
+            # draw all experts' weights (keeps every rank's generator in step), keep the local ones
+            for e in range(cfg.num_experts):
+                keep = lo <= e < hi
+                for nm, shp in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+                    t = _randn(shp, std, dev, dtype, gen)
+                    if keep:
+                        raw[p + f"mlp.experts.{e}.{nm}.weight"] = t
+            if cfg.num_shared_experts:
+                SI = cfg.shared_expert_intermediate_size
+                sp = p + ("mlp.shared_expert." if cfg.shared_expert_gate else "mlp.shared_experts.")
+                mk(sp + "gate_proj.weight", (SI, H))
+                mk(sp + "up_proj.weight", (SI, H))
+                mk(sp + "down_proj.weight", (H, SI))
+                if cfg.shared_expert_gate:
+                    mk(p + "mlp.shared_expert_gate.weight", (1, H))
+        else:
+            I = cfg.intermediate_size
+            mk(p + "mlp.gate_proj.weight", (I, H))
+            mk(p + "mlp.up_proj.weight", (I, H))
+            mk(p + "mlp.down_proj.weight", (H, I))
+        return raw
+
+    def top_tensors():
+        raw.clear()
+        mk("model.embed_tokens.weight", (cfg.vocab_size, H))
+        ones("model.norm.weight", H)
+        if not cfg.tie_embeddings:
+            mk("lm_head.weight", (cfg.vocab_size, H))
+        return raw
+
+    finalize_model(m, top_tensors, layer_tensors, wdtype=wdtype, moe_wdtype=moe_wdtype)
+    return m

@@ -1,0 +1,133 @@
+"""ctypes loader for the in-tree native libraries.
+
+``kernels()`` returns the CUDA kernel library (``lib/libfb_kernels.so``); it raises if the library is
+missing while a GPU is present, so that a GPU run can never silently fall back to the PyTorch path.
+``runtime()`` returns the host runtime library (``lib/libfb_runtime.so``).
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from pathlib import Path
+
+_LIB_DIR = Path(__file__).resolve().parent.parent / "lib"
+_lock = threading.Lock()
+_kernels = None
+_runtime = None
+
+P = c_void_p
+I = c_int
+F = c_float
+LL = c_longlong
+
+_KERNEL_SIGS = {
+    "fb_gemm_16bit": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
+    "fb_gemm_pick_split": [I, I, I, I],
+    "fb_rmsnorm": [P, P, P, P, I, I, I, I, F, F, I, P],
+    "fb_qkv_post": [P, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
+    "fb_silu_mul": [P, P, I, I, I, I, I, P],
+    "fb_embedding": [P, P, P, I, I, I, P],
+    "fb_argmax": [P, P, P, I, I, I, I, I, P],
+    "fb_route_topk": [P, P, P, P, I, I, I, I, I, I, I, F, P],
+    "fb_attn_decode_plan": [P, I, P, P, I, P],
+    "fb_attn_decode": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, LL, I, I, F, I, I, P],
+    "fb_attn_prefill": [P, I, LL, P, P, P, I, P, I, P, P, P, I, I, I, LL, I, F, I, P],
+}
+
+_ERROR_READERS = ["gemm", "elementwise", "attn_decode", "attn_prefill"]
+
+
+class KernelLibraryMissing(RuntimeError):
+    pass
+
+
+def kernels():
+    global _kernels
+    if _kernels is not None:
+        return _kernels
+    with _lock:
+        if _kernels is not None:
+            return _kernels
+        path = _LIB_DIR / "libfb_kernels.so"
+        if not path.exists():
+            raise KernelLibraryMissing(
+                f"{path} not found: run `python -m fastllm_b200.build` (sm_100a kernels are required on GPU)")
+        lib = ctypes.CDLL(str(path))
+        for name, args in _KERNEL_SIGS.items():
+            if hasattr(lib, name):
+                fn = getattr(lib, name)
+                fn.argtypes = args
+                fn.restype = c_int
+        for name in list(_ERROR_READERS):
+            fn = getattr(lib, f"fb_{name}_read_error", None)
+            if fn is not None:
+                fn.argtypes = [ctypes.POINTER(c_int), c_int]
+                fn.restype = c_int
+        _kernels = lib
+        return lib
+
+
+def register_sigs(sigs: dict, error_readers: list[str] | None = None) -> None:
+    """Let other op modules add signatures for kernels that live in the same library."""
+    _KERNEL_SIGS.update(sigs)
+    if error_readers:
+        for r in error_readers:
+            if r not in _ERROR_READERS:
+                _ERROR_READERS.append(r)
+    if _kernels is not None:
+        for name, args in sigs.items():
+            if hasattr(_kernels, name):
+                fn = getattr(_kernels, name)
+                fn.argtypes = args
+                fn.restype = c_int
+        for name in error_readers or []:
+            fn = getattr(_kernels, f"fb_{name}_read_error", None)
+            if fn is not None:
+                fn.argtypes = [ctypes.POINTER(c_int), c_int]
+                fn.restype = c_int
+
+
+class DeviceKernelError(RuntimeError):
+    """A kernel recorded an error (bounded wait ran out, bad argument) in its device-side status word."""
+
+
+def check_device_errors(reset: bool = True) -> None:
+    """Read every translation unit's device error word; raise if any kernel reported a problem.
+
+    Costs one small device-to-host copy per translation unit, so call it between steps, not per kernel.
+    """
+    lib = kernels()
+    buf = (c_int * 8)()
+    for name in _ERROR_READERS:
+        fn = getattr(lib, f"fb_{name}_read_error", None)
+        if fn is None:
+            continue
+        rc = fn(buf, 1 if reset else 0)
+        if rc != 0:
+            raise DeviceKernelError(f"reading error word of '{name}' failed with cudaError {rc}")
+        if buf[0] != 0:
+            raise DeviceKernelError(
+                f"kernel error in '{name}': code={buf[0]} kernel_id={buf[1]} site={buf[2]} block=({buf[3]},{buf[4]})")
+
+
+def runtime():
+    global _runtime
+    if _runtime is not None:
+        return _runtime
+    with _lock:
+        if _runtime is not None:
+            return _runtime
+        path = _LIB_DIR / "libfb_runtime.so"
+        if not path.exists():
+            from .. import build
+
+            build.build_runtime()
+        _runtime = ctypes.CDLL(str(path))
+        return _runtime
+
+
+def check(rc: int, what: str) -> None:
+    if rc != 0:
+        raise RuntimeError(f"{what} failed with code {rc}")

@@ -1,0 +1,251 @@
+"""RoPE tables, fused QKV post-processing and paged attention.
+
+KV cache layout is ``[num_pages, page_len, kv_heads, head_dim]`` per layer for K and for V (the
+reference's page pool shape, include/fastllm.h:643-698, page_len 128); a token's ``slot`` is
+``page * page_len + offset``.
+
+CUDA tensors run the sm_100a kernels (``attn_decode.cu``, ``attn_prefill.cu``, ``elementwise.cu``);
+CPU tensors run the PyTorch definitions below, which double as the test oracle.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _lib
+from .basic import _ptr, _stream, dtype_code
+
+PAGE_LEN = 128
+ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
+
+
+# ---------------------------------------------------------------------------------------------------
+# RoPE tables: all frequency-scaling variants reduce to a (cos, sin) table indexed by position.
+# Reference kernels: RopeEncoding / Llama3RopeEncoding / YarnRopeEncoding
+# (src/devices/cuda/fastllm-cuda.cu:2340, 2510, 2417) and the linear / dynamic-NTK handling in
+# src/models/llama.cpp:82-93.
+# ---------------------------------------------------------------------------------------------------
+def _yarn_find_dim(num_rot, dim, base, max_pos):
+    return (dim * math.log(max_pos / (num_rot * 2 * math.pi))) / (2 * math.log(base))
+
+
+def rope_inv_freq(rot_dim: int, base: float, scaling: dict | None = None, max_pos: int = 0):
+    """Return (inv_freq [rot_dim/2] float64 tensor, attention scale factor)."""
+    inv = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+    mscale = 1.0
+    if not scaling:
+        return inv, mscale
+    kind = scaling.get("rope_type", scaling.get("type", "default"))
+    factor = float(scaling.get("factor", 1.0))
+    if kind == "linear":
+        inv = inv / factor
+    elif kind == "dynamic":
+        orig = int(scaling.get("original_max_position_embeddings", max_pos or 2048))
+        if max_pos > orig:
+            nb = base * ((factor * max_pos / orig) - (factor - 1)) ** (rot_dim / (rot_dim - 2))
+            inv = 1.0 / (nb ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+    elif kind == "llama3":
+        lo = float(scaling.get("low_freq_factor", 1.0))
+        hi = float(scaling.get("high_freq_factor", 4.0))
+        orig = float(scaling.get("original_max_position_embeddings", 8192))
+        wavelen = 2 * math.pi / inv
+        smooth = (orig / wavelen - lo) / (hi - lo)
+        scaled = torch.where(wavelen > orig / lo, inv / factor, inv)
+        mid = (wavelen <= orig / lo) & (wavelen >= orig / hi)
+        inv = torch.where(mid, (1 - smooth) * inv / factor + smooth * inv, scaled)
+    elif kind == "yarn":
+        orig = int(scaling.get("original_max_position_embeddings", 4096))
+        beta_fast = float(scaling.get("beta_fast", 32))
+        beta_slow = float(scaling.get("beta_slow", 1))
+        low = max(math.floor(_yarn_find_dim(beta_fast, rot_dim, base, orig)), 0)
+        high = min(math.ceil(_yarn_find_dim(beta_slow, rot_dim, base, orig)), rot_dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(rot_dim // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
+        inv_mask = 1 - ramp
+        inv = inv / factor * (1 - inv_mask) + inv * inv_mask
+        ms = float(scaling.get("mscale", 1.0))
+        ms_all = float(scaling.get("mscale_all_dim", 0.0))
+
+        def get_mscale(scale, m):
+            return 1.0 if scale <= 1 else 0.1 * m * math.log(scale) + 1.0
+
+        if "attention_factor" in scaling and scaling["attention_factor"] is not None:
+            mscale = float(scaling["attention_factor"])
+        elif ms_all:
+            mscale = get_mscale(factor, ms) / get_mscale(factor, ms_all)
+        else:
+            mscale = get_mscale(factor, 1.0)
+    return inv, mscale
+
+
+def build_rope_tables(rot_dim: int, max_pos: int, base: float, scaling: dict | None = None, device="cpu"):
+    """(cos, sin) fp32 tables ``[max_pos, rot_dim/2]``; the yarn magnitude factor is folded in."""
+    inv, mscale = rope_inv_freq(rot_dim, base, scaling, max_pos)
+    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
+    return (ang.cos() * mscale).float().to(device).contiguous(), (ang.sin() * mscale).float().to(device).contiguous()
+
+
+def apply_rope_ref(x, positions, cos, sin, mode, rot):
+    """x: [T, H, D]; rotates the first ``rot`` dims. fp32 math, returns x.dtype."""
+    if mode == ROPE_NONE:
+        return x
+    xf = x.float()
+    c = cos[positions.long()][:, None, :]
+    s = sin[positions.long()][:, None, :]
+    xr, rest = xf[..., :rot], xf[..., rot:]
+    if mode == ROPE_NEOX:
+        a, b = xr[..., : rot // 2], xr[..., rot // 2:]
+        out = torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+    else:
+        a, b = xr[..., 0::2], xr[..., 1::2]
+        out = torch.stack([a * c - b * s, a * s + b * c], dim=-1).flatten(-2)
+    return torch.cat([out, rest], dim=-1).to(x.dtype)
+
+
+def _head_norm_ref(x, w, eps, unit_offset):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * (w.float() + unit_offset)).to(x.dtype)
+
+
+def qkv_post(qkv, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, head_dim, cos, sin, rope_mode=ROPE_NEOX,
+             rot_dim=None, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_unit_offset=0.0, q_out=None):
+    """Split packed QKV, per-head RMSNorm on Q/K (optional), RoPE, append K/V to the page pools, return Q.
+
+    qkv: ``[T, (Hq + 2 Hkv) * D]``; positions, slots: int32 ``[T]``; pools ``[pages, page_len, Hkv, D]``.
+    One launch on CUDA (reference: QKVRMSNormRopeSplitAppendPagedCache, src/devices/cuda/fastllm-cuda.cu:12190).
+    """
+    T = qkv.shape[0]
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    rot = rot_dim or D
+    if not qkv.is_cuda:
+        q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+        q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
+        if q_norm_w is not None:
+            q = _head_norm_ref(q, q_norm_w, eps, norm_unit_offset)
+        if k_norm_w is not None:
+            k = _head_norm_ref(k, k_norm_w, eps, norm_unit_offset)
+        q = apply_rope_ref(q, positions, cos, sin, rope_mode, rot)
+        k = apply_rope_ref(k, positions, cos, sin, rope_mode, rot)
+        valid = slots >= 0
+        kp = k_pool.view(-1, Hkv, D)
+        vp = v_pool.view(-1, Hkv, D)
+        kp[slots[valid].long()] = k[valid].to(kp.dtype)
+        vp[slots[valid].long()] = v[valid].to(vp.dtype)
+        return q.reshape(T, Hq * D)
+    if q_out is None:
+        q_out = torch.empty((T, Hq * D), device=qkv.device, dtype=qkv.dtype)
+    rc = _lib.kernels().fb_qkv_post(_ptr(qkv), qkv.stride(0), _ptr(q_out), q_out.stride(0), _ptr(k_pool), _ptr(v_pool),
+                                    _ptr(positions), _ptr(slots), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos), _ptr(sin), T, Hq,
+                                    Hkv, D, rot, rope_mode, float(eps), float(norm_unit_offset), dtype_code(qkv.dtype),
+                                    _stream())
+    _lib.check(rc, "fb_qkv_post")
+    return q_out
+
+
+# ---------------------------------------------------------------------------------------------------
+# paged attention
+# ---------------------------------------------------------------------------------------------------
+def paged_attention_ref(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim):
+    """Causal attention of packed new tokens against the paged cache (fp32 math).
+
+    q: ``[T, Hq*D]``; request b owns rows ``cu_q[b]:cu_q[b+1]`` whose absolute positions are the last
+    ``q_len`` positions of its ``kv_lens[b]`` cached tokens.  Decode is the case q_len == 1.
+    """
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    G = Hq // Hkv
+    out = torch.zeros_like(q)
+    page_len = k_pool.shape[1]
+    cu = cu_q.tolist()
+    for b in range(len(cu) - 1):
+        q0, q1 = cu[b], cu[b + 1]
+        if q1 == q0:
+            continue
+        L = int(kv_lens[b])
+        npg = (L + page_len - 1) // page_len
+        pages = page_table[b, :npg].long()
+        k = k_pool[pages].reshape(-1, Hkv, D)[:L].float()
+        v = v_pool[pages].reshape(-1, Hkv, D)[:L].float()
+        qq = q[q0:q1].reshape(q1 - q0, Hkv, G, D).float()
+        s = torch.einsum("qhgd,khd->hgqk", qq, k) * scale
+        qpos = torch.arange(L - (q1 - q0), L, device=q.device)[:, None]
+        kpos = torch.arange(L, device=q.device)[None, :]
+        s = s.masked_fill(kpos > qpos, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        o = torch.einsum("hgqk,khd->qhgd", p, v)
+        out[q0:q1] = o.reshape(q1 - q0, Hq * D).to(q.dtype)
+    return out
+
+
+class DecodeWorkspace:
+    """Device scratch for split-KV decode attention, sized once for (max_batch, max_pages_per_seq)."""
+
+    def __init__(self, max_batch, num_kv_heads, group, max_pages, device, head_dim=128):
+        self.max_batch, self.max_pages = max_batch, max_pages
+        self.work = torch.zeros((max_batch * max_pages, 2), device=device, dtype=torch.int32)
+        self.n_work = torch.zeros((1,), device=device, dtype=torch.int32)
+        self.part_o = torch.empty((max_batch * num_kv_heads * max_pages * group * head_dim,), device=device,
+                                  dtype=torch.float32)
+        self.part_ml = torch.empty((max_batch * num_kv_heads * max_pages * group * 2,), device=device, dtype=torch.float32)
+
+    def plan(self, seq_lens: torch.Tensor):
+        """Flatten (request, page) work items for the current sequence lengths (one tiny launch per step)."""
+        B = seq_lens.numel()
+        rc = _lib.kernels().fb_attn_decode_plan(_ptr(seq_lens), B, _ptr(self.work), _ptr(self.n_work),
+                                                self.work.shape[0], _stream())
+        _lib.check(rc, "fb_attn_decode_plan")
+
+
+def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num_kv_heads, head_dim,
+                ws: DecodeWorkspace | None = None, out=None, planned=False, grid_ctas=0):
+    """One new token per request. q: ``[B, Hq*D]`` -> ``[B, Hq*D]``."""
+    B = q.shape[0]
+    if not q.is_cuda:
+        cu = torch.arange(B + 1, dtype=torch.int32)
+        return paged_attention_ref(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim)
+    G = num_q_heads // num_kv_heads
+    if head_dim != 128 or G > 16 or k_pool.shape[1] != PAGE_LEN:
+        cu = torch.arange(B + 1, dtype=torch.int32, device=q.device)
+        return paged_attention_ref(q, k_pool, v_pool, page_table, seq_lens.cpu(), cu.cpu(), scale, num_q_heads, num_kv_heads,
+                                   head_dim)
+    if ws is None:
+        ws = DecodeWorkspace(B, num_kv_heads, G, page_table.shape[1], q.device)
+    if not planned:
+        ws.plan(seq_lens)
+    if out is None:
+        out = torch.empty_like(q)
+    num_slots = k_pool.shape[0] * k_pool.shape[1]
+    rc = _lib.kernels().fb_attn_decode(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(ws.work),
+                                       _ptr(ws.n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
+                                       num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
+                                       float(scale), dtype_code(q.dtype), grid_ctas, _stream())
+    _lib.check(rc, "fb_attn_decode")
+    return out
+
+
+def attn_prefill(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim, out=None,
+                 cu_q_host=None):
+    """Packed causal prefill (also chunked prefill / prefix-cache continuation). q: ``[T, Hq*D]``."""
+    if not q.is_cuda or head_dim != 128 or k_pool.shape[1] != PAGE_LEN:
+        o = paged_attention_ref(q, k_pool, v_pool, page_table, kv_lens.cpu(), cu_q.cpu(), scale, num_q_heads, num_kv_heads,
+                                head_dim)
+        return o
+    cu = cu_q_host if cu_q_host is not None else cu_q.tolist()
+    blocks = []
+    for b in range(len(cu) - 1):
+        for q0 in range(0, cu[b + 1] - cu[b], 128):
+            blocks.append((b, q0))
+    if out is None:
+        out = torch.empty_like(q)
+    if not blocks:
+        return out
+    blk = torch.tensor(blocks, dtype=torch.int32).to(q.device, non_blocking=True)
+    num_slots = k_pool.shape[0] * k_pool.shape[1]
+    rc = _lib.kernels().fb_attn_prefill(_ptr(q), q.stride(0), q.shape[0], _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0),
+                                        _ptr(blk), len(blocks), _ptr(cu_q), _ptr(kv_lens), _ptr(page_table), num_q_heads,
+                                        num_kv_heads, head_dim, num_slots, page_table.stride(0), float(scale),
+                                        dtype_code(q.dtype), _stream())
+    _lib.check(rc, "fb_attn_prefill")
+    return out

@@ -1,0 +1,196 @@
+"""Dense operators: Linear (+bias, +residual, +SwiGLU), RMSNorm, SiLU-mul, embedding, arg-max.
+
+On CUDA tensors every function launches the hand-written sm_100a kernels from ``libfb_kernels.so``; on
+CPU tensors it evaluates the plain PyTorch definition, which is also the numerical oracle of the tests.
+Operator semantics follow the reference's op API (include/fastllm.h:874-1318): ``Linear(x[n,m], W[k,m],
+b[k]) -> y[n,k]`` with weights stored ``[out, in]`` row-major.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+
+GEMM_BIAS, GEMM_RESIDUAL, GEMM_SWIGLU, GEMM_OUT_F32 = 1, 2, 4, 8
+
+
+def _ptr(t):
+    return ctypes.c_void_p(t.data_ptr()) if t is not None else ctypes.c_void_p(0)
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.bfloat16:
+        return 1
+    if dt == torch.float16:
+        return 0
+    raise TypeError(f"16-bit kernels need fp16/bf16, got {dt}")
+
+
+# ---------------------------------------------------------------------------------------------------
+# gate/up weight interleave used by the fused SwiGLU epilogue
+# ---------------------------------------------------------------------------------------------------
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """Stack gate and up rows so that every 128-row tile holds 64 gate rows followed by their 64 up rows.
+
+    Works for weights ``[I, H]`` and for per-row vectors ``[I]`` (biases, scales).  ``I`` must be a
+    multiple of 64.
+    """
+    inter = w_gate.shape[0]
+    if inter % 64 != 0:
+        raise ValueError("intermediate size must be a multiple of 64 for the fused SwiGLU layout")
+    rest = w_gate.shape[1:]
+    g = w_gate.reshape(inter // 64, 64, *rest)
+    u = w_up.reshape(inter // 64, 64, *rest)
+    return torch.cat([g, u], dim=1).reshape(2 * inter, *rest).contiguous()
+
+
+def deinterleave_gate_up(w: torch.Tensor):
+    inter = w.shape[0] // 2
+    rest = w.shape[1:]
+    t = w.reshape(inter // 64, 2, 64, *rest)
+    return t[:, 0].reshape(inter, *rest), t[:, 1].reshape(inter, *rest)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Linear
+# ---------------------------------------------------------------------------------------------------
+def linear_ref(x, w, bias=None, residual=None, swiglu=False, interleaved=True, out_dtype=None):
+    """fp32 reference of ``linear``; mirrors the fused epilogue order (bias -> swiglu -> residual)."""
+    y = x.float() @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if swiglu:
+        if interleaved:
+            n = y.shape[-1]
+            t = y.reshape(*y.shape[:-1], n // 128, 2, 64)
+            g, u = t[..., 0, :], t[..., 1, :]
+            y = (F.silu(g) * u).reshape(*y.shape[:-1], n // 2)
+        else:
+            g, u = y.chunk(2, dim=-1)
+            y = F.silu(g) * u
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(out_dtype or x.dtype)
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: bool = False, interleaved: bool = True,
+           out_f32: bool = False, out: torch.Tensor | None = None, nsplit: int = 0) -> torch.Tensor:
+    """``y = x @ w.T`` with optional fused bias, SwiGLU (``w`` = gate/up stacked) and residual add.
+
+    x: ``[M, K]`` (row stride may exceed K), w: ``[N, K]``.  16-bit CUDA tensors run the tcgen05 GEMM.
+    """
+    if not x.is_cuda:
+        return linear_ref(x, w, bias, residual, swiglu, interleaved, torch.float32 if out_f32 else None)
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    N = w.shape[0]
+    if swiglu and not interleaved:
+        raise ValueError("CUDA SwiGLU epilogue needs tile-interleaved gate/up weights (interleave_gate_up)")
+    n_out = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((M, n_out), device=x.device, dtype=torch.float32 if out_f32 else x.dtype)
+    flags = (GEMM_BIAS if bias is not None else 0) | (GEMM_RESIDUAL if residual is not None else 0) | \
+            (GEMM_SWIGLU if swiglu else 0) | (GEMM_OUT_F32 if out_f32 else 0)
+    res2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
+    lib = _lib.kernels()
+    dt = dtype_code(x.dtype)
+    if M <= 256 or N % 32 != 0:
+        step = 256
+        for m0 in range(0, M, step):
+            m1 = min(M, m0 + step)
+            rc = lib.fb_gemm_16bit(_ptr(x2[m0:m1]), _ptr(w), _ptr(out[m0:m1]), _ptr(bias),
+                                   _ptr(res2[m0:m1]) if res2 is not None else _ptr(None), m1 - m0, N, K, x2.stride(0),
+                                   w.stride(0), out.stride(0), res2.stride(0) if res2 is not None else 0, dt, flags, nsplit,
+                                   _stream())
+            _lib.check(rc, "fb_gemm_16bit")
+    else:
+        rc = lib.fb_gemm_16bit(_ptr(x2), _ptr(w), _ptr(out), _ptr(bias), _ptr(res2), M, N, K, x2.stride(0), w.stride(0),
+                               out.stride(0), res2.stride(0) if res2 is not None else 0, dt, flags, nsplit, _stream())
+        _lib.check(rc, "fb_gemm_16bit")
+    return out.reshape(*lead, n_out)
+
+
+# ---------------------------------------------------------------------------------------------------
+# RMSNorm
+# ---------------------------------------------------------------------------------------------------
+def rmsnorm_ref(x, w, eps, residual=None, unit_offset=0.0):
+    h = x.float()
+    if residual is not None:
+        h = (h + residual.float()).to(x.dtype).float()
+    y = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps) * (w.float() + unit_offset)
+    return y.to(x.dtype), (h.to(x.dtype) if residual is not None else None)
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None, unit_offset: float = 0.0,
+            out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm over the last dim.  With ``residual`` given: ``residual += x`` in place, then normalise it."""
+    if not x.is_cuda:
+        y, new_res = rmsnorm_ref(x, w, eps, residual, unit_offset)
+        if residual is not None:
+            residual.copy_(new_res)
+        return y
+    x2 = x.reshape(-1, x.shape[-1])
+    M, H = x2.shape
+    if out is None:
+        out = torch.empty((M, H), device=x.device, dtype=x.dtype)
+    if residual is not None and not residual.is_contiguous():
+        raise ValueError("residual must be contiguous")
+    rc = _lib.kernels().fb_rmsnorm(_ptr(x2), _ptr(w), _ptr(out), _ptr(residual), M, H, x2.stride(0), out.stride(0), float(eps),
+                                   float(unit_offset), dtype_code(x.dtype), _stream())
+    _lib.check(rc, "fb_rmsnorm")
+    return out.reshape(x.shape)
+
+
+# ---------------------------------------------------------------------------------------------------
+# SiLU-mul, embedding, arg-max
+# ---------------------------------------------------------------------------------------------------
+def silu_mul(x: torch.Tensor) -> torch.Tensor:
+    """``silu(x[..., :I]) * x[..., I:]``"""
+    inter = x.shape[-1] // 2
+    if not x.is_cuda:
+        g, u = x.float().chunk(2, dim=-1)
+        return (F.silu(g) * u).to(x.dtype)
+    x2 = x.reshape(-1, x.shape[-1])
+    out = torch.empty((x2.shape[0], inter), device=x.device, dtype=x.dtype)
+    rc = _lib.kernels().fb_silu_mul(_ptr(x2), _ptr(out), x2.shape[0], inter, x2.stride(0), out.stride(0), dtype_code(x.dtype),
+                                    _stream())
+    _lib.check(rc, "fb_silu_mul")
+    return out.reshape(*x.shape[:-1], inter)
+
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    if not table.is_cuda or table.dtype not in (torch.float16, torch.bfloat16):
+        return F.embedding(ids.long(), table)
+    ids32 = ids.reshape(-1).to(torch.int32)
+    M, H = ids32.numel(), table.shape[1]
+    if out is None:
+        out = torch.empty((M, H), device=table.device, dtype=table.dtype)
+    rc = _lib.kernels().fb_embedding(_ptr(ids32), _ptr(table), _ptr(out), M, H, table.shape[0], _stream())
+    _lib.check(rc, "fb_embedding")
+    return out.reshape(*ids.shape, H)
+
+
+def argmax(logits: torch.Tensor, id_offset: int = 0, want_values: bool = False, out: torch.Tensor | None = None):
+    """Row-wise arg-max (ties -> lowest index) as int32; optionally also the max values (fp32)."""
+    if not logits.is_cuda:
+        v, i = logits.float().max(dim=-1)
+        i = (i + id_offset).to(torch.int32)
+        return (i, v) if want_values else i
+    l2 = logits.reshape(-1, logits.shape[-1])
+    M, V = l2.shape
+    ids = out if out is not None else torch.empty((M,), device=logits.device, dtype=torch.int32)
+    vals = torch.empty((M,), device=logits.device, dtype=torch.float32) if want_values else None
+    kind = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}[logits.dtype]
+    rc = _lib.kernels().fb_argmax(_ptr(l2), _ptr(ids), _ptr(vals), M, V, l2.stride(0), id_offset, kind, _stream())
+    _lib.check(rc, "fb_argmax")
+    return (ids, vals) if want_values else ids

@@ -1,0 +1,181 @@
+"""Numerics of every CUDA kernel against the plain PyTorch fp32 definition of the same op."""
+import math
+
+import pytest
+import torch
+
+from fastllm_b200.ops import _lib, attention as A, basic as B
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _close(a, b, atol, rtol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = (err > tol).sum().item()
+    assert bad == 0, f"{what}: {bad}/{a.numel()} mismatches, max err {err.max().item():.4g}, ref max {b.abs().max().item():.4g}"
+
+
+@pytest.fixture(autouse=True)
+def _device_errors():
+    yield
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K,nsplit", [(1, 256, 256, 1), (7, 384, 512, 2), (16, 4096, 4096, 0), (33, 1024, 2048, 4),
+                                          (64, 6144, 4096, 0), (64, 4096, 14336, 8), (100, 512, 1024, 0), (200, 1024, 512, 2),
+                                          (256, 256, 4096, 0)])
+def test_gemm_small_m(dtype, M, N, K, nsplit):
+    torch.manual_seed(0)
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(dtype)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(dtype)
+    y = B.linear(x, w, nsplit=nsplit)
+    ref = B.linear_ref(x, w)
+    _close(y, ref, 2e-2, 2e-2, f"gemm {M}x{N}x{K}")
+
+
+def test_gemm_epilogues():
+    torch.manual_seed(1)
+    M, N, K = 48, 1024, 1024
+    dt = torch.bfloat16
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(dt)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(dt)
+    bias = torch.randn(N, device=DEV).to(dt)
+    res = torch.randn(M, N, device=DEV).to(dt)
+    _close(B.linear(x, w, bias=bias), B.linear_ref(x, w, bias=bias), 3e-2, 2e-2, "bias")
+    _close(B.linear(x, w, residual=res), B.linear_ref(x, w, residual=res), 3e-2, 2e-2, "residual")
+    _close(B.linear(x, w, bias=bias, residual=res, out_f32=True), B.linear_ref(x, w, bias, res, out_dtype=torch.float32), 2e-2,
+           2e-2, "f32 out")
+    for ns in (1, 2, 4, 8):
+        y = B.linear(x, w, swiglu=True, nsplit=ns)
+        _close(y, B.linear_ref(x, w, swiglu=True), 3e-2, 3e-2, f"swiglu split {ns}")
+    res2 = torch.randn(M, N // 2, device=DEV).to(dt)
+    _close(B.linear(x, w, bias=bias, swiglu=True, residual=res2), B.linear_ref(x, w, bias, res2, swiglu=True), 3e-2, 3e-2,
+           "swiglu+bias+res")
+
+
+@pytest.mark.parametrize("M,N,K", [(257, 256, 256), (1024, 4096, 4096), (300, 384, 1024), (2048, 1024, 512)])
+def test_gemm_large_m(M, N, K):
+    torch.manual_seed(2)
+    dt = torch.bfloat16
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(dt)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(dt)
+    bias = torch.randn(N, device=DEV).to(dt)
+    res = torch.randn(M, N, device=DEV).to(dt)
+    _close(B.linear(x, w), B.linear_ref(x, w), 3e-2, 2e-2, "plain")
+    _close(B.linear(x, w, bias=bias, residual=res), B.linear_ref(x, w, bias, res), 3e-2, 2e-2, "bias+res")
+    if N % 128 == 0:
+        _close(B.linear(x, w, swiglu=True), B.linear_ref(x, w, swiglu=True), 3e-2, 3e-2, "swiglu")
+
+
+def test_interleave_roundtrip():
+    g, u = torch.randn(256, 8), torch.randn(256, 8)
+    w = B.interleave_gate_up(g, u)
+    g2, u2 = B.deinterleave_gate_up(w)
+    assert torch.equal(g, g2) and torch.equal(u, u2)
+
+
+@pytest.mark.parametrize("H", [1024, 4096, 7168])
+def test_rmsnorm(H):
+    torch.manual_seed(3)
+    dt = torch.bfloat16
+    x = torch.randn(37, H, device=DEV).to(dt)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(dt)
+    _close(B.rmsnorm(x, w, 1e-6), B.rmsnorm_ref(x, w, 1e-6)[0], 2e-2, 2e-2, "rmsnorm")
+    res = torch.randn(37, H, device=DEV).to(dt)
+    res_k = res.clone()
+    y = B.rmsnorm(x, w, 1e-5, residual=res_k)
+    yr, rr = B.rmsnorm_ref(x, w, 1e-5, residual=res)
+    _close(res_k, rr, 1e-2, 1e-2, "residual out")
+    _close(y, yr, 3e-2, 2e-2, "rmsnorm+res")
+
+
+def test_silu_embedding_argmax():
+    torch.manual_seed(4)
+    dt = torch.bfloat16
+    x = torch.randn(19, 2 * 768, device=DEV).to(dt)
+    _close(B.silu_mul(x), B.silu_mul(x.cpu()).to(DEV), 2e-2, 2e-2, "silu_mul")
+    table = torch.randn(1000, 256, device=DEV).to(dt)
+    ids = torch.randint(0, 1000, (33,), device=DEV)
+    assert torch.equal(B.embedding(ids, table), table[ids])
+    logits = torch.randn(9, 50000, device=DEV)
+    assert torch.equal(B.argmax(logits).long(), logits.argmax(-1))
+    assert torch.equal(B.argmax(logits.to(dt)).long().cpu(), B.argmax(logits.to(dt).cpu()).long())
+
+
+def _make_cache(B_, lens, Hkv, D, dt, extra_pages=3):
+    n_pages = sum((l + 127) // 128 for l in lens) + extra_pages
+    perm = torch.randperm(n_pages)
+    max_pages = max((l + 127) // 128 for l in lens)
+    pt = torch.zeros(B_, max_pages, dtype=torch.int32)
+    c = 0
+    for b, l in enumerate(lens):
+        n = (l + 127) // 128
+        pt[b, :n] = perm[c:c + n].int()
+        c += n
+    k_pool = torch.zeros(n_pages, 128, Hkv, D, dtype=dt)
+    v_pool = torch.zeros(n_pages, 128, Hkv, D, dtype=dt)
+    for b, l in enumerate(lens):
+        for i in range((l + 127) // 128):
+            n = min(128, l - i * 128)
+            k_pool[pt[b, i], :n] = (torch.randn(n, Hkv, D) * 0.7).to(dt)
+            v_pool[pt[b, i], :n] = torch.randn(n, Hkv, D).to(dt)
+    return k_pool, v_pool, pt
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(32, 8), (16, 8), (8, 1), (16, 16)])
+def test_attn_decode(Hq, Hkv):
+    torch.manual_seed(5)
+    D, dt = 128, torch.bfloat16
+    lens = [1, 127, 128, 129, 300, 1025, 77]
+    Bn = len(lens)
+    k_pool, v_pool, pt = _make_cache(Bn, lens, Hkv, D, dt)
+    q = torch.randn(Bn, Hq * D).to(dt)
+    seq = torch.tensor(lens, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    ref = A.attn_decode(q, k_pool, v_pool, pt, seq, scale, Hq, Hkv, D)
+    out = A.attn_decode(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), pt.to(DEV), seq.to(DEV), scale, Hq, Hkv, D)
+    _close(out.cpu(), ref, 2e-2, 2e-2, "attn_decode")
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
+def test_attn_prefill(Hq, Hkv):
+    torch.manual_seed(6)
+    D, dt = 128, torch.bfloat16
+    kv_lens = [5, 128, 200, 513, 300]
+    q_lens = [5, 128, 200, 513, 45]          # last request: chunk continuing a 255-token history
+    Bn = len(kv_lens)
+    k_pool, v_pool, pt = _make_cache(Bn, kv_lens, Hkv, D, dt)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32)
+    q = (torch.randn(int(cu[-1]), Hq * D) * 0.7).to(dt)
+    kvl = torch.tensor(kv_lens, dtype=torch.int32)
+    scale = 1 / math.sqrt(D)
+    ref = A.paged_attention_ref(q, k_pool, v_pool, pt, kvl, cu, scale, Hq, Hkv, D)
+    out = A.attn_prefill(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), pt.to(DEV), kvl.to(DEV), cu.to(DEV), scale, Hq, Hkv, D)
+    _close(out.cpu(), ref, 2e-2, 2e-2, "attn_prefill")
+
+
+@pytest.mark.parametrize("mode,rot,qknorm", [(A.ROPE_NEOX, 128, True), (A.ROPE_NEOX, 128, False), (A.ROPE_INTERLEAVED, 64, False),
+                                             (A.ROPE_NEOX, 64, True), (A.ROPE_NONE, 128, False)])
+def test_qkv_post(mode, rot, qknorm):
+    torch.manual_seed(7)
+    Hq, Hkv, D, dt, T = 16, 8, 128, torch.bfloat16, 21
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D).to(dt)
+    pos = torch.randint(0, 500, (T,), dtype=torch.int32)
+    slots = torch.randperm(4 * 128)[:T].int()
+    slots[3] = -1
+    cos, sin = A.build_rope_tables(rot, 512, 10000.0)
+    qn = (1 + 0.1 * torch.randn(D)).to(dt) if qknorm else None
+    kn = (1 + 0.1 * torch.randn(D)).to(dt) if qknorm else None
+    kp, vp = torch.zeros(4, 128, Hkv, D, dtype=dt), torch.zeros(4, 128, Hkv, D, dtype=dt)
+    q_ref = A.qkv_post(qkv, pos, slots, kp, vp, Hq, Hkv, D, cos, sin, mode, rot, qn, kn, 1e-6)
+    kp2, vp2 = torch.zeros_like(kp).to(DEV), torch.zeros_like(vp).to(DEV)
+    q_out = A.qkv_post(qkv.to(DEV), pos.to(DEV), slots.to(DEV), kp2, vp2, Hq, Hkv, D, cos.to(DEV), sin.to(DEV), mode, rot,
+                       qn.to(DEV) if qknorm else None, kn.to(DEV) if qknorm else None, 1e-6)
+    _close(q_out.cpu(), q_ref, 3e-2, 2e-2, "q")
+    _close(kp2.cpu(), kp, 3e-2, 2e-2, "k pool")
+    _close(vp2.cpu(), vp, 0, 0, "v pool")
