@@ -1,0 +1,212 @@
+#!/usr/bin/env python
+"""Headline benchmark: decode output tokens/s of Llama-3-8B (bf16, random-init) at 64 concurrent requests,
+1024-token prompts, paged KV (page 128), tensor parallel over N GPUs of one node.
+
+A *step* is one decode step of the whole batch (64 new tokens).  The prompts are prefilled first
+(untimed), then W warm-up decode steps and K timed decode steps run through the public engine API.
+
+Two numbers come out of the same K steps:
+  * ``value``  -- device time: CUDA events around each step's GPU work on the launching stream, summed
+                  over the K steps, max over ranks.
+  * ``e2e``    -- wall time of the K ``engine.step()`` calls, which every step copy that step's inputs
+                  from pinned host memory to the device and read the sampled tokens back.
+
+``--impl reference`` runs the unmodified reference (installed under baseline/_ref) on the same
+architecture / batch / lengths through its own Python API and prints the same JSON shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="llama-3-8b")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt-len", type=int, default=1024)
+    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--dtype", default="auto", help="weight dtype: auto(bf16) | int8 | int4g128 | fp8")
+    ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
+    ap.add_argument("--no-graph", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clock / throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for ln in self.proc.stdout:
+            self.lines.append(ln.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except Exception:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.models import TPInfo, preset, random_init
+    from fastllm_b200.ops import _lib
+    from fastllm_b200.parallel.tp import TPComm, init_distributed
+
+    rank, world, local = init_distributed()
+    if world != args.gpus:
+        if args.gpus > 1 and world == 1:
+            raise SystemExit("launch multi-GPU runs with torchrun (python -m torch.distributed.run --nproc-per-node N ...)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    cfg = preset(args.model)
+    tp = TPInfo(rank, world, TPComm(rank, world, dev) if world > 1 else None)
+    if world > 1 and args.comm in ("auto", "fused"):
+        from fastllm_b200.parallel import symm
+
+        tp.comm.fused = symm.try_create(tp.comm, cfg, args.batch, strict=(args.comm == "fused"))
+    model = random_init(cfg, dev, torch.bfloat16, tp=tp, seed=0, wdtype=args.dtype)
+    B, P, O = args.batch, args.prompt_len, args.output_len
+    need_tokens = int(B * (P + O + 256) / 0.75)   # leaves the 80 % admission limit room for all B prompts
+    ecfg = EngineConfig(max_batch=max(B, 1), max_context=((P + O + 127) // 128 + 1) * 128, max_tokens=need_tokens,
+                        use_cuda_graph=not args.no_graph, prefix_cache=False, chunked_prefill_size=8192)
+    eng = LLMEngine(model, ecfg)
+    gen = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=gen).tolist() for _ in range(B)]
+    gcfg = GenerationConfig(max_new_tokens=O, ignore_eos=True)
+    for p in prompts:
+        eng.launch(p, gcfg)
+    # ---- prefill (untimed) ----
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    while any(r.state.name in ("WAITING", "PREFILL") for r in list(eng.requests.values())):
+        eng.step()
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    assert sum(r.state.name == "DECODE" for r in eng.requests.values()) == B, "not every request reached decode"
+    K, W = args.steps, args.warmup
+    if W + K > O - 1:
+        K = max(1, O - 1 - W)
+    for _ in range(W):
+        eng.step()
+    _lib.check_device_errors()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    runner = eng.runner
+    launches0 = runner.kernel_launches
+    t_start = time.perf_counter()
+    step_wall = []
+    for i in range(K):
+        ts = time.perf_counter()
+        ev[i][0].record()
+        n = eng.step()
+        ev[i][1].record()
+        step_wall.append(time.perf_counter() - ts)
+        assert n == B, f"step produced {n} tokens, expected {B}"
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t_start
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    _lib.check_device_errors()
+    dev_ms = sum(a.elapsed_time(b) for a, b in ev)
+    t = torch.tensor([dev_ms, wall * 1000.0], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, wall_ms = t.tolist()
+    slot = runner.slots.get(runner._bucket(B))
+    per_step_launches = getattr(runner, "launches_per_decode_step", 0)
+    if rank == 0:
+        value = B * K / (dev_ms / 1000.0)
+        e2e = B * K / (wall_ms / 1000.0)
+        meta_bytes = int(slot.meta_host.numel() * 4) if slot is not None else 0
+        out = {
+            "metric": "decode output tok/s (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if args.dtype == "auto" else args.dtype,
+            "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
+            "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O, "parallelism": f"tp{world}",
+                       "kv_cache": "paged, page 128, bf16", "l2": "inputs larger than L2 (weights + KV >> 126 MB per step)",
+                       "cuda_graph": not args.no_graph, "comm": (tp.comm.fused.name if (tp.comm and tp.comm.fused) else ("nccl" if world > 1 else "none"))},
+            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": B * 4,
+                    "p50_tpot_ms": statistics.median(step_wall) * 1000.0},
+            "gpu_launches": per_step_launches * K,
+            "clocks": clocks,
+            "prefill_s": prefill_s,
+            "impl": "ours",
+        }
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        from baseline import reference_arm
+
+        reference_arm.run(args)
+        return
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

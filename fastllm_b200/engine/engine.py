@@ -1,0 +1,329 @@
+"""Continuous-batching engine: admission, prefix reuse, chunked prefill, decode, eviction, result queues.
+
+Behaviour follows the reference's new main loop (src/models/basellm.cpp:1262-2663):
+* waiting requests are admitted while used pages stay under ``prefill_page_limit`` (80 %) of the pool,
+  longest-first among the pending ones;
+* prompts are looked up in the page trie and only the uncached tail is prefilled, in chunks of
+  ``chunked_prefill_size`` tokens;
+* when a decode step cannot get a page, the longest decoding request is evicted and later recomputed;
+* results are pushed to per-handle queues; ``launch`` / ``fetch`` / ``abort`` mirror
+  LaunchResponseTokens / FetchResponseTokens / AbortResponse (basellm.cpp:2665+).
+"""
+from __future__ import annotations
+
+import threading
+import time
+
+import torch
+
+from ..models.decoder import DecoderModel
+from . import sampling
+from .request import GenerationConfig, Request, RequestState
+from .runner import EngineConfig, ModelRunner
+
+
+class LLMEngine:
+    def __init__(self, model: DecoderModel, cfg: EngineConfig | None = None, num_pages: int | None = None,
+                 eos_token_ids=None):
+        self.cfg = cfg or EngineConfig()
+        self.model = model
+        self.runner = ModelRunner(model, self.cfg, num_pages)
+        self.pm = self.runner.kv.manager
+        self.page_len = self.cfg.page_len
+        self.eos = set(eos_token_ids if eos_token_ids is not None else model.cfg.eos_token_ids)
+        self.waiting: list[Request] = []
+        self.running: list[Request] = []
+        self.requests: dict[int, Request] = {}
+        self.lock = threading.Lock()
+        self.cv = threading.Condition(self.lock)
+        self._thread: threading.Thread | None = None
+        self._stop = False
+        self.step_count = 0
+        self.decode_steps = 0
+        self.decode_tokens = 0
+        self.error: Exception | None = None
+
+    # ----------------------------------------------------------------------------------- public API
+    def launch(self, prompt_ids, gen: GenerationConfig | None = None, handle: int | None = None) -> int:
+        req = Request(prompt_ids, gen or GenerationConfig(), handle)
+        limit = self.cfg.max_context
+        if len(req.prompt_ids) >= limit:
+            req.prompt_ids = req.prompt_ids[-(limit - 1):]
+        if not req.prompt_ids:
+            req.prompt_ids = [0]
+        with self.cv:
+            self.requests[req.handle] = req
+            self.waiting.append(req)
+            self.cv.notify_all()
+        return req.handle
+
+    def abort(self, handle: int) -> None:
+        with self.cv:
+            r = self.requests.get(handle)
+            if r is not None:
+                r.abort_flag = True
+                self.cv.notify_all()
+
+    def can_fetch(self, handle: int) -> bool:
+        r = self.requests.get(handle)
+        return r is None or not r.results.empty()
+
+    def fetch(self, handle: int, timeout: float | None = None):
+        """Next generated token id, or -1 when the request has finished (reference: fetch_response_llm_model)."""
+        r = self.requests.get(handle)
+        if r is None:
+            return -1
+        tok = r.results.get(timeout=timeout)
+        if tok < 0:
+            with self.lock:
+                self.requests.pop(handle, None)
+        return tok
+
+    def stats(self, handle: int) -> dict:
+        r = self.requests.get(handle)
+        return r.stats.as_dict() if r else {}
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # --------------------------------------------------------------------------------- background loop
+    def start(self):
+        if self._thread is None:
+            self._stop = False
+            self._thread = threading.Thread(target=self._loop, name="fastllm-b200-engine", daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        with self.cv:
+            self._stop = True
+            self.cv.notify_all()
+        if self._thread is not None:
+            self._thread.join(timeout=10)
+            self._thread = None
+
+    def _loop(self):
+        if self.model.device.type == "cuda":
+            torch.cuda.set_device(self.model.device)
+        while True:
+            with self.cv:
+                while not self._stop and not self.has_work():
+                    self.cv.wait(timeout=0.01)
+                if self._stop:
+                    return
+            try:
+                self.step()
+            except Exception as e:  # surface the failure to every waiting client instead of hanging them
+                self.error = e
+                with self.cv:
+                    for r in list(self.requests.values()):
+                        self._finish(r, "error")
+                    self.waiting.clear()
+                    self.running.clear()
+                raise
+
+    # ------------------------------------------------------------------------------------- scheduling
+    def _used_fraction(self) -> float:
+        return 1.0 - self.pm.num_available() / max(1, self.pm.num_pages)
+
+    def _pages_needed(self, n_tokens: int) -> int:
+        return (n_tokens + self.page_len - 1) // self.page_len
+
+    def _admit(self):
+        """Move waiting requests to running while pages and batch slots allow."""
+        with self.lock:
+            pending = [r for r in self.waiting if not r.abort_flag]
+            aborted = [r for r in self.waiting if r.abort_flag]
+            self.waiting = []
+        for r in aborted:
+            self._finish(r, "abort")
+        pending.sort(key=lambda r: -len(r.prefill_ids))
+        keep = []
+        for r in pending:
+            if len(self.running) >= self.cfg.max_batch:
+                keep.append(r)
+                continue
+            toks = r.prefill_ids
+            cached = self.pm.query(toks) if self.cfg.prefix_cache else []
+            need = self._pages_needed(len(toks) + 1) - len(cached)
+            avail = self.pm.num_available()
+            limit_ok = (self.pm.num_pages - (avail - need)) <= self.cfg.prefill_page_limit * self.pm.num_pages or not self.running
+            pages = self.pm.alloc(need) if (need <= avail and limit_ok) else None
+            if pages is None:
+                self.pm.release(cached)
+                keep.append(r)
+                continue
+            r.pages = cached + pages
+            r.num_computed = len(cached) * self.page_len
+            r.num_cached_prefix = r.num_computed
+            r.stats.cached_tokens = r.num_computed
+            r.state = RequestState.PREFILL
+            self.running.append(r)
+        if keep:
+            with self.lock:
+                self.waiting = keep + self.waiting
+
+    def _finish(self, r: Request, reason: str):
+        if r.finished():
+            return
+        r.state = RequestState.ABORTED if reason == "abort" else RequestState.FINISHED
+        r.finish_reason = reason
+        r.stats.finished = time.time()
+        if r.pages:
+            if self.cfg.prefix_cache and reason != "error":
+                n_full = r.num_computed // self.page_len
+                self.pm.record(r.all_ids[:n_full * self.page_len], r.pages[:n_full])
+            self.pm.release(r.pages)
+            r.pages = []
+        r.results.put(-1)
+
+    def _evict_for_pages(self, need: int) -> bool:
+        """Free pages by evicting the longest decoding request (it is re-queued for recomputation)."""
+        cands = [r for r in self.running if r.state == RequestState.DECODE]
+        if len(cands) <= 1:
+            return False
+        victim = max(cands, key=lambda r: r.total_len)
+        self.running.remove(victim)
+        self.pm.release(victim.pages)
+        victim.pages = []
+        victim.num_computed = 0
+        victim.recompute_tokens = victim.all_ids[:-1] if victim.output_ids else victim.prompt_ids
+        victim.state = RequestState.WAITING
+        with self.lock:
+            self.waiting.insert(0, victim)
+        return True
+
+    # ------------------------------------------------------------------------------------------ step
+    def step(self) -> int:
+        """Run one scheduler iteration (a prefill step if any request needs one, else a decode step).
+        Returns the number of tokens produced."""
+        self._admit()
+        for r in [r for r in self.running if r.abort_flag]:
+            self.running.remove(r)
+            self._finish(r, "abort")
+        if not self.running:
+            return 0
+        self.step_count += 1
+        pre = [r for r in self.running if r.state == RequestState.PREFILL]
+        if pre:
+            return self._prefill_step(pre)
+        return self._decode_step([r for r in self.running if r.state == RequestState.DECODE])
+
+    def _prefill_step(self, reqs) -> int:
+        budget = self.cfg.chunked_prefill_size
+        chunks, owners = [], []
+        for r in reqs:
+            if budget <= 0:
+                break
+            toks = r.prefill_ids
+            n = min(len(toks) - r.num_computed, budget)
+            if n <= 0:
+                continue
+            done = r.num_computed + n == len(toks)
+            chunks.append((toks[r.num_computed:r.num_computed + n], r.num_computed, r.pages, done))
+            owners.append((r, n, done))
+            budget -= n
+        logits = self.runner.prefill(chunks)
+        produced = 0
+        finals = [r for r, _, d in owners if d]
+        for r, n, _ in owners:
+            r.num_computed += n
+        if finals:
+            toks = self._sample(finals, logits)
+            for r, t in zip(finals, toks):
+                if r.recompute_tokens is not None and r.output_ids:
+                    # recomputation after eviction: the next token was already produced before the eviction
+                    r.recompute_tokens = None
+                    r.state = RequestState.DECODE
+                    continue
+                r.recompute_tokens = None
+                r.state = RequestState.DECODE
+                if not r.stats.first_token:
+                    r.stats.first_token = time.time()
+                produced += self._emit(r, int(t))
+        return produced
+
+    def _decode_step(self, reqs) -> int:
+        if not reqs:
+            return 0
+        # make sure every request has a page for the token it is about to write
+        for r in list(reqs):
+            pos = r.total_len - 1            # position of the token fed in this step
+            need = self._pages_needed(pos + 1) - len(r.pages)
+            while need > 0:
+                pg = self.pm.alloc(need)
+                if pg is not None:
+                    r.pages.extend(pg)
+                    break
+                if not self._evict_for_pages(need):
+                    self.running.remove(r)
+                    self._finish(r, "length")
+                    reqs.remove(r)
+                    break
+                reqs = [x for x in reqs if x in self.running]
+                if r not in reqs:
+                    break
+        reqs = [r for r in reqs if r in self.running and r.state == RequestState.DECODE]
+        if not reqs:
+            return 0
+        ids = [r.all_ids[-1] for r in reqs]
+        positions = [r.total_len - 1 for r in reqs]
+        all_greedy = all(r.gen.is_simple_greedy() for r in reqs)
+        out_ids, logits = self.runner.decode(ids, positions, [r.pages for r in reqs], want_logits=not all_greedy)
+        for r in reqs:
+            r.num_computed = r.total_len
+        if all_greedy:
+            toks = out_ids.tolist()
+        else:
+            toks = self._sample(reqs, logits)
+        produced = 0
+        for r, t in zip(reqs, toks):
+            produced += self._emit(r, int(t))
+        self.decode_steps += 1
+        self.decode_tokens += produced
+        return produced
+
+    def _sample(self, reqs, logits):
+        m = self.model
+        if m.tp.size > 1:
+            logits = m.tp.comm.gather_logits(logits, m.vocab_shard, m.cfg.vocab_size)
+        if all(r.gen.is_simple_greedy() for r in reqs):
+            return sampling.greedy(logits).tolist()
+        lg = logits.float().clone()
+        sampling.apply_repeat_penalty(lg, [r.all_ids[-r.gen.last_n:] for r in reqs], [r.gen.repeat_penalty for r in reqs])
+        greedy_rows = [r.gen.is_simple_greedy() or not r.gen.do_sample for r in reqs]
+        tk = [1 if g else r.gen.top_k for r, g in zip(reqs, greedy_rows)]
+        toks = sampling.sample(lg, tk, [r.gen.top_p for r in reqs], [r.gen.temperature for r in reqs])
+        for r, row in zip(reqs, range(len(reqs))):
+            if r.gen.output_logits:
+                r.last_logits = logits[row].float().cpu()
+        return toks.tolist()
+
+    def _emit(self, r: Request, tok: int) -> int:
+        r.output_ids.append(tok)
+        r.stats.output_tokens = len(r.output_ids)
+        g = r.gen
+        stop = False
+        reason = None
+        is_eos = (tok in self.eos and not g.ignore_eos) or tok in g.stop_token_ids
+        if is_eos and len(r.output_ids) > g.min_new_tokens:
+            stop, reason = True, "stop"
+        elif g.max_new_tokens > 0 and len(r.output_ids) >= g.max_new_tokens:
+            stop, reason = True, "length"
+        elif r.total_len >= self.cfg.max_context:
+            stop, reason = True, "length"
+        if not (is_eos and stop):
+            r.results.put(tok)
+        if stop:
+            if r in self.running:
+                self.running.remove(r)
+            self._finish(r, reason)
+        return 1
+
+    # -------------------------------------------------------------------------------- convenience
+    def generate(self, prompts, gen: GenerationConfig | None = None):
+        """Blocking helper: run the given prompts (lists of token ids) to completion, return output ids."""
+        handles = [self.launch(p, gen) for p in prompts]
+        reqs = [self.requests[h] for h in handles]
+        while any(not r.finished() for r in reqs):
+            self.step()
+        return [r.output_ids for r in reqs]

@@ -1,0 +1,116 @@
+"""Paged KV cache: device page pools per layer plus the host page manager (C++, with prefix trie).
+
+Pool shape per layer follows the reference (``[maxPages, pageLen, numHeads, headDim]``,
+src/fastllm.cpp:4885-4992); capacity is derived from free device memory times ``gpu_mem_ratio`` like the
+reference's warm-up (src/models/basellm.cpp:3905+).  Pools are zero-filled: the attention kernels rely
+on unused slots holding finite values.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from ..ops import _lib
+from ..ops.attention import PAGE_LEN
+
+
+class PageManager:
+    """Thin ctypes wrapper over ``csrc/runtime/page_manager.cpp``."""
+
+    def __init__(self, num_pages: int, page_len: int = PAGE_LEN):
+        self.lib = _lib.runtime()
+        L = self.lib
+        L.fbpm_create.restype = ctypes.c_void_p
+        L.fbpm_create.argtypes = [ctypes.c_int, ctypes.c_int]
+        L.fbpm_destroy.argtypes = [ctypes.c_void_p]
+        L.fbpm_num_available.argtypes = [ctypes.c_void_p]
+        L.fbpm_num_free.argtypes = [ctypes.c_void_p]
+        ip = ctypes.POINTER(ctypes.c_int)
+        L.fbpm_alloc.argtypes = [ctypes.c_void_p, ctypes.c_int, ip]
+        L.fbpm_release.argtypes = [ctypes.c_void_p, ip, ctypes.c_int]
+        L.fbpm_query.argtypes = [ctypes.c_void_p, ip, ctypes.c_int, ip, ctypes.c_int]
+        L.fbpm_record.argtypes = [ctypes.c_void_p, ip, ctypes.c_int, ip, ctypes.c_int]
+        L.fbpm_clear_cache.argtypes = [ctypes.c_void_p]
+        L.fbpm_stats.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_longlong)]
+        self.num_pages, self.page_len = num_pages, page_len
+        self.h = ctypes.c_void_p(L.fbpm_create(num_pages, page_len))
+
+    def __del__(self):
+        try:
+            if self.h:
+                self.lib.fbpm_destroy(self.h)
+                self.h = None
+        except Exception:
+            pass
+
+    @staticmethod
+    def _arr(v):
+        return (ctypes.c_int * len(v))(*v)
+
+    def num_available(self) -> int:
+        return self.lib.fbpm_num_available(self.h)
+
+    def num_free(self) -> int:
+        return self.lib.fbpm_num_free(self.h)
+
+    def alloc(self, n: int) -> list[int] | None:
+        if n <= 0:
+            return []
+        out = (ctypes.c_int * n)()
+        got = self.lib.fbpm_alloc(self.h, n, out)
+        return list(out) if got == n else None
+
+    def release(self, pages) -> None:
+        if pages:
+            self.lib.fbpm_release(self.h, self._arr(pages), len(pages))
+
+    def query(self, tokens) -> list[int]:
+        """Pages holding the longest cached whole-page prefix of ``tokens`` (a reference is taken on each)."""
+        n = len(tokens)
+        maxp = max(1, n // self.page_len)
+        out = (ctypes.c_int * maxp)()
+        got = self.lib.fbpm_query(self.h, self._arr(tokens), n, out, maxp)
+        return list(out[:got])
+
+    def record(self, tokens, pages) -> None:
+        if pages:
+            self.lib.fbpm_record(self.h, self._arr(tokens), len(tokens), self._arr(pages), len(pages))
+
+    def clear_cache(self) -> None:
+        self.lib.fbpm_clear_cache(self.h)
+
+    def stats(self) -> dict:
+        out = (ctypes.c_longlong * 4)()
+        self.lib.fbpm_stats(self.h, out)
+        return dict(free=out[0], cached=out[1], lookups=out[2], hits=out[3])
+
+
+class KVCache:
+    """Device page pools of one rank + the shared page manager."""
+
+    def __init__(self, model, num_pages: int, page_len: int = PAGE_LEN):
+        self.num_pages = num_pages
+        self.page_len = page_len
+        ks, vs = model.kv_cache_shape(num_pages)
+        dev, dt = model.device, model.dtype
+        self.pools = []
+        for _ in range(model.cfg.num_layers):
+            k = torch.zeros(ks, device=dev, dtype=dt)
+            v = torch.zeros(vs, device=dev, dtype=dt) if vs is not None else None
+            self.pools.append((k, v))
+        self.manager = PageManager(num_pages, page_len)
+
+    @staticmethod
+    def plan_num_pages(model, gpu_mem_ratio: float = 0.9, max_tokens: int | None = None, reserve_bytes: int = 2 << 30) -> int:
+        per_page = model.kv_bytes_per_page()
+        if model.device.type == "cuda":
+            free, _total = torch.cuda.mem_get_info(model.device)
+            budget = int(free * gpu_mem_ratio) - reserve_bytes
+            n = max(16, budget // per_page)
+        else:
+            n = 512
+        if max_tokens:
+            n = min(n, math.ceil(max_tokens / PAGE_LEN) + 8)
+        return int(n)

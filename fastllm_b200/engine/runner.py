@@ -1,0 +1,217 @@
+"""Model runner: turns scheduler decisions into device batches, owns the decode CUDA graphs.
+
+Decode steps are captured once per batch-size bucket into a CUDA graph (whole layer stack + greedy
+sampler) and replayed with new metadata, as the reference pre-captures per-batch-size decode graphs
+after warm-up (src/models/qwen3.cpp:1632, 1723-2210).  Step metadata (token ids, positions, cache slots,
+sequence lengths, page table) travels in ONE pinned host buffer -> ONE H2D copy per step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+from ..models.decoder import DecoderModel, ForwardBatch
+from ..ops import _lib
+from ..ops import attention as A
+from ..ops import basic as B
+from .kv_cache import KVCache
+
+
+@dataclass
+class EngineConfig:
+    max_batch: int = 256
+    max_context: int = 8192
+    chunked_prefill_size: int = 8192
+    gpu_mem_ratio: float = 0.9
+    max_tokens: int | None = None
+    prefill_page_limit: float = 0.8      # admit new prefills only while used pages stay below this fraction
+    use_cuda_graph: bool = True
+    graph_batch_sizes: list = field(default_factory=lambda: [1, 2, 4, 8, 16, 32, 64, 128, 256, 512])
+    prefix_cache: bool = True
+    page_len: int = A.PAGE_LEN
+    check_device_errors_every: int = 64
+
+
+class _DecodeSlot:
+    """Static buffers (and the captured graph) of one decode batch-size bucket."""
+
+    def __init__(self, runner: "ModelRunner", bsz: int):
+        dev = runner.device
+        P = runner.max_pages
+        self.bsz = bsz
+        n = 4 * bsz + bsz * P
+        pin = dev.type == "cuda"
+        self.meta_host = torch.zeros(n, dtype=torch.int32, pin_memory=pin)
+        self.meta_np = self.meta_host.numpy()
+        self.meta_dev = torch.zeros(n, dtype=torch.int32, device=dev)
+        md = self.meta_dev
+        self.ids, self.positions, self.slots, self.kv_lens = (md[i * bsz:(i + 1) * bsz] for i in range(4))
+        self.page_table = md[4 * bsz:].view(bsz, P)
+        self.cu_q = torch.arange(bsz + 1, dtype=torch.int32, device=dev)
+        self.out_ids = torch.zeros(bsz, dtype=torch.int32, device=dev)
+        self.out_host = torch.zeros(bsz, dtype=torch.int32, pin_memory=pin)
+        self.logits = None
+        self.graph = None
+        m = runner.model
+        G = max(1, m.num_heads_local // m.num_kv_heads_local)
+        self.ws = None
+        if dev.type == "cuda" and not m.cfg.use_mla:
+            self.ws = A.DecodeWorkspace(bsz, m.num_kv_heads_local, G, P, dev, m.cfg.head_dim)
+
+    def batch(self) -> ForwardBatch:
+        return ForwardBatch(ids=self.ids, positions=self.positions, slots=self.slots, page_table=self.page_table,
+                            kv_lens=self.kv_lens, cu_q=self.cu_q, logit_rows=None, is_decode=True,
+                            cu_q_host=list(range(self.bsz + 1)), decode_ws=self.ws)
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, cfg: EngineConfig, num_pages: int | None = None):
+        self.model = model
+        self.cfg = cfg
+        self.device = model.device
+        self.max_pages = (cfg.max_context + cfg.page_len - 1) // cfg.page_len
+        if num_pages is None:
+            num_pages = KVCache.plan_num_pages(model, cfg.gpu_mem_ratio, cfg.max_tokens)
+        self.kv = KVCache(model, num_pages, cfg.page_len)
+        self.slots: dict[int, _DecodeSlot] = {}
+        self.graph_ok = cfg.use_cuda_graph and self.device.type == "cuda" and self._graph_safe()
+        self.steps = 0
+        self.kernel_launches = 0
+        self.launches_per_decode_step = 0
+        model.rope_tables()
+
+    def _graph_safe(self) -> bool:
+        c = self.model.cfg
+        if c.use_mla:
+            return False
+        if c.is_moe:
+            from ..ops import moe_grouped
+
+            return getattr(moe_grouped, "GRAPH_SAFE", False)
+        return True
+
+    # ---------------------------------------------------------------------------------------------
+    def prefill(self, chunks):
+        """chunks: list of (token_ids, start_pos, pages, want_logits). Returns fp32 logits ``[R, V_local]``
+        for the chunks that asked for them (last token of the chunk), in order."""
+        dev = self.device
+        ids, pos, slots, cu, kv_lens, rows = [], [], [], [0], [], []
+        P = self.max_pages
+        pt = np.zeros((len(chunks), P), dtype=np.int32)
+        pl = self.cfg.page_len
+        for b, (toks, start, pages, want) in enumerate(chunks):
+            n = len(toks)
+            ids.extend(toks)
+            pos.extend(range(start, start + n))
+            pg = np.asarray(pages, dtype=np.int64)
+            p_idx = np.arange(start, start + n)
+            slots.extend((pg[p_idx // pl] * pl + p_idx % pl).tolist())
+            cu.append(cu[-1] + n)
+            kv_lens.append(start + n)
+            pt[b, :len(pages)] = pages
+            if want:
+                rows.append(cu[-1] - 1)
+        T = len(ids)
+        meta = torch.tensor(ids + pos + slots, dtype=torch.int32)
+        if dev.type == "cuda":
+            meta = meta.pin_memory().to(dev, non_blocking=True)
+        fb = ForwardBatch(ids=meta[:T], positions=meta[T:2 * T], slots=meta[2 * T:3 * T],
+                          page_table=torch.from_numpy(pt).to(dev), kv_lens=torch.tensor(kv_lens, dtype=torch.int32).to(dev),
+                          cu_q=torch.tensor(cu, dtype=torch.int32).to(dev),
+                          logit_rows=torch.tensor(rows, dtype=torch.long).to(dev) if rows else torch.zeros(0, dtype=torch.long, device=dev),
+                          is_decode=False, cu_q_host=cu)
+        if not rows:
+            # still run the stack to fill the cache; ask for one row to keep shapes valid
+            fb.logit_rows = torch.zeros(1, dtype=torch.long, device=dev)
+        logits = self.model.forward(fb, self.kv.pools)
+        self.steps += 1
+        return logits if rows else None
+
+    # ---------------------------------------------------------------------------------------------
+    def _bucket(self, n: int) -> int:
+        for b in self.cfg.graph_batch_sizes:
+            if b >= n:
+                return b
+        return n
+
+    def _get_slot(self, bsz: int) -> _DecodeSlot:
+        s = self.slots.get(bsz)
+        if s is None:
+            s = _DecodeSlot(self, bsz)
+            self.slots[bsz] = s
+        return s
+
+    def _decode_forward(self, s: _DecodeSlot):
+        fb = s.batch()
+        if s.ws is not None:
+            s.ws.plan(s.kv_lens)
+            fb.decode_planned = True
+        logits = self.model.forward(fb, self.kv.pools)
+        s.logits = logits
+        self._greedy(logits, s.out_ids)
+
+    def _greedy(self, logits, out_ids):
+        m = self.model
+        if m.tp.size == 1:
+            B.argmax(logits, out=out_ids)
+        else:
+            lo, hi = m.vocab_shard
+            lg = logits
+            if hi - lo < lg.shape[1]:
+                lg = lg[:, :hi - lo]
+            ids, vals = B.argmax(lg, id_offset=lo, want_values=True)
+            out_ids.copy_(m.tp.comm.merge_argmax(ids, vals))
+
+    def decode(self, ids, positions, pages_per_req, want_logits=False):
+        """One token per request. Returns (token ids int32 host tensor [n], logits or None)."""
+        n = len(ids)
+        pl = self.cfg.page_len
+        bsz = self._bucket(n) if self.graph_ok else n
+        s = self._get_slot(bsz)
+        mp = s.meta_np
+        mp[:4 * bsz] = 0
+        mp[2 * bsz:3 * bsz] = -1                      # padded rows never write the cache
+        mp[0:n] = ids
+        mp[bsz:bsz + n] = positions
+        pt = mp[4 * bsz:].reshape(bsz, self.max_pages)
+        for b in range(n):
+            pg = pages_per_req[b]
+            p = positions[b]
+            mp[2 * bsz + b] = pg[p // pl] * pl + p % pl
+            mp[3 * bsz + b] = p + 1
+            pt[b, :len(pg)] = pg
+        s.meta_dev.copy_(s.meta_host, non_blocking=True)
+        if self.graph_ok:
+            if s.graph is None:
+                self._capture(s)
+            s.graph.replay()
+        else:
+            c0 = _lib.launch_count()
+            self._decode_forward(s)
+            self.launches_per_decode_step = _lib.launch_count() - c0
+        s.out_host.copy_(s.out_ids, non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        self.steps += 1
+        if self.device.type == "cuda" and self.steps % self.cfg.check_device_errors_every == 0:
+            _lib.check_device_errors()
+        logits = s.logits[:n] if want_logits else None
+        return s.out_host[:n], logits
+
+    def _capture(self, s: _DecodeSlot):
+        # warm-up run outside capture (lazy inits, tensor-map cache, cudaFuncSetAttribute), then capture
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._decode_forward(s)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        c0 = _lib.launch_count()
+        with torch.cuda.graph(g):
+            self._decode_forward(s)
+        self.launches_per_decode_step = _lib.launch_count() - c0
+        s.graph = g
+        torch.cuda.synchronize()

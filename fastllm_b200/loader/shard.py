@@ -1,0 +1,182 @@
+"""Turn canonical (Llama-style) named tensors into the per-rank weights of a ``DecoderModel``.
+
+Covers what the reference does at load time: merging q/k/v into one QKV matrix and gate/up into one
+matrix with their quantisation metadata (weightMergeRules, src/model.cpp:3943-4090), splitting for
+tensor parallelism -- QKV by KV head, gate/up as paired halves, O/down along the input dim
+(BuildMultiCudaRowSplitScheme, src/devices/multicuda/fastllm-multicuda.cu:882-980) -- expert placement
+for expert parallelism (src/devices/multicuda/multicudadevice.cpp:6226-6236) and quantising to the
+requested ``--dtype`` / ``--moe_dtype``.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..ops import basic as B
+from ..ops import moe as MOE
+from ..ops.quant import LinearWeight
+
+
+def _shard_rows(w, rank, size):
+    n = w.shape[0] // size
+    return w[rank * n:(rank + 1) * n]
+
+
+def _shard_cols(w, rank, size):
+    n = w.shape[1] // size
+    return w[:, rank * n:(rank + 1) * n]
+
+
+def _heads_rows(w, head_dim, h0, h1):
+    return w[h0 * head_dim:h1 * head_dim]
+
+
+def _to(t, m):
+    if t is None:
+        return None
+    if t.is_floating_point() and t.dtype not in (torch.float8_e4m3fn,):
+        t = t.to(m.dtype)
+    return t.to(m.device).contiguous()
+
+
+def _lin(m, w, wdtype, bias=None, interleaved=False):
+    return LinearWeight.from_dense(_to(w, m), wdtype, _to(bias, m), interleaved, act_dtype=m.dtype)
+
+
+def _gate_up(m, gate, up, wdtype, bias_g=None, bias_u=None):
+    """Merge gate and up into the tile-interleaved layout (CUDA) or plain stacking (CPU)."""
+    if m.on_cuda and gate.shape[0] % 64 == 0:
+        w = B.interleave_gate_up(_to(gate, m), _to(up, m))
+        b = B.interleave_gate_up(_to(bias_g, m), _to(bias_u, m)) if bias_g is not None else None
+        return LinearWeight.from_dense(w, wdtype, b, True, act_dtype=m.dtype)
+    w = torch.cat([_to(gate, m), _to(up, m)], dim=0)
+    b = torch.cat([_to(bias_g, m), _to(bias_u, m)]) if bias_g is not None else None
+    return LinearWeight.from_dense(w, wdtype, b, False, act_dtype=m.dtype)
+
+
+def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
+    """Fill ``m.layers[i]`` from the canonical tensors of layer ``i`` (dict is consumed)."""
+    from ..models.decoder import LayerWeights
+
+    cfg, tp = m.cfg, m.tp
+    p = f"model.layers.{i}."
+    lw = LayerWeights()
+    a, f = lw.attn, lw.mlp
+    g = lambda k: t.get(p + k)
+    a.ln = _to(g("input_layernorm.weight"), m)
+    f.ln = _to(g("post_attention_layernorm.weight"), m)
+    r, n = tp.rank, tp.size
+    if cfg.use_mla:
+        nope, rope, vd, lora = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
+        Hl = cfg.num_heads // n
+        qd = nope + rope
+        if g("self_attn.q_a_proj.weight") is not None:
+            a.q_a = _lin(m, g("self_attn.q_a_proj.weight"), wdtype)
+            a.q_a_norm = _to(g("self_attn.q_a_layernorm.weight"), m)
+            a.q_b = _lin(m, _heads_rows(g("self_attn.q_b_proj.weight"), qd, r * Hl, (r + 1) * Hl), wdtype)
+        else:
+            a.q_b = _lin(m, _heads_rows(g("self_attn.q_proj.weight"), qd, r * Hl, (r + 1) * Hl), wdtype)
+        a.kv_a = _lin(m, g("self_attn.kv_a_proj_with_mqa.weight"), wdtype)
+        a.kv_a_norm = _to(g("self_attn.kv_a_layernorm.weight"), m)
+        kvb = g("self_attn.kv_b_proj.weight").to(torch.float32).view(cfg.num_heads, nope + vd, lora)[r * Hl:(r + 1) * Hl]
+        a.w_uk = _to(kvb[:, :nope, :], m)
+        a.w_uv = _to(kvb[:, nope:, :], m)
+        a.o = _lin(m, _shard_cols(g("self_attn.o_proj.weight"), r, n), wdtype)
+    else:
+        D = cfg.head_dim
+        Hq_l = cfg.num_heads // n
+        Hkv_l = m.num_kv_heads_local
+        kv0 = (r * cfg.num_kv_heads) // n if cfg.num_kv_heads >= n else r // m.kv_replicas
+        if g("self_attn.qkv_proj.weight") is not None:        # already merged (phi3-style): [q | k | v]
+            w = g("self_attn.qkv_proj.weight")
+            qw, kw, vw = w.split([cfg.num_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D], dim=0)
+            bq = bk = bv = None
+            if g("self_attn.qkv_proj.bias") is not None:
+                bq, bk, bv = g("self_attn.qkv_proj.bias").split([cfg.num_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D])
+        else:
+            qw, kw, vw = g("self_attn.q_proj.weight"), g("self_attn.k_proj.weight"), g("self_attn.v_proj.weight")
+            bq, bk, bv = g("self_attn.q_proj.bias"), g("self_attn.k_proj.bias"), g("self_attn.v_proj.bias")
+        w = torch.cat([_heads_rows(qw, D, r * Hq_l, (r + 1) * Hq_l), _heads_rows(kw, D, kv0, kv0 + Hkv_l),
+                       _heads_rows(vw, D, kv0, kv0 + Hkv_l)], dim=0)
+        b = None
+        if bq is not None:
+            b = torch.cat([_heads_rows(bq, D, r * Hq_l, (r + 1) * Hq_l), _heads_rows(bk, D, kv0, kv0 + Hkv_l),
+                           _heads_rows(bv, D, kv0, kv0 + Hkv_l)])
+        a.qkv = _lin(m, w, wdtype, b)
+        ob = g("self_attn.o_proj.bias")
+        a.o = _lin(m, _shard_cols(g("self_attn.o_proj.weight"), r, n), wdtype, ob if (ob is not None and r == 0) else None)
+        a.q_norm = _to(g("self_attn.q_norm.weight"), m)
+        a.k_norm = _to(g("self_attn.k_norm.weight"), m)
+    # ---- feed-forward ----
+    if cfg.layer_is_moe(i):
+        f.router = g("mlp.gate.weight").to(m.device, torch.float32).contiguous()
+        rb = g("mlp.gate.e_score_correction_bias")
+        f.router_bias = rb.to(m.device, torch.float32).contiguous() if rb is not None else None
+        mw = moe_wdtype or wdtype
+        lo, hi = MOE.local_expert_range(cfg.num_experts, m.ep)
+        moe_tp = (m.ep is None or m.ep.size == 1) and n > 1      # no EP: shard every expert's intermediate dim
+        gu, dn = [], []
+        for e in range(lo, hi):
+            gw, uw, dw = (g(f"mlp.experts.{e}.{nm}.weight") for nm in ("gate_proj", "up_proj", "down_proj"))
+            if moe_tp:
+                gw, uw, dw = _shard_rows(gw, r, n), _shard_rows(uw, r, n), _shard_cols(dw, r, n)
+            gu.append(_gate_up(m, gw, uw, mw))
+            dn.append(_lin(m, dw, mw))
+            for nm in ("gate_proj", "up_proj", "down_proj"):
+                t.pop(p + f"mlp.experts.{e}.{nm}.weight", None)
+        f.experts = MOE.ExpertWeights(cfg.num_experts, lo, gu, dn)
+        sp = "mlp.shared_expert." if g("mlp.shared_expert.gate_proj.weight") is not None else "mlp.shared_experts."
+        if g(sp + "gate_proj.weight") is not None:
+            f.shared_gate_up = _gate_up(m, _shard_rows(g(sp + "gate_proj.weight"), r, n), _shard_rows(g(sp + "up_proj.weight"), r, n), wdtype)
+            f.shared_down = _lin(m, _shard_cols(g(sp + "down_proj.weight"), r, n), wdtype)
+            sg = g("mlp.shared_expert_gate.weight")
+            f.shared_gate = _to(sg, m) if sg is not None else None
+    else:
+        if g("mlp.gate_up_proj.weight") is not None:           # merged [gate | up]
+            gw, uw = g("mlp.gate_up_proj.weight").chunk(2, dim=0)
+        else:
+            gw, uw = g("mlp.gate_proj.weight"), g("mlp.up_proj.weight")
+        bg, bu, bd = g("mlp.gate_proj.bias"), g("mlp.up_proj.bias"), g("mlp.down_proj.bias")
+        f.gate_up = _gate_up(m, _shard_rows(gw, r, n), _shard_rows(uw, r, n), wdtype,
+                             _shard_rows(bg, r, n) if bg is not None else None, _shard_rows(bu, r, n) if bu is not None else None)
+        f.down = _lin(m, _shard_cols(g("mlp.down_proj.weight"), r, n), wdtype, bd if (bd is not None and r == 0) else None)
+    while len(m.layers) <= i:
+        m.layers.append(None)
+    m.layers[i] = lw
+
+
+def build_top(m, t: dict, wdtype="dense"):
+    cfg, tp = m.cfg, m.tp
+    m.embed = _to(t["model.embed_tokens.weight"], m)
+    m.final_norm = _to(t["model.norm.weight"], m)
+    head = t.get("lm_head.weight")
+    if head is None or cfg.tie_embeddings:
+        head = t["model.embed_tokens.weight"]
+    if tp.size > 1:
+        per = (cfg.vocab_size + tp.size - 1) // tp.size
+        per = (per + 127) // 128 * 128
+        lo = min(cfg.vocab_size, tp.rank * per)
+        hi = min(cfg.vocab_size, lo + per)
+        m.vocab_shard = (lo, hi)
+        shard = head[lo:hi]
+        if shard.shape[0] < per:   # keep every rank's shard the same shape (pad rows score -inf via zero weights + mask)
+            pad = torch.zeros((per - shard.shape[0], shard.shape[1]), dtype=shard.dtype, device=shard.device)
+            shard = torch.cat([shard, pad], dim=0)
+        # lm_head stays 16-bit: its rounding decides the sampled token
+        m.lm_head = _lin(m, shard, "dense")
+    else:
+        if head is t["model.embed_tokens.weight"] and m.embed is not None:
+            m.lm_head = LinearWeight("dense", m.embed, dtype=m.dtype)
+        else:
+            m.lm_head = _lin(m, head, "dense")
+
+
+def finalize_model(m, top_fn, layer_fn, wdtype="dense", moe_wdtype=None):
+    """``top_fn()`` / ``layer_fn(i)`` return dicts of canonical tensors; they are consumed one layer at a time."""
+    build_top(m, top_fn(), wdtype)
+    for i in range(m.cfg.num_layers):
+        build_layer(m, i, layer_fn(i), wdtype, moe_wdtype)
+    if m.on_cuda:
+        from ..ops import moe_grouped
+
+        moe_grouped.prepare_model(m)
+    return m

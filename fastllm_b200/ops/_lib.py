@@ -43,6 +43,44 @@ class KernelLibraryMissing(RuntimeError):
     pass
 
 
+_launch_count = 0
+_LAUNCHES_PER_CALL = {"fb_attn_decode": 2}
+
+
+def launch_count() -> int:
+    """Number of kernel launches issued through this library so far (launcher calls x kernels per call)."""
+    return _launch_count
+
+
+class _KernelProxy:
+    """Attribute access returns the ctypes function wrapped with a launch counter."""
+
+    def __init__(self, lib):
+        self._lib = lib
+        self._cache = {}
+
+    def __getattr__(self, name):
+        c = self._cache.get(name)
+        if c is not None:
+            return c
+        fn = getattr(self._lib, name)
+        if not name.startswith("fb_") or name.endswith("_read_error") or name == "fb_gemm_pick_split":
+            self._cache[name] = fn
+            return fn
+        n = _LAUNCHES_PER_CALL.get(name, 1)
+
+        def counted(*args, _fn=fn, _n=n):
+            global _launch_count
+            _launch_count += _n
+            return _fn(*args)
+
+        self._cache[name] = counted
+        return counted
+
+    def has(self, name) -> bool:
+        return hasattr(self._lib, name)
+
+
 def kernels():
     global _kernels
     if _kernels is not None:
@@ -65,8 +103,8 @@ def kernels():
             if fn is not None:
                 fn.argtypes = [ctypes.POINTER(c_int), c_int]
                 fn.restype = c_int
-        _kernels = lib
-        return lib
+        _kernels = _KernelProxy(lib)
+        return _kernels
 
 
 def register_sigs(sigs: dict, error_readers: list[str] | None = None) -> None:
@@ -77,13 +115,14 @@ def register_sigs(sigs: dict, error_readers: list[str] | None = None) -> None:
             if r not in _ERROR_READERS:
                 _ERROR_READERS.append(r)
     if _kernels is not None:
+        raw = _kernels._lib
         for name, args in sigs.items():
-            if hasattr(_kernels, name):
-                fn = getattr(_kernels, name)
+            if hasattr(raw, name):
+                fn = getattr(raw, name)
                 fn.argtypes = args
                 fn.restype = c_int
         for name in error_readers or []:
-            fn = getattr(_kernels, f"fb_{name}_read_error", None)
+            fn = getattr(raw, f"fb_{name}_read_error", None)
             if fn is not None:
                 fn.argtypes = [ctypes.POINTER(c_int), c_int]
                 fn.restype = c_int
@@ -98,7 +137,7 @@ def check_device_errors(reset: bool = True) -> None:
 
     Costs one small device-to-host copy per translation unit, so call it between steps, not per kernel.
     """
-    lib = kernels()
+    lib = kernels()._lib
     buf = (c_int * 8)()
     for name in _ERROR_READERS:
         fn = getattr(lib, f"fb_{name}_read_error", None)

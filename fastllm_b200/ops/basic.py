@@ -185,6 +185,9 @@ def argmax(logits: torch.Tensor, id_offset: int = 0, want_values: bool = False, 
     if not logits.is_cuda:
         v, i = logits.float().max(dim=-1)
         i = (i + id_offset).to(torch.int32)
+        if out is not None:
+            out.copy_(i)
+            i = out
         return (i, v) if want_values else i
     l2 = logits.reshape(-1, logits.shape[-1])
     M, V = l2.shape

@@ -1,0 +1,149 @@
+"""Mixture-of-experts operators: router top-k, expert FFN, and the latent (MLA) paged attention.
+
+Router semantics follow the reference's ``SelectExpert`` (src/devices/cpu/cpudevice.cpp:8885-8955): the
+top-k is taken on ``score + bias`` while the returned weight is the un-biased score, optionally
+renormalised and multiplied by ``route_scale``.  Group-limited routing (DeepSeek-V3: keep the
+``topk_group`` best of ``n_group`` expert groups, ranked by the sum of their two best biased scores)
+does not exist in the reference; it is implemented to the Hugging Face DeepSeek-V3 definition.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.nn.functional as F
+
+from . import _lib
+from .basic import _ptr, _stream
+from .quant import LinearWeight
+
+
+# ---------------------------------------------------------------------------------------------------
+def route_topk_ref(logits, bias, topk, score_mode, renorm, n_group=1, topk_group=1, route_scale=1.0):
+    lf = logits.float()
+    if score_mode == 0:
+        sc = torch.softmax(lf, dim=-1)
+    elif score_mode == 1:
+        sc = torch.sigmoid(lf)
+    else:
+        sc = lf
+    sel = sc + bias.float() if bias is not None else sc.clone()
+    M, E = sc.shape
+    if n_group > 1 and topk_group < n_group:
+        gs = sel.view(M, n_group, E // n_group).topk(2, dim=-1)[0].sum(-1)
+        gidx = gs.topk(topk_group, dim=-1)[1]
+        gmask = torch.zeros_like(gs).scatter_(1, gidx, 1.0)
+        emask = gmask[:, :, None].expand(M, n_group, E // n_group).reshape(M, E)
+        sel = sel.masked_fill(emask == 0, float("-inf"))
+    idx = sel.topk(topk, dim=-1)[1]
+    w = sc.gather(1, idx)
+    if renorm:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return idx.to(torch.int32), (w * route_scale).float()
+
+
+def route_topk(logits, bias, topk, score_mode, renorm, n_group=1, topk_group=1, route_scale=1.0):
+    """logits fp32 ``[M, E]`` -> (expert index int32 ``[M, topk]``, weight fp32 ``[M, topk]``)."""
+    if not logits.is_cuda or logits.shape[1] > 512:
+        return route_topk_ref(logits, bias, topk, score_mode, renorm, n_group, topk_group, route_scale)
+    lg = logits.float().contiguous()
+    M, E = lg.shape
+    idx = torch.empty((M, topk), device=lg.device, dtype=torch.int32)
+    w = torch.empty((M, topk), device=lg.device, dtype=torch.float32)
+    b = bias.float().contiguous() if bias is not None else None
+    rc = _lib.kernels().fb_route_topk(_ptr(lg), _ptr(b), _ptr(idx), _ptr(w), M, E, topk, score_mode, 1 if renorm else 0,
+                                      n_group, topk_group, float(route_scale), _stream())
+    _lib.check(rc, "fb_route_topk")
+    return idx, w
+
+
+# ---------------------------------------------------------------------------------------------------
+class ExpertWeights:
+    """Routed experts owned by this rank: per-expert gate/up (tile-interleaved) and down weights."""
+
+    def __init__(self, num_experts_total: int, first: int, gate_up: list[LinearWeight], down: list[LinearWeight]):
+        self.total = num_experts_total
+        self.first = first
+        self.count = len(gate_up)
+        self.gate_up = gate_up
+        self.down = down
+        self.stacked = None     # filled by ops.moe_grouped when a grouped kernel can take the whole set
+
+
+def local_expert_range(num_experts: int, ep) -> tuple[int, int]:
+    """Contiguous block of experts owned by this expert-parallel rank."""
+    if ep is None or ep.size == 1:
+        return 0, num_experts
+    per = (num_experts + ep.size - 1) // ep.size
+    lo = min(num_experts, ep.rank * per)
+    return lo, min(num_experts, lo + per)
+
+
+def output_is_complete(ep) -> bool:
+    """True when moe_forward already returns the sum over all ranks' experts."""
+    return bool(ep is not None and getattr(ep, "combines", False))
+
+
+def moe_forward(x, idx, wts, experts: ExpertWeights, ep=None):
+    """``y[t] = sum_k wts[t,k] * down_e(silu(gate_e x) * up_e x)`` over the experts this rank owns.
+
+    Tokens are grouped by expert; each non-empty local expert runs the two GEMMs on its token group.
+    With expert parallelism the result is this rank's partial sum (the caller all-reduces it).
+    """
+    if experts.stacked is not None and x.is_cuda:
+        from . import moe_grouped
+
+        y = moe_grouped.forward(x, idx, wts, experts)
+        if y is not None:
+            return y
+    T, H = x.shape
+    y = torch.zeros((T, H), device=x.device, dtype=torch.float32)
+    flat_e = idx.reshape(-1).long()
+    flat_t = torch.arange(T, device=x.device).repeat_interleave(idx.shape[1])
+    flat_w = wts.reshape(-1)
+    local = (flat_e >= experts.first) & (flat_e < experts.first + experts.count)
+    if not bool(local.any()):
+        return y.to(x.dtype)
+    order = torch.argsort(flat_e[local], stable=True)
+    e_sorted = flat_e[local][order]
+    t_sorted = flat_t[local][order]
+    w_sorted = flat_w[local][order]
+    uniq, counts = torch.unique_consecutive(e_sorted, return_counts=True)
+    start = 0
+    for e, n in zip(uniq.tolist(), counts.tolist()):
+        rows = t_sorted[start:start + n]
+        xe = x.index_select(0, rows)
+        le = e - experts.first
+        he = experts.down[le](experts.gate_up[le](xe, swiglu=True))
+        y.index_add_(0, rows, he.float() * w_sorted[start:start + n, None])
+        start += n
+    return y.to(x.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
+    """Absorbed MLA over the paged latent cache.
+
+    q_full: ``[T, H, lora + rope]`` (q_nope already multiplied by W_UK); lat_pool: ``[pages, page_len, 1,
+    lora + rope]``.  Scores use all ``lora + rope`` dims, values are the first ``lora`` dims.  Returns
+    ``[T, H, lora]``.  (Reference: MergeMLAPaged, src/devices/cuda/attention/fastllm-attention.cu:3619-3727.)
+    """
+    T, H, Dq = q_full.shape
+    out = torch.zeros((T, H, lora), device=q_full.device, dtype=q_full.dtype)
+    page_len = lat_pool.shape[1]
+    cu = fb.cu_q_host if fb.cu_q_host is not None else fb.cu_q.tolist()
+    kv_lens = fb.kv_lens.tolist()
+    for b in range(len(cu) - 1):
+        q0, q1 = cu[b], cu[b + 1]
+        if q1 == q0:
+            continue
+        L = kv_lens[b]
+        npg = (L + page_len - 1) // page_len
+        lat = lat_pool[fb.page_table[b, :npg].long()].reshape(-1, Dq)[:L].float()
+        s = torch.einsum("qhd,kd->hqk", q_full[q0:q1].float(), lat) * scale
+        qpos = torch.arange(L - (q1 - q0), L, device=s.device)[:, None]
+        kpos = torch.arange(L, device=s.device)[None, :]
+        s = s.masked_fill(kpos > qpos, float("-inf"))
+        p = torch.softmax(s, dim=-1)
+        out[q0:q1] = torch.einsum("hqk,kl->qhl", p, lat[:, :lora]).to(out.dtype)
+    return out

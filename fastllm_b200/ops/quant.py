@@ -1,0 +1,158 @@
+"""Weight quantisation formats and the ``LinearWeight`` holder that dispatches a linear layer by format.
+
+Formats (numerics follow the reference quantiser, include/fastllm.h:239-306 and
+src/fastllm.cpp:1033-1145, 1311-1577):
+
+* ``int8``   per-output-channel asymmetric: ``scale = (max-min)/255``, ``zero = round(-min/scale)``,
+             ``w ~ scale * (q - zero)``, q stored as uint8.
+* ``int4g``  group-wise asymmetric 4 bit (group 128 by default): per (row, group) ``min`` and
+             ``scale = (max-min)/15``, ``w ~ min + scale * q``; two values per byte, FIRST value in the
+             HIGH nibble.
+* ``fp8``    FP8-E4M3 with one fp32 scale per 128x128 weight block (``weight_scale_inv`` convention of
+             block-scaled checkpoints): ``w ~ fp8 * scale``.
+* ``dense``  fp16 / bf16.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import basic as B
+
+FP8_MAX = 448.0
+
+
+# ---------------------------------------------------------------------------------------------------
+# quantisers (pure torch; run on whatever device the weight lives on)
+# ---------------------------------------------------------------------------------------------------
+def quantize_int8(w: torch.Tensor):
+    wf = w.float()
+    mn = wf.amin(dim=1, keepdim=True).clamp(max=0.0)
+    mx = wf.amax(dim=1, keepdim=True).clamp(min=0.0)
+    scale = ((mx - mn) / 255.0).clamp(min=1e-12)
+    zero = torch.round(-mn / scale).clamp(0, 255)
+    q = torch.round(wf / scale + zero).clamp(0, 255).to(torch.uint8)
+    return q, scale.squeeze(1), zero.squeeze(1)
+
+
+def dequantize_int8(q, scale, zero, dtype):
+    return ((q.float() - zero[:, None]) * scale[:, None]).to(dtype)
+
+
+def quantize_int4g(w: torch.Tensor, group: int = 128):
+    n, k = w.shape
+    if k % group != 0:
+        raise ValueError(f"in-features {k} not divisible by group {group}")
+    wf = w.float().reshape(n, k // group, group)
+    mn = wf.amin(dim=2, keepdim=True)
+    mx = wf.amax(dim=2, keepdim=True)
+    scale = ((mx - mn) / 15.0).clamp(min=1e-12)
+    q = torch.round((wf - mn) / scale).clamp(0, 15).to(torch.uint8).reshape(n, k)
+    packed = (q[:, 0::2] << 4) | q[:, 1::2]
+    return packed.contiguous(), scale.squeeze(2).contiguous(), mn.squeeze(2).contiguous()
+
+
+def dequantize_int4g(packed, scale, mn, dtype, group: int = 128):
+    n, kh = packed.shape
+    q = torch.stack([(packed >> 4) & 0xF, packed & 0xF], dim=2).reshape(n, kh * 2).float()
+    q = q.reshape(n, -1, group)
+    return (q * scale[:, :, None] + mn[:, :, None]).reshape(n, kh * 2).to(dtype)
+
+
+def quantize_fp8_block(w: torch.Tensor, block: int = 128):
+    n, k = w.shape
+    nb, kb = (n + block - 1) // block, (k + block - 1) // block
+    wf = torch.zeros((nb * block, kb * block), dtype=torch.float32, device=w.device)
+    wf[:n, :k] = w.float()
+    t = wf.reshape(nb, block, kb, block)
+    amax = t.abs().amax(dim=(1, 3)).clamp(min=1e-12)
+    scale = amax / FP8_MAX
+    q = (t / scale[:, None, :, None]).reshape(nb * block, kb * block)[:n, :k].to(torch.float8_e4m3fn)
+    return q.contiguous(), scale.contiguous()
+
+
+def dequantize_fp8_block(q, scale, dtype, block: int = 128):
+    n, k = q.shape
+    s = scale.repeat_interleave(block, 0)[:n].repeat_interleave(block, 1)[:, :k]
+    return (q.float() * s).to(dtype)
+
+
+def normalize_wdtype(name: str | None) -> tuple[str, int]:
+    """Map CLI dtype names (``--dtype`` / ``--moe_dtype``) to (kind, group)."""
+    if name is None:
+        return "dense", 0
+    n = str(name).lower()
+    if n in ("auto", "float16", "fp16", "half", "bfloat16", "bf16", "float32", "fp32", "dense"):
+        return "dense", 0
+    if n in ("int8",):
+        return "int8", 0
+    if n.startswith("int4g"):
+        g = n[5:]
+        return "int4g", int(g) if g else 128
+    if n in ("int4",):
+        return "int4g", 128
+    if n in ("fp8", "fp8_e4m3", "float8", "fp8_block128"):
+        return "fp8", 128
+    raise ValueError(f"unsupported weight dtype '{name}'")
+
+
+# ---------------------------------------------------------------------------------------------------
+class LinearWeight:
+    """Weight (+ optional bias) of one linear layer in one of the storage formats above."""
+
+    __slots__ = ("kind", "w", "scale", "zero", "bias", "group", "n", "k", "interleaved", "dtype", "_dq")
+
+    def __init__(self, kind, w, scale=None, zero=None, bias=None, group=0, dtype=torch.bfloat16, interleaved=False):
+        self.kind, self.w, self.scale, self.zero, self.bias, self.group = kind, w, scale, zero, bias, group
+        self.n = w.shape[0]
+        self.k = w.shape[1] * (2 if kind == "int4g" else 1)
+        self.dtype = dtype
+        self.interleaved = interleaved      # gate/up rows interleaved per 128-row tile for the SwiGLU epilogue
+        self._dq = None
+
+    @staticmethod
+    def from_dense(w: torch.Tensor, wdtype: str = "dense", bias=None, interleaved=False, act_dtype=None) -> "LinearWeight":
+        kind, group = normalize_wdtype(wdtype)
+        act_dtype = act_dtype or (w.dtype if w.dtype in (torch.float16, torch.bfloat16) else torch.bfloat16)
+        if kind == "dense":
+            return LinearWeight("dense", w.contiguous(), bias=bias, dtype=w.dtype, interleaved=interleaved)
+        if kind == "int8":
+            q, s, z = quantize_int8(w)
+            return LinearWeight("int8", q, s, z, bias, dtype=act_dtype, interleaved=interleaved)
+        if kind == "int4g":
+            if w.shape[1] % group != 0:
+                return LinearWeight("dense", w.contiguous(), bias=bias, dtype=w.dtype, interleaved=interleaved)
+            q, s, mn = quantize_int4g(w, group)
+            return LinearWeight("int4g", q, s, mn, bias, group, act_dtype, interleaved)
+        q, s = quantize_fp8_block(w, 128)
+        return LinearWeight("fp8", q, s, None, bias, 128, act_dtype, interleaved)
+
+    def dequant(self, dtype=None) -> torch.Tensor:
+        dtype = dtype or self.dtype
+        if self.kind == "dense":
+            return self.w if self.w.dtype == dtype else self.w.to(dtype)
+        if self.kind == "int8":
+            return dequantize_int8(self.w, self.scale, self.zero, dtype)
+        if self.kind == "int4g":
+            return dequantize_int4g(self.w, self.scale, self.zero, dtype, self.group)
+        return dequantize_fp8_block(self.w, self.scale, dtype, self.group)
+
+    def nbytes(self) -> int:
+        n = self.w.numel() * self.w.element_size()
+        for t in (self.scale, self.zero, self.bias):
+            if t is not None:
+                n += t.numel() * t.element_size()
+        return n
+
+    def __call__(self, x, residual=None, swiglu=False, out_f32=False):
+        if self.kind == "dense":
+            w = self.w
+            if w.dtype != x.dtype:
+                w = w.to(x.dtype)
+            return B.linear(x, w, self.bias, residual, swiglu, self.interleaved, out_f32)
+        if x.is_cuda:
+            from . import quant_gemm
+
+            y = quant_gemm.linear_quant(x, self, residual, swiglu, out_f32)
+            if y is not None:
+                return y
+        return B.linear(x, self.dequant(x.dtype), self.bias, residual, swiglu, self.interleaved, out_f32)
