@@ -19,7 +19,6 @@ FB_DEFINE_ERROR_API(attn_decode)
 namespace fb {
 
 constexpr int KID_ATTN_DECODE = 10;
-constexpr int AD_STAGES = 3;
 constexpr int AD_D = 128;
 constexpr int AD_PAGE = 128;
 constexpr int AD_NPAD = 16;
@@ -27,7 +26,7 @@ constexpr int AD_K_BYTES = AD_PAGE * AD_D * 2;     // 32 KB
 constexpr int AD_Q_BYTES = AD_NPAD * AD_D * 2;     // 4 KB
 constexpr int AD_STAGE_BYTES = 2 * AD_K_BYTES + AD_Q_BYTES;   // K, V, Q
 constexpr int AD_P_BYTES = AD_NPAD * AD_PAGE * 2;  // 4 KB
-constexpr int AD_SMEM_BYTES = AD_STAGES * AD_STAGE_BYTES + AD_P_BYTES + 1024 /*barriers+red*/ + 1024 /*align*/;
+constexpr int ad_smem_bytes(int stages) { return stages * AD_STAGE_BYTES + AD_P_BYTES + 1024 /*barriers+red*/ + 1024 /*align*/; }
 
 struct AttnDecodeParams {
   const int* work;        // [n_work][2] = (request, page index within the request)
@@ -37,6 +36,7 @@ struct AttnDecodeParams {
   float* part_o;          // [B, Hkv, max_splits, G, D]
   float* part_ml;         // [B, Hkv, max_splits, G, 2]
   int max_pages, max_splits, Hq, Hkv, G;
+  int B, max_items;       // bounds for validating work items read from device memory
   float scale_log2;       // softmax scale * log2(e)
   uint32_t idesc_s, idesc_o;
 };
@@ -68,8 +68,8 @@ __global__ void attn_decode_plan_kernel(const int* __restrict__ seq_lens, int B,
   if (t == 0) { const int total = offs[B]; *n_work = total < max_items ? total : max_items; }
 }
 
-template <bool BF16>
-__global__ void __launch_bounds__(192, 1)
+template <bool BF16, int AD_STAGES>
+__global__ void __launch_bounds__(192, AD_STAGES == 1 ? 3 : 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const __grid_constant__ CUtensorMap tmQ, const AttnDecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -78,8 +78,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + AD_P_BYTES);
   uint64_t* full_k = bars;                  // [STAGES]  K + Q landed
   uint64_t* full_v = bars + AD_STAGES;      // [STAGES]
-  uint64_t* empty = bars + 2 * AD_STAGES;   // [STAGES]
-  uint64_t* s_full = bars + 3 * AD_STAGES;
+  uint64_t* empty_k = bars + 2 * AD_STAGES;   // [STAGES]  K + Q consumed (S MMA done)
+  uint64_t* empty_v = bars + 3 * AD_STAGES;   // [STAGES]  V consumed (PV MMA done)
+  uint64_t* s_full = bars + 4 * AD_STAGES;
   uint64_t* p_ready = s_full + 1;
   uint64_t* o_full = s_full + 2;
   uint64_t* o_empty = s_full + 3;
@@ -88,11 +89,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   float* red_sum = red_max + 64;                                  // [2 parity][4 warps][16]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int total = (*p.n_work) * p.Hkv;
+  int n_items = *p.n_work;
+  if (n_items < 0) n_items = 0;
+  if (n_items > p.max_items) n_items = p.max_items;   // never trust a count read from memory beyond the list's capacity
+  const int total = n_items * p.Hkv;
   bool dead = false;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < AD_STAGES; ++s) { mbar_init(&full_k[s], 1); mbar_init(&full_v[s], 1); mbar_init(&empty[s], 1); }
+    for (int s = 0; s < AD_STAGES; ++s) { mbar_init(&full_k[s], 1); mbar_init(&full_v[s], 1); mbar_init(&empty_k[s], 1); mbar_init(&empty_v[s], 1); }
     mbar_init(s_full, 1);
     mbar_init(p_ready, 128);
     mbar_init(o_full, 1);
@@ -112,11 +116,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       int it = 0;
       for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
         const int item = w / p.Hkv, kvh = w - item * p.Hkv;
-        const int b = p.work[2 * item], pg = p.work[2 * item + 1];
+        int b = p.work[2 * item], pg = p.work[2 * item + 1];
+        if ((unsigned)b >= (unsigned)p.B || (unsigned)pg >= (unsigned)p.max_splits || pg >= p.max_pages) {
+          report_error(ERR_BAD_ARG, KID_ATTN_DECODE, 20);
+          b = 0; pg = 0;
+        }
         const int page = p.page_table[(size_t)b * p.max_pages + pg];
         const int s = it % AD_STAGES;
         const uint32_t ph = (uint32_t)(it / AD_STAGES) & 1u;
-        if (!mbar_wait(&empty[s], ph ^ 1u, dead, KID_ATTN_DECODE, 1)) break;
+        if (!mbar_wait(&empty_k[s], ph ^ 1u, dead, KID_ATTN_DECODE, 1)) break;
         uint8_t* kb = smem + s * AD_STAGE_BYTES;
         uint8_t* vb = kb + AD_K_BYTES;
         uint8_t* qb = vb + AD_K_BYTES;
@@ -125,6 +133,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         tma_load_2d(kb + AD_K_BYTES / 2, &tmK, &full_k[s], kvh * AD_D + 64, page * AD_PAGE);
         tma_load_2d(qb, &tmQ, &full_k[s], 0, b * p.Hq + kvh * p.G);
         tma_load_2d(qb + AD_Q_BYTES / 2, &tmQ, &full_k[s], 64, b * p.Hq + kvh * p.G);
+        if (!mbar_wait(&empty_v[s], ph ^ 1u, dead, KID_ATTN_DECODE, 8)) break;
         mbar_expect_tx(&full_v[s], AD_K_BYTES);
         tma_load_2d(vb, &tmV, &full_v[s], kvh * AD_D, page * AD_PAGE);
         tma_load_2d(vb + AD_K_BYTES / 2, &tmV, &full_v[s], kvh * AD_D + 64, page * AD_PAGE);
@@ -150,6 +159,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           umma_f16(tmem_s, da, db, p.idesc_s, k != 0 ? 1u : 0u);
         }
         umma_commit(s_full);
+        umma_commit(&empty_k[s]);
         if (!mbar_wait(p_ready, iph, dead, KID_ATTN_DECODE, 3)) break;
         if (!mbar_wait(&full_v[s], ph, dead, KID_ATTN_DECODE, 4)) break;
         if (it > 0 && !mbar_wait(o_empty, iph ^ 1u, dead, KID_ATTN_DECODE, 5)) break;
@@ -163,7 +173,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           umma_f16(tmem_o, da, db, p.idesc_o, k != 0 ? 1u : 0u);
         }
         umma_commit(o_full);
-        umma_commit(&empty[s]);
+        umma_commit(&empty_v[s]);
       }
     }
     __syncwarp();
@@ -174,7 +184,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     int it = 0;
     for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
       const int item = w / p.Hkv, kvh = w - item * p.Hkv;
-      const int b = p.work[2 * item], pg = p.work[2 * item + 1];
+      int b = p.work[2 * item], pg = p.work[2 * item + 1];
+      if ((unsigned)b >= (unsigned)p.B || (unsigned)pg >= (unsigned)p.max_splits || pg >= p.max_pages) { b = 0; pg = 0; }
       const int seq = p.seq_lens[b];
       const uint32_t iph = (uint32_t)it & 1u;
       const bool valid = pg * AD_PAGE + t < seq;
@@ -281,8 +292,8 @@ extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n
 // k_pool/v_pool: [num_slots, Hkv, 128].  dtype: 0 = fp16, 1 = bf16.
 extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
                               const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
-                              int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, float scale,
-                              int dtype, int grid_ctas, void* stream_) {
+                              int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, int max_items,
+                              float scale, int dtype, int grid_ctas, void* stream_) {
   if (B <= 0) return 0;
   if (D != AD_D || Hq % Hkv != 0) return -1;
   const int G = Hq / Hkv;
@@ -295,21 +306,30 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
   AttnDecodeParams p;
   p.work = work; p.n_work = n_work; p.page_table = page_table; p.seq_lens = seq_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.max_pages = max_pages; p.max_splits = max_splits; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
+  p.B = B; p.max_items = max_items;
   p.scale_log2 = scale * 1.4426950408889634f;
   const uint32_t f = dtype == 1 ? 1u : 0u;
   p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);
   p.idesc_o = make_idesc(f, f, 1, 0, 128, AD_NPAD);
-  if (grid_ctas <= 0) grid_ctas = 148;
-  if (dtype == 1) {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM_BYTES); cfg = true; }
-    attn_decode_kernel<true><<<grid_ctas, 192, AD_SMEM_BYTES, stream>>>(tmK, tmV, tmQ, p);
-    attn_decode_combine_kernel<true><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits);
-  } else {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AD_SMEM_BYTES); cfg = true; }
-    attn_decode_kernel<false><<<grid_ctas, 192, AD_SMEM_BYTES, stream>>>(tmK, tmV, tmQ, p);
-    attn_decode_combine_kernel<false><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits);
+  // stages: 1 -> 3 resident CTAs per SM hide each other's load latency; 3 -> one CTA per SM with a deep ring
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   }
+  const bool deep = grid_ctas < 0;
+  if (grid_ctas < 0) grid_ctas = -grid_ctas;
+  if (grid_ctas == 0) grid_ctas = deep ? sm_count : 2 * sm_count;
+#define FB_AD_LAUNCH(BF, ST)                                                                                            \
+  {                                                                                                                     \
+    static bool cfg = false;                                                                                            \
+    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); cfg = true; } \
+    attn_decode_kernel<BF, ST><<<grid_ctas, 192, ad_smem_bytes(ST), stream>>>(tmK, tmV, tmQ, p);                         \
+    attn_decode_combine_kernel<BF><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits); \
+  }
+  if (dtype == 1) { if (deep) FB_AD_LAUNCH(true, 3) else FB_AD_LAUNCH(true, 1) }
+  else { if (deep) FB_AD_LAUNCH(false, 3) else FB_AD_LAUNCH(false, 1) }
+#undef FB_AD_LAUNCH
   return (int)cudaGetLastError();
 }

@@ -1,0 +1,391 @@
+// Tensor-parallel communication kernels over NVLink peer memory (sm_100a): no NCCL call on these paths.
+//
+//  * fb_gemm_ar_norm: row-parallel small-M GEMM (tcgen05, swap-AB, cluster split-K) FUSED with
+//    reduce-scatter -> (+residual) -> RMSNorm -> all-gather in ONE kernel:
+//       phase 1  every CTA writes its fp32 partial tile into this rank's slice of the symmetric arena
+//       sync 1   one arrival per CTA on a counter in every rank (multimem.red through NVSwitch, or P2P red)
+//       phase 2  rank r owns token rows [r*M/tp, (r+1)*M/tp): it sums the partials of all ranks for its
+//                rows (multimem.ld_reduce = in-switch reduction, or P2P loads in rank order), adds the
+//                residual row, writes the new residual stream row and its RMSNorm'd version to EVERY
+//                rank (multimem.st, or P2P stores)
+//       sync 2   second counter; the kernel ends only when every rank's rows have landed here, so the
+//                next kernel on the stream can read the full hidden state without further waits.
+//  * fb_ar_norm: phases 2.. alone for partials produced elsewhere (MoE output, embeddings).
+//  * fb_argmax_merge: all-gather of per-rank (max, arg-max) candidates + merge (vocab-sharded greedy).
+//
+// The reference's counterpart is a separate custom all-reduce launch after the GEMM, with unbounded
+// spins (src/devices/multicuda/fastllm-custom-allreduce.cu:242-368, fused add at :638); here every wait
+// is bounded in time and reports through the error word.
+//
+// Counters only grow; the expected value is carried in a local word, so no reset races exist.  All CTAs
+// of a launch must be co-resident (they wait for each other across ranks): launchers check the grid
+// against the SM count.
+#include "gemm_smallm.cuh"
+#include "tmap.h"
+
+FB_DEFINE_ERROR_API(comm)
+
+namespace fb {
+
+constexpr int KID_GEMM_AR = 30;
+constexpr int KID_AR_NORM = 31;
+constexpr int KID_ARGMAX_MERGE = 32;
+constexpr int MAX_TP = 8;
+
+// arena header layout (bytes from the arena base); each word on its own 128-byte line
+constexpr uint32_t OFF_CNT1 = 0, OFF_CNT2 = 128, OFF_EXPECT = 256, OFF_TICKET = 384, OFF_HEADER_END = 1024;
+
+struct CommCtx {
+  uint8_t* local;            // this rank's arena
+  uint8_t* mc;               // multicast mapping of the arena (nullptr: use peer pointers)
+  uint8_t* peer[MAX_TP];     // every rank's arena as seen from this GPU (peer[rank] == local)
+  int rank, tp;
+};
+
+struct ArNormParams {
+  CommCtx c;
+  uint64_t off_part;         // fp32 [M, N] partial sums (symmetric offset)
+  uint64_t off_h;            // 16-bit [M, N] residual stream (read: own rows; written: all ranks)
+  uint64_t off_x;            // 16-bit [M, N] normalised output
+  const uint16_t* ln_w;      // RMSNorm weight [N] (nullptr: skip the norm, x is not written)
+  int M, N;
+  int has_residual;
+  float eps, unit_offset;
+};
+
+__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void mc_red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 mc_ld_reduce_f32x4(const void* p) {
+  float4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void mc_st_b32x4(void* p, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};\n"
+               ::"l"(p), "f"(__uint_as_float(v.x)), "f"(__uint_as_float(v.y)), "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w))
+               : "memory");
+}
+
+// one arrival on counter `off` of every rank
+__device__ __forceinline__ void signal_all(const CommCtx& c, uint32_t off) {
+  __threadfence_system();
+  if (c.mc) {
+    mc_red_add_release_sys(reinterpret_cast<uint32_t*>(c.mc + off), 1u);
+  } else {
+    for (int r = 0; r < c.tp; ++r) red_add_release_sys(reinterpret_cast<uint32_t*>(c.peer[r] + off), 1u);
+  }
+}
+// bounded wait until the local counter has reached `target` (wrap-safe)
+__device__ __forceinline__ bool wait_counter(const CommCtx& c, uint32_t off, uint32_t target, int kernel_id, int site) {
+  const uint32_t* p = reinterpret_cast<const uint32_t*>(c.local + off);
+  if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
+    if (globaltimer_ns() - t0 > FB_WAIT_LIMIT_NS) break;
+    __nanosleep(20);
+  }
+  report_error(ERR_PEER_TIMEOUT, kernel_id, site);
+  return false;
+}
+
+// Phases 2.. of the fused all-reduce; called by every thread of every CTA.  `base` = value of the expect word
+// read at kernel start; n_ctas = CTAs per rank in this launch.
+template <bool BF16>
+__device__ __forceinline__ void ar_norm_tail(const ArNormParams& p, uint32_t base, int cta, int n_ctas, int kernel_id) {
+  __shared__ float sh_red[8];
+  __shared__ int sh_ok;
+  const CommCtx& c = p.c;
+  const uint32_t target = base + (uint32_t)(c.tp * n_ctas);
+  const int tid = threadIdx.x, nthr = blockDim.x;
+  // ---- sync 1: all partials of all ranks are in their arenas ----
+  __syncthreads();
+  if (tid == 0) {
+    signal_all(c, OFF_CNT1);
+    sh_ok = wait_counter(c, OFF_CNT1, target, kernel_id, 1) ? 1 : 0;
+  }
+  __syncthreads();
+  const bool ok = sh_ok != 0;
+  // ---- phase 2: own rows ----
+  const int rows_per = (p.M + c.tp - 1) / c.tp;
+  const int row0 = c.rank * rows_per;
+  int row1 = row0 + rows_per; if (row1 > p.M) row1 = p.M;
+  const int N = p.N;
+  const int chunks = N >> 3;                         // 8 columns per chunk
+  constexpr int MAXC = 12;
+  for (int row = row0 + cta; ok && row < row1; row += n_ctas) {
+    uint4 hv[MAXC];
+    float ss = 0.f;
+    int cnt = 0;
+    for (int ch = tid; ch < chunks; ch += nthr, ++cnt) {
+      const size_t eoff = (size_t)row * N + (size_t)ch * 8;
+      float4 a, b;
+      if (c.mc) {
+        a = mc_ld_reduce_f32x4(c.mc + p.off_part + eoff * 4);
+        b = mc_ld_reduce_f32x4(c.mc + p.off_part + eoff * 4 + 16);
+      } else {
+        a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
+        for (int r = 0; r < c.tp; ++r) {
+          const float4* src = reinterpret_cast<const float4*>(c.peer[r] + p.off_part + eoff * 4);
+          const float4 u = src[0], w = src[1];
+          a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+          b.x += w.x; b.y += w.y; b.z += w.z; b.w += w.w;
+        }
+      }
+      if (p.has_residual) {
+        const uint4 rv = *reinterpret_cast<const uint4*>(c.local + p.off_h + eoff * 2);
+        const float2 r0 = unpack_16<BF16>(rv.x), r1 = unpack_16<BF16>(rv.y), r2 = unpack_16<BF16>(rv.z), r3 = unpack_16<BF16>(rv.w);
+        a.x += r0.x; a.y += r0.y; a.z += r1.x; a.w += r1.y;
+        b.x += r2.x; b.y += r2.y; b.z += r3.x; b.w += r3.y;
+      }
+      uint4 o;
+      o.x = pack_16<BF16>(a.x, a.y); o.y = pack_16<BF16>(a.z, a.w); o.z = pack_16<BF16>(b.x, b.y); o.w = pack_16<BF16>(b.z, b.w);
+      if (cnt < MAXC) hv[cnt] = o;
+      // the norm sees the rounded values, exactly what a separate RMSNorm kernel would read back
+      const float2 q0 = unpack_16<BF16>(o.x), q1 = unpack_16<BF16>(o.y), q2 = unpack_16<BF16>(o.z), q3 = unpack_16<BF16>(o.w);
+      ss += q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y + q2.x * q2.x + q2.y * q2.y + q3.x * q3.x + q3.y * q3.y;
+      if (c.mc) {
+        mc_st_b32x4(c.mc + p.off_h + eoff * 2, o);
+      } else {
+        for (int r = 0; r < c.tp; ++r) *reinterpret_cast<uint4*>(c.peer[r] + p.off_h + eoff * 2) = o;
+      }
+    }
+    if (p.ln_w != nullptr) {
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      __syncthreads();
+      if ((tid & 31) == 0) sh_red[tid >> 5] = ss;
+      __syncthreads();
+      float tot = 0.f;
+      for (int w = 0; w < (nthr >> 5); ++w) tot += sh_red[w];
+      const float inv = rsqrtf(tot / (float)N + p.eps);
+      cnt = 0;
+      for (int ch = tid; ch < chunks; ch += nthr, ++cnt) {
+        const size_t eoff = (size_t)row * N + (size_t)ch * 8;
+        const uint4 h = hv[cnt < MAXC ? cnt : MAXC - 1];
+        const uint4 wv = *reinterpret_cast<const uint4*>(p.ln_w + (size_t)ch * 8);
+        const float2 h0 = unpack_16<BF16>(h.x), h1 = unpack_16<BF16>(h.y), h2 = unpack_16<BF16>(h.z), h3 = unpack_16<BF16>(h.w);
+        const float2 w0 = unpack_16<BF16>(wv.x), w1 = unpack_16<BF16>(wv.y), w2 = unpack_16<BF16>(wv.z), w3 = unpack_16<BF16>(wv.w);
+        const float uo = p.unit_offset;
+        uint4 o;
+        o.x = pack_16<BF16>(h0.x * inv * (w0.x + uo), h0.y * inv * (w0.y + uo));
+        o.y = pack_16<BF16>(h1.x * inv * (w1.x + uo), h1.y * inv * (w1.y + uo));
+        o.z = pack_16<BF16>(h2.x * inv * (w2.x + uo), h2.y * inv * (w2.y + uo));
+        o.w = pack_16<BF16>(h3.x * inv * (w3.x + uo), h3.y * inv * (w3.y + uo));
+        if (c.mc) {
+          mc_st_b32x4(c.mc + p.off_x + eoff * 2, o);
+        } else {
+          for (int r = 0; r < c.tp; ++r) *reinterpret_cast<uint4*>(c.peer[r] + p.off_x + eoff * 2) = o;
+        }
+      }
+    }
+  }
+  // ---- sync 2: every rank's rows have been written everywhere ----
+  __syncthreads();
+  if (tid == 0) {
+    signal_all(c, OFF_CNT2);
+    wait_counter(c, OFF_CNT2, target, kernel_id, 2);
+    // the last CTA of this rank to get here publishes the new expected value for the next launch
+    uint32_t* ticket = reinterpret_cast<uint32_t*>(c.local + OFF_TICKET);
+    if (atomicAdd(ticket, 1u) == (uint32_t)(n_ctas - 1)) {
+      *ticket = 0u;
+      *reinterpret_cast<volatile uint32_t*>(c.local + OFF_EXPECT) = target;
+      __threadfence();
+    }
+  }
+}
+
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(192, 1)
+gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams g,
+                    const ArNormParams p) {
+  const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
+  uint32_t tmem_base;
+  gemm_smallm_device<MPAD, BF16>(tmW, tmX, g, tmem_base, KID_GEMM_AR);
+  if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD>::TMEM_COLS);
+  const int n_ctas = gridDim.x * gridDim.y;
+  ar_norm_tail<BF16>(p, base, blockIdx.y * gridDim.x + blockIdx.x, n_ctas, KID_GEMM_AR);
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(192, 1) ar_norm_kernel(const ArNormParams p) {
+  const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
+  ar_norm_tail<BF16>(p, base, blockIdx.x, gridDim.x, KID_AR_NORM);
+}
+
+// ---- vocab-sharded greedy merge: every rank publishes (max value, arg-max id) per row, then picks the best ----
+struct ArgmaxMergeParams {
+  CommCtx c;
+  uint64_t off_buf;          // [tp][B][2] 32-bit words (value as float bits, id)
+  const float* vals; const int* ids; int* out; int B;
+};
+__global__ void argmax_merge_kernel(const ArgmaxMergeParams p) {
+  __shared__ int sh_ok;
+  const CommCtx& c = p.c;
+  const uint32_t base = *reinterpret_cast<volatile uint32_t*>(c.local + OFF_EXPECT);
+  const uint32_t target = base + (uint32_t)c.tp;
+  const int tid = threadIdx.x;
+  for (int b = tid; b < p.B; b += blockDim.x) {
+    const uint2 v = make_uint2(__float_as_uint(p.vals[b]), (uint32_t)p.ids[b]);
+    const uint64_t off = p.off_buf + ((uint64_t)(c.rank * p.B + b)) * 8;
+    if (c.mc) {
+      asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1,%2};\n" ::"l"(c.mc + off), "f"(__uint_as_float(v.x)),
+                   "f"(__uint_as_float(v.y)) : "memory");
+    } else {
+      for (int r = 0; r < c.tp; ++r) *reinterpret_cast<uint2*>(c.peer[r] + off) = v;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    signal_all(c, OFF_CNT1);
+    sh_ok = wait_counter(c, OFF_CNT1, target, KID_ARGMAX_MERGE, 1) ? 1 : 0;
+  }
+  __syncthreads();
+  if (sh_ok) {
+    for (int b = tid; b < p.B; b += blockDim.x) {
+      float best = -INFINITY; int bi = 0;
+      for (int r = 0; r < c.tp; ++r) {
+        const volatile uint32_t* src = reinterpret_cast<const volatile uint32_t*>(c.local + p.off_buf + ((uint64_t)(r * p.B + b)) * 8);
+        const float f = __uint_as_float(src[0]);
+        if (f > best) { best = f; bi = (int)src[1]; }      // strict: ties keep the lower rank = lower token id
+      }
+      p.out[b] = bi;
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    // second counter keeps the buffer from being overwritten by a rank that is one launch ahead
+    signal_all(c, OFF_CNT2);
+    wait_counter(c, OFF_CNT2, target, KID_ARGMAX_MERGE, 2);
+    *reinterpret_cast<volatile uint32_t*>(c.local + OFF_EXPECT) = target;
+    __threadfence();
+  }
+}
+
+static int g_sm_count = 0;
+static int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return g_sm_count;
+}
+
+static void fill_ctx(CommCtx& c, void* local, void* mc, void* const* peers, int rank, int tp) {
+  c.local = (uint8_t*)local; c.mc = (uint8_t*)mc; c.rank = rank; c.tp = tp;
+  for (int i = 0; i < MAX_TP; ++i) c.peer[i] = i < tp ? (uint8_t*)peers[i] : nullptr;
+}
+
+template <int MPAD, bool BF16>
+static cudaError_t launch_gemm_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& g, const ArNormParams& p,
+                                  int nsplit, int n_tiles, cudaStream_t stream) {
+  using Cfg = SmallMCfg<MPAD>;
+  auto kern = gemm_ar_norm_kernel<MPAD, BF16>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  // all CTAs wait for each other across ranks: they must all be resident at once
+  int max_clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0 && n_tiles > max_clusters)
+    return cudaErrorLaunchOutOfResources;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, g, p);
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_gemm_pick_split(int M, int N, int K, int sm_count);
+
+// Arena header must be zeroed (and all ranks synchronised) once before the first launch.
+// X: [M, K_local] activations of this rank; W: [N, K_local] this rank's weight shard; bias only on one rank.
+// off_part / off_h / off_x: symmetric offsets inside the arena.  has_residual: h += sum (else h = sum).
+// ln_w == nullptr skips the norm.  Returns cudaErrorLaunchOutOfResources if the grid cannot be co-resident.
+extern "C" int fb_gemm_ar_norm(const void* X, const void* W, const void* bias, int M, int N, int K, int ldx, int ldw,
+                               void* arena_local, void* arena_mc, void* const* peers, int rank, int tp, unsigned long long off_part,
+                               unsigned long long off_h, unsigned long long off_x, const void* ln_w, int has_residual, float eps,
+                               float unit_offset, int dtype, int nsplit, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || M > 256 || K % 64 != 0 || N % 8 != 0 || N > 18432 || tp > MAX_TP) return -1;
+  const bool bf16 = dtype == 1;
+  const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  const int n_tiles = (N + 127) / 128;
+  if (nsplit <= 0) nsplit = fb_gemm_pick_split(M, N, K, sm_count());
+  while (nsplit > 1 && n_tiles * nsplit > sm_count()) nsplit >>= 1;
+  if (n_tiles * nsplit > sm_count()) return (int)cudaErrorLaunchOutOfResources;
+  GemmParams g;
+  g.out = (uint8_t*)arena_local + off_part; g.bias = bias; g.residual = nullptr;
+  g.M = M; g.N = N; g.K = K; g.ld_out = N; g.ld_res = 0;
+  g.kb_total = K / 64; g.kb_per_split = (g.kb_total + nsplit - 1) / nsplit;
+  g.flags = GEMM_OUT_F32 | (bias ? GEMM_BIAS : 0);
+  g.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
+  ArNormParams p;
+  fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
+  p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
+  p.has_residual = has_residual; p.eps = eps; p.unit_offset = unit_offset;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, W, N, K, ldw, 128, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
+#define FB_GA(MP)                                                                                       \
+  return (int)(bf16 ? launch_gemm_ar<MP, true>(tmW, tmX, g, p, nsplit, n_tiles, stream)                  \
+                    : launch_gemm_ar<MP, false>(tmW, tmX, g, p, nsplit, n_tiles, stream));
+  switch (mpad) {
+    case 16: FB_GA(16)
+    case 32: FB_GA(32)
+    case 64: FB_GA(64)
+    case 128: FB_GA(128)
+    default: FB_GA(256)
+  }
+#undef FB_GA
+}
+
+// All-reduce (+residual, +RMSNorm) of fp32 partials that already sit at off_part in every rank's arena.
+extern "C" int fb_ar_norm(int M, int N, void* arena_local, void* arena_mc, void* const* peers, int rank, int tp,
+                          unsigned long long off_part, unsigned long long off_h, unsigned long long off_x, const void* ln_w,
+                          int has_residual, float eps, float unit_offset, int dtype, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N % 8 != 0 || N > 18432 || tp > MAX_TP) return -1;
+  ArNormParams p;
+  fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
+  p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
+  p.has_residual = has_residual; p.eps = eps; p.unit_offset = unit_offset;
+  int rows_per = (M + tp - 1) / tp;
+  int grid = rows_per < 1 ? 1 : rows_per;
+  if (grid > sm_count()) grid = sm_count();
+  if (dtype == 1) ar_norm_kernel<true><<<grid, 192, 0, stream>>>(p);
+  else ar_norm_kernel<false><<<grid, 192, 0, stream>>>(p);
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_argmax_merge(const float* vals, const int* ids, int* out, int B, void* arena_local, void* arena_mc,
+                               void* const* peers, int rank, int tp, unsigned long long off_buf, void* stream_) {
+  if (B <= 0 || tp > MAX_TP) return -1;
+  ArgmaxMergeParams p;
+  fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
+  p.off_buf = off_buf; p.vals = vals; p.ids = ids; p.out = out; p.B = B;
+  argmax_merge_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,202 @@
+// Small-M (decode) tcgen05 GEMM body shared by the plain GEMM kernel and the fused GEMM + all-reduce kernel.
+// See gemm_bf16.cu for the design notes.
+#pragma once
+#include "ptx.cuh"
+
+namespace fb {
+
+constexpr int KID_GEMM_SMALLM_PLAIN = 1;
+constexpr int KID_GEMM_LARGEM = 2;
+
+enum GemmFlags : int {
+  GEMM_BIAS = 1,       // += bias[n]
+  GEMM_RESIDUAL = 2,   // += residual[m, n]
+  GEMM_SWIGLU = 4,     // out[m, i] = silu(gate) * up   (N_out = N / 2)
+  GEMM_OUT_F32 = 8,    // write fp32 instead of the 16-bit input dtype
+};
+
+struct GemmParams {
+  void* out;
+  const void* bias;
+  const void* residual;
+  int M, N, K;
+  int ld_out, ld_res;
+  int kb_per_split;   // 64-wide k blocks per cluster rank
+  int kb_total;
+  uint32_t idesc;
+  int flags;
+};
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
+
+template <int MPAD>
+struct SmallMCfg {
+  static constexpr int A_BYTES = 128 * 128;            // 128 rows x 64 bf16
+  static constexpr int B_BYTES = MPAD * 128;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int MAX_STAGES = (200 * 1024) / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 10 ? 10 : MAX_STAGES;
+  static constexpr int RED_BYTES = MPAD * 128 * 4;     // fp32 partial tile [MPAD][128]
+  static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
+  static constexpr int SMEM_BYTES = BODY_BYTES + 256 + 1024;   // + barriers + alignment slack
+  static constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
+};
+
+// Body of the small-M kernel.  Returns with the output tile written and every cluster peer done reading this
+// CTA's shared memory; the caller still owns TMEM (returned in tmem_base_out) and must release it from warp 1.
+template <int MPAD, bool BF16>
+__device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
+                                                   uint32_t& tmem_base_out, int kernel_id) {
+  using Cfg = SmallMCfg<MPAD>;
+  const int KID_GEMM_SMALLM = kernel_id;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* accum_bar = empty_bar + Cfg::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = (int)cluster_ctarank();
+  const int nsplit = (int)cluster_nctarank();
+  const int n_tile = blockIdx.y;
+  const int kb0 = split * p.kb_per_split;
+  int kb_cnt = p.kb_total - kb0;
+  if (kb_cnt > p.kb_per_split) kb_cnt = p.kb_per_split;
+  if (kb_cnt < 0) kb_cnt = 0;
+  bool dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(accum_bar, 1);
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_SMALLM, 1)) break;
+        uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 64, n_tile * 128, pol_w);
+        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], (kb0 + i) * 64, 0, pol_x);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_SMALLM, 2)) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+        const uint64_t db = make_smem_desc(a_addr + Cfg::A_BYTES, 16, 1024, SWZ_128B);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, p.idesc, (i | k) != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(accum_bar);
+    }
+    __syncwarp();
+  } else {
+    // epilogue warps 2..5: TMEM lanes [32q, 32q+32) -> fp32 partial tile P[token][n] in shared memory
+    const int q = warp & 3;
+    float* P = reinterpret_cast<float*>(smem);
+    const int n_local = q * 32 + lane;
+    if (kb_cnt > 0) {
+      mbar_wait(accum_bar, 0, dead, KID_GEMM_SMALLM, 3);
+      tc_fence_after_sync();
+      constexpr int CH = MPAD < 32 ? MPAD : 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < MPAD; c0 += CH) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if (CH == 32) tmem_ld_32x32b_x32(taddr, r); else tmem_ld_32x32b_x16(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; ++j) P[(c0 + j) * 128 + n_local] = __uint_as_float(r[j]);
+      }
+    } else {
+      for (int j = 0; j < MPAD; ++j) P[j * 128 + n_local] = 0.f;
+    }
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+
+  // ---- cross-CTA reduction over the k splits + epilogue; this CTA owns a column slice of the tile ----
+  {
+    const bool swiglu = (p.flags & GEMM_SWIGLU) != 0;
+    const int outw = swiglu ? 64 : 128;
+    const int per = outw / nsplit;           // columns owned by this CTA (>= 8)
+    const int vec_per_row = per >> 2;
+    const int items = p.M * vec_per_row;
+    const uint32_t P_addr = smem_u32(smem);
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+      const int j = it / vec_per_row;
+      const int c = split * per + (it - j * vec_per_row) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), acc2 = acc;
+      for (int s = 0; s < nsplit; ++s) {
+        const uint32_t ra = mapa_u32(P_addr + (uint32_t)(j * 128 + c) * 4u, (uint32_t)s);
+        float4 v = ld_dsmem_f4(ra);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        if (swiglu) {
+          float4 u = ld_dsmem_f4(ra + 64 * 4);
+          acc2.x += u.x; acc2.y += u.y; acc2.z += u.z; acc2.w += u.w;
+        }
+      }
+      int n_out;
+      if (swiglu) {
+        n_out = n_tile * 64 + c;
+        if (p.flags & GEMM_BIAS) {
+          const uint32_t* bg = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_tile * 128 + c);
+          float2 b0 = unpack_16<BF16>(bg[0]), b1 = unpack_16<BF16>(bg[1]);
+          float2 u0 = unpack_16<BF16>(bg[32]), u1 = unpack_16<BF16>(bg[33]);
+          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+          acc2.x += u0.x; acc2.y += u0.y; acc2.z += u1.x; acc2.w += u1.y;
+        }
+        acc.x = silu_f(acc.x) * acc2.x; acc.y = silu_f(acc.y) * acc2.y;
+        acc.z = silu_f(acc.z) * acc2.z; acc.w = silu_f(acc.w) * acc2.w;
+        if (n_out >= (p.N >> 1)) continue;
+      } else {
+        n_out = n_tile * 128 + c;
+        if (n_out >= p.N) continue;
+        if (p.flags & GEMM_BIAS) {
+          const uint32_t* bp = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_out);
+          float2 b0 = unpack_16<BF16>(bp[0]), b1 = unpack_16<BF16>(bp[1]);
+          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+        }
+      }
+      if (p.flags & GEMM_RESIDUAL) {
+        const uint2 rv = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)j * p.ld_res + n_out);
+        float2 r0 = unpack_16<BF16>(rv.x), r1 = unpack_16<BF16>(rv.y);
+        acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
+      }
+      if (p.flags & GEMM_OUT_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)j * p.ld_out + n_out) = acc;
+      } else {
+        uint2 o;
+        o.x = pack_16<BF16>(acc.x, acc.y);
+        o.y = pack_16<BF16>(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)j * p.ld_out + n_out) = o;
+      }
+    }
+  }
+  cluster_sync_all();   // peers may still be reading this CTA's partial tile
+  tmem_base_out = tmem_base;
+}
+
+}  // namespace fb

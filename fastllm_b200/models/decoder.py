@@ -110,6 +110,7 @@ class DecoderModel:
         self.num_kv_heads_local = max(1, cfg.num_kv_heads // self.tp.size)
         self.kv_replicas = max(1, self.tp.size // cfg.num_kv_heads)
         self._rope = None
+        self._fused_active = False
         self.rope_mode = {"neox": A.ROPE_NEOX, "interleaved": A.ROPE_INTERLEAVED, "none": A.ROPE_NONE}[cfg.rope_mode]
         self.rot_dim = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
         self.attn_scale = 1.0 / math.sqrt(cfg.q_head_dim)
@@ -143,10 +144,10 @@ class DecoderModel:
         return n * self.cfg.num_layers * torch.finfo(self.dtype).bits // 8
 
     # -----------------------------------------------------------------------------------------------
-    def _attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual):
+    def _attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual, next_ln):
         c = self.cfg
         if c.use_mla:
-            return self._mla_attention(lw, x, fb, kv, residual)
+            return self._mla_attention(lw, x, fb, kv, residual, next_ln)
         Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
         cos, sin = self.rope_tables()
         qkv = lw.qkv(x)
@@ -159,7 +160,7 @@ class DecoderModel:
         else:
             a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
                                cu_q_host=fb.cu_q_host)
-        return self._row_parallel(lw.o, a, residual)
+        return self._row_parallel_norm(lw.o, a, residual, next_ln)
 
     def _row_parallel(self, w: LinearWeight, x, residual):
         """Row-parallel linear (input dim sharded): partial GEMM, then sum over ranks, plus the residual."""
@@ -167,7 +168,38 @@ class DecoderModel:
             return w(x, residual=residual)
         return self.tp.comm.row_linear(w, x, residual)
 
-    def _mla_attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual):
+    def _norm(self, h, ln_w):
+        return B.rmsnorm(h, ln_w, self.cfg.rms_eps, unit_offset=self.cfg.norm_unit_offset)
+
+    def _row_parallel_norm(self, w: LinearWeight, x, h, next_ln):
+        """``h += row_parallel_linear(x)`` then ``RMSNorm(h)`` for the next block.  Returns (h, x_norm).
+
+        With the fused NVLink path this is ONE kernel (GEMM + reduce-scatter + residual + norm + all-gather).
+        """
+        c = self.cfg
+        if self._fused_active:
+            r = self.tp.comm.fused.gemm_ar_norm(w, x, next_ln, c.rms_eps, c.norm_unit_offset, True)
+            if r is None:
+                part = w(x)
+                r = self.tp.comm.fused.ar_norm(part, next_ln, c.rms_eps, c.norm_unit_offset, True)
+            return r
+        h = self._row_parallel(w, x, h)
+        return h, self._norm(h, next_ln)
+
+    def _reduce_norm(self, partial, h, next_ln, needs_reduce: bool):
+        """Same for a partial sum that did not come from a single GEMM (mixture-of-experts output)."""
+        c = self.cfg
+        if needs_reduce and self._fused_active:
+            return self.tp.comm.fused.ar_norm(partial, next_ln, c.rms_eps, c.norm_unit_offset, True)
+        if needs_reduce:
+            h = self.tp.all_reduce(partial, h)
+        elif self._fused_active:
+            h = self.tp.comm.fused.load_h(partial + h)
+        else:
+            h = partial + h
+        return h, self._norm(h, next_ln)
+
+    def _mla_attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual, next_ln):
         """Absorbed multi-head latent attention over a paged latent cache (kv_lora + rope dims per token).
 
         Reference: src/models/deepseekv2.cpp:283-697 (q_nope x W_UK -> MergeMLAPaged -> x W_UV -> o_proj).
@@ -199,14 +231,14 @@ class DecoderModel:
         q_full = torch.cat([q_lat, q_pe.to(x.dtype)], dim=-1)              # [T, H, lora + rope]
         o_lat = MOE.mla_paged_attention(q_full, lat_pool, fb, self.attn_scale, lora)   # [T, H, lora]
         o = torch.einsum("thl,hvl->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype).reshape(T, H * vd)
-        return self._row_parallel(lw.o, o, residual)
+        return self._row_parallel_norm(lw.o, o, residual, next_ln)
 
     # -----------------------------------------------------------------------------------------------
-    def _mlp(self, lw: MLPWeights, x, residual, layer_idx):
+    def _mlp(self, lw: MLPWeights, x, residual, layer_idx, next_ln):
         c = self.cfg
         if lw.experts is None:
             act = lw.gate_up(x, swiglu=True)
-            return self._row_parallel(lw.down, act, residual)
+            return self._row_parallel_norm(lw.down, act, residual, next_ln)
         # ---- mixture of experts ----
         logits = torch.matmul(x.float(), lw.router.t())
         idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
@@ -218,42 +250,41 @@ class DecoderModel:
             if lw.shared_gate is not None:
                 s = s * torch.sigmoid(torch.matmul(x.float(), lw.shared_gate.float().t())).to(s.dtype)
             y = y + s
-        if self.tp.size > 1 and (self.ep is None or lw.shared_gate_up is not None) and not MOE.output_is_complete(self.ep):
-            return self.tp.all_reduce(y, residual)
-        return y + residual
+        return self._reduce_norm(y, residual, next_ln, self.tp.size > 1)
 
     # -----------------------------------------------------------------------------------------------
     @torch.no_grad()
     def forward(self, fb: ForwardBatch, kv_caches) -> torch.Tensor:
         """Returns fp32 logits ``[R, vocab_local]`` for ``fb.logit_rows`` (all rows if None)."""
         c = self.cfg
+        T = fb.ids.shape[0]
+        fused = self.tp.comm.fused if (self.tp.size > 1 and self.tp.comm is not None) else None
+        self._fused_active = bool(fused is not None and self.on_cuda and fused.usable(T, c.hidden_size))
+        if fb.is_decode and self.on_cuda and fb.decode_ws is not None and not fb.decode_planned:
+            fb.decode_ws.plan(fb.kv_lens)
+            fb.decode_planned = True
         h = self.embed_tokens(fb.ids)
+        if self._fused_active:
+            h = fused.load_h(h)
+        n_layers = len(self.layers)
+        x = self._norm(h, self.layers[0].attn.ln)
         for i, lw in enumerate(self.layers):
-            x = B.rmsnorm(h, lw.attn.ln, c.rms_eps, unit_offset=c.norm_unit_offset)
-            h = self._attention(lw.attn, x, fb, kv_caches[i], h)
-            x = B.rmsnorm(h, lw.mlp.ln, c.rms_eps, unit_offset=c.norm_unit_offset)
-            h = self._mlp(lw.mlp, x, h, i)
+            h, x = self._attention(lw.attn, x, fb, kv_caches[i], h, lw.mlp.ln)
+            next_ln = self.layers[i + 1].attn.ln if i + 1 < n_layers else self.final_norm
+            h, x = self._mlp(lw.mlp, x, h, i, next_ln)
+        # x is RMSNorm(h) with the final norm weight (row-wise, so selecting rows afterwards is equivalent)
         if fb.logit_rows is not None:
-            h = h.index_select(0, fb.logit_rows)
-        x = B.rmsnorm(h, self.final_norm, c.rms_eps, unit_offset=c.norm_unit_offset)
+            x = x.index_select(0, fb.logit_rows)
         logits = self.lm_head(x, out_f32=True)
         if c.logit_scale != 1.0:
             logits = logits * c.logit_scale
         return logits
 
     def embed_tokens(self, ids):
-        c = self.cfg
-        if self.tp.size > 1 and self.embed.shape[0] != c.vocab_size:
-            lo, hi = self.vocab_shard
-            local = ids - lo
-            mask = (local >= 0) & (local < hi - lo)
-            h = B.embedding(torch.where(mask, local, torch.zeros_like(local)), self.embed)
-            h = h * mask[:, None].to(h.dtype)
-            h = self.tp.all_reduce(h)
-        else:
-            h = B.embedding(ids, self.embed)
-        if c.embed_scale != 1.0:
-            h = h * c.embed_scale
+        """Token embedding; the table is replicated on every tensor-parallel rank (no collective needed)."""
+        h = B.embedding(ids, self.embed)
+        if self.cfg.embed_scale != 1.0:
+            h = h * self.cfg.embed_scale
         return h
 
 

@@ -212,6 +212,8 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
                                    head_dim)
     if ws is None:
         ws = DecodeWorkspace(B, num_kv_heads, G, page_table.shape[1], q.device)
+    if B > ws.max_batch or page_table.shape[1] > ws.max_pages:
+        raise ValueError("decode workspace too small for this batch / page table")
     if not planned:
         ws.plan(seq_lens)
     if out is None:
@@ -220,7 +222,7 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
     rc = _lib.kernels().fb_attn_decode(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(ws.work),
                                        _ptr(ws.n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
                                        num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
-                                       float(scale), dtype_code(q.dtype), grid_ctas, _stream())
+                                       ws.work.shape[0], float(scale), dtype_code(q.dtype), grid_ctas, _stream())
     _lib.check(rc, "fb_attn_decode")
     return out
 

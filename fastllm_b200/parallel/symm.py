@@ -1,0 +1,150 @@
+"""Symmetric peer-memory arena and the fused tensor-parallel kernels that run on it.
+
+``torch.distributed._symmetric_memory`` does the plumbing only: it allocates one arena per rank, exchanges
+the handles and returns every peer's pointer plus the NVSwitch multicast mapping.  All data movement is
+done by our own kernels (``csrc/comm.cu``) with P2P or ``multimem`` loads/stores; no NCCL call is made
+on the decode path.  (Reference counterpart: peer-access setup + custom all-reduce buffers,
+src/devices/multicuda/fastllm-custom-allreduce.cu:2234-2481.)
+
+Arena layout (same offsets on every rank):
+    [0, 1 KiB)          counters / expected value / ticket
+    part   fp32 [max_m, max_n]     per-rank partial sums of the row-parallel GEMM
+    h      16-bit [max_m, hidden]  residual stream (replicated, written by the row owners)
+    x      16-bit [max_m, hidden]  RMSNorm(h) for the next column-parallel GEMM
+    amax   [tp, max_m, 2] u32      greedy candidates of the vocab shards
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+from ..ops.basic import _ptr, _stream, dtype_code
+
+P, I, F, ULL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong
+_lib.register_sigs({
+    "fb_gemm_ar_norm": [P, P, P, I, I, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, I, P],
+    "fb_ar_norm": [I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
+    "fb_argmax_merge": [P, P, P, I, P, P, P, I, I, ULL, P],
+}, ["comm"])
+
+HEADER = 1024
+
+
+def _align(n, a=4096):
+    return (n + a - 1) // a * a
+
+
+class FusedComm:
+    name = "fused-p2p"
+
+    def __init__(self, comm, hidden: int, max_m: int, max_n: int, dtype=torch.bfloat16, use_multicast: bool = True):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.comm = comm
+        self.rank, self.tp, self.device = comm.rank, comm.size, comm.device
+        self.hidden, self.max_m, self.max_n, self.dtype = hidden, max_m, max(max_n, hidden), dtype
+        self.off_part = _align(HEADER)
+        self.off_h = _align(self.off_part + max_m * self.max_n * 4)
+        self.off_x = _align(self.off_h + max_m * hidden * 2)
+        self.off_amax = _align(self.off_x + max_m * hidden * 2)
+        self.nbytes = _align(self.off_amax + self.tp * max_m * 8, 1 << 21)
+        self.arena = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+        self.handle = symm_mem.rendezvous(self.arena, dist.group.WORLD)
+        self.arena.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        ptrs = list(self.handle.buffer_ptrs)
+        self.peers = (ctypes.c_void_p * 8)(*([ctypes.c_void_p(p) for p in ptrs] + [ctypes.c_void_p(0)] * (8 - len(ptrs))))
+        mc = int(getattr(self.handle, "multicast_ptr", 0) or 0)
+        if not use_multicast or os.environ.get("FB_DISABLE_MULTICAST", "0") == "1":
+            mc = 0
+        self.mc = mc
+        self.name = "fused-nvls-multimem" if mc else "fused-p2p"
+        self.local = ptrs[self.rank]
+        assert self.local == self.arena.data_ptr()
+        self.h_buf = self.arena[self.off_h:self.off_h + max_m * hidden * 2].view(dtype).view(max_m, hidden)
+        self.x_buf = self.arena[self.off_x:self.off_x + max_m * hidden * 2].view(dtype).view(max_m, hidden)
+        self.part_buf = self.arena[self.off_part:self.off_part + max_m * self.max_n * 4].view(torch.float32)
+
+    # ---------------------------------------------------------------------------------------------
+    def usable(self, M: int, N: int) -> bool:
+        return 0 < M <= min(self.max_m, 256) and N == self.hidden and N % 8 == 0
+
+    def load_h(self, h: torch.Tensor) -> torch.Tensor:
+        """Place the (replicated) residual stream rows into the arena; returns the arena view."""
+        M = h.shape[0]
+        v = self.h_buf[:M]
+        v.copy_(h)
+        return v
+
+    def gemm_ar_norm(self, w, x: torch.Tensor, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True):
+        """h[:M] (+)= sum over ranks of x @ w.T ; x_out = RMSNorm(h) * ln_w.  One launch.  Returns (h, x_out) views."""
+        M, K = x.shape
+        N = w.n
+        if w.kind != "dense" or not self.usable(M, N) or (w.bias is not None and self.rank != 0 and False):
+            return None
+        wt = w.w if w.w.dtype == x.dtype else w.w.to(x.dtype)
+        bias = w.bias if self.rank == 0 else None
+        rc = _lib.kernels().fb_gemm_ar_norm(_ptr(x), _ptr(wt), _ptr(bias), M, N, K, x.stride(0), wt.stride(0),
+                                            ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
+                                            self.off_part, self.off_h, self.off_x, _ptr(ln_w), 1 if has_residual else 0,
+                                            float(eps), float(unit_offset), dtype_code(x.dtype), 0, _stream())
+        if rc != 0:
+            if rc == 701:      # cudaErrorLaunchOutOfResources: grid cannot be co-resident -> caller uses the unfused path
+                return None
+            _lib.check(rc, "fb_gemm_ar_norm")
+        return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
+
+    def ar_norm(self, partial: torch.Tensor, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True):
+        """Same as gemm_ar_norm for a partial sum computed elsewhere (any float dtype, ``[M, hidden]``)."""
+        M, N = partial.shape
+        if not (0 < M <= self.max_m and N == self.hidden):
+            return None
+        self.part_buf[:M * N].view(M, N).copy_(partial)
+        rc = _lib.kernels().fb_ar_norm(M, N, ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
+                                       self.off_part, self.off_h, self.off_x, _ptr(ln_w), 1 if has_residual else 0, float(eps),
+                                       float(unit_offset), dtype_code(self.dtype), _stream())
+        _lib.check(rc, "fb_ar_norm")
+        return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
+
+    # -- TPComm hooks --------------------------------------------------------------------------------
+    def all_reduce(self, t, residual=None):
+        return None        # generic tensors go through NCCL; the decoder calls the fused entry points directly
+
+    def row_linear(self, w, x, residual):
+        return None
+
+    def merge_argmax(self, ids: torch.Tensor, vals: torch.Tensor):
+        B = ids.shape[0]
+        if B > self.max_m:
+            return None
+        out = torch.empty_like(ids)
+        rc = _lib.kernels().fb_argmax_merge(_ptr(vals), _ptr(ids), _ptr(out), B, ctypes.c_void_p(self.local),
+                                            ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp, self.off_amax, _stream())
+        _lib.check(rc, "fb_argmax_merge")
+        return out
+
+    def reset(self):
+        """Re-initialise the counters after a reported peer timeout (all ranks must call this together)."""
+        torch.cuda.synchronize()
+        dist.barrier()
+        self.arena[:HEADER].zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+
+
+def try_create(comm, cfg, max_m: int, strict: bool = False, dtype=torch.bfloat16):
+    """Create the fused communicator; on failure return None (NCCL path) unless ``strict``."""
+    try:
+        max_m = max(16, min(256, max_m))
+        return FusedComm(comm, cfg.hidden_size, max_m, cfg.hidden_size, dtype)
+    except Exception as e:  # symmetric memory unavailable (no P2P, old driver, ...)
+        if strict:
+            raise
+        if comm.rank == 0:
+            print(f"[fastllm_b200] fused NVLink path unavailable ({e!r}); using NCCL collectives", flush=True)
+        return None

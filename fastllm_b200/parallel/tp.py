@@ -55,16 +55,18 @@ class TPComm:
             if out is not None:
                 return out
         packed = torch.stack([vals.float(), ids.float()], dim=0).contiguous()          # [2, B]
-        allp = torch.empty((self.size, 2, ids.shape[0]), device=ids.device, dtype=torch.float32)
-        dist.all_gather_into_tensor(allp, packed, group=self.group)
+        flat = torch.empty((self.size * 2, ids.shape[0]), device=ids.device, dtype=torch.float32)
+        dist.all_gather_into_tensor(flat, packed, group=self.group)
+        allp = flat.view(self.size, 2, ids.shape[0])
         best = allp[:, 0, :].argmax(dim=0, keepdim=True)                                  # first max = lowest rank
         return allp[:, 1, :].gather(0, best).squeeze(0).to(torch.int32)
 
     def gather_logits(self, logits: torch.Tensor, shard, vocab: int) -> torch.Tensor:
         """All-gather vocab-sharded logits ``[R, V_local]`` into ``[R, vocab]``."""
         R, VL = logits.shape
-        allp = torch.empty((self.size, R, VL), device=logits.device, dtype=logits.dtype)
-        dist.all_gather_into_tensor(allp, logits.contiguous(), group=self.group)
+        flat = torch.empty((self.size * R, VL), device=logits.device, dtype=logits.dtype)
+        dist.all_gather_into_tensor(flat, logits.contiguous(), group=self.group)
+        allp = flat.view(self.size, R, VL)
         return allp.permute(1, 0, 2).reshape(R, self.size * VL)[:, :vocab].contiguous()
 
     def barrier(self):
