@@ -1,0 +1,136 @@
+"""Reference arm of bench.py: the unmodified reference (installed under baseline/_ref from a cmake build of the
+reference sources) serving the same architecture / batch / lengths through its own public Python API
+(`ftllm.util.make_normal_llm_model` + `launch_response_llm_model` / `fetch_response_llm_model`, the calls its own
+`ftllm bench` makes, tools/fastllm_pytools/benchmark.py:98-160).
+
+The reference is one process driving all GPUs (`--device multicuda:0,1,...`), so under torchrun only rank 0
+works and the other ranks exit.  Its scheduler cannot be stepped from outside; a "step" is therefore observed
+at the fetch loop: step k is complete when every request has delivered its k-th token.  Time is wall clock
+at that loop (no device events are reachable through the reference's API).
+"""
+from __future__ import annotations
+
+import ctypes
+import json
+import os
+import statistics
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REF = os.path.join(ROOT, "baseline", "_ref")
+
+
+def _unavailable(why: str):
+    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+
+
+def run(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if not os.path.exists(os.path.join(REF, "ftllm", "libfastllm_tools.so")):
+        _unavailable("baseline/_ref/ftllm/libfastllm_tools.so missing (reference not built in this checkout)")
+        return
+    try:
+        import torch
+
+        n_vis = torch.cuda.device_count()
+    except Exception as e:  # pragma: no cover
+        _unavailable(f"torch/cuda not usable: {e!r}")
+        return
+    if n_vis < args.gpus:
+        _unavailable(f"{args.gpus} GPUs requested, {n_vis} visible")
+        return
+    sys.path.insert(0, ROOT)
+    from baseline import synth
+
+    model_dir = os.environ.get("FB_REF_MODEL_DIR", f"/tmp/fb_ref_{args.model}")
+    t0 = time.time()
+    synth.write_model(args.model, model_dir)
+    t_synth = time.time() - t0
+    sys.path.insert(0, REF)
+    try:
+        from ftllm import benchmark as rb
+        from ftllm import llm as rllm
+        from ftllm.util import make_normal_llm_model, make_normal_parser
+    except Exception as e:
+        _unavailable(f"import of the reference package failed: {e!r}"[:300])
+        return
+    B, P, O = args.batch, args.prompt_len, args.output_len
+    device = "cuda" if args.gpus == 1 else "multicuda:" + ",".join(str(i) for i in range(args.gpus))
+    argv = [model_dir, "--device", device, "--dtype", "bfloat16", "--atype", "bfloat16", "--max_batch", str(B),
+            "--tokens", str(int(B * (P + O + 256) / 0.75)), "--page_size", "128"]
+    parser = make_normal_parser("reference bench")
+    rb.add_benchmark_args(parser)
+    rargs = parser.parse_args(argv)
+    os.environ.setdefault("FASTLLM_CUDA_GRAPH", "1")
+    try:
+        model = make_normal_llm_model(rargs)
+    except SystemExit as e:
+        _unavailable(f"reference model construction exited: {e!r}")
+        return
+    except Exception as e:
+        _unavailable(f"reference model construction failed: {e!r}"[:300])
+        return
+    import torch
+
+    gen = torch.Generator().manual_seed(1234)
+    vocab = json.load(open(os.path.join(model_dir, "config.json")))["vocab_size"]
+    prompts = [torch.randint(0, vocab - 1, (P,), generator=gen).tolist() for _ in range(B)]
+    gargs = {"do_sample": False, "top_p": 1.0, "top_k": 1, "temperature": 1.0, "repeat_penalty": 1.0}
+    lib = rllm.fastllm_lib
+    # warm-up request (the reference's own bench does the same)
+    h = rb._launch_raw_response(model, prompts[0][:64], 4, gargs)
+    while lib.fetch_response_llm_model(model.model, h) > -1:
+        pass
+    K, W = args.steps, args.warmup
+    if W + K > O - 1:
+        K = max(1, O - 1 - W)
+    handles = [rb._launch_raw_response(model, p, O, gargs) for p in prompts]
+    counts = [0] * B
+    done = [False] * B
+    t_launch = time.perf_counter()
+    step_done_time = {}
+
+    def min_count():
+        return min(c for c in counts)
+
+    # fetch round-robin: fetch blocks until the handle has a token, so after one pass every request advanced by one
+    first_token_t = None
+    cur = 0
+    while not all(done):
+        for i in range(B):
+            if done[i]:
+                continue
+            tok = lib.fetch_response_llm_model(model.model, handles[i])
+            if tok <= -1:
+                done[i] = True
+                continue
+            counts[i] += 1
+        cur += 1
+        step_done_time[cur] = time.perf_counter()
+        if first_token_t is None:
+            first_token_t = step_done_time[cur]
+        if cur >= 1 + W + K:
+            break
+    alive = sum(1 for d in done if not d)
+    if cur < 1 + W + K or alive < B:
+        _unavailable(f"reference run ended early: {cur} steps observed, {alive}/{B} requests alive")
+        os._exit(0)
+    t_a, t_b = step_done_time[1 + W], step_done_time[1 + W + K]
+    secs = t_b - t_a
+    steps = [step_done_time[s + 1] - step_done_time[s] for s in range(1 + W, 1 + W + K)]
+    out = {
+        "metric": "decode output tok/s (device-timed, max over ranks)", "value": B * K / secs, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": secs / K * 1000.0, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
+        "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O,
+                   "parallelism": device, "timing": "wall clock at the reference's fetch loop (no device events in its API)"},
+        "e2e": {"value": B * K / secs, "unit": "tokens/s", "p50_tpot_ms": statistics.median(steps) * 1000.0,
+                "ttft_s": first_token_t - t_launch},
+        "impl": "reference", "synth_model_s": t_synth,
+    }
+    print(json.dumps(out), flush=True)
+    os._exit(0)

@@ -2,12 +2,14 @@
 //
 //  * fb_gemm_ar_norm: row-parallel small-M GEMM (tcgen05, swap-AB, cluster split-K) FUSED with
 //    reduce-scatter -> (+residual) -> RMSNorm -> all-gather in ONE kernel:
-//       phase 1  every CTA writes its fp32 partial tile into this rank's slice of the symmetric arena
-//       sync 1   one arrival per CTA on a counter in every rank (multimem.red through NVSwitch, or P2P red)
-//       phase 2  rank r owns token rows [r*M/tp, (r+1)*M/tp): it sums the partials of all ranks for its
-//                rows (multimem.ld_reduce = in-switch reduction, or P2P loads in rank order), adds the
-//                residual row, writes the new residual stream row and its RMSNorm'd version to EVERY
-//                rank (multimem.st, or P2P stores)
+//       phase 1  rank r owns token rows [r*M/tp, (r+1)*M/tp).  The GEMM epilogue PUSHES each fp32 partial row
+//                straight into its owner's arena (slot = source rank) with peer stores: the reduce-scatter
+//                costs one NVLink traversal, no pull round trip
+//       sync 1   one aggregated arrival per rank on a counter in every rank (multimem.red through NVSwitch,
+//                or P2P red)
+//       phase 2  the owner sums the tp slots of its rows in rank order (local reads, deterministic), adds
+//                the residual row, writes the new residual-stream row and its RMSNorm'd version to EVERY
+//                rank (multimem.st through NVSwitch multicast, or P2P stores)
 //       sync 2   second counter; the kernel ends only when every rank's rows have landed here, so the
 //                next kernel on the stream can read the full hidden state without further waits.
 //  * fb_ar_norm: phases 2.. alone for partials produced elsewhere (MoE output, embeddings).
@@ -33,7 +35,7 @@ constexpr int KID_ARGMAX_MERGE = 32;
 constexpr int MAX_TP = 8;
 
 // arena header layout (bytes from the arena base); each word on its own 128-byte line
-constexpr uint32_t OFF_CNT1 = 0, OFF_CNT2 = 128, OFF_EXPECT = 256, OFF_TICKET = 384, OFF_HEADER_END = 1024;
+constexpr uint32_t OFF_CNT1 = 0, OFF_CNT2 = 128, OFF_EXPECT = 256, OFF_TICKET = 384, OFF_LOCAL1 = 512, OFF_LOCAL2 = 640, OFF_TRACE = 768;   // OFF_TRACE: 8 x u64 phase time stamps of CTA 0
 
 struct CommCtx {
   uint8_t* local;            // this rank's arena
@@ -44,20 +46,23 @@ struct CommCtx {
 
 struct ArNormParams {
   CommCtx c;
-  uint64_t off_part;         // fp32 [M, N] partial sums (symmetric offset)
+  uint64_t off_part;         // fp32 [tp, M, N]: slot s holds rank s's partial rows (only this rank's own rows are used)
   uint64_t off_h;            // 16-bit [M, N] residual stream (read: own rows; written: all ranks)
   uint64_t off_x;            // 16-bit [M, N] normalised output
   const uint16_t* ln_w;      // RMSNorm weight [N] (nullptr: skip the norm, x is not written)
+  const void* src;           // stand-alone kernel: this rank's partial [M, N] to push (nullptr in the GEMM kernel)
+  int src_f32;               // src is fp32 (else the 16-bit activation dtype)
   int M, N;
   int has_residual;
+  int trace;                 // != 0: CTA 0 writes globaltimer stamps of each phase to OFF_TRACE
   float eps, unit_offset;
 };
 
-__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void red_add_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ void mc_red_add_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void mc_red_add_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -77,12 +82,25 @@ __device__ __forceinline__ void mc_st_b32x4(void* p, uint4 v) {
 }
 
 // one arrival on counter `off` of every rank
+// (one system-scope fence, then relaxed reductions: the fence is the expensive part, do it once)
 __device__ __forceinline__ void signal_all(const CommCtx& c, uint32_t off) {
   __threadfence_system();
   if (c.mc) {
-    mc_red_add_release_sys(reinterpret_cast<uint32_t*>(c.mc + off), 1u);
+    mc_red_add_relaxed_sys(reinterpret_cast<uint32_t*>(c.mc + off), 1u);
   } else {
-    for (int r = 0; r < c.tp; ++r) red_add_release_sys(reinterpret_cast<uint32_t*>(c.peer[r] + off), 1u);
+    for (int r = 0; r < c.tp; ++r) red_add_relaxed_sys(reinterpret_cast<uint32_t*>(c.peer[r] + off), 1u);
+  }
+}
+// CTA-level arrival: CTAs of this rank first meet on a local counter; the last one sends ONE arrival to every rank,
+// so the cross-GPU counter sees tp arrivals per launch instead of tp x CTAs atomics on one address.
+// Ordering: every CTA fences at GPU scope before its local arrival; the last arriver's system-scope fence is
+// cumulative over everything it observed through the local counter.
+__device__ __forceinline__ void arrive_aggregated(const CommCtx& c, uint32_t off_local, uint32_t off_remote, int n_ctas) {
+  __threadfence();
+  uint32_t* lc = reinterpret_cast<uint32_t*>(c.local + off_local);
+  if (atomicAdd(lc, 1u) == (uint32_t)(n_ctas - 1)) {
+    *lc = 0u;                       // nobody reads it again in this launch
+    signal_all(c, off_remote);
   }
 }
 // bounded wait until the local counter has reached `target` (wrap-safe)
@@ -100,47 +118,53 @@ __device__ __forceinline__ bool wait_counter(const CommCtx& c, uint32_t off, uin
 }
 
 // Phases 2.. of the fused all-reduce; called by every thread of every CTA.  `base` = value of the expect word
-// read at kernel start; n_ctas = CTAs per rank in this launch.
+// read at kernel start; n_ctas = CTAs per rank in this launch.  CTAs come in groups of `csize` (one thread-block
+// cluster): a group owns whole rows, each of its CTAs one column slice; the row's sum of squares is exchanged
+// through distributed shared memory.
 template <bool BF16>
-__device__ __forceinline__ void ar_norm_tail(const ArNormParams& p, uint32_t base, int cta, int n_ctas, int kernel_id) {
+__device__ __forceinline__ void ar_norm_tail(const ArNormParams& p, uint32_t base, int group, int n_groups, int crank,
+                                             int csize, int kernel_id) {
   __shared__ float sh_red[8];
+  __shared__ float sh_ss;
   __shared__ int sh_ok;
   const CommCtx& c = p.c;
-  const uint32_t target = base + (uint32_t)(c.tp * n_ctas);
+  const int n_ctas = n_groups * csize;
+  const uint32_t target = base + (uint32_t)c.tp;      // one aggregated arrival per rank per counter
   const int tid = threadIdx.x, nthr = blockDim.x;
+  uint64_t* trace = (p.trace && group == 0 && crank == 0 && tid == 0) ? reinterpret_cast<uint64_t*>(c.local + OFF_TRACE) : nullptr;
   // ---- sync 1: all partials of all ranks are in their arenas ----
   __syncthreads();
   if (tid == 0) {
-    signal_all(c, OFF_CNT1);
+    if (trace) trace[1] = globaltimer_ns();
+    arrive_aggregated(c, OFF_LOCAL1, OFF_CNT1, n_ctas);
+    if (trace) trace[2] = globaltimer_ns();
     sh_ok = wait_counter(c, OFF_CNT1, target, kernel_id, 1) ? 1 : 0;
+    if (trace) trace[3] = globaltimer_ns();
   }
   __syncthreads();
-  const bool ok = sh_ok != 0;
+  const bool ok = sh_ok != 0;      // a CTA that timed out still walks the loop (cluster barriers must match) but moves no data
   // ---- phase 2: own rows ----
   const int rows_per = (p.M + c.tp - 1) / c.tp;
   const int row0 = c.rank * rows_per;
   int row1 = row0 + rows_per; if (row1 > p.M) row1 = p.M;
   const int N = p.N;
   const int chunks = N >> 3;                         // 8 columns per chunk
+  const int cpc = (chunks + csize - 1) / csize;      // chunks per CTA of the group
+  const int ch0 = crank * cpc;
+  int ch1 = ch0 + cpc; if (ch1 > chunks) ch1 = chunks;
   constexpr int MAXC = 12;
-  for (int row = row0 + cta; ok && row < row1; row += n_ctas) {
+  for (int row = row0 + group; row < row1; row += n_groups) {
     uint4 hv[MAXC];
     float ss = 0.f;
     int cnt = 0;
-    for (int ch = tid; ch < chunks; ch += nthr, ++cnt) {
+    for (int ch = ch0 + tid; ok && ch < ch1; ch += nthr, ++cnt) {
       const size_t eoff = (size_t)row * N + (size_t)ch * 8;
-      float4 a, b;
-      if (c.mc) {
-        a = mc_ld_reduce_f32x4(c.mc + p.off_part + eoff * 4);
-        b = mc_ld_reduce_f32x4(c.mc + p.off_part + eoff * 4 + 16);
-      } else {
-        a = make_float4(0.f, 0.f, 0.f, 0.f); b = a;
-        for (int r = 0; r < c.tp; ++r) {
-          const float4* src = reinterpret_cast<const float4*>(c.peer[r] + p.off_part + eoff * 4);
-          const float4 u = src[0], w = src[1];
-          a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
-          b.x += w.x; b.y += w.y; b.z += w.z; b.w += w.w;
-        }
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      for (int r = 0; r < c.tp; ++r) {
+        const float4* src = reinterpret_cast<const float4*>(c.local + p.off_part + (((size_t)r * p.M + row) * N + (size_t)ch * 8) * 4);
+        const float4 u = src[0], w = src[1];
+        a.x += u.x; a.y += u.y; a.z += u.z; a.w += u.w;
+        b.x += w.x; b.y += w.y; b.z += w.z; b.w += w.w;
       }
       if (p.has_residual) {
         const uint4 rv = *reinterpret_cast<const uint4*>(c.local + p.off_h + eoff * 2);
@@ -168,9 +192,17 @@ __device__ __forceinline__ void ar_norm_tail(const ArNormParams& p, uint32_t bas
       __syncthreads();
       float tot = 0.f;
       for (int w = 0; w < (nthr >> 5); ++w) tot += sh_red[w];
+      if (csize > 1) {
+        if (tid == 0) sh_ss = tot;
+        cluster_sync_all();
+        const uint32_t a_ss = smem_u32(&sh_ss);
+        tot = 0.f;
+        for (int r = 0; r < csize; ++r) tot += ld_dsmem_f32(mapa_u32(a_ss, (uint32_t)r));
+        cluster_sync_all();          // peers have read sh_ss before the next row overwrites it
+      }
       const float inv = rsqrtf(tot / (float)N + p.eps);
       cnt = 0;
-      for (int ch = tid; ch < chunks; ch += nthr, ++cnt) {
+      for (int ch = ch0 + tid; ok && ch < ch1; ch += nthr, ++cnt) {
         const size_t eoff = (size_t)row * N + (size_t)ch * 8;
         const uint4 h = hv[cnt < MAXC ? cnt : MAXC - 1];
         const uint4 wv = *reinterpret_cast<const uint4*>(p.ln_w + (size_t)ch * 8);
@@ -193,8 +225,11 @@ __device__ __forceinline__ void ar_norm_tail(const ArNormParams& p, uint32_t bas
   // ---- sync 2: every rank's rows have been written everywhere ----
   __syncthreads();
   if (tid == 0) {
-    signal_all(c, OFF_CNT2);
+    if (trace) trace[4] = globaltimer_ns();
+    arrive_aggregated(c, OFF_LOCAL2, OFF_CNT2, n_ctas);
+    if (trace) trace[5] = globaltimer_ns();
     wait_counter(c, OFF_CNT2, target, kernel_id, 2);
+    if (trace) trace[6] = globaltimer_ns();
     // the last CTA of this rank to get here publishes the new expected value for the next launch
     uint32_t* ticket = reinterpret_cast<uint32_t*>(c.local + OFF_TICKET);
     if (atomicAdd(ticket, 1u) == (uint32_t)(n_ctas - 1)) {
@@ -210,17 +245,39 @@ __global__ void __launch_bounds__(192, 1)
 gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams g,
                     const ArNormParams p) {
   const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) reinterpret_cast<uint64_t*>(p.c.local + OFF_TRACE)[0] = globaltimer_ns();
   uint32_t tmem_base;
   gemm_smallm_device<MPAD, BF16>(tmW, tmX, g, tmem_base, KID_GEMM_AR);
   if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD>::TMEM_COLS);
-  const int n_ctas = gridDim.x * gridDim.y;
-  ar_norm_tail<BF16>(p, base, blockIdx.y * gridDim.x + blockIdx.x, n_ctas, KID_GEMM_AR);
+  // cluster = the gridDim.x k-split CTAs of one weight tile
+  ar_norm_tail<BF16>(p, base, blockIdx.y, gridDim.y, blockIdx.x, gridDim.x, KID_GEMM_AR);
 }
 
 template <bool BF16>
 __global__ void __launch_bounds__(192, 1) ar_norm_kernel(const ArNormParams p) {
   const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
-  ar_norm_tail<BF16>(p, base, blockIdx.x, gridDim.x, KID_AR_NORM);
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<uint64_t*>(p.c.local + OFF_TRACE)[0] = globaltimer_ns();
+  // phase 1: push this rank's partial rows to their owners (slot = this rank)
+  const CommCtx& c = p.c;
+  const int rows_per = (p.M + c.tp - 1) / c.tp;
+  const int chunks = p.N >> 3;
+  const long long total = (long long)p.M * chunks;
+  for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (long long)gridDim.x * blockDim.x) {
+    const int row = (int)(it / chunks), ch = (int)(it - (long long)row * chunks);
+    float4 a, b;
+    if (p.src_f32) {
+      const float4* sp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.src) + (size_t)row * p.N + (size_t)ch * 8);
+      a = sp[0]; b = sp[1];
+    } else {
+      const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const uint16_t*>(p.src) + (size_t)row * p.N + (size_t)ch * 8);
+      const float2 v0 = unpack_16<BF16>(v.x), v1 = unpack_16<BF16>(v.y), v2 = unpack_16<BF16>(v.z), v3 = unpack_16<BF16>(v.w);
+      a = make_float4(v0.x, v0.y, v1.x, v1.y); b = make_float4(v2.x, v2.y, v3.x, v3.y);
+    }
+    float4* dst = reinterpret_cast<float4*>(c.peer[row / rows_per] + p.off_part + (((size_t)c.rank * p.M + row) * p.N + (size_t)ch * 8) * 4);
+    dst[0] = a; dst[1] = b;
+  }
+  const int cs = (int)cluster_nctarank();
+  ar_norm_tail<BF16>(p, base, blockIdx.x / cs, gridDim.x / cs, (int)cluster_ctarank(), cs, KID_AR_NORM);
 }
 
 // ---- vocab-sharded greedy merge: every rank publishes (max value, arg-max id) per row, then picks the best ----
@@ -339,13 +396,16 @@ extern "C" int fb_gemm_ar_norm(const void* X, const void* W, const void* bias, i
   GemmParams g;
   g.out = (uint8_t*)arena_local + off_part; g.bias = bias; g.residual = nullptr;
   g.M = M; g.N = N; g.K = K; g.ld_out = N; g.ld_res = 0;
+  g.scatter_tp = tp; g.scatter_rows = (M + tp - 1) / tp; g.scatter_rank = rank;
+  for (int i = 0; i < 8; ++i) g.scatter_out[i] = i < tp ? reinterpret_cast<float*>((uint8_t*)peers[i] + off_part) : nullptr;
   g.kb_total = K / 64; g.kb_per_split = (g.kb_total + nsplit - 1) / nsplit;
   g.flags = GEMM_OUT_F32 | (bias ? GEMM_BIAS : 0);
   g.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
   ArNormParams p;
   fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
   p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
-  p.has_residual = has_residual; p.eps = eps; p.unit_offset = unit_offset;
+  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
+  p.src = nullptr; p.src_f32 = 0;
   CUtensorMap tmW, tmX;
   if (!make_tmap_2d(&tmW, W, N, K, ldw, 128, 64, 2, 3)) return -2;
   if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
@@ -362,8 +422,8 @@ extern "C" int fb_gemm_ar_norm(const void* X, const void* W, const void* bias, i
 #undef FB_GA
 }
 
-// All-reduce (+residual, +RMSNorm) of fp32 partials that already sit at off_part in every rank's arena.
-extern "C" int fb_ar_norm(int M, int N, void* arena_local, void* arena_mc, void* const* peers, int rank, int tp,
+// All-reduce (+residual, +RMSNorm) of this rank's partial `src` [M, N] (fp32 if src_f32 else the 16-bit dtype).
+extern "C" int fb_ar_norm(const void* src, int src_f32, int M, int N, void* arena_local, void* arena_mc, void* const* peers, int rank, int tp,
                           unsigned long long off_part, unsigned long long off_h, unsigned long long off_x, const void* ln_w,
                           int has_residual, float eps, float unit_offset, int dtype, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -371,13 +431,23 @@ extern "C" int fb_ar_norm(int M, int N, void* arena_local, void* arena_mc, void*
   ArNormParams p;
   fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
   p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
-  p.has_residual = has_residual; p.eps = eps; p.unit_offset = unit_offset;
+  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
+  p.src = src; p.src_f32 = src_f32;
   int rows_per = (M + tp - 1) / tp;
-  int grid = rows_per < 1 ? 1 : rows_per;
-  if (grid > sm_count()) grid = sm_count();
-  if (dtype == 1) ar_norm_kernel<true><<<grid, 192, 0, stream>>>(p);
-  else ar_norm_kernel<false><<<grid, 192, 0, stream>>>(p);
-  return (int)cudaGetLastError();
+  const int cs = N >= 4096 ? 4 : (N >= 2048 ? 2 : 1);     // CTAs per row
+  int groups = rows_per < 1 ? 1 : rows_per;
+  if (groups * cs > sm_count()) groups = sm_count() / cs;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(groups * cs, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  if (dtype == 1) return (int)cudaLaunchKernelEx(&cfg, ar_norm_kernel<true>, p);
+  return (int)cudaLaunchKernelEx(&cfg, ar_norm_kernel<false>, p);
 }
 
 extern "C" int fb_argmax_merge(const float* vals, const int* ids, int* out, int B, void* arena_local, void* arena_mc,

@@ -26,12 +26,12 @@ FB_DEFINE_ERROR_API(gemm)
 
 namespace fb {
 
-template <int MPAD, bool BF16>
-__global__ void __launch_bounds__(192, 1)
+template <int MPAD, bool BF16, int OCC>
+__global__ void __launch_bounds__(192, OCC)
 gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p) {
   uint32_t tmem_base;
-  gemm_smallm_device<MPAD, BF16>(tmW, tmX, p, tmem_base, KID_GEMM_SMALLM_PLAIN);
-  if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD>::TMEM_COLS);
+  gemm_smallm_device<MPAD, BF16, OCC>(tmW, tmX, p, tmem_base, KID_GEMM_SMALLM_PLAIN);
+  if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD, OCC>::TMEM_COLS);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -204,11 +204,11 @@ gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 // ---------------------------------------------------------------------------------------------------
 // host launchers
 // ---------------------------------------------------------------------------------------------------
-template <int MPAD, bool BF16>
+template <int MPAD, bool BF16, int OCC>
 static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int nsplit, int n_tiles,
                                  cudaStream_t stream) {
-  using Cfg = SmallMCfg<MPAD>;
-  auto kern = gemm_smallm_kernel<MPAD, BF16>;
+  using Cfg = SmallMCfg<MPAD, OCC>;
+  auto kern = gemm_smallm_kernel<MPAD, BF16, OCC>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -248,14 +248,15 @@ static cudaError_t launch_largem(const CUtensorMap& tmX, const CUtensorMap& tmW,
 }  // namespace fb
 
 // Heuristic used by the launcher: how many cluster ranks split K so that about one CTA lands on each SM.
-extern "C" int fb_gemm_pick_split(int M, int N, int K, int sm_count) {
-  // Largest power-of-two split that still fits one wave (one CTA per SM) and leaves >= 4 k-blocks per rank.
+extern "C" int fb_gemm_pick_split(int M, int N, int K, int slots) {
+  // Largest power-of-two split whose CTAs are all resident at once (slots = SMs x CTAs per SM) and that leaves
+  // at least 8 k-blocks per rank.
   const int n_tiles = (N + 127) / 128;
   const int kb = K / 64;
   int best = 1;
   for (int s = 2; s <= 8; s *= 2) {
-    if (n_tiles * s > sm_count) break;
-    if (kb / s < 4) break;
+    if (n_tiles * s > slots) break;
+    if (kb / s < 8) break;
     const int per = (kb + s - 1) / s;
     if ((s - 1) * per >= kb) break;             // every rank must own at least one block
     best = s;
@@ -277,6 +278,8 @@ extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void
   p.M = M; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res;
   p.kb_total = K / 64;
   p.flags = flags;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0;
+  for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
   const bool bf16 = dtype == 1;
   if (M <= 256) {
     const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
@@ -286,7 +289,14 @@ extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void
       cudaGetDevice(&dev);
       cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     }
-    if (nsplit <= 0) nsplit = fb_gemm_pick_split(M, N, K, sm_count);
+    // nsplit argument: low 4 bits = k split (0 = auto), bits 4.. = CTAs per SM (0 = auto)
+    int occ = nsplit > 0 ? (nsplit >> 4) : 0;
+    nsplit = nsplit > 0 ? (nsplit & 15) : 0;
+    // two CTAs per SM pay off once there are more weight tiles than SMs (no k split): one CTA streams while the
+    // other is in its prologue / epilogue
+    if (occ == 0) occ = (mpad <= 128 && (N + 127) / 128 > sm_count) ? 2 : 1;
+    if (mpad > 128) occ = 1;
+    if (nsplit <= 0) nsplit = fb_gemm_pick_split(M, N, K, sm_count * occ);
     if (nsplit != 1 && nsplit != 2 && nsplit != 4 && nsplit != 8) return -1;
     p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
     p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
@@ -295,14 +305,19 @@ extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void
     if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
     const int n_tiles = (N + 127) / 128;
 #define FB_SM(MP)                                                                                        \
-  return (int)(bf16 ? launch_smallm<MP, true>(tmW, tmX, p, nsplit, n_tiles, stream)                      \
-                    : launch_smallm<MP, false>(tmW, tmX, p, nsplit, n_tiles, stream));
+  if (occ == 2)                                                                                          \
+    return (int)(bf16 ? launch_smallm<MP, true, 2>(tmW, tmX, p, nsplit, n_tiles, stream)                 \
+                      : launch_smallm<MP, false, 2>(tmW, tmX, p, nsplit, n_tiles, stream));              \
+  return (int)(bf16 ? launch_smallm<MP, true, 1>(tmW, tmX, p, nsplit, n_tiles, stream)                   \
+                    : launch_smallm<MP, false, 1>(tmW, tmX, p, nsplit, n_tiles, stream));
     switch (mpad) {
       case 16: FB_SM(16)
       case 32: FB_SM(32)
       case 64: FB_SM(64)
       case 128: FB_SM(128)
-      default: FB_SM(256)
+      default:
+        return (int)(bf16 ? launch_smallm<256, true, 1>(tmW, tmX, p, nsplit, n_tiles, stream)
+                          : launch_smallm<256, false, 1>(tmW, tmX, p, nsplit, n_tiles, stream));
     }
 #undef FB_SM
   }

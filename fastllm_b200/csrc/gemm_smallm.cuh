@@ -25,16 +25,22 @@ struct GemmParams {
   int kb_total;
   uint32_t idesc;
   int flags;
+  // Row scatter (tensor-parallel reduce-scatter by push): with scatter_tp > 0 and GEMM_OUT_F32 the fp32 row j goes to
+  // scatter_out[j / scatter_rows] (a peer's arena), at row (scatter_rank * M + j) of a [tp * M, ld_out] matrix.
+  int scatter_tp, scatter_rows, scatter_rank;
+  float* scatter_out[8];
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
-template <int MPAD>
+// OCC = CTAs meant to be co-resident per SM: 1 -> deep ring (~200 KB), 2 -> two CTAs share the SM so that one
+// streams weights while the other is in its prologue / epilogue.
+template <int MPAD, int OCC = 1>
 struct SmallMCfg {
   static constexpr int A_BYTES = 128 * 128;            // 128 rows x 64 bf16
   static constexpr int B_BYTES = MPAD * 128;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int MAX_STAGES = (200 * 1024) / STAGE_BYTES;
+  static constexpr int MAX_STAGES = ((200 * 1024) / OCC) / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 10 ? 10 : MAX_STAGES;
   static constexpr int RED_BYTES = MPAD * 128 * 4;     // fp32 partial tile [MPAD][128]
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
@@ -45,10 +51,10 @@ struct SmallMCfg {
 
 // Body of the small-M kernel.  Returns with the output tile written and every cluster peer done reading this
 // CTA's shared memory; the caller still owns TMEM (returned in tmem_base_out) and must release it from warp 1.
-template <int MPAD, bool BF16>
+template <int MPAD, bool BF16, int OCC = 1>
 __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
                                                    uint32_t& tmem_base_out, int kernel_id) {
-  using Cfg = SmallMCfg<MPAD>;
+  using Cfg = SmallMCfg<MPAD, OCC>;
   const int KID_GEMM_SMALLM = kernel_id;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -185,7 +191,10 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
         float2 r0 = unpack_16<BF16>(rv.x), r1 = unpack_16<BF16>(rv.y);
         acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
       }
-      if (p.flags & GEMM_OUT_F32) {
+      if (p.scatter_tp > 0) {
+        float* dst = p.scatter_out[j / p.scatter_rows] + ((size_t)p.scatter_rank * p.M + j) * p.ld_out + n_out;
+        *reinterpret_cast<float4*>(dst) = acc;
+      } else if (p.flags & GEMM_OUT_F32) {
         *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)j * p.ld_out + n_out) = acc;
       } else {
         uint2 o;

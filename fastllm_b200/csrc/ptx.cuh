@@ -262,6 +262,12 @@ __device__ __forceinline__ float4 ld_dsmem_f4(uint32_t cluster_addr) {
   return v;
 }
 
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(cluster_addr));
+  return v;
+}
+
 // ---------------------------------------------------------------------------------------------
 // small numeric helpers
 // ---------------------------------------------------------------------------------------------

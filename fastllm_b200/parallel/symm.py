@@ -8,7 +8,7 @@ src/devices/multicuda/fastllm-custom-allreduce.cu:2234-2481.)
 
 Arena layout (same offsets on every rank):
     [0, 1 KiB)          counters / expected value / ticket
-    part   fp32 [max_m, max_n]     per-rank partial sums of the row-parallel GEMM
+    part   fp32 [tp, max_m, max_n] slot s = partial rows pushed by rank s (reduce-scatter by push)
     h      16-bit [max_m, hidden]  residual stream (replicated, written by the row owners)
     x      16-bit [max_m, hidden]  RMSNorm(h) for the next column-parallel GEMM
     amax   [tp, max_m, 2] u32      greedy candidates of the vocab shards
@@ -27,7 +27,7 @@ from ..ops.basic import _ptr, _stream, dtype_code
 P, I, F, ULL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong
 _lib.register_sigs({
     "fb_gemm_ar_norm": [P, P, P, I, I, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, I, P],
-    "fb_ar_norm": [I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
+    "fb_ar_norm": [P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
     "fb_argmax_merge": [P, P, P, I, P, P, P, I, I, ULL, P],
 }, ["comm"])
 
@@ -48,7 +48,7 @@ class FusedComm:
         self.rank, self.tp, self.device = comm.rank, comm.size, comm.device
         self.hidden, self.max_m, self.max_n, self.dtype = hidden, max_m, max(max_n, hidden), dtype
         self.off_part = _align(HEADER)
-        self.off_h = _align(self.off_part + max_m * self.max_n * 4)
+        self.off_h = _align(self.off_part + self.tp * max_m * self.max_n * 4)
         self.off_x = _align(self.off_h + max_m * hidden * 2)
         self.off_amax = _align(self.off_x + max_m * hidden * 2)
         self.nbytes = _align(self.off_amax + self.tp * max_m * 8, 1 << 21)
@@ -68,7 +68,7 @@ class FusedComm:
         assert self.local == self.arena.data_ptr()
         self.h_buf = self.arena[self.off_h:self.off_h + max_m * hidden * 2].view(dtype).view(max_m, hidden)
         self.x_buf = self.arena[self.off_x:self.off_x + max_m * hidden * 2].view(dtype).view(max_m, hidden)
-        self.part_buf = self.arena[self.off_part:self.off_part + max_m * self.max_n * 4].view(torch.float32)
+        self.trace = False          # True: kernels stamp their phases (read back with read_trace)
 
     # ---------------------------------------------------------------------------------------------
     def usable(self, M: int, N: int) -> bool:
@@ -91,8 +91,8 @@ class FusedComm:
         bias = w.bias if self.rank == 0 else None
         rc = _lib.kernels().fb_gemm_ar_norm(_ptr(x), _ptr(wt), _ptr(bias), M, N, K, x.stride(0), wt.stride(0),
                                             ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
-                                            self.off_part, self.off_h, self.off_x, _ptr(ln_w), 1 if has_residual else 0,
-                                            float(eps), float(unit_offset), dtype_code(x.dtype), 0, _stream())
+                                            self.off_part, self.off_h, self.off_x, _ptr(ln_w),
+                                            (1 if has_residual else 0) | (2 if self.trace else 0), float(eps), float(unit_offset), dtype_code(x.dtype), 0, _stream())
         if rc != 0:
             if rc == 701:      # cudaErrorLaunchOutOfResources: grid cannot be co-resident -> caller uses the unfused path
                 return None
@@ -104,9 +104,11 @@ class FusedComm:
         M, N = partial.shape
         if not (0 < M <= self.max_m and N == self.hidden):
             return None
-        self.part_buf[:M * N].view(M, N).copy_(partial)
-        rc = _lib.kernels().fb_ar_norm(M, N, ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
-                                       self.off_part, self.off_h, self.off_x, _ptr(ln_w), 1 if has_residual else 0, float(eps),
+        if partial.dtype not in (torch.float32, self.dtype) or not partial.is_contiguous():
+            partial = partial.to(self.dtype).contiguous()
+        rc = _lib.kernels().fb_ar_norm(_ptr(partial), 1 if partial.dtype == torch.float32 else 0, M, N, ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
+                                       self.off_part, self.off_h, self.off_x, _ptr(ln_w),
+                                       (1 if has_residual else 0) | (2 if self.trace else 0), float(eps),
                                        float(unit_offset), dtype_code(self.dtype), _stream())
         _lib.check(rc, "fb_ar_norm")
         return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
@@ -127,6 +129,12 @@ class FusedComm:
                                             ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp, self.off_amax, _stream())
         _lib.check(rc, "fb_argmax_merge")
         return out
+
+    def read_trace(self):
+        """Phase time stamps (ns, device global timer) of CTA 0 in the last traced launch:
+        [start, sync1 arrive begin, sync1 arrive end, sync1 wait end, sync2 arrive begin, sync2 arrive end, sync2 wait end]."""
+        torch.cuda.synchronize()
+        return self.arena[768:768 + 56].view(torch.int64).cpu().tolist()
 
     def reset(self):
         """Re-initialise the counters after a reported peer timeout (all ranks must call this together)."""
