@@ -1,0 +1,188 @@
+"""Load a Hugging Face model folder (config.json + safetensors) into a ``DecoderModel``.
+
+Covers the reference's ``CreateLLMModelFromHF`` pipeline (src/model.cpp:3205-4188): config parsing, tensor
+name mapping per family, pre-quantised checkpoints (block-scaled FP8 ``weight_scale_inv``, AWQ
+``qweight/qzeros/scales``, exporter ``fastllm`` blobs), ``--dtype`` / ``--moe_dtype`` quantisation at load,
+``dtype_config`` regex rules (last match wins, src/model.cpp:3454-3466), q/k/v and gate/up merging, and
+tensor-parallel sharding.  Tensors are streamed one layer at a time so host memory stays bounded.
+"""
+from __future__ import annotations
+
+import json
+import re
+from pathlib import Path
+
+import torch
+
+from ..models.config import ModelConfig, load_config
+from ..models.decoder import DecoderModel, TPInfo
+from . import safetensors as st
+from .shard import finalize_model
+
+# AWQ packs eight 4-bit values per int32 in this nibble order (reference: src/model.cpp:1143-1218)
+_AWQ_ORDER = [0, 4, 1, 5, 2, 6, 3, 7]
+
+
+def dequant_fp8_block(w: torch.Tensor, scale_inv: torch.Tensor, dtype=torch.bfloat16, block: int = 128) -> torch.Tensor:
+    """``w`` float8_e4m3 [N, K], ``scale_inv`` fp32 [ceil(N/128), ceil(K/128)] -> dense."""
+    n, k = w.shape
+    s = scale_inv.float().repeat_interleave(block, 0)[:n].repeat_interleave(block, 1)[:, :k]
+    return (w.float() * s).to(dtype)
+
+
+def dequant_awq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """AWQ GEMM layout: qweight int32 [K, N/8], qzeros int32 [K/g, N/8], scales fp16 [K/g, N] -> dense [N, K]."""
+    K, n8 = qweight.shape
+    N = n8 * 8
+    shifts = torch.tensor([4 * i for i in _AWQ_ORDER], dtype=torch.int32)
+    w = ((qweight[:, :, None] >> shifts[None, None, :]) & 0xF).reshape(K, N)          # [K, N]
+    z = ((qzeros[:, :, None] >> shifts[None, None, :]) & 0xF).reshape(qzeros.shape[0], N)
+    g = K // scales.shape[0]
+    z = z.repeat_interleave(g, 0)
+    sc = scales.float().repeat_interleave(g, 0)
+    return ((w.float() - z.float()) * sc).t().contiguous().to(dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+# name canonicalisation: every family is mapped onto the Llama naming that loader.shard understands
+# ---------------------------------------------------------------------------------------------------
+_RENAMES = [
+    (r"^transformer\.h\.", "model.layers."), (r"^transformer\.wte\.", "model.embed_tokens."),
+    (r"^transformer\.ln_f\.", "model.norm."), (r"^language_model\.model\.", "model."), (r"^language_model\.lm_head\.", "lm_head."),
+    (r"^model\.language_model\.", "model."),
+    (r"\.attention\.wqkv\.", ".self_attn.qkv_proj."), (r"\.attention\.wo\.", ".self_attn.o_proj."),
+    (r"\.feed_forward\.w1\.", ".mlp.gate_proj."), (r"\.feed_forward\.w3\.", ".mlp.up_proj."),
+    (r"\.feed_forward\.w2\.", ".mlp.down_proj."), (r"\.attention_norm\.", ".input_layernorm."),
+    (r"\.ffn_norm\.", ".post_attention_layernorm."), (r"^model\.tok_embeddings\.", "model.embed_tokens."),
+    (r"^output\.", "lm_head."),
+    (r"\.self_attn\.W_pack\.", ".self_attn.qkv_proj."),
+    (r"\.block_sparse_moe\.gate\.", ".mlp.gate."), (r"\.block_sparse_moe\.experts\.(\d+)\.w1\.", r".mlp.experts.\1.gate_proj."),
+    (r"\.block_sparse_moe\.experts\.(\d+)\.w3\.", r".mlp.experts.\1.up_proj."),
+    (r"\.block_sparse_moe\.experts\.(\d+)\.w2\.", r".mlp.experts.\1.down_proj."),
+    (r"\.attn\.c_attn\.", ".self_attn.qkv_proj."), (r"\.attn\.c_proj\.", ".self_attn.o_proj."),
+    (r"\.ln_1\.", ".input_layernorm."), (r"\.ln_2\.", ".post_attention_layernorm."),
+    (r"\.mlp\.w2\.", ".mlp.gate_proj."), (r"\.mlp\.w1\.", ".mlp.up_proj."), (r"\.mlp\.c_proj\.", ".mlp.down_proj."),
+]
+
+
+def canonical_name(name: str) -> str:
+    for pat, rep in _RENAMES:
+        name = re.sub(pat, rep, name)
+    return name
+
+
+class HFCheckpoint:
+    """Index of all tensors in a folder with lazy, per-layer access and on-the-fly de-quantisation."""
+
+    def __init__(self, path: str | Path, cfg: ModelConfig, dtype=torch.bfloat16):
+        self.files, where = st.open_model_dir(path)
+        self.cfg, self.dtype = cfg, dtype
+        self.where = {}
+        for raw, fi in where.items():
+            self.where[canonical_name(raw)] = (fi, raw)
+        self.names = list(self.where.keys())
+
+    def raw(self, name):
+        fi, rawname = self.where[name]
+        return self.files[fi].get(rawname)
+
+    def has(self, name):
+        return name in self.where
+
+    def weight(self, prefix: str):
+        """Dense 16-bit weight for ``prefix`` ('....q_proj'), de-quantising pre-quantised formats."""
+        if self.has(prefix + ".weight"):
+            w = self.raw(prefix + ".weight")
+            if w.dtype == torch.float8_e4m3fn:
+                sname = prefix + ".weight_scale_inv" if self.has(prefix + ".weight_scale_inv") else prefix + ".weight_scale"
+                if self.has(sname):
+                    sc = self.raw(sname)
+                    if sc.numel() == 1:
+                        return (w.float() * sc.float().item()).to(self.dtype)
+                    return dequant_fp8_block(w, sc, self.dtype)
+                return w.float().to(self.dtype)
+            return w
+        if self.has(prefix + ".qweight"):
+            return dequant_awq(self.raw(prefix + ".qweight"), self.raw(prefix + ".qzeros"), self.raw(prefix + ".scales"), self.dtype)
+        return None
+
+    def collect(self, prefix: str) -> dict:
+        """All tensors under ``prefix`` as canonical name -> dense tensor (quantised triples collapsed to .weight)."""
+        out = {}
+        done = set()
+        for n in self.names:
+            if not n.startswith(prefix):
+                continue
+            base, _, leaf = n.rpartition(".")
+            if leaf in ("weight_scale_inv", "weight_scale", "qzeros", "scales", "g_idx"):
+                continue
+            if leaf in ("weight", "qweight"):
+                if base in done:
+                    continue
+                done.add(base)
+                out[base + ".weight"] = self.weight(base)
+            else:
+                out[n] = self.raw(n)
+        return out
+
+    def close(self):
+        for f in self.files:
+            f.close()
+
+
+def resolve_wdtype(name: str, default: str, rules: list | None) -> str:
+    """Apply ``dtype_config`` rules ``[{"key": regex, "dtype": name}, ...]``; the last matching rule wins."""
+    out = default
+    for r in rules or []:
+        if re.search(r["key"], name):
+            out = r["dtype"]
+    return out
+
+
+def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto", moe_wdtype: str | None = None,
+               tp: TPInfo | None = None, ep=None, dtype_config: list | str | None = None) -> DecoderModel:
+    """Build a ready-to-run ``DecoderModel`` from an HF folder."""
+    cfg = load_config(path)
+    if dtype is None:
+        dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}.get(cfg.torch_dtype, torch.bfloat16)
+        if str(device).startswith("cuda") and dtype == torch.float32:
+            dtype = torch.bfloat16
+    if wdtype in ("float16", "fp16", "half"):
+        dtype = torch.float16
+    if wdtype in ("bfloat16", "bf16"):
+        dtype = torch.bfloat16
+    if isinstance(dtype_config, str) and dtype_config:
+        dtype_config = json.loads(Path(dtype_config).read_text()) if Path(dtype_config).exists() else json.loads(dtype_config)
+    ck = HFCheckpoint(path, cfg, dtype if dtype != torch.float32 else torch.float32)
+    if wdtype == "auto" and cfg.quantization_config:
+        q = cfg.quantization_config
+        method = str(q.get("quant_method", "")).lower()
+        if method == "fp8":
+            wdtype = "fp8"
+        elif method in ("awq", "gptq", "compressed-tensors"):
+            wdtype = f"int4g{q.get('group_size', 128)}"
+    m = DecoderModel(cfg, device, dtype, tp, ep)
+
+    def top_fn():
+        t = {}
+        for k in ("model.embed_tokens.weight", "model.norm.weight", "lm_head.weight"):
+            if ck.has(k):
+                t[k] = ck.raw(k)
+        return t
+
+    def layer_fn(i):
+        return ck.collect(f"model.layers.{i}.")
+
+    # dtype_config rules are evaluated per layer-level prefix (attention / mlp / experts)
+    if dtype_config:
+        base_w, base_m = wdtype, moe_wdtype
+
+        class _Rules:
+            pass
+
+        # resolved lazily inside shard.build_layer through these callables
+        m.wdtype_for = lambda name: resolve_wdtype(name, base_w, dtype_config)
+        m.moe_wdtype_for = lambda name: resolve_wdtype(name, base_m or base_w, dtype_config)
+    finalize_model(m, top_fn, layer_fn, wdtype=wdtype, moe_wdtype=moe_wdtype)
+    ck.close()
+    return m

@@ -65,6 +65,16 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
     a.ln = _to(g("input_layernorm.weight"), m)
     f.ln = _to(g("post_attention_layernorm.weight"), m)
     r, n = tp.rank, tp.size
+    base_w, base_mw = wdtype, (moe_wdtype or wdtype)
+
+    def W(name):          # per-tensor weight dtype (dtype_config rules may override the default)
+        f_ = getattr(m, "wdtype_for", None)
+        return f_(p + name) if f_ else base_w
+
+    def MW(name):
+        f_ = getattr(m, "moe_wdtype_for", None)
+        return f_(p + name) if f_ else base_mw
+
     if cfg.use_mla:
         nope, rope, vd, lora = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         Hl = cfg.num_heads // n
@@ -101,9 +111,9 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         if bq is not None:
             b = torch.cat([_heads_rows(bq, D, r * Hq_l, (r + 1) * Hq_l), _heads_rows(bk, D, kv0, kv0 + Hkv_l),
                            _heads_rows(bv, D, kv0, kv0 + Hkv_l)])
-        a.qkv = _lin(m, w, wdtype, b)
+        a.qkv = _lin(m, w, W("self_attn.qkv_proj.weight"), b)
         ob = g("self_attn.o_proj.bias")
-        a.o = _lin(m, _shard_cols(g("self_attn.o_proj.weight"), r, n), wdtype, ob if (ob is not None and r == 0) else None)
+        a.o = _lin(m, _shard_cols(g("self_attn.o_proj.weight"), r, n), W("self_attn.o_proj.weight"), ob if (ob is not None and r == 0) else None)
         a.q_norm = _to(g("self_attn.q_norm.weight"), m)
         a.k_norm = _to(g("self_attn.k_norm.weight"), m)
     # ---- feed-forward ----
@@ -111,7 +121,6 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         f.router = g("mlp.gate.weight").to(m.device, torch.float32).contiguous()
         rb = g("mlp.gate.e_score_correction_bias")
         f.router_bias = rb.to(m.device, torch.float32).contiguous() if rb is not None else None
-        mw = moe_wdtype or wdtype
         lo, hi = MOE.local_expert_range(cfg.num_experts, m.ep)
         moe_tp = (m.ep is None or m.ep.size == 1) and n > 1      # no EP: shard every expert's intermediate dim
         gu, dn = [], []
@@ -119,8 +128,8 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
             gw, uw, dw = (g(f"mlp.experts.{e}.{nm}.weight") for nm in ("gate_proj", "up_proj", "down_proj"))
             if moe_tp:
                 gw, uw, dw = _shard_rows(gw, r, n), _shard_rows(uw, r, n), _shard_cols(dw, r, n)
-            gu.append(_gate_up(m, gw, uw, mw))
-            dn.append(_lin(m, dw, mw))
+            gu.append(_gate_up(m, gw, uw, MW(f"mlp.experts.{e}.gate_proj.weight")))
+            dn.append(_lin(m, dw, MW(f"mlp.experts.{e}.down_proj.weight")))
             for nm in ("gate_proj", "up_proj", "down_proj"):
                 t.pop(p + f"mlp.experts.{e}.{nm}.weight", None)
         f.experts = MOE.ExpertWeights(cfg.num_experts, lo, gu, dn)
@@ -136,9 +145,9 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         else:
             gw, uw = g("mlp.gate_proj.weight"), g("mlp.up_proj.weight")
         bg, bu, bd = g("mlp.gate_proj.bias"), g("mlp.up_proj.bias"), g("mlp.down_proj.bias")
-        f.gate_up = _gate_up(m, _shard_rows(gw, r, n), _shard_rows(uw, r, n), wdtype,
+        f.gate_up = _gate_up(m, _shard_rows(gw, r, n), _shard_rows(uw, r, n), W("mlp.gate_proj.weight"),
                              _shard_rows(bg, r, n) if bg is not None else None, _shard_rows(bu, r, n) if bu is not None else None)
-        f.down = _lin(m, _shard_cols(g("mlp.down_proj.weight"), r, n), wdtype, bd if (bd is not None and r == 0) else None)
+        f.down = _lin(m, _shard_cols(g("mlp.down_proj.weight"), r, n), W("mlp.down_proj.weight"), bd if (bd is not None and r == 0) else None)
     while len(m.layers) <= i:
         m.layers.append(None)
     m.layers[i] = lw

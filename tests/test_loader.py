@@ -1,0 +1,94 @@
+"""Loader: safetensors round trip, HF folder -> model parity with the random-init path, dtype_config rules,
+pre-quantised (block FP8) checkpoints, and parity with Hugging Face transformers on tiny random models."""
+import json
+import os
+
+import pytest
+import torch
+
+from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+from fastllm_b200.loader import hf, safetensors as st
+from fastllm_b200.models import preset, random_init
+from fastllm_b200.ops import quant
+
+
+def test_safetensors_roundtrip(tmp_path):
+    t = {"a": torch.randn(3, 5), "b": torch.randn(4, 4).bfloat16(), "c": torch.arange(7, dtype=torch.int32),
+         "d": torch.randn(8, 8).to(torch.float8_e4m3fn)}
+    st.save_file(t, tmp_path / "x.safetensors", metadata={"format": "pt"})
+    f = st.SafeTensorFile(tmp_path / "x.safetensors")
+    for k, v in t.items():
+        got = f.get(k)
+        assert got.dtype == v.dtype and torch.equal(got.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else got,
+                                                    v.view(torch.uint8) if v.dtype == torch.float8_e4m3fn else v)
+    f.close()
+
+
+def _write_hf(tmp_path, name, transform=None):
+    from baseline import synth
+
+    d = synth.write_model(name, str(tmp_path / name), dtype=torch.float32, std=0.05)
+    return d
+
+
+def test_hf_folder_matches_transformers(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    d = _write_hf(tmp_path, "tiny-llama")
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16)
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, 500, (37,), generator=g).tolist()
+    out = eng.generate([prompt], GenerationConfig(max_new_tokens=8, ignore_eos=True))[0]
+    ref = transformers.AutoModelForCausalLM.from_pretrained(d, torch_dtype=torch.float32)
+    ref.eval()
+    with torch.no_grad():
+        ids = torch.tensor([prompt])
+        gen = ref.generate(ids, max_new_tokens=8, do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert gen[0, len(prompt):].tolist() == out
+
+
+def test_qwen3_matches_transformers(tmp_path):
+    transformers = pytest.importorskip("transformers")
+    d = _write_hf(tmp_path, "tiny-qwen3")
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16)
+    prompt = list(range(5, 150, 3))
+    out = eng.generate([prompt], GenerationConfig(max_new_tokens=6, ignore_eos=True))[0]
+    ref = transformers.AutoModelForCausalLM.from_pretrained(d, torch_dtype=torch.float32)
+    ref.eval()
+    with torch.no_grad():
+        gen = ref.generate(torch.tensor([prompt]), max_new_tokens=6, do_sample=False, eos_token_id=None, pad_token_id=0)
+    assert gen[0, len(prompt):].tolist() == out
+
+
+def test_dtype_config_rules():
+    rules = [{"key": "mlp", "dtype": "int4g128"}, {"key": "down_proj", "dtype": "int8"}]
+    assert hf.resolve_wdtype("model.layers.0.mlp.gate_proj.weight", "float16", rules) == "int4g128"
+    assert hf.resolve_wdtype("model.layers.0.mlp.down_proj.weight", "float16", rules) == "int8"
+    assert hf.resolve_wdtype("model.layers.0.self_attn.q_proj.weight", "float16", rules) == "float16"
+
+
+def test_fp8_block_checkpoint(tmp_path):
+    w = torch.randn(256, 384) * 0.05
+    q, s = quant.quantize_fp8_block(w)
+    back = hf.dequant_fp8_block(q, s, torch.float32)
+    assert (back - w).abs().max() < 0.02
+    assert torch.allclose(back, quant.dequantize_fp8_block(q, s, torch.float32))
+
+
+@pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8"])
+def test_quant_roundtrip_error(kind):
+    torch.manual_seed(0)
+    w = torch.randn(64, 256) * 0.05
+    lw = quant.LinearWeight.from_dense(w, kind, act_dtype=torch.float32)
+    err = (lw.dequant(torch.float32) - w).abs().max().item()
+    assert err < {"int8": 0.002, "int4g128": 0.03, "fp8": 0.02}[kind]
+    x = torch.randn(5, 256)
+    y = lw(x)
+    assert torch.allclose(y, x @ lw.dequant(torch.float32).t(), atol=1e-4)
+
+
+def test_int4g_packing_high_nibble_first():
+    w = torch.tensor([[0.0, 15.0] * 64])
+    packed, scale, mn = quant.quantize_int4g(w, 128)
+    assert packed[0, 0].item() == 0x0F      # first value (0) in the high nibble, second (15) in the low nibble
