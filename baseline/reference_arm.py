@@ -29,6 +29,21 @@ def run(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    # The reference's error path waits for a key press: give it an empty stdin, and bound the whole arm in time.
+    try:
+        os.dup2(os.open(os.devnull, os.O_RDONLY), 0)
+    except OSError:
+        pass
+    import threading
+
+    limit_s = float(os.environ.get("FB_REF_TIME_LIMIT", "900"))
+
+    def _watchdog():
+        time.sleep(limit_s)
+        _unavailable(f"reference run did not finish within {int(limit_s)} s")
+        os._exit(0)
+
+    threading.Thread(target=_watchdog, daemon=True).start()
     if not os.path.exists(os.path.join(REF, "ftllm", "libfastllm_tools.so")):
         _unavailable("baseline/_ref/ftllm/libfastllm_tools.so missing (reference not built in this checkout)")
         return
@@ -59,7 +74,9 @@ def run(args):
         return
     B, P, O = args.batch, args.prompt_len, args.output_len
     device = "cuda" if args.gpus == 1 else "multicuda:" + ",".join(str(i) for i in range(args.gpus))
-    argv = [model_dir, "--device", device, "--dtype", "bfloat16", "--atype", "bfloat16", "--max_batch", str(B),
+    # The reference's Llama path accepts fp32 / fp16 activations only ("Attention's input's type should be float32 or
+    # float16" with bf16), so its arm runs the same 16-bit width in fp16.
+    argv = [model_dir, "--device", device, "--dtype", "float16", "--atype", "float16", "--max_batch", str(B),
             "--tokens", str(int(B * (P + O + 256) / 0.75)), "--page_size", "128"]
     parser = make_normal_parser("reference bench")
     rb.add_benchmark_args(parser)
@@ -124,7 +141,7 @@ def run(args):
     out = {
         "metric": "decode output tok/s (device-timed, max over ranks)", "value": B * K / secs, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": secs / K * 1000.0, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (the reference's Llama path rejects bf16 activations)",
         "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
         "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O,
                    "parallelism": device, "timing": "wall clock at the reference's fetch loop (no device events in its API)"},
