@@ -333,3 +333,107 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
 #undef FB_AD_LAUNCH
   return (int)cudaGetLastError();
 }
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared and documented in attn_decode_static.h)
+// ---------------------------------------------------------------------------------------------------
+#include "attn_decode_static.h"
+
+namespace fb {
+
+// layout of the static scratch (floats / ints):  [work: 2*MAX_ITEMS ints][n_work: 64 ints (one used)]
+//                                                [part_ml: 2*MAX_SLOTS floats][part_o: 128*MAX_SLOTS floats]
+constexpr size_t ST_WORK_WORDS = 2 * (size_t)FB_STATIC_MAX_ITEMS;
+constexpr size_t ST_NWORK_WORDS = 64;
+constexpr size_t ST_ML_WORDS = 2 * (size_t)FB_STATIC_MAX_SLOTS;
+constexpr size_t ST_O_WORDS = (size_t)AD_D * FB_STATIC_MAX_SLOTS;
+constexpr size_t ST_TOTAL_WORDS = ST_WORK_WORDS + ST_NWORK_WORDS + ST_ML_WORDS + ST_O_WORDS;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) uint32_t g_static_scratch[ST_TOTAL_WORDS];
+
+constexpr int ST_MAX_DEVICES = 64;
+static uint32_t* g_static_ptr[ST_MAX_DEVICES];        // device address of the array, per device (0 = not set up)
+static std::mutex g_static_mu;
+
+// Encodes one 2-D tensor map without touching the shared descriptor cache (no host allocation either).
+static bool encode_tmap_2d_direct(CUtensorMap* out, const void* ptr, uint64_t rows, uint64_t cols, uint64_t ld,
+                                  uint32_t box_rows, uint32_t box_cols) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || ((ld * 2) & 15)) return false;
+  cuuint64_t gdim[2] = {cols, rows};
+  cuuint64_t gstride[1] = {ld * 2};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace fb
+
+extern "C" int fb_attn_decode_static(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out,
+                                     const int* page_table, const int* seq_lens, int B, int Hq, int Hkv, int D,
+                                     long long num_slots, int max_pages, float scale, int dtype, void* stream_) {
+  using namespace fb;
+  if (B <= 0) return 0;
+  if (D != AD_D || Hkv <= 0 || Hq % Hkv != 0 || B > 1024 || max_pages <= 0 || (dtype != 0 && dtype != 1)) return -1;
+  const int G = Hq / Hkv;
+  if (G > AD_NPAD) return -1;
+  const long long items = (long long)B * max_pages;
+  const long long slots = items * Hkv * G;
+  if (items > FB_STATIC_MAX_ITEMS || slots > FB_STATIC_MAX_SLOTS) return FB_STATIC_TOO_LARGE;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= ST_MAX_DEVICES) return -1;
+  uint32_t* base = nullptr;
+  {
+    std::lock_guard<std::mutex> g(g_static_mu);
+    if (g_static_ptr[dev] == nullptr) {
+      // once per device, with that device current: resolve the device address of the file-scope array
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess) return (int)e;
+      e = cudaFuncSetAttribute(attn_decode_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1));
+      if (e != cudaSuccess) return (int)e;
+      e = cudaFuncSetAttribute(attn_decode_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1));
+      if (e != cudaSuccess) return (int)e;
+      g_static_ptr[dev] = reinterpret_cast<uint32_t*>(p);
+    }
+    base = g_static_ptr[dev];
+  }
+  int* work = reinterpret_cast<int*>(base);
+  int* n_work = reinterpret_cast<int*>(base + ST_WORK_WORDS);
+  float* part_ml = reinterpret_cast<float*>(base + ST_WORK_WORDS + ST_NWORK_WORDS);
+  float* part_o = reinterpret_cast<float*>(base + ST_WORK_WORDS + ST_NWORK_WORDS + ST_ML_WORDS);
+  CUtensorMap tmK, tmV, tmQ;
+  if (!encode_tmap_2d_direct(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64)) return -2;
+  if (!encode_tmap_2d_direct(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64)) return -2;
+  if (!encode_tmap_2d_direct(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 64)) return -2;
+  int threads = 32;
+  while (threads < B) threads <<= 1;
+  attn_decode_plan_kernel<<<1, threads, 0, stream>>>(seq_lens, B, work, n_work, (int)items);
+  AttnDecodeParams p;
+  p.work = work; p.n_work = n_work; p.page_table = page_table; p.seq_lens = seq_lens; p.part_o = part_o; p.part_ml = part_ml;
+  p.max_pages = max_pages; p.max_splits = max_pages; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
+  p.B = B; p.max_items = (int)items;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  const uint32_t f = dtype == 1 ? 1u : 0u;
+  p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);
+  p.idesc_o = make_idesc(f, f, 1, 0, 128, AD_NPAD);
+  int sms = 0;
+  e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return (int)e;
+  const int grid = 2 * sms;
+  if (dtype == 1) {
+    attn_decode_kernel<true, 1><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, p);
+    attn_decode_combine_kernel<true><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages);
+  } else {
+    attn_decode_kernel<false, 1><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, p);
+    attn_decode_combine_kernel<false><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages);
+  }
+  return (int)cudaGetLastError();
+}
