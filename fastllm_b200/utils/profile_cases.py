@@ -1,0 +1,64 @@
+"""Small single-kernel workloads for profiling (`python -m fastllm_b200.utils.profile_cases <case>`).
+
+Each case allocates a few hundred MB (inputs larger than the 126 MB L2 so DRAM counters mean something), runs
+the kernel a handful of times and exits; meant to be wrapped as
+`ncu --set full --clock-control none -k regex:<kernel> -s 2 -c 2 -o <out> python -m fastllm_b200.utils.profile_cases <case>`.
+"""
+from __future__ import annotations
+
+import math
+import sys
+
+import torch
+
+from ..ops import _lib
+from ..ops import attention as A
+from ..ops import basic as B
+
+
+def gemm_decode(n=28672, k=4096, m=64, swiglu=True, iters=4):
+    dev = "cuda"
+    ws = [(torch.randn(n, k, device=dev) * 0.02).bfloat16() for _ in range(2)]
+    x = torch.randn(m, k, device=dev).bfloat16()
+    for i in range(iters):
+        B.linear(x, ws[i % 2], swiglu=swiglu)
+    torch.cuda.synchronize()
+
+
+def attn_decode(batch=64, length=1100, hq=32, hkv=8, iters=4):
+    dev, D = "cuda", 128
+    npg = (length + 127) // 128
+    pages = batch * npg
+    k_pool = (torch.randn(pages, 128, hkv, D, device=dev) * 0.5).bfloat16()
+    v_pool = torch.randn(pages, 128, hkv, D, device=dev).bfloat16()
+    pt = torch.randperm(pages, device=dev).int().view(batch, npg)
+    seq = torch.full((batch,), length, dtype=torch.int32, device=dev)
+    q = torch.randn(batch, hq * D, device=dev).bfloat16()
+    ws = A.DecodeWorkspace(batch, hkv, hq // hkv, npg, dev)
+    torch.cuda.synchronize()
+    for _ in range(iters):
+        A.attn_decode(q, k_pool, v_pool, pt, seq, 1 / math.sqrt(D), hq, hkv, D, ws=ws)
+    torch.cuda.synchronize()
+
+
+def gemm_prefill(m=4096, n=6144, k=4096, iters=4):
+    dev = "cuda"
+    w = (torch.randn(n, k, device=dev) * 0.02).bfloat16()
+    x = torch.randn(m, k, device=dev).bfloat16()
+    for _ in range(iters):
+        B.linear(x, w)
+    torch.cuda.synchronize()
+
+
+CASES = {
+    "gemm_decode_gate_up": lambda: gemm_decode(28672, 4096, 64, True),
+    "gemm_decode_down": lambda: gemm_decode(4096, 14336, 64, False),
+    "attn_decode": attn_decode,
+    "gemm_prefill": gemm_prefill,
+}
+
+if __name__ == "__main__":
+    name = sys.argv[1] if len(sys.argv) > 1 else "gemm_decode_gate_up"
+    CASES[name]()
+    _lib.check_device_errors()
+    print("ok", name)
