@@ -1,0 +1,313 @@
+"""Public Python API: ``llm.model(path, ...)`` with ``response`` / ``stream_response`` / handle-based streaming.
+
+Mirrors the surface of the reference's ``ftllm.llm`` (tools/fastllm_pytools/llm.py: ``model.__init__`` :1083,
+``response`` :1929, ``stream_response`` :1947, ``launch_stream_response`` :2082, ``abort_handle`` :2402,
+``stream_response_handle`` :2429, ``response_logits`` :1900, module-level ``set_device_map`` etc. :589-640), on
+top of the in-process engine instead of a ctypes bridge to a separate runtime.
+"""
+from __future__ import annotations
+
+import asyncio
+import os
+import threading
+from pathlib import Path
+from typing import Iterable
+
+import torch
+
+from .engine import EngineConfig, GenerationConfig, LLMEngine
+from .models.decoder import TPInfo
+from .tokenizer import StreamDecoder, Tokenizer
+
+# ---- module-level settings (reference: set_device_map / set_cpu_threads / ... before creating a model) ----
+_settings = {"device": None, "device_map": None, "moe_device_map": None, "threads": None, "max_batch": 256, "max_tokens": None,
+             "gpu_mem_ratio": 0.9, "chunked_prefill_size": 8192, "max_context": 8192, "page_size": 128, "cuda_graph": True,
+             "prefix_cache": True}
+
+fastllm_data_type_dict = {"": 0, "auto": 100003, "int2g": 11, "int4g": 9, "int4": 8, "int8": 3, "float16": 7, "fp16": 7, "half": 7,
+                          "bfloat16": 1, "bf16": 1, "float32": 0, "fp8": 10, "float8": 10, "fp8_e4m3": 10}
+
+
+def set_device_map(device_map, is_moe: bool = False):
+    """``"cuda"``, ``"cuda:1"``, ``"cpu"``, a list of devices or a ``{device: layers}`` dict (layer split)."""
+    _settings["moe_device_map" if is_moe else "device_map"] = device_map
+
+
+def set_cpu_threads(n: int):
+    _settings["threads"] = n
+    torch.set_num_threads(max(1, n))
+
+
+def get_cpu_threads() -> int:
+    return torch.get_num_threads()
+
+
+def set_max_batch(n: int):
+    _settings["max_batch"] = n
+
+
+def set_max_tokens(n: int):
+    _settings["max_tokens"] = n
+
+
+def set_gpu_mem_ratio(r: float):
+    _settings["gpu_mem_ratio"] = r
+
+
+def set_chunked_prefill_size(n: int):
+    _settings["chunked_prefill_size"] = n
+
+
+def set_max_context_length(n: int):
+    _settings["max_context"] = n
+
+
+def set_page_size(n: int):
+    if n not in (-1, 128):
+        raise ValueError("this build uses 128-token KV pages (one page = one tensor-core tile)")
+
+
+def set_cuda_graph(on: bool):
+    _settings["cuda_graph"] = bool(on)
+
+
+def set_prefix_cache(on: bool):
+    _settings["prefix_cache"] = bool(on)
+
+
+def _resolve_device():
+    dm = _settings["device_map"]
+    if isinstance(dm, str):
+        d = dm.replace("multicuda", "cuda")
+        return d.split(",")[0] if ":" in d else d
+    if isinstance(dm, (list, tuple)) and dm:
+        return str(dm[0])
+    if isinstance(dm, dict) and dm:
+        return str(next(iter(dm)))
+    return "cuda" if torch.cuda.is_available() else "cpu"
+
+
+class model:
+    """A loaded model plus its serving engine (started lazily on first request)."""
+
+    def __init__(self, path: str, id: int = -99999, dtype: str = "auto", kv_cache_dtype: str = "auto", moe_dtype: str = "",
+                 system_prompt: str = "", eos_token: Iterable[str] | None = None, tokenizer_type: str = "auto",
+                 model_json: str = "", graph=None, lora: str = "", dtype_config: str = "", ori_model_path: str = "",
+                 chat_template: str = "", tool_call_parser: str = "auto", device: str | None = None, tp: TPInfo | None = None,
+                 engine_config: EngineConfig | None = None, _model=None):
+        from .loader import hf as hf_loader
+
+        self.path = path
+        self.system_prompt = system_prompt
+        self.tool_call_parser = tool_call_parser
+        dev = device or _resolve_device()
+        tpl = Path(chat_template).read_text(encoding="utf-8") if chat_template and os.path.exists(chat_template) else (chat_template or None)
+        self.tokenizer = Tokenizer(path if path and os.path.isdir(path) else None, prefer_native=(tokenizer_type == "native"),
+                                   chat_template=tpl)
+        self.hf_tokenizer = self.tokenizer.hf
+        if _model is not None:
+            self.torch_model = _model
+        elif path and path.endswith(".flm"):
+            from .loader import flm
+
+            self.torch_model = flm.load_model(path, device=dev, tp=tp)
+        elif path and path.endswith(".gguf"):
+            from .loader import gguf
+
+            self.torch_model = gguf.load_model(path, device=dev, ori=ori_model_path or None)
+        else:
+            self.torch_model = hf_loader.load_model(path, device=dev, wdtype=dtype or "auto", moe_wdtype=moe_dtype or None, tp=tp,
+                                                    dtype_config=dtype_config or None)
+        cfg = self.torch_model.cfg
+        eos = set(cfg.eos_token_ids) | set(self.tokenizer.eos_ids())
+        for t in eos_token or []:
+            ids = self.tokenizer.encode(t)
+            if len(ids) == 1:
+                eos.add(ids[0])
+        self.eos_token_ids = sorted(eos)
+        ec = engine_config or EngineConfig(max_batch=_settings["max_batch"], max_context=min(_settings["max_context"], cfg.max_position),
+                                           chunked_prefill_size=_settings["chunked_prefill_size"], gpu_mem_ratio=_settings["gpu_mem_ratio"],
+                                           max_tokens=_settings["max_tokens"], use_cuda_graph=_settings["cuda_graph"],
+                                           prefix_cache=_settings["prefix_cache"])
+        self.engine = LLMEngine(self.torch_model, ec, eos_token_ids=self.eos_token_ids)
+        self.default_generation_config = {"repetition_penalty": 1.0, "top_p": 0.8, "top_k": 1, "temperature": 1.0}
+        gc = Path(path) / "generation_config.json" if path and os.path.isdir(path) else None
+        if gc is not None and gc.exists():
+            import json
+
+            g = json.loads(gc.read_text())
+            for k in ("repetition_penalty", "top_p", "top_k", "temperature"):
+                if g.get(k) is not None:
+                    self.default_generation_config[k] = g[k]
+        self._lock = threading.Lock()
+
+    # ---- text helpers -------------------------------------------------------------------------------
+    def encode(self, text: str) -> list[int]:
+        return self.tokenizer.encode(text)
+
+    def decode(self, ids) -> str:
+        return self.tokenizer.decode(list(ids))
+
+    def apply_chat_template(self, messages, add_generation_prompt=True, tools=None, **kw) -> str:
+        msgs = list(messages)
+        if self.system_prompt and not any(m.get("role") == "system" for m in msgs):
+            msgs = [{"role": "system", "content": self.system_prompt}] + msgs
+        return self.tokenizer.apply_chat_template(msgs, add_generation_prompt=add_generation_prompt, tools=tools, **kw)
+
+    def get_prompt(self, query: str, history=None) -> str:
+        msgs = []
+        for q, a in history or []:
+            msgs += [{"role": "user", "content": q}, {"role": "assistant", "content": a}]
+        msgs.append({"role": "user", "content": query})
+        return self.apply_chat_template(msgs)
+
+    def _to_ids(self, query, history=None) -> list[int]:
+        if isinstance(query, (list, tuple)) and query and isinstance(query[0], int):
+            return list(query)
+        if isinstance(query, (list, tuple)):            # list of chat messages
+            return self.encode(self.apply_chat_template(list(query)))
+        return self.encode(self.get_prompt(query, history))
+
+    def _gen_config(self, max_length=4096, do_sample=True, top_p=None, top_k=None, temperature=None, repeat_penalty=None,
+                    stop_token_ids=None, min_length=0, **kw) -> GenerationConfig:
+        d = self.default_generation_config
+        top_k = d["top_k"] if top_k is None else top_k
+        temperature = d["temperature"] if temperature is None else temperature
+        sample = bool(do_sample) and top_k != 1 and temperature > 1e-6
+        return GenerationConfig(max_new_tokens=max_length, min_new_tokens=min_length, do_sample=sample, top_k=top_k if sample else 1,
+                                top_p=d["top_p"] if top_p is None else top_p, temperature=temperature,
+                                repeat_penalty=d["repetition_penalty"] if repeat_penalty is None else repeat_penalty,
+                                stop_token_ids=list(stop_token_ids or []), output_logits=bool(kw.get("output_logits", False)))
+
+    # ---- handle-level API ---------------------------------------------------------------------------
+    def launch_stream_response(self, query, history=None, **gen_kwargs) -> int:
+        ids = self._to_ids(query, history)
+        self.engine.start()
+        return self.engine.launch(ids, self._gen_config(**gen_kwargs))
+
+    def abort_handle(self, handle: int):
+        self.engine.abort(handle)
+
+    def stream_response_handle(self, handle: int, one_by_one: bool = True, skip_special_tokens: bool = True):
+        sd = StreamDecoder(self.tokenizer, skip_special_tokens)
+        while True:
+            tok = self.engine.fetch(handle)
+            if tok < 0:
+                break
+            piece = sd.push(tok)
+            if piece:
+                yield piece
+
+    def stream_response_raw(self, input_tokens, **gen_kwargs):
+        h = self.launch_stream_response(list(input_tokens), **gen_kwargs)
+        while True:
+            tok = self.engine.fetch(h)
+            if tok < 0:
+                break
+            yield tok
+
+    # ---- convenience API ----------------------------------------------------------------------------
+    def stream_response(self, query, history=None, max_length=4096, do_sample=True, top_p=None, top_k=None, temperature=None,
+                        repeat_penalty=None, one_by_one=True, stop_token_ids=None, **kw):
+        h = self.launch_stream_response(query, history, max_length=max_length, do_sample=do_sample, top_p=top_p, top_k=top_k,
+                                        temperature=temperature, repeat_penalty=repeat_penalty, stop_token_ids=stop_token_ids)
+        try:
+            yield from self.stream_response_handle(h, one_by_one)
+        except GeneratorExit:
+            self.abort_handle(h)
+            raise
+
+    async def stream_response_async(self, query, history=None, **kw):
+        loop = asyncio.get_running_loop()
+        h = self.launch_stream_response(query, history, **kw)
+        sd = StreamDecoder(self.tokenizer)
+        try:
+            while True:
+                tok = await loop.run_in_executor(None, self.engine.fetch, h)
+                if tok < 0:
+                    break
+                piece = sd.push(tok)
+                if piece:
+                    yield piece
+        except (asyncio.CancelledError, GeneratorExit):
+            self.abort_handle(h)
+            raise
+
+    def response(self, query, history=None, **kw) -> str:
+        return "".join(self.stream_response(query, history, **kw))
+
+    def response_logits(self, query, history=None):
+        """Logits of the token that follows the prompt (fp32 tensor ``[vocab]``)."""
+        ids = self._to_ids(query, history)
+        self.engine.start()
+        h = self.engine.launch(ids, GenerationConfig(max_new_tokens=1, output_logits=True, do_sample=True, top_k=2, temperature=1.0))
+        req = self.engine.requests[h]
+        while self.engine.fetch(h) >= 0:
+            pass
+        return req.last_logits
+
+    def response_batch(self, queries, **kw) -> list[str]:
+        hs = [self.launch_stream_response(q, **kw) for q in queries]
+        return ["".join(self.stream_response_handle(h)) for h in hs]
+
+    def get_response_statistics(self, handle: int) -> dict:
+        return self.engine.stats(handle)
+
+    def warmup(self):
+        list(self.stream_response_raw([1, 2, 3, 4], max_length=2, do_sample=False))
+
+    def get_type(self) -> str:
+        return self.torch_model.cfg.model_type
+
+    def get_struct(self) -> str:
+        return self.torch_model.cfg.model_type
+
+    def get_max_input_len(self) -> int:
+        return self.engine.cfg.max_context
+
+    def get_kv_cache_token_limit(self) -> int:
+        return self.engine.runner.kv.num_pages * self.engine.cfg.page_len
+
+    def save(self, path: str, dtype: str = "auto"):
+        from .loader import flm
+
+        flm.save_model(self.torch_model, self.tokenizer, path, dtype)
+
+    def release_memory(self):
+        self.engine.stop()
+        self.engine = None
+        self.torch_model = None
+        if torch.cuda.is_available():
+            torch.cuda.empty_cache()
+
+    def stop_token_ctypes(self, stop_token_ids):      # kept for scripts written against the reference package
+        return (0, None) if stop_token_ids is None else (len(stop_token_ids), list(stop_token_ids))
+
+
+def from_hf(hf_model, tokenizer=None, dtype: str = "float16", device: str | None = None):
+    """Create a ``model`` from an in-memory Hugging Face model (reference: llm.from_hf, hf_model.py)."""
+    from .loader.shard import finalize_model
+    from .models.config import from_hf_dict
+    from .models.decoder import DecoderModel
+
+    cfg = from_hf_dict(hf_model.config.to_dict())
+    sd = {k: v.detach() for k, v in hf_model.state_dict().items()}
+    dev = device or _resolve_device()
+    tdt = torch.float32 if dev == "cpu" else (torch.bfloat16 if dtype in ("bfloat16", "bf16") else torch.float16)
+    m = DecoderModel(cfg, dev, tdt)
+    from .loader.hf import canonical_name
+
+    sd = {canonical_name(k): v for k, v in sd.items()}
+    finalize_model(m, lambda: {k: v for k, v in sd.items() if not k.startswith("model.layers.")},
+                   lambda i: {k: v for k, v in sd.items() if k.startswith(f"model.layers.{i}.")},
+                   wdtype=dtype if dtype not in ("float16", "bfloat16", "float32") else "dense")
+    obj = model.__new__(model)
+    model.__init__(obj, "", _model=m, device=dev)
+    if tokenizer is not None:
+        obj.tokenizer.hf = tokenizer
+        obj.hf_tokenizer = tokenizer
+        if getattr(tokenizer, "chat_template", None):
+            obj.tokenizer.chat_template = tokenizer.chat_template
+        if tokenizer.eos_token_id is not None:
+            obj.engine.eos.add(tokenizer.eos_token_id)
+    return obj
