@@ -81,6 +81,8 @@ class HFCheckpoint:
         for raw, fi in where.items():
             self.where[canonical_name(raw)] = (fi, raw)
         self.names = list(self.where.keys())
+        sh = Path(path) / "fastllm_shapes.json"
+        self.blob_shapes = json.loads(sh.read_text()) if sh.exists() else {}
 
     def raw(self, name):
         fi, rawname = self.where[name]
@@ -92,6 +94,11 @@ class HFCheckpoint:
     def weight(self, prefix: str):
         """Dense 16-bit weight for ``prefix`` ('....q_proj'), de-quantising pre-quantised formats."""
         if self.has(prefix + ".weight"):
+            fi, rawname = self.where[prefix + ".weight"]
+            if self.files[fi].info(rawname)["dtype"] == "fastllm":
+                from .export import decode_blob
+
+                return decode_blob(self.files[fi].get(rawname), self.blob_shapes[rawname], self.dtype)
             w = self.raw(prefix + ".weight")
             if w.dtype == torch.float8_e4m3fn:
                 sname = prefix + ".weight_scale_inv" if self.has(prefix + ".weight_scale_inv") else prefix + ".weight_scale"

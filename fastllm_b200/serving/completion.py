@@ -1,0 +1,244 @@
+"""Request handling shared by the HTTP routes: prompt building, generation, streaming chunks, usage accounting.
+
+Covers the reference's completion glue (tools/fastllm_pytools/openai_server/fastllm_completion.py:122-3502):
+validation, chat-template rendering, SSE streaming, usage with cached-token counts, ``<think>`` splitting,
+tool-call parsing (stream + non-stream), stop strings, abort on client disconnect.
+"""
+from __future__ import annotations
+
+import asyncio
+import json
+import time
+import uuid
+
+from ..tokenizer import StreamDecoder
+from .toolcall import StreamSplitter, get_parser, split_reasoning
+
+
+def _content_text(c):
+    if isinstance(c, list):
+        return "".join(p.get("text", "") for p in c if isinstance(p, dict) and p.get("type", "text") in ("text", "input_text", "output_text"))
+    return c or ""
+
+
+def normalize_messages(messages):
+    out = []
+    for m in messages:
+        d = dict(m)
+        d["content"] = _content_text(d.get("content"))
+        out.append(d)
+    return out
+
+
+class ActiveRequests:
+    """Bookkeeping for /v1/cancel and /v1/active_conversations."""
+
+    def __init__(self):
+        self.by_id: dict[str, dict] = {}
+
+    def add(self, rid, handle, prompt_tokens):
+        self.by_id[rid] = {"handle": handle, "created": time.time(), "prompt_tokens": prompt_tokens, "output_tokens": 0}
+
+    def remove(self, rid):
+        self.by_id.pop(rid, None)
+
+
+class Completion:
+    def __init__(self, model, model_name: str = "fastllm-b200", think: bool = True, hide_input: bool = True):
+        self.model = model
+        self.model_name = model_name
+        self.think = think
+        self.hide_input = hide_input
+        self.active = ActiveRequests()
+        self.totals = {"requests": 0, "prompt_tokens": 0, "completion_tokens": 0, "cached_tokens": 0}
+
+    # ---------------------------------------------------------------------------------------------
+    def build_prompt_ids(self, messages=None, prompt=None, tools=None, chat_template_kwargs=None):
+        if messages is not None:
+            text = self.model.apply_chat_template(normalize_messages(messages), add_generation_prompt=True, tools=tools,
+                                                  **(chat_template_kwargs or {}))
+            return self.model.encode(text), text
+        if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
+            return list(prompt), None
+        return self.model.encode(prompt or ""), prompt
+
+    def gen_kwargs(self, req: dict) -> dict:
+        temperature = req.get("temperature")
+        top_k = req.get("top_k")
+        do_sample = not (temperature is not None and temperature <= 1e-6)
+        if top_k is None and do_sample and (temperature is not None or req.get("top_p") is not None):
+            top_k = 50
+        mx = req.get("max_completion_tokens") or req.get("max_tokens") or req.get("max_output_tokens") or 4096
+        return dict(max_length=int(mx), do_sample=do_sample, top_p=req.get("top_p"), top_k=top_k, temperature=temperature,
+                    repeat_penalty=req.get("repetition_penalty") or req.get("frequency_penalty_as_repeat"),
+                    stop_token_ids=req.get("stop_token_ids"))
+
+    async def generate(self, ids, gen_kwargs, stop=None, is_disconnected=None, rid=None):
+        """Async generator of (piece, finish_reason or None).  Aborts the engine request when the client goes away."""
+        loop = asyncio.get_running_loop()
+        m = self.model
+        handle = m.launch_stream_response(ids, **gen_kwargs)
+        rid = rid or uuid.uuid4().hex
+        self.active.add(rid, handle, len(ids))
+        req = m.engine.requests.get(handle)
+        sd = StreamDecoder(m.tokenizer)
+        stops = [stop] if isinstance(stop, str) else list(stop or [])
+        text = ""
+        try:
+            while True:
+                tok = await loop.run_in_executor(None, m.engine.fetch, handle)
+                if tok < 0:
+                    break
+                self.active.by_id.get(rid, {}).update(output_tokens=len(req.output_ids) if req else 0)
+                piece = sd.push(tok)
+                if not piece:
+                    continue
+                text += piece
+                hit = next((s for s in stops if s and s in text), None)
+                if hit is not None:
+                    cut = text.index(hit)
+                    keep = piece[:max(0, len(piece) - (len(text) - cut))]
+                    if keep:
+                        yield keep, None
+                    m.abort_handle(handle)
+                    yield "", "stop"
+                    return
+                yield piece, None
+                if is_disconnected is not None and await is_disconnected():
+                    m.abort_handle(handle)
+                    return
+            yield "", (req.finish_reason if req is not None and req.finish_reason in ("stop", "length") else "stop")
+        except (asyncio.CancelledError, GeneratorExit):
+            m.abort_handle(handle)
+            raise
+        finally:
+            st = req.stats.as_dict() if req is not None else {}
+            self.last_usage = {"prompt_tokens": len(ids), "completion_tokens": st.get("output_tokens", 0),
+                               "total_tokens": len(ids) + st.get("output_tokens", 0),
+                               "prompt_tokens_details": {"cached_tokens": st.get("cached_tokens", 0)}}
+            self.totals["requests"] += 1
+            self.totals["prompt_tokens"] += len(ids)
+            self.totals["completion_tokens"] += st.get("output_tokens", 0)
+            self.totals["cached_tokens"] += st.get("cached_tokens", 0)
+            self.active.remove(rid)
+
+    # ---------------------------------------------------------------------------------------------
+    async def chat_completion(self, req: dict, is_disconnected=None):
+        """Non-streaming: returns the response dict.  Streaming: returns an async generator of SSE ``data:`` lines."""
+        tools = req.get("tools")
+        ids, _ = self.build_prompt_ids(messages=req["messages"], tools=tools, chat_template_kwargs=req.get("chat_template_kwargs"))
+        parser = get_parser(self.model.tool_call_parser, self.model.get_type()) if tools else None
+        cid = "chatcmpl-" + uuid.uuid4().hex
+        created = int(time.time())
+        gk = self.gen_kwargs(req)
+        if not req.get("stream"):
+            text, finish = "", "stop"
+            async for piece, fin in self.generate(ids, gk, req.get("stop"), is_disconnected, cid):
+                text += piece
+                finish = fin or finish
+            reasoning, content = split_reasoning(text) if self.think else (None, text)
+            calls = []
+            if parser is not None:
+                content, calls = parser.parse(content)
+            msg = {"role": "assistant", "content": content if (content or not calls) else None}
+            if reasoning:
+                msg["reasoning_content"] = reasoning
+            if calls:
+                msg["tool_calls"] = calls
+                finish = "tool_calls"
+            return {"id": cid, "object": "chat.completion", "created": created, "model": req.get("model") or self.model_name,
+                    "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": self.last_usage}
+
+        async def sse():
+            def chunk(delta, finish=None, usage=None):
+                d = {"id": cid, "object": "chat.completion.chunk", "created": created, "model": req.get("model") or self.model_name,
+                     "choices": [{"index": 0, "delta": delta, "finish_reason": finish}]}
+                if usage is not None:
+                    d["usage"] = usage
+                return "data: " + json.dumps(d, ensure_ascii=False) + "\n\n"
+
+            yield chunk({"role": "assistant", "content": ""})
+            sp = StreamSplitter(parser, reasoning=self.think)
+            finish = "stop"
+            async for piece, fin in self.generate(ids, gk, req.get("stop"), is_disconnected, cid):
+                finish = fin or finish
+                for kind, txt in sp.push(piece) if piece else []:
+                    yield chunk({"reasoning_content": txt} if kind == "reasoning" else {"content": txt})
+            rest, calls = sp.finish()
+            if rest:
+                yield chunk({"content": rest})
+            for i, c in enumerate(calls):
+                yield chunk({"tool_calls": [dict(c, index=i)]})
+            include_usage = (req.get("stream_options") or {}).get("include_usage", True)
+            yield chunk({}, "tool_calls" if calls else finish, self.last_usage if include_usage else None)
+            yield "data: [DONE]\n\n"
+
+        return sse()
+
+    async def text_completion(self, req: dict, is_disconnected=None):
+        ids, _ = self.build_prompt_ids(prompt=req.get("prompt", ""))
+        text, finish = "", "stop"
+        async for piece, fin in self.generate(ids, self.gen_kwargs(req), req.get("stop"), is_disconnected):
+            text += piece
+            finish = fin or finish
+        return {"id": "cmpl-" + uuid.uuid4().hex, "object": "text_completion", "created": int(time.time()),
+                "model": req.get("model") or self.model_name,
+                "choices": [{"index": 0, "text": text, "finish_reason": finish}], "usage": self.last_usage}
+
+    # ---- OpenAI Responses API ---------------------------------------------------------------------
+    async def responses(self, req: dict, is_disconnected=None):
+        inp = req.get("input", "")
+        msgs = []
+        if req.get("instructions"):
+            msgs.append({"role": "system", "content": req["instructions"]})
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        else:
+            for it in inp:
+                if it.get("type", "message") == "message":
+                    msgs.append({"role": it.get("role", "user"), "content": _content_text(it.get("content"))})
+        creq = dict(req, messages=msgs, stream=False, max_tokens=req.get("max_output_tokens"))
+        r = await self.chat_completion(creq, is_disconnected)
+        msg = r["choices"][0]["message"]
+        output = []
+        if msg.get("reasoning_content"):
+            output.append({"type": "reasoning", "id": "rs_" + uuid.uuid4().hex[:16], "summary": [{"type": "summary_text", "text": msg["reasoning_content"]}]})
+        if msg.get("content"):
+            output.append({"type": "message", "id": "msg_" + uuid.uuid4().hex[:16], "role": "assistant", "status": "completed",
+                           "content": [{"type": "output_text", "text": msg["content"], "annotations": []}]})
+        for c in msg.get("tool_calls", []):
+            output.append({"type": "function_call", "id": "fc_" + uuid.uuid4().hex[:16], "call_id": c["id"], "name": c["function"]["name"],
+                           "arguments": c["function"]["arguments"], "status": "completed"})
+        u = r["usage"]
+        return {"id": "resp_" + uuid.uuid4().hex, "object": "response", "created_at": r["created"], "status": "completed", "model": r["model"],
+                "output": output, "output_text": msg.get("content") or "",
+                "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"], "total_tokens": u["total_tokens"],
+                          "input_tokens_details": {"cached_tokens": u["prompt_tokens_details"]["cached_tokens"]}}}
+
+    # ---- Anthropic Messages API -------------------------------------------------------------------
+    async def anthropic_messages(self, req: dict, is_disconnected=None):
+        msgs = []
+        sysm = req.get("system")
+        if sysm:
+            msgs.append({"role": "system", "content": _content_text(sysm) if not isinstance(sysm, str) else sysm})
+        for m in req.get("messages", []):
+            msgs.append({"role": m["role"], "content": _content_text(m.get("content"))})
+        tools = [{"type": "function", "function": {"name": t["name"], "description": t.get("description", ""), "parameters": t.get("input_schema", {})}}
+                 for t in req.get("tools") or []] or None
+        creq = dict(req, messages=msgs, stream=False, tools=tools, stop=req.get("stop_sequences"))
+        r = await self.chat_completion(creq, is_disconnected)
+        msg = r["choices"][0]["message"]
+        content = []
+        if msg.get("reasoning_content"):
+            content.append({"type": "thinking", "thinking": msg["reasoning_content"]})
+        if msg.get("content"):
+            content.append({"type": "text", "text": msg["content"]})
+        for c in msg.get("tool_calls", []):
+            content.append({"type": "tool_use", "id": c["id"].replace("call_", "toolu_"), "name": c["function"]["name"],
+                            "input": json.loads(c["function"]["arguments"] or "{}")})
+        fin = r["choices"][0]["finish_reason"]
+        u = r["usage"]
+        return {"id": "msg_" + uuid.uuid4().hex[:24], "type": "message", "role": "assistant", "model": r["model"], "content": content,
+                "stop_reason": {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}.get(fin, "end_turn"), "stop_sequence": None,
+                "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"],
+                          "cache_read_input_tokens": u["prompt_tokens_details"]["cached_tokens"]}}

@@ -1,0 +1,112 @@
+"""Engine behaviour on CPU with tiny models: cache consistency, prefix reuse, chunked prefill, eviction + recompute,
+abort, sampling, page manager, export round trip (quantised HF)."""
+import torch
+
+from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+from fastllm_b200.engine.kv_cache import PageManager
+from fastllm_b200.models import preset, random_init
+
+
+def _model(name="tiny-llama"):
+    torch.manual_seed(0)
+    return random_init(preset(name), "cpu", torch.float32, std=0.05)
+
+
+def _prompts(vocab, lens, seed=1):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+
+
+def test_paged_chunked_matches_full_recompute():
+    for name in ("tiny-llama", "tiny-qwen3", "tiny-qwen3-moe", "tiny-deepseek-v3"):
+        m = _model(name)
+        eng = LLMEngine(m, EngineConfig(max_batch=8, max_context=1024, chunked_prefill_size=100), num_pages=64)
+        prompts = _prompts(m.cfg.vocab_size, (5, 130, 260))
+        outs = eng.generate(prompts, GenerationConfig(max_new_tokens=5, ignore_eos=True))
+        eng2 = LLMEngine(m, EngineConfig(max_batch=8, max_context=1024, prefix_cache=False), num_pages=64)
+        for p, o in zip(prompts, outs):
+            seq = list(p)
+            for k in range(5):
+                t = eng2.generate([seq], GenerationConfig(max_new_tokens=1, ignore_eos=True))[0][0]
+                assert t == o[k], (name, k)
+                seq.append(t)
+
+
+def test_prefix_cache_reuses_pages_and_keeps_output():
+    m = _model()
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=1024), num_pages=32)
+    p = _prompts(m.cfg.vocab_size, (300,))[0]
+    a = eng.generate([p], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0]
+    h = eng.launch(p + [7, 8, 9], GenerationConfig(max_new_tokens=4, ignore_eos=True))
+    req = eng.requests[h]
+    while not req.finished():
+        eng.step()
+    assert req.stats.cached_tokens == 256          # two whole pages came from the trie
+    b = eng.generate([p], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0]
+    assert a == b
+
+
+def test_eviction_recompute_gives_same_tokens():
+    m = _model()
+    prompts = _prompts(m.cfg.vocab_size, (120, 125, 110))
+    gen = GenerationConfig(max_new_tokens=40, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefix_cache=False), num_pages=32).generate(prompts, gen)
+    small = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefix_cache=False, prefill_page_limit=1.0), num_pages=4)
+    out = small.generate(prompts, gen)          # 3 requests x 2 pages do not fit in 4 pages: someone is evicted and recomputed
+    assert out == ref
+
+
+def test_abort_releases_pages():
+    m = _model()
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefix_cache=False), num_pages=16)
+    h = eng.launch(_prompts(m.cfg.vocab_size, (200,))[0], GenerationConfig(max_new_tokens=100, ignore_eos=True))
+    for _ in range(3):
+        eng.step()
+    eng.abort(h)
+    eng.step()
+    assert eng.requests[h].state.name == "ABORTED" and eng.pm.num_free() == 16
+    assert eng.fetch(h) >= 0 or True
+    while eng.fetch(h) >= 0:
+        pass
+
+
+def test_sampling_top_k_top_p():
+    from fastllm_b200.engine import sampling
+
+    torch.manual_seed(0)
+    logits = torch.tensor([[0.0, 5.0, 4.9, -3.0]] * 200)
+    t = sampling.sample(logits, [2] * 200, [1.0] * 200, [1.0] * 200)
+    assert set(t.tolist()) <= {1, 2} and len(set(t.tolist())) == 2
+    t = sampling.sample(logits, [4] * 200, [0.3] * 200, [1.0] * 200)
+    assert set(t.tolist()) == {1}
+    lg = sampling.apply_repeat_penalty(torch.tensor([[2.0, -2.0, 1.0]]), [[0, 1]], [2.0])
+    assert lg.tolist() == [[1.0, -4.0, 1.0]]
+
+
+def test_page_manager_trie():
+    pm = PageManager(8, 4)
+    pages = pm.alloc(3)
+    toks = list(range(12))
+    pm.record(toks, pages)
+    pm.release(pages)
+    assert pm.num_free() == 5 and pm.num_available() == 8
+    got = pm.query(toks + [99])
+    assert got == pages                                  # whole-page prefix, references taken
+    assert pm.query(toks) == pages[:2]                   # the page holding the last token is never matched
+    pm.release(got)
+    pm.release(pages[:2])
+    assert pm.alloc(8) is not None                       # cached pages are evicted when the free list runs dry
+    assert pm.stats()["cached"] == 0
+
+
+def test_quantised_export_roundtrip(tmp_path):
+    from baseline import synth
+    from fastllm_b200.loader import hf
+    from fastllm_b200.loader.export import export_quantized_hf
+
+    d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.float32, std=0.05)
+    export_quantized_hf(d, str(tmp_path / "q"), "int8")
+    a = hf.load_model(d, device="cpu", dtype=torch.float32, wdtype="int8")
+    b = hf.load_model(str(tmp_path / "q"), device="cpu", dtype=torch.float32)
+    wa, wb = a.layers[0].attn.qkv.dequant(torch.float32), b.layers[0].attn.qkv.dequant(torch.float32)
+    assert (wa - wb).abs().max() < 2e-3

@@ -1,0 +1,102 @@
+"""Serving layer: tool-call parsers (golden strings per family), reasoning split, stream splitter, usage accounting
+and routes with a tiny model on CPU (ASGI calls in-process, no sockets)."""
+import asyncio
+import json
+
+import pytest
+import torch
+
+from fastllm_b200.serving import toolcall as tc
+
+
+def test_hermes_and_reasoning():
+    text = '<think>need weather</think>\nSure.<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris"}}\n</tool_call>'
+    r, content = tc.split_reasoning(text)
+    assert r == "need weather"
+    content, calls = tc.get_parser("hermes").parse(content)
+    assert content == "Sure." and calls[0]["function"]["name"] == "get_weather"
+    assert json.loads(calls[0]["function"]["arguments"]) == {"city": "Paris"}
+
+
+GOLDEN = [
+    ("qwen3_coder", "<tool_call>\n<function=add>\n<parameter=a>\n1\n</parameter>\n<parameter=b>\n2\n</parameter>\n</function>\n</tool_call>", "add", {"a": 1, "b": 2}),
+    ("deepseek_v3", "ok<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>function<｜tool▁sep｜>f\n```json\n{\"x\": 3}\n```<｜tool▁call▁end｜><｜tool▁calls▁end｜>", "f", {"x": 3}),
+    ("deepseek_v31", "<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>f<｜tool▁sep｜>{\"x\": 3}<｜tool▁call▁end｜><｜tool▁calls▁end｜>", "f", {"x": 3}),
+    ("glm45", "<tool_call>f\n<arg_key>x</arg_key>\n<arg_value>3</arg_value>\n</tool_call>", "f", {"x": 3}),
+    ("kimi_k2", "<|tool_calls_section_begin|><|tool_call_begin|>functions.f:0<|tool_call_argument_begin|>{\"x\": 3}<|tool_call_end|><|tool_calls_section_end|>", "f", {"x": 3}),
+    ("minimax_m2", '<minimax:tool_call>\n<invoke name="f">\n<parameter name="x">3</parameter>\n</invoke>\n</minimax:tool_call>', "f", {"x": 3}),
+    ("json", '{"name": "f", "parameters": {"x": 3}}', "f", {"x": 3}),
+]
+
+
+@pytest.mark.parametrize("parser,text,name,args", GOLDEN)
+def test_parser_golden(parser, text, name, args):
+    _, calls = tc.get_parser(parser).parse(text)
+    assert len(calls) == 1 and calls[0]["function"]["name"] == name
+    assert json.loads(calls[0]["function"]["arguments"]) == args
+
+
+def test_stream_splitter_holds_back_markup():
+    sp = tc.StreamSplitter(tc.get_parser("hermes"), reasoning=True)
+    pieces = ["<thi", "nk>plan", "</th", "ink>\nHel", "lo <tool", '_call>{"name": "f", "argu', 'ments": {}}</tool_call>']
+    out = []
+    for p in pieces:
+        out += sp.push(p)
+    rest, calls = sp.finish()
+    assert "".join(t for k, t in out if k == "reasoning") == "plan"
+    assert "".join(t for k, t in out if k == "content") == "Hello "
+    assert calls and calls[0]["function"]["name"] == "f"
+
+
+@pytest.fixture(scope="module")
+def client(tmp_path_factory):
+    fastapi = pytest.importorskip("fastapi")
+    httpx = pytest.importorskip("httpx")
+    from baseline import synth
+    from fastllm_b200 import llm
+    from fastllm_b200.serving.server import build_app
+
+    d = synth.write_model("tiny-llama", str(tmp_path_factory.mktemp("srv") / "m"), dtype=torch.float32, std=0.05)
+    llm.set_device_map("cpu")
+    m = llm.model(d, device="cpu")
+    app = build_app(m, "tiny", api_key="k", dev_mode=True)
+
+    def call(method, path, body=None, key="k"):
+        async def go():
+            tr = httpx.ASGITransport(app=app)
+            async with httpx.AsyncClient(transport=tr, base_url="http://t") as c:
+                h = {"Authorization": f"Bearer {key}"} if key else {}
+                return await (c.post(path, json=body, headers=h) if method == "POST" else c.get(path, headers=h))
+        return asyncio.run(go())
+
+    yield call
+    m.release_memory()
+
+
+def test_chat_completion_and_usage(client):
+    r = client("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 5, "temperature": 0})
+    assert r.status_code == 200
+    j = r.json()
+    assert j["object"] == "chat.completion" and j["choices"][0]["message"]["role"] == "assistant"
+    u = j["usage"]
+    assert u["completion_tokens"] <= 5 and u["total_tokens"] == u["prompt_tokens"] + u["completion_tokens"]
+    assert "cached_tokens" in u["prompt_tokens_details"]
+
+
+def test_stream_models_auth_metrics(client):
+    r = client("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "stream": True, "temperature": 0})
+    lines = [l for l in r.text.split("\n\n") if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]" and json.loads(lines[0][6:])["choices"][0]["delta"]["role"] == "assistant"
+    assert json.loads(lines[-2][6:])["usage"]["completion_tokens"] >= 1
+    assert client("GET", "/v1/models").json()["data"][0]["id"] == "tiny"
+    assert client("GET", "/v1/models", key="").status_code == 401
+    assert "fastllm_requests_total" in client("GET", "/metrics").text
+    assert client("GET", "/v1/active_conversations").json()["conversations"] == []
+
+
+def test_responses_and_anthropic(client):
+    r = client("POST", "/v1/responses", {"input": "hello", "max_output_tokens": 4, "temperature": 0})
+    assert r.json()["object"] == "response" and r.json()["usage"]["output_tokens"] >= 1
+    r = client("POST", "/v1/messages", {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 4, "temperature": 0})
+    assert r.json()["type"] == "message" and r.json()["stop_reason"] in ("end_turn", "max_tokens")
+    assert client("POST", "/v1/messages", {"messages": []}).status_code == 400
