@@ -1,0 +1,333 @@
+// Weight-only-quantised small-M GEMM for sm_100a:  Y[M,N] = X[M,K] * dequant(Wq)[N,K]^T  (+ bias, residual, SwiGLU)
+//
+// Formats (reference numerics, include/fastllm.h:239-306):
+//   int8   per-output-channel asymmetric      w = scale[n] * (q - zero[n])
+//   int4g  group-wise asymmetric, 2 per byte, first value in the HIGH nibble      w = min[n,g] + scale[n,g] * q
+//   fp8    FP8-E4M3 with one fp32 scale per 128x128 block                          w = scale[n/128,k/128] * q
+// The reference serves these with CUDA-core GEMV kernels for small batches and dequant-to-fp16 + cublasGemmEx
+// otherwise (src/devices/cuda/linear/fastllm-linear-int8.cu, -int4group.cu:1919-2054, -fp8.cu:1778-1868).
+//
+// Here: same swap-AB tcgen05 kernel as the dense decode GEMM, with a dequant stage between TMA and MMA.
+//   warp 0     TMA: packed weight tile [128 n x 64 k] (4 KB int4 / 8 KB int8,fp8) + activation tile -> raw ring
+//   warps 2-5  dequant: raw -> 16-bit in the 128-byte-swizzled K-major layout UMMA reads (int -> fp16 through the
+//              0x6400 "1024 + q" bit trick, FP8 through cvt.f16x2.e4m3x2), group scale/min applied here,
+//              per-channel int8 scale applied in the epilogue (q - zero is exact in fp16)
+//   warp 1     UMMA: A = de-quantised weights in the activations' 16-bit type, B = activations, fp32 accumulate
+//   then the shared cluster split-K reduce + epilogue (gemm_smallm.cuh)
+// Weight bytes cross HBM once, in packed form: the kernel is bound by 0.5 / 1 byte per weight.
+#include "gemm_smallm.cuh"
+#include "tmap.h"
+
+FB_DEFINE_ERROR_API(gemm_quant)
+
+namespace fb {
+
+constexpr int KID_GEMM_QUANT = 3;
+enum QMode : int { Q_INT8 = 1, Q_INT4G = 2, Q_FP8 = 3 };
+
+struct QuantParams {
+  const float* scale;     // int8: [N]; fp8: [ceil(N/128), kb128]; int4g: float2 (scale, min) [groups, N]
+  const float* zero;      // int8: [N]
+  int group_k;            // int4g: k elements per group (multiple of 64); fp8: 128
+  int groups;             // int4g: groups per row; fp8: scale columns
+};
+
+template <int MPAD, int QM>
+struct QuantCfg {
+  static constexpr int RAW_BYTES = QM == Q_INT4G ? 128 * 32 : 128 * 64;
+  static constexpr int B_BYTES = MPAD * 128;
+  static constexpr int STAGE_BYTES = RAW_BYTES + B_BYTES;            // bytes TMA delivers per stage
+  static constexpr int PITCH = (STAGE_BYTES + 1023) / 1024 * 1024;   // stage pitch: keeps the swizzled activation tile 1024-aligned
+  static constexpr int DQ_SLOTS = 3;
+  static constexpr int DQ_BYTES = 128 * 128;
+  static constexpr int RED_BYTES = MPAD * 128 * 4;
+  static constexpr int BUDGET = 196 * 1024 - DQ_SLOTS * DQ_BYTES;
+  static constexpr int STAGES_RAW = BUDGET / PITCH > 12 ? 12 : BUDGET / PITCH;
+  static constexpr int STAGES = STAGES_RAW < 2 ? 2 : STAGES_RAW;
+  static constexpr int PIPE_BYTES = DQ_SLOTS * DQ_BYTES + STAGES * PITCH;
+  static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
+  static constexpr int SMEM_BYTES = BODY_BYTES + 512 + 1024;
+  static constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
+};
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+// weights are produced in the activations' own 16-bit type (both UMMA operands share one format)
+template <bool BF16>
+__device__ __forceinline__ uint32_t out16(__half2 h) {
+  if (!BF16) return h2_as_u32(h);
+  const float2 f = __half22float2(h);
+  return pack_bf16(f.x, f.y);
+}
+
+// two unsigned bytes (values < 1024) -> half2 (lo, hi) exactly, via the 0x6400 | v == 1024 + v representation
+__device__ __forceinline__ __half2 u8x2_to_h2(uint32_t lo, uint32_t hi, __half2 sub) {
+  const uint32_t bits = 0x64006400u | lo | (hi << 16);
+  return __hsub2(*reinterpret_cast<const __half2*>(&bits), sub);
+}
+
+template <int MPAD, bool BF16, int QM>
+__global__ void __launch_bounds__(192, 1)
+gemm_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
+                  const QuantParams qp) {
+  using Cfg = QuantCfg<MPAD, QM>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* dq = smem;                                            // DQ_SLOTS x 16 KB, 1024-aligned
+  uint8_t* stages = smem + Cfg::DQ_SLOTS * Cfg::DQ_BYTES;        // per stage: activation tile first (1024-aligned), raw weights after
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* full_bar = bars;                       // [STAGES]   TMA landed (raw + X)
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;    // [STAGES]   1 UMMA commit + 128 dequant arrivals
+  uint64_t* dq_full = empty_bar + Cfg::STAGES;     // [DQ_SLOTS] 128 dequant arrivals
+  uint64_t* dq_empty = dq_full + Cfg::DQ_SLOTS;    // [DQ_SLOTS] UMMA commit
+  uint64_t* accum_bar = dq_empty + Cfg::DQ_SLOTS;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  constexpr int PITCH = Cfg::PITCH;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = (int)cluster_ctarank();
+  const int nsplit = (int)cluster_nctarank();
+  const int n_tile = blockIdx.y;
+  const int kb0 = split * p.kb_per_split;
+  int kb_cnt = p.kb_total - kb0;
+  if (kb_cnt > p.kb_per_split) kb_cnt = p.kb_per_split;
+  if (kb_cnt < 0) kb_cnt = 0;
+  bool dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 129); }
+    for (int s = 0; s < Cfg::DQ_SLOTS; ++s) { mbar_init(&dq_full[s], 128); mbar_init(&dq_empty[s], 1); }
+    mbar_init(accum_bar, 1);
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      constexpr int KBYTES = QM == Q_INT4G ? 32 : 64;            // packed bytes per 64-wide k block
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_QUANT, 1)) break;
+        uint8_t* xb = stages + s * PITCH;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(xb, &tmX, &full_bar[s], (kb0 + i) * 64, 0, pol_x);
+        tma_load_2d_hint(xb + Cfg::B_BYTES, &tmW, &full_bar[s], (kb0 + i) * KBYTES, n_tile * 128, pol_w);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES, t = i % Cfg::DQ_SLOTS;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, tph = (uint32_t)(i / Cfg::DQ_SLOTS) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_QUANT, 6)) break;
+        if (!mbar_wait(&dq_full[t], tph, dead, KID_GEMM_QUANT, 2)) break;
+        tc_fence_after_sync();
+        const uint64_t da = make_smem_desc(smem_u32(dq + t * Cfg::DQ_BYTES), 16, 1024, SWZ_128B);
+        const uint64_t db = make_smem_desc(smem_u32(stages + s * PITCH), 16, 1024, SWZ_128B);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, p.idesc, (i | k) != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+        umma_commit(&dq_empty[t]);
+      }
+      umma_commit(accum_bar);
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    const int tid = threadIdx.x - 64;                 // 0..127
+    // ------------------------------ dequant stage ------------------------------
+    for (int i = 0; i < kb_cnt; ++i) {
+      const int s = i % Cfg::STAGES, t = i % Cfg::DQ_SLOTS;
+      const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, tph = (uint32_t)(i / Cfg::DQ_SLOTS) & 1u;
+      mbar_wait(&full_bar[s], ph, dead, KID_GEMM_QUANT, 4);
+      mbar_wait(&dq_empty[t], tph ^ 1u, dead, KID_GEMM_QUANT, 5);
+      const uint8_t* raw = stages + s * PITCH + Cfg::B_BYTES;
+      uint8_t* out = dq + t * Cfg::DQ_BYTES;
+      const int kb = kb0 + i;
+      if (QM == Q_INT4G) {
+        const int g = (kb * 64) / qp.group_k;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+          const int u = tid + 128 * it, row = u >> 1, ch = u & 1;
+          const int n = n_tile * 128 + row;
+          float2 sm = make_float2(0.f, 0.f);
+          if (n < p.N) sm = reinterpret_cast<const float2*>(qp.scale)[(size_t)g * p.N + n];
+          const __half2 sc = __float2half2_rn(sm.x), mn = __float2half2_rn(sm.y);
+          const __half2 k1024 = __float2half2_rn(1024.f);
+          const uint4 w = *reinterpret_cast<const uint4*>(raw + row * 32 + ch * 16);
+          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {            // one 32-bit word = 8 values = one 16-byte chunk of fp16
+            const uint32_t x = ws[j];
+            uint32_t o[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b) {
+              const uint32_t byte = (x >> (8 * b)) & 0xFFu;
+              const __half2 v = u8x2_to_h2(byte >> 4, byte & 0xFu, k1024);      // first value = high nibble
+              o[b] = out16<BF16>(__hfma2(v, sc, mn));
+            }
+            const int chunk = ch * 4 + j;
+            *reinterpret_cast<uint4*>(out + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+      } else {
+        float bscale = 1.f;
+        if (QM == Q_FP8) bscale = qp.scale[(size_t)n_tile * qp.groups + (kb * 64) / 128];
+        const __half2 bs2 = __float2half2_rn(bscale);
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int u = tid + 128 * it, row = u >> 2, ch = u & 3;
+          const int n = n_tile * 128 + row;
+          const uint4 w = *reinterpret_cast<const uint4*>(raw + row * 64 + ch * 16);
+          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+          uint32_t o[8];
+          if (QM == Q_INT8) {
+            const float z = n < p.N ? qp.zero[n] : 0.f;
+            const __half2 sub = __float2half2_rn(1024.f + z);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              o[2 * j] = out16<BF16>(u8x2_to_h2(ws[j] & 0xFFu, (ws[j] >> 8) & 0xFFu, sub));
+              o[2 * j + 1] = out16<BF16>(u8x2_to_h2((ws[j] >> 16) & 0xFFu, ws[j] >> 24, sub));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              uint32_t lo, hi;
+              asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}\n"
+                  : "=r"(lo), "=r"(hi) : "r"(ws[j]));
+              o[2 * j] = out16<BF16>(__hmul2(*reinterpret_cast<__half2*>(&lo), bs2));
+              o[2 * j + 1] = out16<BF16>(__hmul2(*reinterpret_cast<__half2*>(&hi), bs2));
+            }
+          }
+          const int c0 = ch * 2;
+          *reinterpret_cast<uint4*>(out + row * 128 + ((c0 ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4*>(out + row * 128 + (((c0 + 1) ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&dq_full[t]);
+      mbar_arrive(&empty_bar[s]);
+    }
+    // ------------------------------ epilogue: TMEM -> fp32 partial tile ------------------------------
+    float* P = reinterpret_cast<float*>(smem);
+    const int n_local = q * 32 + lane;
+    float row_scale = 1.f;
+    if (QM == Q_INT8) { const int n = n_tile * 128 + n_local; row_scale = n < p.N ? qp.scale[n] : 0.f; }
+    if (kb_cnt > 0) {
+      mbar_wait(accum_bar, 0, dead, KID_GEMM_QUANT, 3);
+      tc_fence_after_sync();
+      constexpr int CH = MPAD < 32 ? MPAD : 32;
+#pragma unroll 1
+      for (int c0 = 0; c0 < MPAD; c0 += CH) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if (CH == 32) tmem_ld_32x32b_x32(taddr, r); else tmem_ld_32x32b_x16(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; ++j) P[(c0 + j) * 128 + n_local] = __uint_as_float(r[j]) * row_scale;
+      }
+    } else {
+      for (int j = 0; j < MPAD; ++j) P[j * 128 + n_local] = 0.f;
+    }
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  smallm_reduce_store<BF16>(p, smem, split, nsplit, n_tile);
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_gemm_pick_split(int M, int N, int K, int slots);
+
+template <int MPAD, bool BF16, int QM>
+static cudaError_t launch_quant(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const QuantParams& qp,
+                                int nsplit, int n_tiles, cudaStream_t stream) {
+  using Cfg = QuantCfg<MPAD, QM>;
+  auto kern = gemm_quant_kernel<MPAD, BF16, QM>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, qp);
+}
+
+// qmode: 1 = int8 (Wq uint8 [N,K], scale [N], zero [N]), 2 = int4g (Wq uint8 [N,K/2], scale = float2 (scale,min) [groups,N]),
+// 3 = fp8 block 128 (Wq e4m3 [N,K], scale [ceil(N/128), ceil(K/128)]).  X dtype: 0 = fp16, 1 = bf16.  M <= 256.
+extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, const float* zero, void* out, const void* bias,
+                             const void* residual, int M, int N, int K, int ldx, int ld_out, int ld_res, int dtype, int qmode,
+                             int group_k, int flags, int nsplit, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 256 || K % 64 != 0 || N % 8 != 0 || (dtype != 0 && dtype != 1)) return -1;
+  if (qmode == Q_INT4G && (group_k <= 0 || group_k % 64 != 0 || K % group_k != 0)) return -1;
+  if (qmode == Q_FP8 && K % 128 != 0) return -1;
+  if ((flags & GEMM_SWIGLU) && (N % 128 != 0)) return -1;
+  GemmParams p;
+  p.out = out; p.bias = bias; p.residual = residual;
+  p.M = M; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res;
+  p.kb_total = K / 64; p.flags = flags;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0;
+  for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
+  QuantParams qp;
+  qp.scale = scale; qp.zero = zero;
+  qp.group_k = qmode == Q_INT4G ? group_k : 128;
+  qp.groups = qmode == Q_INT4G ? K / group_k : (K + 127) / 128;
+  const bool bf16 = dtype == 1;
+  const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (nsplit <= 0) nsplit = fb_gemm_pick_split(M, N, K, sm_count);
+  if (nsplit != 1 && nsplit != 2 && nsplit != 4 && nsplit != 8) return -1;
+  p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
+  if (qmode == Q_INT4G) {
+    // a cluster rank must start on a group boundary only in the sense that a k block never straddles groups: group_k % 64 == 0
+  }
+  p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
+  const int kbytes = qmode == Q_INT4G ? K / 2 : K;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, Wq, N, kbytes, kbytes, 128, qmode == Q_INT4G ? 32 : 64, 1, 0)) return -2;
+  if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
+  const int n_tiles = (N + 127) / 128;
+#define FB_Q2(MP, QMV)                                                                                   \
+  return (int)(bf16 ? launch_quant<MP, true, QMV>(tmW, tmX, p, qp, nsplit, n_tiles, stream)               \
+                    : launch_quant<MP, false, QMV>(tmW, tmX, p, qp, nsplit, n_tiles, stream));
+#define FB_Q(MP)                                                                                          \
+  { if (qmode == Q_INT8) { FB_Q2(MP, Q_INT8) } else if (qmode == Q_INT4G) { FB_Q2(MP, Q_INT4G) } else if (qmode == Q_FP8) { FB_Q2(MP, Q_FP8) } else return -1; }
+  switch (mpad) {
+    case 16: FB_Q(16)
+    case 32: FB_Q(32)
+    case 64: FB_Q(64)
+    case 128: FB_Q(128)
+    default: FB_Q(256)
+  }
+#undef FB_Q
+#undef FB_Q2
+}

@@ -49,6 +49,72 @@ struct SmallMCfg {
   static constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
 };
 
+// Cross-CTA reduction over the k splits + epilogue.  Every CTA of the cluster holds its fp32 partial tile P[token][n]
+// at `smem`; this CTA reduces and stores its own column slice (bias -> SwiGLU -> residual -> store / scatter).
+template <bool BF16>
+__device__ __forceinline__ void smallm_reduce_store(const GemmParams& p, uint8_t* smem, int split, int nsplit, int n_tile) {
+  {
+    const bool swiglu = (p.flags & GEMM_SWIGLU) != 0;
+    const int outw = swiglu ? 64 : 128;
+    const int per = outw / nsplit;           // columns owned by this CTA (>= 8)
+    const int vec_per_row = per >> 2;
+    const int items = p.M * vec_per_row;
+    const uint32_t P_addr = smem_u32(smem);
+    for (int it = threadIdx.x; it < items; it += blockDim.x) {
+      const int j = it / vec_per_row;
+      const int c = split * per + (it - j * vec_per_row) * 4;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), acc2 = acc;
+      for (int s = 0; s < nsplit; ++s) {
+        const uint32_t ra = mapa_u32(P_addr + (uint32_t)(j * 128 + c) * 4u, (uint32_t)s);
+        float4 v = ld_dsmem_f4(ra);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        if (swiglu) {
+          float4 u = ld_dsmem_f4(ra + 64 * 4);
+          acc2.x += u.x; acc2.y += u.y; acc2.z += u.z; acc2.w += u.w;
+        }
+      }
+      int n_out;
+      if (swiglu) {
+        n_out = n_tile * 64 + c;
+        if (p.flags & GEMM_BIAS) {
+          const uint32_t* bg = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_tile * 128 + c);
+          float2 b0 = unpack_16<BF16>(bg[0]), b1 = unpack_16<BF16>(bg[1]);
+          float2 u0 = unpack_16<BF16>(bg[32]), u1 = unpack_16<BF16>(bg[33]);
+          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+          acc2.x += u0.x; acc2.y += u0.y; acc2.z += u1.x; acc2.w += u1.y;
+        }
+        acc.x = silu_f(acc.x) * acc2.x; acc.y = silu_f(acc.y) * acc2.y;
+        acc.z = silu_f(acc.z) * acc2.z; acc.w = silu_f(acc.w) * acc2.w;
+        if (n_out >= (p.N >> 1)) continue;
+      } else {
+        n_out = n_tile * 128 + c;
+        if (n_out >= p.N) continue;
+        if (p.flags & GEMM_BIAS) {
+          const uint32_t* bp = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_out);
+          float2 b0 = unpack_16<BF16>(bp[0]), b1 = unpack_16<BF16>(bp[1]);
+          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+        }
+      }
+      if (p.flags & GEMM_RESIDUAL) {
+        const uint2 rv = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)j * p.ld_res + n_out);
+        float2 r0 = unpack_16<BF16>(rv.x), r1 = unpack_16<BF16>(rv.y);
+        acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
+      }
+      if (p.scatter_tp > 0) {
+        float* dst = p.scatter_out[j / p.scatter_rows] + ((size_t)p.scatter_rank * p.M + j) * p.ld_out + n_out;
+        *reinterpret_cast<float4*>(dst) = acc;
+      } else if (p.flags & GEMM_OUT_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)j * p.ld_out + n_out) = acc;
+      } else {
+        uint2 o;
+        o.x = pack_16<BF16>(acc.x, acc.y);
+        o.y = pack_16<BF16>(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)j * p.ld_out + n_out) = o;
+      }
+    }
+  }
+}
+
 // Body of the small-M kernel.  Returns with the output tile written and every cluster peer done reading this
 // CTA's shared memory; the caller still owns TMEM (returned in tmem_base_out) and must release it from warp 1.
 template <int MPAD, bool BF16, int OCC = 1>
@@ -143,67 +209,7 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
   tc_fence_before_sync();
   cluster_sync_all();
 
-  // ---- cross-CTA reduction over the k splits + epilogue; this CTA owns a column slice of the tile ----
-  {
-    const bool swiglu = (p.flags & GEMM_SWIGLU) != 0;
-    const int outw = swiglu ? 64 : 128;
-    const int per = outw / nsplit;           // columns owned by this CTA (>= 8)
-    const int vec_per_row = per >> 2;
-    const int items = p.M * vec_per_row;
-    const uint32_t P_addr = smem_u32(smem);
-    for (int it = threadIdx.x; it < items; it += blockDim.x) {
-      const int j = it / vec_per_row;
-      const int c = split * per + (it - j * vec_per_row) * 4;
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f), acc2 = acc;
-      for (int s = 0; s < nsplit; ++s) {
-        const uint32_t ra = mapa_u32(P_addr + (uint32_t)(j * 128 + c) * 4u, (uint32_t)s);
-        float4 v = ld_dsmem_f4(ra);
-        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-        if (swiglu) {
-          float4 u = ld_dsmem_f4(ra + 64 * 4);
-          acc2.x += u.x; acc2.y += u.y; acc2.z += u.z; acc2.w += u.w;
-        }
-      }
-      int n_out;
-      if (swiglu) {
-        n_out = n_tile * 64 + c;
-        if (p.flags & GEMM_BIAS) {
-          const uint32_t* bg = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_tile * 128 + c);
-          float2 b0 = unpack_16<BF16>(bg[0]), b1 = unpack_16<BF16>(bg[1]);
-          float2 u0 = unpack_16<BF16>(bg[32]), u1 = unpack_16<BF16>(bg[33]);
-          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
-          acc2.x += u0.x; acc2.y += u0.y; acc2.z += u1.x; acc2.w += u1.y;
-        }
-        acc.x = silu_f(acc.x) * acc2.x; acc.y = silu_f(acc.y) * acc2.y;
-        acc.z = silu_f(acc.z) * acc2.z; acc.w = silu_f(acc.w) * acc2.w;
-        if (n_out >= (p.N >> 1)) continue;
-      } else {
-        n_out = n_tile * 128 + c;
-        if (n_out >= p.N) continue;
-        if (p.flags & GEMM_BIAS) {
-          const uint32_t* bp = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_out);
-          float2 b0 = unpack_16<BF16>(bp[0]), b1 = unpack_16<BF16>(bp[1]);
-          acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
-        }
-      }
-      if (p.flags & GEMM_RESIDUAL) {
-        const uint2 rv = *reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p.residual) + (size_t)j * p.ld_res + n_out);
-        float2 r0 = unpack_16<BF16>(rv.x), r1 = unpack_16<BF16>(rv.y);
-        acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
-      }
-      if (p.scatter_tp > 0) {
-        float* dst = p.scatter_out[j / p.scatter_rows] + ((size_t)p.scatter_rank * p.M + j) * p.ld_out + n_out;
-        *reinterpret_cast<float4*>(dst) = acc;
-      } else if (p.flags & GEMM_OUT_F32) {
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)j * p.ld_out + n_out) = acc;
-      } else {
-        uint2 o;
-        o.x = pack_16<BF16>(acc.x, acc.y);
-        o.y = pack_16<BF16>(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)j * p.ld_out + n_out) = o;
-      }
-    }
-  }
+  smallm_reduce_store<BF16>(p, smem, split, nsplit, n_tile);
   cluster_sync_all();   // peers may still be reading this CTA's partial tile
   tmem_base_out = tmem_base;
 }

@@ -1,10 +1,70 @@
 """Weight-only-quantised and block-scaled FP8 GEMM dispatch (CUDA).
 
-``linear_quant`` returns ``None`` when no fused kernel covers the (format, shape) pair; the caller then
-dequantises and runs the dense tcgen05 GEMM.
+``linear_quant`` runs ``csrc/gemm_quant.cu`` (packed weights stream through TMA, dequant in shared memory, tcgen05
+MMA) for up to 256 tokens per launch; larger token counts are processed in 256-row chunks up to a limit, beyond which
+the caller de-quantises once and uses the dense prefill GEMM (``None`` is returned).
 """
 from __future__ import annotations
 
+import ctypes
+
+import torch
+
+from . import _lib
+from .basic import GEMM_BIAS, GEMM_OUT_F32, GEMM_RESIDUAL, GEMM_SWIGLU, _ptr, _stream, dtype_code
+
+P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
+_lib.register_sigs({"fb_gemm_quant": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P]}, ["gemm_quant"])
+
+_QMODE = {"int8": 1, "int4g": 2, "fp8": 3}
+MAX_CHUNKED_TOKENS = 1024
+
+
+def _kernel_tensors(lw):
+    """Scale tensors in the layout the kernel reads (built once per weight)."""
+    if lw._dq is None:
+        if lw.kind == "int8":
+            lw._dq = (lw.scale.float().contiguous(), lw.zero.float().contiguous())
+        elif lw.kind == "int4g":
+            sm = torch.stack([lw.scale.float(), lw.zero.float()], dim=-1)          # [N, groups, 2]
+            lw._dq = (sm.permute(1, 0, 2).contiguous(), None)                      # [groups, N, 2]
+        else:
+            lw._dq = (lw.scale.float().contiguous(), None)
+    return lw._dq
+
 
 def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
-    return None
+    if lw.kind not in _QMODE or x.dtype not in (torch.float16, torch.bfloat16):
+        return None
+    lead = x.shape[:-1]
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    M, K = x2.shape
+    N = lw.n
+    if M > MAX_CHUNKED_TOKENS or K % 64 != 0 or N % 8 != 0:
+        return None
+    if lw.kind == "int4g" and (lw.group % 64 != 0 or K % lw.group != 0):
+        return None
+    if lw.kind == "fp8" and K % 128 != 0:
+        return None
+    if swiglu and (not lw.interleaved or N % 128 != 0):
+        return None
+    scale, zero = _kernel_tensors(lw)
+    n_out = N // 2 if swiglu else N
+    out = torch.empty((M, n_out), device=x.device, dtype=torch.float32 if out_f32 else x.dtype)
+    res2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
+    flags = (GEMM_BIAS if lw.bias is not None else 0) | (GEMM_RESIDUAL if residual is not None else 0) | \
+            (GEMM_SWIGLU if swiglu else 0) | (GEMM_OUT_F32 if out_f32 else 0)
+    bias = lw.bias
+    if bias is not None and bias.dtype != x.dtype:
+        bias = bias.to(x.dtype)
+    lib = _lib.kernels()
+    for m0 in range(0, M, 256):
+        m1 = min(M, m0 + 256)
+        rc = lib.fb_gemm_quant(_ptr(x2[m0:m1]), _ptr(lw.w), _ptr(scale), _ptr(zero), _ptr(out[m0:m1]), _ptr(bias),
+                               _ptr(res2[m0:m1]) if res2 is not None else _ptr(None), m1 - m0, N, K, x2.stride(0), out.stride(0),
+                               res2.stride(0) if res2 is not None else 0, dtype_code(x.dtype), _QMODE[lw.kind], lw.group or 0, flags, 0,
+                               _stream())
+        _lib.check(rc, "fb_gemm_quant")
+    return out.reshape(*lead, n_out)

@@ -179,3 +179,35 @@ def test_qkv_post(mode, rot, qknorm):
     _close(q_out.cpu(), q_ref, 3e-2, 2e-2, "q")
     _close(kp2.cpu(), kp, 3e-2, 2e-2, "k pool")
     _close(vp2.cpu(), vp, 0, 0, "v pool")
+
+
+@pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (13, 384, 1024), (64, 4096, 4096), (200, 1024, 2048), (300, 512, 512)])
+def test_gemm_quant(kind, dtype, M, N, K):
+    from fastllm_b200.ops import quant
+
+    torch.manual_seed(8)
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(dtype)
+    lw = quant.LinearWeight.from_dense(w, kind, act_dtype=dtype)
+    assert lw.kind != "dense"
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(dtype)
+    ref = B.linear_ref(x, lw.dequant(torch.float32))
+    y = lw(x)
+    _close(y, ref, 4e-2, 3e-2, f"quant gemm {kind} {M}x{N}x{K}")
+
+
+def test_gemm_quant_epilogues():
+    from fastllm_b200.ops import quant
+
+    torch.manual_seed(9)
+    M, N, K, dt = 48, 1024, 1024, torch.bfloat16
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(dt)
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(dt)
+    bias = torch.randn(N, device=DEV).to(dt)
+    res = torch.randn(M, N // 2, device=DEV).to(dt)
+    for kind in ("int8", "int4g128", "fp8"):
+        lw = quant.LinearWeight.from_dense(w, kind, bias=bias, interleaved=True, act_dtype=dt)
+        y = lw(x, residual=res, swiglu=True)
+        ref = B.linear_ref(x, lw.dequant(torch.float32), bias, res, swiglu=True)
+        _close(y, ref, 5e-2, 4e-2, f"quant epilogue {kind}")
