@@ -396,7 +396,7 @@ extern "C" int fb_gemm_ar_norm(const void* X, const void* W, const void* bias, i
   GemmParams g;
   g.out = (uint8_t*)arena_local + off_part; g.bias = bias; g.residual = nullptr;
   g.M = M; g.N = N; g.K = K; g.ld_out = N; g.ld_res = 0;
-  g.scatter_tp = tp; g.scatter_rows = (M + tp - 1) / tp; g.scatter_rank = rank;
+  g.scatter_tp = tp; g.scatter_rows = (M + tp - 1) / tp; g.scatter_rank = rank; g.w_row0 = 0; g.x_row0 = 0;
   for (int i = 0; i < 8; ++i) g.scatter_out[i] = i < tp ? reinterpret_cast<float*>((uint8_t*)peers[i] + off_part) : nullptr;
   g.kb_total = K / 64; g.kb_per_split = (g.kb_total + nsplit - 1) / nsplit;
   g.flags = GEMM_OUT_F32 | (bias ? GEMM_BIAS : 0);

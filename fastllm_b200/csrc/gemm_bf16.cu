@@ -278,7 +278,7 @@ extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void
   p.M = M; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res;
   p.kb_total = K / 64;
   p.flags = flags;
-  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0; p.w_row0 = 0; p.x_row0 = 0;
   for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
   const bool bf16 = dtype == 1;
   if (M <= 256) {

@@ -66,9 +66,8 @@ __device__ __forceinline__ __half2 u8x2_to_h2(uint32_t lo, uint32_t hi, __half2 
 }
 
 template <int MPAD, bool BF16, int QM>
-__global__ void __launch_bounds__(192, 1)
-gemm_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
-                  const QuantParams qp) {
+__device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
+                                                  const QuantParams& qp) {
   using Cfg = QuantCfg<MPAD, QM>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -118,8 +117,8 @@ gemm_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_QUANT, 1)) break;
         uint8_t* xb = stages + s * PITCH;
         mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-        tma_load_2d_hint(xb, &tmX, &full_bar[s], (kb0 + i) * 64, 0, pol_x);
-        tma_load_2d_hint(xb + Cfg::B_BYTES, &tmW, &full_bar[s], (kb0 + i) * KBYTES, n_tile * 128, pol_w);
+        tma_load_2d_hint(xb, &tmX, &full_bar[s], (kb0 + i) * 64, p.x_row0, pol_x);
+        tma_load_2d_hint(xb + Cfg::B_BYTES, &tmW, &full_bar[s], (kb0 + i) * KBYTES, p.w_row0 + n_tile * 128, pol_w);
       }
     }
     __syncwarp();
@@ -246,6 +245,40 @@ gemm_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+template <int MPAD, bool BF16, int QM>
+__global__ void __launch_bounds__(192, 1)
+gemm_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
+                  const QuantParams qp) {
+  gemm_quant_device<MPAD, BF16, QM>(tmW, tmX, p, qp);
+}
+
+// Grouped (mixture-of-experts) variant: blockIdx.z = expert * chunks + chunk; weights / scales are stacked per expert.
+struct QuantGroupInfo {
+  const int* counts; const int* offsets;
+  int rows_per_chunk, chunks, n_rows_w;
+  long long scale_stride_e, zero_stride_e;      // floats per expert
+};
+
+template <int MPAD, bool BF16, int QM>
+__global__ void __launch_bounds__(192, 1)
+moe_grouped_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
+                         const QuantParams qbase, const QuantGroupInfo gi) {
+  const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  const int cnt = gi.counts[e];
+  const int row0 = chunk * gi.rows_per_chunk;
+  if (row0 >= cnt) return;
+  GemmParams p = base;
+  const int seg = gi.offsets[e] + row0;
+  p.M = cnt - row0 < gi.rows_per_chunk ? cnt - row0 : gi.rows_per_chunk;
+  p.x_row0 = seg;
+  p.w_row0 = e * gi.n_rows_w;
+  p.out = reinterpret_cast<uint16_t*>(base.out) + (size_t)seg * base.ld_out;
+  QuantParams qp = qbase;
+  qp.scale = qbase.scale + (size_t)e * gi.scale_stride_e;
+  if (qbase.zero != nullptr) qp.zero = qbase.zero + (size_t)e * gi.zero_stride_e;
+  gemm_quant_device<MPAD, BF16, QM>(tmW, tmX, p, qp);
+}
+
 }  // namespace fb
 
 using namespace fb;
@@ -290,7 +323,7 @@ extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, 
   p.out = out; p.bias = bias; p.residual = residual;
   p.M = M; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res;
   p.kb_total = K / 64; p.flags = flags;
-  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0; p.w_row0 = 0; p.x_row0 = 0;
   for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
   QuantParams qp;
   qp.scale = scale; qp.zero = zero;
@@ -330,4 +363,79 @@ extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, 
   }
 #undef FB_Q
 #undef FB_Q2
+}
+
+template <int MPAD, bool BF16, int QM>
+static cudaError_t launch_grouped_quant(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const QuantParams& qp,
+                                        const QuantGroupInfo& gi, int nsplit, int n_tiles, int nz, cudaStream_t stream) {
+  using Cfg = QuantCfg<MPAD, QM>;
+  auto kern = moe_grouped_quant_kernel<MPAD, BF16, QM>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, nz);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, qp, gi);
+}
+
+// Grouped quantised expert GEMM over the expert-sorted buffer; stacked Wq [E_local * N, K bytes], stacked scales.
+extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const float* scale, const float* zero, void* out,
+                                         const int* counts, const int* offsets, int rows_cap, int E_local, int N, int K, int ld_out,
+                                         int max_rows_per_expert, int dtype, int qmode, int group_k, int flags, void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (E_local <= 0 || rows_cap <= 0) return 0;
+  if (K % 64 != 0 || N % 128 != 0 || (dtype != 0 && dtype != 1)) return -1;
+  if (qmode == Q_INT4G && (group_k <= 0 || group_k % 64 != 0 || K % group_k != 0)) return -1;
+  if (qmode == Q_FP8 && K % 128 != 0) return -1;
+  const bool bf16 = dtype == 1;
+  const int mpad = max_rows_per_expert <= 16 ? 16 : max_rows_per_expert <= 32 ? 32 : max_rows_per_expert <= 64 ? 64 : 128;
+  const int chunks = (max_rows_per_expert + mpad - 1) / mpad;
+  GemmParams p;
+  p.out = out; p.bias = nullptr; p.residual = nullptr;
+  p.M = 0; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = 0;
+  p.kb_total = K / 64; p.flags = flags;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0; p.w_row0 = 0; p.x_row0 = 0;
+  for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
+  const int n_tiles = N / 128;
+  int nsplit = 1;
+  while (nsplit < 4 && n_tiles * E_local * nsplit < 148 && (p.kb_total / (nsplit * 2)) >= 8) nsplit *= 2;
+  p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
+  p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
+  QuantParams qp;
+  qp.scale = scale; qp.zero = zero;
+  qp.group_k = qmode == Q_INT4G ? group_k : 128;
+  qp.groups = qmode == Q_INT4G ? K / group_k : (K + 127) / 128;
+  QuantGroupInfo gi;
+  gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
+  gi.scale_stride_e = qmode == Q_INT8 ? N : qmode == Q_INT4G ? (long long)qp.groups * N * 2 : (long long)(N / 128) * qp.groups;
+  gi.zero_stride_e = N;
+  const int kbytes = qmode == Q_INT4G ? K / 2 : K;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, Wq, (uint64_t)E_local * N, kbytes, kbytes, 128, qmode == Q_INT4G ? 32 : 64, 1, 0)) return -2;
+  if (!make_tmap_2d(&tmX, Xs, rows_cap, K, K, mpad, 64, 2, 3)) return -2;
+  const int nz = E_local * chunks;
+  if (nz > 65535) return -1;
+#define FB_GQ2(MP, QMV)                                                                                          \
+  return (int)(bf16 ? launch_grouped_quant<MP, true, QMV>(tmW, tmX, p, qp, gi, nsplit, n_tiles, nz, stream)       \
+                    : launch_grouped_quant<MP, false, QMV>(tmW, tmX, p, qp, gi, nsplit, n_tiles, nz, stream));
+#define FB_GQ(MP)                                                                                                 \
+  { if (qmode == Q_INT8) { FB_GQ2(MP, Q_INT8) } else if (qmode == Q_INT4G) { FB_GQ2(MP, Q_INT4G) } else if (qmode == Q_FP8) { FB_GQ2(MP, Q_FP8) } else return -1; }
+  switch (mpad) {
+    case 16: FB_GQ(16)
+    case 32: FB_GQ(32)
+    case 64: FB_GQ(64)
+    default: FB_GQ(128)
+  }
+#undef FB_GQ
+#undef FB_GQ2
 }

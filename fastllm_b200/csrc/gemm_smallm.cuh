@@ -28,6 +28,7 @@ struct GemmParams {
   // Row scatter (tensor-parallel reduce-scatter by push): with scatter_tp > 0 and GEMM_OUT_F32 the fp32 row j goes to
   // scatter_out[j / scatter_rows] (a peer's arena), at row (scatter_rank * M + j) of a [tp * M, ld_out] matrix.
   int scatter_tp, scatter_rows, scatter_rank;
+  int w_row0, x_row0;        // row offsets added to the weight / activation tile coordinates (grouped GEMM)
   float* scatter_out[8];
 };
 
@@ -162,8 +163,8 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_SMALLM, 1)) break;
         uint8_t* a = smem + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-        tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 64, n_tile * 128, pol_w);
-        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], (kb0 + i) * 64, 0, pol_x);
+        tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 64, p.w_row0 + n_tile * 128, pol_w);
+        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], (kb0 + i) * 64, p.x_row0, pol_x);
       }
     }
     __syncwarp();

@@ -87,9 +87,8 @@ class ModelRunner:
         if c.use_mla:
             return False
         if c.is_moe:
-            from ..ops import moe_grouped
-
-            return getattr(moe_grouped, "GRAPH_SAFE", False)
+            # the per-expert fallback loop synchronises with the host; graphs need every MoE layer on the grouped kernels
+            return all(lw.mlp.experts is None or lw.mlp.experts.stacked is not None for lw in self.model.layers)
         return True
 
     # ---------------------------------------------------------------------------------------------

@@ -238,7 +238,7 @@ def preset(name: str) -> ModelConfig:
                                  num_attention_heads=4, num_key_value_heads=4, intermediate_size=512,
                                  moe_intermediate_size=128, n_routed_experts=16, num_experts_per_tok=4, n_shared_experts=1,
                                  first_k_dense_replace=1, n_group=4, topk_group=2, routed_scaling_factor=2.5,
-                                 scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=96,
+                                 scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=128,
                                  kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
                                  rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=2048))
     raise KeyError(f"unknown preset '{name}'")

@@ -94,6 +94,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: b
         x2 = x2.contiguous()
     M, K = x2.shape
     N = w.shape[0]
+    if K % 64 != 0 or N % 8 != 0 or x.dtype not in (torch.float16, torch.bfloat16) or (x2.data_ptr() & 15) or (x2.stride(0) * 2) % 16:
+        # shapes outside the tensor-core kernels' tiling (rare: odd projection widths): plain PyTorch definition
+        return linear_ref(x, w, bias, residual, swiglu, interleaved, torch.float32 if out_f32 else None)
     if swiglu and not interleaved:
         raise ValueError("CUDA SwiGLU epilogue needs tile-interleaved gate/up weights (interleave_gate_up)")
     n_out = N // 2 if swiglu else N

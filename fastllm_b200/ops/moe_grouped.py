@@ -1,15 +1,125 @@
-"""Grouped expert GEMM path (CUDA): all routed experts of a layer in two launches.
+"""Grouped expert GEMM path (CUDA): all routed experts of a layer in a handful of launches, no host synchronisation
+(CUDA-graph safe).
 
-``prepare_model`` stacks each MoE layer's expert weights into the layout the grouped kernel reads;
-``forward`` returns ``None`` when the grouped kernel cannot take the case and the caller falls back to
-the per-expert loop in ``ops.moe``.
+``prepare_model`` stacks each MoE layer's dense expert weights into ``[E_local * rows, K]`` matrices the grouped kernel
+addresses by expert; ``forward`` runs plan -> gather -> grouped gate/up (+SwiGLU) -> grouped down -> weighted combine.
+Returns ``None`` for cases the grouped kernels do not take (quantised experts, odd shapes); the caller then uses the
+per-expert loop in ``ops.moe``.
 """
 from __future__ import annotations
 
+import ctypes
+
+import torch
+
+from . import _lib
+from .basic import GEMM_SWIGLU, _ptr, _stream, dtype_code
+
+P, I = ctypes.c_void_p, ctypes.c_int
+_lib.register_sigs({
+    "fb_moe_plan": [P, I, I, I, I, P, P, P, P, I, P],
+    "fb_moe_gather": [P, P, P, I, I, I, P],
+    "fb_moe_combine": [P, P, P, P, P, I, I, I, I, P],
+    "fb_moe_grouped_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
+    "fb_moe_grouped_gemm_quant": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
+}, ["moe"])
+
+GRAPH_SAFE = True
+PAD = 16
+
+
+class StackedExperts:
+    """Expert weights of one layer stacked along the row dim; quantised kinds carry stacked scales in kernel layout."""
+
+    def __init__(self, kind, gate_up, down, n_local, inter, hidden, group=0, gu_scale=None, gu_zero=None, dn_scale=None, dn_zero=None):
+        self.kind, self.gate_up, self.down, self.n_local, self.inter, self.hidden, self.group = kind, gate_up, down, n_local, inter, hidden, group
+        self.gu_scale, self.gu_zero, self.dn_scale, self.dn_zero = gu_scale, gu_zero, dn_scale, dn_zero
+
+
+def _stack_scales(ws):
+    from .quant_gemm import _kernel_tensors
+
+    sc, ze = zip(*[_kernel_tensors(w) for w in ws])
+    scale = torch.stack([t.contiguous() for t in sc]).contiguous()
+    zero = torch.stack([t.contiguous() for t in ze]).contiguous() if ze[0] is not None else None
+    return scale, zero
+
+
+def stack_experts(experts) -> StackedExperts | None:
+    gu, dn = experts.gate_up, experts.down
+    if not gu:
+        return None
+    kind = gu[0].kind
+    if any(w.kind != kind or not w.interleaved or w.bias is not None for w in gu) or any(w.kind != kind or w.bias is not None for w in dn):
+        return None
+    two_i, hidden = gu[0].n, gu[0].k
+    if two_i % 128 != 0 or hidden % 128 != 0 or (two_i // 2) % 64 != 0:
+        return None
+    g = torch.cat([w.w for w in gu], dim=0).contiguous()
+    d = torch.cat([w.w for w in dn], dim=0).contiguous()
+    if kind == "dense":
+        return StackedExperts(kind, g, d, len(gu), two_i // 2, hidden)
+    if kind == "int4g" and (gu[0].group % 64 != 0 or hidden % gu[0].group != 0 or (two_i // 2) % gu[0].group != 0):
+        return None
+    if kind == "fp8" and (two_i // 2) % 128 != 0:
+        return None
+    gs, gz = _stack_scales(gu)
+    ds, dz = _stack_scales(dn)
+    return StackedExperts(kind, g, d, len(gu), two_i // 2, hidden, gu[0].group, gs, gz, ds, dz)
+
 
 def prepare_model(m) -> None:
-    return None
+    """Stack the experts of every MoE layer; the per-expert tensors are replaced by views of the stacked matrices."""
+    for lw in m.layers:
+        ex = lw.mlp.experts
+        if ex is None or ex.count == 0:
+            continue
+        st = stack_experts(ex)
+        if st is None:
+            continue
+        ex.stacked = st
+        two_i, H = 2 * st.inter, st.hidden
+        for e in range(ex.count):       # drop the duplicate storage: per-expert weights become views of the stacked matrices
+            ex.gate_up[e].w = st.gate_up[e * two_i:(e + 1) * two_i]
+            ex.down[e].w = st.down[e * H:(e + 1) * H]
 
 
-def forward(x, idx, wts, experts):
-    return None
+def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add: torch.Tensor | None = None):
+    st = experts.stacked
+    if st is None or x.dtype not in (torch.float16, torch.bfloat16):
+        return None
+    T, H = x.shape
+    topk = idx.shape[1]
+    E = st.n_local
+    dev = x.device
+    lib = _lib.kernels()
+    rows_cap = T * topk + E * PAD + 128
+    counts = torch.empty(E, device=dev, dtype=torch.int32)
+    offsets = torch.empty(E, device=dev, dtype=torch.int32)
+    pos = torch.empty((T, topk), device=dev, dtype=torch.int32)
+    total = torch.empty(1, device=dev, dtype=torch.int32)
+    idx = idx.contiguous()
+    wts = wts.float().contiguous()
+    s = _stream()
+    _lib.check(lib.fb_moe_plan(_ptr(idx), T, topk, experts.first, E, _ptr(counts), _ptr(offsets), _ptr(pos), _ptr(total), PAD, s), "fb_moe_plan")
+    xs = torch.empty((rows_cap, H), device=dev, dtype=x.dtype)
+    _lib.check(lib.fb_moe_gather(_ptr(x.contiguous()), _ptr(pos), _ptr(xs), T, topk, H, s), "fb_moe_gather")
+    act = torch.empty((rows_cap, st.inter), device=dev, dtype=x.dtype)
+    ys = torch.empty((rows_cap, H), device=dev, dtype=x.dtype)
+    dt = dtype_code(x.dtype)
+    if st.kind == "dense":
+        _lib.check(lib.fb_moe_grouped_gemm(_ptr(xs), _ptr(st.gate_up), _ptr(act), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
+                                           2 * st.inter, H, st.inter, T, dt, GEMM_SWIGLU, s), "fb_moe_grouped_gemm(gate_up)")
+        _lib.check(lib.fb_moe_grouped_gemm(_ptr(act), _ptr(st.down), _ptr(ys), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
+                                           H, st.inter, H, T, dt, 0, s), "fb_moe_grouped_gemm(down)")
+    else:
+        qm = {"int8": 1, "int4g": 2, "fp8": 3}[st.kind]
+        _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(xs), _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(st.gu_zero), _ptr(act), _ptr(counts),
+                                                 _ptr(offsets), rows_cap, E, 2 * st.inter, H, st.inter, T, dt, qm, st.group or 0,
+                                                 GEMM_SWIGLU, s), "fb_moe_grouped_gemm_quant(gate_up)")
+        _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(act), _ptr(st.down), _ptr(st.dn_scale), _ptr(st.dn_zero), _ptr(ys), _ptr(counts),
+                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, T, dt, qm, st.group or 0, 0, s),
+                   "fb_moe_grouped_gemm_quant(down)")
+    out = torch.empty((T, H), device=dev, dtype=x.dtype)
+    _lib.check(lib.fb_moe_combine(_ptr(ys), _ptr(pos), _ptr(wts), _ptr(add), _ptr(out), T, topk, H, dt, s), "fb_moe_combine")
+    return out

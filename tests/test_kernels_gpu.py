@@ -211,3 +211,51 @@ def test_gemm_quant_epilogues():
         y = lw(x, residual=res, swiglu=True)
         ref = B.linear_ref(x, lw.dequant(torch.float32), bias, res, swiglu=True)
         _close(y, ref, 5e-2, 4e-2, f"quant epilogue {kind}")
+
+
+@pytest.mark.parametrize("T,E,first,n_local,topk", [(7, 8, 0, 8, 2), (64, 16, 4, 8, 4), (130, 32, 0, 32, 8), (300, 8, 2, 4, 2)])
+def test_moe_grouped(T, E, first, n_local, topk):
+    """Grouped expert path vs the per-expert PyTorch definition, including experts owned by other ranks."""
+    from fastllm_b200.ops import moe as MOE, moe_grouped, quant
+
+    torch.manual_seed(10)
+    H, I, dt = 256, 128, torch.bfloat16
+    gu, dn = [], []
+    for e in range(n_local):
+        g = (torch.randn(I, H, device=DEV) * 0.05).to(dt)
+        u = (torch.randn(I, H, device=DEV) * 0.05).to(dt)
+        gu.append(quant.LinearWeight.from_dense(B.interleave_gate_up(g, u), interleaved=True))
+        dn.append(quant.LinearWeight.from_dense((torch.randn(H, I, device=DEV) * 0.05).to(dt)))
+    ex = MOE.ExpertWeights(E, first, gu, dn)
+    x = torch.randn(T, H, device=DEV).to(dt)
+    logits = torch.randn(T, E, device=DEV)
+    idx, w = MOE.route_topk(logits, None, topk, 0, True)
+    ref = MOE.moe_forward(x, idx, w, ex)                 # stacked is None -> per-expert loop
+    ex.stacked = moe_grouped.stack_experts(ex)
+    assert ex.stacked is not None
+    out = moe_grouped.forward(x, idx, w, ex)
+    _close(out, ref, 3e-2, 3e-2, "moe grouped")
+    idx_ref, w_ref = MOE.route_topk_ref(logits, None, topk, 0, True)
+    assert torch.equal(idx.sort(1)[0], idx_ref.sort(1)[0])
+
+
+@pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8"])
+def test_moe_grouped_quant(kind):
+    from fastllm_b200.ops import moe as MOE, moe_grouped, quant
+
+    torch.manual_seed(11)
+    T, E, topk, H, I, dt = 40, 8, 2, 256, 128, torch.bfloat16
+    gu, dn = [], []
+    for e in range(E):
+        g = (torch.randn(I, H, device=DEV) * 0.05).to(dt)
+        u = (torch.randn(I, H, device=DEV) * 0.05).to(dt)
+        gu.append(quant.LinearWeight.from_dense(B.interleave_gate_up(g, u), kind, interleaved=True, act_dtype=dt))
+        dn.append(quant.LinearWeight.from_dense((torch.randn(H, I, device=DEV) * 0.05).to(dt), kind, act_dtype=dt))
+    ex = MOE.ExpertWeights(E, 0, gu, dn)
+    x = torch.randn(T, H, device=DEV).to(dt)
+    idx, w = MOE.route_topk(torch.randn(T, E, device=DEV), None, topk, 0, True)
+    ref = MOE.moe_forward(x, idx, w, ex)
+    ex.stacked = moe_grouped.stack_experts(ex)
+    assert ex.stacked is not None and ex.stacked.kind != "dense"
+    out = moe_grouped.forward(x, idx, w, ex)
+    _close(out, ref, 4e-2, 4e-2, f"moe grouped {kind}")
