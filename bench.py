@@ -42,6 +42,8 @@ def parse_args():
     ap.add_argument("--dtype", default="auto", help="weight dtype: auto(bf16) | int8 | int4g128 | fp8")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--moe-dtype", default="")
+    ap.add_argument("--moe-tp", action="store_true", help="shard every expert over the ranks instead of expert parallelism")
     return ap.parse_args()
 
 
@@ -116,7 +118,12 @@ def run_ours(args):
         from fastllm_b200.parallel import symm
 
         tp.comm.fused = symm.try_create(tp.comm, cfg, args.batch, strict=(args.comm == "fused"))
-    model = random_init(cfg, dev, torch.bfloat16, tp=tp, seed=0, wdtype=args.dtype)
+    ep = None
+    if world > 1 and cfg.is_moe and not args.moe_tp:
+        from fastllm_b200.parallel.ep import EPInfo
+
+        ep = EPInfo.from_tp(tp)
+    model = random_init(cfg, dev, torch.bfloat16, tp=tp, ep=ep, seed=0, wdtype=args.dtype, moe_wdtype=args.moe_dtype or None)
     B, P, O = args.batch, args.prompt_len, args.output_len
     need_tokens = int(B * (P + O + 256) / 0.75)   # leaves the 80 % admission limit room for all B prompts
     ecfg = EngineConfig(max_batch=max(B, 1), max_context=((P + O + 127) // 128 + 1) * 128, max_tokens=need_tokens,
@@ -182,7 +189,7 @@ def run_ours(args):
             "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if args.dtype == "auto" else args.dtype,
             "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
-            "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O, "parallelism": f"tp{world}",
+            "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O, "parallelism": f"tp{world}" + (f"+ep{world}" if ep is not None else ""),
                        "kv_cache": "paged, page 128, bf16", "l2": "inputs larger than L2 (weights + KV >> 126 MB per step)",
                        "cuda_graph": not args.no_graph, "comm": (tp.comm.fused.name if (tp.comm and tp.comm.fused) else ("nccl" if world > 1 else "none"))},
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": B * 4,

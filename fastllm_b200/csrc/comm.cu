@@ -52,6 +52,8 @@ struct ArNormParams {
   const uint16_t* ln_w;      // RMSNorm weight [N] (nullptr: skip the norm, x is not written)
   const void* src;           // stand-alone kernel: this rank's partial [M, N] to push (nullptr in the GEMM kernel)
   int src_f32;               // src is fp32 (else the 16-bit activation dtype)
+  // MoE combine source (src == nullptr, moe_ys != nullptr): partial[row] = sum_k moe_w[row,k] * moe_ys[moe_pos[row,k]] (+ moe_add[row])
+  const uint16_t* moe_ys; const int* moe_pos; const float* moe_w; const uint16_t* moe_add; int moe_topk;
   int M, N;
   int has_residual;
   int trace;                 // != 0: CTA 0 writes globaltimer stamps of each phase to OFF_TRACE
@@ -265,7 +267,24 @@ __global__ void __launch_bounds__(192, 1) ar_norm_kernel(const ArNormParams p) {
   for (long long it = (long long)blockIdx.x * blockDim.x + threadIdx.x; it < total; it += (long long)gridDim.x * blockDim.x) {
     const int row = (int)(it / chunks), ch = (int)(it - (long long)row * chunks);
     float4 a, b;
-    if (p.src_f32) {
+    if (p.moe_ys != nullptr) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int k = 0; k < p.moe_topk; ++k) {
+        const int r = p.moe_pos[row * p.moe_topk + k];
+        if (r < 0) continue;
+        const float wk = p.moe_w[row * p.moe_topk + k];
+        const uint4 v = *reinterpret_cast<const uint4*>(p.moe_ys + (size_t)r * p.N + (size_t)ch * 8);
+        const float2 v0 = unpack_16<BF16>(v.x), v1 = unpack_16<BF16>(v.y), v2 = unpack_16<BF16>(v.z), v3 = unpack_16<BF16>(v.w);
+        acc[0] += wk * v0.x; acc[1] += wk * v0.y; acc[2] += wk * v1.x; acc[3] += wk * v1.y;
+        acc[4] += wk * v2.x; acc[5] += wk * v2.y; acc[6] += wk * v3.x; acc[7] += wk * v3.y;
+      }
+      if (p.moe_add != nullptr) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p.moe_add + (size_t)row * p.N + (size_t)ch * 8);
+        const float2 v0 = unpack_16<BF16>(v.x), v1 = unpack_16<BF16>(v.y), v2 = unpack_16<BF16>(v.z), v3 = unpack_16<BF16>(v.w);
+        acc[0] += v0.x; acc[1] += v0.y; acc[2] += v1.x; acc[3] += v1.y; acc[4] += v2.x; acc[5] += v2.y; acc[6] += v3.x; acc[7] += v3.y;
+      }
+      a = make_float4(acc[0], acc[1], acc[2], acc[3]); b = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    } else if (p.src_f32) {
       const float4* sp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p.src) + (size_t)row * p.N + (size_t)ch * 8);
       a = sp[0]; b = sp[1];
     } else {
@@ -405,7 +424,7 @@ extern "C" int fb_gemm_ar_norm(const void* X, const void* W, const void* bias, i
   fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
   p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
   p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
-  p.src = nullptr; p.src_f32 = 0;
+  p.src = nullptr; p.src_f32 = 0; p.moe_ys = nullptr; p.moe_pos = nullptr; p.moe_w = nullptr; p.moe_add = nullptr; p.moe_topk = 0;
   CUtensorMap tmW, tmX;
   if (!make_tmap_2d(&tmW, W, N, K, ldw, 128, 64, 2, 3)) return -2;
   if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
@@ -422,17 +441,7 @@ extern "C" int fb_gemm_ar_norm(const void* X, const void* W, const void* bias, i
 #undef FB_GA
 }
 
-// All-reduce (+residual, +RMSNorm) of this rank's partial `src` [M, N] (fp32 if src_f32 else the 16-bit dtype).
-extern "C" int fb_ar_norm(const void* src, int src_f32, int M, int N, void* arena_local, void* arena_mc, void* const* peers, int rank, int tp,
-                          unsigned long long off_part, unsigned long long off_h, unsigned long long off_x, const void* ln_w,
-                          int has_residual, float eps, float unit_offset, int dtype, void* stream_) {
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  if (M <= 0 || N % 8 != 0 || N > 18432 || tp > MAX_TP) return -1;
-  ArNormParams p;
-  fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
-  p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
-  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
-  p.src = src; p.src_f32 = src_f32;
+static int launch_ar_norm(ArNormParams& p, int M, int N, int tp, int dtype, cudaStream_t stream) {
   int rows_per = (M + tp - 1) / tp;
   const int cs = N >= 4096 ? 4 : (N >= 2048 ? 2 : 1);     // CTAs per row
   int groups = rows_per < 1 ? 1 : rows_per;
@@ -448,6 +457,36 @@ extern "C" int fb_ar_norm(const void* src, int src_f32, int M, int N, void* aren
   cfg.attrs = attr; cfg.numAttrs = 1;
   if (dtype == 1) return (int)cudaLaunchKernelEx(&cfg, ar_norm_kernel<true>, p);
   return (int)cudaLaunchKernelEx(&cfg, ar_norm_kernel<false>, p);
+}
+
+// All-reduce (+residual, +RMSNorm) of this rank's partial `src` [M, N] (fp32 if src_f32 else the 16-bit dtype).
+extern "C" int fb_ar_norm(const void* src, int src_f32, int M, int N, void* arena_local, void* arena_mc, void* const* peers, int rank,
+                          int tp, unsigned long long off_part, unsigned long long off_h, unsigned long long off_x, const void* ln_w,
+                          int has_residual, float eps, float unit_offset, int dtype, void* stream_) {
+  if (M <= 0 || N % 8 != 0 || N > 18432 || tp > MAX_TP) return -1;
+  ArNormParams p;
+  fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
+  p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
+  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
+  p.src = src; p.src_f32 = src_f32; p.moe_ys = nullptr; p.moe_pos = nullptr; p.moe_w = nullptr; p.moe_add = nullptr; p.moe_topk = 0;
+  return launch_ar_norm(p, M, N, tp, dtype, reinterpret_cast<cudaStream_t>(stream_));
+}
+
+// Expert-parallel combine fused with the cross-rank reduction: this rank's weighted sum over its local experts' outputs
+// (ys rows addressed by pos, -1 = expert on another rank; `add` = e.g. the shared expert's partial) is formed on the fly,
+// pushed to the row owners, reduced, joined with the residual, normalised and broadcast.
+extern "C" int fb_moe_combine_ar_norm(const void* ys, const int* pos, const float* w, const void* add, int topk, int M, int N,
+                                      void* arena_local, void* arena_mc, void* const* peers, int rank, int tp,
+                                      unsigned long long off_part, unsigned long long off_h, unsigned long long off_x, const void* ln_w,
+                                      int has_residual, float eps, float unit_offset, int dtype, void* stream_) {
+  if (M <= 0 || N % 8 != 0 || N > 18432 || tp > MAX_TP) return -1;
+  ArNormParams p;
+  fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
+  p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
+  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
+  p.src = nullptr; p.src_f32 = 0;
+  p.moe_ys = (const uint16_t*)ys; p.moe_pos = pos; p.moe_w = w; p.moe_add = (const uint16_t*)add; p.moe_topk = topk;
+  return launch_ar_norm(p, M, N, tp, dtype, reinterpret_cast<cudaStream_t>(stream_));
 }
 
 extern "C" int fb_argmax_merge(const float* vals, const int* ids, int* out, int B, void* arena_local, void* arena_mc,

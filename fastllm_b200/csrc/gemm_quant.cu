@@ -32,7 +32,8 @@ struct QuantParams {
   int groups;             // int4g: groups per row; fp8: scale columns
 };
 
-template <int MPAD, int QM>
+// OCC: CTAs per SM the shared-memory budget is sized for (2 doubles the dequant warps working per SM)
+template <int MPAD, int QM, int OCC = (MPAD <= 64 ? 2 : 1)>
 struct QuantCfg {
   static constexpr int RAW_BYTES = QM == Q_INT4G ? 128 * 32 : 128 * 64;
   static constexpr int B_BYTES = MPAD * 128;
@@ -41,7 +42,7 @@ struct QuantCfg {
   static constexpr int DQ_SLOTS = 3;
   static constexpr int DQ_BYTES = 128 * 128;
   static constexpr int RED_BYTES = MPAD * 128 * 4;
-  static constexpr int BUDGET = 196 * 1024 - DQ_SLOTS * DQ_BYTES;
+  static constexpr int BUDGET = (196 * 1024) / OCC - DQ_SLOTS * DQ_BYTES;
   static constexpr int STAGES_RAW = BUDGET / PITCH > 12 ? 12 : BUDGET / PITCH;
   static constexpr int STAGES = STAGES_RAW < 2 ? 2 : STAGES_RAW;
   static constexpr int PIPE_BYTES = DQ_SLOTS * DQ_BYTES + STAGES * PITCH;
@@ -182,12 +183,17 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
         float bscale = 1.f;
         if (QM == Q_FP8) bscale = qp.scale[(size_t)n_tile * qp.groups + (kb * 64) / 128];
         const __half2 bs2 = __float2half2_rn(bscale);
+        uint4 wv[4];
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int u = tid + 128 * it;
+          wv[it] = *reinterpret_cast<const uint4*>(raw + (u >> 2) * 64 + (u & 3) * 16);
+        }
 #pragma unroll
         for (int it = 0; it < 4; ++it) {
           const int u = tid + 128 * it, row = u >> 2, ch = u & 3;
           const int n = n_tile * 128 + row;
-          const uint4 w = *reinterpret_cast<const uint4*>(raw + row * 64 + ch * 16);
-          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+          const uint32_t ws[4] = {wv[it].x, wv[it].y, wv[it].z, wv[it].w};
           uint32_t o[8];
           if (QM == Q_INT8) {
             const float z = n < p.N ? qp.zero[n] : 0.f;
@@ -197,14 +203,29 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
               o[2 * j] = out16<BF16>(u8x2_to_h2(ws[j] & 0xFFu, (ws[j] >> 8) & 0xFFu, sub));
               o[2 * j + 1] = out16<BF16>(u8x2_to_h2((ws[j] >> 16) & 0xFFu, ws[j] >> 24, sub));
             }
+          } else if (BF16) {
+            // e4m3 -> bf16 by bit placement: sign to bit 15, the 7 exponent+mantissa bits to bits 10..4; the value comes out
+            // scaled by 2^-120 (exponent bias 7 vs 127), exact also for subnormals; one fp32 multiply applies 2^120 * block scale
+            const float fs = bscale * 1.329227995784916e36f;     // 2^120
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t x = ws[j];
+#pragma unroll
+              for (int hw = 0; hw < 2; ++hw) {
+                const uint32_t b0 = (x >> (16 * hw)) & 0xFFu, b1 = (x >> (16 * hw + 8)) & 0xFFu;
+                const float f0 = __uint_as_float((((b0 & 0x80u) << 8) | ((b0 & 0x7Fu) << 4)) << 16) * fs;
+                const float f1 = __uint_as_float((((b1 & 0x80u) << 8) | ((b1 & 0x7Fu) << 4)) << 16) * fs;
+                o[2 * j + hw] = pack_bf16(f0, f1);
+              }
+            }
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               uint32_t lo, hi;
               asm("{\n\t.reg .b16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.rn.f16x2.e4m3x2 %0, a;\n\tcvt.rn.f16x2.e4m3x2 %1, b;\n\t}\n"
                   : "=r"(lo), "=r"(hi) : "r"(ws[j]));
-              o[2 * j] = out16<BF16>(__hmul2(*reinterpret_cast<__half2*>(&lo), bs2));
-              o[2 * j + 1] = out16<BF16>(__hmul2(*reinterpret_cast<__half2*>(&hi), bs2));
+              o[2 * j] = h2_as_u32(__hmul2(*reinterpret_cast<__half2*>(&lo), bs2));
+              o[2 * j + 1] = h2_as_u32(__hmul2(*reinterpret_cast<__half2*>(&hi), bs2));
             }
           }
           const int c0 = ch * 2;
@@ -246,7 +267,7 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
 }
 
 template <int MPAD, bool BF16, int QM>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
 gemm_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
                   const QuantParams qp) {
   gemm_quant_device<MPAD, BF16, QM>(tmW, tmX, p, qp);
@@ -260,7 +281,7 @@ struct QuantGroupInfo {
 };
 
 template <int MPAD, bool BF16, int QM>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
 moe_grouped_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                          const QuantParams qbase, const QuantGroupInfo gi) {
   const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
@@ -398,7 +419,10 @@ extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const f
   if (qmode == Q_INT4G && (group_k <= 0 || group_k % 64 != 0 || K % group_k != 0)) return -1;
   if (qmode == Q_FP8 && K % 128 != 0) return -1;
   const bool bf16 = dtype == 1;
-  const int mpad = max_rows_per_expert <= 16 ? 16 : max_rows_per_expert <= 32 ? 32 : max_rows_per_expert <= 64 ? 64 : 128;
+  const int hint = max_rows_per_expert >> 16;       // high 16 bits: chunk size hint, low 16 bits: most rows an expert can get
+  max_rows_per_expert &= 0xFFFF;
+  int mpad = max_rows_per_expert <= 16 ? 16 : max_rows_per_expert <= 32 ? 32 : max_rows_per_expert <= 64 ? 64 : 128;
+  if (hint == 16 || hint == 32 || hint == 64 || hint == 128) mpad = hint < mpad ? hint : mpad;
   const int chunks = (max_rows_per_expert + mpad - 1) / mpad;
   GemmParams p;
   p.out = out; p.bias = nullptr; p.residual = nullptr;

@@ -65,6 +65,50 @@ __global__ void moe_plan_kernel(const int* __restrict__ idx, int T, int topk, in
   }
 }
 
+// Small problems (pairs <= 4096): one thread per (token, k) pair; rank inside the expert segment = number of earlier pairs
+// routed to the same expert, so the order is deterministic without any sorting pass.
+__global__ void moe_plan_small_kernel(const int* __restrict__ idx, int pairs, int first, int n_local, int* __restrict__ counts,
+                                      int* __restrict__ offsets, int* __restrict__ pos, int* __restrict__ total_rows, int pad) {
+  __shared__ int s_idx[4096];
+  __shared__ int s_cnt[1024];
+  __shared__ int s_off[1024];
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = idx[i] - first;
+    s_idx[i] = (e >= 0 && e < n_local) ? e : -1;
+  }
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) s_cnt[e] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x)
+    if (s_idx[i] >= 0) atomicAdd(&s_cnt[s_idx[i]], 1);
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    // warp-level exclusive scan of the padded counts, 32 experts at a time
+    int carry = 0;
+    for (int base = 0; base < n_local; base += 32) {
+      const int e = base + threadIdx.x;
+      const int c = e < n_local ? (s_cnt[e] + pad - 1) / pad * pad : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((int)threadIdx.x >= o) incl += v;
+      }
+      if (e < n_local) s_off[e] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (threadIdx.x == 0) *total_rows = carry;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) { counts[e] = s_cnt[e]; offsets[e] = s_off[e]; }
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = s_idx[i];
+    if (e < 0) { pos[i] = -1; continue; }
+    int rank = 0;
+    for (int j = 0; j < i; ++j) rank += (s_idx[j] == e);
+    pos[i] = s_off[e] + rank;
+  }
+}
+
 __global__ void moe_gather_kernel(const uint16_t* __restrict__ x, const int* __restrict__ pos, uint16_t* __restrict__ xs, int T,
                                   int topk, int H) {
   const int pair = blockIdx.x;
@@ -156,6 +200,10 @@ using namespace fb;
 extern "C" int fb_moe_plan(const int* idx, int T, int topk, int first, int n_local, int* counts, int* offsets, int* pos,
                            int* total_rows, int pad, void* stream) {
   if (n_local <= 0 || n_local > 1024 || T <= 0) return -1;
+  if (T * topk <= 4096) {
+    moe_plan_small_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(idx, T * topk, first, n_local, counts, offsets, pos, total_rows, pad);
+    return (int)cudaGetLastError();
+  }
   int threads = 32;
   while (threads < n_local) threads <<= 1;
   if (threads < 256) threads = 256;
@@ -189,7 +237,11 @@ extern "C" int fb_moe_grouped_gemm(const void* Xs, const void* W, void* out, con
   if (E_local <= 0 || rows_cap <= 0) return 0;
   if (K % 64 != 0 || N % 128 != 0 || (dtype != 0 && dtype != 1)) return -1;
   const bool bf16 = dtype == 1;
-  const int mpad = max_rows_per_expert <= 16 ? 16 : max_rows_per_expert <= 32 ? 32 : max_rows_per_expert <= 64 ? 64 : 128;
+  // rows per chunk: low 16 bits of max_rows_per_expert = most rows an expert can get, high 16 bits = chunk size hint (0: auto)
+  const int hint = max_rows_per_expert >> 16;
+  max_rows_per_expert &= 0xFFFF;
+  int mpad = max_rows_per_expert <= 16 ? 16 : max_rows_per_expert <= 32 ? 32 : max_rows_per_expert <= 64 ? 64 : 128;
+  if (hint == 16 || hint == 32 || hint == 64 || hint == 128) mpad = hint < mpad ? hint : mpad;
   const int chunks = (max_rows_per_expert + mpad - 1) / mpad;
   GemmParams p;
   p.out = out; p.bias = bias; p.residual = nullptr;

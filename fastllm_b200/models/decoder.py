@@ -78,6 +78,7 @@ class MLPWeights:
         self.down: LinearWeight | None = None
         # MoE
         self.router = None          # fp32 [E, H]
+        self.router_16 = None       # 16-bit copy for the tensor-core router GEMM
         self.router_bias = None     # fp32 [E]
         self.experts: MOE.ExpertWeights | None = None
         self.shared_gate_up: LinearWeight | None = None
@@ -234,22 +235,43 @@ class DecoderModel:
         return self._row_parallel_norm(lw.o, o, residual, next_ln)
 
     # -----------------------------------------------------------------------------------------------
+    def _router_logits(self, lw: MLPWeights, x):
+        """fp32 router logits.  On CUDA the router runs through the tensor-core GEMM with 16-bit operands and fp32
+        accumulation / output; on CPU in fp32."""
+        if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and lw.router.shape[0] % 8 == 0:
+            if lw.router_16 is None:
+                lw.router_16 = lw.router.to(x.dtype).contiguous()
+            return B.linear(x, lw.router_16, out_f32=True)
+        return torch.matmul(x.float(), lw.router.t())
+
     def _mlp(self, lw: MLPWeights, x, residual, layer_idx, next_ln):
         c = self.cfg
         if lw.experts is None:
             act = lw.gate_up(x, swiglu=True)
             return self._row_parallel_norm(lw.down, act, residual, next_ln)
         # ---- mixture of experts ----
-        logits = torch.matmul(x.float(), lw.router.t())
+        logits = self._router_logits(lw, x)
         idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
                                   0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
                                   c.routed_scaling_factor)
-        y = MOE.moe_forward(x, idx, wts, lw.experts, self.ep)
+        shared = None
         if lw.shared_gate_up is not None:
-            s = lw.shared_down(lw.shared_gate_up(x, swiglu=True))
+            shared = lw.shared_down(lw.shared_gate_up(x, swiglu=True))
             if lw.shared_gate is not None:
-                s = s * torch.sigmoid(torch.matmul(x.float(), lw.shared_gate.float().t())).to(s.dtype)
-            y = y + s
+                shared = shared * torch.sigmoid(torch.matmul(x.float(), lw.shared_gate.float().t())).to(shared.dtype)
+        if self._fused_active and lw.experts.stacked is not None:
+            # expert-parallel combine fused with the cross-rank reduction + residual + norm (one kernel)
+            from ..ops import moe_grouped
+
+            parts = moe_grouped.forward(x, idx, wts, lw.experts, combine=False)
+            if parts is not None:
+                ys, pos, w32 = parts
+                r = self.tp.comm.fused.moe_combine_ar_norm(ys, pos, w32, shared, next_ln, c.rms_eps, c.norm_unit_offset, True)
+                if r is not None:
+                    return r
+        y = MOE.moe_forward(x, idx, wts, lw.experts, self.ep)
+        if shared is not None:
+            y = y + shared
         return self._reduce_norm(y, residual, next_ln, self.tp.size > 1)
 
     # -----------------------------------------------------------------------------------------------

@@ -84,7 +84,8 @@ def prepare_model(m) -> None:
             ex.down[e].w = st.down[e * H:(e + 1) * H]
 
 
-def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add: torch.Tensor | None = None):
+def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add: torch.Tensor | None = None, combine: bool = True):
+    """``combine=False`` stops before the weighted sum and returns ``(ys, pos, wts)`` for a fused cross-rank combine."""
     st = experts.stacked
     if st is None or x.dtype not in (torch.float16, torch.bfloat16):
         return None
@@ -94,6 +95,11 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
     dev = x.device
     lib = _lib.kernels()
     rows_cap = T * topk + E * PAD + 128
+    # chunk size: a few times the mean rows per expert, so the activation tile is not mostly padding; experts that get
+    # more rows simply run more chunks
+    mean = max(1, (T * topk) // max(1, experts.total))
+    hint = 16 if mean <= 6 else 32 if mean <= 12 else 64 if mean <= 24 else 128
+    max_rows = min(T, 0xFFFF) | (hint << 16)
     counts = torch.empty(E, device=dev, dtype=torch.int32)
     offsets = torch.empty(E, device=dev, dtype=torch.int32)
     pos = torch.empty((T, topk), device=dev, dtype=torch.int32)
@@ -109,17 +115,19 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
     dt = dtype_code(x.dtype)
     if st.kind == "dense":
         _lib.check(lib.fb_moe_grouped_gemm(_ptr(xs), _ptr(st.gate_up), _ptr(act), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
-                                           2 * st.inter, H, st.inter, T, dt, GEMM_SWIGLU, s), "fb_moe_grouped_gemm(gate_up)")
+                                           2 * st.inter, H, st.inter, max_rows, dt, GEMM_SWIGLU, s), "fb_moe_grouped_gemm(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm(_ptr(act), _ptr(st.down), _ptr(ys), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
-                                           H, st.inter, H, T, dt, 0, s), "fb_moe_grouped_gemm(down)")
+                                           H, st.inter, H, max_rows, dt, 0, s), "fb_moe_grouped_gemm(down)")
     else:
         qm = {"int8": 1, "int4g": 2, "fp8": 3}[st.kind]
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(xs), _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(st.gu_zero), _ptr(act), _ptr(counts),
-                                                 _ptr(offsets), rows_cap, E, 2 * st.inter, H, st.inter, T, dt, qm, st.group or 0,
+                                                 _ptr(offsets), rows_cap, E, 2 * st.inter, H, st.inter, max_rows, dt, qm, st.group or 0,
                                                  GEMM_SWIGLU, s), "fb_moe_grouped_gemm_quant(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(act), _ptr(st.down), _ptr(st.dn_scale), _ptr(st.dn_zero), _ptr(ys), _ptr(counts),
-                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, T, dt, qm, st.group or 0, 0, s),
+                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, max_rows, dt, qm, st.group or 0, 0, s),
                    "fb_moe_grouped_gemm_quant(down)")
+    if not combine:
+        return ys, pos, wts
     out = torch.empty((T, H), device=dev, dtype=x.dtype)
     _lib.check(lib.fb_moe_combine(_ptr(ys), _ptr(pos), _ptr(wts), _ptr(add), _ptr(out), T, topk, H, dt, s), "fb_moe_combine")
     return out

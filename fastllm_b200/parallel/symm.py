@@ -29,6 +29,7 @@ _lib.register_sigs({
     "fb_gemm_ar_norm": [P, P, P, I, I, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, I, P],
     "fb_ar_norm": [P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
     "fb_argmax_merge": [P, P, P, I, P, P, P, I, I, ULL, P],
+    "fb_moe_combine_ar_norm": [P, P, P, P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
 }, ["comm"])
 
 HEADER = 1024
@@ -111,6 +112,20 @@ class FusedComm:
                                        (1 if has_residual else 0) | (2 if self.trace else 0), float(eps),
                                        float(unit_offset), dtype_code(self.dtype), _stream())
         _lib.check(rc, "fb_ar_norm")
+        return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
+
+    def moe_combine_ar_norm(self, ys, pos, w, add, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True):
+        """Expert-parallel combine: weighted sum of this rank's expert outputs (+ ``add``) formed inside the kernel that
+        pushes it to the row owners, reduces over ranks, adds the residual, normalises and broadcasts.  One launch."""
+        M, topk = pos.shape
+        N = self.hidden
+        if not (0 < M <= self.max_m) or ys.shape[1] != N:
+            return None
+        rc = _lib.kernels().fb_moe_combine_ar_norm(_ptr(ys), _ptr(pos), _ptr(w), _ptr(add), topk, M, N, ctypes.c_void_p(self.local),
+                                                   ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp, self.off_part, self.off_h,
+                                                   self.off_x, _ptr(ln_w), (1 if has_residual else 0) | (2 if self.trace else 0),
+                                                   float(eps), float(unit_offset), dtype_code(self.dtype), _stream())
+        _lib.check(rc, "fb_moe_combine_ar_norm")
         return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
 
     # -- TPComm hooks --------------------------------------------------------------------------------

@@ -84,6 +84,20 @@ def main():
     # bf16 partial sums are ordered differently across ranks: allow rare divergence, require the first tokens to agree
     assert all(o[0] == o1[0] for o, o1 in zip(outs, outs1)), (outs, outs1)
     assert same >= total * 0.5, (outs, outs1)
+    # expert parallel MoE (fused combine + cross-rank reduce) vs one rank
+    from fastllm_b200.parallel.ep import EPInfo
+
+    cfgm = preset("tiny-qwen3-moe")
+    tpm = TPInfo(rank, world, TPComm(rank, world, dev))
+    tpm.comm.fused = symm.FusedComm(tpm.comm, cfgm.hidden_size, 16, cfgm.hidden_size, torch.bfloat16, use_multicast=use_mc)
+    mm = random_init(cfgm, dev, torch.bfloat16, tp=tpm, ep=EPInfo.from_tp(tpm), std=0.05)
+    assert mm.layers[0].mlp.experts.count == cfgm.num_experts // world
+    om = LLMEngine(mm, EngineConfig(max_batch=8, max_context=1024), num_pages=64).generate(prompts, GenerationConfig(max_new_tokens=8, ignore_eos=True))
+    m1m = random_init(cfgm, dev, torch.bfloat16, std=0.05)
+    o1m = LLMEngine(m1m, EngineConfig(max_batch=8, max_context=1024), num_pages=64).generate(prompts, GenerationConfig(max_new_tokens=8, ignore_eos=True))
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    assert all(a[0] == b[0] for a, b in zip(om, o1m)), (om, o1m)
     dist.barrier()
     if rank == 0:
         print(f"TP_GPU_WORKER_OK tokens equal {same}/{total}", flush=True)
