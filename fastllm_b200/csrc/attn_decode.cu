@@ -12,6 +12,7 @@
 //
 // Page pools must be zero-initialised: the unused tail of a request's last page is multiplied by P = 0.
 #include "ptx.cuh"
+#include "launch.h"
 #include "tmap.h"
 
 FB_DEFINE_ERROR_API(attn_decode)
@@ -45,6 +46,8 @@ struct AttnDecodeParams {
 __global__ void attn_decode_plan_kernel(const int* __restrict__ seq_lens, int B, int* __restrict__ work, int* __restrict__ n_work,
                                         int max_items) {
   __shared__ int offs[1025];
+  pdl_launch_dependents();
+  pdl_wait();
   // single CTA; B <= 1024
   const int t = threadIdx.x;
   int np = 0;
@@ -89,11 +92,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   float* red_sum = red_max + 64;                                  // [2 parity][4 warps][16]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  int n_items = *p.n_work;
-  if (n_items < 0) n_items = 0;
-  if (n_items > p.max_items) n_items = p.max_items;   // never trust a count read from memory beyond the list's capacity
-  const int total = n_items * p.Hkv;
   bool dead = false;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < AD_STAGES; ++s) { mbar_init(&full_k[s], 1); mbar_init(&full_v[s], 1); mbar_init(&empty_k[s], 1); mbar_init(&empty_v[s], 1); }
@@ -110,6 +110,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   tc_fence_after_sync();
   const uint32_t tmem_s = *tmem_slot;        // columns [0,16): S^T, [16,32): O^T
   const uint32_t tmem_o = tmem_s + 16;
+  pdl_wait();   // everything above touches only this CTA's shared memory and TMEM
+  int n_items = *p.n_work;
+  if (n_items < 0) n_items = 0;
+  if (n_items > p.max_items) n_items = p.max_items;   // never trust a count read from memory beyond the list's capacity
+  const int total = n_items * p.Hkv;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -258,6 +263,8 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
                                            int Hkv, int G, int max_splits) {
   const int b = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
   const int kvh = hq / G, g = hq - kvh * G;
+  pdl_launch_dependents();
+  pdl_wait();
   const int seq = seq_lens[b];
   const int ns = (seq + AD_PAGE - 1) / AD_PAGE;
   const size_t base = (size_t)(b * Hkv + kvh) * max_splits;
@@ -283,7 +290,7 @@ extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n
   if (B <= 0 || B > 1024) return -1;
   int threads = 32;
   while (threads < B) threads <<= 1;
-  attn_decode_plan_kernel<<<1, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(seq_lens, B, work, n_work, max_items);
+  launch_k(attn_decode_plan_kernel, dim3(1), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream), 0, seq_lens, B, work, n_work, max_items);
   return (int)cudaGetLastError();
 }
 
@@ -325,8 +332,8 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
   {                                                                                                                     \
     static bool cfg = false;                                                                                            \
     if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); cfg = true; } \
-    attn_decode_kernel<BF, ST><<<grid_ctas, 192, ad_smem_bytes(ST), stream>>>(tmK, tmV, tmQ, p);                         \
-    attn_decode_combine_kernel<BF><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits); \
+    launch_k<PDL_ATTN>(attn_decode_kernel<BF, ST>, dim3(grid_ctas), dim3(192), ad_smem_bytes(ST), stream, 0, tmK, tmV, tmQ, p);                         \
+    launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits); \
   }
   if (dtype == 1) { if (deep) FB_AD_LAUNCH(true, 3) else FB_AD_LAUNCH(true, 1) }
   else { if (deep) FB_AD_LAUNCH(false, 3) else FB_AD_LAUNCH(false, 1) }

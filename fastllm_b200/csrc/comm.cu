@@ -23,6 +23,7 @@
 // of a launch must be co-resident (they wait for each other across ranks): launchers check the grid
 // against the SM count.
 #include "gemm_smallm.cuh"
+#include "launch.h"
 #include "tmap.h"
 
 FB_DEFINE_ERROR_API(comm)
@@ -246,10 +247,12 @@ template <int MPAD, bool BF16>
 __global__ void __launch_bounds__(192, 1)
 gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams g,
                     const ArNormParams p) {
-  const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
-  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) reinterpret_cast<uint64_t*>(p.c.local + OFF_TRACE)[0] = globaltimer_ns();
+  const uint64_t t_start = p.trace ? globaltimer_ns() : 0;
   uint32_t tmem_base;
   gemm_smallm_device<MPAD, BF16>(tmW, tmX, g, tmem_base, KID_GEMM_AR);
+  // every thread has passed the dependency wait inside the GEMM: the expect word written by the previous collective is final
+  const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) reinterpret_cast<uint64_t*>(p.c.local + OFF_TRACE)[0] = t_start;
   if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD>::TMEM_COLS);
   // cluster = the gridDim.x k-split CTAs of one weight tile
   ar_norm_tail<BF16>(p, base, blockIdx.y, gridDim.y, blockIdx.x, gridDim.x, KID_GEMM_AR);
@@ -257,6 +260,8 @@ gemm_ar_norm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
 
 template <bool BF16>
 __global__ void __launch_bounds__(192, 1) ar_norm_kernel(const ArNormParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
   if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) reinterpret_cast<uint64_t*>(p.c.local + OFF_TRACE)[0] = globaltimer_ns();
   // phase 1: push this rank's partial rows to their owners (slot = this rank)
@@ -308,6 +313,8 @@ struct ArgmaxMergeParams {
 __global__ void argmax_merge_kernel(const ArgmaxMergeParams p) {
   __shared__ int sh_ok;
   const CommCtx& c = p.c;
+  pdl_launch_dependents();
+  pdl_wait();
   const uint32_t base = *reinterpret_cast<volatile uint32_t*>(c.local + OFF_EXPECT);
   const uint32_t target = base + (uint32_t)c.tp;
   const int tid = threadIdx.x;
@@ -379,10 +386,10 @@ static cudaError_t launch_gemm_ar(const CUtensorMap& tmW, const CUtensorMap& tmX
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
   // all CTAs wait for each other across ranks: they must all be resident at once
   int max_clusters = 0;
   if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) == cudaSuccess && max_clusters > 0 && n_tiles > max_clusters)
@@ -451,10 +458,10 @@ static int launch_ar_norm(ArNormParams& p, int M, int N, int tp, int dtype, cuda
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = 0;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cs; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
   if (dtype == 1) return (int)cudaLaunchKernelEx(&cfg, ar_norm_kernel<true>, p);
   return (int)cudaLaunchKernelEx(&cfg, ar_norm_kernel<false>, p);
 }
@@ -495,6 +502,6 @@ extern "C" int fb_argmax_merge(const float* vals, const int* ids, int* out, int 
   ArgmaxMergeParams p;
   fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
   p.off_buf = off_buf; p.vals = vals; p.ids = ids; p.out = out; p.B = B;
-  argmax_merge_kernel<<<1, 256, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(p);
+  launch_k(argmax_merge_kernel, dim3(1), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream_), 0, p);
   return (int)cudaGetLastError();
 }

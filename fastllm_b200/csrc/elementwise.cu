@@ -9,6 +9,7 @@
 //   greedy sampling                      src/devices/cuda/fastllm-cuda.cu:13579-13784
 //   SelectExpert                         src/devices/cpu/cpudevice.cpp:8885-8955
 #include "ptx.cuh"
+#include "launch.h"
 
 FB_DEFINE_ERROR_API(elementwise)
 
@@ -43,6 +44,8 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 template <bool BF16>
 __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
                                uint16_t* residual, int H, int ldx, int ldy, float eps, float unit_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sh[32];
   extern __shared__ float rowbuf[];   // H floats
   const int row = blockIdx.x;
@@ -104,6 +107,8 @@ struct QkvPostParams {
 
 template <bool BF16>
 __global__ void qkv_post_kernel(const QkvPostParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warps_per_block = blockDim.x >> 5;
   const int gw = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -214,6 +219,8 @@ __global__ void qkv_post_kernel(const QkvPostParams p) {
 // ------------------------------------------------------------------------------------------------
 template <bool BF16>
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int I, int ldx, int ldy) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t total = (size_t)M * (I / 8);
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
     const int m = (int)(idx / (I / 8)), c = (int)(idx % (I / 8)) * 8;
@@ -235,6 +242,8 @@ __global__ void silu_mul_kernel(const uint16_t* __restrict__ x, uint16_t* __rest
 // ------------------------------------------------------------------------------------------------
 __global__ void embedding_kernel(const int* __restrict__ ids, const uint16_t* __restrict__ table, uint16_t* __restrict__ out,
                                  int H, int vocab) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x;
   int id = ids[m];
   if (id < 0 || id >= vocab) id = 0;
@@ -250,6 +259,8 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const uint16_t* __
 template <int KIND>  // 0 = f32, 1 = bf16, 2 = f16
 __global__ void argmax_kernel(const void* __restrict__ logits, int* __restrict__ ids, float* __restrict__ vals, int V, int ld,
                               int id_offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float sv[32];
   __shared__ int si[32];
   const int m = blockIdx.x;
@@ -296,6 +307,8 @@ struct RouteParams {
   float route_scale;
 };
 __global__ void route_topk_kernel(const RouteParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int gw = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (gw >= p.M) return;
   const float* lg = p.logits + (size_t)gw * p.E;
@@ -391,11 +404,11 @@ extern "C" int fb_rmsnorm(const void* x, const void* w, void* y, void* residual,
   if (dtype == 1) {
     static bool cfg = false;
     if (!cfg) { cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); cfg = true; }
-    rmsnorm_kernel<true><<<M, threads, smem, s>>>((const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
+    launch_k(rmsnorm_kernel<true>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
   } else {
     static bool cfg = false;
     if (!cfg) { cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); cfg = true; }
-    rmsnorm_kernel<false><<<M, threads, smem, s>>>((const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
+    launch_k(rmsnorm_kernel<false>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
   }
   return (int)cudaGetLastError();
 }
@@ -415,8 +428,8 @@ extern "C" int fb_qkv_post(const void* qkv, int ld_qkv, void* q_out, int ld_q, v
   const int wpb = 8;
   const int blocks = (int)((warps + wpb - 1) / wpb);
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == 1) qkv_post_kernel<true><<<blocks, wpb * 32, 0, s>>>(p);
-  else qkv_post_kernel<false><<<blocks, wpb * 32, 0, s>>>(p);
+  if (dtype == 1) launch_k(qkv_post_kernel<true>, dim3(blocks), dim3(wpb * 32), 0, s, 0, p);
+  else launch_k(qkv_post_kernel<false>, dim3(blocks), dim3(wpb * 32), 0, s, 0, p);
   return (int)cudaGetLastError();
 }
 
@@ -427,15 +440,15 @@ extern "C" int fb_silu_mul(const void* x, void* y, int M, int I, int ldx, int ld
   int blocks = (int)((total + 255) / 256);
   if (blocks > 148 * 16) blocks = 148 * 16;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == 1) silu_mul_kernel<true><<<blocks, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
-  else silu_mul_kernel<false><<<blocks, 256, 0, s>>>((const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
+  if (dtype == 1) launch_k(silu_mul_kernel<true>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
+  else launch_k(silu_mul_kernel<false>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
   return (int)cudaGetLastError();
 }
 
 extern "C" int fb_embedding(const int* ids, const void* table, void* out, int M, int H, int vocab, void* stream) {
   if (M <= 0) return 0;
   if (H % 8 != 0) return -1;
-  embedding_kernel<<<M, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(ids, (const uint16_t*)table, (uint16_t*)out, H, vocab);
+  launch_k(embedding_kernel, dim3(M), dim3(256), 0, reinterpret_cast<cudaStream_t>(stream), 0, ids, (const uint16_t*)table, (uint16_t*)out, H, vocab);
   return (int)cudaGetLastError();
 }
 
@@ -443,9 +456,9 @@ extern "C" int fb_embedding(const int* ids, const void* table, void* out, int M,
 extern "C" int fb_argmax(const void* logits, int* ids, float* vals, int M, int V, int ld, int id_offset, int kind, void* stream) {
   if (M <= 0) return 0;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (kind == 0) argmax_kernel<0><<<M, 1024, 0, s>>>(logits, ids, vals, V, ld, id_offset);
-  else if (kind == 1) argmax_kernel<1><<<M, 1024, 0, s>>>(logits, ids, vals, V, ld, id_offset);
-  else argmax_kernel<2><<<M, 1024, 0, s>>>(logits, ids, vals, V, ld, id_offset);
+  if (kind == 0) launch_k(argmax_kernel<0>, dim3(M), dim3(1024), 0, s, 0, logits, ids, vals, V, ld, id_offset);
+  else if (kind == 1) launch_k(argmax_kernel<1>, dim3(M), dim3(1024), 0, s, 0, logits, ids, vals, V, ld, id_offset);
+  else launch_k(argmax_kernel<2>, dim3(M), dim3(1024), 0, s, 0, logits, ids, vals, V, ld, id_offset);
   return (int)cudaGetLastError();
 }
 
@@ -455,6 +468,6 @@ extern "C" int fb_route_topk(const float* logits, const float* bias, int* out_id
   if (E > 512 || topk > 32 || n_group > 32 || (n_group > 1 && E % n_group != 0)) return -1;
   RouteParams p{logits, bias, out_idx, out_w, M, E, topk, score_mode, renorm, n_group, topk_group, route_scale};
   const int wpb = 4;
-  route_topk_kernel<<<(M + wpb - 1) / wpb, wpb * 32, 0, reinterpret_cast<cudaStream_t>(stream)>>>(p);
+  launch_k(route_topk_kernel, dim3((M + wpb - 1) / wpb), dim3(wpb * 32), 0, reinterpret_cast<cudaStream_t>(stream), 0, p);
   return (int)cudaGetLastError();
 }

@@ -18,6 +18,7 @@
 // SwiGLU epilogue expects the gate/up weight rows interleaved per 128-row tile: rows [0,64) of tile t are
 // gate rows 64t..64t+63 and rows [64,128) are the matching up rows; output column = 64t + i.
 #include "ptx.cuh"
+#include "launch.h"
 #include "tmap.h"
 
 FB_DEFINE_ERROR_API(gemm)
@@ -220,13 +221,13 @@ static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX,
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = nsplit;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = add_pdl_attr(attr, 1);
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
 }
 

@@ -16,6 +16,7 @@
 //   then the shared cluster split-K reduce + epilogue (gemm_smallm.cuh)
 // Weight bytes cross HBM once, in packed form: the kernel is bound by 0.5 / 1 byte per weight.
 #include "gemm_smallm.cuh"
+#include "launch.h"
 #include "tmap.h"
 
 FB_DEFINE_ERROR_API(gemm_quant)
@@ -92,6 +93,7 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
   if (kb_cnt > p.kb_per_split) kb_cnt = p.kb_per_split;
   if (kb_cnt < 0) kb_cnt = 0;
   bool dead = false;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 129); }
@@ -112,7 +114,15 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
       constexpr int KBYTES = QM == Q_INT4G ? 32 : 64;            // packed bytes per 64-wide k block
-      for (int i = 0; i < kb_cnt; ++i) {
+      // packed weights are independent of the kernel before this one: request the first ring before the dependency wait
+      const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(stages + i * PITCH + Cfg::B_BYTES, &tmW, &full_bar[i], (kb0 + i) * KBYTES, p.w_row0 + n_tile * 128, pol_w);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i) tma_load_2d_hint(stages + i * PITCH, &tmX, &full_bar[i], (kb0 + i) * 64, p.x_row0, pol_x);
+      for (int i = pre; i < kb_cnt; ++i) {
         const int s = i % Cfg::STAGES;
         const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_QUANT, 1)) break;
@@ -123,6 +133,7 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
       }
     }
     __syncwarp();
+    pdl_wait();
   } else if (warp == 1) {
     if (elect_one()) {
       for (int i = 0; i < kb_cnt; ++i) {
@@ -238,6 +249,7 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
       mbar_arrive(&empty_bar[s]);
     }
     // ------------------------------ epilogue: TMEM -> fp32 partial tile ------------------------------
+    pdl_wait();
     float* P = reinterpret_cast<float*>(smem);
     const int n_local = q * 32 + lane;
     float row_scale = 1.f;
@@ -285,6 +297,8 @@ __global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
 moe_grouped_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                          const QuantParams qbase, const QuantGroupInfo gi) {
   const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  pdl_launch_dependents();
+  pdl_wait();   // counts / offsets come from the plan kernel
   const int cnt = gi.counts[e];
   const int row0 = chunk * gi.rows_per_chunk;
   if (row0 >= cnt) return;
@@ -322,10 +336,10 @@ static cudaError_t launch_quant(const CUtensorMap& tmW, const CUtensorMap& tmX, 
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, qp);
 }
 
@@ -402,10 +416,10 @@ static cudaError_t launch_grouped_quant(const CUtensorMap& tmW, const CUtensorMa
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, qp, gi);
 }
 

@@ -139,6 +139,7 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
   if (kb_cnt > p.kb_per_split) kb_cnt = p.kb_per_split;
   if (kb_cnt < 0) kb_cnt = 0;
   bool dead = false;
+  pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -157,7 +158,17 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
     if (elect_one()) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
-      for (int i = 0; i < kb_cnt; ++i) {
+      // Weights do not depend on the kernel before this one: the first ring of weight tiles is requested before the
+      // dependency wait, so the weight stream starts while that kernel drains.  Activations follow the wait.
+      const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, p.w_row0 + n_tile * 128, pol_w);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmX, &full_bar[i], (kb0 + i) * 64, p.x_row0, pol_x);
+      for (int i = pre; i < kb_cnt; ++i) {
         const int s = i % Cfg::STAGES;
         const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_SMALLM, 1)) break;
@@ -168,7 +179,9 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
       }
     }
     __syncwarp();
+    pdl_wait();
   } else if (warp == 1) {
+    pdl_wait();
     if (elect_one()) {
       for (int i = 0; i < kb_cnt; ++i) {
         const int s = i % Cfg::STAGES;
@@ -190,6 +203,7 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
     const int q = warp & 3;
     float* P = reinterpret_cast<float*>(smem);
     const int n_local = q * 32 + lane;
+    pdl_wait();
     if (kb_cnt > 0) {
       mbar_wait(accum_bar, 0, dead, KID_GEMM_SMALLM, 3);
       tc_fence_after_sync();

@@ -13,6 +13,7 @@
 // kernels ("Grouped...Indexed", src/devices/cuda/moe/fastllm-moe-fp8.cu; route count/offset/scatter in
 // fastllm-moe-vllm-marlin.cu:405-528), which run the expert FFNs as CUDA-core GEMVs or Marlin mma.sync.
 #include "gemm_smallm.cuh"
+#include "launch.h"
 #include "tmap.h"
 
 FB_DEFINE_ERROR_API(moe)
@@ -37,6 +38,8 @@ __global__ void moe_plan_kernel(const int* __restrict__ idx, int T, int topk, in
   __shared__ int s_cnt[1024];
   __shared__ int s_off[1025];
   const int e = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const int pairs = T * topk;
   int c = 0;
   if (e < n_local) {
@@ -72,6 +75,8 @@ __global__ void moe_plan_small_kernel(const int* __restrict__ idx, int pairs, in
   __shared__ int s_idx[4096];
   __shared__ int s_cnt[1024];
   __shared__ int s_off[1024];
+  pdl_launch_dependents();
+  pdl_wait();
   for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
     const int e = idx[i] - first;
     s_idx[i] = (e >= 0 && e < n_local) ? e : -1;
@@ -112,6 +117,8 @@ __global__ void moe_plan_small_kernel(const int* __restrict__ idx, int pairs, in
 __global__ void moe_gather_kernel(const uint16_t* __restrict__ x, const int* __restrict__ pos, uint16_t* __restrict__ xs, int T,
                                   int topk, int H) {
   const int pair = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = pos[pair];
   if (r < 0) return;
   const int t = pair / topk;
@@ -124,6 +131,8 @@ template <bool BF16>
 __global__ void moe_combine_kernel(const uint16_t* __restrict__ ys, const int* __restrict__ pos, const float* __restrict__ w,
                                    const uint16_t* __restrict__ add, uint16_t* __restrict__ out, int topk, int H) {
   const int t = blockIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
   for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (int k = 0; k < topk; ++k) {
@@ -153,6 +162,8 @@ __global__ void __launch_bounds__(192, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                         const MoeGroupInfo gi) {
   const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  pdl_launch_dependents();
+  pdl_wait();   // counts / offsets come from the plan kernel
   const int cnt = gi.counts[e];
   const int row0 = chunk * gi.rows_per_chunk;
   if (row0 >= cnt) return;                          // uniform over the cluster (same blockIdx.z)
@@ -186,10 +197,10 @@ static cudaError_t launch_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr; cfg.numAttrs = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, gi);
 }
 
@@ -201,20 +212,20 @@ extern "C" int fb_moe_plan(const int* idx, int T, int topk, int first, int n_loc
                            int* total_rows, int pad, void* stream) {
   if (n_local <= 0 || n_local > 1024 || T <= 0) return -1;
   if (T * topk <= 4096) {
-    moe_plan_small_kernel<<<1, 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(idx, T * topk, first, n_local, counts, offsets, pos, total_rows, pad);
+    launch_k(moe_plan_small_kernel, dim3(1), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), 0, idx, T * topk, first, n_local, counts, offsets, pos, total_rows, pad);
     return (int)cudaGetLastError();
   }
   int threads = 32;
   while (threads < n_local) threads <<= 1;
   if (threads < 256) threads = 256;
-  moe_plan_kernel<<<1, threads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(idx, T, topk, first, n_local, counts, offsets, pos, total_rows, pad);
+  launch_k(moe_plan_kernel, dim3(1), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream), 0, idx, T, topk, first, n_local, counts, offsets, pos, total_rows, pad);
   return (int)cudaGetLastError();
 }
 
 extern "C" int fb_moe_gather(const void* x, const int* pos, void* xs, int T, int topk, int H, void* stream) {
   if (T <= 0) return 0;
   if (H % 8 != 0) return -1;
-  moe_gather_kernel<<<T * topk, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>((const uint16_t*)x, pos, (uint16_t*)xs, T, topk, H);
+  launch_k(moe_gather_kernel, dim3(T * topk), dim3(128), 0, reinterpret_cast<cudaStream_t>(stream), 0, (const uint16_t*)x, pos, (uint16_t*)xs, T, topk, H);
   return (int)cudaGetLastError();
 }
 
@@ -223,8 +234,8 @@ extern "C" int fb_moe_combine(const void* ys, const int* pos, const float* w, co
   if (T <= 0) return 0;
   if (H % 8 != 0) return -1;
   auto s = reinterpret_cast<cudaStream_t>(stream);
-  if (dtype == 1) moe_combine_kernel<true><<<T, 256, 0, s>>>((const uint16_t*)ys, pos, w, (const uint16_t*)add, (uint16_t*)out, topk, H);
-  else moe_combine_kernel<false><<<T, 256, 0, s>>>((const uint16_t*)ys, pos, w, (const uint16_t*)add, (uint16_t*)out, topk, H);
+  if (dtype == 1) launch_k(moe_combine_kernel<true>, dim3(T), dim3(256), 0, s, 0, (const uint16_t*)ys, pos, w, (const uint16_t*)add, (uint16_t*)out, topk, H);
+  else launch_k(moe_combine_kernel<false>, dim3(T), dim3(256), 0, s, 0, (const uint16_t*)ys, pos, w, (const uint16_t*)add, (uint16_t*)out, topk, H);
   return (int)cudaGetLastError();
 }
 
