@@ -114,7 +114,19 @@ class model:
         elif path and path.endswith(".gguf"):
             from .loader import gguf
 
-            self.torch_model = gguf.load_model(path, device=dev, ori=ori_model_path or None)
+            self.torch_model = gguf.load_model(path, device=dev, ori=ori_model_path or None, tp=tp)
+            meta = self.torch_model.gguf_meta
+            if ori_model_path and os.path.isdir(ori_model_path):
+                self.tokenizer = Tokenizer(ori_model_path, prefer_native=(tokenizer_type == "native"), chat_template=tpl)
+                self.hf_tokenizer = self.tokenizer.hf
+            elif self.tokenizer.hf is None and self.tokenizer.native is None:
+                from .tokenizer import NativeBPE
+
+                tj = gguf.tokenizer_json_from_meta(meta)
+                if tj is not None:
+                    self.tokenizer.native = NativeBPE(tj)
+                if self.tokenizer.chat_template is None and isinstance(meta.get("tokenizer.chat_template"), str):
+                    self.tokenizer.chat_template = meta["tokenizer.chat_template"]
         else:
             self.torch_model = hf_loader.load_model(path, device=dev, wdtype=dtype or "auto", moe_wdtype=moe_dtype or None, tp=tp,
                                                     dtype_config=dtype_config or None)
