@@ -90,9 +90,44 @@ def build_runtime(force: bool = False) -> Path:
     return out
 
 
+CPU_MATH = ["-fno-math-errno", "-fno-trapping-math", "-fassociative-math", "-fno-signed-zeros"]
+CPU_ISA = {
+    "_avx2": ["-mavx2", "-mfma", "-mf16c"],
+    "_avx512": ["-mavx512f", "-mavx512bw", "-mavx512vl", "-mavx512dq", "-mavx2", "-mfma", "-mf16c"],
+}
+
+
+def build_cpu(force: bool = False) -> Path:
+    """Native CPU backend: the ISA-specific kernel file is compiled once per instruction set, the dispatcher once."""
+    OBJ.mkdir(exist_ok=True)
+    LIB.mkdir(exist_ok=True)
+    cpu = CSRC / "cpu"
+    headers = sorted(cpu.glob("*.h"))
+    out = LIB / "libfb_cpu.so"
+    base = ["g++", "-O3", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", *CPU_MATH, "-I", str(cpu)]
+    jobs, objs = [], []
+    for suffix, isa in CPU_ISA.items():
+        obj = OBJ / f"cpu_kernels{suffix}.o"
+        objs.append(obj)
+        if force or _newer(cpu / "cpu_kernels.cpp", headers, obj):
+            jobs.append(([*base, *isa, f"-DFB_ISA_SUFFIX={suffix}", "-c", str(cpu / "cpu_kernels.cpp"), "-o", str(obj)], None))
+    for name in ("cpu_ops", "cpu_model"):
+        obj = OBJ / f"{name}.o"
+        objs.append(obj)
+        if force or _newer(cpu / f"{name}.cpp", headers, obj):
+            jobs.append(([*base, "-march=x86-64-v3", "-c", str(cpu / f"{name}.cpp"), "-o", str(obj)], None))
+    if jobs:
+        with ThreadPoolExecutor(max_workers=len(jobs)) as ex:
+            list(ex.map(lambda j: _run(*j), jobs))
+    if force or jobs or not out.exists():
+        _run(["g++", "-shared", "-o", str(out), *map(str, objs), "-lpthread", "-lm"])
+    return out
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_runtime(force)
+    build_cpu(force)
 
 
 if __name__ == "__main__":

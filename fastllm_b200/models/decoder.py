@@ -280,6 +280,10 @@ class DecoderModel:
         """Returns fp32 logits ``[R, vocab_local]`` for ``fb.logit_rows`` (all rows if None)."""
         c = self.cfg
         T = fb.ids.shape[0]
+        if not self.on_cuda and T <= 32:
+            native = self._native_cpu()
+            if native is not None:
+                return native.forward(fb, kv_caches)
         fused = self.tp.comm.fused if (self.tp.size > 1 and self.tp.comm is not None) else None
         self._fused_active = bool(fused is not None and self.on_cuda and fused.usable(T, c.hidden_size))
         if fb.is_decode and self.on_cuda and fb.decode_ws is not None and not fb.decode_planned:
@@ -301,6 +305,14 @@ class DecoderModel:
         if c.logit_scale != 1.0:
             logits = logits * c.logit_scale
         return logits
+
+    def _native_cpu(self):
+        """The whole-model native CPU runner for this model, or None when the architecture is outside its coverage."""
+        if getattr(self, "_cpu_runner", None) is None:
+            from . import cpu_native
+
+            self._cpu_runner = cpu_native.NativeCpuModel(self) if cpu_native.eligible(self) else False
+        return self._cpu_runner or None
 
     def embed_tokens(self, ids):
         """Token embedding; the table is replicated on every tensor-parallel rank (no collective needed)."""

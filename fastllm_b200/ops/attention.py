@@ -14,8 +14,8 @@ import math
 
 import torch
 
-from . import _lib
-from .basic import _ptr, _stream, dtype_code
+from . import _lib, cpu
+from .basic import _ptr, _stream, cpu_native, dtype_code
 
 PAGE_LEN = 128
 ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
@@ -120,6 +120,19 @@ def qkv_post(qkv, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, h
     T = qkv.shape[0]
     Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
     rot = rot_dim or D
+    if cpu_native(qkv) and k_pool.dtype == torch.float32 and qkv.stride(-1) == 1:
+        q = qkv[:, :Hq * D].contiguous()
+        k = qkv[:, Hq * D:(Hq + Hkv) * D].contiguous()
+        v = qkv[:, (Hq + Hkv) * D:]
+        if q_norm_w is not None:
+            q = cpu.rmsnorm(q.view(T * Hq, D), q_norm_w, eps, norm_unit_offset).view(T, Hq * D)
+        if k_norm_w is not None:
+            k = cpu.rmsnorm(k.view(T * Hkv, D), k_norm_w, eps, norm_unit_offset).view(T, Hkv * D)
+        if rope_mode != ROPE_NONE:
+            cpu.rope_(q, positions, cos, sin, Hq, D, rot, rope_mode)
+            cpu.rope_(k, positions, cos, sin, Hkv, D, rot, rope_mode)
+        cpu.kv_append(k, v, slots, k_pool, v_pool)
+        return q
     if not qkv.is_cuda:
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
         q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
@@ -204,6 +217,8 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
     B = q.shape[0]
     if not q.is_cuda:
         cu = torch.arange(B + 1, dtype=torch.int32)
+        if cpu_native(q) and k_pool.dtype == torch.float32:
+            return cpu.attention_paged(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim)
         return paged_attention_ref(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim)
     G = num_q_heads // num_kv_heads
     if head_dim != 128 or G > 16 or k_pool.shape[1] != PAGE_LEN:
@@ -230,6 +245,8 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
 def attn_prefill(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim, out=None,
                  cu_q_host=None):
     """Packed causal prefill (also chunked prefill / prefix-cache continuation). q: ``[T, Hq*D]``."""
+    if cpu_native(q) and k_pool.dtype == torch.float32:
+        return cpu.attention_paged(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim)
     if not q.is_cuda or head_dim != 128 or k_pool.shape[1] != PAGE_LEN:
         o = paged_attention_ref(q, k_pool, v_pool, page_table, kv_lens.cpu(), cu_q.cpu(), scale, num_q_heads, num_kv_heads,
                                 head_dim)

@@ -12,7 +12,7 @@ import ctypes
 import torch
 import torch.nn.functional as F
 
-from . import _lib
+from . import _lib, cpu
 
 GEMM_BIAS, GEMM_RESIDUAL, GEMM_SWIGLU, GEMM_OUT_F32 = 1, 2, 4, 8
 
@@ -80,6 +80,25 @@ def linear_ref(x, w, bias=None, residual=None, swiglu=False, interleaved=True, o
     return y.to(out_dtype or x.dtype)
 
 
+def cpu_native(x: torch.Tensor) -> bool:
+    """True when ``x`` should run on the C++ CPU backend (fp32 CPU tensor and the library is built)."""
+    return (not x.is_cuda) and x.dtype == torch.float32 and cpu.available()
+
+
+def cpu_linear_epilogue(y, residual, swiglu, interleaved, out_dtype=None):
+    """SwiGLU / residual after a native CPU linear, in the same order as the fused CUDA epilogue."""
+    if swiglu:
+        if interleaved:
+            n = y.shape[-1]
+            t = y.reshape(*y.shape[:-1], n // 128, 2, 64)
+            y = (F.silu(t[..., 0, :]) * t[..., 1, :]).reshape(*y.shape[:-1], n // 2)
+        else:
+            y = cpu.swiglu(y)
+    if residual is not None:
+        y = y + residual.float()
+    return y if out_dtype is None else y.to(out_dtype)
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: bool = False, interleaved: bool = True,
            out_f32: bool = False, out: torch.Tensor | None = None, nsplit: int = 0) -> torch.Tensor:
     """``y = x @ w.T`` with optional fused bias, SwiGLU (``w`` = gate/up stacked) and residual add.
@@ -87,6 +106,10 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: b
     x: ``[M, K]`` (row stride may exceed K), w: ``[N, K]``.  16-bit CUDA tensors run the tcgen05 GEMM.
     """
     if not x.is_cuda:
+        # native kernels for decode-sized batches and for 16-bit weights (used in place); large fp32 GEMMs go to the BLAS
+        # behind torch.matmul
+        if cpu_native(x) and (x.numel() // x.shape[-1] <= 32 or w.dtype != torch.float32):
+            return cpu_linear_epilogue(cpu.linear(x, w, bias), residual, swiglu, interleaved)
         return linear_ref(x, w, bias, residual, swiglu, interleaved, torch.float32 if out_f32 else None)
     lead = x.shape[:-1]
     x2 = x.reshape(-1, x.shape[-1])
@@ -138,6 +161,11 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor
             out: torch.Tensor | None = None) -> torch.Tensor:
     """RMSNorm over the last dim.  With ``residual`` given: ``residual += x`` in place, then normalise it."""
     if not x.is_cuda:
+        if cpu_native(x) and (residual is None or residual.dtype == torch.float32):
+            if residual is not None:
+                residual.add_(x)
+                x = residual
+            return cpu.rmsnorm(x, w, eps, unit_offset)
         y, new_res = rmsnorm_ref(x, w, eps, residual, unit_offset)
         if residual is not None:
             residual.copy_(new_res)
@@ -161,6 +189,8 @@ def silu_mul(x: torch.Tensor) -> torch.Tensor:
     """``silu(x[..., :I]) * x[..., I:]``"""
     inter = x.shape[-1] // 2
     if not x.is_cuda:
+        if cpu_native(x):
+            return cpu.swiglu(x)
         g, u = x.float().chunk(2, dim=-1)
         return (F.silu(g) * u).to(x.dtype)
     x2 = x.reshape(-1, x.shape[-1])

@@ -149,6 +149,9 @@ class LinearWeight:
             if w.dtype != x.dtype:
                 w = w.to(x.dtype)
             return B.linear(x, w, self.bias, residual, swiglu, self.interleaved, out_f32)
+        if B.cpu_native(x) and self.kind in ("int8", "int4g"):
+            y = B.cpu.linear(x, self.w, self.bias, self.kind, self.scale, self.zero, self.group)
+            return B.cpu_linear_epilogue(y, residual, swiglu, self.interleaved)
         if x.is_cuda:
             from . import quant_gemm
 
