@@ -54,7 +54,8 @@ def run(args):
     except Exception as e:  # pragma: no cover
         _unavailable(f"torch/cuda not usable: {e!r}")
         return
-    if n_vis < args.gpus:
+    on_cpu = getattr(args, "device", "cuda") == "cpu"
+    if not on_cpu and n_vis < args.gpus:
         _unavailable(f"{args.gpus} GPUs requested, {n_vis} visible")
         return
     sys.path.insert(0, ROOT)
@@ -73,10 +74,11 @@ def run(args):
         _unavailable(f"import of the reference package failed: {e!r}"[:300])
         return
     B, P, O = args.batch, args.prompt_len, args.output_len
-    device = "cuda" if args.gpus == 1 else "multicuda:" + ",".join(str(i) for i in range(args.gpus))
+    device = "cpu" if on_cpu else ("cuda" if args.gpus == 1 else "multicuda:" + ",".join(str(i) for i in range(args.gpus)))
+    wdt = "float32" if on_cpu else "float16"
     # The reference's Llama path accepts fp32 / fp16 activations only ("Attention's input's type should be float32 or
     # float16" with bf16), so its arm runs the same 16-bit width in fp16.
-    argv = [model_dir, "--device", device, "--dtype", "float16", "--atype", "float16", "--max_batch", str(B),
+    argv = [model_dir, "--device", device, "--dtype", wdt, "--atype", wdt, "--max_batch", str(B),
             "--tokens", str(int(B * (P + O + 256) / 0.75)), "--page_size", "128"]
     parser = make_normal_parser("reference bench")
     rb.add_benchmark_args(parser)
@@ -141,7 +143,7 @@ def run(args):
     out = {
         "metric": "decode output tok/s (device-timed, max over ranks)", "value": B * K / secs, "unit": "tokens/s",
         "n_gpus": args.gpus, "steps": K, "warmup": W, "ms_per_step": secs / K * 1000.0, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (the reference's Llama path rejects bf16 activations)",
+        "scaling": "strong", "vs_baseline": None, "dtype": "fp32" if on_cpu else "fp16 (the reference's Llama path rejects bf16 activations)",
         "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
         "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O,
                    "parallelism": device, "timing": "wall clock at the reference's fetch loop (no device events in its API)"},

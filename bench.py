@@ -42,6 +42,8 @@ def parse_args():
     ap.add_argument("--dtype", default="auto", help="weight dtype: auto(bf16) | int8 | int4g128 | fp8")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
+                    help="cpu: the CPU configuration (fp32, C++ backend); use with --model qwen3-0.6b --batch 1 --prompt-len 128 --output-len 128")
     ap.add_argument("--moe-dtype", default="")
     ap.add_argument("--moe-tp", action="store_true", help="shard every expert over the ranks instead of expert parallelism")
     return ap.parse_args()
@@ -210,8 +212,57 @@ def run_ours(args):
     os._exit(0)
 
 
+def run_cpu(args):
+    """CPU configuration: fp32 weights and activations on the native C++ backend, wall-clock timed."""
+    import torch
+
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.models import preset, random_init
+    from fastllm_b200.ops import cpu
+
+    cfg = preset(args.model)
+    wd = args.dtype
+    model = random_init(cfg, "cpu", torch.float32, seed=0, wdtype=wd)
+    B, P, O = args.batch, args.prompt_len, args.output_len
+    eng = LLMEngine(model, EngineConfig(max_batch=B, max_context=((P + O + 127) // 128 + 1) * 128, use_cuda_graph=False,
+                                        prefix_cache=False), num_pages=B * ((P + O + 127) // 128 + 1) + 2)
+    gen = torch.Generator().manual_seed(1234)
+    prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=gen).tolist() for _ in range(B)]
+    for p in prompts:
+        eng.launch(p, GenerationConfig(max_new_tokens=O, ignore_eos=True))
+    t0 = time.perf_counter()
+    while any(r.state.name in ("WAITING", "PREFILL") for r in list(eng.requests.values())):
+        eng.step()
+    prefill_s = time.perf_counter() - t0
+    K, W = args.steps, args.warmup
+    if W + K > O - 1:
+        K = max(1, O - 1 - W)
+    for _ in range(W):
+        eng.step()
+    steps = []
+    for _ in range(K):
+        ts = time.perf_counter()
+        n = eng.step()
+        steps.append(time.perf_counter() - ts)
+        assert n == B
+    secs = sum(steps)
+    out = {"metric": "decode output tok/s (CPU, wall clock)", "value": B * K / secs, "unit": "tokens/s", "n_gpus": 0, "steps": K,
+           "warmup": W, "ms_per_step": secs / K * 1000.0, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+           "dtype": "fp32" if wd == "auto" else f"fp32 activations, {wd} weights",
+           "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
+           "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O, "device": "cpu",
+                      "threads": cpu.get_threads() if cpu.available() else None, "isa": cpu.lib().fbcpu_isa() if cpu.available() else None,
+                      "native_model_runner": bool(model._native_cpu() is not None)},
+           "e2e": {"value": B * K / secs, "unit": "tokens/s", "p50_tpot_ms": statistics.median(steps) * 1000.0, "ttft_s": prefill_s},
+           "gpu_launches": 0, "impl": "ours"}
+    print(json.dumps(out), flush=True)
+
+
 def main():
     args = parse_args()
+    if args.device == "cpu" and args.impl == "ours":
+        run_cpu(args)
+        return
     if args.impl == "reference":
         from baseline import reference_arm
 

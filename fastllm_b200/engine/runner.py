@@ -84,8 +84,8 @@ class ModelRunner:
 
     def _graph_safe(self) -> bool:
         c = self.model.cfg
-        if c.use_mla:
-            return False
+        if c.use_mla or self.model.general_attn or any(lw.attn.window or lw.attn.sinks is not None for lw in self.model.layers):
+            return False        # these paths evaluate attention with host-synchronising PyTorch ops
         if c.is_moe:
             # the per-expert fallback loop synchronises with the host; graphs need every MoE layer on the grouped kernels
             return all(lw.mlp.experts is None or lw.mlp.experts.stacked is not None for lw in self.model.layers)

@@ -63,7 +63,22 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
     a, f = lw.attn, lw.mlp
     g = lambda k: t.get(p + k)
     a.ln = _to(g("input_layernorm.weight"), m)
-    f.ln = _to(g("post_attention_layernorm.weight"), m)
+    if g("pre_feedforward_layernorm.weight") is not None:       # Gemma-2/3: pre- and post-norm around both sub-layers
+        a.post_ln = _to(g("post_attention_layernorm.weight"), m)
+        f.ln = _to(g("pre_feedforward_layernorm.weight"), m)
+        f.post_ln = _to(g("post_feedforward_layernorm.weight"), m)
+    else:
+        f.ln = _to(g("post_attention_layernorm.weight"), m)
+        a.post_ln = _to(g("post_self_attn_layernorm.weight"), m)     # GLM-4
+        f.post_ln = _to(g("post_mlp_layernorm.weight"), m)
+    if cfg.layer_windows is not None and i < len(cfg.layer_windows):
+        a.window = int(cfg.layer_windows[i])
+    elif cfg.sliding_window and cfg.sliding_window < cfg.max_position:
+        a.window = int(cfg.sliding_window)
+    rs = float(cfg.residual_scale)
+
+    def _rs(w):           # residual multiplier folded into the projections that feed the residual stream
+        return w if (w is None or rs == 1.0) else (w.float() * rs).to(w.dtype)
     r, n = tp.rank, tp.size
     base_w, base_mw = wdtype, (moe_wdtype or wdtype)
 
@@ -112,12 +127,31 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
             b = torch.cat([_heads_rows(bq, D, r * Hq_l, (r + 1) * Hq_l), _heads_rows(bk, D, kv0, kv0 + Hkv_l),
                            _heads_rows(bv, D, kv0, kv0 + Hkv_l)])
         a.qkv = _lin(m, w, W("self_attn.qkv_proj.weight"), b)
-        ob = g("self_attn.o_proj.bias")
-        a.o = _lin(m, _shard_cols(g("self_attn.o_proj.weight"), r, n), W("self_attn.o_proj.weight"), ob if (ob is not None and r == 0) else None)
-        a.q_norm = _to(g("self_attn.q_norm.weight"), m)
-        a.k_norm = _to(g("self_attn.k_norm.weight"), m)
+        ob = _rs(g("self_attn.o_proj.bias"))
+        a.o = _lin(m, _shard_cols(_rs(g("self_attn.o_proj.weight")), r, n), W("self_attn.o_proj.weight"), ob if (ob is not None and r == 0) else None)
+        qn, kn = g("self_attn.q_norm.weight"), g("self_attn.k_norm.weight")
+        if qn is None:
+            qn, kn = g("self_attn.query_layernorm.weight"), g("self_attn.key_layernorm.weight")     # Hunyuan names
+        a.q_norm, a.k_norm = _to(qn, m), _to(kn, m)
+        sk = g("self_attn.sinks")
+        if sk is not None:
+            a.sinks = sk[r * Hq_l:(r + 1) * Hq_l].to(m.device, torch.float32).contiguous()
     # ---- feed-forward ----
-    if cfg.layer_is_moe(i):
+    if cfg.layer_is_moe(i) and g("mlp.experts.gate_up_proj") is not None and cfg.moe_act == "gptoss":
+        # gpt-oss: stacked experts [E, H, 2I] with gate / up in alternating columns, biases on every projection
+        f.router = g("mlp.router.weight").to(m.device, torch.float32).contiguous()
+        f.router_logit_bias = g("mlp.router.bias").to(m.device, torch.float32).contiguous()
+        gup, gub = g("mlp.experts.gate_up_proj"), g("mlp.experts.gate_up_proj_bias")
+        dwn, dwb = g("mlp.experts.down_proj"), g("mlp.experts.down_proj_bias")
+        lo, hi = MOE.local_expert_range(cfg.num_experts, m.ep)
+        gu, dn = [], []
+        for e in range(lo, hi):
+            gw, uw = gup[e][:, 0::2].t().contiguous(), gup[e][:, 1::2].t().contiguous()
+            gu.append(_gate_up(m, gw, uw, MW("mlp.experts.gate_up_proj"), gub[e][0::2].contiguous(), gub[e][1::2].contiguous()))
+            dn.append(_lin(m, _rs(dwn[e].t().contiguous()), MW("mlp.experts.down_proj"), _rs(dwb[e])))
+        f.experts = MOE.ExpertWeights(cfg.num_experts, lo, gu, dn)
+        f.experts.act = "gptoss"
+    elif cfg.layer_is_moe(i):
         f.router = g("mlp.gate.weight").to(m.device, torch.float32).contiguous()
         rb = g("mlp.gate.e_score_correction_bias")
         f.router_bias = rb.to(m.device, torch.float32).contiguous() if rb is not None else None
@@ -147,7 +181,8 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         bg, bu, bd = g("mlp.gate_proj.bias"), g("mlp.up_proj.bias"), g("mlp.down_proj.bias")
         f.gate_up = _gate_up(m, _shard_rows(gw, r, n), _shard_rows(uw, r, n), W("mlp.gate_proj.weight"),
                              _shard_rows(bg, r, n) if bg is not None else None, _shard_rows(bu, r, n) if bu is not None else None)
-        f.down = _lin(m, _shard_cols(g("mlp.down_proj.weight"), r, n), W("mlp.down_proj.weight"), bd if (bd is not None and r == 0) else None)
+        bd = _rs(bd)
+        f.down = _lin(m, _shard_cols(_rs(g("mlp.down_proj.weight")), r, n), W("mlp.down_proj.weight"), bd if (bd is not None and r == 0) else None)
     while len(m.layers) <= i:
         m.layers.append(None)
     m.layers[i] = lw

@@ -37,6 +37,15 @@ class ModelConfig:
     embed_scale: float = 1.0
     logit_scale: float = 1.0
     sliding_window: int | None = None
+    layer_windows: list | None = None      # per-layer sliding window (0 = full attention) for alternating patterns
+    attn_softcap: float = 0.0              # tanh soft-capping of attention logits (Gemma-2)
+    final_softcap: float = 0.0             # tanh soft-capping of the output logits
+    attn_scale_override: float | None = None   # softmax scale when it is not 1/sqrt(head_dim)
+    residual_scale: float = 1.0            # multiplier of every sub-layer output before the residual add (folded into weights)
+    post_norms: bool = False               # sandwich norms: the sub-layer output is normalised before the residual add
+    qk_norm_after_rope: bool = False       # Hunyuan: per-head norm applied after the rotary embedding
+    attn_sinks: bool = False               # learned per-head sink logit in the softmax denominator (gpt-oss)
+    moe_act: str = "swiglu"                # swiglu | gptoss (clamped, alpha 1.702, (up + 1))
     # MoE
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -127,7 +136,7 @@ def from_hf_dict(d: dict) -> ModelConfig:
     c.bos_token_id = g("bos_token_id")
     c.quantization_config = g("quantization_config")
     c.torch_dtype = str(g("torch_dtype", g("dtype", "bfloat16"))).replace("torch.", "")
-    prf = g("partial_rotary_factor")
+    prf = g("partial_rotary_factor") or (rs.get("partial_rotary_factor") if isinstance(rs, dict) else None)
     if prf:
         c.rotary_dim = int(c.head_dim * float(prf))
     if mt in ("qwen3", "qwen3_moe"):
@@ -135,11 +144,41 @@ def from_hf_dict(d: dict) -> ModelConfig:
     if mt in ("gemma", "gemma2", "gemma3_text"):
         c.norm_unit_offset = 1.0
         c.embed_scale = float(c.hidden_size) ** 0.5
-    if mt in ("chatglm", "glm"):
-        c.rope_mode = "interleaved" if mt == "chatglm" else "neox"
+    if mt in ("chatglm", "glm", "glm4", "ernie4_5", "ernie4_5_moe"):
+        c.rope_mode = "interleaved"            # rotates adjacent pairs (x[2i], x[2i+1])
+    if mt == "glm4":
+        c.post_norms = True
+    if mt in ("gemma2", "gemma3_text"):
+        c.post_norms = True
+        c.attn_softcap = float(g("attn_logit_softcapping") or 0.0)
+        c.final_softcap = float(g("final_logit_softcapping") or 0.0)
+        if g("query_pre_attn_scalar"):
+            c.attn_scale_override = float(g("query_pre_attn_scalar")) ** -0.5
+    lt = g("layer_types")
+    if isinstance(lt, list) and c.sliding_window:
+        c.layer_windows = [int(c.sliding_window) if t == "sliding_attention" else 0 for t in lt]
+    if mt in ("hunyuan_v1_dense", "hunyuan_v1_moe"):
+        c.qk_norm = True
+        c.qk_norm_after_rope = True
+    if mt in ("granite", "granitemoe"):
+        c.attn_scale_override = float(g("attention_multiplier", c.head_dim ** -0.5))
+        c.embed_scale = float(g("embedding_multiplier", 1.0))
+        c.residual_scale = float(g("residual_multiplier", 1.0))
+        c.logit_scale = 1.0 / float(g("logits_scaling", 1.0))
+    if mt == "minicpm":
+        c.embed_scale = float(g("scale_emb", 1.0))
+        c.residual_scale = float(g("scale_depth", 1.0)) / (c.num_layers ** 0.5)
+        c.logit_scale = 1.0 / (c.hidden_size / float(g("dim_model_base", c.hidden_size)))
+    if mt == "gpt_oss":
+        c.attn_sinks = True
+        c.moe_act = "gptoss"
+        c.num_experts = g("num_local_experts", 0)
+        c.num_experts_per_tok = g("num_experts_per_tok", 4)
+        c.moe_intermediate_size = c.intermediate_size
+        c.norm_topk_prob = True
     # --- MoE families ---
     if mt in ("qwen3_moe", "qwen2_moe", "moe"):
-        c.num_experts = g("num_experts", 0)
+        c.num_experts = g("num_experts", g("num_local_experts", 0))
         c.num_experts_per_tok = g("num_experts_per_tok", 0)
         c.moe_intermediate_size = g("moe_intermediate_size", 0)
         c.norm_topk_prob = bool(g("norm_topk_prob", mt == "qwen3_moe"))

@@ -41,7 +41,9 @@ def eligible(model) -> bool:
     c = model.cfg
     if model.on_cuda or model.dtype != torch.float32 or model.tp.size != 1 or not cpu.available():
         return False
-    if c.use_mla or c.num_experts or c.hidden_act not in ("silu", "swiglu") or c.sliding_window:
+    if c.use_mla or c.num_experts or c.hidden_act not in ("silu", "swiglu") or c.post_norms or model.general_attn or c.final_softcap:
+        return False
+    if any(lw.attn.window or lw.attn.sinks is not None for lw in model.layers):
         return False
     for lw in model.layers:
         for lin in (lw.attn.qkv, lw.attn.o, lw.mlp.gate_up, lw.mlp.down):

@@ -61,6 +61,9 @@ class AttentionWeights:
         self.o: LinearWeight | None = None
         self.q_norm = None
         self.k_norm = None
+        self.post_ln = None      # sandwich norm on the attention output (Gemma-2 / GLM-4)
+        self.sinks = None        # per-head sink logits (gpt-oss)
+        self.window = 0          # sliding-window length of this layer (0: full causal attention)
         # MLA
         self.q_a: LinearWeight | None = None
         self.q_a_norm = None
@@ -76,10 +79,12 @@ class MLPWeights:
         self.ln = None
         self.gate_up: LinearWeight | None = None
         self.down: LinearWeight | None = None
+        self.post_ln = None      # sandwich norm on the MLP output
         # MoE
         self.router = None          # fp32 [E, H]
         self.router_16 = None       # 16-bit copy for the tensor-core router GEMM
-        self.router_bias = None     # fp32 [E]
+        self.router_bias = None     # fp32 [E]   selection-only correction bias (DeepSeek-V3)
+        self.router_logit_bias = None   # fp32 [E] bias of the router projection itself (gpt-oss)
         self.experts: MOE.ExpertWeights | None = None
         self.shared_gate_up: LinearWeight | None = None
         self.shared_down: LinearWeight | None = None
@@ -114,7 +119,9 @@ class DecoderModel:
         self._fused_active = False
         self.rope_mode = {"neox": A.ROPE_NEOX, "interleaved": A.ROPE_INTERLEAVED, "none": A.ROPE_NONE}[cfg.rope_mode]
         self.rot_dim = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
-        self.attn_scale = 1.0 / math.sqrt(cfg.q_head_dim)
+        self.attn_scale = cfg.attn_scale_override if cfg.attn_scale_override else 1.0 / math.sqrt(cfg.q_head_dim)
+        # families whose attention needs options outside the tensor-core kernels run the PyTorch evaluation (not graph-safe)
+        self.general_attn = bool(cfg.attn_softcap or cfg.attn_sinks or cfg.qk_norm_after_rope)
         if cfg.use_mla and cfg.rope_scaling and cfg.rope_scaling.get("mscale_all_dim"):
             ms = 0.1 * float(cfg.rope_scaling["mscale_all_dim"]) * math.log(float(cfg.rope_scaling.get("factor", 1.0))) + 1.0
             self.attn_scale *= ms * ms
@@ -153,6 +160,9 @@ class DecoderModel:
         cos, sin = self.rope_tables()
         qkv = lw.qkv(x)
         k_pool, v_pool = kv
+        if self.general_attn or lw.window or lw.sinks is not None:
+            a = self._attention_general(lw, qkv, fb, kv)
+            return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln)
         q = A.qkv_post(qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
                        lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
         if fb.is_decode:
@@ -161,7 +171,30 @@ class DecoderModel:
         else:
             a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
                                cu_q_host=fb.cu_q_host)
-        return self._row_parallel_norm(lw.o, a, residual, next_ln)
+        return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln)
+
+    def _attention_general(self, lw: AttentionWeights, qkv, fb: ForwardBatch, kv):
+        """Attention for the less common variants (sliding window, sinks, logit soft-capping, norm after RoPE)."""
+        c = self.cfg
+        Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
+        T = qkv.shape[0]
+        cos, sin = self.rope_tables()
+        q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+        q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
+        norm = lambda t, w: A._head_norm_ref(t, w, c.rms_eps, c.norm_unit_offset) if w is not None else t
+        if not c.qk_norm_after_rope:
+            q, k = norm(q, lw.q_norm), norm(k, lw.k_norm)
+        q = A.apply_rope_ref(q, fb.positions, cos, sin, self.rope_mode, self.rot_dim)
+        k = A.apply_rope_ref(k, fb.positions, cos, sin, self.rope_mode, self.rot_dim)
+        if c.qk_norm_after_rope:
+            q, k = norm(q, lw.q_norm), norm(k, lw.k_norm)
+        k_pool, v_pool = kv
+        valid = fb.slots >= 0
+        sl = fb.slots[valid].long()
+        k_pool.view(-1, Hkv, D)[sl] = k[valid].to(k_pool.dtype)
+        v_pool.view(-1, Hkv, D)[sl] = v[valid].to(v_pool.dtype)
+        return A.paged_attention_general(q.reshape(T, Hq * D).to(qkv.dtype), k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q,
+                                         self.attn_scale, Hq, Hkv, D, window=lw.window, sinks=lw.sinks, softcap=c.attn_softcap)
 
     def _row_parallel(self, w: LinearWeight, x, residual):
         """Row-parallel linear (input dim sharded): partial GEMM, then sum over ranks, plus the residual."""
@@ -172,12 +205,16 @@ class DecoderModel:
     def _norm(self, h, ln_w):
         return B.rmsnorm(h, ln_w, self.cfg.rms_eps, unit_offset=self.cfg.norm_unit_offset)
 
-    def _row_parallel_norm(self, w: LinearWeight, x, h, next_ln):
+    def _row_parallel_norm(self, w: LinearWeight, x, h, next_ln, post_ln=None):
         """``h += row_parallel_linear(x)`` then ``RMSNorm(h)`` for the next block.  Returns (h, x_norm).
 
         With the fused NVLink path this is ONE kernel (GEMM + reduce-scatter + residual + norm + all-gather).
         """
         c = self.cfg
+        if post_ln is not None:          # sandwich norm: normalise the sub-layer output, then add it to the residual stream
+            y = self._norm(self._row_parallel(w, x, None), post_ln)
+            h = h + y
+            return h, self._norm(h, next_ln)
         if self._fused_active:
             r = self.tp.comm.fused.gemm_ar_norm(w, x, next_ln, c.rms_eps, c.norm_unit_offset, True)
             if r is None:
@@ -234,6 +271,26 @@ class DecoderModel:
         o = torch.einsum("thl,hvl->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype).reshape(T, H * vd)
         return self._row_parallel_norm(lw.o, o, residual, next_ln)
 
+    @staticmethod
+    def _glu(gu, act: str, interleaved: bool):
+        """``act(gate) * up`` for gated MLPs whose activation is not SiLU (GeGLU of the Gemma family, ...)."""
+        if interleaved:
+            n = gu.shape[-1]
+            t = gu.reshape(*gu.shape[:-1], n // 128, 2, 64)
+            g, u = t[..., 0, :].reshape(*gu.shape[:-1], n // 2), t[..., 1, :].reshape(*gu.shape[:-1], n // 2)
+        else:
+            g, u = gu.chunk(2, dim=-1)
+        gf = g.float()
+        if act in ("gelu_pytorch_tanh", "gelu_new", "gelu_fast"):
+            a = torch.nn.functional.gelu(gf, approximate="tanh")
+        elif act == "gelu":
+            a = torch.nn.functional.gelu(gf)
+        elif act == "relu":
+            a = torch.relu(gf)
+        else:
+            raise ValueError(f"unsupported MLP activation '{act}'")
+        return (a * u.float()).to(gu.dtype)
+
     # -----------------------------------------------------------------------------------------------
     def _router_logits(self, lw: MLPWeights, x):
         """fp32 router logits.  On CUDA the router runs through the tensor-core GEMM with 16-bit operands and fp32
@@ -247,10 +304,15 @@ class DecoderModel:
     def _mlp(self, lw: MLPWeights, x, residual, layer_idx, next_ln):
         c = self.cfg
         if lw.experts is None:
-            act = lw.gate_up(x, swiglu=True)
-            return self._row_parallel_norm(lw.down, act, residual, next_ln)
+            if c.hidden_act in ("silu", "swiglu"):
+                act = lw.gate_up(x, swiglu=True)
+            else:
+                act = self._glu(lw.gate_up(x), c.hidden_act, lw.gate_up.interleaved)
+            return self._row_parallel_norm(lw.down, act, residual, next_ln, lw.post_ln)
         # ---- mixture of experts ----
         logits = self._router_logits(lw, x)
+        if lw.router_logit_bias is not None:
+            logits = logits + lw.router_logit_bias
         idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
                                   0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
                                   c.routed_scaling_factor)
@@ -285,7 +347,7 @@ class DecoderModel:
             if native is not None:
                 return native.forward(fb, kv_caches)
         fused = self.tp.comm.fused if (self.tp.size > 1 and self.tp.comm is not None) else None
-        self._fused_active = bool(fused is not None and self.on_cuda and fused.usable(T, c.hidden_size))
+        self._fused_active = bool(fused is not None and self.on_cuda and fused.usable(T, c.hidden_size) and not c.post_norms)
         if fb.is_decode and self.on_cuda and fb.decode_ws is not None and not fb.decode_planned:
             fb.decode_ws.plan(fb.kv_lens)
             fb.decode_planned = True
@@ -304,6 +366,8 @@ class DecoderModel:
         logits = self.lm_head(x, out_f32=True)
         if c.logit_scale != 1.0:
             logits = logits * c.logit_scale
+        if c.final_softcap:
+            logits = torch.tanh(logits / c.final_softcap) * c.final_softcap
         return logits
 
     def _native_cpu(self):

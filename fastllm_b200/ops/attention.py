@@ -59,8 +59,10 @@ def rope_inv_freq(rot_dim: int, base: float, scaling: dict | None = None, max_po
         orig = int(scaling.get("original_max_position_embeddings", 4096))
         beta_fast = float(scaling.get("beta_fast", 32))
         beta_slow = float(scaling.get("beta_slow", 1))
-        low = max(math.floor(_yarn_find_dim(beta_fast, rot_dim, base, orig)), 0)
-        high = min(math.ceil(_yarn_find_dim(beta_slow, rot_dim, base, orig)), rot_dim - 1)
+        low, high = _yarn_find_dim(beta_fast, rot_dim, base, orig), _yarn_find_dim(beta_slow, rot_dim, base, orig)
+        if scaling.get("truncate", True):          # gpt-oss keeps the fractional correction range
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, rot_dim - 1)
         if low == high:
             high += 0.001
         ramp = ((torch.arange(rot_dim // 2, dtype=torch.float64) - low) / (high - low)).clamp(0, 1)
@@ -187,6 +189,47 @@ def paged_attention_ref(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num
         kpos = torch.arange(L, device=q.device)[None, :]
         s = s.masked_fill(kpos > qpos, float("-inf"))
         p = torch.softmax(s, dim=-1)
+        o = torch.einsum("hgqk,khd->qhgd", p, v)
+        out[q0:q1] = o.reshape(q1 - q0, Hq * D).to(q.dtype)
+    return out
+
+
+def paged_attention_general(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim,
+                            window: int = 0, sinks=None, softcap: float = 0.0):
+    """Causal paged attention with the less common options, evaluated with PyTorch ops on any device:
+    sliding window (each query sees its last ``window`` positions), a per-head sink logit that only enters the softmax
+    denominator, and tanh soft-capping of the logits.  Used by the model families outside the tensor-core kernels' coverage
+    (reference: those families run on the old engine's generic Attention op, src/models/gpt_oss.cpp, src/models/gemma4.cpp)."""
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    G = Hq // Hkv
+    out = torch.zeros_like(q)
+    page_len = k_pool.shape[1]
+    cu = cu_q.tolist()
+    lens = kv_lens.tolist()
+    for b in range(len(cu) - 1):
+        q0, q1 = cu[b], cu[b + 1]
+        if q1 == q0:
+            continue
+        L = int(lens[b])
+        npg = (L + page_len - 1) // page_len
+        pages = page_table[b, :npg].long()
+        k = k_pool[pages].reshape(-1, Hkv, D)[:L].float()
+        v = v_pool[pages].reshape(-1, Hkv, D)[:L].float()
+        qq = q[q0:q1].reshape(q1 - q0, Hkv, G, D).float()
+        s = torch.einsum("qhgd,khd->hgqk", qq, k) * scale
+        if softcap:
+            s = torch.tanh(s / softcap) * softcap
+        qpos = torch.arange(L - (q1 - q0), L, device=q.device)[:, None]
+        kpos = torch.arange(L, device=q.device)[None, :]
+        mask = kpos > qpos
+        if window:
+            mask = mask | (kpos <= qpos - window)
+        s = s.masked_fill(mask, float("-inf"))
+        if sinks is not None:
+            sk = sinks.float().reshape(Hkv, G, 1, 1).expand(Hkv, G, q1 - q0, 1)
+            p = torch.softmax(torch.cat([s, sk], dim=-1), dim=-1)[..., :-1]
+        else:
+            p = torch.softmax(s, dim=-1)
         o = torch.einsum("hgqk,khd->qhgd", p, v)
         out[q0:q1] = o.reshape(q1 - q0, Hq * D).to(q.dtype)
     return out

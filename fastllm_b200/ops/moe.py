@@ -68,6 +68,20 @@ class ExpertWeights:
         self.gate_up = gate_up
         self.down = down
         self.stacked = None     # filled by ops.moe_grouped when a grouped kernel can take the whole set
+        self.act = "swiglu"     # "gptoss": clamped gate/up, gate * sigmoid(1.702 gate) * (up + 1)
+
+
+def glu_gptoss(gu, interleaved: bool, limit: float = 7.0, alpha: float = 1.702):
+    """gpt-oss expert activation on a ``[gate | up]`` projection (tile-interleaved when ``interleaved``)."""
+    if interleaved:
+        n = gu.shape[-1]
+        t = gu.reshape(*gu.shape[:-1], n // 128, 2, 64)
+        g, u = t[..., 0, :].reshape(*gu.shape[:-1], n // 2), t[..., 1, :].reshape(*gu.shape[:-1], n // 2)
+    else:
+        g, u = gu.chunk(2, dim=-1)
+    g = g.float().clamp(max=limit)
+    u = u.float().clamp(min=-limit, max=limit)
+    return ((u + 1.0) * (g * torch.sigmoid(g * alpha))).to(gu.dtype)
 
 
 def local_expert_range(num_experts: int, ep) -> tuple[int, int]:
@@ -90,7 +104,7 @@ def moe_forward(x, idx, wts, experts: ExpertWeights, ep=None):
     Tokens are grouped by expert; each non-empty local expert runs the two GEMMs on its token group.
     With expert parallelism the result is this rank's partial sum (the caller all-reduces it).
     """
-    if experts.stacked is not None and x.is_cuda:
+    if experts.stacked is not None and x.is_cuda and experts.act == "swiglu":
         from . import moe_grouped
 
         y = moe_grouped.forward(x, idx, wts, experts)
@@ -114,7 +128,10 @@ def moe_forward(x, idx, wts, experts: ExpertWeights, ep=None):
         rows = t_sorted[start:start + n]
         xe = x.index_select(0, rows)
         le = e - experts.first
-        he = experts.down[le](experts.gate_up[le](xe, swiglu=True))
+        if experts.act == "gptoss":
+            he = experts.down[le](glu_gptoss(experts.gate_up[le](xe), experts.gate_up[le].interleaved))
+        else:
+            he = experts.down[le](experts.gate_up[le](xe, swiglu=True))
         y.index_add_(0, rows, he.float() * w_sorted[start:start + n, None])
         start += n
     return y.to(x.dtype)
