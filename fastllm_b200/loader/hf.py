@@ -47,6 +47,11 @@ def dequant_awq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
 # name canonicalisation: every family is mapped onto the Llama naming that loader.shard understands
 # ---------------------------------------------------------------------------------------------------
 _RENAMES = [
+    # ChatGLM2/3 and original GLM-4 checkpoints
+    (r"^transformer\.embedding\.word_embeddings\.", "model.embed_tokens."), (r"^transformer\.encoder\.layers\.", "model.layers."),
+    (r"^transformer\.encoder\.final_layernorm\.", "model.norm."), (r"^transformer\.output_layer\.", "lm_head."),
+    (r"\.self_attention\.query_key_value\.", ".self_attn.qkv_proj."), (r"\.self_attention\.dense\.", ".self_attn.o_proj."),
+    (r"\.mlp\.dense_h_to_4h\.", ".mlp.gate_up_proj."), (r"\.mlp\.dense_4h_to_h\.", ".mlp.down_proj."),
     (r"^transformer\.h\.", "model.layers."), (r"^transformer\.wte\.", "model.embed_tokens."),
     (r"^transformer\.ln_f\.", "model.norm."), (r"^language_model\.model\.", "model."), (r"^language_model\.lm_head\.", "lm_head."),
     (r"^model\.language_model\.", "model."),

@@ -113,6 +113,11 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         kv0 = (r * cfg.num_kv_heads) // n if cfg.num_kv_heads >= n else r // m.kv_replicas
         if g("self_attn.qkv_proj.weight") is not None:        # already merged (phi3-style): [q | k | v]
             w = g("self_attn.qkv_proj.weight")
+            if cfg.model_type == "internlm2":
+                # InternLM2 groups the rows per KV head: [G query heads, 1 key head, 1 value head] x num_kv_heads
+                G = cfg.num_heads // cfg.num_kv_heads
+                wg = w.reshape(cfg.num_kv_heads, G + 2, D, w.shape[-1])
+                w = torch.cat([wg[:, :G].reshape(-1, w.shape[-1]), wg[:, G].reshape(-1, w.shape[-1]), wg[:, G + 1].reshape(-1, w.shape[-1])], dim=0)
             qw, kw, vw = w.split([cfg.num_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D], dim=0)
             bq = bk = bv = None
             if g("self_attn.qkv_proj.bias") is not None:

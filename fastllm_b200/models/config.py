@@ -146,6 +146,16 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.embed_scale = float(c.hidden_size) ** 0.5
     if mt in ("chatglm", "glm", "glm4", "ernie4_5", "ernie4_5_moe"):
         c.rope_mode = "interleaved"            # rotates adjacent pairs (x[2i], x[2i+1])
+    if mt == "chatglm":                        # ChatGLM2/3, GLM-4 original checkpoints (their own config keys)
+        c.vocab_size = g("padded_vocab_size", c.vocab_size)
+        c.rotary_dim = c.head_dim // 2
+        c.rope_theta = 10000.0 * float(g("rope_ratio", 1.0))
+        if not g("multi_query_attention", True):
+            c.num_kv_heads = c.num_heads
+    if mt == "qwen":                           # Qwen (v1): intermediate_size counts gate and up together
+        c.intermediate_size = g("intermediate_size", 2 * c.intermediate_size) // 2
+        c.attention_bias = True
+        c.num_kv_heads = c.num_heads
     if mt == "glm4":
         c.post_norms = True
     if mt in ("gemma2", "gemma3_text"):

@@ -74,3 +74,152 @@ def test_family_matches_transformers(name, tmp_path):
     assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
     assert (got - want).abs().max().item() < 2e-3
     assert int(got.argmax()) == int(want.argmax())
+
+
+def _save_renamed(ref, cfg_dict, rename, d, merge=None):
+    """Write ``ref``'s weights under another family's tensor names / layout with that family's config.json."""
+    import json
+    import os
+
+    from fastllm_b200.loader.safetensors import save_file
+
+    os.makedirs(d, exist_ok=True)
+    sd = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    if merge is not None:
+        sd = merge(sd)
+    out = {rename(k): v.contiguous() for k, v in sd.items()}
+    save_file(out, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg_dict, f)
+
+
+def _last_logits(m, prompt):
+    T = len(prompt)
+    eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512), num_pages=8)
+    fb = ForwardBatch(ids=torch.tensor(prompt, dtype=torch.int32), positions=torch.arange(T, dtype=torch.int32),
+                      slots=torch.arange(T, dtype=torch.int32), page_table=torch.tensor([[0, 1, 2, 3]], dtype=torch.int32),
+                      kv_lens=torch.tensor([T], dtype=torch.int32), cu_q=torch.tensor([0, T], dtype=torch.int32),
+                      logit_rows=torch.tensor([T - 1]), cu_q_host=[0, T])
+    return m.forward(fb, eng.runner.kv.pools)[0].float()
+
+
+def _tiny(model_type, **extra):
+    torch.manual_seed(0)
+    cfg = transformers.AutoConfig.for_model(model_type=model_type, **extra)
+    ref = transformers.AutoModelForCausalLM.from_config(cfg, torch_dtype=torch.float32)
+    for p in ref.parameters():
+        if p.dim() >= 2:
+            torch.nn.init.normal_(p, std=0.05)
+    return ref.eval()
+
+
+def test_chatglm_layout(tmp_path):
+    """ChatGLM2/3 / original GLM-4 checkpoints: own tensor names, packed QKV and [gate | up], own config keys."""
+    ref = _tiny("glm", **_C, partial_rotary_factor=0.5, pad_token_id=0)
+    prompt = list(range(7, 70, 2))
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+
+    def merge(sd):
+        out = {}
+        for k, v in sd.items():
+            if ".q_proj." in k:
+                kk, vv = k.replace(".q_proj.", ".k_proj."), k.replace(".q_proj.", ".v_proj.")
+                out[k.replace(".self_attn.q_proj.", ".self_attention.query_key_value.")] = torch.cat([v, sd[kk], sd[vv]], dim=0)
+            elif ".k_proj." in k or ".v_proj." in k:
+                continue
+            else:
+                out[k] = v
+        return out
+
+    def rename(k):
+        k = k.replace("model.embed_tokens.", "transformer.embedding.word_embeddings.").replace("model.layers.", "transformer.encoder.layers.")
+        k = k.replace("model.norm.", "transformer.encoder.final_layernorm.").replace("lm_head.", "transformer.output_layer.")
+        return k.replace(".self_attn.o_proj.", ".self_attention.dense.").replace(".mlp.gate_up_proj.", ".mlp.dense_h_to_4h.").replace(
+            ".mlp.down_proj.", ".mlp.dense_4h_to_h.")
+
+    cfgd = dict(model_type="chatglm", padded_vocab_size=512, hidden_size=256, num_layers=2, num_attention_heads=4, multi_query_attention=True,
+                multi_query_group_num=2, kv_channels=64, ffn_hidden_size=512, layernorm_epsilon=ref.config.rms_norm_eps, add_qkv_bias=True,
+                seq_length=512, rope_ratio=1.0, eos_token_id=2)
+    d = str(tmp_path / "chatglm")
+    _save_renamed(ref, cfgd, rename, d, merge)
+    got = _last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+
+
+def test_internlm2_and_minicpm_layouts(tmp_path):
+    """InternLM2 (grouped wqkv, w1/w3/w2 names) and MiniCPM (embedding / residual / logit scaling) from a llama oracle."""
+    ref = _tiny("llama", **_C)
+    prompt = list(range(9, 80, 2))
+    c = ref.config
+    G = c.num_attention_heads // c.num_key_value_heads
+
+    def merge(sd):
+        out = {}
+        for k, v in sd.items():
+            if ".q_proj." in k:
+                q = v.reshape(c.num_key_value_heads, G, 64, -1)
+                kk = sd[k.replace(".q_proj.", ".k_proj.")].reshape(c.num_key_value_heads, 1, 64, -1)
+                vv = sd[k.replace(".q_proj.", ".v_proj.")].reshape(c.num_key_value_heads, 1, 64, -1)
+                out[k.replace(".self_attn.q_proj.", ".attention.wqkv.")] = torch.cat([q, kk, vv], dim=1).reshape(-1, v.shape[-1])
+            elif ".k_proj." in k or ".v_proj." in k:
+                continue
+            else:
+                out[k] = v
+        return out
+
+    def rename(k):
+        k = k.replace("model.embed_tokens.", "model.tok_embeddings.").replace("lm_head.", "output.")
+        k = k.replace(".self_attn.o_proj.", ".attention.wo.").replace(".mlp.gate_proj.", ".feed_forward.w1.").replace(".mlp.up_proj.", ".feed_forward.w3.")
+        return k.replace(".mlp.down_proj.", ".feed_forward.w2.").replace(".input_layernorm.", ".attention_norm.").replace(".post_attention_layernorm.", ".ffn_norm.")
+
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+    cfgd = dict(c.to_dict(), model_type="internlm2")
+    d = str(tmp_path / "internlm2")
+    _save_renamed(ref, cfgd, rename, d, merge)
+    got = _last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+
+    # MiniCPM = llama with scale_emb, scale_depth / sqrt(layers) on every sub-layer output, logits / (hidden / dim_model_base):
+    # the same numbers come out of a Granite oracle with the equivalent multipliers.
+    ref2 = _tiny("granite", **_NH, attention_multiplier=(256 // 4) ** -0.5, embedding_multiplier=12.0, residual_multiplier=1.4 / (2 ** 0.5),
+                 logits_scaling=256 / 64)
+    with torch.no_grad():
+        want2 = ref2(torch.tensor([prompt])).logits[0, -1].float()
+    cfgd2 = dict(ref2.config.to_dict(), model_type="minicpm", scale_emb=12.0, scale_depth=1.4, dim_model_base=64)
+    d2 = str(tmp_path / "minicpm")
+    _save_renamed(ref2, cfgd2, lambda k: k, d2)
+    got2 = _last_logits(hf.load_model(d2, device="cpu", dtype=torch.float32), prompt)
+    assert torch.nn.functional.cosine_similarity(got2, want2, dim=0).item() > 0.99999
+
+
+def test_qwen_v1_layout(tmp_path):
+    """Qwen (v1): transformer.h.N.attn.c_attn / c_proj, mlp.w1 (up) / w2 (gate) / c_proj, ln_1 / ln_2, QKV bias."""
+    ref = _tiny("qwen2", **{**_NH, "num_key_value_heads": 4})
+    prompt = list(range(11, 90, 3))
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+
+    def merge(sd):
+        out = {}
+        for k, v in sd.items():
+            if ".q_proj." in k:
+                out[k.replace(".self_attn.q_proj.", ".attn.c_attn.")] = torch.cat([v, sd[k.replace(".q_proj.", ".k_proj.")], sd[k.replace(".q_proj.", ".v_proj.")]], dim=0)
+            elif ".k_proj." in k or ".v_proj." in k:
+                continue
+            else:
+                out[k] = v
+        return out
+
+    def rename(k):
+        k = k.replace("model.embed_tokens.", "transformer.wte.").replace("model.layers.", "transformer.h.").replace("model.norm.", "transformer.ln_f.")
+        k = k.replace(".self_attn.o_proj.", ".attn.c_proj.").replace(".mlp.gate_proj.", ".mlp.w2.").replace(".mlp.up_proj.", ".mlp.w1.")
+        return k.replace(".mlp.down_proj.", ".mlp.c_proj.").replace(".input_layernorm.", ".ln_1.").replace(".post_attention_layernorm.", ".ln_2.")
+
+    cfgd = dict(model_type="qwen", vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, kv_channels=64,
+                intermediate_size=1024, layer_norm_epsilon=ref.config.rms_norm_eps, seq_length=512, rotary_emb_base=ref.config.rope_parameters["rope_theta"])
+    d = str(tmp_path / "qwen")
+    _save_renamed(ref, cfgd, rename, d, merge)
+    got = _last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
