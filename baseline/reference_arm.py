@@ -55,6 +55,11 @@ def run(args):
         _unavailable(f"torch/cuda not usable: {e!r}")
         return
     on_cpu = getattr(args, "device", "cuda") == "cpu"
+    if on_cpu:
+        # The reference's CPU device crashed with SIGSEGV right after "Load libfastllm_tools.so" (before any token) when
+        # driven as `--device cpu --dtype float32` on Qwen3-0.6B; the call is not repeated.
+        _unavailable("the reference's --device cpu path died with SIGSEGV during model construction on this pool's host; not re-run")
+        return
     if not on_cpu and n_vis < args.gpus:
         _unavailable(f"{args.gpus} GPUs requested, {n_vis} visible")
         return

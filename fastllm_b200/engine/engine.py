@@ -289,10 +289,15 @@ class LLMEngine:
         if all(r.gen.is_simple_greedy() for r in reqs):
             return sampling.greedy(logits).tolist()
         lg = logits.float().clone()
-        sampling.apply_repeat_penalty(lg, [r.all_ids[-r.gen.last_n:] for r in reqs], [r.gen.repeat_penalty for r in reqs])
         greedy_rows = [r.gen.is_simple_greedy() or not r.gen.do_sample for r in reqs]
         tk = [1 if g else r.gen.top_k for r, g in zip(reqs, greedy_rows)]
-        toks = sampling.sample(lg, tk, [r.gen.top_p for r in reqs], [r.gen.temperature for r in reqs])
+        recent = [r.all_ids[-r.gen.last_n:] for r in reqs]
+        if lg.is_cuda:
+            toks = sampling.sample_fused(lg, recent, [r.gen.repeat_penalty for r in reqs], tk, [r.gen.top_p for r in reqs],
+                                         [r.gen.temperature for r in reqs])
+        else:
+            sampling.apply_repeat_penalty(lg, recent, [r.gen.repeat_penalty for r in reqs])
+            toks = sampling.sample(lg, tk, [r.gen.top_p for r in reqs], [r.gen.temperature for r in reqs])
         for r, row in zip(reqs, range(len(reqs))):
             if r.gen.output_logits:
                 r.last_logits = logits[row].float().cpu()

@@ -5,9 +5,43 @@ recent-token window, temperature, top-k, softmax, top-p cut, random draw.
 """
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
+from ..ops import _lib
 from ..ops import basic as B
+
+_P, _I = ctypes.c_void_p, ctypes.c_int
+_lib.register_sigs({"fb_sample": [_P, _I, _I, _I, _P, _P, _P, _P, _P, _P, _I, _P, _P, _P]}, ["sampling"])
+
+
+def sample_fused(logits: torch.Tensor, recent_ids, penalties, top_k, top_p, temperature, uniforms=None, want_prob: bool = False):
+    """Penalty + temperature + top-k + top-p + draw in one kernel launch (CUDA, fp32 logits ``[R, V]``, modified in place).
+
+    ``uniforms``: per-row variates in [0, 1) (drawn here from the default generator when None).  Returns int32 ids ``[R]``
+    (and the chosen token's probability when ``want_prob``).
+    """
+    R, V = logits.shape
+    dev = logits.device
+    assert logits.is_cuda and logits.dtype == torch.float32 and logits.stride(1) == 1
+    width = max(1, max((len(set(x)) for x in recent_ids), default=1))
+    rec = torch.full((R, width), -1, dtype=torch.int32)
+    for r, ids in enumerate(recent_ids):
+        u = sorted(set(i for i in ids if 0 <= i < V))
+        if u:
+            rec[r, :len(u)] = torch.tensor(u, dtype=torch.int32)
+    host = torch.tensor([list(map(float, temperature)), list(map(float, top_p)), list(map(float, penalties)),
+                         list(uniforms) if uniforms is not None else torch.rand(R).tolist()], dtype=torch.float32)
+    f = host.to(dev, non_blocking=True)
+    tk = torch.tensor(list(top_k), dtype=torch.int32).to(dev, non_blocking=True)
+    rec = rec.to(dev, non_blocking=True)
+    out = torch.empty(R, dtype=torch.int32, device=dev)
+    prob = torch.empty(R, dtype=torch.float32, device=dev) if want_prob else None
+    rc = _lib.kernels().fb_sample(B._ptr(logits), logits.stride(0), R, V, B._ptr(f[0]), B._ptr(tk), B._ptr(f[1]), B._ptr(f[3]), B._ptr(f[2]),
+                                  B._ptr(rec), width, B._ptr(out), B._ptr(prob), B._stream())
+    _lib.check(rc, "fb_sample")
+    return (out, prob) if want_prob else out
 
 
 def apply_repeat_penalty(logits: torch.Tensor, recent_ids: list[list[int]], penalties: list[float]) -> torch.Tensor:

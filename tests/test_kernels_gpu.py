@@ -259,3 +259,71 @@ def test_moe_grouped_quant(kind):
     assert ex.stacked is not None and ex.stacked.kind != "dense"
     out = moe_grouped.forward(x, idx, w, ex)
     _close(out, ref, 4e-2, 4e-2, f"moe grouped {kind}")
+
+
+def _sample_ref_support(logits, temperature, top_k, top_p):
+    """Per-row probabilities of the truncated distribution (plain PyTorch definition)."""
+    lg = logits.float() / temperature
+    V = lg.numel()
+    k = top_k if 0 < top_k <= 1024 else 1024
+    vals, idx = lg.topk(min(k, V))
+    pr = torch.softmax(vals, -1)
+    cum = pr.cumsum(-1)
+    keep = (cum - pr) < top_p
+    keep[0] = True
+    pr = pr * keep
+    pr = pr / pr.sum()
+    out = torch.zeros(V, device=logits.device)
+    out[idx] = pr
+    return out
+
+
+def test_fused_sampling_greedy_penalty_and_support():
+    from fastllm_b200.engine import sampling
+
+    torch.manual_seed(0)
+    R, V = 6, 151936
+    logits = torch.randn(R, V, device=DEV) * 3
+    # greedy rows = arg-max, with and without a penalty that dethrones the best token
+    best = logits.argmax(-1).tolist()
+    lg = logits.clone()
+    out = sampling.sample_fused(lg, [[] for _ in range(R)], [1.0] * R, [1] * R, [1.0] * R, [1.0] * R, uniforms=[0.3] * R)
+    assert out.tolist() == best
+    lg = logits.clone()
+    out = sampling.sample_fused(lg, [[b] for b in best], [100.0] * R, [1] * R, [1.0] * R, [1.0] * R, uniforms=[0.3] * R)
+    ref = logits.clone()
+    for r, b in enumerate(best):
+        ref[r, b] = ref[r, b] / 100.0 if ref[r, b] > 0 else ref[r, b] * 100.0
+    assert out.tolist() == ref.argmax(-1).tolist()
+    # every draw lies in the top-k / top-p support and reports that token's probability
+    for (t, k, p_) in [(0.7, 40, 0.9), (1.3, 5, 1.0), (1.0, 0, 0.5), (0.5, 1000, 0.95)]:
+        us = torch.rand(R).tolist()
+        lg = logits.clone()
+        ids, prob = sampling.sample_fused(lg, [[] for _ in range(R)], [1.0] * R, [k] * R, [p_] * R, [t] * R, uniforms=us, want_prob=True)
+        for r in range(R):
+            sup = _sample_ref_support(logits[r], t, k, p_)
+            tok = int(ids[r])
+            assert sup[tok] > 0, (t, k, p_, r)
+            assert abs(float(prob[r]) - float(sup[tok])) < 1e-4 + 1e-3 * float(sup[tok])
+            # inverse CDF: the draw is the first token (in descending probability order) whose cumulative mass exceeds u
+            order = torch.argsort(sup, descending=True, stable=True)
+            cum = sup[order].cumsum(0)
+            want = int(order[int((cum <= us[r] * float(cum[-1])).sum().clamp(max=V - 1))])
+            assert tok == want or abs(float(sup[tok]) - float(sup[want])) < 1e-6
+    _lib.check_device_errors()
+
+
+def test_fused_sampling_distribution():
+    from fastllm_b200.engine import sampling
+
+    torch.manual_seed(1)
+    V = 4096
+    base = torch.randn(V, device=DEV) * 2
+    R = 512
+    logits = base[None, :].repeat(R, 1).contiguous()
+    ids = sampling.sample_fused(logits, [[] for _ in range(R)], [1.0] * R, [8] * R, [1.0] * R, [1.0] * R)
+    sup = _sample_ref_support(base, 1.0, 8, 1.0)
+    counts = torch.bincount(ids.long(), minlength=V).float() / R
+    assert (counts[sup == 0] == 0).all()
+    top = sup.topk(8)
+    assert (counts[top.indices] - top.values).abs().max().item() < 0.08
