@@ -36,6 +36,12 @@ def _bench(model, args):
     ids = (model.encode(args.prompt_unit) * (args.input_tokens // max(1, len(model.encode(args.prompt_unit))) + 1))[:args.input_tokens]
     eng = model.engine
     gen = GenerationConfig(max_new_tokens=args.output_tokens, ignore_eos=True)
+    prof = None
+    if getattr(args, "profile", False) and eng.model.on_cuda:
+        from .ops import _lib
+
+        eng.runner.graph_ok = False          # events cannot be recorded inside a graph replay
+        prof = _lib.start_profile()
     for _ in range(args.warmup):
         eng.generate([ids], GenerationConfig(max_new_tokens=8, ignore_eos=True))
     t0 = time.perf_counter()
@@ -52,6 +58,11 @@ def _bench(model, args):
            "ttft_s": (first or t1) - t0, "tpot_ms": (t1 - (first or t0)) / max(1, args.output_tokens - 1) * 1e3,
            "batch_tokens_per_second": out / (t1 - t0), "batch_decode_tokens_per_second": (out - args.batch) / max(1e-9, t1 - (first or t0))}
     print(json.dumps(res, indent=1))
+    if prof is not None:
+        from .ops import _lib
+
+        print(prof.format())
+        _lib.stop_profile()
     return res
 
 
@@ -72,6 +83,7 @@ def main(argv=None):
         p.add_argument("--batch", type=int, default=1)
         p.add_argument("--warmup", type=int, default=1)
         p.add_argument("--prompt_unit", type=str, default="FastLLM benchmark context block. ")
+        p.add_argument("--profile", action="store_true", help="print a per-kernel device-time table (runs decode without CUDA graphs)")
     if cmd == "export":
         p.add_argument("-o", "--output", type=str, required=True)
     if cmd == "download":

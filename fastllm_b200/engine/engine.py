@@ -17,6 +17,7 @@ import time
 import torch
 
 from ..models.decoder import DecoderModel
+from ..ops import _lib
 from . import sampling
 from .request import GenerationConfig, Request, RequestState
 from .runner import EngineConfig, ModelRunner
@@ -40,6 +41,8 @@ class LLMEngine:
         self._stop = False
         self.step_count = 0
         self.decode_steps = 0
+        self.device_errors = 0
+        self.last_device_error = ""
         self.decode_tokens = 0
         self.error: Exception | None = None
 
@@ -203,10 +206,30 @@ class LLMEngine:
         if not self.running:
             return 0
         self.step_count += 1
-        pre = [r for r in self.running if r.state == RequestState.PREFILL]
-        if pre:
-            return self._prefill_step(pre)
-        return self._decode_step([r for r in self.running if r.state == RequestState.DECODE])
+        try:
+            pre = [r for r in self.running if r.state == RequestState.PREFILL]
+            if pre:
+                return self._prefill_step(pre)
+            return self._decode_step([r for r in self.running if r.state == RequestState.DECODE])
+        except _lib.DeviceKernelError as e:
+            self._recover(e)
+            return 0
+
+    def _recover(self, err) -> None:
+        """A kernel reported a failed bounded wait / bad argument through its status word (e.g. a tensor-parallel peer
+        that never arrived).  The requests in flight cannot be trusted any more: they end with reason "error"; the
+        collective arena starts a new epoch; requests still waiting are served normally afterwards.  The reference keeps
+        a per-thread CUDA error flag for the same purpose (src/devices/cuda/fastllm-cuda.cu:91-108) and a generation
+        counter for its communicators (src/devices/multicuda/fastllm-multicuda.cu:2150-2222)."""
+        self.device_errors += 1
+        self.last_device_error = str(err)
+        for r in list(self.running):
+            self.running.remove(r)
+            self._finish(r, "error")
+        comm = getattr(self.model.tp, "comm", None)
+        fused = getattr(comm, "fused", None) if comm is not None else None
+        if fused is not None:
+            fused.reset()
 
     def _prefill_step(self, reqs) -> int:
         budget = self.cfg.chunked_prefill_size

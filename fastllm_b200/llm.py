@@ -34,12 +34,19 @@ def set_device_map(device_map, is_moe: bool = False):
 
 
 def set_cpu_threads(n: int):
+    """Worker threads of the native CPU backend (and of PyTorch's own CPU ops)."""
+    from .ops import cpu
+
     _settings["threads"] = n
     torch.set_num_threads(max(1, n))
+    if cpu.available():
+        cpu.set_threads(max(1, n))
 
 
 def get_cpu_threads() -> int:
-    return torch.get_num_threads()
+    from .ops import cpu
+
+    return cpu.get_threads() if cpu.available() else torch.get_num_threads()
 
 
 def set_max_batch(n: int):

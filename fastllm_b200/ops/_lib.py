@@ -52,6 +52,65 @@ def launch_count() -> int:
     return _launch_count
 
 
+class KernelProfile:
+    """Per-kernel device time table (the reference's per-op profile, src/executor.cpp:335-440, printed with
+    FASTLLM_PRINT_PROFILE).  Every launcher call is bracketed by CUDA events on the current stream and an NVTX range;
+    ``report()`` synchronises once and sums the events.  Not usable while a CUDA graph is being captured."""
+
+    def __init__(self):
+        self.events = []
+
+    def timed(self, name, fn, args):
+        import torch
+
+        if torch.cuda.is_current_stream_capturing():
+            return fn(*args)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.nvtx.range_push(name)
+        a.record()
+        rc = fn(*args)
+        b.record()
+        torch.cuda.nvtx.range_pop()
+        self.events.append((name, a, b))
+        return rc
+
+    def report(self) -> dict:
+        import torch
+
+        torch.cuda.synchronize()
+        tot: dict = {}
+        for name, a, b in self.events:
+            t = tot.setdefault(name, [0, 0.0])
+            t[0] += 1
+            t[1] += a.elapsed_time(b)
+        self.events.clear()
+        return {k: {"calls": v[0], "ms": v[1]} for k, v in sorted(tot.items(), key=lambda kv: -kv[1][1])}
+
+    def format(self) -> str:
+        rep = self.report()
+        total = sum(v["ms"] for v in rep.values()) or 1.0
+        lines = [f"{'kernel':32s} {'calls':>8s} {'ms':>10s} {'us/call':>10s} {'share':>7s}"]
+        for k, v in rep.items():
+            lines.append(f"{k:32s} {v['calls']:8d} {v['ms']:10.3f} {v['ms'] / v['calls'] * 1e3:10.1f} {v['ms'] / total * 100:6.1f}%")
+        return "\n".join(lines)
+
+
+_profile: KernelProfile | None = None
+
+
+def start_profile() -> KernelProfile:
+    """Turn on per-kernel timing (decode should run without CUDA graphs while profiling)."""
+    global _profile
+    _profile = KernelProfile()
+    return _profile
+
+
+def stop_profile() -> KernelProfile | None:
+    global _profile
+    p, _profile = _profile, None
+    return p
+
+
 class _KernelProxy:
     """Attribute access returns the ctypes function wrapped with a launch counter."""
 
@@ -69,10 +128,12 @@ class _KernelProxy:
             return fn
         n = _LAUNCHES_PER_CALL.get(name, 1)
 
-        def counted(*args, _fn=fn, _n=n):
+        def counted(*args, _fn=fn, _n=n, _name=name):
             global _launch_count
             _launch_count += _n
-            return _fn(*args)
+            if _profile is None:
+                return _fn(*args)
+            return _profile.timed(_name, _fn, args)
 
         self._cache[name] = counted
         return counted

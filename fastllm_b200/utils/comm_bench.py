@@ -1,0 +1,91 @@
+"""Collective latency micro-benchmark at decode sizes: NCCL all-reduce vs the fused NVLink kernels.
+
+Counterpart of the reference's ``tools/nccl_latency_bench/nccl_latency.cu`` (one process per GPU here, device-timed inside a
+CUDA graph so launch overhead is excluded, max over ranks).  Run with::
+
+    python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m fastllm_b200.utils.comm_bench [--hidden 4096]
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+
+def _timeit(fn, dev, iters=20):
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(3):
+            fn(0)
+    torch.cuda.synchronize()
+    dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            fn(i)
+    g.replay()
+    torch.cuda.synchronize()
+    dist.barrier()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    g.replay()
+    e.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([s.elapsed_time(e) / iters * 1e3], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+
+def main():
+    from ..ops import _lib
+    from ..ops import basic as B
+    from ..ops.quant import LinearWeight
+    from ..parallel import symm
+    from ..parallel.tp import TPComm, init_distributed
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--hidden", type=int, default=4096)
+    ap.add_argument("--inter", type=int, default=14336)
+    ap.add_argument("--tokens", type=int, nargs="+", default=[1, 16, 64])
+    ap.add_argument("--no-multicast", action="store_true")
+    args = ap.parse_args()
+    rank, world, local = init_distributed()
+    dev = torch.device("cuda", local)
+    comm = TPComm(rank, world, dev)
+    H = args.hidden
+    fused = symm.FusedComm(comm, H, max(args.tokens), H, torch.bfloat16, use_multicast=not args.no_multicast)
+    ln = torch.ones(H, device=dev).bfloat16()
+    rows = []
+    for M in args.tokens:
+        part = torch.randn(M, H, device=dev).bfloat16()
+        t_nccl = _timeit(lambda i: dist.all_reduce(part), dev)
+        t_fused = _timeit(lambda i: fused.ar_norm(part, ln, 1e-5), dev)
+        K = args.inter // world
+        ws = [LinearWeight.from_dense((torch.randn(H, K, device=dev) * 0.02).bfloat16()) for _ in range(6)]
+        x = torch.randn(M, K, device=dev).bfloat16()
+        h0 = torch.randn(M, H, device=dev).bfloat16()
+        fused.load_h(h0)
+        t_gemm_fused = _timeit(lambda i: fused.gemm_ar_norm(ws[i % 6], x, ln, 1e-5), dev)
+
+        def nccl_path(i):
+            p = ws[i % 6](x, residual=h0 if rank == 0 else None)
+            dist.all_reduce(p)
+            return B.rmsnorm(p, ln, 1e-5)
+
+        t_gemm_nccl = _timeit(nccl_path, dev)
+        rows.append({"tokens": M, "bytes": M * H * 2, "nccl_allreduce_us": t_nccl, "fused_allreduce_residual_norm_us": t_fused,
+                     "gemm_nccl_norm_us": t_gemm_nccl, "fused_gemm_allreduce_norm_us": t_gemm_fused})
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({"ranks": world, "hidden": H, "multicast": not args.no_multicast, "rows": rows}), flush=True)
+    os._exit(0)
+
+
+if __name__ == "__main__":
+    main()

@@ -110,3 +110,35 @@ def test_quantised_export_roundtrip(tmp_path):
     b = hf.load_model(str(tmp_path / "q"), device="cpu", dtype=torch.float32)
     wa, wb = a.layers[0].attn.qkv.dequant(torch.float32), b.layers[0].attn.qkv.dequant(torch.float32)
     assert (wa - wb).abs().max() < 2e-3
+
+
+def test_engine_recovers_from_device_kernel_error():
+    """Host-side fault injection: one forward raises the error a failed bounded wait produces.  The requests in flight end
+    with reason "error", later requests are served, nothing hangs."""
+    from fastllm_b200.models.config import preset
+    from fastllm_b200.models.decoder import random_init
+    from fastllm_b200.ops import _lib
+
+    m = random_init(preset("tiny-llama"), "cpu", torch.float32, std=0.05)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=256), num_pages=8)
+    good = eng.generate([list(range(3, 20))], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0]
+    h = eng.launch(list(range(3, 20)), GenerationConfig(max_new_tokens=8, ignore_eos=True))
+    eng.step()                          # prefill
+    orig = eng.runner.decode
+    calls = {"n": 0}
+
+    def failing(*a, **k):
+        calls["n"] += 1
+        if calls["n"] == 2:
+            raise _lib.DeviceKernelError("kernel 7 site 1: wait ran out (injected)")
+        return orig(*a, **k)
+
+    eng.runner.decode = failing
+    for _ in range(6):
+        eng.step()
+    r = eng.requests[h]
+    assert r.finished() and r.finish_reason == "error" and eng.device_errors == 1
+    eng.runner.decode = orig
+    again = eng.generate([list(range(3, 20))], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0]
+    assert again == good
+    assert eng.pm.stats()["free"] + eng.pm.stats()["cached"] == 8      # no page leaked by the failed request

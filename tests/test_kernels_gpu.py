@@ -327,3 +327,17 @@ def test_fused_sampling_distribution():
     assert (counts[sup == 0] == 0).all()
     top = sup.topk(8)
     assert (counts[top.indices] - top.values).abs().max().item() < 0.08
+
+
+def test_kernel_profile_table():
+    """Per-kernel device-time table (the --profile flag): counts and non-zero times for the kernels that ran."""
+    prof = _lib.start_profile()
+    try:
+        x = torch.randn(8, 1024, device=DEV, dtype=torch.bfloat16)
+        w = torch.randn(1024, device=DEV, dtype=torch.bfloat16)
+        for _ in range(3):
+            B.rmsnorm(x, w, 1e-6)
+        rep = prof.report()
+    finally:
+        _lib.stop_profile()
+    assert rep["fb_rmsnorm"]["calls"] == 3 and rep["fb_rmsnorm"]["ms"] > 0
