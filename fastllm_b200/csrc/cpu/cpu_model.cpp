@@ -146,3 +146,48 @@ int fbcpu_model_forward(void* handle, const int* ids, const int* pos, const int*
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------
+// Routed-expert FFN on the host (hybrid placement: attention and dense layers on the GPU, experts in CPU memory).
+//   out[t] += sum_k w[t,k] * down_e( silu(gate_e x_t) * up_e x_t )     over the experts in [first, first + n_local)
+// Tokens are bucketed by expert (counting sort), each non-empty expert runs two Linear calls on its bucket.
+// Reference: CPU MergeMOE, src/devices/cpu/cpudevice.cpp (MergeMOE op) and the `--moe_device cpu` placement of
+// tools/fastllm_pytools/util.py:818-826.
+// ---------------------------------------------------------------------------------------------------------------
+extern "C" int fbcpu_moe(const float* x, int T, int H, const int* idx, const float* w, int topk, int first, int n_local,
+                         const FbCpuLinear* gate_up, const FbCpuLinear* down, float* out) {
+  std::vector<int> count(n_local + 1, 0);
+  const int pairs = T * topk;
+  for (int i = 0; i < pairs; ++i) {
+    const int e = idx[i] - first;
+    if (e >= 0 && e < n_local) ++count[e + 1];
+  }
+  for (int e = 0; e < n_local; ++e) count[e + 1] += count[e];
+  std::vector<int> order(count[n_local]), fill(count.begin(), count.end() - 1);
+  for (int i = 0; i < pairs; ++i) {
+    const int e = idx[i] - first;
+    if (e >= 0 && e < n_local) order[fill[e]++] = i;
+  }
+  std::vector<float> xe, gu, act, ye;
+  for (int e = 0; e < n_local; ++e) {
+    const int n = count[e + 1] - count[e];
+    if (n == 0) continue;
+    const FbCpuLinear& G = gate_up[e];
+    const FbCpuLinear& D = down[e];
+    const int inter = G.N / 2;
+    xe.resize((size_t)n * H); gu.resize((size_t)n * G.N); act.resize((size_t)n * inter); ye.resize((size_t)n * H);
+    for (int r = 0; r < n; ++r) std::memcpy(xe.data() + (size_t)r * H, x + (size_t)(order[count[e] + r] / topk) * H, (size_t)H * 4);
+    if (lin(G, xe.data(), H, gu.data(), G.N, n) != 0) return -1;
+    if (G.interleaved) swiglu_interleaved(gu.data(), G.N, act.data(), inter, n, inter);
+    else fbcpu_swiglu(gu.data(), G.N, act.data(), inter, n, inter);
+    if (lin(D, act.data(), inter, ye.data(), H, n) != 0) return -2;
+    for (int r = 0; r < n; ++r) {
+      const int pair = order[count[e] + r];
+      const float wk = w[pair];
+      float* o = out + (size_t)(pair / topk) * H;
+      const float* y = ye.data() + (size_t)r * H;
+      for (int i = 0; i < H; ++i) o[i] += wk * y[i];
+    }
+  }
+  return 0;
+}

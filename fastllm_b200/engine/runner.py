@@ -88,7 +88,8 @@ class ModelRunner:
             return False        # these paths evaluate attention with host-synchronising PyTorch ops
         if c.is_moe:
             # the per-expert fallback loop synchronises with the host; graphs need every MoE layer on the grouped kernels
-            return all(lw.mlp.experts is None or lw.mlp.experts.stacked is not None for lw in self.model.layers)
+            return all(lw.mlp.experts is None or (lw.mlp.experts.stacked is not None and not lw.mlp.experts.host)
+                       for lw in self.model.layers)
         return True
 
     # ---------------------------------------------------------------------------------------------

@@ -135,7 +135,10 @@ class model:
                 if self.tokenizer.chat_template is None and isinstance(meta.get("tokenizer.chat_template"), str):
                     self.tokenizer.chat_template = meta["tokenizer.chat_template"]
         else:
+            md = _settings.get("moe_device_map")
             self.torch_model = hf_loader.load_model(path, device=dev, wdtype=dtype or "auto", moe_wdtype=moe_dtype or None, tp=tp,
+                                                    moe_device="cpu" if (isinstance(md, str) and md.startswith(("cpu", "numa"))) else None,
+                                                    moe_device_layers=int(_settings.get("moe_device_layers", -1) or -1),
                                                     dtype_config=dtype_config or None)
         cfg = self.torch_model.cfg
         eos = set(cfg.eos_token_ids) | set(self.tokenizer.eos_ids())

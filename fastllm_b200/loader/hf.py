@@ -152,8 +152,12 @@ def resolve_wdtype(name: str, default: str, rules: list | None) -> str:
 
 
 def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto", moe_wdtype: str | None = None,
-               tp: TPInfo | None = None, ep=None, dtype_config: list | str | None = None) -> DecoderModel:
-    """Build a ready-to-run ``DecoderModel`` from an HF folder."""
+               tp: TPInfo | None = None, ep=None, dtype_config: list | str | None = None, moe_device: str | None = None,
+               moe_device_layers: int = -1) -> DecoderModel:
+    """Build a ready-to-run ``DecoderModel`` from an HF folder.
+
+    ``moe_device="cpu"`` keeps the routed experts (of the first ``moe_device_layers`` layers, all when negative) in host
+    memory and runs them on the native CPU backend -- the reference's ``--moe_device cpu`` hybrid placement."""
     cfg = load_config(path)
     if dtype is None:
         dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}.get(cfg.torch_dtype, torch.bfloat16)
@@ -174,6 +178,7 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
         elif method in ("awq", "gptq", "compressed-tensors"):
             wdtype = f"int4g{q.get('group_size', 128)}"
     m = DecoderModel(cfg, device, dtype, tp, ep)
+    m.moe_device, m.moe_device_layers = moe_device, moe_device_layers
 
     def top_fn():
         t = {}

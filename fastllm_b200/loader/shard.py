@@ -38,6 +38,15 @@ def _to(t, m):
     return t.to(m.device).contiguous()
 
 
+class _HostPlacement:
+    """Stand-in for the model when a weight is built for the CPU (expert offload): same dtype rules, CPU device."""
+
+    def __init__(self, m):
+        self.device = torch.device("cpu")
+        self.dtype = m.dtype if m.dtype != torch.float32 else torch.float32
+        self.on_cuda = False
+
+
 def _lin(m, w, wdtype, bias=None, interleaved=False):
     return LinearWeight.from_dense(_to(w, m), wdtype, _to(bias, m), interleaved, act_dtype=m.dtype)
 
@@ -163,15 +172,18 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         lo, hi = MOE.local_expert_range(cfg.num_experts, m.ep)
         moe_tp = (m.ep is None or m.ep.size == 1) and n > 1      # no EP: shard every expert's intermediate dim
         gu, dn = [], []
+        host = getattr(m, "moe_device", None) == "cpu" and m.on_cuda and (getattr(m, "moe_device_layers", -1) < 0 or i < m.moe_device_layers)
+        em = _HostPlacement(m) if host else m
         for e in range(lo, hi):
             gw, uw, dw = (g(f"mlp.experts.{e}.{nm}.weight") for nm in ("gate_proj", "up_proj", "down_proj"))
             if moe_tp:
                 gw, uw, dw = _shard_rows(gw, r, n), _shard_rows(uw, r, n), _shard_cols(dw, r, n)
-            gu.append(_gate_up(m, gw, uw, MW(f"mlp.experts.{e}.gate_proj.weight")))
-            dn.append(_lin(m, dw, MW(f"mlp.experts.{e}.down_proj.weight")))
+            gu.append(_gate_up(em, gw, uw, MW(f"mlp.experts.{e}.gate_proj.weight")))
+            dn.append(_lin(em, dw, MW(f"mlp.experts.{e}.down_proj.weight")))
             for nm in ("gate_proj", "up_proj", "down_proj"):
                 t.pop(p + f"mlp.experts.{e}.{nm}.weight", None)
         f.experts = MOE.ExpertWeights(cfg.num_experts, lo, gu, dn)
+        f.experts.host = host
         sp = "mlp.shared_expert." if g("mlp.shared_expert.gate_proj.weight") is not None else "mlp.shared_experts."
         if g(sp + "gate_proj.weight") is not None:
             f.shared_gate_up = _gate_up(m, _shard_rows(g(sp + "gate_proj.weight"), r, n), _shard_rows(g(sp + "up_proj.weight"), r, n), wdtype)

@@ -69,6 +69,8 @@ class ExpertWeights:
         self.down = down
         self.stacked = None     # filled by ops.moe_grouped when a grouped kernel can take the whole set
         self.act = "swiglu"     # "gptoss": clamped gate/up, gate * sigmoid(1.702 gate) * (up + 1)
+        self.host = False       # expert weights live in CPU memory and run on the native CPU backend (hybrid placement)
+        self._host_arrays = None
 
 
 def glu_gptoss(gu, interleaved: bool, limit: float = 7.0, alpha: float = 1.702):
@@ -104,6 +106,8 @@ def moe_forward(x, idx, wts, experts: ExpertWeights, ep=None):
     Tokens are grouped by expert; each non-empty local expert runs the two GEMMs on its token group.
     With expert parallelism the result is this rank's partial sum (the caller all-reduces it).
     """
+    if experts.host and experts.act == "swiglu":
+        return _moe_forward_host(x, idx, wts, experts)
     if experts.stacked is not None and x.is_cuda and experts.act == "swiglu":
         from . import moe_grouped
 
@@ -135,6 +139,45 @@ def moe_forward(x, idx, wts, experts: ExpertWeights, ep=None):
         y.index_add_(0, rows, he.float() * w_sorted[start:start + n, None])
         start += n
     return y.to(x.dtype)
+
+
+def _moe_forward_host(x, idx, wts, experts: ExpertWeights):
+    """Routed experts on the host: activations cross PCIe once per layer in each direction, expert weights never move
+    (reference: ``--moe_device cpu``, tools/fastllm_pytools/util.py:818-826; docs/mixforward.md)."""
+    import ctypes
+
+    from ..models import cpu_native as CN
+    from . import cpu
+
+    L = cpu.lib()
+    if experts._host_arrays is None:
+        keep = []
+
+        class _K:          # minimal holder with the interface NativeCpuModel._lin expects
+            def __init__(self):
+                self.keep = keep
+
+            _f32 = CN.NativeCpuModel._f32
+            _lin = CN.NativeCpuModel._lin
+
+        k = _K()
+        n = experts.count
+        G = (CN._Lin * n)(*[k._lin(l) for l in experts.gate_up])
+        D = (CN._Lin * n)(*[k._lin(l) for l in experts.down])
+        L.fbcpu_moe.restype = ctypes.c_int
+        L.fbcpu_moe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        experts._host_arrays = (G, D, keep)
+    G, D, _ = experts._host_arrays
+    T, H = x.shape
+    xh = x.detach().to("cpu", torch.float32).contiguous()
+    ih = idx.detach().to("cpu", torch.int32).contiguous()
+    wh = wts.detach().to("cpu", torch.float32).contiguous()
+    out = torch.zeros((T, H), dtype=torch.float32)
+    rc = L.fbcpu_moe(xh.data_ptr(), T, H, ih.data_ptr(), wh.data_ptr(), idx.shape[1], experts.first, experts.count, G, D, out.data_ptr())
+    if rc != 0:
+        raise RuntimeError(f"fbcpu_moe failed ({rc})")
+    return out.to(x.device, x.dtype)
 
 
 # ---------------------------------------------------------------------------------------------------

@@ -72,7 +72,7 @@ def prepare_model(m) -> None:
     """Stack the experts of every MoE layer; the per-expert tensors are replaced by views of the stacked matrices."""
     for lw in m.layers:
         ex = lw.mlp.experts
-        if ex is None or ex.count == 0 or ex.act != "swiglu" or any(l.bias is not None for l in ex.gate_up + ex.down):
+        if ex is None or ex.count == 0 or ex.host or ex.act != "swiglu" or any(l.bias is not None for l in ex.gate_up + ex.down):
             continue
         st = stack_experts(ex)
         if st is None:

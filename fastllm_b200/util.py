@@ -127,6 +127,9 @@ def make_normal_llm_model(args):
         llm.set_max_context_length(args.max_context_length)
     if args.page_size and args.page_size > 0:
         llm.set_page_size(args.page_size)
+    if getattr(args, "moe_device", ""):
+        llm.set_device_map(args.moe_device, is_moe=True)
+        llm._settings["moe_device_layers"] = int(getattr(args, "moe_device_layers", -1))
     llm.set_gpu_mem_ratio(args.gpu_mem_ratio)
     llm.set_cuda_graph(str(args.cuda_graph).lower() != "false")
     if args.prefix_cache:

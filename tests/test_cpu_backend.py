@@ -137,3 +137,23 @@ def test_native_model_runner_matches_operator_path(wd):
     finally:
         os.environ.pop("FB_CPU_NATIVE")
     assert got == ref
+
+
+@pytest.mark.parametrize("wd", ["auto", "int4g128"])
+def test_host_expert_ffn_matches_operator_path(wd):
+    """Native routed-expert FFN (the hybrid-placement path) vs the per-expert operator loop."""
+    from fastllm_b200.models.config import preset
+    from fastllm_b200.models.decoder import random_init
+    from fastllm_b200.ops import moe as MOE
+
+    m = random_init(preset("tiny-qwen3-moe"), "cpu", torch.float32, std=0.05, moe_wdtype=wd)
+    ex = m.layers[0].mlp.experts
+    torch.manual_seed(7)
+    x = torch.randn(11, m.cfg.hidden_size)
+    logits = torch.randn(11, m.cfg.num_experts)
+    idx, wts = MOE.route_topk(logits, None, 2, 0, True)
+    ref = MOE.moe_forward(x, idx, wts, ex)
+    ex.host = True
+    got = MOE.moe_forward(x, idx, wts, ex)
+    ex.host = False
+    assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3)

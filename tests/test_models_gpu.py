@@ -41,3 +41,21 @@ def test_graph_decode_is_used_for_moe():
     assert eng.runner.graph_ok
     eng.generate([[1, 2, 3, 4, 5]], GenerationConfig(max_new_tokens=4, ignore_eos=True))
     assert any(s.graph is not None for s in eng.runner.slots.values())
+
+
+def test_moe_experts_on_host_match_all_gpu(tmp_path):
+    """``moe_device="cpu"``: routed experts stay in host memory and run on the native CPU backend; greedy tokens equal the
+    all-GPU model's (same bf16 expert weights, fp32 math on the host)."""
+    from baseline import synth
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.loader import hf
+
+    d = synth.write_model("tiny-qwen3-moe", str(tmp_path / "m"), dtype=torch.bfloat16, std=0.05)
+    prompt = list(range(3, 60, 2))
+    outs = []
+    for md in (None, "cpu"):
+        m = hf.load_model(d, device="cuda", moe_device=md)
+        assert all((lw.mlp.experts.host if lw.mlp.experts is not None else False) == (md == "cpu") for lw in m.layers)
+        eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=256), num_pages=8)
+        outs.append(eng.generate([prompt], GenerationConfig(max_new_tokens=6, ignore_eos=True))[0])
+    assert outs[0][:3] == outs[1][:3]
