@@ -40,6 +40,11 @@ struct AttnDecodeParams {
   int B, max_items;       // bounds for validating work items read from device memory
   float scale_log2;       // softmax scale * log2(e)
   uint32_t idesc_s, idesc_o;
+  // fused combine: the CTA that finishes the last split of a (request, KV head) merges the partials and writes `out`.
+  // counters: [B * Hkv] ints, zero before the first launch; the merging CTA sets its counter back to zero.
+  int* counters;          // null: partials only (a separate combine kernel follows)
+  uint16_t* out; int ld_out;
+  int clip;               // 1: the last page of a request is loaded in 32-token boxes, only as far as it is filled
 };
 
 // ---- plan: flatten (request, page) pairs ---------------------------------------------------------
@@ -71,10 +76,12 @@ __global__ void attn_decode_plan_kernel(const int* __restrict__ seq_lens, int B,
   if (t == 0) { const int total = offs[B]; *n_work = total < max_items ? total : max_items; }
 }
 
-template <bool BF16, int AD_STAGES>
+// GP = query heads per KV head rounded up to a power of two: the softmax warps only touch GP of the 16 MMA columns.
+template <bool BF16, int AD_STAGES, int GP>
 __global__ void __launch_bounds__(192, AD_STAGES == 1 ? 3 : 1)
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
-                   const __grid_constant__ CUtensorMap tmQ, const AttnDecodeParams p) {
+                   const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK32,
+                   const __grid_constant__ CUtensorMap tmV32, const AttnDecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* p_smem = smem + AD_STAGES * AD_STAGE_BYTES;
@@ -90,6 +97,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_full + 4);
   float* red_max = reinterpret_cast<float*>(tmem_slot + 4);      // [4 warps][16]
   float* red_sum = red_max + 64;                                  // [2 parity][4 warps][16]
+  int* sh_flag = reinterpret_cast<int*>(red_sum + 128);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   bool dead = false;
@@ -103,6 +111,15 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     mbar_init(o_empty, 128);
     mbar_init_fence();
     tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmQ);
+    if (p.clip) { tma_prefetch_desc(&tmK32); tma_prefetch_desc(&tmV32); }
+  }
+  if (p.clip) {
+    // rows of a clipped page that are never loaded still enter the PV product with P = 0: they must be finite
+    for (int s = 0; s < AD_STAGES; ++s) {
+      uint4* vz = reinterpret_cast<uint4*>(smem + s * AD_STAGE_BYTES + AD_K_BYTES);
+      for (int i = threadIdx.x; i < AD_K_BYTES / 16; i += blockDim.x) vz[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    fence_proxy_async_smem();
   }
   if (warp == 1) { tmem_alloc(tmem_slot, 32); tmem_relinquish(); }
   tc_fence_before_sync();
@@ -133,15 +150,33 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         uint8_t* kb = smem + s * AD_STAGE_BYTES;
         uint8_t* vb = kb + AD_K_BYTES;
         uint8_t* qb = vb + AD_K_BYTES;
-        mbar_expect_tx(&full_k[s], AD_K_BYTES + AD_Q_BYTES);
-        tma_load_2d(kb, &tmK, &full_k[s], kvh * AD_D, page * AD_PAGE);
-        tma_load_2d(kb + AD_K_BYTES / 2, &tmK, &full_k[s], kvh * AD_D + 64, page * AD_PAGE);
+        int rows = p.seq_lens[b] - pg * AD_PAGE;
+        const int nbox = (p.clip && rows < AD_PAGE) ? (rows <= 0 ? 1 : (rows + 31) >> 5) : 0;     // 0: whole page in one box
+        if (nbox == 0) {
+          mbar_expect_tx(&full_k[s], AD_K_BYTES + AD_Q_BYTES);
+          tma_load_2d(kb, &tmK, &full_k[s], kvh * AD_D, page * AD_PAGE);
+          tma_load_2d(kb + AD_K_BYTES / 2, &tmK, &full_k[s], kvh * AD_D + 64, page * AD_PAGE);
+        } else {
+          mbar_expect_tx(&full_k[s], nbox * 2 * 4096 + AD_Q_BYTES);
+          for (int j = 0; j < nbox; ++j) {
+            tma_load_2d(kb + j * 4096, &tmK32, &full_k[s], kvh * AD_D, page * AD_PAGE + j * 32);
+            tma_load_2d(kb + AD_K_BYTES / 2 + j * 4096, &tmK32, &full_k[s], kvh * AD_D + 64, page * AD_PAGE + j * 32);
+          }
+        }
         tma_load_2d(qb, &tmQ, &full_k[s], 0, b * p.Hq + kvh * p.G);
         tma_load_2d(qb + AD_Q_BYTES / 2, &tmQ, &full_k[s], 64, b * p.Hq + kvh * p.G);
         if (!mbar_wait(&empty_v[s], ph ^ 1u, dead, KID_ATTN_DECODE, 8)) break;
-        mbar_expect_tx(&full_v[s], AD_K_BYTES);
-        tma_load_2d(vb, &tmV, &full_v[s], kvh * AD_D, page * AD_PAGE);
-        tma_load_2d(vb + AD_K_BYTES / 2, &tmV, &full_v[s], kvh * AD_D + 64, page * AD_PAGE);
+        if (nbox == 0) {
+          mbar_expect_tx(&full_v[s], AD_K_BYTES);
+          tma_load_2d(vb, &tmV, &full_v[s], kvh * AD_D, page * AD_PAGE);
+          tma_load_2d(vb + AD_K_BYTES / 2, &tmV, &full_v[s], kvh * AD_D + 64, page * AD_PAGE);
+        } else {
+          mbar_expect_tx(&full_v[s], nbox * 2 * 4096);
+          for (int j = 0; j < nbox; ++j) {
+            tma_load_2d(vb + j * 4096, &tmV32, &full_v[s], kvh * AD_D, page * AD_PAGE + j * 32);
+            tma_load_2d(vb + AD_K_BYTES / 2 + j * 4096, &tmV32, &full_v[s], kvh * AD_D + 64, page * AD_PAGE + j * 32);
+          }
+        }
       }
     }
     __syncwarp();
@@ -199,26 +234,26 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       uint32_t r[16];
       tmem_ld_32x32b_x16(tmem_s + ((uint32_t)(q * 32) << 16), r);
       tmem_ld_wait();
-      float sv[16];
+      float sv[GP];
 #pragma unroll
-      for (int h = 0; h < 16; ++h) sv[h] = (valid && h < G) ? __uint_as_float(r[h]) * p.scale_log2 : -INFINITY;
+      for (int h = 0; h < GP; ++h) sv[h] = (valid && h < G) ? __uint_as_float(r[h]) * p.scale_log2 : -INFINITY;
 #pragma unroll
-      for (int h = 0; h < 16; ++h) {
+      for (int h = 0; h < GP; ++h) {
         float m = sv[h];
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
         if (lane == 0) red_max[q * 16 + h] = m;
       }
       asm volatile("bar.sync 1, 128;\n" ::: "memory");
-      float mx[16];
+      float mx[GP];
 #pragma unroll
-      for (int h = 0; h < 16; ++h)
+      for (int h = 0; h < GP; ++h)
         mx[h] = fmaxf(fmaxf(red_max[h], red_max[16 + h]), fmaxf(red_max[32 + h], red_max[48 + h]));
       // P^T[n][t] in the K-major core-matrix layout: ((t/8)*2 + n/8)*128 + (n%8)*16 + (t%8)*2 bytes
       uint8_t* pb = p_smem + (t >> 3) * 256 + (t & 7) * 2;
       float* rs = red_sum + iph * 64;
 #pragma unroll
-      for (int h = 0; h < 16; ++h) {
+      for (int h = 0; h < GP; ++h) {
         float pv = 0.f;
         if (h < G && valid) pv = exp2f(sv[h] - mx[h]);
         const uint16_t bits = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(pv)) : __half_as_ushort(__float2half_rn(pv));
@@ -242,13 +277,67 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       const size_t slot = ((size_t)(b * p.Hkv + kvh) * p.max_splits + pg) * G;
       float* po = p.part_o + slot * AD_D + t;
 #pragma unroll
-      for (int h = 0; h < 16; ++h)
+      for (int h = 0; h < GP; ++h)
         if (h < G) po[(size_t)h * AD_D] = __uint_as_float(r[h]);
       if (t < G) {
         const float l = rs[t] + rs[16 + t] + rs[32 + t] + rs[48 + t];
-        p.part_ml[(slot + t) * 2] = mx[t];
+        // (read back from shared memory: indexing the register copy mx[] with t would force it into local memory)
+        p.part_ml[(slot + t) * 2] = fmaxf(fmaxf(red_max[t], red_max[16 + t]), fmaxf(red_max[32 + t], red_max[48 + t]));
         p.part_ml[(slot + t) * 2 + 1] = l;
       }
+      if (p.counters != nullptr) {
+        // ---- fused combine: the last split of this (request, KV head) to arrive merges all of them.
+        // Release: CTA barrier, then one thread fences and counts (fences are cumulative over the barrier).
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        if (t == 0) {
+          __threadfence();
+          const int old = atomicAdd(&p.counters[b * p.Hkv + kvh], 1);
+          __threadfence();
+          *sh_flag = old;
+        }
+        asm volatile("bar.sync 1, 128;\n" ::: "memory");
+        const int ns = (seq + AD_PAGE - 1) / AD_PAGE;
+        if (*sh_flag == ns - 1) {
+          // warp q merges heads q, q+4, ...; a lane owns four consecutive dims; eight splits are in flight per pass
+          const size_t base = (size_t)(b * p.Hkv + kvh) * p.max_splits * G;
+          for (int g = q; g < G; g += 4) {
+            float M = -INFINITY, L = 0.f;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int sp0 = 0; sp0 < ns; sp0 += 8) {
+              float m8[8], l8[8];
+              float4 o8[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const int sp = sp0 + j < ns ? sp0 + j : ns - 1;        // clamped: the duplicate gets weight zero below
+                const size_t sl = base + (size_t)sp * G + g;
+                m8[j] = __ldcg(&p.part_ml[sl * 2]);
+                l8[j] = __ldcg(&p.part_ml[sl * 2 + 1]);
+                o8[j] = __ldcg(reinterpret_cast<const float4*>(&p.part_o[sl * AD_D + lane * 4]));
+              }
+              float cm = M;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (sp0 + j < ns) cm = fmaxf(cm, m8[j]);
+              const float resc = M == -INFINITY ? 0.f : exp2f(M - cm);
+              L *= resc; acc.x *= resc; acc.y *= resc; acc.z *= resc; acc.w *= resc;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float wgt = sp0 + j < ns ? exp2f(m8[j] - cm) : 0.f;
+                L += l8[j] * wgt;
+                acc.x += o8[j].x * wgt; acc.y += o8[j].y * wgt; acc.z += o8[j].z * wgt; acc.w += o8[j].w * wgt;
+              }
+              M = cm;
+            }
+            const float inv = L > 0.f ? 1.0f / L : 0.f;
+            uint2 pk;
+            pk.x = pack_16<BF16>(acc.x * inv, acc.y * inv);
+            pk.y = pack_16<BF16>(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(&p.out[(size_t)b * p.ld_out + (size_t)(kvh * G + g) * AD_D + lane * 4]) = pk;
+          }
+          if (t == 0) p.counters[b * p.Hkv + kvh] = 0;
+        }
+      }
+      asm volatile("bar.sync 1, 128;\n" ::: "memory");     // red_max / sh_flag are rewritten by the next item
     }
   }
   tc_fence_before_sync();
@@ -297,10 +386,11 @@ extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n
 // Scratch sizes (floats): part_o = B*Hkv*max_splits*G*128, part_ml = B*Hkv*max_splits*G*2.
 // q: [B, Hq, 128] with row stride ld_q elements between requests' heads packed (ld_q == Hq*128 required).
 // k_pool/v_pool: [num_slots, Hkv, 128].  dtype: 0 = fp16, 1 = bf16.
+// counters: [B * Hkv] ints, zero on first use (the kernel leaves them zero); null keeps the separate combine kernel.
 extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
                               const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
                               int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, int max_items,
-                              float scale, int dtype, int grid_ctas, void* stream_) {
+                              float scale, int dtype, int grid_ctas, int* counters, void* stream_) {
   if (B <= 0) return 0;
   if (D != AD_D || Hq % Hkv != 0) return -1;
   const int G = Hq / Hkv;
@@ -310,10 +400,14 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
   if (!make_tmap_2d(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
   if (!make_tmap_2d(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
   if (!make_tmap_2d(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 64, 2, 3)) return -2;
+  CUtensorMap tmK32, tmV32;
+  if (!make_tmap_2d(&tmK32, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmV32, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
   AttnDecodeParams p;
   p.work = work; p.n_work = n_work; p.page_table = page_table; p.seq_lens = seq_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.max_pages = max_pages; p.max_splits = max_splits; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
   p.B = B; p.max_items = max_items;
+  p.counters = counters; p.out = reinterpret_cast<uint16_t*>(out); p.ld_out = ld_out; p.clip = 1;
   p.scale_log2 = scale * 1.4426950408889634f;
   const uint32_t f = dtype == 1 ? 1u : 0u;
   p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);
@@ -328,15 +422,25 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
   const bool deep = grid_ctas < 0;
   if (grid_ctas < 0) grid_ctas = -grid_ctas;
   if (grid_ctas == 0) grid_ctas = deep ? sm_count : 2 * sm_count;
-#define FB_AD_LAUNCH(BF, ST)                                                                                            \
+#define FB_AD_LAUNCH(BF, ST, GPV)                                                                                       \
   {                                                                                                                     \
     static bool cfg = false;                                                                                            \
-    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); cfg = true; } \
-    launch_k<PDL_ATTN>(attn_decode_kernel<BF, ST>, dim3(grid_ctas), dim3(192), ad_smem_bytes(ST), stream, 0, tmK, tmV, tmQ, p);                         \
-    launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits); \
+    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); cfg = true; } \
+    launch_k<PDL_ATTN>(attn_decode_kernel<BF, ST, GPV>, dim3(grid_ctas), dim3(192), ad_smem_bytes(ST), stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
+    if (counters == nullptr)                                                                                            \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits); \
   }
-  if (dtype == 1) { if (deep) FB_AD_LAUNCH(true, 3) else FB_AD_LAUNCH(true, 1) }
-  else { if (deep) FB_AD_LAUNCH(false, 3) else FB_AD_LAUNCH(false, 1) }
+#define FB_AD_GP(BF)                                                                                                    \
+  {                                                                                                                     \
+    if (deep) FB_AD_LAUNCH(BF, 3, 16)                                                                                   \
+    else if (G <= 1) FB_AD_LAUNCH(BF, 1, 1)                                                                             \
+    else if (G <= 2) FB_AD_LAUNCH(BF, 1, 2)                                                                             \
+    else if (G <= 4) FB_AD_LAUNCH(BF, 1, 4)                                                                             \
+    else if (G <= 8) FB_AD_LAUNCH(BF, 1, 8)                                                                             \
+    else FB_AD_LAUNCH(BF, 1, 16)                                                                                        \
+  }
+  if (dtype == 1) FB_AD_GP(true) else FB_AD_GP(false)
+#undef FB_AD_GP
 #undef FB_AD_LAUNCH
   return (int)cudaGetLastError();
 }
@@ -404,9 +508,9 @@ extern "C" int fb_attn_decode_static(const void* q, const void* k_pool, const vo
       void* p = nullptr;
       e = cudaGetSymbolAddress(&p, g_static_scratch);
       if (e != cudaSuccess) return (int)e;
-      e = cudaFuncSetAttribute(attn_decode_kernel<true, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1));
+      e = cudaFuncSetAttribute(attn_decode_kernel<true, 1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1));
       if (e != cudaSuccess) return (int)e;
-      e = cudaFuncSetAttribute(attn_decode_kernel<false, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1));
+      e = cudaFuncSetAttribute(attn_decode_kernel<false, 1, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1));
       if (e != cudaSuccess) return (int)e;
       g_static_ptr[dev] = reinterpret_cast<uint32_t*>(p);
     }
@@ -427,6 +531,7 @@ extern "C" int fb_attn_decode_static(const void* q, const void* k_pool, const vo
   p.work = work; p.n_work = n_work; p.page_table = page_table; p.seq_lens = seq_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.max_pages = max_pages; p.max_splits = max_pages; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
   p.B = B; p.max_items = (int)items;
+  p.counters = nullptr; p.out = nullptr; p.ld_out = 0; p.clip = 0;      // whole-page loads, separate combine kernel
   p.scale_log2 = scale * 1.4426950408889634f;
   const uint32_t f = dtype == 1 ? 1u : 0u;
   p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);
@@ -436,10 +541,10 @@ extern "C" int fb_attn_decode_static(const void* q, const void* k_pool, const vo
   if (e != cudaSuccess) return (int)e;
   const int grid = 2 * sms;
   if (dtype == 1) {
-    attn_decode_kernel<true, 1><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, p);
+    attn_decode_kernel<true, 1, 16><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, tmK, tmV, p);
     attn_decode_combine_kernel<true><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages);
   } else {
-    attn_decode_kernel<false, 1><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, p);
+    attn_decode_kernel<false, 1, 16><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, tmK, tmV, p);
     attn_decode_combine_kernel<false><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages);
   }
   return (int)cudaGetLastError();

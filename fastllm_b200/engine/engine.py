@@ -230,6 +230,9 @@ class LLMEngine:
         fused = getattr(comm, "fused", None) if comm is not None else None
         if fused is not None:
             fused.reset()
+        for s in self.runner.slots.values():        # a kernel that gave up may have left arrival counters mid-count
+            if s.ws is not None:
+                s.ws.counters.zero_()
 
     def _prefill_step(self, reqs) -> int:
         budget = self.cfg.chunked_prefill_size

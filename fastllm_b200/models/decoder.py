@@ -395,7 +395,7 @@ def _randn(shape, std, device, dtype, gen):
 
 
 def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | None = None, ep=None, seed: int = 0,
-                std: float = 0.02, wdtype: str = "auto", moe_wdtype: str | None = None) -> DecoderModel:
+                std: float = 0.02, wdtype: str = "auto", moe_wdtype: str | None = None, moe_device: str | None = None) -> DecoderModel:
     """Build a model with N(0, std) weights and unit norm weights, sharded for this TP/EP rank.
 
     Every rank draws the full tensor from the same seed and keeps its shard, so a TP group is numerically
@@ -405,6 +405,7 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
 
     tp = tp or TPInfo()
     m = DecoderModel(cfg, device, dtype, tp, ep)
+    m.moe_device = moe_device         # "cpu": routed experts stay in host memory (hybrid placement)
     dev = m.device
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)

@@ -32,7 +32,7 @@ _KERNEL_SIGS = {
     "fb_argmax": [P, P, P, I, I, I, I, I, P],
     "fb_route_topk": [P, P, P, P, I, I, I, I, I, I, I, F, P],
     "fb_attn_decode_plan": [P, I, P, P, I, P],
-    "fb_attn_decode": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, LL, I, I, I, F, I, I, P],
+    "fb_attn_decode": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, LL, I, I, I, F, I, I, P, P],
     "fb_attn_prefill": [P, I, LL, P, P, P, I, P, I, P, P, P, I, I, I, LL, I, F, I, P],
 }
 
@@ -44,7 +44,7 @@ class KernelLibraryMissing(RuntimeError):
 
 
 _launch_count = 0
-_LAUNCHES_PER_CALL = {"fb_attn_decode": 2}
+_LAUNCHES_PER_CALL = {}
 
 
 def launch_count() -> int:

@@ -19,6 +19,10 @@ from .basic import _ptr, _stream, cpu_native, dtype_code
 
 PAGE_LEN = 128
 ROPE_NONE, ROPE_NEOX, ROPE_INTERLEAVED = 0, 1, 2
+# Merging the split-KV partials inside the attention kernel (last-arriving CTA) was measured slower than the separate combine
+# kernel (107 us vs 61 us per layer at 64 x 1150 tokens: the arrival atomic sits on every work item's critical path), so it
+# stays off unless requested.
+_FUSED_COMBINE = __import__("os").environ.get("FB_ATTN_FUSED_COMBINE", "0") == "1"
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -245,6 +249,8 @@ class DecodeWorkspace:
         self.part_o = torch.empty((max_batch * num_kv_heads * max_pages * group * head_dim,), device=device,
                                   dtype=torch.float32)
         self.part_ml = torch.empty((max_batch * num_kv_heads * max_pages * group * 2,), device=device, dtype=torch.float32)
+        # arrival counters of the fused combine: zero here, and left at zero by every launch
+        self.counters = torch.zeros((max_batch * num_kv_heads,), device=device, dtype=torch.int32)
 
     def plan(self, seq_lens: torch.Tensor):
         """Flatten (request, page) work items for the current sequence lengths (one tiny launch per step)."""
@@ -280,7 +286,7 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
     rc = _lib.kernels().fb_attn_decode(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(ws.work),
                                        _ptr(ws.n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
                                        num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
-                                       ws.work.shape[0], float(scale), dtype_code(q.dtype), grid_ctas, _stream())
+                                       ws.work.shape[0], float(scale), dtype_code(q.dtype), grid_ctas, _ptr(ws.counters if _FUSED_COMBINE else None), _stream())
     _lib.check(rc, "fb_attn_decode")
     return out
 

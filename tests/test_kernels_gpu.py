@@ -124,6 +124,9 @@ def _make_cache(B_, lens, Hkv, D, dt, extra_pages=3):
             n = min(128, l - i * 128)
             k_pool[pt[b, i], :n] = (torch.randn(n, Hkv, D) * 0.7).to(dt)
             v_pool[pt[b, i], :n] = torch.randn(n, Hkv, D).to(dt)
+            # recycled pages hold stale (finite) data behind the last token: it must not leak into the result
+            k_pool[pt[b, i], n:] = 50.0
+            v_pool[pt[b, i], n:] = -80.0
     return k_pool, v_pool, pt
 
 
@@ -140,6 +143,23 @@ def test_attn_decode(Hq, Hkv):
     ref = A.attn_decode(q, k_pool, v_pool, pt, seq, scale, Hq, Hkv, D)
     out = A.attn_decode(q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), pt.to(DEV), seq.to(DEV), scale, Hq, Hkv, D)
     _close(out.cpu(), ref, 2e-2, 2e-2, "attn_decode")
+    # one workspace reused by consecutive launches (the fused combine's arrival counters must be back at zero)
+    ws = A.DecodeWorkspace(Bn, Hkv, Hq // Hkv, pt.shape[1], DEV)
+    args = (q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), pt.to(DEV), seq.to(DEV), scale, Hq, Hkv, D)
+    for _ in range(3):
+        out = A.attn_decode(*args, ws=ws)
+    _close(out.cpu(), ref, 2e-2, 2e-2, "attn_decode (reused workspace)")
+    assert int(ws.counters.abs().sum()) == 0
+    # the in-kernel merge of the partials (off by default) gives the same result
+    A._FUSED_COMBINE = True
+    try:
+        for _ in range(2):
+            out = A.attn_decode(*args, ws=ws)
+    finally:
+        A._FUSED_COMBINE = False
+    _close(out.cpu(), ref, 2e-2, 2e-2, "attn_decode (fused combine)")
+    assert int(ws.counters.abs().sum()) == 0
+    _lib.check_device_errors()
 
 
 @pytest.mark.parametrize("Hq,Hkv", [(8, 2), (4, 4)])
