@@ -84,7 +84,9 @@ class ModelRunner:
 
     def _graph_safe(self) -> bool:
         c = self.model.cfg
-        if c.use_mla or self.model.general_attn or any(lw.attn.window or lw.attn.sinks is not None for lw in self.model.layers):
+        if c.use_mla and not (c.kv_lora_rank == 512 and c.qk_rope_head_dim == 64 and self.model.dtype in (torch.float16, torch.bfloat16)):
+            return False        # latent shapes outside the MLA decode kernel run the PyTorch evaluation
+        if self.model.general_attn or any(lw.attn.window or lw.attn.sinks is not None for lw in self.model.layers):
             return False        # these paths evaluate attention with host-synchronising PyTorch ops
         if c.is_moe:
             # the per-expert fallback loop synchronises with the host; graphs need every MoE layer on the grouped kernels

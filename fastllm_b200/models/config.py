@@ -290,4 +290,12 @@ def preset(name: str) -> ModelConfig:
                                  scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=128,
                                  kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
                                  rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=2048))
+    if name == "small-deepseek-v3":      # DeepSeek-V3 attention geometry (latent 512 + rope 64) on a small body
+        return from_hf_dict(dict(model_type="deepseek_v3", vocab_size=1024, hidden_size=512, num_hidden_layers=2,
+                                 num_attention_heads=8, num_key_value_heads=8, intermediate_size=1024,
+                                 moe_intermediate_size=256, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1,
+                                 first_k_dense_replace=1, n_group=2, topk_group=1, routed_scaling_factor=2.5,
+                                 scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=256,
+                                 kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=4096))
     raise KeyError(f"unknown preset '{name}'")

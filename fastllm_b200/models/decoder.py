@@ -142,7 +142,8 @@ class DecoderModel:
         """Per-layer page-pool shapes of this rank: (K shape, V shape or None for MLA)."""
         c = self.cfg
         if c.use_mla:
-            return (num_pages, A.PAGE_LEN, 1, c.kv_lora_rank + c.qk_rope_head_dim), None
+            # one spare page at the end: rows that must not be cached (padded decode rows) are written there
+            return (num_pages + 1, A.PAGE_LEN, 1, c.kv_lora_rank + c.qk_rope_head_dim), None
         s = (num_pages, A.PAGE_LEN, self.num_kv_heads_local, c.head_dim)
         return s, s
 
@@ -258,12 +259,9 @@ class DecoderModel:
         q_pe = A.apply_rope_ref(q[..., nope:], fb.positions, cos, sin, self.rope_mode, rope)
         lat_pool = kv[0]
         flat = lat_pool.view(-1, lora + rope)
-        valid = fb.slots >= 0
         entry = torch.cat([c_lat, k_pe.reshape(T, rope)], dim=-1).to(flat.dtype)
-        if bool(valid.all()):
-            flat[fb.slots.long()] = entry
-        else:
-            flat[fb.slots[valid].long()] = entry[valid]
+        spare = flat.shape[0] - 1                              # last slot of the spare page (no host sync: graph-safe)
+        flat.index_copy_(0, torch.where(fb.slots >= 0, fb.slots, spare).long(), entry)
         # absorb: q_lat[h] = q_nope[h] @ W_UK[h]  -> attention in latent space with a single shared "KV head"
         q_lat = torch.einsum("thn,hnl->thl", q[..., :nope].float(), lw.w_uk.float()).to(x.dtype)
         q_full = torch.cat([q_lat, q_pe.to(x.dtype)], dim=-1)              # [T, H, lora + rope]

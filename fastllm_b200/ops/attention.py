@@ -317,3 +317,43 @@ def attn_prefill(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_head
                                         dtype_code(q.dtype), _stream())
     _lib.check(rc, "fb_attn_prefill")
     return out
+
+
+# ---------------------------------------------------------------------------------------------------
+# MLA decode (absorbed latent attention, kv_lora 512 + rope 64)
+# ---------------------------------------------------------------------------------------------------
+_lib.register_sigs({"fb_mla_decode": [ctypes.c_void_p] * 10 + [ctypes.c_int, ctypes.c_int, ctypes.c_longlong, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_float, ctypes.c_int, ctypes.c_void_p]}, ["attn_mla"])
+_MLA_WS: dict = {}
+
+
+class MlaWorkspace:
+    """Device scratch of the MLA decode kernel for up to (max_batch, max_pages, heads)."""
+
+    def __init__(self, max_batch, max_pages, heads, device):
+        groups = (heads + 31) // 32
+        self.max_items = max_batch * max_pages * groups
+        self.work = torch.zeros((self.max_items, 4), device=device, dtype=torch.int32)
+        self.n_work = torch.zeros((1,), device=device, dtype=torch.int32)
+        self.item_range = torch.zeros((max_batch, 2), device=device, dtype=torch.int32)
+        self.part_o = torch.empty((self.max_items * 32 * 512,), device=device, dtype=torch.float32)
+        self.part_ml = torch.empty((self.max_items * 32 * 2,), device=device, dtype=torch.float32)
+
+
+def mla_decode(q_full, lat_pool, page_table, seq_lens, scale, ws: MlaWorkspace | None = None):
+    """q_full ``[B, H, 576]`` (absorbed q_nope | rotated q_pe), lat_pool ``[pages, 128, 1, 576]`` -> ``[B, H, 512]``."""
+    B, H, _ = q_full.shape
+    P = page_table.shape[1]
+    if ws is None:
+        key = (q_full.device, B, P, H)
+        ws = _MLA_WS.get(key)
+        if ws is None:
+            ws = _MLA_WS[key] = MlaWorkspace(B, P, H, q_full.device)
+    q_full = q_full.contiguous()
+    out = torch.empty((B, H, 512), device=q_full.device, dtype=q_full.dtype)
+    num_slots = lat_pool.shape[0] * lat_pool.shape[1]
+    rc = _lib.kernels().fb_mla_decode(_ptr(q_full), _ptr(lat_pool), _ptr(out), _ptr(page_table), _ptr(seq_lens), _ptr(ws.work),
+                                      _ptr(ws.n_work), _ptr(ws.item_range), _ptr(ws.part_o), _ptr(ws.part_ml), B, H, num_slots,
+                                      page_table.stride(0), ws.max_items, float(scale), dtype_code(q_full.dtype), _stream())
+    _lib.check(rc, "fb_mla_decode")
+    return out

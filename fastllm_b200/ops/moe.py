@@ -141,6 +141,9 @@ def moe_forward(x, idx, wts, experts: ExpertWeights, ep=None):
     return y.to(x.dtype)
 
 
+_MLA_KERNEL = True      # tests switch this off to compare the kernel with the PyTorch evaluation
+
+
 def _moe_forward_host(x, idx, wts, experts: ExpertWeights):
     """Routed experts on the host: activations cross PCIe once per layer in each direction, expert weights never move
     (reference: ``--moe_device cpu``, tools/fastllm_pytools/util.py:818-826; docs/mixforward.md)."""
@@ -189,6 +192,11 @@ def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
     ``[T, H, lora]``.  (Reference: MergeMLAPaged, src/devices/cuda/attention/fastllm-attention.cu:3619-3727.)
     """
     T, H, Dq = q_full.shape
+    if (_MLA_KERNEL and fb.is_decode and q_full.is_cuda and lora == 512 and Dq == 576 and q_full.dtype in (torch.float16, torch.bfloat16)
+            and lat_pool.dtype == q_full.dtype and lat_pool.shape[1] == 128):
+        from .attention import mla_decode
+
+        return mla_decode(q_full, lat_pool, fb.page_table, fb.kv_lens, scale)
     out = torch.zeros((T, H, lora), device=q_full.device, dtype=q_full.dtype)
     page_len = lat_pool.shape[1]
     cu = fb.cu_q_host if fb.cu_q_host is not None else fb.cu_q.tolist()

@@ -361,3 +361,39 @@ def test_kernel_profile_table():
     finally:
         _lib.stop_profile()
     assert rep["fb_rmsnorm"]["calls"] == 3 and rep["fb_rmsnorm"]["ms"] > 0
+
+
+@pytest.mark.parametrize("H", [16, 4, 40, 128])
+def test_mla_decode(H):
+    """Absorbed MLA decode kernel vs the PyTorch evaluation over the same paged latent cache."""
+    from types import SimpleNamespace
+
+    from fastllm_b200.ops import moe as MOE
+
+    torch.manual_seed(11)
+    dt = torch.bfloat16
+    lens = [1, 127, 128, 129, 700, 2049, 77, 300]
+    Bn = len(lens)
+    n_pages = sum((l + 127) // 128 for l in lens) + 2
+    max_p = max((l + 127) // 128 for l in lens)
+    pt = torch.zeros(Bn, max_p, dtype=torch.int32)
+    perm = torch.randperm(n_pages)
+    c = 0
+    lat = torch.full((n_pages, 128, 1, 576), 3.0, dtype=dt)            # stale finite data behind the last token
+    for b, l in enumerate(lens):
+        n = (l + 127) // 128
+        pt[b, :n] = perm[c:c + n].int()
+        c += n
+        for i in range(n):
+            k = min(128, l - i * 128)
+            lat[pt[b, i], :k, 0] = (torch.randn(k, 576) * 0.5).to(dt)
+    q = (torch.randn(Bn, H, 576) * 0.5).to(dt)
+    seq = torch.tensor(lens, dtype=torch.int32)
+    scale = 0.07
+    fb_cpu = SimpleNamespace(is_decode=False, cu_q_host=list(range(Bn + 1)), cu_q=torch.arange(Bn + 1), kv_lens=seq, page_table=pt)
+    ref = MOE.mla_paged_attention(q.float(), lat.float(), fb_cpu, scale, 512)
+    out = A.mla_decode(q.to(DEV), lat.to(DEV), pt.to(DEV), seq.to(DEV), scale)
+    _lib.check_device_errors()
+    _close(out.float().cpu(), ref, 3e-2, 3e-2, f"mla_decode H={H}")
+    out2 = A.mla_decode(q.to(DEV), lat.to(DEV), pt.to(DEV), seq.to(DEV), scale)      # workspace reuse
+    assert torch.equal(out, out2)

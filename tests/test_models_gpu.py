@@ -65,3 +65,24 @@ def test_moe_experts_on_host_match_all_gpu():
         # the engine still generates with host experts (no CUDA graph on this path)
         assert len(eng.generate([prompt], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0]) == 4
     assert torch.nn.functional.cosine_similarity(outs[0], outs[1], dim=0).item() > 0.999
+
+
+def test_mla_decode_kernel_in_model_with_cuda_graph():
+    """DeepSeek-V3 attention geometry: decode through the MLA kernel inside CUDA graphs vs the PyTorch evaluation (eager)."""
+    from fastllm_b200.ops import moe as MOE
+
+    cfg = preset("small-deepseek-v3")
+    prompts = [list(range(5, 5 + n)) for n in (150, 37, 260)]
+    outs = []
+    for kernel in (True, False):
+        MOE._MLA_KERNEL = kernel
+        try:
+            m = random_init(cfg, "cuda", torch.bfloat16, std=0.05)
+            eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, use_cuda_graph=kernel), num_pages=16)
+            assert eng.runner.graph_ok == kernel
+            outs.append(eng.generate(prompts, GenerationConfig(max_new_tokens=8, ignore_eos=True)))
+        finally:
+            MOE._MLA_KERNEL = True
+    _lib.check_device_errors()
+    agree = sum(a[:4] == b[:4] for a, b in zip(*outs))
+    assert agree >= 2, outs
