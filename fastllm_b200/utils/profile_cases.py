@@ -50,7 +50,67 @@ def gemm_prefill(m=4096, n=6144, k=4096, iters=4):
     torch.cuda.synchronize()
 
 
+def gemm_quant(kind="fp8", n=28672, k=4096, m=64, iters=4):
+    from ..ops.quant import LinearWeight
+
+    dev = "cuda"
+    ws = [LinearWeight.from_dense((torch.randn(n, k, device=dev) * 0.02).bfloat16(), kind, interleaved=True) for _ in range(2)]
+    x = torch.randn(m, k, device=dev).bfloat16()
+    for i in range(iters):
+        ws[i % 2](x, swiglu=True)
+    torch.cuda.synchronize()
+
+
+def mla_decode(batch=32, length=2300, heads=16, iters=4):
+    dev = "cuda"
+    npg = (length + 127) // 128
+    pages = batch * npg
+    lat = (torch.randn(pages + 1, 128, 1, 576, device=dev) * 0.5).bfloat16()
+    pt = torch.randperm(pages, device=dev).int().view(batch, npg)
+    seq = torch.full((batch,), length, dtype=torch.int32, device=dev)
+    q = (torch.randn(batch, heads, 576, device=dev) * 0.5).bfloat16()
+    for _ in range(iters):
+        A.mla_decode(q, lat, pt, seq, 0.07)
+    torch.cuda.synchronize()
+
+
+def attn_prefill(batch=4, length=2048, hq=32, hkv=8, iters=3):
+    dev, D = "cuda", 128
+    npg = (length + 127) // 128
+    pages = batch * npg
+    k_pool = (torch.randn(pages, 128, hkv, D, device=dev) * 0.5).bfloat16()
+    v_pool = torch.randn(pages, 128, hkv, D, device=dev).bfloat16()
+    pt = torch.randperm(pages, device=dev).int().view(batch, npg)
+    kv = torch.full((batch,), length, dtype=torch.int32, device=dev)
+    cu = (torch.arange(batch + 1, device=dev) * length).int()
+    q = torch.randn(batch * length, hq * D, device=dev).bfloat16()
+    for _ in range(iters):
+        A.attn_prefill(q, k_pool, v_pool, pt, kv, cu, 1 / math.sqrt(D), hq, hkv, D)
+    torch.cuda.synchronize()
+
+
+def moe_grouped(tokens=128, experts=128, topk=8, hidden=2048, inter=768, kind="fp8", iters=4):
+    from ..models.config import preset
+    from ..models.decoder import random_init
+    from ..ops import moe as MOE
+
+    cfg = preset("qwen3-30b-a3b")
+    cfg.num_layers = 1
+    m = random_init(cfg, "cuda", torch.bfloat16, moe_wdtype=kind)
+    ex = m.layers[0].mlp.experts
+    x = torch.randn(tokens, hidden, device="cuda").bfloat16()
+    idx, w = MOE.route_topk(torch.randn(tokens, experts, device="cuda"), None, topk, 0, True)
+    for _ in range(iters):
+        MOE.moe_forward(x, idx, w, ex)
+    torch.cuda.synchronize()
+
+
 CASES = {
+    "gemm_quant_fp8": lambda: gemm_quant("fp8"),
+    "gemm_quant_int4g": lambda: gemm_quant("int4g128"),
+    "mla_decode": mla_decode,
+    "attn_prefill": attn_prefill,
+    "moe_grouped_fp8": moe_grouped,
     "gemm_decode_gate_up": lambda: gemm_decode(28672, 4096, 64, True),
     "gemm_decode_down": lambda: gemm_decode(4096, 14336, 64, False),
     "attn_decode": attn_decode,
