@@ -16,6 +16,7 @@ from typing import Iterable
 import torch
 
 from .engine import EngineConfig, GenerationConfig, LLMEngine
+from .graph import ComputeGraph  # noqa: F401  (custom model files import it from here, as with the reference)
 from .models.decoder import TPInfo
 from .tokenizer import StreamDecoder, Tokenizer
 
@@ -114,6 +115,11 @@ class model:
         self.hf_tokenizer = self.tokenizer.hf
         if _model is not None:
             self.torch_model = _model
+        elif graph is not None:
+            from . import graph as G
+
+            cls = G.load_custom_file(graph) if isinstance(graph, str) else graph
+            self.torch_model = G.load_graph_model(path, cls, device=dev)
         elif path and path.endswith(".flm"):
             from .loader import flm
 
@@ -139,7 +145,7 @@ class model:
             self.torch_model = hf_loader.load_model(path, device=dev, wdtype=dtype or "auto", moe_wdtype=moe_dtype or None, tp=tp,
                                                     moe_device="cpu" if (isinstance(md, str) and md.startswith(("cpu", "numa"))) else None,
                                                     moe_device_layers=int(_settings.get("moe_device_layers", -1) or -1),
-                                                    dtype_config=dtype_config or None)
+                                                    dtype_config=dtype_config or None, lora=lora or None)
         cfg = self.torch_model.cfg
         eos = set(cfg.eos_token_ids) | set(self.tokenizer.eos_ids())
         for t in eos_token or []:

@@ -118,6 +118,32 @@ class HFCheckpoint:
             return dequant_awq(self.raw(prefix + ".qweight"), self.raw(prefix + ".qzeros"), self.raw(prefix + ".scales"), self.dtype)
         return None
 
+    def attach_lora(self, adapter_dir: str | Path) -> int:
+        """Register a PEFT LoRA adapter folder (``adapter_config.json`` + ``adapter_model.safetensors``): every targeted
+        weight is returned merged, ``W + (alpha / r) * B @ A``.  Returns the number of adapted matrices.
+        (Reference: the ``lora`` argument of ``llm.model``, tools/fastllm_pytools/llm.py:1083.)"""
+        ad = Path(adapter_dir)
+        conf = json.loads((ad / "adapter_config.json").read_text())
+        scale = float(conf.get("lora_alpha", conf.get("r", 1))) / float(conf.get("r", 1))
+        f = st.SafeTensorFile(ad / "adapter_model.safetensors")
+        self.lora = {}
+        for k in f.keys():
+            if ".lora_A" not in k:
+                continue
+            base = k.split(".lora_A")[0]
+            kb = k.replace(".lora_A", ".lora_B")
+            name = canonical_name(re.sub(r"^base_model\.model\.", "", base))
+            self.lora[name] = (f.get(k).float().clone(), f.get(kb).float().clone(), scale)
+        f.close()
+        return len(self.lora)
+
+    def _merged(self, base: str, w):
+        lo = getattr(self, "lora", None)
+        if not lo or base not in lo or w is None:
+            return w
+        a, b, scale = lo[base]
+        return (w.float() + scale * (b @ a)).to(w.dtype)
+
     def collect(self, prefix: str) -> dict:
         """All tensors under ``prefix`` as canonical name -> dense tensor (quantised triples collapsed to .weight)."""
         out = {}
@@ -132,7 +158,7 @@ class HFCheckpoint:
                 if base in done:
                     continue
                 done.add(base)
-                out[base + ".weight"] = self.weight(base)
+                out[base + ".weight"] = self._merged(base, self.weight(base))
             else:
                 out[n] = self.raw(n)
         return out
@@ -153,7 +179,7 @@ def resolve_wdtype(name: str, default: str, rules: list | None) -> str:
 
 def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto", moe_wdtype: str | None = None,
                tp: TPInfo | None = None, ep=None, dtype_config: list | str | None = None, moe_device: str | None = None,
-               moe_device_layers: int = -1) -> DecoderModel:
+               moe_device_layers: int = -1, lora: str | None = None) -> DecoderModel:
     """Build a ready-to-run ``DecoderModel`` from an HF folder.
 
     ``moe_device="cpu"`` keeps the routed experts (of the first ``moe_device_layers`` layers, all when negative) in host
@@ -170,6 +196,8 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
     if isinstance(dtype_config, str) and dtype_config:
         dtype_config = json.loads(Path(dtype_config).read_text()) if Path(dtype_config).exists() else json.loads(dtype_config)
     ck = HFCheckpoint(path, cfg, dtype if dtype != torch.float32 else torch.float32)
+    if lora:
+        ck.attach_lora(lora)
     if wdtype == "auto" and cfg.quantization_config:
         q = cfg.quantization_config
         method = str(q.get("quant_method", "")).lower()

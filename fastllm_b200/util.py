@@ -153,7 +153,7 @@ def make_normal_llm_model(args):
             return EncoderModel(args.path, device)
     m = llm.model(args.path, dtype=args.dtype, kv_cache_dtype=args.kv_cache_dtype, moe_dtype=args.moe_dtype, lora=args.lora,
                   dtype_config=args.dtype_config, ori_model_path=args.ori, chat_template=args.chat_template,
-                  tool_call_parser=args.tool_call_parser, device=device, tp=tp)
+                  tool_call_parser=args.tool_call_parser, device=device, tp=tp, graph=(getattr(args, "custom", "") or None))
     if tp is not None and tp.size > 1:
         from .parallel import symm
 

@@ -92,3 +92,27 @@ def test_int4g_packing_high_nibble_first():
     w = torch.tensor([[0.0, 15.0] * 64])
     packed, scale, mn = quant.quantize_int4g(w, 128)
     assert packed[0, 0].item() == 0x0F      # first value (0) in the high nibble, second (15) in the low nibble
+
+
+def test_lora_adapter_is_merged_at_load(tmp_path):
+    """A PEFT-style adapter folder: the loaded projection equals W + (alpha / r) * B @ A."""
+    import json
+
+    from fastllm_b200.loader.safetensors import save_file
+
+    d = _write_hf(tmp_path, "tiny-llama")
+    base = hf.load_model(d, device="cpu", dtype=torch.float32)
+    torch.manual_seed(0)
+    r, alpha = 4, 8
+    H = base.cfg.hidden_size
+    K = base.cfg.num_heads * base.cfg.head_dim
+    a, b = torch.randn(r, K) * 0.1, torch.randn(H, r) * 0.1          # o_proj of layer 1: [H, heads * head_dim]
+    ad = tmp_path / "adapter"
+    ad.mkdir()
+    (ad / "adapter_config.json").write_text(json.dumps({"r": r, "lora_alpha": alpha, "target_modules": ["o_proj"]}))
+    save_file({"base_model.model.model.layers.1.self_attn.o_proj.lora_A.weight": a,
+               "base_model.model.model.layers.1.self_attn.o_proj.lora_B.weight": b}, ad / "adapter_model.safetensors")
+    tuned = hf.load_model(d, device="cpu", dtype=torch.float32, lora=str(ad))
+    want = base.layers[1].attn.o.w + (alpha / r) * (b @ a)
+    assert torch.allclose(tuned.layers[1].attn.o.w, want, atol=1e-6)
+    assert torch.equal(tuned.layers[0].attn.o.w, base.layers[0].attn.o.w)
