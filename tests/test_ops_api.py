@@ -1,0 +1,96 @@
+"""Operator API (reference operator names): every operator against its plain PyTorch definition on the CPU, and, with a
+GPU, the CUDA result against the CPU result (the reference's optest scheme: CPU run = baseline, other devices compared)."""
+import math
+
+import pytest
+import torch
+
+from fastllm_b200.ops import api as O
+from fastllm_b200.ops import attention as A
+
+
+def test_elementwise_and_layout_ops_cpu():
+    torch.manual_seed(0)
+    x = torch.randn(5, 64)
+    assert torch.allclose(O.Silu(x), torch.nn.functional.silu(x), atol=1e-5)
+    assert torch.allclose(O.GeluNew(x), torch.nn.functional.gelu(x, approximate="tanh"), atol=1e-5)
+    assert torch.allclose(O.Swiglu(x), torch.nn.functional.silu(x[:, :32]) * x[:, 32:], atol=1e-5)
+    assert torch.allclose(O.SoftMax(x), torch.softmax(x, -1), atol=1e-6)
+    assert torch.allclose(O.LayerNorm(x, torch.ones(64), torch.zeros(64)), torch.nn.functional.layer_norm(x, (64,)), atol=1e-4)
+    y = x.clone()
+    O.AddTo(y, x, 0.5)
+    assert torch.allclose(y, 1.5 * x)
+    assert O.Cat(x, x, 1).shape == (5, 128) and O.Split(x, 1, 8, 24).shape == (5, 16) and O.Repeat(x, 0, 3).shape == (15, 64)
+    assert torch.equal(O.Permute(x.reshape(5, 8, 8), (1, 0, 2)), x.reshape(5, 8, 8).permute(1, 0, 2))
+    tk = O.TopK(x, 3)
+    assert tk.shape == (5, 3, 2) and torch.equal(tk[..., 0].long(), x.topk(3).indices)
+
+
+def test_linear_matmul_attention_cpu():
+    torch.manual_seed(1)
+    x, w, b = torch.randn(6, 96), torch.randn(40, 96) * 0.1, torch.randn(40)
+    assert torch.allclose(O.Linear(x, w, b), x @ w.t() + b, atol=1e-4)
+    out = torch.ones(6, 40)
+    O.LinearAdd(x, w, None, out)
+    assert torch.allclose(out, 1 + x @ w.t(), atol=1e-4)
+    wg = torch.randn(128, 96) * 0.1
+    gu = x @ wg.t()
+    assert torch.allclose(O.LinearSwiglu(x, wg), torch.nn.functional.silu(gu[:, :64]) * gu[:, 64:], atol=1e-4)
+    assert torch.allclose(O.MatMulTransB(x, w, 0.5), 0.5 * x @ w.t(), atol=1e-5)
+    q, k, v = torch.randn(4, 3, 16), torch.randn(2, 7, 16), torch.randn(2, 7, 16)
+    got = O.Attention(q, k, v, group=2, causal=True)
+    ref = torch.nn.functional.scaled_dot_product_attention(q[None], k.repeat_interleave(2, 0)[None], v.repeat_interleave(2, 0)[None],
+                                                           attn_mask=torch.ones(3, 7, dtype=torch.bool).tril(diagonal=4))[0]
+    assert torch.allclose(got, ref, atol=1e-5)
+    sc = torch.zeros(2, 3, 5)
+    al = O.AlibiMask(sc, torch.tensor([0.5, 0.25]))
+    assert al[0, 0, 2] == 0 and al[0, 0, 0] == -1.0 and al[1, 2, 0] == -1.0 and al[0, 0, 3] == -1e4
+
+
+def test_rope_and_select_expert_cpu():
+    torch.manual_seed(2)
+    x = torch.randn(4, 2, 32)
+    pos = torch.tensor([0, 5, 9, 2])
+    cos, sin = A.build_rope_tables(32, 16, 10000.0)
+    a = O.LlamaRotatePosition2D(x, pos, sin, cos, 16)
+    b = O.RopeEncoding(x, pos, 32, 10000.0)
+    assert torch.allclose(a, b, atol=1e-5)
+    inter = O.NearlyRotatePosition2D(x, pos, sin, cos, 16)
+    assert not torch.allclose(a, inter) and torch.allclose(inter[0], x[0], atol=1e-6)     # position 0 is the identity
+    lg = torch.randn(7, 16)
+    idx, w = O.FusedSoftmaxSelectExpert(lg, 2, True)
+    p = torch.softmax(lg, -1)
+    ti = p.topk(2).indices
+    assert torch.equal(idx.long(), ti) and torch.allclose(w, p.gather(1, ti) / p.gather(1, ti).sum(-1, keepdim=True), atol=1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("name", ["Linear", "LinearSwiglu", "RMSNorm", "Swiglu", "Embedding", "SelectExpert"])
+def test_cuda_matches_cpu(name):
+    """CPU run = baseline, CUDA compared with atol / rtol (reference: RunSingleCase, test/ops/cppOps.cpp:3395-3470)."""
+    from fastllm_b200.ops import basic as B
+
+    torch.manual_seed(3)
+    dt = torch.bfloat16
+    x = torch.randn(33, 512)
+    if name == "Linear":
+        w, b = torch.randn(256, 512) * 0.05, torch.randn(256)
+        cpu, gpu = O.Linear(x, w, b), O.Linear(x.cuda().to(dt), w.cuda().to(dt), b.cuda().to(dt))
+    elif name == "LinearSwiglu":
+        g, u = torch.randn(256, 512) * 0.05, torch.randn(256, 512) * 0.05
+        cpu = O.LinearSwiglu(x, torch.cat([g, u]))
+        gpu = O.LinearSwiglu(x.cuda().to(dt), B.interleave_gate_up(g.cuda().to(dt), u.cuda().to(dt)), interleaved=True)
+    elif name == "RMSNorm":
+        w = torch.randn(512)
+        cpu, gpu = O.RMSNorm(x, w, 1e-6), O.RMSNorm(x.cuda().to(dt), w.cuda().to(dt), 1e-6)
+    elif name == "Swiglu":
+        cpu, gpu = O.Swiglu(x), O.Swiglu(x.cuda().to(dt))
+    elif name == "Embedding":
+        tab, ids = torch.randn(100, 512), torch.randint(0, 100, (33,))
+        cpu, gpu = O.Embedding(ids, tab), O.Embedding(ids.cuda().int(), tab.cuda().to(dt))
+    else:
+        lg, bias = torch.randn(33, 64), torch.randn(64) * 0.1
+        (ci, cw), (gi, gw) = O.SelectExpert(lg, bias, 4, True, 2.0, "sigmoid"), O.SelectExpert(lg.cuda(), bias.cuda(), 4, True, 2.0, "sigmoid")
+        assert torch.equal(ci.long(), gi.cpu().long())
+        cpu, gpu = cw, gw
+    assert torch.allclose(gpu.float().cpu(), cpu.float(), atol=6e-2, rtol=3e-2)
