@@ -96,7 +96,10 @@ class KVCache:
         ks, vs = model.kv_cache_shape(num_pages)
         dev, dt = model.device, model.dtype
         self.pools = []
-        for _ in range(model.cfg.num_layers):
+        staged = getattr(model, "layer_devices", None)
+        for i in range(model.cfg.num_layers):
+            if staged is not None:
+                dev = staged[i]            # layer-split placement: a layer's pages live on that layer's device
             k = torch.zeros(ks, device=dev, dtype=dt)
             v = torch.zeros(vs, device=dev, dtype=dt) if vs is not None else None
             self.pools.append((k, v))

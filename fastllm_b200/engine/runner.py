@@ -84,6 +84,8 @@ class ModelRunner:
 
     def _graph_safe(self) -> bool:
         c = self.model.cfg
+        if getattr(self.model, "layer_devices", None) is not None:
+            return False        # one graph cannot span the devices of a layer-split placement
         if c.use_mla and not (c.kv_lora_rank == 512 and c.qk_rope_head_dim == 64 and self.model.dtype in (torch.float16, torch.bfloat16)):
             return False        # latent shapes outside the MLA decode kernel run the PyTorch evaluation
         if self.model.general_attn or any(lw.attn.window or lw.attn.sinks is not None for lw in self.model.layers):

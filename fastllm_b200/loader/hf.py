@@ -179,7 +179,7 @@ def resolve_wdtype(name: str, default: str, rules: list | None) -> str:
 
 def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto", moe_wdtype: str | None = None,
                tp: TPInfo | None = None, ep=None, dtype_config: list | str | None = None, moe_device: str | None = None,
-               moe_device_layers: int = -1, lora: str | None = None) -> DecoderModel:
+               moe_device_layers: int = -1, lora: str | None = None, device_map: dict | None = None) -> DecoderModel:
     """Build a ready-to-run ``DecoderModel`` from an HF folder.
 
     ``moe_device="cpu"`` keeps the routed experts (of the first ``moe_device_layers`` layers, all when negative) in host
@@ -205,8 +205,15 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
             wdtype = "fp8"
         elif method in ("awq", "gptq", "compressed-tensors"):
             wdtype = f"int4g{q.get('group_size', 128)}"
+    if device_map:
+        from .shard import split_layers_by_map
+
+        staged = split_layers_by_map(cfg.num_layers, device_map)
+        device = staged[0]
     m = DecoderModel(cfg, device, dtype, tp, ep)
     m.moe_device, m.moe_device_layers = moe_device, moe_device_layers
+    if device_map and len(set(map(str, staged))) > 1:
+        m.layer_devices = staged
 
     def top_fn():
         t = {}

@@ -38,6 +38,20 @@ def _to(t, m):
     return t.to(m.device).contiguous()
 
 
+def split_layers_by_map(num_layers: int, device_map: dict) -> list:
+    """``{'cuda:0': 3, 'cuda:1': 2}`` -> one device per layer, contiguous blocks in proportion to the weights
+    (reference: SelectDeviceFromMap / ApplyDeviceMap, src/fastllm.cpp:5178-5204)."""
+    items = [(torch.device(k), float(v)) for k, v in device_map.items() if float(v) > 0]
+    total = sum(v for _, v in items)
+    out, acc = [], 0.0
+    for dev, v in items:
+        acc += v
+        upto = num_layers if dev is items[-1][0] else round(num_layers * acc / total)
+        out.extend([dev] * max(0, upto - len(out)))
+    out.extend([items[-1][0]] * (num_layers - len(out)))
+    return out[:num_layers]
+
+
 class _HostPlacement:
     """Stand-in for the model when a weight is built for the CPU (expert offload): same dtype rules, CPU device."""
 
@@ -233,9 +247,23 @@ def build_top(m, t: dict, wdtype="dense"):
 
 def finalize_model(m, top_fn, layer_fn, wdtype="dense", moe_wdtype=None):
     """``top_fn()`` / ``layer_fn(i)`` return dicts of canonical tensors; they are consumed one layer at a time."""
+    home = m.device
+    staged = getattr(m, "layer_devices", None)
     build_top(m, top_fn(), wdtype)
     for i in range(m.cfg.num_layers):
+        if staged is not None:
+            m.device = staged[i]           # the builders place tensors on m.device
         build_layer(m, i, layer_fn(i), wdtype, moe_wdtype)
+    m.device = home
+    if staged is not None:                 # the head runs where the last layer left the activations
+        last = staged[-1]
+        m.final_norm = m.final_norm.to(last)
+        hw = m.lm_head
+        hw.w = hw.w.to(last)
+        for name in ("scale", "zero", "bias"):
+            t = getattr(hw, name)
+            if t is not None:
+                setattr(hw, name, t.to(last))
     if m.on_cuda:
         from ..ops import moe_grouped
 

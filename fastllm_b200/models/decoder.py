@@ -117,6 +117,7 @@ class DecoderModel:
         self.kv_replicas = max(1, self.tp.size // cfg.num_kv_heads)
         self._rope = None
         self._fused_active = False
+        self.layer_devices = None          # per-layer devices for the layer-split placement (None: everything on self.device)
         self.rope_mode = {"neox": A.ROPE_NEOX, "interleaved": A.ROPE_INTERLEAVED, "none": A.ROPE_NONE}[cfg.rope_mode]
         self.rot_dim = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
         self.attn_scale = cfg.attn_scale_override if cfg.attn_scale_override else 1.0 / math.sqrt(cfg.q_head_dim)
@@ -127,7 +128,14 @@ class DecoderModel:
             self.attn_scale *= ms * ms
 
     # -----------------------------------------------------------------------------------------------
-    def rope_tables(self, max_pos: int | None = None):
+    def rope_tables(self, max_pos: int | None = None, device=None):
+        if device is not None and torch.device(device) != self.device:
+            key = str(torch.device(device))
+            cache = self.__dict__.setdefault("_rope_by_device", {})
+            if key not in cache:
+                cos, sin = self.rope_tables(max_pos)
+                cache[key] = (cos.to(device), sin.to(device))
+            return cache[key]
         if self._rope is None:
             mp = max_pos or min(self.cfg.max_position, 1 << 17)
             scaling = self.cfg.rope_scaling
@@ -158,7 +166,7 @@ class DecoderModel:
         if c.use_mla:
             return self._mla_attention(lw, x, fb, kv, residual, next_ln)
         Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
-        cos, sin = self.rope_tables()
+        cos, sin = self.rope_tables(device=x.device)
         qkv = lw.qkv(x)
         k_pool, v_pool = kv
         if self.general_attn or lw.window or lw.sinks is not None:
@@ -349,6 +357,8 @@ class DecoderModel:
         if fb.is_decode and self.on_cuda and fb.decode_ws is not None and not fb.decode_planned:
             fb.decode_ws.plan(fb.kv_lens)
             fb.decode_planned = True
+        if self.layer_devices is not None:
+            return self._forward_staged(fb, kv_caches)
         h = self.embed_tokens(fb.ids)
         if self._fused_active:
             h = fused.load_h(h)
@@ -367,6 +377,55 @@ class DecoderModel:
         if c.final_softcap:
             logits = torch.tanh(logits / c.final_softcap) * c.final_softcap
         return logits
+
+    def _forward_staged(self, fb: ForwardBatch, kv_caches) -> torch.Tensor:
+        """Layer-split placement (``--device "{'cuda:0': 3, 'cuda:1': 2}"`` / ``cudapp``): every layer runs on its own
+        device, the residual stream and the normalised activations are handed over by a peer copy at stage boundaries.
+        Sequential like the reference's device map (src/fastllm.cpp:5178-5204, src/executor.cpp:211-339), no micro-batching."""
+        c = self.cfg
+        n_layers = len(self.layers)
+        fbs: dict = {}
+
+        def batch_on(dev):
+            key = str(dev)
+            if key not in fbs:
+                mv = lambda t: t.to(dev, non_blocking=True) if t is not None else None
+                fbs[key] = ForwardBatch(ids=mv(fb.ids), positions=mv(fb.positions), slots=mv(fb.slots), page_table=mv(fb.page_table),
+                                        kv_lens=mv(fb.kv_lens), cu_q=mv(fb.cu_q), logit_rows=mv(fb.logit_rows), is_decode=fb.is_decode,
+                                        cu_q_host=fb.cu_q_host)
+            return fbs[key]
+
+        ln_cache = self.__dict__.setdefault("_ln_by_device", {})
+
+        def ln_on(w, dev):
+            if w.device == dev:
+                return w
+            key = (id(w), str(dev))
+            if key not in ln_cache:
+                ln_cache[key] = w.to(dev)
+            return ln_cache[key]
+
+        dev = self.layer_devices[0]
+        with torch.cuda.device(dev):
+            h = self.embed_tokens(batch_on(dev).ids)
+            x = self._norm(h, self.layers[0].attn.ln)
+        for i, lw in enumerate(self.layers):
+            nd = self.layer_devices[i]
+            if nd != dev:
+                h, x = h.to(nd), x.to(nd)
+                dev = nd
+            with torch.cuda.device(dev):
+                h, x = self._attention(lw.attn, x, batch_on(dev), kv_caches[i], h, lw.mlp.ln)
+                next_ln = self.layers[i + 1].attn.ln if i + 1 < n_layers else self.final_norm
+                h, x = self._mlp(lw.mlp, x, h, i, ln_on(next_ln, dev))
+        with torch.cuda.device(dev):
+            rows = batch_on(dev).logit_rows
+            if rows is not None:
+                x = x.index_select(0, rows)
+            logits = self.lm_head(x, out_f32=True)
+            if c.logit_scale != 1.0:
+                logits = logits * c.logit_scale
+        return logits.to(self.device)
 
     def _native_cpu(self):
         """The whole-model native CPU runner for this model, or None when the architecture is outside its coverage."""

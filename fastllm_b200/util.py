@@ -112,6 +112,9 @@ def make_normal_llm_model(args):
     else:
         llm.set_cpu_threads(max(1, min(32, (os.cpu_count() or 4) - 2)))
     kind, gpu_ids, raw_map = parse_device(args.device)
+    if raw_map:                      # layer-split placement over several GPUs of this process
+        llm.set_device_map(raw_map)
+        gpu_ids = gpu_ids[:1]
     tp_ids = parse_tp(args.tp) or (gpu_ids if len(gpu_ids) > 1 else [])
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if len(tp_ids) > 1 and world == 1:

@@ -116,3 +116,12 @@ def test_lora_adapter_is_merged_at_load(tmp_path):
     want = base.layers[1].attn.o.w + (alpha / r) * (b @ a)
     assert torch.allclose(tuned.layers[1].attn.o.w, want, atol=1e-6)
     assert torch.equal(tuned.layers[0].attn.o.w, base.layers[0].attn.o.w)
+
+
+def test_split_layers_by_device_map():
+    from fastllm_b200.loader.shard import split_layers_by_map
+
+    d = split_layers_by_map(10, {"cuda:0": 3, "cuda:1": 2})
+    assert [str(x) for x in d] == ["cuda:0"] * 6 + ["cuda:1"] * 4
+    assert [str(x) for x in split_layers_by_map(3, {"cuda:0": 1, "cuda:1": 1, "cuda:2": 1})] == ["cuda:0", "cuda:1", "cuda:2"]
+    assert len(split_layers_by_map(7, {"cuda:0": 1})) == 7
