@@ -424,8 +424,8 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
   if (grid_ctas == 0) grid_ctas = deep ? sm_count : 2 * sm_count;
 #define FB_AD_LAUNCH(BF, ST, GPV)                                                                                       \
   {                                                                                                                     \
-    static bool cfg = false;                                                                                            \
-    if (!cfg) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); cfg = true; } \
+    static DeviceOnce cfg;                                                                                            \
+    if (cfg.need()) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); } \
     launch_k<PDL_ATTN>(attn_decode_kernel<BF, ST, GPV>, dim3(grid_ctas), dim3(192), ad_smem_bytes(ST), stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
     if (counters == nullptr)                                                                                            \
       launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits); \

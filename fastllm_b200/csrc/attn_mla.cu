@@ -405,8 +405,8 @@ extern "C" int fb_mla_decode(const void* q, const void* lat_pool, void* out, con
   const int gp = (H <= 16) ? 16 : 32;
 #define FB_MLA_LAUNCH(BF, GPV)                                                                                          \
   {                                                                                                                     \
-    static bool cfg = false;                                                                                            \
-    if (!cfg) { cudaFuncSetAttribute(mla_decode_kernel<BF, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ML_SMEM); cfg = true; } \
+    static DeviceOnce cfg;                                                                                            \
+    if (cfg.need()) { cudaFuncSetAttribute(mla_decode_kernel<BF, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ML_SMEM); } \
     launch_k<PDL_ATTN>(mla_decode_kernel<BF, GPV>, dim3(sm_count), dim3(192), ML_SMEM, stream, 0, tmLat, tmQ, p);        \
     launch_k<PDL_COMBINE>(mla_combine_kernel<BF>, dim3(B, H), dim3(128), 0, stream, 0, part_o, part_ml, item_range, (uint16_t*)out, H, n_groups); \
   }

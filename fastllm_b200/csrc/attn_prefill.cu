@@ -11,6 +11,7 @@
 // The reference routes this through FlashInfer's FA2 mma.sync kernel
 // (src/devices/cuda/attention/fastllm-attention.cu:2490, 3032-3600).
 #include "ptx.cuh"
+#include "launch.h"
 #include "tmap.h"
 
 FB_DEFINE_ERROR_API(attn_prefill)
@@ -271,12 +272,12 @@ extern "C" int fb_attn_prefill(const void* q, int ld_q, long long T, const void*
   p.idesc_o = make_idesc(f, f, 0, 1, 128, 128);
   dim3 grid(n_blocks, Hq);
   if (dtype == 1) {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_SMEM_BYTES); cfg = true; }
+    static DeviceOnce cfg;
+    if (cfg.need()) { cudaFuncSetAttribute(attn_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_SMEM_BYTES); }
     attn_prefill_kernel<true><<<grid, 192, AP_SMEM_BYTES, stream>>>(tmQ, tmK, tmV, p);
   } else {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_SMEM_BYTES); cfg = true; }
+    static DeviceOnce cfg;
+    if (cfg.need()) { cudaFuncSetAttribute(attn_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, AP_SMEM_BYTES); }
     attn_prefill_kernel<false><<<grid, 192, AP_SMEM_BYTES, stream>>>(tmQ, tmK, tmV, p);
   }
   return (int)cudaGetLastError();

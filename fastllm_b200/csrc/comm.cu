@@ -375,11 +375,10 @@ static cudaError_t launch_gemm_ar(const CUtensorMap& tmW, const CUtensorMap& tmX
                                   int nsplit, int n_tiles, cudaStream_t stream) {
   using Cfg = SmallMCfg<MPAD>;
   auto kern = gemm_ar_norm_kernel<MPAD, BF16>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.need()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, 1);

@@ -402,12 +402,12 @@ extern "C" int fb_rmsnorm(const void* x, const void* w, void* y, void* residual,
   const size_t smem = (size_t)H * sizeof(float);
   auto s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == 1) {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); cfg = true; }
+    static DeviceOnce cfg;
+    if (cfg.need()) { cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); }
     launch_k(rmsnorm_kernel<true>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
   } else {
-    static bool cfg = false;
-    if (!cfg) { cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); cfg = true; }
+    static DeviceOnce cfg;
+    if (cfg.need()) { cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); }
     launch_k(rmsnorm_kernel<false>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
   }
   return (int)cudaGetLastError();

@@ -210,11 +210,10 @@ static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX,
                                  cudaStream_t stream) {
   using Cfg = SmallMCfg<MPAD, OCC>;
   auto kern = gemm_smallm_kernel<MPAD, BF16, OCC>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.need()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, 1);
@@ -235,11 +234,10 @@ template <int BN, bool BF16>
 static cudaError_t launch_largem(const CUtensorMap& tmX, const CUtensorMap& tmW, const GemmParams& p, cudaStream_t stream) {
   using Cfg = LargeMCfg<BN>;
   auto kern = gemm_largem_kernel<BN, BF16>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.need()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   dim3 grid((p.N + BN - 1) / BN, (p.M + 127) / 128, 1);
   kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmX, tmW, p);

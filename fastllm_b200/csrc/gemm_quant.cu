@@ -325,11 +325,10 @@ static cudaError_t launch_quant(const CUtensorMap& tmW, const CUtensorMap& tmX, 
                                 int nsplit, int n_tiles, cudaStream_t stream) {
   using Cfg = QuantCfg<MPAD, QM>;
   auto kern = gemm_quant_kernel<MPAD, BF16, QM>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.need()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, 1);
@@ -405,11 +404,10 @@ static cudaError_t launch_grouped_quant(const CUtensorMap& tmW, const CUtensorMa
                                         const QuantGroupInfo& gi, int nsplit, int n_tiles, int nz, cudaStream_t stream) {
   using Cfg = QuantCfg<MPAD, QM>;
   auto kern = moe_grouped_quant_kernel<MPAD, BF16, QM>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.need()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, nz);

@@ -8,6 +8,19 @@
 
 namespace fb {
 
+// Kernel function attributes (dynamic shared-memory limit) belong to a device's context: set them once per device.
+struct DeviceOnce {
+  bool done[64] = {};
+  bool need() {
+    int d = 0;
+    cudaGetDevice(&d);
+    d &= 63;
+    if (done[d]) return false;
+    done[d] = true;
+    return true;
+  }
+};
+
 // Kernel classes for the FB_PDL bit mask: which launches carry the PDL attribute.  Default: the tensor-core GEMM kernels
 // only.  Measured on Llama-3-8B decode (64 x 1024): GEMM-only 5.67 ms/step vs 5.95 without PDL; adding the attention kernel
 // (+0.19 ms), its combine (+0.12 ms) or the row kernels (+0.04 ms) each made the step slower -- CTAs of a multi-CTA-per-SM

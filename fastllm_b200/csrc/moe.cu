@@ -186,11 +186,10 @@ static cudaError_t launch_grouped(const CUtensorMap& tmW, const CUtensorMap& tmX
                                   int nsplit, int n_tiles, int nz, cudaStream_t stream) {
   using Cfg = SmallMCfg<MPAD, 1>;
   auto kern = moe_grouped_gemm_kernel<MPAD, BF16>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;
+  if (configured.need()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    configured = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, nz);
