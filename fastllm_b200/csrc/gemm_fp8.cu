@@ -1,0 +1,380 @@
+// Block-scaled FP8 (e4m3 x e4m3) small-M GEMM for sm_100a: y = x W^T with 128x128 weight scales and 1x128 activation scales.
+//
+// Both operands stay FP8 all the way to the tensor core (tcgen05.mma kind::f8f6f4): the weight tile [128 n x 128 k] comes
+// straight from the checkpoint layout by TMA, the activation tile [MPAD tokens x 128 k] from a buffer quantised by
+// fb_quant_act_fp8 (per token and 128-wide k block).  Swap-AB like the 16-bit decode GEMM: weights are the UMMA A operand.
+// One k block (four K=32 MMAs) accumulates into one of two TMEM buffers; the four promotion warps read it back, multiply by
+// weight_scale[n tile, k block] * act_scale[token, k block] and add into fp32 registers while the tensor core fills the
+// other buffer.  K is split over a thread-block cluster; partial tiles meet in distributed shared memory and the shared
+// epilogue (bias -> SwiGLU -> residual -> store) finishes them.
+//
+// Reference: the W8A8 blockwise CUTLASS path exists only for sm89 / sm120 (src/devices/cuda/linear/fastllm-linear-fp8-cutlass.cu);
+// on a B200 the reference runs FP8 weights as W8A16 GEMV / dequant + cuBLAS (fastllm-linear-fp8.cu:1778-1868).
+#include "gemm_smallm.cuh"
+#include "launch.h"
+#include "tmap.h"
+
+FB_DEFINE_ERROR_API(gemm_fp8)
+
+namespace fb {
+
+constexpr int KID_GEMM_FP8 = 14;
+
+template <int MPAD>
+struct Fp8Cfg {
+  static constexpr int A_BYTES = 128 * 128;              // 128 weight rows x 128 fp8
+  static constexpr int B_BYTES = MPAD * 128;             // MPAD tokens x 128 fp8
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int MAX_STAGES = (100 * 1024) / STAGE_BYTES;          // two CTAs per SM
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int RED_BYTES = MPAD * 128 * 4;
+  static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
+  static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
+  static constexpr int SMEM_BYTES = BODY_BYTES + 256 + 1024;
+  static constexpr int TMEM_COLS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
+};
+
+struct Fp8Scales {
+  const float* w_scale;      // [N / 128, kb_total]
+  const float* a_scale;      // [kb_total, ld_a] (k-block major: one contiguous row of token scales per k block)
+  int ld_a;
+};
+
+template <int MPAD, bool BF16>
+__device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const Fp8Scales& sc) {
+  using Cfg = Fp8Cfg<MPAD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* tm_full = empty_bar + Cfg::STAGES;      // [2] k block accumulated into TMEM buffer b
+  uint64_t* tm_empty = tm_full + 2;                 // [2] promotion warps have read buffer b
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tm_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = (int)cluster_ctarank();
+  const int nsplit = (int)cluster_nctarank();
+  const int n_tile = blockIdx.y;
+  const int kb0 = split * p.kb_per_split;           // k blocks of 128
+  int kb_cnt = p.kb_total - kb0;
+  if (kb_cnt > p.kb_per_split) kb_cnt = p.kb_per_split;
+  if (kb_cnt < 0) kb_cnt = 0;
+  bool dead = false;
+  pdl_launch_dependents();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); }
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
+      for (int i = 0; i < pre; ++i) {          // weights do not depend on the previous kernel
+        mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmW, &full_bar[i], (kb0 + i) * 128, p.w_row0 + n_tile * 128, pol_w);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmX, &full_bar[i], (kb0 + i) * 128, p.x_row0, pol_x);
+      for (int i = pre; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_FP8, 1)) break;
+        uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 128, p.w_row0 + n_tile * 128, pol_w);
+        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], (kb0 + i) * 128, p.x_row0, pol_x);
+      }
+    }
+    __syncwarp();
+    pdl_wait();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES, b = i & 1;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_FP8, 2)) break;
+        if (!mbar_wait(&tm_empty[b], (((uint32_t)i >> 1) & 1u) ^ 1u, dead, KID_GEMM_FP8, 3)) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+        const uint64_t db = make_smem_desc(a_addr + Cfg::A_BYTES, 16, 1024, SWZ_128B);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f8(tmem_base + b * MPAD, da + 2 * k, db + 2 * k, p.idesc, k != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+        umma_commit(&tm_full[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    // promotion warps: TMEM lanes [32q, 32q+32) = weight rows; one fp32 accumulator per token in registers
+    const int q = warp & 3;
+    const int n_local = q * 32 + lane;
+    float acc[MPAD];
+#pragma unroll
+    for (int j = 0; j < MPAD; ++j) acc[j] = 0.f;
+    pdl_wait();
+    const float* wsp = sc.w_scale + (size_t)((p.w_row0 >> 7) + n_tile) * p.kb_total + kb0;
+    constexpr int CH = MPAD < 32 ? MPAD : 32;
+    for (int i = 0; i < kb_cnt; ++i) {
+      const int b = i & 1;
+      if (!mbar_wait(&tm_full[b], ((uint32_t)i >> 1) & 1u, dead, KID_GEMM_FP8, 4)) break;
+      tc_fence_after_sync();
+      const float ws = __ldg(wsp + i);
+      const float4* asp = reinterpret_cast<const float4*>(sc.a_scale + (size_t)(kb0 + i) * sc.ld_a + p.x_row0);
+#pragma unroll
+      for (int c0 = 0; c0 < MPAD; c0 += CH) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + b * MPAD + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if (CH == 32) tmem_ld_32x32b_x32(taddr, r); else tmem_ld_32x32b_x16(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; j += 4) {
+          const float4 a4 = __ldg(asp + ((c0 + j) >> 2));
+          acc[c0 + j + 0] = fmaf(__uint_as_float(r[j + 0]), ws * a4.x, acc[c0 + j + 0]);
+          acc[c0 + j + 1] = fmaf(__uint_as_float(r[j + 1]), ws * a4.y, acc[c0 + j + 1]);
+          acc[c0 + j + 2] = fmaf(__uint_as_float(r[j + 2]), ws * a4.z, acc[c0 + j + 2]);
+          acc[c0 + j + 3] = fmaf(__uint_as_float(r[j + 3]), ws * a4.w, acc[c0 + j + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tm_empty[b]);
+    }
+    // every MMA has completed (the last tm_full was observed) and every TMA tile was consumed: the ring becomes P
+    float* P = reinterpret_cast<float*>(smem);
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < MPAD; ++j) P[j * 128 + n_local] = acc[j];
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  smallm_reduce_store<BF16>(p, smem, split, nsplit, n_tile);
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p, const Fp8Scales sc) {
+  gemm_fp8_device<MPAD, BF16>(tmW, tmX, p, sc);
+}
+
+// Grouped (mixture-of-experts) variant over the expert-sorted activation buffer: blockIdx.z = expert * chunks + chunk.
+struct Fp8GroupInfo {
+  const int* counts; const int* offsets;
+  int rows_per_chunk, chunks, n_rows_w;
+};
+
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+moe_grouped_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
+                       const Fp8Scales sbase, const Fp8GroupInfo gi) {
+  const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  pdl_launch_dependents();
+  pdl_wait();                         // counts / offsets come from the plan kernel
+  const int cnt = gi.counts[e];
+  const int row0 = chunk * gi.rows_per_chunk;
+  if (row0 >= cnt) return;            // uniform over the cluster (same blockIdx.z)
+  GemmParams p = base;
+  const int seg = gi.offsets[e] + row0;
+  p.M = cnt - row0 < gi.rows_per_chunk ? cnt - row0 : gi.rows_per_chunk;
+  p.x_row0 = seg;
+  p.w_row0 = e * gi.n_rows_w;         // stacked weights: the weight-scale tile index (w_row0 / 128 + n_tile) follows from it
+  p.out = reinterpret_cast<uint16_t*>(base.out) + (size_t)seg * base.ld_out;
+  gemm_fp8_device<MPAD, BF16>(tmW, tmX, p, sbase);
+}
+
+// ---- activation quantisation: x [M, K] 16-bit -> xq [M, K] e4m3 + scales [K / 128, ld_a] ------------------------------------
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint16_t lo, hi;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(lo) : "f"(b), "f"(a));     // first source -> upper byte
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(hi) : "f"(d), "f"(c));
+  return (uint32_t)lo | ((uint32_t)hi << 16);
+}
+
+template <bool BF16>
+__global__ void quant_act_fp8_kernel(const uint16_t* __restrict__ x, int ldx, uint8_t* __restrict__ xq, int ldq, float* __restrict__ scales,
+                                     int ld_a, int M, int kb_total, const int* __restrict__ rows_used) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int m = gw / kb_total, kb = gw - m * kb_total;
+  if (m >= M) return;
+  if (rows_used != nullptr && m >= *rows_used) return;         // expert-sorted buffers: rows behind the last routed token
+  const uint2 v = *reinterpret_cast<const uint2*>(x + (size_t)m * ldx + kb * 128 + lane * 4);
+  const float2 a = unpack_16<BF16>(v.x), b = unpack_16<BF16>(v.y);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = fmaxf(amax, 1e-12f) / 448.0f;
+  const float inv = 1.0f / scale;
+  *reinterpret_cast<uint32_t*>(xq + (size_t)m * ldq + kb * 128 + lane * 4) = pack_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+  if (lane == 0) scales[(size_t)kb * ld_a + m] = scale;
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+extern "C" int fb_gemm_pick_split(int M, int N, int K, int slots);
+
+extern "C" int fb_quant_act_fp8(const void* x, int ldx, void* xq, int ldq, float* scales, int ld_a, int M, int K, int dtype,
+                                const int* rows_used, void* stream) {
+  if (M <= 0) return 0;
+  if (K % 128 != 0 || ldx % 4 != 0 || ldq % 4 != 0) return -1;
+  const int kb_total = K / 128, wpb = 8;
+  const int warps = M * kb_total;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1)
+    launch_k(quant_act_fp8_kernel<true>, dim3((warps + wpb - 1) / wpb), dim3(wpb * 32), 0, s, 0, (const uint16_t*)x, ldx, (uint8_t*)xq, ldq, scales, ld_a, M, kb_total, rows_used);
+  else
+    launch_k(quant_act_fp8_kernel<false>, dim3((warps + wpb - 1) / wpb), dim3(wpb * 32), 0, s, 0, (const uint16_t*)x, ldx, (uint8_t*)xq, ldq, scales, ld_a, M, kb_total, rows_used);
+  return (int)cudaGetLastError();
+}
+
+template <int MPAD, bool BF16>
+static cudaError_t launch_fp8(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const Fp8Scales& sc, int nsplit,
+                              int n_tiles, cudaStream_t stream) {
+  using Cfg = Fp8Cfg<MPAD>;
+  auto kern = gemm_fp8_kernel<MPAD, BF16>;
+  static DeviceOnce configured;
+  if (configured.need()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, sc);
+}
+
+// xq: [M, K] e4m3 (row stride ldq bytes), a_scale: [K / 128, ld_a]; Wq: [N, K] e4m3, w_scale: [ceil(N / 128), K / 128].
+// out / bias / residual are 16-bit (dtype 0 = fp16, 1 = bf16) unless GEMM_OUT_F32.  M <= 128.
+extern "C" int fb_gemm_fp8(const void* xq, int ldq, const float* a_scale, int ld_a, const void* Wq, const float* w_scale, void* out,
+                           const void* bias, const void* residual, int M, int N, int K, int ld_out, int ld_res, int dtype, int flags,
+                           int nsplit, void* stream_) {
+  if (M <= 0) return 0;
+  if (M > 128 || K % 128 != 0 || N % 8 != 0) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int mpad = 16;
+  while (mpad < M) mpad <<= 1;
+  const int n_tiles = (N + 127) / 128;
+  const int kb_total = K / 128;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  if (nsplit <= 0) {
+    nsplit = 1;
+    const int slots = sm_count * (mpad <= 64 ? 2 : 1);
+    while (nsplit < 8 && n_tiles * nsplit * 2 <= slots && kb_total / (nsplit * 2) >= 4) nsplit <<= 1;
+  }
+  if ((flags & GEMM_SWIGLU) && nsplit > 8) nsplit = 8;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, Wq, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128, 128, 1, 3)) return -2;
+  if (!make_tmap_2d(&tmX, xq, (uint64_t)M, (uint64_t)K, (uint64_t)ldq, mpad, 128, 1, 3)) return -2;
+  GemmParams p = {};
+  p.out = out; p.bias = bias; p.residual = residual; p.M = M; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res;
+  p.kb_total = kb_total; p.kb_per_split = (kb_total + nsplit - 1) / nsplit; p.flags = flags;
+  p.idesc = make_idesc(0, 0, 0, 0, 128, mpad);
+  Fp8Scales sc;
+  sc.w_scale = w_scale; sc.a_scale = a_scale; sc.ld_a = ld_a;
+  cudaError_t e;
+#define FB_F8(MP)                                                                                        \
+  e = dtype == 1 ? launch_fp8<MP, true>(tmW, tmX, p, sc, nsplit, n_tiles, stream)                        \
+                 : launch_fp8<MP, false>(tmW, tmX, p, sc, nsplit, n_tiles, stream);                      \
+  break;
+  switch (mpad) {
+    case 16: FB_F8(16)
+    case 32: FB_F8(32)
+    case 64: FB_F8(64)
+    default: FB_F8(128)
+  }
+#undef FB_F8
+  return (int)e;
+}
+
+template <int MPAD, bool BF16>
+static cudaError_t launch_grouped_fp8(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const Fp8Scales& sc,
+                                      const Fp8GroupInfo& gi, int nsplit, int n_tiles, int nz, cudaStream_t stream) {
+  using Cfg = Fp8Cfg<MPAD>;
+  auto kern = moe_grouped_fp8_kernel<MPAD, BF16>;
+  static DeviceOnce configured;
+  if (configured.need()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, nz);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, sc, gi);
+}
+
+// Grouped expert GEMM over the expert-sorted, FP8-quantised activation buffer xq [rows_cap, K]; stacked weights
+// Wq [E_local * N, K] with scales [E_local, ceil(N / 128), K / 128].  max_rows: low 16 bits = most rows an expert can hold,
+// high 16 bits = rows per chunk hint (0: derived).
+extern "C" int fb_moe_grouped_gemm_fp8(const void* xq, int ldq, const float* a_scale, int ld_a, const void* Wq, const float* w_scale,
+                                       void* out, const int* counts, const int* offsets, int n_local, int N, int K, int rows_cap,
+                                       int ld_out, int dtype, int flags, int max_rows, void* stream_) {
+  if (n_local <= 0 || rows_cap <= 0) return 0;
+  if (K % 128 != 0 || N % 128 != 0) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const int hint = (max_rows >> 16) & 0xFFFF;
+  max_rows &= 0xFFFF;
+  if (max_rows <= 0) max_rows = rows_cap;
+  int mpad = 16;
+  const int want = hint > 0 ? hint : max_rows;
+  while (mpad < want && mpad < 64) mpad <<= 1;
+  const int chunks = (max_rows + mpad - 1) / mpad;
+  const int n_tiles = N / 128, kb_total = K / 128;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, Wq, (uint64_t)n_local * N, (uint64_t)K, (uint64_t)K, 128, 128, 1, 3)) return -2;
+  if (!make_tmap_2d(&tmX, xq, (uint64_t)rows_cap, (uint64_t)K, (uint64_t)ldq, mpad, 128, 1, 3)) return -2;
+  GemmParams p = {};
+  p.out = out; p.M = mpad; p.N = N; p.K = K; p.ld_out = ld_out; p.flags = flags;
+  p.kb_total = kb_total; p.kb_per_split = kb_total;
+  p.idesc = make_idesc(0, 0, 0, 0, 128, mpad);
+  Fp8Scales sc;
+  sc.w_scale = w_scale; sc.a_scale = a_scale; sc.ld_a = ld_a;
+  Fp8GroupInfo gi;
+  gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
+  cudaError_t e;
+#define FB_G8(MP)                                                                                                         \
+  e = dtype == 1 ? launch_grouped_fp8<MP, true>(tmW, tmX, p, sc, gi, 1, n_tiles, n_local * chunks, stream)                \
+                 : launch_grouped_fp8<MP, false>(tmW, tmX, p, sc, gi, 1, n_tiles, n_local * chunks, stream);              \
+  break;
+  switch (mpad) {
+    case 16: FB_G8(16)
+    case 32: FB_G8(32)
+    default: FB_G8(64)
+  }
+#undef FB_G8
+  return (int)e;
+}

@@ -13,6 +13,7 @@ import ctypes
 import torch
 
 from . import _lib
+from . import quant_gemm as QG
 from .basic import GEMM_SWIGLU, _ptr, _stream, dtype_code
 
 P, I = ctypes.c_void_p, ctypes.c_int
@@ -118,6 +119,16 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
                                            2 * st.inter, H, st.inter, max_rows, dt, GEMM_SWIGLU, s), "fb_moe_grouped_gemm(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm(_ptr(act), _ptr(st.down), _ptr(ys), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
                                            H, st.inter, H, max_rows, dt, 0, s), "fb_moe_grouped_gemm(down)")
+    elif st.kind == "fp8" and QG.FP8_NATIVE and H % 128 == 0 and st.inter % 128 == 0:
+        # W8A8: quantise the gathered rows (only those in use), e4m3 x e4m3 grouped GEMMs, quantise the SwiGLU output again
+        xq, sa, ld_a = QG.quant_act_fp8(xs, total)
+        _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(xq), H, _ptr(sa), ld_a, _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(act), _ptr(counts),
+                                               _ptr(offsets), E, 2 * st.inter, H, rows_cap, st.inter, dt, GEMM_SWIGLU, max_rows, s),
+                   "fb_moe_grouped_gemm_fp8(gate_up)")
+        aq, sb, ld_b = QG.quant_act_fp8(act, total)
+        _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(aq), st.inter, _ptr(sb), ld_b, _ptr(st.down), _ptr(st.dn_scale), _ptr(ys), _ptr(counts),
+                                               _ptr(offsets), E, H, st.inter, rows_cap, H, dt, 0, max_rows, s),
+                   "fb_moe_grouped_gemm_fp8(down)")
     else:
         qm = {"int8": 1, "int4g": 2, "fp8": 3}[st.kind]
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(xs), _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(st.gu_zero), _ptr(act), _ptr(counts),

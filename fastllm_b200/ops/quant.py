@@ -76,6 +76,18 @@ def dequantize_fp8_block(q, scale, dtype, block: int = 128):
     return (q.float() * s).to(dtype)
 
 
+def fake_quant_act_fp8(x: torch.Tensor) -> torch.Tensor:
+    """Round activations to e4m3 per (token, 128-wide k block) and return them in their own dtype.  FP8 layers use the
+    tensor core's e4m3 x e4m3 path for decode-sized batches; larger batches go through 16-bit GEMMs and apply this rounding
+    first, so a request sees the same activation numerics whatever batch it is scheduled in."""
+    K = x.shape[-1]
+    if K % 128 != 0:
+        return x
+    xb = x.float().reshape(-1, K // 128, 128)
+    sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / FP8_MAX
+    return ((xb / sc).to(torch.float8_e4m3fn).float() * sc).reshape(x.shape).to(x.dtype)
+
+
 def normalize_wdtype(name: str | None) -> tuple[str, int]:
     """Map CLI dtype names (``--dtype`` / ``--moe_dtype``) to (kind, group)."""
     if name is None:
@@ -158,4 +170,6 @@ class LinearWeight:
             y = quant_gemm.linear_quant(x, self, residual, swiglu, out_f32)
             if y is not None:
                 return y
+            if self.kind == "fp8" and quant_gemm.FP8_NATIVE:
+                x = fake_quant_act_fp8(x)
         return B.linear(x, self.dequant(x.dtype), self.bias, residual, swiglu, self.interleaved, out_f32)

@@ -16,7 +16,37 @@ from .basic import GEMM_BIAS, GEMM_OUT_F32, GEMM_RESIDUAL, GEMM_SWIGLU, _ptr, _s
 P, I, F = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
 _lib.register_sigs({"fb_gemm_quant": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P]}, ["gemm_quant"])
 
+_lib.register_sigs({
+    "fb_quant_act_fp8": [P, I, P, I, P, I, I, I, I, P, P],
+    "fb_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
+    "fb_moe_grouped_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
+}, ["gemm_fp8"])
+
 _QMODE = {"int8": 1, "int4g": 2, "fp8": 3}
+# FP8 weights run as W8A8 (activations quantised per token and 128-wide k block, e4m3 x e4m3 on the tensor core) for decode-sized
+# batches; FB_FP8_W8A16=1 keeps 16-bit activations (weights de-quantised in shared memory), which is also the path for M > 128.
+FP8_NATIVE = __import__("os").environ.get("FB_FP8_W8A16", "0") != "1"
+
+
+def quant_act_fp8(x2: torch.Tensor, rows_used: torch.Tensor | None = None):
+    """x ``[M, K]`` 16-bit -> (e4m3 ``[M, K]``, scales fp32 ``[K / 128, ld_a]`` with ``ld_a >= M + 128``, multiple of 4)."""
+    M, K = x2.shape
+    ld_a = (M + 128 + 3) // 4 * 4
+    xq = torch.empty((M, K), device=x2.device, dtype=torch.uint8)
+    sa = torch.empty((K // 128, ld_a), device=x2.device, dtype=torch.float32)
+    rc = _lib.kernels().fb_quant_act_fp8(_ptr(x2), x2.stride(0), _ptr(xq), K, _ptr(sa), ld_a, M, K, dtype_code(x2.dtype), _ptr(rows_used),
+                                         _stream())
+    _lib.check(rc, "fb_quant_act_fp8")
+    return xq, sa, ld_a
+
+
+def _linear_fp8_native(x2, lw, out, bias, res2, flags):
+    M, K = x2.shape
+    xq, sa, ld_a = quant_act_fp8(x2)
+    rc = _lib.kernels().fb_gemm_fp8(_ptr(xq), K, _ptr(sa), ld_a, _ptr(lw.w), _ptr(_kernel_tensors(lw)[0]), _ptr(out), _ptr(bias), _ptr(res2),
+                                    M, lw.n, K, out.stride(0), res2.stride(0) if res2 is not None else 0, dtype_code(x2.dtype), flags, 0,
+                                    _stream())
+    _lib.check(rc, "fb_gemm_fp8")
 MAX_CHUNKED_TOKENS = 1024
 
 
@@ -59,6 +89,13 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
     bias = lw.bias
     if bias is not None and bias.dtype != x.dtype:
         bias = bias.to(x.dtype)
+    if lw.kind == "fp8" and FP8_NATIVE and M <= 128 and x2.stride(0) % 4 == 0:
+        _linear_fp8_native(x2, lw, out, bias, res2, flags)
+        return out.reshape(*lead, n_out)
+    if lw.kind == "fp8" and FP8_NATIVE:
+        from .quant import fake_quant_act_fp8
+
+        x2 = fake_quant_act_fp8(x2)          # same activation rounding as the e4m3 x e4m3 path used for small batches
     lib = _lib.kernels()
     for m0 in range(0, M, 256):
         m1 = min(M, m0 + 256)

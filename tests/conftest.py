@@ -23,3 +23,14 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture
+def fp8_w8a16():
+    """Run FP8-weight layers with 16-bit activations (the in-shared-memory dequant kernels) for the duration of a test."""
+    from fastllm_b200.ops import quant_gemm as QG
+
+    old = QG.FP8_NATIVE
+    QG.FP8_NATIVE = False
+    yield
+    QG.FP8_NATIVE = old

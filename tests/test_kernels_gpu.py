@@ -204,7 +204,7 @@ def test_qkv_post(mode, rot, qknorm):
 @pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K", [(1, 256, 256), (13, 384, 1024), (64, 4096, 4096), (200, 1024, 2048), (300, 512, 512)])
-def test_gemm_quant(kind, dtype, M, N, K):
+def test_gemm_quant(kind, dtype, M, N, K, fp8_w8a16):
     from fastllm_b200.ops import quant
 
     torch.manual_seed(8)
@@ -217,7 +217,7 @@ def test_gemm_quant(kind, dtype, M, N, K):
     _close(y, ref, 4e-2, 3e-2, f"quant gemm {kind} {M}x{N}x{K}")
 
 
-def test_gemm_quant_epilogues():
+def test_gemm_quant_epilogues(fp8_w8a16):
     from fastllm_b200.ops import quant
 
     torch.manual_seed(9)
@@ -260,7 +260,7 @@ def test_moe_grouped(T, E, first, n_local, topk):
 
 
 @pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8"])
-def test_moe_grouped_quant(kind):
+def test_moe_grouped_quant(kind, fp8_w8a16):
     from fastllm_b200.ops import moe as MOE, moe_grouped, quant
 
     torch.manual_seed(11)
@@ -397,3 +397,85 @@ def test_mla_decode(H):
     _close(out.float().cpu(), ref, 3e-2, 3e-2, f"mla_decode H={H}")
     out2 = A.mla_decode(q.to(DEV), lat.to(DEV), pt.to(DEV), seq.to(DEV), scale)      # workspace reuse
     assert torch.equal(out, out2)
+
+
+def _fp8_ref(x, lw):
+    """What the W8A8 kernel computes: activations rounded to e4m3 per (token, 128-wide k block), weights as stored."""
+    from fastllm_b200.ops import quant as Q
+
+    M, K = x.shape
+    xb = x.float().reshape(M, K // 128, 128)
+    sc = (xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / 448.0)
+    xq = (xb / sc).to(torch.float8_e4m3fn).float() * sc
+    w = Q.dequantize_fp8_block(lw.w, lw.scale, torch.float32, 128)
+    return xq.reshape(M, K) @ w.t()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (16, 384, 1024), (64, 4096, 4096), (100, 1024, 14336), (128, 512, 2048)])
+def test_gemm_fp8_native(M, N, K):
+    from fastllm_b200.ops import quant as Q
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(M + N)
+    dt = torch.bfloat16
+    w = (torch.randn(N, K, device=DEV) * 0.03).to(dt)
+    lw = Q.LinearWeight.from_dense(w, "fp8")
+    x = torch.randn(M, K, device=DEV).to(dt)
+    assert QG.FP8_NATIVE
+    out = lw(x)
+    ref = _fp8_ref(x, lw)
+    _lib.check_device_errors()
+    _close(out.float().cpu(), ref.cpu(), 2e-2, 1e-2, f"gemm_fp8 {M}x{N}x{K}")
+    # and it stays close to the un-quantised product
+    exact = x.float() @ w.float().t()
+    rel = (out.float() - exact).norm() / exact.norm()
+    assert rel < 0.06, rel
+
+
+def test_gemm_fp8_native_epilogues():
+    from fastllm_b200.ops import quant as Q
+
+    torch.manual_seed(9)
+    dt = torch.bfloat16
+    M, K, I = 48, 1024, 512
+    g, u = (torch.randn(I, K, device=DEV) * 0.03).to(dt), (torch.randn(I, K, device=DEV) * 0.03).to(dt)
+    lw = Q.LinearWeight.from_dense(B.interleave_gate_up(g, u), "fp8", interleaved=True)
+    x = torch.randn(M, K, device=DEV).to(dt)
+    out = lw(x, swiglu=True)
+    full = _fp8_ref(x, lw)                                  # interleaved columns
+    t = full.reshape(M, (2 * I) // 128, 2, 64)
+    ref = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(M, I)
+    _close(out.float().cpu(), ref.cpu(), 3e-2, 2e-2, "gemm_fp8 swiglu")
+    wd = (torch.randn(K, I, device=DEV) * 0.03).to(dt)
+    ld = Q.LinearWeight.from_dense(wd, "fp8", bias=torch.randn(K, device=DEV).to(dt))
+    res = torch.randn(M, K, device=DEV).to(dt)
+    a = torch.randn(M, I, device=DEV).to(dt)
+    out2 = ld(a, residual=res)
+    ref2 = _fp8_ref(a, ld) + ld.bias.float() + res.float()
+    _close(out2.float().cpu(), ref2.cpu(), 3e-2, 2e-2, "gemm_fp8 bias+residual")
+    _lib.check_device_errors()
+
+
+def test_moe_grouped_fp8_native_matches_w8a16():
+    """Grouped expert GEMMs with FP8 activations vs the 16-bit-activation path on the same FP8 expert weights."""
+    from fastllm_b200.models.config import preset
+    from fastllm_b200.models.decoder import random_init
+    from fastllm_b200.ops import moe as MOE
+    from fastllm_b200.ops import quant_gemm as QG
+
+    cfg = preset("tiny-qwen3-moe")
+    m = random_init(cfg, "cuda", torch.bfloat16, std=0.05, moe_wdtype="fp8")
+    ex = m.layers[0].mlp.experts
+    assert ex.stacked is not None and ex.stacked.kind == "fp8"
+    torch.manual_seed(3)
+    x = torch.randn(37, cfg.hidden_size, device=DEV).bfloat16()
+    idx, w = MOE.route_topk(torch.randn(37, cfg.num_experts, device=DEV), None, 2, 0, True)
+    y8 = MOE.moe_forward(x, idx, w, ex)
+    QG.FP8_NATIVE = False
+    try:
+        y16 = MOE.moe_forward(x, idx, w, ex)
+    finally:
+        QG.FP8_NATIVE = True
+    _lib.check_device_errors()
+    rel = (y8.float() - y16.float()).norm() / y16.float().norm()
+    assert rel < 0.08, rel
