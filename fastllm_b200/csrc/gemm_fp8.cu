@@ -225,11 +225,48 @@ __global__ void quant_act_fp8_kernel(const uint16_t* __restrict__ x, int ldx, ui
   if (lane == 0) scales[(size_t)kb * ld_a + m] = scale;
 }
 
+// Gather for the grouped expert GEMM fused with the activation quantisation: row pos[pair] of the expert-sorted FP8 buffer
+// receives token pair / topk, quantised per 128-wide k block.  One CTA per (token, k) pair, one warp per k block.
+template <bool BF16>
+__global__ void moe_gather_quant_fp8_kernel(const uint16_t* __restrict__ x, const int* __restrict__ pos, uint8_t* __restrict__ xq,
+                                            float* __restrict__ scales, int ld_a, int topk, int H) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int pair = blockIdx.x;
+  const int r = pos[pair];
+  if (r < 0) return;
+  const int t = pair / topk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int kb = warp; kb < (H >> 7); kb += nw) {
+    const uint2 v = *reinterpret_cast<const uint2*>(x + (size_t)t * H + kb * 128 + lane * 4);
+    const float2 a = unpack_16<BF16>(v.x), b = unpack_16<BF16>(v.y);
+    float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float scale = fmaxf(amax, 1e-12f) / 448.0f;
+    const float inv = 1.0f / scale;
+    *reinterpret_cast<uint32_t*>(xq + (size_t)r * H + kb * 128 + lane * 4) = pack_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+    if (lane == 0) scales[(size_t)kb * ld_a + r] = scale;
+  }
+}
+
 }  // namespace fb
 
 using namespace fb;
 
 extern "C" int fb_gemm_pick_split(int M, int N, int K, int slots);
+
+extern "C" int fb_moe_gather_quant_fp8(const void* x, const int* pos, void* xq, float* scales, int ld_a, int T, int topk, int H, int dtype,
+                                       void* stream) {
+  if (T <= 0) return 0;
+  if (H % 128 != 0) return -1;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1)
+    launch_k(moe_gather_quant_fp8_kernel<true>, dim3(T * topk), dim3(128), 0, s, 0, (const uint16_t*)x, pos, (uint8_t*)xq, scales, ld_a, topk, H);
+  else
+    launch_k(moe_gather_quant_fp8_kernel<false>, dim3(T * topk), dim3(128), 0, s, 0, (const uint16_t*)x, pos, (uint8_t*)xq, scales, ld_a, topk, H);
+  return (int)cudaGetLastError();
+}
 
 extern "C" int fb_quant_act_fp8(const void* x, int ldx, void* xq, int ldq, float* scales, int ld_a, int M, int K, int dtype,
                                 const int* rows_used, void* stream) {

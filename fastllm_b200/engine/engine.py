@@ -324,10 +324,16 @@ class LLMEngine:
         else:
             sampling.apply_repeat_penalty(lg, recent, [r.gen.repeat_penalty for r in reqs])
             toks = sampling.sample(lg, tk, [r.gen.top_p for r in reqs], [r.gen.temperature for r in reqs])
+        out = toks.tolist()
         for r, row in zip(reqs, range(len(reqs))):
             if r.gen.output_logits:
                 r.last_logits = logits[row].float().cpu()
-        return toks.tolist()
+            if r.gen.logprobs:
+                # log-probabilities of the model distribution (before penalties and truncation), as the OpenAI API defines them
+                lp = torch.log_softmax(logits[row].float(), dim=-1)
+                tv, ti = lp.topk(min(int(r.gen.logprobs), lp.numel()))
+                r.logprob_entries.append((float(lp[out[row]]), list(zip(ti.tolist(), tv.tolist()))))
+        return out
 
     def _emit(self, r: Request, tok: int) -> int:
         r.output_ids.append(tok)

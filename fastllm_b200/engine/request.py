@@ -87,6 +87,7 @@ class Request:
         self.finish_reason: str | None = None
         self.stats = RequestStats(arrival=time.time(), prompt_tokens=len(self.prompt_ids))
         self.last_logits = None
+        self.logprob_entries: list = []   # per output token: (token logprob, [(token id, logprob), ...]) when gen.logprobs > 0
         self.recompute_tokens: list[int] | None = None   # set when evicted: prompt + outputs to prefill again
 
     @property

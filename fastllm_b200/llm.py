@@ -206,7 +206,8 @@ class model:
         return GenerationConfig(max_new_tokens=max_length, min_new_tokens=min_length, do_sample=sample, top_k=top_k if sample else 1,
                                 top_p=d["top_p"] if top_p is None else top_p, temperature=temperature,
                                 repeat_penalty=d["repetition_penalty"] if repeat_penalty is None else repeat_penalty,
-                                stop_token_ids=list(stop_token_ids or []), output_logits=bool(kw.get("output_logits", False)))
+                                stop_token_ids=list(stop_token_ids or []), output_logits=bool(kw.get("output_logits", False)),
+                                logprobs=int(kw.get("logprobs", 0) or 0))
 
     # ---- handle-level API ---------------------------------------------------------------------------
     def launch_stream_response(self, query, history=None, **gen_kwargs) -> int:

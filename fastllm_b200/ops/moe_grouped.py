@@ -109,19 +109,27 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
     wts = wts.float().contiguous()
     s = _stream()
     _lib.check(lib.fb_moe_plan(_ptr(idx), T, topk, experts.first, E, _ptr(counts), _ptr(offsets), _ptr(pos), _ptr(total), PAD, s), "fb_moe_plan")
-    xs = torch.empty((rows_cap, H), device=dev, dtype=x.dtype)
-    _lib.check(lib.fb_moe_gather(_ptr(x.contiguous()), _ptr(pos), _ptr(xs), T, topk, H, s), "fb_moe_gather")
+    dt = dtype_code(x.dtype)
+    fp8_native = st.kind == "fp8" and QG.FP8_NATIVE and H % 128 == 0 and st.inter % 128 == 0
     act = torch.empty((rows_cap, st.inter), device=dev, dtype=x.dtype)
     ys = torch.empty((rows_cap, H), device=dev, dtype=x.dtype)
-    dt = dtype_code(x.dtype)
+    if fp8_native:
+        # gather fused with the e4m3 quantisation of the rows (the 16-bit sorted copy is never materialised)
+        ld_a = (rows_cap + 128 + 3) // 4 * 4
+        xq = torch.empty((rows_cap, H), device=dev, dtype=torch.uint8)
+        sa = torch.empty((H // 128, ld_a), device=dev, dtype=torch.float32)
+        _lib.check(lib.fb_moe_gather_quant_fp8(_ptr(x.contiguous()), _ptr(pos), _ptr(xq), _ptr(sa), ld_a, T, topk, H, dt, s),
+                   "fb_moe_gather_quant_fp8")
+    else:
+        xs = torch.empty((rows_cap, H), device=dev, dtype=x.dtype)
+        _lib.check(lib.fb_moe_gather(_ptr(x.contiguous()), _ptr(pos), _ptr(xs), T, topk, H, s), "fb_moe_gather")
     if st.kind == "dense":
         _lib.check(lib.fb_moe_grouped_gemm(_ptr(xs), _ptr(st.gate_up), _ptr(act), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
                                            2 * st.inter, H, st.inter, max_rows, dt, GEMM_SWIGLU, s), "fb_moe_grouped_gemm(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm(_ptr(act), _ptr(st.down), _ptr(ys), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
                                            H, st.inter, H, max_rows, dt, 0, s), "fb_moe_grouped_gemm(down)")
-    elif st.kind == "fp8" and QG.FP8_NATIVE and H % 128 == 0 and st.inter % 128 == 0:
-        # W8A8: quantise the gathered rows (only those in use), e4m3 x e4m3 grouped GEMMs, quantise the SwiGLU output again
-        xq, sa, ld_a = QG.quant_act_fp8(xs, total)
+    elif fp8_native:
+        # W8A8: e4m3 x e4m3 grouped GEMMs; the SwiGLU output is quantised again for the down projection
         _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(xq), H, _ptr(sa), ld_a, _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(act), _ptr(counts),
                                                _ptr(offsets), E, 2 * st.inter, H, rows_cap, st.inter, dt, GEMM_SWIGLU, max_rows, s),
                    "fb_moe_grouped_gemm_fp8(gate_up)")

@@ -20,6 +20,7 @@ _lib.register_sigs({
     "fb_quant_act_fp8": [P, I, P, I, P, I, I, I, I, P, P],
     "fb_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "fb_moe_grouped_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
+    "fb_moe_gather_quant_fp8": [P, P, P, P, I, I, I, I, I, P],
 }, ["gemm_fp8"])
 
 _QMODE = {"int8": 1, "int4g": 2, "fp8": 3}

@@ -69,11 +69,26 @@ class Completion:
         if top_k is None and do_sample and (temperature is not None or req.get("top_p") is not None):
             top_k = 50
         mx = req.get("max_completion_tokens") or req.get("max_tokens") or req.get("max_output_tokens") or 4096
+        lp = 0
+        if req.get("logprobs"):                 # chat API: logprobs=true (+ top_logprobs=n); completions API: logprobs=n
+            lp = int(req.get("top_logprobs") or (req["logprobs"] if isinstance(req["logprobs"], int) and not isinstance(req["logprobs"], bool) else 1))
         return dict(max_length=int(mx), do_sample=do_sample, top_p=req.get("top_p"), top_k=top_k, temperature=temperature,
                     repeat_penalty=req.get("repetition_penalty") or req.get("frequency_penalty_as_repeat"),
-                    stop_token_ids=req.get("stop_token_ids"))
+                    stop_token_ids=req.get("stop_token_ids"), logprobs=max(0, min(lp, 20)))
 
-    async def generate(self, ids, gen_kwargs, stop=None, is_disconnected=None, rid=None):
+    def logprobs_content(self, r) -> list | None:
+        """OpenAI ``choices[].logprobs.content`` entries of a finished request (None when logprobs were not requested)."""
+        if r is None or not r.gen.logprobs:
+            return None
+        tok = self.model.tokenizer
+        out = []
+        for tid, (lp, top) in zip(r.output_ids, r.logprob_entries):
+            piece = tok.decode([tid], skip_special_tokens=False)
+            out.append({"token": piece, "logprob": lp, "bytes": list(piece.encode("utf-8")),
+                        "top_logprobs": [{"token": tok.decode([i], skip_special_tokens=False), "logprob": v} for i, v in top]})
+        return out
+
+    async def generate(self, ids, gen_kwargs, stop=None, is_disconnected=None, rid=None, info: dict | None = None):
         """Async generator of (piece, finish_reason or None).  Aborts the engine request when the client goes away."""
         loop = asyncio.get_running_loop()
         m = self.model
@@ -81,6 +96,8 @@ class Completion:
         rid = rid or uuid.uuid4().hex
         self.active.add(rid, handle, len(ids))
         req = m.engine.requests.get(handle)
+        if info is not None:
+            info["request"] = req
         sd = StreamDecoder(m.tokenizer)
         stops = [stop] if isinstance(stop, str) else list(stop or [])
         text = ""
@@ -133,7 +150,8 @@ class Completion:
         gk = self.gen_kwargs(req)
         if not req.get("stream"):
             text, finish = "", "stop"
-            async for piece, fin in self.generate(ids, gk, req.get("stop"), is_disconnected, cid):
+            info: dict = {}
+            async for piece, fin in self.generate(ids, gk, req.get("stop"), is_disconnected, cid, info):
                 text += piece
                 finish = fin or finish
             reasoning, content = split_reasoning(text) if self.think else (None, text)
@@ -146,8 +164,12 @@ class Completion:
             if calls:
                 msg["tool_calls"] = calls
                 finish = "tool_calls"
+            choice = {"index": 0, "message": msg, "finish_reason": finish}
+            lpc = self.logprobs_content(info.get("request")) if gk.get("logprobs") else None
+            if lpc is not None:
+                choice["logprobs"] = {"content": lpc}
             return {"id": cid, "object": "chat.completion", "created": created, "model": req.get("model") or self.model_name,
-                    "choices": [{"index": 0, "message": msg, "finish_reason": finish}], "usage": self.last_usage}
+                    "choices": [choice], "usage": self.last_usage}
 
         async def sse():
             def chunk(delta, finish=None, usage=None):

@@ -100,3 +100,15 @@ def test_responses_and_anthropic(client):
     r = client("POST", "/v1/messages", {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 4, "temperature": 0})
     assert r.json()["type"] == "message" and r.json()["stop_reason"] in ("end_turn", "max_tokens")
     assert client("POST", "/v1/messages", {"messages": []}).status_code == 400
+
+
+def test_chat_completion_logprobs(client):
+    r = client("POST", "/v1/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "temperature": 0,
+                                                "logprobs": True, "top_logprobs": 3})
+    j = r.json()
+    content = j["choices"][0]["logprobs"]["content"]
+    assert 1 <= len(content) <= 4
+    for e in content:
+        assert e["logprob"] <= 0 and len(e["top_logprobs"]) == 3
+        # greedy decoding: the chosen token is the most likely one
+        assert abs(e["logprob"] - e["top_logprobs"][0]["logprob"]) < 1e-5
