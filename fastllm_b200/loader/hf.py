@@ -47,6 +47,8 @@ def dequant_awq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
 # name canonicalisation: every family is mapped onto the Llama naming that loader.shard understands
 # ---------------------------------------------------------------------------------------------------
 _RENAMES = [
+    (r"\.mlp\.moe_statics\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),          # Ernie-4.5-MoE
+    (r"\.mlp\.gate\.wg\.", ".mlp.gate."), (r"\.mlp\.shared_mlp\.", ".mlp.shared_experts."),         # Hunyuan-MoE
     # ChatGLM2/3 and original GLM-4 checkpoints
     (r"^transformer\.embedding\.word_embeddings\.", "model.embed_tokens."), (r"^transformer\.encoder\.layers\.", "model.layers."),
     (r"^transformer\.encoder\.final_layernorm\.", "model.norm."), (r"^transformer\.output_layer\.", "lm_head."),

@@ -182,7 +182,7 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
     elif cfg.layer_is_moe(i):
         f.router = g("mlp.gate.weight").to(m.device, torch.float32).contiguous()
         rb = g("mlp.gate.e_score_correction_bias")
-        f.router_bias = rb.to(m.device, torch.float32).contiguous() if rb is not None else None
+        f.router_bias = rb.reshape(-1).to(m.device, torch.float32).contiguous() if rb is not None else None
         lo, hi = MOE.local_expert_range(cfg.num_experts, m.ep)
         moe_tp = (m.ep is None or m.ep.size == 1) and n > 1      # no EP: shard every expert's intermediate dim
         gu, dn = [], []

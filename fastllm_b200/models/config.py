@@ -198,6 +198,16 @@ def from_hf_dict(d: dict) -> ModelConfig:
             c.num_shared_experts = 1
             c.shared_expert_intermediate_size = sis
             c.shared_expert_gate = True
+    elif mt == "hunyuan_v1_moe":
+        c.num_experts = g("num_experts", 0)
+        tk = g("moe_topk", 1)
+        c.num_experts_per_tok = tk[0] if isinstance(tk, list) else tk
+        c.moe_intermediate_size = c.intermediate_size          # experts use the full intermediate size
+        c.norm_topk_prob = True
+        ns = g("num_shared_expert", 0)
+        ns = ns[0] if isinstance(ns, list) else ns
+        c.num_shared_experts = int(ns or 0)
+        c.shared_expert_intermediate_size = c.intermediate_size * c.num_shared_experts
     elif mt == "mixtral":
         c.num_experts = g("num_local_experts", 8)
         c.num_experts_per_tok = g("num_experts_per_tok", 2)
@@ -210,13 +220,13 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.norm_topk_prob = bool(g("norm_topk_prob", True))
         c.num_shared_experts = g("n_shared_experts", g("moe_num_shared_experts", 0)) or 0
         c.shared_expert_intermediate_size = c.moe_intermediate_size * c.num_shared_experts
-        c.first_k_dense = g("first_k_dense_replace", 0) or 0
+        c.first_k_dense = g("first_k_dense_replace", g("moe_layer_start_index", 0)) or 0
         c.moe_layer_freq = g("moe_layer_freq", 1) or 1
         c.scoring_func = g("scoring_func", "sigmoid" if mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe") else "softmax")
         c.n_group = g("n_group", 1) or 1
         c.topk_group = g("topk_group", 1) or 1
         c.routed_scaling_factor = float(g("routed_scaling_factor", 1.0))
-        c.router_bias = g("topk_method", "") == "noaux_tc" or mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe")
+        c.router_bias = g("topk_method", "") == "noaux_tc" or mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe", "ernie4_5_moe")
         if mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32"):
             c.use_mla = True
             c.q_lora_rank = g("q_lora_rank") or 0

@@ -37,6 +37,9 @@ FAMILIES = {
     "glm4_moe": dict(model_type="glm4_moe", **_C, moe_intermediate_size=128, n_routed_experts=8, num_experts_per_tok=2,
                      n_shared_experts=1, first_k_dense_replace=1, n_group=1, topk_group=1, partial_rotary_factor=0.5, use_qk_norm=True),
     "ernie4_5": dict(model_type="ernie4_5", **_C),
+    "ernie4_5_moe": dict(model_type="ernie4_5_moe", **_C, moe_intermediate_size=128, moe_num_experts=8, moe_k=2, moe_num_shared_experts=1,
+                         moe_layer_start_index=1, moe_layer_interval=1),
+    "hunyuan_v1_moe": dict(model_type="hunyuan_v1_moe", **_C, num_experts=4, moe_topk=2, num_shared_expert=1, moe_intermediate_size=128),
     "hunyuan_v1_dense": dict(model_type="hunyuan_v1_dense", **_C),
     "gpt_oss": dict(model_type="gpt_oss", **_C, num_local_experts=4, num_experts_per_tok=2, sliding_window=16),
     "granite": dict(model_type="granite", **_NH, attention_multiplier=0.2, embedding_multiplier=3.0, residual_multiplier=0.5,
