@@ -23,7 +23,9 @@ def _chat_loop(model, args):
             continue
         print("AI: ", end="", flush=True)
         out = ""
-        for piece in model.stream_response(q, history=history):
+        from .util import sampling_kwargs
+
+        for piece in model.stream_response(q, history=history, **sampling_kwargs(args)):
             out += piece
             print(piece, end="", flush=True)
         print()
@@ -88,6 +90,13 @@ def main(argv=None):
         p.add_argument("-o", "--output", type=str, required=True)
     if cmd == "download":
         p.add_argument("--repo", type=str, default="")
+        p.add_argument("--local-dir", dest="local_dir", type=str, default="")
+        p.add_argument("--revision", type=str, default="")
+        p.add_argument("--include", type=str, nargs="*", default=None)
+        p.add_argument("--exclude", type=str, nargs="*", default=None)
+        p.add_argument("--hf_token", type=str, default="")
+        p.add_argument("--hf_username", type=str, default="")
+        p.add_argument("-j", "--workers", dest="workers", type=int, default=8)
     args = p.parse_args(argv)
     if cmd == "config":
         print(json.dumps({k: v for k, v in vars(args).items() if v not in (None, "", -1, False)}, indent=1))
@@ -95,7 +104,8 @@ def main(argv=None):
     if cmd == "download":
         from .download import download
 
-        print(download(args.repo or args.model or args.path, args.cache_dir or None))
+        print(download(args.repo or args.model or args.path, args.cache_dir or None, args.local_dir or None, args.revision or None,
+                       args.include, args.exclude, args.hf_token or None, args.workers))
         return 0
     if cmd == "export":
         from .loader import flm

@@ -5,7 +5,10 @@ from __future__ import annotations
 import os
 
 
-def download(repo: str, cache_dir: str | None = None) -> str:
+def download(repo: str, cache_dir: str | None = None, local_dir: str | None = None, revision: str | None = None,
+             include: list | None = None, exclude: list | None = None, token: str | None = None, workers: int = 8) -> str:
+    """Snapshot a model repository (resumable).  ``include`` / ``exclude`` are glob patterns as in the reference's
+    ``ftllm download --include ... --exclude ...``."""
     if not repo:
         raise SystemExit("download: give a repository id, e.g. Qwen/Qwen3-0.6B")
     if os.path.isdir(repo):
@@ -15,7 +18,8 @@ def download(repo: str, cache_dir: str | None = None) -> str:
     except ImportError as e:
         raise SystemExit(f"download needs the huggingface_hub package: {e}")
     try:
-        return snapshot_download(repo, cache_dir=cache_dir, resume_download=True,
-                                 allow_patterns=["*.json", "*.safetensors", "*.txt", "*.model", "*.jinja", "*.tiktoken"])
+        return snapshot_download(repo, cache_dir=cache_dir, local_dir=local_dir, revision=revision, token=token, max_workers=workers,
+                                 allow_patterns=include or ["*.json", "*.safetensors", "*.txt", "*.model", "*.jinja", "*.tiktoken"],
+                                 ignore_patterns=exclude or None)
     except Exception as e:
         raise SystemExit(f"download of '{repo}' failed (offline host?): {e}")

@@ -9,6 +9,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import sys
 
 import torch
 
@@ -51,7 +52,35 @@ def make_normal_parser(des: str = "fastllm_b200", add_help: bool = True) -> argp
     p.add_argument("--ori", type=str, default="")
     p.add_argument("--tool_call_parser", type=str, default="auto")
     p.add_argument("--chat_template", type=str, default="")
+    # sampling defaults of the interactive commands (reference: chat.py / tui.py)
+    p.add_argument("--top_p", type=float, default=None)
+    p.add_argument("--top_k", type=int, default=None)
+    p.add_argument("--temperature", type=float, default=None)
+    p.add_argument("--repeat_penalty", type=float, default=None)
+    # accepted for command-line compatibility; these name mechanisms this build does not have (a weight slab allocator, an
+    # external Triton compile server, speculative draft models, linear-attention state snapshots): they change nothing here
+    p.add_argument("--cuda_slab", type=str, default="")
+    p.add_argument("--triton", type=str, default="")
+    p.add_argument("--mtp", type=str, default="")
+    p.add_argument("--dspark", type=str, default="")
+    p.add_argument("--speculative_algorithm", type=str, default="")
+    p.add_argument("--speculative_draft_model_path", type=str, default="")
+    p.add_argument("--speculative_dspark_block_size", type=int, default=0)
+    p.add_argument("--speculative_dspark_confidence_threshold", type=float, default=0.0)
+    p.add_argument("--prefix_cache_snapshot_interval_pages", type=int, default=0)
+    p.add_argument("--prefix_cache_snapshot_max_per_request", type=int, default=0)
+    p.add_argument("--prefix_cache_snapshot_max_records", type=int, default=0)
     return p
+
+
+def sampling_kwargs(args) -> dict:
+    """Generation keyword arguments from the --top_p / --top_k / --temperature / --repeat_penalty flags (unset flags omitted)."""
+    kw = {}
+    for name in ("top_p", "top_k", "temperature", "repeat_penalty"):
+        v = getattr(args, name, None)
+        if v is not None:
+            kw[name] = v
+    return kw
 
 
 def parse_tp(tp: str) -> list[int]:
@@ -105,6 +134,10 @@ def make_normal_llm_model(args):
     from . import llm
 
     args = apply_config_file(args)
+    for flag in ("mtp", "dspark", "speculative_algorithm", "speculative_draft_model_path"):
+        if getattr(args, flag, ""):
+            print(f"[fastllm_b200] --{flag} is accepted but speculative decoding is not part of this build; decoding normally",
+                  file=sys.stderr)
     if not args.path:
         raise SystemExit("no model given: pass a model path (HF folder, .flm or .gguf)")
     if args.threads and args.threads > 0:
