@@ -280,6 +280,24 @@ class model:
         hs = [self.launch_stream_response(q, **kw) for q in queries]
         return ["".join(self.stream_response_handle(h)) for h in hs]
 
+    def add_cache(self, prompt) -> int:
+        """Prefill ``prompt`` once so that its full pages sit in the prefix cache for later requests that start with it
+        (reference: add_cache_llm_model, tools/src/pytools.cpp:1006).  Returns the number of prompt tokens."""
+        ids = self._to_ids(prompt) if not (isinstance(prompt, list) and prompt and isinstance(prompt[0], int)) else list(prompt)
+        self.engine.start()
+        h = self.engine.launch(ids, GenerationConfig(max_new_tokens=1, ignore_eos=True))
+        while self.engine.fetch(h) >= 0:
+            pass
+        return len(ids)
+
+    def set_adapter(self, name: str):
+        """LoRA adapters are merged into the weights at load time (``llm.model(path, lora=adapter_dir)``); switching adapters
+        on a loaded model is not supported."""
+        raise NotImplementedError("adapters are merged at load: construct llm.model(path, lora=adapter_dir)")
+
+    def disable_adapter(self):
+        raise NotImplementedError("adapters are merged at load: construct llm.model(path) without lora to run the base model")
+
     def get_response_statistics(self, handle: int) -> dict:
         return self.engine.stats(handle)
 

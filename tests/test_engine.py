@@ -142,3 +142,20 @@ def test_engine_recovers_from_device_kernel_error():
     again = eng.generate([list(range(3, 20))], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0]
     assert again == good
     assert eng.pm.stats()["free"] + eng.pm.stats()["cached"] == 8      # no page leaked by the failed request
+
+
+def test_add_cache_populates_prefix_cache(tmp_path):
+    from baseline import synth
+    from fastllm_b200 import llm
+
+    d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.float32, std=0.05)
+    llm.set_device_map("cpu")
+    m = llm.model(d, device="cpu")
+    prefix = list(range(3, 3 + 300))                      # two full 128-token pages + a tail
+    assert m.add_cache(prefix) == 300
+    h = m.launch_stream_response(prefix + [7, 8, 9], max_length=2, do_sample=False)
+    req = m.engine.requests[h]
+    while m.engine.fetch(h) >= 0:
+        pass
+    assert req.stats.as_dict()["cached_tokens"] >= 256
+    m.release_memory()
