@@ -1,0 +1,435 @@
+// Integer small-M GEMM for sm_100a: 8-bit activations x int8 / int4-group weights on the tensor core (tcgen05.mma kind::i8).
+//
+// The 16-bit-activation kernels for these weight formats (gemm_quant.cu) convert every weight tile to bf16 in shared memory
+// and are bound by that conversion (slower than the plain bf16 GEMM at decode sizes).  Here the weights reach the tensor core
+// as signed bytes: int8 weights directly by TMA (stored as q - 128), int4-group weights after a nibble -> byte unpack that is
+// four bit operations per eight values.  Activations are quantised per token and 128-wide k block to int8 by
+// fb_quant_act_i8, which also records the block sums of the quantised values (needed for zero points / group minima).
+// One k block = four K=32 MMAs into one of two TMEM buffers (exact int32 sums); the promotion warps turn it into fp32:
+//     int8 per channel  (w = s_n (q - z_n)):        acc[m] += (sum - z'_n * xs[m,kb]) * a[m,kb]          finally * s_n
+//     int4 group g = kb (w = min_ng + s_ng q):      acc[m] += (sum * s_ng + min_ng * xs[m,kb]) * a[m,kb]
+// with z' = z - 128, xs = sum of the quantised activations of the block, a = activation scale.  Split-K clusters and the
+// epilogue are the ones of the 16-bit decode GEMM.
+//
+// Reference kernels for these formats: CUDA-core GEMV / dequant + cuBLAS (src/devices/cuda/linear/fastllm-linear-int8.cu,
+// fastllm-linear-int4group.cu) and Marlin mma.sync (fastllm-marlin.cu).
+#include "gemm_smallm.cuh"
+#include "launch.h"
+#include "tmap.h"
+
+FB_DEFINE_ERROR_API(gemm_i8)
+
+namespace fb {
+
+constexpr int KID_GEMM_I8 = 15;
+constexpr int WK_INT8 = 1, WK_INT4G = 2;
+
+template <int MPAD, int WK>
+struct I8Cfg {
+  static constexpr int A_BYTES = 128 * 128;                              // 128 weight rows x 128 int8 (MMA operand)
+  static constexpr int RAW_BYTES = WK == WK_INT4G ? 128 * 64 : 0;        // packed nibbles of one k block
+  static constexpr int B_BYTES = MPAD * 128;
+  // int8: the TMA tile is the operand.  int4g: TMA brings the packed tile, the unpack fills one of two operand slots.
+  static constexpr int STAGE_BYTES = (WK == WK_INT4G ? RAW_BYTES : A_BYTES) + B_BYTES;
+  static constexpr int DQ_SLOTS = WK == WK_INT4G ? 2 : 0;
+  static constexpr int BUDGET = 100 * 1024 - DQ_SLOTS * A_BYTES;
+  static constexpr int MAX_STAGES = BUDGET / STAGE_BYTES;
+  static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
+  static constexpr int RED_BYTES = MPAD * 128 * 4;
+  static constexpr int PIPE_BYTES = DQ_SLOTS * A_BYTES + STAGES * STAGE_BYTES;
+  static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
+  static constexpr int SMEM_BYTES = BODY_BYTES + 512 + 1024;
+  static constexpr int TMEM_COLS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
+};
+
+struct I8Scales {
+  const float* w_scale;      // int8: [N];  int4g: [N, kb_total]
+  const float* w_zero;       // int8: zero point - 128 [N];  int4g: group minima [N, kb_total]
+  const float* a_scale;      // [kb_total, ld_a]
+  const float* a_sum;        // [kb_total, ld_a]  sums of the quantised activations per block
+  int ld_a;
+};
+
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}\n"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// instruction descriptor for kind::i8: D = s32 (2), A and B = signed 8 bit (1), both K-major
+__host__ __device__ constexpr uint32_t make_idesc_i8(uint32_t M, uint32_t N) {
+  return (2u << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
+}
+
+template <int MPAD, bool BF16, int WK>
+__device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const I8Scales& sc) {
+  using Cfg = I8Cfg<MPAD, WK>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* dq = smem;                                               // int4g: two unpacked operand slots (1024-aligned)
+  uint8_t* stages = smem + Cfg::DQ_SLOTS * Cfg::A_BYTES;            // per stage: [activation tile | weight tile (int8) or packed tile (int4g)]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;     // int8: MMA commit.  int4g: 128 unpack arrivals + MMA commit
+  uint64_t* tm_full = empty_bar + Cfg::STAGES;      // [2]
+  uint64_t* tm_empty = tm_full + 2;                 // [2]
+  uint64_t* dq_full = tm_empty + 2;                 // [2] int4g: operand slot unpacked (128 arrivals)
+  uint64_t* dq_empty = dq_full + 2;                 // [2] int4g: MMA of that slot committed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 2);
+  // activation tiles must start on 1024-byte boundaries (128-byte swizzle): B first in every stage, stage sizes are multiples of 1024
+  static_assert(Cfg::STAGE_BYTES % 1024 == 0, "stage size");
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = (int)cluster_ctarank();
+  const int nsplit = (int)cluster_nctarank();
+  const int n_tile = blockIdx.y;
+  const int kb0 = split * p.kb_per_split;           // k blocks of 128
+  int kb_cnt = p.kb_total - kb0;
+  if (kb_cnt > p.kb_per_split) kb_cnt = p.kb_per_split;
+  if (kb_cnt < 0) kb_cnt = 0;
+  bool dead = false;
+  pdl_launch_dependents();
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], WK == WK_INT4G ? 129 : 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); mbar_init(&dq_full[b], 128); mbar_init(&dq_empty[b], 1); }
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  constexpr int WBYTES = WK == WK_INT4G ? 64 : 128;       // weight bytes per row and k block in global memory
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
+      for (int i = 0; i < pre; ++i) {
+        mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(stages + i * Cfg::STAGE_BYTES + Cfg::B_BYTES, &tmW, &full_bar[i], (kb0 + i) * WBYTES, p.w_row0 + n_tile * 128, pol_w);
+      }
+      pdl_wait();
+      for (int i = 0; i < pre; ++i)
+        tma_load_2d_hint(stages + i * Cfg::STAGE_BYTES, &tmX, &full_bar[i], (kb0 + i) * 128, p.x_row0, pol_x);
+      for (int i = pre; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_I8, 1)) break;
+        uint8_t* st = stages + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_2d_hint(st + Cfg::B_BYTES, &tmW, &full_bar[s], (kb0 + i) * WBYTES, p.w_row0 + n_tile * 128, pol_w);
+        tma_load_2d_hint(st, &tmX, &full_bar[s], (kb0 + i) * 128, p.x_row0, pol_x);
+      }
+    }
+    __syncwarp();
+    pdl_wait();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      for (int i = 0; i < kb_cnt; ++i) {
+        const int s = i % Cfg::STAGES, b = i & 1;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = ((uint32_t)i >> 1) & 1u;
+        if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_I8, 2)) break;
+        if (WK == WK_INT4G && !mbar_wait(&dq_full[b], bph, dead, KID_GEMM_I8, 5)) break;
+        if (!mbar_wait(&tm_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 3)) break;
+        tc_fence_after_sync();
+        const uint32_t x_addr = smem_u32(stages + s * Cfg::STAGE_BYTES);
+        const uint32_t w_addr = WK == WK_INT4G ? smem_u32(dq + b * Cfg::A_BYTES) : x_addr + Cfg::B_BYTES;
+        const uint64_t da = make_smem_desc(w_addr, 16, 1024, SWZ_128B);
+        const uint64_t db = make_smem_desc(x_addr, 16, 1024, SWZ_128B);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_i8(tmem_base + b * MPAD, da + 2 * k, db + 2 * k, p.idesc, k != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+        if (WK == WK_INT4G) umma_commit(&dq_empty[b]);
+        umma_commit(&tm_full[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    const int n_local = q * 32 + lane;
+    const int tid = threadIdx.x - 64;                    // 0..127 among the four promotion warps
+    float acc[MPAD];
+#pragma unroll
+    for (int j = 0; j < MPAD; ++j) acc[j] = 0.f;
+    pdl_wait();
+    const int n_glob = p.w_row0 + n_tile * 128 + n_local;
+    const bool n_ok = n_tile * 128 + n_local < p.N;
+    float zrow = 0.f, srow = 1.f;
+    if (WK == WK_INT8 && n_ok) { zrow = sc.w_zero[n_glob]; srow = sc.w_scale[n_glob]; }
+    constexpr int CH = MPAD < 32 ? MPAD : 32;
+
+    // int4g: unpack the packed tile of k block i into operand slot i & 1 (thread t handles 16-byte chunks t, t+128, ...)
+    auto unpack = [&](int i) {
+      const int s = i % Cfg::STAGES, b = i & 1;
+      const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = ((uint32_t)i >> 1) & 1u;
+      if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_I8, 6)) return;
+      if (!mbar_wait(&dq_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 7)) return;
+      const uint8_t* raw = stages + s * Cfg::STAGE_BYTES + Cfg::B_BYTES;
+      uint8_t* out = dq + b * Cfg::A_BYTES;
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int idx = tid + it * 128;                  // 512 chunks of 16 packed bytes
+        const int row = idx >> 2, c4 = idx & 3;
+        const uint4 v = *reinterpret_cast<const uint4*>(raw + idx * 16);
+        uint32_t o[8];
+        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t hi = (w4[e] >> 4) & 0x0F0F0F0Fu, lo = w4[e] & 0x0F0F0F0Fu;      // first value of a byte = high nibble
+          o[2 * e] = __byte_perm(hi, lo, 0x5140);
+          o[2 * e + 1] = __byte_perm(hi, lo, 0x7362);
+        }
+        uint8_t* rowp = out + row * 128;
+        const int c0 = 2 * c4, c1 = 2 * c4 + 1;
+        *reinterpret_cast<uint4*>(rowp + ((c0 ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(rowp + ((c1 ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&dq_full[b]);
+      mbar_arrive(&empty_bar[s]);
+    };
+
+    if (WK == WK_INT4G && kb_cnt > 0) unpack(0);
+    for (int i = 0; i < kb_cnt; ++i) {
+      if (WK == WK_INT4G && i + 1 < kb_cnt) unpack(i + 1);
+      const int b = i & 1;
+      if (!mbar_wait(&tm_full[b], ((uint32_t)i >> 1) & 1u, dead, KID_GEMM_I8, 4)) break;
+      tc_fence_after_sync();
+      float wa = 1.f, wb = -zrow;
+      if (WK == WK_INT4G && n_ok) {
+        wa = __ldg(sc.w_scale + (size_t)n_glob * p.kb_total + kb0 + i);
+        wb = __ldg(sc.w_zero + (size_t)n_glob * p.kb_total + kb0 + i);
+      }
+      const float4* asp = reinterpret_cast<const float4*>(sc.a_scale + (size_t)(kb0 + i) * sc.ld_a + p.x_row0);
+      const float4* xsp = reinterpret_cast<const float4*>(sc.a_sum + (size_t)(kb0 + i) * sc.ld_a + p.x_row0);
+#pragma unroll
+      for (int c0 = 0; c0 < MPAD; c0 += CH) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + b * MPAD + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if (CH == 32) tmem_ld_32x32b_x32(taddr, r); else tmem_ld_32x32b_x16(taddr, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < CH; j += 4) {
+          const float4 a4 = __ldg(asp + ((c0 + j) >> 2));
+          const float4 x4 = __ldg(xsp + ((c0 + j) >> 2));
+          acc[c0 + j + 0] = fmaf(fmaf(__int2float_rn((int)r[j + 0]), wa, wb * x4.x), a4.x, acc[c0 + j + 0]);
+          acc[c0 + j + 1] = fmaf(fmaf(__int2float_rn((int)r[j + 1]), wa, wb * x4.y), a4.y, acc[c0 + j + 1]);
+          acc[c0 + j + 2] = fmaf(fmaf(__int2float_rn((int)r[j + 2]), wa, wb * x4.z), a4.z, acc[c0 + j + 2]);
+          acc[c0 + j + 3] = fmaf(fmaf(__int2float_rn((int)r[j + 3]), wa, wb * x4.w), a4.w, acc[c0 + j + 3]);
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&tm_empty[b]);
+    }
+    float* P = reinterpret_cast<float*>(smem);
+    asm volatile("bar.sync 1, 128;\n" ::: "memory");
+#pragma unroll
+    for (int j = 0; j < MPAD; ++j) P[j * 128 + n_local] = n_ok ? acc[j] * srow : 0.f;
+  }
+  tc_fence_before_sync();
+  cluster_sync_all();
+  smallm_reduce_store<BF16>(p, smem, split, nsplit, n_tile);
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
+template <int MPAD, bool BF16, int WK>
+__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p, const I8Scales sc) {
+  gemm_i8_device<MPAD, BF16, WK>(tmW, tmX, p, sc);
+}
+
+struct I8GroupInfo {
+  const int* counts; const int* offsets;
+  int rows_per_chunk, chunks, n_rows_w;
+};
+
+template <int MPAD, bool BF16, int WK>
+__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+moe_grouped_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
+                      const I8Scales sbase, const I8GroupInfo gi) {
+  const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int cnt = gi.counts[e];
+  const int row0 = chunk * gi.rows_per_chunk;
+  if (row0 >= cnt) return;
+  GemmParams p = base;
+  const int seg = gi.offsets[e] + row0;
+  p.M = cnt - row0 < gi.rows_per_chunk ? cnt - row0 : gi.rows_per_chunk;
+  p.x_row0 = seg;
+  p.w_row0 = e * gi.n_rows_w;         // per-row scale tables of the stacked experts are indexed by w_row0 + row
+  p.out = reinterpret_cast<uint16_t*>(base.out) + (size_t)seg * base.ld_out;
+  gemm_i8_device<MPAD, BF16, WK>(tmW, tmX, p, sbase);
+}
+
+// ---- activation quantisation: x [M, K] 16-bit -> int8 [M, K], scales and block sums [K / 128, ld_a] ------------------------
+template <bool BF16>
+__global__ void quant_act_i8_kernel(const uint16_t* __restrict__ x, int ldx, int8_t* __restrict__ xq, int ldq, float* __restrict__ scales,
+                                    float* __restrict__ sums, int ld_a, int M, int kb_total, const int* __restrict__ rows_used,
+                                    const int* __restrict__ pos, int topk) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int m = gw / kb_total, kb = gw - m * kb_total;
+  if (m >= M) return;
+  int src = m, dst = m;
+  if (pos != nullptr) {                 // gather mode: m enumerates (token, k) pairs, the row goes to pos[m] of the sorted buffer
+    dst = pos[m];
+    if (dst < 0) return;
+    src = m / topk;
+  } else if (rows_used != nullptr && m >= *rows_used) {
+    return;
+  }
+  const uint2 v = *reinterpret_cast<const uint2*>(x + (size_t)src * ldx + kb * 128 + lane * 4);
+  const float2 a = unpack_16<BF16>(v.x), b = unpack_16<BF16>(v.y);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  const float scale = fmaxf(amax, 1e-12f) / 127.0f;
+  const float inv = 1.0f / scale;
+  const int q0 = __float2int_rn(a.x * inv), q1 = __float2int_rn(a.y * inv), q2 = __float2int_rn(b.x * inv), q3 = __float2int_rn(b.y * inv);
+  *reinterpret_cast<uint32_t*>(xq + (size_t)dst * ldq + kb * 128 + lane * 4) =
+      (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+  int s = q0 + q1 + q2 + q3;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  if (lane == 0) { scales[(size_t)kb * ld_a + dst] = scale; sums[(size_t)kb * ld_a + dst] = (float)s; }
+}
+
+}  // namespace fb
+
+using namespace fb;
+
+// pos == null: quantise rows [0, M) (or [0, *rows_used)).  pos != null: M = tokens * topk pairs, row pos[pair] <- token pair / topk.
+extern "C" int fb_quant_act_i8(const void* x, int ldx, void* xq, int ldq, float* scales, float* sums, int ld_a, int M, int K, int dtype,
+                               const int* rows_used, const int* pos, int topk, void* stream) {
+  if (M <= 0) return 0;
+  if (K % 128 != 0 || ldx % 4 != 0 || ldq % 4 != 0) return -1;
+  const int kb_total = K / 128, wpb = 8;
+  const int warps = M * kb_total;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1)
+    launch_k(quant_act_i8_kernel<true>, dim3((warps + wpb - 1) / wpb), dim3(wpb * 32), 0, s, 0, (const uint16_t*)x, ldx, (int8_t*)xq, ldq,
+             scales, sums, ld_a, M, kb_total, rows_used, pos, topk);
+  else
+    launch_k(quant_act_i8_kernel<false>, dim3((warps + wpb - 1) / wpb), dim3(wpb * 32), 0, s, 0, (const uint16_t*)x, ldx, (int8_t*)xq, ldq,
+             scales, sums, ld_a, M, kb_total, rows_used, pos, topk);
+  return (int)cudaGetLastError();
+}
+
+template <int MPAD, bool BF16, int WK>
+static cudaError_t launch_i8(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const I8Scales& sc, const I8GroupInfo* gi,
+                             int nsplit, int n_tiles, int nz, cudaStream_t stream) {
+  using Cfg = I8Cfg<MPAD, WK>;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, nz);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
+  if (gi == nullptr) {
+    auto kern = gemm_i8_kernel<MPAD, BF16, WK>;
+    static DeviceOnce configured;
+    if (configured.need()) {
+      cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+      if (e != cudaSuccess) return e;
+    }
+    return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, sc);
+  }
+  auto kern = moe_grouped_i8_kernel<MPAD, BF16, WK>;
+  static DeviceOnce configured_g;
+  if (configured_g.need()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+  }
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, sc, *gi);
+}
+
+template <int WK>
+static int dispatch_i8(int mpad, int dtype, const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const I8Scales& sc,
+                       const I8GroupInfo* gi, int nsplit, int n_tiles, int nz, cudaStream_t stream) {
+  cudaError_t e;
+#define FB_I8(MP)                                                                                                  \
+  e = dtype == 1 ? launch_i8<MP, true, WK>(tmW, tmX, p, sc, gi, nsplit, n_tiles, nz, stream)                       \
+                 : launch_i8<MP, false, WK>(tmW, tmX, p, sc, gi, nsplit, n_tiles, nz, stream);                     \
+  break;
+  switch (mpad) {
+    case 16: FB_I8(16)
+    case 32: FB_I8(32)
+    case 64: FB_I8(64)
+    default: FB_I8(128)
+  }
+#undef FB_I8
+  return (int)e;
+}
+
+// wkind: 1 = int8 per channel (Wq int8 = q - 128, w_scale [N], w_zero = zero - 128 [N]);
+//        2 = int4 group 128 (Wq packed [N, K / 2], w_scale / w_zero (group minima) [N, K / 128]).
+// counts == null: plain GEMM, M <= 128.  counts != null: grouped over the expert-sorted buffer (rows_cap rows, n_local experts,
+// max_rows: low 16 bits = most rows of one expert, high 16 bits = rows-per-chunk hint).
+extern "C" int fb_gemm_i8(const void* xq, int ldq, const float* a_scale, const float* a_sum, int ld_a, const void* Wq, const float* w_scale,
+                          const float* w_zero, void* out, const void* bias, const void* residual, int M, int N, int K, int ld_out,
+                          int ld_res, int dtype, int flags, int wkind, int nsplit, const int* counts, const int* offsets, int n_local,
+                          int rows_cap, int max_rows, void* stream_) {
+  if (M <= 0 && counts == nullptr) return 0;
+  if (K % 128 != 0 || N % 8 != 0 || (wkind != WK_INT8 && wkind != WK_INT4G)) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const int kb_total = K / 128;
+  const int wbytes = wkind == WK_INT4G ? K / 2 : K;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  GemmParams p = {};
+  p.out = out; p.bias = bias; p.residual = residual; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res; p.flags = flags;
+  p.kb_total = kb_total;
+  I8Scales sc;
+  sc.w_scale = w_scale; sc.w_zero = w_zero; sc.a_scale = a_scale; sc.a_sum = a_sum; sc.ld_a = ld_a;
+  CUtensorMap tmW, tmX;
+  int mpad = 16;
+  if (counts == nullptr) {
+    if (M > 128) return -1;
+    while (mpad < M) mpad <<= 1;
+    const int n_tiles = (N + 127) / 128;
+    if (nsplit <= 0) {
+      nsplit = 1;
+      const int slots = sm_count * (mpad <= 64 ? 2 : 1);
+      while (nsplit < 8 && n_tiles * nsplit * 2 <= slots && kb_total / (nsplit * 2) >= 4) nsplit <<= 1;
+    }
+    if (!make_tmap_2d(&tmW, Wq, (uint64_t)N, (uint64_t)wbytes, (uint64_t)wbytes, 128, wkind == WK_INT4G ? 64 : 128, 1, wkind == WK_INT4G ? 0 : 3)) return -2;
+    if (!make_tmap_2d(&tmX, xq, (uint64_t)M, (uint64_t)K, (uint64_t)ldq, mpad, 128, 1, 3)) return -2;
+    p.M = M; p.kb_per_split = (kb_total + nsplit - 1) / nsplit;
+    p.idesc = make_idesc_i8(128, mpad);
+    return wkind == WK_INT8 ? dispatch_i8<WK_INT8>(mpad, dtype, tmW, tmX, p, sc, nullptr, nsplit, n_tiles, 1, stream)
+                            : dispatch_i8<WK_INT4G>(mpad, dtype, tmW, tmX, p, sc, nullptr, nsplit, n_tiles, 1, stream);
+  }
+  if (N % 128 != 0 || n_local <= 0 || rows_cap <= 0) return -1;
+  const int hint = (max_rows >> 16) & 0xFFFF;
+  max_rows &= 0xFFFF;
+  if (max_rows <= 0) max_rows = rows_cap;
+  const int want = hint > 0 ? hint : max_rows;
+  while (mpad < want && mpad < 64) mpad <<= 1;
+  const int chunks = (max_rows + mpad - 1) / mpad;
+  const int n_tiles = N / 128;
+  if (!make_tmap_2d(&tmW, Wq, (uint64_t)n_local * N, (uint64_t)wbytes, (uint64_t)wbytes, 128, wkind == WK_INT4G ? 64 : 128, 1, wkind == WK_INT4G ? 0 : 3)) return -2;
+  if (!make_tmap_2d(&tmX, xq, (uint64_t)rows_cap, (uint64_t)K, (uint64_t)ldq, mpad, 128, 1, 3)) return -2;
+  p.M = mpad; p.kb_per_split = kb_total;
+  p.idesc = make_idesc_i8(128, mpad);
+  I8GroupInfo gi;
+  gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
+  return wkind == WK_INT8 ? dispatch_i8<WK_INT8>(mpad, dtype, tmW, tmX, p, sc, &gi, 1, n_tiles, n_local * chunks, stream)
+                          : dispatch_i8<WK_INT4G>(mpad, dtype, tmW, tmX, p, sc, &gi, 1, n_tiles, n_local * chunks, stream);
+}

@@ -35,6 +35,23 @@ class StackedExperts:
     def __init__(self, kind, gate_up, down, n_local, inter, hidden, group=0, gu_scale=None, gu_zero=None, dn_scale=None, dn_zero=None):
         self.kind, self.gate_up, self.down, self.n_local, self.inter, self.hidden, self.group = kind, gate_up, down, n_local, inter, hidden, group
         self.gu_scale, self.gu_zero, self.dn_scale, self.dn_zero = gu_scale, gu_zero, dn_scale, dn_zero
+        self.signed = False            # int8: the stacked bytes hold q - 128 (operand form of the integer tensor-core path)
+        self.a8 = None                 # (gate_up scale, zero / min, down scale, zero / min) in the integer kernel's layout
+
+
+def _prepare_a8(st: StackedExperts, experts) -> None:
+    """Stacked scale tables for the int8-activation kernels (``[E * rows]`` per channel, ``[E * rows, K / 128]`` per group);
+    int8 weight bytes are switched to q - 128 in place, once, together with the per-expert views of the same storage."""
+    shift = 128.0 if st.kind == "int8" else 0.0
+    if st.kind == "int8" and not st.signed:
+        st.gate_up.view(torch.uint8).bitwise_xor_(0x80)
+        st.down.view(torch.uint8).bitwise_xor_(0x80)
+        st.signed = True
+        for w in experts.gate_up + experts.down:
+            w.signed = True
+    cat = lambda ws, f: torch.cat([f(w).float().reshape(w.n, -1) for w in ws], dim=0).contiguous()
+    st.a8 = (cat(experts.gate_up, lambda w: w.scale), cat(experts.gate_up, lambda w: w.zero) - shift,
+             cat(experts.down, lambda w: w.scale), cat(experts.down, lambda w: w.zero) - shift)
 
 
 def _stack_scales(ws):
@@ -111,6 +128,11 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
     _lib.check(lib.fb_moe_plan(_ptr(idx), T, topk, experts.first, E, _ptr(counts), _ptr(offsets), _ptr(pos), _ptr(total), PAD, s), "fb_moe_plan")
     dt = dtype_code(x.dtype)
     fp8_native = st.kind == "fp8" and QG.FP8_NATIVE and H % 128 == 0 and st.inter % 128 == 0
+    int_a8 = QG.INT_A8 and (st.kind == "int8" or (st.kind == "int4g" and st.group == 128)) and H % 128 == 0 and st.inter % 128 == 0
+    if st.signed and not int_a8:
+        return None
+    if int_a8 and st.a8 is None:
+        _prepare_a8(st, experts)
     act = torch.empty((rows_cap, st.inter), device=dev, dtype=x.dtype)
     ys = torch.empty((rows_cap, H), device=dev, dtype=x.dtype)
     if fp8_native:
@@ -120,6 +142,9 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
         sa = torch.empty((H // 128, ld_a), device=dev, dtype=torch.float32)
         _lib.check(lib.fb_moe_gather_quant_fp8(_ptr(x.contiguous()), _ptr(pos), _ptr(xq), _ptr(sa), ld_a, T, topk, H, dt, s),
                    "fb_moe_gather_quant_fp8")
+    elif int_a8:
+        # gather fused with the int8 quantisation of the rows
+        xq, sa, sx, ld_a = QG.quant_act_i8(x.contiguous(), pos=pos, topk=topk, rows_cap=rows_cap)
     else:
         xs = torch.empty((rows_cap, H), device=dev, dtype=x.dtype)
         _lib.check(lib.fb_moe_gather(_ptr(x.contiguous()), _ptr(pos), _ptr(xs), T, topk, H, s), "fb_moe_gather")
@@ -137,6 +162,16 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
         _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(aq), st.inter, _ptr(sb), ld_b, _ptr(st.down), _ptr(st.dn_scale), _ptr(ys), _ptr(counts),
                                                _ptr(offsets), E, H, st.inter, rows_cap, H, dt, 0, max_rows, s),
                    "fb_moe_grouped_gemm_fp8(down)")
+    elif int_a8:
+        wk = 1 if st.kind == "int8" else 2
+        gs, gz, ds, dz = st.a8
+        _lib.check(lib.fb_gemm_i8(_ptr(xq), H, _ptr(sa), _ptr(sx), ld_a, _ptr(st.gate_up), _ptr(gs), _ptr(gz), _ptr(act), _ptr(None),
+                                  _ptr(None), 0, 2 * st.inter, H, st.inter, 0, dt, GEMM_SWIGLU, wk, 1, _ptr(counts), _ptr(offsets), E,
+                                  rows_cap, max_rows, s), "fb_gemm_i8(gate_up)")
+        aq, sb, sbx, ld_b = QG.quant_act_i8(act, rows_used=total)
+        _lib.check(lib.fb_gemm_i8(_ptr(aq), st.inter, _ptr(sb), _ptr(sbx), ld_b, _ptr(st.down), _ptr(ds), _ptr(dz), _ptr(ys), _ptr(None),
+                                  _ptr(None), 0, H, st.inter, H, 0, dt, 0, wk, 1, _ptr(counts), _ptr(offsets), E, rows_cap, max_rows, s),
+                   "fb_gemm_i8(down)")
     else:
         qm = {"int8": 1, "int4g": 2, "fp8": 3}[st.kind]
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(xs), _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(st.gu_zero), _ptr(act), _ptr(counts),

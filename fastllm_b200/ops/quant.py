@@ -88,6 +88,16 @@ def fake_quant_act_fp8(x: torch.Tensor) -> torch.Tensor:
     return ((xb / sc).to(torch.float8_e4m3fn).float() * sc).reshape(x.shape).to(x.dtype)
 
 
+def fake_quant_act_i8(x: torch.Tensor) -> torch.Tensor:
+    """Round activations to int8 per (token, 128-wide k block); see ``fake_quant_act_fp8``."""
+    K = x.shape[-1]
+    if K % 128 != 0:
+        return x
+    xb = x.float().reshape(-1, K // 128, 128)
+    sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / 127.0
+    return (torch.round(xb / sc).clamp(-127, 127) * sc).reshape(x.shape).to(x.dtype)
+
+
 def normalize_wdtype(name: str | None) -> tuple[str, int]:
     """Map CLI dtype names (``--dtype`` / ``--moe_dtype``) to (kind, group)."""
     if name is None:
@@ -111,7 +121,7 @@ def normalize_wdtype(name: str | None) -> tuple[str, int]:
 class LinearWeight:
     """Weight (+ optional bias) of one linear layer in one of the storage formats above."""
 
-    __slots__ = ("kind", "w", "scale", "zero", "bias", "group", "n", "k", "interleaved", "dtype", "_dq")
+    __slots__ = ("kind", "w", "scale", "zero", "bias", "group", "n", "k", "interleaved", "dtype", "_dq", "signed", "_a8")
 
     def __init__(self, kind, w, scale=None, zero=None, bias=None, group=0, dtype=torch.bfloat16, interleaved=False):
         self.kind, self.w, self.scale, self.zero, self.bias, self.group = kind, w, scale, zero, bias, group
@@ -120,6 +130,8 @@ class LinearWeight:
         self.dtype = dtype
         self.interleaved = interleaved      # gate/up rows interleaved per 128-row tile for the SwiGLU epilogue
         self._dq = None
+        self._a8 = None
+        self.signed = False                 # int8 only: bytes hold q - 128 (the integer tensor-core path's operand form)
 
     @staticmethod
     def from_dense(w: torch.Tensor, wdtype: str = "dense", bias=None, interleaved=False, act_dtype=None) -> "LinearWeight":
@@ -143,6 +155,8 @@ class LinearWeight:
         if self.kind == "dense":
             return self.w if self.w.dtype == dtype else self.w.to(dtype)
         if self.kind == "int8":
+            if self.signed:
+                return ((self.w.view(torch.int8).float() + 128.0 - self.zero[:, None]) * self.scale[:, None]).to(dtype)
             return dequantize_int8(self.w, self.scale, self.zero, dtype)
         if self.kind == "int4g":
             return dequantize_int4g(self.w, self.scale, self.zero, dtype, self.group)
@@ -172,4 +186,6 @@ class LinearWeight:
                 return y
             if self.kind == "fp8" and quant_gemm.FP8_NATIVE:
                 x = fake_quant_act_fp8(x)
+            elif quant_gemm.uses_int_a8(self):
+                x = fake_quant_act_i8(x)
         return B.linear(x, self.dequant(x.dtype), self.bias, residual, swiglu, self.interleaved, out_f32)

@@ -21,12 +21,68 @@ _lib.register_sigs({
     "fb_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "fb_moe_grouped_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "fb_moe_gather_quant_fp8": [P, P, P, P, I, I, I, I, I, P],
-}, ["gemm_fp8"])
+    "fb_quant_act_i8": [P, I, P, I, P, P, I, I, I, I, P, P, I, P],
+    "fb_gemm_i8": [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, I, I, P],
+}, ["gemm_fp8", "gemm_i8"])
 
 _QMODE = {"int8": 1, "int4g": 2, "fp8": 3}
 # FP8 weights run as W8A8 (activations quantised per token and 128-wide k block, e4m3 x e4m3 on the tensor core) for decode-sized
 # batches; FB_FP8_W8A16=1 keeps 16-bit activations (weights de-quantised in shared memory), which is also the path for M > 128.
 FP8_NATIVE = __import__("os").environ.get("FB_FP8_W8A16", "0") != "1"
+
+
+# int8 / int4-group(128) weights run with int8 activations on the integer tensor-core path (FB_INT_A16=1 keeps 16-bit activations)
+INT_A8 = __import__("os").environ.get("FB_INT_A16", "0") != "1"
+
+
+INT_A8_MAX_M = 512      # above this the weights are de-quantised once and the plain 16-bit GEMM runs
+
+
+def uses_int_a8(lw) -> bool:
+    return INT_A8 and ((lw.kind == "int8") or (lw.kind == "int4g" and lw.group == 128)) and lw.k % 128 == 0
+
+
+def quant_act_i8(x2: torch.Tensor, rows_used=None, pos=None, topk: int = 1, rows_cap: int | None = None):
+    """x ``[M, K]`` 16-bit -> (int8 ``[rows, K]``, scales, block sums ``[K / 128, ld_a]``).  With ``pos`` the rows are
+    scattered to ``pos[pair]`` of an expert-sorted buffer of ``rows_cap`` rows (gather fused with the quantisation)."""
+    M, K = x2.shape
+    rows = rows_cap if rows_cap is not None else M
+    ld_a = (rows + 128 + 3) // 4 * 4
+    xq = torch.empty((rows, K), device=x2.device, dtype=torch.int8)
+    sa = torch.empty((K // 128, ld_a), device=x2.device, dtype=torch.float32)
+    xs = torch.empty((K // 128, ld_a), device=x2.device, dtype=torch.float32)
+    n = M * topk if pos is not None else M
+    rc = _lib.kernels().fb_quant_act_i8(_ptr(x2), x2.stride(0), _ptr(xq), K, _ptr(sa), _ptr(xs), ld_a, n, K, dtype_code(x2.dtype),
+                                        _ptr(rows_used), _ptr(pos), topk, _stream())
+    _lib.check(rc, "fb_quant_act_i8")
+    return xq, sa, xs, ld_a
+
+
+def _a8_tensors(lw):
+    """Weight-side tensors of the integer path: (bytes, scale, zero-or-min, kind code).  int8 storage is switched to q - 128 once."""
+    if lw.kind == "int8":
+        if not lw.signed:
+            lw.w = (lw.w.view(torch.uint8) ^ 0x80).view(torch.uint8)
+            lw.signed = True
+        if lw._a8 is None:
+            lw._a8 = (lw.scale.float().contiguous(), (lw.zero.float() - 128.0).contiguous())
+        return lw.w, lw._a8[0], lw._a8[1], 1
+    if lw._a8 is None:
+        lw._a8 = (lw.scale.float().contiguous(), lw.zero.float().contiguous())
+    return lw.w, lw._a8[0], lw._a8[1], 2
+
+
+def _linear_i8(x2, lw, out, bias, res2, flags):
+    M, K = x2.shape
+    w, sc, zr, kind = _a8_tensors(lw)
+    xq, sa, xs, ld_a = quant_act_i8(x2)
+    for m0 in range(0, M, 128):           # the kernel takes up to 128 rows; the weights of later chunks come from L2
+        m1 = min(M, m0 + 128)
+        rc = _lib.kernels().fb_gemm_i8(_ptr(xq[m0:m1]), K, _ptr(sa[:, m0:]), _ptr(xs[:, m0:]), ld_a, _ptr(w), _ptr(sc), _ptr(zr),
+                                       _ptr(out[m0:m1]), _ptr(bias), _ptr(res2[m0:m1]) if res2 is not None else _ptr(None),
+                                       m1 - m0, lw.n, K, out.stride(0), res2.stride(0) if res2 is not None else 0,
+                                       dtype_code(x2.dtype), flags, kind, 0, _ptr(None), _ptr(None), 0, 0, 0, _stream())
+        _lib.check(rc, "fb_gemm_i8")
 
 
 def quant_act_fp8(x2: torch.Tensor, rows_used: torch.Tensor | None = None):
@@ -81,7 +137,12 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
         return None
     if swiglu and (not lw.interleaved or N % 128 != 0):
         return None
-    scale, zero = _kernel_tensors(lw)
+    a8 = uses_int_a8(lw)
+    if a8 and (M > INT_A8_MAX_M or x2.stride(0) % 4 != 0):
+        return None                       # large batches: de-quantise + 16-bit GEMM on the same int8-rounded activations
+    if lw.kind == "int8" and lw.signed and not a8:
+        return None
+    scale, zero = (None, None) if a8 else _kernel_tensors(lw)[:2]
     n_out = N // 2 if swiglu else N
     out = torch.empty((M, n_out), device=x.device, dtype=torch.float32 if out_f32 else x.dtype)
     res2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
@@ -90,6 +151,9 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
     bias = lw.bias
     if bias is not None and bias.dtype != x.dtype:
         bias = bias.to(x.dtype)
+    if a8:
+        _linear_i8(x2, lw, out, bias, res2, flags)
+        return out.reshape(*lead, n_out)
     if lw.kind == "fp8" and FP8_NATIVE and M <= 128 and x2.stride(0) % 4 == 0:
         _linear_fp8_native(x2, lw, out, bias, res2, flags)
         return out.reshape(*lead, n_out)

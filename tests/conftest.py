@@ -27,10 +27,11 @@ def pytest_collection_modifyitems(config, items):
 
 @pytest.fixture
 def fp8_w8a16():
-    """Run FP8-weight layers with 16-bit activations (the in-shared-memory dequant kernels) for the duration of a test."""
+    """Run quantised-weight layers with 16-bit activations (the in-shared-memory dequant kernels) for the duration of a test."""
     from fastllm_b200.ops import quant_gemm as QG
 
-    old = QG.FP8_NATIVE
+    old, old_i = QG.FP8_NATIVE, QG.INT_A8
     QG.FP8_NATIVE = False
+    QG.INT_A8 = False
     yield
-    QG.FP8_NATIVE = old
+    QG.FP8_NATIVE, QG.INT_A8 = old, old_i

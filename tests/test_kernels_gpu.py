@@ -479,3 +479,87 @@ def test_moe_grouped_fp8_native_matches_w8a16():
     _lib.check_device_errors()
     rel = (y8.float() - y16.float()).norm() / y16.float().norm()
     assert rel < 0.08, rel
+
+
+def _i8_act(x):
+    M, K = x.shape
+    xb = x.float().reshape(M, K // 128, 128)
+    sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / 127.0
+    return (torch.round(xb / sc).clamp(-127, 127) * sc).reshape(M, K)
+
+
+@pytest.mark.parametrize("kind", ["int8", "int4g128"])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 512), (16, 384, 1024), (64, 4096, 4096), (100, 1024, 14336), (128, 520, 2048), (300, 1024, 2048)])
+def test_gemm_int_a8(kind, M, N, K):
+    """Integer tensor-core path: int8 activations x int8 / int4-group weights vs the same quantised operands in fp32."""
+    from fastllm_b200.ops import quant as Q
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(M + N)
+    dt = torch.bfloat16
+    w = (torch.randn(N, K, device=DEV) * 0.03).to(dt)
+    lw = Q.LinearWeight.from_dense(w, kind)
+    wdq = lw.dequant(torch.float32)
+    x = torch.randn(M, K, device=DEV).to(dt)
+    assert QG.uses_int_a8(lw)
+    out = lw(x)
+    _lib.check_device_errors()
+    ref = _i8_act(x) @ wdq.t()
+    _close(out.float().cpu(), ref.cpu(), 2e-2, 1e-2, f"gemm_i8 {kind} {M}x{N}x{K}")
+    assert torch.allclose(lw.dequant(torch.float32), wdq)          # int8 storage switched to q - 128 without changing the values
+    exact = x.float() @ w.float().t()
+    rel = (out.float() - exact).norm() / exact.norm()
+    assert rel < (0.03 if kind == "int8" else 0.15), rel
+
+
+def test_gemm_int_a8_epilogues():
+    from fastllm_b200.ops import quant as Q
+
+    torch.manual_seed(9)
+    dt = torch.bfloat16
+    M, K, I = 48, 1024, 512
+    g, u = (torch.randn(I, K, device=DEV) * 0.03).to(dt), (torch.randn(I, K, device=DEV) * 0.03).to(dt)
+    x = torch.randn(M, K, device=DEV).to(dt)
+    for kind in ("int8", "int4g128"):
+        lw = Q.LinearWeight.from_dense(B.interleave_gate_up(g, u), kind, interleaved=True)
+        out = lw(x, swiglu=True)
+        full = _i8_act(x) @ lw.dequant(torch.float32).t()
+        t = full.reshape(M, (2 * I) // 128, 2, 64)
+        ref = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(M, I)
+        _close(out.float().cpu(), ref.cpu(), 3e-2, 2e-2, f"gemm_i8 swiglu {kind}")
+        wd = (torch.randn(K, I, device=DEV) * 0.03).to(dt)
+        ld = Q.LinearWeight.from_dense(wd, kind, bias=torch.randn(K, device=DEV).to(dt))
+        res = torch.randn(M, K, device=DEV).to(dt)
+        a = torch.randn(M, I, device=DEV).to(dt)
+        out2 = ld(a, residual=res)
+        ref2 = _i8_act(a) @ ld.dequant(torch.float32).t() + ld.bias.float() + res.float()
+        _close(out2.float().cpu(), ref2.cpu(), 3e-2, 2e-2, f"gemm_i8 bias+residual {kind}")
+    _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("kind", ["int8", "int4g128"])
+def test_moe_grouped_int_a8(kind):
+    """Grouped expert GEMMs on the integer tensor-core path vs the per-expert 16-bit evaluation of the same quantised weights."""
+    from fastllm_b200.models.config import preset
+    from fastllm_b200.models.decoder import random_init
+    from fastllm_b200.ops import moe as MOE
+    from fastllm_b200.ops import quant_gemm as QG
+
+    cfg = preset("tiny-qwen3-moe")
+    m = random_init(cfg, "cuda", torch.bfloat16, std=0.05, moe_wdtype=kind)
+    ex = m.layers[0].mlp.experts
+    assert ex.stacked is not None
+    torch.manual_seed(4)
+    for T in (5, 150):
+        x = torch.randn(T, cfg.hidden_size, device=DEV).bfloat16()
+        idx, w = MOE.route_topk(torch.randn(T, cfg.num_experts, device=DEV), None, 2, 0, True)
+        y8 = MOE.moe_forward(x, idx, w, ex)
+        assert ex.stacked.a8 is not None
+        QG.INT_A8 = False
+        try:
+            y16 = MOE.moe_forward(x, idx, w, ex)
+        finally:
+            QG.INT_A8 = True
+        _lib.check_device_errors()
+        rel = (y8.float() - y16.float()).norm() / y16.float().norm()
+        assert rel < 0.03, (T, rel)
