@@ -24,14 +24,17 @@ template <int MPAD>
 struct Fp8Cfg {
   static constexpr int A_BYTES = 128 * 128;              // 128 weight rows x 128 fp8
   static constexpr int B_BYTES = MPAD * 128;             // MPAD tokens x 128 fp8
-  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int MAX_STAGES = (100 * 1024) / STAGE_BYTES;          // two CTAs per SM
+  static constexpr int SC_OFF = A_BYTES + B_BYTES;       // this k block's activation scales (MPAD floats) travel with the tiles
+  static constexpr int TX_BYTES = SC_OFF + MPAD * 4;
+  static constexpr int STAGE_BYTES = SC_OFF + 1024;      // tiles stay 1024-byte aligned
+  static constexpr int MAX_STAGES = (106 * 1024) / STAGE_BYTES;          // two CTAs per SM
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int RED_BYTES = MPAD * 128 * 4;
   static constexpr int PIPE_BYTES = STAGES * STAGE_BYTES;
   static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
   static constexpr int SMEM_BYTES = BODY_BYTES + 256 + 1024;
-  static constexpr int TMEM_COLS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
+  static constexpr int NBUF = MPAD <= 64 ? 4 : 2;        // TMEM accumulator ring
+  static constexpr int TMEM_COLS = NBUF * MPAD < 32 ? 32 : NBUF * MPAD;
 };
 
 struct Fp8Scales {
@@ -47,9 +50,9 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
   uint64_t* empty_bar = full_bar + Cfg::STAGES;
-  uint64_t* tm_full = empty_bar + Cfg::STAGES;      // [2] k block accumulated into TMEM buffer b
-  uint64_t* tm_empty = tm_full + 2;                 // [2] promotion warps have read buffer b
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tm_empty + 2);
+  uint64_t* tm_full = empty_bar + Cfg::STAGES;      // [NBUF] k block accumulated into TMEM buffer b
+  uint64_t* tm_empty = tm_full + Cfg::NBUF;         // [NBUF] promotion warps have read buffer b
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tm_empty + Cfg::NBUF);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = (int)cluster_ctarank();
@@ -63,8 +66,9 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); }
+    // a stage is released by the MMA commit (tiles) and the 128 promotion threads (scale row)
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 129); }
+    for (int b = 0; b < Cfg::NBUF; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); }
     mbar_init_fence();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
@@ -81,20 +85,23 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
       const uint64_t pol_x = l2_policy_evict_last();
       const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
       for (int i = 0; i < pre; ++i) {          // weights do not depend on the previous kernel
-        mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[i], Cfg::TX_BYTES);
         tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmW, &full_bar[i], (kb0 + i) * 128, p.w_row0 + n_tile * 128, pol_w);
       }
       pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmX, &full_bar[i], (kb0 + i) * 128, p.x_row0, pol_x);
+      auto load_act = [&](int i, uint8_t* st, uint64_t* bar) {
+        tma_load_2d_hint(st + Cfg::A_BYTES, &tmX, bar, (kb0 + i) * 128, p.x_row0, pol_x);
+        bulk_load_1d(st + Cfg::SC_OFF, sc.a_scale + (size_t)(kb0 + i) * sc.ld_a + p.x_row0, MPAD * 4, bar);
+      };
+      for (int i = 0; i < pre; ++i) load_act(i, smem + i * Cfg::STAGE_BYTES, &full_bar[i]);
       for (int i = pre; i < kb_cnt; ++i) {
         const int s = i % Cfg::STAGES;
         const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_FP8, 1)) break;
         uint8_t* a = smem + s * Cfg::STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], Cfg::TX_BYTES);
         tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 128, p.w_row0 + n_tile * 128, pol_w);
-        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], (kb0 + i) * 128, p.x_row0, pol_x);
+        load_act(i, a, &full_bar[s]);
       }
     }
     __syncwarp();
@@ -102,10 +109,10 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
   } else if (warp == 1) {
     if (elect_one()) {
       for (int i = 0; i < kb_cnt; ++i) {
-        const int s = i % Cfg::STAGES, b = i & 1;
+        const int s = i % Cfg::STAGES, b = i % Cfg::NBUF;
         const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
         if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_FP8, 2)) break;
-        if (!mbar_wait(&tm_empty[b], (((uint32_t)i >> 1) & 1u) ^ 1u, dead, KID_GEMM_FP8, 3)) break;
+        if (!mbar_wait(&tm_empty[b], ((uint32_t)(i / Cfg::NBUF) & 1u) ^ 1u, dead, KID_GEMM_FP8, 3)) break;
         tc_fence_after_sync();
         const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
         const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
@@ -128,11 +135,13 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
     const float* wsp = sc.w_scale + (size_t)((p.w_row0 >> 7) + n_tile) * p.kb_total + kb0;
     constexpr int CH = MPAD < 32 ? MPAD : 32;
     for (int i = 0; i < kb_cnt; ++i) {
-      const int b = i & 1;
-      if (!mbar_wait(&tm_full[b], ((uint32_t)i >> 1) & 1u, dead, KID_GEMM_FP8, 4)) break;
+      const int b = i % Cfg::NBUF, s = i % Cfg::STAGES;
+      const float ws = __ldg(wsp + i);               // issued before the waits: the latency overlaps the MMA of this block
+      // the scale row is written by a bulk copy that completes on full_bar: observe it in this thread too
+      if (!mbar_wait(&full_bar[s], (uint32_t)(i / Cfg::STAGES) & 1u, dead, KID_GEMM_FP8, 5)) break;
+      if (!mbar_wait(&tm_full[b], (uint32_t)(i / Cfg::NBUF) & 1u, dead, KID_GEMM_FP8, 4)) break;
       tc_fence_after_sync();
-      const float ws = __ldg(wsp + i);
-      const float4* asp = reinterpret_cast<const float4*>(sc.a_scale + (size_t)(kb0 + i) * sc.ld_a + p.x_row0);
+      const float4* asp = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES + Cfg::SC_OFF);     // same address in every lane
 #pragma unroll
       for (int c0 = 0; c0 < MPAD; c0 += CH) {
         uint32_t r[32];
@@ -141,7 +150,7 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < CH; j += 4) {
-          const float4 a4 = __ldg(asp + ((c0 + j) >> 2));
+          const float4 a4 = asp[(c0 + j) >> 2];
           acc[c0 + j + 0] = fmaf(__uint_as_float(r[j + 0]), ws * a4.x, acc[c0 + j + 0]);
           acc[c0 + j + 1] = fmaf(__uint_as_float(r[j + 1]), ws * a4.y, acc[c0 + j + 1]);
           acc[c0 + j + 2] = fmaf(__uint_as_float(r[j + 2]), ws * a4.z, acc[c0 + j + 2]);
@@ -150,6 +159,7 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
       }
       tc_fence_before_sync();
       mbar_arrive(&tm_empty[b]);
+      mbar_arrive(&empty_bar[s]);
     }
     // every MMA has completed (the last tm_full was observed) and every TMA tile was consumed: the ring becomes P
     float* P = reinterpret_cast<float*>(smem);

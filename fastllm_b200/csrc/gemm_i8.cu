@@ -5,11 +5,12 @@
 // as signed bytes: int8 weights directly by TMA (stored as q - 128), int4-group weights after a nibble -> byte unpack that is
 // four bit operations per eight values.  Activations are quantised per token and 128-wide k block to int8 by
 // fb_quant_act_i8, which also records the block sums of the quantised values (needed for zero points / group minima).
-// One k block = four K=32 MMAs into one of two TMEM buffers (exact int32 sums); the promotion warps turn it into fp32:
-//     int8 per channel  (w = s_n (q - z_n)):        acc[m] += (sum - z'_n * xs[m,kb]) * a[m,kb]          finally * s_n
+// One k block = four K=32 MMAs into one buffer of a TMEM ring (exact int32 sums); the promotion warps turn it into fp32:
+//     int8 per channel  (w = s_n (q - z_n)):        acc[m] += sum * a[m,kb];   T[m] += xs[m,kb] * a[m,kb]   finally s_n (acc - z'_n T)
 //     int4 group g = kb (w = min_ng + s_ng q):      acc[m] += (sum * s_ng + min_ng * xs[m,kb]) * a[m,kb]
-// with z' = z - 128, xs = sum of the quantised activations of the block, a = activation scale.  Split-K clusters and the
-// epilogue are the ones of the 16-bit decode GEMM.
+// with z' = z - 128, xs = sum of the quantised activations of the block, a = activation scale.  The a / xs rows of a k block
+// travel with its tiles (bulk copy into the stage), so the promotion reads them from shared memory instead of waiting on L2
+// once per k block.  Split-K clusters and the epilogue are the ones of the 16-bit decode GEMM.
 //
 // Reference kernels for these formats: CUDA-core GEMV / dequant + cuBLAS (src/devices/cuda/linear/fastllm-linear-int8.cu,
 // fastllm-linear-int4group.cu) and Marlin mma.sync (fastllm-marlin.cu).
@@ -29,17 +30,21 @@ struct I8Cfg {
   static constexpr int A_BYTES = 128 * 128;                              // 128 weight rows x 128 int8 (MMA operand)
   static constexpr int RAW_BYTES = WK == WK_INT4G ? 128 * 64 : 0;        // packed nibbles of one k block
   static constexpr int B_BYTES = MPAD * 128;
+  static constexpr int W_BYTES = WK == WK_INT4G ? RAW_BYTES : A_BYTES;
+  static constexpr int SC_OFF = B_BYTES + W_BYTES;                       // activation scales, then block sums (MPAD floats each)
+  static constexpr int TX_BYTES = SC_OFF + 2 * MPAD * 4;
   // int8: the TMA tile is the operand.  int4g: TMA brings the packed tile, the unpack fills one of two operand slots.
-  static constexpr int STAGE_BYTES = (WK == WK_INT4G ? RAW_BYTES : A_BYTES) + B_BYTES;
+  static constexpr int STAGE_BYTES = SC_OFF + 1024;
   static constexpr int DQ_SLOTS = WK == WK_INT4G ? 2 : 0;
-  static constexpr int BUDGET = 100 * 1024 - DQ_SLOTS * A_BYTES;
+  static constexpr int BUDGET = 106 * 1024 - DQ_SLOTS * A_BYTES;      // two CTAs per SM
   static constexpr int MAX_STAGES = BUDGET / STAGE_BYTES;
   static constexpr int STAGES = MAX_STAGES > 8 ? 8 : MAX_STAGES;
   static constexpr int RED_BYTES = MPAD * 128 * 4;
   static constexpr int PIPE_BYTES = DQ_SLOTS * A_BYTES + STAGES * STAGE_BYTES;
   static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
-  static constexpr int SMEM_BYTES = BODY_BYTES + 512 + 1024;
-  static constexpr int TMEM_COLS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
+  static constexpr int SMEM_BYTES = BODY_BYTES + 1024 + 1024;          // barriers (256 B) + zero-point sums T (MPAD floats at +512)
+  static constexpr int NBUF = MPAD <= 64 ? 4 : 2;                        // TMEM accumulator ring
+  static constexpr int TMEM_COLS = NBUF * MPAD < 32 ? 32 : NBUF * MPAD;
 };
 
 struct I8Scales {
@@ -62,6 +67,10 @@ __host__ __device__ constexpr uint32_t make_idesc_i8(uint32_t M, uint32_t N) {
   return (2u << 4) | (1u << 7) | (1u << 10) | ((N >> 3) << 17) | ((M >> 4) << 24);
 }
 
+// int32 block sum -> float without the conversion pipe: |v| < 2^22 (127 * 128 * 128 at most), so v + 0x4B400000 is the bit
+// pattern of 1.5 * 2^23 + v
+__device__ __forceinline__ float sum_to_float(uint32_t v) { return __uint_as_float(v + 0x4B400000u) - 12582912.0f; }
+
 template <int MPAD, bool BF16, int WK>
 __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const I8Scales& sc) {
   using Cfg = I8Cfg<MPAD, WK>;
@@ -70,10 +79,10 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
   uint8_t* dq = smem;                                               // int4g: two unpacked operand slots (1024-aligned)
   uint8_t* stages = smem + Cfg::DQ_SLOTS * Cfg::A_BYTES;            // per stage: [activation tile | weight tile (int8) or packed tile (int4g)]
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
-  uint64_t* empty_bar = full_bar + Cfg::STAGES;     // int8: MMA commit.  int4g: 128 unpack arrivals + MMA commit
-  uint64_t* tm_full = empty_bar + Cfg::STAGES;      // [2]
-  uint64_t* tm_empty = tm_full + 2;                 // [2]
-  uint64_t* dq_full = tm_empty + 2;                 // [2] int4g: operand slot unpacked (128 arrivals)
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;     // MMA commit + 128 promotion arrivals (scales read, packed tile unpacked)
+  uint64_t* tm_full = empty_bar + Cfg::STAGES;      // [NBUF]
+  uint64_t* tm_empty = tm_full + Cfg::NBUF;         // [NBUF]
+  uint64_t* dq_full = tm_empty + Cfg::NBUF;         // [2] int4g: operand slot unpacked (128 arrivals)
   uint64_t* dq_empty = dq_full + 2;                 // [2] int4g: MMA of that slot committed
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(dq_empty + 2);
   // activation tiles must start on 1024-byte boundaries (128-byte swizzle): B first in every stage, stage sizes are multiples of 1024
@@ -91,8 +100,9 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], WK == WK_INT4G ? 129 : 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); mbar_init(&dq_full[b], 128); mbar_init(&dq_empty[b], 1); }
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 129); }
+    for (int b = 0; b < Cfg::NBUF; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&dq_full[b], 128); mbar_init(&dq_empty[b], 1); }
     mbar_init_fence();
     tma_prefetch_desc(&tmW);
     tma_prefetch_desc(&tmX);
@@ -110,20 +120,25 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
       const uint64_t pol_x = l2_policy_evict_last();
       const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
       for (int i = 0; i < pre; ++i) {
-        mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[i], Cfg::TX_BYTES);
         tma_load_2d_hint(stages + i * Cfg::STAGE_BYTES + Cfg::B_BYTES, &tmW, &full_bar[i], (kb0 + i) * WBYTES, p.w_row0 + n_tile * 128, pol_w);
       }
       pdl_wait();
-      for (int i = 0; i < pre; ++i)
-        tma_load_2d_hint(stages + i * Cfg::STAGE_BYTES, &tmX, &full_bar[i], (kb0 + i) * 128, p.x_row0, pol_x);
+      auto load_act = [&](int i, uint8_t* st, uint64_t* bar) {
+        tma_load_2d_hint(st, &tmX, bar, (kb0 + i) * 128, p.x_row0, pol_x);
+        const size_t off = (size_t)(kb0 + i) * sc.ld_a + p.x_row0;
+        bulk_load_1d(st + Cfg::SC_OFF, sc.a_scale + off, MPAD * 4, bar);
+        bulk_load_1d(st + Cfg::SC_OFF + MPAD * 4, sc.a_sum + off, MPAD * 4, bar);
+      };
+      for (int i = 0; i < pre; ++i) load_act(i, stages + i * Cfg::STAGE_BYTES, &full_bar[i]);
       for (int i = pre; i < kb_cnt; ++i) {
         const int s = i % Cfg::STAGES;
         const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_I8, 1)) break;
         uint8_t* st = stages + s * Cfg::STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        mbar_expect_tx(&full_bar[s], Cfg::TX_BYTES);
         tma_load_2d_hint(st + Cfg::B_BYTES, &tmW, &full_bar[s], (kb0 + i) * WBYTES, p.w_row0 + n_tile * 128, pol_w);
-        tma_load_2d_hint(st, &tmX, &full_bar[s], (kb0 + i) * 128, p.x_row0, pol_x);
+        load_act(i, st, &full_bar[s]);
       }
     }
     __syncwarp();
@@ -131,20 +146,20 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
   } else if (warp == 1) {
     if (elect_one()) {
       for (int i = 0; i < kb_cnt; ++i) {
-        const int s = i % Cfg::STAGES, b = i & 1;
-        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = ((uint32_t)i >> 1) & 1u;
+        const int s = i % Cfg::STAGES, b = i % Cfg::NBUF, d = i & 1;
+        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = (uint32_t)(i / Cfg::NBUF) & 1u, dph = ((uint32_t)i >> 1) & 1u;
         if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_I8, 2)) break;
-        if (WK == WK_INT4G && !mbar_wait(&dq_full[b], bph, dead, KID_GEMM_I8, 5)) break;
+        if (WK == WK_INT4G && !mbar_wait(&dq_full[d], dph, dead, KID_GEMM_I8, 5)) break;
         if (!mbar_wait(&tm_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 3)) break;
         tc_fence_after_sync();
         const uint32_t x_addr = smem_u32(stages + s * Cfg::STAGE_BYTES);
-        const uint32_t w_addr = WK == WK_INT4G ? smem_u32(dq + b * Cfg::A_BYTES) : x_addr + Cfg::B_BYTES;
+        const uint32_t w_addr = WK == WK_INT4G ? smem_u32(dq + d * Cfg::A_BYTES) : x_addr + Cfg::B_BYTES;
         const uint64_t da = make_smem_desc(w_addr, 16, 1024, SWZ_128B);
         const uint64_t db = make_smem_desc(x_addr, 16, 1024, SWZ_128B);
 #pragma unroll
         for (int k = 0; k < 4; ++k) umma_i8(tmem_base + b * MPAD, da + 2 * k, db + 2 * k, p.idesc, k != 0 ? 1u : 0u);
         umma_commit(&empty_bar[s]);
-        if (WK == WK_INT4G) umma_commit(&dq_empty[b]);
+        if (WK == WK_INT4G) umma_commit(&dq_empty[d]);
         umma_commit(&tm_full[b]);
       }
     }
@@ -154,6 +169,7 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
     const int n_local = q * 32 + lane;
     const int tid = threadIdx.x - 64;                    // 0..127 among the four promotion warps
     float acc[MPAD];
+    float tsum = 0.f;                                    // int8: T[m] of token m = tid over this CTA's k range
 #pragma unroll
     for (int j = 0; j < MPAD; ++j) acc[j] = 0.f;
     pdl_wait();
@@ -191,22 +207,25 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
       }
       fence_proxy_async_smem();
       mbar_arrive(&dq_full[b]);
-      mbar_arrive(&empty_bar[s]);
     };
 
     if (WK == WK_INT4G && kb_cnt > 0) unpack(0);
     for (int i = 0; i < kb_cnt; ++i) {
       if (WK == WK_INT4G && i + 1 < kb_cnt) unpack(i + 1);
-      const int b = i & 1;
-      if (!mbar_wait(&tm_full[b], ((uint32_t)i >> 1) & 1u, dead, KID_GEMM_I8, 4)) break;
-      tc_fence_after_sync();
-      float wa = 1.f, wb = -zrow;
-      if (WK == WK_INT4G && n_ok) {
+      const int b = i % Cfg::NBUF, s = i % Cfg::STAGES;
+      float wa = 1.f, wb = 0.f;
+      if (WK == WK_INT4G && n_ok) {                 // issued before the wait: the latency overlaps the MMA of this block
         wa = __ldg(sc.w_scale + (size_t)n_glob * p.kb_total + kb0 + i);
         wb = __ldg(sc.w_zero + (size_t)n_glob * p.kb_total + kb0 + i);
       }
-      const float4* asp = reinterpret_cast<const float4*>(sc.a_scale + (size_t)(kb0 + i) * sc.ld_a + p.x_row0);
-      const float4* xsp = reinterpret_cast<const float4*>(sc.a_sum + (size_t)(kb0 + i) * sc.ld_a + p.x_row0);
+      // the scale rows are written by the bulk copies that complete on full_bar: observe it in this thread too
+      if (WK == WK_INT8 && !mbar_wait(&full_bar[s], (uint32_t)(i / Cfg::STAGES) & 1u, dead, KID_GEMM_I8, 8)) break;
+      if (!mbar_wait(&tm_full[b], (uint32_t)(i / Cfg::NBUF) & 1u, dead, KID_GEMM_I8, 4)) break;
+      tc_fence_after_sync();
+      const float4* asp = reinterpret_cast<const float4*>(stages + s * Cfg::STAGE_BYTES + Cfg::SC_OFF);      // same address in every lane
+      const float4* xsp = asp + MPAD / 4;
+      if (WK == WK_INT8 && tid < MPAD)
+        tsum = fmaf(reinterpret_cast<const float*>(xsp)[tid], reinterpret_cast<const float*>(asp)[tid], tsum);
 #pragma unroll
       for (int c0 = 0; c0 < MPAD; c0 += CH) {
         uint32_t r[32];
@@ -215,21 +234,34 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < CH; j += 4) {
-          const float4 a4 = __ldg(asp + ((c0 + j) >> 2));
-          const float4 x4 = __ldg(xsp + ((c0 + j) >> 2));
-          acc[c0 + j + 0] = fmaf(fmaf(__int2float_rn((int)r[j + 0]), wa, wb * x4.x), a4.x, acc[c0 + j + 0]);
-          acc[c0 + j + 1] = fmaf(fmaf(__int2float_rn((int)r[j + 1]), wa, wb * x4.y), a4.y, acc[c0 + j + 1]);
-          acc[c0 + j + 2] = fmaf(fmaf(__int2float_rn((int)r[j + 2]), wa, wb * x4.z), a4.z, acc[c0 + j + 2]);
-          acc[c0 + j + 3] = fmaf(fmaf(__int2float_rn((int)r[j + 3]), wa, wb * x4.w), a4.w, acc[c0 + j + 3]);
+          const float4 a4 = asp[(c0 + j) >> 2];
+          if (WK == WK_INT8) {
+            acc[c0 + j + 0] = fmaf(sum_to_float(r[j + 0]), a4.x, acc[c0 + j + 0]);
+            acc[c0 + j + 1] = fmaf(sum_to_float(r[j + 1]), a4.y, acc[c0 + j + 1]);
+            acc[c0 + j + 2] = fmaf(sum_to_float(r[j + 2]), a4.z, acc[c0 + j + 2]);
+            acc[c0 + j + 3] = fmaf(sum_to_float(r[j + 3]), a4.w, acc[c0 + j + 3]);
+          } else {
+            const float4 x4 = xsp[(c0 + j) >> 2];
+            acc[c0 + j + 0] = fmaf(fmaf(sum_to_float(r[j + 0]), wa, wb * x4.x), a4.x, acc[c0 + j + 0]);
+            acc[c0 + j + 1] = fmaf(fmaf(sum_to_float(r[j + 1]), wa, wb * x4.y), a4.y, acc[c0 + j + 1]);
+            acc[c0 + j + 2] = fmaf(fmaf(sum_to_float(r[j + 2]), wa, wb * x4.z), a4.z, acc[c0 + j + 2]);
+            acc[c0 + j + 3] = fmaf(fmaf(sum_to_float(r[j + 3]), wa, wb * x4.w), a4.w, acc[c0 + j + 3]);
+          }
         }
       }
       tc_fence_before_sync();
       mbar_arrive(&tm_empty[b]);
+      mbar_arrive(&empty_bar[s]);
     }
     float* P = reinterpret_cast<float*>(smem);
+    float* Tsm = reinterpret_cast<float*>(smem + Cfg::BODY_BYTES + 512);
+    if (WK == WK_INT8 && tid < MPAD) Tsm[tid] = tsum;
     asm volatile("bar.sync 1, 128;\n" ::: "memory");
 #pragma unroll
-    for (int j = 0; j < MPAD; ++j) P[j * 128 + n_local] = n_ok ? acc[j] * srow : 0.f;
+    for (int j = 0; j < MPAD; ++j) {
+      const float v = WK == WK_INT8 ? fmaf(-zrow, Tsm[j], acc[j]) : acc[j];
+      P[j * 128 + n_local] = n_ok ? v * srow : 0.f;
+    }
   }
   tc_fence_before_sync();
   cluster_sync_all();

@@ -31,6 +31,7 @@ struct QuantParams {
   const float* zero;      // int8: [N]
   int group_k;            // int4g: k elements per group (multiple of 64); fp8: 128
   int groups;             // int4g: groups per row; fp8: scale columns
+  uint32_t xor_mask;      // int8: 0x80808080 when the bytes are stored as q - 128 (operand form of the integer path), else 0
 };
 
 // OCC: CTAs per SM the shared-memory budget is sized for (2 doubles the dequant warps working per SM)
@@ -211,8 +212,9 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
             const __half2 sub = __float2half2_rn(1024.f + z);
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-              o[2 * j] = out16<BF16>(u8x2_to_h2(ws[j] & 0xFFu, (ws[j] >> 8) & 0xFFu, sub));
-              o[2 * j + 1] = out16<BF16>(u8x2_to_h2((ws[j] >> 16) & 0xFFu, ws[j] >> 24, sub));
+              const uint32_t w = ws[j] ^ qp.xor_mask;
+              o[2 * j] = out16<BF16>(u8x2_to_h2(w & 0xFFu, (w >> 8) & 0xFFu, sub));
+              o[2 * j + 1] = out16<BF16>(u8x2_to_h2((w >> 16) & 0xFFu, w >> 24, sub));
             }
           } else if (BF16) {
             // e4m3 -> bf16 by bit placement: sign to bit 15, the 7 exponent+mantissa bits to bits 10..4; the value comes out
@@ -344,6 +346,7 @@ static cudaError_t launch_quant(const CUtensorMap& tmW, const CUtensorMap& tmX, 
 
 // qmode: 1 = int8 (Wq uint8 [N,K], scale [N], zero [N]), 2 = int4g (Wq uint8 [N,K/2], scale = float2 (scale,min) [groups,N]),
 // 3 = fp8 block 128 (Wq e4m3 [N,K], scale [ceil(N/128), ceil(K/128)]).  X dtype: 0 = fp16, 1 = bf16.  M <= 256.
+// int8 with group_k < 0: the bytes hold q - 128 (two's complement), zero still refers to q.
 extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, const float* zero, void* out, const void* bias,
                              const void* residual, int M, int N, int K, int ldx, int ld_out, int ld_res, int dtype, int qmode,
                              int group_k, int flags, int nsplit, void* stream_) {
@@ -363,6 +366,7 @@ extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, 
   qp.scale = scale; qp.zero = zero;
   qp.group_k = qmode == Q_INT4G ? group_k : 128;
   qp.groups = qmode == Q_INT4G ? K / group_k : (K + 127) / 128;
+  qp.xor_mask = (qmode == Q_INT8 && group_k < 0) ? 0x80808080u : 0u;      // int8 with group_k < 0: bytes hold q - 128
   const bool bf16 = dtype == 1;
   const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   static int sm_count = 0;
@@ -451,6 +455,7 @@ extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const f
   qp.scale = scale; qp.zero = zero;
   qp.group_k = qmode == Q_INT4G ? group_k : 128;
   qp.groups = qmode == Q_INT4G ? K / group_k : (K + 127) / 128;
+  qp.xor_mask = (qmode == Q_INT8 && group_k < 0) ? 0x80808080u : 0u;      // int8 with group_k < 0: bytes hold q - 128
   QuantGroupInfo gi;
   gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
   gi.scale_stride_e = qmode == Q_INT8 ? N : qmode == Q_INT4G ? (long long)qp.groups * N * 2 : (long long)(N / 128) * qp.groups;

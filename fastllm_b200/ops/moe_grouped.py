@@ -129,8 +129,6 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
     dt = dtype_code(x.dtype)
     fp8_native = st.kind == "fp8" and QG.FP8_NATIVE and H % 128 == 0 and st.inter % 128 == 0
     int_a8 = QG.INT_A8 and (st.kind == "int8" or (st.kind == "int4g" and st.group == 128)) and H % 128 == 0 and st.inter % 128 == 0
-    if st.signed and not int_a8:
-        return None
     if int_a8 and st.a8 is None:
         _prepare_a8(st, experts)
     act = torch.empty((rows_cap, st.inter), device=dev, dtype=x.dtype)
@@ -174,11 +172,12 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
                    "fb_gemm_i8(down)")
     else:
         qm = {"int8": 1, "int4g": 2, "fp8": 3}[st.kind]
+        grp = -1 if st.signed else (st.group or 0)           # -1: int8 bytes hold q - 128
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(xs), _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(st.gu_zero), _ptr(act), _ptr(counts),
-                                                 _ptr(offsets), rows_cap, E, 2 * st.inter, H, st.inter, max_rows, dt, qm, st.group or 0,
+                                                 _ptr(offsets), rows_cap, E, 2 * st.inter, H, st.inter, max_rows, dt, qm, grp,
                                                  GEMM_SWIGLU, s), "fb_moe_grouped_gemm_quant(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(act), _ptr(st.down), _ptr(st.dn_scale), _ptr(st.dn_zero), _ptr(ys), _ptr(counts),
-                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, max_rows, dt, qm, st.group or 0, 0, s),
+                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, max_rows, dt, qm, grp, 0, s),
                    "fb_moe_grouped_gemm_quant(down)")
     if not combine:
         return ys, pos, wts

@@ -186,6 +186,4 @@ class LinearWeight:
                 return y
             if self.kind == "fp8" and quant_gemm.FP8_NATIVE:
                 x = fake_quant_act_fp8(x)
-            elif quant_gemm.uses_int_a8(self):
-                x = fake_quant_act_i8(x)
         return B.linear(x, self.dequant(x.dtype), self.bias, residual, swiglu, self.interleaved, out_f32)

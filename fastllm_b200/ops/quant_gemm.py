@@ -137,11 +137,7 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
         return None
     if swiglu and (not lw.interleaved or N % 128 != 0):
         return None
-    a8 = uses_int_a8(lw)
-    if a8 and (M > INT_A8_MAX_M or x2.stride(0) % 4 != 0):
-        return None                       # large batches: de-quantise + 16-bit GEMM on the same int8-rounded activations
-    if lw.kind == "int8" and lw.signed and not a8:
-        return None
+    a8 = uses_int_a8(lw) and M <= INT_A8_MAX_M and x2.stride(0) % 4 == 0
     scale, zero = (None, None) if a8 else _kernel_tensors(lw)[:2]
     n_out = N // 2 if swiglu else N
     out = torch.empty((M, n_out), device=x.device, dtype=torch.float32 if out_f32 else x.dtype)
@@ -162,11 +158,12 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
 
         x2 = fake_quant_act_fp8(x2)          # same activation rounding as the e4m3 x e4m3 path used for small batches
     lib = _lib.kernels()
+    group = -1 if (lw.kind == "int8" and lw.signed) else (lw.group or 0)      # -1: int8 bytes hold q - 128
     for m0 in range(0, M, 256):
         m1 = min(M, m0 + 256)
         rc = lib.fb_gemm_quant(_ptr(x2[m0:m1]), _ptr(lw.w), _ptr(scale), _ptr(zero), _ptr(out[m0:m1]), _ptr(bias),
                                _ptr(res2[m0:m1]) if res2 is not None else _ptr(None), m1 - m0, N, K, x2.stride(0), out.stride(0),
-                               res2.stride(0) if res2 is not None else 0, dtype_code(x.dtype), _QMODE[lw.kind], lw.group or 0, flags, 0,
+                               res2.stride(0) if res2 is not None else 0, dtype_code(x.dtype), _QMODE[lw.kind], group, flags, 0,
                                _stream())
         _lib.check(rc, "fb_gemm_quant")
     return out.reshape(*lead, n_out)

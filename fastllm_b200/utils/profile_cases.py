@@ -108,6 +108,10 @@ def moe_grouped(tokens=128, experts=128, topk=8, hidden=2048, inter=768, kind="f
 CASES = {
     "gemm_quant_fp8": lambda: gemm_quant("fp8"),
     "gemm_quant_int4g": lambda: gemm_quant("int4g128"),
+    "gemm_quant_fp8_m16": lambda: gemm_quant("fp8", m=16),
+    "gemm_quant_int8": lambda: gemm_quant("int8"),
+    "gemm_quant_int8_m16": lambda: gemm_quant("int8", m=16),
+    "gemm_quant_int4g_m16": lambda: gemm_quant("int4g128", m=16),
     "mla_decode": mla_decode,
     "attn_prefill": attn_prefill,
     "moe_grouped_fp8": moe_grouped,

@@ -502,7 +502,11 @@ def test_gemm_int_a8(kind, M, N, K):
     wdq = lw.dequant(torch.float32)
     x = torch.randn(M, K, device=DEV).to(dt)
     assert QG.uses_int_a8(lw)
-    out = lw(x)
+    old, QG.INT_A8_MAX_M = QG.INT_A8_MAX_M, 512          # also the 128-row chunk loop
+    try:
+        out = lw(x)
+    finally:
+        QG.INT_A8_MAX_M = old
     _lib.check_device_errors()
     ref = _i8_act(x) @ wdq.t()
     _close(out.float().cpu(), ref.cpu(), 2e-2, 1e-2, f"gemm_i8 {kind} {M}x{N}x{K}")
@@ -554,8 +558,8 @@ def test_moe_grouped_int_a8(kind):
         x = torch.randn(T, cfg.hidden_size, device=DEV).bfloat16()
         idx, w = MOE.route_topk(torch.randn(T, cfg.num_experts, device=DEV), None, 2, 0, True)
         y8 = MOE.moe_forward(x, idx, w, ex)
-        assert ex.stacked.a8 is not None
-        QG.INT_A8 = False
+        assert ex.stacked.a8 is not None and (kind != "int8" or ex.stacked.signed)
+        QG.INT_A8 = False              # the 16-bit-activation kernels on the same (now q - 128) bytes
         try:
             y16 = MOE.moe_forward(x, idx, w, ex)
         finally:
