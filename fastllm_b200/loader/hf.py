@@ -30,6 +30,39 @@ def dequant_fp8_block(w: torch.Tensor, scale_inv: torch.Tensor, dtype=torch.bflo
     return (w.float() * s).to(dtype)
 
 
+_FP4_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0)       # e2m1
+
+
+def _fp4_unpack(packed: torch.Tensor) -> torch.Tensor:
+    """uint8 [..., n] -> fp32 [..., 2n]: the low nibble is the even element, the high nibble the odd one."""
+    lut = torch.tensor(_FP4_VALUES, dtype=torch.float32, device=packed.device)
+    lo, hi = (packed & 0x0F).long(), (packed >> 4).long()
+    return torch.stack([lut[lo], lut[hi]], dim=-1).reshape(*packed.shape[:-1], packed.shape[-1] * 2)
+
+
+def dequant_mxfp4(blocks: torch.Tensor, scales: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
+    """MXFP4 (gpt-oss checkpoints): ``blocks`` uint8 [..., rows, K/32, 16] with two e2m1 values per byte, ``scales`` uint8
+    e8m0 [..., rows, K/32] (value 2^(s - 127)) -> dense [..., rows, K].  Reference: the MXFP4 expert path of
+    src/models/gpt_oss.cpp and src/devices/cuda/moe/fastllm-moe-vllm-marlin.cu:293-331 (repacks the same format for Marlin)."""
+    vals = _fp4_unpack(blocks)                                             # [..., rows, K/32, 32]
+    sc = torch.exp2(scales.float() - 127.0)[..., None]
+    return (vals * sc).reshape(*blocks.shape[:-2], blocks.shape[-2] * 32).to(dtype)
+
+
+def dequant_nvfp4(w: torch.Tensor, block_scale: torch.Tensor, global_scale: torch.Tensor | None, dtype=torch.bfloat16) -> torch.Tensor:
+    """NVFP4: ``w`` uint8 [N, K/2] (e2m1 pairs), ``block_scale`` e4m3 (or e8m0 as uint8) [N, K/block] with block 16 or 32,
+    optional fp32 ``global_scale`` -> dense [N, K].  Reference formats NVFP4_BLOCK_16 / _E8M0 / NVFP4_BLOCK_32_E8M0
+    (include/fastllm.h:308-339; de-quantisers src/devices/cuda/linear/fastllm-linear-fp8.cu:2375-2690)."""
+    N, K = w.shape[0], w.shape[1] * 2
+    vals = _fp4_unpack(w)
+    blk = K // block_scale.shape[1]
+    sc = torch.exp2(block_scale.float() - 127.0) if block_scale.dtype == torch.uint8 else block_scale.float()
+    out = vals.reshape(N, K // blk, blk) * sc[..., None]
+    if global_scale is not None:
+        out = out * global_scale.float().reshape(-1)[0]
+    return out.reshape(N, K).to(dtype)
+
+
 def dequant_awq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor, dtype=torch.bfloat16) -> torch.Tensor:
     """AWQ GEMM layout: qweight int32 [K, N/8], qzeros int32 [K/g, N/8], scales fp16 [K/g, N] -> dense [N, K]."""
     K, n8 = qweight.shape
@@ -115,6 +148,9 @@ class HFCheckpoint:
                         return (w.float() * sc.float().item()).to(self.dtype)
                     return dequant_fp8_block(w, sc, self.dtype)
                 return w.float().to(self.dtype)
+            if w.dtype == torch.uint8 and self.has(prefix + ".weight_scale"):          # NVFP4 (two e2m1 values per byte)
+                g2 = self.raw(prefix + ".weight_scale_2") if self.has(prefix + ".weight_scale_2") else None
+                return dequant_nvfp4(w, self.raw(prefix + ".weight_scale"), g2, self.dtype)
             return w
         if self.has(prefix + ".qweight"):
             return dequant_awq(self.raw(prefix + ".qweight"), self.raw(prefix + ".qzeros"), self.raw(prefix + ".scales"), self.dtype)
@@ -154,7 +190,13 @@ class HFCheckpoint:
             if not n.startswith(prefix):
                 continue
             base, _, leaf = n.rpartition(".")
-            if leaf in ("weight_scale_inv", "weight_scale", "qzeros", "scales", "g_idx"):
+            if leaf in ("weight_scale_inv", "weight_scale", "weight_scale_2", "input_scale", "qzeros", "scales", "g_idx"):
+                continue
+            if leaf.endswith("_scales") and self.has(n[:-7] + "_blocks"):
+                continue
+            if leaf.endswith("_blocks") and self.has(n[:-7] + "_scales"):
+                # MXFP4 stacked experts [E, rows, K/32, 16] -> the 16-bit checkpoint layout [E, K, rows]
+                out[n[:-7]] = dequant_mxfp4(self.raw(n), self.raw(n[:-7] + "_scales"), self.dtype).transpose(-1, -2).contiguous()
                 continue
             if leaf in ("weight", "qweight"):
                 if base in done:

@@ -35,7 +35,8 @@ FP8_NATIVE = __import__("os").environ.get("FB_FP8_W8A16", "0") != "1"
 INT_A8 = __import__("os").environ.get("FB_INT_A16", "0") != "1"
 
 
-INT_A8_MAX_M = 512      # above this the weights are de-quantised once and the plain 16-bit GEMM runs
+# rows up to which the integer path is the faster one (measured on B200); above it the 16-bit-activation kernels run
+INT_A8_MAX_M = {"int8": 128, "int4g": 64}
 
 
 def uses_int_a8(lw) -> bool:
@@ -137,7 +138,7 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
         return None
     if swiglu and (not lw.interleaved or N % 128 != 0):
         return None
-    a8 = uses_int_a8(lw) and M <= INT_A8_MAX_M and x2.stride(0) % 4 == 0
+    a8 = uses_int_a8(lw) and M <= INT_A8_MAX_M[lw.kind] and x2.stride(0) % 4 == 0
     scale, zero = (None, None) if a8 else _kernel_tensors(lw)[:2]
     n_out = N // 2 if swiglu else N
     out = torch.empty((M, n_out), device=x.device, dtype=torch.float32 if out_f32 else x.dtype)

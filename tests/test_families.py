@@ -226,3 +226,83 @@ def test_qwen_v1_layout(tmp_path):
     _save_renamed(ref, cfgd, rename, d, merge)
     got = _last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), prompt)
     assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+
+
+def _to_fp4(x):
+    """Nearest e2m1 code (0..15) of every element of ``x`` (already divided by its block scale)."""
+    lut = torch.tensor(hf._FP4_VALUES)
+    return (x[..., None] - lut).abs().argmin(-1).to(torch.uint8)
+
+
+def test_gpt_oss_mxfp4_checkpoint(tmp_path):
+    """gpt-oss as published: experts stored as MXFP4 ``*_blocks`` / ``*_scales``.  The loader must give the same logits as the
+    16-bit checkpoint that holds the de-quantised values."""
+    import json
+    import os
+
+    from fastllm_b200.loader.safetensors import save_file
+
+    ref = _tiny("gpt_oss", **_C, num_local_experts=4, num_experts_per_tok=2, sliding_window=16)
+    sd = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    packed, dense = {}, {}
+    for k, v in sd.items():
+        if k.endswith("mlp.experts.gate_up_proj") or k.endswith("mlp.experts.down_proj"):
+            w = v.transpose(1, 2).contiguous()                                 # [E, rows, K]
+            E, R, K = w.shape
+            wb = w.reshape(E, R, K // 32, 32)
+            e = torch.ceil(torch.log2(wb.abs().amax(-1).clamp(min=1e-20) / 6.0)).clamp(-127, 127)
+            codes = _to_fp4(wb / torch.exp2(e)[..., None])                     # [E, R, K/32, 32]
+            packed[k + "_blocks"] = (codes[..., 0::2] | (codes[..., 1::2] << 4)).contiguous()
+            packed[k + "_scales"] = (e + 127).to(torch.uint8).contiguous()
+            deq = (torch.tensor(hf._FP4_VALUES)[codes.long()] * torch.exp2(e)[..., None]).reshape(E, R, K)
+            dense[k] = deq.transpose(1, 2).contiguous()
+            assert torch.equal(hf.dequant_mxfp4(packed[k + "_blocks"], packed[k + "_scales"], torch.float32), deq)
+        else:
+            packed[k] = v.contiguous()
+            dense[k] = v.contiguous()
+    logits = []
+    for name, tensors in (("mx", packed), ("dense", dense)):
+        d = str(tmp_path / name)
+        os.makedirs(d)
+        save_file(tensors, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(ref.config.to_dict(), f)
+        logits.append(_last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), list(range(5, 60, 3))))
+    assert torch.allclose(logits[0], logits[1], atol=1e-5)
+
+
+def test_nvfp4_checkpoint(tmp_path):
+    """NVFP4 linear weights (uint8 pairs + e4m3 block-16 scales + fp32 global scale) load as their de-quantised values."""
+    import json
+    import os
+
+    from fastllm_b200.loader.safetensors import save_file
+
+    ref = _tiny("llama", **_C)
+    sd = {k: v.detach().clone() for k, v in ref.state_dict().items()}
+    packed, dense = {}, {}
+    for k, v in sd.items():
+        if k.endswith("_proj.weight"):
+            N, K = v.shape
+            g = v.abs().max() / (6.0 * 448.0)
+            wb = v.reshape(N, K // 16, 16)
+            bs = (wb.abs().amax(-1) / 6.0 / g).to(torch.float8_e4m3fn)
+            codes = _to_fp4(wb / (bs.float() * g).clamp(min=1e-20)[..., None]).reshape(N, K)
+            base = k[:-len(".weight")]
+            packed[k] = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+            packed[base + ".weight_scale"] = bs.contiguous()
+            packed[base + ".weight_scale_2"] = g.reshape(1).float()
+            packed[base + ".input_scale"] = torch.ones(1)
+            dense[k] = (torch.tensor(hf._FP4_VALUES)[codes.long()].reshape(N, K // 16, 16) * (bs.float() * g)[..., None]).reshape(N, K)
+        else:
+            packed[k] = v.contiguous()
+            dense[k] = v.contiguous()
+    logits = []
+    for name, tensors in (("nv", packed), ("dense", dense)):
+        d = str(tmp_path / name)
+        os.makedirs(d)
+        save_file(tensors, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+        with open(os.path.join(d, "config.json"), "w") as f:
+            json.dump(ref.config.to_dict(), f)
+        logits.append(_last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), list(range(5, 60, 3))))
+    assert torch.allclose(logits[0], logits[1], atol=1e-4)

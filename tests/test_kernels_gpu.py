@@ -502,7 +502,7 @@ def test_gemm_int_a8(kind, M, N, K):
     wdq = lw.dequant(torch.float32)
     x = torch.randn(M, K, device=DEV).to(dt)
     assert QG.uses_int_a8(lw)
-    old, QG.INT_A8_MAX_M = QG.INT_A8_MAX_M, 512          # also the 128-row chunk loop
+    old, QG.INT_A8_MAX_M = QG.INT_A8_MAX_M, {"int8": 512, "int4g": 512}          # also the 128-row chunk loop
     try:
         out = lw(x)
     finally:
