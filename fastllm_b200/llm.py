@@ -290,13 +290,33 @@ class model:
             pass
         return len(ids)
 
+    def load_adapter(self, name: str, adapter_dir: str) -> int:
+        """Attach a PEFT LoRA adapter folder under ``name`` for run-time switching (``fastllm_b200/lora.py``)."""
+        from . import lora
+
+        n = lora.load_adapter(self.engine.model, name, adapter_dir)
+        self._adapters = getattr(self, "_adapters", set()) | {name}
+        return n
+
+    def _switch_adapter(self, name):
+        from . import lora
+
+        lora.set_adapter(name)
+        runner = self.engine.runner
+        for slot in runner.slots.values():          # the captured decode graphs hold the previous operator sequence
+            slot.graph = None
+
     def set_adapter(self, name: str):
-        """LoRA adapters are merged into the weights at load time (``llm.model(path, lora=adapter_dir)``); switching adapters
-        on a loaded model is not supported."""
-        raise NotImplementedError("adapters are merged at load: construct llm.model(path, lora=adapter_dir)")
+        """Run with the adapter ``name`` (loaded by ``load_adapter``) from the next request on.
+        Reference: tools/fastllm_pytools/llm.py:2709."""
+        if name not in getattr(self, "_adapters", set()):
+            raise KeyError(f"adapter '{name}' is not loaded: call load_adapter(name, adapter_dir) first "
+                           f"(llm.model(path, lora=dir) merges an adapter at load instead)")
+        self._switch_adapter(name)
 
     def disable_adapter(self):
-        raise NotImplementedError("adapters are merged at load: construct llm.model(path) without lora to run the base model")
+        """Back to the base weights.  Reference: tools/fastllm_pytools/llm.py:2712."""
+        self._switch_adapter(None)
 
     def get_response_statistics(self, handle: int) -> dict:
         return self.engine.stats(handle)

@@ -429,6 +429,10 @@ class DecoderModel:
 
     def _native_cpu(self):
         """The whole-model native CPU runner for this model, or None when the architecture is outside its coverage."""
+        from ..ops.quant import LinearWeight
+
+        if LinearWeight.active_adapter is not None:
+            return None                       # run-time adapters are applied by the per-operator path
         if getattr(self, "_cpu_runner", None) is None:
             from . import cpu_native
 

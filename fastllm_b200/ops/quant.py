@@ -121,7 +121,8 @@ def normalize_wdtype(name: str | None) -> tuple[str, int]:
 class LinearWeight:
     """Weight (+ optional bias) of one linear layer in one of the storage formats above."""
 
-    __slots__ = ("kind", "w", "scale", "zero", "bias", "group", "n", "k", "interleaved", "dtype", "_dq", "signed", "_a8")
+    __slots__ = ("kind", "w", "scale", "zero", "bias", "group", "n", "k", "interleaved", "dtype", "_dq", "signed", "_a8", "adapters")
+    active_adapter: str | None = None       # name of the run-time low-rank adapter applied by every weight that carries it
 
     def __init__(self, kind, w, scale=None, zero=None, bias=None, group=0, dtype=torch.bfloat16, interleaved=False):
         self.kind, self.w, self.scale, self.zero, self.bias, self.group = kind, w, scale, zero, bias, group
@@ -131,6 +132,7 @@ class LinearWeight:
         self.interleaved = interleaved      # gate/up rows interleaved per 128-row tile for the SwiGLU epilogue
         self._dq = None
         self._a8 = None
+        self.adapters = None                # name -> (A [r, K], B [N, r]) run-time low-rank deltas (fastllm_b200/lora.py)
         self.signed = False                 # int8 only: bytes hold q - 128 (the integer tensor-core path's operand form)
 
     @staticmethod
@@ -170,6 +172,25 @@ class LinearWeight:
         return n
 
     def __call__(self, x, residual=None, swiglu=False, out_f32=False):
+        if LinearWeight.active_adapter is not None and self.adapters and LinearWeight.active_adapter in self.adapters:
+            # y = W x + B (A x): the delta goes in before the activation, so the fused epilogues are applied afterwards
+            a, b = self.adapters[LinearWeight.active_adapter]
+            y = self._base(x, None, False, False)
+            y = y + B.linear(B.linear(x, a.to(x.dtype)), b.to(x.dtype))
+            if swiglu:
+                t = y.float()
+                if self.interleaved:
+                    t = t.reshape(*t.shape[:-1], t.shape[-1] // 128, 2, 64)
+                    g, u = t[..., 0, :], t[..., 1, :]
+                else:
+                    g, u = t.chunk(2, dim=-1)
+                y = (torch.nn.functional.silu(g) * u).reshape(*y.shape[:-1], y.shape[-1] // 2).to(y.dtype)
+            if residual is not None:
+                y = y + residual
+            return y.float() if out_f32 else y
+        return self._base(x, residual, swiglu, out_f32)
+
+    def _base(self, x, residual=None, swiglu=False, out_f32=False):
         if self.kind == "dense":
             w = self.w
             if w.dtype != x.dtype:

@@ -159,3 +159,51 @@ def test_add_cache_populates_prefix_cache(tmp_path):
         pass
     assert req.stats.as_dict()["cached_tokens"] >= 256
     m.release_memory()
+
+
+def test_llm_model_adapter_switching(tmp_path):
+    import pytest
+
+    """``load_adapter`` / ``set_adapter`` / ``disable_adapter`` on a loaded model change (and restore) what it generates."""
+    import json
+
+    from baseline import synth
+    from fastllm_b200 import llm
+    from fastllm_b200.loader.safetensors import save_file
+
+    d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.float32, std=0.05)
+    llm.set_device_map("cpu")
+    m = llm.model(d, device="cpu")
+    c = m.engine.model.cfg
+    torch.manual_seed(2)
+    t = {}
+    for i in range(c.num_layers):
+        t[f"base_model.model.model.layers.{i}.mlp.down_proj.lora_A.weight"] = torch.randn(4, c.intermediate_size) * 0.3
+        t[f"base_model.model.model.layers.{i}.mlp.down_proj.lora_B.weight"] = torch.randn(c.hidden_size, 4) * 0.3
+    ad = tmp_path / "ad"
+    ad.mkdir()
+    (ad / "adapter_config.json").write_text(json.dumps({"r": 4, "lora_alpha": 8}))
+    save_file(t, ad / "adapter_model.safetensors")
+    prompt = list(range(5, 40))
+
+    def run():
+        h = m.launch_stream_response(prompt, max_length=6, do_sample=False)
+        out = []
+        while True:
+            tok = m.engine.fetch(h)
+            if tok < 0:
+                return out
+            out.append(tok)
+
+    base = run()
+    with pytest.raises(KeyError):
+        m.set_adapter("a")
+    assert m.load_adapter("a", str(ad)) == c.num_layers
+    try:
+        m.set_adapter("a")
+        tuned = run()
+        assert tuned != base
+    finally:
+        m.disable_adapter()
+    assert run() == base
+    m.release_memory()

@@ -118,6 +118,58 @@ def test_lora_adapter_is_merged_at_load(tmp_path):
     assert torch.equal(tuned.layers[0].attn.o.w, base.layers[0].attn.o.w)
 
 
+def test_runtime_adapter_matches_merged_and_switches(tmp_path):
+    """Run-time adapters on every projection kind (fused qkv, o, interleaved gate/up, down): same logits as the merged load,
+    and the base logits again after ``set_adapter(None)``."""
+    import json
+
+    from fastllm_b200 import lora
+    from fastllm_b200.engine import EngineConfig, LLMEngine
+    from fastllm_b200.loader.safetensors import save_file
+    from fastllm_b200.models.decoder import ForwardBatch
+
+    d = _write_hf(tmp_path, "tiny-llama")
+    base = hf.load_model(d, device="cpu", dtype=torch.float32)
+    c = base.cfg
+    torch.manual_seed(1)
+    r, alpha = 4, 8
+    shapes = {"self_attn.q_proj": (c.num_heads * c.head_dim, c.hidden_size), "self_attn.v_proj": (c.num_kv_heads * c.head_dim, c.hidden_size),
+              "self_attn.o_proj": (c.hidden_size, c.num_heads * c.head_dim), "mlp.gate_proj": (c.intermediate_size, c.hidden_size),
+              "mlp.up_proj": (c.intermediate_size, c.hidden_size), "mlp.down_proj": (c.hidden_size, c.intermediate_size)}
+    t = {}
+    for i in range(c.num_layers):
+        for nm, (n, k) in shapes.items():
+            t[f"base_model.model.model.layers.{i}.{nm}.lora_A.weight"] = torch.randn(r, k) * 0.1
+            t[f"base_model.model.model.layers.{i}.{nm}.lora_B.weight"] = torch.randn(n, r) * 0.1
+    ad = tmp_path / "adapter"
+    ad.mkdir()
+    (ad / "adapter_config.json").write_text(json.dumps({"r": r, "lora_alpha": alpha}))
+    save_file(t, ad / "adapter_model.safetensors")
+    merged = hf.load_model(d, device="cpu", dtype=torch.float32, lora=str(ad))
+
+    def logits(m):
+        prompt = list(range(3, 40, 2))
+        T = len(prompt)
+        eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=256), num_pages=4)
+        fb = ForwardBatch(ids=torch.tensor(prompt, dtype=torch.int32), positions=torch.arange(T, dtype=torch.int32),
+                          slots=torch.arange(T, dtype=torch.int32), page_table=torch.tensor([[0, 1]], dtype=torch.int32),
+                          kv_lens=torch.tensor([T], dtype=torch.int32), cu_q=torch.tensor([0, T], dtype=torch.int32),
+                          logit_rows=torch.tensor([T - 1]), cu_q_host=[0, T])
+        return m.forward(fb, eng.runner.kv.pools)[0].float()
+
+    want_base, want_tuned = logits(base), logits(merged)
+    assert (want_base - want_tuned).abs().max() > 1e-3
+    assert lora.load_adapter(base, "a", str(ad)) == 4 * c.num_layers
+    try:
+        lora.set_adapter("a")
+        assert torch.allclose(logits(base), want_tuned, atol=2e-4)
+        lora.set_adapter("other")                      # a name no weight carries: base behaviour
+        assert torch.allclose(logits(base), want_base, atol=1e-5)
+    finally:
+        lora.set_adapter(None)
+    assert torch.allclose(logits(base), want_base, atol=1e-5)
+
+
 def test_split_layers_by_device_map():
     from fastllm_b200.loader.shard import split_layers_by_map
 
