@@ -94,7 +94,7 @@ class KVCache:
         self.num_pages = num_pages
         self.page_len = page_len
         ks, vs = model.kv_cache_shape(num_pages)
-        dev, dt = model.device, model.dtype
+        dev, dt = model.device, (getattr(model, "kv_dtype", None) or model.dtype)
         self.pools = []
         staged = getattr(model, "layer_devices", None)
         for i in range(model.cfg.num_layers):

@@ -147,6 +147,8 @@ class model:
                                                     moe_device_layers=int(_settings.get("moe_device_layers", -1) or -1),
                                                     dtype_config=dtype_config or None, lora=lora or None,
                                                     device_map=_settings["device_map"] if isinstance(_settings.get("device_map"), dict) else None)
+        if kv_cache_dtype not in ("auto", "", None):
+            self.torch_model.set_kv_cache_dtype(kv_cache_dtype)
         cfg = self.torch_model.cfg
         eos = set(cfg.eos_token_ids) | set(self.tokenizer.eos_ids())
         for t in eos_token or []:

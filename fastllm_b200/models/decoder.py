@@ -158,7 +158,28 @@ class DecoderModel:
     def kv_bytes_per_page(self) -> int:
         ks, vs = self.kv_cache_shape(1)
         n = math.prod(ks) + (math.prod(vs) if vs else 0)
-        return n * self.cfg.num_layers * torch.finfo(self.dtype).bits // 8
+        return n * self.cfg.num_layers * torch.finfo(getattr(self, "kv_dtype", None) or self.dtype).bits // 8
+
+    def set_kv_cache_dtype(self, name: str | None) -> None:
+        """``fp8_e4m3``: keys and values are stored as unscaled e4m3 (half the cache bytes); attention then runs on the
+        general (gather + PyTorch) path, the tcgen05 attention kernels read 16-bit pages only.
+        Reference: basellm::SetKVCacheDataType (src/models/basellm.cpp:3567-3580), ``--kv_cache_dtype``."""
+        name = (name or "auto").lower()
+        if name in ("auto", ""):
+            return
+        table = {"fp8": torch.float8_e4m3fn, "fp8_e4m3": torch.float8_e4m3fn, "float8": torch.float8_e4m3fn,
+                 "float16": torch.float16, "half": torch.float16, "fp16": torch.float16, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+                 "float32": torch.float32, "fp32": torch.float32}
+        if name not in table:
+            raise ValueError("kv_cache_dtype should be float32, float16, bfloat16 or fp8_e4m3")
+        dt = table[name]
+        if dt == self.dtype:
+            return
+        if self.cfg.use_mla:
+            raise NotImplementedError("the MLA latent cache is kept in the activation dtype")
+        self.kv_dtype = dt
+        self.general_attn = True
+        self._cpu_runner = False              # the whole-model CPU runner owns fp32 pages
 
     # -----------------------------------------------------------------------------------------------
     def _attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual, next_ln):

@@ -207,3 +207,30 @@ def test_llm_model_adapter_switching(tmp_path):
         m.disable_adapter()
     assert run() == base
     m.release_memory()
+
+
+def test_fp8_kv_cache(tmp_path):
+    """``kv_cache_dtype="fp8_e4m3"``: e4m3 pages (half the bytes), generation close to the 16/32-bit cache."""
+    from baseline import synth
+    from fastllm_b200 import llm
+
+    d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.float32, std=0.05)
+    llm.set_device_map("cpu")
+    prompt = list(range(5, 150))
+    outs, logits = [], []
+    for kvd in ("auto", "fp8_e4m3"):
+        m = llm.model(d, device="cpu", kv_cache_dtype=kvd)
+        k_pool = m.engine.runner.kv.pools[0][0]
+        assert (k_pool.dtype == torch.float8_e4m3fn) == (kvd != "auto")
+        logits.append(torch.as_tensor(m.response_logits(prompt)).float())
+        h = m.launch_stream_response(prompt, max_length=4, do_sample=False)
+        toks = []
+        while True:
+            t = m.engine.fetch(h)
+            if t < 0:
+                break
+            toks.append(t)
+        outs.append(toks)
+        m.release_memory()
+    assert len(outs[1]) == 4
+    assert torch.nn.functional.cosine_similarity(logits[0].flatten(), logits[1].flatten(), dim=0) > 0.99
