@@ -235,6 +235,42 @@ __global__ void quant_act_fp8_kernel(const uint16_t* __restrict__ x, int ldx, ui
   if (lane == 0) scales[(size_t)kb * ld_a + m] = scale;
 }
 
+// Rounds activations to the values the 8-bit-activation GEMMs see (per token and 128-wide k block; INT8: round(x / s) * s with
+// s = amax / 127, else e4m3 with s = amax / 448) and writes them back as 16-bit numbers.  Batches too large for the small-M
+// 8-bit kernels run the 16-bit-activation kernels on these values, so a request gets the same numerics at every batch size.
+template <bool BF16, bool INT8>
+__global__ void round_act_kernel(const uint16_t* __restrict__ x, int ldx, uint16_t* __restrict__ out, int ldo, int M, int kb_total) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int wpb = blockDim.x >> 5;
+  const int gw = blockIdx.x * wpb + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int m = gw / kb_total, kb = gw - m * kb_total;
+  if (m >= M) return;
+  const uint2 v = *reinterpret_cast<const uint2*>(x + (size_t)m * ldx + kb * 128 + lane * 4);
+  const float2 a = unpack_16<BF16>(v.x), b = unpack_16<BF16>(v.y);
+  float amax = fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y)));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  float r0, r1, r2, r3;
+  if (INT8) {
+    const float scale = fmaxf(amax, 1e-12f) / 127.0f, inv = 1.0f / scale;
+    r0 = rintf(a.x * inv) * scale; r1 = rintf(a.y * inv) * scale; r2 = rintf(b.x * inv) * scale; r3 = rintf(b.y * inv) * scale;
+  } else {
+    const float scale = fmaxf(amax, 1e-12f) / 448.0f, inv = 1.0f / scale;
+    const uint32_t q = pack_e4m3x4(a.x * inv, a.y * inv, b.x * inv, b.y * inv);
+    uint32_t h01, h23;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h01) : "h"((uint16_t)(q & 0xFFFFu)));
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h23) : "h"((uint16_t)(q >> 16)));
+    const float2 f01 = __half22float2(*reinterpret_cast<const __half2*>(&h01)), f23 = __half22float2(*reinterpret_cast<const __half2*>(&h23));
+    r0 = f01.x * scale; r1 = f01.y * scale; r2 = f23.x * scale; r3 = f23.y * scale;
+  }
+  uint2 o;
+  o.x = pack_16<BF16>(r0, r1);
+  o.y = pack_16<BF16>(r2, r3);
+  *reinterpret_cast<uint2*>(out + (size_t)m * ldo + kb * 128 + lane * 4) = o;
+}
+
 // Gather for the grouped expert GEMM fused with the activation quantisation: row pos[pair] of the expert-sorted FP8 buffer
 // receives token pair / topk, quantised per 128-wide k block.  One CTA per (token, k) pair, one warp per k block.
 template <bool BF16>
@@ -275,6 +311,26 @@ extern "C" int fb_moe_gather_quant_fp8(const void* x, const int* pos, void* xq, 
     launch_k(moe_gather_quant_fp8_kernel<true>, dim3(T * topk), dim3(128), 0, s, 0, (const uint16_t*)x, pos, (uint8_t*)xq, scales, ld_a, topk, H);
   else
     launch_k(moe_gather_quant_fp8_kernel<false>, dim3(T * topk), dim3(128), 0, s, 0, (const uint16_t*)x, pos, (uint8_t*)xq, scales, ld_a, topk, H);
+  return (int)cudaGetLastError();
+}
+
+// mode 0: int8 grid, 1: e4m3 grid.  x, out: [M, K] 16-bit (row strides ldx, ldo elements, multiples of 4); K % 128 == 0.
+extern "C" int fb_round_act(const void* x, int ldx, void* out, int ldo, int M, int K, int dtype, int mode, void* stream) {
+  if (M <= 0) return 0;
+  if (K % 128 != 0 || ldx % 4 != 0 || ldo % 4 != 0 || (mode != 0 && mode != 1)) return -1;
+  const int kb_total = K / 128, wpb = 8;
+  const long long warps = (long long)M * kb_total;
+  const dim3 grid((unsigned)((warps + wpb - 1) / wpb)), block(wpb * 32);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  auto xi = (const uint16_t*)x;
+  auto xo = (uint16_t*)out;
+  if (dtype == 1) {
+    if (mode == 0) launch_k(round_act_kernel<true, true>, grid, block, 0, s, 0, xi, ldx, xo, ldo, M, kb_total);
+    else launch_k(round_act_kernel<true, false>, grid, block, 0, s, 0, xi, ldx, xo, ldo, M, kb_total);
+  } else {
+    if (mode == 0) launch_k(round_act_kernel<false, true>, grid, block, 0, s, 0, xi, ldx, xo, ldo, M, kb_total);
+    else launch_k(round_act_kernel<false, false>, grid, block, 0, s, 0, xi, ldx, xo, ldo, M, kb_total);
+  }
   return (int)cudaGetLastError();
 }
 

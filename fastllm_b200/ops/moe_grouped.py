@@ -44,11 +44,17 @@ def _prepare_a8(st: StackedExperts, experts) -> None:
     int8 weight bytes are switched to q - 128 in place, once, together with the per-expert views of the same storage."""
     shift = 128.0 if st.kind == "int8" else 0.0
     if st.kind == "int8" and not st.signed:
-        st.gate_up.view(torch.uint8).bitwise_xor_(0x80)
-        st.down.view(torch.uint8).bitwise_xor_(0x80)
-        st.signed = True
-        for w in experts.gate_up + experts.down:
-            w.signed = True
+        already = [w.signed for w in experts.gate_up + experts.down]
+        if all(already):                           # the per-expert weights were switched before they were stacked
+            st.signed = True
+        elif any(already):
+            raise RuntimeError("experts of one layer mix q and q - 128 int8 storage")
+        else:
+            st.gate_up.view(torch.uint8).bitwise_xor_(0x80)
+            st.down.view(torch.uint8).bitwise_xor_(0x80)
+            st.signed = True
+            for w in experts.gate_up + experts.down:
+                w.signed = True
     cat = lambda ws, f: torch.cat([f(w).float().reshape(w.n, -1) for w in ws], dim=0).contiguous()
     st.a8 = (cat(experts.gate_up, lambda w: w.scale), cat(experts.gate_up, lambda w: w.zero) - shift,
              cat(experts.down, lambda w: w.scale), cat(experts.down, lambda w: w.zero) - shift)
@@ -96,10 +102,14 @@ def prepare_model(m) -> None:
         if st is None:
             continue
         ex.stacked = st
+        st.signed = st.kind == "int8" and all(w.signed for w in ex.gate_up + ex.down)
         two_i, H = 2 * st.inter, st.hidden
         for e in range(ex.count):       # drop the duplicate storage: per-expert weights become views of the stacked matrices
             ex.gate_up[e].w = st.gate_up[e * two_i:(e + 1) * two_i]
             ex.down[e].w = st.down[e * H:(e + 1) * H]
+        if QG.INT_A8 and st.kind in ("int8", "int4g") and st.gate_up.is_cuda and (st.kind == "int8" or st.group == 128) \
+                and H % 128 == 0 and st.inter % 128 == 0:
+            _prepare_a8(st, ex)                    # scale tables of the integer path, before any CUDA graph is captured
 
 
 def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add: torch.Tensor | None = None, combine: bool = True):

@@ -83,6 +83,10 @@ def fake_quant_act_fp8(x: torch.Tensor) -> torch.Tensor:
     K = x.shape[-1]
     if K % 128 != 0:
         return x
+    if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):
+        from . import quant_gemm
+
+        return quant_gemm.round_act(x, 1)
     xb = x.float().reshape(-1, K // 128, 128)
     sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / FP8_MAX
     return ((xb / sc).to(torch.float8_e4m3fn).float() * sc).reshape(x.shape).to(x.dtype)
@@ -93,6 +97,10 @@ def fake_quant_act_i8(x: torch.Tensor) -> torch.Tensor:
     K = x.shape[-1]
     if K % 128 != 0:
         return x
+    if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):
+        from . import quant_gemm
+
+        return quant_gemm.round_act(x, 0)
     xb = x.float().reshape(-1, K // 128, 128)
     sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / 127.0
     return (torch.round(xb / sc).clamp(-127, 127) * sc).reshape(x.shape).to(x.dtype)
@@ -143,7 +151,12 @@ class LinearWeight:
             return LinearWeight("dense", w.contiguous(), bias=bias, dtype=w.dtype, interleaved=interleaved)
         if kind == "int8":
             q, s, z = quantize_int8(w)
-            return LinearWeight("int8", q, s, z, bias, dtype=act_dtype, interleaved=interleaved)
+            lw = LinearWeight("int8", q, s, z, bias, dtype=act_dtype, interleaved=interleaved)
+            if q.is_cuda:
+                from . import quant_gemm
+
+                quant_gemm.prepare(lw)          # operand form of the integer path, before any CUDA graph is captured
+            return lw
         if kind == "int4g":
             if w.shape[1] % group != 0:
                 return LinearWeight("dense", w.contiguous(), bias=bias, dtype=w.dtype, interleaved=interleaved)
@@ -207,4 +220,6 @@ class LinearWeight:
                 return y
             if self.kind == "fp8" and quant_gemm.FP8_NATIVE:
                 x = fake_quant_act_fp8(x)
+            elif quant_gemm.uses_int_a8(self):
+                x = fake_quant_act_i8(x)
         return B.linear(x, self.dequant(x.dtype), self.bias, residual, swiglu, self.interleaved, out_f32)

@@ -18,6 +18,7 @@ _lib.register_sigs({"fb_gemm_quant": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, 
 
 _lib.register_sigs({
     "fb_quant_act_fp8": [P, I, P, I, P, I, I, I, I, P, P],
+    "fb_round_act": [P, I, P, I, I, I, I, I, P],
     "fb_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "fb_moe_grouped_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
     "fb_moe_gather_quant_fp8": [P, P, P, P, I, I, I, I, I, P],
@@ -59,11 +60,32 @@ def quant_act_i8(x2: torch.Tensor, rows_used=None, pos=None, topk: int = 1, rows
     return xq, sa, xs, ld_a
 
 
+def round_act(x: torch.Tensor, mode: int) -> torch.Tensor:
+    """``x`` rounded to the int8 (mode 0) or e4m3 (mode 1) grid of its (token, 128-wide k block), in its own 16-bit dtype."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1 or x2.stride(0) % 4 != 0:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], x2.shape[1]), device=x.device, dtype=x.dtype)
+    rc = _lib.kernels().fb_round_act(_ptr(x2), x2.stride(0), _ptr(out), out.stride(0), x2.shape[0], x2.shape[1], dtype_code(x.dtype), mode,
+                                     _stream())
+    _lib.check(rc, "fb_round_act")
+    return out.reshape(x.shape)
+
+
+def prepare(lw) -> None:
+    """Bring a freshly built weight into the form its kernels read (int8: q - 128 bytes for the integer path)."""
+    if uses_int_a8(lw) and lw.w.is_cuda:
+        _a8_tensors(lw)
+
+
 def _a8_tensors(lw):
     """Weight-side tensors of the integer path: (bytes, scale, zero-or-min, kind code).  int8 storage is switched to q - 128 once."""
     if lw.kind == "int8":
         if not lw.signed:
-            lw.w = (lw.w.view(torch.uint8) ^ 0x80).view(torch.uint8)
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("int8 weight reaches the integer path for the first time inside a CUDA graph capture; "
+                                   "call quant_gemm.prepare(weight) when the weight is built")
+            lw.w.view(torch.uint8).bitwise_xor_(0x80)          # in place: views of stacked expert storage stay views
             lw.signed = True
         if lw._a8 is None:
             lw._a8 = (lw.scale.float().contiguous(), (lw.zero.float() - 128.0).contiguous())
@@ -158,6 +180,8 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
         from .quant import fake_quant_act_fp8
 
         x2 = fake_quant_act_fp8(x2)          # same activation rounding as the e4m3 x e4m3 path used for small batches
+    elif uses_int_a8(lw):
+        x2 = round_act(x2, 0)                # same activation rounding as the int8 x int8 path used for small batches
     lib = _lib.kernels()
     group = -1 if (lw.kind == "int8" and lw.signed) else (lw.group or 0)      # -1: int8 bytes hold q - 128
     for m0 in range(0, M, 256):

@@ -567,3 +567,26 @@ def test_moe_grouped_int_a8(kind):
         _lib.check_device_errors()
         rel = (y8.float() - y16.float()).norm() / y16.float().norm()
         assert rel < 0.03, (T, rel)
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_round_act(mode):
+    """Activation rounding kernel (int8 / e4m3 grid per token and 128-wide block) vs the PyTorch definition."""
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(mode)
+    x = (torch.randn(37, 1024, device=DEV) * 3).bfloat16()
+    got = QG.round_act(x, mode).float()
+    xb = x.float().reshape(37, 8, 128)
+    if mode == 0:
+        sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / 127.0
+        ref = torch.round(xb / sc) * sc
+    else:
+        sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-12) / 448.0
+        ref = (xb / sc).to(torch.float8_e4m3fn).float() * sc
+    ref = ref.reshape(37, 1024).bfloat16().float()
+    # x * (1 / s) vs x / s can land on the other side of a rounding boundary for a few elements: one grid step there at most
+    step = (sc * (1.0 if mode == 0 else 32.0)).expand(37, 8, 128).reshape(37, 1024)
+    assert ((got - ref).abs() <= step * 1.01 + ref.abs() / 64 + 1e-6).all()          # + bf16 rounding of both sides
+    assert ((got - ref).abs() > 1e-6).float().mean() < 0.01
+    _lib.check_device_errors()

