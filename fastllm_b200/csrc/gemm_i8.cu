@@ -187,13 +187,15 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
       if (!mbar_wait(&dq_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 7)) return;
       const uint8_t* raw = stages + s * Cfg::STAGE_BYTES + Cfg::B_BYTES;
       uint8_t* out = dq + b * Cfg::A_BYTES;
+      uint4 pk[4];                                         // all four loads first: the stores below must not serialise them
+#pragma unroll
+      for (int it = 0; it < 4; ++it) pk[it] = *reinterpret_cast<const uint4*>(raw + (tid + it * 128) * 16);
 #pragma unroll
       for (int it = 0; it < 4; ++it) {
         const int idx = tid + it * 128;                  // 512 chunks of 16 packed bytes
         const int row = idx >> 2, c4 = idx & 3;
-        const uint4 v = *reinterpret_cast<const uint4*>(raw + idx * 16);
         uint32_t o[8];
-        const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+        const uint32_t w4[4] = {pk[it].x, pk[it].y, pk[it].z, pk[it].w};
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const uint32_t hi = (w4[e] >> 4) & 0x0F0F0F0Fu, lo = w4[e] & 0x0F0F0F0Fu;      // first value of a byte = high nibble
