@@ -190,6 +190,14 @@ class HFCheckpoint:
             if not n.startswith(prefix):
                 continue
             base, _, leaf = n.rpartition(".")
+            if getattr(self, "want_spans", False) and n.endswith(".gate_proj.weight") and ".experts." in n \
+                    and not getattr(self, "lora", None):
+                up = n[:-len("gate_proj.weight")] + "up_proj.weight"
+                if up in self.where and self.where[up][0] == self.where[n][0]:
+                    fi = self.where[n][0]
+                    sp = self.files[fi].span(self.where[n][1], self.where[up][1])
+                    if sp is not None:          # [gate; up] of one expert as a single view of the file mapping
+                        out[n[:-len("gate_proj.weight")] + "gate_up_span"] = sp
             if leaf in ("weight_scale_inv", "weight_scale", "weight_scale_2", "input_scale", "qzeros", "scales", "g_idx"):
                 continue
             if leaf.endswith("_scales") and self.has(n[:-7] + "_blocks"):
@@ -227,7 +235,11 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
     """Build a ready-to-run ``DecoderModel`` from an HF folder.
 
     ``moe_device="cpu"`` keeps the routed experts (of the first ``moe_device_layers`` layers, all when negative) in host
-    memory and runs them on the native CPU backend -- the reference's ``--moe_device cpu`` hybrid placement."""
+    memory and runs them on the native CPU backend -- the reference's ``--moe_device cpu`` hybrid placement.
+    ``moe_device="disk"`` is the same placement with the expert matrices left in the checkpoint's file mapping (no copy into
+    anonymous memory: pages come from the SSD through the page cache as the router touches an expert), for models larger than
+    RAM -- the reference's disk device (src/devices/disk/diskdevice.cpp:45-49).  It applies to 16/32-bit checkpoints whose
+    dtype is the run-time dtype; anything else is read into memory as for ``"cpu"``."""
     cfg = load_config(path)
     if dtype is None:
         dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}.get(cfg.torch_dtype, torch.bfloat16)
@@ -255,7 +267,9 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
         staged = split_layers_by_map(cfg.num_layers, device_map)
         device = staged[0]
     m = DecoderModel(cfg, device, dtype, tp, ep)
-    m.moe_device, m.moe_device_layers = moe_device, moe_device_layers
+    m.moe_disk = moe_device == "disk"
+    ck.want_spans = m.moe_disk
+    m.moe_device, m.moe_device_layers = ("cpu" if m.moe_disk else moe_device), moe_device_layers
     if device_map and len(set(map(str, staged))) > 1:
         m.layer_devices = staged
 

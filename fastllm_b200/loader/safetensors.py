@@ -60,6 +60,20 @@ class SafeTensorFile:
             return torch.empty(e["shape"], dtype=tdt)
         return t.view(tdt).reshape(e["shape"])
 
+    def span(self, first: str, second: str):
+        """One tensor over two matrices that lie back to back in the file (same dtype and column count): ``[rows_a + rows_b, K]``
+        without a copy, else None.  Writers that sort tensors by name put an expert's gate_proj and up_proj side by side."""
+        a, b = self.header[first], self.header[second]
+        if a["dtype"] != b["dtype"] or a["dtype"] not in _DTYPES or len(a["shape"]) != 2 or a["shape"][1:] != b["shape"][1:]:
+            return None
+        if a["data_offsets"][1] != b["data_offsets"][0]:
+            return None
+        raw = self._buf[self.data_start + a["data_offsets"][0]:self.data_start + b["data_offsets"][1]]
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore")
+            t = torch.from_numpy(raw)
+        return t.view(_DTYPES[a["dtype"]]).reshape(a["shape"][0] + b["shape"][0], a["shape"][1])
+
     def close(self):
         try:
             self._buf = None

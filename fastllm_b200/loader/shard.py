@@ -13,7 +13,7 @@ import torch
 
 from ..ops import basic as B
 from ..ops import moe as MOE
-from ..ops.quant import LinearWeight
+from ..ops.quant import LinearWeight, normalize_wdtype
 
 
 def _shard_rows(w, rank, size):
@@ -190,6 +190,16 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         em = _HostPlacement(m) if host else m
         for e in range(lo, hi):
             gw, uw, dw = (g(f"mlp.experts.{e}.{nm}.weight") for nm in ("gate_proj", "up_proj", "down_proj"))
+            span = g(f"mlp.experts.{e}.gate_up_span") if getattr(m, "moe_disk", False) else None
+            t.pop(p + f"mlp.experts.{e}.gate_up_span", None)
+            if span is not None and not moe_tp and (host or not m.on_cuda) and span.dtype == em.dtype \
+                    and normalize_wdtype(MW(f"mlp.experts.{e}.gate_proj.weight"))[0] == "dense":
+                # disk placement: [gate; up] and down stay views of the checkpoint's file mapping
+                gu.append(LinearWeight("dense", span, dtype=em.dtype, interleaved=False))
+                dn.append(LinearWeight("dense", dw, dtype=em.dtype))
+                for nm in ("gate_proj", "up_proj", "down_proj"):
+                    t.pop(p + f"mlp.experts.{e}.{nm}.weight", None)
+                continue
             if moe_tp:
                 gw, uw, dw = _shard_rows(gw, r, n), _shard_rows(uw, r, n), _shard_cols(dw, r, n)
             gu.append(_gate_up(em, gw, uw, MW(f"mlp.experts.{e}.gate_proj.weight")))

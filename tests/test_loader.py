@@ -177,3 +177,62 @@ def test_split_layers_by_device_map():
     assert [str(x) for x in d] == ["cuda:0"] * 6 + ["cuda:1"] * 4
     assert [str(x) for x in split_layers_by_map(3, {"cuda:0": 1, "cuda:1": 1, "cuda:2": 1})] == ["cuda:0", "cuda:1", "cuda:2"]
     assert len(split_layers_by_map(7, {"cuda:0": 1})) == 7
+
+
+def test_moe_device_disk_keeps_experts_in_the_file_mapping(tmp_path):
+    """``moe_device="disk"``: expert matrices are views of the checkpoint mapping (no copy), results equal the normal load."""
+    import mmap
+
+    from fastllm_b200.engine import EngineConfig, LLMEngine
+    from fastllm_b200.models.decoder import ForwardBatch
+
+    import json
+    import os
+
+    from fastllm_b200.loader.safetensors import save_file
+
+    transformers = pytest.importorskip("transformers")
+    torch.manual_seed(0)
+    cfg = transformers.AutoConfig.for_model(model_type="qwen3_moe", vocab_size=512, hidden_size=256, num_hidden_layers=2,
+                                            num_attention_heads=4, num_key_value_heads=2, intermediate_size=512, head_dim=64,
+                                            max_position_embeddings=512, num_experts=4, num_experts_per_tok=2,
+                                            moe_intermediate_size=128, decoder_sparse_step=1, norm_topk_prob=True)
+    ref = transformers.AutoModelForCausalLM.from_config(cfg, dtype=torch.float32)
+    sd = {}
+    for k, v in ref.state_dict().items():          # classic per-expert names, written in sorted order (gate_proj next to up_proj)
+        v = v.detach()
+        if k.endswith("mlp.experts.gate_up_proj"):
+            for e in range(v.shape[0]):
+                sd[k[:-len("gate_up_proj")] + f"{e}.gate_proj.weight"] = v[e][:v.shape[1] // 2].contiguous()
+                sd[k[:-len("gate_up_proj")] + f"{e}.up_proj.weight"] = v[e][v.shape[1] // 2:].contiguous()
+        elif k.endswith("mlp.experts.down_proj"):
+            for e in range(v.shape[0]):
+                sd[k[:-len("down_proj")] + f"{e}.down_proj.weight"] = v[e].contiguous()
+        else:
+            sd[k] = v.contiguous()
+    d = str(tmp_path / "moe")
+    os.makedirs(d)
+    save_file({k: sd[k] for k in sorted(sd)}, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg.to_dict(), f)
+    base = hf.load_model(d, device="cpu", dtype=torch.float32)
+    disk = hf.load_model(d, device="cpu", dtype=torch.float32, moe_device="disk")
+    ex_b, ex_d = base.layers[0].mlp.experts, disk.layers[0].mlp.experts
+    assert torch.equal(ex_b.gate_up[1].w, ex_d.gate_up[1].w) and torch.equal(ex_b.down[1].w, ex_d.down[1].w)
+    # a view of a file mapping is page-aligned storage + header offset, and two experts are file-distance apart, not malloc-distance
+    w0, w1 = ex_d.gate_up[0].w, ex_d.gate_up[1].w
+    per_expert = 3 * w0.numel() // 2 * w0.element_size()          # gate + up + down bytes of one expert
+    assert abs(w1.data_ptr() - w0.data_ptr()) == per_expert
+    assert not w0.requires_grad and w0._base is not None             # a view, not an owning tensor
+
+    def logits(m):
+        prompt = list(range(3, 40, 2))
+        T = len(prompt)
+        eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=256), num_pages=4)
+        fb = ForwardBatch(ids=torch.tensor(prompt, dtype=torch.int32), positions=torch.arange(T, dtype=torch.int32),
+                          slots=torch.arange(T, dtype=torch.int32), page_table=torch.tensor([[0, 1]], dtype=torch.int32),
+                          kv_lens=torch.tensor([T], dtype=torch.int32), cu_q=torch.tensor([0, T], dtype=torch.int32),
+                          logit_rows=torch.tensor([T - 1]), cu_q_host=[0, T])
+        return m.forward(fb, eng.runner.kv.pools)[0].float()
+
+    assert torch.allclose(logits(base), logits(disk), atol=1e-5)
