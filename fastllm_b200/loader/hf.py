@@ -81,6 +81,9 @@ def dequant_awq(qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tenso
 # ---------------------------------------------------------------------------------------------------
 _RENAMES = [
     (r"\.mlp\.moe_statics\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),          # Ernie-4.5-MoE
+    (r"\.block_sparse_moe\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),          # MiniMax-M2
+    (r"\.mlp\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),
+    (r"\.self_attn\.W_pack\.", ".self_attn.qkv_proj."),                                            # Baichuan: fused [q; k; v]
     (r"\.mlp\.gate\.wg\.", ".mlp.gate."), (r"\.mlp\.shared_mlp\.", ".mlp.shared_experts."),         # Hunyuan-MoE
     # ChatGLM2/3 and original GLM-4 checkpoints
     (r"^transformer\.embedding\.word_embeddings\.", "model.embed_tokens."), (r"^transformer\.encoder\.layers\.", "model.layers."),

@@ -43,6 +43,7 @@ class ModelConfig:
     attn_scale_override: float | None = None   # softmax scale when it is not 1/sqrt(head_dim)
     residual_scale: float = 1.0            # multiplier of every sub-layer output before the residual add (folded into weights)
     post_norms: bool = False               # sandwich norms: the sub-layer output is normalised before the residual add
+    qk_norm_full: bool = False             # MiniMax-M2: one RMSNorm over all heads of q (and of k) instead of per head
     qk_norm_after_rope: bool = False       # Hunyuan: per-head norm applied after the rotary embedding
     attn_sinks: bool = False               # learned per-head sink logit in the softmax denominator (gpt-oss)
     moe_act: str = "swiglu"                # swiglu | gptoss (clamped, alpha 1.702, (up + 1))
@@ -213,7 +214,20 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.num_experts_per_tok = g("num_experts_per_tok", 2)
         c.moe_intermediate_size = c.intermediate_size
         c.norm_topk_prob = True
-    elif mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe", "minimax_m2", "ernie4_5_moe"):
+    elif mt == "minimax_m2":
+        # GQA + full-width QK norm + partial rotary; every layer MoE: sigmoid scores, selection bias, renormalised top-k
+        # (reference: src/models/minimax_m2.cpp)
+        c.num_experts = g("num_local_experts", g("num_experts", 0)) or 0
+        c.num_experts_per_tok = g("num_experts_per_tok", 0)
+        c.moe_intermediate_size = c.intermediate_size
+        c.norm_topk_prob = True
+        c.scoring_func = g("scoring_func", "sigmoid")
+        c.router_bias = True
+        c.qk_norm = bool(g("use_qk_norm", True))
+        c.qk_norm_full = c.qk_norm and g("qk_norm_type", "per_layer") == "per_layer"
+        if g("rotary_dim") and not prf:
+            c.rotary_dim = int(g("rotary_dim"))
+    elif mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe", "ernie4_5_moe"):
         c.num_experts = g("n_routed_experts", g("num_experts", g("moe_num_experts", 0))) or 0
         c.num_experts_per_tok = g("num_experts_per_tok", g("moe_k", 0))
         c.moe_intermediate_size = g("moe_intermediate_size", 0)

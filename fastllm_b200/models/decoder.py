@@ -122,7 +122,7 @@ class DecoderModel:
         self.rot_dim = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
         self.attn_scale = cfg.attn_scale_override if cfg.attn_scale_override else 1.0 / math.sqrt(cfg.q_head_dim)
         # families whose attention needs options outside the tensor-core kernels run the PyTorch evaluation (not graph-safe)
-        self.general_attn = bool(cfg.attn_softcap or cfg.attn_sinks or cfg.qk_norm_after_rope)
+        self.general_attn = bool(cfg.attn_softcap or cfg.attn_sinks or cfg.qk_norm_after_rope or cfg.qk_norm_full)
         if cfg.use_mla and cfg.rope_scaling and cfg.rope_scaling.get("mscale_all_dim"):
             ms = 0.1 * float(cfg.rope_scaling["mscale_all_dim"]) * math.log(float(cfg.rope_scaling.get("factor", 1.0))) + 1.0
             self.attn_scale *= ms * ms
@@ -212,6 +212,10 @@ class DecoderModel:
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
         q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
         norm = lambda t, w: A._head_norm_ref(t, w, c.rms_eps, c.norm_unit_offset) if w is not None else t
+        if c.qk_norm_full:           # one norm over the whole projection (all heads of this rank = all heads: one rank only)
+            if self.tp.size != 1:
+                raise NotImplementedError("full-width QK norm needs all heads on one rank")
+            norm = lambda t, w: A._head_norm_ref(t.reshape(T, 1, -1), w, c.rms_eps, c.norm_unit_offset).reshape(t.shape) if w is not None else t
         if not c.qk_norm_after_rope:
             q, k = norm(q, lw.q_norm), norm(k, lw.k_norm)
         q = A.apply_rope_ref(q, fb.positions, cos, sin, self.rope_mode, self.rot_dim)

@@ -42,6 +42,8 @@ FAMILIES = {
     "hunyuan_v1_moe": dict(model_type="hunyuan_v1_moe", **_C, num_experts=4, moe_topk=2, num_shared_expert=1, moe_intermediate_size=128),
     "hunyuan_v1_dense": dict(model_type="hunyuan_v1_dense", **_C),
     "gpt_oss": dict(model_type="gpt_oss", **_C, num_local_experts=4, num_experts_per_tok=2, sliding_window=16),
+    "minimax_m2": dict(model_type="minimax_m2", **_C, num_local_experts=4, num_experts_per_tok=2,
+                       rope_parameters={"rope_type": "default", "rope_theta": 1e6, "partial_rotary_factor": 0.5}),
     "granite": dict(model_type="granite", **_NH, attention_multiplier=0.2, embedding_multiplier=3.0, residual_multiplier=0.5,
                     logits_scaling=2.0),
 }
@@ -306,3 +308,37 @@ def test_nvfp4_checkpoint(tmp_path):
             json.dump(ref.config.to_dict(), f)
         logits.append(_last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), list(range(5, 60, 3))))
     assert torch.allclose(logits[0], logits[1], atol=1e-4)
+
+
+def test_baichuan_and_internlm3_layouts(tmp_path):
+    """Baichuan (rotary variants: ``W_pack`` = [q; k; v]) and InternLM3 (Llama names, ``qkv_bias`` / ``bias`` flags) from oracles."""
+    ref = _tiny("llama", **{**_NH, "num_key_value_heads": 4})
+    prompt = list(range(7, 70, 2))
+
+    def merge(sd):
+        out = {}
+        for k, v in sd.items():
+            if ".q_proj." in k:
+                out[k.replace(".q_proj.", ".W_pack.")] = torch.cat([v, sd[k.replace(".q_proj.", ".k_proj.")], sd[k.replace(".q_proj.", ".v_proj.")]], dim=0)
+            elif ".k_proj." not in k and ".v_proj." not in k:
+                out[k] = v
+        return out
+
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+    d = str(tmp_path / "baichuan")
+    _save_renamed(ref, dict(ref.config.to_dict(), model_type="baichuan"), lambda k: k, d, merge)
+    got = _last_logits(hf.load_model(d, device="cpu", dtype=torch.float32), prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+
+    ref3 = _tiny("qwen2", **_NH)                                   # q/k/v bias, no o / mlp bias = InternLM3 with qkv_bias
+    for n_, p_ in ref3.named_parameters():
+        if n_.endswith("_proj.bias"):
+            torch.nn.init.normal_(p_, std=0.1)
+    with torch.no_grad():
+        want3 = ref3(torch.tensor([prompt])).logits[0, -1].float()
+    d3 = str(tmp_path / "internlm3")
+    cfg3 = {k: v for k, v in ref3.config.to_dict().items() if k not in ("use_sliding_window", "sliding_window", "layer_types", "max_window_layers")}
+    _save_renamed(ref3, dict(cfg3, model_type="internlm3", qkv_bias=True, bias=False), lambda k: k, d3)
+    got3 = _last_logits(hf.load_model(d3, device="cpu", dtype=torch.float32), prompt)
+    assert torch.nn.functional.cosine_similarity(got3, want3, dim=0).item() > 0.99999
