@@ -51,6 +51,11 @@ struct QuantCfg {
   static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
   static constexpr int SMEM_BYTES = BODY_BYTES + 512 + 1024;
   static constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
+  // dequant warps: four per CTA with two CTAs per SM; eight when the tile leaves room for one CTA only (the conversion is
+  // a dependent load - convert - store chain per thread, so its rate follows the number of warps in flight)
+  static constexpr int DQ_WARPS = MPAD <= 64 ? 4 : 8;
+  static constexpr int DQ_THREADS = DQ_WARPS * 32;
+  static constexpr int THREADS = 64 + DQ_THREADS;
 };
 
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
@@ -97,8 +102,8 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 129); }
-    for (int s = 0; s < Cfg::DQ_SLOTS; ++s) { mbar_init(&dq_full[s], 128); mbar_init(&dq_empty[s], 1); }
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], Cfg::DQ_THREADS + 1); }
+    for (int s = 0; s < Cfg::DQ_SLOTS; ++s) { mbar_init(&dq_full[s], Cfg::DQ_THREADS); mbar_init(&dq_empty[s], 1); }
     mbar_init(accum_bar, 1);
     mbar_init_fence();
     tma_prefetch_desc(&tmW);
@@ -155,7 +160,8 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
     __syncwarp();
   } else {
     const int q = warp & 3;
-    const int tid = threadIdx.x - 64;                 // 0..127
+    const int tid = threadIdx.x - 64;                 // 0..DQ_THREADS-1
+    constexpr int DQT = Cfg::DQ_THREADS;
     // ------------------------------ dequant stage ------------------------------
     for (int i = 0; i < kb_cnt; ++i) {
       const int s = i % Cfg::STAGES, t = i % Cfg::DQ_SLOTS;
@@ -168,8 +174,8 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
       if (QM == Q_INT4G) {
         const int g = (kb * 64) / qp.group_k;
 #pragma unroll
-        for (int it = 0; it < 2; ++it) {
-          const int u = tid + 128 * it, row = u >> 1, ch = u & 1;
+        for (int it = 0; it < 256 / DQT; ++it) {
+          const int u = tid + DQT * it, row = u >> 1, ch = u & 1;
           const int n = n_tile * 128 + row;
           float2 sm = make_float2(0.f, 0.f);
           if (n < p.N) sm = reinterpret_cast<const float2*>(qp.scale)[(size_t)g * p.N + n];
@@ -195,15 +201,15 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
         float bscale = 1.f;
         if (QM == Q_FP8) bscale = qp.scale[(size_t)n_tile * qp.groups + (kb * 64) / 128];
         const __half2 bs2 = __float2half2_rn(bscale);
-        uint4 wv[4];
+        uint4 wv[512 / DQT];
 #pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int u = tid + 128 * it;
+        for (int it = 0; it < 512 / DQT; ++it) {
+          const int u = tid + DQT * it;
           wv[it] = *reinterpret_cast<const uint4*>(raw + (u >> 2) * 64 + (u & 3) * 16);
         }
 #pragma unroll
-        for (int it = 0; it < 4; ++it) {
-          const int u = tid + 128 * it, row = u >> 2, ch = u & 3;
+        for (int it = 0; it < 512 / DQT; ++it) {
+          const int u = tid + DQT * it, row = u >> 2, ch = u & 3;
           const int n = n_tile * 128 + row;
           const uint32_t ws[4] = {wv[it].x, wv[it].y, wv[it].z, wv[it].w};
           uint32_t o[8];
@@ -256,7 +262,9 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
     const int n_local = q * 32 + lane;
     float row_scale = 1.f;
     if (QM == Q_INT8) { const int n = n_tile * 128 + n_local; row_scale = n < p.N ? qp.scale[n] : 0.f; }
-    if (kb_cnt > 0) {
+    if (warp >= 6) {
+      // extra dequant warps: no TMEM lane quarter of their own
+    } else if (kb_cnt > 0) {
       mbar_wait(accum_bar, 0, dead, KID_GEMM_QUANT, 3);
       tc_fence_after_sync();
       constexpr int CH = MPAD < 32 ? MPAD : 32;
@@ -281,7 +289,7 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
 }
 
 template <int MPAD, bool BF16, int QM>
-__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+__global__ void __launch_bounds__((QuantCfg<MPAD, QM>::THREADS), (MPAD <= 64 ? 2 : 1))
 gemm_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
                   const QuantParams qp) {
   gemm_quant_device<MPAD, BF16, QM>(tmW, tmX, p, qp);
@@ -295,7 +303,7 @@ struct QuantGroupInfo {
 };
 
 template <int MPAD, bool BF16, int QM>
-__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+__global__ void __launch_bounds__((QuantCfg<MPAD, QM>::THREADS), (MPAD <= 64 ? 2 : 1))
 moe_grouped_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                          const QuantParams qbase, const QuantGroupInfo gi) {
   const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
@@ -334,7 +342,7 @@ static cudaError_t launch_quant(const CUtensorMap& tmW, const CUtensorMap& tmX, 
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, 1);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -415,7 +423,7 @@ static cudaError_t launch_grouped_quant(const CUtensorMap& tmW, const CUtensorMa
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, nz);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
