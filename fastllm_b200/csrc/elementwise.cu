@@ -41,9 +41,18 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 //           else                      y = norm(x) * w.        One CTA per row, H % 8 == 0.
 // `unit_offset` adds 1 to the weight (Gemma convention).
 // ------------------------------------------------------------------------------------------------
-template <bool BF16>
+// Optional second output for the 8-bit-activation GEMMs that consume the normalised row: the row quantised per 128-wide block
+// (QMODE 1: int8 with scale amax / 127 and the block sums of the quantised values; QMODE 2: e4m3 with scale amax / 448),
+// computed from the 16-bit-rounded outputs so that it equals what the stand-alone quantiser would produce from y.
+struct NormQuantOut {
+  uint8_t* xq; int ldq;          // [M, H] bytes
+  float* scales; float* sums;    // [H / 128, ld_a]
+  int ld_a;
+};
+
+template <bool BF16, int QMODE = 0>
 __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ w, uint16_t* __restrict__ y,
-                               uint16_t* residual, int H, int ldx, int ldy, float eps, float unit_offset) {
+                               uint16_t* residual, int H, int ldx, int ldy, float eps, float unit_offset, NormQuantOut qo = {}) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float sh[32];
@@ -83,6 +92,37 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* _
     o.z = pack_16<BF16>(r[4] * inv * (wc.x + unit_offset), r[5] * inv * (wc.y + unit_offset));
     o.w = pack_16<BF16>(r[6] * inv * (wd.x + unit_offset), r[7] * inv * (wd.y + unit_offset));
     yp[i] = o;
+    if (QMODE != 0) {
+      // 16 consecutive threads hold one 128-wide block (H % 128 == 0: a half-warp is inside the row or outside as a whole)
+      const uint32_t mask = (threadIdx.x & 16) ? 0xFFFF0000u : 0x0000FFFFu;
+      const float2 a = unpack_16<BF16>(o.x), b = unpack_16<BF16>(o.y), c = unpack_16<BF16>(o.z), d = unpack_16<BF16>(o.w);
+      float amax = fmaxf(fmaxf(fmaxf(fabsf(a.x), fabsf(a.y)), fmaxf(fabsf(b.x), fabsf(b.y))),
+                         fmaxf(fmaxf(fabsf(c.x), fabsf(c.y)), fmaxf(fabsf(d.x), fabsf(d.y))));
+#pragma unroll
+      for (int sft = 8; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(mask, amax, sft));
+      const int kb = i >> 4;
+      uint2 q;
+      if (QMODE == 1) {
+        const float scale = fmaxf(amax, 1e-12f) / 127.0f, iv = 1.0f / scale;
+        const int q0 = __float2int_rn(a.x * iv), q1 = __float2int_rn(a.y * iv), q2 = __float2int_rn(b.x * iv), q3 = __float2int_rn(b.y * iv);
+        const int q4 = __float2int_rn(c.x * iv), q5 = __float2int_rn(c.y * iv), q6 = __float2int_rn(d.x * iv), q7 = __float2int_rn(d.y * iv);
+        q.x = (uint32_t)(q0 & 0xFF) | ((uint32_t)(q1 & 0xFF) << 8) | ((uint32_t)(q2 & 0xFF) << 16) | ((uint32_t)(q3 & 0xFF) << 24);
+        q.y = (uint32_t)(q4 & 0xFF) | ((uint32_t)(q5 & 0xFF) << 8) | ((uint32_t)(q6 & 0xFF) << 16) | ((uint32_t)(q7 & 0xFF) << 24);
+        int sm = q0 + q1 + q2 + q3 + q4 + q5 + q6 + q7;
+#pragma unroll
+        for (int sft = 8; sft > 0; sft >>= 1) sm += __shfl_xor_sync(mask, sm, sft);
+        if ((threadIdx.x & 15) == 0) {
+          qo.scales[(size_t)kb * qo.ld_a + row] = scale;
+          qo.sums[(size_t)kb * qo.ld_a + row] = (float)sm;
+        }
+      } else {
+        const float scale = fmaxf(amax, 1e-12f) / 448.0f, iv = 1.0f / scale;
+        q.x = pack_e4m3x4(a.x * iv, a.y * iv, b.x * iv, b.y * iv);
+        q.y = pack_e4m3x4(c.x * iv, c.y * iv, d.x * iv, d.y * iv);
+        if ((threadIdx.x & 15) == 0) qo.scales[(size_t)kb * qo.ld_a + row] = scale;
+      }
+      *reinterpret_cast<uint2*>(qo.xq + (size_t)row * qo.ldq + i * 8) = q;
+    }
   }
 }
 
@@ -393,6 +433,32 @@ __global__ void route_topk_kernel(const RouteParams p) {
 
 using namespace fb;
 
+// RMSNorm that also emits the row quantised for an 8-bit-activation GEMM (mode 1: int8 + scales + block sums, mode 2: e4m3 +
+// scales; scale tables [H / 128, ld_a]).  H % 128 == 0.
+extern "C" int fb_rmsnorm_quant(const void* x, const void* w, void* y, void* residual, int M, int H, int ldx, int ldy, float eps,
+                                float unit_offset, int dtype, int mode, void* xq, int ldq, float* scales, float* sums, int ld_a,
+                                void* stream) {
+  if (M <= 0) return 0;
+  if (H % 128 != 0 || H > 32768 || (mode != 1 && mode != 2) || ldq % 8 != 0) return -1;
+  int threads = H / 8;
+  threads = threads > 1024 ? 1024 : ((threads + 31) / 32) * 32;
+  const size_t smem = (size_t)H * sizeof(float);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  NormQuantOut qo;
+  qo.xq = (uint8_t*)xq; qo.ldq = ldq; qo.scales = scales; qo.sums = sums; qo.ld_a = ld_a;
+#define FB_NQ(BF, QM)                                                                                                          \
+  {                                                                                                                            \
+    static DeviceOnce cfg;                                                                                                     \
+    if (cfg.need()) { cudaFuncSetAttribute(rmsnorm_kernel<BF, QM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); }  \
+    launch_k(rmsnorm_kernel<BF, QM>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, \
+             (uint16_t*)residual, H, ldx, ldy, eps, unit_offset, qo);                                                          \
+  }
+  if (dtype == 1) { if (mode == 1) FB_NQ(true, 1) else FB_NQ(true, 2) }
+  else { if (mode == 1) FB_NQ(false, 1) else FB_NQ(false, 2) }
+#undef FB_NQ
+  return (int)cudaGetLastError();
+}
+
 extern "C" int fb_rmsnorm(const void* x, const void* w, void* y, void* residual, int M, int H, int ldx, int ldy, float eps,
                           float unit_offset, int dtype, void* stream) {
   if (M <= 0) return 0;
@@ -404,11 +470,11 @@ extern "C" int fb_rmsnorm(const void* x, const void* w, void* y, void* residual,
   if (dtype == 1) {
     static DeviceOnce cfg;
     if (cfg.need()) { cudaFuncSetAttribute(rmsnorm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); }
-    launch_k(rmsnorm_kernel<true>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
+    launch_k(rmsnorm_kernel<true>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset, NormQuantOut{});
   } else {
     static DeviceOnce cfg;
     if (cfg.need()) { cudaFuncSetAttribute(rmsnorm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32768 * 4); }
-    launch_k(rmsnorm_kernel<false>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset);
+    launch_k(rmsnorm_kernel<false>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, (uint16_t*)residual, H, ldx, ldy, eps, unit_offset, NormQuantOut{});
   }
   return (int)cudaGetLastError();
 }

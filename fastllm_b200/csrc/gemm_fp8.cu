@@ -206,12 +206,6 @@ moe_grouped_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
 }
 
 // ---- activation quantisation: x [M, K] 16-bit -> xq [M, K] e4m3 + scales [K / 128, ld_a] ------------------------------------
-__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
-  uint16_t lo, hi;
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(lo) : "f"(b), "f"(a));     // first source -> upper byte
-  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(hi) : "f"(d), "f"(c));
-  return (uint32_t)lo | ((uint32_t)hi << 16);
-}
 
 template <bool BF16>
 __global__ void quant_act_fp8_kernel(const uint16_t* __restrict__ x, int ldx, uint8_t* __restrict__ xq, int ldq, float* __restrict__ scales,

@@ -237,7 +237,27 @@ class DecoderModel:
         return self.tp.comm.row_linear(w, x, residual)
 
     def _norm(self, h, ln_w):
-        return B.rmsnorm(h, ln_w, self.cfg.rms_eps, unit_offset=self.cfg.norm_unit_offset)
+        qm = 0
+        if h.is_cuda and h.dim() == 2:
+            cons = self._norm_consumers().get(id(ln_w))
+            if cons is not None:
+                from ..ops import quant_gemm
+
+                qm = quant_gemm.act_quant_mode(cons, h.shape[0])
+        return B.rmsnorm(h, ln_w, self.cfg.rms_eps, unit_offset=self.cfg.norm_unit_offset, quant_mode=qm)
+
+    def _norm_consumers(self) -> dict:
+        """Norm weight -> the single quantised projection that reads that norm's output (its quantiser is fused into the norm)."""
+        m = getattr(self, "_norm_cons", None)
+        if m is None:
+            m = {}
+            for lw in self.layers:
+                if lw.attn.ln is not None and lw.attn.qkv is not None and lw.attn.qkv.kind != "dense":
+                    m[id(lw.attn.ln)] = lw.attn.qkv
+                if lw.mlp.ln is not None and lw.mlp.gate_up is not None and lw.mlp.experts is None and lw.mlp.gate_up.kind != "dense":
+                    m[id(lw.mlp.ln)] = lw.mlp.gate_up
+            self._norm_cons = m
+        return m
 
     def _row_parallel_norm(self, w: LinearWeight, x, h, next_ln, post_ln=None):
         """``h += row_parallel_linear(x)`` then ``RMSNorm(h)`` for the next block.  Returns (h, x_norm).

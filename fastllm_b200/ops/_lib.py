@@ -26,6 +26,7 @@ _KERNEL_SIGS = {
     "fb_gemm_16bit": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
     "fb_gemm_pick_split": [I, I, I, I],
     "fb_rmsnorm": [P, P, P, P, I, I, I, I, F, F, I, P],
+    "fb_rmsnorm_quant": [P, P, P, P, I, I, I, I, F, F, I, I, P, I, P, P, I, P],
     "fb_qkv_post": [P, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
     "fb_silu_mul": [P, P, I, I, I, I, I, P],
     "fb_embedding": [P, P, P, I, I, I, P],

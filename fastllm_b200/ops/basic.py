@@ -158,8 +158,12 @@ def rmsnorm_ref(x, w, eps, residual=None, unit_offset=0.0):
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor | None = None, unit_offset: float = 0.0,
-            out: torch.Tensor | None = None) -> torch.Tensor:
-    """RMSNorm over the last dim.  With ``residual`` given: ``residual += x`` in place, then normalise it."""
+            out: torch.Tensor | None = None, quant_mode: int = 0) -> torch.Tensor:
+    """RMSNorm over the last dim.  With ``residual`` given: ``residual += x`` in place, then normalise it.
+
+    ``quant_mode`` 1 (int8) / 2 (e4m3): the kernel also writes the row quantised per 128-wide block for the 8-bit-activation
+    GEMM that consumes it; the result carries it as ``y.fb_quant = (mode, xq, scales, sums, ld_a)`` and the quantised linear
+    layers pick it up instead of launching their own quantiser."""
     if not x.is_cuda:
         if cpu_native(x) and (residual is None or residual.dtype == torch.float32):
             if residual is not None:
@@ -176,6 +180,18 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor
         out = torch.empty((M, H), device=x.device, dtype=x.dtype)
     if residual is not None and not residual.is_contiguous():
         raise ValueError("residual must be contiguous")
+    if quant_mode and H % 128 == 0 and M <= 128 and x.dtype in (torch.float16, torch.bfloat16):
+        ld_a = (M + 128 + 3) // 4 * 4
+        xq = torch.empty((M, H), device=x.device, dtype=torch.int8 if quant_mode == 1 else torch.uint8)
+        sa = torch.empty((H // 128, ld_a), device=x.device, dtype=torch.float32)
+        xs = torch.empty((H // 128, ld_a), device=x.device, dtype=torch.float32) if quant_mode == 1 else None
+        rc = _lib.kernels().fb_rmsnorm_quant(_ptr(x2), _ptr(w), _ptr(out), _ptr(residual), M, H, x2.stride(0), out.stride(0), float(eps),
+                                             float(unit_offset), dtype_code(x.dtype), quant_mode, _ptr(xq), H, _ptr(sa), _ptr(xs), ld_a,
+                                             _stream())
+        _lib.check(rc, "fb_rmsnorm_quant")
+        y = out.reshape(x.shape)
+        y.fb_quant = (quant_mode, xq, sa, xs, ld_a)
+        return y
     rc = _lib.kernels().fb_rmsnorm(_ptr(x2), _ptr(w), _ptr(out), _ptr(residual), M, H, x2.stride(0), out.stride(0), float(eps),
                                    float(unit_offset), dtype_code(x.dtype), _stream())
     _lib.check(rc, "fb_rmsnorm")

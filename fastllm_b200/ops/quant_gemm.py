@@ -72,6 +72,17 @@ def round_act(x: torch.Tensor, mode: int) -> torch.Tensor:
     return out.reshape(x.shape)
 
 
+def act_quant_mode(lw, M: int) -> int:
+    """Which quantised form of its input ``lw`` consumes for ``M`` rows: 1 int8, 2 e4m3, 0 none (16-bit activations)."""
+    if lw is None or lw.k % 128 != 0 or lw.adapters:
+        return 0
+    if uses_int_a8(lw) and M <= INT_A8_MAX_M[lw.kind]:
+        return 1
+    if lw.kind == "fp8" and FP8_NATIVE and M <= 128:
+        return 2
+    return 0
+
+
 def prepare(lw) -> None:
     """Bring a freshly built weight into the form its kernels read (int8: q - 128 bytes for the integer path)."""
     if uses_int_a8(lw) and lw.w.is_cuda:
@@ -95,10 +106,13 @@ def _a8_tensors(lw):
     return lw.w, lw._a8[0], lw._a8[1], 2
 
 
-def _linear_i8(x2, lw, out, bias, res2, flags):
+def _linear_i8(x2, lw, out, bias, res2, flags, pre=None):
     M, K = x2.shape
     w, sc, zr, kind = _a8_tensors(lw)
-    xq, sa, xs, ld_a = quant_act_i8(x2)
+    if pre is not None and pre[0] == 1 and pre[1].shape == (M, K):
+        _, xq, sa, xs, ld_a = pre              # quantised by the kernel that produced x (fused RMSNorm)
+    else:
+        xq, sa, xs, ld_a = quant_act_i8(x2)
     for m0 in range(0, M, 128):           # the kernel takes up to 128 rows; the weights of later chunks come from L2
         m1 = min(M, m0 + 128)
         rc = _lib.kernels().fb_gemm_i8(_ptr(xq[m0:m1]), K, _ptr(sa[:, m0:]), _ptr(xs[:, m0:]), ld_a, _ptr(w), _ptr(sc), _ptr(zr),
@@ -120,9 +134,12 @@ def quant_act_fp8(x2: torch.Tensor, rows_used: torch.Tensor | None = None):
     return xq, sa, ld_a
 
 
-def _linear_fp8_native(x2, lw, out, bias, res2, flags):
+def _linear_fp8_native(x2, lw, out, bias, res2, flags, pre=None):
     M, K = x2.shape
-    xq, sa, ld_a = quant_act_fp8(x2)
+    if pre is not None and pre[0] == 2 and pre[1].shape == (M, K):
+        _, xq, sa, _xs, ld_a = pre             # quantised by the kernel that produced x (fused RMSNorm)
+    else:
+        xq, sa, ld_a = quant_act_fp8(x2)
     rc = _lib.kernels().fb_gemm_fp8(_ptr(xq), K, _ptr(sa), ld_a, _ptr(lw.w), _ptr(_kernel_tensors(lw)[0]), _ptr(out), _ptr(bias), _ptr(res2),
                                     M, lw.n, K, out.stride(0), res2.stride(0) if res2 is not None else 0, dtype_code(x2.dtype), flags, 0,
                                     _stream())
@@ -147,6 +164,7 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
     if lw.kind not in _QMODE or x.dtype not in (torch.float16, torch.bfloat16):
         return None
     lead = x.shape[:-1]
+    pre = getattr(x, "fb_quant", None)
     x2 = x.reshape(-1, x.shape[-1])
     if x2.stride(-1) != 1:
         x2 = x2.contiguous()
@@ -171,10 +189,10 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
     if bias is not None and bias.dtype != x.dtype:
         bias = bias.to(x.dtype)
     if a8:
-        _linear_i8(x2, lw, out, bias, res2, flags)
+        _linear_i8(x2, lw, out, bias, res2, flags, pre)
         return out.reshape(*lead, n_out)
     if lw.kind == "fp8" and FP8_NATIVE and M <= 128 and x2.stride(0) % 4 == 0:
-        _linear_fp8_native(x2, lw, out, bias, res2, flags)
+        _linear_fp8_native(x2, lw, out, bias, res2, flags, pre)
         return out.reshape(*lead, n_out)
     if lw.kind == "fp8" and FP8_NATIVE:
         from .quant import fake_quant_act_fp8

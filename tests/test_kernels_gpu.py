@@ -590,3 +590,27 @@ def test_round_act(mode):
     assert ((got - ref).abs() <= step * 1.01 + ref.abs() / 64 + 1e-6).all()          # + bf16 rounding of both sides
     assert ((got - ref).abs() > 1e-6).float().mean() < 0.01
     _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_rmsnorm_fused_quant(mode):
+    """RMSNorm with the activation quantiser fused in: same 16-bit output as the plain norm, same bytes / scales / block sums as
+    the stand-alone quantiser applied to that output."""
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(mode)
+    for M, H in ((1, 1024), (37, 4096), (64, 2048)):
+        x = torch.randn(M, H, device=DEV).bfloat16()
+        w = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+        y0 = B.rmsnorm(x, w, 1e-5)
+        y = B.rmsnorm(x, w, 1e-5, quant_mode=mode)
+        assert torch.equal(y, y0)
+        m, xq, sa, xs, ld_a = y.fb_quant
+        assert m == mode
+        if mode == 1:
+            rq, rsa, rxs, _ = QG.quant_act_i8(y0)
+            assert torch.equal(xq, rq) and torch.equal(sa[:, :M], rsa[:, :M]) and torch.equal(xs[:, :M], rxs[:, :M])
+        else:
+            rq, rsa, _ = QG.quant_act_fp8(y0)
+            assert torch.equal(xq, rq) and torch.equal(sa[:, :M], rsa[:, :M])
+    _lib.check_device_errors()
