@@ -102,6 +102,31 @@ __global__ void rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* _
       for (int sft = 8; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(mask, amax, sft));
       const int kb = i >> 4;
       uint2 q;
+      if (QMODE == 3 || QMODE == 4) {
+        // y itself rounded to the int8 (3) / e4m3 (4) grid of its block: what a large batch feeds to the 16-bit-activation
+        // kernels of a layer whose small batches run on 8-bit activations
+        float v[8] = {a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y};
+        if (QMODE == 3) {
+          const float scale = fmaxf(amax, 1e-12f) / 127.0f, iv = 1.0f / scale;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = rintf(v[e] * iv) * scale;
+        } else {
+          const float scale = fmaxf(amax, 1e-12f) / 448.0f, iv = 1.0f / scale;
+          const uint32_t p0 = pack_e4m3x4(v[0] * iv, v[1] * iv, v[2] * iv, v[3] * iv), p1 = pack_e4m3x4(v[4] * iv, v[5] * iv, v[6] * iv, v[7] * iv);
+          const uint32_t pk[2] = {p0, p1};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            uint32_t h;
+            asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h) : "h"((uint16_t)(pk[e >> 1] >> (16 * (e & 1)))));
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h));
+            v[2 * e] = f.x * scale; v[2 * e + 1] = f.y * scale;
+          }
+        }
+        uint4 ro;
+        ro.x = pack_16<BF16>(v[0], v[1]); ro.y = pack_16<BF16>(v[2], v[3]); ro.z = pack_16<BF16>(v[4], v[5]); ro.w = pack_16<BF16>(v[6], v[7]);
+        yp[i] = ro;
+        continue;
+      }
       if (QMODE == 1) {
         const float scale = fmaxf(amax, 1e-12f) / 127.0f, iv = 1.0f / scale;
         const int q0 = __float2int_rn(a.x * iv), q1 = __float2int_rn(a.y * iv), q2 = __float2int_rn(b.x * iv), q3 = __float2int_rn(b.y * iv);
@@ -434,12 +459,12 @@ __global__ void route_topk_kernel(const RouteParams p) {
 using namespace fb;
 
 // RMSNorm that also emits the row quantised for an 8-bit-activation GEMM (mode 1: int8 + scales + block sums, mode 2: e4m3 +
-// scales; scale tables [H / 128, ld_a]).  H % 128 == 0.
+// scales; scale tables [H / 128, ld_a]), or writes y rounded to the int8 (mode 3) / e4m3 (mode 4) grid.  H % 128 == 0.
 extern "C" int fb_rmsnorm_quant(const void* x, const void* w, void* y, void* residual, int M, int H, int ldx, int ldy, float eps,
                                 float unit_offset, int dtype, int mode, void* xq, int ldq, float* scales, float* sums, int ld_a,
                                 void* stream) {
   if (M <= 0) return 0;
-  if (H % 128 != 0 || H > 32768 || (mode != 1 && mode != 2) || ldq % 8 != 0) return -1;
+  if (H % 128 != 0 || H > 32768 || mode < 1 || mode > 4 || (mode <= 2 && ldq % 8 != 0)) return -1;
   int threads = H / 8;
   threads = threads > 1024 ? 1024 : ((threads + 31) / 32) * 32;
   const size_t smem = (size_t)H * sizeof(float);
@@ -453,8 +478,8 @@ extern "C" int fb_rmsnorm_quant(const void* x, const void* w, void* y, void* res
     launch_k(rmsnorm_kernel<BF, QM>, dim3(M), dim3(threads), smem, s, 0, (const uint16_t*)x, (const uint16_t*)w, (uint16_t*)y, \
              (uint16_t*)residual, H, ldx, ldy, eps, unit_offset, qo);                                                          \
   }
-  if (dtype == 1) { if (mode == 1) FB_NQ(true, 1) else FB_NQ(true, 2) }
-  else { if (mode == 1) FB_NQ(false, 1) else FB_NQ(false, 2) }
+  if (dtype == 1) { if (mode == 1) FB_NQ(true, 1) else if (mode == 2) FB_NQ(true, 2) else if (mode == 3) FB_NQ(true, 3) else FB_NQ(true, 4) }
+  else { if (mode == 1) FB_NQ(false, 1) else if (mode == 2) FB_NQ(false, 2) else if (mode == 3) FB_NQ(false, 3) else FB_NQ(false, 4) }
 #undef FB_NQ
   return (int)cudaGetLastError();
 }

@@ -161,6 +161,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor
             out: torch.Tensor | None = None, quant_mode: int = 0) -> torch.Tensor:
     """RMSNorm over the last dim.  With ``residual`` given: ``residual += x`` in place, then normalise it.
 
+    ``quant_mode`` 3 / 4: ``y`` itself is rounded to the int8 / e4m3 grid per 128-wide block (``y.fb_quant = (mode, ...)`` marks it).
     ``quant_mode`` 1 (int8) / 2 (e4m3): the kernel also writes the row quantised per 128-wide block for the 8-bit-activation
     GEMM that consumes it; the result carries it as ``y.fb_quant = (mode, xq, scales, sums, ld_a)`` and the quantised linear
     layers pick it up instead of launching their own quantiser."""
@@ -180,7 +181,16 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, residual: torch.Tensor
         out = torch.empty((M, H), device=x.device, dtype=x.dtype)
     if residual is not None and not residual.is_contiguous():
         raise ValueError("residual must be contiguous")
-    if quant_mode and H % 128 == 0 and M <= 128 and x.dtype in (torch.float16, torch.bfloat16):
+    if quant_mode in (3, 4) and H % 128 == 0 and x.dtype in (torch.float16, torch.bfloat16):
+        # y rounded to the 8-bit grid its consumer's small-batch kernels use (large batches run on 16-bit activations)
+        rc = _lib.kernels().fb_rmsnorm_quant(_ptr(x2), _ptr(w), _ptr(out), _ptr(residual), M, H, x2.stride(0), out.stride(0), float(eps),
+                                             float(unit_offset), dtype_code(x.dtype), quant_mode, _ptr(None), 0, _ptr(None), _ptr(None), 0,
+                                             _stream())
+        _lib.check(rc, "fb_rmsnorm_quant")
+        y = out.reshape(x.shape)
+        y.fb_quant = (quant_mode, None, None, None, 0)
+        return y
+    if quant_mode in (1, 2) and H % 128 == 0 and M <= 128 and x.dtype in (torch.float16, torch.bfloat16):
         ld_a = (M + 128 + 3) // 4 * 4
         xq = torch.empty((M, H), device=x.device, dtype=torch.int8 if quant_mode == 1 else torch.uint8)
         sa = torch.empty((H // 128, ld_a), device=x.device, dtype=torch.float32)

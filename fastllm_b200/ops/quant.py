@@ -218,8 +218,11 @@ class LinearWeight:
             y = quant_gemm.linear_quant(x, self, residual, swiglu, out_f32)
             if y is not None:
                 return y
+            pre = getattr(x, "fb_quant", None)
             if self.kind == "fp8" and quant_gemm.FP8_NATIVE:
-                x = fake_quant_act_fp8(x)
+                if not (pre is not None and pre[0] == 4):
+                    x = fake_quant_act_fp8(x)
             elif quant_gemm.uses_int_a8(self):
-                x = fake_quant_act_i8(x)
+                if not (pre is not None and pre[0] == 3):
+                    x = fake_quant_act_i8(x)
         return B.linear(x, self.dequant(x.dtype), self.bias, residual, swiglu, self.interleaved, out_f32)

@@ -73,13 +73,14 @@ def round_act(x: torch.Tensor, mode: int) -> torch.Tensor:
 
 
 def act_quant_mode(lw, M: int) -> int:
-    """Which quantised form of its input ``lw`` consumes for ``M`` rows: 1 int8, 2 e4m3, 0 none (16-bit activations)."""
+    """Which form of its input ``lw`` consumes for ``M`` rows: 1 int8 bytes, 2 e4m3 bytes, 3 / 4 16-bit values rounded to the
+    int8 / e4m3 grid (batches above the 8-bit kernels' row limit), 0 plain 16-bit activations."""
     if lw is None or lw.k % 128 != 0 or lw.adapters:
         return 0
-    if uses_int_a8(lw) and M <= INT_A8_MAX_M[lw.kind]:
-        return 1
-    if lw.kind == "fp8" and FP8_NATIVE and M <= 128:
-        return 2
+    if uses_int_a8(lw):
+        return 1 if M <= INT_A8_MAX_M[lw.kind] else 3
+    if lw.kind == "fp8" and FP8_NATIVE:
+        return 2 if M <= 128 else 4
     return 0
 
 
@@ -197,9 +198,11 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
     if lw.kind == "fp8" and FP8_NATIVE:
         from .quant import fake_quant_act_fp8
 
-        x2 = fake_quant_act_fp8(x2)          # same activation rounding as the e4m3 x e4m3 path used for small batches
+        if not (pre is not None and pre[0] == 4):
+            x2 = fake_quant_act_fp8(x2)      # same activation rounding as the e4m3 x e4m3 path used for small batches
     elif uses_int_a8(lw):
-        x2 = round_act(x2, 0)                # same activation rounding as the int8 x int8 path used for small batches
+        if not (pre is not None and pre[0] == 3):
+            x2 = round_act(x2, 0)            # same activation rounding as the int8 x int8 path used for small batches
     lib = _lib.kernels()
     group = -1 if (lw.kind == "int8" and lw.signed) else (lw.group or 0)      # -1: int8 bytes hold q - 128
     for m0 in range(0, M, 256):

@@ -614,3 +614,19 @@ def test_rmsnorm_fused_quant(mode):
             rq, rsa, _ = QG.quant_act_fp8(y0)
             assert torch.equal(xq, rq) and torch.equal(sa[:, :M], rsa[:, :M])
     _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("mode", [3, 4])
+def test_rmsnorm_fused_rounding(mode):
+    """RMSNorm whose output is rounded to the int8 / e4m3 grid in the same launch == plain norm followed by the rounding kernel."""
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(mode)
+    for M, H in ((3, 1024), (300, 4096)):
+        x = torch.randn(M, H, device=DEV).bfloat16()
+        w = (1 + 0.1 * torch.randn(H, device=DEV)).bfloat16()
+        want = QG.round_act(B.rmsnorm(x, w, 1e-5), mode - 3)
+        got = B.rmsnorm(x, w, 1e-5, quant_mode=mode)
+        assert got.fb_quant[0] == mode
+        assert torch.equal(got, want)
+    _lib.check_device_errors()
