@@ -184,15 +184,17 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__
 struct Fp8GroupInfo {
   const int* counts; const int* offsets;
   int rows_per_chunk, chunks, n_rows_w;
+  int n_local, compact;        // compact: grid.z enumerates existing (expert, chunk) pairs (moe_find_item)
 };
 
 template <int MPAD, bool BF16>
 __global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
 moe_grouped_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                        const Fp8Scales sbase, const Fp8GroupInfo gi) {
-  const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
   pdl_launch_dependents();
   pdl_wait();                         // counts / offsets come from the plan kernel
+  if (gi.compact && !moe_find_item(gi.counts, gi.n_local, gi.rows_per_chunk, (int)blockIdx.z, e, chunk)) return;
   const int cnt = gi.counts[e];
   const int row0 = chunk * gi.rows_per_chunk;
   if (row0 >= cnt) return;            // uniform over the cluster (same blockIdx.z)
@@ -439,7 +441,8 @@ static cudaError_t launch_grouped_fp8(const CUtensorMap& tmW, const CUtensorMap&
 // high 16 bits = rows per chunk hint (0: derived).
 extern "C" int fb_moe_grouped_gemm_fp8(const void* xq, int ldq, const float* a_scale, int ld_a, const void* Wq, const float* w_scale,
                                        void* out, const int* counts, const int* offsets, int n_local, int N, int K, int rows_cap,
-                                       int ld_out, int dtype, int flags, int max_rows, void* stream_) {
+                                       int ld_out, int dtype, int flags, int max_rows, int total_rows, void* stream_) {
+  // total_rows > 0: upper bound of the routed rows over all local experts; the grid then has one slot per existing row chunk
   if (n_local <= 0 || rows_cap <= 0) return 0;
   if (K % 128 != 0 || N % 128 != 0) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
@@ -462,10 +465,16 @@ extern "C" int fb_moe_grouped_gemm_fp8(const void* xq, int ldq, const float* a_s
   sc.w_scale = w_scale; sc.a_scale = a_scale; sc.ld_a = ld_a;
   Fp8GroupInfo gi;
   gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
+  gi.n_local = n_local; gi.compact = 0;
+  int nz = n_local * chunks;
+  if (total_rows > 0) {
+    const int bound = n_local + (total_rows + mpad - 1) / mpad;       // sum of ceil(count / mpad) <= experts + rows / mpad
+    if (bound < nz) { nz = bound; gi.compact = 1; }
+  }
   cudaError_t e;
 #define FB_G8(MP)                                                                                                         \
-  e = dtype == 1 ? launch_grouped_fp8<MP, true>(tmW, tmX, p, sc, gi, 1, n_tiles, n_local * chunks, stream)                \
-                 : launch_grouped_fp8<MP, false>(tmW, tmX, p, sc, gi, 1, n_tiles, n_local * chunks, stream);              \
+  e = dtype == 1 ? launch_grouped_fp8<MP, true>(tmW, tmX, p, sc, gi, 1, n_tiles, nz, stream)                              \
+                 : launch_grouped_fp8<MP, false>(tmW, tmX, p, sc, gi, 1, n_tiles, nz, stream);                            \
   break;
   switch (mpad) {
     case 16: FB_G8(16)

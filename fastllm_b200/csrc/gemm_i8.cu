@@ -281,15 +281,17 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
 struct I8GroupInfo {
   const int* counts; const int* offsets;
   int rows_per_chunk, chunks, n_rows_w;
+  int n_local, compact;        // compact: grid.z enumerates existing (expert, chunk) pairs (moe_find_item)
 };
 
 template <int MPAD, bool BF16, int WK>
 __global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
 moe_grouped_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                       const I8Scales sbase, const I8GroupInfo gi) {
-  const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
   pdl_launch_dependents();
   pdl_wait();
+  if (gi.compact && !moe_find_item(gi.counts, gi.n_local, gi.rows_per_chunk, (int)blockIdx.z, e, chunk)) return;
   const int cnt = gi.counts[e];
   const int row0 = chunk * gi.rows_per_chunk;
   if (row0 >= cnt) return;
@@ -411,6 +413,7 @@ static int dispatch_i8(int mpad, int dtype, const CUtensorMap& tmW, const CUtens
 // wkind: 1 = int8 per channel (Wq int8 = q - 128, w_scale [N], w_zero = zero - 128 [N]);
 //        2 = int4 group 128 (Wq packed [N, K / 2], w_scale / w_zero (group minima) [N, K / 128]).
 // counts == null: plain GEMM, M <= 128.  counts != null: grouped over the expert-sorted buffer (rows_cap rows, n_local experts,
+// M = upper bound of the routed rows or 0,
 // max_rows: low 16 bits = most rows of one expert, high 16 bits = rows-per-chunk hint).
 extern "C" int fb_gemm_i8(const void* xq, int ldq, const float* a_scale, const float* a_sum, int ld_a, const void* Wq, const float* w_scale,
                           const float* w_zero, void* out, const void* bias, const void* residual, int M, int N, int K, int ld_out,
@@ -464,6 +467,12 @@ extern "C" int fb_gemm_i8(const void* xq, int ldq, const float* a_scale, const f
   p.idesc = make_idesc_i8(128, mpad);
   I8GroupInfo gi;
   gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
-  return wkind == WK_INT8 ? dispatch_i8<WK_INT8>(mpad, dtype, tmW, tmX, p, sc, &gi, 1, n_tiles, n_local * chunks, stream)
-                          : dispatch_i8<WK_INT4G>(mpad, dtype, tmW, tmX, p, sc, &gi, 1, n_tiles, n_local * chunks, stream);
+  gi.n_local = n_local; gi.compact = 0;
+  int nz = n_local * chunks;
+  if (M > 0) {                        // grouped call: M = upper bound of the routed rows over all local experts
+    const int bound = n_local + (M + mpad - 1) / mpad;
+    if (bound < nz) { nz = bound; gi.compact = 1; }
+  }
+  return wkind == WK_INT8 ? dispatch_i8<WK_INT8>(mpad, dtype, tmW, tmX, p, sc, &gi, 1, n_tiles, nz, stream)
+                          : dispatch_i8<WK_INT4G>(mpad, dtype, tmW, tmX, p, sc, &gi, 1, n_tiles, nz, stream);
 }

@@ -5,6 +5,37 @@
 
 namespace fb {
 
+// Grouped (mixture-of-experts) launches: grid slot j -> (expert, row chunk).  The slots enumerate only the chunks that exist,
+// expert by expert (sum over experts of ceil(count / rows_per_chunk)), so the grid needs E + rows / rows_per_chunk slots instead
+// of E * (most rows any expert could get / rows_per_chunk), nearly all of which would be empty.  Every warp computes the same
+// answer from the counts (a 32-wide scan per 32 experts); returns false for a slot past the last chunk.
+__device__ __forceinline__ bool moe_find_item(const int* __restrict__ counts, int n_local, int rows_per_chunk, int j, int& e, int& chunk) {
+  const int lane = threadIdx.x & 31;
+  int base = 0;
+  for (int e0 = 0; e0 < n_local; e0 += 32) {
+    const int ee = e0 + lane;
+    const int nch = ee < n_local ? (counts[ee] + rows_per_chunk - 1) / rows_per_chunk : 0;
+    int incl = nch;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    const int total = __shfl_sync(0xffffffffu, incl, 31);
+    if (j < base + total) {
+      const int excl = base + incl - nch;
+      const unsigned hit = __ballot_sync(0xffffffffu, j >= excl && j < excl + nch);
+      const int src = __ffs(hit) - 1;
+      e = e0 + src;
+      chunk = j - __shfl_sync(0xffffffffu, excl, src);
+      return true;
+    }
+    base += total;
+  }
+  return false;
+}
+
+
 constexpr int KID_GEMM_SMALLM_PLAIN = 1;
 constexpr int KID_GEMM_LARGEM = 2;
 

@@ -164,21 +164,21 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
     elif fp8_native:
         # W8A8: e4m3 x e4m3 grouped GEMMs; the SwiGLU output is quantised again for the down projection
         _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(xq), H, _ptr(sa), ld_a, _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(act), _ptr(counts),
-                                               _ptr(offsets), E, 2 * st.inter, H, rows_cap, st.inter, dt, GEMM_SWIGLU, max_rows, s),
+                                               _ptr(offsets), E, 2 * st.inter, H, rows_cap, st.inter, dt, GEMM_SWIGLU, max_rows, T * topk, s),
                    "fb_moe_grouped_gemm_fp8(gate_up)")
         aq, sb, ld_b = QG.quant_act_fp8(act, total)
         _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(aq), st.inter, _ptr(sb), ld_b, _ptr(st.down), _ptr(st.dn_scale), _ptr(ys), _ptr(counts),
-                                               _ptr(offsets), E, H, st.inter, rows_cap, H, dt, 0, max_rows, s),
+                                               _ptr(offsets), E, H, st.inter, rows_cap, H, dt, 0, max_rows, T * topk, s),
                    "fb_moe_grouped_gemm_fp8(down)")
     elif int_a8:
         wk = 1 if st.kind == "int8" else 2
         gs, gz, ds, dz = st.a8
         _lib.check(lib.fb_gemm_i8(_ptr(xq), H, _ptr(sa), _ptr(sx), ld_a, _ptr(st.gate_up), _ptr(gs), _ptr(gz), _ptr(act), _ptr(None),
-                                  _ptr(None), 0, 2 * st.inter, H, st.inter, 0, dt, GEMM_SWIGLU, wk, 1, _ptr(counts), _ptr(offsets), E,
+                                  _ptr(None), T * topk, 2 * st.inter, H, st.inter, 0, dt, GEMM_SWIGLU, wk, 1, _ptr(counts), _ptr(offsets), E,
                                   rows_cap, max_rows, s), "fb_gemm_i8(gate_up)")
         aq, sb, sbx, ld_b = QG.quant_act_i8(act, rows_used=total)
         _lib.check(lib.fb_gemm_i8(_ptr(aq), st.inter, _ptr(sb), _ptr(sbx), ld_b, _ptr(st.down), _ptr(ds), _ptr(dz), _ptr(ys), _ptr(None),
-                                  _ptr(None), 0, H, st.inter, H, 0, dt, 0, wk, 1, _ptr(counts), _ptr(offsets), E, rows_cap, max_rows, s),
+                                  _ptr(None), T * topk, H, st.inter, H, 0, dt, 0, wk, 1, _ptr(counts), _ptr(offsets), E, rows_cap, max_rows, s),
                    "fb_gemm_i8(down)")
     else:
         qm = {"int8": 1, "int4g": 2, "fp8": 3}[st.kind]

@@ -20,7 +20,7 @@ _lib.register_sigs({
     "fb_quant_act_fp8": [P, I, P, I, P, I, I, I, I, P, P],
     "fb_round_act": [P, I, P, I, I, I, I, I, P],
     "fb_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
-    "fb_moe_grouped_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
+    "fb_moe_grouped_gemm_fp8": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
     "fb_moe_gather_quant_fp8": [P, P, P, P, I, I, I, I, I, P],
     "fb_quant_act_i8": [P, I, P, I, P, P, I, I, I, I, P, P, I, P],
     "fb_gemm_i8": [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, I, I, P],
