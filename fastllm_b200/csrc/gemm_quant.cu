@@ -300,15 +300,17 @@ struct QuantGroupInfo {
   const int* counts; const int* offsets;
   int rows_per_chunk, chunks, n_rows_w;
   long long scale_stride_e, zero_stride_e;      // floats per expert
+  int n_local, compact;                         // compact: grid.z enumerates existing (expert, chunk) pairs (moe_find_item)
 };
 
 template <int MPAD, bool BF16, int QM>
 __global__ void __launch_bounds__((QuantCfg<MPAD, QM>::THREADS), (MPAD <= 64 ? 2 : 1))
 moe_grouped_quant_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                          const QuantParams qbase, const QuantGroupInfo gi) {
-  const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
   pdl_launch_dependents();
   pdl_wait();   // counts / offsets come from the plan kernel
+  if (gi.compact && !moe_find_item(gi.counts, gi.n_local, gi.rows_per_chunk, (int)blockIdx.z, e, chunk)) return;
   const int cnt = gi.counts[e];
   const int row0 = chunk * gi.rows_per_chunk;
   if (row0 >= cnt) return;
@@ -436,7 +438,8 @@ static cudaError_t launch_grouped_quant(const CUtensorMap& tmW, const CUtensorMa
 // Grouped quantised expert GEMM over the expert-sorted buffer; stacked Wq [E_local * N, K bytes], stacked scales.
 extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const float* scale, const float* zero, void* out,
                                          const int* counts, const int* offsets, int rows_cap, int E_local, int N, int K, int ld_out,
-                                         int max_rows_per_expert, int dtype, int qmode, int group_k, int flags, void* stream_) {
+                                         int max_rows_per_expert, int dtype, int qmode, int group_k, int flags, int total_rows,
+                                         void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (E_local <= 0 || rows_cap <= 0) return 0;
   if (K % 64 != 0 || N % 128 != 0 || (dtype != 0 && dtype != 1)) return -1;
@@ -472,7 +475,12 @@ extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const f
   CUtensorMap tmW, tmX;
   if (!make_tmap_2d(&tmW, Wq, (uint64_t)E_local * N, kbytes, kbytes, 128, qmode == Q_INT4G ? 32 : 64, 1, 0)) return -2;
   if (!make_tmap_2d(&tmX, Xs, rows_cap, K, K, mpad, 64, 2, 3)) return -2;
-  const int nz = E_local * chunks;
+  int nz = E_local * chunks;
+  gi.n_local = E_local; gi.compact = 0;
+  if (total_rows > 0) {               // upper bound of the routed rows: one grid slot per existing row chunk
+    const int bound = E_local + (total_rows + mpad - 1) / mpad;
+    if (bound < nz) { nz = bound; gi.compact = 1; }
+  }
   if (nz > 65535) return -1;
 #define FB_GQ2(MP, QMV)                                                                                          \
   return (int)(bf16 ? launch_grouped_quant<MP, true, QMV>(tmW, tmX, p, qp, gi, nsplit, n_tiles, nz, stream)       \

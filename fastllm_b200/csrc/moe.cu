@@ -30,6 +30,7 @@ struct MoeGroupInfo {
   int n_rows_w;            // weight rows per expert in the stacked matrix
   long long out_stride_e;  // unused (outputs follow the sorted rows)
   int ld_bias_e;           // bias elements per expert (0: no per-expert stride)
+  int n_local, compact;    // compact: grid.z enumerates existing (expert, chunk) pairs (moe_find_item)
 };
 
 // counts/offsets/pos for the experts in [first, first + n_local)
@@ -161,9 +162,10 @@ template <int MPAD, bool BF16>
 __global__ void __launch_bounds__(192, 1)
 moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                         const MoeGroupInfo gi) {
-  const int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
+  int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
   pdl_launch_dependents();
   pdl_wait();   // counts / offsets come from the plan kernel
+  if (gi.compact && !moe_find_item(gi.counts, gi.n_local, gi.rows_per_chunk, (int)blockIdx.z, e, chunk)) return;
   const int cnt = gi.counts[e];
   const int row0 = chunk * gi.rows_per_chunk;
   if (row0 >= cnt) return;                          // uniform over the cluster (same blockIdx.z)
@@ -242,7 +244,7 @@ extern "C" int fb_moe_combine(const void* ys, const int* pos, const float* w, co
 // max_rows_per_expert bounds the chunk count (T for decode: every token could pick the same expert).
 extern "C" int fb_moe_grouped_gemm(const void* Xs, const void* W, void* out, const void* bias, const int* counts, const int* offsets,
                                    int rows_cap, int E_local, int N, int K, int ld_out, int max_rows_per_expert, int dtype, int flags,
-                                   void* stream_) {
+                                   int total_rows, void* stream_) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (E_local <= 0 || rows_cap <= 0) return 0;
   if (K % 64 != 0 || N % 128 != 0 || (dtype != 0 && dtype != 1)) return -1;
@@ -271,7 +273,12 @@ extern "C" int fb_moe_grouped_gemm(const void* Xs, const void* W, void* out, con
   CUtensorMap tmW, tmX;
   if (!make_tmap_2d(&tmW, W, (uint64_t)E_local * N, K, K, 128, 64, 2, 3)) return -2;
   if (!make_tmap_2d(&tmX, Xs, rows_cap, K, K, mpad, 64, 2, 3)) return -2;
-  const int nz = E_local * chunks;
+  int nz = E_local * chunks;
+  gi.n_local = E_local; gi.compact = 0;
+  if (total_rows > 0) {               // upper bound of the routed rows: one grid slot per existing row chunk
+    const int bound = E_local + (total_rows + mpad - 1) / mpad;
+    if (bound < nz) { nz = bound; gi.compact = 1; }
+  }
   if (nz > 65535) return -1;
 #define FB_MG(MP)                                                                                              \
   return (int)(bf16 ? launch_grouped<MP, true>(tmW, tmX, p, gi, nsplit, n_tiles, nz, stream)                    \

@@ -21,8 +21,8 @@ _lib.register_sigs({
     "fb_moe_plan": [P, I, I, I, I, P, P, P, P, I, P],
     "fb_moe_gather": [P, P, P, I, I, I, P],
     "fb_moe_combine": [P, P, P, P, P, I, I, I, I, P],
-    "fb_moe_grouped_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, P],
-    "fb_moe_grouped_gemm_quant": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
+    "fb_moe_grouped_gemm": [P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P],
+    "fb_moe_grouped_gemm_quant": [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, P],
 }, ["moe"])
 
 GRAPH_SAFE = True
@@ -158,9 +158,9 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
         _lib.check(lib.fb_moe_gather(_ptr(x.contiguous()), _ptr(pos), _ptr(xs), T, topk, H, s), "fb_moe_gather")
     if st.kind == "dense":
         _lib.check(lib.fb_moe_grouped_gemm(_ptr(xs), _ptr(st.gate_up), _ptr(act), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
-                                           2 * st.inter, H, st.inter, max_rows, dt, GEMM_SWIGLU, s), "fb_moe_grouped_gemm(gate_up)")
+                                           2 * st.inter, H, st.inter, max_rows, dt, GEMM_SWIGLU, T * topk, s), "fb_moe_grouped_gemm(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm(_ptr(act), _ptr(st.down), _ptr(ys), _ptr(None), _ptr(counts), _ptr(offsets), rows_cap, E,
-                                           H, st.inter, H, max_rows, dt, 0, s), "fb_moe_grouped_gemm(down)")
+                                           H, st.inter, H, max_rows, dt, 0, T * topk, s), "fb_moe_grouped_gemm(down)")
     elif fp8_native:
         # W8A8: e4m3 x e4m3 grouped GEMMs; the SwiGLU output is quantised again for the down projection
         _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(xq), H, _ptr(sa), ld_a, _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(act), _ptr(counts),
@@ -185,9 +185,9 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
         grp = -1 if st.signed else (st.group or 0)           # -1: int8 bytes hold q - 128
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(xs), _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(st.gu_zero), _ptr(act), _ptr(counts),
                                                  _ptr(offsets), rows_cap, E, 2 * st.inter, H, st.inter, max_rows, dt, qm, grp,
-                                                 GEMM_SWIGLU, s), "fb_moe_grouped_gemm_quant(gate_up)")
+                                                 GEMM_SWIGLU, T * topk, s), "fb_moe_grouped_gemm_quant(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(act), _ptr(st.down), _ptr(st.dn_scale), _ptr(st.dn_zero), _ptr(ys), _ptr(counts),
-                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, max_rows, dt, qm, grp, 0, s),
+                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, max_rows, dt, qm, grp, 0, T * topk, s),
                    "fb_moe_grouped_gemm_quant(down)")
     if not combine:
         return ys, pos, wts
