@@ -7,7 +7,7 @@
 // fb_quant_act_i8, which also records the block sums of the quantised values (needed for zero points / group minima).
 // One k block = four K=32 MMAs into one buffer of a TMEM ring (exact int32 sums); the promotion warps turn it into fp32:
 //     int8 per channel  (w = s_n (q - z_n)):        acc[m] += sum * a[m,kb];   T[m] += xs[m,kb] * a[m,kb]   finally s_n (acc - z'_n T)
-//     int4 group g = kb (w = min_ng + s_ng q):      acc[m] += (sum * s_ng + min_ng * xs[m,kb]) * a[m,kb]
+//     int4 group g = kb (w = min_ng + s_ng q):      acc[m] += (sum * s_ng + min_ng * xs[m,kb]) * a[m,kb]     ((s, min) as [kb, n] pairs)
 // with z' = z - 128, xs = sum of the quantised activations of the block, a = activation scale.  The a / xs rows of a k block
 // travel with its tiles (bulk copy into the stage), so the promotion reads them from shared memory instead of waiting on L2
 // once per k block.  Split-K clusters and the epilogue are the ones of the 16-bit decode GEMM.
@@ -48,8 +48,9 @@ struct I8Cfg {
 };
 
 struct I8Scales {
-  const float* w_scale;      // int8: [N];  int4g: [N, kb_total]
-  const float* w_zero;       // int8: zero point - 128 [N];  int4g: group minima [N, kb_total]
+  const float* w_scale;      // int8: [N];  int4g: float2 (scale, min) [kb_total, n_rows] (a warp reads one line per k block)
+  const float* w_zero;       // int8: zero point - 128 [N];  int4g: unused
+  int n_rows;                // int4g: rows of the (scale, min) table = weight rows of this matrix
   const float* a_scale;      // [kb_total, ld_a]
   const float* a_sum;        // [kb_total, ld_a]  sums of the quantised activations per block
   int ld_a;
@@ -217,8 +218,8 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
       const int b = i % Cfg::NBUF, s = i % Cfg::STAGES;
       float wa = 1.f, wb = 0.f;
       if (WK == WK_INT4G && n_ok) {                 // issued before the wait: the latency overlaps the MMA of this block
-        wa = __ldg(sc.w_scale + (size_t)n_glob * p.kb_total + kb0 + i);
-        wb = __ldg(sc.w_zero + (size_t)n_glob * p.kb_total + kb0 + i);
+        const float2 sm = __ldg(reinterpret_cast<const float2*>(sc.w_scale) + (size_t)(kb0 + i) * sc.n_rows + n_tile * 128 + n_local);
+        wa = sm.x; wb = sm.y;
       }
       // the scale rows are written by the bulk copies that complete on full_bar: observe it in this thread too
       if (WK == WK_INT8 && !mbar_wait(&full_bar[s], (uint32_t)(i / Cfg::STAGES) & 1u, dead, KID_GEMM_I8, 8)) break;
@@ -301,7 +302,9 @@ moe_grouped_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_cons
   p.x_row0 = seg;
   p.w_row0 = e * gi.n_rows_w;         // per-row scale tables of the stacked experts are indexed by w_row0 + row
   p.out = reinterpret_cast<uint16_t*>(base.out) + (size_t)seg * base.ld_out;
-  gemm_i8_device<MPAD, BF16, WK>(tmW, tmX, p, sbase);
+  I8Scales sc = sbase;
+  if (WK == WK_INT4G) sc.w_scale = sbase.w_scale + (size_t)e * base.kb_total * gi.n_rows_w * 2;      // [E, kb_total, N, 2]
+  gemm_i8_device<MPAD, BF16, WK>(tmW, tmX, p, sc);
 }
 
 // ---- activation quantisation: x [M, K] 16-bit -> int8 [M, K], scales and block sums [K / 128, ld_a] ------------------------
@@ -411,7 +414,7 @@ static int dispatch_i8(int mpad, int dtype, const CUtensorMap& tmW, const CUtens
 }
 
 // wkind: 1 = int8 per channel (Wq int8 = q - 128, w_scale [N], w_zero = zero - 128 [N]);
-//        2 = int4 group 128 (Wq packed [N, K / 2], w_scale / w_zero (group minima) [N, K / 128]).
+//        2 = int4 group 128 (Wq packed [N, K / 2], w_scale = float2 (scale, min) [K / 128, N], per expert when grouped; w_zero unused).
 // counts == null: plain GEMM, M <= 128.  counts != null: grouped over the expert-sorted buffer (rows_cap rows, n_local experts,
 // M = upper bound of the routed rows or 0,
 // max_rows: low 16 bits = most rows of one expert, high 16 bits = rows-per-chunk hint).
@@ -434,7 +437,7 @@ extern "C" int fb_gemm_i8(const void* xq, int ldq, const float* a_scale, const f
   p.out = out; p.bias = bias; p.residual = residual; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = ld_res; p.flags = flags;
   p.kb_total = kb_total;
   I8Scales sc;
-  sc.w_scale = w_scale; sc.w_zero = w_zero; sc.a_scale = a_scale; sc.a_sum = a_sum; sc.ld_a = ld_a;
+  sc.w_scale = w_scale; sc.w_zero = w_zero; sc.a_scale = a_scale; sc.a_sum = a_sum; sc.ld_a = ld_a; sc.n_rows = N;
   CUtensorMap tmW, tmX;
   int mpad = 16;
   if (counts == nullptr) {

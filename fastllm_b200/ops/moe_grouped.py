@@ -55,6 +55,9 @@ def _prepare_a8(st: StackedExperts, experts) -> None:
             st.signed = True
             for w in experts.gate_up + experts.down:
                 w.signed = True
+    if st.kind == "int4g":          # the stacked (scale, min) pair tables [E, groups, N, 2] of the 16-bit route serve both
+        st.a8 = (st.gu_scale, None, st.dn_scale, None)
+        return
     cat = lambda ws, f: torch.cat([f(w).float().reshape(w.n, -1) for w in ws], dim=0).contiguous()
     st.a8 = (cat(experts.gate_up, lambda w: w.scale), cat(experts.gate_up, lambda w: w.zero) - shift,
              cat(experts.down, lambda w: w.scale), cat(experts.down, lambda w: w.zero) - shift)

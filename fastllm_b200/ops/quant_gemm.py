@@ -102,9 +102,7 @@ def _a8_tensors(lw):
         if lw._a8 is None:
             lw._a8 = (lw.scale.float().contiguous(), (lw.zero.float() - 128.0).contiguous())
         return lw.w, lw._a8[0], lw._a8[1], 1
-    if lw._a8 is None:
-        lw._a8 = (lw.scale.float().contiguous(), lw.zero.float().contiguous())
-    return lw.w, lw._a8[0], lw._a8[1], 2
+    return lw.w, _kernel_tensors(lw)[0], None, 2          # (scale, min) pairs [groups, N, 2], shared with the 16-bit route
 
 
 def _linear_i8(x2, lw, out, bias, res2, flags, pre=None):
