@@ -43,6 +43,11 @@ struct I8Cfg {
   static constexpr int PIPE_BYTES = DQ_SLOTS * A_BYTES + STAGES * STAGE_BYTES;
   static constexpr int BODY_BYTES = PIPE_BYTES > RED_BYTES ? PIPE_BYTES : RED_BYTES;
   static constexpr int SMEM_BYTES = BODY_BYTES + 1024 + 1024;          // barriers (256 B) + zero-point sums T (MPAD floats at +512)
+  // int4g with few rows: four extra warps do nothing but unpack nibbles, so the unpack of block i + 1 and the promotion of
+  // block i run side by side instead of one after the other in the same four warps (102 registers per thread at two CTAs
+  // per SM are enough for sixteen accumulators)
+  static constexpr bool SPLIT = WK == WK_INT4G && MPAD <= 16;
+  static constexpr int THREADS = SPLIT ? 320 : 192;
   static constexpr int NBUF = MPAD <= 64 ? 4 : 2;                        // TMEM accumulator ring
   static constexpr int TMEM_COLS = NBUF * MPAD < 32 ? 32 : NBUF * MPAD;
 };
@@ -71,6 +76,41 @@ __host__ __device__ constexpr uint32_t make_idesc_i8(uint32_t M, uint32_t N) {
 // int32 block sum -> float without the conversion pipe: |v| < 2^22 (127 * 128 * 128 at most), so v + 0x4B400000 is the bit
 // pattern of 1.5 * 2^23 + v
 __device__ __forceinline__ float sum_to_float(uint32_t v) { return __uint_as_float(v + 0x4B400000u) - 12582912.0f; }
+
+// int4g: unpack the packed tile of k block i into operand slot i & 1 (thread t of 128 handles 16-byte chunks t, t + 128, ...)
+template <class Cfg>
+__device__ __forceinline__ void unpack_int4_tile(int i, int tid, uint8_t* stages, uint8_t* dq, uint64_t* full_bar, uint64_t* empty_bar,
+                                                 uint64_t* dq_full, uint64_t* dq_empty, bool& dead) {
+      const int s = i % Cfg::STAGES, b = i & 1;
+      const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = ((uint32_t)i >> 1) & 1u;
+  if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_I8, 6)) return;
+      if (!mbar_wait(&dq_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 7)) return;
+      const uint8_t* raw = stages + s * Cfg::STAGE_BYTES + Cfg::B_BYTES;
+      uint8_t* out = dq + b * Cfg::A_BYTES;
+      uint4 pk[4];                                         // all four loads first: the stores below must not serialise them
+#pragma unroll
+      for (int it = 0; it < 4; ++it) pk[it] = *reinterpret_cast<const uint4*>(raw + (tid + it * 128) * 16);
+#pragma unroll
+      for (int it = 0; it < 4; ++it) {
+        const int idx = tid + it * 128;                  // 512 chunks of 16 packed bytes
+        const int row = idx >> 2, c4 = idx & 3;
+        uint32_t o[8];
+        const uint32_t w4[4] = {pk[it].x, pk[it].y, pk[it].z, pk[it].w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t hi = (w4[e] >> 4) & 0x0F0F0F0Fu, lo = w4[e] & 0x0F0F0F0Fu;      // first value of a byte = high nibble
+          o[2 * e] = __byte_perm(hi, lo, 0x5140);
+          o[2 * e + 1] = __byte_perm(hi, lo, 0x7362);
+        }
+        uint8_t* rowp = out + row * 128;
+        const int c0 = 2 * c4, c1 = 2 * c4 + 1;
+        *reinterpret_cast<uint4*>(rowp + ((c0 ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(rowp + ((c1 ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(&dq_full[b]);
+      if (Cfg::SPLIT) mbar_arrive(&empty_bar[s]);          // dedicated unpack warps: the packed tile is theirs to release
+}
 
 template <int MPAD, bool BF16, int WK>
 __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const I8Scales& sc) {
@@ -101,7 +141,7 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 129); }
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], Cfg::SPLIT ? 257 : 129); }
     for (int b = 0; b < Cfg::NBUF; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); }
     for (int b = 0; b < 2; ++b) { mbar_init(&dq_full[b], 128); mbar_init(&dq_empty[b], 1); }
     mbar_init_fence();
@@ -165,6 +205,10 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
       }
     }
     __syncwarp();
+  } else if (warp >= 6) {
+    // dedicated unpack warps (SPLIT configurations only)
+    const int tid = threadIdx.x - 192;
+    for (int i = 0; i < kb_cnt; ++i) unpack_int4_tile<Cfg>(i, tid, stages, dq, full_bar, empty_bar, dq_full, dq_empty, dead);
   } else {
     const int q = warp & 3;
     const int n_local = q * 32 + lane;
@@ -180,41 +224,9 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
     if (WK == WK_INT8 && n_ok) { zrow = sc.w_zero[n_glob]; srow = sc.w_scale[n_glob]; }
     constexpr int CH = MPAD < 32 ? MPAD : 32;
 
-    // int4g: unpack the packed tile of k block i into operand slot i & 1 (thread t handles 16-byte chunks t, t+128, ...)
-    auto unpack = [&](int i) {
-      const int s = i % Cfg::STAGES, b = i & 1;
-      const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = ((uint32_t)i >> 1) & 1u;
-      if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_I8, 6)) return;
-      if (!mbar_wait(&dq_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 7)) return;
-      const uint8_t* raw = stages + s * Cfg::STAGE_BYTES + Cfg::B_BYTES;
-      uint8_t* out = dq + b * Cfg::A_BYTES;
-      uint4 pk[4];                                         // all four loads first: the stores below must not serialise them
-#pragma unroll
-      for (int it = 0; it < 4; ++it) pk[it] = *reinterpret_cast<const uint4*>(raw + (tid + it * 128) * 16);
-#pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int idx = tid + it * 128;                  // 512 chunks of 16 packed bytes
-        const int row = idx >> 2, c4 = idx & 3;
-        uint32_t o[8];
-        const uint32_t w4[4] = {pk[it].x, pk[it].y, pk[it].z, pk[it].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t hi = (w4[e] >> 4) & 0x0F0F0F0Fu, lo = w4[e] & 0x0F0F0F0Fu;      // first value of a byte = high nibble
-          o[2 * e] = __byte_perm(hi, lo, 0x5140);
-          o[2 * e + 1] = __byte_perm(hi, lo, 0x7362);
-        }
-        uint8_t* rowp = out + row * 128;
-        const int c0 = 2 * c4, c1 = 2 * c4 + 1;
-        *reinterpret_cast<uint4*>(rowp + ((c0 ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4*>(rowp + ((c1 ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&dq_full[b]);
-    };
-
-    if (WK == WK_INT4G && kb_cnt > 0) unpack(0);
+    if (WK == WK_INT4G && !Cfg::SPLIT && kb_cnt > 0) unpack_int4_tile<Cfg>(0, tid, stages, dq, full_bar, empty_bar, dq_full, dq_empty, dead);
     for (int i = 0; i < kb_cnt; ++i) {
-      if (WK == WK_INT4G && i + 1 < kb_cnt) unpack(i + 1);
+      if (WK == WK_INT4G && !Cfg::SPLIT && i + 1 < kb_cnt) unpack_int4_tile<Cfg>(i + 1, tid, stages, dq, full_bar, empty_bar, dq_full, dq_empty, dead);
       const int b = i % Cfg::NBUF, s = i % Cfg::STAGES;
       float wa = 1.f, wb = 0.f;
       if (WK == WK_INT4G && n_ok) {                 // issued before the wait: the latency overlaps the MMA of this block
@@ -222,7 +234,7 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
         wa = sm.x; wb = sm.y;
       }
       // the scale rows are written by the bulk copies that complete on full_bar: observe it in this thread too
-      if (WK == WK_INT8 && !mbar_wait(&full_bar[s], (uint32_t)(i / Cfg::STAGES) & 1u, dead, KID_GEMM_I8, 8)) break;
+      if ((WK == WK_INT8 || Cfg::SPLIT) && !mbar_wait(&full_bar[s], (uint32_t)(i / Cfg::STAGES) & 1u, dead, KID_GEMM_I8, 8)) break;
       if (!mbar_wait(&tm_full[b], (uint32_t)(i / Cfg::NBUF) & 1u, dead, KID_GEMM_I8, 4)) break;
       tc_fence_after_sync();
       const float4* asp = reinterpret_cast<const float4*>(stages + s * Cfg::STAGE_BYTES + Cfg::SC_OFF);      // same address in every lane
@@ -274,7 +286,7 @@ __device__ __forceinline__ void gemm_i8_device(const CUtensorMap& tmW, const CUt
 }
 
 template <int MPAD, bool BF16, int WK>
-__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+__global__ void __launch_bounds__((I8Cfg<MPAD, WK>::THREADS), (MPAD <= 64 ? 2 : 1))
 gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p, const I8Scales sc) {
   gemm_i8_device<MPAD, BF16, WK>(tmW, tmX, p, sc);
 }
@@ -286,7 +298,7 @@ struct I8GroupInfo {
 };
 
 template <int MPAD, bool BF16, int WK>
-__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+__global__ void __launch_bounds__((I8Cfg<MPAD, WK>::THREADS), (MPAD <= 64 ? 2 : 1))
 moe_grouped_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams base,
                       const I8Scales sbase, const I8GroupInfo gi) {
   int e = blockIdx.z / gi.chunks, chunk = blockIdx.z - e * gi.chunks;
@@ -370,7 +382,7 @@ static cudaError_t launch_i8(const CUtensorMap& tmW, const CUtensorMap& tmX, con
   using Cfg = I8Cfg<MPAD, WK>;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(nsplit, n_tiles, nz);
-  cfg.blockDim = dim3(192, 1, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];

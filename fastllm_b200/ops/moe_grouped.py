@@ -130,6 +130,8 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
     # more rows simply run more chunks
     mean = max(1, (T * topk) // max(1, experts.total))
     hint = 16 if mean <= 6 else 32 if mean <= 12 else 64 if mean <= 24 else 128
+    if st.kind == "int4g" and QG.INT_A8 and mean <= 12:
+        hint = 16          # the 16-row integer kernel has dedicated unpack warps; a second chunk re-reads its weights from L2
     max_rows = min(T, 0xFFFF) | (hint << 16)
     counts = torch.empty(E, device=dev, dtype=torch.int32)
     offsets = torch.empty(E, device=dev, dtype=torch.int32)
