@@ -345,11 +345,20 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   if (warp == 1) tmem_dealloc(tmem_s, 32);
 }
 
+// Optional second output of the combine: its row quantised for the 8-bit-activation output projection.  One (request, head)
+// row of 128 values is exactly one 128-wide k block of that projection (QMODE 1: int8 + scale + block sum, 2: e4m3 + scale;
+// tables [Hq, ld_a]), computed from the 16-bit-rounded output so it equals what the stand-alone quantiser would produce.
+struct CombineQuant {
+  uint8_t* xq; int ldq;
+  float* scales; float* sums;
+  int ld_a;
+};
+
 // ---- combine: one CTA per (request, query head), 128 threads = head dims --------------------------
-template <bool BF16>
+template <bool BF16, int QMODE = 0>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            const int* __restrict__ seq_lens, uint16_t* __restrict__ out, int ld_out, int Hq,
-                                           int Hkv, int G, int max_splits) {
+                                           int Hkv, int G, int max_splits, CombineQuant cq = {}) {
   const int b = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
   const int kvh = hq / G, g = hq - kvh * G;
   pdl_launch_dependents();
@@ -369,6 +378,34 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
   const float o = ns > 0 ? acc / L : 0.f;
   uint16_t bits = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
   out[(size_t)b * ld_out + (size_t)hq * AD_D + d] = bits;
+  if (QMODE != 0) {
+    __shared__ float red[8];
+    const float v = BF16 ? __bfloat162float(__ushort_as_bfloat16(bits)) : __half2float(__ushort_as_half(bits));
+    float amax = fabsf(v);
+#pragma unroll
+    for (int sft = 16; sft > 0; sft >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, sft));
+    if ((d & 31) == 0) red[d >> 5] = amax;
+    __syncthreads();
+    amax = fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3]));
+    if (QMODE == 1) {
+      const float scale = fmaxf(amax, 1e-12f) / 127.0f, iv = 1.0f / scale;
+      const int q = __float2int_rn(v * iv);
+      cq.xq[(size_t)b * cq.ldq + (size_t)hq * AD_D + d] = (uint8_t)(q & 0xFF);
+      int sm = q;
+#pragma unroll
+      for (int sft = 16; sft > 0; sft >>= 1) sm += __shfl_xor_sync(0xffffffffu, sm, sft);
+      if ((d & 31) == 0) red[4 + (d >> 5)] = (float)sm;
+      __syncthreads();
+      if (d == 0) {
+        cq.scales[(size_t)hq * cq.ld_a + b] = scale;
+        cq.sums[(size_t)hq * cq.ld_a + b] = red[4] + red[5] + red[6] + red[7];
+      }
+    } else {
+      const float scale = fmaxf(amax, 1e-12f) / 448.0f, iv = 1.0f / scale;
+      cq.xq[(size_t)b * cq.ldq + (size_t)hq * AD_D + d] = (uint8_t)(pack_e4m3x4(v * iv, 0.f, 0.f, 0.f) & 0xFFu);
+      if (d == 0) cq.scales[(size_t)hq * cq.ld_a + b] = scale;
+    }
+  }
 }
 
 }  // namespace fb
@@ -390,8 +427,14 @@ extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n
 extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
                               const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
                               int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, int max_items,
-                              float scale, int dtype, int grid_ctas, int* counters, void* stream_) {
+                              float scale, int dtype, int grid_ctas, int* counters, int qmode, void* xq, int ldq, float* q_scales,
+                              float* q_sums, int ld_a, void* stream_) {
+  // qmode 1 / 2: the combine also writes the output quantised to int8 / e4m3 per (request, head) for the output projection
+  // (xq [B, Hq * 128] bytes, q_scales / q_sums [Hq, ld_a]); needs the separate combine kernel (counters == null)
   if (B <= 0) return 0;
+  if (qmode != 0 && (counters != nullptr || (qmode != 1 && qmode != 2))) return -1;
+  CombineQuant cq;
+  cq.xq = (uint8_t*)xq; cq.ldq = ldq; cq.scales = q_scales; cq.sums = q_sums; cq.ld_a = ld_a;
   if (D != AD_D || Hq % Hkv != 0) return -1;
   const int G = Hq / Hkv;
   if (G > AD_NPAD) return -1;
@@ -427,8 +470,12 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
     static DeviceOnce cfg;                                                                                            \
     if (cfg.need()) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); } \
     launch_k<PDL_ATTN>(attn_decode_kernel<BF, ST, GPV>, dim3(grid_ctas), dim3(192), ad_smem_bytes(ST), stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
-    if (counters == nullptr)                                                                                            \
-      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits); \
+    if (counters == nullptr && qmode == 0)                                                                              \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq); \
+    else if (counters == nullptr && qmode == 1)                                                                         \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 1>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq); \
+    else if (counters == nullptr)                                                                                       \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 2>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq); \
   }
 #define FB_AD_GP(BF)                                                                                                    \
   {                                                                                                                     \
@@ -542,10 +589,10 @@ extern "C" int fb_attn_decode_static(const void* q, const void* k_pool, const vo
   const int grid = 2 * sms;
   if (dtype == 1) {
     attn_decode_kernel<true, 1, 16><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, tmK, tmV, p);
-    attn_decode_combine_kernel<true><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages);
+    attn_decode_combine_kernel<true, 0><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages, CombineQuant{});
   } else {
     attn_decode_kernel<false, 1, 16><<<grid, 192, ad_smem_bytes(1), stream>>>(tmK, tmV, tmQ, tmK, tmV, p);
-    attn_decode_combine_kernel<false><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages);
+    attn_decode_combine_kernel<false, 0><<<dim3(B, Hq), AD_D, 0, stream>>>(part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_pages, CombineQuant{});
   }
   return (int)cudaGetLastError();
 }

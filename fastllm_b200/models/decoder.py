@@ -196,8 +196,14 @@ class DecoderModel:
         q = A.qkv_post(qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
                        lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
         if fb.is_decode:
+            qm = 0
+            if lw.o.kind != "dense" and lw.post_ln is None:
+                from ..ops import quant_gemm
+
+                qm = quant_gemm.act_quant_mode(lw.o, q.shape[0])
+                qm = qm if qm in (1, 2) else 0
             a = A.attn_decode(q, k_pool, v_pool, fb.page_table, fb.kv_lens, self.attn_scale, Hq, Hkv, D, ws=fb.decode_ws,
-                              planned=fb.decode_planned)
+                              planned=fb.decode_planned, quant_mode=qm)
         else:
             a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
                                cu_q_host=fb.cu_q_host)

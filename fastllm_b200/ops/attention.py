@@ -261,8 +261,11 @@ class DecodeWorkspace:
 
 
 def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num_kv_heads, head_dim,
-                ws: DecodeWorkspace | None = None, out=None, planned=False, grid_ctas=0):
-    """One new token per request. q: ``[B, Hq*D]`` -> ``[B, Hq*D]``."""
+                ws: DecodeWorkspace | None = None, out=None, planned=False, grid_ctas=0, quant_mode: int = 0):
+    """One new token per request. q: ``[B, Hq*D]`` -> ``[B, Hq*D]``.
+
+    ``quant_mode`` 1 (int8) / 2 (e4m3): the combine kernel also writes the output quantised per (request, head) -- one 128-wide
+    k block of the output projection -- and the result carries it as ``out.fb_quant`` (see ``ops.basic.rmsnorm``)."""
     B = q.shape[0]
     if not q.is_cuda:
         cu = torch.arange(B + 1, dtype=torch.int32)
@@ -283,11 +286,25 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
     if out is None:
         out = torch.empty_like(q)
     num_slots = k_pool.shape[0] * k_pool.shape[1]
+    xq = sa = xs = None
+    ld_a = 0
+    if quant_mode in (1, 2) and not _FUSED_COMBINE and B <= 128:
+        K = num_q_heads * head_dim
+        ld_a = (B + 128 + 3) // 4 * 4
+        xq = torch.empty((B, K), device=q.device, dtype=torch.int8 if quant_mode == 1 else torch.uint8)
+        sa = torch.empty((num_q_heads, ld_a), device=q.device, dtype=torch.float32)
+        xs = torch.empty((num_q_heads, ld_a), device=q.device, dtype=torch.float32) if quant_mode == 1 else None
+    else:
+        quant_mode = 0
     rc = _lib.kernels().fb_attn_decode(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(ws.work),
                                        _ptr(ws.n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
                                        num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
-                                       ws.work.shape[0], float(scale), dtype_code(q.dtype), grid_ctas, _ptr(ws.counters if _FUSED_COMBINE else None), _stream())
+                                       ws.work.shape[0], float(scale), dtype_code(q.dtype), grid_ctas,
+                                       _ptr(ws.counters if _FUSED_COMBINE else None), quant_mode, _ptr(xq),
+                                       num_q_heads * head_dim, _ptr(sa), _ptr(xs), ld_a, _stream())
     _lib.check(rc, "fb_attn_decode")
+    if quant_mode:
+        out.fb_quant = (quant_mode, xq, sa, xs, ld_a)
     return out
 
 

@@ -630,3 +630,31 @@ def test_rmsnorm_fused_rounding(mode):
         assert got.fb_quant[0] == mode
         assert torch.equal(got, want)
     _lib.check_device_errors()
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_attn_decode_fused_quant(mode):
+    """Decode attention whose combine also quantises the output for the output projection: same 16-bit output, same bytes /
+    scales / block sums as the stand-alone quantiser applied to it."""
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(6)
+    Hq, Hkv, D, dt = 8, 2, 128, torch.bfloat16
+    lens = [1, 127, 129, 300, 1025]
+    Bn = len(lens)
+    k_pool, v_pool, pt = _make_cache(Bn, lens, Hkv, D, dt)
+    q = torch.randn(Bn, Hq * D).to(dt)
+    seq = torch.tensor(lens, dtype=torch.int32)
+    args = (q.to(DEV), k_pool.to(DEV), v_pool.to(DEV), pt.to(DEV), seq.to(DEV), 1 / math.sqrt(D), Hq, Hkv, D)
+    plain = A.attn_decode(*args)
+    out = A.attn_decode(*args, quant_mode=mode)
+    assert torch.equal(out, plain)
+    m, xq, sa, xs, ld_a = out.fb_quant
+    assert m == mode
+    if mode == 1:
+        rq, rsa, rxs, _ = QG.quant_act_i8(plain)
+        assert torch.equal(xq, rq) and torch.equal(sa[:, :Bn], rsa[:, :Bn]) and torch.equal(xs[:, :Bn], rxs[:, :Bn])
+    else:
+        rq, rsa, _ = QG.quant_act_fp8(plain)
+        assert torch.equal(xq, rq) and torch.equal(sa[:, :Bn], rsa[:, :Bn])
+    _lib.check_device_errors()
