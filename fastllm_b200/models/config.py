@@ -43,6 +43,7 @@ class ModelConfig:
     attn_scale_override: float | None = None   # softmax scale when it is not 1/sqrt(head_dim)
     residual_scale: float = 1.0            # multiplier of every sub-layer output before the residual add (folded into weights)
     post_norms: bool = False               # sandwich norms: the sub-layer output is normalised before the residual add
+    rope_local_theta: float = 0.0          # Gemma-3: sliding-window layers rotate with this base (and no scaling)
     qk_norm_full: bool = False             # MiniMax-M2: one RMSNorm over all heads of q (and of k) instead of per head
     qk_norm_after_rope: bool = False       # Hunyuan: per-head norm applied after the rotary embedding
     attn_sinks: bool = False               # learned per-head sink logit in the softmax denominator (gpt-oss)
@@ -122,6 +123,11 @@ def from_hf_dict(d: dict) -> ModelConfig:
     c.rms_eps = g("rms_norm_eps", g("layernorm_epsilon", g("layer_norm_eps", c.rms_eps)))
     c.rope_theta = float(g("rope_theta", g("rotary_emb_base", 10000.0)))
     rs = g("rope_scaling") or g("rope_parameters")
+    if isinstance(rs, dict) and isinstance(rs.get("full_attention"), dict):
+        # per-layer-type rope parameters (Gemma-3): global layers use "full_attention", sliding layers their own base
+        loc = rs.get("sliding_attention") or {}
+        c.rope_local_theta = float(loc.get("rope_theta", 10000.0))
+        rs = rs["full_attention"]
     if isinstance(rs, dict):
         if "rope_theta" in rs:
             c.rope_theta = float(rs["rope_theta"])
@@ -140,8 +146,10 @@ def from_hf_dict(d: dict) -> ModelConfig:
     prf = g("partial_rotary_factor") or (rs.get("partial_rotary_factor") if isinstance(rs, dict) else None)
     if prf:
         c.rotary_dim = int(c.head_dim * float(prf))
-    if mt in ("qwen3", "qwen3_moe"):
+    if mt in ("qwen3", "qwen3_moe", "gemma3_text"):
         c.qk_norm = True
+    if mt == "gemma3_text" and g("rope_local_base_freq") and not c.rope_local_theta:
+        c.rope_local_theta = float(g("rope_local_base_freq"))          # config.json of released checkpoints
     if mt in ("gemma", "gemma2", "gemma3_text"):
         c.norm_unit_offset = 1.0
         c.embed_scale = float(c.hidden_size) ** 0.5
@@ -166,6 +174,9 @@ def from_hf_dict(d: dict) -> ModelConfig:
         if g("query_pre_attn_scalar"):
             c.attn_scale_override = float(g("query_pre_attn_scalar")) ** -0.5
     lt = g("layer_types")
+    if lt is None and mt == "gemma3_text" and c.sliding_window:
+        pat = int(g("sliding_window_pattern", 6) or 6)          # older configs: every pat-th layer is a global one
+        lt = ["full_attention" if (i + 1) % pat == 0 else "sliding_attention" for i in range(c.num_layers)]
     if isinstance(lt, list) and c.sliding_window:
         c.layer_windows = [int(c.sliding_window) if t == "sliding_attention" else 0 for t in lt]
     if mt in ("hunyuan_v1_dense", "hunyuan_v1_moe"):

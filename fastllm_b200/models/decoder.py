@@ -128,7 +128,14 @@ class DecoderModel:
             self.attn_scale *= ms * ms
 
     # -----------------------------------------------------------------------------------------------
-    def rope_tables(self, max_pos: int | None = None, device=None):
+    def rope_tables(self, max_pos: int | None = None, device=None, local: bool = False):
+        if local and self.cfg.rope_local_theta:
+            # sliding-window layers of Gemma-3: their own base, no scaling
+            t = self.__dict__.get("_rope_local")
+            if t is None:
+                mp = max_pos or min(self.cfg.max_position, 1 << 17)
+                t = self._rope_local = A.build_rope_tables(self.rot_dim, mp, self.cfg.rope_local_theta, None, self.device)
+            return t if device is None or torch.device(device) == self.device else (t[0].to(device), t[1].to(device))
         if device is not None and torch.device(device) != self.device:
             key = str(torch.device(device))
             cache = self.__dict__.setdefault("_rope_by_device", {})
@@ -214,7 +221,7 @@ class DecoderModel:
         c = self.cfg
         Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
         T = qkv.shape[0]
-        cos, sin = self.rope_tables()
+        cos, sin = self.rope_tables(device=qkv.device, local=bool(lw.window))
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
         q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
         norm = lambda t, w: A._head_norm_ref(t, w, c.rms_eps, c.norm_unit_offset) if w is not None else t

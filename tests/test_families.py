@@ -42,6 +42,8 @@ FAMILIES = {
     "hunyuan_v1_moe": dict(model_type="hunyuan_v1_moe", **_C, num_experts=4, moe_topk=2, num_shared_expert=1, moe_intermediate_size=128),
     "hunyuan_v1_dense": dict(model_type="hunyuan_v1_dense", **_C),
     "gpt_oss": dict(model_type="gpt_oss", **_C, num_local_experts=4, num_experts_per_tok=2, sliding_window=16),
+    "gemma3_text": dict(model_type="gemma3_text", **_C, sliding_window=16, query_pre_attn_scalar=64,
+                        layer_types=["sliding_attention", "full_attention"]),
     "minimax_m2": dict(model_type="minimax_m2", **_C, num_local_experts=4, num_experts_per_tok=2,
                        rope_parameters={"rope_type": "default", "rope_theta": 1e6, "partial_rotary_factor": 0.5}),
     "granite": dict(model_type="granite", **_NH, attention_multiplier=0.2, embedding_multiplier=3.0, residual_multiplier=0.5,
