@@ -43,6 +43,7 @@ class ModelConfig:
     attn_scale_override: float | None = None   # softmax scale when it is not 1/sqrt(head_dim)
     residual_scale: float = 1.0            # multiplier of every sub-layer output before the residual add (folded into weights)
     post_norms: bool = False               # sandwich norms: the sub-layer output is normalised before the residual add
+    latent_norm_eps: float = 0.0           # MLA q_a / kv_a norms when they do not follow rms_norm_eps (GLM-MoE-DSA: 1e-6)
     rope_local_theta: float = 0.0          # Gemma-3: sliding-window layers rotate with this base (and no scaling)
     qk_norm_full: bool = False             # MiniMax-M2: one RMSNorm over all heads of q (and of k) instead of per head
     qk_norm_after_rope: bool = False       # Hunyuan: per-head norm applied after the rotary embedding
@@ -238,7 +239,7 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.qk_norm_full = c.qk_norm and g("qk_norm_type", "per_layer") == "per_layer"
         if g("rotary_dim") and not prf:
             c.rotary_dim = int(g("rotary_dim"))
-    elif mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe", "ernie4_5_moe"):
+    elif mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32", "glm_moe_dsa", "glm4_moe", "ernie4_5_moe"):
         c.num_experts = g("n_routed_experts", g("num_experts", g("moe_num_experts", 0))) or 0
         c.num_experts_per_tok = g("num_experts_per_tok", g("moe_k", 0))
         c.moe_intermediate_size = g("moe_intermediate_size", 0)
@@ -247,19 +248,21 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.shared_expert_intermediate_size = c.moe_intermediate_size * c.num_shared_experts
         c.first_k_dense = g("first_k_dense_replace", g("moe_layer_start_index", 0)) or 0
         c.moe_layer_freq = g("moe_layer_freq", 1) or 1
-        c.scoring_func = g("scoring_func", "sigmoid" if mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe") else "softmax")
+        c.scoring_func = g("scoring_func", "sigmoid" if mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm_moe_dsa", "glm4_moe") else "softmax")
         c.n_group = g("n_group", 1) or 1
         c.topk_group = g("topk_group", 1) or 1
         c.routed_scaling_factor = float(g("routed_scaling_factor", 1.0))
-        c.router_bias = g("topk_method", "") == "noaux_tc" or mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm4_moe", "ernie4_5_moe")
-        if mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32"):
+        c.router_bias = g("topk_method", "") == "noaux_tc" or mt in ("deepseek_v3", "kimi_k2", "deepseek_v32", "glm_moe_dsa", "glm4_moe", "ernie4_5_moe")
+        if mt in ("deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32", "glm_moe_dsa"):
             c.use_mla = True
             c.q_lora_rank = g("q_lora_rank") or 0
             c.kv_lora_rank = g("kv_lora_rank", 512)
             c.qk_nope_head_dim = g("qk_nope_head_dim", 128)
             c.qk_rope_head_dim = g("qk_rope_head_dim", 64)
             c.v_head_dim = g("v_head_dim", 128)
-            c.rope_mode = "interleaved"
+            c.rope_mode = "neox" if mt == "glm_moe_dsa" else "interleaved"
+            if mt == "glm_moe_dsa":
+                c.latent_norm_eps = 1e-6
             c.head_dim = c.qk_nope_head_dim + c.qk_rope_head_dim
         if mt == "glm4_moe":
             c.qk_norm = bool(g("use_qk_norm", False))

@@ -314,12 +314,12 @@ class DecoderModel:
         nope, rope, lora, vd = c.qk_nope_head_dim, c.qk_rope_head_dim, c.kv_lora_rank, c.v_head_dim
         T = x.shape[0]
         if lw.q_a is not None:
-            q = lw.q_b(B.rmsnorm(lw.q_a(x), lw.q_a_norm, c.rms_eps))
+            q = lw.q_b(B.rmsnorm(lw.q_a(x), lw.q_a_norm, c.latent_norm_eps or c.rms_eps))
         else:
             q = lw.q_b(x)
         q = q.view(T, H, nope + rope)
         ckv = lw.kv_a(x)                                   # [T, lora + rope]
-        c_lat = B.rmsnorm(ckv[:, :lora].contiguous(), lw.kv_a_norm, c.rms_eps)
+        c_lat = B.rmsnorm(ckv[:, :lora].contiguous(), lw.kv_a_norm, c.latent_norm_eps or c.rms_eps)
         cos, sin = self.rope_tables()
         k_pe = A.apply_rope_ref(ckv[:, lora:].reshape(T, 1, rope), fb.positions, cos, sin, self.rope_mode, rope)
         q_pe = A.apply_rope_ref(q[..., nope:], fb.positions, cos, sin, self.rope_mode, rope)

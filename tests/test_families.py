@@ -34,6 +34,8 @@ FAMILIES = {
     "deepseek_v2": dict(model_type="deepseek_v2", **_MLA, n_group=1, topk_group=1, q_lora_rank=None),
     "deepseek_v3": dict(model_type="deepseek_v3", **_MLA, n_group=2, topk_group=1, routed_scaling_factor=2.5, norm_topk_prob=True,
                         q_lora_rank=128),
+    "glm_moe_dsa": dict(model_type="glm_moe_dsa", **_MLA, n_group=1, topk_group=1, q_lora_rank=128,
+                        mlp_layer_types=["dense", "sparse", "sparse"]),
     "glm4_moe": dict(model_type="glm4_moe", **_C, moe_intermediate_size=128, n_routed_experts=8, num_experts_per_tok=2,
                      n_shared_experts=1, first_k_dense_replace=1, n_group=1, topk_group=1, partial_rotary_factor=0.5, use_qk_norm=True),
     "ernie4_5": dict(model_type="ernie4_5", **_C),
@@ -56,7 +58,10 @@ def test_family_matches_transformers(name, tmp_path):
     torch.manual_seed(0)
     try:
         cfg = transformers.AutoConfig.for_model(**FAMILIES[name])
-        ref = transformers.AutoModelForCausalLM.from_config(cfg, torch_dtype=torch.float32)
+        # glm_moe_dsa: with the fused attention back end the oracle hands over the indexer mask alone (every position is
+        # selected at this length) and loses the causal mask; the eager back end combines the two
+        extra = {"attn_implementation": "eager"} if name == "glm_moe_dsa" else {}
+        ref = transformers.AutoModelForCausalLM.from_config(cfg, torch_dtype=torch.float32, **extra)
     except Exception as e:      # architecture not present in the installed transformers
         pytest.skip(f"transformers cannot build {name}: {e}")
     for p in ref.parameters():
