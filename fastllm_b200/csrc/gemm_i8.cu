@@ -81,35 +81,35 @@ __device__ __forceinline__ float sum_to_float(uint32_t v) { return __uint_as_flo
 template <class Cfg>
 __device__ __forceinline__ void unpack_int4_tile(int i, int tid, uint8_t* stages, uint8_t* dq, uint64_t* full_bar, uint64_t* empty_bar,
                                                  uint64_t* dq_full, uint64_t* dq_empty, bool& dead) {
-      const int s = i % Cfg::STAGES, b = i & 1;
-      const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = ((uint32_t)i >> 1) & 1u;
+  const int s = i % Cfg::STAGES, b = i & 1;
+  const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, bph = ((uint32_t)i >> 1) & 1u;
   if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_I8, 6)) return;
-      if (!mbar_wait(&dq_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 7)) return;
-      const uint8_t* raw = stages + s * Cfg::STAGE_BYTES + Cfg::B_BYTES;
-      uint8_t* out = dq + b * Cfg::A_BYTES;
-      uint4 pk[4];                                         // all four loads first: the stores below must not serialise them
+  if (!mbar_wait(&dq_empty[b], bph ^ 1u, dead, KID_GEMM_I8, 7)) return;
+  const uint8_t* raw = stages + s * Cfg::STAGE_BYTES + Cfg::B_BYTES;
+  uint8_t* out = dq + b * Cfg::A_BYTES;
+  uint4 pk[4];                                         // all four loads first: the stores below must not serialise them
 #pragma unroll
-      for (int it = 0; it < 4; ++it) pk[it] = *reinterpret_cast<const uint4*>(raw + (tid + it * 128) * 16);
+  for (int it = 0; it < 4; ++it) pk[it] = *reinterpret_cast<const uint4*>(raw + (tid + it * 128) * 16);
 #pragma unroll
-      for (int it = 0; it < 4; ++it) {
-        const int idx = tid + it * 128;                  // 512 chunks of 16 packed bytes
-        const int row = idx >> 2, c4 = idx & 3;
-        uint32_t o[8];
-        const uint32_t w4[4] = {pk[it].x, pk[it].y, pk[it].z, pk[it].w};
+  for (int it = 0; it < 4; ++it) {
+    const int idx = tid + it * 128;                  // 512 chunks of 16 packed bytes
+    const int row = idx >> 2, c4 = idx & 3;
+    uint32_t o[8];
+    const uint32_t w4[4] = {pk[it].x, pk[it].y, pk[it].z, pk[it].w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const uint32_t hi = (w4[e] >> 4) & 0x0F0F0F0Fu, lo = w4[e] & 0x0F0F0F0Fu;      // first value of a byte = high nibble
-          o[2 * e] = __byte_perm(hi, lo, 0x5140);
-          o[2 * e + 1] = __byte_perm(hi, lo, 0x7362);
-        }
-        uint8_t* rowp = out + row * 128;
-        const int c0 = 2 * c4, c1 = 2 * c4 + 1;
-        *reinterpret_cast<uint4*>(rowp + ((c0 ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4*>(rowp + ((c1 ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(&dq_full[b]);
-      if (Cfg::SPLIT) mbar_arrive(&empty_bar[s]);          // dedicated unpack warps: the packed tile is theirs to release
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t hi = (w4[e] >> 4) & 0x0F0F0F0Fu, lo = w4[e] & 0x0F0F0F0Fu;      // first value of a byte = high nibble
+      o[2 * e] = __byte_perm(hi, lo, 0x5140);
+      o[2 * e + 1] = __byte_perm(hi, lo, 0x7362);
+    }
+    uint8_t* rowp = out + row * 128;
+    const int c0 = 2 * c4, c1 = 2 * c4 + 1;
+    *reinterpret_cast<uint4*>(rowp + ((c0 ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(rowp + ((c1 ^ (row & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+  fence_proxy_async_smem();
+  mbar_arrive(&dq_full[b]);
+  if (Cfg::SPLIT) mbar_arrive(&empty_bar[s]);          // dedicated unpack warps: the packed tile is theirs to release
 }
 
 template <int MPAD, bool BF16, int WK>
