@@ -83,6 +83,147 @@ def set_prefix_cache(on: bool):
     _settings["prefix_cache"] = bool(on)
 
 
+# ---- the rest of the reference's module-level switches (tools/fastllm_pytools/llm.py:290-640) -------------------------------
+def set_model_load_progress_callback(callback):
+    """``callback(stage, current, total, completed_bytes, total_bytes)`` during model load (None removes it)."""
+    from .serving import progress
+
+    progress.set_callback(callback)
+
+
+def report_model_load_progress(stage, current=0, total=0, completed_bytes=0, total_bytes=0):
+    from .serving import progress
+
+    progress.emit(str(stage), int(current), int(total), completed_bytes=int(completed_bytes), total_bytes=int(total_bytes))
+
+
+def export_llm_model_fromhf(path: str, output: str, dtype: str = "float16", moe_dtype: str = "", lora: str = "", dtype_config: str = ""):
+    """Quantise an HF folder into a reloadable HF-layout export (the ``ftllm export`` command)."""
+    from .loader.export import export_quantized_hf
+
+    if lora or dtype_config:
+        raise NotImplementedError("export takes dtype / moe_dtype; adapters and dtype_config rules apply at load time")
+    export_quantized_hf(path, output, "float16" if dtype == "auto" else dtype, moe_dtype or None)
+
+
+def softmax(a):
+    import numpy as np
+
+    a = np.asarray(a, dtype=np.float64)
+    e = np.exp(a - a.max())
+    return e / e.sum()
+
+
+def has_device(device_type: str) -> bool:
+    d = str(device_type).lower()
+    if d == "cpu":
+        return True
+    if d == "cuda":
+        return torch.cuda.is_available()
+    if d == "multicuda":
+        return torch.cuda.is_available() and torch.cuda.device_count() > 1
+    if d in ("numa", "disk"):
+        return True          # host placements of the routed experts (``--moe_device``)
+    return False
+
+
+def print_ins_info():
+    """Instruction sets the native CPU backend was built for / runs with."""
+    from .ops import cpu
+
+    print("cpu backend:", cpu.isa() if cpu.available() else "not built", "| cuda:", torch.cuda.is_available())
+
+
+def set_cpu_kvcache(cpu_kvcache):
+    """KV pages in host memory.  The tensor-core attention kernels read HBM pages only: the switch is recorded and models on a
+    GPU keep their cache on the device (a CPU model's cache is in host memory anyway)."""
+    _settings["cpu_kvcache"] = bool(cpu_kvcache)
+
+
+def get_cpu_kvcache():
+    return bool(_settings.get("cpu_kvcache", False))
+
+
+def set_cpu_historycache(cpu_historycache):
+    """Prefix-cache history in host memory: recorded; cached prefix pages stay in the device page pool."""
+    _settings["cpu_historycache"] = bool(cpu_historycache)
+
+
+def get_cpu_historycache():
+    return bool(_settings.get("cpu_historycache", False))
+
+
+def set_cuda_embedding(cuda_embedding):
+    _settings["cuda_embedding"] = bool(cuda_embedding)          # the embedding table always lives with the model's first layer
+
+
+def set_cuda_slab(mb: int):
+    _settings["cuda_slab_mb"] = int(mb)                          # device memory comes from PyTorch's caching allocator
+
+
+def disable_cuda_malloc():
+    """Steady-state decode allocates nothing new (static CUDA-graph buffers); kept for interface compatibility."""
+    _settings["cuda_malloc_disabled"] = True
+
+
+def set_enable_amx(enable_amx):
+    _settings["enable_amx"] = bool(enable_amx)                   # the CPU backend dispatches AVX2 / AVX-512 by itself
+
+
+def set_cuda_shared_expert(cuda_shared_expert):
+    _settings["cuda_shared_expert"] = bool(cuda_shared_expert)   # shared experts stay on the GPU under ``--moe_device cpu``
+
+
+def set_cpu_low_mem(low_mem):
+    _settings["cpu_low_mem"] = bool(low_mem)
+
+
+def get_cpu_low_mem():
+    return bool(_settings.get("cpu_low_mem", False))
+
+
+def set_layered_moe_device_map(device_map):
+    """Placement of the routed experts (``"cpu"``, ``"disk"``, a list or ``{device: weight}``); same as
+    ``set_device_map(device_map, is_moe=True)``."""
+    if isinstance(device_map, (list, tuple)) and device_map:
+        device_map = str(device_map[0])
+    elif isinstance(device_map, dict) and device_map:
+        device_map = str(next(iter(device_map)))
+    _settings["moe_device_map"] = device_map
+
+
+def set_moe_device_layers(layers: int):
+    """Only the first ``layers`` MoE layers use the expert placement (negative: all)."""
+    _settings["moe_device_layers"] = int(layers)
+
+
+def GraphNode(name: str, type: str = "data", value=None):
+    d = {"name": name, "type": type}
+    if value:
+        d["value"] = value
+    return d
+
+
+def FloatGraphNode(v):
+    if isinstance(v, (int, str)):
+        v = float(v)
+    if isinstance(v, float):
+        return GraphNode("", "constant.float", v)
+    if isinstance(v, dict):
+        v["type"] = "config.float"
+    return v
+
+
+def IntGraphNode(v):
+    if isinstance(v, float):
+        v = int(v)
+    if isinstance(v, int):
+        return GraphNode("", "constant.int", v)
+    if isinstance(v, dict):
+        v["type"] = "config.int"
+    return v
+
+
 def _resolve_device():
     dm = _settings["device_map"]
     if isinstance(dm, str):

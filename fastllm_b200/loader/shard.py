@@ -257,6 +257,8 @@ def build_top(m, t: dict, wdtype="dense"):
 
 def finalize_model(m, top_fn, layer_fn, wdtype="dense", moe_wdtype=None):
     """``top_fn()`` / ``layer_fn(i)`` return dicts of canonical tensors; they are consumed one layer at a time."""
+    from ..serving import progress
+
     home = m.device
     staged = getattr(m, "layer_devices", None)
     build_top(m, top_fn(), wdtype)
@@ -264,6 +266,7 @@ def finalize_model(m, top_fn, layer_fn, wdtype="dense", moe_wdtype=None):
         if staged is not None:
             m.device = staged[i]           # the builders place tensors on m.device
         build_layer(m, i, layer_fn(i), wdtype, moe_wdtype)
+        progress.emit("load_weights", i + 1, m.cfg.num_layers)
     m.device = home
     if staged is not None:                 # the head runs where the last layer left the activations
         last = staged[-1]

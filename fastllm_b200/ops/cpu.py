@@ -63,6 +63,11 @@ def get_threads() -> int:
     return lib().fbcpu_get_threads()
 
 
+def isa() -> str:
+    """Instruction set the dispatcher picked on this machine."""
+    return {256: "avx2", 512: "avx512"}.get(int(lib().fbcpu_isa()), "unknown")
+
+
 def _p(t):
     return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
 

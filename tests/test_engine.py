@@ -234,3 +234,39 @@ def test_fp8_kv_cache(tmp_path):
         m.release_memory()
     assert len(outs[1]) == 4
     assert torch.nn.functional.cosine_similarity(logits[0].flatten(), logits[1].flatten(), dim=0) > 0.99
+
+
+def test_module_level_switches(tmp_path, capsys):
+    """The reference's module-level helpers exist and behave: device probes, progress callback, graph-node helpers, settings."""
+    from baseline import synth
+    from fastllm_b200 import llm
+
+    assert llm.has_device("cpu") and not llm.has_device("tfacc")
+    assert abs(float(llm.softmax([1.0, 2.0, 3.0]).sum()) - 1.0) < 1e-9
+    assert llm.GraphNode("x") == {"name": "x", "type": "data"}
+    assert llm.FloatGraphNode(2)["type"] == "constant.float" and llm.IntGraphNode(3.0)["value"] == 3
+    llm.set_cpu_kvcache(True)
+    assert llm.get_cpu_kvcache()
+    llm.set_cpu_kvcache(False)
+    llm.set_cpu_low_mem(True)
+    assert llm.get_cpu_low_mem()
+    llm.set_cpu_low_mem(False)
+    for f, a in ((llm.set_cuda_embedding, True), (llm.set_cuda_slab, 64), (llm.set_enable_amx, False), (llm.set_cuda_shared_expert, True),
+                 (llm.set_moe_device_layers, -1)):
+        f(a)
+    llm.disable_cuda_malloc()
+    llm.print_ins_info()
+    assert "cpu backend" in capsys.readouterr().out
+    events = []
+    llm.set_model_load_progress_callback(lambda stage, cur, tot, cb, tb: events.append((stage, cur, tot)))
+    try:
+        d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.float32, std=0.05)
+        llm.set_device_map("cpu")
+        m = llm.model(d, device="cpu")
+        n = m.engine.model.cfg.num_layers
+        assert ("load_weights", n, n) in events
+        llm.report_model_load_progress("custom", 1, 2)
+        assert events[-1] == ("custom", 1, 2)
+        m.release_memory()
+    finally:
+        llm.set_model_load_progress_callback(None)
