@@ -462,6 +462,146 @@ class model:
         """Back to the base weights.  Reference: tools/fastllm_pytools/llm.py:2712."""
         self._switch_adapter(None)
 
+    # ---- HF-style conveniences and run-time setters of the reference (tools/fastllm_pytools/llm.py:1338-2810) --------------
+    def eval(self):
+        return self
+
+    def generate(self, inputs, max_length: int = 4096, do_sample: bool = True, top_p=None, top_k=None, temperature=None,
+                 repeat_penalty=None, stop_token_ids=None, **kw):
+        """Token-id lists in, token-id lists out (prompt + generated ids, like ``transformers`` ``generate``)."""
+        rows = inputs.tolist() if hasattr(inputs, "tolist") else list(inputs)
+        if rows and isinstance(rows[0], int):
+            rows = [rows]
+        hs = [self.launch_stream_response([int(t) for t in r], max_length=max_length, do_sample=do_sample, top_p=top_p, top_k=top_k,
+                                          temperature=temperature, repeat_penalty=repeat_penalty, stop_token_ids=stop_token_ids)
+              for r in rows]
+        outs = []
+        for r, h in zip(rows, hs):
+            out = list(r)
+            while True:
+                tok = self.engine.fetch(h)
+                if tok < 0:
+                    break
+                out.append(tok)
+            outs.append(out)
+        return outs
+
+    def chat(self, tokenizer, query: str, history=None, max_length: int = 8192, do_sample=True, top_p=0.8, top_k=1, temperature=1.0,
+             repeat_penalty=1.0, stop_token_ids=None, **kwargs):
+        """ChatGLM-style: returns ``(response, history + [(query, response)])``; ``tokenizer`` is accepted for compatibility."""
+        history = list(history or [])
+        text = self.response(query, history, max_length=max_length, do_sample=do_sample, top_p=top_p, top_k=top_k,
+                             temperature=temperature, repeat_penalty=repeat_penalty, stop_token_ids=stop_token_ids)
+        return text, history + [(query, text)]
+
+    def stream_chat(self, tokenizer, query: str, history=None, past_key_values=None, max_length: int = 8192, do_sample=True, top_p=0.8,
+                    top_k=1, temperature=1.0, repeat_penalty=1.0, return_past_key_values=False, stop_token_ids=None, **kwargs):
+        history = list(history or [])
+        text = ""
+        for piece in self.stream_response(query, history, max_length=max_length, do_sample=do_sample, top_p=top_p, top_k=top_k,
+                                          temperature=temperature, repeat_penalty=repeat_penalty, stop_token_ids=stop_token_ids):
+            text += piece
+            item = (text, history + [(query, text)])
+            yield item + (None,) if return_past_key_values else item
+
+    def trans_conversation(self, conversation):
+        """Messages whose ``content`` is a list of typed parts are flattened to their text."""
+        out = []
+        for m in conversation:
+            c = m.get("content")
+            if isinstance(c, list):
+                c = "".join(p.get("text", "") for p in c if isinstance(p, dict))
+            out.append(dict(m, content=c))
+        return out
+
+    def get_input_token_len(self, conversation, add_generation_prompt=True, **kw) -> int:
+        if isinstance(conversation, str):
+            return len(self.encode(self.get_prompt(conversation)))
+        return len(self.encode(self.apply_chat_template(self.trans_conversation(list(conversation)),
+                                                        add_generation_prompt=add_generation_prompt)))
+
+    def tokenizer_encode_string(self, content: str) -> list[int]:
+        return self.encode(content)
+
+    def tokenizer_decode_token(self, token_id: int) -> bytes:
+        cache = getattr(self, "tokenizer_decode_token_cache", None)
+        if cache is not None and token_id in cache:
+            return cache[token_id]
+        return self.tokenizer.decode_bytes([int(token_id)]) if hasattr(self.tokenizer, "decode_bytes") \
+            else self.decode([int(token_id)]).encode("utf-8", errors="ignore")
+
+    def build_tokenizer_decode_token_cache(self):
+        if getattr(self, "tokenizer_decode_token_cache", None) is None:
+            self.tokenizer_decode_token_cache = None
+            self.tokenizer_decode_token_cache = {i: self.tokenizer_decode_token(i) for i in range(self.torch_model.cfg.vocab_size)}
+
+    def token_healing(self, prompt: str):
+        """Generate from ``prompt`` with its last token re-chosen among the tokens that start with that token's text (so a
+        prompt cut in the middle of a word continues with the natural token)."""
+        ids = self.encode(prompt)
+        if len(ids) < 2:
+            return self.response(ids)
+        tail = self.decode(ids[-1:])
+        logits = torch.as_tensor(self.response_logits(ids[:-1])).float()
+        cand = [i for i in range(min(logits.numel(), self.torch_model.cfg.vocab_size)) if self.decode([i]).startswith(tail)] or [ids[-1]]
+        best = max(cand, key=lambda i: float(logits[i]))
+        return self.decode([best])[len(tail):] + self.response(ids[:-1] + [best])
+
+    def _engine_cfg(self):
+        return self.engine.cfg
+
+    def set_max_batch(self, batch: int):
+        self._engine_cfg().max_batch = max(1, int(batch))
+
+    def get_max_batch(self) -> int:
+        return int(self._engine_cfg().max_batch)
+
+    def set_max_context_length(self, length: int):
+        self._engine_cfg().max_context = int(length)
+
+    def set_chunked_prefill_size(self, size: int):
+        self._engine_cfg().chunked_prefill_size = max(128, int(size))
+
+    def set_kv_cache_limit(self, limit: str):
+        """``"8G"`` / ``"512M"`` / bytes: informational here -- the page pool is sized when the model is built
+        (``gpu_mem_ratio`` / ``max_tokens``); the value is kept for ``get_kv_cache_token_limit`` callers."""
+        s_ = str(limit).strip().lower()
+        mul = {"k": 1 << 10, "m": 1 << 20, "g": 1 << 30}.get(s_[-1:], 1)
+        self.kv_cache_limit_bytes = int(float(s_[:-1] if s_[-1:] in "kmg" else s_) * mul)
+
+    def set_save_history(self, save: bool):
+        self.save_history = bool(save)            # prefix reuse is the page trie's job (``set_prefix_cache``)
+
+    def set_verbose(self, verbose: int):
+        self.verbose = int(verbose)
+
+    def set_atype(self, atype: str):
+        want = {"float16": torch.float16, "half": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32, "auto": None}.get(str(atype))
+        if want is not None and want != self.torch_model.dtype:
+            raise ValueError(f"activations are {self.torch_model.dtype} since load time; pass dtype= to llm.model to choose another type")
+
+    def set_moe_atype(self, moe_atype: str):
+        self.set_atype(moe_atype)
+
+    def set_kv_cache_dtype(self, kv_cache_dtype: str):
+        if str(kv_cache_dtype) not in ("auto", ""):
+            raise RuntimeError("the page pool exists already: pass kv_cache_dtype= to llm.model(...)")
+
+    def set_moe_experts(self, experts: int):
+        """Route every token to ``experts`` experts instead of the checkpoint's top-k."""
+        self.torch_model.cfg.num_experts_per_tok = int(experts)
+        for slot in self.engine.runner.slots.values():
+            slot.graph = None
+
+    def set_cuda_shared_expert(self, cuda_shared_expert: bool):
+        set_cuda_shared_expert(cuda_shared_expert)
+
+    def embedding_sentence(self, input: str, normalize: bool = True):
+        raise TypeError("embedding_sentence is served by encoder models: fastllm_b200.models.bert / the server's /v1/embed route")
+
+    def reranker_compute_score(self, pairs):
+        raise TypeError("reranker_compute_score is served by encoder models: fastllm_b200.models.bert / the server's /v1/rerank route")
+
     def get_response_statistics(self, handle: int) -> dict:
         return self.engine.stats(handle)
 

@@ -270,3 +270,44 @@ def test_module_level_switches(tmp_path, capsys):
         m.release_memory()
     finally:
         llm.set_model_load_progress_callback(None)
+
+
+def test_model_convenience_methods(tmp_path):
+    """``generate`` / ``chat`` / ``stream_chat`` / token helpers / run-time setters of the reference's ``model`` class."""
+    import pytest
+
+    from baseline import synth
+    from fastllm_b200 import llm
+
+    d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.float32, std=0.05)
+    llm.set_device_map("cpu")
+    m = llm.model(d, device="cpu")
+    assert m.eval() is m
+    prompt = list(range(5, 25))
+    outs = m.generate([prompt, prompt[:7]], max_length=5, do_sample=False)
+    assert outs[0][:len(prompt)] == prompt and len(outs[0]) == len(prompt) + 5 and len(outs[1]) == 7 + 5
+    again = m.generate(torch.tensor([prompt]), max_length=5, do_sample=False)
+    assert again[0] == outs[0]
+    text, hist = m.chat(None, "hello", history=[], max_length=4, do_sample=False)
+    assert hist == [("hello", text)]
+    last = None
+    for last in m.stream_chat(None, "hello", history=[], max_length=4, do_sample=False):
+        pass
+    assert (last[0] if last is not None else "") == text
+    n = m.get_input_token_len([{"role": "user", "content": [{"type": "text", "text": "hello"}]}])
+    assert n == m.get_input_token_len([{"role": "user", "content": "hello"}]) > 0
+    ids = m.tokenizer_encode_string("hello world")
+    assert b"".join(m.tokenizer_decode_token(i) for i in ids).decode("utf-8", errors="ignore").strip() == m.decode(ids).strip()
+    m.set_max_batch(3)
+    assert m.get_max_batch() == 3
+    m.set_chunked_prefill_size(256)
+    m.set_max_context_length(512)
+    m.set_kv_cache_limit("2G")
+    assert m.kv_cache_limit_bytes == 2 << 30
+    have = str(m.torch_model.dtype).replace("torch.", "")
+    m.set_atype(have)
+    with pytest.raises(ValueError):
+        m.set_atype("float16" if have != "float16" else "float32")
+    with pytest.raises(RuntimeError):
+        m.set_kv_cache_dtype("fp8_e4m3")
+    m.release_memory()
