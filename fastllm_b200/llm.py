@@ -597,10 +597,16 @@ class model:
         set_cuda_shared_expert(cuda_shared_expert)
 
     def embedding_sentence(self, input: str, normalize: bool = True):
-        raise TypeError("embedding_sentence is served by encoder models: fastllm_b200.models.bert / the server's /v1/embed route")
+        """Sentence embedding of an encoder model (bert / xlm-roberta folders: ``models.embedding.EncoderModel``)."""
+        from .models.embedding import embed_texts
+
+        return embed_texts(self, [input], normalize=normalize)[0]
 
     def reranker_compute_score(self, pairs):
-        raise TypeError("reranker_compute_score is served by encoder models: fastllm_b200.models.bert / the server's /v1/rerank route")
+        """Relevance score of every ``(query, text)`` pair (sequence-classification encoder folders)."""
+        from .models.embedding import rerank_scores
+
+        return [rerank_scores(self, q, [t])[0] for q, t in pairs]
 
     def get_response_statistics(self, handle: int) -> dict:
         return self.engine.stats(handle)
