@@ -97,6 +97,11 @@ def main(argv=None):
         p.add_argument("--hf_token", type=str, default="")
         p.add_argument("--hf_username", type=str, default="")
         p.add_argument("-j", "--workers", dest="workers", type=int, default=8)
+        # accepted for scripts written against the reference's downloader (which shells out to aria2c / wget); this one
+        # downloads with its own worker threads
+        p.add_argument("--tool", choices=["aria2c", "wget"], default="aria2c")
+        p.add_argument("-x", dest="threads_per_file", type=int, default=4)
+        p.add_argument("--dataset", action="store_true", help="the repository is a dataset")
     args = p.parse_args(argv)
     if cmd == "config":
         print(json.dumps({k: v for k, v in vars(args).items() if v not in (None, "", -1, False)}, indent=1))
@@ -105,7 +110,7 @@ def main(argv=None):
         from .download import download
 
         print(download(args.repo or args.model or args.path, args.cache_dir or None, args.local_dir or None, args.revision or None,
-                       args.include, args.exclude, args.hf_token or None, args.workers))
+                       args.include, args.exclude, args.hf_token or None, args.workers, dataset=args.dataset))
         return 0
     if cmd == "export":
         from .loader import flm

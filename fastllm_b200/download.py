@@ -6,7 +6,8 @@ import os
 
 
 def download(repo: str, cache_dir: str | None = None, local_dir: str | None = None, revision: str | None = None,
-             include: list | None = None, exclude: list | None = None, token: str | None = None, workers: int = 8) -> str:
+             include: list | None = None, exclude: list | None = None, token: str | None = None, workers: int = 8,
+             dataset: bool = False) -> str:
     """Snapshot a model repository (resumable).  ``include`` / ``exclude`` are glob patterns as in the reference's
     ``ftllm download --include ... --exclude ...``."""
     if not repo:
@@ -18,6 +19,9 @@ def download(repo: str, cache_dir: str | None = None, local_dir: str | None = No
     except ImportError as e:
         raise SystemExit(f"download needs the huggingface_hub package: {e}")
     try:
+        if dataset:
+            return snapshot_download(repo, repo_type="dataset", cache_dir=cache_dir, local_dir=local_dir, revision=revision, token=token,
+                                     max_workers=workers, allow_patterns=include or None, ignore_patterns=exclude or None)
         return snapshot_download(repo, cache_dir=cache_dir, local_dir=local_dir, revision=revision, token=token, max_workers=workers,
                                  allow_patterns=include or ["*.json", "*.safetensors", "*.txt", "*.model", "*.jinja", "*.tiktoken"],
                                  ignore_patterns=exclude or None)

@@ -136,6 +136,8 @@ def add_server_args(p: argparse.ArgumentParser):
     p.add_argument("--think", type=str, default="true")
     p.add_argument("--hide_input", action="store_true")
     p.add_argument("--dev_mode", action="store_true")
+    p.add_argument("--startup-progress", dest="startup_progress", choices=["off", "ndjson"], default="off",
+                   help="ndjson: FTLLM_PROGRESS events on stderr while the model loads")
 
 
 def serve(args):
@@ -144,6 +146,10 @@ def serve(args):
     from ..util import make_normal_llm_model
     from .progress import emit
 
+    if getattr(args, "startup_progress", "off") == "ndjson":
+        import os
+
+        os.environ["FTLLM_PROGRESS"] = "1"
     emit("load", 0, 1)
     model = make_normal_llm_model(args)
     emit("load", 1, 1)
