@@ -137,6 +137,8 @@ def from_hf_dict(d: dict) -> ModelConfig:
     c.max_position = g("max_position_embeddings", g("seq_length", c.max_position))
     c.tie_embeddings = bool(g("tie_word_embeddings", False))
     c.attention_bias = bool(g("attention_bias", g("qkv_bias", g("add_qkv_bias", mt in ("qwen2", "qwen2_moe", "qwen")))))
+    if mt == "internlm" and g("bias") is not None:          # InternLM (v1): one flag for the q / k / v / o biases
+        c.attention_bias = bool(g("bias"))
     c.mlp_bias = bool(g("mlp_bias", False))
     c.hidden_act = g("hidden_act", g("hidden_activation", "silu"))
     c.sliding_window = g("sliding_window") if g("use_sliding_window", True) else None

@@ -349,3 +349,8 @@ def test_baichuan_and_internlm3_layouts(tmp_path):
     _save_renamed(ref3, dict(cfg3, model_type="internlm3", qkv_bias=True, bias=False), lambda k: k, d3)
     got3 = _last_logits(hf.load_model(d3, device="cpu", dtype=torch.float32), prompt)
     assert torch.nn.functional.cosine_similarity(got3, want3, dim=0).item() > 0.99999
+    # InternLM (v1): the same tensors under model_type "internlm" with its single "bias" flag
+    d1 = str(tmp_path / "internlm")
+    _save_renamed(ref3, dict(cfg3, model_type="internlm", bias=True), lambda k: k, d1)
+    got1 = _last_logits(hf.load_model(d1, device="cpu", dtype=torch.float32), prompt)
+    assert torch.nn.functional.cosine_similarity(got1, want3, dim=0).item() > 0.99999
