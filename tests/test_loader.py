@@ -236,3 +236,20 @@ def test_moe_device_disk_keeps_experts_in_the_file_mapping(tmp_path):
         return m.forward(fb, eng.runner.kv.pools)[0].float()
 
     assert torch.allclose(logits(base), logits(disk), atol=1e-5)
+
+
+def test_activation_mode_routing():
+    """Which activation form a quantised projection asks its producer for (fused quantiser in the norm / attention combine)."""
+    from fastllm_b200.ops import quant_gemm as QG
+    from fastllm_b200.ops.quant import LinearWeight
+
+    w = torch.randn(256, 512) * 0.05
+    dense, i8, i4, f8 = (LinearWeight.from_dense(w, k) for k in ("dense", "int8", "int4g128", "fp8"))
+    assert QG.act_quant_mode(dense, 4) == 0 and QG.act_quant_mode(None, 4) == 0
+    assert QG.act_quant_mode(i8, 1) == 1 and QG.act_quant_mode(i8, 128) == 1 and QG.act_quant_mode(i8, 129) == 3
+    assert QG.act_quant_mode(i4, 64) == 1 and QG.act_quant_mode(i4, 65) == 3
+    assert QG.act_quant_mode(f8, 128) == 2 and QG.act_quant_mode(f8, 4096) == 4
+    i8.adapters = {"a": (torch.zeros(4, 512), torch.zeros(256, 4))}
+    assert QG.act_quant_mode(i8, 1) == 0          # a run-time adapter needs the 16-bit activations
+    odd = LinearWeight.from_dense(torch.randn(64, 192) * 0.05, "int8")
+    assert QG.act_quant_mode(odd, 1) == 0         # K not a multiple of the 128-wide quantisation block
