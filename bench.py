@@ -62,7 +62,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -99,38 +99,58 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def _worker_hook(loop, eng):
+    """Worker ranks time their own decode steps between the two marks rank 0 publishes, then join the max-over-ranks reduce."""
+    import torch
+    import torch.distributed as dist
+
+    def begin():
+        loop.timing = []
+
+    def end():
+        torch.cuda.synchronize()
+        ms = sum(a.elapsed_time(b) for a, b in (loop.timing or []))
+        loop.timing = None
+        t = torch.tensor([ms, 0.0], device=eng.model.device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+
+    def barrier():
+        torch.cuda.synchronize()
+        dist.barrier()
+
+    loop.handlers.update(timing_begin=begin, timing_end=end, barrier=barrier)
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
 
-    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
-    from fastllm_b200.models import TPInfo, preset, random_init
+    from fastllm_b200.engine import GenerationConfig
+    from fastllm_b200.models import preset
     from fastllm_b200.ops import _lib
-    from fastllm_b200.parallel.tp import TPComm, init_distributed
+    from fastllm_b200.parallel.launcher import TPGroup
 
-    rank, world, local = init_distributed()
-    if world != args.gpus:
-        if args.gpus > 1 and world == 1:
-            raise SystemExit("launch multi-GPU runs with torchrun (python -m torch.distributed.run --nproc-per-node N ...)")
+    world_env = int(os.environ.get("WORLD_SIZE", "1"))
+    if world_env != args.gpus and args.gpus > 1 and world_env == 1:
+        raise SystemExit("launch multi-GPU runs with torchrun (python -m torch.distributed.run --nproc-per-node N ...)")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
     cfg = preset(args.model)
-    tp = TPInfo(rank, world, TPComm(rank, world, dev) if world > 1 else None)
-    if world > 1 and args.comm in ("auto", "fused"):
-        from fastllm_b200.parallel import symm
-
-        tp.comm.fused = symm.try_create(tp.comm, cfg, args.batch, strict=(args.comm == "fused"))
-    ep = None
-    if world > 1 and cfg.is_moe and not args.moe_tp:
-        from fastllm_b200.parallel.ep import EPInfo
-
-        ep = EPInfo.from_tp(tp)
-    model = random_init(cfg, dev, torch.bfloat16, tp=tp, ep=ep, seed=0, wdtype=args.dtype, moe_wdtype=args.moe_dtype or None)
     B, P, O = args.batch, args.prompt_len, args.output_len
     need_tokens = int(B * (P + O + 256) / 0.75)   # leaves the 80 % admission limit room for all B prompts
-    ecfg = EngineConfig(max_batch=max(B, 1), max_context=((P + O + 127) // 128 + 1) * 128, max_tokens=need_tokens,
-                        use_cuda_graph=not args.no_graph, prefix_cache=False, chunked_prefill_size=8192)
-    eng = LLMEngine(model, ecfg)
+    spec = {"kind": "preset", "model": args.model, "dtype": "bfloat16", "seed": 0, "wdtype": args.dtype,
+            "moe_wdtype": args.moe_dtype or None, "moe_tp": bool(args.moe_tp), "comm": args.comm, "max_m": B,
+            "engine": dict(max_batch=max(B, 1), max_context=((P + O + 127) // 128 + 1) * 128, max_tokens=need_tokens,
+                           use_cuda_graph=not args.no_graph, prefix_cache=False, chunked_prefill_size=8192),
+            "_worker_hook": _worker_hook}
+    # Every rank builds its shard; ranks > 0 then serve rank 0's step plans inside attach() and return when it is done.
+    group, eng, _ = TPGroup.attach(spec, device=f"cuda:{local}")
+    if group is None:
+        return              # a worker rank: it served inside attach() and has already released its GPU state
+    world = group.world
+    ctl = eng.control
+    tp = eng.model.tp
+    dev = eng.model.device
     gen = torch.Generator().manual_seed(1234)
     prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=gen).tolist() for _ in range(B)]
     gcfg = GenerationConfig(max_new_tokens=O, ignore_eos=True)
@@ -150,15 +170,16 @@ def run_ours(args):
     for _ in range(W):
         eng.step()
     _lib.check_device_errors()
-    if world > 1:
+    if ctl is not None:
+        ctl.call("barrier")
         dist.barrier()
     torch.cuda.synchronize()
     sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
+    sampler.start()
+    if ctl is not None:
+        ctl.call("timing_begin")
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     runner = eng.runner
-    launches0 = runner.kernel_launches
     t_start = time.perf_counter()
     step_wall = []
     for i in range(K):
@@ -170,46 +191,60 @@ def run_ours(args):
         assert n == B, f"step produced {n} tokens, expected {B}"
     torch.cuda.synchronize()
     wall = time.perf_counter() - t_start
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop()
     _lib.check_device_errors()
     dev_ms = sum(a.elapsed_time(b) for a, b in ev)
     t = torch.tensor([dev_ms, wall * 1000.0], device=dev, dtype=torch.float64)
-    if world > 1:
+    if ctl is not None:
+        ctl.call("timing_end")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     dev_ms, wall_ms = t.tolist()
     slot = runner.slots.get(runner._bucket(B))
     per_step_launches = getattr(runner, "launches_per_decode_step", 0)
-    if rank == 0:
-        value = B * K / (dev_ms / 1000.0)
-        e2e = B * K / (wall_ms / 1000.0)
-        meta_bytes = int(slot.meta_host.numel() * 4) if slot is not None else 0
-        out = {
-            "metric": "decode output tok/s (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
-            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16" if args.dtype == "auto" else args.dtype,
-            "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
-            "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O, "parallelism": f"tp{world}" + (f"+ep{world}" if ep is not None else ""),
-                       "kv_cache": "paged, page 128, bf16", "l2": "inputs larger than L2 (weights + KV >> 126 MB per step)",
-                       "cuda_graph": not args.no_graph, "comm": (tp.comm.fused.name if (tp.comm and tp.comm.fused) else ("nccl" if world > 1 else "none"))},
-            "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": B * 4,
-                    "p50_tpot_ms": statistics.median(step_wall) * 1000.0},
-            "gpu_launches": per_step_launches * K,
-            "clocks": clocks,
-            "prefill_s": prefill_s,
-            "impl": "ours",
-        }
-        print(json.dumps(out), flush=True)
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
+    value = B * K / (dev_ms / 1000.0)
+    e2e = B * K / (wall_ms / 1000.0)
+    meta_bytes = int(slot.meta_host.numel() * 4) if slot is not None else 0
+    ep = eng.model.ep
+    out = {
+        "metric": "decode output tok/s (device-timed, max over ranks)", "value": value, "unit": "tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": _vs_baseline(args, world, value), "dtype": "bf16" if args.dtype == "auto" else args.dtype,
+        "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
+        "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O, "parallelism": f"tp{world}" + (f"+ep{world}" if ep is not None else ""),
+                   "kv_cache": "paged, page 128, bf16", "l2": "inputs larger than L2 (weights + KV >> 126 MB per step)",
+                   "cuda_graph": not args.no_graph, "comm": (tp.comm.fused.name if (tp.comm and tp.comm.fused) else ("nccl" if world > 1 else "none")),
+                   "control_plane": "rank 0 schedules; ranks 1..N-1 replay its step plans from a shared-memory ring" if world > 1 else "single rank"},
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": B * 4,
+                "p50_tpot_ms": statistics.median(step_wall) * 1000.0},
+        "gpu_launches": per_step_launches * K,
+        "clocks": clocks,
+        "prefill_s": prefill_s,
+        "impl": "ours",
+    }
+    print(json.dumps(out), flush=True)
+    _teardown(eng, group)
+
+
+def _vs_baseline(args, world, value):
+    """value / the reference's measured number for the same configuration and GPU count (baseline/measured_reference.json,
+    the table of BASELINE.md); None when that configuration has no reference measurement."""
+    try:
+        table = json.load(open(os.path.join(ROOT, "baseline", "measured_reference.json")))
+    except OSError:
+        return None
+    key = f"{args.model}|{args.dtype}|b{args.batch}|p{args.prompt_len}"
+    ref = table.get(key, {}).get(str(world))
+    return (value / ref) if ref else None
+
+
+def _teardown(eng, group):
+    """Orderly exit (release the worker ranks, captured graphs, symmetric arena, process group -- in that order) so that the
+    interpreter finishes normally and its exit hooks run."""
+    if group is not None:
+        eng.shutdown()
+        group.shutdown()
     sys.stdout.flush()
     sys.stderr.flush()
-    # Leave without tearing down NCCL communicators that captured CUDA graphs still reference: that teardown
-    # can block for minutes; the process is done and the result line is out.
-    os._exit(0)
 
 
 def run_cpu(args):

@@ -296,7 +296,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
           *sh_flag = old;
         }
         asm volatile("bar.sync 1, 128;\n" ::: "memory");
-        const int ns = (seq + AD_PAGE - 1) / AD_PAGE;
+        int ns = (seq + AD_PAGE - 1) / AD_PAGE;
+        if (ns > p.max_splits) {      // a length beyond the page table: merge only the slots this (request, head) owns
+          ns = p.max_splits;
+          if (t == 0) report_error(ERR_BAD_ARG, KID_ATTN_DECODE, 21);
+        }
         if (*sh_flag == ns - 1) {
           // warp q merges heads q, q+4, ...; a lane owns four consecutive dims; eight splits are in flight per pass
           const size_t base = (size_t)(b * p.Hkv + kvh) * p.max_splits * G;
@@ -364,7 +368,11 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
   pdl_launch_dependents();
   pdl_wait();
   const int seq = seq_lens[b];
-  const int ns = (seq + AD_PAGE - 1) / AD_PAGE;
+  int ns = (seq + AD_PAGE - 1) / AD_PAGE;
+  if (ns > max_splits) {          // a length beyond the page table: merge only the slots this (request, head) owns
+    ns = max_splits;
+    if (d == 0) report_error(ERR_BAD_ARG, KID_ATTN_DECODE, 22);
+  }
   const size_t base = (size_t)(b * Hkv + kvh) * max_splits;
   float M = -INFINITY;
   for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[((base + s) * G + g) * 2]);

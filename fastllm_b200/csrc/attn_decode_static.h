@@ -5,8 +5,8 @@
 // plug-ins that are handed tensors by another runtime and own no allocator, and callers inside a region where
 // an allocation could synchronise the device or fragment a pool they do not control.
 //
-// fb_attn_decode_static does the same work as fb_attn_decode_plan + fb_attn_decode (same kernels, same
-// numerics) but takes NO scratch pointers: the work list, the per-page partial outputs and their
+// fb_attn_decode_static does the same work as fb_attn_decode_plan + fb_attn_decode (same kernels) but takes
+// NO scratch pointers: the work list, the per-page partial outputs and their
 // (max, sum) pairs live in one file-scope device array inside the library.  The caller passes only the
 // inputs (q, page pools, page table, sequence lengths) and the output.
 //
@@ -21,6 +21,14 @@
 // All calls on a device share the one array and it keeps the previous call's contents; nothing in it has to
 // start at zero (every word is written before it is read within a call).  Two calls that overlap on the GPU
 // (different streams, no dependency between them) race on it: serialise them.
+//
+// Preconditions on the caller's buffers (the regular entry point is more forgiving on the second):
+//   * seq_lens[b] <= max_pages * 128 for every request.  A longer length is reported through the library's
+//     error word (bad argument) and only the first max_pages pages are merged; the output row is then wrong.
+//   * every page a request's table names holds FINITE values in all 128 rows, including the rows past the
+//     request's length in its last page.  This entry loads whole pages; rows past the length get probability
+//     zero, but 0 x NaN or 0 x Inf from a never-written tail would still poison the output row.  Pools that
+//     come from a zero-filled allocation satisfy this; a pool of uninitialised memory does not.
 //
 // Calls no cudaMalloc / cudaFree and no allocating library routine.
 #pragma once

@@ -11,8 +11,10 @@ Behaviour follows the reference's new main loop (src/models/basellm.cpp:1262-266
 """
 from __future__ import annotations
 
+import queue
 import threading
 import time
+import traceback
 
 import torch
 
@@ -25,10 +27,12 @@ from .runner import EngineConfig, ModelRunner
 
 class LLMEngine:
     def __init__(self, model: DecoderModel, cfg: EngineConfig | None = None, num_pages: int | None = None,
-                 eos_token_ids=None):
+                 eos_token_ids=None, control=None):
         self.cfg = cfg or EngineConfig()
         self.model = model
         self.runner = ModelRunner(model, self.cfg, num_pages)
+        self.control = control          # parallel.control.ControlPlane: this rank schedules, the other ranks replay its plans
+        self.runner.control = control
         self.pm = self.runner.kv.manager
         self.page_len = self.cfg.page_len
         self.eos = set(eos_token_ids if eos_token_ids is not None else model.cfg.eos_token_ids)
@@ -44,10 +48,12 @@ class LLMEngine:
         self.device_errors = 0
         self.last_device_error = ""
         self.decode_tokens = 0
-        self.error: Exception | None = None
+        self.error: Exception | None = None     # the last exception a scheduler step raised (kept for diagnosis)
+        self.dead = False                       # the background loop gave up after repeated failures
 
     # ----------------------------------------------------------------------------------- public API
     def launch(self, prompt_ids, gen: GenerationConfig | None = None, handle: int | None = None) -> int:
+        self._raise_if_dead()
         req = Request(prompt_ids, gen or GenerationConfig(), handle)
         limit = self.cfg.max_context
         if len(req.prompt_ids) >= limit:
@@ -76,11 +82,27 @@ class LLMEngine:
         r = self.requests.get(handle)
         if r is None:
             return -1
-        tok = r.results.get(timeout=timeout)
+        if timeout is None and self._thread is not None:
+            # never block for ever on a loop that has died: poll, and raise once the thread is gone
+            while True:
+                try:
+                    tok = r.results.get(timeout=0.5)
+                    break
+                except queue.Empty:
+                    self._raise_if_dead()
+                    if not self._thread.is_alive() and not self._stop:
+                        self.dead = True
+                        self._raise_if_dead()
+        else:
+            tok = r.results.get(timeout=timeout)
         if tok < 0:
             with self.lock:
                 self.requests.pop(handle, None)
         return tok
+
+    def _raise_if_dead(self):
+        if self.dead:
+            raise RuntimeError(f"the engine loop stopped after repeated failures: {self.error!r}")
 
     def stats(self, handle: int) -> dict:
         r = self.requests.get(handle)
@@ -104,6 +126,14 @@ class LLMEngine:
             self._thread.join(timeout=10)
             self._thread = None
 
+    def shutdown(self):
+        """Stop the background loop and release the worker ranks of a multi-process group."""
+        self.stop()
+        if self.control is not None:
+            self.control.stop()
+            self.control = None
+            self.runner.control = None
+
     def _loop(self):
         if self.model.device.type == "cuda":
             torch.cuda.set_device(self.model.device)
@@ -115,14 +145,23 @@ class LLMEngine:
                     return
             try:
                 self.step()
-            except Exception as e:  # surface the failure to every waiting client instead of hanging them
+                self._consecutive_failures = 0
+            except Exception as e:
+                # A failed step ends the requests that were part of it with reason "error" and the loop goes on
+                # serving; only a failure that keeps repeating stops the thread, and then launch / fetch raise.
                 self.error = e
+                self._consecutive_failures = getattr(self, "_consecutive_failures", 0) + 1
+                traceback.print_exc()
                 with self.cv:
-                    for r in list(self.requests.values()):
-                        self._finish(r, "error")
-                    self.waiting.clear()
+                    victims = list(self.running) or list(self.waiting)   # nothing running: admission itself failed
+                    for r in victims:
+                        if not r.finished():
+                            self._finish(r, "error")
                     self.running.clear()
-                raise
+                    self.waiting = [r for r in self.waiting if not r.finished()]
+                if self._consecutive_failures >= 8:
+                    self.dead = True
+                    return
 
     # ------------------------------------------------------------------------------------- scheduling
     def _used_fraction(self) -> float:
@@ -226,13 +265,9 @@ class LLMEngine:
         for r in list(self.running):
             self.running.remove(r)
             self._finish(r, "error")
-        comm = getattr(self.model.tp, "comm", None)
-        fused = getattr(comm, "fused", None) if comm is not None else None
-        if fused is not None:
-            fused.reset()
-        for s in self.runner.slots.values():        # a kernel that gave up may have left arrival counters mid-count
-            if s.ws is not None:
-                s.ws.counters.zero_()
+        if self.control is not None:
+            self.control.reset()
+        self.runner.reset_after_device_error()
 
     def _prefill_step(self, reqs) -> int:
         budget = self.cfg.chunked_prefill_size
@@ -273,6 +308,8 @@ class LLMEngine:
             return 0
         # make sure every request has a page for the token it is about to write
         for r in list(reqs):
+            if r not in self.running or r.state != RequestState.DECODE:
+                continue                     # evicted (or ended) earlier in this loop on behalf of another request
             pos = r.total_len - 1            # position of the token fed in this step
             need = self._pages_needed(pos + 1) - len(r.pages)
             while need > 0:
@@ -281,12 +318,11 @@ class LLMEngine:
                     r.pages.extend(pg)
                     break
                 if not self._evict_for_pages(need):
-                    self.running.remove(r)
+                    if r in self.running:
+                        self.running.remove(r)
                     self._finish(r, "length")
-                    reqs.remove(r)
                     break
-                reqs = [x for x in reqs if x in self.running]
-                if r not in reqs:
+                if r not in self.running:    # the victim was the request that is asking
                     break
         reqs = [r for r in reqs if r in self.running and r.state == RequestState.DECODE]
         if not reqs:
@@ -311,6 +347,8 @@ class LLMEngine:
     def _sample(self, reqs, logits):
         m = self.model
         if m.tp.size > 1:
+            if self.control is not None:
+                self.control.gather_logits()
             logits = m.tp.comm.gather_logits(logits, m.vocab_shard, m.cfg.vocab_size)
         if all(r.gen.is_simple_greedy() for r in reqs):
             return sampling.greedy(logits).tolist()

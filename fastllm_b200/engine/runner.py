@@ -74,13 +74,37 @@ class ModelRunner:
         self.max_pages = (cfg.max_context + cfg.page_len - 1) // cfg.page_len
         if num_pages is None:
             num_pages = KVCache.plan_num_pages(model, cfg.gpu_mem_ratio, cfg.max_tokens)
+            num_pages = self._agree_on_pages(num_pages)
         self.kv = KVCache(model, num_pages, cfg.page_len)
+        self.control = None      # parallel.control.ControlPlane on the scheduler rank of a multi-process group
         self.slots: dict[int, _DecodeSlot] = {}
         self.graph_ok = cfg.use_cuda_graph and self.device.type == "cuda" and self._graph_safe()
         self.steps = 0
         self.kernel_launches = 0
         self.launches_per_decode_step = 0
         model.rope_tables()
+
+    def _agree_on_pages(self, num_pages: int) -> int:
+        """Page ids are chosen by the scheduler rank and used by every rank: all pools get the smallest planned size."""
+        import torch.distributed as dist
+
+        if self.model.tp.size > 1 and dist.is_available() and dist.is_initialized():
+            dev = self.device if dist.get_backend() == "nccl" else torch.device("cpu")
+            t = torch.tensor([num_pages], dtype=torch.int64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            num_pages = int(t.item())
+        return num_pages
+
+    def reset_after_device_error(self) -> None:
+        """After a kernel reported a failed bounded wait: start a new epoch of the collective arena (every rank calls
+        this together) and clear arrival counters a kernel that gave up may have left mid-count."""
+        comm = getattr(self.model.tp, "comm", None)
+        fused = getattr(comm, "fused", None) if comm is not None else None
+        if fused is not None:
+            fused.reset()
+        for s in self.slots.values():
+            if s.ws is not None:
+                s.ws.counters.zero_()
 
     def _graph_safe(self) -> bool:
         c = self.model.cfg
@@ -100,6 +124,8 @@ class ModelRunner:
     def prefill(self, chunks):
         """chunks: list of (token_ids, start_pos, pages, want_logits). Returns fp32 logits ``[R, V_local]``
         for the chunks that asked for them (last token of the chunk), in order."""
+        if self.control is not None:
+            self.control.prefill(chunks)
         dev = self.device
         ids, pos, slots, cu, kv_lens, rows = [], [], [], [0], [], []
         P = self.max_pages
@@ -186,6 +212,17 @@ class ModelRunner:
             mp[2 * bsz + b] = pg[p // pl] * pl + p % pl
             mp[3 * bsz + b] = p + 1
             pt[b, :len(pg)] = pg
+        if self.control is not None:
+            self.control.decode(n, bsz, want_logits, mp)
+        return self._run_decode(s, n, want_logits)
+
+    def decode_from_plan(self, n: int, bsz: int, want_logits: bool, meta):
+        """A worker rank's decode step: the metadata buffer arrives ready-made from the scheduler rank."""
+        s = self._get_slot(bsz)
+        s.meta_np[:] = meta
+        return self._run_decode(s, n, want_logits)
+
+    def _run_decode(self, s: _DecodeSlot, n: int, want_logits: bool):
         s.meta_dev.copy_(s.meta_host, non_blocking=True)
         if self.graph_ok:
             if s.graph is None:

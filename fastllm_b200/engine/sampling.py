@@ -62,10 +62,11 @@ def sample(logits: torch.Tensor, top_k, top_p, temperature, generators=None) -> 
     dev = logits.device
     t = torch.tensor([max(x, 1e-6) for x in temperature], device=dev, dtype=torch.float32)[:, None]
     lg = logits.float() / t
-    kmax = int(min(V, max(max(top_k), 1)))
-    kmax = min(V, kmax if kmax > 0 else 50)
+    # top_k <= 0 means "top-k off": like the CUDA sampler, such a row draws from its 1024 best candidates
+    eff = [int(k) if k > 0 else min(V, 1024) for k in top_k]
+    kmax = int(min(V, max(max(eff), 1)))
     vals, idx = lg.topk(kmax, dim=-1)
-    ks = torch.tensor([k if k > 0 else kmax for k in top_k], device=dev)[:, None]
+    ks = torch.tensor(eff, device=dev)[:, None]
     ar = torch.arange(kmax, device=dev)[None, :]
     vals = vals.masked_fill(ar >= ks, float("-inf"))
     probs = torch.softmax(vals, dim=-1)

@@ -236,16 +236,49 @@ def _resolve_device():
     return "cuda" if torch.cuda.is_available() else "cpu"
 
 
+def _parallel_devices(tp, device=None) -> list[str]:
+    """Devices of a parallel group from the ``tp`` argument: a count, ``"auto"``, ``"0,2"``, a list of ids / device strings."""
+    if tp == "env":
+        return []
+    if isinstance(tp, str):
+        from .util import parse_tp
+
+        tp = parse_tp(tp)
+    if isinstance(tp, int):
+        tp = list(range(tp))
+    out = []
+    for d in tp or []:
+        out.append(d if isinstance(d, str) else (f"cuda:{int(d)}" if (device or "cuda").startswith("cuda") else "cpu"))
+    return out
+
+
 class model:
     """A loaded model plus its serving engine (started lazily on first request)."""
 
     def __init__(self, path: str, id: int = -99999, dtype: str = "auto", kv_cache_dtype: str = "auto", moe_dtype: str = "",
                  system_prompt: str = "", eos_token: Iterable[str] | None = None, tokenizer_type: str = "auto",
                  model_json: str = "", graph=None, lora: str = "", dtype_config: str = "", ori_model_path: str = "",
-                 chat_template: str = "", tool_call_parser: str = "auto", device: str | None = None, tp: TPInfo | None = None,
-                 engine_config: EngineConfig | None = None, _model=None):
+                 chat_template: str = "", tool_call_parser: str = "auto", device: str | None = None, tp=None,
+                 engine_config: EngineConfig | None = None, _model=None, _defer_fused: bool = False):
+        """``tp``: ``None`` (one device); a GPU count, ``"auto"``, a list of GPU ids / device strings -- the model is
+        then sharded over those devices, this process being rank 0 and one spawned worker process per further
+        device (``parallel/launcher.py``); ``"env"`` inside a job whose ranks an outer launcher started (RANK /
+        WORLD_SIZE set: rank 0 returns a normal model object, the other ranks serve inside this call and come back
+        with ``is_worker`` set when rank 0 shuts down); or a ready ``TPInfo`` (one rank of an SPMD program)."""
         from .loader import hf as hf_loader
 
+        self._group = None
+        self.is_worker = False
+        if tp is not None and not isinstance(tp, TPInfo):
+            devices = _parallel_devices(tp, device)
+            if tp == "env" or len(devices) > 1:
+                kwargs = dict(path=path, dtype=dtype, kv_cache_dtype=kv_cache_dtype, moe_dtype=moe_dtype, system_prompt=system_prompt,
+                              eos_token=list(eos_token) if eos_token else None, tokenizer_type=tokenizer_type, model_json=model_json,
+                              graph=graph if isinstance(graph, str) else None, lora=lora, dtype_config=dtype_config,
+                              ori_model_path=ori_model_path, chat_template=chat_template, tool_call_parser=tool_call_parser)
+                self._init_parallel(kwargs, devices, engine_config, attach=(tp == "env"))
+                return
+            tp, device = None, (devices[0] if devices else device)
         self.path = path
         self.system_prompt = system_prompt
         self.tool_call_parser = tool_call_parser
@@ -303,6 +336,10 @@ class model:
                                            max_tokens=_settings["max_tokens"], use_cuda_graph=_settings["cuda_graph"],
                                            prefix_cache=_settings["prefix_cache"])
         self.engine = LLMEngine(self.torch_model, ec, eos_token_ids=self.eos_token_ids)
+        if tp is not None and tp.size > 1 and tp.comm is not None and not _defer_fused and self.torch_model.on_cuda:
+            from .parallel import symm
+
+            tp.comm.fused = symm.try_create(tp.comm, cfg, min(256, ec.max_batch))
         self.default_generation_config = {"repetition_penalty": 1.0, "top_p": 0.8, "top_k": 1, "temperature": 1.0}
         gc = Path(path) / "generation_config.json" if path and os.path.isdir(path) else None
         if gc is not None and gc.exists():
@@ -313,6 +350,31 @@ class model:
                 if g.get(k) is not None:
                     self.default_generation_config[k] = g[k]
         self._lock = threading.Lock()
+
+    def _init_parallel(self, kwargs: dict, devices: list[str], engine_config, attach: bool):
+        """Become rank 0 of a tensor-parallel group (or, for the other ranks of an outer launcher's job, serve in it)."""
+        import dataclasses
+
+        from .parallel.launcher import TPGroup
+
+        spec = {"kind": "hf", "kwargs": {k: v for k, v in kwargs.items() if v not in (None, "")}, "settings": dict(_settings)}
+        if engine_config is not None:
+            spec["engine"] = dataclasses.asdict(engine_config)
+        if attach:
+            group, _eng, inner = TPGroup.attach(spec)
+        else:
+            group, _eng, inner = TPGroup.launch(spec, devices)
+        self.__dict__.update(inner.__dict__)
+        self._group = group
+        self.is_worker = group is None
+
+    def shutdown(self):
+        """Stop the engine loop and, for a parallel model, release the worker ranks."""
+        if getattr(self, "engine", None) is not None:
+            self.engine.shutdown()
+        if self._group is not None:
+            self._group.shutdown()
+            self._group = None
 
     # ---- text helpers -------------------------------------------------------------------------------
     def encode(self, text: str) -> list[int]:
@@ -632,7 +694,7 @@ class model:
         flm.save_model(self.torch_model, self.tokenizer, path, dtype)
 
     def release_memory(self):
-        self.engine.stop()
+        self.shutdown()
         self.engine = None
         self.torch_model = None
         if torch.cuda.is_available():

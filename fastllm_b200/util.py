@@ -150,9 +150,6 @@ def make_normal_llm_model(args):
         gpu_ids = gpu_ids[:1]
     tp_ids = parse_tp(args.tp) or (gpu_ids if len(gpu_ids) > 1 else [])
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    if len(tp_ids) > 1 and world == 1:
-        raise SystemExit(f"tensor parallel over GPUs {tp_ids} runs one process per GPU: launch with "
-                         f"`python -m torch.distributed.run --nproc-per-node {len(tp_ids)} -m fastllm_b200.cli ...`")
     if args.max_batch and args.max_batch > 0:
         llm.set_max_batch(args.max_batch)
     if args.tokens and args.tokens > 0:
@@ -170,16 +167,14 @@ def make_normal_llm_model(args):
     llm.set_cuda_graph(str(args.cuda_graph).lower() != "false")
     if args.prefix_cache:
         llm.set_prefix_cache(str(args.prefix_cache).lower() == "true")
+    # Several GPUs: this process becomes rank 0 and spawns one worker process per further GPU (`--tp N`,
+    # `--device multicuda:0,1`); inside a job started by an outer launcher (torchrun) the ranks attach instead.
     tp = None
     device = "cpu" if kind == "cpu" else (f"cuda:{gpu_ids[0]}" if len(gpu_ids) == 1 else "cuda")
     if world > 1:
-        from .models.decoder import TPInfo
-        from .parallel import symm
-        from .parallel.tp import TPComm, init_distributed
-
-        rank, world, local = init_distributed()
-        device = f"cuda:{local}"
-        tp = TPInfo(rank, world, TPComm(rank, world, device))
+        tp = "env"
+    elif len(tp_ids) > 1:
+        tp = [f"cuda:{i}" for i in tp_ids] if kind != "cpu" else ["cpu"] * len(tp_ids)
     cfg_path = os.path.join(args.path, "config.json")
     if os.path.isfile(cfg_path):
         mt = json.load(open(cfg_path)).get("model_type", "")
@@ -190,9 +185,8 @@ def make_normal_llm_model(args):
     m = llm.model(args.path, dtype=args.dtype, kv_cache_dtype=args.kv_cache_dtype, moe_dtype=args.moe_dtype, lora=args.lora,
                   dtype_config=args.dtype_config, ori_model_path=args.ori, chat_template=args.chat_template,
                   tool_call_parser=args.tool_call_parser, device=device, tp=tp, graph=(getattr(args, "custom", "") or None))
-    if tp is not None and tp.size > 1:
-        from .parallel import symm
-
-        tp.comm.fused = symm.try_create(tp.comm, m.torch_model.cfg, min(256, llm._settings["max_batch"]))
+    if m.is_worker:
+        # a non-zero rank of an outer launcher's job: it has served until rank 0 shut the group down
+        raise SystemExit(0)
     m.torch_model.source_path = args.path
     return m

@@ -56,6 +56,60 @@ def test_eviction_recompute_gives_same_tokens():
     assert out == ref
 
 
+def test_eviction_of_a_request_later_in_the_batch():
+    """A short request admitted first crosses a page boundary while a longer one, later in the batch, holds the
+    remaining pages: the longer one is evicted on the short one's behalf and must then be skipped by the same
+    page-allocation loop; both finish with the tokens of an unconstrained run and the pool ends fully free."""
+    m = _model()
+    p_short, p_long = _prompts(m.cfg.vocab_size, (100, 180), seed=3)
+    gen = GenerationConfig(max_new_tokens=40, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefix_cache=False), num_pages=32).generate([p_short, p_long], gen)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefix_cache=False, prefill_page_limit=1.0), num_pages=3)
+    h0 = eng.launch(p_short, gen)
+    eng.step()                                   # the short request is admitted and prefilled alone
+    h1 = eng.launch(p_long, gen)
+    reqs = [eng.requests[h0], eng.requests[h1]]
+    for _ in range(2000):
+        if all(r.finished() for r in reqs):
+            break
+        eng.step()
+    assert [r.output_ids for r in reqs] == ref
+    assert all(r.finish_reason == "length" for r in reqs)
+    assert eng.pm.num_free() == 3
+
+
+def test_engine_loop_survives_a_failed_step():
+    """A step that raises ends the requests in flight with reason "error"; the background loop keeps serving."""
+    m = _model()
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefix_cache=False), num_pages=16)
+    real = eng.runner.decode
+    state = {"fail": True}
+
+    def flaky(*a, **k):
+        if state["fail"]:
+            state["fail"] = False
+            raise RuntimeError("injected step failure")
+        return real(*a, **k)
+
+    eng.runner.decode = flaky
+    eng.start()
+    try:
+        gen = GenerationConfig(max_new_tokens=4, ignore_eos=True)
+        h = eng.launch(_prompts(m.cfg.vocab_size, (20,))[0], gen)
+        toks = []
+        while (t := eng.fetch(h)) >= 0:
+            toks.append(t)
+        assert len(toks) <= 1                       # at most the prefill's token came out before the failure
+        assert isinstance(eng.error, RuntimeError) and not eng.dead
+        h2 = eng.launch(_prompts(m.cfg.vocab_size, (20,))[0], gen)
+        toks = []
+        while (t := eng.fetch(h2)) >= 0:
+            toks.append(t)
+        assert len(toks) == 4
+    finally:
+        eng.stop()
+
+
 def test_abort_releases_pages():
     m = _model()
     eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefix_cache=False), num_pages=16)
@@ -79,6 +133,8 @@ def test_sampling_top_k_top_p():
     assert set(t.tolist()) <= {1, 2} and len(set(t.tolist())) == 2
     t = sampling.sample(logits, [4] * 200, [0.3] * 200, [1.0] * 200)
     assert set(t.tolist()) == {1}
+    t = sampling.sample(logits, [0] * 200, [1.0] * 200, [1.0] * 200)          # top_k <= 0: top-k is off, not greedy
+    assert len(set(t.tolist())) > 1
     lg = sampling.apply_repeat_penalty(torch.tensor([[2.0, -2.0, 1.0]]), [[0, 1]], [2.0])
     assert lg.tolist() == [[1.0, -4.0, 1.0]]
 

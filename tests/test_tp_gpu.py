@@ -44,3 +44,16 @@ def test_layer_split_placement_two_gpus(tmp_path):
         eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=256), num_pages=8)
         outs.append(eng.generate(prompts, GenerationConfig(max_new_tokens=6, ignore_eos=True)))
     assert outs[0] == outs[1]
+
+
+def test_server_command_tp2_streams_on_two_gpus(tmp_path):
+    """``ftllm server <model> --tp 2`` on two GPUs: rank 0 serves HTTP and schedules, the spawned rank 1 replays its step
+    plans; the fused NVLink kernels run under CUDA graphs.  One streamed chat completion must arrive and finish."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    from baseline import synth
+    from tests.serve_tp_helper import run_server_and_stream
+
+    d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.bfloat16, std=0.05)
+    chunks, finish = run_server_and_stream(d, ["--tp", "2"])
+    assert finish in ("length", "stop") and len(chunks) >= 1

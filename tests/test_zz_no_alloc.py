@@ -5,7 +5,7 @@ device allocation after start-up, a plug-in that only borrows tensors from anoth
 library offers one entry point that keeps its scratch in a fixed device array of its own.  This test calls
 that entry point through its exported C symbol, twice in a row with different inputs (the array is shared
 and keeps the previous call's contents), and checks each result against the regular entry point that takes
-caller-allocated scratch.  It also checks that an over-sized request is refused before anything is launched.
+caller-allocated scratch and against the plain PyTorch evaluation of the same attention.  It also checks that an over-sized request is refused before anything is launched.
 """
 import ctypes
 import math
@@ -61,6 +61,10 @@ def test_static_scratch_entry_matches_regular_entry():
         err = (out.float() - ref.float()).abs()
         tol = 2e-2 + 2e-2 * ref.float().abs()
         assert bool((err <= tol).all()), f"max err {err.max().item()}"
+        # and against the plain PyTorch evaluation of paged attention (what attn_decode computes for CPU tensors)
+        ref32 = A.attn_decode(q.cpu(), k_pool.cpu(), v_pool.cpu(), pt.cpu(), seq.cpu(), scale, Hq, Hkv, D).float()
+        err = (out.float().cpu() - ref32).abs()
+        assert bool((err <= 2e-2 + 2e-2 * ref32.abs()).all()), f"max err vs PyTorch {err.max().item()}"
 
 
 def test_static_scratch_entry_rejects_oversize():
