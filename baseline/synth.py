@@ -78,6 +78,9 @@ def write_model(name: str, out_dir: str, dtype=torch.bfloat16, seed: int = 0, st
     top = {"model.embed_tokens.weight": rn(cfg.vocab_size, H), "model.norm.weight": torch.ones(H, dtype=dtype)}
     if not cfg.tie_embeddings:
         top["lm_head.weight"] = rn(cfg.vocab_size, H)
+        # the end-of-sequence row is zero: its logit is exactly 0 for every hidden state and never wins an arg-max over
+        # ~10^5 random logits, so a greedy benchmark run cannot stop early
+        top["lm_head.weight"][cfg.vocab_size - 1].zero_()
     flush(top)
     for i in range(cfg.num_layers):
         p = f"model.layers.{i}."

@@ -57,6 +57,7 @@ struct ArNormParams {
   const uint16_t* moe_ys; const int* moe_pos; const float* moe_w; const uint16_t* moe_add; int moe_topk;
   int M, N;
   int has_residual;
+  int defer_sync2;           // != 0: end after the broadcast + arrival; the consumer kernel waits on CNT2 >= EXPECT itself
   int trace;                 // != 0: CTA 0 writes globaltimer stamps of each phase to OFF_TRACE
   float eps, unit_offset;
 };
@@ -66,11 +67,6 @@ __device__ __forceinline__ void red_add_relaxed_sys(uint32_t* p, uint32_t v) {
 }
 __device__ __forceinline__ void mc_red_add_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("multimem.red.relaxed.sys.global.add.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
-  return v;
 }
 __device__ __forceinline__ float4 mc_ld_reduce_f32x4(const void* p) {
   float4 v;
@@ -108,16 +104,7 @@ __device__ __forceinline__ void arrive_aggregated(const CommCtx& c, uint32_t off
 }
 // bounded wait until the local counter has reached `target` (wrap-safe)
 __device__ __forceinline__ bool wait_counter(const CommCtx& c, uint32_t off, uint32_t target, int kernel_id, int site) {
-  const uint32_t* p = reinterpret_cast<const uint32_t*>(c.local + off);
-  if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
-  const uint64_t t0 = globaltimer_ns();
-  while (true) {
-    if ((int32_t)(ld_acquire_sys(p) - target) >= 0) return true;
-    if (globaltimer_ns() - t0 > FB_WAIT_LIMIT_NS) break;
-    __nanosleep(20);
-  }
-  report_error(ERR_PEER_TIMEOUT, kernel_id, site);
-  return false;
+  return wait_counter_ge(reinterpret_cast<const uint32_t*>(c.local + off), target, kernel_id, site);
 }
 
 // Phases 2.. of the fused all-reduce; called by every thread of every CTA.  `base` = value of the expect word
@@ -181,10 +168,16 @@ __device__ __forceinline__ void ar_norm_tail(const ArNormParams& p, uint32_t bas
       // the norm sees the rounded values, exactly what a separate RMSNorm kernel would read back
       const float2 q0 = unpack_16<BF16>(o.x), q1 = unpack_16<BF16>(o.y), q2 = unpack_16<BF16>(o.z), q3 = unpack_16<BF16>(o.w);
       ss += q0.x * q0.x + q0.y * q0.y + q1.x * q1.x + q1.y * q1.y + q2.x * q2.x + q2.y * q2.y + q3.x * q3.x + q3.y * q3.y;
-      if (c.mc) {
-        mc_st_b32x4(c.mc + p.off_h + eoff * 2, o);
-      } else {
-        for (int r = 0; r < c.tp; ++r) *reinterpret_cast<uint4*>(c.peer[r] + p.off_h + eoff * 2) = o;
+      // The residual stream stays with the row's owner: nobody else reads it (the next collective's phase 2 reads own
+      // rows only), so it does not cross NVLink.
+      *reinterpret_cast<uint4*>(c.local + p.off_h + eoff * 2) = o;
+      if (p.ln_w == nullptr) {
+        // no norm: the summed rows themselves are the result every rank needs
+        if (c.mc) {
+          mc_st_b32x4(c.mc + p.off_x + eoff * 2, o);
+        } else {
+          for (int r = 0; r < c.tp; ++r) *reinterpret_cast<uint4*>(c.peer[r] + p.off_x + eoff * 2) = o;
+        }
       }
     }
     if (p.ln_w != nullptr) {
@@ -231,7 +224,7 @@ __device__ __forceinline__ void ar_norm_tail(const ArNormParams& p, uint32_t bas
     if (trace) trace[4] = globaltimer_ns();
     arrive_aggregated(c, OFF_LOCAL2, OFF_CNT2, n_ctas);
     if (trace) trace[5] = globaltimer_ns();
-    wait_counter(c, OFF_CNT2, target, kernel_id, 2);
+    if (!p.defer_sync2) wait_counter(c, OFF_CNT2, target, kernel_id, 2);
     if (trace) trace[6] = globaltimer_ns();
     // the last CTA of this rank to get here publishes the new expected value for the next launch
     uint32_t* ticket = reinterpret_cast<uint32_t*>(c.local + OFF_TICKET);
@@ -429,7 +422,7 @@ extern "C" int fb_gemm_ar_norm(const void* X, const void* W, const void* bias, i
   ArNormParams p;
   fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
   p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
-  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
+  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.defer_sync2 = (has_residual >> 2) & 1; p.eps = eps; p.unit_offset = unit_offset;
   p.src = nullptr; p.src_f32 = 0; p.moe_ys = nullptr; p.moe_pos = nullptr; p.moe_w = nullptr; p.moe_add = nullptr; p.moe_topk = 0;
   CUtensorMap tmW, tmX;
   if (!make_tmap_2d(&tmW, W, N, K, ldw, 128, 64, 2, 3)) return -2;
@@ -473,7 +466,7 @@ extern "C" int fb_ar_norm(const void* src, int src_f32, int M, int N, void* aren
   ArNormParams p;
   fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
   p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
-  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
+  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.defer_sync2 = (has_residual >> 2) & 1; p.eps = eps; p.unit_offset = unit_offset;
   p.src = src; p.src_f32 = src_f32; p.moe_ys = nullptr; p.moe_pos = nullptr; p.moe_w = nullptr; p.moe_add = nullptr; p.moe_topk = 0;
   return launch_ar_norm(p, M, N, tp, dtype, reinterpret_cast<cudaStream_t>(stream_));
 }
@@ -489,11 +482,25 @@ extern "C" int fb_moe_combine_ar_norm(const void* ys, const int* pos, const floa
   ArNormParams p;
   fill_ctx(p.c, arena_local, arena_mc, peers, rank, tp);
   p.off_part = off_part; p.off_h = off_h; p.off_x = off_x; p.ln_w = (const uint16_t*)ln_w; p.M = M; p.N = N;
-  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.eps = eps; p.unit_offset = unit_offset;
+  p.has_residual = has_residual & 1; p.trace = (has_residual >> 1) & 1; p.defer_sync2 = (has_residual >> 2) & 1; p.eps = eps; p.unit_offset = unit_offset;
   p.src = nullptr; p.src_f32 = 0;
   p.moe_ys = (const uint16_t*)ys; p.moe_pos = pos; p.moe_w = w; p.moe_add = (const uint16_t*)add; p.moe_topk = topk;
   return launch_ar_norm(p, M, N, tp, dtype, reinterpret_cast<cudaStream_t>(stream_));
 }
+
+// One-thread kernel that ends once the deferred all-gather of the previous fused collective has landed on this rank
+// (CNT2 >= EXPECT); for consumers that cannot wait themselves.
+__global__ void comm_wait_kernel(const uint8_t* local) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(local + fb::OFF_EXPECT);
+  fb::wait_counter_ge(reinterpret_cast<const uint32_t*>(local + fb::OFF_CNT2), target, fb::KID_AR_NORM, 3);
+}
+extern "C" int fb_comm_wait(const void* arena_local, void* stream_) {
+  launch_k(comm_wait_kernel, dim3(1), dim3(1), 0, reinterpret_cast<cudaStream_t>(stream_), 0, reinterpret_cast<const uint8_t*>(arena_local));
+  return (int)cudaGetLastError();
+}
+extern "C" void fb_comm_header_offsets(unsigned* cnt2, unsigned* expect) { *cnt2 = fb::OFF_CNT2; *expect = fb::OFF_EXPECT; }
 
 extern "C" int fb_argmax_merge(const float* vals, const int* ids, int* out, int B, void* arena_local, void* arena_mc,
                                void* const* peers, int rank, int tp, unsigned long long off_buf, void* stream_) {

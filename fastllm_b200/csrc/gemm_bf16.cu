@@ -265,8 +265,21 @@ extern "C" int fb_gemm_pick_split(int M, int N, int K, int slots) {
 
 // Y = X W^T.  dtype: 0 = fp16, 1 = bf16.  X: [M, K] row stride ldx; W: [N, K] row stride ldw (elements).
 // nsplit <= 0 picks automatically.  Returns 0 on success, a cudaError_t, or -1 for unsupported shapes.
+extern "C" int fb_gemm_16bit_wait(const void* X, const void* W, void* out, const void* bias, const void* residual, int M, int N,
+                                  int K, int ldx, int ldw, int ld_out, int ld_res, int dtype, int flags, int nsplit,
+                                  const void* wait_cnt, const void* wait_expect, void* stream_);
+
 extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void* bias, const void* residual, int M, int N,
                              int K, int ldx, int ldw, int ld_out, int ld_res, int dtype, int flags, int nsplit, void* stream_) {
+  return fb_gemm_16bit_wait(X, W, out, bias, residual, M, N, K, ldx, ldw, ld_out, ld_res, dtype, flags, nsplit, nullptr, nullptr, stream_);
+}
+
+// Same, for activations that a fused collective broadcast without waiting for its peers (small-M path only): the kernel
+// itself waits until the arrival counter *wait_cnt has reached *wait_expect before it reads X.  Returns -3 when a wait
+// is requested for a shape that the small-M kernel does not cover.
+extern "C" int fb_gemm_16bit_wait(const void* X, const void* W, void* out, const void* bias, const void* residual, int M, int N,
+                                  int K, int ldx, int ldw, int ld_out, int ld_res, int dtype, int flags, int nsplit,
+                                  const void* wait_cnt, const void* wait_expect, void* stream_) {
   using namespace fb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0) return 0;
@@ -279,6 +292,9 @@ extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void
   p.flags = flags;
   p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0; p.w_row0 = 0; p.x_row0 = 0;
   for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
+  p.wait_cnt = reinterpret_cast<const uint32_t*>(wait_cnt);
+  p.wait_expect = reinterpret_cast<const uint32_t*>(wait_expect);
+  if (wait_cnt != nullptr && M > 256) return -3;
   const bool bf16 = dtype == 1;
   if (M <= 256) {
     const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;

@@ -61,6 +61,11 @@ struct GemmParams {
   int scatter_tp, scatter_rows, scatter_rank;
   int w_row0, x_row0;        // row offsets added to the weight / activation tile coordinates (grouped GEMM)
   float* scatter_out[8];
+  // Deferred all-gather wait: the activations were broadcast by a fused collective kernel that did not wait for its
+  // peers' rows to land.  The producer thread waits (bounded) until *wait_cnt has reached *wait_expect after it has
+  // requested the first ring of weight tiles and before it requests any activation tile.
+  const uint32_t* wait_cnt = nullptr;
+  const uint32_t* wait_expect = nullptr;
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
@@ -197,6 +202,12 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
         tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, p.w_row0 + n_tile * 128, pol_w);
       }
       pdl_wait();
+      if (p.wait_cnt != nullptr) {
+        // the expect word was written by the kernel before this one and is final after the dependency wait
+        const uint32_t target = *reinterpret_cast<const volatile uint32_t*>(p.wait_expect);
+        wait_counter_ge(p.wait_cnt, target, KID_GEMM_SMALLM, 9);      // on expiry: reported; the tile is computed from what is there
+        fence_proxy_async_global();
+      }
       for (int i = 0; i < pre; ++i)
         tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmX, &full_bar[i], (kb0 + i) * 64, p.x_row0, pol_x);
       for (int i = pre; i < kb_cnt; ++i) {

@@ -29,9 +29,10 @@ __device__ __forceinline__ void report_error(int code, int kernel_id, int site) 
   }
 }
 
-#ifndef FB_WAIT_LIMIT_NS
-#define FB_WAIT_LIMIT_NS 2000000000ull   // every device-side wait gives up after 2 s of wall time
-#endif
+// Every device-side wait gives up after this many nanoseconds of wall time (default 2 s).  A run-time value, one copy per
+// translation unit, set through fb_<unit>_set_wait_limit_ns; read only on the slow path of a wait (after a failed poll).
+static __device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+#define FB_WAIT_LIMIT_NS (*reinterpret_cast<volatile unsigned long long*>(&fb::g_wait_limit_ns))
 
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
@@ -100,6 +101,30 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, bool& 
   report_error(ERR_WAIT_TIMEOUT, kernel_id, site);
   return false;
 }
+
+// ---------------------------------------------------------------------------------------------
+// cross-GPU arrival counters (written by peers with system-scope reductions)
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];\n" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Bounded wait until *p has reached `target` (wrap-safe).  On expiry the failure is recorded and false returned.
+__device__ __forceinline__ bool wait_counter_ge(const uint32_t* p, uint32_t target, int kernel_id, int site) {
+  if ((int32_t)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if ((int32_t)(ld_acquire_sys_u32(p) - target) >= 0) return true;
+    if (globaltimer_ns() - t0 > FB_WAIT_LIMIT_NS) break;
+    __nanosleep(20);
+  }
+  report_error(ERR_PEER_TIMEOUT, kernel_id, site);
+  return false;
+}
+// Orders this thread's earlier generic-proxy accesses (e.g. the acquire load of a counter) before its later
+// async-proxy accesses (TMA loads of the data that counter guards).
+__device__ __forceinline__ void fence_proxy_async_global() { asm volatile("fence.proxy.async.global;\n" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------------
 // fences
@@ -327,4 +352,7 @@ __device__ __forceinline__ float2 unpack_16(uint32_t v) {
       e = cudaMemcpyToSymbol(fb::g_error_word, z, sizeof(z));                                      \
     }                                                                                              \
     return (int)e;                                                                                 \
+  }                                                                                                \
+  extern "C" int fb_##name##_set_wait_limit_ns(unsigned long long ns) {                            \
+    return (int)cudaMemcpyToSymbol(fb::g_wait_limit_ns, &ns, sizeof(ns));                          \
   }

@@ -189,17 +189,17 @@ class DecoderModel:
         self._cpu_runner = False              # the whole-model CPU runner owns fp32 pages
 
     # -----------------------------------------------------------------------------------------------
-    def _attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual, next_ln):
+    def _attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual, next_ln, consumer=None):
         c = self.cfg
         if c.use_mla:
-            return self._mla_attention(lw, x, fb, kv, residual, next_ln)
+            return self._mla_attention(lw, x, fb, kv, residual, next_ln, consumer)
         Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
         cos, sin = self.rope_tables(device=x.device)
         qkv = lw.qkv(x)
         k_pool, v_pool = kv
         if self.general_attn or lw.window or lw.sinks is not None:
             a = self._attention_general(lw, qkv, fb, kv)
-            return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln)
+            return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
         q = A.qkv_post(qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
                        lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
         if fb.is_decode:
@@ -214,7 +214,7 @@ class DecoderModel:
         else:
             a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
                                cu_q_host=fb.cu_q_host)
-        return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln)
+        return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
 
     def _attention_general(self, lw: AttentionWeights, qkv, fb: ForwardBatch, kv):
         """Attention for the less common variants (sliding window, sinks, logit soft-capping, norm after RoPE)."""
@@ -272,10 +272,19 @@ class DecoderModel:
             self._norm_cons = m
         return m
 
-    def _row_parallel_norm(self, w: LinearWeight, x, h, next_ln, post_ln=None):
+    @staticmethod
+    def _waits_itself(consumer) -> bool:
+        """True when ``consumer`` (the projection that reads the normalised rows next) runs the dense tensor-core GEMM,
+        whose producer thread can wait for a deferred all-gather after it has requested its first weight tiles."""
+        return (consumer is not None and consumer.kind == "dense" and LinearWeight.active_adapter is None
+                and consumer.k % 64 == 0 and consumer.n % 8 == 0)
+
+    def _row_parallel_norm(self, w: LinearWeight, x, h, next_ln, post_ln=None, consumer=None):
         """``h += row_parallel_linear(x)`` then ``RMSNorm(h)`` for the next block.  Returns (h, x_norm).
 
-        With the fused NVLink path this is ONE kernel (GEMM + reduce-scatter + residual + norm + all-gather).
+        With the fused NVLink path this is ONE kernel (GEMM + reduce-scatter + residual + norm + all-gather); when the
+        next reader of the normalised rows is ``consumer`` (a dense projection), the kernel does not wait for the
+        all-gather to land: that wait moves into the consumer's GEMM, behind its weight prefetch.
         """
         c = self.cfg
         if post_ln is not None:          # sandwich norm: normalise the sub-layer output, then add it to the residual stream
@@ -283,10 +292,11 @@ class DecoderModel:
             h = h + y
             return h, self._norm(h, next_ln)
         if self._fused_active:
-            r = self.tp.comm.fused.gemm_ar_norm(w, x, next_ln, c.rms_eps, c.norm_unit_offset, True)
+            defer = self._waits_itself(consumer)
+            r = self.tp.comm.fused.gemm_ar_norm(w, x, next_ln, c.rms_eps, c.norm_unit_offset, True, defer=defer)
             if r is None:
                 part = w(x)
-                r = self.tp.comm.fused.ar_norm(part, next_ln, c.rms_eps, c.norm_unit_offset, True)
+                r = self.tp.comm.fused.ar_norm(part, next_ln, c.rms_eps, c.norm_unit_offset, True, defer=defer)
             return r
         h = self._row_parallel(w, x, h)
         return h, self._norm(h, next_ln)
@@ -304,7 +314,7 @@ class DecoderModel:
             h = partial + h
         return h, self._norm(h, next_ln)
 
-    def _mla_attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual, next_ln):
+    def _mla_attention(self, lw: AttentionWeights, x, fb: ForwardBatch, kv, residual, next_ln, consumer=None):
         """Absorbed multi-head latent attention over a paged latent cache (kv_lora + rope dims per token).
 
         Reference: src/models/deepseekv2.cpp:283-697 (q_nope x W_UK -> MergeMLAPaged -> x W_UV -> o_proj).
@@ -333,7 +343,7 @@ class DecoderModel:
         q_full = torch.cat([q_lat, q_pe.to(x.dtype)], dim=-1)              # [T, H, lora + rope]
         o_lat = MOE.mla_paged_attention(q_full, lat_pool, fb, self.attn_scale, lora)   # [T, H, lora]
         o = torch.einsum("thl,hvl->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype).reshape(T, H * vd)
-        return self._row_parallel_norm(lw.o, o, residual, next_ln)
+        return self._row_parallel_norm(lw.o, o, residual, next_ln, consumer=consumer)
 
     @staticmethod
     def _glu(gu, act: str, interleaved: bool):
@@ -365,14 +375,14 @@ class DecoderModel:
             return B.linear(x, lw.router_16, out_f32=True)
         return torch.matmul(x.float(), lw.router.t())
 
-    def _mlp(self, lw: MLPWeights, x, residual, layer_idx, next_ln):
+    def _mlp(self, lw: MLPWeights, x, residual, layer_idx, next_ln, consumer=None):
         c = self.cfg
         if lw.experts is None:
             if c.hidden_act in ("silu", "swiglu"):
                 act = lw.gate_up(x, swiglu=True)
             else:
                 act = self._glu(lw.gate_up(x), c.hidden_act, lw.gate_up.interleaved)
-            return self._row_parallel_norm(lw.down, act, residual, next_ln, lw.post_ln)
+            return self._row_parallel_norm(lw.down, act, residual, next_ln, lw.post_ln, consumer)
         # ---- mixture of experts ----
         logits = self._router_logits(lw, x)
         if lw.router_logit_bias is not None:
@@ -423,13 +433,23 @@ class DecoderModel:
         n_layers = len(self.layers)
         x = self._norm(h, self.layers[0].attn.ln)
         for i, lw in enumerate(self.layers):
-            h, x = self._attention(lw.attn, x, fb, kv_caches[i], h, lw.mlp.ln)
-            next_ln = self.layers[i + 1].attn.ln if i + 1 < n_layers else self.final_norm
-            h, x = self._mlp(lw.mlp, x, h, i, next_ln)
+            # the projection that reads each fused collective's output first (it can take over the all-gather wait)
+            mlp_first = lw.mlp.gate_up if lw.mlp.experts is None else None
+            h, x = self._attention(lw.attn, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
+            if i + 1 < n_layers:
+                next_ln = self.layers[i + 1].attn.ln
+                na = self.layers[i + 1].attn
+                nxt = (na.q_a if na.q_a is not None else na.q_b) if c.use_mla else na.qkv
+            else:
+                next_ln = self.final_norm
+                nxt = self.lm_head if fb.logit_rows is None else None
+            h, x = self._mlp(lw.mlp, x, h, i, next_ln, nxt)
         # x is RMSNorm(h) with the final norm weight (row-wise, so selecting rows afterwards is equivalent)
         if fb.logit_rows is not None:
+            B.flush_pending_wait()
             x = x.index_select(0, fb.logit_rows)
         logits = self.lm_head(x, out_f32=True)
+        B.flush_pending_wait()          # no-op unless the head ran outside the GEMM that waits itself
         if c.logit_scale != 1.0:
             logits = logits * c.logit_scale
         if c.final_softcap:

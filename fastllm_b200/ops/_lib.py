@@ -24,6 +24,7 @@ LL = c_longlong
 
 _KERNEL_SIGS = {
     "fb_gemm_16bit": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
+    "fb_gemm_16bit_wait": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P, P],
     "fb_gemm_pick_split": [I, I, I, I],
     "fb_rmsnorm": [P, P, P, P, I, I, I, I, F, F, I, P],
     "fb_rmsnorm_quant": [P, P, P, P, I, I, I, I, F, F, I, I, P, I, P, P, I, P],
@@ -211,6 +212,20 @@ def check_device_errors(reset: bool = True) -> None:
         if buf[0] != 0:
             raise DeviceKernelError(
                 f"kernel error in '{name}': code={buf[0]} kernel_id={buf[1]} site={buf[2]} block=({buf[3]},{buf[4]})")
+
+
+def set_wait_limit_ns(ns: int) -> None:
+    """Time after which a device-side wait (mbarrier, peer arrival counter) gives up and reports, for every kernel of the
+    library on the current device.  Default 2 s; tests of the failure path use milliseconds."""
+    lib = kernels()._lib
+    for name in _ERROR_READERS:
+        fn = getattr(lib, f"fb_{name}_set_wait_limit_ns", None)
+        if fn is not None:
+            fn.argtypes = [ctypes.c_ulonglong]
+            fn.restype = c_int
+            rc = fn(int(ns))
+            if rc != 0:
+                raise RuntimeError(f"setting the wait limit of '{name}' failed with cudaError {rc}")
 
 
 def runtime():

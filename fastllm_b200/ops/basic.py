@@ -99,6 +99,35 @@ def cpu_linear_epilogue(y, residual, swiglu, interleaved, out_dtype=None):
     return y if out_dtype is None else y.to(out_dtype)
 
 
+# A fused tensor-parallel collective that ended without waiting for its peers' rows leaves a pending wait here:
+# (address of the arrival counter, address of its expected value, fallback that launches a stand-alone wait kernel).
+# The next ``linear`` hands the two addresses to its GEMM, whose producer thread waits after it has requested its first
+# weight tiles; any other path calls ``flush_pending_wait`` first.
+_pending_wait = None
+
+
+def set_pending_wait(cnt_ptr: int, expect_ptr: int, flush_fn) -> None:
+    global _pending_wait
+    flush_pending_wait()
+    _pending_wait = (cnt_ptr, expect_ptr, flush_fn)
+
+
+def flush_pending_wait() -> None:
+    """Resolve an outstanding deferred wait with a stand-alone kernel (consumers that cannot wait themselves)."""
+    global _pending_wait
+    if _pending_wait is not None:
+        fn = _pending_wait[2]
+        _pending_wait = None
+        fn()
+
+
+def _take_pending_wait():
+    global _pending_wait
+    w = _pending_wait
+    _pending_wait = None
+    return w
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: bool = False, interleaved: bool = True,
            out_f32: bool = False, out: torch.Tensor | None = None, nsplit: int = 0) -> torch.Tensor:
     """``y = x @ w.T`` with optional fused bias, SwiGLU (``w`` = gate/up stacked) and residual add.
@@ -106,6 +135,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: b
     x: ``[M, K]`` (row stride may exceed K), w: ``[N, K]``.  16-bit CUDA tensors run the tcgen05 GEMM.
     """
     if not x.is_cuda:
+        flush_pending_wait()
         # native kernels for decode-sized batches and for 16-bit weights (used in place); large fp32 GEMMs go to the BLAS
         # behind torch.matmul
         if cpu_native(x) and (x.numel() // x.shape[-1] <= 32 or w.dtype != torch.float32):
@@ -119,6 +149,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: b
     N = w.shape[0]
     if K % 64 != 0 or N % 8 != 0 or x.dtype not in (torch.float16, torch.bfloat16) or (x2.data_ptr() & 15) or (x2.stride(0) * 2) % 16:
         # shapes outside the tensor-core kernels' tiling (rare: odd projection widths): plain PyTorch definition
+        flush_pending_wait()
         return linear_ref(x, w, bias, residual, swiglu, interleaved, torch.float32 if out_f32 else None)
     if swiglu and not interleaved:
         raise ValueError("CUDA SwiGLU epilogue needs tile-interleaved gate/up weights (interleave_gate_up)")
@@ -132,14 +163,24 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: b
     dt = dtype_code(x.dtype)
     if M <= 256 or N % 32 != 0:
         step = 256
+        pend = _take_pending_wait()
         for m0 in range(0, M, step):
             m1 = min(M, m0 + step)
+            if pend is not None:
+                rc = lib.fb_gemm_16bit_wait(_ptr(x2[m0:m1]), _ptr(w), _ptr(out[m0:m1]), _ptr(bias),
+                                            _ptr(res2[m0:m1]) if res2 is not None else _ptr(None), m1 - m0, N, K, x2.stride(0),
+                                            w.stride(0), out.stride(0), res2.stride(0) if res2 is not None else 0, dt, flags, nsplit,
+                                            ctypes.c_void_p(pend[0]), ctypes.c_void_p(pend[1]), _stream())
+                pend = None
+                _lib.check(rc, "fb_gemm_16bit_wait")
+                continue
             rc = lib.fb_gemm_16bit(_ptr(x2[m0:m1]), _ptr(w), _ptr(out[m0:m1]), _ptr(bias),
                                    _ptr(res2[m0:m1]) if res2 is not None else _ptr(None), m1 - m0, N, K, x2.stride(0),
                                    w.stride(0), out.stride(0), res2.stride(0) if res2 is not None else 0, dt, flags, nsplit,
                                    _stream())
             _lib.check(rc, "fb_gemm_16bit")
     else:
+        flush_pending_wait()
         rc = lib.fb_gemm_16bit(_ptr(x2), _ptr(w), _ptr(out), _ptr(bias), _ptr(res2), M, N, K, x2.stride(0), w.stride(0),
                                out.stride(0), res2.stride(0) if res2 is not None else 0, dt, flags, nsplit, _stream())
         _lib.check(rc, "fb_gemm_16bit")

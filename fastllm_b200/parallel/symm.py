@@ -22,6 +22,7 @@ import torch
 import torch.distributed as dist
 
 from ..ops import _lib
+from ..ops import basic as B
 from ..ops.basic import _ptr, _stream, dtype_code
 
 P, I, F, ULL = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_ulonglong
@@ -30,7 +31,9 @@ _lib.register_sigs({
     "fb_ar_norm": [P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
     "fb_argmax_merge": [P, P, P, I, P, P, P, I, I, ULL, P],
     "fb_moe_combine_ar_norm": [P, P, P, P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
+    "fb_comm_wait": [P, P],
 }, ["comm"])
+OFF_CNT2, OFF_EXPECT = 128, 256      # arena header words the deferred all-gather wait reads (csrc/comm.cu)
 
 HEADER = 1024
 
@@ -77,13 +80,30 @@ class FusedComm:
 
     def load_h(self, h: torch.Tensor) -> torch.Tensor:
         """Place the (replicated) residual stream rows into the arena; returns the arena view."""
+        B.flush_pending_wait()
         M = h.shape[0]
         v = self.h_buf[:M]
         v.copy_(h)
         return v
 
-    def gemm_ar_norm(self, w, x: torch.Tensor, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True):
-        """h[:M] (+)= sum over ranks of x @ w.T ; x_out = RMSNorm(h) * ln_w.  One launch.  Returns (h, x_out) views."""
+    def _flags(self, has_residual: bool, defer: bool) -> int:
+        return (1 if has_residual else 0) | (2 if self.trace else 0) | (4 if defer else 0)
+
+    def _after_launch(self, defer: bool) -> None:
+        if defer:
+            B.set_pending_wait(self.local + OFF_CNT2, self.local + OFF_EXPECT, self.wait_all_gather)
+
+    def wait_all_gather(self) -> None:
+        """Stand-alone wait for a deferred all-gather (used when the next consumer is not a kernel that waits itself)."""
+        _lib.check(_lib.kernels().fb_comm_wait(ctypes.c_void_p(self.local), _stream()), "fb_comm_wait")
+
+    def gemm_ar_norm(self, w, x: torch.Tensor, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True,
+                     defer: bool = False):
+        """h[:M] (+)= sum over ranks of x @ w.T ; x_out = RMSNorm(h) * ln_w.  One launch.  Returns (h, x_out) views; of
+        ``h`` only this rank's own rows are current (the residual stream stays with the row owner).
+
+        ``defer``: the kernel ends after broadcasting its rows, without waiting for the peers' rows; the next ``linear``
+        on this stream waits inside its GEMM, after its weight prefetch (``ops.basic.set_pending_wait``)."""
         M, K = x.shape
         N = w.n
         if w.kind != "dense" or not self.usable(M, N) or (w.bias is not None and self.rank != 0 and False):
@@ -93,14 +113,16 @@ class FusedComm:
         rc = _lib.kernels().fb_gemm_ar_norm(_ptr(x), _ptr(wt), _ptr(bias), M, N, K, x.stride(0), wt.stride(0),
                                             ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
                                             self.off_part, self.off_h, self.off_x, _ptr(ln_w),
-                                            (1 if has_residual else 0) | (2 if self.trace else 0), float(eps), float(unit_offset), dtype_code(x.dtype), 0, _stream())
+                                            self._flags(has_residual, defer), float(eps), float(unit_offset), dtype_code(x.dtype), 0, _stream())
         if rc != 0:
             if rc == 701:      # cudaErrorLaunchOutOfResources: grid cannot be co-resident -> caller uses the unfused path
                 return None
             _lib.check(rc, "fb_gemm_ar_norm")
-        return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
+        self._after_launch(defer)
+        return self.h_buf[:M], self.x_buf[:M]
 
-    def ar_norm(self, partial: torch.Tensor, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True):
+    def ar_norm(self, partial: torch.Tensor, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True,
+                defer: bool = False):
         """Same as gemm_ar_norm for a partial sum computed elsewhere (any float dtype, ``[M, hidden]``)."""
         M, N = partial.shape
         if not (0 < M <= self.max_m and N == self.hidden):
@@ -109,12 +131,14 @@ class FusedComm:
             partial = partial.to(self.dtype).contiguous()
         rc = _lib.kernels().fb_ar_norm(_ptr(partial), 1 if partial.dtype == torch.float32 else 0, M, N, ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
                                        self.off_part, self.off_h, self.off_x, _ptr(ln_w),
-                                       (1 if has_residual else 0) | (2 if self.trace else 0), float(eps),
+                                       self._flags(has_residual, defer), float(eps),
                                        float(unit_offset), dtype_code(self.dtype), _stream())
         _lib.check(rc, "fb_ar_norm")
-        return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
+        self._after_launch(defer)
+        return self.h_buf[:M], self.x_buf[:M]
 
-    def moe_combine_ar_norm(self, ys, pos, w, add, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True):
+    def moe_combine_ar_norm(self, ys, pos, w, add, ln_w, eps: float, unit_offset: float = 0.0, has_residual: bool = True,
+                            defer: bool = False):
         """Expert-parallel combine: weighted sum of this rank's expert outputs (+ ``add``) formed inside the kernel that
         pushes it to the row owners, reduces over ranks, adds the residual, normalises and broadcasts.  One launch."""
         M, topk = pos.shape
@@ -123,10 +147,11 @@ class FusedComm:
             return None
         rc = _lib.kernels().fb_moe_combine_ar_norm(_ptr(ys), _ptr(pos), _ptr(w), _ptr(add), topk, M, N, ctypes.c_void_p(self.local),
                                                    ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp, self.off_part, self.off_h,
-                                                   self.off_x, _ptr(ln_w), (1 if has_residual else 0) | (2 if self.trace else 0),
+                                                   self.off_x, _ptr(ln_w), self._flags(has_residual, defer),
                                                    float(eps), float(unit_offset), dtype_code(self.dtype), _stream())
         _lib.check(rc, "fb_moe_combine_ar_norm")
-        return self.h_buf[:M], (self.x_buf[:M] if ln_w is not None else None)
+        self._after_launch(defer)
+        return self.h_buf[:M], self.x_buf[:M]
 
     # -- TPComm hooks --------------------------------------------------------------------------------
     def all_reduce(self, t, residual=None):
@@ -136,11 +161,12 @@ class FusedComm:
         return None
 
     def merge_argmax(self, ids: torch.Tensor, vals: torch.Tensor):
-        B = ids.shape[0]
-        if B > self.max_m:
+        n = ids.shape[0]
+        if n > self.max_m:
             return None
+        B.flush_pending_wait()
         out = torch.empty_like(ids)
-        rc = _lib.kernels().fb_argmax_merge(_ptr(vals), _ptr(ids), _ptr(out), B, ctypes.c_void_p(self.local),
+        rc = _lib.kernels().fb_argmax_merge(_ptr(vals), _ptr(ids), _ptr(out), n, ctypes.c_void_p(self.local),
                                             ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp, self.off_amax, _stream())
         _lib.check(rc, "fb_argmax_merge")
         return out

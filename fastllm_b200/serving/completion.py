@@ -197,6 +197,26 @@ class Completion:
 
         return sse()
 
+    async def _events(self, req: dict, is_disconnected=None, rid=None):
+        """Protocol-neutral stream of one chat request: ``("reasoning" | "content", text)`` pieces as they are decoded,
+        ``("tool_call", call)`` for every parsed call, and a final ``("finish", reason)``.  The three streaming protocols
+        (chat-completions chunks, Responses events, Anthropic events) are renderings of this stream."""
+        tools = req.get("tools")
+        ids, _ = self.build_prompt_ids(messages=req["messages"], tools=tools, chat_template_kwargs=req.get("chat_template_kwargs"))
+        parser = get_parser(self.model.tool_call_parser, self.model.get_type()) if tools else None
+        sp = StreamSplitter(parser, reasoning=self.think)
+        finish = "stop"
+        async for piece, fin in self.generate(ids, self.gen_kwargs(req), req.get("stop"), is_disconnected, rid):
+            finish = fin or finish
+            for kind, txt in sp.push(piece) if piece else []:
+                yield kind, txt
+        rest, calls = sp.finish()
+        if rest:
+            yield "content", rest
+        for c in calls:
+            yield "tool_call", c
+        yield "finish", ("tool_calls" if calls else finish)
+
     async def text_completion(self, req: dict, is_disconnected=None):
         ids, _ = self.build_prompt_ids(prompt=req.get("prompt", ""))
         text, finish = "", "stop"
@@ -219,7 +239,12 @@ class Completion:
             for it in inp:
                 if it.get("type", "message") == "message":
                     msgs.append({"role": it.get("role", "user"), "content": _content_text(it.get("content"))})
+        for t in req.get("tools") or []:          # Responses tools are flat; the chat template wants the nested form
+            if t.get("type") == "function" and "function" not in t:
+                t["function"] = {"name": t.get("name"), "description": t.get("description", ""), "parameters": t.get("parameters", {})}
         creq = dict(req, messages=msgs, stream=False, max_tokens=req.get("max_output_tokens"))
+        if req.get("stream"):
+            return self._responses_stream(creq, is_disconnected)
         r = await self.chat_completion(creq, is_disconnected)
         msg = r["choices"][0]["message"]
         output = []
@@ -237,6 +262,145 @@ class Completion:
                 "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"], "total_tokens": u["total_tokens"],
                           "input_tokens_details": {"cached_tokens": u["prompt_tokens_details"]["cached_tokens"]}}}
 
+    async def _responses_stream(self, creq: dict, is_disconnected=None):
+        """Server-sent events of the Responses protocol (reference: tools/fastllm_pytools/server.py:152-168 streams
+        ``/v1/responses``): response.created / in_progress, then per output item ``output_item.added`` ->
+        deltas -> ``*.done`` -> ``output_item.done``, and ``response.completed`` with the whole response and usage."""
+        rid = "resp_" + uuid.uuid4().hex
+        created = int(time.time())
+        model_name = creq.get("model") or self.model_name
+        seq = 0
+
+        def ev(kind, **body):
+            nonlocal seq
+            d = dict(type=kind, sequence_number=seq, **body)
+            seq += 1
+            return f"event: {kind}\ndata: " + json.dumps(d, ensure_ascii=False) + "\n\n"
+
+        def shell(status, output=None, usage=None):
+            return {"id": rid, "object": "response", "created_at": created, "status": status, "model": model_name,
+                    "output": output or [], "usage": usage}
+
+        yield ev("response.created", response=shell("in_progress"))
+        yield ev("response.in_progress", response=shell("in_progress"))
+        output = []
+        cur = None          # the open item: {"kind", "item", "text"}
+
+        def close_item():
+            nonlocal cur
+            out = []
+            if cur is None:
+                return out
+            idx = len(output)
+            it = cur["item"]
+            if cur["kind"] == "content":
+                part = {"type": "output_text", "text": cur["text"], "annotations": []}
+                it["content"] = [part]
+                it["status"] = "completed"
+                out.append(ev("response.output_text.done", item_id=it["id"], output_index=idx, content_index=0, text=cur["text"]))
+                out.append(ev("response.content_part.done", item_id=it["id"], output_index=idx, content_index=0, part=part))
+            else:
+                it["summary"] = [{"type": "summary_text", "text": cur["text"]}]
+                out.append(ev("response.reasoning_summary_text.done", item_id=it["id"], output_index=idx, summary_index=0, text=cur["text"]))
+            out.append(ev("response.output_item.done", output_index=idx, item=it))
+            output.append(it)
+            cur = None
+            return out
+
+        finish = "stop"
+        async for kind, val in self._events(creq, is_disconnected, rid):
+            if kind in ("content", "reasoning"):
+                if cur is None or cur["kind"] != kind:
+                    for line in close_item():
+                        yield line
+                    idx = len(output)
+                    if kind == "content":
+                        item = {"type": "message", "id": "msg_" + uuid.uuid4().hex[:16], "role": "assistant", "status": "in_progress", "content": []}
+                        yield ev("response.output_item.added", output_index=idx, item=item)
+                        yield ev("response.content_part.added", item_id=item["id"], output_index=idx, content_index=0,
+                                 part={"type": "output_text", "text": "", "annotations": []})
+                    else:
+                        item = {"type": "reasoning", "id": "rs_" + uuid.uuid4().hex[:16], "summary": []}
+                        yield ev("response.output_item.added", output_index=idx, item=item)
+                    cur = {"kind": kind, "item": item, "text": ""}
+                cur["text"] += val
+                if kind == "content":
+                    yield ev("response.output_text.delta", item_id=cur["item"]["id"], output_index=len(output), content_index=0, delta=val)
+                else:
+                    yield ev("response.reasoning_summary_text.delta", item_id=cur["item"]["id"], output_index=len(output), summary_index=0, delta=val)
+            elif kind == "tool_call":
+                for line in close_item():
+                    yield line
+                idx = len(output)
+                item = {"type": "function_call", "id": "fc_" + uuid.uuid4().hex[:16], "call_id": val["id"], "name": val["function"]["name"],
+                        "arguments": "", "status": "in_progress"}
+                yield ev("response.output_item.added", output_index=idx, item=item)
+                args = val["function"]["arguments"] or ""
+                yield ev("response.function_call_arguments.delta", item_id=item["id"], output_index=idx, delta=args)
+                yield ev("response.function_call_arguments.done", item_id=item["id"], output_index=idx, arguments=args)
+                item = dict(item, arguments=args, status="completed")
+                yield ev("response.output_item.done", output_index=idx, item=item)
+                output.append(item)
+            else:
+                finish = val
+        for line in close_item():
+            yield line
+        u = self.last_usage
+        usage = {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"], "total_tokens": u["total_tokens"],
+                 "input_tokens_details": {"cached_tokens": u["prompt_tokens_details"]["cached_tokens"]}}
+        final = shell("incomplete" if finish == "length" else "completed", output, usage)
+        final["output_text"] = "".join(p["text"] for it in output if it["type"] == "message" for p in it["content"])
+        if finish == "length":
+            final["incomplete_details"] = {"reason": "max_output_tokens"}
+        yield ev("response.incomplete" if finish == "length" else "response.completed", response=final)
+
+    async def _anthropic_stream(self, creq: dict, is_disconnected=None):
+        """Server-sent events of the Anthropic Messages protocol (reference: tools/fastllm_pytools/server.py:169-180):
+        message_start, then per content block start / deltas / stop, message_delta with the stop reason and output
+        token count, message_stop."""
+        mid = "msg_" + uuid.uuid4().hex[:24]
+        model_name = creq.get("model") or self.model_name
+
+        def ev(kind, **body):
+            return f"event: {kind}\ndata: " + json.dumps(dict(type=kind, **body), ensure_ascii=False) + "\n\n"
+
+        yield ev("message_start", message={"id": mid, "type": "message", "role": "assistant", "model": model_name, "content": [],
+                                           "stop_reason": None, "stop_sequence": None, "usage": {"input_tokens": 0, "output_tokens": 0}})
+        yield ev("ping")
+        index = -1
+        open_kind = None
+        finish = "stop"
+        async for kind, val in self._events(creq, is_disconnected, mid):
+            if kind in ("content", "reasoning"):
+                if open_kind != kind:
+                    if open_kind is not None:
+                        yield ev("content_block_stop", index=index)
+                    index += 1
+                    open_kind = kind
+                    block = {"type": "text", "text": ""} if kind == "content" else {"type": "thinking", "thinking": ""}
+                    yield ev("content_block_start", index=index, content_block=block)
+                delta = {"type": "text_delta", "text": val} if kind == "content" else {"type": "thinking_delta", "thinking": val}
+                yield ev("content_block_delta", index=index, delta=delta)
+            elif kind == "tool_call":
+                if open_kind is not None:
+                    yield ev("content_block_stop", index=index)
+                    open_kind = None
+                index += 1
+                yield ev("content_block_start", index=index, content_block={"type": "tool_use", "id": val["id"].replace("call_", "toolu_"),
+                                                                            "name": val["function"]["name"], "input": {}})
+                yield ev("content_block_delta", index=index, delta={"type": "input_json_delta", "partial_json": val["function"]["arguments"] or "{}"})
+                yield ev("content_block_stop", index=index)
+            else:
+                finish = val
+        if open_kind is not None:
+            yield ev("content_block_stop", index=index)
+        u = self.last_usage
+        yield ev("message_delta", delta={"stop_reason": {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}.get(finish, "end_turn"),
+                                         "stop_sequence": None},
+                 usage={"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"],
+                        "cache_read_input_tokens": u["prompt_tokens_details"]["cached_tokens"]})
+        yield ev("message_stop")
+
     # ---- Anthropic Messages API -------------------------------------------------------------------
     async def anthropic_messages(self, req: dict, is_disconnected=None):
         msgs = []
@@ -248,6 +412,8 @@ class Completion:
         tools = [{"type": "function", "function": {"name": t["name"], "description": t.get("description", ""), "parameters": t.get("input_schema", {})}}
                  for t in req.get("tools") or []] or None
         creq = dict(req, messages=msgs, stream=False, tools=tools, stop=req.get("stop_sequences"))
+        if req.get("stream"):
+            return self._anthropic_stream(creq, is_disconnected)
         r = await self.chat_completion(creq, is_disconnected)
         msg = r["choices"][0]["message"]
         content = []

@@ -53,14 +53,27 @@ def build_app(model, model_name: str = "fastllm-b200", api_key: str = "", dev_mo
     @app.post("/v1/responses")
     @app.post("/v1/response")
     async def responses(request: Request):
-        return JSONResponse(await comp.responses(await request.json(), request.is_disconnected))
+        req = await request.json()
+        try:
+            r = await comp.responses(req, request.is_disconnected)
+        except Exception as e:
+            return _bad(f"{type(e).__name__}: {e}", 500)
+        if req.get("stream"):
+            return StreamingResponse(r, media_type="text/event-stream")
+        return JSONResponse(r)
 
     @app.post("/v1/messages")
     async def messages(request: Request):
         req = await request.json()
         if "max_tokens" not in req:
             return _bad("'max_tokens' is required")
-        return JSONResponse(await comp.anthropic_messages(req, request.is_disconnected))
+        try:
+            r = await comp.anthropic_messages(req, request.is_disconnected)
+        except Exception as e:
+            return _bad(f"{type(e).__name__}: {e}", 500)
+        if req.get("stream"):
+            return StreamingResponse(r, media_type="text/event-stream")
+        return JSONResponse(r)
 
     @app.post("/v1/embed")
     @app.post("/v1/embeddings")

@@ -112,3 +112,48 @@ def test_chat_completion_logprobs(client):
         assert e["logprob"] <= 0 and len(e["top_logprobs"]) == 3
         # greedy decoding: the chosen token is the most likely one
         assert abs(e["logprob"] - e["top_logprobs"][0]["logprob"]) < 1e-5
+
+
+def _sse_events(text):
+    out = []
+    for block in text.split("\n\n"):
+        ev, data = None, None
+        for ln in block.split("\n"):
+            if ln.startswith("event: "):
+                ev = ln[7:]
+            elif ln.startswith("data: "):
+                data = json.loads(ln[6:])
+        if ev is not None:
+            out.append((ev, data))
+    return out
+
+
+def test_responses_stream_events(client):
+    r = client("POST", "/v1/responses", {"input": "hello", "max_output_tokens": 6, "temperature": 0, "stream": True})
+    assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+    evs = _sse_events(r.text)
+    kinds = [k for k, _ in evs]
+    assert kinds[0] == "response.created" and kinds[1] == "response.in_progress"
+    assert kinds[-1] in ("response.completed", "response.incomplete")
+    assert [d["sequence_number"] for _, d in evs] == list(range(len(evs)))
+    deltas = "".join(d["delta"] for k, d in evs if k == "response.output_text.delta")
+    final = evs[-1][1]["response"]
+    assert final["output_text"] == deltas and final["usage"]["output_tokens"] >= 1
+    if deltas:
+        assert "response.output_item.added" in kinds and "response.output_text.done" in kinds and "response.output_item.done" in kinds
+    # same request without streaming gives the same text
+    r2 = client("POST", "/v1/responses", {"input": "hello", "max_output_tokens": 6, "temperature": 0})
+    assert r2.json()["output_text"] == deltas
+
+
+def test_anthropic_stream_events(client):
+    r = client("POST", "/v1/messages", {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0, "stream": True})
+    assert r.status_code == 200
+    evs = _sse_events(r.text)
+    kinds = [k for k, _ in evs]
+    assert kinds[0] == "message_start" and kinds[-1] == "message_stop" and kinds[-2] == "message_delta"
+    assert evs[-2][1]["delta"]["stop_reason"] in ("end_turn", "max_tokens") and evs[-2][1]["usage"]["output_tokens"] >= 1
+    text = "".join(d["delta"]["text"] for k, d in evs if k == "content_block_delta" and d["delta"]["type"] == "text_delta")
+    r2 = client("POST", "/v1/messages", {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0})
+    assert "".join(b["text"] for b in r2.json()["content"] if b["type"] == "text") == text
+    assert kinds.count("content_block_start") == kinds.count("content_block_stop")

@@ -43,7 +43,9 @@ def main():
         h, xn = r
         torch.cuda.synchronize()
         _lib.check_device_errors()
-        eh = (h.float() - ref_h.float()).abs().max().item()
+        rows_per = (M + world - 1) // world
+        own = slice(rank * rows_per, min(M, (rank + 1) * rows_per))     # the residual stream stays with the row owner
+        eh = (h[own].float() - ref_h[own].float()).abs().max().item() if own.start < M else 0.0
         ex = (xn.float() - ref_x.float()).abs().max().item()
         assert eh < 0.08 and ex < 0.08, f"gemm_ar_norm mismatch it={it}: {eh} {ex}"
         # stand-alone all-reduce + norm of a partial
@@ -51,9 +53,12 @@ def main():
         tot = part.clone()
         dist.all_reduce(tot)
         ref_h2 = (tot + h.float()).bfloat16()
+        # the owner's h rows carry on from the first kernel; other rows of ref_h2 are rebuilt from the reference h
+        ref_h2 = (tot + ref_h.float()).bfloat16()
         h2, x2 = fused.ar_norm(part, ln, 1e-5)
         torch.cuda.synchronize()
-        assert (h2.float() - ref_h2.float()).abs().max().item() < 0.08
+        if own.start < M:
+            assert (h2[own].float() - ref_h2[own].float()).abs().max().item() < 0.08
         assert (x2.float() - B.rmsnorm_ref(ref_h2, ln, 1e-5)[0].float()).abs().max().item() < 0.08
     # argmax merge
     vals = torch.randn(17, device=dev) + (rank == 1) * 0.0
@@ -81,9 +86,24 @@ def main():
     _lib.check_device_errors()
     same = sum(a == b for o, o1 in zip(outs, outs1) for a, b in zip(o, o1))
     total = sum(len(o) for o in outs)
-    # bf16 partial sums are ordered differently across ranks: allow rare divergence, require the first tokens to agree
     assert all(o[0] == o1[0] for o, o1 in zip(outs, outs1)), (outs, outs1)
-    assert same >= total * 0.5, (outs, outs1)
+    # logits of one decode step from identical cache contents: the sharded model must agree with the single-rank model to
+    # bf16 accumulation noise (a dropped shard or a stale row shows up as an O(1) error here, whatever the arg-max does)
+    def step_logits(engine, full_vocab):
+        hs = [engine.launch(p, GenerationConfig(max_new_tokens=3, ignore_eos=True, output_logits=True)) for p in prompts]
+        rq = [engine.requests[h] for h in hs]
+        while any(len(r.output_ids) < 2 and not r.finished() for r in rq):
+            engine.step()
+        lg = torch.stack([r.last_logits[:full_vocab] for r in rq])
+        for h in hs:
+            engine.abort(h)
+        engine.step()
+        return lg
+    lg_tp = step_logits(eng, cfg.vocab_size)
+    lg_1 = step_logits(eng1, cfg.vocab_size)
+    scale_ref = lg_1.abs().max().item()
+    err = (lg_tp - lg_1).abs().max().item()
+    assert err < 0.05 * scale_ref + 0.05, f"TP logits differ from single-rank logits: max abs {err} (scale {scale_ref})" 
     # expert parallel MoE (fused combine + cross-rank reduce) vs one rank
     from fastllm_b200.parallel.ep import EPInfo
 
