@@ -35,6 +35,17 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD, OCC>::TMEM_COLS);
 }
 
+// QKV projection with the per-head post-processing (norm, RoPE, cache append) as its epilogue
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(192, 1)
+gemm_qkv_post_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
+                     const QkvEpilogueParams qp) {
+  uint32_t tmem_base;
+  QkvEpilogue<BF16> epi{qp};
+  gemm_smallm_device<MPAD, BF16, 1, QkvEpilogue<BF16>>(tmW, tmX, p, tmem_base, KID_GEMM_SMALLM_PLAIN, epi);
+  if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD, 1>::TMEM_COLS);
+}
+
 // ---------------------------------------------------------------------------------------------------
 // large-M kernel: tile 128 tokens x BN out-features, BK = 64
 // ---------------------------------------------------------------------------------------------------
@@ -230,6 +241,31 @@ static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX,
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
 }
 
+template <int MPAD, bool BF16>
+static cudaError_t launch_qkv_post(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const QkvEpilogueParams& qp,
+                                   int nsplit, int n_tiles, cudaStream_t stream) {
+  using Cfg = SmallMCfg<MPAD, 1>;
+  auto kern = gemm_qkv_post_kernel<MPAD, BF16>;
+  static DeviceOnce configured;
+  if (configured.need()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = add_pdl_attr(attr, 1);
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, qp);
+}
+
 template <int BN, bool BF16>
 static cudaError_t launch_largem(const CUtensorMap& tmX, const CUtensorMap& tmW, const GemmParams& p, cudaStream_t stream) {
   using Cfg = LargeMCfg<BN>;
@@ -346,4 +382,59 @@ extern "C" int fb_gemm_16bit_wait(const void* X, const void* W, void* out, const
   if (bn == 256)
     return (int)(bf16 ? launch_largem<256, true>(tmX, tmW, p, stream) : launch_largem<256, false>(tmX, tmW, p, stream));
   return (int)(bf16 ? launch_largem<128, true>(tmX, tmW, p, stream) : launch_largem<128, false>(tmX, tmW, p, stream));
+}
+
+// QKV projection (head_dim 128, M <= 256, N = (Hq + 2 Hkv) * 128) with split / per-head RMSNorm / RoPE / paged-cache append in
+// the epilogue: Q rows go to q_out, K and V rows to their cache slots (slots[j] < 0: not cached).  wait_cnt / wait_expect as in
+// fb_gemm_16bit_wait.  rope_mode 0 none, 1 neox, 2 interleaved; rot must be a multiple of 8.  Returns -1 for other shapes.
+extern "C" int fb_gemm_qkv_post(const void* X, const void* W, const void* bias, int M, int N, int K, int ldx, int ldw, int dtype,
+                                const void* wait_cnt, const void* wait_expect, void* q_out, int ld_q, void* k_pool, void* v_pool,
+                                const int* positions, const int* slots, const void* q_norm_w, const void* k_norm_w,
+                                const float* cos_tab, const float* sin_tab, int Hq, int Hkv, int rot, int rope_mode, float eps,
+                                float norm_unit_offset, void* stream_) {
+  using namespace fb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0) return 0;
+  if (M > 256 || K % 64 != 0 || N != (Hq + 2 * Hkv) * 128 || (dtype != 0 && dtype != 1) || rot % 8 != 0 || rot > 128 || rot < 0) return -1;
+  GemmParams p;
+  p.out = nullptr; p.bias = bias; p.residual = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ld_out = 0; p.ld_res = 0;
+  p.kb_total = K / 64;
+  p.flags = bias ? GEMM_BIAS : 0;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0; p.w_row0 = 0; p.x_row0 = 0;
+  for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
+  p.wait_cnt = reinterpret_cast<const uint32_t*>(wait_cnt);
+  p.wait_expect = reinterpret_cast<const uint32_t*>(wait_expect);
+  const bool bf16 = dtype == 1;
+  const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int n_tiles = N / 128;
+  if (n_tiles > sm_count) return -1;
+  const int nsplit = fb_gemm_pick_split(M, N, K, sm_count);
+  p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
+  p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
+  QkvEpilogueParams qp;
+  qp.q_out = (uint16_t*)q_out; qp.ld_q = ld_q; qp.k_pool = (uint16_t*)k_pool; qp.v_pool = (uint16_t*)v_pool;
+  qp.positions = positions; qp.slots = slots; qp.q_norm_w = (const uint16_t*)q_norm_w; qp.k_norm_w = (const uint16_t*)k_norm_w;
+  qp.cos_tab = cos_tab; qp.sin_tab = sin_tab; qp.Hq = Hq; qp.Hkv = Hkv; qp.rot = rot; qp.rope_mode = rope_mode;
+  qp.eps = eps; qp.norm_unit_offset = norm_unit_offset;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, W, N, K, ldw, 128, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
+#define FB_QP(MP)                                                                                     \
+  return (int)(bf16 ? launch_qkv_post<MP, true>(tmW, tmX, p, qp, nsplit, n_tiles, stream)              \
+                    : launch_qkv_post<MP, false>(tmW, tmX, p, qp, nsplit, n_tiles, stream));
+  switch (mpad) {
+    case 16: FB_QP(16)
+    case 32: FB_QP(32)
+    case 64: FB_QP(64)
+    case 128: FB_QP(128)
+    default: FB_QP(256)
+  }
+#undef FB_QP
 }

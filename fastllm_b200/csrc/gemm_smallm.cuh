@@ -152,11 +152,121 @@ __device__ __forceinline__ void smallm_reduce_store(const GemmParams& p, uint8_t
   }
 }
 
+// Default epilogue: column slices, bias -> SwiGLU -> residual -> store / scatter.
+template <bool BF16>
+struct StoreEpilogue {
+  __device__ __forceinline__ void operator()(const GemmParams& p, uint8_t* smem, int split, int nsplit, int n_tile) const {
+    smallm_reduce_store<BF16>(p, smem, split, nsplit, n_tile);
+  }
+};
+
+// Epilogue of the QKV projection for head_dim 128: one 128-wide output tile is exactly one head, so everything the reference
+// does in a separate launch after the projection (split, per-head RMSNorm of Q and K, RoPE, K/V rows into their cache pages,
+// Q to its buffer: QKVRMSNormRopeSplitAppendPagedCache, src/devices/cuda/fastllm-cuda.cu:12190) happens here on the fp32 tile.
+// The k-split reduction is by token rows (a warp owns a row, a lane four consecutive dims), so a head's 128 values of one
+// token are in one warp.  Values are rounded to the 16-bit dtype at the points where the unfused sequence stores them
+// (projection output, norm output), which keeps the two paths bit-compatible.
+struct QkvEpilogueParams {
+  uint16_t* q_out; int ld_q;
+  uint16_t* k_pool; uint16_t* v_pool;
+  const int* positions; const int* slots;
+  const uint16_t* q_norm_w; const uint16_t* k_norm_w;
+  const float* cos_tab; const float* sin_tab;
+  int Hq, Hkv, rot, rope_mode;         // rope_mode: 0 none, 1 neox (i pairs with i + rot/2), 2 interleaved (2i, 2i+1)
+  float eps, norm_unit_offset;
+};
+
+template <bool BF16>
+struct QkvEpilogue {
+  QkvEpilogueParams q;
+  __device__ __forceinline__ void operator()(const GemmParams& p, uint8_t* smem, int split, int nsplit, int n_tile) const {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const uint32_t P_addr = smem_u32(smem);
+    const int rows_per = (p.M + nsplit - 1) / nsplit;
+    const int r0 = split * rows_per;
+    int r1 = r0 + rows_per; if (r1 > p.M) r1 = p.M;
+    const int head = n_tile;
+    const bool is_q = head < q.Hq, is_k = !is_q && head < q.Hq + q.Hkv;
+    const uint16_t* nw = is_q ? q.q_norm_w : (is_k ? q.k_norm_w : nullptr);
+    const int half = q.rot >> 1;
+    const int e0 = lane * 4;
+    for (int j = r0 + warp; j < r1; j += nwarps) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < nsplit; ++s) {
+        const float4 v = ld_dsmem_f4(mapa_u32(P_addr + (uint32_t)(j * 128 + e0) * 4u, (uint32_t)s));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      if (p.flags & GEMM_BIAS) {
+        const uint32_t* bp = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint16_t*>(p.bias) + n_tile * 128 + e0);
+        const float2 b0 = unpack_16<BF16>(bp[0]), b1 = unpack_16<BF16>(bp[1]);
+        acc.x += b0.x; acc.y += b0.y; acc.z += b1.x; acc.w += b1.y;
+      }
+      // the projection's output as it would have been stored
+      float2 t0 = unpack_16<BF16>(pack_16<BF16>(acc.x, acc.y)), t1 = unpack_16<BF16>(pack_16<BF16>(acc.z, acc.w));
+      float v[4] = {t0.x, t0.y, t1.x, t1.y};
+      if (nw != nullptr) {
+        float ss = v[0] * v[0] + v[1] * v[1] + v[2] * v[2] + v[3] * v[3];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float inv = rsqrtf(ss / 128.0f + q.eps);
+        const uint32_t* wp = reinterpret_cast<const uint32_t*>(nw + e0);
+        const float2 w0 = unpack_16<BF16>(wp[0]), w1 = unpack_16<BF16>(wp[1]);
+        t0 = unpack_16<BF16>(pack_16<BF16>(v[0] * inv * (w0.x + q.norm_unit_offset), v[1] * inv * (w0.y + q.norm_unit_offset)));
+        t1 = unpack_16<BF16>(pack_16<BF16>(v[2] * inv * (w1.x + q.norm_unit_offset), v[3] * inv * (w1.y + q.norm_unit_offset)));
+        v[0] = t0.x; v[1] = t0.y; v[2] = t1.x; v[3] = t1.y;
+      }
+      if ((is_q || is_k) && q.rope_mode != 0) {
+        const int pos = q.positions[j];
+        const float* ct = q.cos_tab + (size_t)pos * half;
+        const float* st = q.sin_tab + (size_t)pos * half;
+        if (q.rope_mode == 2) {
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const int i = lane * 2 + k;          // pair index
+            if (i < half) {
+              const float c = ct[i], sn = st[i], a = v[2 * k], b = v[2 * k + 1];
+              v[2 * k] = a * c - b * sn;
+              v[2 * k + 1] = a * sn + b * c;
+            }
+          }
+        } else {
+          // neox; rot is a multiple of 8, so a lane's four dims lie on one side and its partner lane holds the other side
+          const int hl = half >> 2;              // lanes per half
+          const bool first = e0 < half, in_rot = e0 < q.rot;
+          const int partner = first ? lane + hl : lane - hl;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float other = __shfl_sync(0xffffffffu, v[k], in_rot ? (partner & 31) : lane);
+            if (in_rot) {
+              const int f = (first ? e0 : e0 - half) + k;
+              const float c = ct[f], sn = st[f];
+              v[k] = first ? v[k] * c - other * sn : v[k] * c + other * sn;
+            }
+          }
+        }
+      }
+      uint16_t* dst;
+      if (is_q) {
+        dst = q.q_out + (size_t)j * q.ld_q + (size_t)head * 128;
+      } else {
+        const int slot = q.slots[j];
+        if (slot < 0) continue;                  // warp-uniform: the whole warp works on row j
+        const int kvh = is_k ? head - q.Hq : head - q.Hq - q.Hkv;
+        dst = (is_k ? q.k_pool : q.v_pool) + ((size_t)slot * q.Hkv + kvh) * 128;
+      }
+      uint2 o;
+      o.x = pack_16<BF16>(v[0], v[1]);
+      o.y = pack_16<BF16>(v[2], v[3]);
+      *reinterpret_cast<uint2*>(dst + e0) = o;
+    }
+  }
+};
+
 // Body of the small-M kernel.  Returns with the output tile written and every cluster peer done reading this
 // CTA's shared memory; the caller still owns TMEM (returned in tmem_base_out) and must release it from warp 1.
-template <int MPAD, bool BF16, int OCC = 1>
+template <int MPAD, bool BF16, int OCC = 1, class Epi = StoreEpilogue<BF16>>
 __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p,
-                                                   uint32_t& tmem_base_out, int kernel_id) {
+                                                   uint32_t& tmem_base_out, int kernel_id, const Epi& epi = Epi()) {
   using Cfg = SmallMCfg<MPAD, OCC>;
   const int KID_GEMM_SMALLM = kernel_id;
   extern __shared__ uint8_t smem_raw[];
@@ -266,7 +376,7 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
   tc_fence_before_sync();
   cluster_sync_all();
 
-  smallm_reduce_store<BF16>(p, smem, split, nsplit, n_tile);
+  epi(p, smem, split, nsplit, n_tile);
   cluster_sync_all();   // peers may still be reading this CTA's partial tile
   tmem_base_out = tmem_base;
 }

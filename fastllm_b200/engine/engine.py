@@ -353,6 +353,14 @@ class LLMEngine:
         if all(r.gen.is_simple_greedy() for r in reqs):
             return sampling.greedy(logits).tolist()
         lg = logits.float().clone()
+        for row, r in enumerate(reqs):
+            proc = r.gen.logits_processor
+            allowed = proc(r.output_ids) if proc is not None else None
+            if allowed is not None:
+                keep = torch.as_tensor(list(allowed), dtype=torch.long, device=lg.device)
+                masked = torch.full_like(lg[row], float("-inf"))
+                masked[keep] = lg[row, keep]
+                lg[row] = masked
         greedy_rows = [r.gen.is_simple_greedy() or not r.gen.do_sample for r in reqs]
         tk = [1 if g else r.gen.top_k for r, g in zip(reqs, greedy_rows)]
         recent = [r.all_ids[-r.gen.last_n:] for r in reqs]

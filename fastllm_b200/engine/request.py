@@ -27,11 +27,14 @@ class GenerationConfig:
     output_logits: bool = False
     seed: int | None = None
     logprobs: int = 0
+    # ``logits_processor(output_ids) -> allowed token ids or None``: tokens outside the returned set are masked before sampling
+    # (tool-call name constraints).  A request that carries one is sampled on the host-visible path, never in the decode graph.
+    logits_processor: object | None = None
 
     def is_simple_greedy(self) -> bool:
         """Arg-max decoding with no penalty: eligible for the in-graph greedy sampler
         (reference: GenerationConfig::IsSimpleGreedy)."""
-        if self.output_logits or self.logprobs:
+        if self.output_logits or self.logprobs or self.logits_processor is not None:
             return False
         if abs(self.repeat_penalty - 1.0) > 1e-8:
             return False

@@ -413,7 +413,7 @@ class model:
                                 top_p=d["top_p"] if top_p is None else top_p, temperature=temperature,
                                 repeat_penalty=d["repetition_penalty"] if repeat_penalty is None else repeat_penalty,
                                 stop_token_ids=list(stop_token_ids or []), output_logits=bool(kw.get("output_logits", False)),
-                                logprobs=int(kw.get("logprobs", 0) or 0))
+                                logprobs=int(kw.get("logprobs", 0) or 0), logits_processor=kw.get("logits_processor"))
 
     # ---- handle-level API ---------------------------------------------------------------------------
     def launch_stream_response(self, query, history=None, **gen_kwargs) -> int:

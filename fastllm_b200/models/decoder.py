@@ -195,13 +195,16 @@ class DecoderModel:
             return self._mla_attention(lw, x, fb, kv, residual, next_ln, consumer)
         Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
         cos, sin = self.rope_tables(device=x.device)
-        qkv = lw.qkv(x)
         k_pool, v_pool = kv
         if self.general_attn or lw.window or lw.sinks is not None:
-            a = self._attention_general(lw, qkv, fb, kv)
+            a = self._attention_general(lw, lw.qkv(x), fb, kv)
             return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
-        q = A.qkv_post(qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
-                       lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
+        # decode-sized batches with head_dim 128: projection, per-head norm, RoPE and cache append are one launch
+        q = A.qkv_proj_post(x, lw.qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
+                            lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset) if x.dim() == 2 else None
+        if q is None:
+            q = A.qkv_post(lw.qkv(x), fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
+                           lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
         if fb.is_decode:
             qm = 0
             if lw.o.kind != "dense" and lw.post_ln is None:

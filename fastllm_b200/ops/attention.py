@@ -164,6 +164,40 @@ def qkv_post(qkv, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, h
     return q_out
 
 
+_FUSED_QKV = __import__("os").environ.get("FB_FUSED_QKV_POST", "1") == "1"
+
+
+def qkv_proj_post(x, w, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, head_dim, cos, sin, rope_mode=ROPE_NEOX,
+                  rot_dim=None, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_unit_offset=0.0):
+    """QKV projection + ``qkv_post`` in one launch for decode-sized batches: ``w`` is a dense ``LinearWeight`` with
+    ``(Hq + 2 Hkv) * 128`` output rows; the per-head norm / RoPE / cache append run as the GEMM's epilogue.  Returns Q
+    ``[T, Hq * 128]``, or None when the shape is outside the fused kernel (the caller then runs the two steps)."""
+    from .basic import _take_pending_wait
+    from .quant import LinearWeight
+
+    Hq, Hkv, D = num_q_heads, num_kv_heads, head_dim
+    rot = rot_dim or D
+    T = x.shape[0]
+    if (not _FUSED_QKV or not x.is_cuda or D != 128 or T > 256 or w.kind != "dense" or LinearWeight.active_adapter is not None
+            or x.dtype not in (torch.float16, torch.bfloat16) or w.w.dtype != x.dtype or w.n != (Hq + 2 * Hkv) * D or w.k % 64 != 0
+            or rot % 8 != 0 or rot > D or w.n // 128 > 148 or k_pool.dtype != x.dtype or x.stride(-1) != 1
+            or (x.data_ptr() & 15) or (x.stride(0) * 2) % 16):
+        return None
+    q_out = torch.empty((T, Hq * D), device=x.device, dtype=x.dtype)
+    pend = _take_pending_wait()
+    P = ctypes.c_void_p
+    rc = _lib.kernels().fb_gemm_qkv_post(_ptr(x), _ptr(w.w), _ptr(w.bias), T, w.n, w.k, x.stride(0), w.w.stride(0), dtype_code(x.dtype),
+                                         P(pend[0]) if pend else P(0), P(pend[1]) if pend else P(0), _ptr(q_out), q_out.stride(0),
+                                         _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(slots), _ptr(q_norm_w), _ptr(k_norm_w),
+                                         _ptr(cos), _ptr(sin), Hq, Hkv, rot, rope_mode, float(eps), float(norm_unit_offset), _stream())
+    if rc == -1:
+        if pend is not None:
+            pend[2]()
+        return None
+    _lib.check(rc, "fb_gemm_qkv_post")
+    return q_out
+
+
 # ---------------------------------------------------------------------------------------------------
 # paged attention
 # ---------------------------------------------------------------------------------------------------

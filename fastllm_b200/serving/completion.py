@@ -74,7 +74,23 @@ class Completion:
             lp = int(req.get("top_logprobs") or (req["logprobs"] if isinstance(req["logprobs"], int) and not isinstance(req["logprobs"], bool) else 1))
         return dict(max_length=int(mx), do_sample=do_sample, top_p=req.get("top_p"), top_k=top_k, temperature=temperature,
                     repeat_penalty=req.get("repetition_penalty") or req.get("frequency_penalty_as_repeat"),
-                    stop_token_ids=req.get("stop_token_ids"), logprobs=max(0, min(lp, 20)))
+                    stop_token_ids=req.get("stop_token_ids"), logprobs=max(0, min(lp, 20)),
+                    logits_processor=self.tool_constraint(req))
+
+    def tool_constraint(self, req: dict):
+        """Name constraint for requests that declare tools: while the model writes a function name in its tool-call markup only
+        continuations of a declared name can be sampled (on by default, ``"tool_call_constraint": false`` in the request or
+        ``tool_choice: "none"`` turns it off)."""
+        tools = req.get("tools")
+        if not tools or req.get("tool_call_constraint") is False or req.get("tool_choice") == "none":
+            return None
+        from .toolcall_constraints import build_constraint
+
+        try:
+            name = get_parser(self.model.tool_call_parser, self.model.get_type()).name
+            return build_constraint(self.model.tokenizer, name, tools)
+        except Exception:
+            return None
 
     def logprobs_content(self, r) -> list | None:
         """OpenAI ``choices[].logprobs.content`` entries of a finished request (None when logprobs were not requested)."""

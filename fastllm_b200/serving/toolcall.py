@@ -154,6 +154,115 @@ class MinimaxM2Parser(ToolParser):
         return (text.split("<minimax:tool_call>")[0].strip(), calls) if calls else (text, [])
 
 
+def _typed(v: str):
+    j = _loads_lenient(v)
+    return j if (j is not None and not isinstance(j, str)) else v
+
+
+class DeepSeekV4Parser(ToolParser):
+    """DSML: ``<｜DSML｜tool_calls><｜DSML｜invoke name="NAME"><｜DSML｜parameter name="K" string="true|false">V</｜DSML｜parameter>
+    ...</｜DSML｜invoke></｜DSML｜tool_calls>``; ``string="false"`` values are JSON.  The tag prefix also appears spelled ``\\DSML\\``.
+    (reference: openai_server/tool_parsers/deepseekv4_tool_parser.py:58-80)"""
+    name = "deepseek_v4"
+    start_markers = ("<｜DSML｜tool_calls>", "<\\DSML\\tool_calls>")
+    _T = r"(?:｜DSML｜|\\DSML\\)"
+    _block = re.compile(r"<" + _T + r"tool_calls>(.*?)(?:</" + _T + r"tool_calls>|$)", re.S)
+    _inv = re.compile(r'<' + _T + r'invoke\s+name="([^"]+)"\s*>(.*?)</' + _T + r'invoke>', re.S)
+    _par = re.compile(r'<' + _T + r'parameter\s+name="([^"]+)"\s+string="(true|false)"\s*>(.*?)</' + _T + r'parameter>', re.S)
+
+    def parse(self, text):
+        calls = []
+        for b in self._block.finditer(text):
+            for m in self._inv.finditer(b.group(1)):
+                args = {}
+                for k, is_str, v in self._par.findall(m.group(2)):
+                    if is_str == "true":
+                        args[k] = v
+                    else:
+                        j = _loads_lenient(v)
+                        args[k] = v if j is None else j
+                calls.append(_call(m.group(1), args))
+        if not calls:
+            return text, []
+        content = self._block.sub("", text)
+        return (content if content.strip() else ""), calls
+
+
+class HYV3Parser(ToolParser):
+    """Hunyuan V3: ``<tool_calls><tool_call>NAME<tool_sep><arg_key>K</arg_key><arg_value>V</arg_value>...</tool_call></tool_calls>``;
+    the special tokens may carry a ``:suffix`` inside the angle brackets (``<tool_call:x>``), which is accepted on every tag.
+    (reference: openai_server/tool_parsers/hy_v3_tool_parser.py:61-110, 140-160)"""
+    name = "hy_v3"
+    start_markers = ("<tool_calls", "<tool_call")
+    _sfx = r"(?::[^>]*)?"
+    _call_re = re.compile(r"<tool_call" + _sfx + r">(.*?)<tool_sep" + _sfx + r">(.*?)(?:</tool_call" + _sfx + r">|$)", re.S)
+    _kv = re.compile(r"<arg_key" + _sfx + r">(.*?)</arg_key" + _sfx + r">\s*<arg_value" + _sfx + r">(.*?)</arg_value" + _sfx + r">", re.S)
+    _strip = re.compile(r"<tool_calls" + _sfx + r">.*?(?:</tool_calls" + _sfx + r">|$)|<tool_call" + _sfx + r">.*?(?:</tool_call" + _sfx + r">|$)", re.S)
+
+    def parse(self, text):
+        calls = []
+        for m in self._call_re.finditer(text):
+            args = {k.strip(): _typed(v) for k, v in self._kv.findall(m.group(2))}
+            calls.append(_call(m.group(1).strip(), args))
+        return (self._strip.sub("", text).strip(), calls) if calls else (text, [])
+
+
+class KimiK3Parser(ToolParser):
+    """Kimi K3 XTML: ``<|open|>tools<|sep|><|open|>call tool="NAME" index="1"<|sep|><|open|>argument key="K" type="string|json"<|sep|>V
+    <|close|>argument<|sep|>...<|close|>call<|sep|><|close|>tools<|sep|>``; attribute values escape ``"`` and ``&`` as entities; a call
+    may carry one ``<|open|>json<|sep|>{...}<|close|>json<|sep|>`` block instead of arguments.  Call ids are ``NAME:index-1``.
+    (reference: openai_server/tool_parsers/kimi_k3_tool_parser.py:63-200)"""
+    name = "kimi_k3"
+    start_markers = ("<|open|>tools", "<|open|>call")
+    _O, _C, _S = r"<\|open\|>", r"<\|close\|>", r"<\|sep\|>"
+    _UNTIL = r"(?:(?!" + _S + r").)*?"
+    _call_re = re.compile(_O + r"\s*call\s+(?P<attrs>" + _UNTIL + r")" + _S + r"(?P<body>.*?)" + _C + r"\s*call\s*" + _S, re.S)
+    _arg_re = re.compile(_O + r"\s*argument\s+(?P<attrs>" + _UNTIL + r")" + _S + r"(?P<value>.*?)" + _C + r"\s*argument\s*" + _S, re.S)
+    _json_re = re.compile(_O + r"\s*json(?:\s+" + _UNTIL + r")?" + _S + r"(?P<value>.*?)" + _C + r"\s*json\s*" + _S, re.S)
+    _attr_re = re.compile(r'(?P<key>\w+)="(?P<value>[^"]*)"')
+    _head_re = re.compile(_O + r"\s*(?:tools\s*" + _S + r"|call[\s<])")
+
+    def _attrs(self, t):
+        return {m["key"]: m["value"].replace("&quot;", '"').replace("&amp;", "&") for m in self._attr_re.finditer(t)}
+
+    def parse(self, text):
+        calls = []
+        for m in self._call_re.finditer(text):
+            a = self._attrs(m["attrs"])
+            if not a.get("tool"):
+                continue
+            args = {}
+            for am in self._arg_re.finditer(m["body"]):
+                aa = self._attrs(am["attrs"])
+                v = am["value"]
+                if aa.get("type", "string") != "string":
+                    j = _loads_lenient(v)
+                    v = v if j is None else j
+                args[aa.get("key", "")] = v
+            if not args:
+                jm = self._json_re.search(m["body"])
+                j = _loads_lenient(jm["value"]) if jm else None
+                if isinstance(j, dict):
+                    args = j
+            c = _call(a["tool"], args)
+            if a.get("index", "").isdigit():
+                c["id"] = f"{a['tool']}:{int(a['index']) - 1}"
+            calls.append(c)
+        if not calls:
+            return text, []
+        hm = self._head_re.search(text)
+        return (text[:hm.start()].strip() if hm else ""), calls
+
+
+class PoolsideV1Parser(Glm45Parser):
+    """Poolside: the GLM-4.5 key/value form, ``<tool_call>NAME\\n<arg_key>K</arg_key><arg_value>V</arg_value>...</tool_call>``; a call
+    without arguments is ``<tool_call>NAME</tool_call>``; keys never contain ``<``.
+    (reference: openai_server/tool_parsers/poolside_v1_tool_parser.py:50-70)"""
+    name = "poolside_v1"
+    _re = re.compile(r"<tool_call>\s*([^\n<]+?)\s*\n?\s*((?:<arg_key>.*?)?)</tool_call>", re.S)
+    _kv = re.compile(r"<arg_key>([^<]*?)</arg_key>\s*<arg_value>(.*?)</arg_value>", re.S)
+
+
 class JsonParser(ToolParser):
     """Bare JSON object / array of ``{"name", "arguments"|"parameters"}`` (Llama-3.1 style)."""
     name = "json"
@@ -166,13 +275,15 @@ class JsonParser(ToolParser):
         return ("", calls) if calls else (text, [])
 
 
-PARSERS = {p.name: p for p in (HermesParser, Qwen3CoderParser, DeepSeekV3Parser, DeepSeekV31Parser, Glm45Parser, KimiK2Parser,
-                               MinimaxM2Parser, JsonParser)}
+PARSERS = {p.name: p for p in (HermesParser, Qwen3CoderParser, DeepSeekV3Parser, DeepSeekV31Parser, DeepSeekV4Parser, Glm45Parser,
+                               KimiK2Parser, KimiK3Parser, HYV3Parser, PoolsideV1Parser, MinimaxM2Parser, JsonParser)}
 PARSERS["glm47"] = Glm45Parser
 PARSERS["llama3_json"] = JsonParser
 
 _AUTO = {"qwen2": "hermes", "qwen3": "hermes", "qwen3_moe": "hermes", "deepseek_v3": "deepseek_v3", "deepseek_v32": "deepseek_v31",
-         "kimi_k2": "kimi_k2", "glm4_moe": "glm45", "minimax_m2": "minimax_m2", "llama": "json"}
+         "kimi_k2": "kimi_k2", "kimi_k3": "kimi_k3", "glm4_moe": "glm45", "glm_moe_dsa": "glm47", "minimax_m2": "minimax_m2", "llama": "json",
+         "deepseek_v4": "deepseek_v4", "hy_v3": "hy_v3", "hunyuan_v1_dense": "hermes", "hunyuan_v1_moe": "hermes", "laguna": "poolside_v1",
+         "qwen3_next": "hermes", "qwen3_5": "qwen3_coder", "qwen3_5_moe": "qwen3_coder"}
 
 
 def get_parser(name: str = "auto", model_type: str = "") -> ToolParser:

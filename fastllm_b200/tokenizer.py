@@ -128,6 +128,13 @@ class Tokenizer:
             return self.native.decode(ids, skip_special_tokens)
         return bytes(i for i in ids if 0 <= i < 256).decode("utf-8", errors="replace")
 
+    def vocab_size(self) -> int:
+        if self.hf is not None:
+            return len(self.hf)
+        if self.native is not None:
+            return self.native.vocab_size()
+        return 256
+
     def eos_ids(self) -> list[int]:
         out = []
         if self.hf is not None and self.hf.eos_token_id is not None:

@@ -712,3 +712,38 @@ def test_peer_wait_runs_out_and_is_reported():
         _close(xv, B.rmsnorm_ref(ref_h, ln, 1e-5)[0], 3e-2, 3e-2, "x after recovery")
     finally:
         _lib.set_wait_limit_ns(2_000_000_000)
+
+
+@pytest.mark.parametrize("mode,rot,qknorm,bias", [(A.ROPE_NEOX, 128, True, False), (A.ROPE_NEOX, 64, False, True),
+                                                  (A.ROPE_INTERLEAVED, 128, False, False), (A.ROPE_NONE, 128, True, True)])
+@pytest.mark.parametrize("T,K", [(1, 256), (21, 1024), (64, 4096), (200, 512)])
+def test_qkv_projection_with_fused_post(mode, rot, qknorm, bias, T, K):
+    """QKV GEMM whose epilogue does split + per-head norm + RoPE + cache append, against the PyTorch fp32 definition of the
+    projection followed by the PyTorch definition of the post-processing."""
+    from fastllm_b200.ops.quant import LinearWeight
+
+    torch.manual_seed(17)
+    Hq, Hkv, D, dt = 8, 2, 128, torch.bfloat16
+    N = (Hq + 2 * Hkv) * D
+    x = (torch.randn(T, K) * 0.5).to(dt)
+    w = (torch.randn(N, K) * 0.05).to(dt)
+    b = torch.randn(N).to(dt) if bias else None
+    pos = torch.randint(0, 500, (T,), dtype=torch.int32)
+    slots = torch.randperm(4 * 128)[:T].int()
+    if T > 3:
+        slots[3] = -1
+    cos, sin = A.build_rope_tables(rot, 512, 10000.0)
+    qn = (1 + 0.1 * torch.randn(D)).to(dt) if qknorm else None
+    kn = (1 + 0.1 * torch.randn(D)).to(dt) if qknorm else None
+    kp, vp = torch.zeros(4, 128, Hkv, D, dtype=dt), torch.zeros(4, 128, Hkv, D, dtype=dt)
+    qkv_ref = B.linear_ref(x, w, bias=b)
+    q_ref = A.qkv_post(qkv_ref, pos, slots, kp, vp, Hq, Hkv, D, cos, sin, mode, rot, qn, kn, 1e-6)
+    kp2, vp2 = torch.zeros_like(kp).to(DEV), torch.zeros_like(vp).to(DEV)
+    lw = LinearWeight.from_dense(w.to(DEV), bias=b.to(DEV) if bias else None)
+    d = lambda t: t.to(DEV) if t is not None else None
+    q_out = A.qkv_proj_post(x.to(DEV), lw, pos.to(DEV), slots.to(DEV), kp2, vp2, Hq, Hkv, D, cos.to(DEV), sin.to(DEV), mode, rot,
+                            d(qn), d(kn), 1e-6)
+    assert q_out is not None, "fused QKV kernel refused a supported shape"
+    _close(q_out.cpu(), q_ref, 4e-2, 3e-2, "q", fro=2e-2)
+    _close(kp2.cpu(), kp, 4e-2, 3e-2, "k pool", fro=2e-2)
+    _close(vp2.cpu(), vp, 3e-2, 2e-2, "v pool", fro=2e-2)

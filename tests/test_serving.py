@@ -157,3 +157,87 @@ def test_anthropic_stream_events(client):
     r2 = client("POST", "/v1/messages", {"messages": [{"role": "user", "content": "hello"}], "max_tokens": 6, "temperature": 0})
     assert "".join(b["text"] for b in r2.json()["content"] if b["type"] == "text") == text
     assert kinds.count("content_block_start") == kinds.count("content_block_stop")
+
+
+MORE_GOLDEN = [
+    ("deepseek_v4", '查一下。\n<｜DSML｜tool_calls><｜DSML｜invoke name="plan_trip"><｜DSML｜parameter name="days" string="false">3</｜DSML｜parameter>'
+                    '<｜DSML｜parameter name="note" string="true">靠窗</｜DSML｜parameter></｜DSML｜invoke></｜DSML｜tool_calls>',
+     "plan_trip", {"days": 3, "note": "靠窗"}, "查一下。\n"),
+    ("hy_v3", "<tool_calls><tool_call>f<tool_sep><arg_key>x</arg_key><arg_value>3</arg_value></tool_call></tool_calls>", "f", {"x": 3}, ""),
+    ("hy_v3", "<tool_calls:a1><tool_call:a1>f<tool_sep:a1><arg_key:a1>x</arg_key:a1><arg_value:a1>3</arg_value:a1></tool_call:a1></tool_calls:a1>",
+     "f", {"x": 3}, ""),
+    ("kimi_k3", 'ok <|open|>tools<|sep|><|open|>call tool="f" index="1"<|sep|><|open|>argument key="x" type="json"<|sep|>3<|close|>argument<|sep|>'
+                '<|close|>call<|sep|><|close|>tools<|sep|>', "f", {"x": 3}, "ok"),
+    ("kimi_k3", '<|open|>call tool="f" index="2"<|sep|><|open|>json<|sep|>{"x": 3}<|close|>json<|sep|><|close|>call<|sep|>', "f", {"x": 3}, ""),
+    ("poolside_v1", "<tool_call>f\n<arg_key>x</arg_key><arg_value>3</arg_value></tool_call>", "f", {"x": 3}, ""),
+    ("glm47", "<tool_call>f\n<arg_key>x</arg_key>\n<arg_value>3</arg_value>\n</tool_call>", "f", {"x": 3}, ""),
+]
+
+
+@pytest.mark.parametrize("parser,text,name,args,content", MORE_GOLDEN)
+def test_more_parser_golden(parser, text, name, args, content):
+    got, calls = tc.get_parser(parser).parse(text)
+    assert len(calls) == 1 and calls[0]["function"]["name"] == name
+    assert json.loads(calls[0]["function"]["arguments"]) == args
+    assert (got or "") == content
+    # streamed in small pieces: no markup leaks into the content, the call comes out at the end
+    sp = tc.StreamSplitter(tc.get_parser(parser), reasoning=False)
+    out = []
+    for i in range(0, len(text), 5):
+        out += sp.push(text[i:i + 5])
+    rest, calls2 = sp.finish()
+    streamed = "".join(t for _, t in out) + (rest or "")
+    assert len(calls2) == 1 and calls2[0]["function"]["name"] == name
+    assert "tool_call" not in streamed and "DSML" not in streamed and "<|open|>" not in streamed
+
+
+class _CharTok:
+    """One token per character; decode joins."""
+
+    chars = [chr(c) for c in range(32, 127)] + ["\n"]
+
+    def vocab_size(self):
+        return len(self.chars)
+
+    def decode(self, ids, skip_special_tokens=False):
+        return "".join(self.chars[i] for i in ids)
+
+    def encode(self, s):
+        return [self.chars.index(c) for c in s]
+
+
+def test_tool_name_constraint_masks_to_declared_names():
+    from fastllm_b200.serving.toolcall_constraints import ToolNameConstraint, build_constraint
+
+    tok = _CharTok()
+    c = ToolNameConstraint(tok, "hermes", ["get_weather", "get_time", "search"])
+    assert c(tok.encode("Let me think. ")) is None                           # outside a name position: unconstrained
+    pre = tok.encode('<tool_call>\n{"name": "')
+    first = {tok.chars[i] for i in c(pre)}
+    assert first == {"g", "s"}
+    after = {tok.chars[i] for i in c(pre + tok.encode("get_"))}
+    assert after == {"w", "t"}
+    done = {tok.chars[i] for i in c(pre + tok.encode("search"))}
+    assert done == {'"'}                                                     # a complete name can only be closed
+    assert c(pre + tok.encode('search"')) is None                            # closed: unconstrained again
+    tools = [{"type": "function", "function": {"name": "add"}}]
+    assert build_constraint(tok, "qwen3_coder", tools)(tok.encode("<function=")) == [tok.chars.index("a")]
+    assert build_constraint(tok, "json", tools) is None                      # no name position in that format
+
+
+def test_engine_applies_logits_processor():
+    """The sampler masks what the request's processor does not allow, greedy or sampled, on the scheduler rank."""
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.models import preset, random_init
+
+    m = random_init(preset("tiny-llama"), "cpu", torch.float32, std=0.05)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=256), num_pages=16)
+    allowed = [5, 9, 11]
+    seen = []
+
+    def proc(out_ids):
+        seen.append(len(out_ids))
+        return allowed if len(out_ids) % 2 == 0 else None
+
+    outs = eng.generate([[1, 2, 3, 4]], GenerationConfig(max_new_tokens=8, ignore_eos=True, logits_processor=proc))[0]
+    assert all(t in allowed for t in outs[0::2]) and len(outs) == 8 and seen[:3] == [0, 1, 2]
