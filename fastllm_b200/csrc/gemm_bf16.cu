@@ -415,6 +415,8 @@ extern "C" int fb_gemm_qkv_post(const void* X, const void* W, const void* bias, 
   }
   const int n_tiles = N / 128;
   if (n_tiles > sm_count) return -1;
+  // Power-of-two cluster sizes only: clusters of 3 or 6 CTAs measured 35-50 % slower on this part (they fit the GPCs badly
+  // and fewer of them are resident at once), although 48 heads x 3 would cover 144 of the 148 SMs.
   const int nsplit = fb_gemm_pick_split(M, N, K, sm_count);
   p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
   p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);

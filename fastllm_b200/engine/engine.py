@@ -272,6 +272,15 @@ class LLMEngine:
     def _prefill_step(self, reqs) -> int:
         budget = self.cfg.chunked_prefill_size
         chunks, owners = [], []
+        # Requests that are already decoding ride along as one-token chunks, so a long prompt's prefill never stalls them for
+        # more than one chunk (the reference batches prefill and decode rows in one forward, src/models/basellm.cpp:1786-2545).
+        decoding = []
+        if self.cfg.mixed_prefill_decode:
+            decoding = self._ensure_decode_pages([r for r in self.running if r.state == RequestState.DECODE])
+            reqs = [r for r in reqs if r in self.running and r.state == RequestState.PREFILL]
+            for r in decoding:
+                chunks.append(([r.all_ids[-1]], r.total_len - 1, r.pages, True))
+            budget = max(self.page_len, budget - len(decoding))
         for r in reqs:
             if budget <= 0:
                 break
@@ -283,14 +292,22 @@ class LLMEngine:
             chunks.append((toks[r.num_computed:r.num_computed + n], r.num_computed, r.pages, done))
             owners.append((r, n, done))
             budget -= n
+        if not chunks:
+            return 0
         logits = self.runner.prefill(chunks)
         produced = 0
         finals = [r for r, _, d in owners if d]
         for r, n, _ in owners:
             r.num_computed += n
-        if finals:
-            toks = self._sample(finals, logits)
-            for r, t in zip(finals, toks):
+        for r in decoding:
+            r.num_computed = r.total_len
+        if decoding or finals:
+            toks = self._sample(decoding + finals, logits)
+            for r, t in zip(decoding, toks):
+                produced += self._emit(r, int(t))
+            if decoding:
+                self.decode_tokens += len(decoding)
+            for r, t in zip(finals, toks[len(decoding):]):
                 if r.recompute_tokens is not None and r.output_ids:
                     # recomputation after eviction: the next token was already produced before the eviction
                     r.recompute_tokens = None
@@ -306,25 +323,7 @@ class LLMEngine:
     def _decode_step(self, reqs) -> int:
         if not reqs:
             return 0
-        # make sure every request has a page for the token it is about to write
-        for r in list(reqs):
-            if r not in self.running or r.state != RequestState.DECODE:
-                continue                     # evicted (or ended) earlier in this loop on behalf of another request
-            pos = r.total_len - 1            # position of the token fed in this step
-            need = self._pages_needed(pos + 1) - len(r.pages)
-            while need > 0:
-                pg = self.pm.alloc(need)
-                if pg is not None:
-                    r.pages.extend(pg)
-                    break
-                if not self._evict_for_pages(need):
-                    if r in self.running:
-                        self.running.remove(r)
-                    self._finish(r, "length")
-                    break
-                if r not in self.running:    # the victim was the request that is asking
-                    break
-        reqs = [r for r in reqs if r in self.running and r.state == RequestState.DECODE]
+        reqs = self._ensure_decode_pages(reqs)
         if not reqs:
             return 0
         ids = [r.all_ids[-1] for r in reqs]
@@ -343,6 +342,28 @@ class LLMEngine:
         self.decode_steps += 1
         self.decode_tokens += produced
         return produced
+
+    def _ensure_decode_pages(self, reqs):
+        """Make sure every decoding request has a page for the token it is about to write; evicts the longest decoding
+        request when the pool is empty.  Returns the requests that can run this step."""
+        for r in list(reqs):
+            if r not in self.running or r.state != RequestState.DECODE:
+                continue                     # evicted (or ended) earlier in this loop on behalf of another request
+            pos = r.total_len - 1            # position of the token fed in this step
+            need = self._pages_needed(pos + 1) - len(r.pages)
+            while need > 0:
+                pg = self.pm.alloc(need)
+                if pg is not None:
+                    r.pages.extend(pg)
+                    break
+                if not self._evict_for_pages(need):
+                    if r in self.running:
+                        self.running.remove(r)
+                    self._finish(r, "length")
+                    break
+                if r not in self.running:    # the victim was the request that is asking
+                    break
+        return [r for r in reqs if r in self.running and r.state == RequestState.DECODE]
 
     def _sample(self, reqs, logits):
         m = self.model

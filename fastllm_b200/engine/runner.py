@@ -32,6 +32,7 @@ class EngineConfig:
     prefix_cache: bool = True
     page_len: int = A.PAGE_LEN
     check_device_errors_every: int = 64
+    mixed_prefill_decode: bool = True    # a prefill step also advances the requests that are already decoding (one token each)
 
 
 class _DecodeSlot:

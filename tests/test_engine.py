@@ -367,3 +367,29 @@ def test_model_convenience_methods(tmp_path):
     with pytest.raises(RuntimeError):
         m.set_kv_cache_dtype("fp8_e4m3")
     m.release_memory()
+
+
+def test_decode_rides_along_with_prefill_chunks():
+    """A request that is decoding keeps producing one token per scheduler step while a long prompt is prefilled in chunks, and
+    both end with the tokens of an unmixed run."""
+    m = _model()
+    short, long_ = _prompts(m.cfg.vocab_size, (20, 700), seed=5)
+    gen = GenerationConfig(max_new_tokens=12, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=1024, prefix_cache=False, mixed_prefill_decode=False),
+                    num_pages=32).generate([short, long_], gen)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=1024, prefix_cache=False, chunked_prefill_size=128), num_pages=32)
+    h0 = eng.launch(short, gen)
+    eng.step()                                      # prefill of the short request -> its first token
+    r0 = eng.requests[h0]
+    assert len(r0.output_ids) == 1
+    h1 = eng.launch(long_, gen)
+    r1 = eng.requests[h1]
+    per_step = []
+    while r1.state.name in ("WAITING", "PREFILL"):
+        before = len(r0.output_ids)
+        eng.step()
+        per_step.append(len(r0.output_ids) - before)
+    assert len(per_step) >= 5 and all(n == 1 for n in per_step[:5])     # never stalled by the 700-token prompt
+    while not (r0.finished() and r1.finished()):
+        eng.step()
+    assert [r0.output_ids, r1.output_ids] == ref
