@@ -71,6 +71,11 @@ def _bench(model, args):
 def main(argv=None):
     argv = list(sys.argv[1:] if argv is None else argv)
     cmds = {"run", "chat", "tui", "server", "serve", "webui", "bench", "benchmark", "export", "download", "config"}
+    if not argv or argv[0] == "tui":
+        # no arguments: the deployment form, as with the reference (tools/fastllm_pytools/cli.py:113-118)
+        from . import tui
+
+        return tui.main(plain="--plain" in argv)
     cmd = argv.pop(0) if argv and argv[0] in cmds else "chat"
     from .util import make_normal_llm_model, make_normal_parser
 

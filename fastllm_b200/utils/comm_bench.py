@@ -9,7 +9,6 @@ from __future__ import annotations
 
 import argparse
 import json
-import os
 
 import torch
 import torch.distributed as dist
@@ -77,14 +76,40 @@ def main():
             return B.rmsnorm(p, ln, 1e-5)
 
         t_gemm_nccl = _timeit(nccl_path, dev)
+        # the pair a decoder layer runs: fused row-parallel GEMM, then the column-parallel GEMM that reads its output --
+        # with the all-gather wait inside the first kernel, and with the wait deferred into the consumer GEMM
+        wc = [LinearWeight.from_dense((torch.randn(2 * args.inter // world, H, device=dev) * 0.02).bfloat16()) for _ in range(3)]
+
+        def pair(i, defer):
+            _h, xn = fused.gemm_ar_norm(ws[i % 6], x, ln, 1e-5, defer=defer)
+            return wc[i % 3](xn, swiglu=False)
+
+        t_pair = _timeit(lambda i: pair(i, False), dev)
+        t_pair_deferred = _timeit(lambda i: pair(i, True), dev)
+        # phase stamps of one traced launch (CTA 0 of this rank; device global timer, ns)
+        fused.trace = True
+        fused.gemm_ar_norm(ws[0], x, ln, 1e-5)
+        tr = fused.read_trace()
+        fused.trace = False
+        ph = {"gemm_and_push_us": (tr[1] - tr[0]) / 1e3, "sync1_arrive_us": (tr[2] - tr[1]) / 1e3, "sync1_wait_us": (tr[3] - tr[2]) / 1e3,
+              "reduce_norm_broadcast_us": (tr[4] - tr[3]) / 1e3, "sync2_arrive_us": (tr[5] - tr[4]) / 1e3, "sync2_wait_us": (tr[6] - tr[5]) / 1e3}
+        w_bytes = H * K * 2
+        nv_bytes = M * H * 4 * (world - 1) / world + M * H * 2 * (world - 1) / world      # partial rows pushed out + x rows received
+        roof_us = max(w_bytes / 6.54e12, nv_bytes / 770e9) * 1e6
         rows.append({"tokens": M, "bytes": M * H * 2, "nccl_allreduce_us": t_nccl, "fused_allreduce_residual_norm_us": t_fused,
-                     "gemm_nccl_norm_us": t_gemm_nccl, "fused_gemm_allreduce_norm_us": t_gemm_fused})
+                     "gemm_nccl_norm_us": t_gemm_nccl, "fused_gemm_allreduce_norm_us": t_gemm_fused,
+                     "pair_us": t_pair, "pair_deferred_wait_us": t_pair_deferred, "phases": ph,
+                     "roofline_us": roof_us, "fused_fraction_of_roofline": roof_us / t_gemm_fused})
     torch.cuda.synchronize()
     _lib.check_device_errors()
     dist.barrier()
     if rank == 0:
         print(json.dumps({"ranks": world, "hidden": H, "multicast": not args.no_multicast, "rows": rows}), flush=True)
-    os._exit(0)
+    comm.fused = None
+    del fused
+    torch.cuda.synchronize()
+    dist.barrier()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":
