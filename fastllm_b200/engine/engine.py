@@ -33,6 +33,11 @@ class LLMEngine:
         self.runner = ModelRunner(model, self.cfg, num_pages)
         self.control = control          # parallel.control.ControlPlane: this rank schedules, the other ranks replay its plans
         self.runner.control = control
+        # models with linear-attention layers keep per-request recurrent state in slots; whole-page prefix reuse would need
+        # state snapshots at the page boundaries, so it is off for them
+        self.state_free = list(range(self.runner.state_slots))
+        if self.runner.state_slots:
+            self.cfg.prefix_cache = False
         self.pm = self.runner.kv.manager
         self.page_len = self.cfg.page_len
         self.eos = set(eos_token_ids if eos_token_ids is not None else model.cfg.eos_token_ids)
@@ -181,7 +186,7 @@ class LLMEngine:
         pending.sort(key=lambda r: -len(r.prefill_ids))
         keep = []
         for r in pending:
-            if len(self.running) >= self.cfg.max_batch:
+            if len(self.running) >= self.cfg.max_batch or (self.runner.state_slots and not self.state_free):
                 keep.append(r)
                 continue
             toks = r.prefill_ids
@@ -195,6 +200,8 @@ class LLMEngine:
                 keep.append(r)
                 continue
             r.pages = cached + pages
+            if self.runner.state_slots:
+                r.state_slot = self.state_free.pop()
             r.num_computed = len(cached) * self.page_len
             r.num_cached_prefix = r.num_computed
             r.stats.cached_tokens = r.num_computed
@@ -216,7 +223,13 @@ class LLMEngine:
                 self.pm.record(r.all_ids[:n_full * self.page_len], r.pages[:n_full])
             self.pm.release(r.pages)
             r.pages = []
+        self._release_state(r)
         r.results.put(-1)
+
+    def _release_state(self, r: Request) -> None:
+        if getattr(r, "state_slot", None) is not None and r.state_slot >= 0:
+            self.state_free.append(r.state_slot)
+            r.state_slot = -1
 
     def _evict_for_pages(self, need: int) -> bool:
         """Free pages by evicting the longest decoding request (it is re-queued for recomputation)."""
@@ -227,6 +240,7 @@ class LLMEngine:
         self.running.remove(victim)
         self.pm.release(victim.pages)
         victim.pages = []
+        self._release_state(victim)
         victim.num_computed = 0
         victim.recompute_tokens = victim.all_ids[:-1] if victim.output_ids else victim.prompt_ids
         victim.state = RequestState.WAITING
@@ -279,7 +293,7 @@ class LLMEngine:
             decoding = self._ensure_decode_pages([r for r in self.running if r.state == RequestState.DECODE])
             reqs = [r for r in reqs if r in self.running and r.state == RequestState.PREFILL]
             for r in decoding:
-                chunks.append(([r.all_ids[-1]], r.total_len - 1, r.pages, True))
+                chunks.append(([r.all_ids[-1]], r.total_len - 1, r.pages, True, r.state_slot))
             budget = max(self.page_len, budget - len(decoding))
         for r in reqs:
             if budget <= 0:
@@ -289,7 +303,7 @@ class LLMEngine:
             if n <= 0:
                 continue
             done = r.num_computed + n == len(toks)
-            chunks.append((toks[r.num_computed:r.num_computed + n], r.num_computed, r.pages, done))
+            chunks.append((toks[r.num_computed:r.num_computed + n], r.num_computed, r.pages, done, r.state_slot))
             owners.append((r, n, done))
             budget -= n
         if not chunks:
@@ -329,7 +343,8 @@ class LLMEngine:
         ids = [r.all_ids[-1] for r in reqs]
         positions = [r.total_len - 1 for r in reqs]
         all_greedy = all(r.gen.is_simple_greedy() for r in reqs)
-        out_ids, logits = self.runner.decode(ids, positions, [r.pages for r in reqs], want_logits=not all_greedy)
+        out_ids, logits = self.runner.decode(ids, positions, [r.pages for r in reqs], want_logits=not all_greedy,
+                                             state_slots=[r.state_slot for r in reqs] if self.runner.state_slots else None)
         for r in reqs:
             r.num_computed = r.total_len
         if all_greedy:

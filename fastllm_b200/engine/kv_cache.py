@@ -90,27 +90,46 @@ class PageManager:
 class KVCache:
     """Device page pools of one rank + the shared page manager."""
 
-    def __init__(self, model, num_pages: int, page_len: int = PAGE_LEN):
+    def __init__(self, model, num_pages: int, page_len: int = PAGE_LEN, state_slots: int = 0):
         self.num_pages = num_pages
         self.page_len = page_len
         ks, vs = model.kv_cache_shape(num_pages)
         dev, dt = model.device, (getattr(model, "kv_dtype", None) or model.dtype)
         self.pools = []
+        self.state_slots = state_slots         # requests that can hold linear-attention state at once (+ one scratch slot)
+        self.linear_layers = [i for i in range(model.cfg.num_layers) if model.cfg.layer_is_linear(i)]
         staged = getattr(model, "layer_devices", None)
         for i in range(model.cfg.num_layers):
             if staged is not None:
                 dev = staged[i]            # layer-split placement: a layer's pages live on that layer's device
+            if model.cfg.layer_is_linear(i):
+                # no pages: a convolution window and a delta-rule state per request slot; the last slot is scratch for
+                # padded decode rows
+                cs, rs = model.linear_state_shapes(state_slots + 1)
+                self.pools.append((torch.zeros(cs, device=dev, dtype=model.dtype), torch.zeros(rs, device=dev, dtype=torch.float32)))
+                continue
             k = torch.zeros(ks, device=dev, dtype=dt)
             v = torch.zeros(vs, device=dev, dtype=dt) if vs is not None else None
             self.pools.append((k, v))
         self.manager = PageManager(num_pages, page_len)
 
+
+    def reset_state(self, slot: int) -> None:
+        """Zero the linear-attention state of one request slot (a request starts, or restarts after an eviction)."""
+        for conv, rec in self.linear_pools():
+            conv[slot].zero_()
+            rec[slot].zero_()
+
+    def linear_pools(self):
+        return [self.pools[i] for i in self.linear_layers]
+
     @staticmethod
     def plan_num_pages(model, gpu_mem_ratio: float = 0.9, max_tokens: int | None = None, reserve_bytes: int = 2 << 30) -> int:
+        """Pages that fit the memory budget (after the linear-attention state pools, when the model has such layers)."""
         per_page = model.kv_bytes_per_page()
         if model.device.type == "cuda":
             free, _total = torch.cuda.mem_get_info(model.device)
-            budget = int(free * gpu_mem_ratio) - reserve_bytes
+            budget = int(free * gpu_mem_ratio) - reserve_bytes - getattr(model, "_state_bytes_reserved", 0)
             n = max(16, budget // per_page)
         else:
             n = 512

@@ -92,6 +92,7 @@ class Request:
         self.last_logits = None
         self.logprob_entries: list = []   # per output token: (token logprob, [(token id, logprob), ...]) when gen.logprobs > 0
         self.recompute_tokens: list[int] | None = None   # set when evicted: prompt + outputs to prefill again
+        self.state_slot = -1           # linear-attention state slot while the request is running (-1: none)
 
     @property
     def all_ids(self):

@@ -42,14 +42,14 @@ class _DecodeSlot:
         dev = runner.device
         P = runner.max_pages
         self.bsz = bsz
-        n = 4 * bsz + bsz * P
+        n = 5 * bsz + bsz * P
         pin = dev.type == "cuda"
         self.meta_host = torch.zeros(n, dtype=torch.int32, pin_memory=pin)
         self.meta_np = self.meta_host.numpy()
         self.meta_dev = torch.zeros(n, dtype=torch.int32, device=dev)
         md = self.meta_dev
-        self.ids, self.positions, self.slots, self.kv_lens = (md[i * bsz:(i + 1) * bsz] for i in range(4))
-        self.page_table = md[4 * bsz:].view(bsz, P)
+        self.ids, self.positions, self.slots, self.kv_lens, self.state_slots = (md[i * bsz:(i + 1) * bsz] for i in range(5))
+        self.page_table = md[5 * bsz:].view(bsz, P)
         self.cu_q = torch.arange(bsz + 1, dtype=torch.int32, device=dev)
         self.out_ids = torch.zeros(bsz, dtype=torch.int32, device=dev)
         self.out_host = torch.zeros(bsz, dtype=torch.int32, pin_memory=pin)
@@ -64,7 +64,7 @@ class _DecodeSlot:
     def batch(self) -> ForwardBatch:
         return ForwardBatch(ids=self.ids, positions=self.positions, slots=self.slots, page_table=self.page_table,
                             kv_lens=self.kv_lens, cu_q=self.cu_q, logit_rows=None, is_decode=True,
-                            cu_q_host=list(range(self.bsz + 1)), decode_ws=self.ws)
+                            cu_q_host=list(range(self.bsz + 1)), decode_ws=self.ws, state_slots=self.state_slots)
 
 
 class ModelRunner:
@@ -74,9 +74,11 @@ class ModelRunner:
         self.device = model.device
         self.max_pages = (cfg.max_context + cfg.page_len - 1) // cfg.page_len
         if num_pages is None:
+            model._state_bytes_reserved = model.linear_state_bytes_per_slot() * (cfg.max_batch + 1)
             num_pages = KVCache.plan_num_pages(model, cfg.gpu_mem_ratio, cfg.max_tokens)
             num_pages = self._agree_on_pages(num_pages)
-        self.kv = KVCache(model, num_pages, cfg.page_len)
+        self.state_slots = cfg.max_batch if model.cfg.has_linear_attn else 0
+        self.kv = KVCache(model, num_pages, cfg.page_len, self.state_slots)
         self.control = None      # parallel.control.ControlPlane on the scheduler rank of a multi-process group
         self.slots: dict[int, _DecodeSlot] = {}
         self.graph_ok = cfg.use_cuda_graph and self.device.type == "cuda" and self._graph_safe()
@@ -115,6 +117,10 @@ class ModelRunner:
             return False        # latent shapes outside the MLA decode kernel run the PyTorch evaluation
         if self.model.general_attn or any(lw.attn.window or lw.attn.sinks is not None for lw in self.model.layers):
             return False        # these paths evaluate attention with host-synchronising PyTorch ops
+        if not c.use_mla and c.head_dim != 128:
+            return False        # the tensor-core attention kernels cover head_dim 128; other widths run the PyTorch evaluation
+        if c.has_linear_attn and not (c.lin_k_dim == 128 and c.lin_v_dim == 128 and self.model.dtype in (torch.float16, torch.bfloat16)):
+            return False        # delta-rule state shapes outside the recurrent kernel run the PyTorch evaluation
         if c.is_moe:
             # the per-expert fallback loop synchronises with the host; graphs need every MoE layer on the grouped kernels
             return all(lw.mlp.experts is None or (lw.mlp.experts.stacked is not None and not lw.mlp.experts.host)
@@ -132,7 +138,13 @@ class ModelRunner:
         P = self.max_pages
         pt = np.zeros((len(chunks), P), dtype=np.int32)
         pl = self.cfg.page_len
-        for b, (toks, start, pages, want) in enumerate(chunks):
+        sslots = []
+        for b, ch in enumerate(chunks):
+            toks, start, pages, want = ch[:4]
+            ss = ch[4] if len(ch) > 4 and ch[4] is not None and ch[4] >= 0 else self.state_slots     # default: the scratch slot
+            sslots.append(ss)
+            if self.state_slots and start == 0:
+                self.kv.reset_state(ss)              # a request starts (or restarts after an eviction) from empty state
             n = len(toks)
             ids.extend(toks)
             pos.extend(range(start, start + n))
@@ -152,7 +164,9 @@ class ModelRunner:
                           page_table=torch.from_numpy(pt).to(dev), kv_lens=torch.tensor(kv_lens, dtype=torch.int32).to(dev),
                           cu_q=torch.tensor(cu, dtype=torch.int32).to(dev),
                           logit_rows=torch.tensor(rows, dtype=torch.long).to(dev) if rows else torch.zeros(0, dtype=torch.long, device=dev),
-                          is_decode=False, cu_q_host=cu)
+                          is_decode=False, cu_q_host=cu,
+                          state_slots=torch.tensor(sslots, dtype=torch.int32).to(dev) if self.state_slots else None,
+                          state_slots_host=sslots if self.state_slots else None)
         if not rows:
             # still run the stack to fill the cache; ask for one row to keep shapes valid
             fb.logit_rows = torch.zeros(1, dtype=torch.long, device=dev)
@@ -195,7 +209,7 @@ class ModelRunner:
             ids, vals = B.argmax(lg, id_offset=lo, want_values=True)
             out_ids.copy_(m.tp.comm.merge_argmax(ids, vals))
 
-    def decode(self, ids, positions, pages_per_req, want_logits=False):
+    def decode(self, ids, positions, pages_per_req, want_logits=False, state_slots=None):
         """One token per request. Returns (token ids int32 host tensor [n], logits or None)."""
         n = len(ids)
         pl = self.cfg.page_len
@@ -204,9 +218,12 @@ class ModelRunner:
         mp = s.meta_np
         mp[:4 * bsz] = 0
         mp[2 * bsz:3 * bsz] = -1                      # padded rows never write the cache
+        mp[4 * bsz:5 * bsz] = self.state_slots        # ... and keep their linear-attention state in the scratch slot
         mp[0:n] = ids
         mp[bsz:bsz + n] = positions
-        pt = mp[4 * bsz:].reshape(bsz, self.max_pages)
+        if state_slots is not None:
+            mp[4 * bsz:4 * bsz + n] = state_slots
+        pt = mp[5 * bsz:].reshape(bsz, self.max_pages)
         for b in range(n):
             pg = pages_per_req[b]
             p = positions[b]

@@ -113,7 +113,9 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         f_ = getattr(m, "moe_wdtype_for", None)
         return f_(p + name) if f_ else base_mw
 
-    if cfg.use_mla:
+    if cfg.layer_is_linear(i):
+        lw.lin = build_linear_attn(m, g, a.ln, W)
+    elif cfg.use_mla:
         nope, rope, vd, lora = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         Hl = cfg.num_heads // n
         qd = nope + rope
@@ -148,6 +150,16 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         else:
             qw, kw, vw = g("self_attn.q_proj.weight"), g("self_attn.k_proj.weight"), g("self_attn.v_proj.weight")
             bq, bk, bv = g("self_attn.q_proj.bias"), g("self_attn.k_proj.bias"), g("self_attn.v_proj.bias")
+            if cfg.attn_output_gate:
+                # q_proj carries [query | gate] per head: the gate rows become their own projection
+                qg = qw.reshape(cfg.num_heads, 2, D, qw.shape[-1])
+                qw, gate_w = qg[:, 0].reshape(cfg.num_heads * D, -1), qg[:, 1].reshape(cfg.num_heads * D, -1)
+                gate_b = None
+                if bq is not None:
+                    bg_ = bq.reshape(cfg.num_heads, 2, D)
+                    bq, gate_b = bg_[:, 0].reshape(-1), bg_[:, 1].reshape(-1)
+                a.out_gate = _lin(m, _heads_rows(gate_w, D, r * Hq_l, (r + 1) * Hq_l), W("self_attn.q_proj.weight"),
+                                  _heads_rows(gate_b, D, r * Hq_l, (r + 1) * Hq_l) if gate_b is not None else None)
         w = torch.cat([_heads_rows(qw, D, r * Hq_l, (r + 1) * Hq_l), _heads_rows(kw, D, kv0, kv0 + Hkv_l),
                        _heads_rows(vw, D, kv0, kv0 + Hkv_l)], dim=0)
         b = None
@@ -227,6 +239,49 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
     while len(m.layers) <= i:
         m.layers.append(None)
     m.layers[i] = lw
+
+
+def build_linear_attn(m, g, ln, W):
+    """Gated-DeltaNet weights of one layer for this rank.  Accepts the grouped layout of Qwen3-Next (``in_proj_qkvz`` /
+    ``in_proj_ba``, rows grouped per key head) and the plain layout of Qwen3.5 (``in_proj_qkv``, ``in_proj_z``, ``in_proj_b``,
+    ``in_proj_a``); heads are sharded over the tensor-parallel ranks by key head."""
+    from ..models.decoder import LinearAttnWeights
+
+    cfg, tp = m.cfg, m.tp
+    r, n = tp.rank, tp.size
+    Hk, Hv, Dk, Dv, K = cfg.lin_num_k_heads, cfg.lin_num_v_heads, cfg.lin_k_dim, cfg.lin_v_dim, cfg.lin_conv_kernel
+    rep = Hv // Hk
+    la = LinearAttnWeights()
+    la.ln = ln
+    if g("linear_attn.in_proj_qkvz.weight") is not None:
+        w = g("linear_attn.in_proj_qkvz.weight")
+        Hd = w.shape[-1]
+        wg = w.reshape(Hk, 2 * Dk + 2 * rep * Dv, Hd)
+        qw, kw = wg[:, :Dk].reshape(Hk * Dk, Hd), wg[:, Dk:2 * Dk].reshape(Hk * Dk, Hd)
+        vw = wg[:, 2 * Dk:2 * Dk + rep * Dv].reshape(Hv * Dv, Hd)
+        zw = wg[:, 2 * Dk + rep * Dv:].reshape(Hv * Dv, Hd)
+        ba = g("linear_attn.in_proj_ba.weight").reshape(Hk, 2 * rep, Hd)
+        bw, aw = ba[:, :rep].reshape(Hv, Hd), ba[:, rep:].reshape(Hv, Hd)
+    else:
+        w = g("linear_attn.in_proj_qkv.weight")
+        qw, kw, vw = w.split([Hk * Dk, Hk * Dk, Hv * Dv], dim=0)
+        zw, bw, aw = g("linear_attn.in_proj_z.weight"), g("linear_attn.in_proj_b.weight"), g("linear_attn.in_proj_a.weight")
+    cw = g("linear_attn.conv1d.weight").reshape(2 * Hk * Dk + Hv * Dv, K)
+    cq, ck, cv = cw.split([Hk * Dk, Hk * Dk, Hv * Dv], dim=0)
+    Hk_l, Hv_l = Hk // n, Hv // n
+    hs = lambda t, d, H_l: t[r * H_l * d:(r + 1) * H_l * d]
+    in_w = torch.cat([hs(qw, Dk, Hk_l), hs(kw, Dk, Hk_l), hs(vw, Dv, Hv_l), hs(zw, Dv, Hv_l), hs(bw, 1, Hv_l), hs(aw, 1, Hv_l)], dim=0)
+    pad = (-in_w.shape[0]) % 8                      # the GEMM wants a multiple of 8 output rows
+    if pad:
+        in_w = torch.cat([in_w, torch.zeros(pad, in_w.shape[1], dtype=in_w.dtype)], dim=0)
+    la.in_proj = _lin(m, in_w, W("linear_attn.in_proj_qkvz.weight"))
+    la.conv_w = _to(torch.cat([hs(cq, Dk, Hk_l), hs(ck, Dk, Hk_l), hs(cv, Dv, Hv_l)], dim=0), m)
+    la.A_log = g("linear_attn.A_log")[r * Hv_l:(r + 1) * Hv_l].to(m.device, torch.float32).contiguous()
+    la.dt_bias = g("linear_attn.dt_bias")[r * Hv_l:(r + 1) * Hv_l].to(m.device, torch.float32).contiguous()
+    la.norm_w = _to(g("linear_attn.norm.weight"), m)
+    la.out = _lin(m, g("linear_attn.out_proj.weight")[:, r * Hv_l * Dv:(r + 1) * Hv_l * Dv], W("linear_attn.out_proj.weight"))
+    la.Hk, la.Hv, la.Dk, la.Dv = Hk_l, Hv_l, Dk, Dv
+    return la
 
 
 def build_top(m, t: dict, wdtype="dense"):

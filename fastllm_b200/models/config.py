@@ -71,6 +71,15 @@ class ModelConfig:
     qk_nope_head_dim: int = 0
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
+    # hybrid linear attention (Gated DeltaNet: Qwen3-Next, Qwen3.5)
+    layer_types: list | None = None        # per layer "linear_attention" | "full_attention" (None: all full attention)
+    lin_num_k_heads: int = 0
+    lin_num_v_heads: int = 0
+    lin_k_dim: int = 0
+    lin_v_dim: int = 0
+    lin_conv_kernel: int = 4
+    attn_output_gate: bool = False         # q_proj also produces a per-head gate; the attention output is multiplied by its sigmoid
+    mlp_only_layers: list = field(default_factory=list)   # layers that keep a dense MLP in an otherwise sparse model
     # bookkeeping
     eos_token_ids: list = field(default_factory=list)
     bos_token_id: int | None = None
@@ -83,7 +92,18 @@ class ModelConfig:
         return self.num_experts > 0
 
     def layer_is_moe(self, i: int) -> bool:
+        if i in self.mlp_only_layers:
+            return False
+        if self.model_type in ("qwen3_next", "qwen3_5_moe", "qwen3_5_moe_text") and self.moe_layer_freq > 1:
+            return self.is_moe and (i + 1) % self.moe_layer_freq == 0
         return self.is_moe and i >= self.first_k_dense and (i % self.moe_layer_freq == 0 or self.moe_layer_freq == 1)
+
+    def layer_is_linear(self, i: int) -> bool:
+        return bool(self.layer_types) and i < len(self.layer_types) and self.layer_types[i] == "linear_attention"
+
+    @property
+    def has_linear_attn(self) -> bool:
+        return bool(self.layer_types) and "linear_attention" in self.layer_types
 
     @property
     def q_head_dim(self) -> int:
@@ -201,12 +221,31 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.num_experts_per_tok = g("num_experts_per_tok", 4)
         c.moe_intermediate_size = c.intermediate_size
         c.norm_topk_prob = True
+    if mt in ("qwen3_next", "qwen3_5", "qwen3_5_text", "qwen3_5_moe", "qwen3_5_moe_text"):
+        # hybrid stack: Gated-DeltaNet layers with a gated full-attention layer every few layers; zero-centred norm weights
+        # (reference: src/models/qwen3_next.cpp, qwen3_5.cpp)
+        c.qk_norm = True
+        c.norm_unit_offset = 1.0
+        c.attn_output_gate = True
+        lt = g("layer_types")
+        if lt is None:
+            every = int(g("full_attention_interval", 4) or 4)
+            lt = ["full_attention" if (i + 1) % every == 0 else "linear_attention" for i in range(c.num_layers)]
+        c.layer_types = list(lt)
+        c.lin_num_k_heads = g("linear_num_key_heads", 16)
+        c.lin_num_v_heads = g("linear_num_value_heads", 32)
+        c.lin_k_dim = g("linear_key_head_dim", 128)
+        c.lin_v_dim = g("linear_value_head_dim", 128)
+        c.lin_conv_kernel = g("linear_conv_kernel_dim", 4)
+        c.mlp_only_layers = list(g("mlp_only_layers", []) or [])
+        if not prf and not c.rotary_dim:
+            c.rotary_dim = int(c.head_dim * 0.25)
     # --- MoE families ---
-    if mt in ("qwen3_moe", "qwen2_moe", "moe"):
+    if mt in ("qwen3_moe", "qwen2_moe", "moe", "qwen3_next", "qwen3_5_moe", "qwen3_5_moe_text"):
         c.num_experts = g("num_experts", g("num_local_experts", 0))
         c.num_experts_per_tok = g("num_experts_per_tok", 0)
         c.moe_intermediate_size = g("moe_intermediate_size", 0)
-        c.norm_topk_prob = bool(g("norm_topk_prob", mt == "qwen3_moe"))
+        c.norm_topk_prob = bool(g("norm_topk_prob", mt != "qwen2_moe" and mt != "moe"))
         c.moe_layer_freq = g("decoder_sparse_step", 1) or 1
         sis = g("shared_expert_intermediate_size", 0) or 0
         if sis:
@@ -322,6 +361,24 @@ def preset(name: str) -> ModelConfig:
                                  num_attention_heads=4, num_key_value_heads=2, head_dim=128, intermediate_size=512,
                                  moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2, norm_topk_prob=True,
                                  rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=2048))
+    if name == "tiny-qwen3-next":
+        return from_hf_dict(dict(model_type="qwen3_next", vocab_size=512, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, intermediate_size=512, num_experts=8, num_experts_per_tok=2,
+                                 moe_intermediate_size=128, shared_expert_intermediate_size=128, linear_num_key_heads=2,
+                                 linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32, full_attention_interval=2,
+                                 max_position_embeddings=2048, rms_norm_eps=1e-6, eos_token_id=511))
+    if name == "small-qwen3-next":       # Qwen3-Next layer geometry (128-wide delta-rule heads, 128-wide attention heads) on a small body
+        return from_hf_dict(dict(model_type="qwen3_next", vocab_size=1024, hidden_size=512, num_hidden_layers=4, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=128, intermediate_size=1024, num_experts=8, num_experts_per_tok=2,
+                                 moe_intermediate_size=256, shared_expert_intermediate_size=256, linear_num_key_heads=2,
+                                 linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128, full_attention_interval=2,
+                                 max_position_embeddings=2048, rms_norm_eps=1e-6, eos_token_id=1023))
+    if name in ("qwen3-next-80b-a3b",):
+        return from_hf_dict(dict(model_type="qwen3_next", vocab_size=151936, hidden_size=2048, num_hidden_layers=48, num_attention_heads=16,
+                                 num_key_value_heads=2, head_dim=256, intermediate_size=5120, num_experts=512, num_experts_per_tok=10,
+                                 moe_intermediate_size=512, shared_expert_intermediate_size=512, linear_num_key_heads=16,
+                                 linear_num_value_heads=32, linear_key_head_dim=128, linear_value_head_dim=128, full_attention_interval=4,
+                                 max_position_embeddings=262144, rms_norm_eps=1e-6, rope_theta=1e7, eos_token_id=151645))
     if name == "tiny-deepseek-v3":
         return from_hf_dict(dict(model_type="deepseek_v3", vocab_size=512, hidden_size=256, num_hidden_layers=3,
                                  num_attention_heads=4, num_key_value_heads=4, intermediate_size=512,

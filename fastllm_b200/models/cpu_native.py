@@ -43,6 +43,8 @@ def eligible(model) -> bool:
         return False
     if c.use_mla or c.num_experts or c.hidden_act not in ("silu", "swiglu") or c.post_norms or model.general_attn or c.final_softcap:
         return False
+    if c.has_linear_attn or c.attn_output_gate:
+        return False
     if any(lw.attn.window or lw.attn.sinks is not None for lw in model.layers):
         return False
     for lw in model.layers:

@@ -40,6 +40,8 @@ class ForwardBatch:
     cu_q_host: list | None = None
     decode_ws: A.DecodeWorkspace | None = None
     decode_planned: bool = False
+    state_slots: torch.Tensor | None = None      # int32 [B]: recurrent-state slot of each request (linear-attention layers)
+    state_slots_host: list | None = None
 
 
 @dataclass
@@ -63,6 +65,7 @@ class AttentionWeights:
         self.k_norm = None
         self.post_ln = None      # sandwich norm on the attention output (Gemma-2 / GLM-4)
         self.sinks = None        # per-head sink logits (gpt-oss)
+        self.out_gate: LinearWeight | None = None   # per-head output gate projection (Qwen3-Next: sigmoid(gate) * attention)
         self.window = 0          # sliding-window length of this layer (0: full causal attention)
         # MLA
         self.q_a: LinearWeight | None = None
@@ -72,6 +75,22 @@ class AttentionWeights:
         self.kv_a_norm = None
         self.w_uk = None       # [H, nope, kv_lora]   absorbed K up-projection
         self.w_uv = None       # [H, v_dim, kv_lora]  absorbed V up-projection
+
+
+class LinearAttnWeights:
+    """Gated-DeltaNet layer (this rank's heads): one merged input projection with output columns
+    ``[q | k | v | z | b | a]``, the depth-wise convolution over ``[q | k | v]``, per-head decay parameters, the gated norm
+    and the output projection."""
+
+    def __init__(self):
+        self.ln = None
+        self.in_proj: LinearWeight | None = None
+        self.conv_w = None        # [C, K]
+        self.A_log = None         # fp32 [Hv]
+        self.dt_bias = None       # fp32 [Hv]
+        self.norm_w = None        # [Dv]
+        self.out: LinearWeight | None = None
+        self.Hk = self.Hv = self.Dk = self.Dv = 0
 
 
 class MLPWeights:
@@ -95,6 +114,7 @@ class LayerWeights:
     def __init__(self):
         self.attn = AttentionWeights()
         self.mlp = MLPWeights()
+        self.lin: LinearAttnWeights | None = None      # set instead of ``attn`` projections on linear-attention layers
 
 
 class DecoderModel:
@@ -165,7 +185,22 @@ class DecoderModel:
     def kv_bytes_per_page(self) -> int:
         ks, vs = self.kv_cache_shape(1)
         n = math.prod(ks) + (math.prod(vs) if vs else 0)
-        return n * self.cfg.num_layers * torch.finfo(getattr(self, "kv_dtype", None) or self.dtype).bits // 8
+        paged_layers = sum(1 for i in range(self.cfg.num_layers) if not self.cfg.layer_is_linear(i))
+        return n * max(1, paged_layers) * torch.finfo(getattr(self, "kv_dtype", None) or self.dtype).bits // 8
+
+    def linear_state_shapes(self, n_slots: int):
+        """Per linear-attention layer: (convolution window pool, delta-rule state pool) shapes for ``n_slots`` requests."""
+        c = self.cfg
+        Hk, Hv = c.lin_num_k_heads // self.tp.size, c.lin_num_v_heads // self.tp.size
+        C = 2 * Hk * c.lin_k_dim + Hv * c.lin_v_dim
+        return (n_slots, C, c.lin_conv_kernel - 1), (n_slots, Hv, c.lin_k_dim, c.lin_v_dim)
+
+    def linear_state_bytes_per_slot(self) -> int:
+        if not self.cfg.has_linear_attn:
+            return 0
+        cs, rs = self.linear_state_shapes(1)
+        n_lin = sum(1 for i in range(self.cfg.num_layers) if self.cfg.layer_is_linear(i))
+        return n_lin * (math.prod(cs) * torch.finfo(self.dtype).bits // 8 + math.prod(rs) * 4)
 
     def set_kv_cache_dtype(self, name: str | None) -> None:
         """``fp8_e4m3``: keys and values are stored as unscaled e4m3 (half the cache bytes); attention then runs on the
@@ -217,7 +252,33 @@ class DecoderModel:
         else:
             a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
                                cu_q_host=fb.cu_q_host)
+        if lw.out_gate is not None:
+            a = (a.float() * torch.sigmoid(lw.out_gate(x).float())).to(a.dtype)
         return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
+
+    def _linear_attention(self, lw: LinearAttnWeights, x, fb: ForwardBatch, state, residual, next_ln, consumer=None):
+        """Gated-DeltaNet token mixer over the request's convolution window and delta-rule state
+        (reference: src/models/qwen3_next.cpp; operators RecurrentGatedDeltaRule / ChunkGatedDeltaRulePrefill)."""
+        from ..ops import linear_attn as L
+
+        c = self.cfg
+        conv_state, rec_state = state
+        kd, vd = lw.Hk * lw.Dk, lw.Hv * lw.Dv
+        C = 2 * kd + vd
+        proj = lw.in_proj(x)                                   # [T, C + vd + 2 Hv]
+        mixed, z = proj[:, :C], proj[:, C:C + vd]
+        b, a = proj[:, C + vd:C + vd + lw.Hv], proj[:, C + vd + lw.Hv:C + vd + 2 * lw.Hv]
+        T = x.shape[0]
+        if fb.is_decode:
+            y = L.causal_conv1d_decode(mixed, lw.conv_w, conv_state, fb.state_slots)
+            core = L.gated_delta_decode(y, a, b, z, lw.A_log, lw.dt_bias, lw.norm_w, c.rms_eps, rec_state, fb.state_slots,
+                                        lw.Hk, lw.Hv, lw.Dk, lw.Dv)
+        else:
+            y = L.causal_conv1d(mixed, lw.conv_w, conv_state, fb.cu_q_host, fb.state_slots_host)
+            q, k, v = y[:, :kd].reshape(T, lw.Hk, lw.Dk), y[:, kd:2 * kd].reshape(T, lw.Hk, lw.Dk), y[:, 2 * kd:].reshape(T, lw.Hv, lw.Dv)
+            o = L.gated_delta_rule(q, k, v, a, b, lw.A_log, lw.dt_bias, rec_state, fb.cu_q_host, fb.state_slots_host, lw.Hv // lw.Hk)
+            core = L.rmsnorm_gated(o, z.reshape(T, lw.Hv, lw.Dv), lw.norm_w, c.rms_eps).reshape(T, vd)
+        return self._row_parallel_norm(lw.out, core, residual, next_ln, consumer=consumer)
 
     def _attention_general(self, lw: AttentionWeights, qkv, fb: ForwardBatch, kv):
         """Attention for the less common variants (sliding window, sinks, logit soft-capping, norm after RoPE)."""
@@ -434,15 +495,20 @@ class DecoderModel:
         if self._fused_active:
             h = fused.load_h(h)
         n_layers = len(self.layers)
-        x = self._norm(h, self.layers[0].attn.ln)
+        l0 = self.layers[0]
+        x = self._norm(h, l0.lin.ln if l0.lin is not None else l0.attn.ln)
         for i, lw in enumerate(self.layers):
             # the projection that reads each fused collective's output first (it can take over the all-gather wait)
             mlp_first = lw.mlp.gate_up if lw.mlp.experts is None else None
-            h, x = self._attention(lw.attn, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
+            if lw.lin is not None:
+                h, x = self._linear_attention(lw.lin, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
+            else:
+                h, x = self._attention(lw.attn, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
             if i + 1 < n_layers:
-                next_ln = self.layers[i + 1].attn.ln
-                na = self.layers[i + 1].attn
-                nxt = (na.q_a if na.q_a is not None else na.q_b) if c.use_mla else na.qkv
+                nl = self.layers[i + 1]
+                next_ln = nl.lin.ln if nl.lin is not None else nl.attn.ln
+                na = nl.attn
+                nxt = nl.lin.in_proj if nl.lin is not None else ((na.q_a if na.q_a is not None else na.q_b) if c.use_mla else na.qkv)
             else:
                 next_ln = self.final_norm
                 nxt = self.lm_head if fb.logit_rows is None else None
@@ -558,7 +624,9 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
         raw[name] = _randn(shape, s, dev, dtype, gen)
 
     def ones(name, n):
-        raw[name] = torch.ones(n, device=dev, dtype=dtype)
+        # unit gain: weight 1, or 0 for families whose norms multiply by (1 + weight); the gated delta-net norm is always plain
+        unit = 0.0 if (cfg.norm_unit_offset == 1.0 and not name.endswith("linear_attn.norm.weight")) else 1.0
+        raw[name] = torch.full((n,), unit, device=dev, dtype=dtype)
 
     # The state dict is produced layer by layer and consumed immediately to bound memory.
     def layer_tensors(i):
@@ -566,7 +634,17 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
         p = f"model.layers.{i}."
         ones(p + "input_layernorm.weight", H)
         ones(p + "post_attention_layernorm.weight", H)
-        if cfg.use_mla:
+        if cfg.layer_is_linear(i):
+            Hk, Hv, Dk, Dv = cfg.lin_num_k_heads, cfg.lin_num_v_heads, cfg.lin_k_dim, cfg.lin_v_dim
+            lp = p + "linear_attn."
+            mk(lp + "in_proj_qkvz.weight", (2 * Hk * Dk + 2 * Hv * Dv, H))
+            mk(lp + "in_proj_ba.weight", (2 * Hv, H))
+            mk(lp + "conv1d.weight", (2 * Hk * Dk + Hv * Dv, 1, cfg.lin_conv_kernel), 0.3)
+            raw[lp + "A_log"] = torch.log(torch.rand(Hv, device=dev, generator=gen) * 4 + 0.5)
+            raw[lp + "dt_bias"] = torch.ones(Hv, device=dev, dtype=torch.float32)
+            ones(lp + "norm.weight", Dv)
+            mk(lp + "out_proj.weight", (H, Hv * Dv))
+        elif cfg.use_mla:
             qd = cfg.qk_nope_head_dim + cfg.qk_rope_head_dim
             if cfg.q_lora_rank:
                 mk(p + "self_attn.q_a_proj.weight", (cfg.q_lora_rank, H))
@@ -580,7 +658,7 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
             mk(p + "self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim))
         else:
             D = cfg.head_dim
-            mk(p + "self_attn.q_proj.weight", (cfg.num_heads * D, H))
+            mk(p + "self_attn.q_proj.weight", (cfg.num_heads * D * (2 if cfg.attn_output_gate else 1), H))
             mk(p + "self_attn.k_proj.weight", (cfg.num_kv_heads * D, H))
             mk(p + "self_attn.v_proj.weight", (cfg.num_kv_heads * D, H))
             mk(p + "self_attn.o_proj.weight", (H, cfg.num_heads * D))

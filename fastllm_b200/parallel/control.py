@@ -186,11 +186,13 @@ def decode_decode_plan(buf: np.ndarray):
 
 
 def encode_prefill_plan(chunks) -> np.ndarray:
-    """chunks: list of (token_ids, start_pos, pages, want_logits)."""
+    """chunks: list of (token_ids, start_pos, pages, want_logits[, state_slot])."""
     head = [len(chunks)]
     body: list[int] = []
-    for toks, start, pages, want in chunks:
-        head += [len(toks), int(start), len(pages), int(bool(want))]
+    for ch in chunks:
+        toks, start, pages, want = ch[:4]
+        ss = ch[4] if len(ch) > 4 and ch[4] is not None else -1
+        head += [len(toks), int(start), len(pages), int(bool(want)), int(ss)]
         body += list(toks)
         body += list(pages)
     return np.asarray(head + body, dtype=np.int32)
@@ -199,15 +201,15 @@ def encode_prefill_plan(chunks) -> np.ndarray:
 def decode_prefill_plan(buf: np.ndarray):
     a = buf.view(np.int32)
     nc = int(a[0])
-    off = 1 + 4 * nc
+    off = 1 + 5 * nc
     chunks = []
     for c in range(nc):
-        nt, start, npg, want = (int(x) for x in a[1 + 4 * c:5 + 4 * c])
+        nt, start, npg, want, ss = (int(x) for x in a[1 + 5 * c:6 + 5 * c])
         toks = a[off:off + nt].tolist()
         off += nt
         pages = a[off:off + npg].tolist()
         off += npg
-        chunks.append((toks, start, pages, bool(want)))
+        chunks.append((toks, start, pages, bool(want), ss))
     return chunks
 
 

@@ -393,3 +393,26 @@ def test_decode_rides_along_with_prefill_chunks():
     while not (r0.finished() and r1.finished()):
         eng.step()
     assert [r0.output_ids, r1.output_ids] == ref
+
+
+def test_hybrid_linear_attention_engine_consistency():
+    """Qwen3-Next-style hybrid stack: chunked prefill + stateful decode (convolution window and delta-rule state per request
+    slot) reproduces token-by-token recomputation; eviction restarts a request from empty state; slots are returned."""
+    m = _model("tiny-qwen3-next")
+    assert m.cfg.has_linear_attn and m.layers[0].lin is not None and m.layers[1].lin is None
+    prompts = _prompts(m.cfg.vocab_size, (5, 130, 70))
+    gen = GenerationConfig(max_new_tokens=6, ignore_eos=True)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, chunked_prefill_size=48), num_pages=32)
+    outs = eng.generate(prompts, gen)
+    assert sorted(eng.state_free) == [0, 1, 2, 3] and not eng.cfg.prefix_cache
+    eng2 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=32)
+    for p, o in zip(prompts, outs):
+        seq = list(p)
+        for k in range(6):
+            t = eng2.generate([seq], GenerationConfig(max_new_tokens=1, ignore_eos=True))[0][0]
+            assert t == o[k], k
+            seq.append(t)
+    # a pool too small for all three: someone is evicted, recomputed from scratch (state reset) and still matches
+    small = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefill_page_limit=1.0), num_pages=3)
+    assert small.generate(prompts, GenerationConfig(max_new_tokens=30, ignore_eos=True)) == \
+        LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=32).generate(prompts, GenerationConfig(max_new_tokens=30, ignore_eos=True))

@@ -48,6 +48,14 @@ FAMILIES = {
                         layer_types=["sliding_attention", "full_attention"]),
     "minimax_m2": dict(model_type="minimax_m2", **_C, num_local_experts=4, num_experts_per_tok=2,
                        rope_parameters={"rope_type": "default", "rope_theta": 1e6, "partial_rotary_factor": 0.5}),
+    "qwen3_next": dict(model_type="qwen3_next", **_C, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
+                       shared_expert_intermediate_size=256, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+                       linear_value_head_dim=32, layer_types=["linear_attention", "full_attention"]),
+    "qwen3_5_text": dict(model_type="qwen3_5_text", **_C, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
+                         linear_value_head_dim=32, layer_types=["linear_attention", "full_attention"]),
+    "qwen3_5_moe_text": dict(model_type="qwen3_5_moe_text", **_C, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
+                             shared_expert_intermediate_size=256, linear_num_key_heads=2, linear_num_value_heads=4,
+                             linear_key_head_dim=32, linear_value_head_dim=32, layer_types=["linear_attention", "full_attention"]),
     "granite": dict(model_type="granite", **_NH, attention_multiplier=0.2, embedding_multiplier=3.0, residual_multiplier=0.5,
                     logits_scaling=2.0),
 }
@@ -81,7 +89,8 @@ def test_family_matches_transformers(name, tmp_path):
     fb = ForwardBatch(ids=torch.tensor(prompt, dtype=torch.int32), positions=torch.arange(T, dtype=torch.int32),
                       slots=torch.arange(T, dtype=torch.int32), page_table=torch.tensor([[0, 1, 2, 3]], dtype=torch.int32),
                       kv_lens=torch.tensor([T], dtype=torch.int32), cu_q=torch.tensor([0, T], dtype=torch.int32),
-                      logit_rows=torch.tensor([T - 1]), cu_q_host=[0, T])
+                      logit_rows=torch.tensor([T - 1]), cu_q_host=[0, T],
+                      state_slots=torch.tensor([0], dtype=torch.int32), state_slots_host=[0])
     got = m.forward(fb, eng.runner.kv.pools)[0].float()[:want.numel()]
     assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
     assert (got - want).abs().max().item() < 2e-3

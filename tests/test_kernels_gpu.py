@@ -747,3 +747,37 @@ def test_qkv_projection_with_fused_post(mode, rot, qknorm, bias, T, K):
     _close(q_out.cpu(), q_ref, 4e-2, 3e-2, "q", fro=2e-2)
     _close(kp2.cpu(), kp, 4e-2, 3e-2, "k pool", fro=2e-2)
     _close(vp2.cpu(), vp, 3e-2, 2e-2, "v pool", fro=2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_gdn_conv_update_and_recurrent_step(dtype):
+    """Gated-DeltaNet decode kernels (convolution window step; delta-rule step + gated norm) against the PyTorch fp32
+    definition, over three consecutive steps so the carried state is checked too."""
+    from fastllm_b200.ops import linear_attn as L
+
+    torch.manual_seed(23)
+    Bn, Hk, Hv, Dk, Dv, K = 5, 2, 4, 128, 128, 4
+    C = 2 * Hk * Dk + Hv * Dv
+    n_slots = 9
+    slots = torch.tensor([7, 2, 8, 0, 3], dtype=torch.int32)
+    w = (torch.randn(C, K) * 0.4).to(dtype)
+    conv_ref = (torch.randn(n_slots, C, K - 1) * 0.5).to(dtype)
+    rec_ref = torch.randn(n_slots, Hv, Dk, Dv) * 0.1
+    A_log, dt_bias = torch.log(torch.rand(Hv) * 4 + 0.5), torch.rand(Hv)
+    norm_w = (1 + 0.1 * torch.randn(Dv)).to(dtype)
+    conv_g, rec_g = conv_ref.clone().to(DEV), rec_ref.clone().to(DEV)
+    d = lambda t: t.to(DEV)
+    for step in range(3):
+        x = (torch.randn(Bn, C) * 0.7).to(dtype)
+        a, b = torch.randn(Bn, Hv).to(dtype), torch.randn(Bn, Hv).to(dtype)
+        z = torch.randn(Bn, Hv * Dv).to(dtype)
+        y_ref = L.causal_conv1d_decode(x, w, conv_ref, slots)                       # CPU tensors: the PyTorch definition
+        o_ref = L.gated_delta_decode(y_ref, a, b, z, A_log, dt_bias, norm_w, 1e-6, rec_ref, slots, Hk, Hv, Dk, Dv)
+        y = L.causal_conv1d_decode(d(x), d(w), conv_g, d(slots))
+        _close(y.cpu(), y_ref, 2e-2, 2e-2, f"conv step {step}")
+        o = L.gated_delta_decode(d(y_ref), d(a), d(b), d(z), d(A_log), d(dt_bias), d(norm_w), 1e-6, rec_g, d(slots), Hk, Hv, Dk, Dv)
+        _close(o.cpu(), o_ref, 3e-2, 3e-2, f"delta step {step}", fro=2e-2)
+        _close(conv_g.cpu(), conv_ref, 0, 0, f"conv state {step}")
+        _close(rec_g.cpu(), rec_ref, 1e-3, 1e-3, f"rule state {step}", fro=1e-3)
+    untouched = [s for s in range(n_slots) if s not in slots.tolist()]
+    assert torch.equal(rec_g.cpu()[untouched], rec_ref[untouched])
