@@ -244,3 +244,228 @@ def MergeMOE(x, index, score, experts, shared=None, shared_scale=1.0):
 
 
 FusedMOE = MergeMOE
+
+
+# ---- the rest of the reference's operator list (src/devices/cuda/cudadevice.cpp:4019-4139, cpudevice.cpp:284-394) ----------
+def EmbeddingDirect(ids, weight, out):
+    out.copy_(Embedding(ids, weight))
+    return out
+
+
+def RMSNormPart(x, weight, eps, start, end):
+    """RMSNorm of the column range ``[start, end)`` of every row, other columns untouched (tensor-parallel sharded norms)."""
+    out = x.clone()
+    out[..., start:end] = B.rmsnorm(x[..., start:end].contiguous(), weight, eps)
+    return out
+
+
+def Normalize(x, axis=-1, eps=1e-12):
+    return (x.float() / x.float().norm(dim=axis, keepdim=True).clamp_min(eps)).to(x.dtype)
+
+
+def Copy(dst, src):
+    dst.copy_(src)
+    return dst
+
+
+def CatDirect(dst, x, axis):
+    """Append ``x`` to ``dst`` along ``axis`` (the reference grows a pre-expanded buffer in place; here a new tensor is returned)."""
+    return x.clone() if dst is None or dst.numel() == 0 else torch.cat([dst, x], dim=axis)
+
+
+def Pad(x, axis, before, after, value=0.0):
+    pads = [0, 0] * x.dim()
+    ax = axis % x.dim()
+    pads[2 * (x.dim() - 1 - ax)], pads[2 * (x.dim() - 1 - ax) + 1] = before, after
+    return F.pad(x, pads, value=value)
+
+
+def MulSingleTo(x, v):
+    return x.mul_(v)
+
+
+def ChannelMulTo(x, scale):
+    """``x[..., c] *= scale[c]``."""
+    return x.mul_(scale.to(x.dtype))
+
+
+def Clamp(x, lo, hi):
+    return x.clamp(lo, hi)
+
+
+def CrossSwiglu(x):
+    """SwiGLU over interleaved columns: gate = even columns, up = odd columns."""
+    xf = x.float()
+    return (F.silu(xf[..., 0::2]) * xf[..., 1::2]).to(x.dtype)
+
+
+def SwigluGptOss(x, alpha=1.702, limit=7.0):
+    """gpt-oss gated activation on interleaved (gate, up) columns: clamp, ``gate * sigmoid(alpha * gate) * (up + 1)``."""
+    xf = x.float()
+    g, u = xf[..., 0::2].clamp(max=limit), xf[..., 1::2].clamp(-limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1)).to(x.dtype)
+
+
+def MambaSoftplus(x, bias=None):
+    return F.softplus(x.float() + (bias.float() if bias is not None else 0.0)).to(x.dtype)
+
+
+def SigmoidMambaSoftplus(a, b, A_log, dt_bias):
+    """Gated-DeltaNet gates from the raw projections: ``(beta, g) = (sigmoid(b), -exp(A_log) * softplus(a + dt_bias))``."""
+    return torch.sigmoid(b.float()), -A_log.float().exp() * F.softplus(a.float() + dt_bias.float())
+
+
+def SigmoidMulTo(x, gate):
+    """``x *= sigmoid(gate)`` (gated attention output)."""
+    return x.mul_(torch.sigmoid(gate.float()).to(x.dtype))
+
+
+def AttentionExtendedMask(scores, mask, value=-1e4):
+    return scores.masked_fill(mask.bool().expand_as(scores), value)
+
+
+def ApplyLognAttn(q, logn, position_ids):
+    """Qwen-1 long-context scaling: every query row is multiplied by ``logn[position]``."""
+    return (q.float() * logn.float()[position_ids.long()].reshape(-1, *([1] * (q.dim() - 1)))).to(q.dtype)
+
+
+def CumSumLastDim(x):
+    return x.float().cumsum(-1).to(x.dtype)
+
+
+def MakeDecayMask(g_cumsum):
+    """``exp(G_i - G_j)`` for ``j <= i`` and 0 above the diagonal, from the running log-decay of a chunk (chunked delta rule)."""
+    d = (g_cumsum.float()[..., :, None] - g_cumsum.float()[..., None, :]).tril().exp().tril()
+    return d
+
+
+def ApplyChunkDecayByLastLogG(k, g_cumsum):
+    """``k_j * exp(G_last - G_j)``: keys weighted for the carry of a chunk's state into the next chunk."""
+    return k.float() * (g_cumsum.float()[..., -1:, None] - g_cumsum.float()[..., :, None]).exp().reshape(*g_cumsum.shape, 1)
+
+
+def TransferAttn(attn):
+    """``(I - A)^-1`` of a strictly lower triangular ``A`` by forward substitution (the in-chunk solve of the delta rule)."""
+    T = attn.float().clone()
+    c = T.shape[-1]
+    for i in range(1, c):
+        T[..., i, :i] = T[..., i, :i] + (T[..., i, :i, None] * T[..., :i, :i]).sum(-2)
+    return T + torch.eye(c, device=T.device, dtype=T.dtype)
+
+
+def Conv1DPerChannel(x, weight, bias=None, pad_left=None):
+    """Depth-wise causal convolution; x ``[B, C, L]``, weight ``[C, K]``: output ``[B, C, L]`` (left padding K-1 by default)."""
+    K = weight.shape[-1]
+    xp = F.pad(x.float(), (K - 1 if pad_left is None else pad_left, 0))
+    return F.conv1d(xp, weight.float().unsqueeze(1), bias.float() if bias is not None else None, groups=x.shape[1]).to(x.dtype)
+
+
+def Conv2D(x, weight, bias=None, stride=1, padding=0):
+    return F.conv2d(x.float(), weight.float(), bias.float() if bias is not None else None, stride=stride, padding=padding).to(x.dtype)
+
+
+def RecurrentGatedDeltaRule(q, k, v, g, beta, state):
+    """One sequence through the gated delta rule, token by token; see ``ops.linear_attn``.  ``state`` is updated in place."""
+    from . import linear_attn as L
+
+    Dk = q.shape[-1]
+    return L.gated_delta_recurrent_ref(L.l2norm(q.float()) * Dk ** -0.5, L.l2norm(k.float()), v.float(), g.float(), beta.float(), state)
+
+
+def ChunkGatedDeltaRulePrefill(q, k, v, g, beta, state, chunk=64):
+    """Same result chunk by chunk with matrix products (prefill form)."""
+    from . import linear_attn as L
+
+    Dk = q.shape[-1]
+    return L.gated_delta_chunked(L.l2norm(q.float()) * Dk ** -0.5, L.l2norm(k.float()), v.float(), g.float(), beta.float(), state, chunk)
+
+
+def RotatePosition2D(x, position_ids, sin, cos, rotary_dim):
+    """ChatGLM 2-D rotation: the first half of the head rotates with the position ids, the second with the block ids;
+    x ``[T, H, D]``, position_ids ``[2, T]``."""
+    D = x.shape[-1]
+    a = A.apply_rope_ref(x[..., :D // 2], position_ids[0], cos, sin, A.ROPE_NEOX, min(2 * rotary_dim, D // 2))
+    b = A.apply_rope_ref(x[..., D // 2:], position_ids[1], cos, sin, A.ROPE_NEOX, min(2 * rotary_dim, D // 2))
+    return torch.cat([a, b], dim=-1)
+
+
+def LlamaRotatePosition2DPart(x, position_ids, sin, cos, rotary_dim, part):
+    """Neox rotation of the first ``part`` dims only (partial rotary)."""
+    return A.apply_rope_ref(x, position_ids, cos, sin, A.ROPE_NEOX, min(part, 2 * rotary_dim))
+
+
+def Qwen35InterleavedRope(x, position_ids, sin, cos, rotary_dim):
+    """Interleaved multi-axis rope of Qwen3.5: with text-only inputs the three position axes coincide and the rotation is
+    the half-split rotation over ``rotary_dim`` dims."""
+    return A.apply_rope_ref(x, position_ids, cos, sin, A.ROPE_NEOX, rotary_dim)
+
+
+def ScaleQRatory(q, scale):
+    return (q.float() * scale).to(q.dtype)
+
+
+def QKVRMSNormRope(qkv, positions, num_q_heads, num_kv_heads, head_dim, cos, sin, q_norm, k_norm, eps, rope_mode=A.ROPE_NEOX, rot=None):
+    """Split + per-head RMSNorm + RoPE without the cache append: returns ``(q, k, v)``."""
+    T = qkv.shape[0]
+    q, k, v = qkv.split([num_q_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * head_dim], dim=-1)
+    q, k = q.reshape(T, num_q_heads, head_dim), k.reshape(T, num_kv_heads, head_dim)
+    if q_norm is not None:
+        q, k = A._head_norm_ref(q, q_norm, eps, 0.0), A._head_norm_ref(k, k_norm, eps, 0.0)
+    q = A.apply_rope_ref(q, positions, cos, sin, rope_mode, rot or head_dim)
+    k = A.apply_rope_ref(k, positions, cos, sin, rope_mode, rot or head_dim)
+    return q.reshape(T, -1), k.reshape(T, -1), v
+
+
+def MergeAttention(x, qkv_w, qkv_b, o_w, o_b, positions, slots, k_pool, v_pool, page_table, kv_lens, cu_q, num_q_heads, num_kv_heads,
+                   head_dim, cos, sin, scale=None, is_decode=False):
+    """The reference's merged attention operator (QKV projection, RoPE, cache append, paged attention, output projection)."""
+    scale = scale if scale is not None else head_dim ** -0.5
+    q = A.qkv_post(B.linear(x, qkv_w, qkv_b), positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, head_dim, cos, sin)
+    a = AttentionPaged(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim, is_decode)
+    return B.linear(a, o_w, o_b)
+
+
+def MLP(x, gate_up_w, down_w, interleaved=False):
+    """The reference's fused MLP operator: ``down(silu(gate(x)) * up(x))``."""
+    return B.linear(B.linear(x, gate_up_w, swiglu=True, interleaved=interleaved), down_w)
+
+
+def CopyKVCache(dst_pool, src_pool, dst_pages, src_pages):
+    """Copy whole pages between pools (prefix sharing / defragmentation)."""
+    dst_pool[torch.as_tensor(dst_pages, device=dst_pool.device).long()] = src_pool[torch.as_tensor(src_pages, device=src_pool.device).long()]
+    return dst_pool
+
+
+AppendPagedCacheBatch = AppendPagedCache
+
+
+def GeneratePagedBatchParams(page_lists, lengths, page_len=A.PAGE_LEN):
+    """Host lists -> ``(page_table [B, P] int32, kv_lens [B] int32, last_page_len [B] int32)`` for a batch of requests."""
+    Bn = len(page_lists)
+    P = max(1, max(len(p) for p in page_lists))
+    pt = torch.zeros(Bn, P, dtype=torch.int32)
+    for b, pg in enumerate(page_lists):
+        pt[b, :len(pg)] = torch.tensor(pg, dtype=torch.int32)
+    kv = torch.tensor(lengths, dtype=torch.int32)
+    return pt, kv, ((kv - 1) % page_len + 1).to(torch.int32)
+
+
+def GenerateAppendPagedCacheBatchParams(page_lists, starts, counts, page_len=A.PAGE_LEN):
+    """Cache slots of ``counts[b]`` new tokens starting at position ``starts[b]`` of every request, packed."""
+    out = []
+    for pg, s, n in zip(page_lists, starts, counts):
+        out += [pg[(s + i) // page_len] * page_len + (s + i) % page_len for i in range(n)]
+    return torch.tensor(out, dtype=torch.int32)
+
+
+# ---- batch variants: one call over a list of per-request tensors ------------------------------------------------------------
+def SplitBatch(x, axis, parts): return list(torch.split(x, x.shape[axis] // parts, dim=axis))
+def CatBatch(xs, axis): return torch.cat(list(xs), dim=axis)
+def MulBatch(xs, v): return [x * v for x in xs]
+def MatMulBatch(As, Bs, alpha=1.0): return [MatMul(a, b, alpha) for a, b in zip(As, Bs)]
+def MatMulTransBBatch(As, Bs, alpha=1.0): return [MatMulTransB(a, b, alpha) for a, b in zip(As, Bs)]
+def SoftMaxBatch(xs, axis=-1): return [SoftMax(x, axis) for x in xs]
+def CatDirectBatch(dsts, xs, axis): return [CatDirect(d, x, axis) for d, x in zip(dsts, xs)]
+def AppendKVCachebatch(caches, xs, axis=0): return [CatDirect(c, x, axis) for c, x in zip(caches, xs)]
+def AttentionBatch(qs, ks, vs, masks=None, group=1, scale=None):
+    return [Attention(q, k, v, None if masks is None else masks[i], group, scale) for i, (q, k, v) in enumerate(zip(qs, ks, vs))]

@@ -94,3 +94,38 @@ def test_cuda_matches_cpu(name):
         assert torch.equal(ci.long(), gi.cpu().long())
         cpu, gpu = cw, gw
     assert torch.allclose(gpu.float().cpu(), cpu.float(), atol=6e-2, rtol=3e-2)
+
+
+def test_linear_attention_and_misc_operators_cpu():
+    """The operators behind the Gated-DeltaNet layers and the smaller ones of the reference's list, against direct formulas."""
+    torch.manual_seed(3)
+    x = torch.randn(2, 4, 10)
+    w = torch.randn(4, 3)
+    y = O.Conv1DPerChannel(x, w)
+    ref = torch.stack([sum(w[c, j] * torch.nn.functional.pad(x[:, c], (2, 0))[:, j:j + 10] for j in range(3)) for c in range(4)], dim=1)
+    assert torch.allclose(y, ref, atol=1e-5)
+    A_ = torch.tril(torch.randn(6, 6), -1) * 0.3
+    assert torch.allclose(O.TransferAttn(A_), torch.linalg.inv(torch.eye(6) - A_), atol=1e-5)
+    g = -torch.rand(2, 6).cumsum(-1)
+    dm = O.MakeDecayMask(g)
+    assert torch.allclose(dm[0, 4, 1], (g[0, 4] - g[0, 1]).exp()) and float(dm[0, 1, 4]) == 0.0
+    assert torch.allclose(O.CumSumLastDim(torch.ones(3, 5)), torch.arange(1.0, 6.0).expand(3, 5))
+    n, H, Dk, Dv = 70, 2, 16, 8
+    q, k, v = torch.randn(n, H, Dk), torch.randn(n, H, Dk), torch.randn(n, H, Dv)
+    gg, beta = -torch.rand(n, H) * 0.3, torch.rand(n, H)
+    s1, s2 = torch.zeros(H, Dk, Dv), torch.zeros(H, Dk, Dv)
+    o1 = O.RecurrentGatedDeltaRule(q, k, v, gg, beta, s1)
+    o2 = O.ChunkGatedDeltaRulePrefill(q, k, v, gg, beta, s2, chunk=16)
+    assert torch.allclose(o1, o2, atol=1e-4) and torch.allclose(s1, s2, atol=1e-4)
+    t = torch.randn(3, 8)
+    assert torch.allclose(O.CrossSwiglu(t), torch.nn.functional.silu(t[:, 0::2]) * t[:, 1::2], atol=1e-6)
+    assert O.Pad(t, 1, 1, 2).shape == (3, 11) and float(O.Pad(t, 1, 1, 2, value=7.0)[0, 0]) == 7.0
+    assert torch.allclose(O.Normalize(t).norm(dim=-1), torch.ones(3), atol=1e-5)
+    part = O.RMSNormPart(t, torch.ones(4), 1e-6, 2, 6)
+    assert torch.equal(part[:, :2], t[:, :2]) and torch.allclose(part[:, 2:6].pow(2).mean(-1), torch.ones(3), atol=1e-3)
+    pt, kv, last = O.GeneratePagedBatchParams([[3, 1], [2]], [130, 5])
+    assert pt.tolist() == [[3, 1], [2, 0]] and kv.tolist() == [130, 5] and last.tolist() == [2, 5]
+    assert O.GenerateAppendPagedCacheBatchParams([[3, 1], [2]], [127, 0], [2, 1]).tolist() == [3 * 128 + 127, 1 * 128, 2 * 128]
+    assert [u.shape for u in O.SplitBatch(torch.zeros(4, 6), 0, 2)] == [(2, 6), (2, 6)]
+    beta2, g2 = O.SigmoidMambaSoftplus(torch.zeros(2), torch.zeros(2), torch.zeros(2), torch.zeros(2))
+    assert torch.allclose(beta2, torch.full((2,), 0.5)) and torch.allclose(g2, torch.full((2,), -math.log(2.0)))
