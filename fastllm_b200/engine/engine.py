@@ -53,6 +53,8 @@ class LLMEngine:
         self.device_errors = 0
         self.last_device_error = ""
         self.decode_tokens = 0
+        self.spec_proposed = 0          # speculative decoding: draft tokens verified / accepted so far
+        self.spec_accepted = 0
         self.error: Exception | None = None     # the last exception a scheduler step raised (kept for diagnosis)
         self.dead = False                       # the background loop gave up after repeated failures
 
@@ -334,12 +336,81 @@ class LLMEngine:
                 produced += self._emit(r, int(t))
         return produced
 
+    # -------------------------------------------------------------------------------- speculative decoding
+    @staticmethod
+    def _ngram_draft(ids: list[int], n_max: int, k: int) -> list[int]:
+        """Draft tokens by prompt lookup: find the latest earlier occurrence of the text's last n tokens (n = n_max .. 1) and
+        propose what followed it."""
+        L = len(ids)
+        for n in range(min(n_max, L - 1), 0, -1):
+            tail = ids[L - n:]
+            for st in range(L - n - 1, -1, -1):
+                if ids[st:st + n] == tail:
+                    out = ids[st + n:st + n + k]
+                    if out:
+                        return out
+        return []
+
+    def _speculative_step(self, reqs) -> int | None:
+        """One decode step that verifies draft tokens: every request feeds its last token plus up to ``speculative_tokens``
+        drafts through one forward pass; the longest prefix of drafts that equals the model's own greedy choices is
+        accepted, plus the model's next token after it -- so a step yields between 1 and k + 1 tokens per request and the
+        output is exactly the greedy output.  The reference's speculative paths (Qwen3.5 MTP heads, the DeepSeek-V4 draft
+        model: tools/fastllm_pytools/util.py:518-532, acceptance kernel src/devices/cuda/fastllm-cuda.cu:13266) verify the
+        same way; here the drafts come from the request's own text.  Returns None when nothing could be drafted."""
+        k = self.cfg.speculative_tokens
+        drafts = []
+        for r in reqs:
+            room = min(k, self.cfg.max_context - r.total_len - 1, (r.gen.max_new_tokens - len(r.output_ids) - 1) if r.gen.max_new_tokens > 0 else k)
+            drafts.append(self._ngram_draft(r.all_ids, self.cfg.speculative_ngram, room) if room > 0 else [])
+        if not any(drafts):
+            return None
+        chunks, owners = [], []
+        for r, d in zip(reqs, drafts):
+            need = self._pages_needed(r.total_len + len(d)) - len(r.pages)
+            if need > 0:
+                pg = self.pm.alloc(need)
+                if pg is None:
+                    d = []                              # no room for drafts: plain single-token step for this request
+                else:
+                    r.pages.extend(pg)
+            chunks.append(([r.all_ids[-1]] + d, r.total_len - 1, r.pages, len(d) + 1, r.state_slot))
+            owners.append((r, d))
+        logits = self.runner.prefill(chunks)
+        if self.model.tp.size > 1:
+            if self.control is not None:
+                self.control.gather_logits()
+            logits = self.model.tp.comm.gather_logits(logits, self.model.vocab_shard, self.model.cfg.vocab_size)
+        choice = sampling.greedy(logits).tolist()
+        produced, row = 0, 0
+        for r, d in owners:
+            mine = choice[row:row + len(d) + 1]
+            row += len(d) + 1
+            n_ok = 0
+            while n_ok < len(d) and d[n_ok] == mine[n_ok]:
+                n_ok += 1
+            self.spec_proposed += len(d)
+            self.spec_accepted += n_ok
+            for t in mine[:n_ok + 1]:
+                if r.finished():
+                    break
+                produced += self._emit(r, int(t))
+            if not r.finished():
+                r.num_computed = r.total_len - 1        # the last emitted token's K/V is written by the next step
+        self.decode_steps += 1
+        self.decode_tokens += produced
+        return produced
+
     def _decode_step(self, reqs) -> int:
         if not reqs:
             return 0
         reqs = self._ensure_decode_pages(reqs)
         if not reqs:
             return 0
+        if self.cfg.speculative == "ngram" and not self.runner.state_slots and all(r.gen.is_simple_greedy() for r in reqs):
+            n = self._speculative_step(reqs)
+            if n is not None:
+                return n
         ids = [r.all_ids[-1] for r in reqs]
         positions = [r.total_len - 1 for r in reqs]
         all_greedy = all(r.gen.is_simple_greedy() for r in reqs)

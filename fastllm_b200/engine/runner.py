@@ -33,6 +33,9 @@ class EngineConfig:
     page_len: int = A.PAGE_LEN
     check_device_errors_every: int = 64
     mixed_prefill_decode: bool = True    # a prefill step also advances the requests that are already decoding (one token each)
+    speculative: str = ""                # "" | "ngram": draft tokens by looking the recent n-gram up in the request's own text
+    speculative_tokens: int = 4          # draft tokens verified per step
+    speculative_ngram: int = 3           # longest suffix that is searched for (shorter ones are tried next)
 
 
 class _DecodeSlot:
@@ -155,7 +158,9 @@ class ModelRunner:
             kv_lens.append(start + n)
             pt[b, :len(pages)] = pages
             if want:
-                rows.append(cu[-1] - 1)
+                # True: the chunk's last row; an integer n > 1: its last n rows (speculative verification reads them all)
+                nrows = 1 if want is True else max(1, min(int(want), n))
+                rows.extend(range(cu[-1] - nrows, cu[-1]))
         T = len(ids)
         meta = torch.tensor(ids + pos + slots, dtype=torch.int32)
         if dev.type == "cuda":

@@ -192,7 +192,7 @@ def encode_prefill_plan(chunks) -> np.ndarray:
     for ch in chunks:
         toks, start, pages, want = ch[:4]
         ss = ch[4] if len(ch) > 4 and ch[4] is not None else -1
-        head += [len(toks), int(start), len(pages), int(bool(want)), int(ss)]
+        head += [len(toks), int(start), len(pages), (1 if want is True else int(want or 0)), int(ss)]
         body += list(toks)
         body += list(pages)
     return np.asarray(head + body, dtype=np.int32)
@@ -209,7 +209,7 @@ def decode_prefill_plan(buf: np.ndarray):
         off += nt
         pages = a[off:off + npg].tolist()
         off += npg
-        chunks.append((toks, start, pages, bool(want), ss))
+        chunks.append((toks, start, pages, (True if want == 1 else (want if want > 1 else False)), ss))
     return chunks
 
 

@@ -134,10 +134,18 @@ def make_normal_llm_model(args):
     from . import llm
 
     args = apply_config_file(args)
-    for flag in ("mtp", "dspark", "speculative_algorithm", "speculative_draft_model_path"):
+    algo = str(getattr(args, "speculative_algorithm", "") or "").lower()
+    if algo in ("ngram", "prompt_lookup", "lookup"):
+        llm._settings["speculative"] = "ngram"
+        if getattr(args, "speculative_dspark_block_size", 0):
+            llm._settings["speculative_tokens"] = int(args.speculative_dspark_block_size)
+    elif algo:
+        print(f"[fastllm_b200] --speculative_algorithm {algo}: only 'ngram' (prompt-lookup drafts, verified in one pass) exists "
+              "in this build; decoding normally", file=sys.stderr)
+    for flag in ("mtp", "dspark", "speculative_draft_model_path"):
         if getattr(args, flag, ""):
-            print(f"[fastllm_b200] --{flag} is accepted but speculative decoding is not part of this build; decoding normally",
-                  file=sys.stderr)
+            print(f"[fastllm_b200] --{flag}: draft heads / draft models are not part of this build "
+                  "(use --speculative_algorithm ngram); decoding normally", file=sys.stderr)
     if not args.path:
         raise SystemExit("no model given: pass a model path (HF folder, .flm or .gguf)")
     if args.threads and args.threads > 0:

@@ -416,3 +416,22 @@ def test_hybrid_linear_attention_engine_consistency():
     small = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, prefill_page_limit=1.0), num_pages=3)
     assert small.generate(prompts, GenerationConfig(max_new_tokens=30, ignore_eos=True)) == \
         LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=32).generate(prompts, GenerationConfig(max_new_tokens=30, ignore_eos=True))
+
+
+def test_ngram_speculative_decoding_keeps_greedy_output():
+    """Prompt-lookup drafts verified in one forward pass: same tokens as plain greedy decoding, in fewer steps when the
+    text repeats itself."""
+    m = _model()
+    base = _prompts(m.cfg.vocab_size, (24,), seed=9)[0]
+    prompts = [base * 5, _prompts(m.cfg.vocab_size, (40,), seed=10)[0]]          # one very repetitive, one random
+    gen = GenerationConfig(max_new_tokens=40, ignore_eos=True)
+    plain = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=32)
+    ref = plain.generate(prompts, gen)
+    spec = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, speculative="ngram", speculative_tokens=4), num_pages=32)
+    out = spec.generate(prompts, gen)
+    assert out == ref
+    assert spec.spec_proposed > 0 and 0 <= spec.spec_accepted <= spec.spec_proposed
+    assert spec.pm.num_available() == 32
+    # a greedy model that has entered a cycle repeats it: the drafts are then accepted and steps are saved
+    if spec.spec_accepted > 0:
+        assert spec.decode_steps < plain.decode_steps
