@@ -280,6 +280,83 @@ __global__ void qkv_post_kernel(const QkvPostParams p) {
 }
 
 // ------------------------------------------------------------------------------------------------
+// Multi-head latent attention, post-processing of the projections of one token (one CTA per token):
+//   latent row  ckv[t, :lora]  -> RMSNorm -> cache entry [0, lora)
+//   shared key  ckv[t, lora:]  -> RoPE    -> cache entry [lora, lora + rope)           (slot < 0: the spare last slot)
+//   query rope  q[t, h, nope:] -> RoPE    -> q_full[t, h, lora:]   for every head
+// The reference runs these as separate operators (RMSNorm, NearlyRotatePosition2D, cache append; src/models/deepseekv2.cpp:283-697).
+// ------------------------------------------------------------------------------------------------
+struct MlaPostParams {
+  const uint16_t* ckv; int ld_ckv;
+  const uint16_t* q; int ld_q;             // [T, H * (nope + rope)]
+  uint16_t* q_full; int ld_qf;             // [T, H * (lora + rope)]
+  uint16_t* pool;                          // [slots, lora + rope]
+  const int* positions; const int* slots;
+  const uint16_t* norm_w;
+  const float* cos_tab; const float* sin_tab;
+  int H, nope, rope, lora, rope_mode, spare_slot;
+  float eps;
+};
+
+template <bool BF16>
+__device__ __forceinline__ void mla_rope_pair(const uint16_t* src, uint16_t* dst, int i, int half, int mode, const float* ct, const float* st) {
+  // pair index i < half: interleaved rotates (2i, 2i+1); neox rotates (i, i + half)
+  const int a_idx = mode == 2 ? 2 * i : i, b_idx = mode == 2 ? 2 * i + 1 : i + half;
+  const float a = BF16 ? __bfloat162float(__ushort_as_bfloat16(src[a_idx])) : __half2float(__ushort_as_half(src[a_idx]));
+  const float b = BF16 ? __bfloat162float(__ushort_as_bfloat16(src[b_idx])) : __half2float(__ushort_as_half(src[b_idx]));
+  const float c = ct[i], sn = st[i];
+  const float ra = a * c - b * sn, rb = mode == 2 ? a * sn + b * c : b * c + a * sn;
+  dst[a_idx] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(ra)) : __half_as_ushort(__float2half_rn(ra));
+  dst[b_idx] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(rb)) : __half_as_ushort(__float2half_rn(rb));
+}
+
+template <bool BF16>
+__global__ void mla_post_kernel(const MlaPostParams p) {
+  __shared__ float red[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, tid = threadIdx.x, nthr = blockDim.x;
+  const uint16_t* row = p.ckv + (size_t)t * p.ld_ckv;
+  int slot = p.slots[t];
+  if (slot < 0) slot = p.spare_slot;
+  uint16_t* entry = p.pool + (size_t)slot * (p.lora + p.rope);
+  // latent RMSNorm
+  float ss = 0.f;
+  for (int i = tid; i < p.lora; i += nthr) {
+    const float v = BF16 ? __bfloat162float(__ushort_as_bfloat16(row[i])) : __half2float(__ushort_as_half(row[i]));
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  if ((tid & 31) == 0) red[tid >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int w = 0; w < (nthr >> 5); ++w) tot += red[w];
+  const float inv = rsqrtf(tot / (float)p.lora + p.eps);
+  for (int i = tid; i < p.lora; i += nthr) {
+    const float v = BF16 ? __bfloat162float(__ushort_as_bfloat16(row[i])) : __half2float(__ushort_as_half(row[i]));
+    const float w = BF16 ? __bfloat162float(__ushort_as_bfloat16(p.norm_w[i])) : __half2float(__ushort_as_half(p.norm_w[i]));
+    const float y = v * inv * w;
+    entry[i] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(y)) : __half_as_ushort(__float2half_rn(y));
+  }
+  // rotary parts
+  const int half = p.rope >> 1;
+  const int pos = p.positions[t];
+  const float* ct = p.cos_tab + (size_t)pos * half;
+  const float* st = p.sin_tab + (size_t)pos * half;
+  const int total = (p.H + 1) * half;          // head index H = the shared key
+  for (int it = tid; it < total; it += nthr) {
+    const int h = it / half, i = it - h * half;
+    if (h == p.H) {
+      mla_rope_pair<BF16>(row + p.lora, entry + p.lora, i, half, p.rope_mode, ct, st);
+    } else {
+      const uint16_t* src = p.q + (size_t)t * p.ld_q + (size_t)h * (p.nope + p.rope) + p.nope;
+      uint16_t* dst = p.q_full + (size_t)t * p.ld_qf + (size_t)h * (p.lora + p.rope) + p.lora;
+      mla_rope_pair<BF16>(src, dst, i, half, p.rope_mode, ct, st);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // SiLU(gate) * up :  x [M, 2I] (gate | up) -> y [M, I]
 // ------------------------------------------------------------------------------------------------
 template <bool BF16>
@@ -560,5 +637,22 @@ extern "C" int fb_route_topk(const float* logits, const float* bias, int* out_id
   RouteParams p{logits, bias, out_idx, out_w, M, E, topk, score_mode, renorm, n_group, topk_group, route_scale};
   const int wpb = 4;
   launch_k(route_topk_kernel, dim3((M + wpb - 1) / wpb), dim3(wpb * 32), 0, reinterpret_cast<cudaStream_t>(stream), 0, p);
+  return (int)cudaGetLastError();
+}
+
+// See MlaPostParams.  rope_mode: 1 neox, 2 interleaved.  spare_slot: where rows with slots[t] < 0 are written (a slot no request reads).
+extern "C" int fb_mla_post(const void* ckv, int ld_ckv, const void* q, int ld_q, void* q_full, int ld_qf, void* pool, const int* positions,
+                           const int* slots, const void* norm_w, const float* cos_tab, const float* sin_tab, int T, int H, int nope,
+                           int rope, int lora, int rope_mode, long long spare_slot, float eps, int dtype, void* stream_) {
+  if (T <= 0) return 0;
+  if ((dtype != 0 && dtype != 1) || (rope & 1) || (rope_mode != 1 && rope_mode != 2)) return -1;
+  MlaPostParams p;
+  p.ckv = (const uint16_t*)ckv; p.ld_ckv = ld_ckv; p.q = (const uint16_t*)q; p.ld_q = ld_q; p.q_full = (uint16_t*)q_full; p.ld_qf = ld_qf;
+  p.pool = (uint16_t*)pool; p.positions = positions; p.slots = slots; p.norm_w = (const uint16_t*)norm_w; p.cos_tab = cos_tab;
+  p.sin_tab = sin_tab; p.H = H; p.nope = nope; p.rope = rope; p.lora = lora; p.rope_mode = rope_mode; p.spare_slot = (int)spare_slot;
+  p.eps = eps;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  if (dtype == 1) launch_k(mla_post_kernel<true>, dim3(T), dim3(256), 0, s, 0, p);
+  else launch_k(mla_post_kernel<false>, dim3(T), dim3(256), 0, s, 0, p);
   return (int)cudaGetLastError();
 }

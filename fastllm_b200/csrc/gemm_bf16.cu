@@ -218,7 +218,7 @@ gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
 // ---------------------------------------------------------------------------------------------------
 template <int MPAD, bool BF16, int OCC>
 static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, int nsplit, int n_tiles,
-                                 cudaStream_t stream) {
+                                 cudaStream_t stream, int batch = 1) {
   using Cfg = SmallMCfg<MPAD, OCC>;
   auto kern = gemm_smallm_kernel<MPAD, BF16, OCC>;
   static DeviceOnce configured;
@@ -227,7 +227,7 @@ static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX,
     if (e != cudaSuccess) return e;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.gridDim = dim3(nsplit, n_tiles, batch);
   cfg.blockDim = dim3(192, 1, 1);
   cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
   cfg.stream = stream;
@@ -439,4 +439,47 @@ extern "C" int fb_gemm_qkv_post(const void* X, const void* W, const void* bias, 
     default: FB_QP(256)
   }
 #undef FB_QP
+}
+
+// Batched small-M GEMM, one launch for `batch` independent products that share the token rows:
+//   out[m, z * out_cols + n] = sum_k X[m, z * x_cols + k] * W[z * N + n, k]      (z < batch, n < N, k < K)
+// X: [M, >= batch * x_cols] (row stride ldx), W: [batch * N, K] (row stride ldw), out row stride ld_out; 16-bit in and out.
+// Used for the absorbed multi-head-latent-attention projections (one small matrix per head).  M <= 256, K % 64 == 0,
+// N % 8 == 0, x_cols % 8 == 0, out_cols % 4 == 0.
+extern "C" int fb_gemm_16bit_batched(const void* X, const void* W, void* out, int M, int N, int K, int batch, int ldx, int ldw, int ld_out,
+                                     int x_cols, int out_cols, int dtype, void* stream_) {
+  using namespace fb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || batch <= 0) return 0;
+  if (M > 256 || K % 64 != 0 || N % 8 != 0 || x_cols % 8 != 0 || out_cols % 4 != 0 || batch > 65535 || (dtype != 0 && dtype != 1)) return -1;
+  GemmParams p;
+  p.out = out; p.bias = nullptr; p.residual = nullptr;
+  p.M = M; p.N = N; p.K = K; p.ld_out = ld_out; p.ld_res = 0;
+  p.kb_total = K / 64; p.kb_per_split = p.kb_total;
+  p.flags = 0;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0; p.w_row0 = 0; p.x_row0 = 0;
+  for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
+  p.batch_w_rows = N; p.batch_x_cols = x_cols; p.batch_out_cols = out_cols;
+  const bool bf16 = dtype == 1;
+  const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
+  CUtensorMap tmW, tmX;
+  // the weight map spans all batches' rows; a tile that overhangs one head's N rows reads the next head's rows, whose
+  // products land in columns >= N of the tile and are dropped by the epilogue's n < N test
+  if (!make_tmap_2d(&tmW, W, (uint64_t)batch * N, K, ldw, 128, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmX, X, M, (uint64_t)(batch - 1) * x_cols + K, ldx, mpad, 64, 2, 3)) return -2;
+  const int n_tiles = (N + 127) / 128;
+#define FB_BT(MP)                                                                                        \
+  return (int)(bf16 ? launch_smallm<MP, true, 2>(tmW, tmX, p, 1, n_tiles, stream, batch)                 \
+                    : launch_smallm<MP, false, 2>(tmW, tmX, p, 1, n_tiles, stream, batch));
+  switch (mpad) {
+    case 16: FB_BT(16)
+    case 32: FB_BT(32)
+    case 64: FB_BT(64)
+    case 128: FB_BT(128)
+    default:
+      return (int)(bf16 ? launch_smallm<256, true, 1>(tmW, tmX, p, 1, n_tiles, stream, batch)
+                        : launch_smallm<256, false, 1>(tmW, tmX, p, 1, n_tiles, stream, batch));
+  }
+#undef FB_BT
 }

@@ -66,6 +66,10 @@ struct GemmParams {
   // requested the first ring of weight tiles and before it requests any activation tile.
   const uint32_t* wait_cnt = nullptr;
   const uint32_t* wait_expect = nullptr;
+  // Batched mode (grid.z = batch index z): weight rows start at z * batch_w_rows, the activation's k range at column
+  // z * batch_x_cols, the output at column z * batch_out_cols -- one launch for a GEMM per attention head (the absorbed
+  // multi-head-latent-attention projections, where every head has its own small matrix and its own slice of the activations).
+  int batch_w_rows = 0, batch_x_cols = 0, batch_out_cols = 0;
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
@@ -137,16 +141,17 @@ __device__ __forceinline__ void smallm_reduce_store(const GemmParams& p, uint8_t
         float2 r0 = unpack_16<BF16>(rv.x), r1 = unpack_16<BF16>(rv.y);
         acc.x += r0.x; acc.y += r0.y; acc.z += r1.x; acc.w += r1.y;
       }
+      const size_t zo = (size_t)blockIdx.z * (size_t)p.batch_out_cols;
       if (p.scatter_tp > 0) {
         float* dst = p.scatter_out[j / p.scatter_rows] + ((size_t)p.scatter_rank * p.M + j) * p.ld_out + n_out;
         *reinterpret_cast<float4*>(dst) = acc;
       } else if (p.flags & GEMM_OUT_F32) {
-        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)j * p.ld_out + n_out) = acc;
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + (size_t)j * p.ld_out + zo + n_out) = acc;
       } else {
         uint2 o;
         o.x = pack_16<BF16>(acc.x, acc.y);
         o.y = pack_16<BF16>(acc.z, acc.w);
-        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)j * p.ld_out + n_out) = o;
+        *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + (size_t)j * p.ld_out + zo + n_out) = o;
       }
     }
   }
@@ -304,12 +309,14 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
     if (elect_one()) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
+      const int w_row = p.w_row0 + (int)blockIdx.z * p.batch_w_rows + n_tile * 128;
+      const int x_col0 = (int)blockIdx.z * p.batch_x_cols;     // a multiple of 8 elements (16 bytes), checked by the launcher
       // Weights do not depend on the kernel before this one: the first ring of weight tiles is requested before the
       // dependency wait, so the weight stream starts while that kernel drains.  Activations follow the wait.
       const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
       for (int i = 0; i < pre; ++i) {
         mbar_expect_tx(&full_bar[i], Cfg::STAGE_BYTES);
-        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, p.w_row0 + n_tile * 128, pol_w);
+        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES, &tmW, &full_bar[i], (kb0 + i) * 64, w_row, pol_w);
       }
       pdl_wait();
       if (p.wait_cnt != nullptr) {
@@ -319,15 +326,15 @@ __device__ __forceinline__ void gemm_smallm_device(const CUtensorMap& tmW, const
         fence_proxy_async_global();
       }
       for (int i = 0; i < pre; ++i)
-        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmX, &full_bar[i], (kb0 + i) * 64, p.x_row0, pol_x);
+        tma_load_2d_hint(smem + i * Cfg::STAGE_BYTES + Cfg::A_BYTES, &tmX, &full_bar[i], x_col0 + (kb0 + i) * 64, p.x_row0, pol_x);
       for (int i = pre; i < kb_cnt; ++i) {
         const int s = i % Cfg::STAGES;
         const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
         if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_SMALLM, 1)) break;
         uint8_t* a = smem + s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-        tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 64, p.w_row0 + n_tile * 128, pol_w);
-        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], (kb0 + i) * 64, p.x_row0, pol_x);
+        tma_load_2d_hint(a, &tmW, &full_bar[s], (kb0 + i) * 64, w_row, pol_w);
+        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], x_col0 + (kb0 + i) * 64, p.x_row0, pol_x);
       }
     }
     __syncwarp();

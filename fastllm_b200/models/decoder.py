@@ -75,6 +75,8 @@ class AttentionWeights:
         self.kv_a_norm = None
         self.w_uk = None       # [H, nope, kv_lora]   absorbed K up-projection
         self.w_uv = None       # [H, v_dim, kv_lora]  absorbed V up-projection
+        self.w_uk_t = None     # [H, kv_lora, nope] in the activation dtype (operand layout of the batched absorb GEMM)
+        self.w_uv_c = None
 
 
 class LinearAttnWeights:
@@ -391,22 +393,22 @@ class DecoderModel:
             q = lw.q_b(B.rmsnorm(lw.q_a(x), lw.q_a_norm, c.latent_norm_eps or c.rms_eps))
         else:
             q = lw.q_b(x)
-        q = q.view(T, H, nope + rope)
         ckv = lw.kv_a(x)                                   # [T, lora + rope]
-        c_lat = B.rmsnorm(ckv[:, :lora].contiguous(), lw.kv_a_norm, c.latent_norm_eps or c.rms_eps)
         cos, sin = self.rope_tables()
-        k_pe = A.apply_rope_ref(ckv[:, lora:].reshape(T, 1, rope), fb.positions, cos, sin, self.rope_mode, rope)
-        q_pe = A.apply_rope_ref(q[..., nope:], fb.positions, cos, sin, self.rope_mode, rope)
         lat_pool = kv[0]
-        flat = lat_pool.view(-1, lora + rope)
-        entry = torch.cat([c_lat, k_pe.reshape(T, rope)], dim=-1).to(flat.dtype)
-        spare = flat.shape[0] - 1                              # last slot of the spare page (no host sync: graph-safe)
-        flat.index_copy_(0, torch.where(fb.slots >= 0, fb.slots, spare).long(), entry)
-        # absorb: q_lat[h] = q_nope[h] @ W_UK[h]  -> attention in latent space with a single shared "KV head"
-        q_lat = torch.einsum("thn,hnl->thl", q[..., :nope].float(), lw.w_uk.float()).to(x.dtype)
-        q_full = torch.cat([q_lat, q_pe.to(x.dtype)], dim=-1)              # [T, H, lora + rope]
+        # latent norm + rope of the shared key into the cache entry, rope of the heads' rotary query parts: one launch
+        q_full = torch.empty((T, H, lora + rope), device=x.device, dtype=x.dtype)
+        A.mla_post(ckv, q, q_full, lat_pool, fb.positions, fb.slots, lw.kv_a_norm, cos, sin, H, nope, rope, lora, self.rope_mode,
+                   c.latent_norm_eps or c.rms_eps)
+        # absorb: q_lat[h] = q_nope[h] @ W_UK[h] -> attention in latent space with a single shared "KV head"; one batched
+        # tensor-core launch over the heads, written straight into q_full[..., :lora]
+        if lw.w_uk_t is None:
+            lw.w_uk_t = lw.w_uk.transpose(1, 2).to(x.dtype).contiguous()      # [H, lora, nope]
+            lw.w_uv_c = lw.w_uv.to(x.dtype).contiguous()                      # [H, vd, lora]
+        B.linear_batched(q, lw.w_uk_t, H, nope + rope, q_full.view(T, H * (lora + rope)), lora + rope)
         o_lat = MOE.mla_paged_attention(q_full, lat_pool, fb, self.attn_scale, lora)   # [T, H, lora]
-        o = torch.einsum("thl,hvl->thv", o_lat.float(), lw.w_uv.float()).to(x.dtype).reshape(T, H * vd)
+        o = torch.empty((T, H * vd), device=x.device, dtype=x.dtype)
+        B.linear_batched(o_lat.reshape(T, H * lora), lw.w_uv_c, H, lora, o, vd)
         return self._row_parallel_norm(lw.o, o, residual, next_ln, consumer=consumer)
 
     @staticmethod

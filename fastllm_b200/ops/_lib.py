@@ -26,6 +26,8 @@ _KERNEL_SIGS = {
     "fb_gemm_16bit": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
     "fb_gemm_16bit_wait": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P, P],
     "fb_gemm_qkv_post": [P, P, P, I, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, F, F, P],
+    "fb_gemm_16bit_batched": [P, P, P, I, I, I, I, I, I, I, I, I, I, P],
+    "fb_mla_post": [P, I, P, I, P, I, P, P, P, P, P, P, I, I, I, I, I, I, LL, F, I, P],
     "fb_gemm_pick_split": [I, I, I, I],
     "fb_rmsnorm": [P, P, P, P, I, I, I, I, F, F, I, P],
     "fb_rmsnorm_quant": [P, P, P, P, I, I, I, I, F, F, I, I, P, I, P, P, I, P],

@@ -167,6 +167,31 @@ def qkv_post(qkv, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, h
 _FUSED_QKV = __import__("os").environ.get("FB_FUSED_QKV_POST", "1") == "1"
 
 
+def mla_post(ckv, q, q_full, lat_pool, positions, slots, norm_w, cos, sin, H, nope, rope, lora, rope_mode, eps):
+    """Multi-head latent attention, everything between the projections and the attention in one launch: RMSNorm of the
+    latent row and RoPE of the shared key into the cache entry (``slots`` < 0 go to the pool's spare last slot), RoPE of every
+    head's rotary query part into ``q_full[..., lora:]``.  ckv ``[T, lora + rope]``, q ``[T, H * (nope + rope)]``,
+    q_full ``[T, H, lora + rope]``, lat_pool ``[pages, page_len, 1, lora + rope]``."""
+    T = ckv.shape[0]
+    flat = lat_pool.view(-1, lora + rope)
+    spare = flat.shape[0] - 1
+    if ckv.is_cuda and ckv.dtype in (torch.float16, torch.bfloat16) and lat_pool.dtype == ckv.dtype and q.dtype == ckv.dtype \
+            and rope_mode in (ROPE_NEOX, ROPE_INTERLEAVED) and ckv.stride(-1) == 1 and q.stride(-1) == 1:
+        rc = _lib.kernels().fb_mla_post(_ptr(ckv), ckv.stride(0), _ptr(q), q.stride(0), _ptr(q_full), q_full.stride(0), _ptr(lat_pool),
+                                        _ptr(positions), _ptr(slots), _ptr(norm_w), _ptr(cos), _ptr(sin), T, H, nope, rope, lora, rope_mode,
+                                        spare, float(eps), dtype_code(ckv.dtype), _stream())
+        _lib.check(rc, "fb_mla_post")
+        return
+    from .basic import rmsnorm
+
+    c_lat = rmsnorm(ckv[:, :lora].contiguous(), norm_w, eps)
+    k_pe = apply_rope_ref(ckv[:, lora:].reshape(T, 1, rope), positions, cos, sin, rope_mode, rope)
+    qv = q.view(T, H, nope + rope)
+    q_full[..., lora:] = apply_rope_ref(qv[..., nope:], positions, cos, sin, rope_mode, rope).to(q_full.dtype)
+    entry = torch.cat([c_lat, k_pe.reshape(T, rope)], dim=-1).to(flat.dtype)
+    flat.index_copy_(0, torch.where(slots >= 0, slots, spare).long(), entry)
+
+
 def qkv_proj_post(x, w, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, head_dim, cos, sin, rope_mode=ROPE_NEOX,
                   rot_dim=None, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_unit_offset=0.0):
     """QKV projection + ``qkv_post`` in one launch for decode-sized batches: ``w`` is a dense ``LinearWeight`` with

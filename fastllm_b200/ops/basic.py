@@ -187,6 +187,31 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: b
     return out.reshape(*lead, n_out)
 
 
+def linear_batched(x: torch.Tensor, w: torch.Tensor, batch: int, x_cols: int, out: torch.Tensor, out_cols: int) -> torch.Tensor:
+    """``out[m, z * out_cols + n] = sum_k x[m, z * x_cols + k] * w[z, n, k]`` for ``z < batch``: one small GEMM per attention head
+    in one launch (the absorbed multi-head-latent-attention projections).  x ``[M, >= batch * x_cols]``, w ``[batch, N, K]``
+    contiguous, out ``[M, >= batch * out_cols]`` (written in place and returned)."""
+    M = x.shape[0]
+    _, N, K = w.shape
+    ok = (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and w.dtype == x.dtype and out.dtype == x.dtype and K % 64 == 0
+          and N % 8 == 0 and x_cols % 8 == 0 and out_cols % 4 == 0 and x.stride(-1) == 1 and out.stride(-1) == 1
+          and not (x.data_ptr() & 15) and not ((x.stride(0) * 2) & 15) and w.is_contiguous())
+    if not ok:
+        flush_pending_wait()
+        xs = x.as_strided((M, batch, K), (x.stride(0), x_cols, 1))
+        ov = out.as_strided((M, batch, N), (out.stride(0), out_cols, 1))
+        ov.copy_(torch.einsum("mzk,znk->mzn", xs.float(), w.float()).to(out.dtype))
+        return out
+    flush_pending_wait()
+    lib = _lib.kernels()
+    for m0 in range(0, M, 256):
+        m1 = min(M, m0 + 256)
+        rc = lib.fb_gemm_16bit_batched(_ptr(x[m0:m1]), _ptr(w), _ptr(out[m0:m1]), m1 - m0, N, K, batch, x.stride(0), K, out.stride(0),
+                                       x_cols, out_cols, dtype_code(x.dtype), _stream())
+        _lib.check(rc, "fb_gemm_16bit_batched")
+    return out
+
+
 # ---------------------------------------------------------------------------------------------------
 # RMSNorm
 # ---------------------------------------------------------------------------------------------------

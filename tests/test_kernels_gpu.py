@@ -781,3 +781,46 @@ def test_gdn_conv_update_and_recurrent_step(dtype):
         _close(rec_g.cpu(), rec_ref, 1e-3, 1e-3, f"rule state {step}", fro=1e-3)
     untouched = [s for s in range(n_slots) if s not in slots.tolist()]
     assert torch.equal(rec_g.cpu()[untouched], rec_ref[untouched])
+
+
+@pytest.mark.parametrize("M,batch,N,K,x_cols,out_cols", [(1, 4, 512, 128, 192, 576), (37, 16, 512, 128, 192, 576), (64, 8, 128, 512, 512, 128),
+                                                        (200, 3, 72, 64, 64, 80), (300, 2, 128, 128, 128, 128)])
+def test_gemm_batched_per_head(M, batch, N, K, x_cols, out_cols):
+    """One launch, one small GEMM per head: strided activation slices in, strided output slices out (MLA absorb shapes)."""
+    torch.manual_seed(19)
+    dt = torch.bfloat16
+    x = (torch.randn(M, batch * x_cols, device=DEV) * 0.5).to(dt)
+    w = (torch.randn(batch, N, K, device=DEV) * 0.08).to(dt)
+    out = torch.full((M, batch * out_cols), 7.0, device=DEV, dtype=dt)
+    B.linear_batched(x, w, batch, x_cols, out, out_cols)
+    ref = torch.einsum("mzk,znk->mzn", x.view(M, batch, x_cols)[..., :K].float(), w.float())
+    got = out.view(M, batch, out_cols)
+    _close(got[..., :N], ref, 3e-2, 2e-2, "batched gemm", fro=1e-2)
+    if out_cols > N:
+        assert bool((got[..., N:] == 7.0).all()), "columns outside a head's N outputs were written"
+
+
+@pytest.mark.parametrize("mode", [A.ROPE_INTERLEAVED, A.ROPE_NEOX])
+def test_mla_post_kernel(mode):
+    """Latent RMSNorm + shared-key RoPE into the cache entry and per-head query RoPE, against the PyTorch definition."""
+    torch.manual_seed(21)
+    T, H, nope, rope, lora, dt = 19, 6, 128, 64, 512, torch.bfloat16
+    ckv = torch.randn(T, lora + rope).to(dt)
+    q = torch.randn(T, H * (nope + rope)).to(dt)
+    pos = torch.randint(0, 400, (T,), dtype=torch.int32)
+    slots = torch.randperm(3 * 128)[:T].int()
+    slots[5] = -1
+    nw = (1 + 0.1 * torch.randn(lora)).to(dt)
+    cos, sin = A.build_rope_tables(rope, 512, 10000.0)
+    pool_c = torch.zeros(3 + 1, 128, 1, lora + rope, dtype=dt)
+    qf_c = torch.zeros(T, H, lora + rope, dtype=dt)
+    A.mla_post(ckv, q, qf_c, pool_c, pos, slots, nw, cos, sin, H, nope, rope, lora, mode, 1e-6)       # CPU tensors: PyTorch path
+    pool_g = torch.zeros_like(pool_c).to(DEV)
+    qf_g = torch.zeros_like(qf_c).to(DEV)
+    d = lambda t: t.to(DEV)
+    A.mla_post(d(ckv), d(q), qf_g, pool_g, d(pos), d(slots), d(nw), d(cos), d(sin), H, nope, rope, lora, mode, 1e-6)
+    _close(qf_g.cpu()[..., lora:], qf_c[..., lora:], 3e-2, 2e-2, "q rope")
+    flat_g, flat_c = pool_g.cpu().view(-1, lora + rope), pool_c.view(-1, lora + rope)
+    keep = slots[slots >= 0].long()
+    _close(flat_g[keep], flat_c[keep], 3e-2, 2e-2, "cache entries")
+    assert float(flat_g[:-1].abs().sum()) > 0 and float(flat_g[-1].abs().sum()) > 0          # the skipped row went to the spare slot
