@@ -45,18 +45,27 @@ struct AttnDecodeParams {
   int* counters;          // null: partials only (a separate combine kernel follows)
   uint16_t* out; int ld_out;
   int clip;               // 1: the last page of a request is loaded in 32-token boxes, only as far as it is filled
+  // attention variants (reference: include/models/qwen3_cuda_common.h:1262-1263, src/models/gpt_oss.cpp)
+  int window;             // > 0: sliding window, the query at position seq-1 sees keys at positions >= seq - window
+  float softcap;          // > 0: logits become softcap * tanh(logit / softcap) before the softmax (Gemma-2)
+  float scale;            // plain softmax scale (scale_log2 / log2(e)), used with softcap
 };
 
 // ---- plan: flatten (request, page) pairs ---------------------------------------------------------
 __global__ void attn_decode_plan_kernel(const int* __restrict__ seq_lens, int B, int* __restrict__ work, int* __restrict__ n_work,
-                                        int max_items) {
+                                        int max_items, int window = 0) {
   __shared__ int offs[1025];
   pdl_launch_dependents();
   pdl_wait();
   // single CTA; B <= 1024
   const int t = threadIdx.x;
-  int np = 0;
-  if (t < B) np = (seq_lens[t] + AD_PAGE - 1) / AD_PAGE;
+  int np = 0, first = 0;
+  if (t < B) {
+    const int seq = seq_lens[t];
+    np = (seq + AD_PAGE - 1) / AD_PAGE;
+    if (window > 0 && seq > window) first = (seq - window) / AD_PAGE;     // pages wholly before the window are not listed
+    np -= first;
+  }
   offs[t + 1] = np;
   if (t == 0) offs[0] = 0;
   __syncthreads();
@@ -71,7 +80,7 @@ __global__ void attn_decode_plan_kernel(const int* __restrict__ seq_lens, int B,
   if (t < B) {
     const int base = offs[t];
     for (int i = 0; i < np; ++i)
-      if (base + i < max_items) { work[2 * (base + i)] = t; work[2 * (base + i) + 1] = i; }
+      if (base + i < max_items) { work[2 * (base + i)] = t; work[2 * (base + i) + 1] = first + i; }
   }
   if (t == 0) { const int total = offs[B]; *n_work = total < max_items ? total : max_items; }
 }
@@ -228,7 +237,8 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       if ((unsigned)b >= (unsigned)p.B || (unsigned)pg >= (unsigned)p.max_splits || pg >= p.max_pages) { b = 0; pg = 0; }
       const int seq = p.seq_lens[b];
       const uint32_t iph = (uint32_t)it & 1u;
-      const bool valid = pg * AD_PAGE + t < seq;
+      const int kpos = pg * AD_PAGE + t;
+      const bool valid = kpos < seq && (p.window <= 0 || kpos >= seq - p.window);
       mbar_wait(s_full, iph, dead, KID_ATTN_DECODE, 6);
       tc_fence_after_sync();
       uint32_t r[16];
@@ -236,7 +246,11 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       tmem_ld_wait();
       float sv[GP];
 #pragma unroll
-      for (int h = 0; h < GP; ++h) sv[h] = (valid && h < G) ? __uint_as_float(r[h]) * p.scale_log2 : -INFINITY;
+      for (int h = 0; h < GP; ++h) {
+        float x = __uint_as_float(r[h]) * p.scale_log2;
+        if (p.softcap > 0.f) x = p.softcap * tanhf(__uint_as_float(r[h]) * p.scale / p.softcap) * 1.4426950408889634f;
+        sv[h] = (valid && h < G) ? x : -INFINITY;
+      }
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
         float m = sv[h];
@@ -362,7 +376,8 @@ struct CombineQuant {
 template <bool BF16, int QMODE = 0>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                            const int* __restrict__ seq_lens, uint16_t* __restrict__ out, int ld_out, int Hq,
-                                           int Hkv, int G, int max_splits, CombineQuant cq = {}) {
+                                           int Hkv, int G, int max_splits, CombineQuant cq = {}, int window = 0,
+                                           const float* __restrict__ sinks = nullptr) {
   const int b = blockIdx.x, hq = blockIdx.y, d = threadIdx.x;
   const int kvh = hq / G, g = hq - kvh * G;
   pdl_launch_dependents();
@@ -374,16 +389,20 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
     if (d == 0) report_error(ERR_BAD_ARG, KID_ATTN_DECODE, 22);
   }
   const size_t base = (size_t)(b * Hkv + kvh) * max_splits;
+  const int s0 = (window > 0 && seq > window) ? (seq - window) / AD_PAGE : 0;      // first page the plan listed
   float M = -INFINITY;
-  for (int s = 0; s < ns; ++s) M = fmaxf(M, part_ml[((base + s) * G + g) * 2]);
-  float acc = 0.f, L = 0.f;
-  for (int s = 0; s < ns; ++s) {
+  for (int s = s0; s < ns; ++s) M = fmaxf(M, part_ml[((base + s) * G + g) * 2]);
+  // attention sink: a per-head logit that takes part in the softmax normalisation only
+  const float sink = sinks != nullptr ? sinks[hq] * 1.4426950408889634f : -INFINITY;
+  M = fmaxf(M, sink);
+  float acc = 0.f, L = sinks != nullptr ? exp2f(sink - M) : 0.f;
+  for (int s = s0; s < ns; ++s) {
     const size_t sl = (base + s) * G + g;
     const float wgt = exp2f(part_ml[sl * 2] - M);
     L += part_ml[sl * 2 + 1] * wgt;
     acc += part_o[sl * AD_D + d] * wgt;
   }
-  const float o = ns > 0 ? acc / L : 0.f;
+  const float o = (ns > 0 && L > 0.f) ? acc / L : 0.f;
   uint16_t bits = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));
   out[(size_t)b * ld_out + (size_t)hq * AD_D + d] = bits;
   if (QMODE != 0) {
@@ -420,23 +439,46 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
 
 using namespace fb;
 
-extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n_work, int max_items, void* stream) {
+extern "C" int fb_attn_decode_plan_window(const int* seq_lens, int B, int* work, int* n_work, int max_items, int window, void* stream) {
   if (B <= 0 || B > 1024) return -1;
   int threads = 32;
   while (threads < B) threads <<= 1;
-  launch_k(attn_decode_plan_kernel, dim3(1), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream), 0, seq_lens, B, work, n_work, max_items);
+  launch_k(attn_decode_plan_kernel, dim3(1), dim3(threads), 0, reinterpret_cast<cudaStream_t>(stream), 0, seq_lens, B, work, n_work, max_items, window);
   return (int)cudaGetLastError();
+}
+extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n_work, int max_items, void* stream) {
+  return fb_attn_decode_plan_window(seq_lens, B, work, n_work, max_items, 0, stream);
 }
 
 // Scratch sizes (floats): part_o = B*Hkv*max_splits*G*128, part_ml = B*Hkv*max_splits*G*2.
 // q: [B, Hq, 128] with row stride ld_q elements between requests' heads packed (ld_q == Hq*128 required).
 // k_pool/v_pool: [num_slots, Hkv, 128].  dtype: 0 = fp16, 1 = bf16.
 // counters: [B * Hkv] ints, zero on first use (the kernel leaves them zero); null keeps the separate combine kernel.
+extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
+                                   const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
+                                   int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, int max_items,
+                                   float scale, int dtype, int grid_ctas, int* counters, int qmode, void* xq, int ldq, float* q_scales,
+                                   float* q_sums, int ld_a, int window, float softcap, const float* sinks, void* stream_);
+
 extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
                               const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
                               int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, int max_items,
                               float scale, int dtype, int grid_ctas, int* counters, int qmode, void* xq, int ldq, float* q_scales,
                               float* q_sums, int ld_a, void* stream_) {
+  return fb_attn_decode_opts(q, k_pool, v_pool, out, ld_out, work, n_work, page_table, seq_lens, part_o, part_ml, B, Hq, Hkv, D, num_slots,
+                             max_pages, max_splits, max_items, scale, dtype, grid_ctas, counters, qmode, xq, ldq, q_scales, q_sums, ld_a,
+                             0, 0.f, nullptr, stream_);
+}
+
+// window > 0: sliding-window attention (the work list must come from fb_attn_decode_plan_window with the same window);
+// softcap > 0: tanh soft-capping of the logits; sinks: fp32 [Hq] per-head sink logits (null: none).  The variants use the
+// separate combine kernel (counters must be null).
+extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
+                                   const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
+                                   int B, int Hq, int Hkv, int D, long long num_slots, int max_pages, int max_splits, int max_items,
+                                   float scale, int dtype, int grid_ctas, int* counters, int qmode, void* xq, int ldq, float* q_scales,
+                                   float* q_sums, int ld_a, int window, float softcap, const float* sinks, void* stream_) {
+  if ((window > 0 || sinks != nullptr) && counters != nullptr) return -1;
   // qmode 1 / 2: the combine also writes the output quantised to int8 / e4m3 per (request, head) for the output projection
   // (xq [B, Hq * 128] bytes, q_scales / q_sums [Hq, ld_a]); needs the separate combine kernel (counters == null)
   if (B <= 0) return 0;
@@ -460,6 +502,7 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
   p.B = B; p.max_items = max_items;
   p.counters = counters; p.out = reinterpret_cast<uint16_t*>(out); p.ld_out = ld_out; p.clip = 1;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.window = window; p.softcap = softcap; p.scale = scale;
   const uint32_t f = dtype == 1 ? 1u : 0u;
   p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);
   p.idesc_o = make_idesc(f, f, 1, 0, 128, AD_NPAD);
@@ -479,11 +522,11 @@ extern "C" int fb_attn_decode(const void* q, const void* k_pool, const void* v_p
     if (cfg.need()) { cudaFuncSetAttribute(attn_decode_kernel<BF, ST, GPV>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(ST)); } \
     launch_k<PDL_ATTN>(attn_decode_kernel<BF, ST, GPV>, dim3(grid_ctas), dim3(192), ad_smem_bytes(ST), stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
     if (counters == nullptr && qmode == 0)                                                                              \
-      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq); \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
     else if (counters == nullptr && qmode == 1)                                                                         \
-      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 1>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq); \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 1>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
     else if (counters == nullptr)                                                                                       \
-      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 2>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq); \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<BF, 2>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
   }
 #define FB_AD_GP(BF)                                                                                                    \
   {                                                                                                                     \
@@ -587,6 +630,7 @@ extern "C" int fb_attn_decode_static(const void* q, const void* k_pool, const vo
   p.max_pages = max_pages; p.max_splits = max_pages; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
   p.B = B; p.max_items = (int)items;
   p.counters = nullptr; p.out = nullptr; p.ld_out = 0; p.clip = 0;      // whole-page loads, separate combine kernel
+  p.window = 0; p.softcap = 0.f; p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   const uint32_t f = dtype == 1 ? 1u : 0u;
   p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);

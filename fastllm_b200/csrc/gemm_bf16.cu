@@ -57,73 +57,14 @@ struct LargeMCfg {
   static constexpr int STAGES = (196 * 1024) / STAGE_BYTES > 8 ? 8 : (196 * 1024) / STAGE_BYTES;
   static constexpr int BODY_BYTES = STAGES * STAGE_BYTES;
   static constexpr int SMEM_BYTES = BODY_BYTES + 256 + 1024;
-  static constexpr int TMEM_COLS = BN;
+  static constexpr int TMEM_COLS = 2 * BN;              // two accumulators: epilogue of tile i overlaps the MMAs of tile i + 1
 };
 
+// Epilogue of one 128-token x BN-feature tile: TMEM lanes [32q, 32q+32) of accumulator `tmem_acc` -> bias / residual / SwiGLU ->
+// 16-bit or fp32 rows in global memory.  A thread owns one token row and writes 64 / 128 contiguous bytes per 32-column step.
 template <int BN, bool BF16>
-__global__ void __launch_bounds__(192, 1)
-gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
-  using Cfg = LargeMCfg<BN>;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
-  uint64_t* empty_bar = full_bar + Cfg::STAGES;
-  uint64_t* accum_bar = empty_bar + Cfg::STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x, m_tile = blockIdx.y;
-  const int kb_cnt = p.kb_total;
-  bool dead = false;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-    mbar_init(accum_bar, 1);
-    mbar_init_fence();
-    tma_prefetch_desc(&tmW);
-    tma_prefetch_desc(&tmX);
-  }
-  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem_base = *tmem_slot;
-
-  if (warp == 0) {
-    if (elect_one()) {
-      for (int i = 0; i < kb_cnt; ++i) {
-        const int s = i % Cfg::STAGES;
-        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
-        if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_LARGEM, 1)) break;
-        uint8_t* a = smem + s * Cfg::STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-        tma_load_2d(a, &tmX, &full_bar[s], i * 64, m_tile * 128);
-        tma_load_2d(a + Cfg::A_BYTES, &tmW, &full_bar[s], i * 64, n_tile * BN);
-      }
-    }
-    __syncwarp();
-  } else if (warp == 1) {
-    if (elect_one()) {
-      for (int i = 0; i < kb_cnt; ++i) {
-        const int s = i % Cfg::STAGES;
-        const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u;
-        if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_LARGEM, 2)) break;
-        tc_fence_after_sync();
-        const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
-        const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
-        const uint64_t db = make_smem_desc(a_addr + Cfg::A_BYTES, 16, 1024, SWZ_128B);
-#pragma unroll
-        for (int k = 0; k < 4; ++k) umma_f16(tmem_base, da + 2 * k, db + 2 * k, p.idesc, (i | k) != 0 ? 1u : 0u);
-        umma_commit(&empty_bar[s]);
-      }
-      umma_commit(accum_bar);
-    }
-    __syncwarp();
-  } else {
-    const int q = warp & 3;
+__device__ __forceinline__ void largem_epilogue(const GemmParams& p, uint32_t tmem_acc, int m_tile, int n_tile, int q, int lane) {
     const int m = m_tile * 128 + q * 32 + lane;
-    mbar_wait(accum_bar, 0, dead, KID_GEMM_LARGEM, 3);
-    tc_fence_after_sync();
     const bool swiglu = (p.flags & GEMM_SWIGLU) != 0;
     const uint16_t* bias16 = reinterpret_cast<const uint16_t*>(p.bias);
     if (!swiglu) {
@@ -131,7 +72,7 @@ gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         __syncwarp();
-        tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
         tmem_ld_wait();
         const int n0 = n_tile * BN + c0;
         if (m >= p.M || n0 >= p.N) continue;
@@ -178,8 +119,8 @@ gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
         for (int c0 = 0; c0 < 64; c0 += 32) {
           uint32_t g[32], u[32];
           __syncwarp();
-          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(blk * 128 + c0), g);
-          tmem_ld_32x32b_x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(blk * 128 + 64 + c0), u);
+          tmem_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(blk * 128 + c0), g);
+          tmem_ld_32x32b_x32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(blk * 128 + 64 + c0), u);
           tmem_ld_wait();
           const int nin = n_tile * BN + blk * 128 + c0;            // gate row index in W
           const int nout = (n_tile * BN + blk * 128) / 2 + c0;
@@ -206,6 +147,102 @@ gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           }
         }
       }
+    }
+}
+
+// Persistent, warp-specialised large-M kernel.  One CTA per SM walks the output tiles (m fastest, so the CTAs of a wave share
+// a few weight tiles through L2); warp 0 streams operand tiles by TMA through a ring that keeps running across tile boundaries,
+// warp 1 issues the UMMAs, warps 2..5 run the epilogue.  TMEM holds two accumulators: while the epilogue warps drain tile i
+// the tensor core already accumulates tile i + 1, so the tensor pipe does not idle during epilogues and the per-tile prologue
+// (TMEM allocation, barrier set-up, pipeline fill) is paid once per CTA instead of once per tile.
+template <int BN, bool BF16>
+__global__ void __launch_bounds__(192, 1)
+gemm_largem_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const GemmParams p,
+                   int tiles_m, int tiles_n) {
+  using Cfg = LargeMCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* acc_full = empty_bar + Cfg::STAGES;        // [2] accumulator ready for the epilogue
+  uint64_t* acc_empty = acc_full + 2;                  // [2] accumulator drained (4 epilogue warps arrive)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_cnt = p.kb_total;
+  const int tiles = tiles_m * tiles_n;
+  bool dead = false;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int it = 0;                                          // k-block counter across all of this CTA's tiles
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x) {
+        const int n_tile = t / tiles_m, m_tile = t - n_tile * tiles_m;
+        for (int i = 0; i < kb_cnt; ++i, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], ph ^ 1u, dead, KID_GEMM_LARGEM, 1)) break;
+          uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+          tma_load_2d(a, &tmX, &full_bar[s], i * 64, m_tile * 128);
+          tma_load_2d(a + Cfg::A_BYTES, &tmW, &full_bar[s], i * 64, n_tile * BN);
+        }
+        if (dead) break;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      int it = 0, u = 0;                                   // u: tiles done by this CTA
+      for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++u) {
+        const int buf = u & 1;
+        const uint32_t use = (uint32_t)(u >> 1) & 1u;      // how often this buffer has been used, parity
+        if (!mbar_wait(&acc_empty[buf], use ^ 1u, dead, KID_GEMM_LARGEM, 4)) break;     // first use passes at once
+        tc_fence_after_sync();
+        const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+        for (int i = 0; i < kb_cnt; ++i, ++it) {
+          const int s = it % Cfg::STAGES;
+          const uint32_t ph = (uint32_t)(it / Cfg::STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], ph, dead, KID_GEMM_LARGEM, 2)) break;
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+          const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+          const uint64_t db = make_smem_desc(a_addr + Cfg::A_BYTES, 16, 1024, SWZ_128B);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) umma_f16(acc, da + 2 * k, db + 2 * k, p.idesc, (i | k) != 0 ? 1u : 0u);
+          umma_commit(&empty_bar[s]);
+        }
+        if (dead) break;
+        umma_commit(&acc_full[buf]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    int u = 0;
+    for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++u) {
+      const int n_tile = t / tiles_m, m_tile = t - n_tile * tiles_m;
+      const int buf = u & 1;
+      const uint32_t use = (uint32_t)(u >> 1) & 1u;
+      if (!mbar_wait(&acc_full[buf], use, dead, KID_GEMM_LARGEM, 3)) break;
+      tc_fence_after_sync();
+      largem_epilogue<BN, BF16>(p, tmem_base + (uint32_t)(buf * BN), m_tile, n_tile, q, lane);
+      tc_fence_before_sync();                              // this warp's TMEM reads are done before the buffer is handed back
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   tc_fence_before_sync();
@@ -275,8 +312,16 @@ static cudaError_t launch_largem(const CUtensorMap& tmX, const CUtensorMap& tmW,
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
     if (e != cudaSuccess) return e;
   }
-  dim3 grid((p.N + BN - 1) / BN, (p.M + 127) / 128, 1);
-  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmX, tmW, p);
+  const int tiles_n = (p.N + BN - 1) / BN, tiles_m = (p.M + 127) / 128;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const long long tiles = (long long)tiles_n * tiles_m;
+  const int grid = (int)(tiles < sm_count ? tiles : sm_count);
+  kern<<<grid, 192, Cfg::SMEM_BYTES, stream>>>(tmX, tmW, p, tiles_m, tiles_n);
   return cudaGetLastError();
 }
 

@@ -62,7 +62,9 @@ class _DecodeSlot:
         G = max(1, m.num_heads_local // m.num_kv_heads_local)
         self.ws = None
         if dev.type == "cuda" and not m.cfg.use_mla:
-            self.ws = A.DecodeWorkspace(bsz, m.num_kv_heads_local, G, P, dev, m.cfg.head_dim)
+            windows = {int(lw.attn.window) for lw in m.layers if lw.attn.window}
+            # one sliding-window length per model is planned alongside the full list (layers alternate local / global)
+            self.ws = A.DecodeWorkspace(bsz, m.num_kv_heads_local, G, P, dev, m.cfg.head_dim, window=windows.pop() if len(windows) == 1 else 0)
 
     def batch(self) -> ForwardBatch:
         return ForwardBatch(ids=self.ids, positions=self.positions, slots=self.slots, page_table=self.page_table,
@@ -118,8 +120,10 @@ class ModelRunner:
             return False        # one graph cannot span the devices of a layer-split placement
         if c.use_mla and not (c.kv_lora_rank == 512 and c.qk_rope_head_dim == 64 and self.model.dtype in (torch.float16, torch.bfloat16)):
             return False        # latent shapes outside the MLA decode kernel run the PyTorch evaluation
-        if self.model.general_attn or any(lw.attn.window or lw.attn.sinks is not None for lw in self.model.layers):
+        if self.model.general_attn or getattr(self.model, "kv_dtype", None) not in (None, self.model.dtype):
             return False        # these paths evaluate attention with host-synchronising PyTorch ops
+        if len({int(lw.attn.window) for lw in self.model.layers if lw.attn.window}) > 1 or (c.rope_local_theta and any(lw.attn.window for lw in self.model.layers)):
+            return False        # several window lengths / a second RoPE base for local layers: PyTorch evaluation
         if not c.use_mla and c.head_dim != 128:
             return False        # the tensor-core attention kernels cover head_dim 128; other widths run the PyTorch evaluation
         if c.has_linear_attn and not (c.lin_k_dim == 128 and c.lin_v_dim == 128 and self.model.dtype in (torch.float16, torch.bfloat16)):

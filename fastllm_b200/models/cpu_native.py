@@ -43,7 +43,7 @@ def eligible(model) -> bool:
         return False
     if c.use_mla or c.num_experts or c.hidden_act not in ("silu", "swiglu") or c.post_norms or model.general_attn or c.final_softcap:
         return False
-    if c.has_linear_attn or c.attn_output_gate:
+    if c.has_linear_attn or c.attn_output_gate or c.attn_softcap or c.attn_sinks:
         return False
     if any(lw.attn.window or lw.attn.sinks is not None for lw in model.layers):
         return False

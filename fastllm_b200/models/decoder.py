@@ -144,7 +144,7 @@ class DecoderModel:
         self.rot_dim = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
         self.attn_scale = cfg.attn_scale_override if cfg.attn_scale_override else 1.0 / math.sqrt(cfg.q_head_dim)
         # families whose attention needs options outside the tensor-core kernels run the PyTorch evaluation (not graph-safe)
-        self.general_attn = bool(cfg.attn_softcap or cfg.attn_sinks or cfg.qk_norm_after_rope or cfg.qk_norm_full)
+        self.general_attn = bool(cfg.qk_norm_after_rope or cfg.qk_norm_full)
         if cfg.use_mla and cfg.rope_scaling and cfg.rope_scaling.get("mscale_all_dim"):
             ms = 0.1 * float(cfg.rope_scaling["mscale_all_dim"]) * math.log(float(cfg.rope_scaling.get("factor", 1.0))) + 1.0
             self.attn_scale *= ms * ms
@@ -233,7 +233,13 @@ class DecoderModel:
         Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
         cos, sin = self.rope_tables(device=x.device)
         k_pool, v_pool = kv
-        if self.general_attn or lw.window or lw.sinks is not None:
+        variant = bool(c.attn_softcap or lw.window or lw.sinks is not None)
+        # sliding window, sink logits and soft-capping run inside the decode kernels; what the fused post-processing cannot
+        # express (norm after RoPE, one norm over all heads, e4m3 pages) and every prefill of a variant layer take the
+        # PyTorch evaluation
+        kernel_variant = (variant and fb.is_decode and x.is_cuda and D == 128 and not (c.qk_norm_after_rope or c.qk_norm_full)
+                          and k_pool.dtype == x.dtype and not c.rope_local_theta)
+        if (self.general_attn or variant) and not kernel_variant:
             a = self._attention_general(lw, lw.qkv(x), fb, kv)
             return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
         # decode-sized batches with head_dim 128: projection, per-head norm, RoPE and cache append are one launch
@@ -250,7 +256,8 @@ class DecoderModel:
                 qm = quant_gemm.act_quant_mode(lw.o, q.shape[0])
                 qm = qm if qm in (1, 2) else 0
             a = A.attn_decode(q, k_pool, v_pool, fb.page_table, fb.kv_lens, self.attn_scale, Hq, Hkv, D, ws=fb.decode_ws,
-                              planned=fb.decode_planned, quant_mode=qm)
+                              planned=fb.decode_planned, quant_mode=qm, window=int(lw.window or 0), softcap=float(c.attn_softcap or 0.0),
+                              sinks=lw.sinks)
         else:
             a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
                                cu_q_host=fb.cu_q_host)

@@ -37,6 +37,8 @@ _KERNEL_SIGS = {
     "fb_argmax": [P, P, P, I, I, I, I, I, P],
     "fb_route_topk": [P, P, P, P, I, I, I, I, I, I, I, F, P],
     "fb_attn_decode_plan": [P, I, P, P, I, P],
+    "fb_attn_decode_plan_window": [P, I, P, P, I, I, P],
+    "fb_attn_decode_opts": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, LL, I, I, I, F, I, I, P, I, P, I, P, P, I, I, F, P, P],
     "fb_attn_decode": [P, P, P, P, I, P, P, P, P, P, P, I, I, I, I, LL, I, I, I, F, I, I, P, I, P, I, P, P, I, P],
     "fb_attn_prefill": [P, I, LL, P, P, P, I, P, I, P, P, P, I, I, I, LL, I, F, I, P],
 }

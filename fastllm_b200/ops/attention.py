@@ -301,10 +301,14 @@ def paged_attention_general(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale,
 class DecodeWorkspace:
     """Device scratch for split-KV decode attention, sized once for (max_batch, max_pages_per_seq)."""
 
-    def __init__(self, max_batch, num_kv_heads, group, max_pages, device, head_dim=128):
+    def __init__(self, max_batch, num_kv_heads, group, max_pages, device, head_dim=128, window: int = 0):
         self.max_batch, self.max_pages = max_batch, max_pages
         self.work = torch.zeros((max_batch * max_pages, 2), device=device, dtype=torch.int32)
         self.n_work = torch.zeros((1,), device=device, dtype=torch.int32)
+        # sliding-window layers get their own work list: pages that lie wholly before the window are not visited
+        self.window = int(window)
+        self.work_w = torch.zeros((max_batch * max_pages, 2), device=device, dtype=torch.int32) if window else None
+        self.n_work_w = torch.zeros((1,), device=device, dtype=torch.int32) if window else None
         self.part_o = torch.empty((max_batch * num_kv_heads * max_pages * group * head_dim,), device=device,
                                   dtype=torch.float32)
         self.part_ml = torch.empty((max_batch * num_kv_heads * max_pages * group * 2,), device=device, dtype=torch.float32)
@@ -317,27 +321,43 @@ class DecodeWorkspace:
         rc = _lib.kernels().fb_attn_decode_plan(_ptr(seq_lens), B, _ptr(self.work), _ptr(self.n_work),
                                                 self.work.shape[0], _stream())
         _lib.check(rc, "fb_attn_decode_plan")
+        if self.window:
+            rc = _lib.kernels().fb_attn_decode_plan_window(_ptr(seq_lens), B, _ptr(self.work_w), _ptr(self.n_work_w),
+                                                           self.work_w.shape[0], self.window, _stream())
+            _lib.check(rc, "fb_attn_decode_plan_window")
 
 
 def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num_kv_heads, head_dim,
-                ws: DecodeWorkspace | None = None, out=None, planned=False, grid_ctas=0, quant_mode: int = 0):
+                ws: DecodeWorkspace | None = None, out=None, planned=False, grid_ctas=0, quant_mode: int = 0,
+                window: int = 0, softcap: float = 0.0, sinks=None):
     """One new token per request. q: ``[B, Hq*D]`` -> ``[B, Hq*D]``.
+
+    ``window`` > 0: sliding-window attention; ``softcap`` > 0: tanh soft-capping of the logits; ``sinks``: fp32 ``[Hq]`` per-head
+    sink logits in the softmax denominator.  All three run inside the same kernels.
 
     ``quant_mode`` 1 (int8) / 2 (e4m3): the combine kernel also writes the output quantised per (request, head) -- one 128-wide
     k block of the output projection -- and the result carries it as ``out.fb_quant`` (see ``ops.basic.rmsnorm``)."""
     B = q.shape[0]
+    variant = bool(window or softcap or sinks is not None)
     if not q.is_cuda:
         cu = torch.arange(B + 1, dtype=torch.int32)
+        if variant:
+            return paged_attention_general(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim,
+                                           window=window, sinks=sinks, softcap=softcap)
         if cpu_native(q) and k_pool.dtype == torch.float32:
             return cpu.attention_paged(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim)
         return paged_attention_ref(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim)
     G = num_q_heads // num_kv_heads
-    if head_dim != 128 or G > 16 or k_pool.shape[1] != PAGE_LEN:
+    if head_dim != 128 or G > 16 or k_pool.shape[1] != PAGE_LEN or k_pool.dtype != q.dtype:
         cu = torch.arange(B + 1, dtype=torch.int32, device=q.device)
+        if variant or k_pool.dtype != q.dtype:
+            return paged_attention_general(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim,
+                                           window=window, sinks=sinks, softcap=softcap)
         return paged_attention_ref(q, k_pool, v_pool, page_table, seq_lens.cpu(), cu.cpu(), scale, num_q_heads, num_kv_heads,
                                    head_dim)
-    if ws is None:
-        ws = DecodeWorkspace(B, num_kv_heads, G, page_table.shape[1], q.device)
+    if ws is None or (window and ws.window != window):
+        ws = DecodeWorkspace(B, num_kv_heads, G, page_table.shape[1], q.device, window=window)
+        planned = False
     if B > ws.max_batch or page_table.shape[1] > ws.max_pages:
         raise ValueError("decode workspace too small for this batch / page table")
     if not planned:
@@ -355,6 +375,18 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
         xs = torch.empty((num_q_heads, ld_a), device=q.device, dtype=torch.float32) if quant_mode == 1 else None
     else:
         quant_mode = 0
+    if variant:
+        work, n_work = (ws.work_w, ws.n_work_w) if window else (ws.work, ws.n_work)
+        rc = _lib.kernels().fb_attn_decode_opts(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(work),
+                                                _ptr(n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
+                                                num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
+                                                ws.work.shape[0], float(scale), dtype_code(q.dtype), grid_ctas, _ptr(None), quant_mode,
+                                                _ptr(xq), num_q_heads * head_dim, _ptr(sa), _ptr(xs), ld_a, int(window), float(softcap),
+                                                _ptr(sinks), _stream())
+        _lib.check(rc, "fb_attn_decode_opts")
+        if quant_mode:
+            out.fb_quant = (quant_mode, xq, sa, xs, ld_a)
+        return out
     rc = _lib.kernels().fb_attn_decode(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(ws.work),
                                        _ptr(ws.n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
                                        num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,

@@ -824,3 +824,27 @@ def test_mla_post_kernel(mode):
     keep = slots[slots >= 0].long()
     _close(flat_g[keep], flat_c[keep], 3e-2, 2e-2, "cache entries")
     assert float(flat_g[:-1].abs().sum()) > 0 and float(flat_g[-1].abs().sum()) > 0          # the skipped row went to the spare slot
+
+
+@pytest.mark.parametrize("window,softcap,use_sinks", [(200, 0.0, False), (0, 30.0, False), (0, 0.0, True), (128, 50.0, True)])
+def test_attn_decode_variants(window, softcap, use_sinks):
+    """Sliding window, logit soft-capping and sink logits inside the decode attention kernels against the PyTorch evaluation."""
+    torch.manual_seed(31)
+    Hq, Hkv, D, dt = 16, 4, 128, torch.bfloat16
+    lens = [1, 127, 129, 300, 1025, 77, 640]
+    Bn = len(lens)
+    k_pool, v_pool, pt = _make_cache(Bn, lens, Hkv, D, dt)
+    q = torch.randn(Bn, Hq * D).to(dt)
+    seq = torch.tensor(lens, dtype=torch.int32)
+    sinks = torch.randn(Hq) if use_sinks else None
+    scale = 1 / math.sqrt(D)
+    cu = torch.arange(Bn + 1, dtype=torch.int32)
+    ref = A.paged_attention_general(q, k_pool, v_pool, pt, seq, cu, scale, Hq, Hkv, D, window=window, sinks=sinks, softcap=softcap)
+    d = lambda t: t.to(DEV) if t is not None else None
+    out = A.attn_decode(d(q), d(k_pool), d(v_pool), d(pt), d(seq), scale, Hq, Hkv, D, window=window, softcap=softcap, sinks=d(sinks))
+    _close(out.cpu(), ref, 2e-2, 2e-2, "attn_decode variant", fro=2e-2)
+    # with a reused workspace that carries both work lists (what the engine does)
+    ws = A.DecodeWorkspace(Bn, Hkv, Hq // Hkv, pt.shape[1], DEV, window=window)
+    for _ in range(2):
+        out = A.attn_decode(d(q), d(k_pool), d(v_pool), d(pt), d(seq), scale, Hq, Hkv, D, ws=ws, window=window, softcap=softcap, sinks=d(sinks))
+    _close(out.cpu(), ref, 2e-2, 2e-2, "attn_decode variant (workspace)", fro=2e-2)

@@ -109,3 +109,38 @@ def test_hybrid_linear_attention_model_graph_decode():
     _lib.check_device_errors()
     same = sum(a == b for x, y in zip(o1, o2) for a, b in zip(x, y))
     assert all(x[0] == y[0] for x, y in zip(o1, o2)) and same >= 0.7 * sum(len(x) for x in o1), (o1, o2)
+
+
+def test_attention_variants_decode_in_cuda_graphs(tmp_path):
+    """gpt-oss (sinks + alternating sliding window) and Gemma-2 (soft-capping + sliding window) decode through the kernels'
+    variant paths inside CUDA graphs; tokens must agree with the eager PyTorch evaluation of the same weights."""
+    transformers = pytest.importorskip("transformers")
+    from fastllm_b200.loader import hf
+
+    base = dict(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, intermediate_size=512,
+                max_position_embeddings=1024, head_dim=128)
+    fams = {"gpt_oss": dict(model_type="gpt_oss", **base, num_local_experts=4, num_experts_per_tok=2, sliding_window=64),
+            "gemma2": dict(model_type="gemma2", **base, sliding_window=64, query_pre_attn_scalar=128)}
+    prompts = [list(range(5, 5 + n)) for n in (150, 37, 260)]
+    for name, kw in fams.items():
+        torch.manual_seed(0)
+        ref = transformers.AutoModelForCausalLM.from_config(transformers.AutoConfig.for_model(**kw), torch_dtype=torch.bfloat16)
+        for p_ in ref.parameters():
+            if p_.dim() >= 2:
+                torch.nn.init.normal_(p_, std=0.05)
+        d = str(tmp_path / name)
+        ref.save_pretrained(d, safe_serialization=True)
+        m = hf.load_model(d, device="cuda")
+        e1 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16)
+        assert e1.runner.graph_ok, name
+        o1 = e1.generate(prompts, GenerationConfig(max_new_tokens=8, ignore_eos=True))
+        import fastllm_b200.models.decoder as DEC
+        e2 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, use_cuda_graph=False), num_pages=16)
+        m.general_attn = True                      # force the PyTorch evaluation for the comparison run
+        try:
+            o2 = e2.generate(prompts, GenerationConfig(max_new_tokens=8, ignore_eos=True))
+        finally:
+            m.general_attn = False
+        _lib.check_device_errors()
+        agree = sum(a[:3] == b[:3] for a, b in zip(o1, o2))
+        assert agree >= 2, (name, o1, o2)
