@@ -46,6 +46,9 @@ def parse_args():
                     help="cpu: the CPU configuration (fp32, C++ backend); use with --model qwen3-0.6b --batch 1 --prompt-len 128 --output-len 128")
     ap.add_argument("--moe-dtype", default="")
     ap.add_argument("--moe-tp", action="store_true", help="shard every expert over the ranks instead of expert parallelism")
+    ap.add_argument("--draw-lengths", action="store_true",
+                    help="prompt lengths uniform in [128, --prompt-len] and output lengths uniform in [64, --output-len], drawn from the seed "
+                         "(dynamic batching: requests finish at different steps)")
     return ap.parse_args()
 
 
@@ -152,10 +155,14 @@ def run_ours(args):
     tp = eng.model.tp
     dev = eng.model.device
     gen = torch.Generator().manual_seed(1234)
-    prompts = [torch.randint(0, cfg.vocab_size, (P,), generator=gen).tolist() for _ in range(B)]
-    gcfg = GenerationConfig(max_new_tokens=O, ignore_eos=True)
-    for p in prompts:
-        eng.launch(p, gcfg)
+    if args.draw_lengths:
+        plens = torch.randint(128, P + 1, (B,), generator=gen).tolist()
+        olens = torch.randint(64, O + 1, (B,), generator=gen).tolist()
+    else:
+        plens, olens = [P] * B, [O] * B
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gen).tolist() for n in plens]
+    for p, o in zip(prompts, olens):
+        eng.launch(p, GenerationConfig(max_new_tokens=o, ignore_eos=True))
     # ---- prefill (untimed) ----
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -163,9 +170,9 @@ def run_ours(args):
         eng.step()
     torch.cuda.synchronize()
     prefill_s = time.perf_counter() - t0
-    assert sum(r.state.name == "DECODE" for r in eng.requests.values()) == B, "not every request reached decode"
+    assert args.draw_lengths or sum(r.state.name == "DECODE" for r in eng.requests.values()) == B, "not every request reached decode"
     K, W = args.steps, args.warmup
-    if W + K > O - 1:
+    if W + K > min(olens) - 1 and not args.draw_lengths:
         K = max(1, O - 1 - W)
     for _ in range(W):
         eng.step()
@@ -182,13 +189,19 @@ def run_ours(args):
     runner = eng.runner
     t_start = time.perf_counter()
     step_wall = []
+    produced = 0
     for i in range(K):
         ts = time.perf_counter()
         ev[i][0].record()
         n = eng.step()
         ev[i][1].record()
         step_wall.append(time.perf_counter() - ts)
-        assert n == B, f"step produced {n} tokens, expected {B}"
+        produced += n
+        assert n == B or args.draw_lengths, f"step produced {n} tokens, expected {B}"
+        if not eng.has_work():
+            K = i + 1
+            ev = ev[:K]
+            break
     torch.cuda.synchronize()
     wall = time.perf_counter() - t_start
     clocks = sampler.stop()
@@ -201,8 +214,8 @@ def run_ours(args):
     dev_ms, wall_ms = t.tolist()
     slot = runner.slots.get(runner._bucket(B))
     per_step_launches = getattr(runner, "launches_per_decode_step", 0)
-    value = B * K / (dev_ms / 1000.0)
-    e2e = B * K / (wall_ms / 1000.0)
+    value = produced / (dev_ms / 1000.0)
+    e2e = produced / (wall_ms / 1000.0)
     meta_bytes = int(slot.meta_host.numel() * 4) if slot is not None else 0
     ep = eng.model.ep
     out = {
@@ -210,7 +223,9 @@ def run_ours(args):
         "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": dev_ms / K, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": _vs_baseline(args, world, value), "dtype": "bf16" if args.dtype == "auto" else args.dtype,
         "data": "synthetic (uniform random token ids, random-init weights N(0,0.02))",
-        "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O, "parallelism": f"tp{world}" + (f"+ep{world}" if ep is not None else ""),
+        "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O,
+                   "lengths": "prompt uniform 128..seq_len, output uniform 64..output_len, drawn from the seed" if args.draw_lengths else "fixed",
+                   "parallelism": f"tp{world}" + (f"+ep{world}" if ep is not None else ""),
                    "kv_cache": "paged, page 128, bf16", "l2": "inputs larger than L2 (weights + KV >> 126 MB per step)",
                    "cuda_graph": not args.no_graph, "comm": (tp.comm.fused.name if (tp.comm and tp.comm.fused) else ("nccl" if world > 1 else "none")),
                    "control_plane": "rank 0 schedules; ranks 1..N-1 replay its step plans from a shared-memory ring" if world > 1 else "single rank"},

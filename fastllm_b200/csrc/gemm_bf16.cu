@@ -419,7 +419,15 @@ extern "C" int fb_gemm_16bit_wait(const void* X, const void* W, void* out, const
   }
   if (N % 32 != 0) return -1;
   p.kb_per_split = p.kb_total;
-  const int bn = (N >= 256 && N % 256 == 0) || N > 2048 ? 256 : 128;
+  int bn = (N >= 256 && N % 256 == 0) || N > 2048 ? 256 : 128;
+  {
+    // too few 128 x 256 tiles to occupy the SMs (a few hundred tokens): halve the tile width to double the CTA count
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    const long long t256 = (long long)((N + 255) / 256) * ((M + 127) / 128);
+    if (bn == 256 && t256 < sms && !(flags & GEMM_SWIGLU && N % 256 != 0)) bn = 128;
+  }
   p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, bn);
   CUtensorMap tmW, tmX;
   if (!make_tmap_2d(&tmX, X, M, K, ldx, 128, 64, 2, 3)) return -2;

@@ -269,7 +269,13 @@ class ModelRunner:
         return s.out_host[:n], logits
 
     def _capture(self, s: _DecodeSlot):
-        # warm-up run outside capture (lazy inits, tensor-map cache, cudaFuncSetAttribute), then capture
+        # warm-up run outside capture (lazy inits, tensor-map cache, cudaFuncSetAttribute), then capture.
+        # Writing K/V twice to the same cache slot is harmless, advancing a recurrent state twice is not: the warm-up run
+        # works on the scratch state slot, the requests' own slots are put back before the first replay.
+        saved_slots = None
+        if self.state_slots:
+            saved_slots = s.state_slots.clone()
+            s.state_slots.fill_(self.state_slots)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -282,4 +288,6 @@ class ModelRunner:
             self._decode_forward(s)
         self.launches_per_decode_step = _lib.launch_count() - c0
         s.graph = g
+        if saved_slots is not None:
+            s.state_slots.copy_(saved_slots)
         torch.cuda.synchronize()
