@@ -285,8 +285,10 @@ attn_prefill2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(q_full + 7);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = p.blocks[2 * blockIdx.x], q0 = p.blocks[2 * blockIdx.x + 1];
-  const int hq0 = 2 * blockIdx.y, kvh = hq0 / p.G;
+  // grid: x = head pair (fast), y = query block; the host lists the blocks longest-first, so CTAs are handed out heaviest
+  // first and the short blocks near the start of a sequence fill the tail of the launch
+  const int b = p.blocks[2 * blockIdx.y], q0 = p.blocks[2 * blockIdx.y + 1];
+  const int hq0 = 2 * blockIdx.x, kvh = hq0 / p.G;
   const int q_begin = p.cu_q[b], q_len = p.cu_q[b + 1] - q_begin;
   const int kv_len = p.kv_lens[b];
   const int pos0 = kv_len - q_len + q0;
@@ -400,14 +402,24 @@ attn_prefill2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tmem_ld_32x32b_x32(tmem_s + lane_off, sreg);
       tmem_ld_32x32b_x32(tmem_s + lane_off + 32, sreg + 32);
       tmem_ld_wait();
-      float m_new = m_run;
+      // Raw logits stay in registers; the softmax scale is folded into the exponent's FMA.  Only steps that touch the
+      // causal diagonal of this block (or the end of the cache) pay for the mask; kv0 + 63 <= pos0 means every row of
+      // the block sees the whole step.
+      const bool full_step = kv0 + AP2_KV - 1 <= pos0 && kv0 + AP2_KV <= kv_len;
+      float m_raw = -INFINITY;
+      if (full_step) {
 #pragma unroll
-      for (int j = 0; j < 64; ++j) {
-        const int kv = kv0 + j;
-        const float sv = (kv <= pos && kv < kv_len) ? __uint_as_float(sreg[j]) * p.scale_log2 : -INFINITY;
-        sreg[j] = __float_as_uint(sv);
-        m_new = fmaxf(m_new, sv);
+        for (int j = 0; j < 64; ++j) m_raw = fmaxf(m_raw, __uint_as_float(sreg[j]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const int kv = kv0 + j;
+          const float sv = (kv <= pos && kv < kv_len) ? __uint_as_float(sreg[j]) : -INFINITY;
+          sreg[j] = __float_as_uint(sv);
+          m_raw = fmaxf(m_raw, sv);
+        }
       }
+      const float m_new = fmaxf(m_run, m_raw * p.scale_log2);          // scale > 0: the maximum commutes with it
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float alpha = exp2f(m_run - m_use);
       if (it > 0) {
@@ -433,10 +445,10 @@ attn_prefill2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         uint32_t pk[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          const float p0 = exp2f(__uint_as_float(sreg[8 * g + 2 * j]) - m_use), p1 = exp2f(__uint_as_float(sreg[8 * g + 2 * j + 1]) - m_use);
+          const float p0 = exp2f(fmaf(__uint_as_float(sreg[8 * g + 2 * j]), p.scale_log2, -m_use));
+          const float p1 = exp2f(fmaf(__uint_as_float(sreg[8 * g + 2 * j + 1]), p.scale_log2, -m_use));
           pk[j] = pack_16<BF16>(p0, p1);
-          const float2 back = unpack_16<BF16>(pk[j]);
-          l_add += back.x + back.y;
+          l_add += p0 + p1;
         }
         *reinterpret_cast<uint4*>(prow + ((g ^ (r & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
@@ -506,7 +518,8 @@ extern "C" int fb_attn_prefill(const void* q, int ld_q, long long T, const void*
     if (!make_tmap_2d(&tmK64, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AP2_KV, 64, 2, 3)) return -2;
     if (!make_tmap_2d(&tmV64, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AP2_KV, 64, 2, 3)) return -2;
     p.idesc_s = make_idesc(f, f, 0, 0, 128, AP2_KV);
-    dim3 grid2(n_blocks, Hq / 2);
+    if (n_blocks > 65535) return -1;
+    dim3 grid2(Hq / 2, n_blocks);
     if (dtype == 1) {
       static DeviceOnce cfg;
       if (cfg.need()) { cudaFuncSetAttribute(attn_prefill2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, AP2_SMEM_BYTES); }

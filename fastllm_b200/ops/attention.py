@@ -413,6 +413,7 @@ def attn_prefill(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_head
     for b in range(len(cu) - 1):
         for q0 in range(0, cu[b + 1] - cu[b], 128):
             blocks.append((b, q0))
+    blocks.sort(key=lambda t: -t[1])        # causal work grows with the block's start: longest blocks are scheduled first
     if out is None:
         out = torch.empty_like(q)
     if not blocks:
