@@ -273,7 +273,7 @@ def build_linear_attn(m, g, ln, W):
     in_w = torch.cat([hs(qw, Dk, Hk_l), hs(kw, Dk, Hk_l), hs(vw, Dv, Hv_l), hs(zw, Dv, Hv_l), hs(bw, 1, Hv_l), hs(aw, 1, Hv_l)], dim=0)
     pad = (-in_w.shape[0]) % 8                      # the GEMM wants a multiple of 8 output rows
     if pad:
-        in_w = torch.cat([in_w, torch.zeros(pad, in_w.shape[1], dtype=in_w.dtype)], dim=0)
+        in_w = torch.cat([in_w, torch.zeros(pad, in_w.shape[1], dtype=in_w.dtype, device=in_w.device)], dim=0)
     la.in_proj = _lin(m, in_w, W("linear_attn.in_proj_qkvz.weight"))
     la.conv_w = _to(torch.cat([hs(cq, Dk, Hk_l), hs(ck, Dk, Hk_l), hs(cv, Dv, Hv_l)], dim=0), m)
     la.A_log = g("linear_attn.A_log")[r * Hv_l:(r + 1) * Hv_l].to(m.device, torch.float32).contiguous()

@@ -611,6 +611,14 @@ def _randn(shape, std, device, dtype, gen):
     return (torch.randn(shape, device=device, dtype=torch.float32, generator=gen) * std).to(dtype)
 
 
+def _name_seed(seed: int, name: str) -> int:
+    """Stable per-tensor seed: every tensor's values depend on (seed, name) only, not on what was drawn before it, so a
+    rank can skip the tensors it does not keep (the other ranks' experts) and still agree with its peers on the rest."""
+    import zlib
+
+    return (seed * 1000003 + zlib.crc32(name.encode())) & 0x7FFFFFFFFFFFFFFF
+
+
 def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | None = None, ep=None, seed: int = 0,
                 std: float = 0.02, wdtype: str = "auto", moe_wdtype: str | None = None, moe_device: str | None = None) -> DecoderModel:
     """Build a model with N(0, std) weights and unit norm weights, sharded for this TP/EP rank.
@@ -630,6 +638,7 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
     raw: dict[str, torch.Tensor] = {}
 
     def mk(name, shape, s=std):
+        gen.manual_seed(_name_seed(seed, name))
         raw[name] = _randn(shape, s, dev, dtype, gen)
 
     def ones(name, n):
@@ -649,6 +658,7 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
             mk(lp + "in_proj_qkvz.weight", (2 * Hk * Dk + 2 * Hv * Dv, H))
             mk(lp + "in_proj_ba.weight", (2 * Hv, H))
             mk(lp + "conv1d.weight", (2 * Hk * Dk + Hv * Dv, 1, cfg.lin_conv_kernel), 0.3)
+            gen.manual_seed(_name_seed(seed, lp + "A_log"))
             raw[lp + "A_log"] = torch.log(torch.rand(Hv, device=dev, generator=gen) * 4 + 0.5)
             raw[lp + "dt_bias"] = torch.ones(Hv, device=dev, dtype=torch.float32)
             ones(lp + "norm.weight", Dv)
@@ -684,13 +694,10 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
                 raw[p + "mlp.gate.e_score_correction_bias"] = torch.zeros(cfg.num_experts, device=dev, dtype=torch.float32)
             lo, hi = MOE.local_expert_range(cfg.num_experts, ep)
             I = cfg.moe_intermediate_size
-            # draw all experts' weights (keeps every rank's generator in step), keep the local ones
-            for e in range(cfg.num_experts):
-                keep = lo <= e < hi
+            # tensors are seeded by name, so only this rank's experts are drawn (with MoE tensor parallelism: all of them)
+            for e in range(lo, hi):
                 for nm, shp in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
-                    t = _randn(shp, std, dev, dtype, gen)
-                    if keep:
-                        raw[p + f"mlp.experts.{e}.{nm}.weight"] = t
+                    mk(p + f"mlp.experts.{e}.{nm}.weight", shp)
             if cfg.num_shared_experts:
                 SI = cfg.shared_expert_intermediate_size
                 sp = p + ("mlp.shared_expert." if cfg.shared_expert_gate else "mlp.shared_experts.")

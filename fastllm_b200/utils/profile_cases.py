@@ -105,7 +105,47 @@ def moe_grouped(tokens=128, experts=128, topk=8, hidden=2048, inter=768, kind="f
     torch.cuda.synchronize()
 
 
+def gemm_qkv_post(tokens=64, hq=32, hkv=8, k=4096, iters=4):
+    from ..ops.quant import LinearWeight
+
+    dev, D = "cuda", 128
+    n = (hq + 2 * hkv) * D
+    ws = [LinearWeight.from_dense((torch.randn(n, k, device=dev) * 0.02).bfloat16()) for _ in range(3)]       # 3 x 50 MB > L2
+    x = torch.randn(tokens, k, device=dev).bfloat16()
+    cos, sin = A.build_rope_tables(D, 4096, 5e5, None, dev)
+    pos = torch.arange(tokens, device=dev).int()
+    slots = torch.arange(tokens, device=dev).int()
+    kp = torch.zeros(4, 128, hkv, D, device=dev, dtype=torch.bfloat16)
+    vp = torch.zeros_like(kp)
+    for i in range(iters):
+        A.qkv_proj_post(x, ws[i % 3], pos, slots, kp, vp, hq, hkv, D, cos, sin)
+    torch.cuda.synchronize()
+
+
+def gdn_decode(batch=64, hk=16, hv=32, iters=4):
+    from ..ops import linear_attn as L
+
+    dev, D, dt = "cuda", 128, torch.bfloat16
+    C = 2 * hk * D + hv * D
+    conv = torch.zeros(batch + 1, C, 3, device=dev, dtype=dt)
+    rec = torch.randn(batch + 1, hv, D, D, device=dev) * 0.05            # 64 x 32 x 64 KB = 134 MB of state
+    w = (torch.randn(C, 4, device=dev) * 0.3).to(dt)
+    slots = torch.arange(batch, device=dev).int()
+    A_log, dtb = torch.zeros(hv, device=dev), torch.ones(hv, device=dev)
+    nw = torch.ones(D, device=dev, dtype=dt)
+    for _ in range(iters):
+        x = torch.randn(batch, C, device=dev).to(dt)
+        a, b = torch.randn(batch, hv, device=dev).to(dt), torch.randn(batch, hv, device=dev).to(dt)
+        z = torch.randn(batch, hv * D, device=dev).to(dt)
+        y = L.causal_conv1d_decode(x, w, conv, slots)
+        L.gated_delta_decode(y, a, b, z, A_log, dtb, nw, 1e-6, rec, slots, hk, hv, D, D)
+    torch.cuda.synchronize()
+
+
 CASES = {
+    "gemm_qkv_post": gemm_qkv_post,
+    "gdn_decode": gdn_decode,
+    "gemm_prefill_gate_up": lambda: gemm_prefill(4096, 28672, 4096),
     "gemm_quant_fp8": lambda: gemm_quant("fp8"),
     "gemm_quant_int4g": lambda: gemm_quant("int4g128"),
     "gemm_quant_fp8_m16": lambda: gemm_quant("fp8", m=16),
