@@ -84,6 +84,89 @@ class NativeBPE:
         return self.L.fbtok_vocab_size(self.h)
 
 
+class NativeUnigram:
+    """ctypes wrapper over the C++ Unigram core (``csrc/runtime/unigram.cpp``): the SentencePiece-style models of
+    ``tokenizer.json`` (``model.type == "Unigram"``: T5, ALBERT, XLM-R, older Llama / Gemma exports).  The Metaspace
+    convention is applied here: spaces become U+2581 before segmentation (with a leading one unless the file says
+    otherwise) and back to spaces after decoding."""
+
+    SPACE = "\u2581"
+
+    def __init__(self, tokenizer_json: str | Path | dict):
+        L = _lib.runtime()
+        L.fbuni_create.restype = ctypes.c_void_p
+        L.fbuni_destroy.argtypes = [ctypes.c_void_p]
+        L.fbuni_add_piece.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_float]
+        L.fbuni_finish.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+        L.fbuni_add_special.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int, ctypes.c_int]
+        L.fbuni_encode.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_int, ctypes.POINTER(ctypes.c_int), ctypes.c_int]
+        L.fbuni_decode.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int), ctypes.c_int, ctypes.c_char_p, ctypes.c_int, ctypes.c_int]
+        L.fbuni_vocab_size.argtypes = [ctypes.c_void_p]
+        self.L = L
+        self.h = ctypes.c_void_p(L.fbuni_create())
+        tj = tokenizer_json if isinstance(tokenizer_json, dict) else json.loads(Path(tokenizer_json).read_text(encoding="utf-8"))
+        model = tj.get("model", {})
+        for piece, score in model.get("vocab", []):
+            b = piece.encode("utf-8")
+            L.fbuni_add_piece(self.h, b, len(b), float(score))
+        L.fbuni_finish(self.h, int(model.get("unk_id") or 0), 1 if model.get("byte_fallback") else 0)
+        self.special = {}
+        for a in tj.get("added_tokens", []):
+            b = a["content"].encode("utf-8")
+            L.fbuni_add_special(self.h, b, len(b), int(a["id"]))
+            self.special[a["content"]] = int(a["id"])
+        pre = tj.get("pre_tokenizer") or {}
+        metas = [pre] + list(pre.get("pretokenizers", [])) if isinstance(pre, dict) else []
+        meta = next((m for m in metas if m.get("type") == "Metaspace"), {})
+        scheme = meta.get("prepend_scheme", "always" if meta.get("add_prefix_space", True) else "never")
+        self.prepend = scheme in ("always", "first")
+
+    def __del__(self):
+        try:
+            self.L.fbuni_destroy(self.h)
+        except Exception:
+            pass
+
+    def encode(self, text: str) -> list[int]:
+        t = text.replace(" ", self.SPACE)
+        if self.prepend and not t.startswith(self.SPACE):
+            t = self.SPACE + t
+        b = t.encode("utf-8")
+        cap = max(16, len(b) + 8)
+        out = (ctypes.c_int * cap)()
+        n = self.L.fbuni_encode(self.h, b, len(b), out, cap)
+        if n < 0:
+            cap = -n
+            out = (ctypes.c_int * cap)()
+            n = self.L.fbuni_encode(self.h, b, len(b), out, cap)
+        return list(out[:n])
+
+    def decode_bytes(self, ids, skip_special_tokens=True) -> bytes:
+        arr = (ctypes.c_int * len(ids))(*ids)
+        cap = max(64, len(ids) * 24)
+        buf = ctypes.create_string_buffer(cap)
+        n = self.L.fbuni_decode(self.h, arr, len(ids), buf, cap, 1 if skip_special_tokens else 0)
+        if n < 0:
+            cap = -n
+            buf = ctypes.create_string_buffer(cap)
+            n = self.L.fbuni_decode(self.h, arr, len(ids), buf, cap, 1 if skip_special_tokens else 0)
+        return buf.raw[:n]
+
+    def decode(self, ids, skip_special_tokens=True) -> str:
+        s = self.decode_bytes(ids, skip_special_tokens).decode("utf-8", errors="replace").replace(self.SPACE, " ")
+        return s[1:] if (self.prepend and s.startswith(" ")) else s
+
+    @property
+    def vocab_size(self):
+        return self.L.fbuni_vocab_size(self.h)
+
+
+def native_tokenizer(tokenizer_json: str | Path | dict):
+    """The native core that matches the file's model type (byte-level BPE or Unigram)."""
+    tj = tokenizer_json if isinstance(tokenizer_json, dict) else json.loads(Path(tokenizer_json).read_text(encoding="utf-8"))
+    return NativeUnigram(tj) if (tj.get("model") or {}).get("type") == "Unigram" else NativeBPE(tj)
+
+
 class Tokenizer:
     """Uniform interface: encode / decode / apply_chat_template / streaming decode."""
 
@@ -109,7 +192,7 @@ class Tokenizer:
                 except Exception:
                     self.hf = None
             if self.hf is None and (self.path / "tokenizer.json").exists():
-                self.native = NativeBPE(self.path / "tokenizer.json")
+                self.native = native_tokenizer(self.path / "tokenizer.json")
         if isinstance(self.chat_template, list):       # some configs store named templates
             self.chat_template = next((t["template"] for t in self.chat_template if t.get("name") == "default"),
                                       self.chat_template[0]["template"])
@@ -132,7 +215,7 @@ class Tokenizer:
         if self.hf is not None:
             return len(self.hf)
         if self.native is not None:
-            return self.native.vocab_size()
+            return int(self.native.vocab_size)
         return 256
 
     def eos_ids(self) -> list[int]:

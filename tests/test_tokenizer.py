@@ -47,3 +47,31 @@ def test_chat_template_render():
     s = render(tpl, [{"role": "user", "content": "hi"}], add_generation_prompt=True)
     assert s == "<|user|>hi</s><|assistant|>"
     assert "<|im_start|>user" in render(None, [{"role": "user", "content": "hi"}])
+
+
+def test_native_unigram_matches_hf_tokenizers(tmp_path):
+    """The C++ Unigram core against the Hugging Face ``tokenizers`` implementation on the same model file."""
+    import json
+
+    tokenizers = pytest.importorskip("tokenizers")
+    from tokenizers import Tokenizer as HFTok, decoders, models, pre_tokenizers
+
+    from fastllm_b200.tokenizer import NativeUnigram, native_tokenizer
+
+    pieces = [("<unk>", 0.0), ("<s>", 0.0)] + [(f"<0x{b:02X}>", -20.0) for b in range(256)]
+    words = ["▁the", "▁", "the", "▁hello", "hello", "he", "llo", "▁world", "wor", "ld", "world", "▁a", "an", "b", "c", "d", "e",
+             "h", "l", "o", "r", "t", "w", "a", "n", "▁to", "ken", "iz", "er", "▁tokenizer", "s", "é", "▁caf"]
+    for i, w in enumerate(words):
+        pieces.append((w, -1.0 - 0.37 * (i % 7) - 0.01 * len(w)))
+    tok = HFTok(models.Unigram(pieces, unk_id=0, byte_fallback=True))
+    tok.pre_tokenizer = pre_tokenizers.Metaspace(replacement="▁", prepend_scheme="always")
+    tok.decoder = decoders.Sequence([decoders.Metaspace(replacement="▁", prepend_scheme="always"), decoders.ByteFallback(), decoders.Fuse()])
+    path = tmp_path / "tokenizer.json"
+    tok.save(str(path))
+    nat = native_tokenizer(path)
+    assert isinstance(nat, NativeUnigram) and nat.vocab_size == len(pieces)
+    for text in ["hello world", "the tokenizers are here", "a b c", "café 中 hello", "hello  world", "x"]:
+        want = tok.encode(text, add_special_tokens=False).ids
+        got = nat.encode(text)
+        assert got == want, (text, got, want)
+        assert nat.decode(got) == tok.decode(want), text
