@@ -340,7 +340,7 @@ class model:
         if tp is not None and tp.size > 1 and tp.comm is not None and not _defer_fused and self.torch_model.on_cuda:
             from .parallel import symm
 
-            tp.comm.fused = symm.try_create(tp.comm, cfg, min(256, ec.max_batch))
+            tp.comm.fused = symm.try_create(tp.comm, cfg, min(256, ec.max_batch), max_big_m=symm.prefill_rows(ec))
         self.default_generation_config = {"repetition_penalty": 1.0, "top_p": 0.8, "top_k": 1, "temperature": 1.0}
         gc = Path(path) / "generation_config.json" if path and os.path.isdir(path) else None
         if gc is not None and gc.exists():

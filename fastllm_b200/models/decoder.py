@@ -468,7 +468,7 @@ class DecoderModel:
             shared = lw.shared_down(lw.shared_gate_up(x, swiglu=True))
             if lw.shared_gate is not None:
                 shared = shared * torch.sigmoid(torch.matmul(x.float(), lw.shared_gate.float().t())).to(shared.dtype)
-        if self._fused_active and lw.experts.stacked is not None:
+        if self._fused_active and lw.experts.stacked is not None and not self.tp.comm.fused._big(x.shape[0]):
             # expert-parallel combine fused with the cross-rank reduction + residual + norm (one kernel)
             from ..ops import moe_grouped
 

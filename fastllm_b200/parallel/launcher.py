@@ -61,7 +61,8 @@ def build_rank_model(spec: dict, rank: int, world: int, device: str):
         if world > 1 and dev.type == "cuda" and comm_mode in ("auto", "fused"):
             from . import symm
 
-            tp.comm.fused = symm.try_create(tp.comm, cfg, int(spec.get("max_m", ecfg.max_batch)), strict=(comm_mode == "fused"))
+            tp.comm.fused = symm.try_create(tp.comm, cfg, int(spec.get("max_m", ecfg.max_batch)), strict=(comm_mode == "fused"),
+                                            max_big_m=symm.prefill_rows(ecfg))
         ep = EPInfo.from_tp(tp) if (world > 1 and cfg.is_moe and not spec.get("moe_tp")) else None
         model = random_init(cfg, dev, dt, tp=tp, ep=ep, seed=int(spec.get("seed", 0)), std=float(spec.get("std", 0.02)),
                             wdtype=spec.get("wdtype", "auto"), moe_wdtype=spec.get("moe_wdtype") or None)
@@ -77,7 +78,8 @@ def build_rank_model(spec: dict, rank: int, world: int, device: str):
         if world > 1 and dev.type == "cuda" and comm_mode in ("auto", "fused"):
             from . import symm
 
-            tp.comm.fused = symm.try_create(tp.comm, m.torch_model.cfg, min(256, m.engine.cfg.max_batch), strict=(comm_mode == "fused"))
+            tp.comm.fused = symm.try_create(tp.comm, m.torch_model.cfg, min(256, m.engine.cfg.max_batch), strict=(comm_mode == "fused"),
+                                            max_big_m=symm.prefill_rows(m.engine.cfg))
         return m.engine, m
     raise ValueError(f"unknown model spec kind '{kind}'")
 

@@ -12,6 +12,9 @@ Arena layout (same offsets on every rank):
     h      16-bit [max_m, hidden]  residual stream (replicated, written by the row owners)
     x      16-bit [max_m, hidden]  RMSNorm(h) for the next column-parallel GEMM
     amax   [tp, max_m, 2] u32      greedy candidates of the vocab shards
+    big    (only when ``max_big_m`` > 256) second header (per-row-block ready / expect / done words, job ticket) and
+           src 16-bit [max_big_m, hidden]: this rank's partial sums of a prefill-sized batch, read by every rank through
+           the multicast mapping; h and x are then sized for ``max_big_m`` rows
 """
 from __future__ import annotations
 
@@ -32,10 +35,14 @@ _lib.register_sigs({
     "fb_argmax_merge": [P, P, P, I, P, P, P, I, I, ULL, P],
     "fb_moe_combine_ar_norm": [P, P, P, P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
     "fb_comm_wait": [P, P],
-}, ["comm"])
+    "fb_gemm_ar_norm_big": [P, P, P, I, I, I, I, I, P, P, P, I, I, ULL, ULL, ULL, ULL, P, I, F, F, I, P],
+    "fb_ar_norm_big": [P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, ULL, P, I, F, F, I, P],
+}, ["comm", "comm_prefill"])
 OFF_CNT2, OFF_EXPECT = 128, 256      # arena header words the deferred all-gather wait reads (csrc/comm.cu)
 
 HEADER = 1024
+BIG_HEADER = (3 * 512 + 1) * 4      # ready / expect / done words of 512 row blocks + the job ticket (csrc/comm_prefill.cu)
+SMALL_M = 256                       # rows the latency-regime kernels take; above it the bandwidth-regime kernels run
 
 
 def _align(n, a=4096):
@@ -45,17 +52,22 @@ def _align(n, a=4096):
 class FusedComm:
     name = "fused-p2p"
 
-    def __init__(self, comm, hidden: int, max_m: int, max_n: int, dtype=torch.bfloat16, use_multicast: bool = True):
+    def __init__(self, comm, hidden: int, max_m: int, max_n: int, dtype=torch.bfloat16, use_multicast: bool = True,
+                 max_big_m: int = 0):
         import torch.distributed._symmetric_memory as symm_mem
 
         self.comm = comm
         self.rank, self.tp, self.device = comm.rank, comm.size, comm.device
         self.hidden, self.max_m, self.max_n, self.dtype = hidden, max_m, max(max_n, hidden), dtype
+        self.max_big_m = max_big_m if (max_big_m > SMALL_M and hidden <= 8192 and max_big_m <= 65536) else 0
+        rows = max(max_m, self.max_big_m)          # h / x hold whichever batch is larger
         self.off_part = _align(HEADER)
         self.off_h = _align(self.off_part + self.tp * max_m * self.max_n * 4)
-        self.off_x = _align(self.off_h + max_m * hidden * 2)
-        self.off_amax = _align(self.off_x + max_m * hidden * 2)
-        self.nbytes = _align(self.off_amax + self.tp * max_m * 8, 1 << 21)
+        self.off_x = _align(self.off_h + rows * hidden * 2)
+        self.off_amax = _align(self.off_x + rows * hidden * 2)
+        self.off_bighdr = _align(self.off_amax + self.tp * max_m * 8)
+        self.off_src = _align(self.off_bighdr + BIG_HEADER)
+        self.nbytes = _align(self.off_src + self.max_big_m * hidden * 2, 1 << 21)
         self.arena = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
         self.handle = symm_mem.rendezvous(self.arena, dist.group.WORLD)
         self.arena.zero_()
@@ -67,16 +79,26 @@ class FusedComm:
         if not use_multicast or os.environ.get("FB_DISABLE_MULTICAST", "0") == "1":
             mc = 0
         self.mc = mc
+        # The prefill-sized kernels move whole activations.  A multicast reduction load makes NVSwitch fetch the row from
+        # every rank, the requester included, so with two ranks it puts 3x the bytes of plain peer loads on the links
+        # (measured, 8192 x 4096 rows: reduce phase 159 us against 96 us); from four ranks on the in-switch sum moves fewer
+        # bytes than tp - 1 peer loads.  FB_BIG_MULTICAST=0 / 1 overrides.
+        big = os.environ.get("FB_BIG_MULTICAST", "auto")
+        self.big_mc = mc if (big == "1" or (big == "auto" and self.tp >= 4)) else 0
         self.name = "fused-nvls-multimem" if mc else "fused-p2p"
         self.local = ptrs[self.rank]
         assert self.local == self.arena.data_ptr()
-        self.h_buf = self.arena[self.off_h:self.off_h + max_m * hidden * 2].view(dtype).view(max_m, hidden)
-        self.x_buf = self.arena[self.off_x:self.off_x + max_m * hidden * 2].view(dtype).view(max_m, hidden)
+        self.h_buf = self.arena[self.off_h:self.off_h + rows * hidden * 2].view(dtype).view(rows, hidden)
+        self.x_buf = self.arena[self.off_x:self.off_x + rows * hidden * 2].view(dtype).view(rows, hidden)
         self.trace = False          # True: kernels stamp their phases (read back with read_trace)
 
     # ---------------------------------------------------------------------------------------------
     def usable(self, M: int, N: int) -> bool:
-        return 0 < M <= min(self.max_m, 256) and N == self.hidden and N % 8 == 0
+        return 0 < M <= max(min(self.max_m, SMALL_M), self.max_big_m) and N == self.hidden and N % 8 == 0
+
+    def _big(self, M: int) -> bool:
+        """Prefill-sized batch: the bandwidth-regime kernels (row blocks of 128 owned round-robin) take it."""
+        return M > min(self.max_m, SMALL_M)
 
     def load_h(self, h: torch.Tensor) -> torch.Tensor:
         """Place the (replicated) residual stream rows into the arena; returns the arena view."""
@@ -110,6 +132,15 @@ class FusedComm:
             return None
         wt = w.w if w.w.dtype == x.dtype else w.w.to(x.dtype)
         bias = w.bias if self.rank == 0 else None
+        if self._big(M):
+            if K % 64 != 0 or x.stride(1) != 1 or os.environ.get("FB_FUSED_PREFILL_GEMM", "1") == "0":
+                return None
+            rc = _lib.kernels().fb_gemm_ar_norm_big(_ptr(x), _ptr(wt), _ptr(bias), M, N, K, x.stride(0), wt.stride(0),
+                                                    ctypes.c_void_p(self.local), ctypes.c_void_p(self.big_mc), self.peers, self.rank, self.tp,
+                                                    self.off_bighdr, self.off_src, self.off_h, self.off_x, _ptr(ln_w),
+                                                    self._flags(has_residual, False), float(eps), float(unit_offset), dtype_code(x.dtype), _stream())
+            _lib.check(rc, "fb_gemm_ar_norm_big")
+            return self.h_buf[:M], self.x_buf[:M]
         rc = _lib.kernels().fb_gemm_ar_norm(_ptr(x), _ptr(wt), _ptr(bias), M, N, K, x.stride(0), wt.stride(0),
                                             ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
                                             self.off_part, self.off_h, self.off_x, _ptr(ln_w),
@@ -125,10 +156,17 @@ class FusedComm:
                 defer: bool = False):
         """Same as gemm_ar_norm for a partial sum computed elsewhere (any float dtype, ``[M, hidden]``)."""
         M, N = partial.shape
-        if not (0 < M <= self.max_m and N == self.hidden):
+        if not self.usable(M, N):
             return None
         if partial.dtype not in (torch.float32, self.dtype) or not partial.is_contiguous():
             partial = partial.to(self.dtype).contiguous()
+        if self._big(M):
+            rc = _lib.kernels().fb_ar_norm_big(_ptr(partial), 1 if partial.dtype == torch.float32 else 0, M, N, ctypes.c_void_p(self.local),
+                                               ctypes.c_void_p(self.big_mc), self.peers, self.rank, self.tp, self.off_bighdr, self.off_src,
+                                               self.off_h, self.off_x, _ptr(ln_w), self._flags(has_residual, False), float(eps),
+                                               float(unit_offset), dtype_code(self.dtype), _stream())
+            _lib.check(rc, "fb_ar_norm_big")
+            return self.h_buf[:M], self.x_buf[:M]
         rc = _lib.kernels().fb_ar_norm(_ptr(partial), 1 if partial.dtype == torch.float32 else 0, M, N, ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp,
                                        self.off_part, self.off_h, self.off_x, _ptr(ln_w),
                                        self._flags(has_residual, defer), float(eps),
@@ -143,7 +181,7 @@ class FusedComm:
         pushes it to the row owners, reduces over ranks, adds the residual, normalises and broadcasts.  One launch."""
         M, topk = pos.shape
         N = self.hidden
-        if not (0 < M <= self.max_m) or ys.shape[1] != N:
+        if not (0 < M <= min(self.max_m, SMALL_M)) or ys.shape[1] != N:
             return None
         rc = _lib.kernels().fb_moe_combine_ar_norm(_ptr(ys), _ptr(pos), _ptr(w), _ptr(add), topk, M, N, ctypes.c_void_p(self.local),
                                                    ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp, self.off_part, self.off_h,
@@ -182,15 +220,25 @@ class FusedComm:
         torch.cuda.synchronize()
         dist.barrier()
         self.arena[:HEADER].zero_()
+        self.arena[self.off_bighdr:self.off_bighdr + BIG_HEADER].zero_()
         torch.cuda.synchronize()
         dist.barrier()
 
 
-def try_create(comm, cfg, max_m: int, strict: bool = False, dtype=torch.bfloat16):
-    """Create the fused communicator; on failure return None (NCCL path) unless ``strict``."""
+def prefill_rows(engine_cfg) -> int:
+    """Largest token batch one forward pass of this engine can carry: a prefill chunk plus the decode rows mixed into it
+    (0 turns the bandwidth-regime kernels off: FB_FUSED_PREFILL=0)."""
+    if os.environ.get("FB_FUSED_PREFILL", "1") == "0":
+        return 0
+    return min(65536, int(engine_cfg.chunked_prefill_size) + int(engine_cfg.max_batch))
+
+
+def try_create(comm, cfg, max_m: int, strict: bool = False, dtype=torch.bfloat16, max_big_m: int = 0):
+    """Create the fused communicator; on failure return None (NCCL path) unless ``strict``.  ``max_big_m`` > 256 also
+    reserves the buffers of the prefill-sized (bandwidth-regime) kernels for that many token rows."""
     try:
         max_m = max(16, min(256, max_m))
-        return FusedComm(comm, cfg.hidden_size, max_m, cfg.hidden_size, dtype)
+        return FusedComm(comm, cfg.hidden_size, max_m, cfg.hidden_size, dtype, max_big_m=max_big_m)
     except Exception as e:  # symmetric memory unavailable (no P2P, old driver, ...)
         if strict:
             raise

@@ -60,6 +60,50 @@ def main():
         if own.start < M:
             assert (h2[own].float() - ref_h2[own].float()).abs().max().item() < 0.08
         assert (x2.float() - B.rmsnorm_ref(ref_h2, ln, 1e-5)[0].float()).abs().max().item() < 0.08
+    # prefill-sized batches: the bandwidth-regime kernels (row blocks of 128 owned round-robin, in-switch reduction when
+    # the multicast mapping exists).  Ragged last block, one block fewer than ranks own, narrow and wide hidden sizes.
+    for Hb, cases in ((1024, [(600, 512), (1024, 256), (257, 1024), (600, 512)]), (5120, [(300, 256)])):
+        big = symm.FusedComm(comm, Hb, 64, Hb, torch.bfloat16, use_multicast=use_mc, max_big_m=1024)
+        assert big.max_big_m == 1024
+        for it, (M, K) in enumerate(cases):
+            x_full = (torch.randn(M, K * world, device=dev) * 0.5).bfloat16()
+            w_full = (torch.randn(Hb, K * world, device=dev) * 0.03).bfloat16()
+            h0 = torch.randn(M, Hb, device=dev).bfloat16()
+            ln = (1 + 0.1 * torch.randn(Hb, device=dev)).bfloat16()
+            ref_h = (x_full.float() @ w_full.float().t() + h0.float()).bfloat16()
+            ref_x = B.rmsnorm_ref(ref_h, ln, 1e-5)[0]
+            xs = x_full[:, rank * K:(rank + 1) * K].contiguous()
+            ws = LinearWeight.from_dense(w_full[:, rank * K:(rank + 1) * K].contiguous())
+            big.load_h(h0)
+            r = big.gemm_ar_norm(ws, xs, ln, 1e-5)
+            assert r is not None, "fused prefill kernel refused the shape"
+            h, xn = r
+            torch.cuda.synchronize()
+            _lib.check_device_errors()
+            own = torch.zeros(M, dtype=torch.bool, device=dev)
+            for b0 in range(rank * 128, M, world * 128):
+                own[b0:b0 + 128] = True
+            eh = (h[own].float() - ref_h[own].float()).abs().max().item() if own.any() else 0.0
+            ex = (xn.float() - ref_x.float()).abs().max().item()
+            fro = ((xn.float() - ref_x.float()).norm() / ref_x.float().norm()).item()
+            assert eh < 0.1 and ex < 0.1 and fro < 1e-2, f"gemm_ar_norm_big mismatch H={Hb} it={it}: {eh} {ex} {fro}"
+            part = (torch.randn(M, Hb, device=dev) * (rank + 1)).bfloat16()
+            tot = part.float()
+            dist.all_reduce(tot)
+            ref_h2 = (tot + ref_h.float()).bfloat16()
+            h2, x2 = big.ar_norm(part, ln, 1e-5)
+            torch.cuda.synchronize()
+            _lib.check_device_errors()
+            if own.any():
+                assert (h2[own].float() - ref_h2[own].float()).abs().max().item() < 0.15
+            ref_x2 = B.rmsnorm_ref(ref_h2, ln, 1e-5)[0].float()
+            assert ((x2.float() - ref_x2).norm() / ref_x2.norm()).item() < 1e-2
+            # no norm weight: the summed rows themselves are broadcast
+            h3, x3 = big.ar_norm(part, None, 1e-5, has_residual=False)
+            torch.cuda.synchronize()
+            assert ((x3.float() - tot).norm() / tot.norm()).item() < 1e-2
+        comm.fused = fused
+        del big
     # argmax merge
     vals = torch.randn(17, device=dev) + (rank == 1) * 0.0
     ids = torch.arange(17, device=dev, dtype=torch.int32) + 1000 * rank
@@ -73,7 +117,7 @@ def main():
     # tiny model: TP group with the fused path (CUDA graph decode) vs the same model on one rank
     cfg = preset("tiny-llama")
     tp = TPInfo(rank, world, TPComm(rank, world, dev))
-    tp.comm.fused = symm.FusedComm(tp.comm, cfg.hidden_size, 16, cfg.hidden_size, torch.bfloat16, use_multicast=use_mc)
+    tp.comm.fused = symm.FusedComm(tp.comm, cfg.hidden_size, 16, cfg.hidden_size, torch.bfloat16, use_multicast=use_mc, max_big_m=1024)
     m = random_init(cfg, dev, torch.bfloat16, tp=tp, std=0.05)
     eng = LLMEngine(m, EngineConfig(max_batch=8, max_context=1024), num_pages=64)
     g = torch.Generator().manual_seed(1)
@@ -109,7 +153,7 @@ def main():
 
     cfgm = preset("tiny-qwen3-moe")
     tpm = TPInfo(rank, world, TPComm(rank, world, dev))
-    tpm.comm.fused = symm.FusedComm(tpm.comm, cfgm.hidden_size, 16, cfgm.hidden_size, torch.bfloat16, use_multicast=use_mc)
+    tpm.comm.fused = symm.FusedComm(tpm.comm, cfgm.hidden_size, 16, cfgm.hidden_size, torch.bfloat16, use_multicast=use_mc, max_big_m=1024)
     mm = random_init(cfgm, dev, torch.bfloat16, tp=tpm, ep=EPInfo.from_tp(tpm), std=0.05)
     assert mm.layers[0].mlp.experts.count == cfgm.num_experts // world
     om = LLMEngine(mm, EngineConfig(max_batch=8, max_context=1024), num_pages=64).generate(prompts, GenerationConfig(max_new_tokens=8, ignore_eos=True))
