@@ -620,11 +620,15 @@ def _name_seed(seed: int, name: str) -> int:
 
 
 def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | None = None, ep=None, seed: int = 0,
-                std: float = 0.02, wdtype: str = "auto", moe_wdtype: str | None = None, moe_device: str | None = None) -> DecoderModel:
+                std: float = 0.02, wdtype: str = "auto", moe_wdtype: str | None = None, moe_device: str | None = None,
+                expert_pool: int = 0) -> DecoderModel:
     """Build a model with N(0, std) weights and unit norm weights, sharded for this TP/EP rank.
 
     Every rank draws the full tensor from the same seed and keeps its shard, so a TP group is numerically
     a sharding of one model.  ``wdtype`` / ``moe_wdtype`` select weight quantisation (see ops.quant).
+    ``expert_pool`` > 0: of a layer's local experts only the first ``expert_pool`` are drawn from the generator, the others
+    are scaled copies of those (same storage size and traffic; spares the random-number passes for models with hundreds of
+    experts, where drawing 80 G values per rank takes minutes).
     """
     from ..loader.shard import finalize_model   # local import: loader depends on this module
 
@@ -697,7 +701,11 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
             # tensors are seeded by name, so only this rank's experts are drawn (with MoE tensor parallelism: all of them)
             for e in range(lo, hi):
                 for nm, shp in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
-                    mk(p + f"mlp.experts.{e}.{nm}.weight", shp)
+                    if expert_pool > 0 and e - lo >= expert_pool:
+                        base = raw[p + f"mlp.experts.{lo + (e - lo) % expert_pool}.{nm}.weight"]
+                        raw[p + f"mlp.experts.{e}.{nm}.weight"] = base * (1.0 + ((e - lo) // expert_pool) / 64.0)
+                    else:
+                        mk(p + f"mlp.experts.{e}.{nm}.weight", shp)
             if cfg.num_shared_experts:
                 SI = cfg.shared_expert_intermediate_size
                 sp = p + ("mlp.shared_expert." if cfg.shared_expert_gate else "mlp.shared_experts.")
