@@ -380,6 +380,41 @@ __global__ void silu_mul_kernel(const uint16_t* __restrict__ x, uint16_t* __rest
 }
 
 // ------------------------------------------------------------------------------------------------
+// act(gate) * up for the other gated MLPs (GeGLU of the Gemma family, ReGLU): ACT 1 = GELU tanh approximation, 2 = GELU (erf),
+// 3 = ReLU, 0 = SiLU.  Two layouts of x [M, 2I]: gate | up halves, or interleaved per 128 columns (64 gate, 64 up), the layout
+// the fused gate/up weights are stored in.  The reference runs these as separate Gelu / Mul launches
+// (src/devices/cuda/fastllm-cuda.cu GeluNew / MulTo kernels).
+// ------------------------------------------------------------------------------------------------
+template <int ACT>
+__device__ __forceinline__ float glu_act(float v) {
+  if (ACT == 1) return 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+  if (ACT == 2) return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
+  if (ACT == 3) return v > 0.f ? v : 0.f;
+  return v / (1.f + __expf(-v));
+}
+template <bool BF16, int ACT>
+__global__ void glu_act_kernel(const uint16_t* __restrict__ x, uint16_t* __restrict__ y, int M, int I, int ldx, int ldy, int interleaved) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)M * (I / 8);
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const int m = (int)(idx / (I / 8)), c = (int)(idx % (I / 8)) * 8;
+    const int gc = interleaved ? (c >> 6) * 128 + (c & 63) : c;
+    const int uc = interleaved ? gc + 64 : I + c;
+    const uint4 g = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + gc);
+    const uint4 u = *reinterpret_cast<const uint4*>(x + (size_t)m * ldx + uc);
+    const uint32_t gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      float2 a = unpack_16<BF16>(gs[k]), b = unpack_16<BF16>(us[k]);
+      o[k] = pack_16<BF16>(glu_act<ACT>(a.x) * b.x, glu_act<ACT>(a.y) * b.y);
+    }
+    *reinterpret_cast<uint4*>(y + (size_t)m * ldy + c) = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Embedding gather: out[m, :] = table[ids[m], :]
 // ------------------------------------------------------------------------------------------------
 __global__ void embedding_kernel(const int* __restrict__ ids, const uint16_t* __restrict__ table, uint16_t* __restrict__ out,
@@ -610,6 +645,27 @@ extern "C" int fb_silu_mul(const void* x, void* y, int M, int I, int ldx, int ld
   auto s = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == 1) launch_k(silu_mul_kernel<true>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
   else launch_k(silu_mul_kernel<false>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy);
+  return (int)cudaGetLastError();
+}
+
+// act: 0 SiLU, 1 GELU (tanh), 2 GELU (erf), 3 ReLU; interleaved != 0: gate / up alternate in blocks of 64 columns (I % 64 == 0)
+extern "C" int fb_glu_act(const void* x, void* y, int M, int I, int ldx, int ldy, int act, int interleaved, int dtype, void* stream) {
+  if (M <= 0) return 0;
+  if (I % 8 != 0 || act < 0 || act > 3 || (interleaved && I % 64 != 0) || (dtype != 0 && dtype != 1)) return -1;
+  const size_t total = (size_t)M * (I / 8);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+#define FB_GLU(A)                                                                                                                          \
+  if (dtype == 1) launch_k(glu_act_kernel<true, A>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy, interleaved); \
+  else launch_k(glu_act_kernel<false, A>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)x, (uint16_t*)y, M, I, ldx, ldy, interleaved);
+  switch (act) {
+    case 0: FB_GLU(0) break;
+    case 1: FB_GLU(1) break;
+    case 2: FB_GLU(2) break;
+    default: FB_GLU(3) break;
+  }
+#undef FB_GLU
   return (int)cudaGetLastError();
 }
 

@@ -420,23 +420,8 @@ class DecoderModel:
 
     @staticmethod
     def _glu(gu, act: str, interleaved: bool):
-        """``act(gate) * up`` for gated MLPs whose activation is not SiLU (GeGLU of the Gemma family, ...)."""
-        if interleaved:
-            n = gu.shape[-1]
-            t = gu.reshape(*gu.shape[:-1], n // 128, 2, 64)
-            g, u = t[..., 0, :].reshape(*gu.shape[:-1], n // 2), t[..., 1, :].reshape(*gu.shape[:-1], n // 2)
-        else:
-            g, u = gu.chunk(2, dim=-1)
-        gf = g.float()
-        if act in ("gelu_pytorch_tanh", "gelu_new", "gelu_fast"):
-            a = torch.nn.functional.gelu(gf, approximate="tanh")
-        elif act == "gelu":
-            a = torch.nn.functional.gelu(gf)
-        elif act == "relu":
-            a = torch.relu(gf)
-        else:
-            raise ValueError(f"unsupported MLP activation '{act}'")
-        return (a * u.float()).to(gu.dtype)
+        """``act(gate) * up`` for gated MLPs whose activation is not SiLU (GeGLU of the Gemma family, ...): one kernel."""
+        return B.glu_act(gu, act, interleaved)
 
     # -----------------------------------------------------------------------------------------------
     def _router_logits(self, lw: MLPWeights, x):

@@ -293,6 +293,41 @@ def silu_mul(x: torch.Tensor) -> torch.Tensor:
     return out.reshape(*x.shape[:-1], inter)
 
 
+GLU_ACTS = {"silu": 0, "swiglu": 0, "gelu_pytorch_tanh": 1, "gelu_new": 1, "gelu_fast": 1, "gelu_tanh": 1, "gelu": 2, "relu": 3}
+
+
+def glu_act_ref(x: torch.Tensor, act: str, interleaved: bool = False) -> torch.Tensor:
+    """PyTorch fp32 statement of ``act(gate) * up`` (both layouts)."""
+    if interleaved:
+        n = x.shape[-1]
+        t = x.reshape(*x.shape[:-1], n // 128, 2, 64)
+        g, u = t[..., 0, :].reshape(*x.shape[:-1], n // 2), t[..., 1, :].reshape(*x.shape[:-1], n // 2)
+    else:
+        g, u = x.chunk(2, dim=-1)
+    gf = g.float()
+    code = GLU_ACTS[act]
+    a = F.silu(gf) if code == 0 else F.gelu(gf, approximate="tanh") if code == 1 else F.gelu(gf) if code == 2 else torch.relu(gf)
+    return (a * u.float()).to(x.dtype)
+
+
+def glu_act(x: torch.Tensor, act: str, interleaved: bool = False) -> torch.Tensor:
+    """``act(gate) * up`` of a fused gate/up projection output ``[..., 2I]`` -> ``[..., I]``.  ``interleaved``: gate and up
+    alternate in blocks of 64 columns (the layout of the fused gate/up weights); else the gate half comes first."""
+    if act not in GLU_ACTS:
+        raise ValueError(f"unsupported MLP activation '{act}'")
+    inter = x.shape[-1] // 2
+    if not x.is_cuda or x.dtype not in (torch.float16, torch.bfloat16) or inter % 8 != 0 or (interleaved and inter % 64 != 0):
+        return glu_act_ref(x, act, interleaved)
+    x2 = x.reshape(-1, x.shape[-1])
+    if x2.stride(-1) != 1:
+        x2 = x2.contiguous()
+    out = torch.empty((x2.shape[0], inter), device=x.device, dtype=x.dtype)
+    rc = _lib.kernels().fb_glu_act(_ptr(x2), _ptr(out), x2.shape[0], inter, x2.stride(0), out.stride(0), GLU_ACTS[act],
+                                   1 if interleaved else 0, dtype_code(x.dtype), _stream())
+    _lib.check(rc, "fb_glu_act")
+    return out.reshape(*x.shape[:-1], inter)
+
+
 def embedding(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     if not table.is_cuda or table.dtype not in (torch.float16, torch.bfloat16):
         return F.embedding(ids.long(), table)

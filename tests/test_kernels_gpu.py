@@ -99,6 +99,19 @@ def test_rmsnorm(H):
     _close(y, yr, 3e-2, 2e-2, "rmsnorm+res")
 
 
+@pytest.mark.parametrize("act", ["gelu_pytorch_tanh", "gelu", "relu", "silu"])
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_glu_act(act, interleaved):
+    """GeGLU / ReGLU kernel (both gate/up layouts) against the fp32 PyTorch statement."""
+    torch.manual_seed(14)
+    for dt in (torch.bfloat16, torch.float16):
+        x = (torch.randn(37, 2 * 704, device=DEV) * 1.5).to(dt)
+        got = B.glu_act(x, act, interleaved)
+        ref = B.glu_act_ref(x.float(), act, interleaved)
+        assert got.shape == (37, 704) and got.dtype == dt
+        _close(got, ref, 2e-2, 2e-2, f"glu_act {act} {interleaved}", fro=6e-3)
+
+
 def test_silu_embedding_argmax():
     torch.manual_seed(4)
     dt = torch.bfloat16
