@@ -111,7 +111,7 @@ def build_cpu(force: bool = False) -> Path:
         objs.append(obj)
         if force or _newer(cpu / "cpu_kernels.cpp", headers, obj):
             jobs.append(([*base, *isa, f"-DFB_ISA_SUFFIX={suffix}", "-c", str(cpu / "cpu_kernels.cpp"), "-o", str(obj)], None))
-    for name in ("cpu_ops", "cpu_model"):
+    for name in ("cpu_ops", "cpu_model", "numa_moe"):
         obj = OBJ / f"{name}.o"
         objs.append(obj)
         if force or _newer(cpu / f"{name}.cpp", headers, obj):

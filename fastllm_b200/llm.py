@@ -318,7 +318,8 @@ class model:
             md = _settings.get("moe_device_map")
             self.torch_model = hf_loader.load_model(path, device=dev, wdtype=dtype or "auto", moe_wdtype=moe_dtype or None, tp=tp,
                                                     moe_device=("disk" if (isinstance(md, str) and md.startswith("disk")) else
-                                                                "cpu" if (isinstance(md, str) and md.startswith(("cpu", "numa"))) else None),
+                                                                "numa" if (isinstance(md, str) and md.startswith("numa")) else
+                                                                "cpu" if (isinstance(md, str) and md.startswith("cpu")) else None),
                                                     moe_device_layers=int(_settings.get("moe_device_layers", -1) or -1),
                                                     dtype_config=dtype_config or None, lora=lora or None,
                                                     device_map=_settings["device_map"] if isinstance(_settings.get("device_map"), dict) else None)

@@ -239,6 +239,8 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
 
     ``moe_device="cpu"`` keeps the routed experts (of the first ``moe_device_layers`` layers, all when negative) in host
     memory and runs them on the native CPU backend -- the reference's ``--moe_device cpu`` hybrid placement.
+    ``moe_device="numa"`` is the host placement with every expert cut across the memory nodes, each slice in memory its
+    node's pinned threads allocated (``csrc/cpu/numa_moe.cpp``).
     ``moe_device="disk"`` is the same placement with the expert matrices left in the checkpoint's file mapping (no copy into
     anonymous memory: pages come from the SSD through the page cache as the router touches an expert), for models larger than
     RAM -- the reference's disk device (src/devices/disk/diskdevice.cpp:45-49).  It applies to 16/32-bit checkpoints whose
@@ -277,7 +279,8 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
     m = DecoderModel(cfg, device, dtype, tp, ep)
     m.moe_disk = moe_device == "disk"
     ck.want_spans = m.moe_disk
-    m.moe_device, m.moe_device_layers = ("cpu" if m.moe_disk else moe_device), moe_device_layers
+    m.moe_numa = moe_device == "numa"          # host placement with every expert cut across the memory nodes
+    m.moe_device, m.moe_device_layers = ("cpu" if (m.moe_disk or m.moe_numa) else moe_device), moe_device_layers
     if device_map and len(set(map(str, staged))) > 1:
         m.layer_devices = staged
 

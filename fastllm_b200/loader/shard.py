@@ -220,6 +220,7 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
                 t.pop(p + f"mlp.experts.{e}.{nm}.weight", None)
         f.experts = MOE.ExpertWeights(cfg.num_experts, lo, gu, dn)
         f.experts.host = host
+        f.experts.numa = bool(host and getattr(m, "moe_numa", False))
         sp = "mlp.shared_expert." if g("mlp.shared_expert.gate_proj.weight") is not None else "mlp.shared_experts."
         if g(sp + "gate_proj.weight") is not None:
             f.shared_gate_up = _gate_up(m, _shard_rows(g(sp + "gate_proj.weight"), r, n), _shard_rows(g(sp + "up_proj.weight"), r, n), wdtype)

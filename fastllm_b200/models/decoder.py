@@ -619,7 +619,8 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
 
     tp = tp or TPInfo()
     m = DecoderModel(cfg, device, dtype, tp, ep)
-    m.moe_device = moe_device         # "cpu": routed experts stay in host memory (hybrid placement)
+    m.moe_numa = moe_device == "numa"
+    m.moe_device = "cpu" if m.moe_numa else moe_device         # "cpu": routed experts stay in host memory (hybrid placement)
     dev = m.device
     gen = torch.Generator(device=dev)
     gen.manual_seed(seed)

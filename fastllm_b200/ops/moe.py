@@ -10,6 +10,8 @@ from __future__ import annotations
 
 import ctypes
 
+import os
+
 import torch
 import torch.nn.functional as F
 
@@ -171,15 +173,28 @@ def _moe_forward_host(x, idx, wts, experts: ExpertWeights):
         L.fbcpu_moe.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
                                 ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         experts._host_arrays = (G, D, keep)
+        L.fbnuma_create.restype = ctypes.c_void_p
+        L.fbnuma_create.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+        L.fbnuma_destroy.argtypes = [ctypes.c_void_p]
+        L.fbnuma_moe.restype = ctypes.c_int
+        L.fbnuma_moe.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                 ctypes.c_int, ctypes.c_void_p]
+        if getattr(experts, "numa", False) and experts.act == "swiglu":
+            # every expert cut across the memory nodes; the slices are copies made by the nodes' own threads
+            experts._numa_handle = L.fbnuma_create(G, D, n, int(os.environ.get("FB_NUMA_THREADS_PER_NODE", "0")))
     G, D, _ = experts._host_arrays
     T, H = x.shape
     xh = x.detach().to("cpu", torch.float32).contiguous()
     ih = idx.detach().to("cpu", torch.int32).contiguous()
     wh = wts.detach().to("cpu", torch.float32).contiguous()
     out = torch.zeros((T, H), dtype=torch.float32)
-    rc = L.fbcpu_moe(xh.data_ptr(), T, H, ih.data_ptr(), wh.data_ptr(), idx.shape[1], experts.first, experts.count, G, D, out.data_ptr())
+    nh = getattr(experts, "_numa_handle", None)
+    if nh:
+        rc = L.fbnuma_moe(ctypes.c_void_p(nh), xh.data_ptr(), T, H, ih.data_ptr(), wh.data_ptr(), idx.shape[1], experts.first, out.data_ptr())
+    else:
+        rc = L.fbcpu_moe(xh.data_ptr(), T, H, ih.data_ptr(), wh.data_ptr(), idx.shape[1], experts.first, experts.count, G, D, out.data_ptr())
     if rc != 0:
-        raise RuntimeError(f"fbcpu_moe failed ({rc})")
+        raise RuntimeError(f"host MoE failed ({rc})")
     return out.to(x.device, x.dtype)
 
 

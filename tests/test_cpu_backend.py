@@ -1,4 +1,7 @@
 """Native CPU backend against the plain PyTorch definition of every operator (both ISA builds run where the host has them)."""
+import ctypes
+import os
+
 import pytest
 import torch
 
@@ -157,3 +160,38 @@ def test_host_expert_ffn_matches_operator_path(wd):
     got = MOE.moe_forward(x, idx, wts, ex)
     ex.host = False
     assert torch.allclose(got, ref, atol=2e-4, rtol=1e-3)
+
+
+@pytest.mark.parametrize("wd", ["auto", "int8", "int4g128"])
+def test_numa_expert_placement_matches_single_node(wd, monkeypatch):
+    """Experts cut across two (emulated) memory nodes with pinned thread teams: same result as the single-node host path,
+    bit for bit (the row kernels and the summation order per token are the same)."""
+    from fastllm_b200.models.config import preset
+    from fastllm_b200.models.decoder import random_init
+    from fastllm_b200.ops import cpu
+    from fastllm_b200.ops import moe as MOE
+
+    ncpu = len(os.sched_getaffinity(0))
+    cpus = sorted(os.sched_getaffinity(0))
+    half = max(1, ncpu // 2)
+    groups = [cpus[:half], cpus[half:] or cpus[:half]]
+    monkeypatch.setenv("FB_NUMA_NODES", ";".join(",".join(map(str, g)) for g in groups))
+    assert cpu.lib().fbnuma_node_count() == 2
+    m = random_init(preset("tiny-qwen3-moe"), "cpu", torch.float32, std=0.05, moe_wdtype=wd)
+    ex = m.layers[0].mlp.experts
+    torch.manual_seed(9)
+    for T in (1, 13, 70):
+        x = torch.randn(T, m.cfg.hidden_size)
+        logits = torch.randn(T, m.cfg.num_experts)
+        idx, wts = MOE.route_topk(logits, None, 2, 0, True)
+        ex.host, ex.numa = True, False
+        ex._host_arrays = None
+        ref = MOE.moe_forward(x, idx, wts, ex)
+        ex.numa = True
+        ex._host_arrays = None
+        got = MOE.moe_forward(x, idx, wts, ex)
+        assert getattr(ex, "_numa_handle", None)
+        assert torch.equal(got, ref), (wd, T, (got - ref).abs().max())
+        cpu.lib().fbnuma_destroy(ctypes.c_void_p(ex._numa_handle))
+        ex._numa_handle = None
+    ex.host = ex.numa = False
