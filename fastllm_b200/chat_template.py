@@ -1,9 +1,10 @@
 """Chat-template rendering (Hugging Face ``chat_template`` Jinja dialect).
 
 The reference ships its own Jinja lexer/parser/evaluator in C++ (include/template.h, src/template.cpp) so
-that templates work without Python; this layer lives in Python, so the sandboxed ``jinja2`` environment the
-templates were written for does the evaluation, with the helpers HF templates rely on (``raise_exception``,
-``strftime_now``, ``tojson``).  Without a template a ChatML layout is used.
+that templates work without third-party packages; here ``template_engine`` is that evaluator (lexer, parser,
+interpreter, the helpers HF templates rely on: ``raise_exception``, ``strftime_now``, ``tojson``, ``namespace``).
+A template that uses a construct it does not know is handed to the sandboxed ``jinja2`` environment when that
+package is installed.  Without a template a ChatML layout is used.
 """
 from __future__ import annotations
 
@@ -49,8 +50,24 @@ def _environment():
 def render(template: str | None, messages, add_generation_prompt: bool = True, tools=None, **kw) -> str:
     if not template:
         return _fallback(messages, add_generation_prompt)
+    from . import template_engine
+
+    try:
+        t = _compiled.get(template)
+        if t is None:
+            t = _compiled[template] = template_engine.Template(template)
+            if len(_compiled) > 32:
+                _compiled.pop(next(iter(_compiled)))
+        return t.render(messages=messages, add_generation_prompt=add_generation_prompt, tools=tools, **kw)
+    except template_engine.TemplateError as e:
+        own_error = e
+    except (TypeError, ValueError, KeyError, IndexError, AttributeError) as e:
+        own_error = e
     try:
         t = _environment().from_string(template)
     except ImportError:
-        return _fallback(messages, add_generation_prompt)
+        raise own_error
     return t.render(messages=messages, add_generation_prompt=add_generation_prompt, tools=tools, **kw)
+
+
+_compiled: dict = {}
