@@ -126,7 +126,8 @@ class ModelRunner:
             return False        # several window lengths / a second RoPE base for local layers: PyTorch evaluation
         if not c.use_mla and c.head_dim != 128:
             return False        # the tensor-core attention kernels cover head_dim 128; other widths run the PyTorch evaluation
-        if c.has_linear_attn and not (c.lin_k_dim == 128 and c.lin_v_dim == 128 and self.model.dtype in (torch.float16, torch.bfloat16)):
+        if c.has_linear_attn and not (c.lin_kind == "gdn" and c.lin_k_dim == 128 and c.lin_v_dim == 128
+                                      and self.model.dtype in (torch.float16, torch.bfloat16)):
             return False        # delta-rule state shapes outside the recurrent kernel run the PyTorch evaluation
         if c.is_moe:
             # the per-expert fallback loop synchronises with the host; graphs need every MoE layer on the grouped kernels

@@ -114,7 +114,7 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         return f_(p + name) if f_ else base_mw
 
     if cfg.layer_is_linear(i):
-        lw.lin = build_linear_attn(m, g, a.ln, W)
+        lw.lin = build_linear_attn(m, g, a.ln, W, i)
     elif cfg.use_mla:
         nope, rope, vd, lora = cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim, cfg.kv_lora_rank
         Hl = cfg.num_heads // n
@@ -172,6 +172,9 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         qn, kn = g("self_attn.q_norm.weight"), g("self_attn.k_norm.weight")
         if qn is None:
             qn, kn = g("self_attn.query_layernorm.weight"), g("self_attn.key_layernorm.weight")     # Hunyuan names
+        if cfg.qk_norm_full and qn is not None and n > 1:
+            # one norm over all heads: every rank keeps the weights of its own heads (the squares are summed across ranks)
+            qn, kn = qn[r * Hq_l * D:(r + 1) * Hq_l * D], kn[kv0 * D:(kv0 + Hkv_l) * D]
         a.q_norm, a.k_norm = _to(qn, m), _to(kn, m)
         sk = g("self_attn.sinks")
         if sk is not None:
@@ -242,7 +245,7 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
     m.layers[i] = lw
 
 
-def build_linear_attn(m, g, ln, W):
+def build_linear_attn(m, g, ln, W, layer_idx: int = 0):
     """Gated-DeltaNet weights of one layer for this rank.  Accepts the grouped layout of Qwen3-Next (``in_proj_qkvz`` /
     ``in_proj_ba``, rows grouped per key head) and the plain layout of Qwen3.5 (``in_proj_qkv``, ``in_proj_z``, ``in_proj_b``,
     ``in_proj_a``); heads are sharded over the tensor-parallel ranks by key head."""
@@ -254,6 +257,19 @@ def build_linear_attn(m, g, ln, W):
     rep = Hv // Hk
     la = LinearAttnWeights()
     la.ln = ln
+    if cfg.lin_kind == "lightning":
+        # MiniMax-Text-01 / M1: fused projection with rows [head][q | k | v], output gate, norm over all heads; by head over ranks
+        from ..ops.linear_attn import lightning_slopes
+
+        Hl, D = Hv // n, Dv
+        la.kind = "lightning"
+        la.in_proj = _lin(m, g("self_attn.qkv_proj.weight")[r * Hl * 3 * D:(r + 1) * Hl * 3 * D], W("self_attn.qkv_proj.weight"))
+        la.gate = _lin(m, g("self_attn.output_gate.weight")[r * Hl * D:(r + 1) * Hl * D], W("self_attn.output_gate.weight"))
+        la.norm_w = _to(g("self_attn.norm.weight")[r * Hl * D:(r + 1) * Hl * D], m)
+        la.out = _lin(m, g("self_attn.out_proj.weight")[:, r * Hl * D:(r + 1) * Hl * D], W("self_attn.out_proj.weight"))
+        la.slope = lightning_slopes(Hv, layer_idx, cfg.num_layers)[r * Hl:(r + 1) * Hl].to(m.device).contiguous()
+        la.Hk, la.Hv, la.Dk, la.Dv = Hl, Hl, D, D
+        return la
     if g("linear_attn.in_proj_qkvz.weight") is not None:
         w = g("linear_attn.in_proj_qkvz.weight")
         Hd = w.shape[-1]

@@ -78,6 +78,12 @@ class ModelConfig:
     lin_k_dim: int = 0
     lin_v_dim: int = 0
     lin_conv_kernel: int = 4
+    lin_kind: str = "gdn"                  # "gdn" Gated DeltaNet | "lightning" decayed linear attention (MiniMax-Text-01 / M1)
+    lin_block: int = 256                   # lightning attention: block length of the chunked evaluation
+    # DeepNorm-style residual (MiniMax-Text-01 / M1): the block input is normalised first and the NORMALISED rows are the
+    # residual: y = alpha * norm(x) + beta * f(norm(x)).  (alpha, beta) for full-attention layers, linear layers, MLPs.
+    postnorm_residual: bool = False
+    resid_factors: tuple = (1.0, 1.0, 1.0, 1.0, 1.0, 1.0)
     attn_output_gate: bool = False         # q_proj also produces a per-head gate; the attention output is multiplied by its sigmoid
     mlp_only_layers: list = field(default_factory=list)   # layers that keep a dense MLP in an otherwise sparse model
     # bookkeeping
@@ -113,7 +119,7 @@ class ModelConfig:
 LLAMA_LIKE = {"llama", "mistral", "internlm", "internlm3", "baichuan", "yi", "deepseek", "qwen2", "qwen3", "minicpm",
               "phi3", "glm4", "glm", "gemma", "gemma2", "ernie4_5", "hunyuan", "telechat", "internlm2", "qwen"}
 MOE_LIKE = {"qwen3_moe", "qwen2_moe", "moe", "mixtral", "deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32",
-            "glm4_moe", "ernie4_5_moe", "minimax_m2", "hunyuan_moe", "gpt_oss", "PanguProMoE"}
+            "glm4_moe", "ernie4_5_moe", "minimax_m2", "minimax", "hunyuan_moe", "gpt_oss", "PanguProMoE"}
 
 
 def _eos_list(v) -> list:
@@ -267,6 +273,32 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.num_experts_per_tok = g("num_experts_per_tok", 2)
         c.moe_intermediate_size = c.intermediate_size
         c.norm_topk_prob = True
+    elif mt in ("minimax", "minimax_text_01", "minimax_m1"):
+        # MiniMax-Text-01 / M1: lightning (decayed linear) attention layers with a softmax-attention layer every few layers,
+        # every layer MoE (softmax scores, renormalised top-k), DeepNorm-style residuals on normalised rows
+        # (reference: src/models/minimax.cpp)
+        c.num_experts = g("num_local_experts", g("num_experts", 0)) or 0
+        c.num_experts_per_tok = g("num_experts_per_tok", 2)
+        c.moe_intermediate_size = c.intermediate_size
+        c.norm_topk_prob = True
+        lt = g("layer_types")
+        if lt is None:
+            at = g("attn_type_list")                      # original checkpoints: 0 = lightning, 1 = softmax attention
+            lt = (["full_attention" if int(t) == 1 else "linear_attention" for t in at] if at
+                  else ["full_attention" if (i % 2) else "linear_attention" for i in range(c.num_layers)])
+        c.layer_types = list(lt)
+        c.lin_kind = "lightning"
+        c.lin_block = int(g("block_size", 256) or 256)
+        c.lin_num_k_heads = c.lin_num_v_heads = c.num_heads
+        c.lin_k_dim = c.lin_v_dim = c.head_dim
+        c.lin_conv_kernel = 1
+        c.postnorm_residual = True
+        c.resid_factors = tuple(float(g(k, g(k2, 1.0)) or 1.0) for k, k2 in (
+            ("full_attn_alpha_factor", "layernorm_full_attention_alpha"), ("full_attn_beta_factor", "layernorm_full_attention_beta"),
+            ("linear_attn_alpha_factor", "layernorm_linear_attention_alpha"), ("linear_attn_beta_factor", "layernorm_linear_attention_beta"),
+            ("mlp_alpha_factor", "layernorm_mlp_alpha"), ("mlp_beta_factor", "layernorm_mlp_beta")))
+        if g("rotary_dim") and not prf:
+            c.rotary_dim = int(g("rotary_dim"))
     elif mt == "minimax_m2":
         # GQA + full-width QK norm + partial rotary; every layer MoE: sigmoid scores, selection bias, renormalised top-k
         # (reference: src/models/minimax_m2.cpp)
@@ -367,6 +399,17 @@ def preset(name: str) -> ModelConfig:
                                  moe_intermediate_size=128, shared_expert_intermediate_size=128, linear_num_key_heads=2,
                                  linear_num_value_heads=4, linear_key_head_dim=32, linear_value_head_dim=32, full_attention_interval=2,
                                  max_position_embeddings=2048, rms_norm_eps=1e-6, eos_token_id=511))
+    if name == "tiny-minimax-m1":        # lightning-attention / softmax-attention hybrid with DeepNorm-style residual factors
+        return from_hf_dict(dict(model_type="minimax", vocab_size=512, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, intermediate_size=256, num_local_experts=8, num_experts_per_tok=2,
+                                 block_size=32, layer_types=["linear_attention", "full_attention"] * 2,
+                                 full_attn_alpha_factor=1.5, full_attn_beta_factor=0.8, linear_attn_alpha_factor=1.25,
+                                 linear_attn_beta_factor=0.9, mlp_alpha_factor=1.1, mlp_beta_factor=0.7,
+                                 max_position_embeddings=2048, rms_norm_eps=1e-5, eos_token_id=511))
+    if name == "tiny-minimax-m2":        # full-width QK norm, partial rotary, sigmoid router with selection bias
+        return from_hf_dict(dict(model_type="minimax_m2", vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, intermediate_size=256, num_local_experts=8, num_experts_per_tok=2,
+                                 rotary_dim=32, max_position_embeddings=2048, rms_norm_eps=1e-6, eos_token_id=511))
     if name == "small-qwen3-next":       # Qwen3-Next layer geometry (128-wide delta-rule heads, 128-wide attention heads) on a small body
         return from_hf_dict(dict(model_type="qwen3_next", vocab_size=1024, hidden_size=512, num_hidden_layers=4, num_attention_heads=4,
                                  num_key_value_heads=2, head_dim=128, intermediate_size=1024, num_experts=8, num_experts_per_tok=2,

@@ -93,6 +93,11 @@ class LinearAttnWeights:
         self.norm_w = None        # [Dv]
         self.out: LinearWeight | None = None
         self.Hk = self.Hv = self.Dk = self.Dv = 0
+        # lightning attention (kind == "lightning"): in_proj is the fused q/k/v projection (per head q | k | v), gate the
+        # output-gate projection, slope the per-head decay rates, norm_w spans all of this rank's heads
+        self.kind = "gdn"
+        self.gate: LinearWeight | None = None
+        self.slope = None
 
 
 class MLPWeights:
@@ -139,6 +144,7 @@ class DecoderModel:
         self.kv_replicas = max(1, self.tp.size // cfg.num_kv_heads)
         self._rope = None
         self._fused_active = False
+        self._beta = 1.0                  # scale of the running sub-layer's contribution (DeepNorm-style residual models)
         self.layer_devices = None          # per-layer devices for the layer-split placement (None: everything on self.device)
         self.rope_mode = {"neox": A.ROPE_NEOX, "interleaved": A.ROPE_INTERLEAVED, "none": A.ROPE_NONE}[cfg.rope_mode]
         self.rot_dim = cfg.qk_rope_head_dim if cfg.use_mla else (cfg.rotary_dim or cfg.head_dim)
@@ -194,6 +200,8 @@ class DecoderModel:
         """Per linear-attention layer: (convolution window pool, delta-rule state pool) shapes for ``n_slots`` requests."""
         c = self.cfg
         Hk, Hv = c.lin_num_k_heads // self.tp.size, c.lin_num_v_heads // self.tp.size
+        if c.lin_kind == "lightning":          # no convolution window; one [D, D] state per head
+            return (n_slots, 0, 0), (n_slots, Hv, c.lin_k_dim, c.lin_v_dim)
         C = 2 * Hk * c.lin_k_dim + Hv * c.lin_v_dim
         return (n_slots, C, c.lin_conv_kernel - 1), (n_slots, Hv, c.lin_k_dim, c.lin_v_dim)
 
@@ -272,6 +280,8 @@ class DecoderModel:
 
         c = self.cfg
         conv_state, rec_state = state
+        if lw.kind == "lightning":
+            return self._lightning_attention(lw, x, fb, rec_state, residual, next_ln, consumer)
         kd, vd = lw.Hk * lw.Dk, lw.Hv * lw.Dv
         C = 2 * kd + vd
         proj = lw.in_proj(x)                                   # [T, C + vd + 2 Hv]
@@ -289,6 +299,29 @@ class DecoderModel:
             core = L.rmsnorm_gated(o, z.reshape(T, lw.Hv, lw.Dv), lw.norm_w, c.rms_eps).reshape(T, vd)
         return self._row_parallel_norm(lw.out, core, residual, next_ln, consumer=consumer)
 
+    def _lightning_attention(self, lw: LinearAttnWeights, x, fb: ForwardBatch, rec_state, residual, next_ln, consumer=None):
+        """Lightning attention layer of MiniMax-Text-01 / M1: SiLU on the fused q/k/v projection, decayed linear attention
+        over the request's ``[H, D, D]`` state, RMSNorm over all heads, sigmoid output gate, output projection
+        (reference: src/models/minimax.cpp)."""
+        from ..ops import linear_attn as L
+
+        c = self.cfg
+        T = x.shape[0]
+        H, D = lw.Hv, lw.Dv
+        qkv = torch.nn.functional.silu(lw.in_proj(x).float()).reshape(T, H, 3 * D)
+        q, k, v = qkv[..., :D], qkv[..., D:2 * D], qkv[..., 2 * D:]
+        if fb.is_decode:
+            o = L.lightning_decode(q, k, v, lw.slope, rec_state, fb.state_slots)
+        else:
+            o = L.lightning_attention(q, k, v, lw.slope, rec_state, fb.cu_q_host, fb.state_slots_host, c.lin_block)
+        o = o.reshape(T, H * D)
+        ss = o.pow(2).sum(-1, keepdim=True)
+        if self.tp.size > 1:                  # the norm spans all heads: the ranks add up their heads' squares
+            ss = self.tp.all_reduce(ss.contiguous(), None)
+        o = o * torch.rsqrt(ss / (c.num_heads * D) + c.rms_eps) * lw.norm_w.float()
+        core = (torch.sigmoid(lw.gate(x).float()) * o).to(x.dtype)
+        return self._row_parallel_norm(lw.out, core, residual, next_ln, consumer=consumer)
+
     def _attention_general(self, lw: AttentionWeights, qkv, fb: ForwardBatch, kv):
         """Attention for the less common variants (sliding window, sinks, logit soft-capping, norm after RoPE)."""
         c = self.cfg
@@ -298,10 +331,17 @@ class DecoderModel:
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
         q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
         norm = lambda t, w: A._head_norm_ref(t, w, c.rms_eps, c.norm_unit_offset) if w is not None else t
-        if c.qk_norm_full:           # one norm over the whole projection (all heads of this rank = all heads: one rank only)
-            if self.tp.size != 1:
-                raise NotImplementedError("full-width QK norm needs all heads on one rank")
-            norm = lambda t, w: A._head_norm_ref(t.reshape(T, 1, -1), w, c.rms_eps, c.norm_unit_offset).reshape(t.shape) if w is not None else t
+        if c.qk_norm_full:           # one norm over the whole projection (all heads of all ranks)
+            def norm(t, w, total_heads=None):
+                if w is None:
+                    return t
+                tf = t.reshape(T, -1).float()
+                ss = tf.pow(2).sum(-1, keepdim=True)
+                heads = t.shape[1]
+                if self.tp.size > 1:     # this rank holds some of the heads: the ranks add up their squares
+                    ss = self.tp.all_reduce(ss.contiguous(), None)
+                    heads = heads * self.tp.size
+                return (tf * torch.rsqrt(ss / (heads * D) + c.rms_eps) * (w.float() + c.norm_unit_offset)).reshape(t.shape).to(t.dtype)
         if not c.qk_norm_after_rope:
             q, k = norm(q, lw.q_norm), norm(k, lw.k_norm)
         q = A.apply_rope_ref(q, fb.positions, cos, sin, self.rope_mode, self.rot_dim)
@@ -360,6 +400,8 @@ class DecoderModel:
         all-gather to land: that wait moves into the consumer's GEMM, behind its weight prefetch.
         """
         c = self.cfg
+        if self._beta != 1.0:            # DeepNorm-style residual: the sub-layer's contribution is scaled (linear in x)
+            x = x * self._beta
         if post_ln is not None:          # sandwich norm: normalise the sub-layer output, then add it to the residual stream
             y = self._norm(self._row_parallel(w, x, None), post_ln)
             h = h + y
@@ -448,9 +490,13 @@ class DecoderModel:
         idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
                                   0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
                                   c.routed_scaling_factor)
+        if self._beta != 1.0:
+            wts = wts * self._beta
         shared = None
         if lw.shared_gate_up is not None:
             shared = lw.shared_down(lw.shared_gate_up(x, swiglu=True))
+            if self._beta != 1.0:
+                shared = shared * self._beta
             if lw.shared_gate is not None:
                 shared = shared * torch.sigmoid(torch.matmul(x.float(), lw.shared_gate.float().t())).to(shared.dtype)
         if self._fused_active and lw.experts.stacked is not None and not self.tp.comm.fused._big(x.shape[0]):
@@ -479,7 +525,8 @@ class DecoderModel:
             if native is not None:
                 return native.forward(fb, kv_caches)
         fused = self.tp.comm.fused if (self.tp.size > 1 and self.tp.comm is not None) else None
-        self._fused_active = bool(fused is not None and self.on_cuda and fused.usable(T, c.hidden_size) and not c.post_norms)
+        self._fused_active = bool(fused is not None and self.on_cuda and fused.usable(T, c.hidden_size) and not c.post_norms
+                                  and not c.postnorm_residual)
         if fb.is_decode and self.on_cuda and fb.decode_ws is not None and not fb.decode_planned:
             fb.decode_ws.plan(fb.kv_lens)
             fb.decode_planned = True
@@ -494,10 +541,18 @@ class DecoderModel:
         for i, lw in enumerate(self.layers):
             # the projection that reads each fused collective's output first (it can take over the all-gather wait)
             mlp_first = lw.mlp.gate_up if lw.mlp.experts is None else None
+            if c.postnorm_residual:
+                # y = alpha * norm(x) + beta * f(norm(x)): the normalised rows are the residual
+                fa, fbeta, la, lbeta, ma, mbeta = c.resid_factors
+                alpha, self._beta = (la, lbeta) if lw.lin is not None else (fa, fbeta)
+                h = x * alpha if alpha != 1.0 else x
             if lw.lin is not None:
                 h, x = self._linear_attention(lw.lin, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
             else:
                 h, x = self._attention(lw.attn, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
+            if c.postnorm_residual:
+                self._beta = mbeta
+                h = x * ma if ma != 1.0 else x
             if i + 1 < n_layers:
                 nl = self.layers[i + 1]
                 next_ln = nl.lin.ln if nl.lin is not None else nl.attn.ln
@@ -507,6 +562,7 @@ class DecoderModel:
                 next_ln = self.final_norm
                 nxt = self.lm_head if fb.logit_rows is None else None
             h, x = self._mlp(lw.mlp, x, h, i, next_ln, nxt)
+        self._beta = 1.0
         # x is RMSNorm(h) with the final norm weight (row-wise, so selecting rows afterwards is equivalent)
         if fb.logit_rows is not None:
             B.flush_pending_wait()
@@ -642,7 +698,13 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
         p = f"model.layers.{i}."
         ones(p + "input_layernorm.weight", H)
         ones(p + "post_attention_layernorm.weight", H)
-        if cfg.layer_is_linear(i):
+        if cfg.layer_is_linear(i) and cfg.lin_kind == "lightning":
+            HD = cfg.num_heads * cfg.head_dim
+            mk(p + "self_attn.qkv_proj.weight", (3 * HD, H))
+            mk(p + "self_attn.output_gate.weight", (HD, H))
+            ones(p + "self_attn.norm.weight", HD)
+            mk(p + "self_attn.out_proj.weight", (H, HD))
+        elif cfg.layer_is_linear(i):
             Hk, Hv, Dk, Dv = cfg.lin_num_k_heads, cfg.lin_num_v_heads, cfg.lin_k_dim, cfg.lin_v_dim
             lp = p + "linear_attn."
             mk(lp + "in_proj_qkvz.weight", (2 * Hk * Dk + 2 * Hv * Dv, H))
@@ -676,8 +738,8 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
                 mk(p + "self_attn.k_proj.bias", (cfg.num_kv_heads * D,))
                 mk(p + "self_attn.v_proj.bias", (cfg.num_kv_heads * D,))
             if cfg.qk_norm:
-                ones(p + "self_attn.q_norm.weight", D)
-                ones(p + "self_attn.k_norm.weight", D)
+                ones(p + "self_attn.q_norm.weight", cfg.num_heads * D if cfg.qk_norm_full else D)
+                ones(p + "self_attn.k_norm.weight", cfg.num_kv_heads * D if cfg.qk_norm_full else D)
         if cfg.layer_is_moe(i):
             mk(p + "mlp.gate.weight", (cfg.num_experts, H))
             if cfg.router_bias:

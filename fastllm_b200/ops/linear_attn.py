@@ -198,3 +198,53 @@ def gated_delta_decode(mixed, a, b, z, A_log, dt_bias, norm_w, eps, rec_state, s
     rec_state[sl] = S
     o = (S * qf[..., None]).sum(2).to(mixed.dtype)                     # [B, Hv, Dv]
     return rmsnorm_gated(o, z.reshape(B, Hv, Dv), norm_w, eps).reshape(B, Hv * Dv)
+
+
+# ---------------------------------------------------------------------------------------------------
+# Lightning attention (MiniMax-Text-01 / M1): linear attention with a fixed per-head exponential decay
+# ---------------------------------------------------------------------------------------------------
+def lightning_slopes(num_heads: int, layer_idx: int, num_layers: int) -> torch.Tensor:
+    """Per-head decay rates: ``2^(-8 (h+1) / H)`` scaled down linearly with depth (the last layer decays slowest)."""
+    base = 1.0 / (2.0 ** (8.0 / num_heads))
+    rate = base ** (torch.arange(num_heads, dtype=torch.float32) + 1.0)
+    return rate * (1.0 - layer_idx / (num_layers - 1 + 1e-5) + 1e-5)
+
+
+def lightning_attention(q, k, v, slope, state, cu_q_host, slots_host, block: int = 256):
+    """Packed prefill / chunked prefill.  q, k, v ``[T, H, D]``; slope fp32 ``[H]``; state fp32 ``[slots, H, D, D]`` holds
+    ``sum_j decay^(t-j) k_j^T v_j`` per request and is advanced in place.  Blocks of ``block`` tokens: inside a block the
+    decayed causal product, across blocks the carried state.  Returns fp32 ``[T, H, D]``.
+    Reference: the lightning-attention operators of src/models/minimax.cpp."""
+    T, H, D = q.shape
+    out = torch.empty((T, H, D), dtype=torch.float32, device=q.device)
+    s = slope.to(q.device, torch.float32).view(H, 1, 1)
+    for b in range(len(cu_q_host) - 1):
+        a, e = int(cu_q_host[b]), int(cu_q_host[b + 1])
+        if e <= a:
+            continue
+        slot = int(slots_host[b])
+        S = state[slot].to(torch.float32)
+        qb, kb, vb = (t[a:e].to(torch.float32).transpose(0, 1) for t in (q, k, v))        # [H, n, D]
+        for i0 in range(0, e - a, block):
+            m = min(block, e - a - i0)
+            qi, ki, vi = qb[:, i0:i0 + m], kb[:, i0:i0 + m], vb[:, i0:i0 + m]
+            idx = torch.arange(1, m + 1, device=q.device, dtype=torch.float32)
+            diff = idx[:, None] - idx[None, :]
+            diag = torch.where(diff >= 0, torch.exp(-s * diff.clamp(min=0)), torch.zeros((), device=q.device))
+            intra = torch.matmul(torch.matmul(qi, ki.transpose(-1, -2)) * diag, vi)
+            inter = torch.matmul(qi * torch.exp(-s * idx[:, None]), S)
+            out[a + i0:a + i0 + m] = (intra + inter).transpose(0, 1)
+            S = S * torch.exp(-s * m) + torch.matmul((ki * torch.exp(-s * (m - idx)[:, None])).transpose(-1, -2), vi)
+        state[slot] = S.to(state.dtype)
+    return out
+
+
+def lightning_decode(q, k, v, slope, state, slots):
+    """One new token per request (``[B, H, D]``): ``S = decay * S + k^T v``, ``o = q S``; state rows ``slots`` updated."""
+    B, H, D = q.shape
+    sl = slots.long()
+    S = state[sl].to(torch.float32)                                                        # [B, H, D, D]
+    ratio = torch.exp(-slope.to(q.device, torch.float32)).view(1, H, 1, 1)
+    S = S * ratio + k.to(torch.float32).unsqueeze(-1) * v.to(torch.float32).unsqueeze(-2)
+    state[sl] = S.to(state.dtype)
+    return torch.matmul(q.to(torch.float32).unsqueeze(-2), S).squeeze(-2)

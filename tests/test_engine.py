@@ -1,5 +1,6 @@
 """Engine behaviour on CPU with tiny models: cache consistency, prefix reuse, chunked prefill, eviction + recompute,
 abort, sampling, page manager, export round trip (quantised HF)."""
+import pytest
 import torch
 
 from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
@@ -395,10 +396,12 @@ def test_decode_rides_along_with_prefill_chunks():
     assert [r0.output_ids, r1.output_ids] == ref
 
 
-def test_hybrid_linear_attention_engine_consistency():
-    """Qwen3-Next-style hybrid stack: chunked prefill + stateful decode (convolution window and delta-rule state per request
-    slot) reproduces token-by-token recomputation; eviction restarts a request from empty state; slots are returned."""
-    m = _model("tiny-qwen3-next")
+@pytest.mark.parametrize("preset_name", ["tiny-qwen3-next", "tiny-minimax-m1"])
+def test_hybrid_linear_attention_engine_consistency(preset_name):
+    """Hybrid stacks (Gated DeltaNet of Qwen3-Next, lightning attention of MiniMax-M1): chunked prefill + stateful decode
+    (per-request state slots) reproduces token-by-token recomputation; eviction restarts a request from empty state; slots
+    are returned."""
+    m = _model(preset_name)
     assert m.cfg.has_linear_attn and m.layers[0].lin is not None and m.layers[1].lin is None
     prompts = _prompts(m.cfg.vocab_size, (5, 130, 70))
     gen = GenerationConfig(max_new_tokens=6, ignore_eos=True)

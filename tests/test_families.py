@@ -48,6 +48,9 @@ FAMILIES = {
                         layer_types=["sliding_attention", "full_attention"]),
     "minimax_m2": dict(model_type="minimax_m2", **_C, num_local_experts=4, num_experts_per_tok=2,
                        rope_parameters={"rope_type": "default", "rope_theta": 1e6, "partial_rotary_factor": 0.5}),
+    "minimax": dict(model_type="minimax", **_C, num_local_experts=4, num_experts_per_tok=2, block_size=16,
+                    layer_types=["linear_attention", "full_attention"], full_attn_alpha_factor=1.5, full_attn_beta_factor=0.8,
+                    linear_attn_alpha_factor=1.25, linear_attn_beta_factor=0.9, mlp_alpha_factor=1.1, mlp_beta_factor=0.7),
     "qwen3_next": dict(model_type="qwen3_next", **_C, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=128,
                        shared_expert_intermediate_size=256, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=32,
                        linear_value_head_dim=32, layer_types=["linear_attention", "full_attention"]),
