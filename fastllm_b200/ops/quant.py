@@ -118,8 +118,8 @@ def normalize_wdtype(name: str | None) -> tuple[str, int]:
     if n.startswith("int4g"):
         g = n[5:]
         return "int4g", int(g) if g else 128
-    if n in ("int4",):
-        return "int4g", 128
+    if n in ("int4", "int4_nozero", "int4nozero", "int4_channel"):
+        return "int4g", -1              # one (scale, minimum) pair per output channel: the group is the whole row
     if n in ("fp8", "fp8_e4m3", "float8", "fp8_block128"):
         return "fp8", 128
     raise ValueError(f"unsupported weight dtype '{name}'")
@@ -158,6 +158,8 @@ class LinearWeight:
                 quant_gemm.prepare(lw)          # operand form of the integer path, before any CUDA graph is captured
             return lw
         if kind == "int4g":
+            if group < 0:                # per-channel: the reference's INT4_NOZERO (src/fastllm.cpp, PerChannelQuantizationMultiThread)
+                group = w.shape[1]
             if w.shape[1] % group != 0:
                 return LinearWeight("dense", w.contiguous(), bias=bias, dtype=w.dtype, interleaved=interleaved)
             q, s, mn = quantize_int4g(w, group)
