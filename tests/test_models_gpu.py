@@ -27,13 +27,13 @@ def test_first_tokens_match_cpu_reference(name, wdtype):
     # through a second, differently scheduled run instead (chunked prefill + graph decode vs one-shot prefill, eager decode)
     e2 = LLMEngine(mg, EngineConfig(max_batch=8, max_context=1024, chunked_prefill_size=64, use_cuda_graph=False), num_pages=64)
     out_g2 = e2.generate(prompts, gen)
-    same = sum(a == b for o, o2 in zip(out_g, out_g2) for a, b in zip(o, o2))
-    total = sum(len(o) for o in out_g)
     first = sum(o[0] == o2[0] for o, o2 in zip(out_g, out_g2))
     # 8-bit-activation weight formats round the activations per batch-size regime (integer kernel vs rounded 16-bit values),
-    # so one near-tie of a random tiny model may fall the other way
+    # so one near-tie of a random tiny model may fall the other way (that request then continues differently)
     assert first >= (len(prompts) if wdtype == "auto" else len(prompts) - 1), (out_g, out_g2)
-    assert same >= 0.7 * total, (out_g, out_g2)
+    agreeing = [(o, o2) for o, o2 in zip(out_g, out_g2) if o[0] == o2[0]]
+    same = sum(a == b for o, o2 in agreeing for a, b in zip(o, o2))
+    assert same >= 0.7 * sum(len(o) for o, _ in agreeing), (out_g, out_g2)
     assert all(len(o) == 12 for o in out_c)
 
 
