@@ -175,6 +175,14 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
         _lib.check(lib.fb_moe_grouped_gemm_fp8(_ptr(aq), st.inter, _ptr(sb), ld_b, _ptr(st.down), _ptr(st.dn_scale), _ptr(ys), _ptr(counts),
                                                _ptr(offsets), E, H, st.inter, rows_cap, H, dt, 0, max_rows, T * topk, s),
                    "fb_moe_grouped_gemm_fp8(down)")
+    elif int_a8 and st.kind == "int4g" and QG.I4_GEMV and mean <= 2 and max(H, st.inter) <= 16384:
+        # about one row per expert: CUDA-core dp4a kernel, one 128-row weight tile per CTA, rows of an expert in passes of four
+        gs, _, ds, _ = st.a8
+        _lib.check(lib.fb_gemv_i4(_ptr(xq), H, _ptr(sa), _ptr(sx), ld_a, _ptr(st.gate_up), _ptr(gs), _ptr(act), 0, 2 * st.inter, H, st.inter,
+                                  dt, GEMM_SWIGLU, _ptr(counts), _ptr(offsets), E, s), "fb_gemv_i4(gate_up)")
+        aq, sb, sbx, ld_b = QG.quant_act_i8(act, rows_used=total)
+        _lib.check(lib.fb_gemv_i4(_ptr(aq), st.inter, _ptr(sb), _ptr(sbx), ld_b, _ptr(st.down), _ptr(ds), _ptr(ys), 0, H, st.inter, H,
+                                  dt, 0, _ptr(counts), _ptr(offsets), E, s), "fb_gemv_i4(down)")
     elif int_a8:
         wk = 1 if st.kind == "int8" else 2
         gs, gz, ds, dz = st.a8

@@ -8,6 +8,8 @@ from __future__ import annotations
 
 import ctypes
 
+import os
+
 import torch
 
 from . import _lib
@@ -24,6 +26,7 @@ _lib.register_sigs({
     "fb_moe_gather_quant_fp8": [P, P, P, P, I, I, I, I, I, P],
     "fb_quant_act_i8": [P, I, P, I, P, P, I, I, I, I, P, P, I, P],
     "fb_gemm_i8": [P, I, P, P, I, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, I, I, I, P],
+    "fb_gemv_i4": [P, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P, I, P],
 }, ["gemm_fp8", "gemm_i8"])
 
 _QMODE = {"int8": 1, "int4g": 2, "fp8": 3}
@@ -90,6 +93,10 @@ def prepare(lw) -> None:
         _a8_tensors(lw)
 
 
+I4_GEMV = os.environ.get("FB_I4_GEMV", "1") != "0"      # int4-group weights at one to four rows: dp4a kernel (csrc/gemv_i4.cu)
+I4_GEMV_MAX_M = 4
+
+
 def _a8_tensors(lw):
     """Weight-side tensors of the integer path: (bytes, scale, zero-or-min, kind code).  int8 storage is switched to q - 128 once."""
     if lw.kind == "int8":
@@ -112,6 +119,13 @@ def _linear_i8(x2, lw, out, bias, res2, flags, pre=None):
         _, xq, sa, xs, ld_a = pre              # quantised by the kernel that produced x (fused RMSNorm)
     else:
         xq, sa, xs, ld_a = quant_act_i8(x2)
+    if (kind == 2 and M <= I4_GEMV_MAX_M and I4_GEMV and bias is None and res2 is None and (flags & ~GEMM_SWIGLU) == 0
+            and lw.n % 128 == 0 and K <= 16384 and lw.group == 128 and out.dtype == x2.dtype):
+        # one to four rows: the CUDA-core dp4a kernel streams the packed rows directly (no unpack / MMA / promotion pipeline)
+        rc = _lib.kernels().fb_gemv_i4(_ptr(xq), K, _ptr(sa), _ptr(xs), ld_a, _ptr(w), _ptr(sc), _ptr(out), M, lw.n, K, out.stride(0),
+                                       dtype_code(x2.dtype), flags, _ptr(None), _ptr(None), 1, _stream())
+        _lib.check(rc, "fb_gemv_i4")
+        return
     for m0 in range(0, M, 128):           # the kernel takes up to 128 rows; the weights of later chunks come from L2
         m1 = min(M, m0 + 128)
         rc = _lib.kernels().fb_gemm_i8(_ptr(xq[m0:m1]), K, _ptr(sa[:, m0:]), _ptr(xs[:, m0:]), ld_a, _ptr(w), _ptr(sc), _ptr(zr),

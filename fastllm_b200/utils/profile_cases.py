@@ -105,6 +105,55 @@ def moe_grouped(tokens=128, experts=128, topk=8, hidden=2048, inter=768, kind="f
     torch.cuda.synchronize()
 
 
+def moe_ep_rank(model="deepseek-v3", tokens=32, ranks=8, kind="int4g128", iters=6, timed=True):
+    """One expert-parallel rank's share of a routed-expert layer at decode size (e.g. DeepSeek-V3: 32 of 256 experts, top-8,
+    hidden 7168, intermediate 2048): routing of all tokens, only the local experts' rows computed.  Prints the device time per
+    layer call (CUDA events around a CUDA graph of ``iters`` calls over rotating weight copies)."""
+    import dataclasses
+
+    from ..models import TPInfo
+    from ..models.config import preset
+    from ..models.decoder import random_init
+    from ..ops import moe as MOE
+    from ..parallel.ep import EPInfo
+
+    cfg = preset(model)
+    first = cfg.first_k_dense
+    copies = 3
+    cfg = dataclasses.replace(cfg, num_layers=first + copies)
+    tp = TPInfo(0, ranks, None)
+    m = random_init(cfg, "cuda", torch.bfloat16, tp=tp, ep=EPInfo.from_tp(tp), wdtype="dense", moe_wdtype=kind, expert_pool=4)
+    exs = [m.layers[first + i].mlp.experts for i in range(copies)]
+    x = torch.randn(tokens, cfg.hidden_size, device="cuda").bfloat16()
+    idx, w = MOE.route_topk(torch.randn(tokens, cfg.num_experts, device="cuda"), None, cfg.num_experts_per_tok, 0, True)
+    for i in range(3):
+        MOE.moe_forward(x, idx, w, exs[i % copies])
+    torch.cuda.synchronize()
+    if not timed:
+        return
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        MOE.moe_forward(x, idx, w, exs[0])
+    torch.cuda.synchronize()
+    with torch.cuda.graph(g):
+        for i in range(iters):
+            MOE.moe_forward(x, idx, w, exs[i % copies])
+    g.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    g.replay()
+    e.record()
+    torch.cuda.synchronize()
+    local = ((idx >= exs[0].first) & (idx < exs[0].first + exs[0].count))
+    hit = int(torch.unique(idx[local]).numel())
+    per = sum(l.nbytes() for l in exs[0].gate_up[:1] + exs[0].down[:1])
+    print(f"moe_ep_rank {model} {kind} tokens={tokens}: {s.elapsed_time(e) / iters * 1e3:.1f} us per layer call; "
+          f"{int(local.sum())} local rows on {hit} of {exs[0].count} local experts; {hit * per / 1e6:.0f} MB of expert weights touched")
+
+
 def gemm_qkv_post(tokens=64, hq=32, hkv=8, k=4096, iters=4):
     from ..ops.quant import LinearWeight
 
@@ -144,6 +193,10 @@ def gdn_decode(batch=64, hk=16, hv=32, iters=4):
 
 CASES = {
     "gemm_qkv_post": gemm_qkv_post,
+    "moe_ep_rank_dsv3_int4g": lambda: moe_ep_rank("deepseek-v3", 32, 8, "int4g128"),
+    "moe_ep_rank_dsv3_int4g_untimed": lambda: moe_ep_rank("deepseek-v3", 32, 8, "int4g128", timed=False),
+    "moe_ep_rank_dsv3_fp8": lambda: moe_ep_rank("deepseek-v3", 32, 8, "fp8"),
+    "moe_ep_rank_qwen3_fp8": lambda: moe_ep_rank("qwen3-30b-a3b", 128, 8, "fp8"),
     "gdn_decode": gdn_decode,
     "gemm_prefill_gate_up": lambda: gemm_prefill(4096, 28672, 4096),
     "gemm_quant_fp8": lambda: gemm_quant("fp8"),

@@ -534,6 +534,41 @@ def test_gemm_int_a8(kind, M, N, K):
     assert rel < (0.03 if kind == "int8" else 0.15), rel
 
 
+@pytest.mark.parametrize("M", [1, 2, 3, 4])
+@pytest.mark.parametrize("N,K", [(256, 512), (4096, 7168), (7168, 2048), (384, 1536)])
+def test_gemv_int4_dp4a(M, N, K):
+    """int4-group weights at one to four rows (CUDA-core dp4a kernel) vs fp32 on the same quantised operands, and vs the
+    tensor-core route; plain and SwiGLU (interleaved gate / up) outputs."""
+    from fastllm_b200.ops import quant as Q
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(M * 7 + N)
+    dt = torch.bfloat16
+    x = torch.randn(M, K, device=DEV).to(dt)
+    w = (torch.randn(N, K, device=DEV) * 0.03).to(dt)
+    lw = Q.LinearWeight.from_dense(w, "int4g128")
+    assert QG.I4_GEMV and QG.uses_int_a8(lw)
+    out = lw(x)
+    ref = _i8_act(x) @ lw.dequant(torch.float32).t()
+    _close(out.float(), ref, 2e-2, 1e-2, f"gemv_i4 {M}x{N}x{K}", fro=5e-3)
+    QG.I4_GEMV = False
+    try:
+        tc = lw(x)
+    finally:
+        QG.I4_GEMV = True
+    _close(out.float(), tc.float(), 2e-2, 1e-2, "gemv_i4 vs tensor-core route", fro=5e-3)
+    if N % 256 == 0:
+        I = N // 2
+        g, u = w[:I], w[I:]
+        lg = Q.LinearWeight.from_dense(B.interleave_gate_up(g, u), "int4g128", interleaved=True)
+        o2 = lg(x, swiglu=True)
+        full = _i8_act(x) @ lg.dequant(torch.float32).t()
+        t = full.reshape(M, N // 128, 2, 64)
+        r2 = (torch.nn.functional.silu(t[:, :, 0]) * t[:, :, 1]).reshape(M, I)
+        _close(o2.float(), r2, 3e-2, 2e-2, "gemv_i4 swiglu", fro=8e-3)
+    _lib.check_device_errors()
+
+
 def test_gemm_int_a8_epilogues():
     from fastllm_b200.ops import quant as Q
 
@@ -572,9 +607,11 @@ def test_moe_grouped_int_a8(kind):
     ex = m.layers[0].mlp.experts
     assert ex.stacked is not None
     torch.manual_seed(4)
-    for T in (5, 150):
+    for T in (1, 5, 150):          # few rows per expert: int4 experts run the dp4a kernel, int8 and large batches the tensor core
         x = torch.randn(T, cfg.hidden_size, device=DEV).bfloat16()
         idx, w = MOE.route_topk(torch.randn(T, cfg.num_experts, device=DEV), None, 2, 0, True)
+        if T == 5:
+            idx[:, 0] = 3          # one expert with five rows: a second pass of four over its weight tiles
         y8 = MOE.moe_forward(x, idx, w, ex)
         assert ex.stacked.a8 is not None and (kind != "int8" or ex.stacked.signed)
         QG.INT_A8 = False              # the 16-bit-activation kernels on the same (now q - 128) bytes
