@@ -377,11 +377,13 @@ class LLMEngine:
             chunks.append(([r.all_ids[-1]] + d, r.total_len - 1, r.pages, len(d) + 1, r.state_slot))
             owners.append((r, d))
         logits = self.runner.prefill(chunks)
-        if self.model.tp.size > 1:
+        if self.model.tp.size > 1:                  # greedy verification: one candidate per rank and row is enough
             if self.control is not None:
-                self.control.gather_logits()
-            logits = self.model.tp.comm.gather_logits(logits, self.model.vocab_shard, self.model.cfg.vocab_size)
-        choice = sampling.greedy(logits).tolist()
+                self.control.gather_logits(1)
+            vals, ids = self.model.tp.comm.gather_candidates(logits, self.model.vocab_shard, 1)
+            choice = ids.gather(1, vals.argmax(dim=-1, keepdim=True)).view(-1).tolist()
+        else:
+            choice = sampling.greedy(logits).tolist()
         produced, row = 0, 0
         for r, d in owners:
             mine = choice[row:row + len(d) + 1]
@@ -451,9 +453,57 @@ class LLMEngine:
                     break
         return [r for r in reqs if r in self.running and r.state == RequestState.DECODE]
 
+    def _candidate_width(self, reqs) -> int:
+        """How many of each rank's best logits decide this step's tokens: the largest top-k in the batch (1 for greedy rows,
+        the sampler's cap where top-k is off) plus the recent tokens a repetition penalty may push out of that set.
+        0: the step needs whole logit rows (log-probabilities, returned logits, logits processors)."""
+        need = 1
+        for r in reqs:
+            g = r.gen
+            if g.output_logits or g.logprobs or g.logits_processor is not None:
+                return 0
+            greedy = g.is_simple_greedy() or not g.do_sample
+            k = 1 if greedy else (g.top_k if g.top_k > 0 else 1024)
+            if abs(g.repeat_penalty - 1.0) > 1e-8:
+                k += len(set(r.all_ids[-g.last_n:]))
+            need = max(need, k)
+        return 1 << (need - 1).bit_length()              # few distinct shapes
+
+    def _sample_candidates(self, reqs, vals, ids):
+        """Sampling over the gathered per-rank candidates (``vals`` / ``ids`` ``[R, C]``): penalties by token id, then the same
+        top-k / top-p / temperature draw as on whole rows; the drawn column is mapped back to its token id."""
+        lg = vals.float().clone()
+        for row, r in enumerate(reqs):
+            g = r.gen
+            if abs(g.repeat_penalty - 1.0) > 1e-8:
+                recent = torch.as_tensor(sorted(set(r.all_ids[-g.last_n:])), dtype=torch.long, device=lg.device)
+                if recent.numel():
+                    hit = torch.isin(ids[row], recent)
+                    v = lg[row]
+                    lg[row] = torch.where(hit, torch.where(v > 0, v / g.repeat_penalty, v * g.repeat_penalty), v)
+        greedy_rows = [r.gen.is_simple_greedy() or not r.gen.do_sample for r in reqs]
+        if all(greedy_rows):
+            cols = lg.argmax(dim=-1)
+        else:
+            tk = [1 if gr else r.gen.top_k for r, gr in zip(reqs, greedy_rows)]
+            none = [[] for _ in reqs]
+            if lg.is_cuda:
+                cols = sampling.sample_fused(lg, none, [1.0] * len(reqs), tk, [r.gen.top_p for r in reqs],
+                                             [r.gen.temperature for r in reqs]).long()
+            else:
+                cols = sampling.sample(lg, tk, [r.gen.top_p for r in reqs], [r.gen.temperature for r in reqs]).long()
+        return ids.gather(1, cols.view(-1, 1)).view(-1).tolist()
+
     def _sample(self, reqs, logits):
         m = self.model
         if m.tp.size > 1:
+            k = self._candidate_width(reqs) if self.cfg.tp_candidate_sampling else 0
+            if 0 < k < m.lm_head.n // 2:
+                # vocab-sharded head: the ranks exchange their k best (logit, id) pairs per row, not whole logit rows
+                if self.control is not None:
+                    self.control.gather_logits(k)
+                vals, ids = m.tp.comm.gather_candidates(logits, m.vocab_shard, k)
+                return self._sample_candidates(reqs, vals, ids)
             if self.control is not None:
                 self.control.gather_logits()
             logits = m.tp.comm.gather_logits(logits, m.vocab_shard, m.cfg.vocab_size)

@@ -23,6 +23,7 @@ from .kv_cache import KVCache
 class EngineConfig:
     max_batch: int = 256
     max_context: int = 8192
+    tp_candidate_sampling: bool = True     # vocab-sharded sampling exchanges per-rank top-k candidates instead of whole logit rows
     chunked_prefill_size: int = 8192
     gpu_mem_ratio: float = 0.9
     max_tokens: int | None = None

@@ -229,8 +229,9 @@ class ControlPlane:
         self.ring.publish(KIND_PREFILL, encode_prefill_plan(chunks))
         self.published += 1
 
-    def gather_logits(self):
-        self.ring.publish(KIND_GATHER)
+    def gather_logits(self, k: int = 0):
+        """``k`` > 0: the ranks exchange their ``k`` best (logit, token id) candidates per row instead of whole logit rows."""
+        self.ring.publish(KIND_GATHER, int(k).to_bytes(4, "little") if k > 0 else b"")
 
     def reset(self):
         self.ring.publish(KIND_RESET)
@@ -315,7 +316,11 @@ class WorkerLoop:
                     self.last_logits = self.runner.prefill(decode_prefill_plan(buf))
                     self.steps += 1
                 elif kind == KIND_GATHER:
-                    model.tp.comm.gather_logits(self.last_logits, model.vocab_shard, model.cfg.vocab_size)
+                    k = int.from_bytes(bytes(buf[:4]), "little") if len(buf) >= 4 else 0
+                    if k > 0:
+                        model.tp.comm.gather_candidates(self.last_logits, model.vocab_shard, k)
+                    else:
+                        model.tp.comm.gather_logits(self.last_logits, model.vocab_shard, model.cfg.vocab_size)
                 elif kind == KIND_RESET:
                     self.runner.reset_after_device_error()
                 elif kind == KIND_CALL:

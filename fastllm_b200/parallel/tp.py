@@ -69,6 +69,24 @@ class TPComm:
         allp = flat.view(self.size, R, VL)
         return allp.permute(1, 0, 2).reshape(R, self.size * VL)[:, :vocab].contiguous()
 
+    def gather_candidates(self, logits: torch.Tensor, shard, k: int):
+        """Sampling without moving the whole vocabulary: every rank sends the ``k`` largest logits of its vocab shard with
+        their token ids.  Returns (values fp32 ``[R, tp * k]``, global ids int64 ``[R, tp * k]``); the global top-``k`` of
+        every row is among them.  One all-gather of ``R * 2k`` floats per rank instead of ``R * V / tp``."""
+        R, VL = logits.shape
+        lo, hi = shard
+        lg = logits.float()
+        if hi - lo < VL:                      # rows of the padded shard beyond the vocabulary never win
+            lg = lg.clone()
+            lg[:, hi - lo:] = float("-inf")
+        k = max(1, min(int(k), VL))
+        v, i = torch.topk(lg, k, dim=-1)
+        pack = torch.cat([v, (i + lo).float()], dim=-1).contiguous()           # ids < 2^24: exact in fp32
+        flat = torch.empty((self.size * R, 2 * k), device=logits.device, dtype=torch.float32)
+        dist.all_gather_into_tensor(flat, pack, group=self.group)
+        allp = flat.view(self.size, R, 2 * k).permute(1, 0, 2)
+        return allp[:, :, :k].reshape(R, self.size * k).contiguous(), allp[:, :, k:].reshape(R, self.size * k).long().contiguous()
+
     def barrier(self):
         dist.barrier(group=self.group)
 

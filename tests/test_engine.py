@@ -438,3 +438,45 @@ def test_ngram_speculative_decoding_keeps_greedy_output():
     # a greedy model that has entered a cycle repeats it: the drafts are then accepted and steps are saved
     if spec.spec_accepted > 0:
         assert spec.decode_steps < plain.decode_steps
+
+
+def test_candidate_sampling_matches_whole_row_sampling():
+    """Vocab-sharded sampling on per-shard top-k candidates: with repetition penalties the chosen token equals the penalised
+    whole-row arg-max (greedy) and lies in the penalised whole-row top-k (sampling), for shards split at any point."""
+    from types import SimpleNamespace
+
+    from fastllm_b200.engine import sampling
+
+    m = _model()
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=256), num_pages=8)
+    g = torch.Generator().manual_seed(5)
+    V, R = 512, 6
+    for trial in range(8):
+        logits = torch.randn(R, V, generator=g) * 3
+        reqs = []
+        for r in range(R):
+            recent = torch.randint(0, V, (40,), generator=g).tolist() + logits[r].topk(3).indices.tolist()    # the best tokens are penalised
+            gen = GenerationConfig(max_new_tokens=4, do_sample=(r % 2 == 1), top_k=5, top_p=1.0, temperature=0.7, repeat_penalty=1.8)
+            reqs.append(SimpleNamespace(gen=gen, all_ids=recent, output_ids=[]))
+        k = eng._candidate_width(reqs)
+        assert k >= 5 + 1 and (k & (k - 1)) == 0
+        cut = [100, 256, 400, 37][trial % 4]
+        vals, ids = [], []
+        for lo, hi in ((0, cut), (cut, V)):
+            v, i = logits[:, lo:hi].topk(min(k, hi - lo), dim=-1)
+            pad = k - v.shape[1]
+            if pad > 0:
+                v = torch.cat([v, torch.full((R, pad), float("-inf"))], dim=1)
+                i = torch.cat([i, torch.zeros((R, pad), dtype=torch.long)], dim=1)
+            vals.append(v); ids.append(i + lo)
+        got = eng._sample_candidates(reqs, torch.cat(vals, 1), torch.cat(ids, 1))
+        full = logits.clone()
+        sampling.apply_repeat_penalty(full, [r.all_ids for r in reqs], [1.8] * R)
+        for r in range(R):
+            if r % 2 == 0:
+                assert got[r] == int(full[r].argmax())
+            else:
+                assert got[r] in full[r].topk(5).indices.tolist()
+    # whole rows are needed for log-probabilities / returned logits / logits processors
+    reqs[0].gen.logprobs = 3
+    assert eng._candidate_width(reqs) == 0
