@@ -469,3 +469,347 @@ def CatDirectBatch(dsts, xs, axis): return [CatDirect(d, x, axis) for d, x in zi
 def AppendKVCachebatch(caches, xs, axis=0): return [CatDirect(c, x, axis) for c, x in zip(caches, xs)]
 def AttentionBatch(qs, ks, vs, masks=None, group=1, scale=None):
     return [Attention(q, k, v, None if masks is None else masks[i], group, scale) for i, (q, k, v) in enumerate(zip(qs, ks, vs))]
+
+
+# ---- softmax / extended linear / adapters ----------------------------------------------------------
+def Softmax(x, axis=-1):
+    if B.cpu_native(x) and axis in (-1, x.dim() - 1):
+        return C.softmax(x)
+    return torch.softmax(x.float(), dim=axis).to(x.dtype)
+
+
+def SoftmaxBatch(xs, axis=-1):
+    return [Softmax(x, axis) for x in xs]
+
+
+ExTypeNone, ExSwiglu, ExGelu, ExSilu = 0, 1, 2, 3
+
+
+def CanRunLinearEx(ex_type) -> bool:
+    return ex_type in (ExTypeNone, ExSwiglu, ExGelu, ExSilu)
+
+
+def LinearEx(x, weight, bias=None, ex_type=ExTypeNone):
+    """Linear followed by an activation (reference: LinearEx, include/fastllm.h ``LinearExType``).  SwiGLU runs in the GEMM
+    epilogue on the GPU; ``weight`` then holds gate rows followed by up rows."""
+    if ex_type == ExSwiglu:
+        return LinearSwiglu(x, weight, bias)
+    y = Linear(x, weight, bias)
+    if ex_type == ExGelu:
+        return F.gelu(y.float()).to(y.dtype)
+    if ex_type == ExSilu:
+        return Silu(y)
+    return y
+
+
+def CanRunLinearAdd(x, weight, bias=None, out=None) -> bool: return True
+def CanRunLinearSwiglu(x, weight) -> bool: return weight.shape[0] % 2 == 0
+def CanRunSwigluLinearAdd(x, weight, bias=None, out=None) -> bool: return x.shape[-1] % 2 == 0
+def CanRunMLP() -> bool: return True
+def CanRunMergeAttention() -> bool: return True
+def CanRunMergeMOE(*_a, **_k) -> bool: return True
+
+
+def LoraLayer(x, weight, lora_a, lora_b, bias=None, lora_config=None):
+    """``y = W x + (alpha / r) * B (A x)`` (reference: LoraLayer, src/fastllm.cpp).  ``lora_config``: ``lora_alpha``, ``r``."""
+    cfg = lora_config or {}
+    r = float(cfg.get("r", lora_a.shape[0]))
+    scale = float(cfg.get("lora_alpha", r)) / r
+    y = Linear(x, weight, bias)
+    return y + (Linear(Linear(x, lora_a), lora_b).float() * scale).to(y.dtype)
+
+
+def IA3Layer(x, weight, ia3_l, bias=None, ia3_config=None):
+    """(IA)^3: the learned vector rescales the layer's output, or its input for feed-forward layers
+    (``ia3_config['if_feedforward']``) (reference: IA3Layer, src/fastllm.cpp)."""
+    ff = str((ia3_config or {}).get("if_feedforward", "false")).lower() in ("1", "true")
+    if ff:
+        return Linear((x.float() * ia3_l.float()).to(x.dtype), weight, bias)
+    y = Linear(x, weight, bias)
+    return (y.float() * ia3_l.float()).to(y.dtype)
+
+
+def AppendKVCacheBatch(caches, new):
+    """``caches[b]`` (``[heads, len, dim]``) grows by row ``b`` of ``new`` (``[batch, heads, new_len, dim]``)."""
+    return [torch.cat([c, new[b].to(c.dtype)], dim=-2) for b, c in enumerate(caches)]
+
+
+def MergeMLA(q_nope, q_pe, kv_cache, pe_cache, mask, scale):
+    """Absorbed multi-head latent attention over contiguous caches: scores from the latent part (``q_nope`` already multiplied
+    by W_UK, ``[B, H, lora]`` against ``kv_cache [B, L, lora]``) plus the rotary part, softmax, values = the latent rows.
+    (reference: MergeMLA, include/fastllm.h:918; the paged form is ``MergeMLAPaged``)."""
+    s = torch.einsum("bhd,bld->bhl", q_nope.float(), kv_cache.float()) + torch.einsum("bhd,bld->bhl", q_pe.float(), pe_cache.float())
+    s = s * scale
+    if mask is not None and mask.numel():
+        s = s.masked_fill(mask.bool().reshape(s.shape[0], 1, -1)[..., :s.shape[-1]], float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    return torch.einsum("bhl,bld->bhd", p, kv_cache.float()).to(q_nope.dtype)
+
+
+def ToDataType(x, dtype):
+    """Conversion between the float types by name or torch dtype (quantised storage types are built by ``LinearWeight``)."""
+    table = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16, "fp32": torch.float32,
+             "fp16": torch.float16, "bf16": torch.bfloat16}
+    return x.to(table[dtype] if isinstance(dtype, str) else dtype)
+
+
+def ToDataTypeForceCPU(x, dtype):
+    return ToDataType(x.cpu(), dtype)
+
+
+def GetDataTypeName(dtype) -> str:
+    names = {0: "float32", 1: "bfloat16", 2: "int16", 3: "int8", 4: "int4", 5: "int2", 6: "bit", 7: "float16", 8: "int4_nozero",
+             9: "int4_group", 10: "fp8_e4m3", 11: "int2_group", 12: "base3_group"}
+    if isinstance(dtype, int):
+        return names.get(dtype, f"unknown({dtype})")
+    return str(dtype).replace("torch.", "")
+
+
+def NVFP4E8M0ScaleToFloat(v: int) -> float:
+    """An e8m0 block scale byte as a float: 2^(v - 127); 255 is NaN."""
+    return float("nan") if int(v) == 255 else float(2.0 ** (int(v) - 127))
+
+
+def LLMSamplingOnly(logits, config=None):
+    """One token id from a row of logits with the request's sampling settings (top-k, top-p, temperature)."""
+    from ..engine import sampling
+
+    lg = logits.reshape(1, -1).float().clone()
+    g = config
+    if g is None or not getattr(g, "do_sample", False) or getattr(g, "top_k", 1) == 1:
+        return int(lg.argmax())
+    return int(sampling.sample(lg.cpu(), [g.top_k], [g.top_p], [g.temperature])[0])
+
+
+def LLMSampling(logits, config=None, recent_ids=None):
+    """Repetition penalty on the recently produced tokens, then ``LLMSamplingOnly``."""
+    from ..engine import sampling
+
+    lg = logits.reshape(1, -1).float().clone()
+    if config is not None and recent_ids and abs(getattr(config, "repeat_penalty", 1.0) - 1.0) > 1e-8:
+        sampling.apply_repeat_penalty(lg, [list(recent_ids)], [config.repeat_penalty])
+    return LLMSamplingOnly(lg, config)
+
+
+# ---- Kimi-K3 operators (Kimi Delta Attention stack; reference: src/devices/cpu/kimi_k3_ops.cpp) ----------
+def KimiK3RMSNorm(x, weight, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(x.dtype)
+
+
+def KimiK3L2Norm(x, eps=1e-6):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).sum(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def KimiK3RMSNormSigmoidGate(x, gate, weight, eps):
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * weight.float() * torch.sigmoid(gate.float())).to(x.dtype)
+
+
+def KimiK3SiTUAndMul(gate, up, beta=1.0, linear_beta=0.0):
+    """``beta * tanh(g / beta) * sigmoid(g)`` times the (optionally tanh-bounded) up projection."""
+    g, u = gate.float(), up.float()
+    situ = beta * torch.tanh(g / beta) * torch.sigmoid(g)
+    if linear_beta > 0:
+        u = linear_beta * torch.tanh(u / linear_beta)
+    return (situ * u).to(gate.dtype)
+
+
+def KimiK3CausalConv1D(x, weight, kernel_size, cache=None):
+    """Depth-wise causal convolution over ``[batch, seq, channels]`` followed by SiLU; with ``cache``
+    (``[batch, kernel - 1, channels]``) the sequence continues from the cached inputs and the cache is advanced in place."""
+    Bn, S, Cn = x.shape
+    w = weight.reshape(Cn, kernel_size).float()
+    hist = cache.float() if cache is not None else torch.zeros(Bn, kernel_size - 1, Cn, device=x.device)
+    full = torch.cat([hist, x.float()], dim=1)                              # [B, K-1+S, C]
+    win = full.unfold(1, kernel_size, 1)                                    # [B, S, C, K]
+    y = (win * w[None, None]).sum(-1)
+    if cache is not None:
+        cache.copy_(full[:, -(kernel_size - 1):].to(cache.dtype))
+    return F.silu(y).to(x.dtype)
+
+
+def KimiK3UpdatePackedConvCache(q, k, v, history, tokens, cache):
+    """Advance the packed q | k | v convolution cache (``[batch, history, Cq + Ck + Cv]``) by the first ``tokens`` rows of the
+    projected inputs, without evaluating the convolution."""
+    new = torch.cat([q[:, :tokens], k[:, :tokens], v[:, :tokens]], dim=-1).to(cache.dtype)
+    full = torch.cat([cache, new], dim=1)
+    cache.copy_(full[:, -history:])
+    return cache
+
+
+def _kda_gates(raw_gate, raw_beta, a_log, dt_bias, lower_bound):
+    H, D = raw_gate.shape[-2], raw_gate.shape[-1]
+    a = a_log.float().reshape(H, 1) if a_log.numel() == H else a_log.float().reshape(1, D)
+    gate = lower_bound * torch.sigmoid(torch.exp(a) * (raw_gate.float() + dt_bias.float().reshape(H, D)))
+    return gate, torch.sigmoid(raw_beta.float())
+
+
+def KimiK3RecurrentKDA(q, k, v, raw_gate, raw_beta, a_log, dt_bias, lower_bound=-5.0, state=None, output_aux=True, tokens=None,
+                       state_only=False):
+    """Kimi Delta Attention, recurrent form over ``[batch, seq, heads, dim]``: per-channel decay
+    ``exp(lower_bound * sigmoid(exp(A) * (g + dt_bias)))`` on the rows of the ``[dim, dim]`` state, delta-rule write with
+    ``beta = sigmoid(raw_beta)``, read-out scaled by ``dim^-1/2``.  Returns (output, state, decay, beta)."""
+    Bn, S, H, D = k.shape
+    n = S if tokens is None else int(tokens)
+    if state is None:
+        state = torch.zeros(Bn, H, D, D, dtype=torch.float32, device=k.device)
+    gate, beta = _kda_gates(raw_gate, raw_beta, a_log, dt_bias, lower_bound)
+    out = None if state_only else torch.empty(Bn, S, H, D, dtype=torch.float32, device=k.device)
+    kf, vf = k.float(), v.float()
+    qf = None if state_only else q.float()
+    for t in range(n):
+        state.mul_(torch.exp(gate[:, t]).unsqueeze(-1))                      # row c of every head's state decays by its own gate
+        pred = torch.einsum("bhc,bhcv->bhv", kf[:, t], state)
+        delta = (vf[:, t] - pred) * beta[:, t].unsqueeze(-1)
+        state.add_(kf[:, t].unsqueeze(-1) * delta.unsqueeze(-2))
+        if not state_only:
+            out[:, t] = torch.einsum("bhc,bhcv->bhv", qf[:, t], state) * D ** -0.5
+    o = None if state_only else out.to(q.dtype)
+    return (o, state, gate, beta) if output_aux else (o, state)
+
+
+def KimiK3RecurrentKDAOutputOnly(q, k, v, raw_gate, raw_beta, a_log, dt_bias, lower_bound=-5.0, state=None):
+    return KimiK3RecurrentKDA(q, k, v, raw_gate, raw_beta, a_log, dt_bias, lower_bound, state, output_aux=False)
+
+
+def KimiK3RecurrentKDAUpdateState(k, v, raw_gate, raw_beta, a_log, dt_bias, lower_bound, tokens, state):
+    return KimiK3RecurrentKDA(None, k, v, raw_gate, raw_beta, a_log, dt_bias, lower_bound, state, output_aux=False, tokens=tokens,
+                              state_only=True)[1]
+
+
+def KimiK3AttnRes(prefix_sum, block_residual, projection, norm, eps=1e-5):
+    """Attention over residual blocks: every candidate (the running prefix sum and each stored block residual,
+    ``[tokens, blocks, hidden]``) is scored by its RMS-normalised projection on ``norm * projection``; the output is the
+    softmax-weighted mix of the candidates."""
+    w = (norm.float() * projection.float())
+    cand = torch.cat([block_residual.float(), prefix_sum.float().unsqueeze(1)], dim=1)            # [T, blocks + 1, hidden]
+    scores = (cand * torch.rsqrt(cand.pow(2).mean(-1, keepdim=True) + eps) * w).sum(-1)
+    p = torch.softmax(scores, dim=-1)
+    return (p.unsqueeze(-1) * cand).sum(1).to(prefix_sum.dtype)
+
+
+def KimiK3CausalAttention(q, k, v, scale):
+    """Plain causal softmax attention over ``[batch, seq, heads, dim]`` (grouped KV heads are repeated)."""
+    Bn, S, H, D = q.shape
+    rep = H // k.shape[2]
+    kf, vf = k.float().repeat_interleave(rep, 2), v.float().repeat_interleave(rep, 2)
+    s = torch.einsum("bqhd,bkhd->bhqk", q.float(), kf) * scale
+    s = s.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool, device=q.device), 1), float("-inf"))
+    return torch.einsum("bhqk,bkhd->bqhd", torch.softmax(s, -1), vf).to(q.dtype)
+
+
+def KimiK3RoutedExperts(x, index, score, w1s, w2s, w3s, beta=1.0, linear_beta=0.0):
+    """Routed experts with the SiTU activation: ``sum_k score * w2[e](situ(w1[e] x) * bound(w3[e] x))``."""
+    out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+    T, topk = index.shape
+    for t in range(T):
+        for j in range(topk):
+            e = int(index[t, j])
+            h = KimiK3SiTUAndMul(Linear(x[t:t + 1], w1s[e]), Linear(x[t:t + 1], w3s[e]), beta, linear_beta)
+            out[t] += float(score[t, j]) * Linear(h, w2s[e])[0].float()
+    return out.to(x.dtype)
+
+
+# ---- process-wide settings under the reference's names (the implementations live in fastllm_b200.llm) --------------
+def _llm():
+    from .. import llm
+
+    return llm
+
+
+def SetThreads(n): _llm().set_cpu_threads(n)
+def GetThreads(): return _llm().get_cpu_threads()
+def SetLowMemMode(on): _llm().set_cpu_low_mem(on)
+def GetLowMemMode(): return _llm().get_cpu_low_mem()
+def SetKVCacheInCPU(on): _llm().set_cpu_kvcache(on)
+def GetKVCacheInCPU(): return _llm().get_cpu_kvcache()
+def SetHistoryCacheInCPU(on): _llm().set_cpu_historycache(on)
+def GetHistoryCacheInCPU(): return _llm().get_cpu_historycache()
+def SetCudaEmbedding(on): _llm().set_cuda_embedding(on)
+def GetCudaEmbedding(): return bool(_llm()._settings.get("cuda_embedding", True))
+GetCudaEmbeddingRequested = GetCudaEmbedding
+def SetCudaSharedExpert(on): _llm().set_cuda_shared_expert(on)
+def GetCudaSharedExpert(): return bool(_llm()._settings.get("cuda_shared_expert", True))
+def SetCudaSlabMB(mb): _llm().set_cuda_slab(mb)
+def GetCudaSlabMB(): return int(_llm()._settings.get("cuda_slab", 0) or 0)
+def EnableAMX(on): _llm().set_enable_amx(on)
+def GetEnableAMX(): return bool(_llm()._settings.get("enable_amx", False))
+def SetGpuMemRatio(r): _llm().set_gpu_mem_ratio(r)
+def GetGpuMemRatio(): return float(_llm()._settings.get("gpu_mem_ratio", 0.9) or 0.9)
+def SetMaxTokens(n): _llm().set_max_tokens(n)
+def GetMaxTokens(): return _llm()._settings.get("max_tokens")
+def SetPageLen(n): _llm().set_page_size(n)
+def GetPageLen(): return int(_llm()._settings.get("page_size", 128) or 128)
+def SetMoeDeviceLayers(n): _llm().set_moe_device_layers(n)
+def GetMoeDeviceLayers(): return int(_llm()._settings.get("moe_device_layers", -1) or -1)
+def SetDeviceMap(device_map): _llm().set_device_map(device_map)
+def SetMoeDeviceMap(device_map): _llm().set_device_map(device_map, is_moe=True)
+def SetLayeredMoeDeviceMap(device_map): _llm().set_layered_moe_device_map(device_map)
+def SetModelLoadProgressCallback(cb): _llm().set_model_load_progress_callback(cb)
+def ClearModelLoadProgressCallback(): _llm().set_model_load_progress_callback(None)
+
+
+def ReportModelLoadProgress(stage, current, total):
+    from ..serving import progress
+
+    progress.emit(stage, current, total)
+
+
+def HasDeviceType(name) -> bool: return bool(_llm().has_device(name))
+def PrintInstructionInfo(): return _llm().print_ins_info()
+
+
+def SelectDeviceFromMap(device_map: dict, layer: int, n_layers: int) -> str:
+    """Device of ``layer`` under a ratio map like ``{'cuda:0': 3, 'cuda:1': 1}`` (layers are split in proportion, in order)."""
+    from ..loader.shard import split_layers_by_map
+
+    return str(split_layers_by_map(n_layers, device_map)[layer])
+
+
+def ApplyDeviceMap(device_map: dict, layer: int, n_layers: int) -> str:
+    return SelectDeviceFromMap(device_map, layer, n_layers)
+
+
+def SetCurrentThreadExecutor(_executor=None):
+    """One executor serves the process here (kernels launch on the calling thread's current CUDA stream)."""
+    return None
+
+
+def ClearAllPagedCacheManagers():
+    """Paged caches belong to engines here; dropping the engines frees them.  Releases cached allocator blocks."""
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
+
+
+def ClearProfiler():
+    """Start a fresh per-kernel timing table (``ops._lib.KernelProfile``)."""
+    from . import _lib
+
+    _lib.start_profile()
+
+
+def PrintProfiler():
+    from . import _lib
+
+    p = _lib.stop_profile()
+    if p is not None:
+        for name, row in sorted(p.report().items(), key=lambda kv: -kv[1].get("ms", 0.0) if isinstance(kv[1], dict) else 0.0):
+            print(name, row)
+
+
+def GetModelTypeFromFile(path: str) -> str:
+    """``model_type`` of a checkpoint folder (config.json), a GGUF file (``general.architecture``) or a ``.flm`` file."""
+    import json
+    import os
+
+    if os.path.isdir(path):
+        return str(json.load(open(os.path.join(path, "config.json"))).get("model_type", ""))
+    if path.endswith(".gguf"):
+        from ..loader import gguf
+
+        return str(gguf.GGUFFile(path).meta.get("general.architecture", ""))
+    from ..loader import flm
+
+    return str(flm.read_flm(path)[0].get("model_type", ""))

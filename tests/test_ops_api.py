@@ -6,6 +6,7 @@ import pytest
 import torch
 
 from fastllm_b200.ops import api as O
+from fastllm_b200.ops import api
 from fastllm_b200.ops import attention as A
 
 
@@ -129,3 +130,64 @@ def test_linear_attention_and_misc_operators_cpu():
     assert [u.shape for u in O.SplitBatch(torch.zeros(4, 6), 0, 2)] == [(2, 6), (2, 6)]
     beta2, g2 = O.SigmoidMambaSoftplus(torch.zeros(2), torch.zeros(2), torch.zeros(2), torch.zeros(2))
     assert torch.allclose(beta2, torch.full((2,), 0.5)) and torch.allclose(g2, torch.full((2,), -math.log(2.0)))
+
+
+def test_kimi_k3_operators_match_their_definitions():
+    """Kimi-K3 operator names: the recurrent KDA against an explicit per-token loop, state replay, gates and activations."""
+    torch.manual_seed(3)
+    Bn, S, H, D = 2, 5, 3, 8
+    q, k, v, g = (torch.randn(Bn, S, H, D) for _ in range(4))
+    rb = torch.randn(Bn, S, H)
+    a_log, dt = torch.randn(H) * 0.3, torch.randn(H, D) * 0.1
+    out, state, decay, beta = api.KimiK3RecurrentKDA(q, k, v, g, rb, a_log, dt, -5.0)
+    ref_state = torch.zeros(Bn, H, D, D)
+    for b in range(Bn):
+        for h in range(H):
+            for t in range(S):
+                gate = -5.0 * torch.sigmoid(torch.exp(a_log[h]) * (g[b, t, h] + dt[h]))
+                ref_state[b, h] *= torch.exp(gate)[:, None]
+                pred = k[b, t, h] @ ref_state[b, h]
+                delta = (v[b, t, h] - pred) * torch.sigmoid(rb[b, t, h])
+                ref_state[b, h] += k[b, t, h][:, None] * delta[None, :]
+                assert torch.allclose(out[b, t, h], (q[b, t, h] @ ref_state[b, h]) * D ** -0.5, atol=1e-5)
+    assert torch.allclose(state, ref_state, atol=1e-5) and decay.shape == g.shape and beta.shape == rb.shape
+    st2 = api.KimiK3RecurrentKDAUpdateState(k, v, g, rb, a_log, dt, -5.0, 3, None if False else torch.zeros(Bn, H, D, D))
+    o3, st3 = api.KimiK3RecurrentKDAOutputOnly(q[:, :3], k[:, :3], v[:, :3], g[:, :3], rb[:, :3], a_log, dt, -5.0)
+    assert torch.allclose(st2, st3, atol=1e-6)
+    x = torch.randn(4, 16)
+    assert torch.allclose(api.KimiK3L2Norm(x).norm(dim=-1), torch.ones(4), atol=1e-3)
+    gt = torch.randn(4, 16)
+    assert torch.allclose(api.KimiK3RMSNormSigmoidGate(x, gt, torch.ones(16), 1e-6), api.KimiK3RMSNorm(x, torch.ones(16), 1e-6) * torch.sigmoid(gt), atol=1e-6)
+    assert torch.allclose(api.KimiK3SiTUAndMul(gt, x, 1e6, 0.0), gt * torch.sigmoid(gt) * x, atol=1e-4)      # large beta: SiLU(g) * up
+    # convolution with a cache continues the sequence exactly
+    xs, w = torch.randn(1, 7, 6), torch.randn(6, 4)
+    whole = api.KimiK3CausalConv1D(xs, w, 4)
+    cache = torch.zeros(1, 3, 6)
+    parts = torch.cat([api.KimiK3CausalConv1D(xs[:, :3], w, 4, cache), api.KimiK3CausalConv1D(xs[:, 3:], w, 4, cache)], dim=1)
+    assert torch.allclose(whole, parts, atol=1e-6)
+    # residual attention with one block reduces to a two-way softmax mix
+    ps, br = torch.randn(3, 16), torch.randn(3, 1, 16)
+    mix = api.KimiK3AttnRes(ps, br, torch.randn(16), torch.ones(16))
+    assert mix.shape == ps.shape and torch.all((mix - ps).abs() <= (br[:, 0] - ps).abs() + 1e-5)
+
+
+def test_adapter_softmax_and_settings_names():
+    torch.manual_seed(4)
+    x, w = torch.randn(3, 8), torch.randn(6, 8)
+    a, b = torch.randn(2, 8), torch.randn(6, 2)
+    y = api.LoraLayer(x, w, a, b, None, {"lora_alpha": 4, "r": 2})
+    assert torch.allclose(y, x @ w.t() + 2.0 * (x @ a.t()) @ b.t(), atol=1e-5)
+    l = torch.rand(6)
+    assert torch.allclose(api.IA3Layer(x, w, l), (x @ w.t()) * l, atol=1e-5)
+    assert torch.allclose(api.Softmax(x, -1).sum(-1), torch.ones(3), atol=1e-6)
+    assert torch.allclose(api.LinearEx(x, w, None, api.ExSilu), torch.nn.functional.silu(x @ w.t()), atol=1e-5)
+    assert api.NVFP4E8M0ScaleToFloat(127) == 1.0 and api.NVFP4E8M0ScaleToFloat(130) == 8.0
+    assert api.GetDataTypeName(9) == "int4_group" and api.HasDeviceType("cpu")
+    api.SetThreads(2)
+    assert api.GetThreads() == 2
+    assert api.SelectDeviceFromMap({"cpu": 1}, 0, 4) == "cpu"
+    qn, qp = torch.randn(2, 3, 5), torch.randn(2, 3, 2)
+    kv, pe = torch.randn(2, 4, 5), torch.randn(2, 4, 2)
+    o = api.MergeMLA(qn, qp, kv, pe, None, 0.3)
+    s = torch.softmax((torch.einsum("bhd,bld->bhl", qn, kv) + torch.einsum("bhd,bld->bhl", qp, pe)) * 0.3, -1)
+    assert torch.allclose(o, torch.einsum("bhl,bld->bhd", s, kv), atol=1e-5)
