@@ -813,3 +813,26 @@ def GetModelTypeFromFile(path: str) -> str:
     from ..loader import flm
 
     return str(flm.read_flm(path)[0].get("model_type", ""))
+
+
+_step3p5_tables: dict = {}
+
+
+def Step3p5QKVRMSNormRopeSplitAppendPagedCache(qkv, q_norm_w, k_norm_w, positions, slots, k_pool, v_pool, q_heads, k_heads, head_dim,
+                                               rotary_dim, eps, rope_theta, use_llama3=False, llama3_factor=1.0,
+                                               llama3_original_max_position=8192, llama3_low_freq_factor=1.0,
+                                               llama3_high_freq_factor=4.0, max_positions=131072):
+    """Step-3.5 form of the fused QKV post-processing: per-head RMSNorm of Q and K with zero-centred weights (``1 + w``),
+    partial rotary embedding with optional Llama-3 frequency scaling, K / V appended to the paged pools.  The same kernel as
+    ``QKVRMSNormRopeSplitAppendPagedCache``; the scaling only changes the cos / sin table (cached per setting)."""
+    key = (rotary_dim, float(rope_theta), bool(use_llama3), float(llama3_factor), float(llama3_original_max_position),
+           float(llama3_low_freq_factor), float(llama3_high_freq_factor), int(max_positions), str(qkv.device))
+    if key not in _step3p5_tables:
+        scaling = None
+        if use_llama3:
+            scaling = {"rope_type": "llama3", "factor": llama3_factor, "original_max_position_embeddings": llama3_original_max_position,
+                       "low_freq_factor": llama3_low_freq_factor, "high_freq_factor": llama3_high_freq_factor}
+        _step3p5_tables[key] = A.build_rope_tables(rotary_dim, max_positions, rope_theta, scaling, device=qkv.device)
+    cos, sin = _step3p5_tables[key]
+    return A.qkv_post(qkv, positions, slots, k_pool, v_pool, q_heads, k_heads, head_dim, cos, sin, A.ROPE_NEOX, rotary_dim, q_norm_w, k_norm_w,
+                      eps, 1.0)
