@@ -91,6 +91,7 @@ class FusedComm:
         self.h_buf = self.arena[self.off_h:self.off_h + rows * hidden * 2].view(dtype).view(rows, hidden)
         self.x_buf = self.arena[self.off_x:self.off_x + rows * hidden * 2].view(dtype).view(rows, hidden)
         self.trace = False          # True: kernels stamp their phases (read back with read_trace)
+        self.poison = os.environ.get("FB_ARENA_POISON", "0") == "1"
 
     # ---------------------------------------------------------------------------------------------
     def usable(self, M: int, N: int) -> bool:
@@ -104,6 +105,17 @@ class FusedComm:
         """Place the (replicated) residual stream rows into the arena; returns the arena view."""
         B.flush_pending_wait()
         M = h.shape[0]
+        if self.poison:
+            # debug aid: everything a forward pass may read from the arena without having written it first becomes NaN
+            # (0xFF bytes are NaN in bf16 / fp16 / fp32), so a stale partial slot or a row that was never broadcast shows up
+            # in the logits instead of passing as plausible old data.  All ranks do this at the same point of the step.
+            torch.cuda.synchronize()
+            dist.barrier()
+            self.arena[self.off_part:self.off_amax].fill_(0xFF)
+            if self.max_big_m:
+                self.arena[self.off_src:self.off_src + self.max_big_m * self.hidden * 2].fill_(0xFF)
+            torch.cuda.synchronize()
+            dist.barrier()
         v = self.h_buf[:M]
         v.copy_(h)
         return v

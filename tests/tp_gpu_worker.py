@@ -118,7 +118,11 @@ def main():
     cfg = preset("tiny-llama")
     tp = TPInfo(rank, world, TPComm(rank, world, dev))
     tp.comm.fused = symm.FusedComm(tp.comm, cfg.hidden_size, 16, cfg.hidden_size, torch.bfloat16, use_multicast=use_mc, max_big_m=1024)
+    tp.comm.fused.poison = True          # stale arena reads would turn the logits into NaN
     m = random_init(cfg, dev, torch.bfloat16, tp=tp, std=0.05)
+    eng = LLMEngine(m, EngineConfig(max_batch=8, max_context=1024, use_cuda_graph=False), num_pages=64)
+    assert eng.generate([list(range(3, 40))], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0] is not None
+    tp.comm.fused.poison = False
     eng = LLMEngine(m, EngineConfig(max_batch=8, max_context=1024), num_pages=64)
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 130, 200)]
