@@ -121,7 +121,12 @@ def main():
     tp.comm.fused.poison = True          # stale arena reads would turn the logits into NaN
     m = random_init(cfg, dev, torch.bfloat16, tp=tp, std=0.05)
     eng = LLMEngine(m, EngineConfig(max_batch=8, max_context=1024, use_cuda_graph=False), num_pages=64)
-    assert eng.generate([list(range(3, 40))], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0] is not None
+    hp = eng.launch(list(range(3, 300)), GenerationConfig(max_new_tokens=3, ignore_eos=True, output_logits=True))      # prefill-sized, then decode
+    rp = eng.requests[hp]
+    while not rp.finished():
+        eng.step()
+        if rp.last_logits is not None:
+            assert torch.isfinite(rp.last_logits).all(), "a poisoned arena region reached the logits"
     tp.comm.fused.poison = False
     eng = LLMEngine(m, EngineConfig(max_batch=8, max_context=1024), num_pages=64)
     g = torch.Generator().manual_seed(1)
