@@ -772,9 +772,11 @@ def ApplyDeviceMap(device_map: dict, layer: int, n_layers: int) -> str:
     return SelectDeviceFromMap(device_map, layer, n_layers)
 
 
-def SetCurrentThreadExecutor(_executor=None):
-    """One executor serves the process here (kernels launch on the calling thread's current CUDA stream)."""
-    return None
+def SetCurrentThreadExecutor(executor=None):
+    """Install the executor ``ops.executor.GetExecutor`` returns (device order, forced placement, operand migration)."""
+    from . import executor as E
+
+    E.SetCurrentThreadExecutor(executor)
 
 
 def ClearAllPagedCacheManagers():

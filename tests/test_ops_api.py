@@ -191,3 +191,26 @@ def test_adapter_softmax_and_settings_names():
     o = api.MergeMLA(qn, qp, kv, pe, None, 0.3)
     s = torch.softmax((torch.einsum("bhd,bld->bhl", qn, kv) + torch.einsum("bhd,bld->bhl", qp, pe)) * 0.3, -1)
     assert torch.allclose(o, torch.einsum("bhl,bld->bhd", s, kv), atol=1e-5)
+
+
+def test_executor_device_order_and_migration():
+    from fastllm_b200.ops import executor as E
+
+    ex = E.Executor([E.Device("cpu", ops={"Linear", "Softmax"}), E.Device("cpu")])
+    x, w = torch.randn(3, 8), torch.randn(5, 8)
+    y = ex.Run("Linear", x, w)
+    assert torch.allclose(y, x @ w.t(), atol=1e-5)
+    assert ex.Run("Silu", x).shape == x.shape                 # not in the first device's set: falls through to the second
+    assert ex.profiler["Linear"][0] == 1 and "Silu" in ex.profiler
+    ex.SetFirstDevice("cpu")
+    assert ex.GetFirstDeviceType() == "cpu" and ex.HasDevice("cpu") and not ex.HasDevice("cuda") and ex.GetDeviceIds("cpu") == [0, 0]
+    assert ex.CanRunOnFirstDevice("Linear", x, w)
+    with pytest.raises(RuntimeError):
+        ex.RunOnDevice("cuda", "Linear", x, w)
+    with pytest.raises(RuntimeError):
+        ex.Run("NoSuchOperator", x)
+    moved = E.ToDevice({"a": [x, 3], "b": (w,)}, "cpu")
+    assert moved["a"][0] is x and moved["a"][1] == 3
+    assert "Linear" in ex.PrintProfiler()
+    ex.ClearProfiler()
+    assert not ex.profiler
