@@ -16,6 +16,7 @@ import torch
 import torch.nn.functional as F
 
 from . import _lib
+from . import basic as B
 from .basic import _ptr, _stream
 from .quant import LinearWeight
 
@@ -216,17 +217,32 @@ def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
     page_len = lat_pool.shape[1]
     cu = fb.cu_q_host if fb.cu_q_host is not None else fb.cu_q.tolist()
     kv_lens = fb.kv_lens.tolist()
+    on_tc = _MLA_KERNEL and q_full.is_cuda and q_full.dtype in (torch.float16, torch.bfloat16) and Dq % 64 == 0 and lora % 8 == 0
     for b in range(len(cu) - 1):
         q0, q1 = cu[b], cu[b + 1]
         if q1 == q0:
             continue
         L = kv_lens[b]
         npg = (L + page_len - 1) // page_len
-        lat = lat_pool[fb.page_table[b, :npg].long()].reshape(-1, Dq)[:L].float()
+        lat16 = lat_pool[fb.page_table[b, :npg].long()].reshape(-1, Dq)
+        nq = q1 - q0
+        qpos = torch.arange(L - nq, L, device=q_full.device)
+        if on_tc:
+            # Prefill: every head attends to the SAME latent rows, so the heads fold into the row dimension and both
+            # contractions are plain GEMMs on the tensor-core kernels: S[(q, h), k] = Q' . lat^T with fp32 output, softmax in
+            # fp32, O = P . lat[:, :lora].  Keys are padded to a multiple of 64 (their probabilities are exactly zero).
+            Lp = (L + 63) // 64 * 64
+            latp = lat16[:Lp] if lat16.shape[0] >= Lp else torch.cat([lat16, lat16.new_zeros(Lp - lat16.shape[0], Dq)])
+            s = B.linear(q_full[q0:q1].reshape(nq * H, Dq), latp.contiguous(), out_f32=True).view(nq, H, Lp)
+            kpos = torch.arange(Lp, device=s.device)
+            s = (s * scale).masked_fill_((kpos[None, :] > qpos[:, None])[:, None, :], float("-inf"))
+            p = torch.softmax(s, dim=-1).to(q_full.dtype).view(nq * H, Lp)
+            out[q0:q1] = B.linear(p, latp[:, :lora].t().contiguous()).view(nq, H, lora)
+            continue
+        lat = lat16[:L].float()
         s = torch.einsum("qhd,kd->hqk", q_full[q0:q1].float(), lat) * scale
-        qpos = torch.arange(L - (q1 - q0), L, device=s.device)[:, None]
         kpos = torch.arange(L, device=s.device)[None, :]
-        s = s.masked_fill(kpos > qpos, float("-inf"))
+        s = s.masked_fill(kpos > qpos[:, None], float("-inf"))
         p = torch.softmax(s, dim=-1)
         out[q0:q1] = torch.einsum("hqk,kl->qhl", p, lat[:, :lora]).to(out.dtype)
     return out

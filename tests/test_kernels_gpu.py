@@ -417,6 +417,44 @@ def test_mla_decode(H):
     assert torch.equal(out, out2)
 
 
+def test_mla_prefill_on_gemm_kernels():
+    """Absorbed MLA prefill (heads folded into GEMM rows, both contractions on the tensor-core GEMM kernels, chunked prefill
+    with earlier context) vs the fp32 evaluation."""
+    from types import SimpleNamespace
+
+    from fastllm_b200.ops import moe as MOE
+
+    torch.manual_seed(12)
+    dt = torch.bfloat16
+    H = 16
+    new = [5, 130, 64, 300]                  # new tokens per request
+    ctx = [5, 130, 200, 1000]                # total length after this chunk (>= new: the third and fourth continue a context)
+    Bn = len(new)
+    n_pages = sum((l + 127) // 128 for l in ctx) + 1
+    max_p = max((l + 127) // 128 for l in ctx)
+    pt = torch.zeros(Bn, max_p, dtype=torch.int32)
+    perm = torch.randperm(n_pages)
+    c = 0
+    lat = torch.full((n_pages, 128, 1, 576), 2.0, dtype=dt)
+    for b, l in enumerate(ctx):
+        n = (l + 127) // 128
+        pt[b, :n] = perm[c:c + n].int()
+        c += n
+        for i in range(n):
+            k = min(128, l - i * 128)
+            lat[pt[b, i], :k, 0] = (torch.randn(k, 576) * 0.5).to(dt)
+    cu = [0]
+    for n in new:
+        cu.append(cu[-1] + n)
+    q = (torch.randn(cu[-1], H, 576) * 0.5).to(dt)
+    seq = torch.tensor(ctx, dtype=torch.int32)
+    mk = lambda dev: SimpleNamespace(is_decode=False, cu_q_host=cu, cu_q=torch.tensor(cu), kv_lens=seq.to(dev), page_table=pt.to(dev))
+    ref = MOE.mla_paged_attention(q.float(), lat.float(), mk("cpu"), 0.07, 512)
+    out = MOE.mla_paged_attention(q.to(DEV), lat.to(DEV), mk(DEV), 0.07, 512)
+    _lib.check_device_errors()
+    _close(out.float().cpu(), ref, 3e-2, 3e-2, "mla prefill on GEMM kernels", fro=1e-2)
+
+
 def _fp8_ref(x, lw):
     """What the W8A8 kernel computes: activations rounded to e4m3 per (token, 128-wide k block), weights as stored."""
     from fastllm_b200.ops import quant as Q
