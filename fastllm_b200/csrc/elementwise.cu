@@ -415,6 +415,62 @@ __global__ void glu_act_kernel(const uint16_t* __restrict__ x, uint16_t* __restr
 }
 
 // ------------------------------------------------------------------------------------------------
+// Causal row softmax for attention evaluated as two GEMMs (MLA prefill: rows = (query, head) pairs, columns = keys):
+//   P[r, k] = softmax_k(scale * S[r, k]) over k <= first_pos + r / heads, 0 beyond (also over the padded columns), 16-bit out.
+// One CTA per row; the row is read once (held in registers up to 8192 keys, re-read from L2 beyond that).
+// ------------------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(256) softmax_causal_rows_kernel(const float* __restrict__ S, int lds, uint16_t* __restrict__ P, int ldp,
+                                                                  int cols, int heads, int first_pos, float scale) {
+  __shared__ float red[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int r = blockIdx.x, tid = threadIdx.x;
+  int limit = first_pos + r / heads + 1;                 // keys [0, limit) are visible
+  if (limit > cols) limit = cols;
+  const float* row = S + (size_t)r * lds;
+  constexpr int CACHE = 32;                              // 256 threads x 32 = 8192 keys in registers
+  float v[CACHE];
+  float mx = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < CACHE; ++i) {
+    const int k = tid + i * 256;
+    v[i] = k < limit ? row[k] * scale : -INFINITY;
+    mx = fmaxf(mx, v[i]);
+  }
+  for (int k = tid + CACHE * 256; k < limit; k += 256) mx = fmaxf(mx, row[k] * scale);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) red[tid >> 5] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(fmaxf(red[0], red[1]), fmaxf(red[2], red[3])), fmaxf(fmaxf(red[4], red[5]), fmaxf(red[6], red[7])));
+  __syncthreads();
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < CACHE; ++i) {
+    v[i] = (tid + i * 256) < limit ? __expf(v[i] - mx) : 0.f;
+    sum += v[i];
+  }
+  for (int k = tid + CACHE * 256; k < limit; k += 256) sum += __expf(row[k] * scale - mx);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if ((tid & 31) == 0) red[tid >> 5] = sum;
+  __syncthreads();
+  sum = red[0] + red[1] + red[2] + red[3] + red[4] + red[5] + red[6] + red[7];
+  const float inv = sum > 0.f ? 1.0f / sum : 0.f;
+  uint16_t* out = P + (size_t)r * ldp;
+#pragma unroll
+  for (int i = 0; i < CACHE; ++i) {
+    const int k = tid + i * 256;
+    if (k < cols) out[k] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v[i] * inv)) : __half_as_ushort(__float2half_rn(v[i] * inv));
+  }
+  for (int k = tid + CACHE * 256; k < cols; k += 256) {
+    const float pv = k < limit ? __expf(row[k] * scale - mx) * inv : 0.f;
+    out[k] = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(pv)) : __half_as_ushort(__float2half_rn(pv));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
 // Embedding gather: out[m, :] = table[ids[m], :]
 // ------------------------------------------------------------------------------------------------
 __global__ void embedding_kernel(const int* __restrict__ ids, const uint16_t* __restrict__ table, uint16_t* __restrict__ out,
@@ -666,6 +722,17 @@ extern "C" int fb_glu_act(const void* x, void* y, int M, int I, int ldx, int ldy
     default: FB_GLU(3) break;
   }
 #undef FB_GLU
+  return (int)cudaGetLastError();
+}
+
+// rows = queries x heads (query-major); row r sees keys [0, first_pos + r / heads]; P is zero elsewhere (all `cols` columns are written)
+extern "C" int fb_softmax_causal_rows(const float* S, int lds, void* P, int ldp, int rows, int cols, int heads, int first_pos, float scale,
+                                      int dtype, void* stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (heads <= 0 || (dtype != 0 && dtype != 1)) return -1;
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) launch_k(softmax_causal_rows_kernel<true>, dim3(rows), dim3(256), 0, s, 0, S, lds, (uint16_t*)P, ldp, cols, heads, first_pos, scale);
+  else launch_k(softmax_causal_rows_kernel<false>, dim3(rows), dim3(256), 0, s, 0, S, lds, (uint16_t*)P, ldp, cols, heads, first_pos, scale);
   return (int)cudaGetLastError();
 }
 

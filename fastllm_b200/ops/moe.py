@@ -234,9 +234,10 @@ def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
             Lp = (L + 63) // 64 * 64
             latp = lat16[:Lp] if lat16.shape[0] >= Lp else torch.cat([lat16, lat16.new_zeros(Lp - lat16.shape[0], Dq)])
             s = B.linear(q_full[q0:q1].reshape(nq * H, Dq), latp.contiguous(), out_f32=True).view(nq, H, Lp)
-            kpos = torch.arange(Lp, device=s.device)
-            s = (s * scale).masked_fill_((kpos[None, :] > qpos[:, None])[:, None, :], float("-inf"))
-            p = torch.softmax(s, dim=-1).to(q_full.dtype).view(nq * H, Lp)
+            p = torch.empty((nq * H, Lp), device=s.device, dtype=q_full.dtype)
+            rc = _lib.kernels().fb_softmax_causal_rows(_ptr(s), Lp, _ptr(p), Lp, nq * H, Lp, H, L - nq, float(scale),
+                                                       B.dtype_code(q_full.dtype), _stream())
+            _lib.check(rc, "fb_softmax_causal_rows")
             out[q0:q1] = B.linear(p, latp[:, :lora].t().contiguous()).view(nq, H, lora)
             continue
         lat = lat16[:L].float()
