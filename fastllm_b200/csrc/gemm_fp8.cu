@@ -13,6 +13,7 @@
 #include "gemm_smallm.cuh"
 #include "launch.h"
 #include "tmap.h"
+#include "comm.cuh"
 
 FB_DEFINE_ERROR_API(gemm_fp8)
 
@@ -178,6 +179,21 @@ template <int MPAD, bool BF16>
 __global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p, const Fp8Scales sc) {
   gemm_fp8_device<MPAD, BF16>(tmW, tmX, p, sc);
+}
+
+// Row-parallel projection of a tensor-parallel rank FUSED with the collective behind it: the epilogue pushes the fp32 partial
+// rows to their owners' arenas, then the shared tail (csrc/comm.cuh) meets the other ranks, reduces, adds the residual,
+// normalises and broadcasts -- one launch instead of GEMM + all-reduce kernel.
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
+gemm_fp8_ar_norm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams g,
+                        const Fp8Scales sc, const ArNormParams p) {
+  const uint64_t t_start = p.trace ? globaltimer_ns() : 0;
+  gemm_fp8_device<MPAD, BF16>(tmW, tmX, g, sc);
+  // every thread has passed the dependency wait inside the GEMM: the expect word written by the previous collective is final
+  const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) reinterpret_cast<uint64_t*>(p.c.local + OFF_TRACE)[0] = t_start;
+  ar_norm_tail<BF16>(p, base, blockIdx.y, gridDim.y, blockIdx.x, gridDim.x, KID_GEMM_AR);
 }
 
 // Grouped (mixture-of-experts) variant over the expert-sorted activation buffer: blockIdx.z = expert * chunks + chunk.
@@ -364,6 +380,80 @@ static cudaError_t launch_fp8(const CUtensorMap& tmW, const CUtensorMap& tmX, co
   attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, sc);
+}
+
+template <int MPAD, bool BF16>
+static cudaError_t launch_fp8_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& g, const Fp8Scales& sc,
+                                 const ArNormParams& p, int nsplit, int n_tiles, cudaStream_t stream) {
+  using Cfg = Fp8Cfg<MPAD>;
+  auto kern = gemm_fp8_ar_norm_kernel<MPAD, BF16>;
+  static DeviceOnce configured;
+  if (configured.need()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
+  // all CTAs wait for each other across ranks: they must all be resident at once
+  int max_clusters = 0;
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0 || n_tiles > max_clusters)
+    return cudaErrorLaunchOutOfResources;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, g, sc, p);
+}
+
+// Fused form of fb_gemm_fp8 for a row-parallel projection under tensor parallelism (see fb_gemm_ar_norm in comm.cu for the arena
+// arguments and `flags`: bit 0 residual, bit 1 trace, bit 2 deferred all-gather wait).  N = hidden size, M <= 128.
+// Returns cudaErrorLaunchOutOfResources (701) when the grid cannot be co-resident: the caller runs GEMM + collective then.
+extern "C" int fb_gemm_fp8_ar_norm(const void* xq, int ldq, const float* a_scale, int ld_a, const void* Wq, const float* w_scale,
+                                   const void* bias, int M, int N, int K, void* arena_local, void* arena_mc, void* const* peers, int rank,
+                                   int tp, unsigned long long off_part, unsigned long long off_h, unsigned long long off_x,
+                                   const void* ln_w, int flags, float eps, float unit_offset, int dtype, void* stream_) {
+  if (M <= 0 || M > 128 || K % 128 != 0 || N % 8 != 0 || N > 18432 || tp > MAX_TP || tp < 1) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  int mpad = 16;
+  while (mpad < M) mpad <<= 1;
+  const int n_tiles = (N + 127) / 128;
+  const int kb_total = K / 128;
+  const int slots = sm_count() * (mpad <= 64 ? 2 : 1);
+  int nsplit = 1;
+  while (nsplit < 8 && n_tiles * nsplit * 2 <= slots && kb_total / (nsplit * 2) >= 4) nsplit <<= 1;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, Wq, (uint64_t)N, (uint64_t)K, (uint64_t)K, 128, 128, 1, 3)) return -2;
+  if (!make_tmap_2d(&tmX, xq, (uint64_t)M, (uint64_t)K, (uint64_t)ldq, mpad, 128, 1, 3)) return -2;
+  GemmParams g = {};
+  g.bias = bias; g.M = M; g.N = N; g.K = K;
+  g.kb_total = kb_total; g.kb_per_split = (kb_total + nsplit - 1) / nsplit; g.flags = GEMM_OUT_F32 | (bias ? GEMM_BIAS : 0);
+  g.idesc = make_idesc(0, 0, 0, 0, 128, mpad);
+  fill_scatter(g, arena_local, peers, off_part, M, N, rank, tp);
+  Fp8Scales sc;
+  sc.w_scale = w_scale; sc.a_scale = a_scale; sc.ld_a = ld_a;
+  ArNormParams p;
+  fill_ar_norm(p, arena_local, arena_mc, peers, rank, tp, off_part, off_h, off_x, ln_w, M, N, flags, eps, unit_offset);
+  cudaError_t e;
+#define FB_F8A(MP)                                                                                       \
+  e = dtype == 1 ? launch_fp8_ar<MP, true>(tmW, tmX, g, sc, p, nsplit, n_tiles, stream)                   \
+                 : launch_fp8_ar<MP, false>(tmW, tmX, g, sc, p, nsplit, n_tiles, stream);                 \
+  break;
+  for (;;) {            // a k-split whose clusters cannot all be resident at once is halved until they can
+    g.kb_per_split = (kb_total + nsplit - 1) / nsplit;
+    switch (mpad) {
+      case 16: FB_F8A(16)
+      case 32: FB_F8A(32)
+      case 64: FB_F8A(64)
+      default: FB_F8A(128)
+    }
+    if (e != cudaErrorLaunchOutOfResources || nsplit == 1) break;
+    nsplit >>= 1;
+  }
+#undef FB_F8A
+  return (int)e;
 }
 
 // xq: [M, K] e4m3 (row stride ldq bytes), a_scale: [K / 128, ld_a]; Wq: [N, K] e4m3, w_scale: [ceil(N / 128), K / 128].

@@ -17,6 +17,7 @@
 #include "gemm_smallm.cuh"
 #include "launch.h"
 #include "tmap.h"
+#include "comm.cuh"
 
 FB_DEFINE_ERROR_API(gemm_i8)
 
@@ -291,6 +292,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
   gemm_i8_device<MPAD, BF16, WK>(tmW, tmX, p, sc);
 }
 
+// Row-parallel projection of a tensor-parallel rank fused with the collective behind it (see gemm_fp8_ar_norm_kernel).
+template <int MPAD, bool BF16, int WK>
+__global__ void __launch_bounds__((I8Cfg<MPAD, WK>::THREADS), (MPAD <= 64 ? 2 : 1))
+gemm_i8_ar_norm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams g,
+                       const I8Scales sc, const ArNormParams p) {
+  const uint64_t t_start = p.trace ? globaltimer_ns() : 0;
+  gemm_i8_device<MPAD, BF16, WK>(tmW, tmX, g, sc);
+  const uint32_t base = *reinterpret_cast<volatile uint32_t*>(p.c.local + OFF_EXPECT);
+  if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) reinterpret_cast<uint64_t*>(p.c.local + OFF_TRACE)[0] = t_start;
+  ar_norm_tail<BF16>(p, base, blockIdx.y, gridDim.y, blockIdx.x, gridDim.x, KID_GEMM_AR);
+}
+
 struct I8GroupInfo {
   const int* counts; const int* offsets;
   int rows_per_chunk, chunks, n_rows_w;
@@ -423,6 +436,88 @@ static int dispatch_i8(int mpad, int dtype, const CUtensorMap& tmW, const CUtens
   }
 #undef FB_I8
   return (int)e;
+}
+
+template <int MPAD, bool BF16, int WK>
+static cudaError_t launch_i8_ar(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& g, const I8Scales& sc,
+                                const ArNormParams& p, int nsplit, int n_tiles, cudaStream_t stream) {
+  using Cfg = I8Cfg<MPAD, WK>;
+  auto kern = gemm_i8_ar_norm_kernel<MPAD, BF16, WK>;
+  static DeviceOnce configured;
+  if (configured.need()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, n_tiles, 1);
+  cfg.blockDim = dim3(Cfg::THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr; cfg.numAttrs = add_pdl_attr(attr, 1);
+  int max_clusters = 0;                 // all CTAs wait for each other across ranks: they must all be resident at once
+  if (cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg) != cudaSuccess || max_clusters <= 0 || n_tiles > max_clusters)
+    return cudaErrorLaunchOutOfResources;
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, g, sc, p);
+}
+
+template <int WK>
+static int dispatch_i8_ar(int mpad, int dtype, const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& g, const I8Scales& sc,
+                          const ArNormParams& p, int nsplit, int n_tiles, cudaStream_t stream) {
+  cudaError_t e;
+#define FB_I8A(MP)                                                                                                 \
+  e = dtype == 1 ? launch_i8_ar<MP, true, WK>(tmW, tmX, g, sc, p, nsplit, n_tiles, stream)                          \
+                 : launch_i8_ar<MP, false, WK>(tmW, tmX, g, sc, p, nsplit, n_tiles, stream);                        \
+  break;
+  switch (mpad) {
+    case 16: FB_I8A(16)
+    case 32: FB_I8A(32)
+    case 64: FB_I8A(64)
+    default: FB_I8A(128)
+  }
+#undef FB_I8A
+  return (int)e;
+}
+
+// Fused form of fb_gemm_i8 (plain, not grouped) for a row-parallel projection under tensor parallelism; arena arguments and
+// `flags` as in fb_gemm_ar_norm (comm.cu).  Returns 701 when the grid cannot be co-resident.
+extern "C" int fb_gemm_i8_ar_norm(const void* xq, int ldq, const float* a_scale, const float* a_sum, int ld_a, const void* Wq,
+                                  const float* w_scale, const float* w_zero, const void* bias, int M, int N, int K, int wkind,
+                                  void* arena_local, void* arena_mc, void* const* peers, int rank, int tp, unsigned long long off_part,
+                                  unsigned long long off_h, unsigned long long off_x, const void* ln_w, int flags, float eps,
+                                  float unit_offset, int dtype, void* stream_) {
+  if (M <= 0 || M > 128 || K % 128 != 0 || N % 8 != 0 || N > 18432 || tp > MAX_TP || tp < 1) return -1;
+  if (wkind != WK_INT8 && wkind != WK_INT4G) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const int kb_total = K / 128;
+  const int wbytes = wkind == WK_INT4G ? K / 2 : K;
+  int mpad = 16;
+  while (mpad < M) mpad <<= 1;
+  const int n_tiles = (N + 127) / 128;
+  const int slots = sm_count() * (mpad <= 64 ? 2 : 1);
+  int nsplit = 1;
+  while (nsplit < 8 && n_tiles * nsplit * 2 <= slots && kb_total / (nsplit * 2) >= 4) nsplit <<= 1;
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, Wq, (uint64_t)N, (uint64_t)wbytes, (uint64_t)wbytes, 128, wkind == WK_INT4G ? 64 : 128, 1, wkind == WK_INT4G ? 0 : 3)) return -2;
+  if (!make_tmap_2d(&tmX, xq, (uint64_t)M, (uint64_t)K, (uint64_t)ldq, mpad, 128, 1, 3)) return -2;
+  GemmParams g = {};
+  g.bias = bias; g.M = M; g.N = N; g.K = K; g.kb_total = kb_total; g.kb_per_split = (kb_total + nsplit - 1) / nsplit;
+  g.flags = GEMM_OUT_F32 | (bias ? GEMM_BIAS : 0);
+  g.idesc = make_idesc_i8(128, mpad);
+  fill_scatter(g, arena_local, peers, off_part, M, N, rank, tp);
+  I8Scales sc;
+  sc.w_scale = w_scale; sc.w_zero = w_zero; sc.a_scale = a_scale; sc.a_sum = a_sum; sc.ld_a = ld_a; sc.n_rows = N;
+  ArNormParams p;
+  fill_ar_norm(p, arena_local, arena_mc, peers, rank, tp, off_part, off_h, off_x, ln_w, M, N, flags, eps, unit_offset);
+  for (;;) {            // a k-split whose clusters cannot all be resident at once is halved until they can
+    g.kb_per_split = (kb_total + nsplit - 1) / nsplit;
+    const int rc = wkind == WK_INT8 ? dispatch_i8_ar<WK_INT8>(mpad, dtype, tmW, tmX, g, sc, p, nsplit, n_tiles, stream)
+                                    : dispatch_i8_ar<WK_INT4G>(mpad, dtype, tmW, tmX, g, sc, p, nsplit, n_tiles, stream);
+    if (rc != (int)cudaErrorLaunchOutOfResources || nsplit == 1) return rc;
+    nsplit >>= 1;
+  }
 }
 
 // wkind: 1 = int8 per channel (Wq int8 = q - 128, w_scale [N], w_zero = zero - 128 [N]);

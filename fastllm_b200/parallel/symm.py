@@ -35,6 +35,8 @@ _lib.register_sigs({
     "fb_argmax_merge": [P, P, P, I, P, P, P, I, I, ULL, P],
     "fb_moe_combine_ar_norm": [P, P, P, P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
     "fb_comm_wait": [P, P],
+    "fb_gemm_fp8_ar_norm": [P, I, P, I, P, P, P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
+    "fb_gemm_i8_ar_norm": [P, I, P, P, I, P, P, P, P, I, I, I, I, P, P, P, I, I, ULL, ULL, ULL, P, I, F, F, I, P],
     "fb_gemm_ar_norm_big": [P, P, P, I, I, I, I, I, P, P, P, I, I, ULL, ULL, ULL, ULL, P, I, F, F, I, P],
     "fb_ar_norm_big": [P, I, I, I, P, P, P, I, I, ULL, ULL, ULL, ULL, P, I, F, F, I, P],
 }, ["comm", "comm_prefill"])
@@ -140,6 +142,8 @@ class FusedComm:
         on this stream waits inside its GEMM, after its weight prefetch (``ops.basic.set_pending_wait``)."""
         M, K = x.shape
         N = w.n
+        if w.kind != "dense" and self.usable(M, N) and not self._big(M):
+            return self._gemm_ar_norm_quant(w, x, ln_w, eps, unit_offset, has_residual, defer)
         if w.kind != "dense" or not self.usable(M, N) or (w.bias is not None and self.rank != 0 and False):
             return None
         wt = w.w if w.w.dtype == x.dtype else w.w.to(x.dtype)
@@ -161,6 +165,48 @@ class FusedComm:
             if rc == 701:      # cudaErrorLaunchOutOfResources: grid cannot be co-resident -> caller uses the unfused path
                 return None
             _lib.check(rc, "fb_gemm_ar_norm")
+        self._after_launch(defer)
+        return self.h_buf[:M], self.x_buf[:M]
+
+    def _gemm_ar_norm_quant(self, w, x, ln_w, eps, unit_offset, has_residual, defer):
+        """Quantised row-parallel weights on the 8-bit-activation tensor-core kernels (fp8 W8A8, int8 / int4-group with int8
+        activations), fused with the same collective tail.  None: the shape is outside those kernels (caller: GEMM, then
+        ``ar_norm``)."""
+        from ..ops import quant_gemm as QG
+
+        M, K = x.shape
+        N = w.n
+        if x.dtype not in (torch.float16, torch.bfloat16) or K % 128 != 0 or x.stride(-1) != 1 or x.stride(0) % 4 != 0 or w.adapters:
+            return None
+        if os.environ.get("FB_FUSED_QUANT_AR", "1") == "0":
+            return None
+        pre = getattr(x, "fb_quant", None)
+        bias = w.bias if self.rank == 0 else None
+        if bias is not None and bias.dtype != x.dtype:
+            bias = bias.to(x.dtype)
+        lib = _lib.kernels()
+        arena = (ctypes.c_void_p(self.local), ctypes.c_void_p(self.mc), self.peers, self.rank, self.tp, self.off_part, self.off_h, self.off_x,
+                 _ptr(ln_w), self._flags(has_residual, defer), float(eps), float(unit_offset), dtype_code(x.dtype), _stream())
+        if w.kind == "fp8" and QG.FP8_NATIVE and M <= 128:
+            if pre is not None and pre[0] == 2 and pre[1].shape == (M, K):
+                _, xq, sa, _xs, ld_a = pre
+            else:
+                xq, sa, ld_a = QG.quant_act_fp8(x)
+            rc = lib.fb_gemm_fp8_ar_norm(_ptr(xq), K, _ptr(sa), ld_a, _ptr(w.w), _ptr(QG._kernel_tensors(w)[0]), _ptr(bias), M, N, K, *arena)
+        elif QG.uses_int_a8(w) and M <= QG.INT_A8_MAX_M[w.kind]:
+            wq, sc, zr, kind = QG._a8_tensors(w)
+            if pre is not None and pre[0] == 1 and pre[1].shape == (M, K):
+                _, xq, sa, xs, ld_a = pre
+            else:
+                xq, sa, xs, ld_a = QG.quant_act_i8(x)
+            rc = lib.fb_gemm_i8_ar_norm(_ptr(xq), K, _ptr(sa), _ptr(xs), ld_a, _ptr(wq), _ptr(sc), _ptr(zr), _ptr(bias), M, N, K, kind, *arena)
+        else:
+            return None
+        if os.environ.get("FB_DEBUG_FUSED") == "1" and self.rank == 0:
+            print(f"[fused quant] kind={w.kind} M={M} N={N} K={K} pre={'yes' if pre is not None else 'no'} rc={rc}", flush=True)
+        if rc == 701:          # the grid cannot be co-resident: unfused path
+            return None
+        _lib.check(rc, "fb_gemm_quant_ar_norm")
         self._after_launch(defer)
         return self.h_buf[:M], self.x_buf[:M]
 

@@ -60,6 +60,31 @@ def main():
         if own.start < M:
             assert (h2[own].float() - ref_h2[own].float()).abs().max().item() < 0.08
         assert (x2.float() - B.rmsnorm_ref(ref_h2, ln, 1e-5)[0].float()).abs().max().item() < 0.08
+    # quantised row-parallel weights: 8-bit-activation tensor-core GEMMs with the same fused tail
+    from fastllm_b200.ops import quant_gemm as QG
+    for kind, (M, K) in (("fp8", (33, 1024)), ("int8", (64, 512)), ("int4g128", (5, 2048)), ("fp8", (64, 512))):
+        x_full = (torch.randn(M, K * world, device=dev) * 0.5).bfloat16()
+        w_full = (torch.randn(H, K * world, device=dev) * 0.03).bfloat16()
+        h0 = torch.randn(M, H, device=dev).bfloat16()
+        ln = (1 + 0.1 * torch.randn(H, device=dev)).bfloat16()
+        xs = x_full[:, rank * K:(rank + 1) * K].contiguous()
+        ws = LinearWeight.from_dense(w_full[:, rank * K:(rank + 1) * K].contiguous(), kind)
+        part = ws(xs).float()                              # the same kernels' unfused result on this rank's shard
+        dist.all_reduce(part)
+        ref_h = (part + h0.float()).bfloat16()
+        ref_x = B.rmsnorm_ref(ref_h, ln, 1e-5)[0]
+        fused.load_h(h0)
+        r = fused.gemm_ar_norm(ws, xs, ln, 1e-5)
+        assert r is not None, f"fused quantised kernel refused {kind} {M}x{K}"
+        h, xn = r
+        torch.cuda.synchronize()
+        _lib.check_device_errors()
+        rows_per = (M + world - 1) // world
+        own = slice(rank * rows_per, min(M, (rank + 1) * rows_per))
+        if own.start < M:
+            assert (h[own].float() - ref_h[own].float()).abs().max().item() < 0.1, kind
+        fro = ((xn.float() - ref_x.float()).norm() / ref_x.float().norm()).item()
+        assert fro < 1.5e-2, (kind, fro)
     # prefill-sized batches: the bandwidth-regime kernels (row blocks of 128 owned round-robin, in-switch reduction when
     # the multicast mapping exists).  Ragged last block, one block fewer than ranks own, narrow and wide hidden sizes.
     for Hb, cases in ((1024, [(600, 512), (1024, 256), (257, 1024), (600, 512)]), (5120, [(300, 256)])):
