@@ -85,9 +85,39 @@ __global__ void attn_decode_plan_kernel(const int* __restrict__ seq_lens, int B,
   if (t == 0) { const int total = offs[B]; *n_work = total < max_items ? total : max_items; }
 }
 
+// One raw page (128 tokens x 128 e4m3 bytes, row-major) -> the fp16 operand tile: two half tiles of 64 dims (16 KB each), a row
+// of a half tile is 128 bytes and its 16-byte chunk j sits at chunk position j ^ (row & 7) (the 128-byte swizzle TMA applies).
+// 128 threads; eight consecutive threads read one raw row, so the loads are conflict-free.
+__device__ __forceinline__ void kv8_convert_page(const uint8_t* __restrict__ raw, uint8_t* __restrict__ tile, int ctid) {
+  uint4 r[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) r[i] = *reinterpret_cast<const uint4*>(raw + (size_t)(ctid + i * 128) * 16);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int idx = ctid + i * 128, row = idx >> 3, c16 = idx & 7;       // c16: 16 dims of the row
+    const uint32_t w[4] = {r[i].x, r[i].y, r[i].z, r[i].w};
+    uint32_t h[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h[2 * j]) : "h"((unsigned short)(w[j] & 0xFFFFu)));
+      asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h[2 * j + 1]) : "h"((unsigned short)(w[j] >> 16)));
+    }
+    uint8_t* dst = tile + (c16 >> 2) * (AD_K_BYTES / 2) + row * 128;
+    const int cc = (c16 & 3) * 2, sw = row & 7;
+    *reinterpret_cast<uint4*>(dst + ((cc ^ sw) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+    *reinterpret_cast<uint4*>(dst + (((cc + 1) ^ sw) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+  }
+}
+
 // GP = query heads per KV head rounded up to a power of two: the softmax warps only touch GP of the 16 MMA columns.
-template <bool BF16, int AD_STAGES, int GP>
-__global__ void __launch_bounds__(192, AD_STAGES == 1 ? 3 : 1)
+//
+// KV8: the page pools hold unscaled e4m3 bytes (half the cache traffic).  TMA brings a raw page (128 tokens x 128 bytes) into
+// a staging buffer, four extra warps turn it into the 16-bit operand tile -- written in exactly the 128-byte-swizzled layout
+// the 16-bit TMA load would have produced, so the MMA descriptors, the softmax and the epilogue are the same code -- and the
+// next raw page is already in flight while the current one is converted and multiplied.  e4m3 converts exactly to fp16
+// (`cvt.rn.f16x2.e4m3x2`), so this mode computes in fp16: the caller passes fp16 queries.
+template <bool BF16, int AD_STAGES, int GP, bool KV8 = false>
+__global__ void __launch_bounds__(KV8 ? 320 : 192, KV8 ? 2 : (AD_STAGES == 1 ? 3 : 1))
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK32,
                    const __grid_constant__ CUtensorMap tmV32, const AttnDecodeParams p) {
@@ -107,13 +137,24 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   float* red_max = reinterpret_cast<float*>(tmem_slot + 4);      // [4 warps][16]
   float* red_sum = red_max + 64;                                  // [2 parity][4 warps][16]
   int* sh_flag = reinterpret_cast<int*>(red_sum + 128);
+  // KV8: raw page staging (K then V, 16 KB each) behind the barrier block, and its four barriers
+  uint64_t* raw_full_k = reinterpret_cast<uint64_t*>(sh_flag + 2);
+  uint64_t* raw_full_v = raw_full_k + 1;
+  uint64_t* raw_empty_k = raw_full_k + 2;
+  uint64_t* raw_empty_v = raw_full_k + 3;
+  uint8_t* raw_k = p_smem + AD_P_BYTES + 1024;
+  uint8_t* raw_v = raw_k + AD_PAGE * AD_D;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   bool dead = false;
   pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < AD_STAGES; ++s) { mbar_init(&full_k[s], 1); mbar_init(&full_v[s], 1); mbar_init(&empty_k[s], 1); mbar_init(&empty_v[s], 1); }
+    for (int s = 0; s < AD_STAGES; ++s) {
+      // KV8: the operand tiles are completed by the 128 converter threads (plus the producer's arrival for the Q tile)
+      mbar_init(&full_k[s], KV8 ? 129 : 1); mbar_init(&full_v[s], KV8 ? 128 : 1); mbar_init(&empty_k[s], 1); mbar_init(&empty_v[s], 1);
+    }
+    if (KV8) { mbar_init(raw_full_k, 1); mbar_init(raw_full_v, 1); mbar_init(raw_empty_k, 128); mbar_init(raw_empty_v, 128); }
     mbar_init(s_full, 1);
     mbar_init(p_ready, 128);
     mbar_init(o_full, 1);
@@ -155,6 +196,21 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const int page = p.page_table[(size_t)b * p.max_pages + pg];
         const int s = it % AD_STAGES;
         const uint32_t ph = (uint32_t)(it / AD_STAGES) & 1u;
+        if (KV8) {
+          // raw pages first (their staging buffers free up long before the operand tiles do), then Q into the operand stage
+          if (!mbar_wait(raw_empty_k, ph ^ 1u, dead, KID_ATTN_DECODE, 11)) break;
+          mbar_expect_tx(raw_full_k, AD_PAGE * AD_D);
+          tma_load_2d(raw_k, &tmK, raw_full_k, kvh * AD_D, page * AD_PAGE);
+          if (!mbar_wait(raw_empty_v, ph ^ 1u, dead, KID_ATTN_DECODE, 12)) break;
+          mbar_expect_tx(raw_full_v, AD_PAGE * AD_D);
+          tma_load_2d(raw_v, &tmV, raw_full_v, kvh * AD_D, page * AD_PAGE);
+          if (!mbar_wait(&empty_k[s], ph ^ 1u, dead, KID_ATTN_DECODE, 1)) break;
+          uint8_t* qb8 = smem + s * AD_STAGE_BYTES + 2 * AD_K_BYTES;
+          mbar_expect_tx(&full_k[s], AD_Q_BYTES);
+          tma_load_2d(qb8, &tmQ, &full_k[s], 0, b * p.Hq + kvh * p.G);
+          tma_load_2d(qb8 + AD_Q_BYTES / 2, &tmQ, &full_k[s], 64, b * p.Hq + kvh * p.G);
+          continue;
+        }
         if (!mbar_wait(&empty_k[s], ph ^ 1u, dead, KID_ATTN_DECODE, 1)) break;
         uint8_t* kb = smem + s * AD_STAGE_BYTES;
         uint8_t* vb = kb + AD_K_BYTES;
@@ -226,6 +282,27 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     }
     __syncwarp();
+  } else if (KV8 && warp >= 6) {
+    // ---- converter warps: raw e4m3 page -> fp16 operand tile in the swizzled layout of the 16-bit TMA load ----
+    const int ctid = (int)threadIdx.x - 192;
+    int it = 0;
+    for (int w = blockIdx.x; w < total; w += gridDim.x, ++it) {
+      const int s = it % AD_STAGES;
+      const uint32_t ph = (uint32_t)(it / AD_STAGES) & 1u;
+      uint8_t* kb = smem + s * AD_STAGE_BYTES;
+      if (!mbar_wait(raw_full_k, ph, dead, KID_ATTN_DECODE, 13)) break;
+      if (!mbar_wait(&empty_k[s], ph ^ 1u, dead, KID_ATTN_DECODE, 14)) break;       // the previous S MMA is done with the K tile
+      kv8_convert_page(raw_k, kb, ctid);
+      fence_proxy_async_smem();
+      mbar_arrive(&full_k[s]);
+      mbar_arrive(raw_empty_k);
+      if (!mbar_wait(raw_full_v, ph, dead, KID_ATTN_DECODE, 15)) break;
+      if (!mbar_wait(&empty_v[s], ph ^ 1u, dead, KID_ATTN_DECODE, 16)) break;       // the previous PV MMA is done with the V tile
+      kv8_convert_page(raw_v, kb + AD_K_BYTES, ctid);
+      fence_proxy_async_smem();
+      mbar_arrive(&full_v[s]);
+      mbar_arrive(raw_empty_v);
+    }
   } else {
     const int q = warp & 3;                // TMEM lane quarter
     const int t = q * 32 + lane;           // token within page (softmax) / head dim (epilogue)
@@ -452,7 +529,7 @@ extern "C" int fb_attn_decode_plan(const int* seq_lens, int B, int* work, int* n
 
 // Scratch sizes (floats): part_o = B*Hkv*max_splits*G*128, part_ml = B*Hkv*max_splits*G*2.
 // q: [B, Hq, 128] with row stride ld_q elements between requests' heads packed (ld_q == Hq*128 required).
-// k_pool/v_pool: [num_slots, Hkv, 128].  dtype: 0 = fp16, 1 = bf16.
+// k_pool/v_pool: [num_slots, Hkv, 128].  dtype: 0 = fp16, 1 = bf16; 2 / 3 = e4m3 pages with fp16 q and fp16 / bf16 out (fb_attn_decode_opts).
 // counters: [B * Hkv] ints, zero on first use (the kernel leaves them zero); null keeps the separate combine kernel.
 extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void* v_pool, void* out, int ld_out, const int* work,
                                    const int* n_work, const int* page_table, const int* seq_lens, float* part_o, float* part_ml,
@@ -489,18 +566,29 @@ extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void
   const int G = Hq / Hkv;
   if (G > AD_NPAD) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const bool kv8 = dtype == 2 || dtype == 3;          // e4m3 pages, fp16 queries; output fp16 (2) or bf16 (3)
+  const bool kv8_out_bf16 = dtype == 3;
+  if (kv8) dtype = 0;
+  if (kv8 && qmode != 0) return -1;
   CUtensorMap tmK, tmV, tmQ;
-  if (!make_tmap_2d(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
-  if (!make_tmap_2d(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
-  if (!make_tmap_2d(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 64, 2, 3)) return -2;
   CUtensorMap tmK32, tmV32;
-  if (!make_tmap_2d(&tmK32, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
-  if (!make_tmap_2d(&tmV32, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
+  if (kv8) {
+    // raw pages: one box of 128 tokens x 128 bytes, no swizzle (the converter warps build the operand layout)
+    if (!make_tmap_2d(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 128, 1, 0)) return -2;
+    if (!make_tmap_2d(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 128, 1, 0)) return -2;
+    tmK32 = tmK; tmV32 = tmV;
+  } else {
+    if (!make_tmap_2d(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
+    if (!make_tmap_2d(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 64, 2, 3)) return -2;
+    if (!make_tmap_2d(&tmK32, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
+    if (!make_tmap_2d(&tmV32, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
+  }
+  if (!make_tmap_2d(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 64, 2, 3)) return -2;
   AttnDecodeParams p;
   p.work = work; p.n_work = n_work; p.page_table = page_table; p.seq_lens = seq_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.max_pages = max_pages; p.max_splits = max_splits; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
   p.B = B; p.max_items = max_items;
-  p.counters = counters; p.out = reinterpret_cast<uint16_t*>(out); p.ld_out = ld_out; p.clip = 1;
+  p.counters = counters; p.out = reinterpret_cast<uint16_t*>(out); p.ld_out = ld_out; p.clip = kv8 ? 0 : 1;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.softcap = softcap; p.scale = scale;
   const uint32_t f = dtype == 1 ? 1u : 0u;
@@ -537,7 +625,24 @@ extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void
     else if (G <= 8) FB_AD_LAUNCH(BF, 1, 8)                                                                             \
     else FB_AD_LAUNCH(BF, 1, 16)                                                                                        \
   }
-  if (dtype == 1) FB_AD_GP(true) else FB_AD_GP(false)
+#define FB_AD_LAUNCH8(GPV)                                                                                               \
+  {                                                                                                                     \
+    static DeviceOnce cfg8;                                                                                           \
+    if (cfg8.need()) { cudaFuncSetAttribute(attn_decode_kernel<false, 1, GPV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1) + 2 * AD_PAGE * AD_D); } \
+    launch_k<PDL_ATTN>(attn_decode_kernel<false, 1, GPV, true>, dim3(grid_ctas), dim3(320), ad_smem_bytes(1) + 2 * AD_PAGE * AD_D, stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
+    if (counters == nullptr && kv8_out_bf16)                                                                            \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<true, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
+    else if (counters == nullptr)                                                                                       \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<false, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
+  }
+  if (kv8) {
+    if (G <= 1) FB_AD_LAUNCH8(1)
+    else if (G <= 2) FB_AD_LAUNCH8(2)
+    else if (G <= 4) FB_AD_LAUNCH8(4)
+    else if (G <= 8) FB_AD_LAUNCH8(8)
+    else FB_AD_LAUNCH8(16)
+  } else if (dtype == 1) FB_AD_GP(true) else FB_AD_GP(false)
+#undef FB_AD_LAUNCH8
 #undef FB_AD_GP
 #undef FB_AD_LAUNCH
   return (int)cudaGetLastError();

@@ -415,6 +415,38 @@ __global__ void glu_act_kernel(const uint16_t* __restrict__ x, uint16_t* __restr
 }
 
 // ------------------------------------------------------------------------------------------------
+// Append new K / V rows to e4m3 page pools: 16-bit rows [T, row_elems] -> unscaled e4m3 (round to nearest even, saturating at
+// +-448) at pool row slots[t]; rows with a negative slot (padding of a CUDA-graph bucket) are skipped.
+// ------------------------------------------------------------------------------------------------
+template <bool BF16>
+__global__ void kv_append_fp8_kernel(const uint16_t* __restrict__ k, const uint16_t* __restrict__ v, uint8_t* __restrict__ k_pool,
+                                     uint8_t* __restrict__ v_pool, const int* __restrict__ slots, int T, int row_elems) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int per_row = row_elems >> 3;                      // 8 values per thread
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)T * per_row * 2) return;
+  const int which = (int)(idx / ((long long)T * per_row));  // 0: K, 1: V
+  const long long rem = idx - (long long)which * T * per_row;
+  const int t = (int)(rem / per_row), c = (int)(rem - (long long)t * per_row) * 8;
+  const int slot = slots[t];
+  if (slot < 0) return;
+  const uint16_t* src = (which ? v : k) + (size_t)t * row_elems + c;
+  uint8_t* dst = (which ? v_pool : k_pool) + (size_t)slot * row_elems + c;
+  const uint4 x = *reinterpret_cast<const uint4*>(src);
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+  uint32_t o[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_16<BF16>(w[j]);
+    unsigned short pr;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(pr) : "f"(f.y), "f"(f.x));      // first source -> upper byte
+    o[j >> 1] |= (uint32_t)pr << ((j & 1) * 16);
+  }
+  *reinterpret_cast<uint2*>(dst) = make_uint2(o[0], o[1]);
+}
+
+// ------------------------------------------------------------------------------------------------
 // Causal row softmax for attention evaluated as two GEMMs (MLA prefill: rows = (query, head) pairs, columns = keys):
 //   P[r, k] = softmax_k(scale * S[r, k]) over k <= first_pos + r / heads, 0 beyond (also over the padded columns), 16-bit out.
 // One CTA per row; the row is read once (held in registers up to 8192 keys, re-read from L2 beyond that).
@@ -722,6 +754,18 @@ extern "C" int fb_glu_act(const void* x, void* y, int M, int I, int ldx, int ldy
     default: FB_GLU(3) break;
   }
 #undef FB_GLU
+  return (int)cudaGetLastError();
+}
+
+extern "C" int fb_kv_append_fp8(const void* k, const void* v, void* k_pool, void* v_pool, const int* slots, int T, int row_elems, int dtype,
+                                void* stream) {
+  if (T <= 0) return 0;
+  if (row_elems % 8 != 0 || (dtype != 0 && dtype != 1)) return -1;
+  const long long total = (long long)T * (row_elems / 8) * 2;
+  const int blocks = (int)((total + 255) / 256);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) launch_k(kv_append_fp8_kernel<true>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)k, (const uint16_t*)v, (uint8_t*)k_pool, (uint8_t*)v_pool, slots, T, row_elems);
+  else launch_k(kv_append_fp8_kernel<false>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)k, (const uint16_t*)v, (uint8_t*)k_pool, (uint8_t*)v_pool, slots, T, row_elems);
   return (int)cudaGetLastError();
 }
 

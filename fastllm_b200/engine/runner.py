@@ -121,7 +121,9 @@ class ModelRunner:
             return False        # one graph cannot span the devices of a layer-split placement
         if c.use_mla and not (c.kv_lora_rank == 512 and c.qk_rope_head_dim == 64 and self.model.dtype in (torch.float16, torch.bfloat16)):
             return False        # latent shapes outside the MLA decode kernel run the PyTorch evaluation
-        if self.model.general_attn or getattr(self.model, "kv_dtype", None) not in (None, self.model.dtype):
+        kvd = getattr(self.model, "kv_dtype", None)
+        kv8 = kvd == torch.float8_e4m3fn and self.model.kv8_decode_ok
+        if (self.model.general_attn and not kv8) or (kvd not in (None, self.model.dtype) and not kv8):
             return False        # these paths evaluate attention with host-synchronising PyTorch ops
         if len({int(lw.attn.window) for lw in self.model.layers if lw.attn.window}) > 1 or (c.rope_local_theta and any(lw.attn.window for lw in self.model.layers)):
             return False        # several window lengths / a second RoPE base for local layers: PyTorch evaluation

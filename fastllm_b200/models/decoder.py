@@ -151,6 +151,7 @@ class DecoderModel:
         self.attn_scale = cfg.attn_scale_override if cfg.attn_scale_override else 1.0 / math.sqrt(cfg.q_head_dim)
         # families whose attention needs options outside the tensor-core kernels run the PyTorch evaluation (not graph-safe)
         self.general_attn = bool(cfg.qk_norm_after_rope or cfg.qk_norm_full)
+        self.kv8_decode_ok = False
         if cfg.use_mla and cfg.rope_scaling and cfg.rope_scaling.get("mscale_all_dim"):
             ms = 0.1 * float(cfg.rope_scaling["mscale_all_dim"]) * math.log(float(cfg.rope_scaling.get("factor", 1.0))) + 1.0
             self.attn_scale *= ms * ms
@@ -230,7 +231,12 @@ class DecoderModel:
         if self.cfg.use_mla:
             raise NotImplementedError("the MLA latent cache is kept in the activation dtype")
         self.kv_dtype = dt
-        self.general_attn = True
+        self.general_attn = True              # prefill (and everything the decode kernel does not cover) evaluates attention in PyTorch
+        c = self.cfg
+        # e4m3 pages: decode runs the tensor-core kernel's KV8 mode when the fused post-processing can express the layer
+        self.kv8_decode_ok = bool(dt == torch.float8_e4m3fn and self.on_cuda and c.head_dim == 128 and not c.use_mla
+                                  and not (c.qk_norm_after_rope or c.qk_norm_full) and not c.rope_local_theta
+                                  and self.dtype in (torch.float16, torch.bfloat16))
         self._cpu_runner = False              # the whole-model CPU runner owns fp32 pages
 
     # -----------------------------------------------------------------------------------------------
@@ -247,6 +253,21 @@ class DecoderModel:
         # PyTorch evaluation
         kernel_variant = (variant and fb.is_decode and x.is_cuda and D == 128 and not (c.qk_norm_after_rope or c.qk_norm_full)
                           and k_pool.dtype == x.dtype and not c.rope_local_theta)
+        if self.kv8_decode_ok and fb.is_decode and x.is_cuda and x.dim() == 2 and k_pool.dtype == torch.float8_e4m3fn:
+            # e4m3 pages, decode: projection + norm + RoPE into 16-bit scratch rows, one kernel converts and appends them, and the
+            # decode kernel reads the raw pages (KV8 mode); all launches are CUDA-graph safe
+            T = x.shape[0]
+            k_new = torch.empty((T, Hkv, D), device=x.device, dtype=x.dtype)
+            v_new = torch.empty((T, Hkv, D), device=x.device, dtype=x.dtype)
+            rows = self._row_ids(T, x.device)
+            q = A.qkv_post(lw.qkv(x), fb.positions, rows, k_new, v_new, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
+                           lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
+            A.kv_append_fp8(k_new.view(T, Hkv * D), v_new.view(T, Hkv * D), k_pool, v_pool, fb.slots)
+            a = A.attn_decode(q, k_pool, v_pool, fb.page_table, fb.kv_lens, self.attn_scale, Hq, Hkv, D, ws=fb.decode_ws,
+                              planned=fb.decode_planned, window=int(lw.window or 0), softcap=float(c.attn_softcap or 0.0), sinks=lw.sinks)
+            if lw.out_gate is not None:
+                a = (a.float() * torch.sigmoid(lw.out_gate(x).float())).to(a.dtype)
+            return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
         if (self.general_attn or variant) and not kernel_variant:
             a = self._attention_general(lw, lw.qkv(x), fb, kv)
             return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
@@ -321,6 +342,14 @@ class DecoderModel:
         o = o * torch.rsqrt(ss / (c.num_heads * D) + c.rms_eps) * lw.norm_w.float()
         core = (torch.sigmoid(lw.gate(x).float()) * o).to(x.dtype)
         return self._row_parallel_norm(lw.out, core, residual, next_ln, consumer=consumer)
+
+    def _row_ids(self, T: int, device):
+        """``arange(T)`` int32 on ``device`` (cached: CUDA graphs need stable addresses)."""
+        cache = self.__dict__.setdefault("_row_id_cache", {})
+        key = (str(device), T)
+        if key not in cache:
+            cache[key] = torch.arange(T, device=device, dtype=torch.int32)
+        return cache[key]
 
     def _attention_general(self, lw: AttentionWeights, qkv, fb: ForwardBatch, kv):
         """Attention for the less common variants (sliding window, sinks, logit soft-capping, norm after RoPE)."""

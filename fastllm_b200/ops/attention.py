@@ -327,6 +327,23 @@ class DecodeWorkspace:
             _lib.check(rc, "fb_attn_decode_plan_window")
 
 
+def kv_append_fp8(k, v, k_pool, v_pool, slots):
+    """New 16-bit K / V rows ``[T, Hkv * D]`` -> unscaled e4m3 at pool rows ``slots`` (negative: skipped).  One launch."""
+    T = k.shape[0]
+    if not k.is_cuda:
+        ok = slots >= 0
+        sl = slots[ok].long()
+        k_pool.view(-1, k.shape[-1])[sl] = k[ok].to(k_pool.dtype)
+        v_pool.view(-1, v.shape[-1])[sl] = v[ok].to(v_pool.dtype)
+        return
+    rc = _lib.kernels().fb_kv_append_fp8(_ptr(k.contiguous()), _ptr(v.contiguous()), _ptr(k_pool), _ptr(v_pool), _ptr(slots), T, k.shape[-1],
+                                         dtype_code(k.dtype), _stream())
+    _lib.check(rc, "fb_kv_append_fp8")
+
+
+KV8_KERNEL = True          # e4m3 page pools run the decode kernel's KV8 mode (tests switch it off to compare with the PyTorch path)
+
+
 def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num_kv_heads, head_dim,
                 ws: DecodeWorkspace | None = None, out=None, planned=False, grid_ctas=0, quant_mode: int = 0,
                 window: int = 0, softcap: float = 0.0, sinks=None):
@@ -348,7 +365,9 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
             return cpu.attention_paged(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim)
         return paged_attention_ref(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim)
     G = num_q_heads // num_kv_heads
-    if head_dim != 128 or G > 16 or k_pool.shape[1] != PAGE_LEN or k_pool.dtype != q.dtype:
+    kv8 = (k_pool.dtype == torch.float8_e4m3fn and v_pool.dtype == torch.float8_e4m3fn and KV8_KERNEL
+           and q.dtype in (torch.float16, torch.bfloat16))
+    if head_dim != 128 or G > 16 or k_pool.shape[1] != PAGE_LEN or (k_pool.dtype != q.dtype and not kv8):
         cu = torch.arange(B + 1, dtype=torch.int32, device=q.device)
         if variant or k_pool.dtype != q.dtype:
             return paged_attention_general(q, k_pool, v_pool, page_table, seq_lens, cu, scale, num_q_heads, num_kv_heads, head_dim,
@@ -365,6 +384,20 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
     if out is None:
         out = torch.empty_like(q)
     num_slots = k_pool.shape[0] * k_pool.shape[1]
+    if kv8:
+        # e4m3 pages: the kernel turns every raw page into an fp16 operand tile in shared memory (exact conversion) and computes in
+        # fp16, so queries go in and the output comes back as fp16
+        q16 = q if q.dtype == torch.float16 else q.to(torch.float16)
+        o16 = out                       # the combine kernel writes the caller's 16-bit type
+        work, n_work = (ws.work_w, ws.n_work_w) if window else (ws.work, ws.n_work)
+        rc = _lib.kernels().fb_attn_decode_opts(_ptr(q16), _ptr(k_pool), _ptr(v_pool), _ptr(o16), o16.stride(0), _ptr(work),
+                                                _ptr(n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
+                                                num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
+                                                ws.work.shape[0], float(scale), 3 if out.dtype == torch.bfloat16 else 2, grid_ctas, _ptr(None), 0, _ptr(None),
+                                                num_q_heads * head_dim, _ptr(None), _ptr(None), 0, int(window), float(softcap),
+                                                _ptr(sinks), _stream())
+        _lib.check(rc, "fb_attn_decode_opts(kv8)")
+        return out
     xq = sa = xs = None
     ld_a = 0
     if quant_mode in (1, 2) and not _FUSED_COMBINE and B <= 128:

@@ -417,6 +417,44 @@ def test_mla_decode(H):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (16, 1)])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_attn_decode_fp8_kv(Hq, Hkv, dt):
+    """Decode attention over e4m3 page pools (KV8 mode: raw pages converted to fp16 operand tiles in shared memory) vs the
+    PyTorch evaluation on the same e4m3 values."""
+    torch.manual_seed(21)
+    D = 128
+    lens = [1, 127, 128, 129, 700, 1500, 77, 300]
+    Bn = len(lens)
+    n_pages = sum((l + 127) // 128 for l in lens) + 3
+    max_p = max((l + 127) // 128 for l in lens)
+    pt = torch.zeros(Bn, max_p, dtype=torch.int32)
+    perm = torch.randperm(n_pages)
+    c = 0
+    k8 = torch.zeros(n_pages, 128, Hkv, D, dtype=torch.float8_e4m3fn)
+    v8 = torch.zeros(n_pages, 128, Hkv, D, dtype=torch.float8_e4m3fn)
+    for b, l in enumerate(lens):
+        n = (l + 127) // 128
+        pt[b, :n] = perm[c:c + n].int()
+        c += n
+        for i in range(n):
+            k = min(128, l - i * 128)
+            k8[pt[b, i], :k] = (torch.randn(k, Hkv, D) * 0.7).to(torch.float8_e4m3fn)
+            v8[pt[b, i], :k] = torch.randn(k, Hkv, D).to(torch.float8_e4m3fn)
+    q = (torch.randn(Bn, Hq * D) * 0.7).to(dt)
+    seq = torch.tensor(lens, dtype=torch.int32)
+    cu = torch.arange(Bn + 1, dtype=torch.int32)
+    ref = A.paged_attention_general(q.float(), k8.float(), v8.float(), pt, seq, cu, D ** -0.5, Hq, Hkv, D)
+    out = A.attn_decode(q.to(DEV), k8.to(DEV), v8.to(DEV), pt.to(DEV), seq.to(DEV), D ** -0.5, Hq, Hkv, D)
+    _lib.check_device_errors()
+    assert out.dtype == dt
+    _close(out.float().cpu(), ref.float(), 2e-2, 2e-2, f"attn_decode kv8 {Hq}/{Hkv}", fro=8e-3)
+    out2 = A.attn_decode(q.to(DEV), k8.to(DEV), v8.to(DEV), pt.to(DEV), seq.to(DEV), D ** -0.5, Hq, Hkv, D, window=256)
+    ref2 = A.paged_attention_general(q.float(), k8.float(), v8.float(), pt, seq, cu, D ** -0.5, Hq, Hkv, D, window=256)
+    _lib.check_device_errors()
+    _close(out2.float().cpu(), ref2.float(), 2e-2, 2e-2, "attn_decode kv8 window", fro=8e-3)
+
+
 def test_mla_prefill_on_gemm_kernels():
     """Absorbed MLA prefill (heads folded into GEMM rows, both contractions on the tensor-core GEMM kernels, chunked prefill
     with earlier context) vs the fp32 evaluation."""

@@ -145,3 +145,33 @@ def test_attention_variants_decode_in_cuda_graphs(tmp_path):
         _lib.check_device_errors()
         agree = sum(a[:3] == b[:3] for a, b in zip(o1, o2))
         assert agree >= 2, (name, o1, o2)
+
+
+def test_fp8_kv_cache_decodes_on_the_kernel_in_cuda_graphs():
+    """``kv_cache_dtype="fp8_e4m3"`` with 128-wide heads: decode runs the tensor-core kernel's KV8 mode under CUDA graphs (K / V
+    appended as e4m3 by a kernel); tokens must agree with the PyTorch evaluation over the same e4m3 pages."""
+    import dataclasses
+
+    import fastllm_b200.ops.attention as ATT
+
+    cfg = dataclasses.replace(preset("tiny-llama"), head_dim=128, num_heads=4, num_kv_heads=2, hidden_size=512)
+    torch.manual_seed(0)
+    m = random_init(cfg, "cuda", torch.bfloat16, std=0.05)
+    m.set_kv_cache_dtype("fp8_e4m3")
+    assert m.kv8_decode_ok
+    prompts = [list(range(5, 5 + n)) for n in (150, 37, 260)]
+    gen = GenerationConfig(max_new_tokens=10, ignore_eos=True)
+    e1 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16)
+    assert e1.runner.graph_ok and e1.runner.kv.pools[0][0].dtype == torch.float8_e4m3fn
+    o1 = e1.generate(prompts, gen)
+    assert any(s.graph is not None for s in e1.runner.slots.values())
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    m.kv8_decode_ok = False                      # PyTorch evaluation of decode for the comparison run
+    try:
+        e2 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, use_cuda_graph=False), num_pages=16)
+        o2 = e2.generate(prompts, gen)
+    finally:
+        m.kv8_decode_ok = True
+    same = sum(a == b for x, y in zip(o1, o2) for a, b in zip(x, y))
+    assert all(x[0] == y[0] for x, y in zip(o1, o2)) and same >= 0.7 * sum(len(x) for x in o1), (o1, o2)
