@@ -154,6 +154,35 @@ def moe_ep_rank(model="deepseek-v3", tokens=32, ranks=8, kind="int4g128", iters=
           f"{int(local.sum())} local rows on {hit} of {exs[0].count} local experts; {hit * per / 1e6:.0f} MB of expert weights touched")
 
 
+def attn_decode_kv8(batch=64, length=1100, hq=32, hkv=8, iters=10):
+    """Decode attention over bf16 and over e4m3 page pools, device time per call (CUDA events around a CUDA graph)."""
+    from ..ops import attention as A
+
+    D = 128
+    npg = (length + 127) // 128
+    pages = batch * npg
+    pt = torch.randperm(pages, device="cuda").int().view(batch, npg)
+    seq = torch.full((batch,), length, dtype=torch.int32, device="cuda")
+    q = torch.randn(batch, hq * D, device="cuda").bfloat16()
+    k16 = (torch.randn(pages, 128, hkv, D, device="cuda") * 0.5).bfloat16()
+    v16 = torch.randn(pages, 128, hkv, D, device="cuda").bfloat16()
+    for name, (kp, vp) in (("bf16 pages", (k16, v16)), ("e4m3 pages", (k16.to(torch.float8_e4m3fn), v16.to(torch.float8_e4m3fn)))):
+        ws = A.DecodeWorkspace(batch, hkv, hq // hkv, npg, "cuda")
+        for _ in range(3):
+            A.attn_decode(q, kp, vp, pt, seq, D ** -0.5, hq, hkv, D, ws=ws)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(iters):
+                A.attn_decode(q, kp, vp, pt, seq, D ** -0.5, hq, hkv, D, ws=ws)
+        g.replay()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record(); g.replay(); e.record()
+        torch.cuda.synchronize()
+        print(f"attn_decode {name}: {s.elapsed_time(e) / iters * 1e3:.1f} us per call ({batch} x {length} tokens, {hq}/{hkv} heads)")
+
+
 def gemm_qkv_post(tokens=64, hq=32, hkv=8, k=4096, iters=4):
     from ..ops.quant import LinearWeight
 
@@ -193,6 +222,7 @@ def gdn_decode(batch=64, hk=16, hv=32, iters=4):
 
 CASES = {
     "gemm_qkv_post": gemm_qkv_post,
+    "attn_decode_kv8": attn_decode_kv8,
     "moe_ep_rank_dsv3_int4g": lambda: moe_ep_rank("deepseek-v3", 32, 8, "int4g128"),
     "moe_ep_rank_dsv3_int4g_untimed": lambda: moe_ep_rank("deepseek-v3", 32, 8, "int4g128", timed=False),
     "moe_ep_rank_dsv3_fp8": lambda: moe_ep_rank("deepseek-v3", 32, 8, "fp8"),
