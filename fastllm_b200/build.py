@@ -116,6 +116,12 @@ def build_cpu(force: bool = False) -> Path:
         objs.append(obj)
         if force or _newer(cpu / f"{name}.cpp", headers, obj):
             jobs.append(([*base, "-march=x86-64-v3", "-c", str(cpu / f"{name}.cpp"), "-o", str(obj)], None))
+    # VNNI / AVX-512 BF16 / AMX kernels: their own translation unit (only entered after a run-time capability check)
+    obj = OBJ / "cpu_accel.o"
+    objs.append(obj)
+    if force or _newer(cpu / "cpu_accel.cpp", headers, obj):
+        jobs.append(([*base, *CPU_ISA["_avx512"], "-mavx512vnni", "-mavx512bf16", "-mamx-tile", "-mamx-int8", "-mamx-bf16", "-c",
+                      str(cpu / "cpu_accel.cpp"), "-o", str(obj)], None))
     if jobs:
         with ThreadPoolExecutor(max_workers=len(jobs)) as ex:
             list(ex.map(lambda j: _run(*j), jobs))

@@ -162,6 +162,23 @@ inline int rows_per_task(int width) { const int r = 32768 / (width > 0 ? width :
 
 extern "C" {
 
+// reduced-precision-activation kernels of cpu_accel.cpp (VNNI / AVX-512 BF16 / AMX): off unless switched on
+int fbx_caps();
+void fbx_quant_act_s8(const float* x, int ldx, int M, int K, int deint, int8_t* xq, float* scale, float* sum);
+void fbx_to_bf16(const float* x, int ldx, int M, int K, uint16_t* xb);
+void fbx_linear_rows_bf16(const FbLinearArgs* a, const uint16_t* xb, int n0, int n1);
+void fbx_linear_rows_i8(const FbLinearArgs* a, const int8_t* xq, const float* xscale, const float* xsum, int n0, int n1);
+void fbx_amx_pack_i8(const int8_t* xq, int M, int K, int8_t* pk);
+void fbx_amx_pack_bf16(const uint16_t* xb, int M, int K, uint16_t* pk);
+void fbx_amx_linear_rows_bf16(const FbLinearArgs* a, const uint16_t* pk, int n0, int n1);
+void fbx_amx_linear_rows_i8(const FbLinearArgs* a, const int8_t* pk, const float* xscale, const float* xsum, int n0, int n1);
+
+static int g_accel = 0;          // bits requested by fbcpu_set_accel, masked by what the CPU has
+// flags: bit 0 VNNI (int8 / int4-group weights with int8 activations), bit 1 AVX-512 BF16, bit 2 AMX.  Returns the bits in effect.
+int fbcpu_set_accel(int flags) { g_accel = flags & fbx_caps(); return g_accel; }
+int fbcpu_get_accel() { return g_accel; }
+int fbcpu_accel_caps() { return fbx_caps(); }
+
 int fbcpu_get_threads() { return pool().size(); }
 void fbcpu_set_threads(int n) { pool().resize(n); }
 int fbcpu_isa() { return has_avx512() ? 512 : 256; }
@@ -175,6 +192,41 @@ int fbcpu_linear(const float* x, int ldx, const void* w, int wtype, const float*
   FbLinearArgs a;
   a.x = x; a.ldx = ldx; a.w = w; a.wtype = wtype; a.scale = scale; a.zero = zero; a.group = group; a.bias = bias;
   a.y = y; a.ldy = ldy; a.M = M; a.N = N; a.K = K; a.xsum = nullptr;
+  if (g_accel != 0) {
+    const bool amx = (g_accel & 4) && M >= 16;
+    if (wtype == W_BF16 && (g_accel & 6) && K % 32 == 0) {
+      // bf16 weights x bf16 activations: dot-product instructions (two bf16 pairs per lane), or AMX tiles for 16+ rows
+      std::vector<uint16_t> xb((size_t)M * K);
+      fbx_to_bf16(x, ldx, M, K, xb.data());
+      if (amx) {
+        std::vector<uint16_t> pk((size_t)((M + 15) / 16 * 16) * K);
+        fbx_amx_pack_bf16(xb.data(), M, K, pk.data());
+        const int tiles = (N + 15) / 16;
+        pool().run(tiles, [&](int t) { fbx_amx_linear_rows_bf16(&a, pk.data(), t * 16, std::min(N, t * 16 + 16)); });
+        return 0;
+      }
+      if (g_accel & 2) {
+        split_run(N, 8, [&](int n0, int n1) { fbx_linear_rows_bf16(&a, xb.data(), n0, n1); });
+        return 0;
+      }
+    }
+    if ((wtype == W_INT8 || (wtype == W_INT4G && group == 128)) && (g_accel & 1) && K % 128 == 0) {
+      const int nb = K / 128;
+      std::vector<int8_t> xq((size_t)M * K);
+      std::vector<float> xsc((size_t)M * nb), xsm((size_t)M * nb);
+      const bool use_amx = amx && wtype == W_INT8;
+      fbx_quant_act_s8(x, ldx, M, K, wtype == W_INT4G ? 1 : 0, xq.data(), xsc.data(), xsm.data());
+      if (use_amx) {
+        std::vector<int8_t> pk((size_t)((M + 15) / 16 * 16) * K);
+        fbx_amx_pack_i8(xq.data(), M, K, pk.data());
+        const int tiles = (N + 15) / 16;
+        pool().run(tiles, [&](int t) { fbx_amx_linear_rows_i8(&a, pk.data(), xsc.data(), xsm.data(), t * 16, std::min(N, t * 16 + 16)); });
+        return 0;
+      }
+      split_run(N, 8, [&](int n0, int n1) { fbx_linear_rows_i8(&a, xq.data(), xsc.data(), xsm.data(), n0, n1); });
+      return 0;
+    }
+  }
   std::vector<float> xsum;
   if (wtype == W_INT8 || wtype == W_INT4G) {
     const int g = wtype == W_INT8 ? K : group;

@@ -167,7 +167,13 @@ def disable_cuda_malloc():
 
 
 def set_enable_amx(enable_amx):
-    _settings["enable_amx"] = bool(enable_amx)                   # the CPU backend dispatches AVX2 / AVX-512 by itself
+    """Switch the CPU backend's reduced-precision-activation kernels (AMX tiles, AVX-512 VNNI / BF16) on or off; what the CPU
+    does not have stays off.  (Reference: ``--enable_amx``, fastllm.EnableAMX.)"""
+    _settings["enable_amx"] = bool(enable_amx)
+    from .ops import cpu
+
+    if cpu.available():
+        cpu.set_accel(7 if enable_amx else 0)
 
 
 def set_cuda_shared_expert(cuda_shared_expert):

@@ -20,6 +20,7 @@ P, I, F = c_void_p, c_int, c_float
 
 _SIGS = {
     "fbcpu_get_threads": ([], I), "fbcpu_set_threads": ([I], None), "fbcpu_isa": ([], I),
+    "fbcpu_set_accel": ([I], I), "fbcpu_get_accel": ([], I), "fbcpu_accel_caps": ([], I),
     "fbcpu_linear": ([P, I, P, I, P, P, I, P, P, I, I, I, I], I),
     "fbcpu_rmsnorm": ([P, I, P, P, I, I, I, F, F], None),
     "fbcpu_layernorm": ([P, I, P, P, P, I, I, I, F], None),
@@ -51,8 +52,30 @@ def lib():
         n = os.environ.get("FB_CPU_THREADS")
         if n:
             L.fbcpu_set_threads(int(n))
+        acc = os.environ.get("FB_CPU_ACCEL")
+        if acc:
+            L.fbcpu_set_accel(int(acc))
         _LIB = L
     return _LIB
+
+
+ACCEL_VNNI, ACCEL_BF16, ACCEL_AMX = 1, 2, 4
+
+
+def accel_caps() -> int:
+    """Which reduced-precision-activation instruction sets this CPU offers (bits ``ACCEL_VNNI | ACCEL_BF16 | ACCEL_AMX``)."""
+    return int(lib().fbcpu_accel_caps())
+
+
+def set_accel(flags: int) -> int:
+    """Switch the VNNI (int8 / int4-group weights x int8 activations), AVX-512 BF16 and AMX kernels on or off; they round the
+    activations (int8 per token and 128-wide block, or bf16) where the default kernels keep them fp32.  Returns the bits in
+    effect (requested AND available).  ``FB_CPU_ACCEL=7`` in the environment does the same at load."""
+    return int(lib().fbcpu_set_accel(int(flags)))
+
+
+def get_accel() -> int:
+    return int(lib().fbcpu_get_accel())
 
 
 def set_threads(n: int) -> None:

@@ -195,3 +195,47 @@ def test_numa_expert_placement_matches_single_node(wd, monkeypatch):
         cpu.lib().fbnuma_destroy(ctypes.c_void_p(ex._numa_handle))
         ex._numa_handle = None
     ex.host = ex.numa = False
+
+
+def _blocks_s8(x):
+    """Activations rounded to int8 per (row, 128-wide block), as the VNNI / AMX kernels see them."""
+    M, K = x.shape
+    xb = x.reshape(M, K // 128, 128)
+    sc = xb.abs().amax(-1, keepdim=True).clamp(min=1e-20) / 127.0
+    return (torch.round(xb / sc).clamp(-127, 127) * sc).reshape(M, K)
+
+
+@pytest.mark.parametrize("M", [1, 5, 16, 37])
+def test_accelerated_cpu_kernels(M):
+    """VNNI / AVX-512 BF16 / AMX kernels (where the CPU has them) against the same arithmetic in PyTorch: activations rounded
+    to int8 blocks or bf16, exact integer / fp32 accumulation."""
+    caps = cpu.accel_caps()
+    if caps == 0:
+        pytest.skip("no VNNI / AVX-512 BF16 / AMX on this CPU")
+    torch.manual_seed(5)
+    K, N = 512, 200
+    x = torch.randn(M, K)
+    w = torch.randn(N, K) * 0.05
+    b = torch.randn(N)
+    try:
+        for flags in sorted({caps & 3, caps}):          # without and with AMX
+            if flags == 0:
+                continue
+            assert cpu.set_accel(flags) == flags
+            if flags & (cpu.ACCEL_BF16 | cpu.ACCEL_AMX):
+                wb = w.to(torch.bfloat16)
+                ref = x.to(torch.bfloat16).float() @ wb.float().t() + b
+                got = cpu.linear(x, wb, b)
+                assert torch.allclose(got, ref, atol=2e-4, rtol=1e-4), (flags, (got - ref).abs().max())
+            if flags & cpu.ACCEL_VNNI:
+                q, s, z = quant.quantize_int8(w)
+                ref8 = _blocks_s8(x) @ quant.dequantize_int8(q, s, z, torch.float32).t() + b
+                got8 = cpu.linear(x, q, b, "int8", s, z)
+                assert torch.allclose(got8, ref8, atol=3e-4, rtol=1e-4), (flags, (got8 - ref8).abs().max())
+                q4, s4, m4 = quant.quantize_int4g(w, 128)
+                ref4 = _blocks_s8(x) @ quant.dequantize_int4g(q4, s4, m4, torch.float32, 128).t()
+                got4 = cpu.linear(x, q4, None, "int4g", s4, m4, 128)
+                assert torch.allclose(got4, ref4, atol=3e-4, rtol=1e-4), (flags, (got4 - ref4).abs().max())
+    finally:
+        cpu.set_accel(0)
+    assert cpu.get_accel() == 0
