@@ -45,6 +45,7 @@ def parse_args():
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],
                     help="cpu: the CPU configuration (fp32, C++ backend); use with --model qwen3-0.6b --batch 1 --prompt-len 128 --output-len 128")
     ap.add_argument("--moe-dtype", default="")
+    ap.add_argument("--kv-cache-dtype", default="", help="page pool dtype: empty (the activation dtype) | fp8_e4m3")
     ap.add_argument("--moe-tp", action="store_true", help="shard every expert over the ranks instead of expert parallelism")
     ap.add_argument("--draw-lengths", action="store_true",
                     help="prompt lengths uniform in [128, --prompt-len] and output lengths uniform in [64, --output-len], drawn from the seed "
@@ -143,6 +144,7 @@ def run_ours(args):
     need_tokens = int(B * (P + O + 256) / 0.75)   # leaves the 80 % admission limit room for all B prompts
     spec = {"kind": "preset", "model": args.model, "dtype": "bfloat16", "seed": 0, "wdtype": args.dtype,
             "moe_wdtype": args.moe_dtype or None, "moe_tp": bool(args.moe_tp), "comm": args.comm, "max_m": B,
+            "kv_cache_dtype": args.kv_cache_dtype or None,
             "engine": dict(max_batch=max(B, 1), max_context=((P + O + 127) // 128 + 1) * 128, max_tokens=need_tokens,
                            use_cuda_graph=not args.no_graph, prefix_cache=False, chunked_prefill_size=8192),
             "_worker_hook": _worker_hook}
@@ -226,7 +228,7 @@ def run_ours(args):
         "config": {"model": args.model, "global_batch": B, "seq_len": P, "output_len": O,
                    "lengths": "prompt uniform 128..seq_len, output uniform 64..output_len, drawn from the seed" if args.draw_lengths else "fixed",
                    "parallelism": f"tp{world}" + (f"+ep{world}" if ep is not None else ""),
-                   "kv_cache": "paged, page 128, bf16", "l2": "inputs larger than L2 (weights + KV >> 126 MB per step)",
+                   "kv_cache": "paged, page 128, " + (args.kv_cache_dtype or "bf16"), "l2": "inputs larger than L2 (weights + KV >> 126 MB per step)",
                    "cuda_graph": not args.no_graph, "comm": (tp.comm.fused.name if (tp.comm and tp.comm.fused) else ("nccl" if world > 1 else "none")),
                    "control_plane": "rank 0 schedules; ranks 1..N-1 replay its step plans from a shared-memory ring" if world > 1 else "single rank"},
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": B * 4,

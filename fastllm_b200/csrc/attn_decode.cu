@@ -116,14 +116,23 @@ __device__ __forceinline__ void kv8_convert_page(const uint8_t* __restrict__ raw
 // the 16-bit TMA load would have produced, so the MMA descriptors, the softmax and the epilogue are the same code -- and the
 // next raw page is already in flight while the current one is converted and multiplied.  e4m3 converts exactly to fp16
 // (`cvt.rn.f16x2.e4m3x2`), so this mode computes in fp16: the caller passes fp16 queries.
-template <bool BF16, int AD_STAGES, int GP, bool KV8 = false>
-__global__ void __launch_bounds__(KV8 ? 320 : 192, KV8 ? 2 : (AD_STAGES == 1 ? 3 : 1))
+//
+// KV8 == 2: the e4m3 pages go to the tensor core as they are (`kind::f8f6f4`): K page = A operand K-major, V page = A operand
+// read MN-major, no conversion and no 16-bit operand tiles (a stage is 36 KB).  The other operand of each product must be
+// 8-bit too; to keep 16-bit-class accuracy it is split in two e4m3 terms, x = hi + lo / 16: the queries by a small kernel
+// beforehand (Qa, Qb), the probabilities (scaled by 256 so that small ones stay representable) by the softmax warps
+// (Pa, Pb).  Each product runs once per term into its own TMEM accumulator: S = Sa + Sb / 16, O = (Oa + Ob / 16) / 256.
+template <bool BF16, int AD_STAGES, int GP, int KV8 = 0>
+__global__ void __launch_bounds__(KV8 == 1 ? 320 : 192, KV8 == 1 ? 2 : (KV8 == 2 ? 4 : (AD_STAGES == 1 ? 3 : 1)))
 attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                    const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK32,
                    const __grid_constant__ CUtensorMap tmV32, const AttnDecodeParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* p_smem = smem + AD_STAGES * AD_STAGE_BYTES;
+  constexpr int K8_BYTES = AD_PAGE * AD_D;                           // one e4m3 page
+  constexpr int Q8_BYTES = AD_NPAD * AD_D;                           // one e4m3 query tile (16 heads x 128)
+  constexpr int STAGE_B = KV8 == 2 ? 2 * K8_BYTES + 2 * Q8_BYTES : AD_STAGE_BYTES;      // KV8 == 2: K8, V8, Qa, Qb
+  uint8_t* p_smem = smem + AD_STAGES * STAGE_B;
   uint64_t* bars = reinterpret_cast<uint64_t*>(p_smem + AD_P_BYTES);
   uint64_t* full_k = bars;                  // [STAGES]  K + Q landed
   uint64_t* full_v = bars + AD_STAGES;      // [STAGES]
@@ -152,9 +161,9 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < AD_STAGES; ++s) {
       // KV8: the operand tiles are completed by the 128 converter threads (plus the producer's arrival for the Q tile)
-      mbar_init(&full_k[s], KV8 ? 129 : 1); mbar_init(&full_v[s], KV8 ? 128 : 1); mbar_init(&empty_k[s], 1); mbar_init(&empty_v[s], 1);
+      mbar_init(&full_k[s], KV8 == 1 ? 129 : 1); mbar_init(&full_v[s], KV8 == 1 ? 128 : 1); mbar_init(&empty_k[s], 1); mbar_init(&empty_v[s], 1);
     }
-    if (KV8) { mbar_init(raw_full_k, 1); mbar_init(raw_full_v, 1); mbar_init(raw_empty_k, 128); mbar_init(raw_empty_v, 128); }
+    if (KV8 == 1) { mbar_init(raw_full_k, 1); mbar_init(raw_full_v, 1); mbar_init(raw_empty_k, 128); mbar_init(raw_empty_v, 128); }
     mbar_init(s_full, 1);
     mbar_init(p_ready, 128);
     mbar_init(o_full, 1);
@@ -171,12 +180,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
     }
     fence_proxy_async_smem();
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, 32); tmem_relinquish(); }
+  constexpr uint32_t TMEM_COLS = KV8 == 2 ? 64 : 32;
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
-  const uint32_t tmem_s = *tmem_slot;        // columns [0,16): S^T, [16,32): O^T
-  const uint32_t tmem_o = tmem_s + 16;
+  const uint32_t tmem_s = *tmem_slot;        // columns [0,16): S^T, [16,32): O^T   (KV8 == 2: Sa, Sb, Oa, Ob of 16 columns each)
+  const uint32_t tmem_o = tmem_s + (KV8 == 2 ? 32 : 16);
   pdl_wait();   // everything above touches only this CTA's shared memory and TMEM
   int n_items = *p.n_work;
   if (n_items < 0) n_items = 0;
@@ -196,7 +206,19 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const int page = p.page_table[(size_t)b * p.max_pages + pg];
         const int s = it % AD_STAGES;
         const uint32_t ph = (uint32_t)(it / AD_STAGES) & 1u;
-        if (KV8) {
+        if (KV8 == 2) {
+          if (!mbar_wait(&empty_k[s], ph ^ 1u, dead, KID_ATTN_DECODE, 1)) break;
+          uint8_t* k8 = smem + s * STAGE_B;
+          mbar_expect_tx(&full_k[s], K8_BYTES + 2 * Q8_BYTES);
+          tma_load_2d(k8, &tmK, &full_k[s], kvh * AD_D, page * AD_PAGE);
+          tma_load_2d(k8 + 2 * K8_BYTES, &tmQ, &full_k[s], 0, b * p.Hq + kvh * p.G);                 // Qa
+          tma_load_2d(k8 + 2 * K8_BYTES + Q8_BYTES, &tmK32, &full_k[s], 0, b * p.Hq + kvh * p.G);    // Qb (its map rides in the tmK32 slot)
+          if (!mbar_wait(&empty_v[s], ph ^ 1u, dead, KID_ATTN_DECODE, 8)) break;
+          mbar_expect_tx(&full_v[s], K8_BYTES);
+          tma_load_2d(k8 + K8_BYTES, &tmV, &full_v[s], kvh * AD_D, page * AD_PAGE);
+          continue;
+        }
+        if (KV8 == 1) {
           // raw pages first (their staging buffers free up long before the operand tiles do), then Q into the operand stage
           if (!mbar_wait(raw_empty_k, ph ^ 1u, dead, KID_ATTN_DECODE, 11)) break;
           mbar_expect_tx(raw_full_k, AD_PAGE * AD_D);
@@ -254,6 +276,35 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         const uint32_t iph = (uint32_t)it & 1u;
         const uint32_t kb = smem_u32(smem + s * AD_STAGE_BYTES);
         const uint32_t vb = kb + AD_K_BYTES, qb = vb + AD_K_BYTES;
+        if (KV8 == 2) {
+          const uint32_t k8 = smem_u32(smem + s * STAGE_B), v8 = k8 + K8_BYTES, qa = v8 + K8_BYTES, qb8 = qa + Q8_BYTES;
+          if (!mbar_wait(&full_k[s], ph, dead, KID_ATTN_DECODE, 2)) break;
+          tc_fence_after_sync();
+          // Sa = K8 * Qa^T, Sb = K8 * Qb^T: rows of 128 bytes, 128-byte swizzle, 32 dims per instruction
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f8(tmem_s, make_smem_desc(k8 + k * 32, 16, 1024, SWZ_128B), make_smem_desc(qa + k * 32, 16, 1024, SWZ_128B), p.idesc_s, k != 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f8(tmem_s + 16, make_smem_desc(k8 + k * 32, 16, 1024, SWZ_128B), make_smem_desc(qb8 + k * 32, 16, 1024, SWZ_128B), p.idesc_s, k != 0 ? 1u : 0u);
+          umma_commit(s_full);
+          umma_commit(&empty_k[s]);
+          if (!mbar_wait(p_ready, iph, dead, KID_ATTN_DECODE, 3)) break;
+          if (!mbar_wait(&full_v[s], ph, dead, KID_ATTN_DECODE, 4)) break;
+          if (it > 0 && !mbar_wait(o_empty, iph ^ 1u, dead, KID_ATTN_DECODE, 5)) break;
+          tc_fence_after_sync();
+          // Oa = V8^T * Pa^T, Ob = V8^T * Pb^T: the V page read MN-major (dims contiguous, one 128-byte atom wide), 32 tokens per
+          // instruction; P^T [16 x 128 tokens] bytes in the un-swizzled core-matrix layout (8 heads x 16 tokens per core matrix)
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f8(tmem_o, make_smem_desc(v8 + k * 4096, 16, 1024, SWZ_128B), make_smem_desc(smem_u32(p_smem) + k * 512, 256, 128, SWZ_NONE), p.idesc_o, k != 0 ? 1u : 0u);
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            umma_f8(tmem_o + 16, make_smem_desc(v8 + k * 4096, 16, 1024, SWZ_128B), make_smem_desc(smem_u32(p_smem) + 2048 + k * 512, 256, 128, SWZ_NONE), p.idesc_o, k != 0 ? 1u : 0u);
+          umma_commit(o_full);
+          umma_commit(&empty_v[s]);
+          continue;
+        }
         if (!mbar_wait(&full_k[s], ph, dead, KID_ATTN_DECODE, 2)) break;
         tc_fence_after_sync();
         // S^T = K * Q^T : K-major operands, 128-byte swizzle; d 0..63 in the first half tile, 64..127 in the second
@@ -282,7 +333,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       }
     }
     __syncwarp();
-  } else if (KV8 && warp >= 6) {
+  } else if (KV8 == 1 && warp >= 6) {
     // ---- converter warps: raw e4m3 page -> fp16 operand tile in the swizzled layout of the 16-bit TMA load ----
     const int ctid = (int)threadIdx.x - 192;
     int it = 0;
@@ -321,6 +372,13 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       uint32_t r[16];
       tmem_ld_32x32b_x16(tmem_s + ((uint32_t)(q * 32) << 16), r);
       tmem_ld_wait();
+      if (KV8 == 2) {                      // S = Sa + Sb / 16
+        uint32_t r2[16];
+        tmem_ld_32x32b_x16(tmem_s + 16 + ((uint32_t)(q * 32) << 16), r2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int h = 0; h < 16; ++h) r[h] = __float_as_uint(fmaf(__uint_as_float(r2[h]), 0.0625f, __uint_as_float(r[h])));
+      }
       float sv[GP];
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
@@ -343,6 +401,31 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       // P^T[n][t] in the K-major core-matrix layout: ((t/8)*2 + n/8)*128 + (n%8)*16 + (t%8)*2 bytes
       uint8_t* pb = p_smem + (t >> 3) * 256 + (t & 7) * 2;
       float* rs = red_sum + iph * 64;
+      if (KV8 == 2) {
+        // two e4m3 terms of 256 p: Pa = fl8(256 p), Pb = fl8(16 (256 p - Pa)); bytes at ((t / 16) * 2 + h / 8) * 128 + (h % 8) * 16 + t % 16
+        uint8_t* pa8 = p_smem + (t >> 4) * 256 + (t & 15);
+#pragma unroll
+        for (int h = 0; h < GP; ++h) {
+          float pv = 0.f;
+          if (h < G && valid) pv = exp2f(sv[h] - mx[h]) * 256.0f;
+          unsigned short a8, b8;
+          asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(a8) : "f"(0.f), "f"(pv));
+          uint32_t ah;
+          asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(ah) : "h"(a8));
+          const float af = __half2float(__ushort_as_half((unsigned short)(ah & 0xFFFFu)));
+          asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(b8) : "f"(0.f), "f"((pv - af) * 16.0f));
+          uint32_t bh;
+          asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(bh) : "h"(b8));
+          const float bf = __half2float(__ushort_as_half((unsigned short)(bh & 0xFFFFu)));
+          const int off = (h >> 3) * 128 + (h & 7) * 16;
+          pa8[off] = (uint8_t)(a8 & 0xFF);
+          pa8[2048 + off] = (uint8_t)(b8 & 0xFF);
+          float pr = fmaf(bf, 0.0625f, af) * (1.0f / 256.0f);          // what the tensor core will see
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
+          if (lane == 0) rs[q * 16 + h] = pr;
+        }
+      } else {
 #pragma unroll
       for (int h = 0; h < GP; ++h) {
         float pv = 0.f;
@@ -355,6 +438,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
         for (int o = 16; o > 0; o >>= 1) pr += __shfl_xor_sync(0xffffffffu, pr, o);
         if (lane == 0) rs[q * 16 + h] = pr;
       }
+      }
       fence_proxy_async_smem();
       tc_fence_before_sync();
       mbar_arrive(p_ready);
@@ -363,6 +447,14 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
       tc_fence_after_sync();
       tmem_ld_32x32b_x16(tmem_o + ((uint32_t)(q * 32) << 16), r);
       tmem_ld_wait();
+      if (KV8 == 2) {                      // O = (Oa + Ob / 16) / 256
+        uint32_t r2[16];
+        tmem_ld_32x32b_x16(tmem_o + 16 + ((uint32_t)(q * 32) << 16), r2);
+        tmem_ld_wait();
+#pragma unroll
+        for (int h = 0; h < 16; ++h)
+          r[h] = __float_as_uint(fmaf(__uint_as_float(r2[h]), 0.0625f, __uint_as_float(r[h])) * (1.0f / 256.0f));
+      }
       tc_fence_before_sync();
       mbar_arrive(o_empty);
       const size_t slot = ((size_t)(b * p.Hkv + kvh) * p.max_splits + pg) * G;
@@ -437,7 +529,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constan
   }
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_s, 32);
+  if (warp == 1) tmem_dealloc(tmem_s, TMEM_COLS);
 }
 
 // Optional second output of the combine: its row quantised for the 8-bit-activation output projection.  One (request, head)
@@ -566,13 +658,27 @@ extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void
   const int G = Hq / Hkv;
   if (G > AD_NPAD) return -1;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  const bool kv8 = dtype == 2 || dtype == 3;          // e4m3 pages, fp16 queries; output fp16 (2) or bf16 (3)
-  const bool kv8_out_bf16 = dtype == 3;
+  // dtype 2 / 3: e4m3 pages, fp16 queries, fp16 / bf16 output (pages converted to fp16 operand tiles in shared memory).
+  // dtype 4 / 5: e4m3 pages on the fp8 tensor-core path, fp16 / bf16 output; `q` = Qa and `xq` = Qb, the two e4m3 terms of the
+  // queries ([B * Hq, 128] bytes each, from fb_quant_q_e4m3x2).
+  const bool kv8tc = dtype == 4 || dtype == 5;
+  const bool kv8 = dtype == 2 || dtype == 3 || kv8tc;
+  const bool kv8_out_bf16 = dtype == 3 || dtype == 5;
+  const void* q_b = kv8tc ? xq : nullptr;
+  if (kv8tc) { xq = nullptr; qmode = 0; }
   if (kv8) dtype = 0;
   if (kv8 && qmode != 0) return -1;
+  if (kv8tc && q_b == nullptr) return -1;
   CUtensorMap tmK, tmV, tmQ;
   CUtensorMap tmK32, tmV32;
-  if (kv8) {
+  if (kv8tc) {
+    // pages and query terms as tensor-core operands: rows of 128 bytes, 128-byte swizzle
+    if (!make_tmap_2d(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 128, 1, 3)) return -2;
+    if (!make_tmap_2d(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 128, 1, 3)) return -2;
+    if (!make_tmap_2d(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 128, 1, 3)) return -2;
+    if (!make_tmap_2d(&tmK32, q_b, (uint64_t)B * Hq, D, D, AD_NPAD, 128, 1, 3)) return -2;
+    tmV32 = tmV;
+  } else if (kv8) {
     // raw pages: one box of 128 tokens x 128 bytes, no swizzle (the converter warps build the operand layout)
     if (!make_tmap_2d(&tmK, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 128, 1, 0)) return -2;
     if (!make_tmap_2d(&tmV, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, AD_PAGE, 128, 1, 0)) return -2;
@@ -583,7 +689,7 @@ extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void
     if (!make_tmap_2d(&tmK32, k_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
     if (!make_tmap_2d(&tmV32, v_pool, (uint64_t)num_slots, (uint64_t)Hkv * D, (uint64_t)Hkv * D, 32, 64, 2, 3)) return -2;
   }
-  if (!make_tmap_2d(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 64, 2, 3)) return -2;
+  if (!kv8tc && !make_tmap_2d(&tmQ, q, (uint64_t)B * Hq, D, D, AD_NPAD, 64, 2, 3)) return -2;
   AttnDecodeParams p;
   p.work = work; p.n_work = n_work; p.page_table = page_table; p.seq_lens = seq_lens; p.part_o = part_o; p.part_ml = part_ml;
   p.max_pages = max_pages; p.max_splits = max_splits; p.Hq = Hq; p.Hkv = Hkv; p.G = G;
@@ -592,7 +698,7 @@ extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window; p.softcap = softcap; p.scale = scale;
   const uint32_t f = dtype == 1 ? 1u : 0u;
-  p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);
+  p.idesc_s = make_idesc(f, f, 0, 0, 128, AD_NPAD);            // kind::f8f6f4: format 0 = e4m3
   p.idesc_o = make_idesc(f, f, 1, 0, 128, AD_NPAD);
   // stages: 1 -> 3 resident CTAs per SM hide each other's load latency; 3 -> one CTA per SM with a deep ring
   static int sm_count = 0;
@@ -628,14 +734,33 @@ extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void
 #define FB_AD_LAUNCH8(GPV)                                                                                               \
   {                                                                                                                     \
     static DeviceOnce cfg8;                                                                                           \
-    if (cfg8.need()) { cudaFuncSetAttribute(attn_decode_kernel<false, 1, GPV, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1) + 2 * AD_PAGE * AD_D); } \
-    launch_k<PDL_ATTN>(attn_decode_kernel<false, 1, GPV, true>, dim3(grid_ctas), dim3(320), ad_smem_bytes(1) + 2 * AD_PAGE * AD_D, stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
+    if (cfg8.need()) { cudaFuncSetAttribute(attn_decode_kernel<false, 1, GPV, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, ad_smem_bytes(1) + 2 * AD_PAGE * AD_D); } \
+    launch_k<PDL_ATTN>(attn_decode_kernel<false, 1, GPV, 1>, dim3(grid_ctas), dim3(320), ad_smem_bytes(1) + 2 * AD_PAGE * AD_D, stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
     if (counters == nullptr && kv8_out_bf16)                                                                            \
       launch_k<PDL_COMBINE>(attn_decode_combine_kernel<true, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
     else if (counters == nullptr)                                                                                       \
       launch_k<PDL_COMBINE>(attn_decode_combine_kernel<false, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
   }
-  if (kv8) {
+#define FB_AD_LAUNCHTC(GPV)                                                                                              \
+  {                                                                                                                     \
+    constexpr int smem_tc = 2 * AD_PAGE * AD_D + 2 * AD_NPAD * AD_D + AD_P_BYTES + 2048;                              \
+    static DeviceOnce cfgtc;                                                                                          \
+    if (cfgtc.need()) { cudaFuncSetAttribute(attn_decode_kernel<false, 1, GPV, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_tc); } \
+    launch_k<PDL_ATTN>(attn_decode_kernel<false, 1, GPV, 2>, dim3(grid_ctas), dim3(192), smem_tc, stream, 0, tmK, tmV, tmQ, tmK32, tmV32, p); \
+    if (kv8_out_bf16)                                                                                                   \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<true, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
+    else                                                                                                                \
+      launch_k<PDL_COMBINE>(attn_decode_combine_kernel<false, 0>, dim3(B, Hq), dim3(AD_D), 0, stream, 0, part_o, part_ml, seq_lens, (uint16_t*)out, ld_out, Hq, Hkv, G, max_splits, cq, window, sinks); \
+  }
+  if (kv8tc) {
+    if (counters != nullptr) return -1;
+    if (grid_ctas == 2 * sm_count) grid_ctas = 4 * sm_count;       // 43 KB and 80 registers per thread: four CTAs per SM
+    if (G <= 1) FB_AD_LAUNCHTC(1)
+    else if (G <= 2) FB_AD_LAUNCHTC(2)
+    else if (G <= 4) FB_AD_LAUNCHTC(4)
+    else if (G <= 8) FB_AD_LAUNCHTC(8)
+    else FB_AD_LAUNCHTC(16)
+  } else if (kv8) {
     if (G <= 1) FB_AD_LAUNCH8(1)
     else if (G <= 2) FB_AD_LAUNCH8(2)
     else if (G <= 4) FB_AD_LAUNCH8(4)
@@ -643,8 +768,46 @@ extern "C" int fb_attn_decode_opts(const void* q, const void* k_pool, const void
     else FB_AD_LAUNCH8(16)
   } else if (dtype == 1) FB_AD_GP(true) else FB_AD_GP(false)
 #undef FB_AD_LAUNCH8
+#undef FB_AD_LAUNCHTC
 #undef FB_AD_GP
 #undef FB_AD_LAUNCH
+  return (int)cudaGetLastError();
+}
+
+// Two-term e4m3 form of the queries for the fp8 tensor-core mode: q = Qa + Qb / 16 (Qa = fl8(q), Qb = fl8(16 (q - Qa))).
+template <bool BF16>
+__global__ void quant_q_e4m3x2_kernel(const uint16_t* __restrict__ q, uint8_t* __restrict__ qa, uint8_t* __restrict__ qb, long long n8) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const uint4 x = *reinterpret_cast<const uint4*>(q + i * 8);
+  const uint32_t w[4] = {x.x, x.y, x.z, x.w};
+  uint32_t oa[2] = {0u, 0u}, ob[2] = {0u, 0u};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = unpack_16<BF16>(w[j]);
+    unsigned short a8, b8;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(a8) : "f"(f.y), "f"(f.x));
+    uint32_t ah;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(ah) : "h"(a8));
+    const float2 af = __half22float2(*reinterpret_cast<const __half2*>(&ah));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(b8) : "f"((f.y - af.y) * 16.0f), "f"((f.x - af.x) * 16.0f));
+    oa[j >> 1] |= (uint32_t)a8 << ((j & 1) * 16);
+    ob[j >> 1] |= (uint32_t)b8 << ((j & 1) * 16);
+  }
+  *reinterpret_cast<uint2*>(qa + i * 8) = make_uint2(oa[0], oa[1]);
+  *reinterpret_cast<uint2*>(qb + i * 8) = make_uint2(ob[0], ob[1]);
+}
+
+extern "C" int fb_quant_q_e4m3x2(const void* q, void* qa, void* qb, long long n, int dtype, void* stream) {
+  if (n <= 0) return 0;
+  if (n % 8 != 0 || (dtype != 0 && dtype != 1)) return -1;
+  const long long n8 = n / 8;
+  const int blocks = (int)((n8 + 255) / 256);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) launch_k(quant_q_e4m3x2_kernel<true>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)q, (uint8_t*)qa, (uint8_t*)qb, n8);
+  else launch_k(quant_q_e4m3x2_kernel<false>, dim3(blocks), dim3(256), 0, s, 0, (const uint16_t*)q, (uint8_t*)qa, (uint8_t*)qb, n8);
   return (int)cudaGetLastError();
 }
 

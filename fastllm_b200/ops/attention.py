@@ -11,6 +11,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -314,6 +315,15 @@ class DecodeWorkspace:
         self.part_ml = torch.empty((max_batch * num_kv_heads * max_pages * group * 2,), device=device, dtype=torch.float32)
         # arrival counters of the fused combine: zero here, and left at zero by every launch
         self.counters = torch.zeros((max_batch * num_kv_heads,), device=device, dtype=torch.int32)
+        self._q8 = None
+
+    def q8_terms(self, width: int):
+        """Two ``[max_batch, width]`` byte buffers for the e4m3 terms of the queries (fp8 tensor-core mode of the decode kernel)."""
+        if self._q8 is None or self._q8[0].shape[1] != width:
+            dev = self.work.device
+            self._q8 = (torch.empty((self.max_batch, width), device=dev, dtype=torch.uint8),
+                        torch.empty((self.max_batch, width), device=dev, dtype=torch.uint8))
+        return self._q8
 
     def plan(self, seq_lens: torch.Tensor):
         """Flatten (request, page) work items for the current sequence lengths (one tiny launch per step)."""
@@ -342,6 +352,9 @@ def kv_append_fp8(k, v, k_pool, v_pool, slots):
 
 
 KV8_KERNEL = True          # e4m3 page pools run the decode kernel's KV8 mode (tests switch it off to compare with the PyTorch path)
+# e4m3 pages straight into the fp8 tensor core (queries and probabilities as two e4m3 terms each) instead of converting every
+# page to an fp16 operand tile in shared memory
+KV8_MMA = os.environ.get("FB_KV8_MMA", "1") != "0"
 
 
 def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num_kv_heads, head_dim,
@@ -387,9 +400,23 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
     if kv8:
         # e4m3 pages: the kernel turns every raw page into an fp16 operand tile in shared memory (exact conversion) and computes in
         # fp16, so queries go in and the output comes back as fp16
+        work, n_work = (ws.work_w, ws.n_work_w) if window else (ws.work, ws.n_work)
+        if KV8_MMA:
+            qc = q if q.is_contiguous() else q.contiguous()
+            qa, qb = ws.q8_terms(num_q_heads * head_dim)
+            rc = _lib.kernels().fb_quant_q_e4m3x2(_ptr(qc), _ptr(qa), _ptr(qb), B * num_q_heads * head_dim, dtype_code(q.dtype),
+                                                  _stream())
+            _lib.check(rc, "fb_quant_q_e4m3x2")
+            rc = _lib.kernels().fb_attn_decode_opts(_ptr(qa), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(work),
+                                                    _ptr(n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
+                                                    num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
+                                                    ws.work.shape[0], float(scale), 5 if out.dtype == torch.bfloat16 else 4, grid_ctas,
+                                                    _ptr(None), 0, _ptr(qb), num_q_heads * head_dim, _ptr(None), _ptr(None), 0,
+                                                    int(window), float(softcap), _ptr(sinks), _stream())
+            _lib.check(rc, "fb_attn_decode_opts(kv8 mma)")
+            return out
         q16 = q if q.dtype == torch.float16 else q.to(torch.float16)
         o16 = out                       # the combine kernel writes the caller's 16-bit type
-        work, n_work = (ws.work_w, ws.n_work_w) if window else (ws.work, ws.n_work)
         rc = _lib.kernels().fb_attn_decode_opts(_ptr(q16), _ptr(k_pool), _ptr(v_pool), _ptr(o16), o16.stride(0), _ptr(work),
                                                 _ptr(n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
                                                 num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,

@@ -66,6 +66,8 @@ def build_rank_model(spec: dict, rank: int, world: int, device: str):
         ep = EPInfo.from_tp(tp) if (world > 1 and cfg.is_moe and not spec.get("moe_tp")) else None
         model = random_init(cfg, dev, dt, tp=tp, ep=ep, seed=int(spec.get("seed", 0)), std=float(spec.get("std", 0.02)),
                             wdtype=spec.get("wdtype", "auto"), moe_wdtype=spec.get("moe_wdtype") or None)
+        if spec.get("kv_cache_dtype"):
+            model.set_kv_cache_dtype(spec["kv_cache_dtype"])
         eng = LLMEngine(model, ecfg, num_pages=spec.get("num_pages"), eos_token_ids=spec.get("eos_token_ids"))
         return eng, None
     if kind == "hf":

@@ -419,9 +419,12 @@ def test_mla_decode(H):
 
 @pytest.mark.parametrize("Hq,Hkv", [(32, 8), (8, 8), (16, 1)])
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
-def test_attn_decode_fp8_kv(Hq, Hkv, dt):
-    """Decode attention over e4m3 page pools (KV8 mode: raw pages converted to fp16 operand tiles in shared memory) vs the
-    PyTorch evaluation on the same e4m3 values."""
+@pytest.mark.parametrize("mma8", [True, False])
+def test_attn_decode_fp8_kv(Hq, Hkv, dt, mma8, monkeypatch):
+    """Decode attention over e4m3 page pools vs the PyTorch evaluation on the same e4m3 values.  ``mma8``: pages straight into
+    the fp8 tensor core with two-term e4m3 queries / probabilities; else raw pages converted to fp16 operand tiles in shared
+    memory."""
+    monkeypatch.setattr(A, "KV8_MMA", mma8)
     torch.manual_seed(21)
     D = 128
     lens = [1, 127, 128, 129, 700, 1500, 77, 300]
