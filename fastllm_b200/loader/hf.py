@@ -85,6 +85,7 @@ _RENAMES = [
     (r"\.mlp\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),
     (r"\.self_attn\.W_pack\.", ".self_attn.qkv_proj."),                                            # Baichuan: fused [q; k; v]
     (r"\.mlp\.gate\.wg\.", ".mlp.gate."), (r"\.mlp\.shared_mlp\.", ".mlp.shared_experts."),         # Hunyuan-MoE
+    (r"\.mlp\.router\.gate\.", ".mlp.gate."), (r"\.mlp\.expert_bias$", ".mlp.gate.e_score_correction_bias"),   # Hunyuan v3
     # ChatGLM2/3 and original GLM-4 checkpoints
     (r"^transformer\.embedding\.word_embeddings\.", "model.embed_tokens."), (r"^transformer\.encoder\.layers\.", "model.layers."),
     (r"^transformer\.encoder\.final_layernorm\.", "model.norm."), (r"^transformer\.output_layer\.", "lm_head."),
@@ -103,6 +104,9 @@ _RENAMES = [
     (r"\.block_sparse_moe\.experts\.(\d+)\.w3\.", r".mlp.experts.\1.up_proj."),
     (r"\.block_sparse_moe\.experts\.(\d+)\.w2\.", r".mlp.experts.\1.down_proj."),
     (r"\.attn\.c_attn\.", ".self_attn.qkv_proj."), (r"\.attn\.c_proj\.", ".self_attn.o_proj."),
+    (r"\.attn\.qkv_proj\.", ".self_attn.qkv_proj."), (r"\.attn\.out_proj\.", ".self_attn.o_proj."),      # CodeGen / MOSS, GPT-J
+    (r"\.attn\.([qkv])_proj\.", r".self_attn.\1_proj."),
+    (r"\.mlp\.fc_in\.", ".mlp.up_proj."), (r"\.mlp\.fc_out\.", ".mlp.down_proj."),
     (r"\.ln_1\.", ".input_layernorm."), (r"\.ln_2\.", ".post_attention_layernorm."),
     (r"\.mlp\.w2\.", ".mlp.gate_proj."), (r"\.mlp\.w1\.", ".mlp.up_proj."), (r"\.mlp\.c_proj\.", ".mlp.down_proj."),
 ]
@@ -286,7 +290,7 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
 
     def top_fn():
         t = {}
-        for k in ("model.embed_tokens.weight", "model.norm.weight", "lm_head.weight"):
+        for k in ("model.embed_tokens.weight", "model.norm.weight", "model.norm.bias", "lm_head.weight", "lm_head.bias"):
             if ck.has(k):
                 t[k] = ck.raw(k)
         return t

@@ -86,6 +86,8 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
     a, f = lw.attn, lw.mlp
     g = lambda k: t.get(p + k)
     a.ln = _to(g("input_layernorm.weight"), m)
+    if g("input_layernorm.bias") is not None:                   # LayerNorm families: the bias rides beside its weight
+        m.ln_bias[id(a.ln)] = _to(g("input_layernorm.bias"), m)
     if g("pre_feedforward_layernorm.weight") is not None:       # Gemma-2/3: pre- and post-norm around both sub-layers
         a.post_ln = _to(g("post_attention_layernorm.weight"), m)
         f.ln = _to(g("pre_feedforward_layernorm.weight"), m)
@@ -130,7 +132,7 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         kvb = g("self_attn.kv_b_proj.weight").to(torch.float32).view(cfg.num_heads, nope + vd, lora)[r * Hl:(r + 1) * Hl]
         a.w_uk = _to(kvb[:, :nope, :], m)
         a.w_uv = _to(kvb[:, nope:, :], m)
-        a.o = _lin(m, _shard_cols(g("self_attn.o_proj.weight"), r, n), wdtype)
+        a.o = _lin(m, _shard_cols(_rs(g("self_attn.o_proj.weight")), r, n), wdtype)
     else:
         D = cfg.head_dim
         Hq_l = cfg.num_heads // n
@@ -143,6 +145,10 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
                 G = cfg.num_heads // cfg.num_kv_heads
                 wg = w.reshape(cfg.num_kv_heads, G + 2, D, w.shape[-1])
                 w = torch.cat([wg[:, :G].reshape(-1, w.shape[-1]), wg[:, G].reshape(-1, w.shape[-1]), wg[:, G + 1].reshape(-1, w.shape[-1])], dim=0)
+            if cfg.model_type in ("moss", "codegen"):
+                # CodeGen keeps four blocks of [query | value | key] rows, each covering a quarter of the heads
+                w4 = w.reshape(4, 3, cfg.num_heads * D // 4, w.shape[-1])
+                w = torch.cat([w4[:, 0].reshape(-1, w.shape[-1]), w4[:, 2].reshape(-1, w.shape[-1]), w4[:, 1].reshape(-1, w.shape[-1])], dim=0)
             qw, kw, vw = w.split([cfg.num_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D], dim=0)
             bq = bk = bv = None
             if g("self_attn.qkv_proj.bias") is not None:
@@ -198,6 +204,8 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         f.router = g("mlp.gate.weight").to(m.device, torch.float32).contiguous()
         rb = g("mlp.gate.e_score_correction_bias")
         f.router_bias = rb.reshape(-1).to(m.device, torch.float32).contiguous() if rb is not None else None
+        rsc = g("mlp.router_scale")                                  # Pangu Pro MoE: learned per-expert output scale
+        f.router_scale = rsc.reshape(-1).to(m.device, torch.float32).contiguous() if rsc is not None else None
         lo, hi = MOE.local_expert_range(cfg.num_experts, m.ep)
         moe_tp = (m.ep is None or m.ep.size == 1) and n > 1      # no EP: shard every expert's intermediate dim
         gu, dn = [], []
@@ -230,6 +238,10 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
             f.shared_down = _lin(m, _shard_cols(g(sp + "down_proj.weight"), r, n), wdtype)
             sg = g("mlp.shared_expert_gate.weight")
             f.shared_gate = _to(sg, m) if sg is not None else None
+    elif not cfg.mlp_gated:
+        ub, db = g("mlp.up_proj.bias"), _rs(g("mlp.down_proj.bias"))
+        f.up = _lin(m, _shard_rows(g("mlp.up_proj.weight"), r, n), W("mlp.up_proj.weight"), _shard_rows(ub, r, n) if ub is not None else None)
+        f.down = _lin(m, _shard_cols(_rs(g("mlp.down_proj.weight")), r, n), W("mlp.down_proj.weight"), db if (db is not None and r == 0) else None)
     else:
         if g("mlp.gate_up_proj.weight") is not None:           # merged [gate | up]
             gw, uw = g("mlp.gate_up_proj.weight").chunk(2, dim=0)
@@ -305,7 +317,10 @@ def build_top(m, t: dict, wdtype="dense"):
     cfg, tp = m.cfg, m.tp
     m.embed = _to(t["model.embed_tokens.weight"], m)
     m.final_norm = _to(t["model.norm.weight"], m)
+    if t.get("model.norm.bias") is not None:
+        m.ln_bias[id(m.final_norm)] = _to(t["model.norm.bias"], m)
     head = t.get("lm_head.weight")
+    hb = t.get("lm_head.bias")                 # CodeGen / MOSS, GPT-J
     if head is None or cfg.tie_embeddings:
         head = t["model.embed_tokens.weight"]
     if tp.size > 1:
@@ -318,13 +333,15 @@ def build_top(m, t: dict, wdtype="dense"):
         if shard.shape[0] < per:   # keep every rank's shard the same shape (pad rows score -inf via zero weights + mask)
             pad = torch.zeros((per - shard.shape[0], shard.shape[1]), dtype=shard.dtype, device=shard.device)
             shard = torch.cat([shard, pad], dim=0)
+        if hb is not None:
+            hb = torch.cat([hb[lo:hi], torch.zeros(per - (hi - lo), dtype=hb.dtype, device=hb.device)])
         # lm_head stays 16-bit: its rounding decides the sampled token
-        m.lm_head = _lin(m, shard, "dense")
+        m.lm_head = _lin(m, shard, "dense", hb)
     else:
-        if head is t["model.embed_tokens.weight"] and m.embed is not None:
+        if head is t["model.embed_tokens.weight"] and m.embed is not None and hb is None:
             m.lm_head = LinearWeight("dense", m.embed, dtype=m.dtype)
         else:
-            m.lm_head = _lin(m, head, "dense")
+            m.lm_head = _lin(m, head, "dense", hb)
 
 
 def finalize_model(m, top_fn, layer_fn, wdtype="dense", moe_wdtype=None):

@@ -49,6 +49,9 @@ class ModelConfig:
     qk_norm_after_rope: bool = False       # Hunyuan: per-head norm applied after the rotary embedding
     attn_sinks: bool = False               # learned per-head sink logit in the softmax denominator (gpt-oss)
     moe_act: str = "swiglu"                # swiglu | gptoss (clamped, alpha 1.702, (up + 1))
+    norm_kind: str = "rms"                 # rms | layernorm (mean-centred, weight + bias: CodeGen / MOSS, GPT-J)
+    parallel_block: bool = False           # attention and MLP both read the one pre-norm of the layer; one residual add
+    mlp_gated: bool = True                 # False: up projection -> activation -> down projection
     # MoE
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -64,6 +67,7 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     router_bias: bool = False              # e_score_correction_bias
+    route_group_top1: bool = False         # Pangu Pro MoE: the experts form num_experts_per_tok groups; the best of each group is taken
     # MLA
     use_mla: bool = False
     q_lora_rank: int = 0
@@ -116,10 +120,10 @@ class ModelConfig:
         return self.qk_nope_head_dim + self.qk_rope_head_dim if self.use_mla else self.head_dim
 
 
-LLAMA_LIKE = {"llama", "mistral", "internlm", "internlm3", "baichuan", "yi", "deepseek", "qwen2", "qwen3", "minicpm",
+LLAMA_LIKE = {"llama", "mistral", "internlm", "internlm3", "baichuan", "yi", "deepseek", "qwen2", "qwen3", "minicpm", "minicpm3",
               "phi3", "glm4", "glm", "gemma", "gemma2", "ernie4_5", "hunyuan", "telechat", "internlm2", "qwen"}
 MOE_LIKE = {"qwen3_moe", "qwen2_moe", "moe", "mixtral", "deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32",
-            "glm4_moe", "ernie4_5_moe", "minimax_m2", "minimax", "hunyuan_moe", "gpt_oss", "PanguProMoE"}
+            "glm4_moe", "ernie4_5_moe", "minimax_m2", "minimax", "hunyuan_moe", "gpt_oss", "PanguProMoE", "hy_v3"}
 
 
 def _eos_list(v) -> list:
@@ -211,12 +215,27 @@ def from_hf_dict(d: dict) -> ModelConfig:
     if mt in ("hunyuan_v1_dense", "hunyuan_v1_moe"):
         c.qk_norm = True
         c.qk_norm_after_rope = True
+    if mt in ("moss", "codegen", "gptj"):
+        # CodeGen / MOSS-moon and GPT-J: LayerNorm with bias, attention and a two-matrix GELU MLP in parallel from the one
+        # norm of the layer, rotary over the first rotary_dim dims of every head in adjacent pairs
+        # (reference: src/models/moss.cpp:66-84, 99-118)
+        c.norm_kind = "layernorm"
+        c.parallel_block = True
+        c.mlp_gated = False
+        c.rope_mode = "interleaved"
+        c.rotary_dim = int(g("rotary_dim") or c.head_dim)
+        c.hidden_act = g("activation_function", "gelu_new")
+        c.rms_eps = float(g("layer_norm_epsilon", 1e-5))
+        c.intermediate_size = int(g("n_inner") or 4 * c.hidden_size)
+        c.max_position = int(g("n_positions", g("n_ctx", c.max_position)))
+        c.num_kv_heads = c.num_heads
+        c.mlp_bias = True
     if mt in ("granite", "granitemoe"):
         c.attn_scale_override = float(g("attention_multiplier", c.head_dim ** -0.5))
         c.embed_scale = float(g("embedding_multiplier", 1.0))
         c.residual_scale = float(g("residual_multiplier", 1.0))
         c.logit_scale = 1.0 / float(g("logits_scaling", 1.0))
-    if mt == "minicpm":
+    if mt in ("minicpm", "minicpm3"):
         c.embed_scale = float(g("scale_emb", 1.0))
         c.residual_scale = float(g("scale_depth", 1.0)) / (c.num_layers ** 0.5)
         c.logit_scale = 1.0 / (c.hidden_size / float(g("dim_model_base", c.hidden_size)))
@@ -339,6 +358,49 @@ def from_hf_dict(d: dict) -> ModelConfig:
             c.head_dim = c.qk_nope_head_dim + c.qk_rope_head_dim
         if mt == "glm4_moe":
             c.qk_norm = bool(g("use_qk_norm", False))
+    elif mt in ("hy_v3", "HYV3ForCausalLM"):
+        # Hunyuan v3: per-head QK norm before the rotary embedding, softmax or sigmoid router with a selection bias
+        # (``mlp.expert_bias``), renormalised top-k times a scaling factor, shared MLP, leading dense layers; layers stored
+        # beyond num_hidden_layers (multi-token-prediction heads) are not part of the decoder
+        # (reference: src/models/hy_v3.cpp:2217-2232, 2002-2046)
+        c.model_type = "hy_v3"
+        c.qk_norm = True
+        c.num_experts = g("num_experts", 0) or 0
+        c.num_experts_per_tok = g("num_experts_per_tok", g("moe_topk", 0)) or 0
+        c.moe_intermediate_size = g("moe_intermediate_size", g("expert_hidden_dim", c.intermediate_size))
+        c.norm_topk_prob = bool(g("norm_topk_prob", g("route_norm", True)))
+        c.first_k_dense = g("first_k_dense_replace", 0) or 0
+        c.num_shared_experts = g("num_shared_experts", g("n_shared_experts", 0)) or 0
+        c.shared_expert_intermediate_size = c.moe_intermediate_size * c.num_shared_experts
+        c.scoring_func = "sigmoid" if g("moe_router_use_sigmoid", False) else "softmax"
+        c.routed_scaling_factor = float(g("routed_scaling_factor", g("router_scaling_factor", 1.0)))
+        c.router_bias = True
+    elif mt == "PanguProMoE":
+        # Pangu Pro MoE (mixture of grouped experts): softmax scores, one expert from each of num_experts_per_tok equal groups,
+        # weight = score x a learned per-expert scale, no renormalisation; un-gated shared expert; biases on q / k / v / o
+        # (reference: src/models/pangu_moe.cpp:385-432)
+        c.num_experts = g("num_experts", 0) or 0
+        c.num_experts_per_tok = g("num_experts_per_tok", 0) or 0
+        c.moe_intermediate_size = g("moe_intermediate_size", c.intermediate_size)
+        c.norm_topk_prob = False
+        c.route_group_top1 = True
+        c.attention_bias = bool(g("attention_bias", g("qkv_bias", True)))
+        sis = g("shared_expert_intermediate_size", 0) or 0
+        if sis:
+            c.num_shared_experts = 1
+            c.shared_expert_intermediate_size = sis
+    if mt == "minicpm3":
+        # MiniCPM3: multi-head latent attention (rotate-half rotary on the shared rope dims) over dense MLPs, with the MiniCPM
+        # embedding / residual / logit multipliers (reference: src/models/minicpm3.cpp:60-90, 147-152)
+        c.use_mla = True
+        c.q_lora_rank = g("q_lora_rank") or 0
+        c.kv_lora_rank = g("kv_lora_rank", 256)
+        c.qk_nope_head_dim = g("qk_nope_head_dim", 64)
+        c.qk_rope_head_dim = g("qk_rope_head_dim", 32)
+        c.v_head_dim = g("v_head_dim", c.hidden_size // c.num_heads)
+        c.rope_mode = "neox"
+        c.head_dim = c.qk_nope_head_dim + c.qk_rope_head_dim
+        c.num_kv_heads = c.num_heads
     return c
 
 
@@ -410,6 +472,24 @@ def preset(name: str) -> ModelConfig:
         return from_hf_dict(dict(model_type="minimax_m2", vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
                                  num_key_value_heads=2, head_dim=64, intermediate_size=256, num_local_experts=8, num_experts_per_tok=2,
                                  rotary_dim=32, max_position_embeddings=2048, rms_norm_eps=1e-6, eos_token_id=511))
+    if name == "tiny-minicpm3":          # latent attention over dense MLPs with the MiniCPM multipliers
+        return from_hf_dict(dict(model_type="minicpm3", vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                 intermediate_size=512, q_lora_rank=128, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16,
+                                 v_head_dim=32, scale_emb=12.0, scale_depth=1.4, dim_model_base=64, rms_norm_eps=1e-5,
+                                 max_position_embeddings=2048, eos_token_id=511))
+    if name == "tiny-moss":              # LayerNorm, parallel attention / GELU MLP block, partial pairwise rotary
+        return from_hf_dict(dict(model_type="moss", vocab_size=512, n_embd=256, n_layer=2, n_head=4, rotary_dim=32, n_positions=2048,
+                                 activation_function="gelu_new", layer_norm_epsilon=1e-5, eos_token_id=511))
+    if name == "tiny-hy-v3":             # per-head QK norm, sigmoid router with selection bias, shared MLP, one leading dense layer
+        return from_hf_dict(dict(model_type="hy_v3", vocab_size=512, hidden_size=256, num_hidden_layers=3, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128, num_experts=8,
+                                 num_experts_per_tok=2, num_shared_experts=1, first_k_dense_replace=1, moe_router_use_sigmoid=True,
+                                 router_scaling_factor=2.0, max_position_embeddings=2048, rms_norm_eps=1e-6, eos_token_id=511))
+    if name == "tiny-pangu-moe":         # grouped experts: one expert from each of num_experts_per_tok groups
+        return from_hf_dict(dict(model_type="PanguProMoE", vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128, num_experts=8,
+                                 num_experts_per_tok=4, shared_expert_intermediate_size=256, max_position_embeddings=2048,
+                                 rms_norm_eps=1e-5, eos_token_id=511))
     if name == "small-qwen3-next":       # Qwen3-Next layer geometry (128-wide delta-rule heads, 128-wide attention heads) on a small body
         return from_hf_dict(dict(model_type="qwen3_next", vocab_size=1024, hidden_size=512, num_hidden_layers=4, num_attention_heads=4,
                                  num_key_value_heads=2, head_dim=128, intermediate_size=1024, num_experts=8, num_experts_per_tok=2,

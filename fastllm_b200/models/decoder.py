@@ -18,6 +18,7 @@ import math
 from dataclasses import dataclass, field
 
 import torch
+import torch.nn.functional as F
 
 from ..ops import attention as A
 from ..ops import basic as B
@@ -104,12 +105,14 @@ class MLPWeights:
     def __init__(self):
         self.ln = None
         self.gate_up: LinearWeight | None = None
+        self.up: LinearWeight | None = None      # two-matrix MLPs (no gate): up -> activation -> down
         self.down: LinearWeight | None = None
         self.post_ln = None      # sandwich norm on the MLP output
         # MoE
         self.router = None          # fp32 [E, H]
         self.router_16 = None       # 16-bit copy for the tensor-core router GEMM
         self.router_bias = None     # fp32 [E]   selection-only correction bias (DeepSeek-V3)
+        self.router_scale = None    # fp32 [E]   learned per-expert output scale (Pangu Pro MoE)
         self.router_logit_bias = None   # fp32 [E] bias of the router projection itself (gpt-oss)
         self.experts: MOE.ExpertWeights | None = None
         self.shared_gate_up: LinearWeight | None = None
@@ -152,6 +155,7 @@ class DecoderModel:
         # families whose attention needs options outside the tensor-core kernels run the PyTorch evaluation (not graph-safe)
         self.general_attn = bool(cfg.qk_norm_after_rope or cfg.qk_norm_full)
         self.kv8_decode_ok = False
+        self.ln_bias = {}                  # LayerNorm families: id(norm weight) -> its bias
         if cfg.use_mla and cfg.rope_scaling and cfg.rope_scaling.get("mscale_all_dim"):
             ms = 0.1 * float(cfg.rope_scaling["mscale_all_dim"]) * math.log(float(cfg.rope_scaling.get("factor", 1.0))) + 1.0
             self.attn_scale *= ms * ms
@@ -392,6 +396,9 @@ class DecoderModel:
         return self.tp.comm.row_linear(w, x, residual)
 
     def _norm(self, h, ln_w):
+        if self.cfg.norm_kind == "layernorm":
+            return F.layer_norm(h.float(), (h.shape[-1],), ln_w.float(), self.ln_bias[id(ln_w)].float() if id(ln_w) in self.ln_bias else None,
+                                self.cfg.rms_eps).to(h.dtype)
         qm = 0
         if h.is_cuda and h.dim() == 2:
             cons = self._norm_consumers().get(id(ln_w))
@@ -429,6 +436,8 @@ class DecoderModel:
         all-gather to land: that wait moves into the consumer's GEMM, behind its weight prefetch.
         """
         c = self.cfg
+        if next_ln is None:              # parallel block: the attention output joins the residual, the MLP's call normalises
+            return self._row_parallel(w, x, h), None
         if self._beta != 1.0:            # DeepNorm-style residual: the sub-layer's contribution is scaled (linear in x)
             x = x * self._beta
         if post_ln is not None:          # sandwich norm: normalise the sub-layer output, then add it to the residual stream
@@ -506,6 +515,11 @@ class DecoderModel:
 
     def _mlp(self, lw: MLPWeights, x, residual, layer_idx, next_ln, consumer=None):
         c = self.cfg
+        if lw.experts is None and lw.up is not None:         # two-matrix MLP: up -> activation -> down
+            u = lw.up(x).float()
+            code = B.GLU_ACTS.get(c.hidden_act, 1)
+            act = (F.silu(u) if code == 0 else F.gelu(u, approximate="tanh") if code == 1 else F.gelu(u) if code == 2 else torch.relu(u)).to(x.dtype)
+            return self._row_parallel_norm(lw.down, act, residual, next_ln, lw.post_ln, consumer)
         if lw.experts is None:
             if c.hidden_act in ("silu", "swiglu"):
                 act = lw.gate_up(x, swiglu=True)
@@ -516,9 +530,12 @@ class DecoderModel:
         logits = self._router_logits(lw, x)
         if lw.router_logit_bias is not None:
             logits = logits + lw.router_logit_bias
-        idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
-                                  0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
-                                  c.routed_scaling_factor)
+        if c.route_group_top1:
+            idx, wts = MOE.route_group_top1(logits, c.num_experts_per_tok, lw.router_scale)
+        else:
+            idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
+                                      0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
+                                      c.routed_scaling_factor)
         if self._beta != 1.0:
             wts = wts * self._beta
         shared = None
@@ -555,7 +572,7 @@ class DecoderModel:
                 return native.forward(fb, kv_caches)
         fused = self.tp.comm.fused if (self.tp.size > 1 and self.tp.comm is not None) else None
         self._fused_active = bool(fused is not None and self.on_cuda and fused.usable(T, c.hidden_size) and not c.post_norms
-                                  and not c.postnorm_residual)
+                                  and not c.postnorm_residual and not c.parallel_block and c.norm_kind == "rms")
         if fb.is_decode and self.on_cuda and fb.decode_ws is not None and not fb.decode_planned:
             fb.decode_ws.plan(fb.kv_lens)
             fb.decode_planned = True
@@ -575,7 +592,9 @@ class DecoderModel:
                 fa, fbeta, la, lbeta, ma, mbeta = c.resid_factors
                 alpha, self._beta = (la, lbeta) if lw.lin is not None else (fa, fbeta)
                 h = x * alpha if alpha != 1.0 else x
-            if lw.lin is not None:
+            if c.parallel_block:
+                h, _ = self._attention(lw.attn, x, fb, kv_caches[i], h, None, None)       # h + attention(x); the MLP reads x too
+            elif lw.lin is not None:
                 h, x = self._linear_attention(lw.lin, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
             else:
                 h, x = self._attention(lw.attn, x, fb, kv_caches[i], h, lw.mlp.ln, mlp_first)
@@ -726,7 +745,10 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
         raw.clear()
         p = f"model.layers.{i}."
         ones(p + "input_layernorm.weight", H)
-        ones(p + "post_attention_layernorm.weight", H)
+        if cfg.norm_kind == "layernorm":
+            mk(p + "input_layernorm.bias", (H,))
+        if not cfg.parallel_block:
+            ones(p + "post_attention_layernorm.weight", H)
         if cfg.layer_is_linear(i) and cfg.lin_kind == "lightning":
             HD = cfg.num_heads * cfg.head_dim
             mk(p + "self_attn.qkv_proj.weight", (3 * HD, H))
@@ -773,6 +795,8 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
             mk(p + "mlp.gate.weight", (cfg.num_experts, H))
             if cfg.router_bias:
                 raw[p + "mlp.gate.e_score_correction_bias"] = torch.zeros(cfg.num_experts, device=dev, dtype=torch.float32)
+            if cfg.route_group_top1:
+                raw[p + "mlp.router_scale"] = torch.ones(cfg.num_experts, device=dev, dtype=torch.float32)
             lo, hi = MOE.local_expert_range(cfg.num_experts, ep)
             I = cfg.moe_intermediate_size
             # tensors are seeded by name, so only this rank's experts are drawn (with MoE tensor parallelism: all of them)
@@ -793,15 +817,21 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
                     mk(p + "mlp.shared_expert_gate.weight", (1, H))
         else:
             I = cfg.intermediate_size
-            mk(p + "mlp.gate_proj.weight", (I, H))
+            if cfg.mlp_gated:
+                mk(p + "mlp.gate_proj.weight", (I, H))
             mk(p + "mlp.up_proj.weight", (I, H))
             mk(p + "mlp.down_proj.weight", (H, I))
+            if cfg.mlp_bias and not cfg.mlp_gated:
+                mk(p + "mlp.up_proj.bias", (I,))
+                mk(p + "mlp.down_proj.bias", (H,))
         return raw
 
     def top_tensors():
         raw.clear()
         mk("model.embed_tokens.weight", (cfg.vocab_size, H))
         ones("model.norm.weight", H)
+        if cfg.norm_kind == "layernorm":
+            mk("model.norm.bias", (H,))
         if not cfg.tie_embeddings:
             mk("lm_head.weight", (cfg.vocab_size, H))
         return raw

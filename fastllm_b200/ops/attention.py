@@ -90,6 +90,20 @@ def rope_inv_freq(rot_dim: int, base: float, scaling: dict | None = None, max_po
 
 def build_rope_tables(rot_dim: int, max_pos: int, base: float, scaling: dict | None = None, device="cpu"):
     """(cos, sin) fp32 tables ``[max_pos, rot_dim/2]``; the yarn magnitude factor is folded in."""
+    kind = (scaling or {}).get("rope_type", (scaling or {}).get("type", "default"))
+    if kind in ("longrope", "su") and scaling.get("short_factor") is not None:
+        # Phi-3 / MiniCPM3 long-context tables: per-dimension divisors, the short set for positions inside the original window
+        # and the long set beyond it; rows scaled by sqrt(1 + ln(extension) / ln(original window))
+        orig = int(scaling.get("original_max_position_embeddings", max_pos) or max_pos)
+        inv = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+        short = torch.tensor(scaling["short_factor"], dtype=torch.float64)[: rot_dim // 2]
+        long = torch.tensor(scaling.get("long_factor", scaling["short_factor"]), dtype=torch.float64)[: rot_dim // 2]
+        ext = float(scaling.get("factor") or (max_pos / orig if orig else 1.0))
+        ms = scaling.get("attention_factor")
+        ms = float(ms) if ms is not None else (1.0 if ext <= 1.0 else math.sqrt(1.0 + math.log(ext) / math.log(orig)))
+        pos = torch.arange(max_pos, dtype=torch.float64)[:, None]
+        ang = torch.where(pos < orig, pos * (inv / short)[None, :], pos * (inv / long)[None, :])
+        return (ang.cos() * ms).float().to(device).contiguous(), (ang.sin() * ms).float().to(device).contiguous()
     inv, mscale = rope_inv_freq(rot_dim, base, scaling, max_pos)
     ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * inv[None, :]
     return (ang.cos() * mscale).float().to(device).contiguous(), (ang.sin() * mscale).float().to(device).contiguous()

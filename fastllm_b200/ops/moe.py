@@ -60,6 +60,20 @@ def route_topk(logits, bias, topk, score_mode, renorm, n_group=1, topk_group=1, 
     return idx, w
 
 
+def route_group_top1(logits, groups: int, expert_scale=None):
+    """Mixture of grouped experts (Pangu Pro MoE): the experts form ``groups`` equal, contiguous groups and the best-scoring
+    expert of every group is taken; weight = softmax score (over all experts) x the expert's learned scale, not renormalised.
+    Reference: src/models/pangu_moe.cpp:392-430.  Tensor ops only (CUDA-graph safe)."""
+    sc = torch.softmax(logits.float(), dim=-1)
+    M, E = sc.shape
+    per = E // groups
+    val, j = sc.view(M, groups, per).max(dim=-1)
+    idx = j + torch.arange(groups, device=sc.device)[None, :] * per
+    if expert_scale is not None:
+        val = val * expert_scale.float()[idx]
+    return idx.to(torch.int32), val.float()
+
+
 # ---------------------------------------------------------------------------------------------------
 class ExpertWeights:
     """Routed experts owned by this rank: per-expert gate/up (tile-interleaved) and down weights."""

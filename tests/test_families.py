@@ -366,3 +366,138 @@ def test_baichuan_and_internlm3_layouts(tmp_path):
     _save_renamed(ref3, dict(cfg3, model_type="internlm", bias=True), lambda k: k, d1)
     got1 = _last_logits(hf.load_model(d1, device="cpu", dtype=torch.float32), prompt)
     assert torch.nn.functional.cosine_similarity(got1, want3, dim=0).item() > 0.99999
+
+
+def test_minicpm3_and_hy_v3_layouts(tmp_path):
+    """MiniCPM3 (latent attention with rotate-half rotary, dense MLPs, MiniCPM multipliers) from a DeepSeek-V3 oracle whose
+    weights are pre-divided by the multipliers; Hunyuan v3 (router.gate / expert_bias / shared_mlp names, sigmoid router) from a
+    GLM-4-MoE oracle."""
+    prompt = list(range(7, 90, 3))
+    try:
+        ref = _tiny("deepseek_v3", **dict(_MLA, num_hidden_layers=2, first_k_dense_replace=2), n_group=1, topk_group=1, q_lora_rank=128,
+                    rope_interleave=False)
+    except Exception as e:
+        pytest.skip(f"transformers cannot build the oracle: {e}")
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+    scale_emb, scale_depth, base = 12.0, 1.4, 64
+    rs = scale_depth / (2 ** 0.5)
+
+    def merge(sd):
+        out = {}
+        for k, v in sd.items():
+            if k.endswith("embed_tokens.weight"):
+                v = v / scale_emb
+            elif k.endswith("self_attn.o_proj.weight") or k.endswith("mlp.down_proj.weight"):
+                v = v / rs
+            elif k == "lm_head.weight":
+                v = v * (256 / base)
+            out[k] = v
+        return out
+
+    cfgd = dict(ref.config.to_dict(), model_type="minicpm3", scale_emb=scale_emb, scale_depth=scale_depth, dim_model_base=base,
+                tie_word_embeddings=False)
+    for k in ("n_routed_experts", "num_experts_per_tok", "n_shared_experts", "first_k_dense_replace", "moe_intermediate_size"):
+        cfgd.pop(k, None)
+    d = str(tmp_path / "minicpm3")
+    _save_renamed(ref, cfgd, lambda k: k, d, merge)
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert m.cfg.use_mla and not m.cfg.is_moe and m.cfg.rope_mode == "neox"
+    got = _last_logits(m, prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+    assert (got - want).abs().max().item() < 2e-3
+
+    ref2 = _tiny("glm4_moe", **_C, moe_intermediate_size=128, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1,
+                 first_k_dense_replace=1, n_group=1, topk_group=1, partial_rotary_factor=1.0, use_qk_norm=True,
+                 routed_scaling_factor=2.0, norm_topk_prob=True)
+    with torch.no_grad():
+        for n_, p_ in ref2.named_parameters():
+            if n_.endswith("e_score_correction_bias"):
+                p_.copy_(torch.randn_like(p_) * 0.1)
+        want2 = ref2(torch.tensor([prompt])).logits[0, -1].float()
+
+    def rename(k):
+        return (k.replace(".mlp.gate.weight", ".mlp.router.gate.weight").replace(".mlp.gate.e_score_correction_bias", ".mlp.expert_bias")
+                .replace(".mlp.shared_experts.", ".mlp.shared_mlp."))
+
+    c2 = ref2.config
+    cfgd2 = dict(model_type="hy_v3", architectures=["HYV3ForCausalLM"], vocab_size=c2.vocab_size, hidden_size=c2.hidden_size,
+                 num_hidden_layers=c2.num_hidden_layers, num_attention_heads=c2.num_attention_heads,
+                 num_key_value_heads=c2.num_key_value_heads, head_dim=64, intermediate_size=c2.intermediate_size,
+                 moe_intermediate_size=128, num_experts=8, num_experts_per_tok=2, num_shared_experts=1, first_k_dense_replace=1,
+                 moe_router_use_sigmoid=True, route_norm=True, router_scaling_factor=2.0, rms_norm_eps=c2.rms_norm_eps,
+                 rope_theta=ref2.config.to_dict().get("rope_theta", (c2.to_dict().get("rope_parameters") or {}).get("rope_theta", 10000.0)),
+                 max_position_embeddings=c2.max_position_embeddings, tie_word_embeddings=False, attention_bias=bool(c2.attention_bias))
+    def unstack(sd):                      # the oracle keeps its experts stacked: [E, 2I, H] (gate rows, then up rows) and [E, H, I]
+        out = {}
+        for k, v in sd.items():
+            if k.endswith(".mlp.experts.gate_up_proj"):
+                for e in range(v.shape[0]):
+                    gw, uw = v[e].chunk(2, dim=0)
+                    out[k.replace("gate_up_proj", f"{e}.gate_proj.weight")] = gw
+                    out[k.replace("gate_up_proj", f"{e}.up_proj.weight")] = uw
+            elif k.endswith(".mlp.experts.down_proj"):
+                for e in range(v.shape[0]):
+                    out[k.replace("down_proj", f"{e}.down_proj.weight")] = v[e]
+            else:
+                out[k] = v
+        return out
+
+    d2 = str(tmp_path / "hy_v3")
+    _save_renamed(ref2, cfgd2, rename, d2, unstack)
+    m2 = hf.load_model(d2, device="cpu", dtype=torch.float32)
+    assert m2.cfg.scoring_func == "sigmoid" and m2.cfg.num_shared_experts == 1
+    got2 = _last_logits(m2, prompt)
+    assert torch.nn.functional.cosine_similarity(got2, want2, dim=0).item() > 0.99999
+    assert int(got2.argmax()) == int(want2.argmax())
+
+
+def test_pangu_grouped_routing():
+    """Mixture of grouped experts: one expert per group, softmax score times the expert's scale (loop form of
+    src/models/pangu_moe.cpp:392-430), and a tiny Pangu Pro MoE model generating through the engine."""
+    from fastllm_b200.models import preset, random_init
+    from fastllm_b200.ops import moe as MOE
+
+    torch.manual_seed(3)
+    M, E, k = 6, 12, 4
+    logits = torch.randn(M, E)
+    scale = torch.rand(E) + 0.5
+    idx, w = MOE.route_group_top1(logits, k, scale)
+    sc = torch.softmax(logits, -1)
+    per = E // k
+    for r in range(M):
+        for gi in range(k):
+            best = max(range(gi * per, (gi + 1) * per), key=lambda j: sc[r, j].item())
+            assert int(idx[r, gi]) == best
+            assert abs(float(w[r, gi]) - float(sc[r, best] * scale[best])) < 1e-6
+    cfg = preset("tiny-pangu-moe")
+    assert cfg.route_group_top1 and cfg.attention_bias and cfg.num_shared_experts == 1
+    m = random_init(cfg, "cpu", torch.float32, seed=1)
+    got = _last_logits(m, list(range(3, 50)))
+    assert torch.isfinite(got).all() and got.shape[0] == cfg.vocab_size
+
+
+def test_moss_codegen_layout(tmp_path):
+    """MOSS-moon / CodeGen: LayerNorm with bias, attention and GELU MLP in parallel from one norm, pairwise rotary on the first
+    rotary_dim dims, the four-block [query | value | key] projection layout, biased head -- against transformers' CodeGen."""
+    try:
+        ref = _tiny("codegen", vocab_size=512, n_embd=256, n_layer=2, n_head=4, rotary_dim=32, n_positions=512, n_ctx=512,
+                    tie_word_embeddings=False)
+    except Exception as e:
+        pytest.skip(f"transformers cannot build the oracle: {e}")
+    with torch.no_grad():
+        for n_, p_ in ref.named_parameters():
+            if n_.endswith(".bias"):
+                p_.copy_(torch.randn_like(p_) * 0.05)
+    prompt = list(range(11, 95, 3))
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+    cfgd = dict(ref.config.to_dict(), model_type="moss")
+    d = str(tmp_path / "moss")
+    keep = lambda sd: {k: v for k, v in sd.items() if "causal_mask" not in k and "embed_positions" not in k and not k.endswith(".attn.bias")}
+    _save_renamed(ref, cfgd, lambda k: k, d, keep)
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert m.cfg.parallel_block and m.cfg.norm_kind == "layernorm" and not m.cfg.mlp_gated and m.cfg.rotary_dim == 32
+    got = _last_logits(m, prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+    assert (got - want).abs().max().item() < 2e-3
