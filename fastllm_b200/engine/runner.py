@@ -60,7 +60,7 @@ class _DecodeSlot:
         self.logits = None
         self.graph = None
         m = runner.model
-        G = max(1, m.num_heads_local // m.num_kv_heads_local)
+        G = max(1, max([m.num_heads_local] + [lw.attn.heads or 0 for lw in m.layers]) // m.num_kv_heads_local)
         self.ws = None
         if dev.type == "cuda" and not m.cfg.use_mla:
             windows = {int(lw.attn.window) for lw in m.layers if lw.attn.window}

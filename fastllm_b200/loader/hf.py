@@ -85,6 +85,10 @@ _RENAMES = [
     (r"\.mlp\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),
     (r"\.self_attn\.W_pack\.", ".self_attn.qkv_proj."),                                            # Baichuan: fused [q; k; v]
     (r"\.mlp\.gate\.wg\.", ".mlp.gate."), (r"\.mlp\.shared_mlp\.", ".mlp.shared_experts."),         # Hunyuan-MoE
+    # Step-3.5 (router, selection bias, shared expert, experts stacked along dim 0) and Laguna
+    (r"\.moe\.gate\.", ".mlp.gate."), (r"\.moe\.router_bias$", ".mlp.gate.e_score_correction_bias"),
+    (r"\.moe\.(gate|up|down)_proj\.weight$", r".mlp.experts.stacked_\1"), (r"\.moe\.experts\.", ".mlp.experts."),
+    (r"\.share_expert\.", ".mlp.shared_experts."), (r"\.mlp\.experts\.e_score_correction_bias$", ".mlp.gate.e_score_correction_bias"),
     (r"\.mlp\.router\.gate\.", ".mlp.gate."), (r"\.mlp\.expert_bias$", ".mlp.gate.e_score_correction_bias"),   # Hunyuan v3
     # ChatGLM2/3 and original GLM-4 checkpoints
     (r"^transformer\.embedding\.word_embeddings\.", "model.embed_tokens."), (r"^transformer\.encoder\.layers\.", "model.layers."),

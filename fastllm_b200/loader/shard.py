@@ -135,7 +135,12 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         a.o = _lin(m, _shard_cols(_rs(g("self_attn.o_proj.weight")), r, n), wdtype)
     else:
         D = cfg.head_dim
-        Hq_l = cfg.num_heads // n
+        heads_i = cfg.layer_heads[i] if cfg.layer_heads else cfg.num_heads
+        Hq_l = heads_i // n
+        if cfg.layer_heads:
+            a.heads = Hq_l
+        if cfg.layer_rope:
+            a.rope = cfg.layer_rope[i]
         Hkv_l = m.num_kv_heads_local
         kv0 = (r * cfg.num_kv_heads) // n if cfg.num_kv_heads >= n else r // m.kv_replicas
         if g("self_attn.qkv_proj.weight") is not None:        # already merged (phi3-style): [q | k | v]
@@ -149,10 +154,10 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
                 # CodeGen keeps four blocks of [query | value | key] rows, each covering a quarter of the heads
                 w4 = w.reshape(4, 3, cfg.num_heads * D // 4, w.shape[-1])
                 w = torch.cat([w4[:, 0].reshape(-1, w.shape[-1]), w4[:, 2].reshape(-1, w.shape[-1]), w4[:, 1].reshape(-1, w.shape[-1])], dim=0)
-            qw, kw, vw = w.split([cfg.num_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D], dim=0)
+            qw, kw, vw = w.split([heads_i * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D], dim=0)
             bq = bk = bv = None
             if g("self_attn.qkv_proj.bias") is not None:
-                bq, bk, bv = g("self_attn.qkv_proj.bias").split([cfg.num_heads * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D])
+                bq, bk, bv = g("self_attn.qkv_proj.bias").split([heads_i * D, cfg.num_kv_heads * D, cfg.num_kv_heads * D])
         else:
             qw, kw, vw = g("self_attn.q_proj.weight"), g("self_attn.k_proj.weight"), g("self_attn.v_proj.weight")
             bq, bk, bv = g("self_attn.q_proj.bias"), g("self_attn.k_proj.bias"), g("self_attn.v_proj.bias")
@@ -182,6 +187,9 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
             # one norm over all heads: every rank keeps the weights of its own heads (the squares are summed across ranks)
             qn, kn = qn[r * Hq_l * D:(r + 1) * Hq_l * D], kn[kv0 * D:(kv0 + Hkv_l) * D]
         a.q_norm, a.k_norm = _to(qn, m), _to(kn, m)
+        gp = g("self_attn.g_proj.weight")
+        if gp is not None and cfg.head_gate:            # one gate per query head on the attention output
+            a.head_gate = _lin(m, gp[r * Hq_l:(r + 1) * Hq_l], "dense")
         sk = g("self_attn.sinks")
         if sk is not None:
             a.sinks = sk[r * Hq_l:(r + 1) * Hq_l].to(m.device, torch.float32).contiguous()
@@ -211,8 +219,11 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         gu, dn = [], []
         host = getattr(m, "moe_device", None) == "cpu" and m.on_cuda and (getattr(m, "moe_device_layers", -1) < 0 or i < m.moe_device_layers)
         em = _HostPlacement(m) if host else m
+        stk = [g(f"mlp.experts.stacked_{nm}") for nm in ("gate", "up", "down")]      # Step-3.5: [E, rows, cols] per projection
         for e in range(lo, hi):
             gw, uw, dw = (g(f"mlp.experts.{e}.{nm}.weight") for nm in ("gate_proj", "up_proj", "down_proj"))
+            if gw is None and stk[0] is not None:
+                gw, uw, dw = stk[0][e], stk[1][e], stk[2][e]
             span = g(f"mlp.experts.{e}.gate_up_span") if getattr(m, "moe_disk", False) else None
             t.pop(p + f"mlp.experts.{e}.gate_up_span", None)
             if span is not None and not moe_tp and (host or not m.on_cuda) and span.dtype == em.dtype \
@@ -230,6 +241,9 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
             for nm in ("gate_proj", "up_proj", "down_proj"):
                 t.pop(p + f"mlp.experts.{e}.{nm}.weight", None)
         f.experts = MOE.ExpertWeights(cfg.num_experts, lo, gu, dn)
+        if cfg.swiglu_limits and float(cfg.swiglu_limits[i]) != 0.0:
+            f.experts.limit = float(cfg.swiglu_limits[i])
+            f.experts.act = "swiglu_clamp"
         f.experts.host = host
         f.experts.numa = bool(host and getattr(m, "moe_numa", False))
         sp = "mlp.shared_expert." if g("mlp.shared_expert.gate_proj.weight") is not None else "mlp.shared_experts."
@@ -252,6 +266,8 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
                              _shard_rows(bg, r, n) if bg is not None else None, _shard_rows(bu, r, n) if bu is not None else None)
         bd = _rs(bd)
         f.down = _lin(m, _shard_cols(_rs(g("mlp.down_proj.weight")), r, n), W("mlp.down_proj.weight"), bd if (bd is not None and r == 0) else None)
+    if cfg.swiglu_limits_shared:
+        f.act_limit = float(cfg.swiglu_limits_shared[i])
     while len(m.layers) <= i:
         m.layers.append(None)
     m.layers[i] = lw

@@ -52,6 +52,12 @@ class ModelConfig:
     norm_kind: str = "rms"                 # rms | layernorm (mean-centred, weight + bias: CodeGen / MOSS, GPT-J)
     parallel_block: bool = False           # attention and MLP both read the one pre-norm of the layer; one residual add
     mlp_gated: bool = True                 # False: up projection -> activation -> down projection
+    # per-layer attention geometry (Step-3.5 / Laguna: full-attention and sliding-window layers differ)
+    layer_heads: list | None = None        # query heads per layer (None: num_heads everywhere)
+    layer_rope: list | None = None         # per layer {"theta", "rot_dim", "scaling"} (None: the model-wide rotary tables)
+    head_gate: str = ""                    # "sigmoid" | "softplus": g_proj gives one gate per query head on the attention output
+    swiglu_limits: list | None = None      # per layer clamp of the routed experts' SwiGLU (0: none): silu(gate) <= l, |up| <= l
+    swiglu_limits_shared: list | None = None   # same for the dense MLP / shared expert of the layer
     # MoE
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -123,7 +129,8 @@ class ModelConfig:
 LLAMA_LIKE = {"llama", "mistral", "internlm", "internlm3", "baichuan", "yi", "deepseek", "qwen2", "qwen3", "minicpm", "minicpm3",
               "phi3", "glm4", "glm", "gemma", "gemma2", "ernie4_5", "hunyuan", "telechat", "internlm2", "qwen"}
 MOE_LIKE = {"qwen3_moe", "qwen2_moe", "moe", "mixtral", "deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32",
-            "glm4_moe", "ernie4_5_moe", "minimax_m2", "minimax", "hunyuan_moe", "gpt_oss", "PanguProMoE", "hy_v3"}
+            "glm4_moe", "ernie4_5_moe", "minimax_m2", "minimax", "hunyuan_moe", "gpt_oss", "PanguProMoE", "hy_v3", "step3p5", "step3p7",
+            "laguna"}
 
 
 def _eos_list(v) -> list:
@@ -152,7 +159,8 @@ def from_hf_dict(d: dict) -> ModelConfig:
     c.head_dim = g("head_dim") or g("kv_channels") or c.hidden_size // c.num_heads
     c.intermediate_size = g("intermediate_size", g("ffn_hidden_size", c.intermediate_size))
     c.rms_eps = g("rms_norm_eps", g("layernorm_epsilon", g("layer_norm_eps", c.rms_eps)))
-    c.rope_theta = float(g("rope_theta", g("rotary_emb_base", 10000.0)))
+    rt = g("rope_theta", g("rotary_emb_base", 10000.0))
+    c.rope_theta = float(rt[0] if isinstance(rt, list) else (rt or 10000.0))       # Step-3.5 lists one base per layer
     rs = g("rope_scaling") or g("rope_parameters")
     if isinstance(rs, dict) and isinstance(rs.get("full_attention"), dict):
         # per-layer-type rope parameters (Gemma-3): global layers use "full_attention", sliding layers their own base
@@ -389,6 +397,8 @@ def from_hf_dict(d: dict) -> ModelConfig:
         if sis:
             c.num_shared_experts = 1
             c.shared_expert_intermediate_size = sis
+    if mt in ("step3p5", "step3p7", "laguna"):
+        _step_family(c, g, mt)
     if mt == "minicpm3":
         # MiniCPM3: multi-head latent attention (rotate-half rotary on the shared rope dims) over dense MLPs, with the MiniCPM
         # embedding / residual / logit multipliers (reference: src/models/minicpm3.cpp:60-90, 147-152)
@@ -402,6 +412,92 @@ def from_hf_dict(d: dict) -> ModelConfig:
         c.head_dim = c.qk_nope_head_dim + c.qk_rope_head_dim
         c.num_kv_heads = c.num_heads
     return c
+
+
+def _step_family(c: ModelConfig, g, mt: str) -> None:
+    """Step-3.5 / 3.7 (text) and Laguna: full-attention and sliding-window layers with their own head counts, rotary base
+    and rotary width; per-head QK norm; one learned gate per query head on the attention output; sigmoid router with a
+    selection bias, renormalised top-k times a factor, one shared expert; optional clamps inside the SwiGLU.
+    Reference: src/models/step3p5.cpp:4322-4446, 6320-6670; src/models/laguna.cpp:670-830, 1123-1160."""
+    L = c.num_layers
+    c.qk_norm = True
+    c.scoring_func = "sigmoid"
+    c.router_bias = True
+    c.num_shared_experts = 1
+    lt = g("layer_types")
+    if not isinstance(lt, list) or len(lt) != L:
+        lt = ["full_attention" if i % 4 == 0 else "sliding_attention" for i in range(L)]
+    win = int(g("sliding_window", 512) or 0)
+    c.sliding_window = win or None
+    c.layer_windows = [0 if t == "full_attention" else win for t in lt]
+    if mt == "laguna":
+        c.model_type = "laguna"
+        c.head_gate = "softplus"
+        kv = int(g("num_key_value_heads", 8))
+        hp = g("num_attention_heads_per_layer")
+        c.layer_heads = list(hp) if isinstance(hp, list) and len(hp) == L else [c.num_heads] * L
+        c.num_experts = g("num_experts", 0) or 0
+        c.num_experts_per_tok = g("num_experts_per_tok", 0) or 0
+        c.norm_topk_prob = bool(g("norm_topk_prob", True))
+        c.routed_scaling_factor = float(g("moe_routed_scaling_factor", 1.0))
+        c.shared_expert_intermediate_size = g("shared_expert_intermediate_size", 1024)
+        step = max(1, int(g("decoder_sparse_step", 1) or 1))
+        dense = set(g("mlp_only_layers", []) or [])
+        c.mlp_only_layers = [i for i in range(L) if i in dense or (i + 1) % step != 0]
+        rp = g("rope_parameters") or {}
+        full, slide = dict(rp.get("full_attention") or {}), dict(rp.get("sliding_attention") or {})
+        c.rope_theta = float(full.get("rope_theta", 500000.0))
+        c.rope_scaling = None
+        c.rope_local_theta = 0.0
+        fk = full.get("rope_type", full.get("type", "default"))
+        f_rot = max(2, int(c.head_dim * float(full.get("partial_rotary_factor", 0.5))))
+        s_rot = max(2, int(c.head_dim * float(slide.get("partial_rotary_factor", 1.0))))
+        f_spec = {"theta": c.rope_theta, "rot_dim": f_rot, "scaling": full if fk not in ("default", None) else None}
+        s_spec = {"theta": float(slide.get("rope_theta", 10000.0)), "rot_dim": s_rot, "scaling": None}
+        c.layer_rope = [f_spec if t == "full_attention" else s_spec for t in lt]
+        c.rotary_dim = f_rot
+    else:
+        c.model_type = "step3p5"
+        c.head_gate = "sigmoid"
+        c.norm_unit_offset = 1.0               # the checkpoints store norm weights as deltas from one
+        kv = int(g("num_attention_groups", g("num_key_value_heads", 8)))
+        other = g("attention_other_setting") or {}
+        oh = int(other.get("num_attention_heads", c.num_heads))
+        if int(other.get("num_attention_groups", kv)) != kv:
+            raise NotImplementedError("step3p5: sliding-window layers with their own number of KV heads")
+        c.layer_heads = [c.num_heads if t == "full_attention" else oh for t in lt]
+        c.num_experts = g("moe_num_experts", 0) or 0
+        c.num_experts_per_tok = g("moe_top_k", 0) or 0
+        c.norm_topk_prob = bool(g("norm_expert_weight", True))
+        c.routed_scaling_factor = float(g("moe_router_scaling_factor", 1.0))
+        c.router_bias = bool(g("use_moe_router_bias", True))
+        c.shared_expert_intermediate_size = g("share_expert_dim", c.intermediate_size)
+        me = g("moe_layers_enum")
+        if isinstance(me, str):
+            me = [int(v) for v in me.replace(" ", "").split(",") if v]
+        moe_layers = set(me) if me else set(range(1, L))
+        c.mlp_only_layers = [i for i in range(L) if i not in moe_layers]
+        th = g("rope_theta")
+        thetas = [float(v) for v in th] if isinstance(th, list) else [float(th or 10000.0)] * L
+        thetas += [thetas[-1]] * (L - len(thetas))
+        pr = g("partial_rotary_factors")
+        prs = [float(v) for v in pr] if isinstance(pr, list) else [1.0] * L
+        prs += [1.0] * (L - len(prs))
+        sc = g("rope_scaling")
+        llama3 = isinstance(sc, dict) and sc.get("rope_type", sc.get("type")) == "llama3"
+        c.layer_rope = [{"theta": thetas[i], "rot_dim": max(2, int(c.head_dim * prs[i] + 1e-5)),
+                         "scaling": (sc if (llama3 and lt[i] == "full_attention") else None)} for i in range(L)]
+        c.rope_theta = thetas[0]
+        c.rope_scaling = None
+        c.rotary_dim = c.layer_rope[0]["rot_dim"]
+        for key, attr in (("swiglu_limits", "swiglu_limits"), ("swiglu_limits_shared", "swiglu_limits_shared")):
+            v = g(key)
+            if isinstance(v, list) and any(float(x or 0) != 0.0 for x in v):
+                setattr(c, attr, [float(x or 0.0) for x in v] + [0.0] * (L - len(v)))
+    c.num_kv_heads = kv
+    c.moe_intermediate_size = g("moe_intermediate_size", c.intermediate_size)
+    c.moe_layer_freq = 1
+    c.first_k_dense = 0
 
 
 def load_config(path: str | Path) -> ModelConfig:
@@ -480,6 +576,25 @@ def preset(name: str) -> ModelConfig:
     if name == "tiny-moss":              # LayerNorm, parallel attention / GELU MLP block, partial pairwise rotary
         return from_hf_dict(dict(model_type="moss", vocab_size=512, n_embd=256, n_layer=2, n_head=4, rotary_dim=32, n_positions=2048,
                                  activation_function="gelu_new", layer_norm_epsilon=1e-5, eos_token_id=511))
+    if name == "tiny-step3p5":           # full / sliding layers with 4 / 6 query heads, own rotary base and width, head gates
+        return from_hf_dict(dict(model_type="step3p5", vocab_size=512, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                                 num_attention_groups=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128,
+                                 moe_num_experts=8, moe_top_k=2, share_expert_dim=128, moe_router_scaling_factor=2.0,
+                                 attention_other_setting={"num_attention_heads": 6, "num_attention_groups": 2},
+                                 rope_theta=[1e6, 1e4, 1e4, 1e4], partial_rotary_factors=[0.5, 1.0, 1.0, 1.0], sliding_window=16,
+                                 swiglu_limits=[0, 0, 0, 7.0], swiglu_limits_shared=[0, 0, 0, 16.0],
+                                 max_position_embeddings=2048, rms_norm_eps=1e-5, eos_token_id=511))
+    if name == "tiny-laguna":            # Laguna: softplus head gates, yarn rotary on half of each head in the full-attention layers
+        return from_hf_dict(dict(model_type="laguna", vocab_size=512, hidden_size=256, num_hidden_layers=4, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128,
+                                 num_experts=8, num_experts_per_tok=2, shared_expert_intermediate_size=128,
+                                 moe_routed_scaling_factor=2.5, num_attention_heads_per_layer=[4, 6, 6, 6],
+                                 layer_types=["full_attention", "sliding_attention", "sliding_attention", "sliding_attention"],
+                                 mlp_only_layers=[0], sliding_window=16,
+                                 rope_parameters={"full_attention": {"rope_type": "yarn", "rope_theta": 500000.0, "factor": 8.0,
+                                                                     "original_max_position_embeddings": 256, "partial_rotary_factor": 0.5},
+                                                  "sliding_attention": {"rope_type": "default", "rope_theta": 10000.0}},
+                                 max_position_embeddings=2048, rms_norm_eps=1e-6, eos_token_id=511))
     if name == "tiny-hy-v3":             # per-head QK norm, sigmoid router with selection bias, shared MLP, one leading dense layer
         return from_hf_dict(dict(model_type="hy_v3", vocab_size=512, hidden_size=256, num_hidden_layers=3, num_attention_heads=4,
                                  num_key_value_heads=2, head_dim=64, intermediate_size=512, moe_intermediate_size=128, num_experts=8,

@@ -41,9 +41,9 @@ def eligible(model) -> bool:
     c = model.cfg
     if model.on_cuda or model.dtype != torch.float32 or model.tp.size != 1 or not cpu.available():
         return False
-    if c.use_mla or c.num_experts or c.hidden_act not in ("silu", "swiglu") or c.post_norms or model.general_attn or c.final_softcap:
+    if c.use_mla or c.num_experts or c.hidden_act not in ("silu", "swiglu") or c.norm_kind != "rms" or c.parallel_block or not c.mlp_gated or c.post_norms or model.general_attn or c.final_softcap:
         return False
-    if c.has_linear_attn or c.attn_output_gate or c.attn_softcap or c.attn_sinks:
+    if c.has_linear_attn or c.attn_output_gate or c.attn_softcap or c.attn_sinks or c.layer_heads or c.layer_rope or c.head_gate:
         return False
     if any(lw.attn.window or lw.attn.sinks is not None for lw in model.layers):
         return False

@@ -68,6 +68,9 @@ class AttentionWeights:
         self.sinks = None        # per-head sink logits (gpt-oss)
         self.out_gate: LinearWeight | None = None   # per-head output gate projection (Qwen3-Next: sigmoid(gate) * attention)
         self.window = 0          # sliding-window length of this layer (0: full causal attention)
+        self.heads = None        # this rank's query heads in this layer when layers differ (Step-3.5 / Laguna)
+        self.rope = None         # {"theta", "rot_dim", "scaling"} when the layer has its own rotary tables
+        self.head_gate: LinearWeight | None = None  # [heads, H] projection: one gate per query head on the attention output
         # MLA
         self.q_a: LinearWeight | None = None
         self.q_a_norm = None
@@ -108,6 +111,7 @@ class MLPWeights:
         self.up: LinearWeight | None = None      # two-matrix MLPs (no gate): up -> activation -> down
         self.down: LinearWeight | None = None
         self.post_ln = None      # sandwich norm on the MLP output
+        self.act_limit = 0.0     # clamp inside the dense / shared-expert SwiGLU (Step-3.5); 0: none
         # MoE
         self.router = None          # fp32 [E, H]
         self.router_16 = None       # 16-bit copy for the tensor-core router GEMM
@@ -186,6 +190,27 @@ class DecoderModel:
             self._rope = A.build_rope_tables(self.rot_dim, mp, self.cfg.rope_theta, scaling, self.device)
         return self._rope
 
+    def _layer_geom(self, lw, device, local: bool = False):
+        """(query heads, cos, sin, rotary width) of one attention layer: its own where the layers differ."""
+        Hq = lw.heads or self.num_heads_local
+        if lw.rope is None:
+            cos, sin = self.rope_tables(device=device, local=local)
+            return Hq, cos, sin, self.rot_dim
+        spec = lw.rope
+        key = (float(spec["theta"]), int(spec["rot_dim"]), id(spec.get("scaling")), str(torch.device(device)))
+        cache = self.__dict__.setdefault("_rope_layers", {})
+        if key not in cache:
+            mp = min(self.cfg.max_position, 1 << 17)
+            cache[key] = A.build_rope_tables(int(spec["rot_dim"]), mp, float(spec["theta"]), spec.get("scaling"), device)
+        cos, sin = cache[key]
+        return Hq, cos, sin, int(spec["rot_dim"])
+
+    def _head_gate(self, lw, x, a, Hq, D):
+        """Multiply every head of the attention output by its learned gate: sigmoid (Step-3.5) or softplus (Laguna)."""
+        gt = lw.head_gate(x).float()
+        gt = torch.sigmoid(gt) if self.cfg.head_gate == "sigmoid" else F.softplus(gt)
+        return (a.reshape(-1, Hq, D).float() * gt[:, :, None]).reshape(a.shape).to(a.dtype)
+
     def kv_cache_shape(self, num_pages: int):
         """Per-layer page-pool shapes of this rank: (K shape, V shape or None for MLA)."""
         c = self.cfg
@@ -248,8 +273,8 @@ class DecoderModel:
         c = self.cfg
         if c.use_mla:
             return self._mla_attention(lw, x, fb, kv, residual, next_ln, consumer)
-        Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
-        cos, sin = self.rope_tables(device=x.device)
+        Hkv, D = self.num_kv_heads_local, c.head_dim
+        Hq, cos, sin, rot = self._layer_geom(lw, x.device)
         k_pool, v_pool = kv
         variant = bool(c.attn_softcap or lw.window or lw.sinks is not None)
         # sliding window, sink logits and soft-capping run inside the decode kernels; what the fused post-processing cannot
@@ -264,22 +289,26 @@ class DecoderModel:
             k_new = torch.empty((T, Hkv, D), device=x.device, dtype=x.dtype)
             v_new = torch.empty((T, Hkv, D), device=x.device, dtype=x.dtype)
             rows = self._row_ids(T, x.device)
-            q = A.qkv_post(lw.qkv(x), fb.positions, rows, k_new, v_new, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
+            q = A.qkv_post(lw.qkv(x), fb.positions, rows, k_new, v_new, Hq, Hkv, D, cos, sin, self.rope_mode, rot,
                            lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
             A.kv_append_fp8(k_new.view(T, Hkv * D), v_new.view(T, Hkv * D), k_pool, v_pool, fb.slots)
             a = A.attn_decode(q, k_pool, v_pool, fb.page_table, fb.kv_lens, self.attn_scale, Hq, Hkv, D, ws=fb.decode_ws,
                               planned=fb.decode_planned, window=int(lw.window or 0), softcap=float(c.attn_softcap or 0.0), sinks=lw.sinks)
             if lw.out_gate is not None:
                 a = (a.float() * torch.sigmoid(lw.out_gate(x).float())).to(a.dtype)
+            if lw.head_gate is not None:
+                a = self._head_gate(lw, x, a, Hq, D)
             return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
         if (self.general_attn or variant) and not kernel_variant:
             a = self._attention_general(lw, lw.qkv(x), fb, kv)
+            if lw.head_gate is not None:
+                a = self._head_gate(lw, x, a, Hq, D)
             return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
         # decode-sized batches with head_dim 128: projection, per-head norm, RoPE and cache append are one launch
-        q = A.qkv_proj_post(x, lw.qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
+        q = A.qkv_proj_post(x, lw.qkv, fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, rot,
                             lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset) if x.dim() == 2 else None
         if q is None:
-            q = A.qkv_post(lw.qkv(x), fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, self.rot_dim,
+            q = A.qkv_post(lw.qkv(x), fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, rot,
                            lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
         if fb.is_decode:
             qm = 0
@@ -296,6 +325,8 @@ class DecoderModel:
                                cu_q_host=fb.cu_q_host)
         if lw.out_gate is not None:
             a = (a.float() * torch.sigmoid(lw.out_gate(x).float())).to(a.dtype)
+        if lw.head_gate is not None:
+            a = self._head_gate(lw, x, a, Hq, D)
         return self._row_parallel_norm(lw.o, a, residual, next_ln, lw.post_ln, consumer)
 
     def _linear_attention(self, lw: LinearAttnWeights, x, fb: ForwardBatch, state, residual, next_ln, consumer=None):
@@ -358,9 +389,9 @@ class DecoderModel:
     def _attention_general(self, lw: AttentionWeights, qkv, fb: ForwardBatch, kv):
         """Attention for the less common variants (sliding window, sinks, logit soft-capping, norm after RoPE)."""
         c = self.cfg
-        Hq, Hkv, D = self.num_heads_local, self.num_kv_heads_local, c.head_dim
+        Hkv, D = self.num_kv_heads_local, c.head_dim
         T = qkv.shape[0]
-        cos, sin = self.rope_tables(device=qkv.device, local=bool(lw.window))
+        Hq, cos, sin, rot = self._layer_geom(lw, qkv.device, local=bool(lw.window))
         q, k, v = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
         q, k, v = q.reshape(T, Hq, D), k.reshape(T, Hkv, D), v.reshape(T, Hkv, D)
         norm = lambda t, w: A._head_norm_ref(t, w, c.rms_eps, c.norm_unit_offset) if w is not None else t
@@ -377,8 +408,8 @@ class DecoderModel:
                 return (tf * torch.rsqrt(ss / (heads * D) + c.rms_eps) * (w.float() + c.norm_unit_offset)).reshape(t.shape).to(t.dtype)
         if not c.qk_norm_after_rope:
             q, k = norm(q, lw.q_norm), norm(k, lw.k_norm)
-        q = A.apply_rope_ref(q, fb.positions, cos, sin, self.rope_mode, self.rot_dim)
-        k = A.apply_rope_ref(k, fb.positions, cos, sin, self.rope_mode, self.rot_dim)
+        q = A.apply_rope_ref(q, fb.positions, cos, sin, self.rope_mode, rot)
+        k = A.apply_rope_ref(k, fb.positions, cos, sin, self.rope_mode, rot)
         if c.qk_norm_after_rope:
             q, k = norm(q, lw.q_norm), norm(k, lw.k_norm)
         k_pool, v_pool = kv
@@ -521,7 +552,9 @@ class DecoderModel:
             act = (F.silu(u) if code == 0 else F.gelu(u, approximate="tanh") if code == 1 else F.gelu(u) if code == 2 else torch.relu(u)).to(x.dtype)
             return self._row_parallel_norm(lw.down, act, residual, next_ln, lw.post_ln, consumer)
         if lw.experts is None:
-            if c.hidden_act in ("silu", "swiglu"):
+            if lw.act_limit:
+                act = MOE.glu_clamped(lw.gate_up(x), lw.gate_up.interleaved, lw.act_limit)
+            elif c.hidden_act in ("silu", "swiglu"):
                 act = lw.gate_up(x, swiglu=True)
             else:
                 act = self._glu(lw.gate_up(x), c.hidden_act, lw.gate_up.interleaved)
@@ -540,7 +573,10 @@ class DecoderModel:
             wts = wts * self._beta
         shared = None
         if lw.shared_gate_up is not None:
-            shared = lw.shared_down(lw.shared_gate_up(x, swiglu=True))
+            if lw.act_limit:
+                shared = lw.shared_down(MOE.glu_clamped(lw.shared_gate_up(x), lw.shared_gate_up.interleaved, lw.act_limit))
+            else:
+                shared = lw.shared_down(lw.shared_gate_up(x, swiglu=True))
             if self._beta != 1.0:
                 shared = shared * self._beta
             if lw.shared_gate is not None:
@@ -780,12 +816,15 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
             mk(p + "self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim))
         else:
             D = cfg.head_dim
-            mk(p + "self_attn.q_proj.weight", (cfg.num_heads * D * (2 if cfg.attn_output_gate else 1), H))
+            nh = cfg.layer_heads[i] if cfg.layer_heads else cfg.num_heads
+            mk(p + "self_attn.q_proj.weight", (nh * D * (2 if cfg.attn_output_gate else 1), H))
             mk(p + "self_attn.k_proj.weight", (cfg.num_kv_heads * D, H))
             mk(p + "self_attn.v_proj.weight", (cfg.num_kv_heads * D, H))
-            mk(p + "self_attn.o_proj.weight", (H, cfg.num_heads * D))
+            mk(p + "self_attn.o_proj.weight", (H, nh * D))
+            if cfg.head_gate:
+                mk(p + "self_attn.g_proj.weight", (nh, H))
             if cfg.attention_bias:
-                mk(p + "self_attn.q_proj.bias", (cfg.num_heads * D,))
+                mk(p + "self_attn.q_proj.bias", (nh * D,))
                 mk(p + "self_attn.k_proj.bias", (cfg.num_kv_heads * D,))
                 mk(p + "self_attn.v_proj.bias", (cfg.num_kv_heads * D,))
             if cfg.qk_norm:

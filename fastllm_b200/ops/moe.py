@@ -85,7 +85,8 @@ class ExpertWeights:
         self.gate_up = gate_up
         self.down = down
         self.stacked = None     # filled by ops.moe_grouped when a grouped kernel can take the whole set
-        self.act = "swiglu"     # "gptoss": clamped gate/up, gate * sigmoid(1.702 gate) * (up + 1)
+        self.act = "swiglu"     # "gptoss": clamped gate/up, gate * sigmoid(1.702 gate) * (up + 1); "swiglu_clamp": see limit
+        self.limit = 0.0        # "swiglu_clamp" (Step-3.5): min(silu(gate), limit) * clamp(up, -limit, limit)
         self.host = False       # expert weights live in CPU memory and run on the native CPU backend (hybrid placement)
         self._host_arrays = None
 
@@ -101,6 +102,21 @@ def glu_gptoss(gu, interleaved: bool, limit: float = 7.0, alpha: float = 1.702):
     g = g.float().clamp(max=limit)
     u = u.float().clamp(min=-limit, max=limit)
     return ((u + 1.0) * (g * torch.sigmoid(g * alpha))).to(gu.dtype)
+
+
+def glu_clamped(gu, interleaved: bool, limit: float):
+    """SwiGLU with the activated gate capped at ``limit`` and the up branch clamped to ``[-limit, limit]``
+    (reference: src/models/step3p5.cpp:6604-6612)."""
+    if interleaved:
+        n = gu.shape[-1]
+        t = gu.reshape(*gu.shape[:-1], n // 128, 2, 64)
+        g, u = t[..., 0, :].reshape(*gu.shape[:-1], n // 2), t[..., 1, :].reshape(*gu.shape[:-1], n // 2)
+    else:
+        g, u = gu.chunk(2, dim=-1)
+    a = torch.nn.functional.silu(g.float())
+    if limit:
+        a, u = a.clamp(max=limit), u.float().clamp(min=-limit, max=limit)
+    return (a * u.float()).to(gu.dtype)
 
 
 def local_expert_range(num_experts: int, ep) -> tuple[int, int]:
@@ -151,6 +167,8 @@ def moe_forward(x, idx, wts, experts: ExpertWeights, ep=None):
         le = e - experts.first
         if experts.act == "gptoss":
             he = experts.down[le](glu_gptoss(experts.gate_up[le](xe), experts.gate_up[le].interleaved))
+        elif experts.act == "swiglu_clamp":
+            he = experts.down[le](glu_clamped(experts.gate_up[le](xe), experts.gate_up[le].interleaved, experts.limit))
         else:
             he = experts.down[le](experts.gate_up[le](xe, swiglu=True))
         y.index_add_(0, rows, he.float() * w_sorted[start:start + n, None])

@@ -501,3 +501,136 @@ def test_moss_codegen_layout(tmp_path):
     got = _last_logits(m, prompt)
     assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
     assert (got - want).abs().max().item() < 2e-3
+
+
+def _step3p5_reference(sd, cfg, ids):
+    """Plain full-sequence evaluation of the Step-3.5 text decoder from a state dict in the checkpoint's own naming
+    (reference semantics: src/models/step3p5.cpp:6320-6670)."""
+    import math
+
+    F = torch.nn.functional
+    D, L, eps = cfg["head_dim"], cfg["num_hidden_layers"], cfg["rms_norm_eps"]
+    kv = cfg["num_attention_groups"]
+    lt = cfg["layer_types"]
+    T = len(ids)
+    rms = lambda t, w: t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * (w + 1.0)
+    pos = torch.arange(T, dtype=torch.float32)
+
+    def rope(t, theta, rot):
+        inv = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+        ang = pos[:, None] * inv[None, :]
+        c, s = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        a, b, rest = t[..., :rot // 2], t[..., rot // 2:rot], t[..., rot:]
+        return torch.cat([a * c - b * s, b * c + a * s, rest], dim=-1)
+
+    def glu(g, u, lim):
+        a = F.silu(g)
+        if lim:
+            a, u = a.clamp(max=lim), u.clamp(min=-lim, max=lim)
+        return a * u
+
+    x = sd["model.embed_tokens.weight"][ids]
+    for i in range(L):
+        p = f"model.layers.{i}."
+        full = lt[i] == "full_attention"
+        nh = cfg["num_attention_heads"] if full else cfg["attention_other_setting"]["num_attention_heads"]
+        h = rms(x, sd[p + "input_layernorm.weight"])
+        q = (h @ sd[p + "self_attn.q_proj.weight"].t()).view(T, nh, D)
+        k = (h @ sd[p + "self_attn.k_proj.weight"].t()).view(T, kv, D)
+        v = (h @ sd[p + "self_attn.v_proj.weight"].t()).view(T, kv, D)
+        q, k = rms(q, sd[p + "self_attn.q_norm.weight"]), rms(k, sd[p + "self_attn.k_norm.weight"])
+        rot = int(D * cfg["partial_rotary_factors"][i])
+        q, k = rope(q, cfg["rope_theta"][i], rot), rope(k, cfg["rope_theta"][i], rot)
+        k, v = k.repeat_interleave(nh // kv, dim=1), v.repeat_interleave(nh // kv, dim=1)
+        sc = torch.einsum("qhd,khd->hqk", q, k) / math.sqrt(D)
+        qi, ki = torch.arange(T)[:, None], torch.arange(T)[None, :]
+        mask = ki > qi
+        if not full:
+            mask = mask | (ki <= qi - cfg["sliding_window"])
+        a = torch.einsum("hqk,khd->qhd", torch.softmax(sc.masked_fill(mask[None], float("-inf")), -1), v)
+        a = a * torch.sigmoid(h @ sd[p + "self_attn.g_proj.weight"].t())[:, :, None]
+        x = x + a.reshape(T, nh * D) @ sd[p + "self_attn.o_proj.weight"].t()
+        h = rms(x, sd[p + "post_attention_layernorm.weight"])
+        ls, le = cfg["swiglu_limits_shared"][i], cfg["swiglu_limits"][i]
+        if i in cfg["moe_layers"]:
+            y = glu(h @ sd[p + "share_expert.gate_proj.weight"].t(), h @ sd[p + "share_expert.up_proj.weight"].t(), ls) \
+                @ sd[p + "share_expert.down_proj.weight"].t()
+            pr = torch.sigmoid(h @ sd[p + "moe.gate.weight"].t())
+            idx = (pr + sd[p + "moe.router_bias"]).topk(cfg["moe_top_k"], dim=-1)[1]
+            w = pr.gather(1, idx)
+            w = w / w.sum(-1, keepdim=True) * cfg["moe_router_scaling_factor"]
+            for t in range(T):
+                for j in range(idx.shape[1]):
+                    e = int(idx[t, j])
+                    he = glu(h[t] @ sd[p + "moe.gate_proj.weight"][e].t(), h[t] @ sd[p + "moe.up_proj.weight"][e].t(), le)
+                    y[t] += w[t, j] * (he @ sd[p + "moe.down_proj.weight"][e].t())
+            x = x + y
+        else:
+            x = x + glu(h @ sd[p + "mlp.gate_proj.weight"].t(), h @ sd[p + "mlp.up_proj.weight"].t(), ls) @ sd[p + "mlp.down_proj.weight"].t()
+    return rms(x, sd["model.norm.weight"]) @ sd["lm_head.weight"].t()
+
+
+def test_step3p5_checkpoint(tmp_path):
+    """Step-3.5 text decoder from a checkpoint in its own naming (stacked experts under ``moe.``, ``share_expert.``,
+    ``g_proj`` head gates, norm weights stored as deltas from one): layers with 4 / 6 query heads, their own rotary base and
+    width, sliding windows, clamped SwiGLU -- against a plain full-sequence evaluation."""
+    import json
+    import os
+
+    from fastllm_b200.loader.safetensors import save_file
+
+    torch.manual_seed(5)
+    H, D, L, E, I, V = 128, 32, 4, 8, 64, 256
+    cfg = dict(model_type="step3p5", vocab_size=V, hidden_size=H, num_hidden_layers=L, num_attention_heads=4, num_attention_groups=2,
+               head_dim=D, intermediate_size=128, moe_intermediate_size=I, moe_num_experts=E, moe_top_k=2, share_expert_dim=64,
+               moe_router_scaling_factor=2.0, attention_other_setting={"num_attention_heads": 6, "num_attention_groups": 2},
+               layer_types=["full_attention", "sliding_attention", "sliding_attention", "full_attention"],
+               rope_theta=[1e6, 1e4, 1e4, 1e6], partial_rotary_factors=[0.5, 1.0, 1.0, 0.5], sliding_window=8,
+               swiglu_limits=[0, 0, 0.05, 0.05], swiglu_limits_shared=[0, 0, 0, 0.08], moe_layers_enum="1,2,3",
+               max_position_embeddings=512, rms_norm_eps=1e-5, tie_word_embeddings=False)
+    r = lambda *s: torch.randn(*s) * 0.08
+    sd = {"model.embed_tokens.weight": r(V, H), "model.norm.weight": r(H), "lm_head.weight": r(V, H)}
+    for i in range(L):
+        p = f"model.layers.{i}."
+        nh = 4 if cfg["layer_types"][i] == "full_attention" else 6
+        sd.update({p + "input_layernorm.weight": r(H), p + "post_attention_layernorm.weight": r(H),
+                   p + "self_attn.q_proj.weight": r(nh * D, H), p + "self_attn.k_proj.weight": r(2 * D, H),
+                   p + "self_attn.v_proj.weight": r(2 * D, H), p + "self_attn.o_proj.weight": r(H, nh * D),
+                   p + "self_attn.q_norm.weight": r(D), p + "self_attn.k_norm.weight": r(D), p + "self_attn.g_proj.weight": r(nh, H)})
+        if i == 0:
+            sd.update({p + "mlp.gate_proj.weight": r(128, H), p + "mlp.up_proj.weight": r(128, H), p + "mlp.down_proj.weight": r(H, 128)})
+        else:
+            sd.update({p + "moe.gate.weight": r(E, H), p + "moe.router_bias": r(E), p + "moe.gate_proj.weight": r(E, I, H),
+                       p + "moe.up_proj.weight": r(E, I, H), p + "moe.down_proj.weight": r(E, H, I),
+                       p + "share_expert.gate_proj.weight": r(64, H), p + "share_expert.up_proj.weight": r(64, H),
+                       p + "share_expert.down_proj.weight": r(H, 64)})
+    d = str(tmp_path / "step3p5")
+    os.makedirs(d)
+    save_file({k: v.contiguous() for k, v in sd.items()}, os.path.join(d, "model.safetensors"), metadata={"format": "pt"})
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(cfg, f)
+    prompt = list(range(3, 75, 2))
+    want = _step3p5_reference(sd, dict(cfg, moe_layers={1, 2, 3}), prompt)[-1]
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert m.cfg.layer_heads == [4, 6, 6, 4] and m.layers[2].mlp.experts.act == "swiglu_clamp" and m.layers[1].attn.window == 8
+    got = _last_logits(m, prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+    assert (got - want).abs().max().item() < 2e-3
+
+
+def test_laguna_preset_runs():
+    """Laguna: softplus head gates, yarn rotary over half of each head in the full-attention layers; chunked prefill plus
+    decode reproduces the one-shot prefill logits."""
+    from fastllm_b200.models import preset, random_init
+
+    cfg = preset("tiny-laguna")
+    assert cfg.head_gate == "softplus" and cfg.layer_rope[0]["scaling"]["rope_type"] == "yarn" and cfg.layer_rope[1]["rot_dim"] == 64
+    m = random_init(cfg, "cpu", torch.float32, seed=2, std=0.05)
+    prompt = list(range(4, 64))
+    full = _last_logits(m, prompt)
+    eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512, chunked_prefill_size=16), num_pages=8)
+    from fastllm_b200.engine import GenerationConfig
+
+    toks = eng.generate([prompt], GenerationConfig(max_new_tokens=2, ignore_eos=True))[0]
+    assert torch.isfinite(full).all()
+    assert int(toks[0]) == int(full.argmax())
