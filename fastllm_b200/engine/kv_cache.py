@@ -108,8 +108,16 @@ class KVCache:
                 cs, rs = model.linear_state_shapes(state_slots + 1)
                 self.pools.append((torch.zeros(cs, device=dev, dtype=model.dtype), torch.zeros(rs, device=dev, dtype=torch.float32)))
                 continue
-            k = torch.zeros(ks, device=dev, dtype=dt)
-            v = torch.zeros(vs, device=dev, dtype=dt) if vs is not None else None
+            lks, lvs = ks, vs
+            if hasattr(model, "kv_cache_shape_layer"):
+                # layers with their own page shape; a layer that projects no keys / values reads an earlier layer's pools
+                shp = model.kv_cache_shape_layer(i, num_pages)
+                if shp is None:
+                    self.pools.append(self.pools[model.kv_donor(i)])
+                    continue
+                lks, lvs = shp
+            k = torch.zeros(lks, device=dev, dtype=dt)
+            v = torch.zeros(lvs, device=dev, dtype=dt) if lvs is not None else None
             self.pools.append((k, v))
         self.manager = PageManager(num_pages, page_len)
 

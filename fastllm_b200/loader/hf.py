@@ -90,6 +90,9 @@ _RENAMES = [
     (r"\.moe\.(gate|up|down)_proj\.weight$", r".mlp.experts.stacked_\1"), (r"\.moe\.experts\.", ".mlp.experts."),
     (r"\.share_expert\.", ".mlp.shared_experts."), (r"\.mlp\.experts\.e_score_correction_bias$", ".mlp.gate.e_score_correction_bias"),
     (r"\.mlp\.router\.gate\.", ".mlp.gate."), (r"\.mlp\.expert_bias$", ".mlp.gate.e_score_correction_bias"),   # Hunyuan v3
+    # TeleChat
+    (r"^transformer\.word_embeddings\.", "model.embed_tokens."), (r"^transformer\.lm_head\.", "lm_head."),
+    (r"\.self_attention\.query\.", ".self_attn.q_proj."), (r"\.self_attention\.key_value\.", ".self_attn.kv_proj."),
     # ChatGLM2/3 and original GLM-4 checkpoints
     (r"^transformer\.embedding\.word_embeddings\.", "model.embed_tokens."), (r"^transformer\.encoder\.layers\.", "model.layers."),
     (r"^transformer\.encoder\.final_layernorm\.", "model.norm."), (r"^transformer\.output_layer\.", "lm_head."),
@@ -284,6 +287,14 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
 
         staged = split_layers_by_map(cfg.num_layers, device_map)
         device = staged[0]
+    if cfg.model_type in ("gemma4", "gemma4_text"):
+        from ..models import gemma4
+
+        if tp is not None and tp.size > 1:
+            raise NotImplementedError("gemma4 runs on one rank")
+        m = gemma4.build(ck, cfg, device, dtype, wdtype if wdtype != "auto" else "dense", moe_wdtype)
+        ck.close()
+        return m
     m = DecoderModel(cfg, device, dtype, tp, ep)
     m.moe_disk = moe_device == "disk"
     ck.want_spans = m.moe_disk

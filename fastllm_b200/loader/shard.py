@@ -161,6 +161,18 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         else:
             qw, kw, vw = g("self_attn.q_proj.weight"), g("self_attn.k_proj.weight"), g("self_attn.v_proj.weight")
             bq, bk, bv = g("self_attn.q_proj.bias"), g("self_attn.k_proj.bias"), g("self_attn.v_proj.bias")
+            if kw is None and g("self_attn.kv_proj.weight") is not None:
+                # TeleChat: one projection with rows [head][key | value]
+                kvw = g("self_attn.kv_proj.weight").reshape(cfg.num_kv_heads, 2, D, -1)
+                kw, vw = kvw[:, 0].reshape(cfg.num_kv_heads * D, -1), kvw[:, 1].reshape(cfg.num_kv_heads * D, -1)
+                kvb = g("self_attn.kv_proj.bias")
+                if kvb is not None:
+                    kvb = kvb.reshape(cfg.num_kv_heads, 2, D)
+                    bk, bv = kvb[:, 0].reshape(-1), kvb[:, 1].reshape(-1)
+                    if bq is None:
+                        bq = torch.zeros(heads_i * D, dtype=kvb.dtype)
+                elif bq is not None:
+                    bk = bv = torch.zeros(cfg.num_kv_heads * D, dtype=bq.dtype)
             if cfg.attn_output_gate:
                 # q_proj carries [query | gate] per head: the gate rows become their own projection
                 qg = qw.reshape(cfg.num_heads, 2, D, qw.shape[-1])

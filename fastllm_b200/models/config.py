@@ -223,6 +223,13 @@ def from_hf_dict(d: dict) -> ModelConfig:
     if mt in ("hunyuan_v1_dense", "hunyuan_v1_moe"):
         c.qk_norm = True
         c.qk_norm_after_rope = True
+    if mt == "telechat":
+        # TeleChat-7B / 12B and TeleChat2: llama-like; keys and values come out of one projection interleaved per head; the
+        # first generation rotates with a fixed NTK base 10000 * 3^(d / (d - 2)) (reference: src/models/graph/telechat.cpp:11-43)
+        c.intermediate_size = g("ffn_hidden_size", c.intermediate_size)
+        c.max_position = g("seq_length", g("max_position_embeddings", c.max_position))
+        if "Telechat2ForCausalLM" not in (c.architectures or []) and not g("rope_theta"):
+            c.rope_theta = 10000.0 * 3.0 ** (c.head_dim / (c.head_dim - 2))
     if mt in ("moss", "codegen", "gptj"):
         # CodeGen / MOSS-moon and GPT-J: LayerNorm with bias, attention and a two-matrix GELU MLP in parallel from the one
         # norm of the layer, rotary over the first rotary_dim dims of every head in adjacent pairs

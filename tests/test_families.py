@@ -634,3 +634,98 @@ def test_laguna_preset_runs():
     toks = eng.generate([prompt], GenerationConfig(max_new_tokens=2, ignore_eos=True))[0]
     assert torch.isfinite(full).all()
     assert int(toks[0]) == int(full.argmax())
+
+
+def test_telechat_layout(tmp_path):
+    """TeleChat: ``transformer.h.N.self_attention.query / key_value / dense`` (keys and values interleaved per head, biases on
+    the output projections), fixed NTK rotary base -- from a llama oracle with the same base."""
+    D = 64
+    theta = 10000.0 * 3.0 ** (D / (D - 2))
+    ref = _tiny("llama", **dict(_C, num_key_value_heads=4), rope_theta=theta, attention_bias=True, mlp_bias=True)
+    with torch.no_grad():
+        for n_, p_ in ref.named_parameters():
+            if n_.endswith(".bias"):
+                p_.copy_(torch.randn_like(p_) * 0.05)
+    prompt = list(range(9, 80, 2))
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+
+    def merge(sd):
+        out = {}
+        for k, v in sd.items():
+            if ".k_proj." in k:
+                vv = sd[k.replace(".k_proj.", ".v_proj.")]
+                kk = v.reshape(4, 1, D, -1) if v.dim() == 2 else v.reshape(4, 1, D)
+                vv = vv.reshape(4, 1, D, -1) if vv.dim() == 2 else vv.reshape(4, 1, D)
+                out[k.replace(".self_attn.k_proj.", ".self_attention.key_value.")] = torch.cat([kk, vv], dim=1).reshape(-1, *v.shape[1:])
+            elif ".v_proj." in k:
+                continue
+            else:
+                out[k] = v
+        return out
+
+    def rename(k):
+        k = k.replace("model.embed_tokens.", "transformer.word_embeddings.").replace("model.layers.", "transformer.h.")
+        k = k.replace("model.norm.", "transformer.ln_f.").replace("lm_head.", "transformer.lm_head.")
+        return k.replace(".self_attn.q_proj.", ".self_attention.query.").replace(".self_attn.o_proj.", ".self_attention.dense.")
+
+    c = ref.config
+    cfgd = dict(model_type="telechat", architectures=["TelechatForCausalLM"], vocab_size=c.vocab_size, hidden_size=c.hidden_size,
+                n_layer=c.num_hidden_layers, n_head=c.num_attention_heads, ffn_hidden_size=c.intermediate_size, seq_length=512,
+                layer_norm_epsilon=c.rms_norm_eps, tie_word_embeddings=False, attention_bias=True)
+    d = str(tmp_path / "telechat")
+    _save_renamed(ref, cfgd, rename, d, merge)
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert abs(m.cfg.rope_theta - theta) < 1e-3
+    got = _last_logits(m, prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+    assert (got - want).abs().max().item() < 2e-3
+
+
+_G4 = dict(model_type="gemma4_text", vocab_size=512, hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+           num_key_value_heads=2, head_dim=32, global_head_dim=64, max_position_embeddings=512, sliding_window=16,
+           layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"], final_logit_softcapping=30.0,
+           vocab_size_per_layer_input=512, pad_token_id=0)
+
+
+@pytest.mark.parametrize("variant", ["per_layer_inputs_shared_kv", "moe_k_eq_v"])
+def test_gemma4_text_matches_transformers(variant, tmp_path):
+    """Gemma-4 text: layers with their own head width and page pools, keys / values shared by the last layers, values from
+    the key projection, per-layer token inputs, proportional rotary, the expert block beside the dense MLP."""
+    extra = (dict(hidden_size_per_layer_input=16, num_kv_shared_layers=2, use_double_wide_mlp=True) if variant.startswith("per_layer")
+             else dict(hidden_size_per_layer_input=0, attention_k_eq_v=True, num_global_key_value_heads=1, enable_moe_block=True,
+                       num_experts=4, top_k_experts=2, moe_intermediate_size=64))
+    torch.manual_seed(0)
+    try:
+        cfg = transformers.AutoConfig.for_model(**dict(_G4, **extra))
+        ref = transformers.AutoModelForCausalLM.from_config(cfg, torch_dtype=torch.float32, attn_implementation="eager")
+    except Exception as e:
+        pytest.skip(f"transformers cannot build gemma4_text: {e}")
+    with torch.no_grad():
+        for n_, p_ in ref.named_parameters():
+            if p_.dim() >= 2:
+                torch.nn.init.normal_(p_, std=0.05)
+            else:
+                p_.copy_(1.0 + torch.randn_like(p_) * 0.1)
+        for n_, b_ in ref.named_buffers():
+            if n_.endswith("layer_scalar"):
+                b_.fill_(0.9)
+    ref.eval()
+    d = str(tmp_path / "g4")
+    ref.save_pretrained(d, safe_serialization=True)
+    prompt = list(range(5, 90, 3))
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    got = _last_logits(m, prompt)[:want.numel()]
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+    assert (got - want).abs().max().item() < 2e-3
+    # chunked prefill then decode steps through the engine (shared pools, per-layer page shapes) agree with one-shot logits
+    from fastllm_b200.engine import GenerationConfig
+
+    eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512, chunked_prefill_size=16), num_pages=8)
+    toks = eng.generate([prompt], GenerationConfig(max_new_tokens=3, ignore_eos=True))[0]
+    assert int(toks[0]) == int(want.argmax())
+    with torch.no_grad():
+        want2 = ref(torch.tensor([prompt + [int(toks[0])]])).logits[0, -1].float()
+    assert int(toks[1]) == int(want2.argmax())
