@@ -39,7 +39,7 @@ def parse_args():
     ap.add_argument("--batch", type=int, default=64)
     ap.add_argument("--prompt-len", type=int, default=1024)
     ap.add_argument("--output-len", type=int, default=256)
-    ap.add_argument("--dtype", default="auto", help="weight dtype: auto(bf16) | int8 | int4g128 | fp8")
+    ap.add_argument("--dtype", default="auto", help="weight dtype: auto(bf16) | int8 | int4g128 | fp8 | nvfp4 | mxfp4")
     ap.add_argument("--comm", default="auto", choices=["auto", "fused", "nccl"])
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--device", default="cuda", choices=["cuda", "cpu"],

@@ -4,6 +4,8 @@
 //   int8   per-output-channel asymmetric      w = scale[n] * (q - zero[n])
 //   int4g  group-wise asymmetric, 2 per byte, first value in the HIGH nibble      w = min[n,g] + scale[n,g] * q
 //   fp8    FP8-E4M3 with one fp32 scale per 128x128 block                          w = scale[n/128,k/128] * q
+//   fp4    e2m1, 2 per byte, first value in the LOW nibble, one bf16 scale per 16 (NVFP4: e4m3-valued scales and a
+//          per-tensor fp32 factor) or 32 (MXFP4: power-of-two scales) k elements    w = global * scale[n,k/g] * q
 // The reference serves these with CUDA-core GEMV kernels for small batches and dequant-to-fp16 + cublasGemmEx
 // otherwise (src/devices/cuda/linear/fastllm-linear-int8.cu, -int4group.cu:1919-2054, -fp8.cu:1778-1868).
 //
@@ -24,20 +26,21 @@ FB_DEFINE_ERROR_API(gemm_quant)
 namespace fb {
 
 constexpr int KID_GEMM_QUANT = 3;
-enum QMode : int { Q_INT8 = 1, Q_INT4G = 2, Q_FP8 = 3 };
+enum QMode : int { Q_INT8 = 1, Q_INT4G = 2, Q_FP8 = 3, Q_FP4 = 4 };
 
 struct QuantParams {
-  const float* scale;     // int8: [N]; fp8: [ceil(N/128), kb128]; int4g: float2 (scale, min) [groups, N]
-  const float* zero;      // int8: [N]
-  int group_k;            // int4g: k elements per group (multiple of 64); fp8: 128
+  const float* scale;     // int8: [N]; fp8: [ceil(N/128), kb128]; int4g: float2 (scale, min) [groups, N]; fp4: bf16 [N, groups]
+  const float* zero;      // int8: [N]; fp4: one per-tensor factor (null: 1)
+  int group_k;            // int4g: k elements per group (multiple of 64); fp8: 128; fp4: 16 or 32
   int groups;             // int4g: groups per row; fp8: scale columns
-  uint32_t xor_mask;      // int8: 0x80808080 when the bytes are stored as q - 128 (operand form of the integer path), else 0
+  uint32_t xor_mask;      // int8: 0x80808080 when the bytes are stored as q - 128 (operand form of the integer path), else 0;
+                          // fp4: 1 when the scale table lies within fp16's range (fp16 activations: half2 de-quantiser)
 };
 
 // OCC: CTAs per SM the shared-memory budget is sized for (2 doubles the dequant warps working per SM)
 template <int MPAD, int QM, int OCC = (MPAD <= 64 ? 2 : 1)>
 struct QuantCfg {
-  static constexpr int RAW_BYTES = QM == Q_INT4G ? 128 * 32 : 128 * 64;
+  static constexpr int RAW_BYTES = (QM == Q_INT4G || QM == Q_FP4) ? 128 * 32 : 128 * 64;
   static constexpr int B_BYTES = MPAD * 128;
   static constexpr int STAGE_BYTES = RAW_BYTES + B_BYTES;            // bytes TMA delivers per stage
   static constexpr int PITCH = (STAGE_BYTES + 1023) / 1024 * 1024;   // stage pitch: keeps the swizzled activation tile 1024-aligned
@@ -53,7 +56,7 @@ struct QuantCfg {
   static constexpr int TMEM_COLS = MPAD < 32 ? 32 : MPAD;
   // dequant warps: four per CTA with two CTAs per SM; eight when the tile leaves room for one CTA only (the conversion is
   // a dependent load - convert - store chain per thread, so its rate follows the number of warps in flight)
-  static constexpr int DQ_WARPS = MPAD <= 64 ? 4 : 8;
+  static constexpr int DQ_WARPS = (MPAD <= 64 && QM != Q_FP4) ? 4 : 8;      // fp4: the longest conversion chain per value
   static constexpr int DQ_THREADS = DQ_WARPS * 32;
   static constexpr int THREADS = 64 + DQ_THREADS;
 };
@@ -119,7 +122,7 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
     if (elect_one()) {
       const uint64_t pol_w = l2_policy_evict_first();
       const uint64_t pol_x = l2_policy_evict_last();
-      constexpr int KBYTES = QM == Q_INT4G ? 32 : 64;            // packed bytes per 64-wide k block
+      constexpr int KBYTES = (QM == Q_INT4G || QM == Q_FP4) ? 32 : 64;            // packed bytes per 64-wide k block
       // packed weights are independent of the kernel before this one: request the first ring before the dependency wait
       const int pre = kb_cnt < Cfg::STAGES ? kb_cnt : Cfg::STAGES;
       for (int i = 0; i < pre; ++i) {
@@ -163,6 +166,23 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
     const int tid = threadIdx.x - 64;                 // 0..DQ_THREADS-1
     constexpr int DQT = Cfg::DQ_THREADS;
     // ------------------------------ dequant stage ------------------------------
+    // fp4: the block scales of a k block come from global memory; they are requested one k block ahead, so that their
+    // latency is not part of the chain barrier -> convert -> store
+    constexpr int FP4_UNITS = QM == Q_FP4 ? 256 / DQT : 1;
+    uint32_t fp4_s[FP4_UNITS];
+    auto fp4_fetch = [&](int kb) {
+#pragma unroll
+      for (int it = 0; it < FP4_UNITS; ++it) {
+        const int u = tid + DQT * it, row = u >> 1, ch = u & 1;
+        const int n = n_tile * 128 + row;
+        fp4_s[it] = 0u;
+        if (n < p.N) {
+          const uint16_t* sp = reinterpret_cast<const uint16_t*>(qp.scale) + (size_t)n * qp.groups + (kb * 64 + ch * 32) / qp.group_k;
+          fp4_s[it] = qp.group_k == 16 ? *reinterpret_cast<const uint32_t*>(sp) : (uint32_t)sp[0] * 0x10001u;
+        }
+      }
+    };
+    if (QM == Q_FP4 && kb_cnt > 0) fp4_fetch(kb0);
     for (int i = 0; i < kb_cnt; ++i) {
       const int s = i % Cfg::STAGES, t = i % Cfg::DQ_SLOTS;
       const uint32_t ph = (uint32_t)(i / Cfg::STAGES) & 1u, tph = (uint32_t)(i / Cfg::DQ_SLOTS) & 1u;
@@ -197,6 +217,42 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
             *reinterpret_cast<uint4*>(out + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
         }
+      } else if (QM == Q_FP4) {
+#pragma unroll
+        for (int it = 0; it < 256 / DQT; ++it) {
+          const int u = tid + DQT * it, row = u >> 1, ch = u & 1;           // 32 k values = 16 packed bytes per unit
+          // scales of the unit's two 16-value halves (two bf16 values in one word)
+          const float s0 = __uint_as_float(fp4_s[it] << 16), s1 = __uint_as_float(fp4_s[it] & 0xFFFF0000u);
+          const uint4 w = *reinterpret_cast<const uint4*>(raw + row * 32 + ch * 16);
+          const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {            // one 32-bit word = 8 values = one 16-byte chunk of 16-bit operands
+            uint32_t h[4];
+            asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+                "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+                "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
+                : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(ws[j]));
+            const float sc = j < 2 ? s0 : s1;
+            uint32_t o[4];
+            if (!BF16 && qp.xor_mask != 0u) {
+              // fp16 activations: the product e2m1 x scale is exact in fp16 while the scale table stays inside fp16's range,
+              // which the host has checked -- one multiply per value pair.  (Both operands of one MMA must have the same 16-bit
+              // format: an fp16 weight operand beside bf16 activations raises an illegal-instruction error.)
+              const __half2 sc2 = __float2half2_rn(sc);
+#pragma unroll
+              for (int b = 0; b < 4; ++b) o[b] = h2_as_u32(__hmul2(*reinterpret_cast<const __half2*>(&h[b]), sc2));
+            } else {
+#pragma unroll
+              for (int b = 0; b < 4; ++b) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[b]));
+                o[b] = BF16 ? pack_bf16(f.x * sc, f.y * sc) : h2_as_u32(__floats2half2_rn(f.x * sc, f.y * sc));
+              }
+            }
+            const int chunk = ch * 4 + j;
+            *reinterpret_cast<uint4*>(out + row * 128 + ((chunk ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        if (i + 1 < kb_cnt) fp4_fetch(kb + 1);
       } else {
         float bscale = 1.f;
         if (QM == Q_FP8) bscale = qp.scale[(size_t)n_tile * qp.groups + (kb * 64) / 128];
@@ -262,6 +318,7 @@ __device__ __forceinline__ void gemm_quant_device(const CUtensorMap& tmW, const 
     const int n_local = q * 32 + lane;
     float row_scale = 1.f;
     if (QM == Q_INT8) { const int n = n_tile * 128 + n_local; row_scale = n < p.N ? qp.scale[n] : 0.f; }
+    if (QM == Q_FP4 && qp.zero != nullptr) row_scale = qp.zero[0];
     if (warp >= 6) {
       // extra dequant warps: no TMEM lane quarter of their own
     } else if (kb_cnt > 0) {
@@ -355,7 +412,8 @@ static cudaError_t launch_quant(const CUtensorMap& tmW, const CUtensorMap& tmX, 
 }
 
 // qmode: 1 = int8 (Wq uint8 [N,K], scale [N], zero [N]), 2 = int4g (Wq uint8 [N,K/2], scale = float2 (scale,min) [groups,N]),
-// 3 = fp8 block 128 (Wq e4m3 [N,K], scale [ceil(N/128), ceil(K/128)]).  X dtype: 0 = fp16, 1 = bf16.  M <= 256.
+// 3 = fp8 block 128 (Wq e4m3 [N,K], scale [ceil(N/128), ceil(K/128)]), 4 = fp4 (Wq uint8 [N,K/2], scale = bf16 [N, K/group_k],
+// group_k 16 or 32, zero = one per-tensor factor or null).  X dtype: 0 = fp16, 1 = bf16.  M <= 256.
 // int8 with group_k < 0: the bytes hold q - 128 (two's complement), zero still refers to q.
 extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, const float* zero, void* out, const void* bias,
                              const void* residual, int M, int N, int K, int ldx, int ld_out, int ld_res, int dtype, int qmode,
@@ -365,6 +423,7 @@ extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, 
   if (M > 256 || K % 64 != 0 || N % 8 != 0 || (dtype != 0 && dtype != 1)) return -1;
   if (qmode == Q_INT4G && (group_k <= 0 || group_k % 64 != 0 || K % group_k != 0)) return -1;
   if (qmode == Q_FP8 && K % 128 != 0) return -1;
+  if (qmode == Q_FP4 && group_k != 16 && group_k != 32) return -1;
   if ((flags & GEMM_SWIGLU) && (N % 128 != 0)) return -1;
   GemmParams p;
   p.out = out; p.bias = bias; p.residual = residual;
@@ -374,10 +433,11 @@ extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, 
   for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
   QuantParams qp;
   qp.scale = scale; qp.zero = zero;
-  qp.group_k = qmode == Q_INT4G ? group_k : 128;
-  qp.groups = qmode == Q_INT4G ? K / group_k : (K + 127) / 128;
+  qp.group_k = (qmode == Q_INT4G || qmode == Q_FP4) ? group_k : 128;
+  qp.groups = (qmode == Q_INT4G || qmode == Q_FP4) ? K / group_k : (K + 127) / 128;
   qp.xor_mask = (qmode == Q_INT8 && group_k < 0) ? 0x80808080u : 0u;      // int8 with group_k < 0: bytes hold q - 128
   const bool bf16 = dtype == 1;
+  if (qmode == Q_FP4 && (flags & GEMM_FP4_F16W) != 0 && !bf16) qp.xor_mask = 1u;
   const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
   static int sm_count = 0;
   if (sm_count == 0) {
@@ -392,16 +452,17 @@ extern "C" int fb_gemm_quant(const void* X, const void* Wq, const float* scale, 
     // a cluster rank must start on a group boundary only in the sense that a k block never straddles groups: group_k % 64 == 0
   }
   p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
-  const int kbytes = qmode == Q_INT4G ? K / 2 : K;
+  const bool nib = qmode == Q_INT4G || qmode == Q_FP4;
+  const int kbytes = nib ? K / 2 : K;
   CUtensorMap tmW, tmX;
-  if (!make_tmap_2d(&tmW, Wq, N, kbytes, kbytes, 128, qmode == Q_INT4G ? 32 : 64, 1, 0)) return -2;
+  if (!make_tmap_2d(&tmW, Wq, N, kbytes, kbytes, 128, nib ? 32 : 64, 1, 0)) return -2;
   if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
   const int n_tiles = (N + 127) / 128;
 #define FB_Q2(MP, QMV)                                                                                   \
   return (int)(bf16 ? launch_quant<MP, true, QMV>(tmW, tmX, p, qp, nsplit, n_tiles, stream)               \
                     : launch_quant<MP, false, QMV>(tmW, tmX, p, qp, nsplit, n_tiles, stream));
 #define FB_Q(MP)                                                                                          \
-  { if (qmode == Q_INT8) { FB_Q2(MP, Q_INT8) } else if (qmode == Q_INT4G) { FB_Q2(MP, Q_INT4G) } else if (qmode == Q_FP8) { FB_Q2(MP, Q_FP8) } else return -1; }
+  { if (qmode == Q_INT8) { FB_Q2(MP, Q_INT8) } else if (qmode == Q_INT4G) { FB_Q2(MP, Q_INT4G) } else if (qmode == Q_FP8) { FB_Q2(MP, Q_FP8) } else if (qmode == Q_FP4) { FB_Q2(MP, Q_FP4) } else return -1; }
   switch (mpad) {
     case 16: FB_Q(16)
     case 32: FB_Q(32)
@@ -445,6 +506,7 @@ extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const f
   if (K % 64 != 0 || N % 128 != 0 || (dtype != 0 && dtype != 1)) return -1;
   if (qmode == Q_INT4G && (group_k <= 0 || group_k % 64 != 0 || K % group_k != 0)) return -1;
   if (qmode == Q_FP8 && K % 128 != 0) return -1;
+  if (qmode == Q_FP4 && ((group_k != 16 && group_k != 32) || ((long long)N * (K / group_k)) % 2 != 0)) return -1;
   const bool bf16 = dtype == 1;
   const int hint = max_rows_per_expert >> 16;       // high 16 bits: chunk size hint, low 16 bits: most rows an expert can get
   max_rows_per_expert &= 0xFFFF;
@@ -464,16 +526,20 @@ extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const f
   p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
   QuantParams qp;
   qp.scale = scale; qp.zero = zero;
-  qp.group_k = qmode == Q_INT4G ? group_k : 128;
-  qp.groups = qmode == Q_INT4G ? K / group_k : (K + 127) / 128;
+  qp.group_k = (qmode == Q_INT4G || qmode == Q_FP4) ? group_k : 128;
+  qp.groups = (qmode == Q_INT4G || qmode == Q_FP4) ? K / group_k : (K + 127) / 128;
   qp.xor_mask = (qmode == Q_INT8 && group_k < 0) ? 0x80808080u : 0u;      // int8 with group_k < 0: bytes hold q - 128
+  if (qmode == Q_FP4 && (flags & GEMM_FP4_F16W) != 0 && !bf16) qp.xor_mask = 1u;
   QuantGroupInfo gi;
   gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
-  gi.scale_stride_e = qmode == Q_INT8 ? N : qmode == Q_INT4G ? (long long)qp.groups * N * 2 : (long long)(N / 128) * qp.groups;
-  gi.zero_stride_e = N;
-  const int kbytes = qmode == Q_INT4G ? K / 2 : K;
+  // strides in floats; the fp4 scale table holds bf16 values (two per float), its per-tensor factor is one float per expert
+  gi.scale_stride_e = qmode == Q_INT8 ? N : qmode == Q_INT4G ? (long long)qp.groups * N * 2
+                    : qmode == Q_FP4 ? (long long)qp.groups * N / 2 : (long long)(N / 128) * qp.groups;
+  gi.zero_stride_e = qmode == Q_FP4 ? 1 : N;
+  const bool nib = qmode == Q_INT4G || qmode == Q_FP4;
+  const int kbytes = nib ? K / 2 : K;
   CUtensorMap tmW, tmX;
-  if (!make_tmap_2d(&tmW, Wq, (uint64_t)E_local * N, kbytes, kbytes, 128, qmode == Q_INT4G ? 32 : 64, 1, 0)) return -2;
+  if (!make_tmap_2d(&tmW, Wq, (uint64_t)E_local * N, kbytes, kbytes, 128, nib ? 32 : 64, 1, 0)) return -2;
   if (!make_tmap_2d(&tmX, Xs, rows_cap, K, K, mpad, 64, 2, 3)) return -2;
   int nz = E_local * chunks;
   gi.n_local = E_local; gi.compact = 0;
@@ -486,7 +552,7 @@ extern "C" int fb_moe_grouped_gemm_quant(const void* Xs, const void* Wq, const f
   return (int)(bf16 ? launch_grouped_quant<MP, true, QMV>(tmW, tmX, p, qp, gi, nsplit, n_tiles, nz, stream)       \
                     : launch_grouped_quant<MP, false, QMV>(tmW, tmX, p, qp, gi, nsplit, n_tiles, nz, stream));
 #define FB_GQ(MP)                                                                                                 \
-  { if (qmode == Q_INT8) { FB_GQ2(MP, Q_INT8) } else if (qmode == Q_INT4G) { FB_GQ2(MP, Q_INT4G) } else if (qmode == Q_FP8) { FB_GQ2(MP, Q_FP8) } else return -1; }
+  { if (qmode == Q_INT8) { FB_GQ2(MP, Q_INT8) } else if (qmode == Q_INT4G) { FB_GQ2(MP, Q_INT4G) } else if (qmode == Q_FP8) { FB_GQ2(MP, Q_FP8) } else if (qmode == Q_FP4) { FB_GQ2(MP, Q_FP4) } else return -1; }
   switch (mpad) {
     case 16: FB_GQ(16)
     case 32: FB_GQ(32)

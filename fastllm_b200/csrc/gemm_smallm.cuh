@@ -44,6 +44,7 @@ enum GemmFlags : int {
   GEMM_RESIDUAL = 2,   // += residual[m, n]
   GEMM_SWIGLU = 4,     // out[m, i] = silu(gate) * up   (N_out = N / 2)
   GEMM_OUT_F32 = 8,    // write fp32 instead of the 16-bit input dtype
+  GEMM_FP4_F16W = 256, // fp4 weights, fp16 activations: the scale table lies within fp16's range (host-checked): half2 de-quantiser
 };
 
 struct GemmParams {

@@ -66,7 +66,7 @@ def _prepare_a8(st: StackedExperts, experts) -> None:
 def _stack_scales(ws):
     from .quant_gemm import _kernel_tensors
 
-    sc, ze = zip(*[_kernel_tensors(w) for w in ws])
+    sc, ze = zip(*[_kernel_tensors(w)[:2] for w in ws])
     scale = torch.stack([t.contiguous() for t in sc]).contiguous()
     zero = torch.stack([t.contiguous() for t in ze]).contiguous() if ze[0] is not None else None
     return scale, zero
@@ -90,9 +90,14 @@ def stack_experts(experts) -> StackedExperts | None:
         return None
     if kind == "fp8" and (two_i // 2) % 128 != 0:
         return None
+    if kind == "fp4" and gu[0].group not in (16, 32):
+        return None
     gs, gz = _stack_scales(gu)
     ds, dz = _stack_scales(dn)
-    return StackedExperts(kind, g, d, len(gu), two_i // 2, hidden, gu[0].group, gs, gz, ds, dz)
+    st = StackedExperts(kind, g, d, len(gu), two_i // 2, hidden, gu[0].group, gs, gz, ds, dz)
+    if kind == "fp4":
+        st.fp4_f16w = all(QG._kernel_tensors(w)[2] for w in gu + dn)
+    return st
 
 
 def prepare_model(m) -> None:
@@ -194,13 +199,14 @@ def forward(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, experts, add:
                                   _ptr(None), T * topk, H, st.inter, H, 0, dt, 0, wk, 1, _ptr(counts), _ptr(offsets), E, rows_cap, max_rows, s),
                    "fb_gemm_i8(down)")
     else:
-        qm = {"int8": 1, "int4g": 2, "fp8": 3}[st.kind]
+        qm = {"int8": 1, "int4g": 2, "fp8": 3, "fp4": 4}[st.kind]
         grp = -1 if st.signed else (st.group or 0)           # -1: int8 bytes hold q - 128
+        f16w = QG.GEMM_FP4_F16W if (st.kind == "fp4" and getattr(st, "fp4_f16w", False)) else 0
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(xs), _ptr(st.gate_up), _ptr(st.gu_scale), _ptr(st.gu_zero), _ptr(act), _ptr(counts),
                                                  _ptr(offsets), rows_cap, E, 2 * st.inter, H, st.inter, max_rows, dt, qm, grp,
-                                                 GEMM_SWIGLU, T * topk, s), "fb_moe_grouped_gemm_quant(gate_up)")
+                                                 GEMM_SWIGLU | f16w, T * topk, s), "fb_moe_grouped_gemm_quant(gate_up)")
         _lib.check(lib.fb_moe_grouped_gemm_quant(_ptr(act), _ptr(st.down), _ptr(st.dn_scale), _ptr(st.dn_zero), _ptr(ys), _ptr(counts),
-                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, max_rows, dt, qm, grp, 0, T * topk, s),
+                                                 _ptr(offsets), rows_cap, E, H, st.inter, H, max_rows, dt, qm, grp, f16w, T * topk, s),
                    "fb_moe_grouped_gemm_quant(down)")
     if not combine:
         return ys, pos, wts

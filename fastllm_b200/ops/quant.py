@@ -76,6 +76,53 @@ def dequantize_fp8_block(q, scale, dtype, block: int = 128):
     return (q.float() * s).to(dtype)
 
 
+_E2M1 = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+
+
+def _fp4_codes(v: torch.Tensor) -> torch.Tensor:
+    """Round fp32 values (already divided by their block scale) to e2m1 codes 0..15 (sign in bit 3), nearest value, ties to
+    the even code."""
+    grid = torch.tensor(_E2M1, dtype=torch.float32, device=v.device)
+    a = v.abs().clamp(max=6.0)
+    d = (a[..., None] - grid).abs()
+    code = d.argmin(dim=-1)
+    # ties: argmin takes the lower code; move to the upper one when that one is even
+    up = (code + 1).clamp(max=7)
+    tie = (d.gather(-1, up[..., None])[..., 0] == d.gather(-1, code[..., None])[..., 0]) & (up != code) & (up % 2 == 0)
+    code = torch.where(tie, up, code)
+    return (code | ((v < 0).long() << 3)).to(torch.uint8)
+
+
+def quantize_fp4(w: torch.Tensor, block: int = 16):
+    """Dense ``[N, K]`` -> (packed uint8 ``[N, K/2]``, low nibble = even element; bf16 block scales ``[N, K/block]``; fp32
+    per-tensor factor ``[1]`` or None).  ``block`` 16: NVFP4 -- e4m3-valued block scales under one per-tensor factor
+    (amax / (448 * 6)); ``block`` 32: MXFP4 -- power-of-two block scales (the reference's NVFP4_BLOCK_16 / MXFP4 types,
+    include/fastllm.h:308-339)."""
+    N, K = w.shape
+    wf = w.float().reshape(N, K // block, block)
+    amax = wf.abs().amax(-1)
+    if block == 16:
+        g = (wf.abs().max() / (448.0 * 6.0)).clamp(min=1e-30)
+        sc = (amax / 6.0 / g).to(torch.float8_e4m3fn).float().clamp(min=2.0 ** -9)
+        eff = sc * g
+        gl = g.reshape(1).float()
+    else:
+        sc = torch.exp2(torch.ceil(torch.log2((amax / 6.0).clamp(min=2.0 ** -126))))
+        eff, gl = sc, None
+    codes = _fp4_codes(wf / eff[..., None]).reshape(N, K)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+    return packed, sc.to(torch.bfloat16).contiguous(), gl
+
+
+def dequantize_fp4(packed, scale, glob, dtype, block: int = 16):
+    lut = torch.tensor(_E2M1 + tuple(-x for x in _E2M1), dtype=torch.float32, device=packed.device)
+    vals = torch.stack([lut[(packed & 0x0F).long()], lut[(packed >> 4).long()]], dim=-1).reshape(packed.shape[0], -1)
+    out = vals.reshape(packed.shape[0], -1, block) * scale.float()[..., None]
+    if glob is not None:
+        out = out * glob.float().reshape(-1)[0]
+    return out.reshape(packed.shape[0], -1).to(dtype)
+
+
 def fake_quant_act_fp8(x: torch.Tensor) -> torch.Tensor:
     """Round activations to e4m3 per (token, 128-wide k block) and return them in their own dtype.  FP8 layers use the
     tensor core's e4m3 x e4m3 path for decode-sized batches; larger batches go through 16-bit GEMMs and apply this rounding
@@ -122,6 +169,10 @@ def normalize_wdtype(name: str | None) -> tuple[str, int]:
         return "int4g", -1              # one (scale, minimum) pair per output channel: the group is the whole row
     if n in ("fp8", "fp8_e4m3", "float8", "fp8_block128"):
         return "fp8", 128
+    if n in ("nvfp4", "fp4", "fp4_e2m1", "nvfp4_block16"):
+        return "fp4", 16
+    if n in ("mxfp4", "nvfp4_block32_e8m0", "fp4_block32"):
+        return "fp4", 32
     raise ValueError(f"unsupported weight dtype '{name}'")
 
 
@@ -135,7 +186,7 @@ class LinearWeight:
     def __init__(self, kind, w, scale=None, zero=None, bias=None, group=0, dtype=torch.bfloat16, interleaved=False):
         self.kind, self.w, self.scale, self.zero, self.bias, self.group = kind, w, scale, zero, bias, group
         self.n = w.shape[0]
-        self.k = w.shape[1] * (2 if kind == "int4g" else 1)
+        self.k = w.shape[1] * (2 if kind in ("int4g", "fp4") else 1)
         self.dtype = dtype
         self.interleaved = interleaved      # gate/up rows interleaved per 128-row tile for the SwiGLU epilogue
         self._dq = None
@@ -164,6 +215,11 @@ class LinearWeight:
                 return LinearWeight("dense", w.contiguous(), bias=bias, dtype=w.dtype, interleaved=interleaved)
             q, s, mn = quantize_int4g(w, group)
             return LinearWeight("int4g", q, s, mn, bias, group, act_dtype, interleaved)
+        if kind == "fp4":
+            if w.shape[1] % 64 != 0:
+                return LinearWeight("dense", w.contiguous(), bias=bias, dtype=w.dtype, interleaved=interleaved)
+            q, s, gl = quantize_fp4(w, group)
+            return LinearWeight("fp4", q, s, gl, bias, group, act_dtype, interleaved)
         q, s = quantize_fp8_block(w, 128)
         return LinearWeight("fp8", q, s, None, bias, 128, act_dtype, interleaved)
 
@@ -177,6 +233,8 @@ class LinearWeight:
             return dequantize_int8(self.w, self.scale, self.zero, dtype)
         if self.kind == "int4g":
             return dequantize_int4g(self.w, self.scale, self.zero, dtype, self.group)
+        if self.kind == "fp4":
+            return dequantize_fp4(self.w, self.scale, self.zero, dtype, self.group)
         return dequantize_fp8_block(self.w, self.scale, dtype, self.group)
 
     def nbytes(self) -> int:

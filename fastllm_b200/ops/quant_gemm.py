@@ -29,10 +29,13 @@ _lib.register_sigs({
     "fb_gemv_i4": [P, I, P, P, I, P, P, P, I, I, I, I, I, I, P, P, I, P],
 }, ["gemm_fp8", "gemm_i8"])
 
-_QMODE = {"int8": 1, "int4g": 2, "fp8": 3}
+_QMODE = {"int8": 1, "int4g": 2, "fp8": 3, "fp4": 4}
 # FP8 weights run as W8A8 (activations quantised per token and 128-wide k block, e4m3 x e4m3 on the tensor core) for decode-sized
 # batches; FB_FP8_W8A16=1 keeps 16-bit activations (weights de-quantised in shared memory), which is also the path for M > 128.
 FP8_NATIVE = __import__("os").environ.get("FB_FP8_W8A16", "0") != "1"
+# fp4 weights with fp16 activations: half2 de-quantiser (one multiply per value pair) while the scale table fits fp16's range
+FP4_F16W = __import__("os").environ.get("FB_FP4_F16W", "1") != "0"
+GEMM_FP4_F16W = 256
 
 
 # int8 / int4-group(128) weights run with int8 activations on the integer tensor-core path (FB_INT_A16=1 keeps 16-bit activations)
@@ -168,6 +171,13 @@ def _kernel_tensors(lw):
         elif lw.kind == "int4g":
             sm = torch.stack([lw.scale.float(), lw.zero.float()], dim=-1)          # [N, groups, 2]
             lw._dq = (sm.permute(1, 0, 2).contiguous(), None)                      # [groups, N, 2]
+        elif lw.kind == "fp4":
+            # bf16 block scales [N, K / group] read as they are; the per-tensor factor (NVFP4) rides in the zero slot; the third
+            # entry says whether every scale x 6 stays a normal fp16 number (fp16 activations then take the half2 de-quantiser)
+            sf = lw.scale.float()
+            nz = sf[sf > 0]
+            ok = bool(FP4_F16W and (nz.numel() == 0 or (float(nz.max()) * 6.0 < 60000.0 and float(nz.min()) * 0.5 >= 2.0 ** -14)))
+            lw._dq = (lw.scale.to(torch.bfloat16).contiguous(), lw.zero.float().contiguous() if lw.zero is not None else None, ok)
         else:
             lw._dq = (lw.scale.float().contiguous(), None)
     return lw._dq
@@ -189,6 +199,8 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
         return None
     if lw.kind == "fp8" and K % 128 != 0:
         return None
+    if lw.kind == "fp4" and (lw.group not in (16, 32) or (N * (K // lw.group)) % 2 != 0):
+        return None
     if swiglu and (not lw.interleaved or N % 128 != 0):
         return None
     a8 = uses_int_a8(lw) and M <= INT_A8_MAX_M[lw.kind] and x2.stride(0) % 4 == 0
@@ -198,6 +210,8 @@ def linear_quant(x, lw, residual=None, swiglu=False, out_f32=False):
     res2 = residual.reshape(-1, residual.shape[-1]) if residual is not None else None
     flags = (GEMM_BIAS if lw.bias is not None else 0) | (GEMM_RESIDUAL if residual is not None else 0) | \
             (GEMM_SWIGLU if swiglu else 0) | (GEMM_OUT_F32 if out_f32 else 0)
+    if lw.kind == "fp4" and _kernel_tensors(lw)[2]:
+        flags |= GEMM_FP4_F16W
     bias = lw.bias
     if bias is not None and bias.dtype != x.dtype:
         bias = bias.to(x.dtype)

@@ -219,7 +219,7 @@ def test_qkv_post(mode, rot, qknorm):
     _close(vp2.cpu(), vp, 0, 0, "v pool")
 
 
-@pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8"])
+@pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8", "nvfp4", "mxfp4"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("M,N,K", [(1, 256, 256), (13, 384, 1024), (64, 4096, 4096), (200, 1024, 2048), (300, 512, 512)])
 def test_gemm_quant(kind, dtype, M, N, K, fp8_w8a16):
@@ -235,6 +235,28 @@ def test_gemm_quant(kind, dtype, M, N, K, fp8_w8a16):
     _close(y, ref, 4e-2, 3e-2, f"quant gemm {kind} {M}x{N}x{K}")
 
 
+@pytest.mark.parametrize("kind", ["nvfp4", "mxfp4"])
+def test_gemm_fp4_operand_forms(kind, monkeypatch):
+    """fp4 weights with fp16 activations: the half2 de-quantiser and the fp32 one give the same result as the fp32 evaluation
+    of the de-quantised weights."""
+    from fastllm_b200.ops import quant, quant_gemm as QG
+
+    torch.manual_seed(18)
+    M, N, K, dt = 40, 512, 1024, torch.float16
+    w = (torch.randn(N, K, device=DEV) * 0.05).to(dt)
+    x = (torch.randn(M, K, device=DEV) * 0.5).to(dt)
+    outs = []
+    for fast in (True, False):
+        monkeypatch.setattr(QG, "FP4_F16W", fast)
+        lw = quant.LinearWeight.from_dense(w, kind, act_dtype=dt)
+        ref = B.linear_ref(x, lw.dequant(torch.float32))
+        y = lw(x)
+        assert QG._kernel_tensors(lw)[2] == fast
+        _close(y, ref, 3e-2, 2e-2, f"fp4 {kind} fast={fast}", fro=6e-3)
+        outs.append(y.float())
+    assert (outs[0] - outs[1]).norm() / outs[1].norm() < 5e-3
+
+
 def test_gemm_quant_epilogues(fp8_w8a16):
     from fastllm_b200.ops import quant
 
@@ -244,7 +266,7 @@ def test_gemm_quant_epilogues(fp8_w8a16):
     x = (torch.randn(M, K, device=DEV) * 0.5).to(dt)
     bias = torch.randn(N, device=DEV).to(dt)
     res = torch.randn(M, N // 2, device=DEV).to(dt)
-    for kind in ("int8", "int4g128", "fp8"):
+    for kind in ("int8", "int4g128", "fp8", "nvfp4", "mxfp4"):
         lw = quant.LinearWeight.from_dense(w, kind, bias=bias, interleaved=True, act_dtype=dt)
         y = lw(x, residual=res, swiglu=True)
         ref = B.linear_ref(x, lw.dequant(torch.float32), bias, res, swiglu=True)
@@ -277,7 +299,7 @@ def test_moe_grouped(T, E, first, n_local, topk):
     assert torch.equal(idx.sort(1)[0], idx_ref.sort(1)[0])
 
 
-@pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8"])
+@pytest.mark.parametrize("kind", ["int8", "int4g128", "fp8", "nvfp4", "mxfp4"])
 def test_moe_grouped_quant(kind, fp8_w8a16):
     from fastllm_b200.ops import moe as MOE, moe_grouped, quant
 

@@ -253,3 +253,36 @@ def test_activation_mode_routing():
     assert QG.act_quant_mode(i8, 1) == 0          # a run-time adapter needs the 16-bit activations
     odd = LinearWeight.from_dense(torch.randn(64, 192) * 0.05, "int8")
     assert QG.act_quant_mode(odd, 1) == 0         # K not a multiple of the 128-wide quantisation block
+
+
+def test_fp4_quantiser_roundtrip():
+    """NVFP4 (block 16, e4m3-valued scales under a per-tensor factor) and MXFP4 (block 32, power-of-two scales): the packed
+    form de-quantises to the nearest e2m1 grid point of every block, and agrees with the checkpoint de-quantisers."""
+    import torch
+
+    from fastllm_b200.loader import hf
+    from fastllm_b200.ops import quant
+
+    torch.manual_seed(0)
+    w = torch.randn(32, 128) * 0.05
+    for name, block in (("nvfp4", 16), ("mxfp4", 32)):
+        lw = quant.LinearWeight.from_dense(w, name)
+        assert lw.kind == "fp4" and lw.group == block and lw.w.shape == (32, 64) and lw.scale.shape == (32, 128 // block)
+        dq = lw.dequant(torch.float32)
+        rel = (dq - w).norm() / w.norm()
+        assert rel < 0.12, (name, float(rel))
+        # every de-quantised value is scale x an e2m1 value
+        eff = lw.scale.float() * (lw.zero.float() if lw.zero is not None else 1.0)
+        ratio = (dq.reshape(32, -1, block) / eff[..., None]).abs()
+        grid = torch.tensor(quant._E2M1)
+        assert ((ratio[..., None] - grid).abs().amin(-1) < 1e-4).all()
+        # the checkpoint-format de-quantiser reads the same bytes the same way
+        if block == 16:
+            want = hf.dequant_nvfp4(lw.w, lw.scale.float().to(torch.float8_e4m3fn), lw.zero, torch.float32)
+        else:
+            e8 = (torch.log2(lw.scale.float()) + 127).to(torch.uint8)
+            want = hf.dequant_mxfp4(lw.w.reshape(32, 128 // 32, 16), e8, torch.float32)
+        assert torch.allclose(dq, want, rtol=1e-6, atol=1e-8)
+    # values halfway between two grid points go to the even code
+    codes = quant._fp4_codes(torch.tensor([0.25, 0.75, 1.25, 2.5, 5.0, -2.5]))
+    assert codes.tolist() == [0, 2, 2, 4, 6, 12]
