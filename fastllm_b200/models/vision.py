@@ -1,0 +1,224 @@
+"""Vision tower of the Qwen3-VL / Qwen3.5 family and the image pre-processing that feeds it.
+
+An image becomes a grid of 16 x 16 patches (each repeated over two "frames"); the tower embeds the patches (a strided 3-D
+convolution, evaluated as one GEMM over the flattened patches), adds a learned position table interpolated to the grid,
+runs ``depth`` pre-norm blocks of full (non-causal) attention with a 2-D rotary embedding over (row, column), and merges every
+2 x 2 block of patches into one token of the language model's width.  The language model sees those tokens in place of its
+image placeholder tokens, with (time, row, column) rotary positions (``mrope_positions`` / ``mrope_tables`` below).
+
+Reference: the vision path of src/models/qwen3_5.cpp (Qwen3_5Model::VisionForward, the ``visual.*`` weights) and the image
+pre-processing of tools/fastllm_pytools (smart resize to multiples of patch x merge, mean / std 0.5).
+"""
+from __future__ import annotations
+
+import base64
+import io
+import math
+
+import torch
+import torch.nn.functional as F
+
+
+class VisionConfig:
+    def __init__(self, d: dict):
+        g = d.get
+        self.depth = int(g("depth", 27))
+        self.hidden = int(g("hidden_size", 1152))
+        self.inter = int(g("intermediate_size", 4304))
+        self.heads = int(g("num_heads", 16))
+        self.in_ch = int(g("in_channels", 3))
+        self.patch = int(g("patch_size", 16))
+        self.merge = int(g("spatial_merge_size", 2))
+        self.t_patch = int(g("temporal_patch_size", 2))
+        self.out_hidden = int(g("out_hidden_size", 3584))
+        self.num_pos = int(g("num_position_embeddings", 2304))
+        self.act = g("hidden_act", "gelu_pytorch_tanh")
+        self.deepstack = list(g("deepstack_visual_indexes", []) or [])
+
+
+class VisionTower:
+    """Weights (``visual.*``) and forward pass; runs in ``dtype`` on ``device`` with PyTorch ops (the tower runs once per
+    image, not per generated token)."""
+
+    def __init__(self, cfg: VisionConfig, weights: dict, device, dtype):
+        self.cfg, self.device, self.dtype = cfg, torch.device(device), dtype
+        self.w = {k: v.to(self.device, dtype) for k, v in weights.items()}
+        if self.cfg.deepstack:
+            raise NotImplementedError("deep-stack visual features (Qwen3-VL) are not merged into the decoder layers")
+
+    def _lin(self, x, name):
+        return F.linear(x, self.w[name + ".weight"], self.w.get(name + ".bias"))
+
+    def _pos_embed(self, grids):
+        """Learned position table (a square grid) interpolated bilinearly to every image's patch grid, in merge-block order."""
+        c = self.cfg
+        side = int(c.num_pos ** 0.5)
+        table = self.w["pos_embed.weight"].float()
+        out = []
+        for t, h, w in grids:
+            hi, wi = torch.linspace(0, side - 1, h), torch.linspace(0, side - 1, w)
+            h0, w0 = hi.int(), wi.int()
+            h1, w1 = (h0 + 1).clamp(max=side - 1), (w0 + 1).clamp(max=side - 1)
+            dh, dw = (hi - h0)[:, None], (wi - w0)[None, :]
+            idx = lambda a, b: (a[:, None] * side + b[None, :]).reshape(-1).long().to(table.device)
+            wt = lambda m: m.reshape(-1, 1).to(table.device)
+            pe = (table[idx(h0, w0)] * wt((1 - dh) * (1 - dw)) + table[idx(h0, w1)] * wt((1 - dh) * dw)
+                  + table[idx(h1, w0)] * wt(dh * (1 - dw)) + table[idx(h1, w1)] * wt(dh * dw))
+            pe = pe.repeat(t, 1).view(t, h // c.merge, c.merge, w // c.merge, c.merge, -1).permute(0, 1, 3, 2, 4, 5).reshape(t * h * w, -1)
+            out.append(pe)
+        return torch.cat(out).to(self.dtype)
+
+    def _rotary(self, grids):
+        c = self.cfg
+        hd = c.hidden // c.heads
+        dim = hd // 2
+        inv = 1.0 / (10000.0 ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+        rows = []
+        for t, h, w in grids:
+            mh, mw, m = h // c.merge, w // c.merge, c.merge
+            r = (torch.arange(mh)[:, None, None, None] * m + torch.arange(m)[None, None, :, None]).expand(mh, mw, m, m).reshape(-1)
+            cc = (torch.arange(mw)[None, :, None, None] * m + torch.arange(m)[None, None, None, :]).expand(mh, mw, m, m).reshape(-1)
+            fr = torch.cat([r[:, None].float() * inv[None, :], cc[:, None].float() * inv[None, :]], dim=-1)     # [h*w, hd/2]
+            rows.append(fr.repeat(t, 1))
+        fr = torch.cat(rows).to(self.device)
+        emb = torch.cat([fr, fr], dim=-1)
+        return emb.cos(), emb.sin()
+
+    @torch.no_grad()
+    def forward(self, patches: torch.Tensor, grids) -> torch.Tensor:
+        """``patches`` ``[sum(t*h*w), in_ch * t_patch * patch * patch]`` in merge-block order, ``grids`` list of (t, h, w) in
+        patches -> ``[sum(t*h*w) / merge^2, out_hidden]``."""
+        c = self.cfg
+        x = patches.to(self.device, self.dtype)
+        h = F.linear(x, self.w["patch_embed.proj.weight"].reshape(c.hidden, -1), self.w.get("patch_embed.proj.bias"))
+        h = h + self._pos_embed(grids)
+        cos, sin = self._rotary(grids)
+        S = h.shape[0]
+        hd = c.hidden // c.heads
+        bounds = [0]
+        for t, gh, gw in grids:
+            for _ in range(t):
+                bounds.append(bounds[-1] + gh * gw)           # attention stays inside one frame
+        for i in range(c.depth):
+            p = f"blocks.{i}."
+            y = F.layer_norm(h, (c.hidden,), self.w[p + "norm1.weight"], self.w[p + "norm1.bias"], 1e-6)
+            q, k, v = self._lin(y, p + "attn.qkv").reshape(S, 3, c.heads, hd).permute(1, 0, 2, 3).unbind(0)
+            rot = lambda t_: torch.cat([-t_[..., hd // 2:], t_[..., :hd // 2]], dim=-1)
+            qf, kf = q.float(), k.float()
+            q = (qf * cos[:, None, :] + rot(qf) * sin[:, None, :]).to(self.dtype)
+            k = (kf * cos[:, None, :] + rot(kf) * sin[:, None, :]).to(self.dtype)
+            outs = []
+            for a, b in zip(bounds[:-1], bounds[1:]):
+                o = F.scaled_dot_product_attention(q[a:b].transpose(0, 1)[None], k[a:b].transpose(0, 1)[None], v[a:b].transpose(0, 1)[None])
+                outs.append(o[0].transpose(0, 1).reshape(b - a, c.hidden))
+            h = h + self._lin(torch.cat(outs), p + "attn.proj")
+            y = F.layer_norm(h, (c.hidden,), self.w[p + "norm2.weight"], self.w[p + "norm2.bias"], 1e-6)
+            y = self._lin(y, p + "mlp.linear_fc1")
+            y = F.gelu(y, approximate="tanh") if "tanh" in c.act else F.gelu(y)
+            h = h + self._lin(y, p + "mlp.linear_fc2")
+        y = F.layer_norm(h, (c.hidden,), self.w["merger.norm.weight"], self.w["merger.norm.bias"], 1e-6).view(-1, c.hidden * c.merge ** 2)
+        return self._lin(F.gelu(self._lin(y, "merger.linear_fc1")), "merger.linear_fc2")
+
+
+# ---------------------------------------------------------------------------------------------------
+# image -> patches
+# ---------------------------------------------------------------------------------------------------
+def smart_resize(height: int, width: int, factor: int, min_pixels: int = 56 * 56, max_pixels: int = 14 * 14 * 4 * 1280):
+    """Target size: both sides multiples of ``factor``, the area within [min_pixels, max_pixels], the aspect ratio kept."""
+    h = max(factor, round(height / factor) * factor)
+    w = max(factor, round(width / factor) * factor)
+    if h * w > max_pixels:
+        beta = math.sqrt(height * width / max_pixels)
+        h = max(factor, math.floor(height / beta / factor) * factor)
+        w = max(factor, math.floor(width / beta / factor) * factor)
+    elif h * w < min_pixels:
+        beta = math.sqrt(min_pixels / (height * width))
+        h = math.ceil(height * beta / factor) * factor
+        w = math.ceil(width * beta / factor) * factor
+    return h, w
+
+
+def load_image(src):
+    """PIL image from a PIL image, a path, raw bytes or a ``data:image/...;base64,`` URL."""
+    from PIL import Image
+
+    if hasattr(src, "convert"):
+        return src.convert("RGB")
+    if isinstance(src, (bytes, bytearray)):
+        return Image.open(io.BytesIO(src)).convert("RGB")
+    s = str(src)
+    if s.startswith("data:"):
+        return Image.open(io.BytesIO(base64.b64decode(s.split(",", 1)[1]))).convert("RGB")
+    if s.startswith("file://"):
+        s = s[7:]
+    if s.startswith("http://") or s.startswith("https://"):
+        raise ValueError("remote image URLs are not fetched: pass a file path or a data: URL")
+    return Image.open(s).convert("RGB")
+
+
+def image_to_patches(img, cfg: VisionConfig, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5), min_pixels=None, max_pixels=None):
+    """One image -> (``[h*w, in_ch * t_patch * patch * patch]`` fp32 patches in merge-block order, grid ``(1, h, w)``)."""
+    from PIL import Image
+
+    img = load_image(img)
+    f = cfg.patch * cfg.merge
+    kw = {}
+    if min_pixels:
+        kw["min_pixels"] = min_pixels
+    if max_pixels:
+        kw["max_pixels"] = max_pixels
+    H, W = smart_resize(img.height, img.width, f, **kw)
+    img = img.resize((W, H), Image.BICUBIC)
+    x = torch.frombuffer(bytearray(img.tobytes()), dtype=torch.uint8).view(H, W, 3).permute(2, 0, 1).float() / 255.0
+    x = (x - torch.tensor(mean)[:, None, None]) / torch.tensor(std)[:, None, None]
+    return pixels_to_patches(x, cfg)
+
+
+def pixels_to_patches(x: torch.Tensor, cfg: VisionConfig):
+    """``x`` ``[3, H, W]`` normalised pixels (H, W multiples of patch x merge) -> (patches, grid)."""
+    C, H, W = x.shape
+    p, m, tp = cfg.patch, cfg.merge, cfg.t_patch
+    gh, gw = H // p, W // p
+    x = x[None].repeat(tp, 1, 1, 1)                                          # the still image fills every temporal slot
+    x = x.view(tp, C, gh // m, m, p, gw // m, m, p).permute(2, 5, 3, 6, 1, 0, 4, 7)     # block row, block col, in-block row / col, C, T, p, p
+    return x.reshape(gh * gw, C * tp * p * p).contiguous(), (1, gh, gw)
+
+
+# ---------------------------------------------------------------------------------------------------
+# (time, row, column) rotary positions of a prompt with images
+# ---------------------------------------------------------------------------------------------------
+def mrope_positions(ids, image_token_id: int, grids, merge: int):
+    """3-D positions ``[3, T]`` for a prompt whose image placeholder runs (one per image, ``t*h*w / merge^2`` tokens each) are
+    laid out on their (time, row, column) grids; text tokens advance all three axes together.  Also returns the offset between
+    the next token's position and the sequence length (reference semantics: Qwen2-VL ``get_rope_index``)."""
+    T = len(ids)
+    pos = torch.zeros((3, T), dtype=torch.long)
+    nxt, i, gi = 0, 0, 0
+    while i < T:
+        if ids[i] == image_token_id and gi < len(grids):
+            t, h, w = grids[gi]
+            gh, gw = h // merge, w // merge
+            n = t * gh * gw
+            pos[0, i:i + n] = nxt
+            pos[1, i:i + n] = nxt + torch.arange(gh).repeat_interleave(gw).repeat(t)
+            pos[2, i:i + n] = nxt + torch.arange(gw).repeat(gh * t)
+            nxt += max(gh, gw)
+            i += n
+            gi += 1
+        else:
+            pos[:, i] = nxt
+            nxt += 1
+            i += 1
+    return pos, nxt - T
+
+
+def mrope_tables(pos3: torch.Tensor, rot_dim: int, theta: float, sections, device="cpu"):
+    """Per-token (cos, sin) rows ``[T, rot_dim / 2]``: frequency j takes its angle from the time axis, except the interleaved
+    slots ``1, 4, 7, ... < 3 * sections[1]`` (row axis) and ``2, 5, 8, ... < 3 * sections[2]`` (column axis)."""
+    half = rot_dim // 2
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, dtype=torch.float64) / rot_dim))
+    axis = torch.zeros(half, dtype=torch.long)
+    axis[1:3 * sections[1]:3] = 1
+    axis[2:3 * sections[2]:3] = 2
+    ang = pos3.double()[axis, :].t() * inv[None, :]                          # [T, half]
+    return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
