@@ -25,6 +25,40 @@ from .request import GenerationConfig, Request, RequestState
 from .runner import EngineConfig, ModelRunner
 
 
+class MultimodalContext:
+    """What a prompt with images carries beside its token ids: the image tokens' embeddings (rows of the language model's
+    width, in prompt order), the prompt positions they replace, the (time, row, column) rotary positions of every prompt
+    token and the offset between a later token's rotary position and its index in the sequence."""
+
+    def __init__(self, embeds, embed_positions, pos3, delta: int):
+        self.embeds = embeds                                  # [n, H]
+        self.embed_positions = list(embed_positions)          # n prompt indices, ascending
+        self.pos3 = pos3                                      # int64 [3, prompt_len]
+        self.delta = int(delta)
+        self._row_of = {p: i for i, p in enumerate(self.embed_positions)}
+
+    def rows(self, start: int, n: int):
+        """(offsets inside the chunk ``[start, start + n)``, embedding rows) of the image tokens in that chunk."""
+        offs, rows = [], []
+        for p in range(start, start + n):
+            i = self._row_of.get(p)
+            if i is not None:
+                offs.append(p - start)
+                rows.append(i)
+        return offs, rows
+
+    def positions(self, start: int, n: int):
+        """int64 ``[3, n]`` rotary positions of the chunk: from the prompt's table, then ``index + delta`` on all axes."""
+        import torch
+
+        L = self.pos3.shape[1]
+        a = self.pos3[:, start:min(L, start + n)]
+        if start + n > L:
+            tail = torch.arange(max(start, L), start + n) + self.delta
+            a = torch.cat([a, tail[None].expand(3, -1)], dim=1)
+        return a
+
+
 class LLMEngine:
     def __init__(self, model: DecoderModel, cfg: EngineConfig | None = None, num_pages: int | None = None,
                  eos_token_ids=None, control=None):
@@ -59,10 +93,17 @@ class LLMEngine:
         self.dead = False                       # the background loop gave up after repeated failures
 
     # ----------------------------------------------------------------------------------- public API
-    def launch(self, prompt_ids, gen: GenerationConfig | None = None, handle: int | None = None) -> int:
+    def launch(self, prompt_ids, gen: GenerationConfig | None = None, handle: int | None = None, mm=None) -> int:
+        """``mm``: a ``MultimodalContext`` for prompts whose placeholder tokens stand for image embeddings."""
         self._raise_if_dead()
         req = Request(prompt_ids, gen or GenerationConfig(), handle)
         limit = self.cfg.max_context
+        if mm is not None:
+            if self.model.tp.size > 1:
+                raise NotImplementedError("image inputs run on one rank")
+            if len(req.prompt_ids) >= limit:
+                raise ValueError("the prompt with its image tokens does not fit max_context")
+            req.mm = mm
         if len(req.prompt_ids) >= limit:
             req.prompt_ids = req.prompt_ids[-(limit - 1):]
         if not req.prompt_ids:
@@ -192,7 +233,8 @@ class LLMEngine:
                 keep.append(r)
                 continue
             toks = r.prefill_ids
-            cached = self.pm.query(toks) if self.cfg.prefix_cache else []
+            # image placeholder tokens look the same for every image: such prompts neither read nor feed the prefix cache
+            cached = self.pm.query(toks) if (self.cfg.prefix_cache and r.mm is None) else []
             need = self._pages_needed(len(toks) + 1) - len(cached)
             avail = self.pm.num_available()
             limit_ok = (self.pm.num_pages - (avail - need)) <= self.cfg.prefill_page_limit * self.pm.num_pages or not self.running
@@ -220,7 +262,7 @@ class LLMEngine:
         r.finish_reason = reason
         r.stats.finished = time.time()
         if r.pages:
-            if self.cfg.prefix_cache and reason != "error":
+            if self.cfg.prefix_cache and reason != "error" and r.mm is None:
                 n_full = r.num_computed // self.page_len
                 self.pm.record(r.all_ids[:n_full * self.page_len], r.pages[:n_full])
             self.pm.release(r.pages)
@@ -295,7 +337,7 @@ class LLMEngine:
             decoding = self._ensure_decode_pages([r for r in self.running if r.state == RequestState.DECODE])
             reqs = [r for r in reqs if r in self.running and r.state == RequestState.PREFILL]
             for r in decoding:
-                chunks.append(([r.all_ids[-1]], r.total_len - 1, r.pages, True, r.state_slot))
+                chunks.append(([r.all_ids[-1]], r.total_len - 1, r.pages, True, r.state_slot, r.mm))
             budget = max(self.page_len, budget - len(decoding))
         for r in reqs:
             if budget <= 0:
@@ -305,7 +347,7 @@ class LLMEngine:
             if n <= 0:
                 continue
             done = r.num_computed + n == len(toks)
-            chunks.append((toks[r.num_computed:r.num_computed + n], r.num_computed, r.pages, done, r.state_slot))
+            chunks.append((toks[r.num_computed:r.num_computed + n], r.num_computed, r.pages, done, r.state_slot, r.mm))
             owners.append((r, n, done))
             budget -= n
         if not chunks:
@@ -374,7 +416,7 @@ class LLMEngine:
                     d = []                              # no room for drafts: plain single-token step for this request
                 else:
                     r.pages.extend(pg)
-            chunks.append(([r.all_ids[-1]] + d, r.total_len - 1, r.pages, len(d) + 1, r.state_slot))
+            chunks.append(([r.all_ids[-1]] + d, r.total_len - 1, r.pages, len(d) + 1, r.state_slot, r.mm))
             owners.append((r, d))
         logits = self.runner.prefill(chunks)
         if self.model.tp.size > 1:                  # greedy verification: one candidate per rank and row is enough
@@ -417,7 +459,9 @@ class LLMEngine:
         positions = [r.total_len - 1 for r in reqs]
         all_greedy = all(r.gen.is_simple_greedy() for r in reqs)
         out_ids, logits = self.runner.decode(ids, positions, [r.pages for r in reqs], want_logits=not all_greedy,
-                                             state_slots=[r.state_slot for r in reqs] if self.runner.state_slots else None)
+                                             state_slots=[r.state_slot for r in reqs] if self.runner.state_slots else None,
+                                             rope_offsets=[r.mm.delta if r.mm is not None else 0 for r in reqs]
+                                             if any(r.mm is not None for r in reqs) else None)
         for r in reqs:
             r.num_computed = r.total_len
         if all_greedy:

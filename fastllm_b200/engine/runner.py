@@ -150,8 +150,20 @@ class ModelRunner:
         pt = np.zeros((len(chunks), P), dtype=np.int32)
         pl = self.cfg.page_len
         sslots = []
+        mm_rows, mm_vals, pos3 = [], [], []          # image-token rows of the packed batch, their embeddings, 3-D positions
+        any_mm = any(len(ch) > 5 and ch[5] is not None for ch in chunks)
         for b, ch in enumerate(chunks):
             toks, start, pages, want = ch[:4]
+            if any_mm:
+                mm = ch[5] if len(ch) > 5 else None
+                if mm is not None:
+                    offs, rws = mm.rows(start, len(toks))
+                    if offs:
+                        mm_rows.extend(cu[-1] + o for o in offs)
+                        mm_vals.append(mm.embeds[rws])
+                    pos3.append(mm.positions(start, len(toks)))
+                else:
+                    pos3.append(torch.arange(start, start + len(toks))[None].expand(3, -1))
             ss = ch[4] if len(ch) > 4 and ch[4] is not None and ch[4] >= 0 else self.state_slots     # default: the scratch slot
             sslots.append(ss)
             if self.state_slots and start == 0:
@@ -183,6 +195,11 @@ class ModelRunner:
         if not rows:
             # still run the stack to fill the cache; ask for one row to keep shapes valid
             fb.logit_rows = torch.zeros(1, dtype=torch.long, device=dev)
+        if any_mm:
+            fb.rope_pos3 = torch.cat(pos3, dim=1)
+            if mm_rows:
+                fb.embed_rows = torch.tensor(mm_rows, dtype=torch.long, device=dev)
+                fb.embed_vals = torch.cat(mm_vals, dim=0).to(dev)
         logits = self.model.forward(fb, self.kv.pools)
         self.steps += 1
         return logits if rows else None
@@ -222,8 +239,9 @@ class ModelRunner:
             ids, vals = B.argmax(lg, id_offset=lo, want_values=True)
             out_ids.copy_(m.tp.comm.merge_argmax(ids, vals))
 
-    def decode(self, ids, positions, pages_per_req, want_logits=False, state_slots=None):
-        """One token per request. Returns (token ids int32 host tensor [n], logits or None)."""
+    def decode(self, ids, positions, pages_per_req, want_logits=False, state_slots=None, rope_offsets=None):
+        """One token per request. Returns (token ids int32 host tensor [n], logits or None).  ``rope_offsets``: per request,
+        what is added to the token's index to get its rotary position (prompts with images)."""
         n = len(ids)
         pl = self.cfg.page_len
         bsz = self._bucket(n) if self.graph_ok else n
@@ -243,6 +261,8 @@ class ModelRunner:
             mp[2 * bsz + b] = pg[p // pl] * pl + p % pl
             mp[3 * bsz + b] = p + 1
             pt[b, :len(pg)] = pg
+        if rope_offsets is not None:
+            mp[bsz:bsz + n] += np.asarray(rope_offsets, dtype=mp.dtype)
         if self.control is not None:
             self.control.decode(n, bsz, want_logits, mp)
         return self._run_decode(s, n, want_logits)

@@ -329,6 +329,17 @@ class model:
                                                     moe_device_layers=int(_settings.get("moe_device_layers", -1) or -1),
                                                     dtype_config=dtype_config or None, lora=lora or None,
                                                     device_map=_settings["device_map"] if isinstance(_settings.get("device_map"), dict) else None)
+        self._image_options = {}
+        pp = os.path.join(path, "preprocessor_config.json") if os.path.isdir(str(path)) else ""
+        if pp and os.path.exists(pp) and getattr(self.torch_model, "vision", None) is not None:
+            import json as _json
+
+            with open(pp, "r", encoding="utf-8") as f:
+                d = _json.load(f)
+            size = d.get("size") if isinstance(d.get("size"), dict) else {}
+            self._image_options = dict(mean=tuple(d.get("image_mean") or (0.5, 0.5, 0.5)), std=tuple(d.get("image_std") or (0.5, 0.5, 0.5)),
+                                       min_pixels=d.get("min_pixels") or size.get("shortest_edge"),
+                                       max_pixels=d.get("max_pixels") or size.get("longest_edge"))
         if kv_cache_dtype not in ("auto", "", None):
             self.torch_model.set_kv_cache_dtype(kv_cache_dtype)
         cfg = self.torch_model.cfg
@@ -424,10 +435,29 @@ class model:
                                 logprobs=int(kw.get("logprobs", 0) or 0), logits_processor=kw.get("logits_processor"))
 
     # ---- handle-level API ---------------------------------------------------------------------------
-    def launch_stream_response(self, query, history=None, **gen_kwargs) -> int:
+    def launch_stream_response(self, query, history=None, images=None, **gen_kwargs) -> int:
+        """``images``: paths, ``data:`` URLs, bytes or PIL images for a model with a vision tower; a text query gets them in
+        front of the text, a message list may carry them as ``image_url`` / ``image`` content parts instead."""
+        images = list(images or getattr(query, "images", None) or [])
+        if images or (isinstance(query, (list, tuple)) and query and isinstance(query[0], dict)):
+            from .models import vision
+
+            if isinstance(query, str):
+                msgs = []
+                for q, a in history or []:
+                    msgs += [{"role": "user", "content": q}, {"role": "assistant", "content": a}]
+                query = msgs + [{"role": "user", "content": vision.IMAGE_MARKER * len(images) + query}]
+            elif isinstance(query, (list, tuple)) and query and isinstance(query[0], dict):
+                query, found = vision.extract_images(query)
+                images = images or found
         ids = self._to_ids(query, history)
+        mm = None
+        if images:
+            from .models import vision
+
+            ids, mm = vision.build_context(self.torch_model, ids, images, **getattr(self, "_image_options", {}))
         self.engine.start()
-        return self.engine.launch(ids, self._gen_config(**gen_kwargs))
+        return self.engine.launch(ids, self._gen_config(**gen_kwargs), mm=mm)
 
     def abort_handle(self, handle: int):
         self.engine.abort(handle)
@@ -452,9 +482,10 @@ class model:
 
     # ---- convenience API ----------------------------------------------------------------------------
     def stream_response(self, query, history=None, max_length=4096, do_sample=True, top_p=None, top_k=None, temperature=None,
-                        repeat_penalty=None, one_by_one=True, stop_token_ids=None, **kw):
-        h = self.launch_stream_response(query, history, max_length=max_length, do_sample=do_sample, top_p=top_p, top_k=top_k,
-                                        temperature=temperature, repeat_penalty=repeat_penalty, stop_token_ids=stop_token_ids)
+                        repeat_penalty=None, one_by_one=True, stop_token_ids=None, images=None, **kw):
+        h = self.launch_stream_response(query, history, images=images, max_length=max_length, do_sample=do_sample, top_p=top_p,
+                                        top_k=top_k, temperature=temperature, repeat_penalty=repeat_penalty,
+                                        stop_token_ids=stop_token_ids)
         try:
             yield from self.stream_response_handle(h, one_by_one)
         except GeneratorExit:

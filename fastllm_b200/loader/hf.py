@@ -100,7 +100,7 @@ _RENAMES = [
     (r"\.mlp\.dense_h_to_4h\.", ".mlp.gate_up_proj."), (r"\.mlp\.dense_4h_to_h\.", ".mlp.down_proj."),
     (r"^transformer\.h\.", "model.layers."), (r"^transformer\.wte\.", "model.embed_tokens."),
     (r"^transformer\.ln_f\.", "model.norm."), (r"^language_model\.model\.", "model."), (r"^language_model\.lm_head\.", "lm_head."),
-    (r"^model\.language_model\.", "model."),
+    (r"^model\.(language_model\.)+", "model."),
     (r"\.attention\.wqkv\.", ".self_attn.qkv_proj."), (r"\.attention\.wo\.", ".self_attn.o_proj."),
     (r"\.feed_forward\.w1\.", ".mlp.gate_proj."), (r"\.feed_forward\.w3\.", ".mlp.up_proj."),
     (r"\.feed_forward\.w2\.", ".mlp.down_proj."), (r"\.attention_norm\.", ".input_layernorm."),
@@ -324,5 +324,14 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
         m.wdtype_for = lambda name: resolve_wdtype(name, base_w, dtype_config)
         m.moe_wdtype_for = lambda name: resolve_wdtype(name, base_m or base_w, dtype_config)
     finalize_model(m, top_fn, layer_fn, wdtype=wdtype, moe_wdtype=moe_wdtype)
+    vc = cfg.raw.get("vision_config")
+    vis = [n for n in ck.names if n.startswith("model.visual.") or n.startswith("visual.")]
+    if isinstance(vc, dict) and vis and (tp is None or tp.size == 1):
+        # image inputs: the vision tower of the checkpoint (it runs once per image, in the activation dtype)
+        from ..models.vision import VisionConfig, VisionTower
+
+        w = {n.split("visual.", 1)[1]: ck.raw(n) for n in vis}
+        m.vision = VisionTower(VisionConfig(vc), w, m.device, dtype)
+        m.image_token_id = cfg.raw.get("image_token_id")
     ck.close()
     return m

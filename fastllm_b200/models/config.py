@@ -144,7 +144,8 @@ def from_hf_dict(d: dict) -> ModelConfig:
     if "text_config" in d and isinstance(d["text_config"], dict):   # multimodal wrappers keep the LLM config nested
         inner = dict(d["text_config"])
         inner.setdefault("model_type", d.get("model_type", "llama"))
-        for k in ("eos_token_id", "bos_token_id", "tie_word_embeddings", "quantization_config"):
+        for k in ("eos_token_id", "bos_token_id", "tie_word_embeddings", "quantization_config", "vision_config", "image_token_id",
+                  "video_token_id", "vision_start_token_id", "vision_end_token_id"):
             if k in d and k not in inner:
                 inner[k] = d[k]
         d = inner
@@ -184,7 +185,8 @@ def from_hf_dict(d: dict) -> ModelConfig:
     c.bos_token_id = g("bos_token_id")
     c.quantization_config = g("quantization_config")
     c.torch_dtype = str(g("torch_dtype", g("dtype", "bfloat16"))).replace("torch.", "")
-    prf = g("partial_rotary_factor") or (rs.get("partial_rotary_factor") if isinstance(rs, dict) else None)
+    # the value inside rope_parameters is the one the model's rotary embedding reads; the top-level key is its legacy place
+    prf = (rs.get("partial_rotary_factor") if isinstance(rs, dict) else None) or g("partial_rotary_factor")
     if prf:
         c.rotary_dim = int(c.head_dim * float(prf))
     if mt in ("qwen3", "qwen3_moe", "gemma3_text"):

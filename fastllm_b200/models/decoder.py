@@ -43,6 +43,10 @@ class ForwardBatch:
     decode_planned: bool = False
     state_slots: torch.Tensor | None = None      # int32 [B]: recurrent-state slot of each request (linear-attention layers)
     state_slots_host: list | None = None
+    # prompts with images: rows whose embedding is given (image tokens) and (time, row, column) rotary positions [3, T]
+    embed_rows: torch.Tensor | None = None
+    embed_vals: torch.Tensor | None = None
+    rope_pos3: torch.Tensor | None = None
 
 
 @dataclass
@@ -194,6 +198,9 @@ class DecoderModel:
         """(query heads, cos, sin, rotary width) of one attention layer: its own where the layers differ."""
         Hq = lw.heads or self.num_heads_local
         if lw.rope is None:
+            ov = self.__dict__.get("_rope_override")
+            if ov is not None:                   # per-token rows of this forward pass (3-D rotary positions), indexed by row
+                return Hq, ov[0], ov[1], self.rot_dim
             cos, sin = self.rope_tables(device=device, local=local)
             return Hq, cos, sin, self.rot_dim
         spec = lw.rope
@@ -602,7 +609,7 @@ class DecoderModel:
         """Returns fp32 logits ``[R, vocab_local]`` for ``fb.logit_rows`` (all rows if None)."""
         c = self.cfg
         T = fb.ids.shape[0]
-        if not self.on_cuda and T <= 32:
+        if not self.on_cuda and T <= 32 and fb.rope_pos3 is None and fb.embed_rows is None:
             native = self._native_cpu()
             if native is not None:
                 return native.forward(fb, kv_caches)
@@ -615,6 +622,15 @@ class DecoderModel:
         if self.layer_devices is not None:
             return self._forward_staged(fb, kv_caches)
         h = self.embed_tokens(fb.ids)
+        if fb.embed_rows is not None:
+            h[fb.embed_rows] = fb.embed_vals.to(h.dtype)
+        self._rope_override = None
+        if fb.rope_pos3 is not None:
+            from .vision import mrope_tables
+
+            sec = (c.raw.get("rope_parameters") or c.raw.get("rope_scaling") or {}).get("mrope_section") or [self.rot_dim // 2, 0, 0]
+            self._rope_override = mrope_tables(fb.rope_pos3.cpu(), self.rot_dim, c.rope_theta, sec, h.device)
+            fb.positions = torch.arange(T, dtype=torch.int32, device=h.device)       # rows of the per-token tables
         if self._fused_active:
             h = fused.load_h(h)
         n_layers = len(self.layers)
@@ -647,6 +663,7 @@ class DecoderModel:
                 nxt = self.lm_head if fb.logit_rows is None else None
             h, x = self._mlp(lw.mlp, x, h, i, next_ln, nxt)
         self._beta = 1.0
+        self._rope_override = None
         # x is RMSNorm(h) with the final norm weight (row-wise, so selecting rows afterwards is equivalent)
         if fb.logit_rows is not None:
             B.flush_pending_wait()

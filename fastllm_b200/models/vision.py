@@ -222,3 +222,76 @@ def mrope_tables(pos3: torch.Tensor, rot_dim: int, theta: float, sections, devic
     axis[2:3 * sections[2]:3] = 2
     ang = pos3.double()[axis, :].t() * inv[None, :]                          # [T, half]
     return ang.cos().float().to(device).contiguous(), ang.sin().float().to(device).contiguous()
+
+
+# ---------------------------------------------------------------------------------------------------
+# prompts with images
+# ---------------------------------------------------------------------------------------------------
+IMAGE_MARKER = "<|vision_start|><|image_pad|><|vision_end|>"
+
+
+def image_source(part: dict):
+    """The image of one content part in the OpenAI (``image_url``), Responses (``input_image``) or Qwen (``image``) form."""
+    t = part.get("type")
+    if t == "image_url":
+        u = part.get("image_url")
+        return u.get("url") if isinstance(u, dict) else u
+    if t == "input_image":
+        return part.get("image_url") or part.get("file_id")
+    if t == "image":
+        return part.get("image") or part.get("url") or part.get("path")
+    return None
+
+
+def extract_images(messages):
+    """Chat messages whose content lists hold image parts -> (messages with plain-text content, every image replaced by the
+    placeholder markup of the Qwen-VL chat format, the images in prompt order)."""
+    out, images = [], []
+    for m in messages:
+        d = dict(m)
+        c = d.get("content")
+        if isinstance(c, list):
+            text = ""
+            for part in c:
+                if not isinstance(part, dict):
+                    continue
+                src = image_source(part)
+                if src is not None:
+                    images.append(src)
+                    text += IMAGE_MARKER
+                elif part.get("type", "text") in ("text", "input_text", "output_text"):
+                    text += part.get("text", "")
+            d["content"] = text
+        out.append(d)
+    return out, images
+
+
+def build_context(model, ids, images, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5), min_pixels=None, max_pixels=None):
+    """Token ids with one placeholder token per image -> (ids with every placeholder repeated once per merged patch, the
+    request's ``MultimodalContext``: the tower's embeddings for those tokens and the 3-D rotary positions)."""
+    from ..engine.engine import MultimodalContext
+
+    tower = getattr(model, "vision", None)
+    tok = getattr(model, "image_token_id", None)
+    if tower is None or tok is None:
+        raise ValueError("this model has no vision tower: image inputs are not supported")
+    cfg = tower.cfg
+    patches, grids = [], []
+    for im in images:
+        p, g = image_to_patches(im, cfg, mean, std, min_pixels, max_pixels)
+        patches.append(p)
+        grids.append(g)
+    embeds = tower.forward(torch.cat(patches), grids)
+    out, k = [], 0
+    for t in ids:
+        if t == tok and k < len(grids):
+            gt, gh, gw = grids[k]
+            out.extend([tok] * (gt * gh * gw // cfg.merge ** 2))
+            k += 1
+        else:
+            out.append(t)
+    if k != len(images):
+        raise ValueError(f"the prompt holds {k} image placeholders for {len(images)} images")
+    pos3, delta = mrope_positions(out, tok, grids, cfg.merge)
+    at = [i for i, t in enumerate(out) if t == tok][:embeds.shape[0]]
+    return out, MultimodalContext(embeds, at, pos3, delta)

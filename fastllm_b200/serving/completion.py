@@ -30,6 +30,11 @@ def normalize_messages(messages):
     return out
 
 
+class PromptIds(list):
+    """Token ids of a prompt plus the images its placeholder tokens stand for (``launch_stream_response`` picks them up)."""
+    images: list = ()
+
+
 class ActiveRequests:
     """Bookkeeping for /v1/cancel and /v1/active_conversations."""
 
@@ -55,9 +60,16 @@ class Completion:
     # ---------------------------------------------------------------------------------------------
     def build_prompt_ids(self, messages=None, prompt=None, tools=None, chat_template_kwargs=None):
         if messages is not None:
+            images = []
+            if getattr(getattr(self.model, "torch_model", None), "vision", None) is not None:
+                from ..models.vision import extract_images
+
+                messages, images = extract_images(messages)          # image parts -> placeholder markup + the images
             text = self.model.apply_chat_template(normalize_messages(messages), add_generation_prompt=True, tools=tools,
                                                   **(chat_template_kwargs or {}))
-            return self.model.encode(text), text
+            ids = PromptIds(self.model.encode(text))
+            ids.images = images
+            return ids, text
         if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
             return list(prompt), None
         return self.model.encode(prompt or ""), prompt

@@ -85,3 +85,92 @@ def test_mrope_positions_and_tables():
     cos_w, sin_w = rot(torch.zeros(1, 1, 32), pos[:, None, :])
     cos, sin = V.mrope_tables(pos, 32, 10000.0, [6, 5, 5])
     assert torch.allclose(cos, cos_w[0, :, :16], atol=1e-5) and torch.allclose(sin, sin_w[0, :, :16], atol=1e-5)
+
+
+def test_qwen3_5_image_prompt_matches_transformers(tmp_path):
+    """A prompt with an image through the whole path -- checkpoint with ``visual.*`` weights, image -> patches -> tower,
+    placeholder expansion, embeddings in place of the image tokens, (time, row, column) rotary positions in the full-attention
+    layers, chunked prefill and decode -- against transformers' Qwen3.5 conditional-generation model."""
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.loader import hf
+
+    try:
+        from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
+    except Exception as e:
+        pytest.skip(f"transformers has no qwen3_5: {e}")
+    torch.manual_seed(0)
+    text = dict(vocab_size=512, hidden_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                intermediate_size=128, max_position_embeddings=512, linear_num_key_heads=2, linear_num_value_heads=4,
+                linear_key_head_dim=16, linear_value_head_dim=16, layer_types=["linear_attention", "full_attention"],
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                                 "mrope_section": [3, 3, 2], "mrope_interleaved": True})
+    cfg = Qwen3_5Config(text_config=text, vision_config=_VC, image_token_id=500, video_token_id=501, vision_start_token_id=502,
+                        vision_end_token_id=503)
+    ref = Qwen3_5ForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.normal_(p, std=0.08)
+    d = str(tmp_path / "q35vl")
+    ref.save_pretrained(d, safe_serialization=True)
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert getattr(m, "vision", None) is not None and m.image_token_id == 500
+    from PIL import Image
+
+    g = torch.Generator().manual_seed(1)
+    img = Image.fromarray((torch.rand(40, 56, 3, generator=g) * 255).to(torch.uint8).numpy())
+    ids = [5, 6, 7, 502, 500, 503, 8, 9, 10, 11]
+    ids2, mm = V.build_context(m, ids, [img], min_pixels=64, max_pixels=2048)
+    n_img = ids2.count(500)
+    patches, grid = V.image_to_patches(img, m.vision.cfg, min_pixels=64, max_pixels=2048)
+    assert n_img == grid[1] * grid[2] // 4 and n_img > 4 and mm.embeds.shape == (n_img, 96)
+    with torch.no_grad():
+        out = ref(input_ids=torch.tensor([ids2]), pixel_values=patches, image_grid_thw=torch.tensor([grid]),
+                  mm_token_type_ids=torch.tensor([[1 if t == 500 else 0 for t in ids2]]))
+    want = out.logits[0, -1].float()
+    eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512, chunked_prefill_size=16), num_pages=8)
+    h = eng.launch(ids2, GenerationConfig(max_new_tokens=3, ignore_eos=True), mm=mm)
+    req = eng.requests[h]
+    while not req.finished():
+        eng.step()
+    assert int(req.output_ids[0]) == int(want.argmax())
+    # the second token: transformers continues from the 3-D positions (rope delta), one-shot over the longer prompt
+    ids3 = ids2 + [int(req.output_ids[0])]
+    with torch.no_grad():
+        out2 = ref(input_ids=torch.tensor([ids3]), pixel_values=patches, image_grid_thw=torch.tensor([grid]),
+                   mm_token_type_ids=torch.tensor([[1 if t == 500 else 0 for t in ids3]]))
+    assert int(req.output_ids[1]) == int(out2.logits[0, -1].argmax())
+    # logits of the one-shot prefill
+    pages = [0, 1]
+    lg = eng.runner.prefill([(ids2, 0, pages, True, 0, mm)])[0].float()
+    assert torch.nn.functional.cosine_similarity(lg[:want.numel()], want, dim=0).item() > 0.9999
+
+
+def test_image_parts_of_chat_messages():
+    """OpenAI ``image_url`` / Responses ``input_image`` / Qwen ``image`` content parts become the placeholder markup, the
+    images are returned in prompt order; the server's prompt builder hands them on with the token ids."""
+    from fastllm_b200.serving.completion import Completion, PromptIds
+
+    msgs = [{"role": "system", "content": "s"},
+            {"role": "user", "content": [{"type": "image_url", "image_url": {"url": "data:image/png;base64,AAAA"}},
+                                         {"type": "text", "text": "what is this?"}, {"type": "image", "image": "/tmp/x.png"}]},
+            {"role": "assistant", "content": "a"}, {"role": "user", "content": [{"type": "input_image", "image_url": "file:///y.jpg"}]}]
+    out, images = V.extract_images(msgs)
+    assert images == ["data:image/png;base64,AAAA", "/tmp/x.png", "file:///y.jpg"]
+    assert out[1]["content"] == V.IMAGE_MARKER + "what is this?" + V.IMAGE_MARKER and out[3]["content"] == V.IMAGE_MARKER
+    assert out[0]["content"] == "s" and out[2]["content"] == "a"
+
+    class _TM:
+        vision = object()
+
+    class _M:
+        torch_model = _TM()
+
+        def apply_chat_template(self, messages, add_generation_prompt=True, tools=None, **kw):
+            return "|".join(m["content"] for m in messages)
+
+        def encode(self, text):
+            return [len(text), 7]
+
+    ids, text = Completion(_M()).build_prompt_ids(messages=msgs)
+    assert isinstance(ids, PromptIds) and ids.images == images and V.IMAGE_MARKER in text and list(ids) == [len(text), 7]
