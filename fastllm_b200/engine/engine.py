@@ -352,7 +352,16 @@ class LLMEngine:
             budget -= n
         if not chunks:
             return 0
-        logits = self.runner.prefill(chunks)
+        mtp = self._mtp_on()
+        logits = self.runner.prefill(chunks, keep_hidden=mtp)
+        mtp_items, off = [], 0
+        if mtp:                        # (request, first position, rows, first row in the packed batch) of every chunk
+            for r in decoding:
+                mtp_items.append((r, r.total_len - 1, 1, off))
+                off += 1
+            for r, n, _ in owners:
+                mtp_items.append((r, r.num_computed, n, off))
+                off += n
         produced = 0
         finals = [r for r, _, d in owners if d]
         for r, n, _ in owners:
@@ -376,9 +385,73 @@ class LLMEngine:
                 if not r.stats.first_token:
                     r.stats.first_token = time.time()
                 produced += self._emit(r, int(t))
+        if mtp:
+            self._mtp_advance(mtp_items)
         return produced
 
     # -------------------------------------------------------------------------------- speculative decoding
+    def _mtp_on(self) -> bool:
+        return bool(self.cfg.speculative == "mtp" and getattr(self.model, "mtp", None) is not None and self.model.tp.size == 1
+                    and not self.runner.state_slots)
+
+    def _mtp_advance(self, items) -> None:
+        """Run the draft head over the rows the decoder has just produced: for every position whose following token is known
+        it appends that position to the head's own KV pages; the row of a decoding request's newest token pair yields the
+        first draft, further drafts chain the head on its own output (their pages are written again once the true rows
+        arrive).  ``items``: (request, first position, rows, first row in ``model.last_hidden``)."""
+        hidden = self.model.last_hidden
+        chunks, sel, heads = [], [], []
+        for r, start, n, off in items:
+            r.mtp_drafts = []
+            if r.finished():
+                continue
+            ids = r.all_ids
+            avail = min(n, len(ids) - 1 - start)
+            if avail <= 0:
+                continue
+            tail = r.state == RequestState.DECODE and start + avail == len(ids) - 1
+            chunks.append((ids[start + 1:start + 1 + avail], start, r.pages, bool(tail), r.state_slot, r.mm))
+            sel.extend(range(off, off + avail))
+            if tail:
+                heads.append((r, start + avail - 1, len(sel) - 1))
+        if not chunks:
+            return
+        idx = torch.tensor(sel, dtype=torch.long, device=hidden.device)
+        logits, x = self.runner.prefill(chunks, mtp_hidden=hidden.index_select(0, idx))
+        if not heads:
+            return
+        toks = sampling.greedy(logits).tolist()
+        live = []
+        for (r, pos, row), t in zip(heads, toks):
+            r.mtp_drafts = [int(t)]
+            live.append((r, pos, x[row:row + 1]))
+        for _ in range(1, self.cfg.speculative_tokens):
+            chunks, hs, nxt = [], [], []
+            for r, pos, h in live:
+                pos += 1
+                need = self._pages_needed(pos + 1) - len(r.pages)
+                if pos + 2 >= self.cfg.max_context or (need > 0 and not self._grow_pages(r, need)):
+                    continue
+                chunks.append(([r.mtp_drafts[-1]], pos, r.pages, True, r.state_slot, r.mm))
+                hs.append(h)
+                nxt.append((r, pos))
+            if not chunks:
+                break
+            logits, x = self.runner.prefill(chunks, mtp_hidden=torch.cat(hs, dim=0))
+            toks = sampling.greedy(logits).tolist()
+            live = []
+            for i, ((r, pos), t) in enumerate(zip(nxt, toks)):
+                r.mtp_drafts.append(int(t))
+                live.append((r, pos, x[i:i + 1]))
+
+    def _grow_pages(self, r, need: int) -> bool:
+        pg = self.pm.alloc(need)
+        if pg is None:
+            return False
+        r.pages.extend(pg)
+        return True
+
+    # (prompt-lookup drafts)
     @staticmethod
     def _ngram_draft(ids: list[int], n_max: int, k: int) -> list[int]:
         """Draft tokens by prompt lookup: find the latest earlier occurrence of the text's last n tokens (n = n_max .. 1) and
@@ -401,11 +474,15 @@ class LLMEngine:
         model: tools/fastllm_pytools/util.py:518-532, acceptance kernel src/devices/cuda/fastllm-cuda.cu:13266) verify the
         same way; here the drafts come from the request's own text.  Returns None when nothing could be drafted."""
         k = self.cfg.speculative_tokens
+        mtp = self._mtp_on()
         drafts = []
         for r in reqs:
             room = min(k, self.cfg.max_context - r.total_len - 1, (r.gen.max_new_tokens - len(r.output_ids) - 1) if r.gen.max_new_tokens > 0 else k)
-            drafts.append(self._ngram_draft(r.all_ids, self.cfg.speculative_ngram, room) if room > 0 else [])
-        if not any(drafts):
+            if mtp:
+                drafts.append(list(r.mtp_drafts[:max(0, room)]))
+            else:
+                drafts.append(self._ngram_draft(r.all_ids, self.cfg.speculative_ngram, room) if room > 0 else [])
+        if not any(drafts) and not mtp:          # (the draft head needs every step's hidden rows: it always takes this path)
             return None
         chunks, owners = [], []
         for r, d in zip(reqs, drafts):
@@ -418,7 +495,8 @@ class LLMEngine:
                     r.pages.extend(pg)
             chunks.append(([r.all_ids[-1]] + d, r.total_len - 1, r.pages, len(d) + 1, r.state_slot, r.mm))
             owners.append((r, d))
-        logits = self.runner.prefill(chunks)
+        logits = self.runner.prefill(chunks, keep_hidden=mtp)
+        mtp_items = []
         if self.model.tp.size > 1:                  # greedy verification: one candidate per rank and row is enough
             if self.control is not None:
                 self.control.gather_logits(1)
@@ -429,10 +507,11 @@ class LLMEngine:
         produced, row = 0, 0
         for r, d in owners:
             mine = choice[row:row + len(d) + 1]
-            row += len(d) + 1
             n_ok = 0
             while n_ok < len(d) and d[n_ok] == mine[n_ok]:
                 n_ok += 1
+            mtp_items.append((r, r.total_len - 1, n_ok + 1, row))
+            row += len(d) + 1
             self.spec_proposed += len(d)
             self.spec_accepted += n_ok
             for t in mine[:n_ok + 1]:
@@ -441,6 +520,8 @@ class LLMEngine:
                 produced += self._emit(r, int(t))
             if not r.finished():
                 r.num_computed = r.total_len - 1        # the last emitted token's K/V is written by the next step
+        if mtp:
+            self._mtp_advance(mtp_items)
         self.decode_steps += 1
         self.decode_tokens += produced
         return produced
@@ -451,7 +532,9 @@ class LLMEngine:
         reqs = self._ensure_decode_pages(reqs)
         if not reqs:
             return 0
-        if self.cfg.speculative == "ngram" and not self.runner.state_slots and all(r.gen.is_simple_greedy() for r in reqs):
+        if self.cfg.speculative == "mtp" and not self._mtp_on():
+            self.cfg.speculative = "ngram"          # no draft head with this model: prompt-lookup drafts instead
+        if self.cfg.speculative in ("ngram", "mtp") and not self.runner.state_slots and all(r.gen.is_simple_greedy() for r in reqs):
             n = self._speculative_step(reqs)
             if n is not None:
                 return n

@@ -119,6 +119,10 @@ class KVCache:
             k = torch.zeros(lks, device=dev, dtype=dt)
             v = torch.zeros(lvs, device=dev, dtype=dt) if lvs is not None else None
             self.pools.append((k, v))
+        if getattr(model, "mtp", None) is not None:
+            # the draft head's decoder layer keeps its own pages under the same page ids (pool index num_layers)
+            self.pools.append((torch.zeros(ks, device=model.device, dtype=dt),
+                               torch.zeros(vs, device=model.device, dtype=dt) if vs is not None else None))
         self.manager = PageManager(num_pages, page_len)
 
 

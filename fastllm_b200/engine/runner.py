@@ -34,7 +34,8 @@ class EngineConfig:
     page_len: int = A.PAGE_LEN
     check_device_errors_every: int = 64
     mixed_prefill_decode: bool = True    # a prefill step also advances the requests that are already decoding (one token each)
-    speculative: str = ""                # "" | "ngram": draft tokens by looking the recent n-gram up in the request's own text
+    speculative: str = ""                # "" | "ngram": drafts by looking the recent n-gram up in the request's own text | "mtp": drafts
+                                         # from the checkpoint's multi-token-prediction head (falls back to "ngram" without one)
     speculative_tokens: int = 4          # draft tokens verified per step
     speculative_ngram: int = 3           # longest suffix that is searched for (shorter ones are tried next)
 
@@ -139,10 +140,14 @@ class ModelRunner:
         return True
 
     # ---------------------------------------------------------------------------------------------
-    def prefill(self, chunks):
+    def prefill(self, chunks, keep_hidden: bool = False, mtp_hidden=None):
         """chunks: list of (token_ids, start_pos, pages, want_logits). Returns fp32 logits ``[R, V_local]``
-        for the chunks that asked for them (last token of the chunk), in order."""
-        if self.control is not None:
+        for the chunks that asked for them (last token of the chunk), in order.
+
+        ``keep_hidden``: the final-normed rows of the whole packed batch stay in ``model.last_hidden`` (the draft head reads
+        them).  ``mtp_hidden``: run the draft head instead of the decoder -- the chunks then hold, per position, the token that
+        FOLLOWS it, ``mtp_hidden`` the matching hidden rows; returns (logits, the head's final-normed rows)."""
+        if self.control is not None and mtp_hidden is None:
             self.control.prefill(chunks)
         dev = self.device
         ids, pos, slots, cu, kv_lens, rows = [], [], [], [0], [], []
@@ -166,7 +171,7 @@ class ModelRunner:
                     pos3.append(torch.arange(start, start + len(toks))[None].expand(3, -1))
             ss = ch[4] if len(ch) > 4 and ch[4] is not None and ch[4] >= 0 else self.state_slots     # default: the scratch slot
             sslots.append(ss)
-            if self.state_slots and start == 0:
+            if self.state_slots and start == 0 and mtp_hidden is None:
                 self.kv.reset_state(ss)              # a request starts (or restarts after an eviction) from empty state
             n = len(toks)
             ids.extend(toks)
@@ -197,9 +202,13 @@ class ModelRunner:
             fb.logit_rows = torch.zeros(1, dtype=torch.long, device=dev)
         if any_mm:
             fb.rope_pos3 = torch.cat(pos3, dim=1)
-            if mm_rows:
+            if mm_rows and mtp_hidden is None:
                 fb.embed_rows = torch.tensor(mm_rows, dtype=torch.long, device=dev)
                 fb.embed_vals = torch.cat(mm_vals, dim=0).to(dev)
+        if mtp_hidden is not None:
+            logits, x = self.model.mtp_forward(fb, mtp_hidden, self.kv.pools)
+            return (logits if rows else None), x
+        fb.keep_hidden = keep_hidden
         logits = self.model.forward(fb, self.kv.pools)
         self.steps += 1
         return logits if rows else None

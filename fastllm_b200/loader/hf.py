@@ -234,6 +234,10 @@ class HFCheckpoint:
             f.close()
 
 
+def staged_devices(m) -> bool:
+    return getattr(m, "layer_devices", None) is not None
+
+
 def resolve_wdtype(name: str, default: str, rules: list | None) -> str:
     """Apply ``dtype_config`` rules ``[{"key": regex, "dtype": name}, ...]``; the last matching rule wins."""
     out = default
@@ -324,6 +328,21 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
         m.wdtype_for = lambda name: resolve_wdtype(name, base_w, dtype_config)
         m.moe_wdtype_for = lambda name: resolve_wdtype(name, base_m or base_w, dtype_config)
     finalize_model(m, top_fn, layer_fn, wdtype=wdtype, moe_wdtype=moe_wdtype)
+    if cfg.mtp_layers and (tp is None or tp.size == 1) and not staged_devices(m):
+        from .shard import build_mtp
+
+        L = cfg.num_layers
+        t = ck.collect(f"model.layers.{L}.")
+        if not t and any(n.startswith("mtp.") for n in ck.names):
+            # Qwen3.5 naming: mtp.fc / pre_fc_norm_embedding / pre_fc_norm_hidden / norm / layers.0.*
+            ren = {"mtp.fc.weight": "eh_proj.weight", "mtp.pre_fc_norm_embedding.weight": "enorm.weight",
+                   "mtp.pre_fc_norm_hidden.weight": "hnorm.weight", "mtp.norm.weight": "shared_head.norm.weight"}
+            for k, v in ck.collect("mtp.").items():
+                k2 = ren.get(k) or (k[len("mtp.layers.0."):] if k.startswith("mtp.layers.0.") else None)
+                if k2 is not None:
+                    t[f"model.layers.{L}." + k2] = v
+        if t.get(f"model.layers.{L}.eh_proj.weight") is not None:
+            build_mtp(m, t, wdtype, moe_wdtype)
     vc = cfg.raw.get("vision_config")
     vis = [n for n in ck.names if n.startswith("model.visual.") or n.startswith("visual.")]
     if isinstance(vc, dict) and vis and (tp is None or tp.size == 1):

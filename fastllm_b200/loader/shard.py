@@ -341,6 +341,27 @@ def build_linear_attn(m, g, ln, W, layer_idx: int = 0):
     return la
 
 
+def build_mtp(m, t: dict, wdtype="dense", moe_wdtype=None):
+    """Multi-token-prediction module from the canonical tensors of layer ``num_layers`` (DeepSeek-V3 naming: ``enorm``,
+    ``hnorm``, ``eh_proj``, ``shared_head.norm`` [, ``shared_head.head``] beside an ordinary decoder layer)."""
+    from ..models.decoder import MTPModule
+
+    L = m.cfg.num_layers
+    p = f"model.layers.{L}."
+    mt = MTPModule()
+    mt.norm_e, mt.norm_h = _to(t.pop(p + "enorm.weight"), m), _to(t.pop(p + "hnorm.weight"), m)
+    mt.fc = _lin(m, t.pop(p + "eh_proj.weight"), "dense")
+    mt.final_norm = _to(t.pop(p + "shared_head.norm.weight"), m)
+    hw = t.pop(p + "shared_head.head.weight", None)
+    t.pop(p + "embed_tokens.weight", None)                       # a copy of the model's table
+    if hw is not None and m.lm_head is not None and tuple(hw.shape) == (m.lm_head.n, m.lm_head.k) and not m.cfg.tie_embeddings:
+        same = m.lm_head.kind == "dense" and torch.equal(_to(hw, m), m.lm_head.w)
+        mt.head = None if same else _lin(m, hw, "dense")
+    build_layer(m, L, t, wdtype, moe_wdtype)
+    mt.layer = m.layers.pop()                                     # not part of the decoder stack
+    m.mtp = mt
+
+
 def build_top(m, t: dict, wdtype="dense"):
     cfg, tp = m.cfg, m.tp
     m.embed = _to(t["model.embed_tokens.weight"], m)

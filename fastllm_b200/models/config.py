@@ -96,6 +96,7 @@ class ModelConfig:
     resid_factors: tuple = (1.0, 1.0, 1.0, 1.0, 1.0, 1.0)
     attn_output_gate: bool = False         # q_proj also produces a per-head gate; the attention output is multiplied by its sigmoid
     mlp_only_layers: list = field(default_factory=list)   # layers that keep a dense MLP in an otherwise sparse model
+    mtp_layers: int = 0                    # multi-token-prediction modules stored with the checkpoint (draft heads)
     # bookkeeping
     eos_token_ids: list = field(default_factory=list)
     bos_token_id: int | None = None
@@ -185,6 +186,7 @@ def from_hf_dict(d: dict) -> ModelConfig:
     c.bos_token_id = g("bos_token_id")
     c.quantization_config = g("quantization_config")
     c.torch_dtype = str(g("torch_dtype", g("dtype", "bfloat16"))).replace("torch.", "")
+    c.mtp_layers = int(g("mtp_num_hidden_layers", g("num_nextn_predict_layers", 0)) or 0)
     # the value inside rope_parameters is the one the model's rotary embedding reads; the top-level key is its legacy place
     prf = (rs.get("partial_rotary_factor") if isinstance(rs, dict) else None) or g("partial_rotary_factor")
     if prf:
@@ -582,6 +584,10 @@ def preset(name: str) -> ModelConfig:
                                  intermediate_size=512, q_lora_rank=128, kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16,
                                  v_head_dim=32, scale_emb=12.0, scale_depth=1.4, dim_model_base=64, rms_norm_eps=1e-5,
                                  max_position_embeddings=2048, eos_token_id=511))
+    if name == "tiny-llama-mtp":         # tiny llama with one multi-token-prediction module (speculative decoding tests)
+        return from_hf_dict(dict(model_type="llama", vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, intermediate_size=512, rms_norm_eps=1e-5, rope_theta=10000.0,
+                                 max_position_embeddings=2048, num_nextn_predict_layers=1))
     if name == "tiny-moss":              # LayerNorm, parallel attention / GELU MLP block, partial pairwise rotary
         return from_hf_dict(dict(model_type="moss", vocab_size=512, n_embd=256, n_layer=2, n_head=4, rotary_dim=32, n_positions=2048,
                                  activation_function="gelu_new", layer_norm_epsilon=1e-5, eos_token_id=511))

@@ -47,6 +47,7 @@ class ForwardBatch:
     embed_rows: torch.Tensor | None = None
     embed_vals: torch.Tensor | None = None
     rope_pos3: torch.Tensor | None = None
+    keep_hidden: bool = False                    # leave the final-normed rows of the whole batch in ``model.last_hidden``
 
 
 @dataclass
@@ -135,6 +136,22 @@ class LayerWeights:
         self.lin: LinearAttnWeights | None = None      # set instead of ``attn`` projections on linear-attention layers
 
 
+class MTPModule:
+    """One multi-token-prediction module: the embedding of token i + 1 and the final-normed hidden row of position i are
+    normalised, concatenated and projected back to the model width, pass one decoder layer with its own KV pages, a final
+    norm and the model's output head -- the logits predict token i + 2.  (DeepSeek-V3 ``model.layers.<L>.{enorm, hnorm, eh_proj,
+    shared_head.norm}``; Qwen3.5 ``mtp.{pre_fc_norm_embedding, pre_fc_norm_hidden, fc, layers.0, norm}``.)
+    Reference: src/models/qwen3_5.cpp:20875-20884 (input fusion), :13868-13940 (draft chain)."""
+
+    def __init__(self):
+        self.norm_e = None
+        self.norm_h = None
+        self.fc: LinearWeight | None = None        # [H, 2H]: columns [embedding | hidden]
+        self.layer: LayerWeights | None = None
+        self.final_norm = None
+        self.head: LinearWeight | None = None       # None: the model's own output head
+
+
 class DecoderModel:
     """Weights + forward pass of one tensor-parallel rank."""
 
@@ -164,6 +181,8 @@ class DecoderModel:
         self.general_attn = bool(cfg.qk_norm_after_rope or cfg.qk_norm_full)
         self.kv8_decode_ok = False
         self.ln_bias = {}                  # LayerNorm families: id(norm weight) -> its bias
+        self.mtp: MTPModule | None = None  # draft head for speculative decoding
+        self.last_hidden = None
         if cfg.use_mla and cfg.rope_scaling and cfg.rope_scaling.get("mscale_all_dim"):
             ms = 0.1 * float(cfg.rope_scaling["mscale_all_dim"]) * math.log(float(cfg.rope_scaling.get("factor", 1.0))) + 1.0
             self.attn_scale *= ms * ms
@@ -230,7 +249,7 @@ class DecoderModel:
     def kv_bytes_per_page(self) -> int:
         ks, vs = self.kv_cache_shape(1)
         n = math.prod(ks) + (math.prod(vs) if vs else 0)
-        paged_layers = sum(1 for i in range(self.cfg.num_layers) if not self.cfg.layer_is_linear(i))
+        paged_layers = sum(1 for i in range(self.cfg.num_layers) if not self.cfg.layer_is_linear(i)) + (1 if self.mtp is not None else 0)
         return n * max(1, paged_layers) * torch.finfo(getattr(self, "kv_dtype", None) or self.dtype).bits // 8
 
     def linear_state_shapes(self, n_slots: int):
@@ -609,7 +628,7 @@ class DecoderModel:
         """Returns fp32 logits ``[R, vocab_local]`` for ``fb.logit_rows`` (all rows if None)."""
         c = self.cfg
         T = fb.ids.shape[0]
-        if not self.on_cuda and T <= 32 and fb.rope_pos3 is None and fb.embed_rows is None:
+        if not self.on_cuda and T <= 32 and fb.rope_pos3 is None and fb.embed_rows is None and not fb.keep_hidden:
             native = self._native_cpu()
             if native is not None:
                 return native.forward(fb, kv_caches)
@@ -665,6 +684,9 @@ class DecoderModel:
         self._beta = 1.0
         self._rope_override = None
         # x is RMSNorm(h) with the final norm weight (row-wise, so selecting rows afterwards is equivalent)
+        if fb.keep_hidden:
+            B.flush_pending_wait()
+            self.last_hidden = x
         if fb.logit_rows is not None:
             B.flush_pending_wait()
             x = x.index_select(0, fb.logit_rows)
@@ -675,6 +697,30 @@ class DecoderModel:
         if c.final_softcap:
             logits = torch.tanh(logits / c.final_softcap) * c.final_softcap
         return logits
+
+    def mtp_forward(self, fb: ForwardBatch, hidden: torch.Tensor, kv_caches):
+        """Draft head over the packed rows of ``fb``: ``fb.ids`` are the tokens FOLLOWING each row's position, ``hidden`` the
+        final-normed rows of the main model (or of this head, when drafts are chained).  The layer appends to its own page
+        pools (``kv_caches[num_layers]``).  Returns (fp32 logits of ``fb.logit_rows``, final-normed rows of the head)."""
+        mt, c = self.mtp, self.cfg
+        saved = self._fused_active
+        self._fused_active = False
+        try:
+            e = self.embed_tokens(fb.ids)
+            z = mt.fc(torch.cat([self._norm(e, mt.norm_e), self._norm(hidden.to(e.dtype), mt.norm_h)], dim=-1))
+            lw = mt.layer
+            x = self._norm(z, lw.attn.ln)
+            h, x = self._attention(lw.attn, x, fb, kv_caches[c.num_layers], z, lw.mlp.ln, None)
+            h, x = self._mlp(lw.mlp, x, h, c.num_layers, mt.final_norm, None)
+            B.flush_pending_wait()
+            rows = x if fb.logit_rows is None else x.index_select(0, fb.logit_rows)
+            logits = (mt.head or self.lm_head)(rows, out_f32=True)
+            B.flush_pending_wait()
+            if c.logit_scale != 1.0:
+                logits = logits * c.logit_scale
+            return logits, x
+        finally:
+            self._fused_active = saved
 
     def _forward_staged(self, fb: ForwardBatch, kv_caches) -> torch.Tensor:
         """Layer-split placement (``--device "{'cuda:0': 3, 'cuda:1': 2}"`` / ``cudapp``): every layer runs on its own
@@ -893,4 +939,17 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
         return raw
 
     finalize_model(m, top_tensors, layer_tensors, wdtype=wdtype, moe_wdtype=moe_wdtype)
+    if cfg.mtp_layers and (tp is None or tp.size == 1):
+        from ..loader.shard import build_mtp
+
+        L = cfg.num_layers
+        t = dict(layer_tensors(L))
+        p = f"model.layers.{L}."
+        raw.clear()
+        ones(p + "enorm.weight", H)
+        ones(p + "hnorm.weight", H)
+        mk(p + "eh_proj.weight", (H, 2 * H))
+        ones(p + "shared_head.norm.weight", H)
+        t.update(raw)
+        build_mtp(m, t, wdtype, moe_wdtype)
     return m

@@ -135,17 +135,23 @@ def make_normal_llm_model(args):
 
     args = apply_config_file(args)
     algo = str(getattr(args, "speculative_algorithm", "") or "").lower()
-    if algo in ("ngram", "prompt_lookup", "lookup"):
-        llm._settings["speculative"] = "ngram"
-        if getattr(args, "speculative_dspark_block_size", 0):
-            llm._settings["speculative_tokens"] = int(args.speculative_dspark_block_size)
+    mtp_flag = getattr(args, "mtp", "")
+    if algo in ("ngram", "prompt_lookup", "lookup", "mtp", "nextn", "eagle") or mtp_flag:
+        # "mtp": drafts from the checkpoint's multi-token-prediction head (the engine falls back to prompt-lookup drafts when
+        # the model has none, runs tensor-parallel or keeps recurrent state)
+        llm._settings["speculative"] = "mtp" if (algo in ("mtp", "nextn", "eagle") or mtp_flag) else "ngram"
+        n = getattr(args, "speculative_dspark_block_size", 0) or (int(mtp_flag) if str(mtp_flag).isdigit() else 0)
+        if n:
+            llm._settings["speculative_tokens"] = int(n)
+        elif llm._settings["speculative"] == "mtp":
+            llm._settings["speculative_tokens"] = 1
     elif algo:
-        print(f"[fastllm_b200] --speculative_algorithm {algo}: only 'ngram' (prompt-lookup drafts, verified in one pass) exists "
-              "in this build; decoding normally", file=sys.stderr)
-    for flag in ("mtp", "dspark", "speculative_draft_model_path"):
+        print(f"[fastllm_b200] --speculative_algorithm {algo}: 'ngram' (prompt-lookup drafts) and 'mtp' (the checkpoint's draft head) "
+              "exist in this build; decoding normally", file=sys.stderr)
+    for flag in ("dspark", "speculative_draft_model_path"):
         if getattr(args, flag, ""):
-            print(f"[fastllm_b200] --{flag}: draft heads / draft models are not part of this build "
-                  "(use --speculative_algorithm ngram); decoding normally", file=sys.stderr)
+            print(f"[fastllm_b200] --{flag}: separate draft models are not part of this build "
+                  "(use --speculative_algorithm mtp or ngram); decoding normally", file=sys.stderr)
     if not args.path:
         raise SystemExit("no model given: pass a model path (HF folder, .flm or .gguf)")
     if args.threads and args.threads > 0:

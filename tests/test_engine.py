@@ -480,3 +480,50 @@ def test_candidate_sampling_matches_whole_row_sampling():
     # whole rows are needed for log-probabilities / returned logits / logits processors
     reqs[0].gen.logprobs = 3
     assert eng._candidate_width(reqs) == 0
+
+
+def _mtp_model(identity_layers: bool):
+    from fastllm_b200.models import preset, random_init
+
+    m = random_init(preset("tiny-llama-mtp"), "cpu", torch.float32, seed=3, std=0.05)
+    assert m.mtp is not None and len(m.layers) == 2
+    if identity_layers:
+        # every decoder layer (the draft head's too) adds nothing to the residual stream: the next token then depends on the
+        # current token alone, and a head whose fusion keeps the embedding half predicts exactly what the decoder will say
+        H = m.cfg.hidden_size
+        for lw in list(m.layers) + [m.mtp.layer]:
+            lw.attn.o.w.zero_()
+            lw.mlp.down.w.zero_()
+        m.mtp.fc.w.zero_()
+        m.mtp.fc.w[:, :H] = torch.eye(H)
+    return m
+
+
+@pytest.mark.parametrize("k", [1, 3])
+def test_mtp_speculative_matches_greedy(k):
+    """Drafts from the multi-token-prediction head never change the output: with random head weights (drafts mostly rejected)
+    and chunked prefill, several requests at once, the tokens equal plain greedy decoding."""
+    m = _mtp_model(False)
+    prompts = _prompts(m.cfg.vocab_size, (40, 150, 9))
+    gen = GenerationConfig(max_new_tokens=12, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16).generate(prompts, gen)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, chunked_prefill_size=64, speculative="mtp", speculative_tokens=k),
+                    num_pages=16)
+    out = eng.generate(prompts, gen)
+    assert out == ref
+    assert eng.spec_proposed > 0
+
+
+def test_mtp_head_that_predicts_the_decoder_is_accepted():
+    """With decoder layers that add nothing and a head that keeps the embedding half of its fused input, every draft is what
+    the decoder says next: all drafts are accepted and a step yields speculative_tokens + 1 tokens."""
+    m = _mtp_model(True)
+    prompts = _prompts(m.cfg.vocab_size, (30, 70))
+    gen = GenerationConfig(max_new_tokens=16, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16).generate(prompts, gen)
+    for k in (1, 3):
+        eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, chunked_prefill_size=32, speculative="mtp", speculative_tokens=k),
+                        num_pages=16)
+        assert eng.generate(prompts, gen) == ref
+        assert eng.spec_proposed > 0 and eng.spec_accepted == eng.spec_proposed
+        assert eng.decode_steps <= 2 * (16 // (k + 1) + 2)

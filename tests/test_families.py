@@ -729,3 +729,45 @@ def test_gemma4_text_matches_transformers(variant, tmp_path):
     with torch.no_grad():
         want2 = ref(torch.tensor([prompt + [int(toks[0])]])).logits[0, -1].float()
     assert int(toks[1]) == int(want2.argmax())
+
+
+@pytest.mark.parametrize("naming", ["qwen3_5", "deepseek_v3"])
+def test_mtp_weights_are_loaded(naming, tmp_path):
+    """The multi-token-prediction module of a checkpoint (``mtp.*`` in the Qwen3.5 naming, ``model.layers.<L>.*`` with enorm /
+    hnorm / eh_proj / shared_head in the DeepSeek-V3 naming) becomes the model's draft head; the decoder's logits are untouched."""
+    ref = _tiny("llama", **_C)
+    H, L = 256, 2
+    prompt = list(range(9, 60, 2))
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt])).logits[0, -1].float()
+    torch.manual_seed(4)
+    layer = {k.replace("model.layers.0.", ""): torch.randn_like(v) * 0.05 for k, v in ref.state_dict().items() if k.startswith("model.layers.0.")}
+    fc, ne, nh, nf = torch.randn(H, 2 * H) * 0.05, torch.rand(H) + 0.5, torch.rand(H) + 0.5, torch.rand(H) + 0.5
+
+    def merge(sd):
+        out = dict(sd)
+        if naming == "qwen3_5":
+            out.update({"mtp.fc.weight": fc, "mtp.pre_fc_norm_embedding.weight": ne, "mtp.pre_fc_norm_hidden.weight": nh, "mtp.norm.weight": nf})
+            out.update({"mtp.layers.0." + k: v for k, v in layer.items()})
+        else:
+            p = f"model.layers.{L}."
+            out.update({p + "eh_proj.weight": fc, p + "enorm.weight": ne, p + "hnorm.weight": nh, p + "shared_head.norm.weight": nf,
+                        p + "shared_head.head.weight": sd["lm_head.weight"], p + "embed_tokens.weight": sd["model.embed_tokens.weight"]})
+            out.update({p + k: v for k, v in layer.items()})
+        return out
+
+    key = "mtp_num_hidden_layers" if naming == "qwen3_5" else "num_nextn_predict_layers"
+    d = str(tmp_path / naming)
+    _save_renamed(ref, dict(ref.config.to_dict(), **{key: 1}), lambda k: k, d, merge)
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert m.mtp is not None and len(m.layers) == L and m.mtp.head is None
+    assert torch.equal(m.mtp.fc.w, fc) and torch.equal(m.mtp.norm_e, ne) and torch.equal(m.mtp.norm_h, nh) and torch.equal(m.mtp.final_norm, nf)
+    assert torch.equal(m.mtp.layer.attn.o.w, layer["self_attn.o_proj.weight"])
+    got = _last_logits(m, prompt)
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+    eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512, speculative="mtp", speculative_tokens=2), num_pages=8)
+    from fastllm_b200.engine import GenerationConfig
+
+    a = eng.generate([prompt], GenerationConfig(max_new_tokens=8, ignore_eos=True))[0]
+    b = LLMEngine(m, EngineConfig(max_batch=2, max_context=512), num_pages=8).generate([prompt], GenerationConfig(max_new_tokens=8, ignore_eos=True))[0]
+    assert a == b and eng.spec_proposed > 0
