@@ -391,8 +391,7 @@ class LLMEngine:
 
     # -------------------------------------------------------------------------------- speculative decoding
     def _mtp_on(self) -> bool:
-        return bool(self.cfg.speculative == "mtp" and getattr(self.model, "mtp", None) is not None and self.model.tp.size == 1
-                    and not self.runner.state_slots)
+        return bool(self.cfg.speculative == "mtp" and getattr(self.model, "mtp", None) is not None and self.model.tp.size == 1)
 
     def _mtp_advance(self, items) -> None:
         """Run the draft head over the rows the decoder has just produced: for every position whose following token is known
@@ -495,8 +494,11 @@ class LLMEngine:
                     r.pages.extend(pg)
             chunks.append(([r.all_ids[-1]] + d, r.total_len - 1, r.pages, len(d) + 1, r.state_slot, r.mm))
             owners.append((r, d))
+        # models with recurrent (linear-attention) state: the verification pass advances the state over every draft; where a
+        # draft is rejected the state is put back and rebuilt from the accepted tokens alone
+        snap = self.runner.kv.snapshot_states([r.state_slot for r, _ in owners]) if self.runner.state_slots else None
         logits = self.runner.prefill(chunks, keep_hidden=mtp)
-        mtp_items = []
+        mtp_items, redo = [], []
         if self.model.tp.size > 1:                  # greedy verification: one candidate per rank and row is enough
             if self.control is not None:
                 self.control.gather_logits(1)
@@ -511,6 +513,8 @@ class LLMEngine:
             while n_ok < len(d) and d[n_ok] == mine[n_ok]:
                 n_ok += 1
             mtp_items.append((r, r.total_len - 1, n_ok + 1, row))
+            if snap is not None and n_ok < len(d):
+                redo.append(([r.all_ids[-1]] + d[:n_ok], r.total_len - 1, r.pages, False, r.state_slot, r.mm))
             row += len(d) + 1
             self.spec_proposed += len(d)
             self.spec_accepted += n_ok
@@ -520,6 +524,9 @@ class LLMEngine:
                 produced += self._emit(r, int(t))
             if not r.finished():
                 r.num_computed = r.total_len - 1        # the last emitted token's K/V is written by the next step
+        if redo:
+            self.runner.kv.restore_states(snap, [c[4] for c in redo])
+            self.runner.prefill(redo)
         if mtp:
             self._mtp_advance(mtp_items)
         self.decode_steps += 1
@@ -534,7 +541,7 @@ class LLMEngine:
             return 0
         if self.cfg.speculative == "mtp" and not self._mtp_on():
             self.cfg.speculative = "ngram"          # no draft head with this model: prompt-lookup drafts instead
-        if self.cfg.speculative in ("ngram", "mtp") and not self.runner.state_slots and all(r.gen.is_simple_greedy() for r in reqs):
+        if self.cfg.speculative in ("ngram", "mtp") and all(r.gen.is_simple_greedy() for r in reqs):
             n = self._speculative_step(reqs)
             if n is not None:
                 return n

@@ -132,6 +132,20 @@ class KVCache:
             conv[slot].zero_()
             rec[slot].zero_()
 
+    def snapshot_states(self, slots):
+        """Copies of the linear-attention state (convolution window, recurrent state) of the given request slots, per layer."""
+        idx = torch.tensor(list(slots), dtype=torch.long, device=self.pools[self.linear_layers[0]][0].device) if self.linear_layers else None
+        return [(conv.index_select(0, idx), rec.index_select(0, idx)) for conv, rec in self.linear_pools()], list(slots)
+
+    def restore_states(self, snap, slots) -> None:
+        """Put the snapshot rows of ``slots`` (a subset of the snapshot's slots) back."""
+        saved, order = snap
+        rows = [order.index(s) for s in slots]
+        for (conv, rec), (c0, r0) in zip(self.linear_pools(), saved):
+            for s, j in zip(slots, rows):
+                conv[s].copy_(c0[j])
+                rec[s].copy_(r0[j])
+
     def linear_pools(self):
         return [self.pools[i] for i in self.linear_layers]
 

@@ -527,3 +527,24 @@ def test_mtp_head_that_predicts_the_decoder_is_accepted():
         assert eng.generate(prompts, gen) == ref
         assert eng.spec_proposed > 0 and eng.spec_accepted == eng.spec_proposed
         assert eng.decode_steps <= 2 * (16 // (k + 1) + 2)
+
+
+@pytest.mark.parametrize("algo", ["ngram", "mtp"])
+def test_speculative_decoding_on_a_hybrid_model(algo):
+    """Gated-DeltaNet hybrid: a rejected draft has advanced the recurrent state, which is put back from a snapshot and rebuilt
+    from the accepted tokens -- the output equals plain greedy decoding for prompt-lookup drafts and for the draft head."""
+    import dataclasses
+
+    from fastllm_b200.models import preset, random_init
+
+    cfg = dataclasses.replace(preset("tiny-qwen3-next"), mtp_layers=1)
+    m = random_init(cfg, "cpu", torch.float32, seed=5, std=0.05)
+    assert m.mtp is not None and m.cfg.has_linear_attn
+    base = [3, 9, 4, 7, 11, 5]
+    prompts = [base * 6, _prompts(cfg.vocab_size, (50,))[0]]
+    gen = GenerationConfig(max_new_tokens=14, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16).generate(prompts, gen)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, chunked_prefill_size=32, speculative=algo, speculative_tokens=3),
+                    num_pages=16)
+    assert eng.generate(prompts, gen) == ref
+    assert eng.spec_proposed > 0 and eng.spec_accepted < eng.spec_proposed       # some drafts were rejected and rolled back
