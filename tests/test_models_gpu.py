@@ -10,7 +10,9 @@ pytestmark = pytest.mark.gpu
 
 
 @pytest.mark.parametrize("name,wdtype", [("tiny-llama", "auto"), ("tiny-qwen3", "auto"), ("tiny-qwen3-moe", "auto"), ("tiny-deepseek-v3", "auto"),
-                                         ("tiny-llama", "int8"), ("tiny-qwen3-moe", "int4g128"), ("tiny-qwen3", "fp8")])
+                                         ("tiny-llama", "int8"), ("tiny-qwen3-moe", "int4g128"), ("tiny-qwen3", "fp8"),
+                                         ("tiny-qwen3", "nvfp4"), ("tiny-step3p5", "auto"), ("tiny-laguna", "auto"), ("tiny-hy-v3", "auto"),
+                                         ("tiny-pangu-moe", "auto"), ("tiny-minicpm3", "auto"), ("tiny-moss", "auto")])
 def test_first_tokens_match_cpu_reference(name, wdtype):
     cfg = preset(name)
     g = torch.Generator().manual_seed(2)
@@ -175,3 +177,61 @@ def test_fp8_kv_cache_decodes_on_the_kernel_in_cuda_graphs():
         m.kv8_decode_ok = True
     same = sum(a == b for x, y in zip(o1, o2) for a, b in zip(x, y))
     assert all(x[0] == y[0] for x, y in zip(o1, o2)) and same >= 0.7 * sum(len(x) for x in o1), (o1, o2)
+
+
+def test_mtp_speculative_on_gpu():
+    """Drafts from the multi-token-prediction head on the GPU path (head_dim 128 kernels for the decoder and the head's layer):
+    the output equals plain greedy decoding without CUDA graphs."""
+    import dataclasses
+
+    cfg = dataclasses.replace(preset("tiny-qwen3"), mtp_layers=1)
+    m = random_init(cfg, "cuda", torch.bfloat16, std=0.05)
+    assert m.mtp is not None
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 150)]
+    gen = GenerationConfig(max_new_tokens=10, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, use_cuda_graph=False), num_pages=32).generate(prompts, gen)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, speculative="mtp", speculative_tokens=2), num_pages=32)
+    out = eng.generate(prompts, gen)
+    _lib.check_device_errors()
+    assert eng.spec_proposed > 0
+    same = sum(a == b for o, o2 in zip(out, ref) for a, b in zip(o, o2))
+    assert same >= 0.8 * sum(len(o) for o in ref), (out, ref)          # bf16 near-ties may fall differently with other batch shapes
+
+
+def test_image_prompt_on_gpu():
+    """Image-token embeddings and (time, row, column) rotary rows through the GPU prefill kernels (per-token tables indexed by
+    row) agree with the same model evaluated on the CPU in fp32."""
+    from fastllm_b200.engine.engine import MultimodalContext
+    from fastllm_b200.models import vision as V
+
+    cfg = preset("tiny-qwen3")
+    cfg.raw["rope_parameters"] = {"mrope_section": [24, 20, 20]}
+    mg = random_init(cfg, "cuda", torch.bfloat16, std=0.05, seed=7)
+    ids = [5, 6, 7] + [9] * 12 + [8, 10, 11, 12]
+    pos3, delta = V.mrope_positions(ids, 9, [(1, 6, 8)], 2)
+    emb = torch.randn(12, cfg.hidden_size, generator=torch.Generator().manual_seed(1)) * 0.05
+    at = [i for i, t in enumerate(ids) if t == 9]
+    outs = []
+    for dev, dt in (("cuda", torch.bfloat16), ("cpu", torch.float32)):
+        m = mg if dev == "cuda" else random_init(cfg, "cpu", torch.float32, std=0.05, seed=7)
+        if dev == "cpu":          # same weights as the GPU model (its generator differs)
+            for a, b in zip(m.layers, mg.layers):
+                for x, y in ((a.attn.qkv, b.attn.qkv), (a.attn.o, b.attn.o), (a.mlp.gate_up, b.mlp.gate_up), (a.mlp.down, b.mlp.down)):
+                    w = y.w.float().cpu()
+                    if y.interleaved and not x.interleaved:
+                        n = w.shape[0]
+                        t_ = w.reshape(n // 128, 2, 64, -1)
+                        w = torch.cat([t_[:, 0].reshape(n // 2, -1), t_[:, 1].reshape(n // 2, -1)], dim=0)
+                    x.w.copy_(w)
+                for nm in ("ln", "q_norm", "k_norm"):
+                    getattr(a.attn, nm).copy_(getattr(b.attn, nm).float().cpu())
+                a.mlp.ln.copy_(b.mlp.ln.float().cpu())
+            m.embed.copy_(mg.embed.float().cpu())
+            m.final_norm.copy_(mg.final_norm.float().cpu())
+        eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512, use_cuda_graph=False), num_pages=8)
+        mm = MultimodalContext(emb.to(dev, dt), at, pos3, delta)
+        outs.append(eng.runner.prefill([(ids, 0, [0, 1], True, 0, mm)])[0].float().cpu())
+    _lib.check_device_errors()
+    cs = torch.nn.functional.cosine_similarity(outs[0], outs[1], dim=0).item()
+    assert cs > 0.995, cs
