@@ -478,6 +478,20 @@ def attn_prefill(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_head
     """Packed causal prefill (also chunked prefill / prefix-cache continuation). q: ``[T, Hq*D]``."""
     if cpu_native(q) and k_pool.dtype == torch.float32:
         return cpu.attention_paged(q, k_pool, v_pool, page_table, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim)
+    if (q.is_cuda and k_pool.dtype == torch.float8_e4m3fn and head_dim == 128 and k_pool.shape[1] == PAGE_LEN
+            and q.dtype in (torch.float16, torch.bfloat16)):
+        # e4m3 pages: the pages this batch reads are brought into a scratch pool in the activations' type (exact conversion)
+        # and the tensor-core prefill kernel runs on that pool through a re-indexed page table.  Prefill is bound by its
+        # MMAs, the conversion reads every context byte once.
+        P = page_table.shape[1]
+        npg = ((kv_lens.to(torch.long) + PAGE_LEN - 1) // PAGE_LEN).clamp(max=P)
+        mask = torch.arange(P, device=q.device)[None, :] < npg[:, None]
+        used = page_table[mask].long()
+        pt = torch.zeros_like(page_table)
+        pt[mask] = torch.arange(used.numel(), device=q.device, dtype=page_table.dtype)
+        kt = k_pool.index_select(0, used).to(q.dtype)
+        vt = v_pool.index_select(0, used).to(q.dtype)
+        return attn_prefill(q, kt, vt, pt, kv_lens, cu_q, scale, num_q_heads, num_kv_heads, head_dim, out, cu_q_host)
     if not q.is_cuda or head_dim != 128 or k_pool.shape[1] != PAGE_LEN:
         o = paged_attention_ref(q, k_pool, v_pool, page_table, kv_lens.cpu(), cu_q.cpu(), scale, num_q_heads, num_kv_heads,
                                 head_dim)

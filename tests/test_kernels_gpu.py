@@ -480,6 +480,38 @@ def test_attn_decode_fp8_kv(Hq, Hkv, dt, mma8, monkeypatch):
     _close(out2.float().cpu(), ref2.float(), 2e-2, 2e-2, "attn_decode kv8 window", fro=8e-3)
 
 
+def test_attn_prefill_fp8_kv():
+    """Chunked prefill over e4m3 page pools (the pages a batch reads are de-quantised into a scratch pool for the tensor-core
+    prefill kernel) vs the PyTorch evaluation on the same e4m3 values."""
+    torch.manual_seed(22)
+    Hq, Hkv, D, dt = 8, 2, 128, torch.bfloat16
+    new = [5, 130, 64, 300]
+    ctx = [5, 130, 200, 700]
+    Bn = len(new)
+    n_pages = sum((l + 127) // 128 for l in ctx) + 2
+    max_p = max((l + 127) // 128 for l in ctx)
+    pt = torch.zeros(Bn, max_p, dtype=torch.int32)
+    perm = torch.randperm(n_pages)
+    c = 0
+    k8 = torch.zeros(n_pages, 128, Hkv, D, dtype=torch.float8_e4m3fn)
+    v8 = torch.zeros(n_pages, 128, Hkv, D, dtype=torch.float8_e4m3fn)
+    for b, l in enumerate(ctx):
+        n = (l + 127) // 128
+        pt[b, :n] = perm[c:c + n].int()
+        c += n
+        for i in range(n):
+            k = min(128, l - i * 128)
+            k8[pt[b, i], :k] = (torch.randn(k, Hkv, D) * 0.7).to(torch.float8_e4m3fn)
+            v8[pt[b, i], :k] = torch.randn(k, Hkv, D).to(torch.float8_e4m3fn)
+    cu = torch.tensor([0] + list(torch.tensor(new).cumsum(0)), dtype=torch.int32)
+    q = (torch.randn(sum(new), Hq * D) * 0.7).to(dt)
+    seq = torch.tensor(ctx, dtype=torch.int32)
+    ref = A.paged_attention_general(q.float(), k8.float(), v8.float(), pt, seq, cu, D ** -0.5, Hq, Hkv, D)
+    out = A.attn_prefill(q.to(DEV), k8.to(DEV), v8.to(DEV), pt.to(DEV), seq.to(DEV), cu.to(DEV), D ** -0.5, Hq, Hkv, D,
+                         cu_q_host=cu.tolist())
+    _close(out.float().cpu(), ref.float(), 2e-2, 2e-2, "attn_prefill kv8", fro=8e-3)
+
+
 def test_mla_prefill_on_gemm_kernels():
     """Absorbed MLA prefill (heads folded into GEMM rows, both contractions on the tensor-core GEMM kernels, chunked prefill
     with earlier context) vs the fp32 evaluation."""

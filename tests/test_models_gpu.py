@@ -163,7 +163,8 @@ def test_fp8_kv_cache_decodes_on_the_kernel_in_cuda_graphs():
     assert m.kv8_decode_ok
     prompts = [list(range(5, 5 + n)) for n in (150, 37, 260)]
     gen = GenerationConfig(max_new_tokens=10, ignore_eos=True)
-    e1 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16)
+    # (chunks of 128 tokens: the later chunks of a prompt attend to e4m3 pages written by the earlier ones)
+    e1 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, chunked_prefill_size=128), num_pages=16)
     assert e1.runner.graph_ok and e1.runner.kv.pools[0][0].dtype == torch.float8_e4m3fn
     o1 = e1.generate(prompts, gen)
     assert any(s.graph is not None for s in e1.runner.slots.values())
