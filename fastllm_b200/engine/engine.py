@@ -391,14 +391,13 @@ class LLMEngine:
 
     # -------------------------------------------------------------------------------- speculative decoding
     def _mtp_on(self) -> bool:
-        return bool(self.cfg.speculative == "mtp" and getattr(self.model, "mtp", None) is not None and self.model.tp.size == 1)
+        return bool(self.cfg.speculative == "mtp" and getattr(self.model, "mtp", None) is not None)
 
     def _mtp_advance(self, items) -> None:
         """Run the draft head over the rows the decoder has just produced: for every position whose following token is known
         it appends that position to the head's own KV pages; the row of a decoding request's newest token pair yields the
         first draft, further drafts chain the head on its own output (their pages are written again once the true rows
         arrive).  ``items``: (request, first position, rows, first row in ``model.last_hidden``)."""
-        hidden = self.model.last_hidden
         chunks, sel, heads = [], [], []
         for r, start, n, off in items:
             r.mtp_drafts = []
@@ -415,33 +414,39 @@ class LLMEngine:
                 heads.append((r, start + avail - 1, len(sel) - 1))
         if not chunks:
             return
-        idx = torch.tensor(sel, dtype=torch.long, device=hidden.device)
-        logits, x = self.runner.prefill(chunks, mtp_hidden=hidden.index_select(0, idx))
+        logits = self.runner.mtp_pass(chunks, sel, 0)
         if not heads:
             return
-        toks = sampling.greedy(logits).tolist()
         live = []
-        for (r, pos, row), t in zip(heads, toks):
+        for (r, pos, row), t in zip(heads, self._greedy_rows(logits)):
             r.mtp_drafts = [int(t)]
-            live.append((r, pos, x[row:row + 1]))
+            live.append((r, pos, row))
         for _ in range(1, self.cfg.speculative_tokens):
-            chunks, hs, nxt = [], [], []
-            for r, pos, h in live:
+            chunks, rows, nxt = [], [], []
+            for r, pos, row in live:
                 pos += 1
                 need = self._pages_needed(pos + 1) - len(r.pages)
                 if pos + 2 >= self.cfg.max_context or (need > 0 and not self._grow_pages(r, need)):
                     continue
                 chunks.append(([r.mtp_drafts[-1]], pos, r.pages, True, r.state_slot, r.mm))
-                hs.append(h)
+                rows.append(row)
                 nxt.append((r, pos))
             if not chunks:
                 break
-            logits, x = self.runner.prefill(chunks, mtp_hidden=torch.cat(hs, dim=0))
-            toks = sampling.greedy(logits).tolist()
+            logits = self.runner.mtp_pass(chunks, rows, 1)           # the head's own rows of the pass before
             live = []
-            for i, ((r, pos), t) in enumerate(zip(nxt, toks)):
+            for i, ((r, pos), t) in enumerate(zip(nxt, self._greedy_rows(logits))):
                 r.mtp_drafts.append(int(t))
-                live.append((r, pos, x[i:i + 1]))
+                live.append((r, pos, i))
+
+    def _greedy_rows(self, logits) -> list:
+        """Arg-max token of every row; with a sharded vocabulary the ranks exchange their best candidate per row."""
+        if self.model.tp.size > 1:
+            if self.control is not None:
+                self.control.gather_logits(1)
+            vals, ids = self.model.tp.comm.gather_candidates(logits, self.model.vocab_shard, 1)
+            return ids.gather(1, vals.argmax(dim=-1, keepdim=True)).view(-1).tolist()
+        return sampling.greedy(logits).tolist()
 
     def _grow_pages(self, r, need: int) -> bool:
         pg = self.pm.alloc(need)

@@ -148,7 +148,7 @@ class ModelRunner:
         them).  ``mtp_hidden``: run the draft head instead of the decoder -- the chunks then hold, per position, the token that
         FOLLOWS it, ``mtp_hidden`` the matching hidden rows; returns (logits, the head's final-normed rows)."""
         if self.control is not None and mtp_hidden is None:
-            self.control.prefill(chunks)
+            self.control.prefill(chunks, keep_hidden)
         dev = self.device
         ids, pos, slots, cu, kv_lens, rows = [], [], [], [0], [], []
         P = self.max_pages
@@ -212,6 +212,18 @@ class ModelRunner:
         logits = self.model.forward(fb, self.kv.pools)
         self.steps += 1
         return logits if rows else None
+
+    def mtp_pass(self, chunks, sel, src: int):
+        """One pass of the draft head over ``chunks`` (per position, the token that follows it); its hidden input rows are rows
+        ``sel`` of the decoder's last kept pass (``src`` 0) or of the head's own last pass (``src`` 1: chained drafts).  Worker
+        ranks replay the same call from the published plan.  Returns the logits of the rows that asked for them."""
+        if self.control is not None:
+            self.control.mtp(chunks, sel, src)
+        base = self.model.last_hidden if src == 0 else self._mtp_x
+        idx = torch.tensor(list(sel), dtype=torch.long, device=base.device)
+        logits, x = self.prefill(chunks, mtp_hidden=base.index_select(0, idx))
+        self._mtp_x = x
+        return logits
 
     # ---------------------------------------------------------------------------------------------
     def _bucket(self, n: int) -> int:

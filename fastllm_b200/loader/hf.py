@@ -328,7 +328,7 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
         m.wdtype_for = lambda name: resolve_wdtype(name, base_w, dtype_config)
         m.moe_wdtype_for = lambda name: resolve_wdtype(name, base_m or base_w, dtype_config)
     finalize_model(m, top_fn, layer_fn, wdtype=wdtype, moe_wdtype=moe_wdtype)
-    if cfg.mtp_layers and (tp is None or tp.size == 1) and not staged_devices(m):
+    if cfg.mtp_layers and not staged_devices(m):
         from .shard import build_mtp
 
         L = cfg.num_layers

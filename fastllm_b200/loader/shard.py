@@ -354,7 +354,7 @@ def build_mtp(m, t: dict, wdtype="dense", moe_wdtype=None):
     mt.final_norm = _to(t.pop(p + "shared_head.norm.weight"), m)
     hw = t.pop(p + "shared_head.head.weight", None)
     t.pop(p + "embed_tokens.weight", None)                       # a copy of the model's table
-    if hw is not None and m.lm_head is not None and tuple(hw.shape) == (m.lm_head.n, m.lm_head.k) and not m.cfg.tie_embeddings:
+    if hw is not None and m.tp.size == 1 and m.lm_head is not None and tuple(hw.shape) == (m.lm_head.n, m.lm_head.k) and not m.cfg.tie_embeddings:
         same = m.lm_head.kind == "dense" and torch.equal(_to(hw, m), m.lm_head.w)
         mt.head = None if same else _lin(m, hw, "dense")
     build_layer(m, L, t, wdtype, moe_wdtype)

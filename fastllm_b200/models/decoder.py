@@ -945,7 +945,7 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
         return raw
 
     finalize_model(m, top_tensors, layer_tensors, wdtype=wdtype, moe_wdtype=moe_wdtype)
-    if cfg.mtp_layers and (tp is None or tp.size == 1):
+    if cfg.mtp_layers:
         from ..loader.shard import build_mtp
 
         L = cfg.num_layers

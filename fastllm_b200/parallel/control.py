@@ -28,7 +28,7 @@ import numpy as np
 
 from ..ops import _lib
 
-KIND_STOP, KIND_DECODE, KIND_PREFILL, KIND_GATHER, KIND_RESET, KIND_CALL = 0, 1, 2, 3, 4, 5
+KIND_STOP, KIND_DECODE, KIND_PREFILL, KIND_GATHER, KIND_RESET, KIND_CALL, KIND_PREFILL_KEEP, KIND_MTP = 0, 1, 2, 3, 4, 5, 6, 7
 CONT = 0x100                    # this message continues in the next one (payload larger than a slot)
 OK, TIMEOUT, CLOSED, TOO_BIG, BAD, OVERRUN = range(6)
 
@@ -225,8 +225,16 @@ class ControlPlane:
         self.ring.publish(KIND_DECODE, encode_decode_plan(n, bsz, want_logits, meta_np))
         self.published += 1
 
-    def prefill(self, chunks):
-        self.ring.publish(KIND_PREFILL, encode_prefill_plan(chunks))
+    def prefill(self, chunks, keep_hidden: bool = False):
+        self.ring.publish(KIND_PREFILL_KEEP if keep_hidden else KIND_PREFILL, encode_prefill_plan(chunks))
+        self.published += 1
+
+    def mtp(self, chunks, sel, src: int):
+        """A pass of the draft head: the plan of its chunks, then which rows of the stored hidden rows feed it (``src`` 0: the
+        decoder's last pass, 1: the head's own last pass)."""
+        plan = encode_prefill_plan(chunks)
+        tail = np.asarray([int(src), len(sel)] + [int(i) for i in sel], dtype=np.int32)
+        self.ring.publish(KIND_MTP, np.concatenate([np.asarray([plan.size], dtype=np.int32), plan, tail]))
         self.published += 1
 
     def gather_logits(self, k: int = 0):
@@ -312,8 +320,14 @@ class WorkerLoop:
                         self.timing.append(ev)
                     self.last_logits = logits
                     self.steps += 1
-                elif kind == KIND_PREFILL:
-                    self.last_logits = self.runner.prefill(decode_prefill_plan(buf))
+                elif kind in (KIND_PREFILL, KIND_PREFILL_KEEP):
+                    self.last_logits = self.runner.prefill(decode_prefill_plan(buf), keep_hidden=kind == KIND_PREFILL_KEEP)
+                    self.steps += 1
+                elif kind == KIND_MTP:
+                    a = buf.view(np.int32)
+                    n = int(a[0])
+                    tail = a[1 + n:]
+                    self.last_logits = self.runner.mtp_pass(decode_prefill_plan(a[1:1 + n]), tail[2:2 + int(tail[1])].tolist(), int(tail[0]))
                     self.steps += 1
                 elif kind == KIND_GATHER:
                     k = int.from_bytes(bytes(buf[:4]), "little") if len(buf) >= 4 else 0

@@ -194,3 +194,47 @@ def test_server_command_with_tp_streams_a_chat_completion(tmp_path):
     d = synth.write_model("tiny-llama", str(tmp_path / "m"), dtype=torch.float32, std=0.05)
     chunks, finish = run_server_and_stream(d, ["--device", "cpu", "--tp", "2", "--dtype", "float32"])
     assert finish in ("length", "stop") and len(chunks) >= 1
+
+
+_SPEC_MTP = {"kind": "preset", "model": "tiny-llama-mtp", "dtype": "float32", "std": 0.05, "seed": 0, "num_pages": 12,
+             "engine": {"max_batch": 4, "max_context": 512, "prefix_cache": False, "chunked_prefill_size": 64,
+                        "speculative": "mtp", "speculative_tokens": 2}}
+
+
+def _mtp_prompts(vocab):
+    g = torch.Generator().manual_seed(11)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in (70, 33)]
+
+
+def _rank0_mtp(q):
+    from fastllm_b200.engine import GenerationConfig
+    from fastllm_b200.parallel.launcher import TPGroup
+
+    group, eng, _ = TPGroup.launch(_SPEC_MTP, ["cpu", "cpu"])
+    try:
+        assert eng.model.tp.size == 2 and eng.model.mtp is not None
+        out = eng.generate(_mtp_prompts(eng.model.cfg.vocab_size), GenerationConfig(max_new_tokens=12, ignore_eos=True))
+        q.put((out, eng.spec_proposed))
+    finally:
+        group.shutdown()
+    assert all(p.returncode == 0 for p in group.procs)
+
+
+def test_control_plane_carries_the_draft_head_passes():
+    """Drafts from the multi-token-prediction head under tensor parallelism: the worker rank replays the decoder passes (keeping
+    their hidden rows), the head's passes and the candidate exchanges from the published plans; tokens equal one rank's greedy
+    output."""
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.models import preset, random_init
+
+    m = random_init(preset("tiny-llama-mtp"), "cpu", torch.float32, std=0.05, seed=0)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=12).generate(
+        _mtp_prompts(m.cfg.vocab_size), GenerationConfig(max_new_tokens=12, ignore_eos=True))
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_rank0_mtp, args=(q,))
+    p.start()
+    out, proposed = q.get(timeout=300)
+    p.join(timeout=60)
+    assert p.exitcode == 0
+    assert out == ref and proposed > 0
