@@ -8,6 +8,7 @@ b[k]) -> y[n,k]`` with weights stored ``[out, in]`` row-major.
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 import torch.nn.functional as F
@@ -128,6 +129,22 @@ def _take_pending_wait():
     return w
 
 
+F32_SPLIT = os.environ.get("FB_F32_SPLIT", "1") != "0"
+_F32_PARTS: dict = {}
+
+
+def _f32_split(w: torch.Tensor):
+    """(bf16 head, bf16 remainder) of an fp32 weight, built once per weight tensor."""
+    key = (w.data_ptr(), tuple(w.shape), w._version)
+    p = _F32_PARTS.get(key)
+    if p is None:
+        if len(_F32_PARTS) > 4096:
+            _F32_PARTS.clear()
+        wh = w.to(torch.bfloat16)
+        p = _F32_PARTS[key] = (wh, (w - wh.float()).to(torch.bfloat16))
+    return p
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: bool = False, interleaved: bool = True,
            out_f32: bool = False, out: torch.Tensor | None = None, nsplit: int = 0) -> torch.Tensor:
     """``y = x @ w.T`` with optional fused bias, SwiGLU (``w`` = gate/up stacked) and residual add.
@@ -147,6 +164,26 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias=None, residual=None, swiglu: b
         x2 = x2.contiguous()
     M, K = x2.shape
     N = w.shape[0]
+    if (x.dtype == torch.float32 and w.dtype == torch.float32 and K % 64 == 0 and N % 8 == 0 and F32_SPLIT and out is None
+            and w.is_contiguous()):
+        # fp32 activations and weights on the tensor core: both operands are split into a bf16 head and a bf16 remainder
+        # (x = xh + xl with 16 mantissa bits between them) and y = xh wh' + xh wl' + xl wh' runs as three bf16 GEMMs with fp32
+        # accumulation; the dropped xl wl' term is 2^-16 relative, far below TF32's 2^-11 operand rounding
+        # (reference: a CUDA-core fp32 GEMV / cuBLAS SGEMM, src/devices/cuda/linear/fastllm-linear-fp32.cu:11)
+        flush_pending_wait()
+        wh, wl = _f32_split(w)
+        xh = x2.to(torch.bfloat16)
+        xl = (x2 - xh.float()).to(torch.bfloat16)
+        y = linear(xh, wh, out_f32=True)
+        y += linear(xh, wl, out_f32=True)
+        y += linear(xl, wh, out_f32=True)
+        if bias is not None:
+            y += bias.float()
+        if swiglu:
+            y = glu_act_ref(y, "silu", interleaved)
+        if residual is not None:
+            y += residual.reshape(-1, residual.shape[-1]).float()
+        return y.reshape(*lead, y.shape[-1])
     if K % 64 != 0 or N % 8 != 0 or x.dtype not in (torch.float16, torch.bfloat16) or (x2.data_ptr() & 15) or (x2.stride(0) * 2) % 16:
         # shapes outside the tensor-core kernels' tiling (rare: odd projection widths): plain PyTorch definition
         flush_pending_wait()

@@ -77,6 +77,24 @@ def test_gemm_large_m(M, N, K):
         _close(B.linear(x, w, swiglu=True), B.linear_ref(x, w, swiglu=True), 3e-2, 3e-2, "swiglu")
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 512, 1024), (70, 1024, 512), (600, 256, 2048)])
+def test_linear_fp32_on_split_bf16_operands(M, N, K):
+    """fp32 activations x fp32 weights as three bf16 tensor-core GEMMs over (head, remainder) splits: the error against an fp64
+    evaluation stays at fp32-matmul level, two orders of magnitude below a single bf16 GEMM."""
+    torch.manual_seed(30)
+    x = torch.randn(M, K, device=DEV)
+    w = torch.randn(N, K, device=DEV) * 0.05
+    bias = torch.randn(N, device=DEV)
+    res = torch.randn(M, N, device=DEV)
+    ref = (x.double() @ w.double().t() + bias.double() + res.double())
+    y = B.linear(x, w, bias, res)
+    assert y.dtype == torch.float32
+    rel = ((y.double() - ref).norm() / ref.norm()).item()
+    one = B.linear(x.bfloat16(), w.bfloat16(), out_f32=True).double() + bias.double() + res.double()
+    rel_bf16 = ((one - ref).norm() / ref.norm()).item()
+    assert rel < 2e-5 and rel < rel_bf16 / 50, (rel, rel_bf16)
+
+
 def test_interleave_roundtrip():
     g, u = torch.randn(256, 8), torch.randn(256, 8)
     w = B.interleave_gate_up(g, u)
