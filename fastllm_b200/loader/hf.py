@@ -167,7 +167,9 @@ class HFCheckpoint:
                 return dequant_nvfp4(w, self.raw(prefix + ".weight_scale"), g2, self.dtype)
             return w
         if self.has(prefix + ".qweight"):
-            return dequant_awq(self.raw(prefix + ".qweight"), self.raw(prefix + ".qzeros"), self.raw(prefix + ".scales"), self.dtype)
+            # (fp32 when the run-time format is 4-bit group-wise: the quantiser then recovers the checkpoint's own grid)
+            return dequant_awq(self.raw(prefix + ".qweight"), self.raw(prefix + ".qzeros"), self.raw(prefix + ".scales"),
+                               torch.float32 if getattr(self, "keep_f32_4bit", False) else self.dtype)
         return None
 
     def attach_lora(self, adapter_dir: str | Path) -> int:
@@ -286,6 +288,7 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
             wdtype = "fp8"
         elif method in ("awq", "gptq", "compressed-tensors"):
             wdtype = f"int4g{q.get('group_size', 128)}"
+    ck.keep_f32_4bit = str(wdtype).startswith("int4")
     if device_map:
         from .shard import split_layers_by_map
 

@@ -61,17 +61,25 @@ class _HostPlacement:
         self.on_cuda = False
 
 
+def _q_src(w, m, wdtype):
+    """Weight on the model's device; an fp32 source that is about to be quantised keeps its precision (4-bit checkpoints
+    de-quantised in fp32 get their own grid back from the group-wise quantiser)."""
+    if w is not None and w.dtype == torch.float32 and normalize_wdtype(wdtype)[0] == "int4g":
+        return w.to(m.device).contiguous()
+    return _to(w, m)
+
+
 def _lin(m, w, wdtype, bias=None, interleaved=False):
-    return LinearWeight.from_dense(_to(w, m), wdtype, _to(bias, m), interleaved, act_dtype=m.dtype)
+    return LinearWeight.from_dense(_q_src(w, m, wdtype), wdtype, _to(bias, m), interleaved, act_dtype=m.dtype)
 
 
 def _gate_up(m, gate, up, wdtype, bias_g=None, bias_u=None):
     """Merge gate and up into the tile-interleaved layout (CUDA) or plain stacking (CPU)."""
     if m.on_cuda and gate.shape[0] % 64 == 0:
-        w = B.interleave_gate_up(_to(gate, m), _to(up, m))
+        w = B.interleave_gate_up(_q_src(gate, m, wdtype), _q_src(up, m, wdtype))
         b = B.interleave_gate_up(_to(bias_g, m), _to(bias_u, m)) if bias_g is not None else None
         return LinearWeight.from_dense(w, wdtype, b, True, act_dtype=m.dtype)
-    w = torch.cat([_to(gate, m), _to(up, m)], dim=0)
+    w = torch.cat([_q_src(gate, m, wdtype), _q_src(up, m, wdtype)], dim=0)
     b = torch.cat([_to(bias_g, m), _to(bias_u, m)]) if bias_g is not None else None
     return LinearWeight.from_dense(w, wdtype, b, False, act_dtype=m.dtype)
 

@@ -39,6 +39,9 @@ def dequantize_int8(q, scale, zero, dtype):
 
 
 def quantize_int4g(w: torch.Tensor, group: int = 128):
+    """Group-wise asymmetric 4-bit: ``w = min + scale * q``, q in 0..15.  Groups whose values already lie on a 16-point grid
+    (weights that come out of a 4-bit checkpoint, e.g. AWQ ``(q - zero) * scale`` kept in fp32) get that grid back exactly --
+    its step is found from the smallest gap between the group's distinct values -- instead of a new min / max grid."""
     n, k = w.shape
     if k % group != 0:
         raise ValueError(f"in-features {k} not divisible by group {group}")
@@ -46,6 +49,19 @@ def quantize_int4g(w: torch.Tensor, group: int = 128):
     mn = wf.amin(dim=2, keepdim=True)
     mx = wf.amax(dim=2, keepdim=True)
     scale = ((mx - mn) / 15.0).clamp(min=1e-12)
+    if w.dtype == torch.float32:
+        rng = (mx - mn).clamp(min=1e-30)
+        srt = wf.sort(dim=2).values
+        gap = srt[..., 1:] - srt[..., :-1]
+        gmin = torch.where(gap > rng * 1e-4, gap, torch.full_like(gap, float("inf"))).amin(dim=2, keepdim=True)
+        k0 = (wf - mn) / scale
+        found = (k0 - k0.round()).abs().amax(dim=2, keepdim=True) < 2e-3          # the min / max grid is already exact
+        for m_ in (1, 2, 3, 4, 5, 6, 7):        # the smallest gap is m steps when neighbouring codes are unused
+            s_ = gmin / m_
+            kk = (wf - mn) / s_
+            ok = torch.isfinite(s_) & ((kk - kk.round()).abs().amax(dim=2, keepdim=True) < 2e-3) & (kk.amax(dim=2, keepdim=True) < 15.5) & ~found
+            scale = torch.where(ok, s_, scale)
+            found |= ok
     q = torch.round((wf - mn) / scale).clamp(0, 15).to(torch.uint8).reshape(n, k)
     packed = (q[:, 0::2] << 4) | q[:, 1::2]
     return packed.contiguous(), scale.squeeze(2).contiguous(), mn.squeeze(2).contiguous()

@@ -286,3 +286,34 @@ def test_fp4_quantiser_roundtrip():
     # values halfway between two grid points go to the even code
     codes = quant._fp4_codes(torch.tensor([0.25, 0.75, 1.25, 2.5, 5.0, -2.5]))
     assert codes.tolist() == [0, 2, 2, 4, 6, 12]
+
+
+def test_awq_weights_keep_their_grid():
+    """AWQ ``(q - zero) * scale`` weights, de-quantised in fp32, come back from the group-wise 4-bit quantiser on their own
+    grid: the run-time weight de-quantises to exactly the checkpoint's values, also for groups that use only a few codes and
+    after rows of several matrices are concatenated."""
+    import torch
+
+    from fastllm_b200.loader import hf
+    from fastllm_b200.ops import quant
+
+    torch.manual_seed(0)
+    K, N, g = 256, 64, 128
+    q = torch.randint(0, 16, (K, N))
+    q[:g, 0] = torch.randint(3, 6, (g,))                     # a group that uses three neighbouring codes
+    q[:g, 1] = torch.tensor([2, 9])[torch.randint(0, 2, (g,))]   # ... and one with a gap of seven steps
+    z = torch.randint(0, 16, (K // g, N))
+    sc = (torch.rand(K // g, N) * 0.02 + 0.001).half()
+    order = hf._AWQ_ORDER
+    pack = lambda t: sum((t[:, i::8].to(torch.int64) << (4 * order[i])) for i in range(8)).to(torch.int32)
+    qweight, qzeros = pack(q), pack(z)
+    dense = hf.dequant_awq(qweight, qzeros, sc, torch.float32)
+    want = ((q.float() - z.float().repeat_interleave(g, 0)) * sc.float().repeat_interleave(g, 0)).t()
+    assert torch.equal(dense, want)
+    lw = quant.LinearWeight.from_dense(dense, "int4g128", act_dtype=torch.bfloat16)
+    assert lw.kind == "int4g" and torch.allclose(lw.dequant(torch.float32), want, rtol=0, atol=1e-7)
+    both = quant.LinearWeight.from_dense(torch.cat([dense, dense.flip(0)], dim=0), "int4g128", act_dtype=torch.bfloat16)
+    assert torch.allclose(both.dequant(torch.float32), torch.cat([want, want.flip(0)], dim=0), rtol=0, atol=1e-7)
+    # the same values rounded to bf16 first no longer sit on a grid: the min / max quantiser takes over (small error, not exact)
+    lossy = quant.LinearWeight.from_dense(dense.bfloat16(), "int4g128")
+    assert (lossy.dequant(torch.float32) - want).abs().max() > 0
