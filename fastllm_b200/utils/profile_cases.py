@@ -154,7 +154,7 @@ def moe_ep_rank(model="deepseek-v3", tokens=32, ranks=8, kind="int4g128", iters=
           f"{int(local.sum())} local rows on {hit} of {exs[0].count} local experts; {hit * per / 1e6:.0f} MB of expert weights touched")
 
 
-def attn_decode_kv8(batch=64, length=1100, hq=32, hkv=8, iters=10):
+def attn_decode_kv8(batch=64, length=1100, hq=32, hkv=8, iters=10, only_e4m3=False):
     """Decode attention over bf16 and over e4m3 page pools, device time per call (CUDA events around a CUDA graph)."""
     from ..ops import attention as A
 
@@ -167,6 +167,8 @@ def attn_decode_kv8(batch=64, length=1100, hq=32, hkv=8, iters=10):
     k16 = (torch.randn(pages, 128, hkv, D, device="cuda") * 0.5).bfloat16()
     v16 = torch.randn(pages, 128, hkv, D, device="cuda").bfloat16()
     for name, (kp, vp) in (("bf16 pages", (k16, v16)), ("e4m3 pages", (k16.to(torch.float8_e4m3fn), v16.to(torch.float8_e4m3fn)))):
+        if only_e4m3 and name.startswith("bf16"):
+            continue
         ws = A.DecodeWorkspace(batch, hkv, hq // hkv, npg, "cuda")
         for _ in range(3):
             A.attn_decode(q, kp, vp, pt, seq, D ** -0.5, hq, hkv, D, ws=ws)
@@ -223,6 +225,7 @@ def gdn_decode(batch=64, hk=16, hv=32, iters=4):
 CASES = {
     "gemm_qkv_post": gemm_qkv_post,
     "attn_decode_kv8": attn_decode_kv8,
+    "attn_decode_kv8_only": lambda: attn_decode_kv8(iters=2, only_e4m3=True),
     "moe_ep_rank_dsv3_int4g": lambda: moe_ep_rank("deepseek-v3", 32, 8, "int4g128"),
     "moe_ep_rank_dsv3_int4g_untimed": lambda: moe_ep_rank("deepseek-v3", 32, 8, "int4g128", timed=False),
     "moe_ep_rank_dsv3_fp8": lambda: moe_ep_rank("deepseek-v3", 32, 8, "fp8"),
