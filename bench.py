@@ -243,8 +243,8 @@ def run_ours(args):
 
 
 def _vs_baseline(args, world, value):
-    """value / the reference's measured number for the same configuration and GPU count (baseline/measured_reference.json,
-    the table of BASELINE.md); None when that configuration has no reference measurement."""
+    """value / the reference's measured number for the same configuration and GPU count (baseline/measured_reference.json);
+    None when that configuration has no reference measurement."""
     try:
         table = json.load(open(os.path.join(ROOT, "baseline", "measured_reference.json")))
     except OSError:
