@@ -99,11 +99,11 @@ class LLMEngine:
         req = Request(prompt_ids, gen or GenerationConfig(), handle)
         limit = self.cfg.max_context
         if mm is not None:
-            if self.model.tp.size > 1:
-                raise NotImplementedError("image inputs run on one rank")
             if len(req.prompt_ids) >= limit:
                 raise ValueError("the prompt with its image tokens does not fit max_context")
             req.mm = mm
+            mm.ctx_id = req.handle
+            mm.sent = False
         if len(req.prompt_ids) >= limit:
             req.prompt_ids = req.prompt_ids[-(limit - 1):]
         if not req.prompt_ids:
@@ -249,6 +249,11 @@ class LLMEngine:
             r.num_computed = len(cached) * self.page_len
             r.num_cached_prefix = r.num_computed
             r.stats.cached_tokens = r.num_computed
+            if r.mm is not None and self.control is not None and not r.mm.sent:
+                # (published from the scheduling thread, like every other plan) the worker ranks get the image tokens'
+                # embeddings and rotary positions before the request's first chunk
+                self.control.mm_put(r.mm)
+                r.mm.sent = True
             r.state = RequestState.PREFILL
             self.running.append(r)
         if keep:
@@ -268,6 +273,8 @@ class LLMEngine:
             self.pm.release(r.pages)
             r.pages = []
         self._release_state(r)
+        if r.mm is not None and self.control is not None and getattr(r.mm, "sent", False):
+            self.control.mm_drop(r.mm.ctx_id)
         r.results.put(-1)
 
     def _release_state(self, r: Request) -> None:

@@ -348,8 +348,9 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
             build_mtp(m, t, wdtype, moe_wdtype)
     vc = cfg.raw.get("vision_config")
     vis = [n for n in ck.names if n.startswith("model.visual.") or n.startswith("visual.")]
-    if isinstance(vc, dict) and vis and (tp is None or tp.size == 1):
-        # image inputs: the vision tower of the checkpoint (it runs once per image, in the activation dtype)
+    if isinstance(vc, dict) and vis and (tp is None or tp.rank == 0):
+        # image inputs: the vision tower of the checkpoint (it runs once per image, in the activation dtype, on the scheduling
+        # rank; the other ranks receive the image tokens' embeddings)
         from ..models.vision import VisionConfig, VisionTower
 
         w = {n.split("visual.", 1)[1]: ck.raw(n) for n in vis}

@@ -28,7 +28,7 @@ import numpy as np
 
 from ..ops import _lib
 
-KIND_STOP, KIND_DECODE, KIND_PREFILL, KIND_GATHER, KIND_RESET, KIND_CALL, KIND_PREFILL_KEEP, KIND_MTP = 0, 1, 2, 3, 4, 5, 6, 7
+KIND_STOP, KIND_DECODE, KIND_PREFILL, KIND_GATHER, KIND_RESET, KIND_CALL, KIND_PREFILL_KEEP, KIND_MTP, KIND_MM_PUT, KIND_MM_DROP = 0, 1, 2, 3, 4, 5, 6, 7, 8, 9
 CONT = 0x100                    # this message continues in the next one (payload larger than a slot)
 OK, TIMEOUT, CLOSED, TOO_BIG, BAD, OVERRUN = range(6)
 
@@ -192,25 +192,61 @@ def encode_prefill_plan(chunks) -> np.ndarray:
     for ch in chunks:
         toks, start, pages, want = ch[:4]
         ss = ch[4] if len(ch) > 4 and ch[4] is not None else -1
-        head += [len(toks), int(start), len(pages), (1 if want is True else int(want or 0)), int(ss)]
+        mm = ch[5] if len(ch) > 5 else None
+        head += [len(toks), int(start), len(pages), (1 if want is True else int(want or 0)), int(ss),
+                 int(getattr(mm, "ctx_id", -1)) if mm is not None else -1]
         body += list(toks)
         body += list(pages)
     return np.asarray(head + body, dtype=np.int32)
 
 
-def decode_prefill_plan(buf: np.ndarray):
+def decode_prefill_plan(buf: np.ndarray, mm_table: dict | None = None):
+    """``mm_table``: the multimodal contexts this rank has received, by id (chunks of prompts with images refer to them)."""
     a = buf.view(np.int32)
     nc = int(a[0])
-    off = 1 + 5 * nc
+    off = 1 + 6 * nc
     chunks = []
     for c in range(nc):
-        nt, start, npg, want, ss = (int(x) for x in a[1 + 5 * c:6 + 5 * c])
+        nt, start, npg, want, ss, mm = (int(x) for x in a[1 + 6 * c:7 + 6 * c])
         toks = a[off:off + nt].tolist()
         off += nt
         pages = a[off:off + npg].tolist()
         off += npg
-        chunks.append((toks, start, pages, (True if want == 1 else (want if want > 1 else False)), ss))
+        chunks.append((toks, start, pages, (True if want == 1 else (want if want > 1 else False)), ss,
+                       (mm_table or {}).get(mm) if mm >= 0 else None))
     return chunks
+
+
+def encode_mm(mm) -> np.ndarray:
+    """A prompt's multimodal context as one message: [id, n, H, prompt length, delta, 0 | 1 (fp32 | bf16 rows)], the image
+    tokens' prompt positions, the 3-D rotary positions, then the embedding rows."""
+    import torch
+
+    emb = mm.embeds.detach().cpu()
+    bf = emb.dtype == torch.bfloat16
+    rows = (emb.view(torch.int16) if bf else emb.float()).contiguous().numpy().view(np.uint8).reshape(-1)
+    n, H = emb.shape
+    head = np.asarray([mm.ctx_id, n, H, mm.pos3.shape[1], mm.delta, 1 if bf else 0], dtype=np.int32)
+    return np.concatenate([head.view(np.uint8), np.asarray(mm.embed_positions, dtype=np.int32).view(np.uint8),
+                           mm.pos3.to(torch.int32).contiguous().numpy().view(np.uint8).reshape(-1), rows])
+
+
+def decode_mm(buf: np.ndarray, device):
+    import torch
+
+    from ..engine.engine import MultimodalContext
+
+    cid, n, H, L, delta, bf = (int(x) for x in buf[:24].view(np.int32))
+    off = 24
+    at = buf[off:off + 4 * n].view(np.int32).tolist()
+    off += 4 * n
+    pos3 = torch.from_numpy(buf[off:off + 12 * L].view(np.int32).reshape(3, L).copy()).long()
+    off += 12 * L
+    raw = buf[off:].copy()
+    emb = torch.from_numpy(raw.view(np.int16).reshape(n, H)).view(torch.bfloat16) if bf else torch.from_numpy(raw.view(np.float32).reshape(n, H))
+    mm = MultimodalContext(emb.to(device), at, pos3, delta)
+    mm.ctx_id = cid
+    return mm
 
 
 class ControlPlane:
@@ -236,6 +272,13 @@ class ControlPlane:
         tail = np.asarray([int(src), len(sel)] + [int(i) for i in sel], dtype=np.int32)
         self.ring.publish(KIND_MTP, np.concatenate([np.asarray([plan.size], dtype=np.int32), plan, tail]))
         self.published += 1
+
+    def mm_put(self, mm):
+        """Hand a prompt's image embeddings and rotary positions to the worker ranks (its chunks then name the context)."""
+        self.ring.publish(KIND_MM_PUT, encode_mm(mm))
+
+    def mm_drop(self, ctx_id: int):
+        self.ring.publish(KIND_MM_DROP, int(ctx_id).to_bytes(4, "little", signed=True))
 
     def gather_logits(self, k: int = 0):
         """``k`` > 0: the ranks exchange their ``k`` best (logit, token id) candidates per row instead of whole logit rows."""
@@ -268,6 +311,7 @@ class WorkerLoop:
         self.steps = 0
         self.errors = 0
         self.handlers = {}          # name -> callable(**args), for KIND_CALL
+        self.mm_table = {}          # multimodal contexts received from rank 0, by id
         self.timing = None          # a list: CUDA event pairs around every decode step are appended (device-time benchmarks)
         self.idle_spin_us = 200
         self.busy_spin_us = 20000   # between decode steps the next plan is microseconds away: keep spinning
@@ -321,13 +365,18 @@ class WorkerLoop:
                     self.last_logits = logits
                     self.steps += 1
                 elif kind in (KIND_PREFILL, KIND_PREFILL_KEEP):
-                    self.last_logits = self.runner.prefill(decode_prefill_plan(buf), keep_hidden=kind == KIND_PREFILL_KEEP)
+                    self.last_logits = self.runner.prefill(decode_prefill_plan(buf, self.mm_table), keep_hidden=kind == KIND_PREFILL_KEEP)
                     self.steps += 1
+                elif kind == KIND_MM_PUT:
+                    mm = decode_mm(np.frombuffer(bytes(buf), dtype=np.uint8), model.device)
+                    self.mm_table[mm.ctx_id] = mm
+                elif kind == KIND_MM_DROP:
+                    self.mm_table.pop(int.from_bytes(bytes(buf[:4]), "little", signed=True), None)
                 elif kind == KIND_MTP:
                     a = buf.view(np.int32)
                     n = int(a[0])
                     tail = a[1 + n:]
-                    self.last_logits = self.runner.mtp_pass(decode_prefill_plan(a[1:1 + n]), tail[2:2 + int(tail[1])].tolist(), int(tail[0]))
+                    self.last_logits = self.runner.mtp_pass(decode_prefill_plan(a[1:1 + n], self.mm_table), tail[2:2 + int(tail[1])].tolist(), int(tail[0]))
                     self.steps += 1
                 elif kind == KIND_GATHER:
                     k = int.from_bytes(bytes(buf[:4]), "little") if len(buf) >= 4 else 0

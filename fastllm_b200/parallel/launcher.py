@@ -57,6 +57,7 @@ def build_rank_model(spec: dict, rank: int, world: int, device: str):
         from .ep import EPInfo
 
         cfg = preset(spec["model"])
+        cfg.raw.update(spec.get("config_raw", {}))          # extra config.json keys for the synthetic architecture (tests)
         dt = getattr(torch, spec.get("dtype", "bfloat16"))
         if world > 1 and dev.type == "cuda" and comm_mode in ("auto", "fused"):
             from . import symm

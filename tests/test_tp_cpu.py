@@ -238,3 +238,64 @@ def test_control_plane_carries_the_draft_head_passes():
     p.join(timeout=60)
     assert p.exitcode == 0
     assert out == ref and proposed > 0
+
+
+_SPEC_MM = {"kind": "preset", "model": "tiny-qwen3", "dtype": "float32", "std": 0.05, "seed": 0, "num_pages": 8,
+            "config_raw": {"rope_parameters": {"mrope_section": [24, 20, 20]}},
+            "engine": {"max_batch": 4, "max_context": 512, "prefix_cache": False, "chunked_prefill_size": 16}}
+
+
+def _mm_case(cfg):
+    from fastllm_b200.engine.engine import MultimodalContext
+    from fastllm_b200.models import vision as V
+
+    ids = [5, 6, 7] + [9] * 12 + [8, 10, 11, 12]
+    pos3, delta = V.mrope_positions(ids, 9, [(1, 6, 8)], 2)
+    emb = torch.randn(12, cfg.hidden_size, generator=torch.Generator().manual_seed(1)) * 0.05
+    return ids, MultimodalContext(emb, [i for i, t in enumerate(ids) if t == 9], pos3, delta)
+
+
+def _rank0_mm(q):
+    from fastllm_b200.engine import GenerationConfig
+    from fastllm_b200.parallel.launcher import TPGroup
+
+    group, eng, _ = TPGroup.launch(_SPEC_MM, ["cpu", "cpu"])
+    try:
+        assert eng.model.cfg.raw["rope_parameters"]["mrope_section"] == [24, 20, 20]
+        ids, mm = _mm_case(eng.model.cfg)
+        h = eng.launch(ids, GenerationConfig(max_new_tokens=6, ignore_eos=True), mm=mm)
+        text = eng.launch([3, 4, 5, 6, 7, 8, 9, 10], GenerationConfig(max_new_tokens=4, ignore_eos=True))
+        reqs = [eng.requests[h], eng.requests[text]]
+        while not all(r.finished() for r in reqs):
+            eng.step()
+        q.put([r.output_ids for r in reqs])
+    finally:
+        group.shutdown()
+    assert all(p.returncode == 0 for p in group.procs)
+
+
+def test_control_plane_carries_image_prompts():
+    """A prompt with image tokens under tensor parallelism: rank 0 hands the embeddings and 3-D rotary positions to the worker
+    rank, whose replayed chunks refer to them; tokens equal one rank's output (a text request runs alongside)."""
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.models import preset, random_init
+
+    m = random_init(preset("tiny-qwen3"), "cpu", torch.float32, std=0.05, seed=0)
+    m.cfg.raw["rope_parameters"] = {"mrope_section": [24, 20, 20]}
+    eng = LLMEngine(m, EngineConfig(**_SPEC_MM["engine"]), num_pages=8)
+    ids, mm = _mm_case(m.cfg)
+    h = eng.launch(ids, GenerationConfig(max_new_tokens=6, ignore_eos=True), mm=mm)
+    t = eng.launch([3, 4, 5, 6, 7, 8, 9, 10], GenerationConfig(max_new_tokens=4, ignore_eos=True))
+    reqs = [eng.requests[h], eng.requests[t]]
+    while not all(r.finished() for r in reqs):
+        eng.step()
+    ref = [r.output_ids for r in reqs]
+    plain = LLMEngine(m, EngineConfig(**_SPEC_MM["engine"]), num_pages=8).generate([ids], GenerationConfig(max_new_tokens=6, ignore_eos=True))[0]
+    assert plain != ref[0]                      # the image embeddings and positions matter for this prompt
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    p = ctx.Process(target=_rank0_mm, args=(q,))
+    p.start()
+    out = q.get(timeout=300)
+    p.join(timeout=60)
+    assert p.exitcode == 0 and out == ref
