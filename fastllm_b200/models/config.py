@@ -146,7 +146,7 @@ def from_hf_dict(d: dict) -> ModelConfig:
         inner = dict(d["text_config"])
         inner.setdefault("model_type", d.get("model_type", "llama"))
         for k in ("eos_token_id", "bos_token_id", "tie_word_embeddings", "quantization_config", "vision_config", "image_token_id",
-                  "video_token_id", "vision_start_token_id", "vision_end_token_id"):
+                  "video_token_id", "vision_start_token_id", "vision_end_token_id", "torch_dtype", "dtype"):
             if k in d and k not in inner:
                 inner[k] = d[k]
         d = inner

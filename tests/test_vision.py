@@ -174,3 +174,75 @@ def test_image_parts_of_chat_messages():
 
     ids, text = Completion(_M()).build_prompt_ids(messages=msgs)
     assert isinstance(ids, PromptIds) and ids.images == images and V.IMAGE_MARKER in text and list(ids) == [len(text), 7]
+
+
+def test_llm_model_answers_about_an_image(tmp_path):
+    """``llm.model(...).response(messages with an image_url part)``: chat template, special-token ids of the placeholder
+    markup, placeholder expansion, tower, engine -- the generated tokens equal transformers' greedy continuation of the same
+    expanded prompt with the same patches."""
+    import base64
+    import io
+    import json
+
+    from fastllm_b200 import llm
+
+    try:
+        from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
+    except Exception as e:
+        pytest.skip(f"transformers has no qwen3_5: {e}")
+    import sys
+
+    sys.path.insert(0, str(__import__("pathlib").Path(__file__).resolve().parent.parent))
+    from baseline import synth
+
+    torch.manual_seed(0)
+    text = dict(vocab_size=512, hidden_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                intermediate_size=128, max_position_embeddings=512, linear_num_key_heads=2, linear_num_value_heads=4,
+                linear_key_head_dim=16, linear_value_head_dim=16, layer_types=["linear_attention", "full_attention"],
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                                 "mrope_section": [3, 3, 2], "mrope_interleaved": True})
+    cfg = Qwen3_5Config(text_config=text, vision_config=_VC, image_token_id=257, video_token_id=260, vision_start_token_id=258,
+                        vision_end_token_id=259, eos_token_id=256)
+    ref = Qwen3_5ForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.normal_(p, std=0.08)
+    d = tmp_path / "q35vl"
+    ref.save_pretrained(str(d), safe_serialization=True)
+    synth.write_tokenizer(d, 256)
+    tk = json.loads((d / "tokenizer.json").read_text())
+    for tid, name in ((257, "<|image_pad|>"), (258, "<|vision_start|>"), (259, "<|vision_end|>")):
+        tk["added_tokens"].append({"id": tid, "content": name, "single_word": False, "lstrip": False, "rstrip": False,
+                                   "normalized": False, "special": True})
+    (d / "tokenizer.json").write_text(json.dumps(tk))
+    (d / "preprocessor_config.json").write_text(json.dumps({"image_mean": [0.5, 0.5, 0.5], "image_std": [0.5, 0.5, 0.5],
+                                                           "size": {"shortest_edge": 64, "longest_edge": 2048}}))
+    from PIL import Image
+
+    g = torch.Generator().manual_seed(1)
+    img = Image.fromarray((torch.rand(40, 56, 3, generator=g) * 255).to(torch.uint8).numpy())
+    buf = io.BytesIO()
+    img.save(buf, format="PNG")
+    url = "data:image/png;base64," + base64.b64encode(buf.getvalue()).decode()
+    model = llm.model(str(d), device="cpu", dtype="float32")
+    try:
+        assert model.torch_model.vision is not None and model._image_options["max_pixels"] == 2048
+        msgs = [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": url}}, {"type": "text", "text": "hi"}]}]
+        h = model.launch_stream_response(msgs, max_length=4, do_sample=False)
+        req = model.engine.requests[h]
+        toks = []
+        while (t := model.engine.fetch(h)) >= 0:
+            toks.append(t)
+        ids2 = req.prompt_ids
+        n_img = ids2.count(257)
+        i0 = ids2.index(257)
+        assert n_img > 4 and ids2[i0 - 1] == 258 and ids2[i0 + n_img] == 259 and req.mm is not None
+        patches, grid = V.image_to_patches(img, model.torch_model.vision.cfg, min_pixels=64, max_pixels=2048)
+        assert n_img == grid[1] * grid[2] // 4
+        with torch.no_grad():
+            out = ref(input_ids=torch.tensor([ids2]), pixel_values=patches, image_grid_thw=torch.tensor([grid]),
+                      mm_token_type_ids=torch.tensor([[1 if t == 257 else 0 for t in ids2]]))
+        assert toks and toks[0] == int(out.logits[0, -1].argmax())
+    finally:
+        model.shutdown() if hasattr(model, "shutdown") else None
