@@ -168,7 +168,21 @@ struct QkvPostParams {
   const float* cos_tab; const float* sin_tab;
   int M, Hq, Hkv, D, rot, rope_mode;
   float eps; float norm_unit_offset;
+  // e4m3 page pools: K / V rows are stored as unscaled e4m3 bytes (the 16-bit value rounded once more), and the queries are
+  // also written as two e4m3 terms q = a + b / 16 for the fp8 tensor-core decode attention ([M, Hq * D] bytes each, or null)
+  int kv8; uint8_t* q8a; uint8_t* q8b;
 };
+
+__device__ __forceinline__ unsigned short e4m3x2_of(float lo, float hi) {
+  unsigned short r;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;\n" : "=h"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+__device__ __forceinline__ float2 e4m3x2_to_f2(unsigned short v) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;\n" : "=r"(h) : "h"(v));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
 
 template <bool BF16>
 __global__ void qkv_post_kernel(const QkvPostParams p) {
@@ -207,6 +221,7 @@ __global__ void qkv_post_kernel(const QkvPostParams p) {
     }
   }
   uint16_t* dst;
+  uint8_t* dst8 = nullptr;
   if (is_q) {
     dst = p.q_out + (size_t)tok * p.ld_q + (size_t)head * D;
   } else {
@@ -214,6 +229,7 @@ __global__ void qkv_post_kernel(const QkvPostParams p) {
     if (slot < 0) return;
     const int kvh = is_k ? head - p.Hq : head - p.Hq - p.Hkv;
     dst = (is_k ? p.k_pool : p.v_pool) + ((size_t)slot * p.Hkv + kvh) * D;
+    if (p.kv8) dst8 = reinterpret_cast<uint8_t*>(is_k ? p.k_pool : p.v_pool) + ((size_t)slot * p.Hkv + kvh) * D;
   }
   if ((is_q || is_k) && p.rope_mode != 0) {
     const int pos = p.positions[tok];
@@ -275,8 +291,27 @@ __global__ void qkv_post_kernel(const QkvPostParams p) {
     }
   }
   cnt = 0;
+  if (dst8 != nullptr) {
+    for (int i = lane; i < npairs; i += 32, ++cnt) {
+      const float2 r = unpack_16<BF16>(pack_16<BF16>(v[2 * cnt], v[2 * cnt + 1]));
+      *reinterpret_cast<unsigned short*>(dst8 + 2 * i) = e4m3x2_of(r.x, r.y);
+    }
+    return;
+  }
   for (int i = lane; i < npairs; i += 32, ++cnt)
     *reinterpret_cast<uint32_t*>(dst + 2 * i) = pack_16<BF16>(v[2 * cnt], v[2 * cnt + 1]);
+  if (is_q && p.q8a != nullptr) {
+    uint8_t* da = p.q8a + ((size_t)tok * p.Hq + head) * D;
+    uint8_t* db = p.q8b + ((size_t)tok * p.Hq + head) * D;
+    cnt = 0;
+    for (int i = lane; i < npairs; i += 32, ++cnt) {
+      const float2 r = unpack_16<BF16>(pack_16<BF16>(v[2 * cnt], v[2 * cnt + 1]));
+      const unsigned short a8 = e4m3x2_of(r.x, r.y);
+      const float2 af = e4m3x2_to_f2(a8);
+      *reinterpret_cast<unsigned short*>(da + 2 * i) = a8;
+      *reinterpret_cast<unsigned short*>(db + 2 * i) = e4m3x2_of((r.x - af.x) * 16.0f, (r.y - af.y) * 16.0f);
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -715,6 +750,30 @@ extern "C" int fb_qkv_post(const void* qkv, int ld_qkv, void* q_out, int ld_q, v
   p.k_pool = (uint16_t*)k_pool; p.v_pool = (uint16_t*)v_pool; p.positions = positions; p.slots = slots;
   p.q_norm_w = (const uint16_t*)q_norm_w; p.k_norm_w = (const uint16_t*)k_norm_w; p.cos_tab = cos_tab; p.sin_tab = sin_tab;
   p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rot = rot; p.rope_mode = rope_mode; p.eps = eps; p.norm_unit_offset = norm_unit_offset;
+  p.kv8 = 0; p.q8a = nullptr; p.q8b = nullptr;
+  const long long warps = (long long)M * (Hq + 2 * Hkv);
+  const int wpb = 8;
+  const int blocks = (int)((warps + wpb - 1) / wpb);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) launch_k(qkv_post_kernel<true>, dim3(blocks), dim3(wpb * 32), 0, s, 0, p);
+  else launch_k(qkv_post_kernel<false>, dim3(blocks), dim3(wpb * 32), 0, s, 0, p);
+  return (int)cudaGetLastError();
+}
+
+// Same for e4m3 page pools: K / V rows are appended as e4m3 bytes; q8a / q8b (null: not wanted) receive the two e4m3 terms of
+// the queries for the fp8 tensor-core decode attention.
+extern "C" int fb_qkv_post_kv8(const void* qkv, int ld_qkv, void* q_out, int ld_q, void* k_pool, void* v_pool, const int* positions,
+                               const int* slots, const void* q_norm_w, const void* k_norm_w, const float* cos_tab,
+                               const float* sin_tab, int M, int Hq, int Hkv, int D, int rot, int rope_mode, float eps,
+                               float norm_unit_offset, int dtype, void* q8a, void* q8b, void* stream) {
+  if (M <= 0) return 0;
+  if (D % 2 != 0 || D > 512 || rot > D || (rot & 3) != 0 || ((q8a == nullptr) != (q8b == nullptr))) return -1;
+  QkvPostParams p;
+  p.qkv = (const uint16_t*)qkv; p.ld_qkv = ld_qkv; p.q_out = (uint16_t*)q_out; p.ld_q = ld_q;
+  p.k_pool = (uint16_t*)k_pool; p.v_pool = (uint16_t*)v_pool; p.positions = positions; p.slots = slots;
+  p.q_norm_w = (const uint16_t*)q_norm_w; p.k_norm_w = (const uint16_t*)k_norm_w; p.cos_tab = cos_tab; p.sin_tab = sin_tab;
+  p.M = M; p.Hq = Hq; p.Hkv = Hkv; p.D = D; p.rot = rot; p.rope_mode = rope_mode; p.eps = eps; p.norm_unit_offset = norm_unit_offset;
+  p.kv8 = 1; p.q8a = (uint8_t*)q8a; p.q8b = (uint8_t*)q8b;
   const long long warps = (long long)M * (Hq + 2 * Hkv);
   const int wpb = 8;
   const int blocks = (int)((warps + wpb - 1) / wpb);

@@ -310,19 +310,18 @@ class DecoderModel:
                           and k_pool.dtype == x.dtype and not c.rope_local_theta)
         if (self.kv8_decode_ok and (fb.is_decode or not variant) and x.is_cuda and x.dim() == 2
                 and k_pool.dtype == torch.float8_e4m3fn):
-            # e4m3 pages: projection + norm + RoPE into 16-bit scratch rows, one kernel converts and appends them; decode reads the
-            # raw pages on the fp8 tensor core (all launches CUDA-graph safe), prefill de-quantises the pages it reads
+            # e4m3 pages: the post-processing launch (norm + RoPE) appends K / V as e4m3 bytes; decode reads the raw pages on the
+            # fp8 tensor core (all launches CUDA-graph safe), prefill de-quantises the pages it reads
             T = x.shape[0]
-            k_new = torch.empty((T, Hkv, D), device=x.device, dtype=x.dtype)
-            v_new = torch.empty((T, Hkv, D), device=x.device, dtype=x.dtype)
-            rows = self._row_ids(T, x.device)
-            q = A.qkv_post(lw.qkv(x), fb.positions, rows, k_new, v_new, Hq, Hkv, D, cos, sin, self.rope_mode, rot,
-                           lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset)
-            A.kv_append_fp8(k_new.view(T, Hkv * D), v_new.view(T, Hkv * D), k_pool, v_pool, fb.slots)
+            q8 = None
+            if fb.is_decode and A.KV8_MMA and fb.decode_ws is not None and T <= fb.decode_ws.max_batch:
+                q8 = fb.decode_ws.q8_terms(Hq * D)             # the post-processing launch also writes the queries' two e4m3 terms
+            q = A.qkv_post(lw.qkv(x), fb.positions, fb.slots, k_pool, v_pool, Hq, Hkv, D, cos, sin, self.rope_mode, rot,
+                           lw.q_norm, lw.k_norm, c.rms_eps, c.norm_unit_offset, q8=q8)
             if fb.is_decode:
                 a = A.attn_decode(q, k_pool, v_pool, fb.page_table, fb.kv_lens, self.attn_scale, Hq, Hkv, D, ws=fb.decode_ws,
                                   planned=fb.decode_planned, window=int(lw.window or 0), softcap=float(c.attn_softcap or 0.0),
-                                  sinks=lw.sinks)
+                                  sinks=lw.sinks, q8_ready=q8 is not None)
             else:                # prefill: the tensor-core prefill kernel over a 16-bit scratch copy of the pages it reads
                 a = A.attn_prefill(q, k_pool, v_pool, fb.page_table, fb.kv_lens, fb.cu_q, self.attn_scale, Hq, Hkv, D,
                                    cu_q_host=fb.cu_q_host)

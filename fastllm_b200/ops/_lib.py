@@ -32,6 +32,7 @@ _KERNEL_SIGS = {
     "fb_rmsnorm": [P, P, P, P, I, I, I, I, F, F, I, P],
     "fb_rmsnorm_quant": [P, P, P, P, I, I, I, I, F, F, I, I, P, I, P, P, I, P],
     "fb_qkv_post": [P, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P],
+    "fb_qkv_post_kv8": [P, I, P, I, P, P, P, P, P, P, P, P, I, I, I, I, I, I, F, F, I, P, P, P],
     "fb_silu_mul": [P, P, I, I, I, I, I, P],
     "fb_glu_act": [P, P, I, I, I, I, I, I, I, P],
     "fb_kv_append_fp8": [P, P, P, P, P, I, I, I, P],

@@ -132,8 +132,11 @@ def _head_norm_ref(x, w, eps, unit_offset):
 
 
 def qkv_post(qkv, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, head_dim, cos, sin, rope_mode=ROPE_NEOX,
-             rot_dim=None, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_unit_offset=0.0, q_out=None):
+             rot_dim=None, q_norm_w=None, k_norm_w=None, eps=1e-6, norm_unit_offset=0.0, q_out=None, q8=None):
     """Split packed QKV, per-head RMSNorm on Q/K (optional), RoPE, append K/V to the page pools, return Q.
+
+    e4m3 page pools (CUDA): the rows are appended as e4m3 bytes by the same launch; ``q8`` = two ``[T, Hq * D]`` byte buffers
+    that receive the queries as two e4m3 terms (the operand form of the fp8 tensor-core decode attention).
 
     qkv: ``[T, (Hq + 2 Hkv) * D]``; positions, slots: int32 ``[T]``; pools ``[pages, page_len, Hkv, D]``.
     One launch on CUDA (reference: QKVRMSNormRopeSplitAppendPagedCache, src/devices/cuda/fastllm-cuda.cu:12190).
@@ -171,6 +174,13 @@ def qkv_post(qkv, positions, slots, k_pool, v_pool, num_q_heads, num_kv_heads, h
         return q.reshape(T, Hq * D)
     if q_out is None:
         q_out = torch.empty((T, Hq * D), device=qkv.device, dtype=qkv.dtype)
+    if k_pool.dtype == torch.float8_e4m3fn:
+        rc = _lib.kernels().fb_qkv_post_kv8(_ptr(qkv), qkv.stride(0), _ptr(q_out), q_out.stride(0), _ptr(k_pool), _ptr(v_pool),
+                                            _ptr(positions), _ptr(slots), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos), _ptr(sin), T, Hq,
+                                            Hkv, D, rot, rope_mode, float(eps), float(norm_unit_offset), dtype_code(qkv.dtype),
+                                            _ptr(q8[0] if q8 is not None else None), _ptr(q8[1] if q8 is not None else None), _stream())
+        _lib.check(rc, "fb_qkv_post_kv8")
+        return q_out
     rc = _lib.kernels().fb_qkv_post(_ptr(qkv), qkv.stride(0), _ptr(q_out), q_out.stride(0), _ptr(k_pool), _ptr(v_pool),
                                     _ptr(positions), _ptr(slots), _ptr(q_norm_w), _ptr(k_norm_w), _ptr(cos), _ptr(sin), T, Hq,
                                     Hkv, D, rot, rope_mode, float(eps), float(norm_unit_offset), dtype_code(qkv.dtype),
@@ -373,7 +383,7 @@ KV8_MMA = os.environ.get("FB_KV8_MMA", "1") != "0"
 
 def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num_kv_heads, head_dim,
                 ws: DecodeWorkspace | None = None, out=None, planned=False, grid_ctas=0, quant_mode: int = 0,
-                window: int = 0, softcap: float = 0.0, sinks=None):
+                window: int = 0, softcap: float = 0.0, sinks=None, q8_ready: bool = False):
     """One new token per request. q: ``[B, Hq*D]`` -> ``[B, Hq*D]``.
 
     ``window`` > 0: sliding-window attention; ``softcap`` > 0: tanh soft-capping of the logits; ``sinks``: fp32 ``[Hq]`` per-head
@@ -416,11 +426,12 @@ def attn_decode(q, k_pool, v_pool, page_table, seq_lens, scale, num_q_heads, num
         # fp16, so queries go in and the output comes back as fp16
         work, n_work = (ws.work_w, ws.n_work_w) if window else (ws.work, ws.n_work)
         if KV8_MMA:
-            qc = q if q.is_contiguous() else q.contiguous()
             qa, qb = ws.q8_terms(num_q_heads * head_dim)
-            rc = _lib.kernels().fb_quant_q_e4m3x2(_ptr(qc), _ptr(qa), _ptr(qb), B * num_q_heads * head_dim, dtype_code(q.dtype),
-                                                  _stream())
-            _lib.check(rc, "fb_quant_q_e4m3x2")
+            if not q8_ready:               # (the QKV post-processing kernel can write the two terms itself)
+                qc = q if q.is_contiguous() else q.contiguous()
+                rc = _lib.kernels().fb_quant_q_e4m3x2(_ptr(qc), _ptr(qa), _ptr(qb), B * num_q_heads * head_dim, dtype_code(q.dtype),
+                                                      _stream())
+                _lib.check(rc, "fb_quant_q_e4m3x2")
             rc = _lib.kernels().fb_attn_decode_opts(_ptr(qa), _ptr(k_pool), _ptr(v_pool), _ptr(out), out.stride(0), _ptr(work),
                                                     _ptr(n_work), _ptr(page_table), _ptr(seq_lens), _ptr(ws.part_o), _ptr(ws.part_ml), B,
                                                     num_q_heads, num_kv_heads, head_dim, num_slots, page_table.stride(0), ws.max_pages,
