@@ -559,17 +559,34 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o, con
   }
   const size_t base = (size_t)(b * Hkv + kvh) * max_splits;
   const int s0 = (window > 0 && seq > window) ? (seq - window) / AD_PAGE : 0;      // first page the plan listed
-  float M = -INFINITY;
-  for (int s = s0; s < ns; ++s) M = fmaxf(M, part_ml[((base + s) * G + g) * 2]);
   // attention sink: a per-head logit that takes part in the softmax normalisation only
   const float sink = sinks != nullptr ? sinks[hq] * 1.4426950408889634f : -INFINITY;
-  M = fmaxf(M, sink);
-  float acc = 0.f, L = sinks != nullptr ? exp2f(sink - M) : 0.f;
-  for (int s = s0; s < ns; ++s) {
-    const size_t sl = (base + s) * G + g;
-    const float wgt = exp2f(part_ml[sl * 2] - M);
-    L += part_ml[sl * 2 + 1] * wgt;
-    acc += part_o[sl * AD_D + d] * wgt;
+  // one pass, eight splits at a time: the (max, sum, output) loads of a group are all independent, the merge is the running
+  // form of the softmax combination (the running maximum replaces a separate pass over the maxima)
+  float M = sink, acc = 0.f, L = sinks != nullptr ? 1.f : 0.f;
+  for (int s = s0; s < ns; s += 8) {
+    float m8[8], l8[8], o8[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (s + j < ns) {
+        const size_t sl = (base + s + j) * G + g;
+        m8[j] = part_ml[sl * 2];
+        l8[j] = part_ml[sl * 2 + 1];
+        o8[j] = part_o[sl * AD_D + d];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (s + j < ns) {
+        const float nm = fmaxf(M, m8[j]);
+        if (nm > -INFINITY) {
+          const float a = exp2f(M - nm), bw = exp2f(m8[j] - nm);
+          acc = acc * a + o8[j] * bw;
+          L = L * a + l8[j] * bw;
+          M = nm;
+        }
+      }
+    }
   }
   const float o = (ns > 0 && L > 0.f) ? acc / L : 0.f;
   uint16_t bits = BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(o)) : __half_as_ushort(__float2half_rn(o));

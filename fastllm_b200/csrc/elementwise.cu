@@ -566,7 +566,37 @@ __global__ void argmax_kernel(const void* __restrict__ logits, int* __restrict__
   const int m = blockIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  int i0 = 0;
+  if (KIND == 0 && (ld & 3) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    // fp32 rows: 16-byte loads, four independent loads in flight per thread (a row is read by one CTA, so the loop has to
+    // hide the memory latency itself); indices ascend within a thread, so "greater than" keeps the lowest index of a tie
+    const float4* row = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(logits) + (size_t)m * ld);
+    const int n4 = V >> 2;
+    int j = threadIdx.x;
+    for (; j + 3 * (int)blockDim.x < n4; j += 4 * blockDim.x) {
+      float4 t[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) t[u] = row[j + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int b = (j + u * blockDim.x) << 2;
+        if (t[u].x > best) { best = t[u].x; bi = b; }
+        if (t[u].y > best) { best = t[u].y; bi = b + 1; }
+        if (t[u].z > best) { best = t[u].z; bi = b + 2; }
+        if (t[u].w > best) { best = t[u].w; bi = b + 3; }
+      }
+    }
+    for (; j < n4; j += blockDim.x) {
+      const float4 t = row[j];
+      const int b = j << 2;
+      if (t.x > best) { best = t.x; bi = b; }
+      if (t.y > best) { best = t.y; bi = b + 1; }
+      if (t.z > best) { best = t.z; bi = b + 2; }
+      if (t.w > best) { best = t.w; bi = b + 3; }
+    }
+    i0 = n4 << 2;
+  }
+  for (int i = i0 + threadIdx.x; i < V; i += blockDim.x) {
     float x;
     if (KIND == 0) x = reinterpret_cast<const float*>(logits)[(size_t)m * ld + i];
     else if (KIND == 1) x = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(logits)[(size_t)m * ld + i]);
@@ -592,7 +622,7 @@ __global__ void argmax_kernel(const void* __restrict__ logits, int* __restrict__
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
     }
-    if (l == 0) { ids[m] = bi + id_offset; if (vals) vals[m] = best; }
+    if (l == 0) { ids[m] = (bi == 0x7fffffff ? 0 : bi) + id_offset; if (vals) vals[m] = best; }
   }
 }
 

@@ -140,6 +140,14 @@ def test_silu_embedding_argmax():
     assert torch.equal(B.embedding(ids, table), table[ids])
     logits = torch.randn(9, 50000, device=DEV)
     assert torch.equal(B.argmax(logits).long(), logits.argmax(-1))
+    big = torch.randn(64, 128256, device=DEV)
+    big[3, 70000] = big[3, 1000] = 50.0                      # a tie: the lowest index wins
+    big[5] = float("-inf")
+    got = B.argmax(big).long()
+    assert torch.equal(got[:5], big[:5].argmax(-1)) and int(got[3]) == 1000 and int(got[5]) == 0
+    assert torch.equal(got[6:], big[6:].argmax(-1))
+    odd = torch.randn(7, 1003, device=DEV)                  # row length that is no multiple of four: scalar path
+    assert torch.equal(B.argmax(odd).long(), odd.argmax(-1))
     assert torch.equal(B.argmax(logits.to(dt)).long().cpu(), B.argmax(logits.to(dt).cpu()).long())
 
 
