@@ -37,14 +37,14 @@ gemm_smallm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 }
 
 // QKV projection with the per-head post-processing (norm, RoPE, cache append) as its epilogue
-template <int MPAD, bool BF16>
-__global__ void __launch_bounds__(192, 1)
+template <int MPAD, bool BF16, int OCC = 1>
+__global__ void __launch_bounds__(192, OCC)
 gemm_qkv_post_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
                      const QkvEpilogueParams qp) {
   uint32_t tmem_base;
   QkvEpilogue<BF16> epi{qp};
-  gemm_smallm_device<MPAD, BF16, 1, QkvEpilogue<BF16>>(tmW, tmX, p, tmem_base, KID_GEMM_SMALLM_PLAIN, epi);
-  if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD, 1>::TMEM_COLS);
+  gemm_smallm_device<MPAD, BF16, OCC, QkvEpilogue<BF16>>(tmW, tmX, p, tmem_base, KID_GEMM_SMALLM_PLAIN, epi);
+  if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD, OCC>::TMEM_COLS);
 }
 
 template <int BN, bool BF16>
@@ -82,11 +82,11 @@ static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX,
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
 }
 
-template <int MPAD, bool BF16>
+template <int MPAD, bool BF16, int OCC = 1>
 static cudaError_t launch_qkv_post(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const QkvEpilogueParams& qp,
                                    int nsplit, int n_tiles, cudaStream_t stream) {
-  using Cfg = SmallMCfg<MPAD, 1>;
-  auto kern = gemm_qkv_post_kernel<MPAD, BF16>;
+  using Cfg = SmallMCfg<MPAD, OCC>;
+  auto kern = gemm_qkv_post_kernel<MPAD, BF16, OCC>;
   static DeviceOnce configured;
   if (configured.need()) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
@@ -274,7 +274,11 @@ extern "C" int fb_gemm_qkv_post(const void* X, const void* W, const void* bias, 
   if (n_tiles > sm_count) return -1;
   // Power-of-two cluster sizes only: clusters of 3 or 6 CTAs measured 35-50 % slower on this part (they fit the GPCs badly
   // and fewer of them are resident at once), although 48 heads x 3 would cover 144 of the 148 SMs.
-  const int nsplit = fb_gemm_pick_split(M, N, K, sm_count);
+  // decode-sized batches: two CTAs per SM (half the pipeline depth each), so that a deeper k-split still has every CTA resident
+  // -- 48 head tiles x 4 = 192 CTAs on 148 SMs instead of 96 on 96
+  static const bool occ2_ok = [] { const char* e = getenv("FB_QKV_POST_OCC2"); return !(e && e[0] == '0'); }();
+  const bool occ2 = mpad <= 64 && occ2_ok;
+  const int nsplit = fb_gemm_pick_split(M, N, K, occ2 ? 2 * sm_count : sm_count);
   p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
   p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
   QkvEpilogueParams qp;
@@ -288,13 +292,19 @@ extern "C" int fb_gemm_qkv_post(const void* X, const void* W, const void* bias, 
 #define FB_QP(MP)                                                                                     \
   return (int)(bf16 ? launch_qkv_post<MP, true>(tmW, tmX, p, qp, nsplit, n_tiles, stream)              \
                     : launch_qkv_post<MP, false>(tmW, tmX, p, qp, nsplit, n_tiles, stream));
+#define FB_QP2(MP)                                                                                    \
+  if (occ2)                                                                                           \
+    return (int)(bf16 ? launch_qkv_post<MP, true, 2>(tmW, tmX, p, qp, nsplit, n_tiles, stream)         \
+                      : launch_qkv_post<MP, false, 2>(tmW, tmX, p, qp, nsplit, n_tiles, stream));      \
+  FB_QP(MP)
   switch (mpad) {
-    case 16: FB_QP(16)
-    case 32: FB_QP(32)
-    case 64: FB_QP(64)
+    case 16: FB_QP2(16)
+    case 32: FB_QP2(32)
+    case 64: FB_QP2(64)
     case 128: FB_QP(128)
     default: FB_QP(256)
   }
+#undef FB_QP2
 #undef FB_QP
 }
 

@@ -200,6 +200,16 @@ def gemm_qkv_post(tokens=64, hq=32, hkv=8, k=4096, iters=4):
     for i in range(iters):
         A.qkv_proj_post(x, ws[i % 3], pos, slots, kp, vp, hq, hkv, D, cos, sin)
     torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(12):
+            A.qkv_proj_post(x, ws[i % 3], pos, slots, kp, vp, hq, hkv, D, cos, sin)
+    g.replay()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record(); g.replay(); e.record()
+    torch.cuda.synchronize()
+    print(f"gemm_qkv_post: {s.elapsed_time(e) / 12 * 1e3:.1f} us per call ({tokens} tokens, N = {n}, K = {k}, weights rotated)")
 
 
 def gdn_decode(batch=64, hk=16, hv=32, iters=4):
