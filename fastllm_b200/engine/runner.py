@@ -205,6 +205,7 @@ class ModelRunner:
             if mm_rows and mtp_hidden is None:
                 fb.embed_rows = torch.tensor(mm_rows, dtype=torch.long, device=dev)
                 fb.embed_vals = torch.cat(mm_vals, dim=0).to(dev)
+        fb.kv_max_host = max(kv_lens) if kv_lens else 0
         if mtp_hidden is not None:
             logits, x = self.model.mtp_forward(fb, mtp_hidden, self.kv.pools)
             return (logits if rows else None), x
@@ -241,6 +242,7 @@ class ModelRunner:
 
     def _decode_forward(self, s: _DecodeSlot):
         fb = s.batch()
+        fb.kv_max_host = getattr(s, "kv_max_host", 0)
         if s.ws is not None:
             s.ws.plan(s.kv_lens)
             fb.decode_planned = True
@@ -284,6 +286,7 @@ class ModelRunner:
             pt[b, :len(pg)] = pg
         if rope_offsets is not None:
             mp[bsz:bsz + n] += np.asarray(rope_offsets, dtype=mp.dtype)
+        s.kv_max_host = (max(positions) + 1) if n else 0
         if self.control is not None:
             self.control.decode(n, bsz, want_logits, mp)
         return self._run_decode(s, n, want_logits)
@@ -292,11 +295,15 @@ class ModelRunner:
         """A worker rank's decode step: the metadata buffer arrives ready-made from the scheduler rank."""
         s = self._get_slot(bsz)
         s.meta_np[:] = meta
+        s.kv_max_host = int(s.meta_np[3 * bsz:3 * bsz + n].max()) if n else 0
         return self._run_decode(s, n, want_logits)
 
     def _run_decode(self, s: _DecodeSlot, n: int, want_logits: bool):
         s.meta_dev.copy_(s.meta_host, non_blocking=True)
-        if self.graph_ok:
+        # sparse-attention models: once a context outgrows the indexer's selection size the step selects keys per request
+        # (host-synchronising tensor ops), outside the captured graph
+        topk = self.model.cfg.index_topk if getattr(self.model, "has_indexer", False) else 0
+        if self.graph_ok and not (topk and getattr(s, "kv_max_host", 0) > topk):
             if s.graph is None:
                 self._capture(s)
             s.graph.replay()

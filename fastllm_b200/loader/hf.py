@@ -263,11 +263,6 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
     RAM -- the reference's disk device (src/devices/disk/diskdevice.cpp:45-49).  It applies to 16/32-bit checkpoints whose
     dtype is the run-time dtype; anything else is read into memory as for ``"cpu"``."""
     cfg = load_config(path)
-    if cfg.model_type in ("glm_moe_dsa", "deepseek_v32"):
-        import warnings
-
-        warnings.warn(f"{cfg.model_type}: the sparse-attention indexer is not evaluated (dense MLA attention); results equal the "
-                      f"model's definition while a request's context stays within index_topk = {cfg.raw.get('index_topk', 2048)} tokens")
     if dtype is None:
         dtype = {"float16": torch.float16, "bfloat16": torch.bfloat16, "float32": torch.float32}.get(cfg.torch_dtype, torch.bfloat16)
         if str(device).startswith("cuda") and dtype == torch.float32:

@@ -141,6 +141,14 @@ def build_layer(m, i: int, t: dict, wdtype="dense", moe_wdtype=None):
         a.w_uk = _to(kvb[:, :nope, :], m)
         a.w_uv = _to(kvb[:, nope:, :], m)
         a.o = _lin(m, _shard_cols(_rs(g("self_attn.o_proj.weight")), r, n), wdtype)
+        if cfg.index_topk and g("self_attn.indexer.wq_b.weight") is not None:
+            # sparse-attention indexer: small projections, the same on every rank
+            a.idx_wq = _lin(m, g("self_attn.indexer.wq_b.weight"), "dense")
+            a.idx_wk = _lin(m, g("self_attn.indexer.wk.weight"), "dense")
+            a.idx_k_norm = (g("self_attn.indexer.k_norm.weight").to(m.device, torch.float32),
+                            g("self_attn.indexer.k_norm.bias").to(m.device, torch.float32))
+            a.idx_weights = g("self_attn.indexer.weights_proj.weight").to(m.device, torch.float32).contiguous()
+            m.has_indexer = True
     else:
         D = cfg.head_dim
         heads_i = cfg.layer_heads[i] if cfg.layer_heads else cfg.num_heads

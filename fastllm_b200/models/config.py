@@ -81,6 +81,10 @@ class ModelConfig:
     qk_nope_head_dim: int = 0
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
+    # sparse attention indexer (DeepSeek-V3.2 / GLM-MoE-DSA): every query attends to its index_topk best-scoring keys
+    index_topk: int = 0
+    index_n_heads: int = 0
+    index_head_dim: int = 0
     # hybrid linear attention (Gated DeltaNet: Qwen3-Next, Qwen3.5)
     layer_types: list | None = None        # per layer "linear_attention" | "full_attention" (None: all full attention)
     lin_num_k_heads: int = 0
@@ -372,6 +376,10 @@ def from_hf_dict(d: dict) -> ModelConfig:
             c.qk_rope_head_dim = g("qk_rope_head_dim", 64)
             c.v_head_dim = g("v_head_dim", 128)
             c.rope_mode = "neox" if mt == "glm_moe_dsa" else "interleaved"
+            if mt in ("glm_moe_dsa", "deepseek_v32"):
+                c.index_topk = int(g("index_topk", 2048) or 0)
+                c.index_n_heads = int(g("index_n_heads", 64) or 0)
+                c.index_head_dim = int(g("index_head_dim", 128) or 0)
             if mt == "glm_moe_dsa":
                 c.latent_norm_eps = 1e-6
             c.head_dim = c.qk_nope_head_dim + c.qk_rope_head_dim
@@ -640,6 +648,15 @@ def preset(name: str) -> ModelConfig:
                                  scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=128,
                                  kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
                                  rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=2048))
+    if name == "tiny-deepseek-v32":      # latent attention with the sparse-attention indexer (selection size 32)
+        return from_hf_dict(dict(model_type="deepseek_v32", vocab_size=512, hidden_size=256, num_hidden_layers=2,
+                                 num_attention_heads=4, num_key_value_heads=4, intermediate_size=512,
+                                 moe_intermediate_size=128, n_routed_experts=8, num_experts_per_tok=2, n_shared_experts=1,
+                                 first_k_dense_replace=1, n_group=1, topk_group=1, routed_scaling_factor=2.5,
+                                 scoring_func="sigmoid", topk_method="noaux_tc", norm_topk_prob=True, q_lora_rank=128,
+                                 kv_lora_rank=64, qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32,
+                                 index_topk=32, index_n_heads=4, index_head_dim=32,
+                                 rms_norm_eps=1e-6, rope_theta=10000.0, max_position_embeddings=2048, eos_token_id=511))
     if name == "small-deepseek-v3":      # DeepSeek-V3 attention geometry (latent 512 + rope 64) on a small body
         return from_hf_dict(dict(model_type="deepseek_v3", vocab_size=1024, hidden_size=512, num_hidden_layers=2,
                                  num_attention_heads=8, num_key_value_heads=8, intermediate_size=1024,

@@ -48,6 +48,7 @@ class ForwardBatch:
     embed_vals: torch.Tensor | None = None
     rope_pos3: torch.Tensor | None = None
     keep_hidden: bool = False                    # leave the final-normed rows of the whole batch in ``model.last_hidden``
+    kv_max_host: int = 0                         # longest context of the batch, known on the host (sparse-attention switch)
 
 
 @dataclass
@@ -86,6 +87,11 @@ class AttentionWeights:
         self.w_uv = None       # [H, v_dim, kv_lora]  absorbed V up-projection
         self.w_uk_t = None     # [H, kv_lora, nope] in the activation dtype (operand layout of the batched absorb GEMM)
         self.w_uv_c = None
+        # sparse-attention indexer (DeepSeek-V3.2 / GLM-MoE-DSA)
+        self.idx_wq: LinearWeight | None = None    # [Hi * Di, q_lora]
+        self.idx_wk: LinearWeight | None = None    # [Di, hidden]
+        self.idx_k_norm = None                      # LayerNorm (weight, bias) of the index keys
+        self.idx_weights = None                     # fp32 [Hi, hidden]: per-head weights of the index score
 
 
 class LinearAttnWeights:
@@ -242,7 +248,8 @@ class DecoderModel:
         c = self.cfg
         if c.use_mla:
             # one spare page at the end: rows that must not be cached (padded decode rows) are written there
-            return (num_pages + 1, A.PAGE_LEN, 1, c.kv_lora_rank + c.qk_rope_head_dim), None
+            idx = (num_pages + 1, A.PAGE_LEN, 1, c.index_head_dim) if (c.index_topk and getattr(self, "has_indexer", False)) else None
+            return (num_pages + 1, A.PAGE_LEN, 1, c.kv_lora_rank + c.qk_rope_head_dim), idx
         s = (num_pages, A.PAGE_LEN, self.num_kv_heads_local, c.head_dim)
         return s, s
 
@@ -538,8 +545,10 @@ class DecoderModel:
         H = self.num_heads_local
         nope, rope, lora, vd = c.qk_nope_head_dim, c.qk_rope_head_dim, c.kv_lora_rank, c.v_head_dim
         T = x.shape[0]
+        qr = None
         if lw.q_a is not None:
-            q = lw.q_b(B.rmsnorm(lw.q_a(x), lw.q_a_norm, c.latent_norm_eps or c.rms_eps))
+            qr = B.rmsnorm(lw.q_a(x), lw.q_a_norm, c.latent_norm_eps or c.rms_eps)
+            q = lw.q_b(qr)
         else:
             q = lw.q_b(x)
         ckv = lw.kv_a(x)                                   # [T, lora + rope]
@@ -555,7 +564,23 @@ class DecoderModel:
             lw.w_uk_t = lw.w_uk.transpose(1, 2).to(x.dtype).contiguous()      # [H, lora, nope]
             lw.w_uv_c = lw.w_uv.to(x.dtype).contiguous()                      # [H, vd, lora]
         B.linear_batched(q, lw.w_uk_t, H, nope + rope, q_full.view(T, H * (lora + rope)), lora + rope)
-        o_lat = MOE.mla_paged_attention(q_full, lat_pool, fb, self.attn_scale, lora)   # [T, H, lora]
+        sel = None
+        if lw.idx_wq is not None and kv[1] is not None and qr is not None:
+            # index keys of the new tokens: projection, LayerNorm, rotate-half rotary on the leading rope dims, into their own
+            # paged pool (rows that must not be cached go to the spare last slot) -- tensor ops only, CUDA-graph safe
+            Di, Hi = c.index_head_dim, c.index_n_heads
+            idx_pool = kv[1]
+            ki = F.layer_norm(lw.idx_wk(x).float(), (Di,), lw.idx_k_norm[0], lw.idx_k_norm[1], 1e-6)
+            ki = A.apply_rope_ref(ki[:, None, :], fb.positions, cos, sin, A.ROPE_NEOX, rope)[:, 0]
+            flat = idx_pool.view(-1, Di)
+            sl = torch.where(fb.slots >= 0, fb.slots, torch.full_like(fb.slots, flat.shape[0] - 1)).long()
+            flat.index_copy_(0, sl, ki.to(flat.dtype))
+            if fb.kv_max_host > c.index_topk:
+                # some context is longer than the selection size: every query keeps its index_topk best-scoring keys
+                qi = A.apply_rope_ref(lw.idx_wq(qr).view(T, Hi, Di), fb.positions, cos, sin, A.ROPE_NEOX, rope)
+                wi = torch.matmul(x.float(), lw.idx_weights.t()) * (Hi ** -0.5)
+                sel = MOE.dsa_select(qi, wi, idx_pool, fb, c.index_topk)
+        o_lat = MOE.mla_paged_attention(q_full, lat_pool, fb, self.attn_scale, lora, sel)   # [T, H, lora]
         o = torch.empty((T, H * vd), device=x.device, dtype=x.dtype)
         B.linear_batched(o_lat.reshape(T, H * lora), lw.w_uv_c, H, lora, o, vd)
         return self._row_parallel_norm(lw.o, o, residual, next_ln, consumer=consumer)
@@ -882,6 +907,13 @@ def random_init(cfg: ModelConfig, device, dtype=torch.bfloat16, tp: TPInfo | Non
             ones(p + "self_attn.kv_a_layernorm.weight", cfg.kv_lora_rank)
             mk(p + "self_attn.kv_b_proj.weight", (cfg.num_heads * (cfg.qk_nope_head_dim + cfg.v_head_dim), cfg.kv_lora_rank))
             mk(p + "self_attn.o_proj.weight", (H, cfg.num_heads * cfg.v_head_dim))
+            if cfg.index_topk and cfg.q_lora_rank:
+                Hi, Di = cfg.index_n_heads, cfg.index_head_dim
+                mk(p + "self_attn.indexer.wq_b.weight", (Hi * Di, cfg.q_lora_rank))
+                mk(p + "self_attn.indexer.wk.weight", (Di, H))
+                raw[p + "self_attn.indexer.k_norm.weight"] = torch.ones(Di, device=dev, dtype=torch.float32)
+                raw[p + "self_attn.indexer.k_norm.bias"] = torch.zeros(Di, device=dev, dtype=torch.float32)
+                mk(p + "self_attn.indexer.weights_proj.weight", (Hi, H))
         else:
             D = cfg.head_dim
             nh = cfg.layer_heads[i] if cfg.layer_heads else cfg.num_heads

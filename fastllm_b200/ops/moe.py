@@ -232,7 +232,35 @@ def _moe_forward_host(x, idx, wts, experts: ExpertWeights):
 
 
 # ---------------------------------------------------------------------------------------------------
-def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
+def dsa_select(q_idx, w_idx, idx_pool, fb, topk: int):
+    """Sparse-attention selection (DeepSeek-V3.2 / GLM-MoE-DSA indexer): for every query row the ``topk`` keys with the largest
+    index score  sum_h w[t, h] * relu(q_idx[t, h] . k_idx[s]) / sqrt(Di)  among the keys it may see.  q_idx ``[T, Hi, Di]``,
+    w_idx fp32 ``[T, Hi]``, idx_pool ``[pages, page_len, 1, Di]`` (the index keys of every cached token).  Returns, per request,
+    a bool mask ``[rows, L]`` of selected keys (None where the whole context fits into ``topk``)."""
+    page_len, Di = idx_pool.shape[1], idx_pool.shape[-1]
+    cu = fb.cu_q_host if fb.cu_q_host is not None else fb.cu_q.tolist()
+    kv_lens = fb.kv_lens.tolist()
+    out = []
+    for b in range(len(cu) - 1):
+        q0, q1 = cu[b], cu[b + 1]
+        L = kv_lens[b]
+        if q1 == q0 or L <= topk:
+            out.append(None)
+            continue
+        npg = (L + page_len - 1) // page_len
+        kk = idx_pool[fb.page_table[b, :npg].long()].reshape(-1, Di)[:L].float()
+        sc = torch.relu(torch.einsum("qhd,kd->qhk", q_idx[q0:q1].float(), kk) * (Di ** -0.5))
+        score = torch.einsum("qhk,qh->qk", sc, w_idx[q0:q1])
+        nq = q1 - q0
+        qpos = torch.arange(L - nq, L, device=score.device)[:, None]
+        kpos = torch.arange(L, device=score.device)[None, :]
+        score = score.masked_fill(kpos > qpos, float("-inf"))
+        top = score.topk(min(topk, L), dim=-1).indices
+        out.append(torch.zeros((nq, L), dtype=torch.bool, device=score.device).scatter_(1, top, True))
+    return out
+
+
+def mla_paged_attention(q_full, lat_pool, fb, scale, lora, select=None):
     """Absorbed MLA over the paged latent cache.
 
     q_full: ``[T, H, lora + rope]`` (q_nope already multiplied by W_UK); lat_pool: ``[pages, page_len, 1,
@@ -240,7 +268,8 @@ def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
     ``[T, H, lora]``.  (Reference: MergeMLAPaged, src/devices/cuda/attention/fastllm-attention.cu:3619-3727.)
     """
     T, H, Dq = q_full.shape
-    if (_MLA_KERNEL and fb.is_decode and q_full.is_cuda and lora == 512 and Dq == 576 and q_full.dtype in (torch.float16, torch.bfloat16)
+    sparse = select is not None and any(m_ is not None for m_ in select)
+    if (not sparse and _MLA_KERNEL and fb.is_decode and q_full.is_cuda and lora == 512 and Dq == 576 and q_full.dtype in (torch.float16, torch.bfloat16)
             and lat_pool.dtype == q_full.dtype and lat_pool.shape[1] == 128):
         from .attention import mla_decode
 
@@ -259,7 +288,8 @@ def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
         lat16 = lat_pool[fb.page_table[b, :npg].long()].reshape(-1, Dq)
         nq = q1 - q0
         qpos = torch.arange(L - nq, L, device=q_full.device)
-        if on_tc:
+        keep = select[b] if select is not None else None
+        if on_tc and keep is None:
             # Prefill: every head attends to the SAME latent rows, so the heads fold into the row dimension and both
             # contractions are plain GEMMs on the tensor-core kernels: S[(q, h), k] = Q' . lat^T with fp32 output, softmax in
             # fp32, O = P . lat[:, :lora].  Keys are padded to a multiple of 64 (their probabilities are exactly zero).
@@ -276,6 +306,8 @@ def mla_paged_attention(q_full, lat_pool, fb, scale, lora):
         s = torch.einsum("qhd,kd->hqk", q_full[q0:q1].float(), lat) * scale
         kpos = torch.arange(L, device=s.device)[None, :]
         s = s.masked_fill(kpos > qpos[:, None], float("-inf"))
+        if keep is not None:                       # sparse attention: only the selected keys of every query row
+            s = s.masked_fill(~keep[None], float("-inf"))
         p = torch.softmax(s, dim=-1)
         out[q0:q1] = torch.einsum("hqk,kl->qhl", p, lat[:, :lora]).to(out.dtype)
     return out

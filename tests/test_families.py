@@ -771,3 +771,55 @@ def test_mtp_weights_are_loaded(naming, tmp_path):
     a = eng.generate([prompt], GenerationConfig(max_new_tokens=8, ignore_eos=True))[0]
     b = LLMEngine(m, EngineConfig(max_batch=2, max_context=512), num_pages=8).generate([prompt], GenerationConfig(max_new_tokens=8, ignore_eos=True))[0]
     assert a == b and eng.spec_proposed > 0
+
+
+def test_glm_moe_dsa_sparse_attention_indexer(tmp_path):
+    """GLM-MoE-DSA / DeepSeek-V3.2 sparse attention: with a selection size below the context every query attends only to its
+    best-scoring keys (index keys kept in their own paged pool); one-shot prefill logits and chunked prefill + decode through
+    the engine agree with transformers."""
+    from fastllm_b200.engine import GenerationConfig
+
+    torch.manual_seed(0)
+    cfgd = dict(model_type="glm_moe_dsa", **_MLA, n_group=1, topk_group=1, q_lora_rank=128, mlp_layer_types=["dense", "sparse", "sparse"],
+                index_topk=16, index_n_heads=4, index_head_dim=32)
+    try:
+        cfg = transformers.AutoConfig.for_model(**cfgd)
+        ref = transformers.AutoModelForCausalLM.from_config(cfg, torch_dtype=torch.float32, attn_implementation="eager")
+    except Exception as e:
+        pytest.skip(f"transformers cannot build glm_moe_dsa: {e}")
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.normal_(p, std=0.05)
+    ref.eval()
+    d = str(tmp_path / "dsa")
+    ref.save_pretrained(d, safe_serialization=True)
+    prompt = list(range(5, 90, 3))                 # 29 tokens: every later query selects 16 of its keys
+    with torch.no_grad():
+        want = ref(torch.tensor([prompt]), use_cache=False).logits[0, -1].float()
+        dense = None
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert getattr(m, "has_indexer", False) and m.cfg.index_topk == 16 and m.layers[0].attn.idx_wq is not None
+    eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512), num_pages=8)
+    assert eng.runner.kv.pools[0][1] is not None and eng.runner.kv.pools[0][1].shape[-1] == 32
+    got = eng.runner.prefill([(prompt, 0, [0, 1], True, 0)])[0].float()[:want.numel()]
+    assert torch.nn.functional.cosine_similarity(got, want, dim=0).item() > 0.99999
+    assert (got - want).abs().max().item() < 2e-3
+    # the selection matters: attending to every key gives different logits
+    m.has_indexer, saved = False, [lw.attn.idx_wq for lw in m.layers]
+    for lw in m.layers:
+        lw.attn.idx_wq = None
+    full = LLMEngine(m, EngineConfig(max_batch=2, max_context=512), num_pages=8).runner.prefill([(prompt, 0, [0, 1], True, 0)])[0].float()
+    assert (full[:want.numel()] - want).abs().max().item() > 1e-3
+    m.has_indexer = True
+    for lw, w in zip(m.layers, saved):
+        lw.attn.idx_wq = w
+    # chunked prefill and decode steps: greedy tokens against transformers' own greedy loop (full re-evaluation per step)
+    eng2 = LLMEngine(m, EngineConfig(max_batch=2, max_context=512, chunked_prefill_size=8), num_pages=8)
+    toks = eng2.generate([prompt], GenerationConfig(max_new_tokens=4, ignore_eos=True))[0]
+    cur = list(prompt)
+    for t in toks:
+        with torch.no_grad():
+            nxt = int(ref(torch.tensor([cur]), use_cache=False).logits[0, -1].argmax())
+        assert int(t) == nxt
+        cur.append(nxt)

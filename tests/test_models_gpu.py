@@ -236,3 +236,24 @@ def test_image_prompt_on_gpu():
     _lib.check_device_errors()
     cs = torch.nn.functional.cosine_similarity(outs[0], outs[1], dim=0).item()
     assert cs > 0.995, cs
+
+
+def test_sparse_attention_indexer_on_gpu():
+    """DeepSeek-V3.2-style indexer on the GPU: index keys are appended inside the CUDA-graph decode while every context fits the
+    selection size; once a context outgrows it the step leaves the graph and selects keys per query.  Tokens agree with the
+    same weights evaluated on the CPU in fp32 for most positions (bf16 near-ties may fall differently)."""
+    cfg = preset("tiny-deepseek-v32")
+    m = random_init(cfg, "cuda", torch.bfloat16, std=0.05, seed=3)
+    assert m.has_indexer
+    prompts = [list(range(7, 7 + 20)), list(range(100, 100 + 45))]      # one below, one above the selection size of 32
+    gen = GenerationConfig(max_new_tokens=20, ignore_eos=True)
+    eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16)
+    out = eng.generate(prompts, gen)
+    _lib.check_device_errors()
+    e2 = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, use_cuda_graph=False, chunked_prefill_size=16), num_pages=16)
+    out2 = e2.generate(prompts, gen)
+    _lib.check_device_errors()
+    assert all(len(o) == 20 for o in out)
+    assert all(a[0] == b[0] for a, b in zip(out, out2))
+    same = sum(x == y for a, b in zip(out, out2) for x, y in zip(a, b))
+    assert same >= 0.7 * 40, (out, out2)

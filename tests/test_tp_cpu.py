@@ -44,7 +44,7 @@ def _single(name):
     return eng.generate(prompts, GenerationConfig(max_new_tokens=6, ignore_eos=True))
 
 
-@pytest.mark.parametrize("name", ["tiny-llama", "tiny-qwen3-moe", "tiny-deepseek-v3", "tiny-minimax-m1", "tiny-minimax-m2", "tiny-hy-v3", "tiny-pangu-moe", "tiny-minicpm3", "tiny-moss", "tiny-step3p5", "tiny-laguna"])
+@pytest.mark.parametrize("name", ["tiny-llama", "tiny-qwen3-moe", "tiny-deepseek-v3", "tiny-minimax-m1", "tiny-minimax-m2", "tiny-hy-v3", "tiny-pangu-moe", "tiny-minicpm3", "tiny-moss", "tiny-step3p5", "tiny-laguna", "tiny-deepseek-v32"])
 def test_tp2_matches_single(name):
     ref = _single(name)
     ctx = mp.get_context("spawn")
