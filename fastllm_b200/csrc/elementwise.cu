@@ -912,3 +912,94 @@ extern "C" int fb_mla_post(const void* ckv, int ld_ckv, const void* q, int ld_q,
   else launch_k(mla_post_kernel<false>, dim3(T), dim3(256), 0, s, 0, p);
   return (int)cudaGetLastError();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Whole-matrix de-quantisation of a weight into the activations' 16-bit type (prefill-sized batches run the dense
+// tensor-core GEMM on the result; the reference de-quantises to fp16 and calls cuBLAS there,
+// src/devices/cuda/linear/fastllm-linear-int4group.cu:1919-2054).  One thread = eight consecutive k of one row.
+//   mode 1 int8:  w = scale[n] * (q - zero[n])            (bytes hold q, or q - 128 when `flag`)
+//   mode 2 int4g: w = min[n, g] + scale[n, g] * q          (two per byte, first value in the high nibble)
+//   mode 3 fp8:   w = e4m3(q) * scale[n / 128, k / 128]
+//   mode 4 fp4:   w = e2m1(q) * scale_bf16[n, k / group] * global   (two per byte, first value in the low nibble)
+// ------------------------------------------------------------------------------------------------
+namespace fb {
+struct DequantParams {
+  const uint8_t* q; const float* scale; const float* zero; uint16_t* out;
+  int N, K, mode, group, groups, flag, ld_out;
+};
+
+template <bool BF16>
+__global__ void dequant_weight_kernel(const DequantParams p) {
+  const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const int k8 = p.K >> 3;
+  if (t >= (long long)p.N * k8) return;
+  const int n = (int)(t / k8), k0 = (int)(t - (long long)n * k8) << 3;
+  float v[8];
+  if (p.mode == 1) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p.q + (size_t)n * p.K + k0);
+    const float sc = p.scale[n], z = p.zero[n] - (p.flag ? 128.f : 0.f);
+    const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t b = (w[j >> 2] >> (8 * (j & 3))) & 0xFFu;
+      v[j] = sc * ((p.flag ? (float)(int8_t)b : (float)b) - z);
+    }
+  } else if (p.mode == 2) {
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(p.q + (size_t)n * (p.K >> 1) + (k0 >> 1));
+    const int g = k0 / p.group;
+    const float sc = p.scale[(size_t)n * p.groups + g], mn = p.zero[(size_t)n * p.groups + g];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t b = (raw >> (8 * j)) & 0xFFu;
+      v[2 * j] = mn + sc * (float)(b >> 4);
+      v[2 * j + 1] = mn + sc * (float)(b & 0xFu);
+    }
+  } else if (p.mode == 3) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p.q + (size_t)n * p.K + k0);
+    const float sc = p.scale[(size_t)(n >> 7) * p.groups + (k0 >> 7)];
+    const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = e4m3x2_to_f2((unsigned short)((w[j >> 1] >> (16 * (j & 1))) & 0xFFFFu));
+      v[2 * j] = f.x * sc; v[2 * j + 1] = f.y * sc;
+    }
+  } else {
+    const uint32_t raw = *reinterpret_cast<const uint32_t*>(p.q + (size_t)n * (p.K >> 1) + (k0 >> 1));
+    const uint16_t sb = reinterpret_cast<const uint16_t*>(p.scale)[(size_t)n * p.groups + k0 / p.group];
+    const float sc = __uint_as_float((uint32_t)sb << 16) * (p.zero != nullptr ? p.zero[0] : 1.f);
+    uint32_t h[4];
+    asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+        "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}\n"
+        : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(raw));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h[j]));
+      v[2 * j] = f.x * sc; v[2 * j + 1] = f.y * sc;
+    }
+  }
+  uint4 o;
+  o.x = pack_16<BF16>(v[0], v[1]); o.y = pack_16<BF16>(v[2], v[3]); o.z = pack_16<BF16>(v[4], v[5]); o.w = pack_16<BF16>(v[6], v[7]);
+  *reinterpret_cast<uint4*>(p.out + (size_t)n * p.ld_out + k0) = o;
+}
+}  // namespace fb
+
+// scale / zero: the weight's own tables (int8: [N] each; int4g: [N, K / group] scale and minimum; fp8: [ceil(N / 128), ceil(K / 128)];
+// fp4: bf16 [N, K / group] and an optional one-element fp32 factor).  flag: int8 bytes hold q - 128.
+extern "C" int fb_dequant_weight(const void* q, const void* scale, const void* zero, void* out, int N, int K, int ld_out, int mode,
+                                 int group, int flag, int dtype, void* stream) {
+  using namespace fb;
+  if (N <= 0 || K <= 0) return 0;
+  if (K % 8 != 0 || ld_out % 8 != 0 || mode < 1 || mode > 4 || (dtype != 0 && dtype != 1)) return -1;
+  if ((mode == 2 || mode == 4) && (group <= 0 || group % 8 != 0 || K % group != 0)) return -1;
+  DequantParams p;
+  p.q = (const uint8_t*)q; p.scale = (const float*)scale; p.zero = (const float*)zero; p.out = (uint16_t*)out;
+  p.N = N; p.K = K; p.mode = mode; p.group = group; p.flag = flag; p.ld_out = ld_out;
+  p.groups = mode == 3 ? (K + 127) / 128 : ((mode == 2 || mode == 4) ? K / group : 0);
+  const long long n = (long long)N * (K / 8);
+  const int blocks = (int)((n + 255) / 256);
+  auto s = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == 1) dequant_weight_kernel<true><<<blocks, 256, 0, s>>>(p);
+  else dequant_weight_kernel<false><<<blocks, 256, 0, s>>>(p);
+  return (int)cudaGetLastError();
+}

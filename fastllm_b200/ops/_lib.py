@@ -37,6 +37,7 @@ _KERNEL_SIGS = {
     "fb_glu_act": [P, P, I, I, I, I, I, I, I, P],
     "fb_kv_append_fp8": [P, P, P, P, P, I, I, I, P],
     "fb_quant_q_e4m3x2": [P, P, P, LL, I, P],
+    "fb_dequant_weight": [P, P, P, P, I, I, I, I, I, I, I, P],
     "fb_softmax_causal_rows": [P, I, P, I, I, I, I, I, F, I, P],
     "fb_embedding": [P, P, P, I, I, I, P],
     "fb_argmax": [P, P, P, I, I, I, I, I, P],

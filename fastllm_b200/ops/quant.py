@@ -139,6 +139,9 @@ def dequantize_fp4(packed, scale, glob, dtype, block: int = 16):
     return out.reshape(packed.shape[0], -1).to(dtype)
 
 
+DEQUANT_KERNEL = __import__("os").environ.get("FB_DEQUANT_KERNEL", "1") != "0"
+
+
 def fake_quant_act_fp8(x: torch.Tensor) -> torch.Tensor:
     """Round activations to e4m3 per (token, 128-wide k block) and return them in their own dtype.  FP8 layers use the
     tensor core's e4m3 x e4m3 path for decode-sized batches; larger batches go through 16-bit GEMMs and apply this rounding
@@ -243,6 +246,22 @@ class LinearWeight:
         dtype = dtype or self.dtype
         if self.kind == "dense":
             return self.w if self.w.dtype == dtype else self.w.to(dtype)
+        if self.w.is_cuda and dtype in (torch.float16, torch.bfloat16) and DEQUANT_KERNEL and self.k % 8 == 0:
+            # one pass over the packed weight (prefill-sized batches run the dense GEMM on the result)
+            from . import _lib
+            from .basic import _ptr, _stream, dtype_code
+
+            mode = {"int8": 1, "int4g": 2, "fp8": 3, "fp4": 4}[self.kind]
+            ok = not ((mode in (2, 4)) and (self.group % 8 != 0 or self.k % self.group != 0))
+            if ok:
+                out = torch.empty((self.n, self.k), device=self.w.device, dtype=dtype)
+                sc = self.scale.to(torch.bfloat16) if mode == 4 else self.scale.float()
+                ze = self.zero.float() if self.zero is not None else None
+                rc = _lib.kernels().fb_dequant_weight(_ptr(self.w), _ptr(sc.contiguous()), _ptr(ze.contiguous() if ze is not None else None),
+                                                      _ptr(out), self.n, self.k, self.k, mode, int(self.group or 0),
+                                                      1 if (mode == 1 and self.signed) else 0, dtype_code(dtype), _stream())
+                _lib.check(rc, "fb_dequant_weight")
+                return out
         if self.kind == "int8":
             if self.signed:
                 return ((self.w.view(torch.int8).float() + 128.0 - self.zero[:, None]) * self.scale[:, None]).to(dtype)

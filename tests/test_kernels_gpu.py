@@ -283,6 +283,31 @@ def test_gemm_fp4_operand_forms(kind, monkeypatch):
     assert (outs[0] - outs[1]).norm() / outs[1].norm() < 5e-3
 
 
+@pytest.mark.parametrize("kind", ["int8", "int4g128", "int4g64", "fp8", "nvfp4", "mxfp4"])
+@pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16])
+def test_dequant_weight_kernel(kind, dt, monkeypatch):
+    """Whole-matrix de-quantisation kernel (the form prefill-sized batches multiply with) vs the PyTorch statement of each
+    format; int8 also in its q - 128 operand form."""
+    from fastllm_b200.ops import quant
+
+    torch.manual_seed(31)
+    w = (torch.randn(384, 512, device=DEV) * 0.05).to(dt)
+    lw = quant.LinearWeight.from_dense(w, kind, act_dtype=dt)
+    assert lw.kind != "dense"
+    got = lw.dequant(dt)
+    monkeypatch.setattr(quant, "DEQUANT_KERNEL", False)
+    want = lw.dequant(torch.float32)
+    assert got.dtype == dt and got.shape == want.shape
+    _close(got, want, 1e-3, 1e-2, f"dequant {kind}", fro=4e-3)
+    x = (torch.randn(1500, 512, device=DEV) * 0.5).to(dt)           # above the chunked small-batch route: dense GEMM on the result
+    monkeypatch.setattr(quant, "DEQUANT_KERNEL", True)
+    y = lw(x)
+    ref = B.linear_ref(x, want)
+    # (formats with 8-bit-activation decode kernels round the activations of large batches the same way: compare in norm)
+    rel = ((y.float() - ref.float()).norm() / ref.float().norm()).item()
+    assert rel < 3e-2, (kind, rel)
+
+
 def test_gemm_quant_epilogues(fp8_w8a16):
     from fastllm_b200.ops import quant
 
