@@ -175,6 +175,147 @@ __device__ __forceinline__ void gemm_fp8_device(const CUtensorMap& tmW, const CU
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
 }
 
+// Several output tiles per CTA (16-bit store, plain or SwiGLU; no k-split): the TMA ring, the MMA issue and the TMEM accumulator
+// ring run on across the tiles, so a projection with a short k (an expert's projections: 6 to 16 k blocks) does not pay the
+// pipeline fill, the barrier / TMEM set-up and the drain once per 128 output rows.  Tiles tile0 .. tile0 + ntile - 1 of the weight
+// rows p.w_row0 + ...; activations as in gemm_fp8_device.  SwiGLU: rows 0..63 of a tile are gate rows and rows 64..127 the up rows
+// of the same 64 output columns, so the two upper promotion warps hand their sums to the two lower ones through shared memory;
+// that buffer takes the place of the last pipeline stage.
+template <int MPAD, bool BF16>
+__device__ __forceinline__ void gemm_fp8_multi_device(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const Fp8Scales& sc,
+                                                      int tile0, int ntile, bool swiglu) {
+  using Cfg = Fp8Cfg<MPAD>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + Cfg::BODY_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* tm_full = empty_bar + Cfg::STAGES;
+  uint64_t* tm_empty = tm_full + Cfg::NBUF;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tm_empty + Cfg::NBUF);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb_cnt = p.kb_total;
+  const int total = ntile * kb_cnt;
+  const int nst = swiglu ? Cfg::STAGES - 1 : Cfg::STAGES;
+  bool dead = false;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 129); }
+    for (int b = 0; b < Cfg::NBUF; ++b) { mbar_init(&tm_full[b], 1); mbar_init(&tm_empty[b], 128); }
+    mbar_init_fence();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, Cfg::TMEM_COLS); tmem_relinquish(); }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      const uint64_t pol_w = l2_policy_evict_first();
+      const uint64_t pol_x = l2_policy_evict_last();
+      for (int g = 0; g < total; ++g) {
+        const int t = g / kb_cnt, i = g - t * kb_cnt;
+        const int s = g % nst;
+        if (g >= nst && !mbar_wait(&empty_bar[s], ((uint32_t)(g / nst) & 1u) ^ 1u, dead, KID_GEMM_FP8, 11)) break;
+        uint8_t* a = smem + s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::TX_BYTES);
+        tma_load_2d_hint(a, &tmW, &full_bar[s], i * 128, p.w_row0 + (tile0 + t) * 128, pol_w);
+        tma_load_2d_hint(a + Cfg::A_BYTES, &tmX, &full_bar[s], i * 128, p.x_row0, pol_x);
+        bulk_load_1d(a + Cfg::SC_OFF, sc.a_scale + (size_t)i * sc.ld_a + p.x_row0, MPAD * 4, &full_bar[s]);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    if (elect_one()) {
+      for (int g = 0; g < total; ++g) {
+        const int s = g % nst, b = g % Cfg::NBUF;
+        if (!mbar_wait(&full_bar[s], (uint32_t)(g / nst) & 1u, dead, KID_GEMM_FP8, 12)) break;
+        if (!mbar_wait(&tm_empty[b], ((uint32_t)(g / Cfg::NBUF) & 1u) ^ 1u, dead, KID_GEMM_FP8, 13)) break;
+        tc_fence_after_sync();
+        const uint32_t a_addr = smem_u32(smem + s * Cfg::STAGE_BYTES);
+        const uint64_t da = make_smem_desc(a_addr, 16, 1024, SWZ_128B);
+        const uint64_t db = make_smem_desc(a_addr + Cfg::A_BYTES, 16, 1024, SWZ_128B);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) umma_f8(tmem_base + b * MPAD, da + 2 * k, db + 2 * k, p.idesc, k != 0 ? 1u : 0u);
+        umma_commit(&empty_bar[s]);
+        umma_commit(&tm_full[b]);
+      }
+    }
+    __syncwarp();
+  } else {
+    const int q = warp & 3;
+    const int n_local = q * 32 + lane;
+    constexpr int CH = MPAD < 32 ? MPAD : 32;
+    uint16_t* outp = reinterpret_cast<uint16_t*>(p.out);
+    float* X = reinterpret_cast<float*>(smem + nst * Cfg::STAGE_BYTES);      // [MPAD][64] up sums (SwiGLU only)
+    int g = 0;
+    for (int t = 0; t < ntile; ++t) {        // a thread whose wait ran out still walks the tiles: it meets the named barriers below
+      float acc[MPAD];
+#pragma unroll
+      for (int j = 0; j < MPAD; ++j) acc[j] = 0.f;
+      const float* wsp = sc.w_scale + (size_t)((p.w_row0 >> 7) + tile0 + t) * p.kb_total;
+      for (int i = 0; i < kb_cnt; ++i, ++g) {
+        const int b = g % Cfg::NBUF, s = g % nst;
+        const float ws = __ldg(wsp + i);
+        if (!mbar_wait(&full_bar[s], (uint32_t)(g / nst) & 1u, dead, KID_GEMM_FP8, 15)) break;
+        if (!mbar_wait(&tm_full[b], (uint32_t)(g / Cfg::NBUF) & 1u, dead, KID_GEMM_FP8, 14)) break;
+        tc_fence_after_sync();
+        const float4* asp = reinterpret_cast<const float4*>(smem + s * Cfg::STAGE_BYTES + Cfg::SC_OFF);
+#pragma unroll
+        for (int c0 = 0; c0 < MPAD; c0 += CH) {
+          uint32_t r[32];
+          const uint32_t taddr = tmem_base + b * MPAD + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+          if (CH == 32) tmem_ld_32x32b_x32(taddr, r); else tmem_ld_32x32b_x16(taddr, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < CH; j += 4) {
+            const float4 a4 = asp[(c0 + j) >> 2];
+            acc[c0 + j + 0] = fmaf(__uint_as_float(r[j + 0]), ws * a4.x, acc[c0 + j + 0]);
+            acc[c0 + j + 1] = fmaf(__uint_as_float(r[j + 1]), ws * a4.y, acc[c0 + j + 1]);
+            acc[c0 + j + 2] = fmaf(__uint_as_float(r[j + 2]), ws * a4.z, acc[c0 + j + 2]);
+            acc[c0 + j + 3] = fmaf(__uint_as_float(r[j + 3]), ws * a4.w, acc[c0 + j + 3]);
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&tm_empty[b]);
+        mbar_arrive(&empty_bar[s]);
+      }
+      if (swiglu) {
+        // producer / consumer named barriers: 2 = "up sums of this tile are in X", 1 = "X has been read"
+        if (q >= 2) {
+          if (t > 0) asm volatile("bar.sync 1, 128;\n" ::: "memory");
+#pragma unroll
+          for (int j = 0; j < MPAD; ++j) X[j * 64 + n_local - 64] = acc[j];
+          asm volatile("bar.arrive 2, 128;\n" ::: "memory");
+        } else {
+          asm volatile("bar.sync 2, 128;\n" ::: "memory");
+          const int n_out = (tile0 + t) * 64 + n_local;
+          const bool live = !dead && n_out < (p.N >> 1);
+#pragma unroll
+          for (int j = 0; j < MPAD; ++j) {
+            const float u = X[j * 64 + n_local];
+            if (live && j < p.M) outp[(size_t)j * p.ld_out + n_out] = (uint16_t)(pack_16<BF16>(silu_f(acc[j]) * u, 0.f) & 0xFFFFu);
+          }
+          if (t + 1 < ntile) asm volatile("bar.arrive 1, 128;\n" ::: "memory");
+        }
+        continue;
+      }
+      if (dead) continue;
+      // a lane owns one output column; consecutive lanes write consecutive columns of a token's row
+      const int n = (tile0 + t) * 128 + n_local;
+      if (n < p.N) {
+#pragma unroll
+        for (int j = 0; j < MPAD; ++j)
+          if (j < p.M) outp[(size_t)j * p.ld_out + n] = (uint16_t)(pack_16<BF16>(acc[j], 0.f) & 0xFFFFu);
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+}
+
 template <int MPAD, bool BF16>
 __global__ void __launch_bounds__(192, (MPAD <= 64 ? 2 : 1))
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p, const Fp8Scales sc) {
@@ -201,6 +342,7 @@ struct Fp8GroupInfo {
   const int* counts; const int* offsets;
   int rows_per_chunk, chunks, n_rows_w;
   int n_local, compact;        // compact: grid.z enumerates existing (expert, chunk) pairs (moe_find_item)
+  int tiles_per_cta;           // > 1: blockIdx.y walks this many 128-row output tiles (plain store, see gemm_fp8_multi_device)
 };
 
 template <int MPAD, bool BF16>
@@ -220,6 +362,12 @@ moe_grouped_fp8_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_con
   p.x_row0 = seg;
   p.w_row0 = e * gi.n_rows_w;         // stacked weights: the weight-scale tile index (w_row0 / 128 + n_tile) follows from it
   p.out = reinterpret_cast<uint16_t*>(base.out) + (size_t)seg * base.ld_out;
+  if (gi.tiles_per_cta > 1) {
+    const int tile0 = blockIdx.y * gi.tiles_per_cta, n_tiles = p.N >> 7;
+    const int nt = n_tiles - tile0 < gi.tiles_per_cta ? n_tiles - tile0 : gi.tiles_per_cta;
+    gemm_fp8_multi_device<MPAD, BF16>(tmW, tmX, p, sbase, tile0, nt, (p.flags & GEMM_SWIGLU) != 0);
+    return;
+  }
   gemm_fp8_device<MPAD, BF16>(tmW, tmX, p, sbase);
 }
 
@@ -529,6 +677,14 @@ static cudaError_t launch_grouped_fp8(const CUtensorMap& tmW, const CUtensorMap&
 // Grouped expert GEMM over the expert-sorted, FP8-quantised activation buffer xq [rows_cap, K]; stacked weights
 // Wq [E_local * N, K] with scales [E_local, ceil(N / 128), K / 128].  max_rows: low 16 bits = most rows an expert can hold,
 // high 16 bits = rows per chunk hint (0: derived).
+// Output tiles per CTA of the plain grouped projection: 0 picks from the grid size, 1 keeps one tile per CTA, n >= 2 forces n.
+static int g_moe_fp8_tiles = [] { const char* e = getenv("FB_MOE_FP8_TILES"); return e ? atoi(e) : 0; }();
+extern "C" int fb_moe_grouped_fp8_set_tiles(int tiles) {
+  const int old = g_moe_fp8_tiles;
+  g_moe_fp8_tiles = tiles < 0 ? 0 : tiles;
+  return old;
+}
+
 extern "C" int fb_moe_grouped_gemm_fp8(const void* xq, int ldq, const float* a_scale, int ld_a, const void* Wq, const float* w_scale,
                                        void* out, const int* counts, const int* offsets, int n_local, int N, int K, int rows_cap,
                                        int ld_out, int dtype, int flags, int max_rows, int total_rows, void* stream_) {
@@ -555,16 +711,39 @@ extern "C" int fb_moe_grouped_gemm_fp8(const void* xq, int ldq, const float* a_s
   sc.w_scale = w_scale; sc.a_scale = a_scale; sc.ld_a = ld_a;
   Fp8GroupInfo gi;
   gi.counts = counts; gi.offsets = offsets; gi.rows_per_chunk = mpad; gi.chunks = chunks; gi.n_rows_w = N;
-  gi.n_local = n_local; gi.compact = 0;
+  gi.n_local = n_local; gi.compact = 0; gi.tiles_per_cta = 1;
   int nz = n_local * chunks;
   if (total_rows > 0) {
     const int bound = n_local + (total_rows + mpad - 1) / mpad;       // sum of ceil(count / mpad) <= experts + rows / mpad
     if (bound < nz) { nz = bound; gi.compact = 1; }
   }
+  int grid_y = n_tiles;
+  const bool multi_kind = flags == 0 || flags == GEMM_SWIGLU;
+  if (multi_kind && g_moe_fp8_tiles >= 2) {
+    gi.tiles_per_cta = g_moe_fp8_tiles < n_tiles ? g_moe_fp8_tiles : n_tiles;
+    grid_y = (n_tiles + gi.tiles_per_cta - 1) / gi.tiles_per_cta;
+  } else if (multi_kind && g_moe_fp8_tiles == 0 && kb_total <= 32) {
+    // an expert's projections have a short k: a CTA walks several output tiles, as many as leave about one CTA per slot of the
+    // GPU (two CTAs per SM).  The number of (expert, row chunk) items that exist is estimated between its bounds.
+    static int slots = 0;
+    if (slots == 0) {
+      int dev = 0, sms = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+      slots = 2 * sms;
+    }
+    int est = total_rows > 0 ? n_local + total_rows / (2 * mpad) : nz;
+    if (est > nz) est = nz;
+    int gy = (slots + est / 2) / est;
+    gy = gy < 1 ? 1 : (gy > n_tiles ? n_tiles : gy);
+    const int nt = (n_tiles + gy - 1) / gy;
+    gi.tiles_per_cta = nt;
+    grid_y = (n_tiles + nt - 1) / nt;
+  }
   cudaError_t e;
 #define FB_G8(MP)                                                                                                         \
-  e = dtype == 1 ? launch_grouped_fp8<MP, true>(tmW, tmX, p, sc, gi, 1, n_tiles, nz, stream)                              \
-                 : launch_grouped_fp8<MP, false>(tmW, tmX, p, sc, gi, 1, n_tiles, nz, stream);                            \
+  e = dtype == 1 ? launch_grouped_fp8<MP, true>(tmW, tmX, p, sc, gi, 1, grid_y, nz, stream)                               \
+                 : launch_grouped_fp8<MP, false>(tmW, tmX, p, sc, gi, 1, grid_y, nz, stream);                             \
   break;
   switch (mpad) {
     case 16: FB_G8(16)

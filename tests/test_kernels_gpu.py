@@ -683,6 +683,56 @@ def test_moe_grouped_fp8_native_matches_w8a16():
     assert rel < 0.08, rel
 
 
+@pytest.mark.parametrize("swiglu", [False, True])
+@pytest.mark.parametrize("tiles", [0, 3, 4, 8])
+def test_moe_grouped_fp8_tiles_per_cta(tiles, swiglu):
+    """The grouped FP8 projections (plain: an expert's down projection; SwiGLU: its gate / up projection) with several output
+    tiles per CTA give the bits of the one-tile-per-CTA launch (same accumulation order), and both match an fp32 reference of
+    the de-quantised operands."""
+    from fastllm_b200.ops import quant_gemm as QG
+
+    torch.manual_seed(5)
+    E, N, K = 8, 1024, 256
+    lib = _lib.kernels()
+    w = torch.randn(E * N, K, device=DEV) * 0.05
+    wb = w.reshape(E * N // 128, 128, K // 128, 128)
+    ws = (wb.abs().amax((1, 3)) / 448.0).clamp(min=1e-12).contiguous()          # (row blocks, k blocks)
+    wq = (wb / ws[:, None, :, None]).reshape(E * N, K).to(torch.float8_e4m3fn).contiguous()
+    counts = torch.tensor([0, 30, 1, 17, 74, 3, 0, 25], device=DEV, dtype=torch.int32)
+    padded = (counts + 3) // 4 * 4          # the routing plan starts every expert's segment on a multiple of four rows (16-byte scale rows)
+    offsets = (torch.cumsum(padded, 0) - padded).int()
+    rows = int(padded.sum())
+    x = torch.randn(rows, K, device=DEV).bfloat16()
+    xq, sa, ld_a = QG.quant_act_fp8(x)
+    xd = (xq.view(torch.float8_e4m3fn).float().reshape(rows, K // 128, 128) * sa[:, :rows].t()[:, :, None]).reshape(rows, K)
+    wd = (wq.float().reshape(E * N // 128, 128, K // 128, 128) * ws[:, None, :, None]).reshape(E, N, K)
+    ref = torch.zeros(rows, N, device=DEV)
+    for e in range(E):
+        o, c = int(offsets[e]), int(counts[e])
+        ref[o:o + c] = xd[o:o + c] @ wd[e].t()
+    if swiglu:                                  # a 128-row tile holds 64 gate rows, then the 64 up rows of the same output columns
+        r4 = ref.reshape(rows, N // 128, 2, 64)
+        ref = (torch.nn.functional.silu(r4[:, :, 0]) * r4[:, :, 1]).reshape(rows, N // 2)
+    n_out = ref.shape[1]
+
+    def run(t):
+        old = lib.fb_moe_grouped_fp8_set_tiles(t)
+        out = torch.zeros(rows, n_out, device=DEV, dtype=torch.bfloat16)
+        try:
+            _lib.check(lib.fb_moe_grouped_gemm_fp8(xq.data_ptr(), K, sa.data_ptr(), ld_a, wq.data_ptr(), ws.data_ptr(), out.data_ptr(),
+                                                   counts.data_ptr(), offsets.data_ptr(), E, N, K, rows, n_out, 1, 4 if swiglu else 0, 74, rows,
+                                                   torch.cuda.current_stream().cuda_stream), "grouped fp8")
+        finally:
+            lib.fb_moe_grouped_fp8_set_tiles(old)
+        torch.cuda.synchronize()
+        _lib.check_device_errors()
+        return out
+
+    base = run(1)
+    _close(base.float().cpu(), ref.cpu(), 2e-2, 2e-2, "grouped fp8 one tile")
+    assert torch.equal(run(tiles), base)
+
+
 def _i8_act(x):
     M, K = x.shape
     xb = x.float().reshape(M, K // 128, 128)
