@@ -232,7 +232,31 @@ def gdn_decode(batch=64, hk=16, hv=32, iters=4):
     torch.cuda.synchronize()
 
 
+def model_kernel_table(model="qwen3-30b-a3b", wdtype="fp8", batch=128, prompt=512, steps=4):
+    """Per-launcher device-time table of whole decode steps (eager, CUDA events around every launch): where a model's step goes."""
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.models import preset, random_init
+
+    cfg = preset(model)
+    m = random_init(cfg, "cuda", torch.bfloat16, std=0.02, wdtype=wdtype, moe_wdtype=wdtype, expert_pool=8)
+    eng = LLMEngine(m, EngineConfig(max_batch=batch, max_context=prompt + 512, use_cuda_graph=False, prefix_cache=False,
+                                    chunked_prefill_size=8192, max_tokens=int(batch * (prompt + 300) / 0.75)))
+    g = torch.Generator().manual_seed(1)
+    for _ in range(batch):
+        eng.launch(torch.randint(0, cfg.vocab_size, (prompt,), generator=g).tolist(), GenerationConfig(max_new_tokens=64, ignore_eos=True))
+    while any(r.state.name in ("WAITING", "PREFILL") for r in eng.requests.values()):
+        eng.step()
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    _lib.start_profile()
+    for _ in range(steps):
+        eng.step()
+    print(_lib.stop_profile().format())
+
+
 CASES = {
+    "model_kernel_table_qwen3_moe_fp8": model_kernel_table,
     "gemm_qkv_post": gemm_qkv_post,
     "attn_decode_kv8": attn_decode_kv8,
     "attn_decode_kv8_only": lambda: attn_decode_kv8(iters=2, only_e4m3=True),
