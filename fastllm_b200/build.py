@@ -1,12 +1,15 @@
 """Build the native libraries in-tree.
 
-Two shared objects are produced under ``fastllm_b200/lib``:
+The shared objects are produced under ``fastllm_b200/lib``:
 
 * ``libfb_kernels.so`` -- every CUDA kernel, compiled for sm_100a only (``nvcc -gencode
   arch=compute_100a,code=sm_100a``).  Plain ``extern "C"`` launchers, no libtorch dependency; Python
   calls them through ctypes with raw device pointers and the current CUDA stream.
 * ``libfb_runtime.so`` -- the host runtime in C++ (paged-KV page manager with prefix trie, tokenizer,
   chat-template engine, quantiser, CPU operator backend).
+
+* ``libfb_cpu.so`` -- the CPU operator backend; ``libfastllm_b200.so`` -- the C ABI for native hosts, with the
+  ``fastllm_chat`` / ``fastllm_benchmark`` / ``fastllm_apiserver`` programs under ``fastllm_b200/bin``.
 
 Run ``python -m fastllm_b200.build`` (add ``--force`` to rebuild everything).  Objects are rebuilt only
 when a source or header is newer than the object.
@@ -130,10 +133,38 @@ def build_cpu(force: bool = False) -> Path:
     return out
 
 
+def build_capi(force: bool = False) -> Path | None:
+    """``libfastllm_b200.so`` (the C ABI for hosts that are not Python: it embeds the interpreter, ``csrc/capi``) and the
+    native hosts over it under ``fastllm_b200/bin``: ``fastllm_chat``, ``fastllm_benchmark``, ``fastllm_apiserver``.
+    Needs the interpreter's headers and shared library; returns ``None`` (nothing built) where they are missing."""
+    import sysconfig
+
+    inc = sysconfig.get_paths()["include"]
+    if not (Path(inc) / "Python.h").exists():
+        return None
+    ver = sysconfig.get_config_var("LDVERSION") or sysconfig.get_config_var("VERSION")
+    libdirs = [d for d in (sysconfig.get_config_var("LIBDIR"), sysconfig.get_config_var("LIBPL")) if d]
+    LIB.mkdir(exist_ok=True)
+    bindir = ROOT / "bin"
+    bindir.mkdir(exist_ok=True)
+    capi, apps = CSRC / "capi", CSRC / "apps"
+    out = LIB / "libfastllm_b200.so"
+    if force or _newer(capi / "fastllm_capi.cpp", [capi / "fastllm_b200.h"], out):
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-I", inc, str(capi / "fastllm_capi.cpp"), "-o", str(out),
+              *[f"-L{d}" for d in libdirs], f"-lpython{ver}", "-ldl", "-lpthread", *[f"-Wl,-rpath,{d}" for d in libdirs]])
+    for name in ("chat", "benchmark", "apiserver"):
+        exe = bindir / f"fastllm_{name}"
+        if force or _newer(apps / f"{name}.cpp", [apps / "app_common.h", capi / "fastllm_b200.h", out], exe):
+            _run(["g++", "-O2", "-std=c++17", "-Wall", str(apps / f"{name}.cpp"), "-o", str(exe), f"-L{LIB}", "-lfastllm_b200", "-lpthread",
+                  "-Wl,-rpath,$ORIGIN/../lib"])
+    return out
+
+
 def build_all(force: bool = False) -> None:
     build_kernels(force)
     build_runtime(force)
     build_cpu(force)
+    build_capi(force)
 
 
 if __name__ == "__main__":
