@@ -30,12 +30,18 @@ class MultimodalContext:
     width, in prompt order), the prompt positions they replace, the (time, row, column) rotary positions of every prompt
     token and the offset between a later token's rotary position and its index in the sequence."""
 
-    def __init__(self, embeds, embed_positions, pos3, delta: int):
+    def __init__(self, embeds, embed_positions, pos3, delta: int, expert_positions=None):
         self.embeds = embeds                                  # [n, H]
         self.embed_positions = list(embed_positions)          # n prompt indices, ascending
         self.pos3 = pos3                                      # int64 [3, prompt_len]
         self.delta = int(delta)
         self._row_of = {p: i for i, p in enumerate(self.embed_positions)}
+        # prompt indices whose rows run through a model's second set of layer weights (CogVLM's visual expert)
+        self.expert_positions = frozenset(expert_positions or ())
+
+    def expert_rows(self, start: int, n: int):
+        """Offsets inside the chunk ``[start, start + n)`` of the rows that take the model's visual-expert weights."""
+        return [p - start for p in range(start, start + n) if p in self.expert_positions] if self.expert_positions else []
 
     def rows(self, start: int, n: int):
         """(offsets inside the chunk ``[start, start + n)``, embedding rows) of the image tokens in that chunk."""

@@ -156,6 +156,7 @@ class ModelRunner:
         pl = self.cfg.page_len
         sslots = []
         mm_rows, mm_vals, pos3 = [], [], []          # image-token rows of the packed batch, their embeddings, 3-D positions
+        ex_rows = []                                 # rows that take a model's visual-expert weights
         any_mm = any(len(ch) > 5 and ch[5] is not None for ch in chunks)
         for b, ch in enumerate(chunks):
             toks, start, pages, want = ch[:4]
@@ -167,6 +168,7 @@ class ModelRunner:
                         mm_rows.extend(cu[-1] + o for o in offs)
                         mm_vals.append(mm.embeds[rws])
                     pos3.append(mm.positions(start, len(toks)))
+                    ex_rows.extend(cu[-1] + o for o in mm.expert_rows(start, len(toks)))
                 else:
                     pos3.append(torch.arange(start, start + len(toks))[None].expand(3, -1))
             ss = ch[4] if len(ch) > 4 and ch[4] is not None and ch[4] >= 0 else self.state_slots     # default: the scratch slot
@@ -205,6 +207,8 @@ class ModelRunner:
             if mm_rows and mtp_hidden is None:
                 fb.embed_rows = torch.tensor(mm_rows, dtype=torch.long, device=dev)
                 fb.embed_vals = torch.cat(mm_vals, dim=0).to(dev)
+            if ex_rows:
+                fb.expert_rows = torch.tensor(ex_rows, dtype=torch.long, device=dev)
         fb.kv_max_host = max(kv_lens) if kv_lens else 0
         if mtp_hidden is not None:
             logits, x = self.model.mtp_forward(fb, mtp_hidden, self.kv.pools)

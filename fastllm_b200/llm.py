@@ -442,7 +442,9 @@ class model:
         if images or (isinstance(query, (list, tuple)) and query and isinstance(query[0], dict)):
             from .models import vision
 
-            if isinstance(query, str):
+            # CogVLM places its image rows behind the first token itself: its prompts carry no placeholder markup
+            marked = getattr(self.torch_model.cfg, "model_type", "") != "cogvlm"
+            if isinstance(query, str) and marked:
                 msgs = []
                 for q, a in history or []:
                     msgs += [{"role": "user", "content": q}, {"role": "assistant", "content": a}]
@@ -450,6 +452,9 @@ class model:
             elif isinstance(query, (list, tuple)) and query and isinstance(query[0], dict):
                 query, found = vision.extract_images(query)
                 images = images or found
+                if not marked:
+                    query = [dict(m, content=m["content"].replace(vision.IMAGE_MARKER, "")) if isinstance(m.get("content"), str) else m
+                             for m in query]
         ids = self._to_ids(query, history)
         mm = None
         if images:

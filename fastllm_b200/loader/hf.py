@@ -84,6 +84,9 @@ _RENAMES = [
     (r"\.block_sparse_moe\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),          # MiniMax-M2
     (r"\.mlp\.e_score_correction_bias", ".mlp.gate.e_score_correction_bias"),
     (r"\.self_attn\.W_pack\.", ".self_attn.qkv_proj."),                                            # Baichuan: fused [q; k; v]
+    # CogVLM: the language expert is the decoder proper (the visual expert is loaded by models/cogvlm.py::attach)
+    (r"\.self_attn\.language_expert_query_key_value\.", ".self_attn.qkv_proj."), (r"\.self_attn\.language_expert_dense\.", ".self_attn.o_proj."),
+    (r"\.mlp\.language_mlp\.", ".mlp."),
     (r"\.mlp\.gate\.wg\.", ".mlp.gate."), (r"\.mlp\.shared_mlp\.", ".mlp.shared_experts."),         # Hunyuan-MoE
     # Step-3.5 (router, selection bias, shared expert, experts stacked along dim 0) and Laguna
     (r"\.moe\.gate\.", ".mlp.gate."), (r"\.moe\.router_bias$", ".mlp.gate.e_score_correction_bias"),
@@ -297,7 +300,14 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
         m = gemma4.build(ck, cfg, device, dtype, wdtype if wdtype != "auto" else "dense", moe_wdtype)
         ck.close()
         return m
-    m = DecoderModel(cfg, device, dtype, tp, ep)
+    if cfg.model_type == "cogvlm":
+        from ..models.cogvlm import CogVLMModel
+
+        if tp is not None and tp.size > 1:
+            raise NotImplementedError("cogvlm runs on one rank")
+        m = CogVLMModel(cfg, device, dtype, tp, ep)
+    else:
+        m = DecoderModel(cfg, device, dtype, tp, ep)
     m.moe_disk = moe_device == "disk"
     ck.want_spans = m.moe_disk
     m.moe_numa = moe_device == "numa"          # host placement with every expert cut across the memory nodes
@@ -341,6 +351,10 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
                     t[f"model.layers.{L}." + k2] = v
         if t.get(f"model.layers.{L}.eh_proj.weight") is not None:
             build_mtp(m, t, wdtype, moe_wdtype)
+    if cfg.model_type == "cogvlm":
+        from ..models import cogvlm
+
+        cogvlm.attach(m, ck, cfg, wdtype)
     vc = cfg.raw.get("vision_config")
     vis = [n for n in ck.names if n.startswith("model.visual.") or n.startswith("visual.")]
     if isinstance(vc, dict) and vis and (tp is None or tp.rank == 0):

@@ -132,7 +132,7 @@ class ModelConfig:
 
 
 LLAMA_LIKE = {"llama", "mistral", "internlm", "internlm3", "baichuan", "yi", "deepseek", "qwen2", "qwen3", "minicpm", "minicpm3",
-              "phi3", "glm4", "glm", "gemma", "gemma2", "ernie4_5", "hunyuan", "telechat", "internlm2", "qwen"}
+              "phi3", "glm4", "glm", "gemma", "gemma2", "ernie4_5", "hunyuan", "telechat", "internlm2", "qwen", "cogvlm"}
 MOE_LIKE = {"qwen3_moe", "qwen2_moe", "moe", "mixtral", "deepseek_v2", "deepseek_v3", "kimi_k2", "deepseek_v32",
             "glm4_moe", "ernie4_5_moe", "minimax_m2", "minimax", "hunyuan_moe", "gpt_oss", "PanguProMoE", "hy_v3", "step3p5", "step3p7",
             "laguna"}
@@ -155,6 +155,8 @@ def from_hf_dict(d: dict) -> ModelConfig:
                 inner[k] = d[k]
         d = inner
     mt = d.get("model_type", "llama")
+    if "CogVLMForCausalLM" in (d.get("architectures") or []) or mt == "CogVLMForCausalLM":
+        mt = "cogvlm"                                   # the checkpoint's config names no model_type
     c = ModelConfig(model_type=mt, raw=d, architectures=d.get("architectures", []))
     g = d.get
     c.vocab_size = g("vocab_size", c.vocab_size)

@@ -47,6 +47,7 @@ class ForwardBatch:
     embed_rows: torch.Tensor | None = None
     embed_vals: torch.Tensor | None = None
     rope_pos3: torch.Tensor | None = None
+    expert_rows: torch.Tensor | None = None      # rows evaluated with a model's visual-expert weights (models/cogvlm.py)
     keep_hidden: bool = False                    # leave the final-normed rows of the whole batch in ``model.last_hidden``
     kv_max_host: int = 0                         # longest context of the batch, known on the host (sparse-attention switch)
 

@@ -271,6 +271,10 @@ def build_context(model, ids, images, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5),
     request's ``MultimodalContext``: the tower's embeddings for those tokens and the 3-D rotary positions)."""
     from ..engine.engine import MultimodalContext
 
+    if getattr(model.cfg, "model_type", "") == "cogvlm":
+        from . import cogvlm
+
+        return cogvlm.build_context(model, ids, images)
     tower = getattr(model, "vision", None)
     tok = getattr(model, "image_token_id", None)
     if tower is None or tok is None:
