@@ -67,10 +67,25 @@ class MultimodalContext:
 
 class LLMEngine:
     def __init__(self, model: DecoderModel, cfg: EngineConfig | None = None, num_pages: int | None = None,
-                 eos_token_ids=None, control=None):
+                 eos_token_ids=None, control=None, draft_model: DecoderModel | None = None):
+        """``draft_model``: a smaller model with the same vocabulary that proposes tokens for ``speculative="draft"``.  Its KV
+        pools have as many pages as the target's and are indexed by the same page ids, so a request's page list serves both."""
         self.cfg = cfg or EngineConfig()
         self.model = model
+        if draft_model is not None:
+            model._extra_page_bytes = draft_model.kv_bytes_per_page()       # the page plan leaves room for the draft's pools
         self.runner = ModelRunner(model, self.cfg, num_pages)
+        self.draft: ModelRunner | None = None
+        if draft_model is not None:
+            import dataclasses
+
+            if control is not None or model.tp.size > 1:
+                raise NotImplementedError("a separate draft model runs on one rank")
+            if self.runner.state_slots or any(lw.lin is not None for lw in draft_model.layers):
+                raise NotImplementedError("draft-model speculation needs attention-only target and draft models")
+            if draft_model.cfg.vocab_size != model.cfg.vocab_size:
+                raise ValueError("the draft model's vocabulary differs from the target's")
+            self.draft = ModelRunner(draft_model, dataclasses.replace(self.cfg, use_cuda_graph=False, speculative=""), self.runner.kv.num_pages)
         self.control = control          # parallel.control.ControlPlane: this rank schedules, the other ranks replay its plans
         self.runner.control = control
         # models with linear-attention layers keep per-request recurrent state in slots; whole-page prefix reuse would need
@@ -368,7 +383,7 @@ class LLMEngine:
         mtp = self._mtp_on()
         logits = self.runner.prefill(chunks, keep_hidden=mtp)
         mtp_items, off = [], 0
-        if mtp:                        # (request, first position, rows, first row in the packed batch) of every chunk
+        if mtp or self._draft_on():    # (request, first position, rows, first row in the packed batch) of every chunk
             for r in decoding:
                 mtp_items.append((r, r.total_len - 1, 1, off))
                 off += 1
@@ -400,11 +415,72 @@ class LLMEngine:
                 produced += self._emit(r, int(t))
         if mtp:
             self._mtp_advance(mtp_items)
+        elif self._draft_on():
+            self._draft_advance(mtp_items, True)
         return produced
 
     # -------------------------------------------------------------------------------- speculative decoding
     def _mtp_on(self) -> bool:
         return bool(self.cfg.speculative == "mtp" and getattr(self.model, "mtp", None) is not None)
+
+    def _draft_on(self) -> bool:
+        return bool(self.cfg.speculative == "draft" and self.draft is not None)
+
+    def _draft_advance(self, items, from_prefill: bool) -> None:
+        """Keep the draft model's KV in step with the target and propose the next tokens.  For every request of ``items`` the
+        draft model reads the true tokens it has not seen yet (a prefill chunk the target has just computed; after a decode
+        step the accepted tokens and the newest one) into its own pools under the request's page ids; a decoding request's
+        last row gives the first draft, and ``speculative_tokens - 1`` further one-token passes chain on the draft's own
+        output.  Rows written for drafts are overwritten with the true tokens' rows by the next call."""
+        chunks, heads, seen = [], [], set()
+        for r, start, _n, _off in items:
+            if id(r) in seen:
+                continue
+            seen.add(id(r))
+            r.mtp_drafts = []
+            if r.finished():
+                continue
+            if from_prefill:
+                # the chunk the target has just computed starts at ``start``: rows before it sit in pages that a request with
+                # the same prefix filled for both models (prefix reuse), rows after it are stale (restart after an eviction)
+                r.draft_computed = start
+            ids = r.all_ids
+            decoding = r.state == RequestState.DECODE
+            upto = len(ids) if decoding else r.num_computed
+            dc = min(r.draft_computed, upto - 1 if decoding else upto)
+            if upto <= dc:
+                continue
+            need = self._pages_needed(upto) - len(r.pages)
+            if need > 0 and not self._grow_pages(r, need):
+                continue
+            chunks.append((ids[dc:upto], dc, r.pages, bool(decoding), None, None))
+            r.draft_computed = upto
+            if decoding:
+                heads.append(r)
+        if not chunks:
+            return
+        logits = self.draft.prefill(chunks)
+        if not heads:
+            return
+        live = []
+        for r, t in zip(heads, sampling.greedy(logits).tolist()):
+            r.mtp_drafts = [int(t)]
+            live.append(r)
+        for j in range(1, self.cfg.speculative_tokens):
+            chunks, nxt = [], []
+            for r in live:
+                pos = len(r.all_ids) - 1 + j                   # position of the draft token that is fed now
+                need = self._pages_needed(pos + 1) - len(r.pages)
+                if pos + 2 >= self.cfg.max_context or (need > 0 and not self._grow_pages(r, need)):
+                    continue
+                chunks.append(([r.mtp_drafts[-1]], pos, r.pages, True, None, None))
+                nxt.append(r)
+            if not chunks:
+                break
+            logits = self.draft.prefill(chunks)
+            for r, t in zip(nxt, sampling.greedy(logits).tolist()):
+                r.mtp_drafts.append(int(t))
+            live = nxt
 
     def _mtp_advance(self, items) -> None:
         """Run the draft head over the rows the decoder has just produced: for every position whose following token is known
@@ -492,14 +568,15 @@ class LLMEngine:
         same way; here the drafts come from the request's own text.  Returns None when nothing could be drafted."""
         k = self.cfg.speculative_tokens
         mtp = self._mtp_on()
+        dm = self._draft_on()
         drafts = []
         for r in reqs:
             room = min(k, self.cfg.max_context - r.total_len - 1, (r.gen.max_new_tokens - len(r.output_ids) - 1) if r.gen.max_new_tokens > 0 else k)
-            if mtp:
+            if mtp or dm:
                 drafts.append(list(r.mtp_drafts[:max(0, room)]))
             else:
                 drafts.append(self._ngram_draft(r.all_ids, self.cfg.speculative_ngram, room) if room > 0 else [])
-        if not any(drafts) and not mtp:          # (the draft head needs every step's hidden rows: it always takes this path)
+        if not any(drafts) and not mtp and not dm:   # (a draft head / model follows every step: it always takes this path)
             return None
         chunks, owners = [], []
         for r, d in zip(reqs, drafts):
@@ -547,6 +624,8 @@ class LLMEngine:
             self.runner.prefill(redo)
         if mtp:
             self._mtp_advance(mtp_items)
+        elif dm:
+            self._draft_advance(mtp_items, False)
         self.decode_steps += 1
         self.decode_tokens += produced
         return produced
@@ -559,7 +638,9 @@ class LLMEngine:
             return 0
         if self.cfg.speculative == "mtp" and not self._mtp_on():
             self.cfg.speculative = "ngram"          # no draft head with this model: prompt-lookup drafts instead
-        if self.cfg.speculative in ("ngram", "mtp") and all(r.gen.is_simple_greedy() for r in reqs):
+        if self.cfg.speculative == "draft" and self.draft is None:
+            self.cfg.speculative = "ngram"          # no draft model was given
+        if self.cfg.speculative in ("ngram", "mtp", "draft") and all(r.gen.is_simple_greedy() for r in reqs):
             n = self._speculative_step(reqs)
             if n is not None:
                 return n

@@ -152,7 +152,7 @@ class KVCache:
     @staticmethod
     def plan_num_pages(model, gpu_mem_ratio: float = 0.9, max_tokens: int | None = None, reserve_bytes: int = 2 << 30) -> int:
         """Pages that fit the memory budget (after the linear-attention state pools, when the model has such layers)."""
-        per_page = model.kv_bytes_per_page()
+        per_page = model.kv_bytes_per_page() + getattr(model, "_extra_page_bytes", 0)     # + a draft model's pools under the same page ids
         if model.device.type == "cuda":
             free, _total = torch.cuda.mem_get_info(model.device)
             budget = int(free * gpu_mem_ratio) - reserve_bytes - getattr(model, "_state_bytes_reserved", 0)

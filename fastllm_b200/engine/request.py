@@ -93,7 +93,8 @@ class Request:
         self.logprob_entries: list = []   # per output token: (token logprob, [(token id, logprob), ...]) when gen.logprobs > 0
         self.recompute_tokens: list[int] | None = None   # set when evicted: prompt + outputs to prefill again
         self.state_slot = -1           # linear-attention state slot while the request is running (-1: none)
-        self.mtp_drafts: list[int] = []   # draft tokens for the next step, from the model's multi-token-prediction head
+        self.mtp_drafts: list[int] = []   # draft tokens for the next step, from the model's multi-token-prediction head or a draft model
+        self.draft_computed = 0           # positions whose true tokens a separate draft model has read into its own KV pools
         self.mm = None                 # multimodal context (engine.MultimodalContext): image embeddings and 3-D rotary positions
 
     @property

@@ -36,6 +36,7 @@ class EngineConfig:
     mixed_prefill_decode: bool = True    # a prefill step also advances the requests that are already decoding (one token each)
     speculative: str = ""                # "" | "ngram": drafts by looking the recent n-gram up in the request's own text | "mtp": drafts
                                          # from the checkpoint's multi-token-prediction head (falls back to "ngram" without one)
+                                         # | "draft": from a separate smaller model given to the engine (``draft_model``)
     speculative_tokens: int = 4          # draft tokens verified per step
     speculative_ngram: int = 3           # longest suffix that is searched for (shorter ones are tried next)
 

@@ -23,7 +23,7 @@ from .tokenizer import StreamDecoder, Tokenizer
 # ---- module-level settings (reference: set_device_map / set_cpu_threads / ... before creating a model) ----
 _settings = {"device": None, "device_map": None, "moe_device_map": None, "threads": None, "max_batch": 256, "max_tokens": None,
              "gpu_mem_ratio": 0.9, "chunked_prefill_size": 8192, "max_context": 8192, "page_size": 128, "cuda_graph": True,
-             "prefix_cache": True, "speculative": "", "speculative_tokens": 4}
+             "prefix_cache": True, "speculative": "", "speculative_tokens": 4, "draft_model_path": "", "draft_dtype": ""}
 
 fastllm_data_type_dict = {"": 0, "auto": 100003, "int2g": 11, "int4g": 9, "int4": 8, "int8": 3, "float16": 7, "fp16": 7, "half": 7,
                           "bfloat16": 1, "bf16": 1, "float32": 0, "fp8": 10, "float8": 10, "fp8_e4m3": 10}
@@ -354,7 +354,13 @@ class model:
                                            max_tokens=_settings["max_tokens"], use_cuda_graph=_settings["cuda_graph"],
                                            prefix_cache=_settings["prefix_cache"], speculative=_settings.get("speculative", ""),
                                            speculative_tokens=int(_settings.get("speculative_tokens", 4)))
-        self.engine = LLMEngine(self.torch_model, ec, eos_token_ids=self.eos_token_ids)
+        draft = None
+        dpath = _settings.get("draft_model_path") or ""
+        if ec.speculative == "draft" and dpath and (tp is None or tp.size == 1):
+            # a smaller model of the same vocabulary proposes tokens (its KV pools sit beside the target's, same page ids)
+            draft = hf_loader.load_model(dpath, device=dev, dtype=self.torch_model.dtype, wdtype=_settings.get("draft_dtype") or dtype or "auto",
+                                         tp=None)
+        self.engine = LLMEngine(self.torch_model, ec, eos_token_ids=self.eos_token_ids, draft_model=draft)
         if tp is not None and tp.size > 1 and tp.comm is not None and not _defer_fused and self.torch_model.on_cuda:
             from .parallel import symm
 

@@ -145,13 +145,21 @@ def make_normal_llm_model(args):
             llm._settings["speculative_tokens"] = int(n)
         elif llm._settings["speculative"] == "mtp":
             llm._settings["speculative_tokens"] = 1
+    elif algo in ("draft", "draft_model") or (not algo and getattr(args, "speculative_draft_model_path", "")):
+        # a separate smaller model of the same vocabulary proposes the tokens (--speculative_draft_model_path)
+        if not getattr(args, "speculative_draft_model_path", ""):
+            raise SystemExit("--speculative_algorithm draft needs --speculative_draft_model_path <model folder>")
+        llm._settings["speculative"] = "draft"
+        llm._settings["draft_model_path"] = args.speculative_draft_model_path
+        n = getattr(args, "speculative_dspark_block_size", 0)
+        if n and n > 0:
+            llm._settings["speculative_tokens"] = int(n)
     elif algo:
-        print(f"[fastllm_b200] --speculative_algorithm {algo}: 'ngram' (prompt-lookup drafts) and 'mtp' (the checkpoint's draft head) "
-              "exist in this build; decoding normally", file=sys.stderr)
-    for flag in ("dspark", "speculative_draft_model_path"):
-        if getattr(args, flag, ""):
-            print(f"[fastllm_b200] --{flag}: separate draft models are not part of this build "
-                  "(use --speculative_algorithm mtp or ngram); decoding normally", file=sys.stderr)
+        print(f"[fastllm_b200] --speculative_algorithm {algo}: 'ngram' (prompt-lookup drafts), 'mtp' (the checkpoint's draft head) and "
+              "'draft' (a separate draft model) exist in this build; decoding normally", file=sys.stderr)
+    if getattr(args, "dspark", ""):
+        print("[fastllm_b200] --dspark: the DeepSeek-V4 block-draft scheme is not part of this build "
+              "(use --speculative_algorithm draft / mtp / ngram); decoding normally", file=sys.stderr)
     if not args.path:
         raise SystemExit("no model given: pass a model path (HF folder, .flm or .gguf)")
     if args.threads and args.threads > 0:

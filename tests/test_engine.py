@@ -548,3 +548,69 @@ def test_speculative_decoding_on_a_hybrid_model(algo):
                     num_pages=16)
     assert eng.generate(prompts, gen) == ref
     assert eng.spec_proposed > 0 and eng.spec_accepted < eng.spec_proposed       # some drafts were rejected and rolled back
+
+
+@pytest.mark.parametrize("same", [False, True])
+def test_draft_model_speculative_matches_greedy(same):
+    """A separate draft model never changes the output.  ``same``: the draft is a copy of the target, so every draft is what the
+    target says next (all accepted, k + 1 tokens per step); otherwise a smaller model with other weights (drafts mostly
+    rejected).  Chunked prefill, several requests, prefix reuse between two requests, page pools shared by page id."""
+    import dataclasses
+
+    from fastllm_b200.models import preset, random_init
+
+    cfg = preset("tiny-llama")
+    m = random_init(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    if same:
+        d = random_init(cfg, "cpu", torch.float32, seed=3, std=0.05)
+    else:
+        d = random_init(dataclasses.replace(cfg, num_layers=1), "cpu", torch.float32, seed=11, std=0.05)
+    prompts = _prompts(cfg.vocab_size, (40, 150, 9))
+    prompts.append(prompts[1][:140] + [5, 6, 7])           # shares a whole-page prefix with the second prompt
+    gen = GenerationConfig(max_new_tokens=13, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512), num_pages=16).generate(prompts, gen)
+    for k in (1, 3):
+        eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, chunked_prefill_size=64, speculative="draft", speculative_tokens=k),
+                        num_pages=16, draft_model=d)
+        assert eng.generate(prompts, gen) == ref
+        assert eng.spec_proposed > 0
+        if same:
+            assert eng.spec_accepted == eng.spec_proposed
+            assert eng.decode_steps <= 13 // (k + 1) + 3
+        # a later request whose prompt is cached: the draft model reads the shared pages under the same page ids
+        again = eng.generate([prompts[1]], gen)
+        assert again == [ref[1]]
+    with pytest.raises(ValueError):
+        LLMEngine(m, EngineConfig(speculative="draft"), num_pages=16,
+                  draft_model=random_init(dataclasses.replace(cfg, vocab_size=cfg.vocab_size + 8), "cpu", torch.float32, seed=1))
+
+
+def test_draft_model_through_llm_model(tmp_path):
+    """``--speculative_algorithm draft --speculative_draft_model_path DIR``: the option parser sets the draft path, ``llm.model``
+    loads the draft beside the target, and the replies equal those without speculation."""
+    import sys
+
+    sys.path.insert(0, str(__import__("pathlib").Path(__file__).resolve().parent.parent))
+    from baseline import synth
+    from fastllm_b200 import llm, util
+
+    big = synth.write_model("tiny-llama", str(tmp_path / "big"), dtype=torch.float32, std=0.05)
+    small = synth.write_model("tiny-llama", str(tmp_path / "small"), dtype=torch.float32, std=0.05, seed=9)
+    llm.set_device_map("cpu")
+    keep = dict(llm._settings)
+    try:
+        plain = llm.model(big, device="cpu", dtype="float32")
+        want = list(plain.stream_response_raw([5, 6, 7, 8, 9, 10], max_length=12, do_sample=False))
+        plain.release_memory()
+        args = util.make_normal_parser().parse_args([big, "--device", "cpu", "--dtype", "float32", "--speculative_algorithm", "draft",
+                                              "--speculative_draft_model_path", small, "--speculative_dspark_block_size", "3"])
+        m = util.make_normal_llm_model(args)
+        try:
+            assert m.engine.draft is not None and m.engine.cfg.speculative == "draft" and m.engine.cfg.speculative_tokens == 3
+            assert list(m.stream_response_raw([5, 6, 7, 8, 9, 10], max_length=12, do_sample=False)) == want
+            assert m.engine.spec_proposed > 0
+        finally:
+            m.release_memory()
+    finally:
+        llm._settings.clear()
+        llm._settings.update(keep)

@@ -200,6 +200,29 @@ def test_mtp_speculative_on_gpu():
     assert same >= 0.8 * sum(len(o) for o in ref), (out, ref)          # bf16 near-ties may fall differently with other batch shapes
 
 
+def test_draft_model_speculative_on_gpu():
+    """A separate one-layer draft model on the GPU: its KV pools share the target's page ids; the target verifies the drafts with
+    the prefill kernels.  With a copy of the target as draft nearly every draft is accepted."""
+    import dataclasses
+
+    cfg = preset("tiny-qwen3")
+    m = random_init(cfg, "cuda", torch.bfloat16, std=0.05, seed=2)
+    g = torch.Generator().manual_seed(4)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (20, 150)]
+    gen = GenerationConfig(max_new_tokens=10, ignore_eos=True)
+    ref = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, use_cuda_graph=False), num_pages=32).generate(prompts, gen)
+    for draft in (random_init(dataclasses.replace(cfg, num_layers=1), "cuda", torch.bfloat16, std=0.05, seed=5),
+                  random_init(cfg, "cuda", torch.bfloat16, std=0.05, seed=2)):
+        eng = LLMEngine(m, EngineConfig(max_batch=4, max_context=512, speculative="draft", speculative_tokens=2), num_pages=32,
+                        draft_model=draft)
+        out = eng.generate(prompts, gen)
+        _lib.check_device_errors()
+        assert eng.spec_proposed > 0
+        same = sum(a == b for o, o2 in zip(out, ref) for a, b in zip(o, o2))
+        assert same >= 0.8 * sum(len(o) for o in ref), (out, ref)      # bf16 near-ties may fall differently with other batch shapes
+    assert eng.spec_accepted >= 0.6 * eng.spec_proposed                 # the copy predicts the target (up to bf16 near-ties)
+
+
 def test_image_prompt_on_gpu():
     """Image-token embeddings and (time, row, column) rotary rows through the GPU prefill kernels (per-token tables indexed by
     row) agree with the same model evaluated on the CPU in fp32."""
