@@ -204,7 +204,7 @@ class LLMEngine:
             self.runner.control = None
 
     def _loop(self):
-        if self.model.device.type == "cuda":
+        if self.model.device.type == "cuda" and self.model.device.index is not None:     # "cuda" alone: the current device
             torch.cuda.set_device(self.model.device)
         while True:
             with self.cv:
