@@ -441,11 +441,16 @@ class model:
                                 logprobs=int(kw.get("logprobs", 0) or 0), logits_processor=kw.get("logits_processor"))
 
     # ---- handle-level API ---------------------------------------------------------------------------
-    def launch_stream_response(self, query, history=None, images=None, **gen_kwargs) -> int:
+    def launch_stream_response(self, query, history=None, images=None, videos=None, **gen_kwargs) -> int:
         """``images``: paths, ``data:`` URLs, bytes or PIL images for a model with a vision tower; a text query gets them in
-        front of the text, a message list may carry them as ``image_url`` / ``image`` content parts instead."""
+        front of the text, a message list may carry them as ``image_url`` / ``image`` content parts instead.  ``videos``: per
+        video a list of frames, a frame directory, an animated GIF / WebP or a ``{"frames": [...], "fps": f}`` dict
+        (``video_url`` / ``video`` parts in a message list); frames are sampled at about two per second and enter the prompt in
+        groups, each behind its time stamp."""
         images = list(images or getattr(query, "images", None) or [])
-        if images or (isinstance(query, (list, tuple)) and query and isinstance(query[0], dict)):
+        videos = list(videos or getattr(query, "videos", None) or [])
+        groups = list(getattr(query, "video_groups", None) or [])       # a prompt whose video markup is expanded already
+        if images or videos or (isinstance(query, (list, tuple)) and query and isinstance(query[0], dict)):
             from .models import vision
 
             # CogVLM places its image rows behind the first token itself: its prompts carry no placeholder markup
@@ -454,21 +459,44 @@ class model:
                 msgs = []
                 for q, a in history or []:
                     msgs += [{"role": "user", "content": q}, {"role": "assistant", "content": a}]
-                query = msgs + [{"role": "user", "content": vision.IMAGE_MARKER * len(images) + query}]
+                slots = "".join(vision.video_slot(k) for k in range(len(videos)))
+                query = msgs + [{"role": "user", "content": vision.IMAGE_MARKER * len(images) + slots + query}]
             elif isinstance(query, (list, tuple)) and query and isinstance(query[0], dict):
-                query, found = vision.extract_images(query)
+                found_v = []
+                query, found = vision.extract_images(query, found_v)
                 images = images or found
+                videos = videos or found_v
                 if not marked:
                     query = [dict(m, content=m["content"].replace(vision.IMAGE_MARKER, "")) if isinstance(m.get("content"), str) else m
                              for m in query]
+            if videos:
+                query, groups = self.expand_videos(query, videos)
         ids = self._to_ids(query, history)
         mm = None
-        if images:
+        if images or groups:
             from .models import vision
 
-            ids, mm = vision.build_context(self.torch_model, ids, images, **getattr(self, "_image_options", {}))
+            ids, mm = vision.build_context(self.torch_model, ids, images, videos=groups or None, **getattr(self, "_image_options", {}))
         self.engine.start()
         return self.engine.launch(ids, self._gen_config(**gen_kwargs), mm=mm)
+
+    def expand_videos(self, messages, videos):
+        """Read and sample every video, cut its frames into temporal groups and put the groups' markup (time stamp + placeholder
+        run each) in place of ``vision.video_slot(k)`` in the messages.  Returns (messages, per-video groups)."""
+        from .models import vision
+
+        tower = getattr(self.torch_model, "vision", None)
+        if tower is None or getattr(self.torch_model, "video_token_id", None) is None:
+            raise ValueError("this model takes no video inputs")
+        opts = getattr(self, "_image_options", {})
+        groups = []
+        for k, v in enumerate(videos):
+            frames, times = vision.load_video(v)
+            g = vision.frames_to_patches(frames, times, tower.cfg, **opts)
+            groups.append(g)
+            messages = [dict(m, content=m["content"].replace(vision.video_slot(k), vision.video_markup(g)))
+                        if isinstance(m.get("content"), str) else m for m in messages]
+        return messages, groups
 
     def abort_handle(self, handle: int):
         self.engine.abort(handle)
@@ -493,8 +521,8 @@ class model:
 
     # ---- convenience API ----------------------------------------------------------------------------
     def stream_response(self, query, history=None, max_length=4096, do_sample=True, top_p=None, top_k=None, temperature=None,
-                        repeat_penalty=None, one_by_one=True, stop_token_ids=None, images=None, **kw):
-        h = self.launch_stream_response(query, history, images=images, max_length=max_length, do_sample=do_sample, top_p=top_p,
+                        repeat_penalty=None, one_by_one=True, stop_token_ids=None, images=None, videos=None, **kw):
+        h = self.launch_stream_response(query, history, images=images, videos=videos, max_length=max_length, do_sample=do_sample, top_p=top_p,
                                         top_k=top_k, temperature=temperature, repeat_penalty=repeat_penalty,
                                         stop_token_ids=stop_token_ids)
         try:

@@ -365,5 +365,6 @@ def load_model(path: str | Path, device="cuda", dtype=None, wdtype: str = "auto"
         w = {n.split("visual.", 1)[1]: ck.raw(n) for n in vis}
         m.vision = VisionTower(VisionConfig(vc), w, m.device, dtype)
         m.image_token_id = cfg.raw.get("image_token_id")
+        m.video_token_id = cfg.raw.get("video_token_id")
     ck.close()
     return m

@@ -185,17 +185,116 @@ def pixels_to_patches(x: torch.Tensor, cfg: VisionConfig):
 
 
 # ---------------------------------------------------------------------------------------------------
+# videos: frames in groups of the tower's temporal patch size; every group is laid out like one image and the prompt
+# carries a time stamp in front of each (reference: the Qwen3.5 multimodal pre-processing of the server,
+# tools/fastllm_pytools/qwen35_multimodal.py; transformers' Qwen3-VL video processor has the same layout)
+# ---------------------------------------------------------------------------------------------------
+def load_video(src, target_fps: float = 2.0, min_frames: int = 4, max_frames: int = 64):
+    """A video -> (sampled frames as PIL images, their time stamps in seconds).  ``src``: a list of frames (paths, bytes,
+    ``data:`` URLs, PIL images), a dict ``{"frames": [...], "fps": f}``, a directory of frame images, an animated GIF / WebP /
+    PNG (path, bytes or ``data:`` URL), or any container OpenCV can read when ``cv2`` is installed.  Frames are sampled
+    uniformly at about ``target_fps`` within ``[min_frames, max_frames]``."""
+    import os
+
+    fps = None
+    if isinstance(src, dict):
+        fps = src.get("fps")
+        src = src.get("frames")
+    frames = None
+    if isinstance(src, (list, tuple)):
+        frames = [load_image(f).convert("RGB") for f in src]
+    elif isinstance(src, str) and os.path.isdir(src):
+        names = sorted(n for n in os.listdir(src) if n.lower().rsplit(".", 1)[-1] in ("png", "jpg", "jpeg", "bmp", "webp"))
+        frames = [load_image(os.path.join(src, n)).convert("RGB") for n in names]
+    else:
+        try:
+            from PIL import ImageSequence
+
+            im = load_image(src)
+            if getattr(im, "n_frames", 1) > 1:
+                dur = im.info.get("duration")
+                fps = 1000.0 / dur if dur else fps
+                frames = [f.convert("RGB") for f in ImageSequence.Iterator(im)]
+        except Exception:
+            frames = None
+        if frames is None and isinstance(src, str) and os.path.exists(src):
+            try:
+                import cv2
+            except ImportError as e:
+                raise ValueError("this video container needs OpenCV (cv2), which is not installed: pass the frames, a frame "
+                                 "directory or an animated GIF / WebP instead") from e
+            from PIL import Image
+
+            cap = cv2.VideoCapture(src)
+            fps = cap.get(cv2.CAP_PROP_FPS) or fps
+            frames = []
+            while True:
+                ok, fr = cap.read()
+                if not ok:
+                    break
+                frames.append(Image.fromarray(cv2.cvtColor(fr, cv2.COLOR_BGR2RGB)))
+            cap.release()
+    if not frames:
+        raise ValueError("no frames could be read from the video input")
+    fps = float(fps) if fps else target_fps
+    n = len(frames)
+    want = int(round(n / fps * target_fps)) if fps > 0 else n
+    want = max(min(min_frames, n), min(want, max_frames, n))
+    idx = [int(round(i * (n - 1) / max(1, want - 1))) for i in range(want)] if want > 1 else [0]
+    return [frames[i] for i in idx], [i / fps for i in idx]
+
+
+def frames_to_patches(frames, times, cfg: VisionConfig, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5), min_pixels=None, max_pixels=None):
+    """Sampled frames -> one ``(patches, grid (1, h, w), time stamp)`` per temporal group of ``cfg.t_patch`` frames (the last
+    frame is repeated to fill the last group).  A group's patches hold its frames in the temporal slots, so the rows equal
+    one ``(t, h, w)`` video grid cut along ``t``."""
+    from PIL import Image
+
+    tp = cfg.t_patch
+    frames, times = list(frames), list(times)
+    while len(frames) % tp:
+        frames.append(frames[-1])
+        times.append(times[-1])
+    f = cfg.patch * cfg.merge
+    kw = {}
+    if min_pixels:
+        kw["min_pixels"] = min_pixels
+    if max_pixels:
+        kw["max_pixels"] = max_pixels
+    H, W = smart_resize(frames[0].height, frames[0].width, f, **kw)
+    px = []
+    for im in frames:
+        im = im.resize((W, H), Image.BICUBIC)
+        x = torch.frombuffer(bytearray(im.tobytes()), dtype=torch.uint8).view(H, W, 3).permute(2, 0, 1).float() / 255.0
+        px.append((x - torch.tensor(mean)[:, None, None]) / torch.tensor(std)[:, None, None])
+    p, m = cfg.patch, cfg.merge
+    gh, gw = H // p, W // p
+    out = []
+    for g in range(0, len(px), tp):
+        x = torch.stack(px[g:g + tp])                                        # [tp, C, H, W]
+        x = x.view(tp, 3, gh // m, m, p, gw // m, m, p).permute(2, 5, 3, 6, 1, 0, 4, 7)
+        out.append((x.reshape(gh * gw, 3 * tp * p * p).contiguous(), (1, gh, gw), sum(times[g:g + tp]) / tp))
+    return out
+
+
+def video_markup(groups) -> str:
+    """Prompt text of one video: a time stamp and one placeholder run per temporal group."""
+    return "".join(f"<{t:.1f} seconds>{VIDEO_MARKER}" for _p, _g, t in groups)
+
+
+# ---------------------------------------------------------------------------------------------------
 # (time, row, column) rotary positions of a prompt with images
 # ---------------------------------------------------------------------------------------------------
-def mrope_positions(ids, image_token_id: int, grids, merge: int):
+def mrope_positions(ids, image_token_id, grids, merge: int):
     """3-D positions ``[3, T]`` for a prompt whose image placeholder runs (one per image, ``t*h*w / merge^2`` tokens each) are
     laid out on their (time, row, column) grids; text tokens advance all three axes together.  Also returns the offset between
     the next token's position and the sequence length (reference semantics: Qwen2-VL ``get_rope_index``)."""
     T = len(ids)
     pos = torch.zeros((3, T), dtype=torch.long)
     nxt, i, gi = 0, 0, 0
+    marks = set(image_token_id) if isinstance(image_token_id, (set, frozenset, list, tuple)) else {image_token_id}
     while i < T:
-        if ids[i] == image_token_id and gi < len(grids):
+        if ids[i] in marks and gi < len(grids):
             t, h, w = grids[gi]
             gh, gw = h // merge, w // merge
             n = t * gh * gw
@@ -228,6 +327,22 @@ def mrope_tables(pos3: torch.Tensor, rot_dim: int, theta: float, sections, devic
 # prompts with images
 # ---------------------------------------------------------------------------------------------------
 IMAGE_MARKER = "<|vision_start|><|image_pad|><|vision_end|>"
+VIDEO_MARKER = "<|vision_start|><|video_pad|><|vision_end|>"
+
+
+def video_slot(k: int) -> str:
+    """Stand-in for the k-th video of a conversation until its frames are read and its markup is known."""
+    return f"\x00video{k}\x00"
+
+
+def video_source(part: dict):
+    t = part.get("type")
+    if t == "video_url":
+        u = part.get("video_url")
+        return u.get("url") if isinstance(u, dict) else u
+    if t in ("video", "input_video"):
+        return part.get("video") or part.get("video_url") or part.get("url") or part.get("path") or part.get("frames")
+    return None
 
 
 def image_source(part: dict):
@@ -243,9 +358,10 @@ def image_source(part: dict):
     return None
 
 
-def extract_images(messages):
+def extract_images(messages, videos: list | None = None):
     """Chat messages whose content lists hold image parts -> (messages with plain-text content, every image replaced by the
-    placeholder markup of the Qwen-VL chat format, the images in prompt order)."""
+    placeholder markup of the Qwen-VL chat format, the images in prompt order).  With a ``videos`` list, ``video_url`` /
+    ``video`` parts are appended to it and leave ``video_slot(k)`` in the text (without one they are an error)."""
     out, images = [], []
     for m in messages:
         d = dict(m)
@@ -256,9 +372,15 @@ def extract_images(messages):
                 if not isinstance(part, dict):
                     continue
                 src = image_source(part)
+                vsrc = video_source(part) if src is None else None
                 if src is not None:
                     images.append(src)
                     text += IMAGE_MARKER
+                elif vsrc is not None:
+                    if videos is None:
+                        raise ValueError("video inputs are not accepted on this route")
+                    text += video_slot(len(videos))
+                    videos.append(vsrc)
                 elif part.get("type", "text") in ("text", "input_text", "output_text"):
                     text += part.get("text", "")
             d["content"] = text
@@ -266,9 +388,10 @@ def extract_images(messages):
     return out, images
 
 
-def build_context(model, ids, images, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5), min_pixels=None, max_pixels=None):
+def build_context(model, ids, images, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5), min_pixels=None, max_pixels=None, videos=None):
     """Token ids with one placeholder token per image -> (ids with every placeholder repeated once per merged patch, the
-    request's ``MultimodalContext``: the tower's embeddings for those tokens and the 3-D rotary positions)."""
+    request's ``MultimodalContext``: the tower's embeddings for those tokens and the 3-D rotary positions).  ``videos``: per
+    video the temporal groups of ``frames_to_patches``; the ids hold one video placeholder token per group."""
     from ..engine.engine import MultimodalContext
 
     if getattr(model.cfg, "model_type", "") == "cogvlm":
@@ -280,22 +403,29 @@ def build_context(model, ids, images, mean=(0.5, 0.5, 0.5), std=(0.5, 0.5, 0.5),
     if tower is None or tok is None:
         raise ValueError("this model has no vision tower: image inputs are not supported")
     cfg = tower.cfg
-    patches, grids = [], []
-    for im in images:
-        p, g = image_to_patches(im, cfg, mean, std, min_pixels, max_pixels)
-        patches.append(p)
-        grids.append(g)
-    embeds = tower.forward(torch.cat(patches), grids)
-    out, k = [], 0
+    vtok = getattr(model, "video_token_id", None)
+    stills = [image_to_patches(im, cfg, mean, std, min_pixels, max_pixels) for im in images]
+    groups = [(p, g) for vid in (videos or []) for p, g, _t in vid]
+    if groups and vtok is None:
+        raise ValueError("this checkpoint names no video placeholder token: video inputs are not supported")
+    patches, grids, out, k, kv = [], [], [], 0, 0        # media in prompt order, images and video groups interleaved
     for t in ids:
-        if t == tok and k < len(grids):
-            gt, gh, gw = grids[k]
-            out.extend([tok] * (gt * gh * gw // cfg.merge ** 2))
+        if t == tok and k < len(stills):
+            p, g = stills[k]
             k += 1
+        elif vtok is not None and t == vtok and kv < len(groups):
+            p, g = groups[kv]
+            kv += 1
         else:
             out.append(t)
-    if k != len(images):
-        raise ValueError(f"the prompt holds {k} image placeholders for {len(images)} images")
-    pos3, delta = mrope_positions(out, tok, grids, cfg.merge)
-    at = [i for i, t in enumerate(out) if t == tok][:embeds.shape[0]]
+            continue
+        patches.append(p)
+        grids.append(g)
+        out.extend([t] * (g[0] * g[1] * g[2] // cfg.merge ** 2))
+    if k != len(stills) or kv != len(groups):
+        raise ValueError(f"the prompt holds {k} image and {kv} video-frame placeholders for {len(stills)} images and {len(groups)} video frame groups")
+    embeds = tower.forward(torch.cat(patches), grids)
+    marks = {tok} if vtok is None else {tok, vtok}
+    pos3, delta = mrope_positions(out, marks, grids, cfg.merge)
+    at = [i for i, t in enumerate(out) if t in marks][:embeds.shape[0]]
     return out, MultimodalContext(embeds, at, pos3, delta)

@@ -31,8 +31,10 @@ def normalize_messages(messages):
 
 
 class PromptIds(list):
-    """Token ids of a prompt plus the images its placeholder tokens stand for (``launch_stream_response`` picks them up)."""
+    """Token ids of a prompt plus the images and video frame groups its placeholder tokens stand for
+    (``launch_stream_response`` picks them up)."""
     images: list = ()
+    video_groups: list = ()
 
 
 class ActiveRequests:
@@ -60,15 +62,19 @@ class Completion:
     # ---------------------------------------------------------------------------------------------
     def build_prompt_ids(self, messages=None, prompt=None, tools=None, chat_template_kwargs=None):
         if messages is not None:
-            images = []
+            images, groups = [], []
             if getattr(getattr(self.model, "torch_model", None), "vision", None) is not None:
                 from ..models.vision import extract_images
 
-                messages, images = extract_images(messages)          # image parts -> placeholder markup + the images
+                videos = []
+                messages, images = extract_images(messages, videos)  # image / video parts -> placeholder markup + the media
+                if videos:
+                    messages, groups = self.model.expand_videos(messages, videos)
             text = self.model.apply_chat_template(normalize_messages(messages), add_generation_prompt=True, tools=tools,
                                                   **(chat_template_kwargs or {}))
             ids = PromptIds(self.model.encode(text))
             ids.images = images
+            ids.video_groups = groups
             return ids, text
         if isinstance(prompt, list) and prompt and isinstance(prompt[0], int):
             return list(prompt), None

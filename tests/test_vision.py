@@ -212,7 +212,7 @@ def test_llm_model_answers_about_an_image(tmp_path):
     ref.save_pretrained(str(d), safe_serialization=True)
     synth.write_tokenizer(d, 256)
     tk = json.loads((d / "tokenizer.json").read_text())
-    for tid, name in ((257, "<|image_pad|>"), (258, "<|vision_start|>"), (259, "<|vision_end|>")):
+    for tid, name in ((257, "<|image_pad|>"), (258, "<|vision_start|>"), (259, "<|vision_end|>"), (260, "<|video_pad|>")):
         tk["added_tokens"].append({"id": tid, "content": name, "single_word": False, "lstrip": False, "rstrip": False,
                                    "normalized": False, "special": True})
     (d / "tokenizer.json").write_text(json.dumps(tk))
@@ -244,5 +244,85 @@ def test_llm_model_answers_about_an_image(tmp_path):
             out = ref(input_ids=torch.tensor([ids2]), pixel_values=patches, image_grid_thw=torch.tensor([grid]),
                       mm_token_type_ids=torch.tensor([[1 if t == 257 else 0 for t in ids2]]))
         assert toks and toks[0] == int(out.logits[0, -1].argmax())
+        # a video part: frames sampled and grouped, one time stamp + placeholder run per group in the rendered prompt
+        clip = [Image.fromarray((torch.rand(40, 56, 3, generator=g) * 255).to(torch.uint8).numpy()) for _ in range(4)]
+        vmsgs = [{"role": "user", "content": [{"type": "video", "video": {"frames": clip, "fps": 2.0}}, {"type": "text", "text": "hi"}]}]
+        h = model.launch_stream_response(vmsgs, max_length=3, do_sample=False)
+        req = model.engine.requests[h]
+        vt = []
+        while (t := model.engine.fetch(h)) >= 0:
+            vt.append(t)
+        ids3 = req.prompt_ids
+        groups = V.frames_to_patches(clip, [0.0, 0.5, 1.0, 1.5], model.torch_model.vision.cfg, min_pixels=64, max_pixels=2048)
+        per = groups[0][1][1] * groups[0][1][2] // 4
+        assert ids3.count(260) == 2 * per and ids3.count(258) == 2 and req.mm is not None
+        with torch.no_grad():
+            out = ref(input_ids=torch.tensor([ids3]), pixel_values_videos=torch.cat([p for p, _g, _t in groups]),
+                      video_grid_thw=torch.tensor([[2, groups[0][1][1], groups[0][1][2]]]),
+                      mm_token_type_ids=torch.tensor([[2 if t == 260 else 0 for t in ids3]]))
+        assert vt and vt[0] == int(out.logits[0, -1].argmax())
     finally:
         model.shutdown() if hasattr(model, "shutdown") else None
+
+
+def test_qwen3_5_video_prompt_matches_transformers(tmp_path):
+    """A prompt with a video: frames in temporal groups (two frames per group fill the tower's temporal patch), one placeholder
+    run per group with text between the runs, every group laid out on its own (row, column) grid -- against transformers'
+    Qwen3.5 model given the same frames as one ``(t, h, w)`` video grid.  Also frame loading / sampling and the markup."""
+    from fastllm_b200.engine import EngineConfig, GenerationConfig, LLMEngine
+    from fastllm_b200.loader import hf
+
+    try:
+        from transformers import Qwen3_5Config, Qwen3_5ForConditionalGeneration
+    except Exception as e:
+        pytest.skip(f"transformers has no qwen3_5: {e}")
+    torch.manual_seed(0)
+    text = dict(vocab_size=512, hidden_size=96, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=32,
+                intermediate_size=128, max_position_embeddings=512, linear_num_key_heads=2, linear_num_value_heads=4,
+                linear_key_head_dim=16, linear_value_head_dim=16, layer_types=["linear_attention", "full_attention"],
+                rope_parameters={"rope_type": "default", "rope_theta": 10000.0, "partial_rotary_factor": 0.5,
+                                 "mrope_section": [3, 3, 2], "mrope_interleaved": True})
+    cfg = Qwen3_5Config(text_config=text, vision_config=_VC, image_token_id=500, video_token_id=501, vision_start_token_id=502,
+                        vision_end_token_id=503)
+    ref = Qwen3_5ForConditionalGeneration(cfg).eval().float()
+    with torch.no_grad():
+        for p in ref.parameters():
+            if p.dim() >= 2:
+                torch.nn.init.normal_(p, std=0.08)
+    d = str(tmp_path / "q35vid")
+    ref.save_pretrained(d, safe_serialization=True)
+    m = hf.load_model(d, device="cpu", dtype=torch.float32)
+    assert m.video_token_id == 501
+    from PIL import Image
+
+    g = torch.Generator().manual_seed(2)
+    clip = [Image.fromarray((torch.rand(24, 32, 3, generator=g) * 255).to(torch.uint8).numpy()) for _ in range(7)]
+    frames, times = V.load_video({"frames": clip, "fps": 4.0}, target_fps=2.0, min_frames=2)
+    assert len(frames) == 4 and times == [0.0, 0.5, 1.0, 1.5]
+    groups = V.frames_to_patches(frames, times, m.vision.cfg, min_pixels=64, max_pixels=2048)
+    assert len(groups) == 2 and groups[0][1][0] == 1 and abs(groups[1][2] - 1.25) < 1e-6
+    assert V.video_markup(groups) == "<0.2 seconds>" + V.VIDEO_MARKER + "<1.2 seconds>" + V.VIDEO_MARKER
+    gh, gw = groups[0][1][1:]
+    ids = [5, 6, 7, 20, 21, 502, 501, 503, 22, 23, 502, 501, 503, 8, 9, 10]
+    ids2, mm = V.build_context(m, ids, [], videos=[groups])
+    n = gh * gw // 4
+    assert ids2.count(501) == 2 * n and mm.embeds.shape == (2 * n, 96)
+    with torch.no_grad():
+        out = ref(input_ids=torch.tensor([ids2]), pixel_values_videos=torch.cat([p for p, _g, _t in groups]),
+                  video_grid_thw=torch.tensor([[2, gh, gw]]), mm_token_type_ids=torch.tensor([[2 if t == 501 else 0 for t in ids2]]))
+    want = out.logits[0, -1].float()
+    eng = LLMEngine(m, EngineConfig(max_batch=2, max_context=512, chunked_prefill_size=16), num_pages=8)
+    h = eng.launch(ids2, GenerationConfig(max_new_tokens=2, ignore_eos=True), mm=mm)
+    req = eng.requests[h]
+    while not req.finished():
+        eng.step()
+    assert int(req.output_ids[0]) == int(want.argmax())
+    lg = eng.runner.prefill([(ids2, 0, [0, 1], True, 0, mm)])[0].float()
+    assert torch.nn.functional.cosine_similarity(lg[:want.numel()], want, dim=0).item() > 0.9999
+    # message parts: a video part leaves a slot that the expansion fills with the groups' markup
+    vids = []
+    msgs, imgs = V.extract_images([{"role": "user", "content": [{"type": "video", "video": {"frames": clip, "fps": 4.0}},
+                                                                 {"type": "text", "text": "what happens?"}]}], vids)
+    assert not imgs and len(vids) == 1 and msgs[0]["content"] == V.video_slot(0) + "what happens?"
+    with pytest.raises(ValueError):
+        V.extract_images([{"role": "user", "content": [{"type": "video_url", "video_url": {"url": "x.gif"}}]}])
