@@ -115,6 +115,71 @@ __global__ void moe_plan_small_kernel(const int* __restrict__ idx, int pairs, in
   }
 }
 
+// The same plan with warp votes: pairs are taken in chunks of 32; a chunk's lanes learn by `match.any` how many earlier lanes
+// go to the same expert, one lane per (chunk, expert) records the chunk's count, a scan over the chunks per expert turns the
+// counts into bases, and rank = base of the chunk + earlier lanes of the chunk.  Same (deterministic) order as above at
+// O(chunks) instead of O(pairs) work per thread.  Needs chunks * n_local <= 8192 (16-bit counts in shared memory).
+__global__ void __launch_bounds__(1024)
+moe_plan_warp_kernel(const int* __restrict__ idx, int pairs, int first, int n_local, int* __restrict__ counts,
+                     int* __restrict__ offsets, int* __restrict__ pos, int* __restrict__ total_rows, int pad) {
+  __shared__ int s_idx[4096];
+  __shared__ uint16_t s_w[8192];
+  __shared__ int s_cnt[1024];
+  __shared__ int s_off[1024];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int chunks = (pairs + 31) >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const uint32_t lt_mask = (1u << lane) - 1u;
+  for (int i = threadIdx.x; i < pairs; i += blockDim.x) {
+    const int e = idx[i] - first;
+    s_idx[i] = (e >= 0 && e < n_local) ? e : -1;
+  }
+  for (int i = threadIdx.x; i < chunks * n_local; i += blockDim.x) s_w[i] = 0;
+  __syncthreads();
+  for (int c = warp; c < chunks; c += nwarps) {
+    const int i = (c << 5) + lane;
+    const int e = i < pairs ? s_idx[i] : -1;
+    const uint32_t same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && (same & lt_mask) == 0) s_w[c * n_local + e] = (uint16_t)__popc(same);
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) {
+    int run = 0;
+    for (int c = 0; c < chunks; ++c) {
+      const int v = s_w[c * n_local + e];
+      s_w[c * n_local + e] = (uint16_t)run;
+      run += v;
+    }
+    s_cnt[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    int carry = 0;
+    for (int base = 0; base < n_local; base += 32) {
+      const int e = base + threadIdx.x;
+      const int c = e < n_local ? (s_cnt[e] + pad - 1) / pad * pad : 0;
+      int incl = c;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if ((int)threadIdx.x >= o) incl += v;
+      }
+      if (e < n_local) s_off[e] = carry + incl - c;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (threadIdx.x == 0) *total_rows = carry;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_local; e += blockDim.x) { counts[e] = s_cnt[e]; offsets[e] = s_off[e]; }
+  for (int c = warp; c < chunks; c += nwarps) {
+    const int i = (c << 5) + lane;
+    const int e = i < pairs ? s_idx[i] : -1;
+    const uint32_t same = __match_any_sync(0xffffffffu, e);
+    if (i < pairs) pos[i] = e < 0 ? -1 : s_off[e] + (int)s_w[c * n_local + e] + __popc(same & lt_mask);
+  }
+}
+
 __global__ void moe_gather_kernel(const uint16_t* __restrict__ x, const int* __restrict__ pos, uint16_t* __restrict__ xs, int T,
                                   int topk, int H) {
   const int pair = blockIdx.x;
@@ -212,6 +277,11 @@ using namespace fb;
 extern "C" int fb_moe_plan(const int* idx, int T, int topk, int first, int n_local, int* counts, int* offsets, int* pos,
                            int* total_rows, int pad, void* stream) {
   if (n_local <= 0 || n_local > 1024 || T <= 0) return -1;
+  static const bool warp_plan = [] { const char* e = getenv("FB_MOE_PLAN_WARP"); return !(e && e[0] == '0'); }();
+  if (warp_plan && T * topk <= 4096 && ((T * topk + 31) / 32) * n_local <= 8192) {
+    launch_k(moe_plan_warp_kernel, dim3(1), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), 0, idx, T * topk, first, n_local, counts, offsets, pos, total_rows, pad);
+    return (int)cudaGetLastError();
+  }
   if (T * topk <= 4096) {
     launch_k(moe_plan_small_kernel, dim3(1), dim3(1024), 0, reinterpret_cast<cudaStream_t>(stream), 0, idx, T * topk, first, n_local, counts, offsets, pos, total_rows, pad);
     return (int)cudaGetLastError();

@@ -683,6 +683,42 @@ def test_moe_grouped_fp8_native_matches_w8a16():
     assert rel < 0.08, rel
 
 
+@pytest.mark.parametrize("T,topk,E,first,n_local,pad", [(128, 8, 128, 0, 128, 4), (37, 2, 8, 0, 8, 4), (100, 8, 256, 64, 32, 16),
+                                                        (512, 8, 64, 0, 64, 4), (1, 6, 160, 0, 160, 1), (700, 8, 16, 8, 8, 4), (400, 8, 128, 0, 128, 4)])
+def test_moe_plan_matches_definition(T, topk, E, first, n_local, pad):
+    """Routing plan: per local expert the row count, the padded segment start, and for every (token, k) pair its row = segment
+    start + number of earlier pairs of the same expert (-1 for experts of other ranks).  Covers the warp-vote kernel, the
+    shared-memory kernel (pairs * experts beyond its table) and the one-thread-per-expert kernel (> 4096 pairs)."""
+    from fastllm_b200.ops import moe_grouped  # noqa: F401  (registers the launcher signatures)
+
+    lib = _lib.kernels()
+    g = torch.Generator().manual_seed(T + E)
+    idx = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(T)]).int().to(DEV)
+    counts = torch.zeros(n_local, dtype=torch.int32, device=DEV)
+    offsets = torch.zeros(n_local, dtype=torch.int32, device=DEV)
+    pos = torch.full((T * topk,), -7, dtype=torch.int32, device=DEV)
+    total = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _lib.check(lib.fb_moe_plan(idx.data_ptr(), T, topk, first, n_local, counts.data_ptr(), offsets.data_ptr(), pos.data_ptr(),
+                               total.data_ptr(), pad, torch.cuda.current_stream().cuda_stream), "fb_moe_plan")
+    torch.cuda.synchronize()
+    flat = idx.flatten().cpu().tolist()
+    want_cnt = [0] * n_local
+    want_rank = []
+    for e in flat:
+        l = e - first
+        if 0 <= l < n_local:
+            want_rank.append((l, want_cnt[l]))
+            want_cnt[l] += 1
+        else:
+            want_rank.append(None)
+    off, acc = [], 0
+    for c in want_cnt:
+        off.append(acc)
+        acc += (c + pad - 1) // pad * pad
+    assert counts.cpu().tolist() == want_cnt and offsets.cpu().tolist() == off and int(total) == acc
+    assert pos.cpu().tolist() == [-1 if r is None else off[r[0]] + r[1] for r in want_rank]
+
+
 @pytest.mark.parametrize("swiglu", [False, True])
 @pytest.mark.parametrize("tiles", [0, 3, 4, 8])
 def test_moe_grouped_fp8_tiles_per_cta(tiles, swiglu):
