@@ -82,6 +82,117 @@ static cudaError_t launch_smallm(const CUtensorMap& tmW, const CUtensorMap& tmX,
   return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p);
 }
 
+// Router projection of a mixture-of-experts layer with the expert selection as its epilogue (up to 128 experts = one weight
+// tile): the k-split partial tiles are reduced by token rows, a warp owns a token and a lane four consecutive experts, then
+// scores (softmax or sigmoid), selection bias, top-k with ties to the lower index, optional renormalisation -- what the
+// separate launch after the router GEMM does (route_topk_kernel), on the fp32 logits before they ever reach memory.
+struct RouteEpilogueParams {
+  int* out_idx; float* out_w; const float* sel_bias;
+  int E, topk, score_mode /*0 softmax 1 sigmoid 2 none*/, renorm;
+  float route_scale;
+};
+
+template <bool BF16>
+struct RouteEpilogue {
+  RouteEpilogueParams r;
+  __device__ __forceinline__ void operator()(const GemmParams& p, uint8_t* smem, int split, int nsplit, int n_tile) const {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const uint32_t P_addr = smem_u32(smem);
+    const int rows_per = (p.M + nsplit - 1) / nsplit;
+    const int r0 = split * rows_per;
+    int r1 = r0 + rows_per; if (r1 > p.M) r1 = p.M;
+    const int e0 = lane * 4;
+    for (int j = r0 + warp; j < r1; j += nwarps) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < nsplit; ++s) {
+        const float4 v = ld_dsmem_f4(mapa_u32(P_addr + (uint32_t)(j * 128 + e0) * 4u, (uint32_t)s));
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      float sc[4] = {acc.x, acc.y, acc.z, acc.w}, sel[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) if (e0 + i >= r.E) sc[i] = -INFINITY;
+      if (r.score_mode == 0) {
+        float mx = fmaxf(fmaxf(sc[0], sc[1]), fmaxf(sc[2], sc[3]));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { sc[i] = e0 + i < r.E ? __expf(sc[i] - mx) : 0.f; sum += sc[i]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[i] /= sum;
+      } else if (r.score_mode == 1) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sc[i] = 1.f / (1.f + __expf(-sc[i]));
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sel[i] = e0 + i < r.E ? sc[i] + (r.sel_bias ? r.sel_bias[e0 + i] : 0.f) : -INFINITY;
+      float wsum = 0.f, my_w = 0.f;
+      int my_i = 0;
+      for (int k = 0; k < r.topk; ++k) {
+        float bv = -INFINITY, bs = 0.f;
+        int bi = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (e0 + i < r.E && (sel[i] > bv || (sel[i] == bv && e0 + i < bi))) { bv = sel[i]; bi = e0 + i; bs = sc[i]; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, bv, o), os = __shfl_xor_sync(0xffffffffu, bs, o);
+          const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+          if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; bs = os; }
+        }
+        if ((bi >> 2) == lane) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) if ((bi & 3) == i) sel[i] = -INFINITY;      // out of the later rounds
+        }
+        wsum += bs;
+        if (lane == k) { my_w = bs; my_i = bi; }
+      }
+      if (lane < r.topk) {
+        float w = my_w;
+        if (r.renorm) w = w / (wsum + 1e-20f);
+        r.out_idx[(size_t)j * r.topk + lane] = my_i;
+        r.out_w[(size_t)j * r.topk + lane] = w * r.route_scale;
+      }
+    }
+  }
+};
+
+template <int MPAD, bool BF16>
+__global__ void __launch_bounds__(192, 1)
+gemm_route_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const GemmParams p,
+                  const RouteEpilogueParams rp) {
+  uint32_t tmem_base;
+  RouteEpilogue<BF16> epi{rp};
+  gemm_smallm_device<MPAD, BF16, 1, RouteEpilogue<BF16>>(tmW, tmX, p, tmem_base, KID_GEMM_SMALLM_PLAIN, epi);
+  if ((threadIdx.x >> 5) == 1) tmem_dealloc(tmem_base, SmallMCfg<MPAD, 1>::TMEM_COLS);
+}
+template <int MPAD, bool BF16>
+static cudaError_t launch_route(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const RouteEpilogueParams& rp,
+                                int nsplit, cudaStream_t stream) {
+  using Cfg = SmallMCfg<MPAD, 1>;
+  auto kern = gemm_route_kernel<MPAD, BF16>;
+  static DeviceOnce configured;
+  if (configured.need()) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(nsplit, 1, 1);
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = nsplit;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = add_pdl_attr(attr, 1);
+  return cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p, rp);
+}
+
 template <int MPAD, bool BF16, int OCC = 1>
 static cudaError_t launch_qkv_post(const CUtensorMap& tmW, const CUtensorMap& tmX, const GemmParams& p, const QkvEpilogueParams& qp,
                                    int nsplit, int n_tiles, cudaStream_t stream) {
@@ -153,6 +264,40 @@ extern "C" int fb_gemm_pick_split(int M, int N, int K, int slots) {
 extern "C" int fb_gemm_16bit_wait(const void* X, const void* W, void* out, const void* bias, const void* residual, int M, int N,
                                   int K, int ldx, int ldw, int ld_out, int ld_res, int dtype, int flags, int nsplit,
                                   const void* wait_cnt, const void* wait_expect, void* stream_);
+
+// Router GEMM + expert selection in one launch: X [M, K] 16-bit, W [E, K] 16-bit (E <= 128), M <= 128.
+extern "C" int fb_gemm_route(const void* X, const void* W, int M, int E, int K, int ldx, int ldw, int dtype, const float* sel_bias,
+                             int* out_idx, float* out_w, int topk, int score_mode, int renorm, float route_scale, void* stream_) {
+  using namespace fb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0) return 0;
+  if (M > 128 || E <= 0 || E > 128 || K % 64 != 0 || (dtype != 0 && dtype != 1) || topk <= 0 || topk > 32 || topk > E) return -1;
+  GemmParams p;
+  p.out = nullptr; p.bias = nullptr; p.residual = nullptr;
+  p.M = M; p.N = E; p.K = K; p.ld_out = 0; p.ld_res = 0;
+  p.kb_total = K / 64;
+  p.flags = 0;
+  p.scatter_tp = 0; p.scatter_rows = 1; p.scatter_rank = 0; p.w_row0 = 0; p.x_row0 = 0;
+  for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
+  const bool bf16 = dtype == 1;
+  const int mpad = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+  int nsplit = 8;
+  while (nsplit > 1 && p.kb_total / nsplit < 2) nsplit >>= 1;          // at least two k blocks per CTA
+  p.kb_per_split = (p.kb_total + nsplit - 1) / nsplit;
+  p.idesc = make_idesc(bf16 ? 1 : 0, bf16 ? 1 : 0, 0, 0, 128, mpad);
+  CUtensorMap tmW, tmX;
+  if (!make_tmap_2d(&tmW, W, E, K, ldw, 128, 64, 2, 3)) return -2;
+  if (!make_tmap_2d(&tmX, X, M, K, ldx, mpad, 64, 2, 3)) return -2;
+  RouteEpilogueParams rp{out_idx, out_w, sel_bias, E, topk, score_mode, renorm, route_scale};
+#define FB_RT(MP) return (int)(bf16 ? launch_route<MP, true>(tmW, tmX, p, rp, nsplit, stream) : launch_route<MP, false>(tmW, tmX, p, rp, nsplit, stream));
+  switch (mpad) {
+    case 16: FB_RT(16)
+    case 32: FB_RT(32)
+    case 64: FB_RT(64)
+    default: FB_RT(128)
+  }
+#undef FB_RT
+}
 
 extern "C" int fb_gemm_16bit(const void* X, const void* W, void* out, const void* bias, const void* residual, int M, int N,
                              int K, int ldx, int ldw, int ld_out, int ld_res, int dtype, int flags, int nsplit, void* stream_) {

@@ -617,15 +617,25 @@ class DecoderModel:
                 act = self._glu(lw.gate_up(x), c.hidden_act, lw.gate_up.interleaved)
             return self._row_parallel_norm(lw.down, act, residual, next_ln, lw.post_ln, consumer)
         # ---- mixture of experts ----
-        logits = self._router_logits(lw, x)
-        if lw.router_logit_bias is not None:
-            logits = logits + lw.router_logit_bias
-        if c.route_group_top1:
-            idx, wts = MOE.route_group_top1(logits, c.num_experts_per_tok, lw.router_scale)
+        fused_route = False
+        if x.is_cuda and lw.router_logit_bias is None and not c.route_group_top1 and x.dtype in (torch.float16, torch.bfloat16):
+            if lw.router_16 is None and lw.router.shape[0] % 8 == 0:
+                lw.router_16 = lw.router.to(x.dtype).contiguous()
+            fused_route = MOE.route_fused_ok(x, lw.router_16, c.num_experts_per_tok, c.n_group, c.topk_group)
+        if fused_route:
+            # decode-sized batch, one weight tile of experts: the router GEMM selects the experts in its epilogue
+            idx, wts = MOE.route_fused(x, lw.router_16, lw.router_bias, c.num_experts_per_tok,
+                                       0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.routed_scaling_factor)
         else:
-            idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
-                                      0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
-                                      c.routed_scaling_factor)
+            logits = self._router_logits(lw, x)
+            if lw.router_logit_bias is not None:
+                logits = logits + lw.router_logit_bias
+            if c.route_group_top1:
+                idx, wts = MOE.route_group_top1(logits, c.num_experts_per_tok, lw.router_scale)
+            else:
+                idx, wts = MOE.route_topk(logits, lw.router_bias, c.num_experts_per_tok,
+                                          0 if c.scoring_func == "softmax" else 1, c.norm_topk_prob, c.n_group, c.topk_group,
+                                          c.routed_scaling_factor)
         if self._beta != 1.0:
             wts = wts * self._beta
         shared = None

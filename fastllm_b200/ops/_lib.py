@@ -26,6 +26,7 @@ _KERNEL_SIGS = {
     "fb_gemm_16bit": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P],
     "fb_gemm_16bit_wait": [P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, P, P, P],
     "fb_gemm_qkv_post": [P, P, P, I, I, I, I, I, I, P, P, P, I, P, P, P, P, P, P, P, P, I, I, I, I, F, F, P],
+    "fb_gemm_route": [P, P, I, I, I, I, I, I, P, P, P, I, I, I, F, P],
     "fb_gemm_16bit_batched": [P, P, P, I, I, I, I, I, I, I, I, I, I, P],
     "fb_mla_post": [P, I, P, I, P, I, P, P, P, P, P, P, I, I, I, I, I, I, LL, F, I, P],
     "fb_gemm_pick_split": [I, I, I, I],

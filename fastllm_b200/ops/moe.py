@@ -60,6 +60,34 @@ def route_topk(logits, bias, topk, score_mode, renorm, n_group=1, topk_group=1, 
     return idx, w
 
 
+# router projection and expert selection in one launch (csrc/gemm_bf16.cu::gemm_route_kernel), FB_ROUTE_FUSED=1.  Off by default:
+# measured on Qwen3-30B-A3B (128 rows, 128 experts, top-8) the one-launch form is 0.2 ms per step SLOWER than GEMM + selection
+# kernel (12.33 against 11.98 - 12.21 ms): the selection then runs on the eight CTAs of the GEMM's cluster, 16 tokens each,
+# instead of on 32 CTAs that start under the GEMM's tail.
+ROUTE_FUSED = __import__("os").environ.get("FB_ROUTE_FUSED", "0") == "1"
+
+
+def route_fused_ok(x, router_16, topk, n_group=1, topk_group=1) -> bool:
+    """The fused kernel covers decode-sized batches (<= 128 rows) of up to 128 experts without group-limited selection."""
+    return bool(ROUTE_FUSED and x.is_cuda and x.dim() == 2 and x.dtype in (torch.float16, torch.bfloat16) and router_16 is not None
+                and router_16.dtype == x.dtype and x.shape[0] <= 128 and router_16.shape[0] <= 128 and x.shape[1] % 64 == 0
+                and topk <= min(32, router_16.shape[0]) and not (n_group > 1 and topk_group < n_group)
+                and x.stride(1) == 1 and router_16.is_contiguous())
+
+
+def route_fused(x, router_16, bias, topk, score_mode, renorm, route_scale=1.0):
+    """``route_topk(x @ router^T, ...)`` as one kernel: (expert index int32 ``[M, topk]``, weight fp32 ``[M, topk]``)."""
+    M, K = x.shape
+    E = router_16.shape[0]
+    idx = torch.empty((M, topk), device=x.device, dtype=torch.int32)
+    w = torch.empty((M, topk), device=x.device, dtype=torch.float32)
+    b = bias.float().contiguous() if bias is not None else None
+    rc = _lib.kernels().fb_gemm_route(_ptr(x), _ptr(router_16), M, E, K, x.stride(0), K, 1 if x.dtype == torch.bfloat16 else 0, _ptr(b),
+                                      _ptr(idx), _ptr(w), topk, score_mode, 1 if renorm else 0, float(route_scale), _stream())
+    _lib.check(rc, "fb_gemm_route")
+    return idx, w
+
+
 def route_group_top1(logits, groups: int, expert_scale=None):
     """Mixture of grouped experts (Pangu Pro MoE): the experts form ``groups`` equal, contiguous groups and the best-scoring
     expert of every group is taken; weight = softmax score (over all experts) x the expert's learned scale, not renormalised.

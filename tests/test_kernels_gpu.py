@@ -683,6 +683,37 @@ def test_moe_grouped_fp8_native_matches_w8a16():
     assert rel < 0.08, rel
 
 
+@pytest.mark.parametrize("M,E,K,topk,mode,renorm,bias", [(128, 128, 2048, 8, 0, True, False), (37, 64, 512, 6, 1, True, True),
+                                                         (1, 128, 4096, 8, 0, False, False), (16, 8, 256, 2, 0, True, False),
+                                                         (100, 96, 1024, 4, 1, False, True)])
+def test_router_gemm_with_selection_epilogue(M, E, K, topk, mode, renorm, bias):
+    """Router projection + expert selection in one launch against the two-launch path (tensor-core GEMM to fp32 logits, then the
+    selection kernel) and against the PyTorch definition on the same logits."""
+    from fastllm_b200.ops import moe as MOE
+
+    torch.manual_seed(M + E)
+    x = torch.randn(M, K, device=DEV).bfloat16()
+    w = (torch.randn(E, K, device=DEV) * 0.05).bfloat16()
+    b = torch.randn(E, device=DEV) * 0.1 if bias else None
+    idx, wt = MOE.route_fused(x, w, b, topk, mode, renorm, 2.5)
+    torch.cuda.synchronize()
+    _lib.check_device_errors()
+    logits = B.linear(x, w, out_f32=True)
+    idx2, wt2 = MOE.route_topk(logits, b, topk, mode, renorm, 1, 1, 2.5)
+    idx3, wt3 = MOE.route_topk_ref(x.float() @ w.float().t(), b, topk, mode, renorm, 1, 1, 2.5)
+    # the k-split partial sums are added in another order than the unfused GEMM's: near-ties may swap, so compare as sets
+    # with a small allowance and the weights of the common experts
+    same = sum(len(set(a.tolist()) & set(c.tolist())) for a, c in zip(idx.cpu(), idx2.cpu()))
+    assert same >= 0.98 * M * topk, same
+    same3 = sum(len(set(a.tolist()) & set(c.tolist())) for a, c in zip(idx.cpu(), idx3.cpu()))
+    assert same3 >= 0.97 * M * topk, same3
+    d1 = torch.zeros(M, E, device=DEV).scatter_(1, idx.long(), wt)
+    d2 = torch.zeros(M, E, device=DEV).scatter_(1, idx2.long(), wt2)
+    rows = ((d1 != 0) == (d2 != 0)).all(dim=1)              # tokens whose selection is the same in both paths
+    assert rows.float().mean() > 0.9
+    assert torch.allclose(d1[rows], d2[rows], rtol=2e-3, atol=1e-5)
+
+
 @pytest.mark.parametrize("T,topk,E,first,n_local,pad", [(128, 8, 128, 0, 128, 4), (37, 2, 8, 0, 8, 4), (100, 8, 256, 64, 32, 16),
                                                         (512, 8, 64, 0, 64, 4), (1, 6, 160, 0, 160, 1), (700, 8, 16, 8, 8, 4), (400, 8, 128, 0, 128, 4)])
 def test_moe_plan_matches_definition(T, topk, E, first, n_local, pad):
