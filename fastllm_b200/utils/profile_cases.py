@@ -250,8 +250,11 @@ def model_kernel_table(model="qwen3-30b-a3b", wdtype="fp8", batch=128, prompt=51
         eng.step()
     torch.cuda.synchronize()
     _lib.start_profile()
+    torch.cuda.profiler.start()          # `ncu --profile-from-start off` then sees the decode steps only
     for _ in range(steps):
         eng.step()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     print(_lib.stop_profile().format())
 
 
